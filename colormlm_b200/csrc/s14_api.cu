@@ -1,0 +1,969 @@
+// C ABI of the S14 MoE path (include/polaris_s14_cuda.h): contexts, operator
+// bind/cmd pairs, the fused layer, router, LM head, the page pool and the route
+// page transaction.  No CPU fallback: every cmd_ call launches a CUDA kernel.
+#include <algorithm>
+#include <cmath>
+#include <cstring>
+#include <memory>
+#include <new>
+#include <string>
+#include <vector>
+
+#include "s14_host.hpp"
+#include "s14_internal.h"
+
+using namespace s14;
+
+// ---- error plumbing ---------------------------------------------------------
+
+static thread_local std::string g_last_error;
+
+static int32_t fail(int32_t code, const std::string &msg) {
+    g_last_error = msg;
+    return code;
+}
+
+static int32_t cuda_fail(cudaError_t e, const char *what) {
+    return fail(S14_ERR_CUDA, std::string(what) + ": " + cudaGetErrorString(e));
+}
+
+#define S14_TRY try {
+#define S14_CATCH                                                      \
+    }                                                                  \
+    catch (const ContractError &e) { return fail(S14_ERR_CONTRACT, e.what()); } \
+    catch (const PoolError &e) { return fail(S14_ERR_POOL, e.what()); }         \
+    catch (const CodeError &e) { return fail(S14_ERR_CODE, e.what()); }         \
+    catch (const std::bad_alloc &) { return fail(S14_ERR_CONTRACT, "out of host memory"); } \
+    catch (const std::exception &e) { return fail(S14_ERR_CONTRACT, e.what()); }
+
+#define CUDA_OK(call)                                      \
+    do {                                                   \
+        cudaError_t _e = (call);                           \
+        if (_e != cudaSuccess) return cuda_fail(_e, #call); \
+    } while (0)
+
+extern "C" const char *s14_last_error(void) { return g_last_error.c_str(); }
+
+// ---- context ----------------------------------------------------------------
+
+static constexpr uint32_t kMaxDim = 4096;  // largest hidden / intermediate of the fused layer
+
+struct s14_ctx {
+    int device = 0;
+    int sm_count = 0;
+    uint32_t mode = S14_ACCUM_PAIRWISE;
+    cudaStream_t compute = nullptr, copy = nullptr;
+    float *h = nullptr;       // [kMaxJobs, kMaxDim] activations between up and down
+    float *d = nullptr;       // [kMaxJobs, kMaxDim] per-job down outputs before the mix
+    float *scores = nullptr;  // [kMaxTokens, 256]
+    float *select = nullptr;  // [kMaxTokens, 256]
+    JobTable *dev_table = nullptr;
+    float *x_stage = nullptr, *y_stage = nullptr;  // [kMaxTokens, kMaxDim]
+    uint32_t *status = nullptr;
+    uint64_t launches = 0;
+};
+
+static cudaStream_t stream_of(s14_ctx *ctx, void *stream) {
+    return stream ? (cudaStream_t)stream : ctx->compute;
+}
+
+extern "C" int32_t s14_ctx_create(int32_t device, s14_ctx **out) {
+    if (!out) return fail(S14_ERR_CONTRACT, "s14_ctx_create: out is NULL");
+    *out = nullptr;
+    int count = 0;
+    CUDA_OK(cudaGetDeviceCount(&count));
+    if (device < 0 || device >= count)
+        return fail(S14_ERR_CONTRACT, "s14_ctx_create: no CUDA device " + std::to_string(device));
+    CUDA_OK(cudaSetDevice(device));
+    cudaDeviceProp prop;
+    CUDA_OK(cudaGetDeviceProperties(&prop, device));
+    if (prop.major < 10)
+        return fail(S14_ERR_CONTRACT, "s14_ctx_create: the kernels are built for sm_100a only; device is sm_" +
+                                          std::to_string(prop.major * 10 + prop.minor));
+    std::unique_ptr<s14_ctx> ctx(new s14_ctx());
+    ctx->device = device;
+    ctx->sm_count = prop.multiProcessorCount;
+    CUDA_OK(cudaStreamCreateWithFlags(&ctx->compute, cudaStreamNonBlocking));
+    CUDA_OK(cudaStreamCreateWithFlags(&ctx->copy, cudaStreamNonBlocking));
+    CUDA_OK(cudaMalloc(&ctx->h, sizeof(float) * kMaxJobs * kMaxDim));
+    CUDA_OK(cudaMalloc(&ctx->d, sizeof(float) * kMaxJobs * kMaxDim));
+    CUDA_OK(cudaMalloc(&ctx->scores, sizeof(float) * kMaxTokens * S14_N_ROUTED_EXPERTS));
+    CUDA_OK(cudaMalloc(&ctx->select, sizeof(float) * kMaxTokens * S14_N_ROUTED_EXPERTS));
+    CUDA_OK(cudaMalloc(&ctx->dev_table, sizeof(JobTable)));
+    CUDA_OK(cudaMalloc(&ctx->x_stage, sizeof(float) * kMaxTokens * kMaxDim));
+    CUDA_OK(cudaMalloc(&ctx->y_stage, sizeof(float) * kMaxTokens * kMaxDim));
+    CUDA_OK(cudaMalloc(&ctx->status, sizeof(uint32_t)));
+    CUDA_OK(cudaMemset(ctx->status, 0, sizeof(uint32_t)));
+    *out = ctx.release();
+    return S14_OK;
+}
+
+extern "C" int32_t s14_ctx_destroy(s14_ctx *ctx) {
+    if (!ctx) return S14_OK;
+    cudaSetDevice(ctx->device);
+    cudaStreamSynchronize(ctx->compute);
+    cudaStreamSynchronize(ctx->copy);
+    cudaFree(ctx->h);
+    cudaFree(ctx->d);
+    cudaFree(ctx->scores);
+    cudaFree(ctx->select);
+    cudaFree(ctx->dev_table);
+    cudaFree(ctx->x_stage);
+    cudaFree(ctx->y_stage);
+    cudaFree(ctx->status);
+    cudaStreamDestroy(ctx->compute);
+    cudaStreamDestroy(ctx->copy);
+    delete ctx;
+    return S14_OK;
+}
+
+extern "C" void *s14_ctx_compute_stream(s14_ctx *ctx) { return ctx ? ctx->compute : nullptr; }
+extern "C" void *s14_ctx_copy_stream(s14_ctx *ctx) { return ctx ? ctx->copy : nullptr; }
+
+extern "C" int32_t s14_ctx_synchronize(s14_ctx *ctx) {
+    if (!ctx) return fail(S14_ERR_CONTRACT, "ctx is NULL");
+    CUDA_OK(cudaStreamSynchronize(ctx->compute));
+    CUDA_OK(cudaStreamSynchronize(ctx->copy));
+    return S14_OK;
+}
+
+extern "C" int32_t s14_ctx_set_accumulation(s14_ctx *ctx, uint32_t mode) {
+    if (!ctx) return fail(S14_ERR_CONTRACT, "ctx is NULL");
+    if (mode != S14_ACCUM_PAIRWISE && mode != S14_ACCUM_REFERENCE)
+        return fail(S14_ERR_CONTRACT, "unknown accumulation mode " + std::to_string(mode));
+    ctx->mode = mode;
+    return S14_OK;
+}
+
+extern "C" uint32_t s14_ctx_accumulation(const s14_ctx *ctx) { return ctx ? ctx->mode : 0; }
+extern "C" int32_t s14_ctx_sm_count(const s14_ctx *ctx) { return ctx ? ctx->sm_count : 0; }
+extern "C" uint64_t s14_ctx_launch_count(const s14_ctx *ctx) { return ctx ? ctx->launches : 0; }
+
+extern "C" int32_t s14_ctx_device_status(s14_ctx *ctx, uint32_t *status) {
+    if (!ctx || !status) return fail(S14_ERR_CONTRACT, "ctx or status is NULL");
+    CUDA_OK(cudaStreamSynchronize(ctx->compute));
+    CUDA_OK(cudaMemcpy(status, ctx->status, sizeof(uint32_t), cudaMemcpyDeviceToHost));
+    if (*status != 0) CUDA_OK(cudaMemset(ctx->status, 0, sizeof(uint32_t)));
+    return S14_OK;
+}
+
+// ---- byte contracts -----------------------------------------------------------
+
+static S14MatvecShape shape_of(s14_matvec_shape s) {
+    S14MatvecShape out;
+    out.n = s.n;
+    out.k = s.k;
+    return out;
+}
+
+extern "C" int32_t s14_shape_new(uint32_t n, uint32_t k, s14_matvec_shape *out) {
+    S14_TRY
+    const S14MatvecShape s = S14MatvecShape::make(n, k);
+    if (out) {
+        out->n = s.n;
+        out->k = s.k;
+    }
+    return S14_OK;
+    S14_CATCH
+}
+
+extern "C" int32_t s14_shape_validate_mxfp4(s14_matvec_shape shape) {
+    S14_TRY
+    shape_of(shape).validate_mxfp4();
+    return S14_OK;
+    S14_CATCH
+}
+
+extern "C" int32_t s14_shape_validate_fp8(s14_matvec_shape shape) {
+    S14_TRY
+    shape_of(shape).validate_fp8();
+    return S14_OK;
+    S14_CATCH
+}
+
+#define SHAPE_BYTES_FN(name, method)                                              \
+    extern "C" int32_t name(s14_matvec_shape shape, uint64_t *out) {              \
+        S14_TRY                                                                   \
+        if (!out) throw ContractError(#name ": out is NULL");                     \
+        *out = shape_of(shape).method();                                          \
+        return S14_OK;                                                            \
+        S14_CATCH                                                                 \
+    }
+SHAPE_BYTES_FN(s14_shape_fp32_input_bytes, fp32_input_bytes)
+SHAPE_BYTES_FN(s14_shape_fp32_output_bytes, fp32_output_bytes)
+SHAPE_BYTES_FN(s14_shape_mxfp4_weight_bytes, mxfp4_weight_bytes)
+SHAPE_BYTES_FN(s14_shape_mxfp4_scale_bytes, mxfp4_scale_bytes)
+SHAPE_BYTES_FN(s14_shape_fp8_weight_bytes, fp8_weight_bytes)
+SHAPE_BYTES_FN(s14_shape_fp8_scale_bytes, fp8_scale_bytes)
+
+extern "C" int32_t s14_validate_ue8m0_codes(const uint8_t *codes, uint64_t len, uint64_t *bad_index) {
+    try {
+        validate_ue8m0_codes(codes, len);
+    } catch (const CodeError &e) {
+        if (bad_index) *bad_index = e.index;
+        return fail(S14_ERR_CODE, e.what());
+    }
+    return S14_OK;
+}
+
+extern "C" int32_t s14_validate_e4m3fn_codes(const uint8_t *codes, uint64_t len, uint64_t *bad_index) {
+    try {
+        validate_e4m3fn_codes(codes, len);
+    } catch (const CodeError &e) {
+        if (bad_index) *bad_index = e.index;
+        return fail(S14_ERR_CODE, e.what());
+    }
+    return S14_OK;
+}
+
+// ---- primitive operators --------------------------------------------------------
+
+static void require_capacity(const s14_buffer *b, uint64_t required, const char *label) {
+    if (!b || !b->ptr) throw ContractError(std::string(label) + " buffer is NULL");
+    if (b->size < required)
+        throw ContractError(std::string(label) + " buffer is " + std::to_string(b->size) +
+                            " B, requires at least " + std::to_string(required) + " B");
+}
+
+static void require_aligned(const void *p, uint64_t a, const char *label) {
+    if (reinterpret_cast<uintptr_t>(p) % a != 0)
+        throw ContractError(std::string(label) + " must be aligned to " + std::to_string(a) + " bytes");
+}
+
+extern "C" int32_t s14_bind_mxfp4(s14_ctx *ctx, s14_matvec_shape shape, const s14_buffer *x,
+                                  const s14_buffer *packed_weight, const s14_buffer *weight_scale,
+                                  const s14_buffer *y, s14_mxfp4_dispatch *out) {
+    S14_TRY
+    if (!ctx || !out) throw ContractError("s14_bind_mxfp4: ctx or out is NULL");
+    const S14MatvecShape s = shape_of(shape).validate_mxfp4();
+    require_capacity(x, s.fp32_input_bytes(), "S14 MXFP4 input");
+    require_capacity(packed_weight, storage_bytes(s.mxfp4_weight_bytes()), "S14 MXFP4 weight");
+    require_capacity(weight_scale, storage_bytes(s.mxfp4_scale_bytes()), "S14 MXFP4 scale");
+    require_capacity(y, s.fp32_output_bytes(), "S14 MXFP4 output");
+    require_aligned(x->ptr, 16, "S14 MXFP4 input");
+    require_aligned(packed_weight->ptr, 16, "S14 MXFP4 weight");
+    require_aligned(weight_scale->ptr, 4, "S14 MXFP4 scale");
+    out->shape = shape;
+    out->x = (const float *)x->ptr;
+    out->packed_weight = (const uint8_t *)packed_weight->ptr;
+    out->weight_scale = (const uint8_t *)weight_scale->ptr;
+    out->y = (float *)y->ptr;
+    return S14_OK;
+    S14_CATCH
+}
+
+extern "C" int32_t s14_cmd_mxfp4_matvec(s14_ctx *ctx, void *stream, const s14_mxfp4_dispatch *dsp) {
+    if (!ctx || !dsp) return fail(S14_ERR_CONTRACT, "s14_cmd_mxfp4_matvec: NULL argument");
+    CUDA_OK(launch_mxfp4_matvec(stream_of(ctx, stream), ctx->mode, ctx->sm_count, dsp->x,
+                                dsp->packed_weight, dsp->weight_scale, dsp->y, dsp->shape.n,
+                                dsp->shape.k));
+    ctx->launches += 1;
+    return S14_OK;
+}
+
+extern "C" int32_t s14_bind_fp8_ex(s14_ctx *ctx, s14_matvec_shape shape, uint32_t scale_format,
+                                   uint32_t n_tokens, const s14_buffer *x, const s14_buffer *weight,
+                                   const s14_buffer *weight_scale, const s14_buffer *y,
+                                   s14_fp8_dispatch *out) {
+    S14_TRY
+    if (!ctx || !out) throw ContractError("s14_bind_fp8: ctx or out is NULL");
+    const S14MatvecShape s = shape_of(shape).validate_fp8();
+    if (scale_format != S14_SCALE_UE8M0 && scale_format != S14_SCALE_F32)
+        throw ContractError("S14 FP8 scale format must be UE8M0 or F32");
+    if (n_tokens == 0 || n_tokens > kMaxTokens)
+        throw ContractError("S14 FP8 matvec takes 1..8 tokens per weight pass");
+    const uint64_t scale_elem = scale_format == S14_SCALE_F32 ? 4 : 1;
+    require_capacity(x, s.fp32_input_bytes() * n_tokens, "S14 FP8 input");
+    require_capacity(weight, storage_bytes(s.fp8_weight_bytes()), "S14 FP8 weight");
+    require_capacity(weight_scale, storage_bytes(s.fp8_scale_bytes() * scale_elem), "S14 FP8 scale");
+    require_capacity(y, s.fp32_output_bytes() * n_tokens, "S14 FP8 output");
+    if (scale_format == S14_SCALE_F32) require_aligned(weight_scale->ptr, 4, "S14 FP8 scale");
+    require_aligned(x->ptr, 4, "S14 FP8 input");
+    out->shape = shape;
+    out->scale_format = scale_format;
+    out->n_tokens = n_tokens;
+    out->x = (const float *)x->ptr;
+    out->weight = (const uint8_t *)weight->ptr;
+    out->weight_scale = weight_scale->ptr;
+    out->y = (float *)y->ptr;
+    return S14_OK;
+    S14_CATCH
+}
+
+extern "C" int32_t s14_bind_fp8(s14_ctx *ctx, s14_matvec_shape shape, const s14_buffer *x,
+                                const s14_buffer *weight, const s14_buffer *weight_scale,
+                                const s14_buffer *y, s14_fp8_dispatch *out) {
+    return s14_bind_fp8_ex(ctx, shape, S14_SCALE_UE8M0, 1, x, weight, weight_scale, y, out);
+}
+
+extern "C" int32_t s14_cmd_fp8_matvec(s14_ctx *ctx, void *stream, const s14_fp8_dispatch *dsp) {
+    if (!ctx || !dsp) return fail(S14_ERR_CONTRACT, "s14_cmd_fp8_matvec: NULL argument");
+    CUDA_OK(launch_fp8_matvec(stream_of(ctx, stream), ctx->mode, ctx->sm_count, dsp->scale_format,
+                              dsp->n_tokens, dsp->x, dsp->weight, dsp->weight_scale, dsp->y,
+                              dsp->shape.n, dsp->shape.k));
+    ctx->launches += 1;
+    return S14_OK;
+}
+
+extern "C" int32_t s14_bind_swiglu_limit(s14_ctx *ctx, uint32_t n, const s14_buffer *gate,
+                                         const s14_buffer *up, const s14_buffer *y,
+                                         s14_swiglu_limit_dispatch *out) {
+    S14_TRY
+    if (!ctx || !out) throw ContractError("s14_bind_swiglu_limit: ctx or out is NULL");
+    if (n == 0) throw ContractError("S14 SwiGLU requires non-zero length");
+    const uint64_t bytes = (uint64_t)n * 4;
+    require_capacity(gate, bytes, "S14 SwiGLU gate");
+    require_capacity(up, bytes, "S14 SwiGLU up");
+    require_capacity(y, bytes, "S14 SwiGLU output");
+    out->n = n;
+    out->gate = (const float *)gate->ptr;
+    out->up = (const float *)up->ptr;
+    out->y = (float *)y->ptr;
+    return S14_OK;
+    S14_CATCH
+}
+
+extern "C" int32_t s14_cmd_swiglu_limit(s14_ctx *ctx, void *stream,
+                                        const s14_swiglu_limit_dispatch *dsp) {
+    if (!ctx || !dsp) return fail(S14_ERR_CONTRACT, "s14_cmd_swiglu_limit: NULL argument");
+    CUDA_OK(launch_swiglu_limit(stream_of(ctx, stream), dsp->gate, dsp->up, dsp->y, dsp->n));
+    ctx->launches += 1;
+    return S14_OK;
+}
+
+extern "C" int32_t s14_bind_route_mix(s14_ctx *ctx, uint32_t n, float route_weight,
+                                      const s14_buffer *expert, const s14_buffer *routed,
+                                      s14_route_mix_dispatch *out) {
+    S14_TRY
+    if (!ctx || !out) throw ContractError("s14_bind_route_mix: ctx or out is NULL");
+    if (n == 0 || !std::isfinite(route_weight) || route_weight < 0.0f)
+        throw ContractError("S14 route mix requires non-zero length and finite non-negative weight");
+    const uint64_t bytes = (uint64_t)n * 4;
+    require_capacity(expert, bytes, "S14 route mix expert");
+    require_capacity(routed, bytes, "S14 route mix output");
+    out->n = n;
+    out->route_weight = route_weight;
+    out->expert = (const float *)expert->ptr;
+    out->routed = (float *)routed->ptr;
+    return S14_OK;
+    S14_CATCH
+}
+
+extern "C" int32_t s14_cmd_route_mix(s14_ctx *ctx, void *stream, const s14_route_mix_dispatch *dsp) {
+    if (!ctx || !dsp) return fail(S14_ERR_CONTRACT, "s14_cmd_route_mix: NULL argument");
+    CUDA_OK(launch_route_mix(stream_of(ctx, stream), dsp->expert, dsp->routed, dsp->n,
+                             dsp->route_weight));
+    ctx->launches += 1;
+    return S14_OK;
+}
+
+extern "C" int32_t s14_bind_moe_accumulate(s14_ctx *ctx, uint32_t n, float weight,
+                                           const s14_buffer *expert, const s14_buffer *accumulator,
+                                           s14_moe_accumulate_dispatch *out) {
+    S14_TRY
+    if (!ctx || !out) throw ContractError("s14_bind_moe_accumulate: ctx or out is NULL");
+    if (n == 0 || !std::isfinite(weight) || weight < 0.0f)
+        throw ContractError("S14 MoE accumulate requires non-zero length and finite non-negative weight");
+    const uint64_t bytes = (uint64_t)n * 4;
+    require_capacity(expert, bytes, "S14 MoE accumulate expert");
+    require_capacity(accumulator, bytes, "S14 MoE accumulator");
+    out->n = n;
+    out->weight = weight;
+    out->expert = (const float *)expert->ptr;
+    out->accumulator = (float *)accumulator->ptr;
+    return S14_OK;
+    S14_CATCH
+}
+
+extern "C" int32_t s14_cmd_moe_accumulate(s14_ctx *ctx, void *stream,
+                                          const s14_moe_accumulate_dispatch *dsp) {
+    if (!ctx || !dsp) return fail(S14_ERR_CONTRACT, "s14_cmd_moe_accumulate: NULL argument");
+    CUDA_OK(launch_moe_accumulate(stream_of(ctx, stream), dsp->expert, dsp->accumulator, dsp->n,
+                                  dsp->weight));
+    ctx->launches += 1;
+    return S14_OK;
+}
+
+// ---- fused layer ------------------------------------------------------------------
+
+static bool fused_dim_ok(uint32_t v) { return v == 1024 || v == 2048 || v == 4096; }
+
+// Groups the (expert, token) pairs so that pairs of one expert are adjacent, shared
+// expert pairs last; token_jobs keeps each token's mix order.
+static void build_job_table(const s14_moe_layer_desc &desc, JobTable &tab) {
+    if (desc.n_tokens == 0 || desc.n_tokens > kMaxTokens)
+        throw ContractError("S14 MoE layer takes 1..8 tokens");
+    if (!fused_dim_ok(desc.hidden) || !fused_dim_ok(desc.inter))
+        throw ContractError("S14 MoE layer: hidden and intermediate must be 1024, 2048 or 4096");
+    if (!desc.routes) throw ContractError("S14 MoE layer: routes is NULL");
+    if (desc.shared_page && desc.shared_kind != S14_PAGE_MXFP4 && desc.shared_kind != S14_PAGE_FP8)
+        throw ContractError("S14 MoE layer: unknown shared page kind");
+    std::memset(&tab, 0, sizeof(tab));
+    struct Pair {
+        uint32_t token, slot;
+        uint16_t expert;
+    };
+    std::vector<Pair> pairs;
+    for (uint32_t t = 0; t < desc.n_tokens; ++t) {
+        const s14_token_route &r = desc.routes[t];
+        if (r.n_routed > S14_EXPERTS_PER_TOKEN)
+            throw ContractError("S14 MoE layer: a token has more than 6 routed experts");
+        if (r.n_routed == 0 && !desc.shared_page)
+            throw ContractError("S14 MoE layer: a token has no expert at all");
+        for (uint32_t j = 0; j < r.n_routed; ++j) {
+            if (!r.pages[j]) throw ContractError("S14 MoE layer: routed page address is NULL");
+            if (reinterpret_cast<uintptr_t>(r.pages[j]) % 16 != 0)
+                throw ContractError("S14 MoE layer: page addresses must be 16-byte aligned");
+            if (!std::isfinite(r.weights[j]) || r.weights[j] < 0.0f)
+                throw ContractError("S14 MoE layer: route weight must be finite and non-negative");
+            for (uint32_t i = 0; i < j; ++i)
+                if (r.expert_ids[i] == r.expert_ids[j])
+                    throw ContractError("S14 MoE layer: route expert repeated");
+            pairs.push_back({t, j, r.expert_ids[j]});
+        }
+    }
+    // stable order: by expert id, then token
+    std::vector<uint32_t> order(pairs.size());
+    for (uint32_t i = 0; i < order.size(); ++i) order[i] = i;
+    std::stable_sort(order.begin(), order.end(), [&](uint32_t a, uint32_t b) {
+        return pairs[a].expert < pairs[b].expert;
+    });
+    std::vector<std::vector<uint8_t>> per_token(desc.n_tokens,
+                                                std::vector<uint8_t>(S14_EXPERTS_PER_TOKEN + 1, 0xff));
+    uint32_t n = 0;
+    for (uint32_t idx : order) {
+        const Pair &p = pairs[idx];
+        const s14_token_route &r = desc.routes[p.token];
+        Job jb;
+        jb.page = r.pages[p.slot];
+        jb.kind = S14_PAGE_MXFP4;
+        jb.token = p.token;
+        jb.weight = r.weights[p.slot];
+        jb.is_shared = 0;
+        tab.jobs[n] = jb;
+        per_token[p.token][p.slot] = (uint8_t)n;
+        ++n;
+    }
+    if (desc.shared_page) {
+        if (reinterpret_cast<uintptr_t>(desc.shared_page) % 16 != 0)
+            throw ContractError("S14 MoE layer: page addresses must be 16-byte aligned");
+        for (uint32_t t = 0; t < desc.n_tokens; ++t) {
+            Job jb;
+            jb.page = desc.shared_page;
+            jb.kind = desc.shared_kind;
+            jb.token = t;
+            jb.weight = 1.0f;
+            jb.is_shared = 1;
+            tab.jobs[n] = jb;
+            per_token[t][desc.routes[t].n_routed] = (uint8_t)n;
+            ++n;
+        }
+    }
+    tab.n_jobs = n;
+    tab.n_tokens = desc.n_tokens;
+    uint32_t pos = 0;
+    for (uint32_t t = 0; t < desc.n_tokens; ++t) {
+        tab.token_job_begin[t] = pos;
+        const uint32_t cnt = desc.routes[t].n_routed + (desc.shared_page ? 1u : 0u);
+        for (uint32_t j = 0; j < cnt; ++j) tab.token_jobs[pos++] = per_token[t][j];
+    }
+    tab.token_job_begin[desc.n_tokens] = pos;
+}
+
+static int32_t enqueue_layer(s14_ctx *ctx, cudaStream_t st, const s14_moe_layer_desc &desc,
+                             const float *x, float *y) {
+    S14_TRY
+    JobTable tab;
+    build_job_table(desc, tab);
+    if (!x || !y) throw ContractError("S14 MoE layer: x or y is NULL");
+    require_aligned(x, 16, "S14 MoE layer x");
+    cudaError_t err;
+    const int launched = launch_moe_layer(st, ctx->mode, ctx->sm_count, nullptr, tab, tab.n_tokens,
+                                          tab.n_jobs, desc.hidden, desc.inter, x, ctx->h, ctx->d, y,
+                                          &err);
+    ctx->launches += launched;
+    if (err != cudaSuccess) return cuda_fail(err, "S14 MoE layer launch");
+    return S14_OK;
+    S14_CATCH
+}
+
+extern "C" int32_t s14_cmd_moe_layer(s14_ctx *ctx, void *stream, const s14_moe_layer_desc *desc) {
+    if (!ctx || !desc) return fail(S14_ERR_CONTRACT, "s14_cmd_moe_layer: NULL argument");
+    return enqueue_layer(ctx, stream_of(ctx, stream), *desc, desc->x, desc->y);
+}
+
+extern "C" int32_t s14_moe_layer_host(s14_ctx *ctx, const s14_moe_layer_desc *desc,
+                                      const float *host_x, float *host_y) {
+    if (!ctx || !desc || !host_x || !host_y)
+        return fail(S14_ERR_CONTRACT, "s14_moe_layer_host: NULL argument");
+    if (desc->n_tokens == 0 || desc->n_tokens > kMaxTokens || desc->hidden > kMaxDim)
+        return fail(S14_ERR_CONTRACT, "s14_moe_layer_host: token count or hidden size out of range");
+    const size_t bytes = sizeof(float) * desc->n_tokens * desc->hidden;
+    CUDA_OK(cudaMemcpyAsync(ctx->x_stage, host_x, bytes, cudaMemcpyHostToDevice, ctx->compute));
+    const int32_t rc = enqueue_layer(ctx, ctx->compute, *desc, ctx->x_stage, ctx->y_stage);
+    if (rc != S14_OK) return rc;
+    CUDA_OK(cudaMemcpyAsync(host_y, ctx->y_stage, bytes, cudaMemcpyDeviceToHost, ctx->compute));
+    CUDA_OK(cudaStreamSynchronize(ctx->compute));
+    return S14_OK;
+}
+
+static void validate_router(const s14_router_desc &r, bool need_outputs) {
+    if (r.n_experts == 0 || r.n_experts > S14_N_ROUTED_EXPERTS)
+        throw ContractError("S14 router: 1..256 experts");
+    if (r.hidden == 0 || r.hidden % 256 != 0) throw ContractError("S14 router: hidden must be a multiple of 256");
+    if (r.n_tokens == 0 || r.n_tokens > kMaxTokens) throw ContractError("S14 router: 1..8 tokens");
+    if (r.top_k == 0 || r.top_k > 8 || r.top_k > r.n_experts) throw ContractError("S14 router: top_k must be 1..8");
+    if (r.score_fn != S14_SCORE_SIGMOID && r.score_fn != S14_SCORE_SQRT_SOFTPLUS)
+        throw ContractError("S14 router: unknown score function");
+    if (!std::isfinite(r.route_scale) || r.route_scale <= 0.0f)
+        throw ContractError("S14 router: route_scale must be finite and positive");
+    if (!r.x || !r.router_weight_bf16) throw ContractError("S14 router: x or weight is NULL");
+    if (need_outputs && (!r.ids_out || !r.weights_out))
+        throw ContractError("S14 router: ids_out or weights_out is NULL");
+    require_aligned(r.x, 16, "S14 router x");
+    require_aligned(r.router_weight_bf16, 16, "S14 router weight");
+}
+
+extern "C" int32_t s14_cmd_router(s14_ctx *ctx, void *stream, const s14_router_desc *desc) {
+    S14_TRY
+    if (!ctx || !desc) throw ContractError("s14_cmd_router: NULL argument");
+    validate_router(*desc, true);
+    cudaError_t err;
+    ctx->launches += launch_router(stream_of(ctx, stream), *desc, ctx->scores, ctx->select, nullptr,
+                                   nullptr, nullptr, 0, &err);
+    if (err != cudaSuccess) return cuda_fail(err, "S14 router launch");
+    return S14_OK;
+    S14_CATCH
+}
+
+extern "C" int32_t s14_cmd_routed_moe_layer(s14_ctx *ctx, void *stream,
+                                            const s14_routed_layer_desc *desc) {
+    S14_TRY
+    if (!ctx || !desc) throw ContractError("s14_cmd_routed_moe_layer: NULL argument");
+    const s14_router_desc &r = desc->router;
+    validate_router(r, false);
+    if (r.n_tokens != 1) throw ContractError("S14 routed layer: one decode token per call");
+    if (r.top_k > S14_EXPERTS_PER_TOKEN) throw ContractError("S14 routed layer: top_k must be <= 6");
+    if (!fused_dim_ok(r.hidden) || !fused_dim_ok(desc->inter))
+        throw ContractError("S14 routed layer: hidden and intermediate must be 1024, 2048 or 4096");
+    if (!desc->page_table || !desc->y) throw ContractError("S14 routed layer: page_table or y is NULL");
+    if (desc->shared_page && desc->shared_kind != S14_PAGE_MXFP4 && desc->shared_kind != S14_PAGE_FP8)
+        throw ContractError("S14 routed layer: unknown shared page kind");
+    cudaStream_t st = stream_of(ctx, stream);
+    cudaError_t err;
+    ctx->launches += launch_router(st, r, ctx->scores, ctx->select, ctx->dev_table, desc->page_table,
+                                   desc->shared_page, desc->shared_kind, &err);
+    if (err != cudaSuccess) return cuda_fail(err, "S14 router launch");
+    JobTable unused;
+    unused.n_jobs = 0;
+    const uint32_t n_jobs = r.top_k + (desc->shared_page ? 1u : 0u);
+    ctx->launches += launch_moe_layer(st, ctx->mode, ctx->sm_count, ctx->dev_table, unused, 1, n_jobs,
+                                      r.hidden, desc->inter, r.x, ctx->h, ctx->d, desc->y, &err);
+    if (err != cudaSuccess) return cuda_fail(err, "S14 MoE layer launch");
+    return S14_OK;
+    S14_CATCH
+}
+
+extern "C" int32_t s14_cmd_head_logits(s14_ctx *ctx, void *stream, const float *x, uint32_t n_tokens,
+                                       const uint16_t *weight_bf16, uint32_t n_rows, uint32_t hidden,
+                                       float *logits_out, uint32_t logits_stride) {
+    S14_TRY
+    if (!ctx || !x || !weight_bf16 || !logits_out) throw ContractError("s14_cmd_head_logits: NULL argument");
+    if (n_tokens == 0 || n_tokens > kMaxTokens) throw ContractError("S14 head: 1..8 tokens");
+    if (n_rows == 0 || hidden == 0 || hidden % 8 != 0)
+        throw ContractError("S14 head: rows must be non-zero and hidden a multiple of 8");
+    if (n_tokens > 1 && logits_stride < n_rows) throw ContractError("S14 head: logits stride < rows");
+    require_aligned(x, 16, "S14 head x");
+    require_aligned(weight_bf16, 16, "S14 head weight");
+    CUDA_OK(launch_head_logits(stream_of(ctx, stream), ctx->sm_count, x, n_tokens, weight_bf16, n_rows,
+                               hidden, logits_out, logits_stride));
+    ctx->launches += 1;
+    return S14_OK;
+    S14_CATCH
+}
+
+extern "C" int32_t s14_cmd_greedy_argmax(s14_ctx *ctx, void *stream, const float *logits,
+                                         uint32_t vocab, int64_t *result) {
+    if (!ctx || !logits || !result || vocab == 0)
+        return fail(S14_ERR_CONTRACT, "s14_cmd_greedy_argmax: NULL or empty argument");
+    CUDA_OK(launch_greedy_argmax(stream_of(ctx, stream), logits, vocab, result));
+    ctx->launches += 1;
+    return S14_OK;
+}
+
+// ---- page pool ----------------------------------------------------------------------
+
+struct s14_pool {
+    s14_ctx *ctx = nullptr;
+    uint8_t *device_base = nullptr;
+    std::unique_ptr<VramPool> pool;
+    cudaEvent_t transfer_fence = nullptr;
+    bool fence_recorded = false;
+};
+
+static ExpertKey key_of(s14_expert_key k) { return ExpertKey{k.layer, k.kind, k.slot}; }
+static s14_expert_key key_to_c(const ExpertKey &k) {
+    s14_expert_key o;
+    std::memset(&o, 0, sizeof(o));
+    o.layer = k.layer;
+    o.kind = k.kind;
+    o.slot = k.slot;
+    return o;
+}
+static SlotBinding binding_of(s14_slot_binding b) { return SlotBinding{key_of(b.key), b.slot, b.generation}; }
+static s14_slot_binding binding_to_c(const SlotBinding &b) {
+    s14_slot_binding o;
+    std::memset(&o, 0, sizeof(o));
+    o.key = key_to_c(b.key);
+    o.slot = b.slot;
+    o.generation = b.generation;
+    return o;
+}
+static LoadingReservation reservation_of(const s14_loading_reservation &r) {
+    LoadingReservation o;
+    o.key = key_of(r.key);
+    o.slot = r.slot;
+    o.generation = r.generation;
+    if (r.has_evicted) o.evicted = key_of(r.evicted);
+    return o;
+}
+static s14_loading_reservation reservation_to_c(const LoadingReservation &r) {
+    s14_loading_reservation o;
+    std::memset(&o, 0, sizeof(o));
+    o.key = key_to_c(r.key);
+    o.slot = r.slot;
+    o.generation = r.generation;
+    o.has_evicted = r.evicted.has_value() ? 1 : 0;
+    if (r.evicted) o.evicted = key_to_c(*r.evicted);
+    return o;
+}
+
+extern "C" int32_t s14_pool_create(s14_ctx *ctx, uint32_t n_slots, uint64_t slot_bytes, s14_pool **out) {
+    S14_TRY
+    if (!out) throw ContractError("s14_pool_create: out is NULL");
+    *out = nullptr;
+    std::unique_ptr<s14_pool> p(new s14_pool());
+    p->pool.reset(new VramPool(n_slots, slot_bytes, nullptr));  // validates sizes first
+    if (ctx) {
+        if (slot_bytes % 16 != 0) throw PoolError("VRAM slot size must be a multiple of 16 bytes");
+        CUDA_OK(cudaSetDevice(ctx->device));
+        void *base = nullptr;
+        CUDA_OK(cudaMalloc(&base, (size_t)n_slots * slot_bytes));
+        p->device_base = (uint8_t *)base;
+        p->pool.reset(new VramPool(n_slots, slot_bytes, p->device_base));
+        p->ctx = ctx;
+        CUDA_OK(cudaEventCreateWithFlags(&p->transfer_fence, cudaEventDisableTiming));
+    }
+    *out = p.release();
+    return S14_OK;
+    S14_CATCH
+}
+
+extern "C" int32_t s14_pool_destroy(s14_pool *pool) {
+    if (!pool) return S14_OK;
+    if (pool->ctx) {
+        cudaSetDevice(pool->ctx->device);
+        cudaStreamSynchronize(pool->ctx->copy);
+        cudaStreamSynchronize(pool->ctx->compute);
+        if (pool->transfer_fence) cudaEventDestroy(pool->transfer_fence);
+        cudaFree(pool->device_base);
+    }
+    delete pool;
+    return S14_OK;
+}
+
+extern "C" uint32_t s14_pool_capacity(const s14_pool *p) { return p ? p->pool->capacity() : 0; }
+extern "C" uint64_t s14_pool_slot_bytes(const s14_pool *p) { return p ? p->pool->slot_bytes() : 0; }
+extern "C" uint32_t s14_pool_n_loaded(const s14_pool *p) { return p ? p->pool->n_loaded() : 0; }
+extern "C" uint64_t s14_pool_total_bytes(const s14_pool *p) { return p ? p->pool->total_bytes() : 0; }
+extern "C" uint64_t s14_pool_slot_offset(const s14_pool *p, uint32_t slot) {
+    return p ? p->pool->slot_offset(slot) : 0;
+}
+extern "C" void *s14_pool_slot_ptr(const s14_pool *p, uint32_t slot) {
+    return (p && slot < p->pool->capacity()) ? p->pool->slot_ptr(slot) : nullptr;
+}
+
+extern "C" int32_t s14_pool_lookup(s14_pool *p, s14_expert_key key, int32_t *found, uint32_t *slot) {
+    S14_TRY
+    if (!p || !found) throw ContractError("s14_pool_lookup: NULL argument");
+    auto r = p->pool->lookup(key_of(key));
+    *found = r ? 1 : 0;
+    if (r && slot) *slot = *r;
+    return S14_OK;
+    S14_CATCH
+}
+
+extern "C" int32_t s14_pool_lookup_and_pin(s14_pool *p, s14_expert_key key, int32_t *found,
+                                           s14_slot_binding *lease) {
+    S14_TRY
+    if (!p || !found || !lease) throw ContractError("s14_pool_lookup_and_pin: NULL argument");
+    auto r = p->pool->lookup_and_pin(key_of(key));
+    *found = r ? 1 : 0;
+    if (r) *lease = binding_to_c(*r);
+    return S14_OK;
+    S14_CATCH
+}
+
+extern "C" int32_t s14_pool_reserve_loading_generation(s14_pool *p, s14_expert_key key,
+                                                       s14_loading_reservation *out) {
+    S14_TRY
+    if (!p || !out) throw ContractError("s14_pool_reserve_loading_generation: NULL argument");
+    *out = reservation_to_c(p->pool->reserve_loading_generation(key_of(key)));
+    return S14_OK;
+    S14_CATCH
+}
+
+extern "C" int32_t s14_pool_mark_ready(s14_pool *p, uint32_t slot, s14_expert_key key) {
+    S14_TRY
+    if (!p) throw ContractError("s14_pool_mark_ready: NULL argument");
+    p->pool->mark_ready(slot, key_of(key));
+    return S14_OK;
+    S14_CATCH
+}
+
+static std::vector<LoadingReservation> reservations_of(const s14_loading_reservation *r, uint32_t n) {
+    std::vector<LoadingReservation> v;
+    for (uint32_t i = 0; i < n; ++i) v.push_back(reservation_of(r[i]));
+    return v;
+}
+
+extern "C" int32_t s14_pool_validate_publish_batch(const s14_pool *p, const s14_loading_reservation *r,
+                                                   uint32_t count) {
+    S14_TRY
+    if (!p || (count && !r)) throw ContractError("s14_pool_validate_publish_batch: NULL argument");
+    p->pool->validate_publish_batch(reservations_of(r, count));
+    return S14_OK;
+    S14_CATCH
+}
+
+extern "C" int32_t s14_pool_publish_batch_and_pin(s14_pool *p, const s14_loading_reservation *r,
+                                                  uint32_t count, s14_slot_binding *leases_out) {
+    S14_TRY
+    if (!p || (count && (!r || !leases_out)))
+        throw ContractError("s14_pool_publish_batch_and_pin: NULL argument");
+    auto leases = p->pool->publish_batch_and_pin(reservations_of(r, count));
+    for (size_t i = 0; i < leases.size(); ++i) leases_out[i] = binding_to_c(leases[i]);
+    return S14_OK;
+    S14_CATCH
+}
+
+extern "C" int32_t s14_pool_validate_binding(const s14_pool *p, s14_slot_binding binding) {
+    S14_TRY
+    if (!p) throw ContractError("s14_pool_validate_binding: NULL argument");
+    p->pool->validate_binding(binding_of(binding));
+    return S14_OK;
+    S14_CATCH
+}
+
+extern "C" int32_t s14_pool_release_after_compute_fence(s14_pool *p, s14_slot_binding lease) {
+    S14_TRY
+    if (!p) throw ContractError("s14_pool_release_after_compute_fence: NULL argument");
+    p->pool->release_after_compute_fence(binding_of(lease));
+    return S14_OK;
+    S14_CATCH
+}
+
+extern "C" int32_t s14_pool_cancel_loading(s14_pool *p, uint32_t slot, s14_expert_key key) {
+    S14_TRY
+    if (!p) throw ContractError("s14_pool_cancel_loading: NULL argument");
+    p->pool->cancel_loading(slot, key_of(key));
+    return S14_OK;
+    S14_CATCH
+}
+
+extern "C" int32_t s14_pool_cancel_reservation(s14_pool *p, s14_loading_reservation reservation) {
+    S14_TRY
+    if (!p) throw ContractError("s14_pool_cancel_reservation: NULL argument");
+    p->pool->cancel_reservation(reservation_of(reservation));
+    return S14_OK;
+    S14_CATCH
+}
+
+extern "C" int32_t s14_pool_upload_page_async(s14_pool *p, const s14_loading_reservation *reservation,
+                                              const void *host_bytes, uint64_t bytes) {
+    S14_TRY
+    if (!p || !reservation || !host_bytes) throw ContractError("s14_pool_upload_page_async: NULL argument");
+    if (!p->ctx) throw PoolError("this pool has no device memory (bookkeeping-only pool)");
+    if (bytes > p->pool->slot_bytes())
+        throw PoolError("expert page is too large for VRAM slot: " + std::to_string(bytes) + " > " +
+                        std::to_string(p->pool->slot_bytes()) + " bytes");
+    // the reservation must still be the live one: same slot, key and generation
+    p->pool->validate_publish_batch({reservation_of(*reservation)});
+    CUDA_OK(cudaMemcpyAsync(p->pool->slot_ptr(reservation->slot), host_bytes, bytes,
+                            cudaMemcpyHostToDevice, p->ctx->copy));
+    return S14_OK;
+    S14_CATCH
+}
+
+extern "C" int32_t s14_pool_transfer_fence(s14_pool *p) {
+    if (!p || !p->ctx) return fail(S14_ERR_POOL, "pool has no device");
+    CUDA_OK(cudaEventRecord(p->transfer_fence, p->ctx->copy));
+    p->fence_recorded = true;
+    return S14_OK;
+}
+
+extern "C" int32_t s14_pool_wait_transfer_fence(s14_pool *p) {
+    if (!p || !p->ctx) return fail(S14_ERR_POOL, "pool has no device");
+    if (!p->fence_recorded) return S14_OK;
+    CUDA_OK(cudaEventSynchronize(p->transfer_fence));
+    return S14_OK;
+}
+
+extern "C" int32_t s14_pool_compute_wait_transfer(s14_pool *p, void *compute_stream) {
+    if (!p || !p->ctx) return fail(S14_ERR_POOL, "pool has no device");
+    if (!p->fence_recorded) return S14_OK;
+    CUDA_OK(cudaStreamWaitEvent(stream_of(p->ctx, compute_stream), p->transfer_fence, 0));
+    return S14_OK;
+}
+
+extern "C" int32_t s14_host_alloc_pinned(uint64_t bytes, void **out) {
+    if (!out || bytes == 0) return fail(S14_ERR_CONTRACT, "s14_host_alloc_pinned: bad argument");
+    CUDA_OK(cudaHostAlloc(out, bytes, cudaHostAllocDefault));
+    return S14_OK;
+}
+
+extern "C" int32_t s14_host_free_pinned(void *ptr) {
+    if (ptr) CUDA_OK(cudaFreeHost(ptr));
+    return S14_OK;
+}
+
+// ---- route page transaction ---------------------------------------------------------
+
+struct s14_moe_pages {
+    std::unique_ptr<S14MoePages> pages;
+};
+struct s14_route_load_batch {
+    RouteLoadBatch batch;
+};
+struct s14_moe_compute_lease {
+    S14MoeComputeLeaseBatch lease;
+};
+
+static RouteDecision route_of(const s14_route_decision &r) {
+    RouteDecision d;
+    d.layer = r.layer;
+    d.kind = r.kind == 0 ? RouterKind::Hash : RouterKind::Score;
+    const uint32_t n = r.n > S14_EXPERTS_PER_TOKEN ? S14_EXPERTS_PER_TOKEN : r.n;
+    d.expert_ids.assign(r.expert_ids, r.expert_ids + n);
+    d.weights.assign(r.weights, r.weights + n);
+    return d;
+}
+
+extern "C" int32_t s14_route_validate_for(const s14_route_decision *route, uint32_t profile) {
+    S14_TRY
+    if (!route) throw ContractError("s14_route_validate_for: route is NULL");
+    if (profile > 1) throw ContractError("unknown graph profile");
+    if (route->n != S14_EXPERTS_PER_TOKEN) throw ContractError("profile requires top-6 ids and weights");
+    route_of(*route).validate_for((GraphProfile)profile);
+    return S14_OK;
+    S14_CATCH
+}
+
+extern "C" int32_t s14_moe_pages_create_ex(s14_pool *routed_pool, s14_pool *shared_pool,
+                                           uint32_t profile, uint64_t min_routed_bytes,
+                                           uint64_t min_shared_bytes, s14_moe_pages **out) {
+    S14_TRY
+    if (!routed_pool || !shared_pool || !out) throw ContractError("s14_moe_pages_create: NULL argument");
+    if (profile > 1) throw ContractError("unknown graph profile");
+    std::unique_ptr<s14_moe_pages> p(new s14_moe_pages());
+    p->pages.reset(new S14MoePages(*routed_pool->pool, *shared_pool->pool, (GraphProfile)profile,
+                                   min_routed_bytes, min_shared_bytes));
+    *out = p.release();
+    return S14_OK;
+    S14_CATCH
+}
+
+extern "C" int32_t s14_moe_pages_create(s14_pool *routed_pool, s14_pool *shared_pool, uint32_t profile,
+                                        s14_moe_pages **out) {
+    return s14_moe_pages_create_ex(routed_pool, shared_pool, profile, S14_EXPERT_PAGE_BYTES,
+                                   S14_SHARED_EXPERT_PAGE_BYTES, out);
+}
+
+extern "C" int32_t s14_moe_pages_destroy(s14_moe_pages *pages) {
+    delete pages;
+    return S14_OK;
+}
+
+extern "C" int32_t s14_moe_pages_begin_after_official_route(s14_moe_pages *pages,
+                                                            const s14_route_decision *route,
+                                                            s14_route_load_batch **batch) {
+    S14_TRY
+    if (!pages || !route || !batch) throw ContractError("begin_after_official_route: NULL argument");
+    *batch = nullptr;
+    if (route->n != S14_EXPERTS_PER_TOKEN) throw ContractError("profile requires top-6 ids and weights");
+    std::unique_ptr<s14_route_load_batch> b(new s14_route_load_batch());
+    b->batch = pages->pages->begin_after_official_route(route_of(*route));
+    *batch = b.release();
+    return S14_OK;
+    S14_CATCH
+}
+
+extern "C" int32_t s14_route_load_batch_missing(const s14_route_load_batch *batch,
+                                                s14_loading_reservation *reservations_out,
+                                                int32_t *is_shared_out, uint32_t *count) {
+    if (!batch || !reservations_out || !is_shared_out || !count)
+        return fail(S14_ERR_CONTRACT, "s14_route_load_batch_missing: NULL argument");
+    uint32_t n = 0;
+    for (const PageState &p : batch->batch.routed_pages)
+        if (p.loading) {
+            reservations_out[n] = reservation_to_c(p.reservation);
+            is_shared_out[n] = 0;
+            ++n;
+        }
+    if (batch->batch.shared_page.loading) {
+        reservations_out[n] = reservation_to_c(batch->batch.shared_page.reservation);
+        is_shared_out[n] = 1;
+        ++n;
+    }
+    *count = n;
+    return S14_OK;
+}
+
+extern "C" int32_t s14_moe_pages_publish_after_transfer_fence(s14_moe_pages *pages,
+                                                              s14_route_load_batch *batch,
+                                                              s14_moe_compute_lease **lease) {
+    if (!pages || !batch || !lease) return fail(S14_ERR_CONTRACT, "publish_after_transfer_fence: NULL argument");
+    *lease = nullptr;
+    std::unique_ptr<s14_route_load_batch> owned(batch);  // consumed either way
+    S14_TRY
+    std::unique_ptr<s14_moe_compute_lease> l(new s14_moe_compute_lease());
+    l->lease = pages->pages->publish_after_transfer_fence(std::move(owned->batch));
+    *lease = l.release();
+    return S14_OK;
+    S14_CATCH
+}
+
+extern "C" int32_t s14_moe_compute_lease_bindings(const s14_moe_compute_lease *lease,
+                                                  s14_slot_binding routed_out[S14_EXPERTS_PER_TOKEN],
+                                                  s14_slot_binding *shared_out,
+                                                  uint16_t ids_out[S14_EXPERTS_PER_TOKEN],
+                                                  float weights_out[S14_EXPERTS_PER_TOKEN]) {
+    if (!lease) return fail(S14_ERR_CONTRACT, "s14_moe_compute_lease_bindings: lease is NULL");
+    const S14MoeComputeLeaseBatch &l = lease->lease;
+    for (size_t i = 0; i < l.routed.size() && i < S14_EXPERTS_PER_TOKEN; ++i) {
+        if (routed_out) routed_out[i] = binding_to_c(l.routed[i]);
+        if (ids_out) ids_out[i] = l.expert_ids[i];
+        if (weights_out) weights_out[i] = l.route_weights[i];
+    }
+    if (shared_out) *shared_out = binding_to_c(l.shared);
+    return S14_OK;
+}
+
+extern "C" int32_t s14_moe_pages_release_after_compute_fence(s14_moe_pages *pages,
+                                                             s14_moe_compute_lease *lease) {
+    S14_TRY
+    if (!pages || !lease) throw ContractError("release_after_compute_fence: NULL argument");
+    pages->pages->release_after_compute_fence(lease->lease);
+    delete lease;
+    return S14_OK;
+    S14_CATCH
+}
+
+extern "C" int32_t s14_moe_pages_cancel(s14_moe_pages *pages, s14_route_load_batch *batch) {
+    if (!pages || !batch) return fail(S14_ERR_CONTRACT, "s14_moe_pages_cancel: NULL argument");
+    std::unique_ptr<s14_route_load_batch> owned(batch);
+    S14_TRY
+    pages->pages->cancel(std::move(owned->batch));
+    return S14_OK;
+    S14_CATCH
+}

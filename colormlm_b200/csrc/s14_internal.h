@@ -1,0 +1,61 @@
+// Internal declarations shared by the kernel file and the C-ABI file.
+#ifndef S14_INTERNAL_H
+#define S14_INTERNAL_H
+
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#include "../../include/polaris_s14_cuda.h"
+
+namespace s14 {
+
+// One (expert page, token) pair of a fused layer call.
+struct Job {
+    const uint8_t *page;
+    uint32_t kind;      // S14_PAGE_MXFP4 | S14_PAGE_FP8
+    uint32_t token;     // row of x / y
+    float weight;       // route weight (unused for the shared expert)
+    uint32_t is_shared; // added last with weight 1
+};
+
+constexpr uint32_t kMaxTokens = S14_MAX_BLOCK_TOKENS;
+constexpr uint32_t kMaxJobs = kMaxTokens * (S14_EXPERTS_PER_TOKEN + 1);
+
+// Jobs are stored grouped by expert page (so that a page's second reader finds it
+// in L2); token_jobs lists each token's jobs in mix order (route order, shared last).
+struct JobTable {
+    uint32_t n_jobs;
+    uint32_t n_tokens;
+    uint32_t token_job_begin[kMaxTokens + 1];
+    uint8_t token_jobs[kMaxJobs];
+    Job jobs[kMaxJobs];
+};
+
+cudaError_t launch_mxfp4_matvec(cudaStream_t st, uint32_t mode, int sm_count, const float *x,
+                                const uint8_t *w, const uint8_t *s, float *y, uint32_t n, uint32_t k);
+cudaError_t launch_fp8_matvec(cudaStream_t st, uint32_t mode, int sm_count, uint32_t scale_format,
+                              uint32_t n_tokens, const float *x, const uint8_t *w, const void *s,
+                              float *y, uint32_t n, uint32_t k);
+cudaError_t launch_swiglu_limit(cudaStream_t st, const float *gate, const float *up, float *y,
+                                uint32_t n);
+cudaError_t launch_route_mix(cudaStream_t st, const float *expert, float *routed, uint32_t n,
+                             float weight);
+cudaError_t launch_moe_accumulate(cudaStream_t st, const float *expert, float *acc, uint32_t n,
+                                  float weight);
+// Returns the number of kernels launched.  h: [kMaxJobs, inter], d: [kMaxJobs, hidden].
+int launch_moe_layer(cudaStream_t st, uint32_t mode, int sm_count, const JobTable *dev_table,
+                     const JobTable &param_table, uint32_t n_tokens, uint32_t n_jobs_max,
+                     uint32_t hidden, uint32_t inter, const float *x, float *h, float *d, float *y,
+                     cudaError_t *err);
+int launch_router(cudaStream_t st, const s14_router_desc &r, float *scores, float *select,
+                  JobTable *table_out, const uint8_t *const *page_table, const uint8_t *shared_page,
+                  uint32_t shared_kind, cudaError_t *err);
+cudaError_t launch_head_logits(cudaStream_t st, int sm_count, const float *x, uint32_t n_tokens,
+                               const uint16_t *w, uint32_t n_rows, uint32_t hidden, float *out,
+                               uint32_t out_stride);
+cudaError_t launch_greedy_argmax(cudaStream_t st, const float *logits, uint32_t vocab,
+                                 int64_t *result);
+
+}  // namespace s14
+
+#endif

@@ -1,0 +1,1046 @@
+// sm_100a kernels of the S14 MoE expert hot path.
+//
+// Two summation orders are implemented for every matvec (see S14_ACCUM_* in
+// include/polaris_s14_cuda.h):
+//   pairwise  - a warp owns an output row, its lanes split K in 16-byte pieces
+//               (128-bit coalesced loads), decode E2M1 / E4M3 with the hardware
+//               cvt to f16x2, multiply-accumulate in F32 inside one scale block,
+//               then carry block sums, lane sums and the final value in F64;
+//   reference - a thread owns an output row and walks k in ascending order with
+//               the reference's separate multiply / multiply / add per element
+//               (examples/s14_vulkan_numeric.rs:1669-1714), bit-identical to it.
+// The elementwise steps (limit-10 SwiGLU, route mix, ordered accumulate) use
+// separate F32 multiplies and adds in both modes, as the reference does.
+#include "s14_internal.h"
+
+#include <cuda_bf16.h>
+#include <cuda_fp16.h>
+#include <cuda_fp8.h>
+
+namespace s14 {
+
+// ---------------------------------------------------------------- decode ----
+
+// Eight E2M1 codes of one 32-bit word (low nibble first) -> four f16x2 words.
+__device__ __forceinline__ void e2m1x8_to_h2x4(uint32_t w, uint32_t &h0, uint32_t &h1,
+                                               uint32_t &h2, uint32_t &h3) {
+    asm("{\n"
+        ".reg .b8 b0, b1, b2, b3;\n"
+        "mov.b32 {b0, b1, b2, b3}, %4;\n"
+        "cvt.rn.f16x2.e2m1x2 %0, b0;\n"
+        "cvt.rn.f16x2.e2m1x2 %1, b1;\n"
+        "cvt.rn.f16x2.e2m1x2 %2, b2;\n"
+        "cvt.rn.f16x2.e2m1x2 %3, b3;\n"
+        "}\n"
+        : "=r"(h0), "=r"(h1), "=r"(h2), "=r"(h3)
+        : "r"(w));
+}
+
+// Four E4M3 codes of one 32-bit word -> two f16x2 words.
+__device__ __forceinline__ void e4m3x4_to_h2x2(uint32_t w, uint32_t &h0, uint32_t &h1) {
+    asm("{\n"
+        ".reg .b16 lo, hi;\n"
+        "mov.b32 {lo, hi}, %2;\n"
+        "cvt.rn.f16x2.e4m3x2 %0, lo;\n"
+        "cvt.rn.f16x2.e4m3x2 %1, hi;\n"
+        "}\n"
+        : "=r"(h0), "=r"(h1)
+        : "r"(w));
+}
+
+__device__ __forceinline__ float2 h2_to_f2(uint32_t h) {
+    __half2 v;
+    *reinterpret_cast<uint32_t *>(&v) = h;
+    return __half22float2(v);
+}
+
+// 2^(code-127) as a double: exact for every code 0..254.
+__device__ __forceinline__ double ue8m0_to_f64(uint32_t code) {
+    return __hiloint2double((int)((code + 896u) << 20), 0);
+}
+
+// 2^(code-127) as a float; code 0 is the subnormal 2^-127.
+__device__ __forceinline__ float ue8m0_to_f32(uint32_t code) {
+    return __uint_as_float(code == 0u ? 0x00400000u : (code << 23));
+}
+
+__device__ __forceinline__ uint4 ldg_stream(const uint4 *p) {
+    uint4 v;
+    asm volatile("ld.global.nc.L1::no_allocate.v4.u32 {%0,%1,%2,%3}, [%4];"
+                 : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w)
+                 : "l"(p));
+    return v;
+}
+
+__device__ __forceinline__ double warp_sum(double v) {
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+    return v;
+}
+
+// F32 dot of 32 E2M1 codes (one 16-byte piece = one scale block) with 32
+// activations held in registers; two independent even/odd chains on the packed
+// F32x2 pipe.
+__device__ __forceinline__ float dot32_e2m1(const uint4 &q, const float *__restrict__ xr) {
+    float2 acc = make_float2(0.f, 0.f);
+    const uint32_t w[4] = {q.x, q.y, q.z, q.w};
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+        uint32_t h0, h1, h2, h3;
+        e2m1x8_to_h2x4(w[i], h0, h1, h2, h3);
+        acc = __ffma2_rn(h2_to_f2(h0), make_float2(xr[i * 8 + 0], xr[i * 8 + 1]), acc);
+        acc = __ffma2_rn(h2_to_f2(h1), make_float2(xr[i * 8 + 2], xr[i * 8 + 3]), acc);
+        acc = __ffma2_rn(h2_to_f2(h2), make_float2(xr[i * 8 + 4], xr[i * 8 + 5]), acc);
+        acc = __ffma2_rn(h2_to_f2(h3), make_float2(xr[i * 8 + 6], xr[i * 8 + 7]), acc);
+    }
+    return acc.x + acc.y;
+}
+
+// F32 dot of 16 E4M3 codes (one 16-byte piece) with 16 activations.
+__device__ __forceinline__ float dot16_e4m3(const uint4 &q, const float *__restrict__ xr) {
+    float2 acc = make_float2(0.f, 0.f);
+    const uint32_t w[4] = {q.x, q.y, q.z, q.w};
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+        uint32_t h0, h1;
+        e4m3x4_to_h2x2(w[i], h0, h1);
+        acc = __ffma2_rn(h2_to_f2(h0), make_float2(xr[i * 4 + 0], xr[i * 4 + 1]), acc);
+        acc = __ffma2_rn(h2_to_f2(h1), make_float2(xr[i * 4 + 2], xr[i * 4 + 3]), acc);
+    }
+    return acc.x + acc.y;
+}
+
+// The reference's SwiGLU (examples/s14_vulkan_numeric.rs:1543-1556) in F32 with
+// separate operations.  expf is evaluated in double and rounded once, which
+// reproduces a correctly rounded expf.
+__device__ __forceinline__ float swiglu_limit_f32(float gate, float up) {
+    const float g = fminf(gate, 10.0f);
+    const float u = fminf(fmaxf(up, -10.0f), 10.0f);
+    const float e = (float)exp(-(double)g);
+    return __fmul_rn(__fdiv_rn(g, __fadd_rn(1.0f, e)), u);
+}
+
+// ------------------------------------------------- primitive operators ------
+
+// y[n] = sum_k x[k] * e2m1(w[n,k]) * 2^(s[n,k/32]-127); warp per row.
+__global__ void __launch_bounds__(256)
+k_mxfp4_matvec_pairwise(const float *__restrict__ x, const uint8_t *__restrict__ w,
+                        const uint8_t *__restrict__ s, float *__restrict__ y, uint32_t n_rows,
+                        uint32_t k) {
+    const uint32_t lane = threadIdx.x & 31u;
+    const uint32_t warp = (blockIdx.x * blockDim.x + threadIdx.x) >> 5;
+    const uint32_t n_warps = (gridDim.x * blockDim.x) >> 5;
+    const uint32_t groups = k >> 5;
+    for (uint32_t n = warp; n < n_rows; n += n_warps) {
+        const uint4 *wrow = reinterpret_cast<const uint4 *>(w + (size_t)n * (k >> 1));
+        const uint8_t *srow = s + (size_t)n * groups;
+        double acc = 0.0;
+        for (uint32_t g = lane; g < groups; g += 32u) {
+            const uint4 q = ldg_stream(wrow + g);
+            float xr[32];
+            const float4 *xp = reinterpret_cast<const float4 *>(x + (size_t)g * 32u);
+#pragma unroll
+            for (int i = 0; i < 8; ++i) {
+                const float4 v = __ldg(xp + i);
+                xr[i * 4 + 0] = v.x;
+                xr[i * 4 + 1] = v.y;
+                xr[i * 4 + 2] = v.z;
+                xr[i * 4 + 3] = v.w;
+            }
+            acc += (double)dot32_e2m1(q, xr) * ue8m0_to_f64(__ldg(srow + g));
+        }
+        acc = warp_sum(acc);
+        if (lane == 0) y[n] = (float)acc;
+    }
+}
+
+// Reference order: thread per row, k ascending, (x*e)*s then add.
+__global__ void __launch_bounds__(128)
+k_mxfp4_matvec_reference(const float *__restrict__ x, const uint8_t *__restrict__ w,
+                         const uint8_t *__restrict__ s, float *__restrict__ y, uint32_t n_rows,
+                         uint32_t k) {
+    const uint32_t n = blockIdx.x * blockDim.x + threadIdx.x;
+    if (n >= n_rows) return;
+    const uint32_t groups = k >> 5;
+    const uint4 *wrow = reinterpret_cast<const uint4 *>(w + (size_t)n * (k >> 1));
+    const uint8_t *srow = s + (size_t)n * groups;
+    float sum = 0.0f;
+    for (uint32_t g = 0; g < groups; ++g) {
+        const uint4 q = __ldg(wrow + g);
+        const float sc = ue8m0_to_f32(__ldg(srow + g));
+        const uint32_t wd[4] = {q.x, q.y, q.z, q.w};
+        const float *xg = x + (size_t)g * 32u;
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            uint32_t h[4];
+            e2m1x8_to_h2x4(wd[i], h[0], h[1], h[2], h[3]);
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+                const float2 e = h2_to_f2(h[j]);
+                sum = __fadd_rn(sum, __fmul_rn(__fmul_rn(__ldg(xg + i * 8 + j * 2), e.x), sc));
+                sum = __fadd_rn(sum, __fmul_rn(__fmul_rn(__ldg(xg + i * 8 + j * 2 + 1), e.y), sc));
+            }
+        }
+    }
+    y[n] = sum;
+}
+
+__device__ __forceinline__ float e4m3_to_f32(uint32_t code) {
+    const __half_raw hr = __nv_cvt_fp8_to_halfraw((__nv_fp8_storage_t)code, __NV_E4M3);
+    return __half2float(__half(hr));
+}
+
+template <bool F32_SCALE>
+__device__ __forceinline__ double fp8_block_scale_f64(const void *scale, size_t idx) {
+    if (F32_SCALE) return (double)__ldg(reinterpret_cast<const float *>(scale) + idx);
+    return ue8m0_to_f64(__ldg(reinterpret_cast<const uint8_t *>(scale) + idx));
+}
+
+template <bool F32_SCALE>
+__device__ __forceinline__ float fp8_block_scale_f32(const void *scale, size_t idx) {
+    if (F32_SCALE) return __ldg(reinterpret_cast<const float *>(scale) + idx);
+    return ue8m0_to_f32(__ldg(reinterpret_cast<const uint8_t *>(scale) + idx));
+}
+
+// y[t,n] = sum_k x[t,k] * e4m3(w[n,k]) * scale[n/128][k/128]; warp per row, any k,
+// NT tokens per weight pass.  Lanes take 16-byte pieces when the row is 16-byte
+// aligned and k is a multiple of 16, single bytes otherwise.
+template <int NT, bool F32_SCALE>
+__global__ void __launch_bounds__(256)
+k_fp8_matvec_pairwise(const float *__restrict__ x, const uint8_t *__restrict__ w,
+                      const void *__restrict__ scale, float *__restrict__ y, uint32_t n_rows,
+                      uint32_t k) {
+    const uint32_t lane = threadIdx.x & 31u;
+    const uint32_t warp = (blockIdx.x * blockDim.x + threadIdx.x) >> 5;
+    const uint32_t n_warps = (gridDim.x * blockDim.x) >> 5;
+    const uint32_t k_groups = (k + 127u) >> 7;
+    const bool vec_ok = ((k & 15u) == 0u) && ((reinterpret_cast<uintptr_t>(w) & 15u) == 0u) &&
+                        ((reinterpret_cast<uintptr_t>(x) & 15u) == 0u);
+    for (uint32_t n = warp; n < n_rows; n += n_warps) {
+        const uint8_t *wrow = w + (size_t)n * k;
+        const size_t srow = (size_t)(n >> 7) * k_groups;
+        double acc[NT];
+#pragma unroll
+        for (int t = 0; t < NT; ++t) acc[t] = 0.0;
+        if (vec_ok) {
+            const uint32_t pieces = k >> 4;
+            for (uint32_t p = lane; p < pieces; p += 32u) {
+                const uint4 q = ldg_stream(reinterpret_cast<const uint4 *>(wrow) + p);
+                const double sc = fp8_block_scale_f64<F32_SCALE>(scale, srow + (p >> 3));
+#pragma unroll
+                for (int t = 0; t < NT; ++t) {
+                    float xr[16];
+                    const float4 *xp =
+                        reinterpret_cast<const float4 *>(x + (size_t)t * k + (size_t)p * 16u);
+#pragma unroll
+                    for (int i = 0; i < 4; ++i) {
+                        const float4 v = __ldg(xp + i);
+                        xr[i * 4 + 0] = v.x;
+                        xr[i * 4 + 1] = v.y;
+                        xr[i * 4 + 2] = v.z;
+                        xr[i * 4 + 3] = v.w;
+                    }
+                    acc[t] += (double)dot16_e4m3(q, xr) * sc;
+                }
+            }
+        } else {
+            for (uint32_t kk = lane; kk < k; kk += 32u) {
+                const double wv = (double)e4m3_to_f32(__ldg(wrow + kk)) *
+                                  fp8_block_scale_f64<F32_SCALE>(scale, srow + (kk >> 7));
+#pragma unroll
+                for (int t = 0; t < NT; ++t) acc[t] += (double)__ldg(x + (size_t)t * k + kk) * wv;
+            }
+        }
+#pragma unroll
+        for (int t = 0; t < NT; ++t) {
+            const double v = warp_sum(acc[t]);
+            if (lane == 0) y[(size_t)t * n_rows + n] = (float)v;
+        }
+    }
+}
+
+// Reference order: thread per (row, token), k ascending, (x*e)*s then add
+// (examples/s14_vulkan_numeric.rs:1698-1714).
+template <bool F32_SCALE>
+__global__ void __launch_bounds__(128)
+k_fp8_matvec_reference(const float *__restrict__ x, const uint8_t *__restrict__ w,
+                       const void *__restrict__ scale, float *__restrict__ y, uint32_t n_rows,
+                       uint32_t k, uint32_t n_tokens) {
+    const uint32_t n = blockIdx.x * blockDim.x + threadIdx.x;
+    const uint32_t t = blockIdx.y;
+    if (n >= n_rows || t >= n_tokens) return;
+    const uint32_t k_groups = (k + 127u) >> 7;
+    const uint8_t *wrow = w + (size_t)n * k;
+    const float *xt = x + (size_t)t * k;
+    const size_t srow = (size_t)(n >> 7) * k_groups;
+    float sum = 0.0f;
+    for (uint32_t kg = 0; kg < k_groups; ++kg) {
+        const float sc = fp8_block_scale_f32<F32_SCALE>(scale, srow + kg);
+        const uint32_t k_end = min(kg * 128u + 128u, k);
+        for (uint32_t kk = kg * 128u; kk < k_end; ++kk)
+            sum = __fadd_rn(sum, __fmul_rn(__fmul_rn(__ldg(xt + kk), e4m3_to_f32(__ldg(wrow + kk))), sc));
+    }
+    y[(size_t)t * n_rows + n] = sum;
+}
+
+// s14_swiglu_limit.comp:14-20
+__global__ void k_swiglu_limit(const float *__restrict__ gate, const float *__restrict__ up,
+                               float *__restrict__ y, uint32_t n) {
+    const uint32_t i = blockIdx.x * blockDim.x + threadIdx.x;
+    if (i < n) y[i] = swiglu_limit_f32(gate[i], up[i]);
+}
+
+// s14_route_mix.comp:16-20
+__global__ void k_route_mix(const float *__restrict__ expert, float *__restrict__ routed, uint32_t n,
+                            float weight) {
+    const uint32_t i = blockIdx.x * blockDim.x + threadIdx.x;
+    if (i < n) routed[i] = __fmul_rn(weight, expert[i]);
+}
+
+// s14_moe_accumulate.comp:17-21
+__global__ void k_moe_accumulate(const float *__restrict__ expert, float *__restrict__ acc,
+                                 uint32_t n, float weight) {
+    const uint32_t i = blockIdx.x * blockDim.x + threadIdx.x;
+    if (i < n) acc[i] = __fadd_rn(acc[i], __fmul_rn(weight, expert[i]));
+}
+
+// ------------------------------------------------------- fused MoE layer ----
+//
+// A job is one (expert page, token) pair.  Jobs of the same expert are adjacent
+// so that the second and later tokens of an expert find its page in L2.
+//   up   : h[job, i]    = swiglu(w1[i,:] . x_t, w3[i,:] . x_t)      i < inter
+//   down : d[job, n]    = w2[n,:] . h[job,:]                        n < hidden
+//   mix  : y[t, n]      = sum over the token's jobs, in route order, of
+//                         weight * d[job, n]  (shared last, weight 1)
+
+__device__ __forceinline__ const JobTable &table_of(const JobTable *dev, const JobTable &param) {
+    return dev ? *dev : param;
+}
+
+struct PageView {
+    const uint8_t *w1, *w3, *w2, *s1, *s3, *s2;
+};
+
+__device__ __forceinline__ PageView page_view(const uint8_t *page, uint32_t kind, uint32_t hidden,
+                                              uint32_t inter) {
+    PageView v;
+    const size_t elems = (size_t)hidden * inter;
+    if (kind == S14_PAGE_MXFP4) {
+        const size_t wb = elems >> 1, sb = elems >> 5;
+        v.w1 = page;
+        v.w3 = page + wb;
+        v.w2 = page + 2 * wb;
+        v.s1 = page + 3 * wb;
+        v.s3 = v.s1 + sb;
+        v.s2 = v.s3 + sb;
+    } else {
+        const size_t sb = (size_t)((inter + 127u) >> 7) * ((hidden + 127u) >> 7);
+        v.w1 = page;
+        v.w3 = page + elems;
+        v.w2 = page + 2 * elems;
+        v.s1 = page + 3 * elems;
+        v.s3 = v.s1 + sb;
+        v.s2 = v.s3 + sb;
+    }
+    return v;
+}
+
+// One MXFP4 row against register-resident activations.  KC = K / 1024; lane l
+// owns the 32 elements k = j*1024 + l*32 ... of every 1024-wide slice j, which is
+// one 16-byte piece and one scale block.
+template <int KC>
+struct RowFrag {
+    uint4 q[KC];
+    uint32_t sc[KC];
+};
+
+template <int KC>
+__device__ __forceinline__ void load_row_mxfp4(RowFrag<KC> &f, const uint8_t *w, const uint8_t *s,
+                                               uint32_t row, uint32_t lane) {
+    const uint4 *wrow = reinterpret_cast<const uint4 *>(w + (size_t)row * (KC * 512));
+    const uint8_t *srow = s + (size_t)row * (KC * 32);
+#pragma unroll
+    for (int j = 0; j < KC; ++j) {
+        f.q[j] = ldg_stream(wrow + j * 32 + lane);
+        f.sc[j] = __ldg(srow + j * 32 + lane);
+    }
+}
+
+template <int KC>
+__device__ __forceinline__ double dot_row_mxfp4(const RowFrag<KC> &f, const float *__restrict__ xr) {
+    double acc = 0.0;
+#pragma unroll
+    for (int j = 0; j < KC; ++j)
+        acc += (double)dot32_e2m1(f.q[j], xr + j * 32) * ue8m0_to_f64(f.sc[j]);
+    return acc;
+}
+
+// One FP8 row with the same lane-to-k mapping (two 16-byte pieces per slice).
+template <int KC>
+__device__ __forceinline__ double dot_row_fp8(const uint8_t *w, const uint8_t *s, uint32_t row,
+                                              uint32_t lane, const float *__restrict__ xr) {
+    const uint8_t *wrow = w + (size_t)row * (KC * 1024);
+    const uint8_t *srow = s + (size_t)(row >> 7) * (KC * 8);
+    double acc = 0.0;
+#pragma unroll
+    for (int j = 0; j < KC; ++j) {
+        const uint4 *p = reinterpret_cast<const uint4 *>(wrow + j * 1024 + lane * 32);
+        const uint4 q0 = __ldg(p), q1 = __ldg(p + 1);
+        const float part = dot16_e4m3(q0, xr + j * 32) + dot16_e4m3(q1, xr + j * 32 + 16);
+        acc += (double)part * ue8m0_to_f64(__ldg(srow + j * 8 + (lane >> 2)));
+    }
+    return acc;
+}
+
+template <int KC>
+__device__ __forceinline__ void load_x_regs(float *xr, const float *__restrict__ x, uint32_t lane) {
+#pragma unroll
+    for (int j = 0; j < KC; ++j) {
+        const float4 *xp = reinterpret_cast<const float4 *>(x + j * 1024 + lane * 32);
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+            const float4 v = xp[i];
+            xr[j * 32 + i * 4 + 0] = v.x;
+            xr[j * 32 + i * 4 + 1] = v.y;
+            xr[j * 32 + i * 4 + 2] = v.z;
+            xr[j * 32 + i * 4 + 3] = v.w;
+        }
+    }
+}
+
+// Up phase, pairwise order.  grid = n_tokens * ctas_per_token; the warps of a CTA
+// keep their token's x in registers and stride over that token's (job, row) space.
+template <int KC>
+__global__ void __launch_bounds__(256, 1)
+k_expert_up_pairwise(const JobTable *__restrict__ dev_table,
+                     const __grid_constant__ JobTable param_table, const float *__restrict__ x,
+                     float *__restrict__ h, uint32_t inter, uint32_t ctas_per_token) {
+    const JobTable &tab = table_of(dev_table, param_table);
+    constexpr uint32_t hidden = KC * 1024;
+    const uint32_t lane = threadIdx.x & 31u;
+    const uint32_t token = blockIdx.x / ctas_per_token;
+    const uint32_t cta_in_token = blockIdx.x - token * ctas_per_token;
+    const uint32_t warp = cta_in_token * (blockDim.x >> 5) + (threadIdx.x >> 5);
+    const uint32_t n_warps = ctas_per_token * (blockDim.x >> 5);
+    const uint32_t job0 = tab.token_job_begin[token];
+    const uint32_t n_jobs = tab.token_job_begin[token + 1] - job0;
+    const uint32_t items = n_jobs * inter;
+
+    float xr[KC * 32];
+    load_x_regs<KC>(xr, x + (size_t)token * hidden, lane);
+
+    RowFrag<KC> g0, u0, g1, u1;
+    uint32_t it = warp;
+    auto issue = [&](RowFrag<KC> &g, RowFrag<KC> &u, uint32_t item) {
+        const uint32_t job = job0 + item / inter, row = item % inter;
+        const Job jb = tab.jobs[tab.token_jobs[job]];
+        if (jb.kind == S14_PAGE_MXFP4) {
+            const PageView pv = page_view(jb.page, jb.kind, hidden, inter);
+            load_row_mxfp4<KC>(g, pv.w1, pv.s1, row, lane);
+            load_row_mxfp4<KC>(u, pv.w3, pv.s3, row, lane);
+        }
+    };
+    auto finish = [&](const RowFrag<KC> &g, const RowFrag<KC> &u, uint32_t item) {
+        const uint32_t job = job0 + item / inter, row = item % inter;
+        const uint32_t jid = tab.token_jobs[job];
+        const Job jb = tab.jobs[jid];
+        double gate, up;
+        if (jb.kind == S14_PAGE_MXFP4) {
+            gate = dot_row_mxfp4<KC>(g, xr);
+            up = dot_row_mxfp4<KC>(u, xr);
+        } else {
+            const PageView pv = page_view(jb.page, jb.kind, hidden, inter);
+            gate = dot_row_fp8<KC>(pv.w1, pv.s1, row, lane, xr);
+            up = dot_row_fp8<KC>(pv.w3, pv.s3, row, lane, xr);
+        }
+        gate = warp_sum(gate);
+        up = warp_sum(up);
+        if (lane == 0) h[(size_t)jid * inter + row] = swiglu_limit_f32((float)gate, (float)up);
+    };
+    if (it < items) issue(g0, u0, it);
+    while (it < items) {
+        const uint32_t nx = it + n_warps;
+        if (nx < items) issue(g1, u1, nx);
+        finish(g0, u0, it);
+        it = nx;
+        if (it >= items) break;
+        const uint32_t nx2 = it + n_warps;
+        if (nx2 < items) issue(g0, u0, nx2);
+        finish(g1, u1, it);
+        it = nx2;
+    }
+}
+
+// Down phase, pairwise order.  grid = n_jobs * ctas_per_job; a CTA's warps keep the
+// job's h in registers and stride over the rows of w2.
+template <int KC>
+__global__ void __launch_bounds__(256, (KC >= 4 ? 1 : 2))
+k_expert_down_pairwise(const JobTable *__restrict__ dev_table,
+                       const __grid_constant__ JobTable param_table, const float *__restrict__ h,
+                       float *__restrict__ d, uint32_t hidden, uint32_t ctas_per_job) {
+    const JobTable &tab = table_of(dev_table, param_table);
+    constexpr uint32_t inter = KC * 1024;
+    const uint32_t lane = threadIdx.x & 31u;
+    const uint32_t jid = blockIdx.x / ctas_per_job;
+    const uint32_t cta_in_job = blockIdx.x - jid * ctas_per_job;
+    const uint32_t warp = cta_in_job * (blockDim.x >> 5) + (threadIdx.x >> 5);
+    const uint32_t n_warps = ctas_per_job * (blockDim.x >> 5);
+    if (jid >= tab.n_jobs) return;
+    const Job jb = tab.jobs[jid];
+    const PageView pv = page_view(jb.page, jb.kind, hidden, inter);
+
+    float xr[KC * 32];
+    load_x_regs<KC>(xr, h + (size_t)jid * inter, lane);
+    float *out = d + (size_t)jid * hidden;
+
+    if (jb.kind != S14_PAGE_MXFP4) {
+        for (uint32_t row = warp; row < hidden; row += n_warps) {
+            const double v = warp_sum(dot_row_fp8<KC>(pv.w2, pv.s2, row, lane, xr));
+            if (lane == 0) out[row] = (float)v;
+        }
+        return;
+    }
+    RowFrag<KC> a0, a1, b0, b1;
+    uint32_t row = warp;
+    const uint32_t step = n_warps;
+    // two rows per stage, two stages in flight
+    auto issue2 = [&](RowFrag<KC> &p, RowFrag<KC> &q, uint32_t r) {
+        if (r < hidden) load_row_mxfp4<KC>(p, pv.w2, pv.s2, r, lane);
+        if (r + step < hidden) load_row_mxfp4<KC>(q, pv.w2, pv.s2, r + step, lane);
+    };
+    auto finish2 = [&](const RowFrag<KC> &p, const RowFrag<KC> &q, uint32_t r) {
+        if (r < hidden) {
+            const double v = warp_sum(dot_row_mxfp4<KC>(p, xr));
+            if (lane == 0) out[r] = (float)v;
+        }
+        if (r + step < hidden) {
+            const double v = warp_sum(dot_row_mxfp4<KC>(q, xr));
+            if (lane == 0) out[r + step] = (float)v;
+        }
+    };
+    if (row < hidden) issue2(a0, a1, row);
+    while (row < hidden) {
+        const uint32_t nx = row + 2 * step;
+        if (nx < hidden) issue2(b0, b1, nx);
+        finish2(a0, a1, row);
+        row = nx;
+        if (row >= hidden) break;
+        const uint32_t nx2 = row + 2 * step;
+        if (nx2 < hidden) issue2(a0, a1, nx2);
+        finish2(b0, b1, row);
+        row = nx2;
+    }
+}
+
+// Reference-order dot of one MXFP4 row: sequential k, (x*e)*s, separate add.
+// x is read from shared memory (every lane reads the same address: broadcast).
+__device__ __forceinline__ float dot_row_mxfp4_reference(const uint8_t *w, const uint8_t *s,
+                                                         uint32_t row, uint32_t k,
+                                                         const float *__restrict__ xs) {
+    const uint32_t groups = k >> 5;
+    const uint4 *wrow = reinterpret_cast<const uint4 *>(w + (size_t)row * (k >> 1));
+    const uint8_t *srow = s + (size_t)row * groups;
+    float sum = 0.0f;
+    for (uint32_t g4 = 0; g4 < groups; g4 += 4) {
+        uint4 q[4];
+        uint32_t scw;
+#pragma unroll
+        for (int j = 0; j < 4; ++j) q[j] = __ldg(wrow + g4 + j);
+        scw = __ldg(reinterpret_cast<const uint32_t *>(srow + g4));
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+            const float sc = ue8m0_to_f32((scw >> (8 * j)) & 0xffu);
+            const uint32_t wd[4] = {q[j].x, q[j].y, q[j].z, q[j].w};
+            const float *xg = xs + (size_t)(g4 + j) * 32u;
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+                uint32_t hh[4];
+                e2m1x8_to_h2x4(wd[i], hh[0], hh[1], hh[2], hh[3]);
+                const float4 xa = *reinterpret_cast<const float4 *>(xg + i * 8);
+                const float4 xb = *reinterpret_cast<const float4 *>(xg + i * 8 + 4);
+                const float xv[8] = {xa.x, xa.y, xa.z, xa.w, xb.x, xb.y, xb.z, xb.w};
+#pragma unroll
+                for (int p = 0; p < 4; ++p) {
+                    const float2 e = h2_to_f2(hh[p]);
+                    sum = __fadd_rn(sum, __fmul_rn(__fmul_rn(xv[p * 2], e.x), sc));
+                    sum = __fadd_rn(sum, __fmul_rn(__fmul_rn(xv[p * 2 + 1], e.y), sc));
+                }
+            }
+        }
+    }
+    return sum;
+}
+
+__device__ __forceinline__ float dot_row_fp8_reference(const uint8_t *w, const uint8_t *s,
+                                                       uint32_t row, uint32_t k,
+                                                       const float *__restrict__ xs) {
+    const uint32_t k_groups = (k + 127u) >> 7;
+    const uint4 *wrow = reinterpret_cast<const uint4 *>(w + (size_t)row * k);
+    const uint8_t *srow = s + (size_t)(row >> 7) * k_groups;
+    float sum = 0.0f;
+    for (uint32_t kg = 0; kg < k_groups; ++kg) {
+        const float sc = ue8m0_to_f32(__ldg(srow + kg));
+        for (uint32_t p = 0; p < 8; ++p) {
+            const uint4 q = __ldg(wrow + kg * 8 + p);
+            const uint32_t wd[4] = {q.x, q.y, q.z, q.w};
+            const float *xg = xs + kg * 128u + p * 16u;
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+                uint32_t h0, h1;
+                e4m3x4_to_h2x2(wd[i], h0, h1);
+                const float4 xa = *reinterpret_cast<const float4 *>(xg + i * 4);
+                const float2 e0 = h2_to_f2(h0), e1 = h2_to_f2(h1);
+                sum = __fadd_rn(sum, __fmul_rn(__fmul_rn(xa.x, e0.x), sc));
+                sum = __fadd_rn(sum, __fmul_rn(__fmul_rn(xa.y, e0.y), sc));
+                sum = __fadd_rn(sum, __fmul_rn(__fmul_rn(xa.z, e1.x), sc));
+                sum = __fadd_rn(sum, __fmul_rn(__fmul_rn(xa.w, e1.y), sc));
+            }
+        }
+    }
+    return sum;
+}
+
+// Up phase, reference order: a thread owns gate row i and up row i of one job.
+// grid = (ceil(inter/32), n_jobs), block = 32.
+__global__ void __launch_bounds__(32)
+k_expert_up_reference(const JobTable *__restrict__ dev_table,
+                      const __grid_constant__ JobTable param_table, const float *__restrict__ x,
+                      float *__restrict__ h, uint32_t hidden, uint32_t inter) {
+    extern __shared__ __align__(16) float xs[];
+    const JobTable &tab = table_of(dev_table, param_table);
+    const uint32_t jid = blockIdx.y;
+    if (jid >= tab.n_jobs) return;
+    const Job jb = tab.jobs[jid];
+    const float *xt = x + (size_t)jb.token * hidden;
+    for (uint32_t i = threadIdx.x; i < hidden; i += blockDim.x) xs[i] = xt[i];
+    __syncthreads();
+    const uint32_t row = blockIdx.x * blockDim.x + threadIdx.x;
+    if (row >= inter) return;
+    const PageView pv = page_view(jb.page, jb.kind, hidden, inter);
+    float gate, up;
+    if (jb.kind == S14_PAGE_MXFP4) {
+        gate = dot_row_mxfp4_reference(pv.w1, pv.s1, row, hidden, xs);
+        up = dot_row_mxfp4_reference(pv.w3, pv.s3, row, hidden, xs);
+    } else {
+        gate = dot_row_fp8_reference(pv.w1, pv.s1, row, hidden, xs);
+        up = dot_row_fp8_reference(pv.w3, pv.s3, row, hidden, xs);
+    }
+    h[(size_t)jid * inter + row] = swiglu_limit_f32(gate, up);
+}
+
+// Down phase, reference order.  grid = (ceil(hidden/32), n_jobs), block = 32.
+__global__ void __launch_bounds__(32)
+k_expert_down_reference(const JobTable *__restrict__ dev_table,
+                        const __grid_constant__ JobTable param_table, const float *__restrict__ h,
+                        float *__restrict__ d, uint32_t hidden, uint32_t inter) {
+    extern __shared__ __align__(16) float xs[];
+    const JobTable &tab = table_of(dev_table, param_table);
+    const uint32_t jid = blockIdx.y;
+    if (jid >= tab.n_jobs) return;
+    const Job jb = tab.jobs[jid];
+    const float *hj = h + (size_t)jid * inter;
+    for (uint32_t i = threadIdx.x; i < inter; i += blockDim.x) xs[i] = hj[i];
+    __syncthreads();
+    const uint32_t row = blockIdx.x * blockDim.x + threadIdx.x;
+    if (row >= hidden) return;
+    const PageView pv = page_view(jb.page, jb.kind, hidden, inter);
+    const float v = (jb.kind == S14_PAGE_MXFP4)
+                        ? dot_row_mxfp4_reference(pv.w2, pv.s2, row, inter, xs)
+                        : dot_row_fp8_reference(pv.w2, pv.s2, row, inter, xs);
+    d[(size_t)jid * hidden + row] = v;
+}
+
+// Ordered mix (examples/s14_vulkan_numeric.rs:936-946): acc = 0; acc += w * d for the
+// token's routed jobs in route order; acc += d_shared.  Separate multiply and add.
+__global__ void __launch_bounds__(256)
+k_moe_mix(const JobTable *__restrict__ dev_table, const __grid_constant__ JobTable param_table,
+          const float *__restrict__ d, float *__restrict__ y, uint32_t hidden) {
+    const JobTable &tab = table_of(dev_table, param_table);
+    const uint32_t token = blockIdx.y;
+    const uint32_t n = blockIdx.x * blockDim.x + threadIdx.x;
+    if (n >= hidden) return;
+    const uint32_t j0 = tab.token_job_begin[token], j1 = tab.token_job_begin[token + 1];
+    float acc = 0.0f;
+    for (uint32_t j = j0; j < j1; ++j) {
+        const uint32_t jid = tab.token_jobs[j];
+        const Job jb = tab.jobs[jid];
+        const float v = d[(size_t)jid * hidden + n];
+        acc = jb.is_shared ? __fadd_rn(acc, v) : __fadd_rn(acc, __fmul_rn(jb.weight, v));
+    }
+    y[(size_t)token * hidden + n] = acc;
+}
+
+// ------------------------------------------------------------- router -------
+
+// logits in double: warp per (token, expert) row of BF16 weights.
+__global__ void __launch_bounds__(256)
+k_router_scores(const float *__restrict__ x, const uint16_t *__restrict__ wr,
+                const float *__restrict__ bias, float *__restrict__ scores,
+                float *__restrict__ select, uint32_t n_experts, uint32_t hidden, uint32_t n_tokens,
+                uint32_t score_fn) {
+    const uint32_t lane = threadIdx.x & 31u;
+    const uint32_t warp = (blockIdx.x * blockDim.x + threadIdx.x) >> 5;
+    if (warp >= n_experts * n_tokens) return;
+    const uint32_t t = warp / n_experts, e = warp - t * n_experts;
+    const uint4 *row = reinterpret_cast<const uint4 *>(wr + (size_t)e * hidden);
+    const float *xt = x + (size_t)t * hidden;
+    double acc = 0.0;
+    for (uint32_t p = lane; p < (hidden >> 3); p += 32u) {
+        const uint4 q = __ldg(row + p);
+        const uint32_t wd[4] = {q.x, q.y, q.z, q.w};
+        const float4 xa = __ldg(reinterpret_cast<const float4 *>(xt + p * 8));
+        const float4 xb = __ldg(reinterpret_cast<const float4 *>(xt + p * 8 + 4));
+        const float xv[8] = {xa.x, xa.y, xa.z, xa.w, xb.x, xb.y, xb.z, xb.w};
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            acc += (double)xv[i * 2] * (double)__uint_as_float(wd[i] << 16);
+            acc += (double)xv[i * 2 + 1] * (double)__uint_as_float(wd[i] & 0xffff0000u);
+        }
+    }
+    acc = warp_sum(acc);
+    if (lane == 0) {
+        const double l = (double)(float)acc;
+        const double sc = (score_fn == S14_SCORE_SIGMOID) ? 1.0 / (1.0 + exp(-l))
+                                                          : sqrt(l > 20.0 ? l : log1p(exp(l)));
+        const float s = (float)sc;
+        scores[(size_t)t * n_experts + e] = s;
+        select[(size_t)t * n_experts + e] = __fadd_rn(s, bias ? bias[e] : 0.0f);
+    }
+}
+
+// top-k of select (descending, ties -> lowest index) with one warp per token, then
+// the normalised weights; optionally writes the decode job table.
+__global__ void __launch_bounds__(32)
+k_router_select(const float *__restrict__ scores, const float *__restrict__ select,
+                uint32_t n_experts, uint32_t top_k, float route_scale, int32_t *__restrict__ ids_out,
+                float *__restrict__ weights_out, JobTable *__restrict__ table_out,
+                const uint8_t *const *__restrict__ page_table, const uint8_t *shared_page,
+                uint32_t shared_kind) {
+    const uint32_t lane = threadIdx.x;
+    const uint32_t t = blockIdx.x;
+    const float *sel = select + (size_t)t * n_experts;
+    const float *sco = scores + (size_t)t * n_experts;
+    float v[8];
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+        const uint32_t e = i * 32 + lane;
+        v[i] = e < n_experts ? sel[e] : -INFINITY;
+    }
+    uint32_t taken = 0;
+    int32_t my_ids[8];
+    float my_scores[8];
+    for (uint32_t j = 0; j < top_k; ++j) {
+        float best = -INFINITY;
+        uint32_t best_e = 0xffffffffu;
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+            const uint32_t e = i * 32 + lane;
+            if (e < n_experts && !((taken >> i) & 1u) && (best_e == 0xffffffffu || v[i] > best)) {
+                best = v[i];
+                best_e = e;
+            }
+        }
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) {
+            const float ob = __shfl_xor_sync(0xffffffffu, best, o);
+            const uint32_t oe = __shfl_xor_sync(0xffffffffu, best_e, o);
+            if (oe != 0xffffffffu && (best_e == 0xffffffffu || ob > best || (ob == best && oe < best_e))) {
+                best = ob;
+                best_e = oe;
+            }
+        }
+        if ((best_e & 31u) == lane) taken |= 1u << (best_e >> 5);
+        my_ids[j] = (int32_t)best_e;
+        my_scores[j] = sco[best_e];
+    }
+    if (lane == 0) {
+        float sum = 0.0f;
+        for (uint32_t j = 0; j < top_k; ++j) sum = __fadd_rn(sum, my_scores[j]);
+        for (uint32_t j = 0; j < top_k; ++j) {
+            const float w = __fmul_rn(__fdiv_rn(my_scores[j], sum), route_scale);
+            if (ids_out) ids_out[(size_t)t * top_k + j] = my_ids[j];
+            if (weights_out) weights_out[(size_t)t * top_k + j] = w;
+            if (table_out) {
+                Job jb;
+                jb.page = page_table[my_ids[j]];
+                jb.kind = S14_PAGE_MXFP4;
+                jb.token = 0;
+                jb.weight = w;
+                jb.is_shared = 0;
+                table_out->jobs[j] = jb;
+                table_out->token_jobs[j] = j;
+            }
+        }
+        if (table_out) {
+            uint32_t n = top_k;
+            if (shared_page) {
+                Job jb;
+                jb.page = shared_page;
+                jb.kind = shared_kind;
+                jb.token = 0;
+                jb.weight = 1.0f;
+                jb.is_shared = 1;
+                table_out->jobs[n] = jb;
+                table_out->token_jobs[n] = n;
+                ++n;
+            }
+            table_out->n_jobs = n;
+            table_out->n_tokens = 1;
+            table_out->token_job_begin[0] = 0;
+            table_out->token_job_begin[1] = n;
+        }
+    }
+}
+
+// --------------------------------------------------------------- LM head ----
+
+// logits[t, v] = sum_k x[t,k] * bf16(W[v,k]); warp per vocabulary row; 8 products
+// in F32, carried in F64.
+template <int NT>
+__global__ void __launch_bounds__(256)
+k_head_logits(const float *__restrict__ x, const uint16_t *__restrict__ w, float *__restrict__ out,
+              uint32_t n_rows, uint32_t hidden, uint32_t out_stride) {
+    const uint32_t lane = threadIdx.x & 31u;
+    const uint32_t warp = (blockIdx.x * blockDim.x + threadIdx.x) >> 5;
+    const uint32_t n_warps = (gridDim.x * blockDim.x) >> 5;
+    for (uint32_t v = warp; v < n_rows; v += n_warps) {
+        const uint4 *row = reinterpret_cast<const uint4 *>(w + (size_t)v * hidden);
+        double acc[NT];
+#pragma unroll
+        for (int t = 0; t < NT; ++t) acc[t] = 0.0;
+        for (uint32_t p = lane; p < (hidden >> 3); p += 32u) {
+            const uint4 q = ldg_stream(row + p);
+            const uint32_t wd[4] = {q.x, q.y, q.z, q.w};
+            float wf[8];
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+                wf[i * 2] = __uint_as_float(wd[i] << 16);
+                wf[i * 2 + 1] = __uint_as_float(wd[i] & 0xffff0000u);
+            }
+#pragma unroll
+            for (int t = 0; t < NT; ++t) {
+                const float4 xa = __ldg(reinterpret_cast<const float4 *>(x + (size_t)t * hidden + p * 8));
+                const float4 xb = __ldg(reinterpret_cast<const float4 *>(x + (size_t)t * hidden + p * 8 + 4));
+                float2 part = make_float2(0.f, 0.f);
+                part = __ffma2_rn(make_float2(wf[0], wf[1]), make_float2(xa.x, xa.y), part);
+                part = __ffma2_rn(make_float2(wf[2], wf[3]), make_float2(xa.z, xa.w), part);
+                part = __ffma2_rn(make_float2(wf[4], wf[5]), make_float2(xb.x, xb.y), part);
+                part = __ffma2_rn(make_float2(wf[6], wf[7]), make_float2(xb.z, xb.w), part);
+                acc[t] += (double)part.x + (double)part.y;
+            }
+        }
+#pragma unroll
+        for (int t = 0; t < NT; ++t) {
+            const double s = warp_sum(acc[t]);
+            if (lane == 0) out[(size_t)t * out_stride + v] = (float)s;
+        }
+    }
+}
+
+// greedy argmax, lowest id wins ties, NaN -> -1; single block.
+__global__ void __launch_bounds__(1024)
+k_greedy_argmax(const float *__restrict__ logits, uint32_t vocab, int64_t *__restrict__ result) {
+    __shared__ float sv[32];
+    __shared__ uint32_t si[32];
+    __shared__ int snan;
+    if (threadIdx.x == 0) snan = 0;
+    __syncthreads();
+    float best = -INFINITY;
+    uint32_t best_i = 0xffffffffu;
+    bool nan = false;
+    for (uint32_t i = threadIdx.x; i < vocab; i += blockDim.x) {
+        const float v = logits[i];
+        nan |= (v != v);
+        if (best_i == 0xffffffffu || v > best) {
+            best = v;
+            best_i = i;
+        }
+    }
+    if (nan) snan = 1;
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+        const float ob = __shfl_xor_sync(0xffffffffu, best, o);
+        const uint32_t oi = __shfl_xor_sync(0xffffffffu, best_i, o);
+        if (oi != 0xffffffffu && (best_i == 0xffffffffu || ob > best || (ob == best && oi < best_i))) {
+            best = ob;
+            best_i = oi;
+        }
+    }
+    if ((threadIdx.x & 31u) == 0) {
+        sv[threadIdx.x >> 5] = best;
+        si[threadIdx.x >> 5] = best_i;
+    }
+    __syncthreads();
+    if (threadIdx.x < 32) {
+        best = sv[threadIdx.x];
+        best_i = si[threadIdx.x];
+        if (threadIdx.x >= (blockDim.x >> 5)) best_i = 0xffffffffu;
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) {
+            const float ob = __shfl_xor_sync(0xffffffffu, best, o);
+            const uint32_t oi = __shfl_xor_sync(0xffffffffu, best_i, o);
+            if (oi != 0xffffffffu && (best_i == 0xffffffffu || ob > best || (ob == best && oi < best_i))) {
+                best = ob;
+                best_i = oi;
+            }
+        }
+        if (threadIdx.x == 0) *result = snan ? -1 : (int64_t)best_i;
+    }
+}
+
+// ------------------------------------------------------------- launchers ----
+
+static inline uint32_t ceil_div(uint32_t a, uint32_t b) { return (a + b - 1) / b; }
+
+cudaError_t launch_mxfp4_matvec(cudaStream_t st, uint32_t mode, int sm_count, const float *x,
+                                const uint8_t *w, const uint8_t *s, float *y, uint32_t n, uint32_t k) {
+    if (mode == S14_ACCUM_REFERENCE) {
+        k_mxfp4_matvec_reference<<<ceil_div(n, 128), 128, 0, st>>>(x, w, s, y, n, k);
+    } else {
+        const uint32_t blocks = min(ceil_div(n, 8), (uint32_t)sm_count * 8u);
+        k_mxfp4_matvec_pairwise<<<blocks, 256, 0, st>>>(x, w, s, y, n, k);
+    }
+    return cudaGetLastError();
+}
+
+template <bool F32S>
+static void launch_fp8_pairwise_nt(cudaStream_t st, uint32_t blocks, uint32_t nt, const float *x,
+                                   const uint8_t *w, const void *s, float *y, uint32_t n, uint32_t k) {
+    switch (nt) {
+    case 1: k_fp8_matvec_pairwise<1, F32S><<<blocks, 256, 0, st>>>(x, w, s, y, n, k); break;
+    case 2: k_fp8_matvec_pairwise<2, F32S><<<blocks, 256, 0, st>>>(x, w, s, y, n, k); break;
+    case 3: k_fp8_matvec_pairwise<3, F32S><<<blocks, 256, 0, st>>>(x, w, s, y, n, k); break;
+    case 4: k_fp8_matvec_pairwise<4, F32S><<<blocks, 256, 0, st>>>(x, w, s, y, n, k); break;
+    case 5: k_fp8_matvec_pairwise<5, F32S><<<blocks, 256, 0, st>>>(x, w, s, y, n, k); break;
+    case 6: k_fp8_matvec_pairwise<6, F32S><<<blocks, 256, 0, st>>>(x, w, s, y, n, k); break;
+    case 7: k_fp8_matvec_pairwise<7, F32S><<<blocks, 256, 0, st>>>(x, w, s, y, n, k); break;
+    default: k_fp8_matvec_pairwise<8, F32S><<<blocks, 256, 0, st>>>(x, w, s, y, n, k); break;
+    }
+}
+
+cudaError_t launch_fp8_matvec(cudaStream_t st, uint32_t mode, int sm_count, uint32_t scale_format,
+                              uint32_t n_tokens, const float *x, const uint8_t *w, const void *s,
+                              float *y, uint32_t n, uint32_t k) {
+    if (mode == S14_ACCUM_REFERENCE) {
+        dim3 grid(ceil_div(n, 128), n_tokens);
+        if (scale_format == S14_SCALE_F32)
+            k_fp8_matvec_reference<true><<<grid, 128, 0, st>>>(x, w, s, y, n, k, n_tokens);
+        else
+            k_fp8_matvec_reference<false><<<grid, 128, 0, st>>>(x, w, s, y, n, k, n_tokens);
+    } else {
+        const uint32_t blocks = min(ceil_div(n, 8), (uint32_t)sm_count * 8u);
+        if (scale_format == S14_SCALE_F32)
+            launch_fp8_pairwise_nt<true>(st, blocks, n_tokens, x, w, s, y, n, k);
+        else
+            launch_fp8_pairwise_nt<false>(st, blocks, n_tokens, x, w, s, y, n, k);
+    }
+    return cudaGetLastError();
+}
+
+cudaError_t launch_swiglu_limit(cudaStream_t st, const float *gate, const float *up, float *y,
+                                uint32_t n) {
+    k_swiglu_limit<<<ceil_div(n, 256), 256, 0, st>>>(gate, up, y, n);
+    return cudaGetLastError();
+}
+
+cudaError_t launch_route_mix(cudaStream_t st, const float *expert, float *routed, uint32_t n,
+                             float weight) {
+    k_route_mix<<<ceil_div(n, 256), 256, 0, st>>>(expert, routed, n, weight);
+    return cudaGetLastError();
+}
+
+cudaError_t launch_moe_accumulate(cudaStream_t st, const float *expert, float *acc, uint32_t n,
+                                  float weight) {
+    k_moe_accumulate<<<ceil_div(n, 256), 256, 0, st>>>(expert, acc, n, weight);
+    return cudaGetLastError();
+}
+
+template <int KC>
+static void launch_up_pairwise(cudaStream_t st, const JobTable *dev, const JobTable &param,
+                               const float *x, float *h, uint32_t inter, uint32_t n_tokens,
+                               uint32_t ctas_per_token) {
+    k_expert_up_pairwise<KC><<<n_tokens * ctas_per_token, 256, 0, st>>>(dev, param, x, h, inter,
+                                                                        ctas_per_token);
+}
+
+template <int KC>
+static void launch_down_pairwise(cudaStream_t st, const JobTable *dev, const JobTable &param,
+                                 const float *h, float *d, uint32_t hidden, uint32_t n_jobs,
+                                 uint32_t ctas_per_job) {
+    k_expert_down_pairwise<KC><<<n_jobs * ctas_per_job, 256, 0, st>>>(dev, param, h, d, hidden,
+                                                                      ctas_per_job);
+}
+
+int launch_moe_layer(cudaStream_t st, uint32_t mode, int sm_count, const JobTable *dev_table,
+                     const JobTable &param_table, uint32_t n_tokens, uint32_t n_jobs_max,
+                     uint32_t hidden, uint32_t inter, const float *x, float *h, float *d, float *y,
+                     cudaError_t *err) {
+    int launches = 0;
+    *err = cudaSuccess;
+    if (mode == S14_ACCUM_REFERENCE) {
+        dim3 gu(ceil_div(inter, 32), n_jobs_max), gd(ceil_div(hidden, 32), n_jobs_max);
+        k_expert_up_reference<<<gu, 32, hidden * sizeof(float), st>>>(dev_table, param_table, x, h,
+                                                                      hidden, inter);
+        k_expert_down_reference<<<gd, 32, inter * sizeof(float), st>>>(dev_table, param_table, h, d,
+                                                                       hidden, inter);
+        launches += 2;
+    } else {
+        const uint32_t ctas_per_token = max(1u, (uint32_t)sm_count / n_tokens);
+        switch (hidden >> 10) {
+        case 1: launch_up_pairwise<1>(st, dev_table, param_table, x, h, inter, n_tokens, ctas_per_token); break;
+        case 2: launch_up_pairwise<2>(st, dev_table, param_table, x, h, inter, n_tokens, ctas_per_token); break;
+        default: launch_up_pairwise<4>(st, dev_table, param_table, x, h, inter, n_tokens, ctas_per_token); break;
+        }
+        const uint32_t ctas_per_job = max(1u, ceil_div(2u * (uint32_t)sm_count, n_jobs_max));
+        switch (inter >> 10) {
+        case 1: launch_down_pairwise<1>(st, dev_table, param_table, h, d, hidden, n_jobs_max, ctas_per_job); break;
+        case 2: launch_down_pairwise<2>(st, dev_table, param_table, h, d, hidden, n_jobs_max, ctas_per_job); break;
+        default: launch_down_pairwise<4>(st, dev_table, param_table, h, d, hidden, n_jobs_max, ctas_per_job); break;
+        }
+        launches += 2;
+    }
+    dim3 gm(ceil_div(hidden, 256), n_tokens);
+    k_moe_mix<<<gm, 256, 0, st>>>(dev_table, param_table, d, y, hidden);
+    launches += 1;
+    *err = cudaGetLastError();
+    return launches;
+}
+
+int launch_router(cudaStream_t st, const s14_router_desc &r, float *scores, float *select,
+                  JobTable *table_out, const uint8_t *const *page_table, const uint8_t *shared_page,
+                  uint32_t shared_kind, cudaError_t *err) {
+    const uint32_t warps = r.n_experts * r.n_tokens;
+    k_router_scores<<<ceil_div(warps, 8), 256, 0, st>>>(r.x, r.router_weight_bf16, r.bias, scores,
+                                                        select, r.n_experts, r.hidden, r.n_tokens,
+                                                        r.score_fn);
+    k_router_select<<<r.n_tokens, 32, 0, st>>>(scores, select, r.n_experts, r.top_k, r.route_scale,
+                                               r.ids_out, r.weights_out, table_out, page_table,
+                                               shared_page, shared_kind);
+    *err = cudaGetLastError();
+    return 2;
+}
+
+cudaError_t launch_head_logits(cudaStream_t st, int sm_count, const float *x, uint32_t n_tokens,
+                               const uint16_t *w, uint32_t n_rows, uint32_t hidden, float *out,
+                               uint32_t out_stride) {
+    const uint32_t blocks = min(ceil_div(n_rows, 8), (uint32_t)sm_count * 8u);
+    switch (n_tokens) {
+    case 1: k_head_logits<1><<<blocks, 256, 0, st>>>(x, w, out, n_rows, hidden, out_stride); break;
+    case 2: k_head_logits<2><<<blocks, 256, 0, st>>>(x, w, out, n_rows, hidden, out_stride); break;
+    case 3: k_head_logits<3><<<blocks, 256, 0, st>>>(x, w, out, n_rows, hidden, out_stride); break;
+    case 4: k_head_logits<4><<<blocks, 256, 0, st>>>(x, w, out, n_rows, hidden, out_stride); break;
+    case 5: k_head_logits<5><<<blocks, 256, 0, st>>>(x, w, out, n_rows, hidden, out_stride); break;
+    case 6: k_head_logits<6><<<blocks, 256, 0, st>>>(x, w, out, n_rows, hidden, out_stride); break;
+    case 7: k_head_logits<7><<<blocks, 256, 0, st>>>(x, w, out, n_rows, hidden, out_stride); break;
+    default: k_head_logits<8><<<blocks, 256, 0, st>>>(x, w, out, n_rows, hidden, out_stride); break;
+    }
+    return cudaGetLastError();
+}
+
+cudaError_t launch_greedy_argmax(cudaStream_t st, const float *logits, uint32_t vocab,
+                                 int64_t *result) {
+    k_greedy_argmax<<<1, 1024, 0, st>>>(logits, vocab, result);
+    return cudaGetLastError();
+}
+
+}  // namespace s14

@@ -1,0 +1,531 @@
+"""Python mirror of the reference's S14 operator / page-pool interface over the C ABI.
+
+Class and method names follow the Rust types of the reference
+(``scheduler/ssd_inference/src/s14_vulkan.rs``, ``vram_pool.rs`` and
+``scheduler/s14_runner/src/runner.rs``): ``S14MatvecShape``,
+``S14NumericPipelines.bind_* / cmd_*``, ``VramPool``, ``S14MoePages``,
+``RouteDecision``.  Device memory is held in torch tensors (torch is only the
+allocator and the stream owner here); every operator runs in
+``libpolaris_s14_cuda.so`` and raises :class:`S14Error` on any contract or CUDA
+failure.  Nothing in this module computes on the CPU.
+"""
+from __future__ import annotations
+
+import ctypes as C
+from dataclasses import dataclass, field
+from typing import List, Optional, Sequence
+
+import numpy as np
+
+from . import _lib as L
+from ._lib import S14Error, check
+
+__all__ = [
+    "S14Error", "S14MatvecShape", "validate_ue8m0_codes", "validate_e4m3fn_codes", "S14Context",
+    "S14NumericPipelines", "VramPool", "S14MoePages", "RouteDecision", "TokenRoute",
+]
+
+
+def _u64_out(fn, shape) -> int:
+    out = C.c_uint64()
+    check(fn(shape, C.byref(out)))
+    return out.value
+
+
+class S14MatvecShape:
+    """Byte contracts of one matvec (s14_vulkan.rs:40-114)."""
+
+    def __init__(self, n: int, k: int):
+        c = L.MatvecShape()
+        check(L.lib().s14_shape_new(n, k, C.byref(c)))
+        self.n, self.k = n, k
+        self._c = c
+
+    def validate_mxfp4(self) -> "S14MatvecShape":
+        check(L.lib().s14_shape_validate_mxfp4(self._c))
+        return self
+
+    def validate_fp8(self) -> "S14MatvecShape":
+        check(L.lib().s14_shape_validate_fp8(self._c))
+        return self
+
+    def fp32_input_bytes(self) -> int:
+        return _u64_out(L.lib().s14_shape_fp32_input_bytes, self._c)
+
+    def fp32_output_bytes(self) -> int:
+        return _u64_out(L.lib().s14_shape_fp32_output_bytes, self._c)
+
+    def mxfp4_weight_bytes(self) -> int:
+        return _u64_out(L.lib().s14_shape_mxfp4_weight_bytes, self._c)
+
+    def mxfp4_scale_bytes(self) -> int:
+        return _u64_out(L.lib().s14_shape_mxfp4_scale_bytes, self._c)
+
+    def fp8_weight_bytes(self) -> int:
+        return _u64_out(L.lib().s14_shape_fp8_weight_bytes, self._c)
+
+    def fp8_scale_bytes(self) -> int:
+        return _u64_out(L.lib().s14_shape_fp8_scale_bytes, self._c)
+
+
+def _host_bytes(codes) -> np.ndarray:
+    return np.ascontiguousarray(np.frombuffer(codes, dtype=np.uint8) if isinstance(codes, (bytes, bytearray))
+                                else np.asarray(codes, dtype=np.uint8))
+
+
+def validate_ue8m0_codes(codes) -> None:
+    """Rejects the UE8M0 NaN code 0xFF before upload (s14_vulkan.rs:143-148)."""
+    a = _host_bytes(codes)
+    check(L.lib().s14_validate_ue8m0_codes(a.ctypes.data, a.size, None))
+
+
+def validate_e4m3fn_codes(codes) -> None:
+    """Rejects the E4M3FN NaN codes 0x7F / 0xFF before upload (s14_vulkan.rs:151-156)."""
+    a = _host_bytes(codes)
+    check(L.lib().s14_validate_e4m3fn_codes(a.ctypes.data, a.size, None))
+
+
+def _buf(t) -> L.Buffer:
+    """{pointer, size} of a torch CUDA tensor, the stand-in for the reference's GpuBuffer."""
+    if not t.is_cuda or not t.is_contiguous():
+        raise ValueError("operator buffers must be contiguous CUDA tensors")
+    return L.Buffer(t.data_ptr(), t.numel() * t.element_size())
+
+
+def _torch_stream() -> int:
+    import torch
+
+    return torch.cuda.current_stream().cuda_stream
+
+
+class S14Context:
+    """One device context: streams, scratch and the accumulation mode (see the header)."""
+
+    def __init__(self, device: int = 0):
+        h = C.c_void_p()
+        check(L.lib().s14_ctx_create(device, C.byref(h)))
+        self._h = h
+        self.device = device
+        self.pipelines = S14NumericPipelines(self)
+
+    def close(self) -> None:
+        if self._h:
+            L.lib().s14_ctx_destroy(self._h)
+            self._h = None
+
+    def __del__(self):
+        try:
+            self.close()
+        except Exception:
+            pass
+
+    @property
+    def handle(self):
+        return self._h
+
+    def set_accumulation(self, mode: int) -> None:
+        check(L.lib().s14_ctx_set_accumulation(self._h, mode))
+
+    @property
+    def accumulation(self) -> int:
+        return L.lib().s14_ctx_accumulation(self._h)
+
+    @property
+    def sm_count(self) -> int:
+        return L.lib().s14_ctx_sm_count(self._h)
+
+    @property
+    def launch_count(self) -> int:
+        return L.lib().s14_ctx_launch_count(self._h)
+
+    def synchronize(self) -> None:
+        check(L.lib().s14_ctx_synchronize(self._h))
+
+    def device_status(self) -> int:
+        s = C.c_uint32()
+        check(L.lib().s14_ctx_device_status(self._h, C.byref(s)))
+        return s.value
+
+    # ---- fused layer / router / head -------------------------------------------------
+    def cmd_moe_layer(self, x, y, routes: Sequence["TokenRoute"], shared_page: Optional[int],
+                      shared_kind: int, hidden: int, inter: int, stream: Optional[int] = None) -> None:
+        desc, keep = _layer_desc(routes, shared_page, shared_kind, hidden, inter)
+        desc.x, desc.y = x.data_ptr(), y.data_ptr()
+        check(L.lib().s14_cmd_moe_layer(self._h, stream if stream is not None else _torch_stream(),
+                                        C.byref(desc)))
+        del keep
+
+    def moe_layer_host(self, host_x: np.ndarray, host_y: np.ndarray, routes: Sequence["TokenRoute"],
+                       shared_page: Optional[int], shared_kind: int, hidden: int, inter: int) -> None:
+        """Host buffers in, host buffers out (copies inside the call); pages stay resident."""
+        desc, keep = _layer_desc(routes, shared_page, shared_kind, hidden, inter)
+        assert host_x.dtype == np.float32 and host_y.dtype == np.float32
+        check(L.lib().s14_moe_layer_host(self._h, C.byref(desc), host_x.ctypes.data, host_y.ctypes.data))
+        del keep
+
+    def cmd_router(self, x, wr_bf16, bias, ids_out, weights_out, *, score_fn: int = L.SCORE_SIGMOID,
+                   top_k: int = 6, route_scale: float = 1.0, stream: Optional[int] = None) -> None:
+        d = _router_desc(x, wr_bf16, bias, ids_out, weights_out, score_fn, top_k, route_scale)
+        check(L.lib().s14_cmd_router(self._h, stream if stream is not None else _torch_stream(),
+                                     C.byref(d)))
+
+    def cmd_routed_moe_layer(self, x, wr_bf16, bias, page_table, shared_page: Optional[int],
+                             shared_kind: int, inter: int, y, ids_out=None, weights_out=None, *,
+                             score_fn: int = L.SCORE_SIGMOID, top_k: int = 6, route_scale: float = 1.0,
+                             stream: Optional[int] = None) -> None:
+        d = L.RoutedLayerDesc()
+        d.router = _router_desc(x, wr_bf16, bias, ids_out, weights_out, score_fn, top_k, route_scale)
+        d.inter = inter
+        d.shared_kind = shared_kind
+        d.page_table = page_table.data_ptr()
+        d.shared_page = shared_page
+        d.y = y.data_ptr()
+        check(L.lib().s14_cmd_routed_moe_layer(
+            self._h, stream if stream is not None else _torch_stream(), C.byref(d)))
+
+    def cmd_head_logits(self, x, weight_bf16, logits_out, *, n_rows: Optional[int] = None,
+                        stream: Optional[int] = None) -> None:
+        n_tokens = 1 if x.dim() == 1 else x.shape[0]
+        rows = n_rows if n_rows is not None else weight_bf16.shape[0]
+        stride = logits_out.shape[-1]
+        check(L.lib().s14_cmd_head_logits(self._h, stream if stream is not None else _torch_stream(),
+                                          x.data_ptr(), n_tokens, weight_bf16.data_ptr(), rows,
+                                          weight_bf16.shape[1], logits_out.data_ptr(), stride))
+
+    def cmd_greedy_argmax(self, logits, result, stream: Optional[int] = None) -> None:
+        check(L.lib().s14_cmd_greedy_argmax(self._h, stream if stream is not None else _torch_stream(),
+                                            logits.data_ptr(), logits.numel(), result.data_ptr()))
+
+
+@dataclass
+class TokenRoute:
+    """One token's route with its pages resolved to device addresses of pinned slots."""
+
+    expert_ids: Sequence[int]
+    weights: Sequence[float]
+    pages: Sequence[int]
+
+
+def _layer_desc(routes, shared_page, shared_kind, hidden, inter):
+    arr = (L.TokenRoute * len(routes))()
+    for t, r in enumerate(routes):
+        n = len(r.expert_ids)
+        if n > L.EXPERTS_PER_TOKEN or len(r.weights) != n or len(r.pages) != n:
+            raise S14Error(L.ERR_CONTRACT, "a token route holds at most 6 matching ids/weights/pages")
+        arr[t].n_routed = n
+        for j in range(n):
+            arr[t].expert_ids[j] = int(r.expert_ids[j])
+            arr[t].weights[j] = float(r.weights[j])
+            arr[t].pages[j] = int(r.pages[j])
+    d = L.MoeLayerDesc()
+    d.hidden, d.inter, d.n_tokens = hidden, inter, len(routes)
+    d.shared_kind = shared_kind
+    d.shared_page = shared_page
+    d.routes = C.cast(arr, C.POINTER(L.TokenRoute))
+    return d, arr
+
+
+def _router_desc(x, wr_bf16, bias, ids_out, weights_out, score_fn, top_k, route_scale):
+    d = L.RouterDesc()
+    d.n_experts, d.hidden = wr_bf16.shape[0], wr_bf16.shape[1]
+    d.n_tokens = 1 if x.dim() == 1 else x.shape[0]
+    d.top_k, d.score_fn, d.route_scale = top_k, score_fn, route_scale
+    d.x = x.data_ptr()
+    d.router_weight_bf16 = wr_bf16.data_ptr()
+    d.bias = bias.data_ptr() if bias is not None else None
+    d.ids_out = ids_out.data_ptr() if ids_out is not None else None
+    d.weights_out = weights_out.data_ptr() if weights_out is not None else None
+    return d
+
+
+class S14NumericPipelines:
+    """The five primitive operators (s14_vulkan.rs:187-425): ``bind_*`` validates shapes
+    and capacities and returns a dispatch record, ``cmd_*`` enqueues it on a stream."""
+
+    def __init__(self, ctx: S14Context):
+        self._ctx = ctx
+
+    def _h(self):
+        return self._ctx.handle
+
+    def bind_mxfp4(self, shape: S14MatvecShape, x, packed_weight, weight_scale, y) -> L.Mxfp4Dispatch:
+        d = L.Mxfp4Dispatch()
+        bx, bw, bs, by = _buf(x), _buf(packed_weight), _buf(weight_scale), _buf(y)
+        check(L.lib().s14_bind_mxfp4(self._h(), shape._c, C.byref(bx), C.byref(bw), C.byref(bs),
+                                     C.byref(by), C.byref(d)))
+        return d
+
+    def bind_fp8(self, shape: S14MatvecShape, x, weight, weight_scale, y, *,
+                 scale_format: int = L.SCALE_UE8M0, n_tokens: int = 1) -> L.Fp8Dispatch:
+        d = L.Fp8Dispatch()
+        bx, bw, bs, by = _buf(x), _buf(weight), _buf(weight_scale), _buf(y)
+        check(L.lib().s14_bind_fp8_ex(self._h(), shape._c, scale_format, n_tokens, C.byref(bx),
+                                      C.byref(bw), C.byref(bs), C.byref(by), C.byref(d)))
+        return d
+
+    def bind_swiglu_limit(self, n: int, gate, up, y) -> L.SwigluLimitDispatch:
+        d = L.SwigluLimitDispatch()
+        bg, bu, by = _buf(gate), _buf(up), _buf(y)
+        check(L.lib().s14_bind_swiglu_limit(self._h(), n, C.byref(bg), C.byref(bu), C.byref(by),
+                                            C.byref(d)))
+        return d
+
+    def bind_route_mix(self, n: int, route_weight: float, expert, routed) -> L.RouteMixDispatch:
+        d = L.RouteMixDispatch()
+        be, br = _buf(expert), _buf(routed)
+        check(L.lib().s14_bind_route_mix(self._h(), n, route_weight, C.byref(be), C.byref(br),
+                                         C.byref(d)))
+        return d
+
+    def bind_moe_accumulate(self, n: int, weight: float, expert, accumulator) -> L.MoeAccumulateDispatch:
+        d = L.MoeAccumulateDispatch()
+        be, ba = _buf(expert), _buf(accumulator)
+        check(L.lib().s14_bind_moe_accumulate(self._h(), n, weight, C.byref(be), C.byref(ba),
+                                              C.byref(d)))
+        return d
+
+    def _stream(self, stream):
+        return stream if stream is not None else _torch_stream()
+
+    def cmd_mxfp4_matvec(self, dispatch, stream=None) -> None:
+        check(L.lib().s14_cmd_mxfp4_matvec(self._h(), self._stream(stream), C.byref(dispatch)))
+
+    def cmd_fp8_matvec(self, dispatch, stream=None) -> None:
+        check(L.lib().s14_cmd_fp8_matvec(self._h(), self._stream(stream), C.byref(dispatch)))
+
+    def cmd_swiglu_limit(self, dispatch, stream=None) -> None:
+        check(L.lib().s14_cmd_swiglu_limit(self._h(), self._stream(stream), C.byref(dispatch)))
+
+    def cmd_route_mix(self, dispatch, stream=None) -> None:
+        check(L.lib().s14_cmd_route_mix(self._h(), self._stream(stream), C.byref(dispatch)))
+
+    def cmd_moe_accumulate(self, dispatch, stream=None) -> None:
+        check(L.lib().s14_cmd_moe_accumulate(self._h(), self._stream(stream), C.byref(dispatch)))
+
+
+def _key(layer: int, kind: int, slot: int) -> L.ExpertKey:
+    return L.ExpertKey(layer, kind, slot)
+
+
+class VramPool:
+    """Fixed-slot page pool (vram_pool.rs:62-422).  ``ctx=None`` gives the bookkeeping-only
+    pool the reference's unit tests build with ``new_for_tests``."""
+
+    def __init__(self, ctx: Optional[S14Context], n_slots: int, slot_bytes: int):
+        h = C.c_void_p()
+        check(L.lib().s14_pool_create(ctx.handle if ctx is not None else None, n_slots, slot_bytes,
+                                      C.byref(h)))
+        self._h = h
+        self._ctx = ctx
+
+    def close(self) -> None:
+        if self._h:
+            L.lib().s14_pool_destroy(self._h)
+            self._h = None
+
+    def __del__(self):
+        try:
+            self.close()
+        except Exception:
+            pass
+
+    @property
+    def handle(self):
+        return self._h
+
+    def capacity(self) -> int:
+        return L.lib().s14_pool_capacity(self._h)
+
+    def slot_bytes(self) -> int:
+        return L.lib().s14_pool_slot_bytes(self._h)
+
+    def n_loaded(self) -> int:
+        return L.lib().s14_pool_n_loaded(self._h)
+
+    def total_bytes(self) -> int:
+        return L.lib().s14_pool_total_bytes(self._h)
+
+    def slot_offset(self, slot: int) -> int:
+        return L.lib().s14_pool_slot_offset(self._h, slot)
+
+    def slot_ptr(self, slot: int) -> Optional[int]:
+        return L.lib().s14_pool_slot_ptr(self._h, slot)
+
+    def lookup(self, key: L.ExpertKey) -> Optional[int]:
+        found, slot = C.c_int32(), C.c_uint32()
+        check(L.lib().s14_pool_lookup(self._h, key, C.byref(found), C.byref(slot)))
+        return slot.value if found.value else None
+
+    def lookup_and_pin(self, key: L.ExpertKey) -> Optional[L.SlotBinding]:
+        found, lease = C.c_int32(), L.SlotBinding()
+        check(L.lib().s14_pool_lookup_and_pin(self._h, key, C.byref(found), C.byref(lease)))
+        return lease if found.value else None
+
+    def reserve_loading_generation(self, key: L.ExpertKey) -> L.LoadingReservation:
+        r = L.LoadingReservation()
+        check(L.lib().s14_pool_reserve_loading_generation(self._h, key, C.byref(r)))
+        return r
+
+    def reserve_loading(self, key: L.ExpertKey):
+        """(slot, evicted key or None), vram_pool.rs:172-175."""
+        r = self.reserve_loading_generation(key)
+        return r.slot, (r.evicted if r.has_evicted else None)
+
+    def mark_ready(self, slot: int, key: L.ExpertKey) -> None:
+        check(L.lib().s14_pool_mark_ready(self._h, slot, key))
+
+    @staticmethod
+    def _arr(reservations):
+        arr = (L.LoadingReservation * max(1, len(reservations)))()
+        for i, r in enumerate(reservations):
+            arr[i] = r
+        return arr
+
+    def validate_publish_batch(self, reservations) -> None:
+        check(L.lib().s14_pool_validate_publish_batch(self._h, self._arr(reservations), len(reservations)))
+
+    def publish_batch_and_pin(self, reservations) -> List[L.SlotBinding]:
+        out = (L.SlotBinding * max(1, len(reservations)))()
+        check(L.lib().s14_pool_publish_batch_and_pin(self._h, self._arr(reservations),
+                                                     len(reservations), out))
+        return [L.SlotBinding.from_buffer_copy(out[i]) for i in range(len(reservations))]
+
+    def validate_binding(self, binding: L.SlotBinding) -> None:
+        check(L.lib().s14_pool_validate_binding(self._h, binding))
+
+    def release_after_compute_fence(self, lease: L.SlotBinding) -> None:
+        check(L.lib().s14_pool_release_after_compute_fence(self._h, lease))
+
+    def cancel_loading(self, slot: int, key: L.ExpertKey) -> None:
+        check(L.lib().s14_pool_cancel_loading(self._h, slot, key))
+
+    def cancel_reservation(self, reservation: L.LoadingReservation) -> None:
+        check(L.lib().s14_pool_cancel_reservation(self._h, reservation))
+
+    # upload engine (the reference's ExpertLoader on a transfer queue)
+    def upload_page_async(self, reservation: L.LoadingReservation, host_ptr: int, nbytes: int) -> None:
+        check(L.lib().s14_pool_upload_page_async(self._h, C.byref(reservation), host_ptr, nbytes))
+
+    def transfer_fence(self) -> None:
+        check(L.lib().s14_pool_transfer_fence(self._h))
+
+    def wait_transfer_fence(self) -> None:
+        check(L.lib().s14_pool_wait_transfer_fence(self._h))
+
+    def compute_wait_transfer(self, stream: Optional[int] = None) -> None:
+        check(L.lib().s14_pool_compute_wait_transfer(
+            self._h, stream if stream is not None else _torch_stream()))
+
+
+ExpertKey = _key
+
+
+@dataclass
+class RouteDecision:
+    """runner.rs:121-126.  ``kind``: 0 hash router (layers 0-2), 1 score router."""
+
+    layer: int
+    kind: int
+    expert_ids: List[int] = field(default_factory=list)
+    weights: List[float] = field(default_factory=list)
+
+    def _c(self) -> L.RouteDecisionC:
+        c = L.RouteDecisionC()
+        c.layer, c.kind = self.layer, self.kind
+        n = min(len(self.expert_ids), len(self.weights))
+        if len(self.expert_ids) != len(self.weights) or n > L.EXPERTS_PER_TOKEN:
+            c.n = 0xFFFF  # rejected by the library: not six ids and six weights
+            return c
+        c.n = n
+        for i in range(n):
+            c.expert_ids[i] = self.expert_ids[i]
+            c.weights[i] = self.weights[i]
+        return c
+
+    def validate_for(self, profile: int = L.PROFILE_S14_TOP6) -> None:
+        c = self._c()
+        check(L.lib().s14_route_validate_for(C.byref(c), profile))
+
+
+class RouteLoadBatch:
+    def __init__(self, handle, route: RouteDecision):
+        self._h = handle
+        self.layer = route.layer
+        self.expert_ids = list(route.expert_ids)
+        self.route_weights = list(route.weights)
+
+    def missing(self):
+        """[(reservation, is_shared)] for the pages that still need an upload."""
+        res = (L.LoadingReservation * 7)()
+        shared = (C.c_int32 * 7)()
+        n = C.c_uint32()
+        check(L.lib().s14_route_load_batch_missing(self._h, res, shared, C.byref(n)))
+        return [(L.LoadingReservation.from_buffer_copy(res[i]), bool(shared[i])) for i in range(n.value)]
+
+
+class S14MoeComputeLeaseBatch:
+    def __init__(self, handle):
+        self._h = handle
+        routed = (L.SlotBinding * L.EXPERTS_PER_TOKEN)()
+        shared = L.SlotBinding()
+        ids = (C.c_uint16 * L.EXPERTS_PER_TOKEN)()
+        w = (C.c_float * L.EXPERTS_PER_TOKEN)()
+        check(L.lib().s14_moe_compute_lease_bindings(handle, routed, C.byref(shared), ids, w))
+        self._routed = [L.SlotBinding.from_buffer_copy(routed[i]) for i in range(L.EXPERTS_PER_TOKEN)]
+        self._shared = shared
+        self._ids = [int(v) for v in ids]
+        self._w = [float(v) for v in w]
+
+    def routed_bindings(self):
+        return self._routed
+
+    def shared_binding(self):
+        return self._shared
+
+    def expert_ids(self):
+        return self._ids
+
+    def route_weights(self):
+        return self._w
+
+
+class S14MoePages:
+    """All-or-nothing page transaction over six routed pages and the shared page
+    (S14VulkanMoePages, s14_vulkan.rs:703-819)."""
+
+    def __init__(self, routed_pool: VramPool, shared_pool: VramPool, profile: int = L.PROFILE_S14_TOP6,
+                 min_routed_bytes: int = L.EXPERT_PAGE_BYTES,
+                 min_shared_bytes: int = L.SHARED_EXPERT_PAGE_BYTES):
+        h = C.c_void_p()
+        check(L.lib().s14_moe_pages_create_ex(routed_pool.handle, shared_pool.handle, profile,
+                                              min_routed_bytes, min_shared_bytes, C.byref(h)))
+        self._h = h
+        self.routed_pool, self.shared_pool = routed_pool, shared_pool
+
+    def __del__(self):
+        try:
+            if self._h:
+                L.lib().s14_moe_pages_destroy(self._h)
+                self._h = None
+        except Exception:
+            pass
+
+    def begin_after_official_route(self, route: RouteDecision) -> RouteLoadBatch:
+        c = route._c()
+        h = C.c_void_p()
+        check(L.lib().s14_moe_pages_begin_after_official_route(self._h, C.byref(c), C.byref(h)))
+        return RouteLoadBatch(h, route)
+
+    def publish_after_transfer_fence(self, batch: RouteLoadBatch) -> S14MoeComputeLeaseBatch:
+        h = C.c_void_p()
+        handle, batch._h = batch._h, None  # consumed either way
+        check(L.lib().s14_moe_pages_publish_after_transfer_fence(self._h, handle, C.byref(h)))
+        return S14MoeComputeLeaseBatch(h)
+
+    def release_after_compute_fence(self, lease: S14MoeComputeLeaseBatch) -> None:
+        check(L.lib().s14_moe_pages_release_after_compute_fence(self._h, lease._h))
+        lease._h = None
+
+    def cancel(self, batch: RouteLoadBatch) -> None:
+        handle, batch._h = batch._h, None
+        check(L.lib().s14_moe_pages_cancel(self._h, handle))

@@ -1,0 +1,420 @@
+/*
+ * polaris_s14_cuda.h - C ABI of the B200 (sm_100a) implementation of the S14 MoE
+ * expert hot path: MXFP4 w1/w3 matvec -> limit-10 SwiGLU -> w2 matvec ->
+ * route-weighted mix over the routed experts plus the shared expert, the FP8
+ * E4M3 block-scaled projection matvec, and the router's (score+bias) top-k.
+ *
+ * This is the boundary a Rust `-sys` crate (or any FFI) binds.  Every entry
+ * point names the reference interface it stands in for, by file:line inside
+ * the reference project.  Conventions:
+ *   - plain pointers and sizes only; device buffers are {pointer, size} pairs;
+ *   - every call returns an int32 status (0 = ok); the message of the last
+ *     failure on the calling thread is returned by s14_last_error();
+ *   - `stream` is a cudaStream_t passed as void* (NULL = the context's compute
+ *     stream); "cmd_" calls only enqueue work, exactly as the reference's
+ *     cmd_* calls only record into a command buffer: uploads, ordering against
+ *     other streams and read-back stay with the caller;
+ *   - a context is bound to one device and is not thread-safe.
+ * There is no CPU fallback anywhere behind this header.
+ */
+#ifndef POLARIS_S14_CUDA_H
+#define POLARIS_S14_CUDA_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define S14_API __attribute__((visibility("default")))
+
+/* ---- status codes -------------------------------------------------------- */
+#define S14_OK 0
+#define S14_ERR_CONTRACT 1 /* shape / capacity / weight / route contract violated */
+#define S14_ERR_CUDA 2     /* a CUDA runtime call failed */
+#define S14_ERR_POOL 3     /* page pool state: full, stale generation, not loading ... */
+#define S14_ERR_CODE 4     /* a NaN code (UE8M0 0xFF, E4M3 0x7F/0xFF) in a payload */
+#define S14_ERR_DEVICE 5   /* the device status word reported a problem */
+
+/* reference: scheduler/s14_runner/src/memory.rs:3, ssd_inference/src/s14_vulkan.rs:14-18 */
+#define S14_EXPERT_PAGE_BYTES 13369344ull
+#define S14_SHARED_EXPERT_PAGE_BYTES 25167360ull
+#define S14_ROUTED_EXPERT_KIND 0x53
+#define S14_SHARED_EXPERT_KIND 0x54
+/* reference: scheduler/s14_runner/src/contract.rs:6-13 */
+#define S14_HIDDEN_SIZE 4096u
+#define S14_N_ROUTED_EXPERTS 256u
+#define S14_EXPERTS_PER_TOKEN 6u
+#define S14_MAX_BLOCK_TOKENS 8u /* largest exact-cascade verify block, cascade.rs:19 */
+
+/* Page encodings understood by the fused layer kernels. */
+#define S14_PAGE_MXFP4 0u /* [w1][w3][w2] E2M1 codes, then [s1][s3][s2] UE8M0 per 32 */
+#define S14_PAGE_FP8 1u   /* [w1][w3][w2] E4M3 codes, then [s1][s3][s2] UE8M0 per 128x128 */
+
+/* Summation order of every matvec of a context.
+ *   S14_ACCUM_PAIRWISE  : lanes of a warp split K; products are accumulated in F32
+ *                         inside one scale block and in F64 across blocks, lanes
+ *                         and warps, then rounded to F32 once (the fast path).
+ *   S14_ACCUM_REFERENCE : one thread per output row, k ascending, two separate
+ *                         multiply-then-add steps per packed byte, (x*w)*s - the
+ *                         exact evaluation order of the reference's F32 CPU code
+ *                         (examples/s14_vulkan_numeric.rs:1669-1714); bit-identical
+ *                         to it, and slower. */
+#define S14_ACCUM_PAIRWISE 0u
+#define S14_ACCUM_REFERENCE 1u
+
+/* Router score function (executor.py:641-642 uses sqrt(softplus)). */
+#define S14_SCORE_SIGMOID 0u
+#define S14_SCORE_SQRT_SOFTPLUS 1u
+
+/* FP8 block-scale storage (s14_fp8_matvec.comp:51-53 uses UE8M0 bytes;
+ * local_s14_primitives/fp8.py:37-46 also accepts floats). */
+#define S14_SCALE_UE8M0 0u
+#define S14_SCALE_F32 1u
+
+typedef struct s14_ctx s14_ctx;
+typedef struct s14_pool s14_pool;
+typedef struct s14_moe_pages s14_moe_pages;
+
+S14_API const char *s14_last_error(void);
+
+/* ---- context: replaces VulkanContext::init + S14NumericPipelines::new/destroy
+ *      (ssd_inference/src/device.rs:26-76, s14_vulkan.rs:195-205, 417-424) ------ */
+S14_API int32_t s14_ctx_create(int32_t device, s14_ctx **out);
+S14_API int32_t s14_ctx_destroy(s14_ctx *ctx);
+S14_API void *s14_ctx_compute_stream(s14_ctx *ctx);
+S14_API void *s14_ctx_copy_stream(s14_ctx *ctx);
+S14_API int32_t s14_ctx_synchronize(s14_ctx *ctx);
+S14_API int32_t s14_ctx_set_accumulation(s14_ctx *ctx, uint32_t mode);
+S14_API uint32_t s14_ctx_accumulation(const s14_ctx *ctx);
+S14_API int32_t s14_ctx_sm_count(const s14_ctx *ctx);
+/* Reads and clears the device status word (0 = no kernel reported a problem). */
+S14_API int32_t s14_ctx_device_status(s14_ctx *ctx, uint32_t *status);
+/* Number of kernels this context has launched since creation. */
+S14_API uint64_t s14_ctx_launch_count(const s14_ctx *ctx);
+
+/* ---- byte contracts: S14MatvecShape (s14_vulkan.rs:40-114) ------------------- */
+typedef struct {
+    uint32_t n;
+    uint32_t k;
+} s14_matvec_shape;
+
+S14_API int32_t s14_shape_new(uint32_t n, uint32_t k, s14_matvec_shape *out);
+S14_API int32_t s14_shape_validate_mxfp4(s14_matvec_shape shape);
+S14_API int32_t s14_shape_validate_fp8(s14_matvec_shape shape);
+S14_API int32_t s14_shape_fp32_input_bytes(s14_matvec_shape shape, uint64_t *out);
+S14_API int32_t s14_shape_fp32_output_bytes(s14_matvec_shape shape, uint64_t *out);
+S14_API int32_t s14_shape_mxfp4_weight_bytes(s14_matvec_shape shape, uint64_t *out);
+S14_API int32_t s14_shape_mxfp4_scale_bytes(s14_matvec_shape shape, uint64_t *out);
+S14_API int32_t s14_shape_fp8_weight_bytes(s14_matvec_shape shape, uint64_t *out);
+S14_API int32_t s14_shape_fp8_scale_bytes(s14_matvec_shape shape, uint64_t *out);
+
+/* validate_ue8m0_codes / validate_e4m3fn_codes (s14_vulkan.rs:143-156): host
+ * bytes, checked before upload.  On failure *bad_index (may be NULL) receives the
+ * first offending byte. */
+S14_API int32_t s14_validate_ue8m0_codes(const uint8_t *codes, uint64_t len, uint64_t *bad_index);
+S14_API int32_t s14_validate_e4m3fn_codes(const uint8_t *codes, uint64_t len, uint64_t *bad_index);
+
+/* ---- the five primitive operators: S14NumericPipelines::bind_* / cmd_*
+ *      (s14_vulkan.rs:207-415).  bind validates shapes and capacities and fills a
+ *      dispatch record; cmd enqueues it. ---------------------------------------- */
+typedef struct {
+    void *ptr;     /* device pointer */
+    uint64_t size; /* bytes available at ptr */
+} s14_buffer;
+
+typedef struct {
+    s14_matvec_shape shape;
+    const float *x;
+    const uint8_t *packed_weight;
+    const uint8_t *weight_scale;
+    float *y;
+} s14_mxfp4_dispatch;
+
+typedef struct {
+    s14_matvec_shape shape;
+    uint32_t scale_format; /* S14_SCALE_UE8M0 | S14_SCALE_F32 */
+    uint32_t n_tokens;     /* 1..8 rows of x / y, row stride k / n floats */
+    const float *x;
+    const uint8_t *weight;
+    const void *weight_scale;
+    float *y;
+} s14_fp8_dispatch;
+
+typedef struct {
+    uint32_t n;
+    const float *gate;
+    const float *up;
+    float *y;
+} s14_swiglu_limit_dispatch;
+
+typedef struct {
+    uint32_t n;
+    float route_weight;
+    const float *expert;
+    float *routed;
+} s14_route_mix_dispatch;
+
+typedef struct {
+    uint32_t n;
+    float weight;
+    const float *expert;
+    float *accumulator;
+} s14_moe_accumulate_dispatch;
+
+/* bind_mxfp4 (s14_vulkan.rs:207-237) / cmd_mxfp4_matvec (:338-351) */
+S14_API int32_t s14_bind_mxfp4(s14_ctx *ctx, s14_matvec_shape shape, const s14_buffer *x,
+                               const s14_buffer *packed_weight, const s14_buffer *weight_scale,
+                               const s14_buffer *y, s14_mxfp4_dispatch *out);
+S14_API int32_t s14_cmd_mxfp4_matvec(s14_ctx *ctx, void *stream, const s14_mxfp4_dispatch *dispatch);
+
+/* bind_fp8 (s14_vulkan.rs:239-269) / cmd_fp8_matvec (:355-368).  The _ex form adds
+ * the two options the reference's callers need around it: F32 block scales and
+ * 1..8 tokens per weight pass. */
+S14_API int32_t s14_bind_fp8(s14_ctx *ctx, s14_matvec_shape shape, const s14_buffer *x,
+                             const s14_buffer *weight, const s14_buffer *weight_scale,
+                             const s14_buffer *y, s14_fp8_dispatch *out);
+S14_API int32_t s14_bind_fp8_ex(s14_ctx *ctx, s14_matvec_shape shape, uint32_t scale_format,
+                                uint32_t n_tokens, const s14_buffer *x, const s14_buffer *weight,
+                                const s14_buffer *weight_scale, const s14_buffer *y,
+                                s14_fp8_dispatch *out);
+S14_API int32_t s14_cmd_fp8_matvec(s14_ctx *ctx, void *stream, const s14_fp8_dispatch *dispatch);
+
+/* bind_swiglu_limit (s14_vulkan.rs:271-291) / cmd_swiglu_limit (:370-384) */
+S14_API int32_t s14_bind_swiglu_limit(s14_ctx *ctx, uint32_t n, const s14_buffer *gate,
+                                      const s14_buffer *up, const s14_buffer *y,
+                                      s14_swiglu_limit_dispatch *out);
+S14_API int32_t s14_cmd_swiglu_limit(s14_ctx *ctx, void *stream,
+                                     const s14_swiglu_limit_dispatch *dispatch);
+
+/* bind_route_mix (s14_vulkan.rs:293-314) / cmd_route_mix (:386-400): routed = w * expert */
+S14_API int32_t s14_bind_route_mix(s14_ctx *ctx, uint32_t n, float route_weight,
+                                   const s14_buffer *expert, const s14_buffer *routed,
+                                   s14_route_mix_dispatch *out);
+S14_API int32_t s14_cmd_route_mix(s14_ctx *ctx, void *stream, const s14_route_mix_dispatch *dispatch);
+
+/* bind_moe_accumulate (s14_vulkan.rs:316-334) / cmd_moe_accumulate (:402-415):
+ * accumulator += w * expert */
+S14_API int32_t s14_bind_moe_accumulate(s14_ctx *ctx, uint32_t n, float weight,
+                                        const s14_buffer *expert, const s14_buffer *accumulator,
+                                        s14_moe_accumulate_dispatch *out);
+S14_API int32_t s14_cmd_moe_accumulate(s14_ctx *ctx, void *stream,
+                                       const s14_moe_accumulate_dispatch *dispatch);
+
+/* ---- fused layer: the 35-dispatch recording of
+ *      examples/s14_vulkan_numeric.rs:1143-1218 as two or three kernels ---------- */
+
+/* One token's route as the reference hands it over (RouteDecision,
+ * s14_runner/src/runner.rs:121-126) with the pages already resolved to device
+ * addresses of pinned pool slots (SlotBinding -> slot_offset,
+ * vram_pool.rs:30-35, 397-399). */
+typedef struct {
+    uint32_t n_routed;                             /* 1..S14_EXPERTS_PER_TOKEN */
+    uint16_t expert_ids[S14_EXPERTS_PER_TOKEN];    /* identity, used to group tokens */
+    float weights[S14_EXPERTS_PER_TOKEN];          /* finite, >= 0 */
+    const uint8_t *pages[S14_EXPERTS_PER_TOKEN];   /* MXFP4 pages, device addresses */
+} s14_token_route;
+
+typedef struct {
+    uint32_t hidden;       /* K of w1/w3, N of w2 (multiple of 1024, <= 8192) */
+    uint32_t inter;        /* N of w1/w3, K of w2 (multiple of 1024, <= 8192) */
+    uint32_t n_tokens;     /* 1..S14_MAX_BLOCK_TOKENS */
+    uint32_t shared_kind;  /* S14_PAGE_MXFP4 | S14_PAGE_FP8 */
+    const uint8_t *shared_page; /* device address, NULL = no shared expert */
+    const s14_token_route *routes; /* host array [n_tokens] */
+    const float *x;        /* device [n_tokens, hidden] */
+    float *y;              /* device [n_tokens, hidden] */
+} s14_moe_layer_desc;
+
+/* Enqueue one MoE layer for 1..8 tokens: every distinct expert's weights are read
+ * once for all tokens routed to it; per token the routed outputs are mixed in
+ * route order, then the shared output is added with weight 1
+ * (examples/s14_vulkan_numeric.rs:929-947).  Uses the context's scratch. */
+S14_API int32_t s14_cmd_moe_layer(s14_ctx *ctx, void *stream, const s14_moe_layer_desc *desc);
+
+/* Router (s14_first_real_token/executor.py:638-668): logits = x . Wr^T with Wr
+ * BF16 [n_experts, hidden]; score = sigmoid | sqrt(softplus); select top_k of
+ * score + bias (ties -> lowest index, descending order); weights = score[idx] /
+ * sum * route_scale.  ids_out int32 [n_tokens, top_k], weights_out F32 likewise,
+ * both device memory.  bias may be NULL. */
+typedef struct {
+    uint32_t n_experts; /* <= 256 */
+    uint32_t hidden;    /* multiple of 256 */
+    uint32_t n_tokens;  /* 1..8 */
+    uint32_t top_k;     /* 1..8 */
+    uint32_t score_fn;
+    float route_scale;
+    const float *x;
+    const uint16_t *router_weight_bf16;
+    const float *bias;
+    int32_t *ids_out;
+    float *weights_out;
+} s14_router_desc;
+
+S14_API int32_t s14_cmd_router(s14_ctx *ctx, void *stream, const s14_router_desc *desc);
+
+/* Router + layer without a host round trip for one decode token: the router's
+ * ids index `page_table` (device array [n_experts] of device page addresses, all
+ * resident).  ids_out / weights_out (device, may be NULL) receive the route. */
+typedef struct {
+    s14_router_desc router; /* n_tokens must be 1; ids_out/weights_out optional */
+    uint32_t inter;
+    uint32_t shared_kind;
+    const uint8_t *const *page_table;
+    const uint8_t *shared_page;
+    float *y;
+} s14_routed_layer_desc;
+
+S14_API int32_t s14_cmd_routed_moe_layer(s14_ctx *ctx, void *stream,
+                                         const s14_routed_layer_desc *desc);
+
+/* LM head (local_s14_primitives/final_head.py:113-149): logits[v] = x . W[v,:]
+ * for the rows [row_begin, row_begin + n_rows) of a BF16 [vocab, hidden] matrix
+ * whose first stored row is row_begin (a vocabulary shard); logits_out points at
+ * the shard's first logit.  n_tokens 1..8. */
+S14_API int32_t s14_cmd_head_logits(s14_ctx *ctx, void *stream, const float *x, uint32_t n_tokens,
+                                    const uint16_t *weight_bf16, uint32_t n_rows, uint32_t hidden,
+                                    float *logits_out, uint32_t logits_stride);
+
+/* greedy_full_vocab_argmax (s14_runner/src/runner.rs:485-508): lowest id wins
+ * ties; a NaN anywhere yields -1.  result is a device int64. */
+S14_API int32_t s14_cmd_greedy_argmax(s14_ctx *ctx, void *stream, const float *logits,
+                                      uint32_t vocab, int64_t *result);
+
+/* The same layer for a caller that holds x and y in host memory (pinned or
+ * pageable): copies host_x [n_tokens, hidden] to context-owned device staging,
+ * runs the layer on the resident pages named by desc (desc->x / desc->y are
+ * ignored), copies the result to host_y and waits for it. */
+S14_API int32_t s14_moe_layer_host(s14_ctx *ctx, const s14_moe_layer_desc *desc, const float *host_x,
+                                   float *host_y);
+
+/* ---- page pool: VramPool (ssd_inference/src/vram_pool.rs:16-422) ------------- */
+typedef struct {
+    uint32_t layer;
+    uint8_t kind;
+    uint32_t slot;
+} s14_expert_key;
+
+typedef struct {
+    s14_expert_key key;
+    uint32_t slot;
+    uint64_t generation;
+} s14_slot_binding; /* a SlotLease carries exactly one of these */
+
+typedef struct {
+    s14_expert_key key;
+    uint32_t slot;
+    uint64_t generation;
+    int32_t has_evicted;
+    s14_expert_key evicted;
+} s14_loading_reservation;
+
+/* VramPool::new (vram_pool.rs:76-114): one cudaMalloc of n_slots * slot_bytes.
+ * ctx == NULL builds the bookkeeping-only pool the reference's unit tests use
+ * (new_for_tests, vram_pool.rs:408-421): no device memory, slot addresses NULL. */
+S14_API int32_t s14_pool_create(s14_ctx *ctx, uint32_t n_slots, uint64_t slot_bytes, s14_pool **out);
+S14_API int32_t s14_pool_destroy(s14_pool *pool);
+S14_API uint32_t s14_pool_capacity(const s14_pool *pool);
+S14_API uint64_t s14_pool_slot_bytes(const s14_pool *pool);
+S14_API uint32_t s14_pool_n_loaded(const s14_pool *pool);
+S14_API uint64_t s14_pool_total_bytes(const s14_pool *pool);
+S14_API uint64_t s14_pool_slot_offset(const s14_pool *pool, uint32_t slot);
+S14_API void *s14_pool_slot_ptr(const s14_pool *pool, uint32_t slot);
+/* lookup (vram_pool.rs:130-138): *found = 0/1 */
+S14_API int32_t s14_pool_lookup(s14_pool *pool, s14_expert_key key, int32_t *found, uint32_t *slot);
+/* lookup_and_pin (:141-166) */
+S14_API int32_t s14_pool_lookup_and_pin(s14_pool *pool, s14_expert_key key, int32_t *found,
+                                        s14_slot_binding *lease);
+/* reserve_loading_generation (:178-243) */
+S14_API int32_t s14_pool_reserve_loading_generation(s14_pool *pool, s14_expert_key key,
+                                                    s14_loading_reservation *out);
+/* mark_ready (:246-268) */
+S14_API int32_t s14_pool_mark_ready(s14_pool *pool, uint32_t slot, s14_expert_key key);
+/* validate_publish_batch (:271-316) */
+S14_API int32_t s14_pool_validate_publish_batch(const s14_pool *pool,
+                                                const s14_loading_reservation *reservations,
+                                                uint32_t count);
+/* publish_batch_and_pin (:320-326) */
+S14_API int32_t s14_pool_publish_batch_and_pin(s14_pool *pool,
+                                               const s14_loading_reservation *reservations,
+                                               uint32_t count, s14_slot_binding *leases_out);
+/* validate_binding (:353-370) */
+S14_API int32_t s14_pool_validate_binding(const s14_pool *pool, s14_slot_binding binding);
+/* release_after_compute_fence (:372-376) */
+S14_API int32_t s14_pool_release_after_compute_fence(s14_pool *pool, s14_slot_binding lease);
+/* cancel_loading (:379-385) / cancel_reservation (:387-408) */
+S14_API int32_t s14_pool_cancel_loading(s14_pool *pool, uint32_t slot, s14_expert_key key);
+S14_API int32_t s14_pool_cancel_reservation(s14_pool *pool, s14_loading_reservation reservation);
+
+/* ExpertLoader::enqueue_from_buf / wait_all (ssd_inference/src/expert_loader.rs:
+ * 362-442, 286-297): copy `bytes` of a page from pinned host memory into the
+ * reserved slot with cudaMemcpyAsync on the context's copy stream.  The "transfer
+ * fence" is a CUDA event: s14_pool_transfer_fence records it after the uploads
+ * enqueued so far, s14_pool_wait_transfer_fence blocks the host on it, and
+ * s14_pool_compute_wait_transfer makes the compute stream wait for it. */
+S14_API int32_t s14_pool_upload_page_async(s14_pool *pool, const s14_loading_reservation *reservation,
+                                           const void *host_bytes, uint64_t bytes);
+S14_API int32_t s14_pool_transfer_fence(s14_pool *pool);
+S14_API int32_t s14_pool_wait_transfer_fence(s14_pool *pool);
+S14_API int32_t s14_pool_compute_wait_transfer(s14_pool *pool, void *compute_stream);
+/* Pinned host staging memory (GpuBuffer::new_staging, buffer.rs:56-75). */
+S14_API int32_t s14_host_alloc_pinned(uint64_t bytes, void **out);
+S14_API int32_t s14_host_free_pinned(void *ptr);
+
+/* ---- page transactions: S14VulkanMoePages (s14_vulkan.rs:661-819) ------------ */
+typedef struct {
+    uint8_t layer;
+    uint8_t kind; /* 0 = hash router, 1 = score router (RouterKind, contract.rs:27-31) */
+    uint16_t expert_ids[S14_EXPERTS_PER_TOKEN];
+    float weights[S14_EXPERTS_PER_TOKEN];
+    uint32_t n; /* number of ids/weights supplied; must be 6 */
+} s14_route_decision;
+
+#define S14_PROFILE_S14_TOP6 0u
+#define S14_PROFILE_FULL_DEPTH43_NATIVE_TOP6 1u
+
+/* RouteDecision::validate_for (s14_runner/src/runner.rs:128-180) */
+S14_API int32_t s14_route_validate_for(const s14_route_decision *route, uint32_t profile);
+
+typedef struct s14_route_load_batch s14_route_load_batch;       /* RouteLoadBatch */
+typedef struct s14_moe_compute_lease s14_moe_compute_lease;     /* S14MoeComputeLeaseBatch */
+
+/* S14VulkanMoePages::new (s14_vulkan.rs:709-734) */
+S14_API int32_t s14_moe_pages_create(s14_pool *routed_pool, s14_pool *shared_pool, uint32_t profile,
+                                     s14_moe_pages **out);
+/* The same with explicit minimum slot sizes (small test shapes; an MXFP4 shared
+ * expert needs only S14_EXPERT_PAGE_BYTES). */
+S14_API int32_t s14_moe_pages_create_ex(s14_pool *routed_pool, s14_pool *shared_pool, uint32_t profile,
+                                        uint64_t min_routed_bytes, uint64_t min_shared_bytes,
+                                        s14_moe_pages **out);
+S14_API int32_t s14_moe_pages_destroy(s14_moe_pages *pages);
+/* begin_after_official_route (:736-775).  On success *batch owns pins/reservations. */
+S14_API int32_t s14_moe_pages_begin_after_official_route(s14_moe_pages *pages,
+                                                         const s14_route_decision *route,
+                                                         s14_route_load_batch **batch);
+/* Pages of the batch that still need an upload (state Loading).  slots_out /
+ * is_shared_out have room for 7 entries; returns the count in *count. */
+S14_API int32_t s14_route_load_batch_missing(const s14_route_load_batch *batch,
+                                             s14_loading_reservation *reservations_out,
+                                             int32_t *is_shared_out, uint32_t *count);
+/* publish_after_transfer_fence (:777-800); consumes the batch either way. */
+S14_API int32_t s14_moe_pages_publish_after_transfer_fence(s14_moe_pages *pages,
+                                                           s14_route_load_batch *batch,
+                                                           s14_moe_compute_lease **lease);
+/* routed_bindings / shared_binding / expert_ids / route_weights (:683-701) */
+S14_API int32_t s14_moe_compute_lease_bindings(const s14_moe_compute_lease *lease,
+                                               s14_slot_binding routed_out[S14_EXPERTS_PER_TOKEN],
+                                               s14_slot_binding *shared_out,
+                                               uint16_t ids_out[S14_EXPERTS_PER_TOKEN],
+                                               float weights_out[S14_EXPERTS_PER_TOKEN]);
+/* release_after_compute_fence (:802-812); consumes the lease on success. */
+S14_API int32_t s14_moe_pages_release_after_compute_fence(s14_moe_pages *pages,
+                                                          s14_moe_compute_lease *lease);
+/* cancel (:814-818); consumes the batch. */
+S14_API int32_t s14_moe_pages_cancel(s14_moe_pages *pages, s14_route_load_batch *batch);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* POLARIS_S14_CUDA_H */

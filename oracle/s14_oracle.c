@@ -1,0 +1,426 @@
+/*
+ * CPU oracle for the S14 MoE expert hot path.  TEST INFRASTRUCTURE ONLY: nothing
+ * in the shipped library or in the Python package may link, load or call this
+ * file; only the test-suite, the smoke check and the benchmark's CPU-baseline
+ * leg use it, and there only as the checker or as the timed CPU reference.
+ *
+ * Every function restates, in plain C, the F32 CPU reference that the
+ * reference project keeps in
+ *   scheduler/ssd_inference/examples/s14_vulkan_numeric.rs
+ * (cited per function below as "numeric.rs:<lines>").  The evaluation order is
+ * kept exactly: one output row at a time, k ascending, two separate
+ * multiply-then-add steps per packed byte, `(x * decode) * scale` association,
+ * no fused multiply-add (build with -ffp-contract=off), libm expf for SiLU.
+ * Rows are independent, so the OpenMP loop over rows (the reference uses a
+ * rayon parallel iterator over rows, numeric.rs:1678, 1701) does not change any
+ * result bit.
+ *
+ * The "_f64" variants accumulate the same exact products in double and are used
+ * as the order-independent "truth" when reporting how far either F32
+ * evaluation order is from the real value.
+ *
+ * The router and LM-head functions restate the Python reference
+ *   fast16/research/polaris_meridian_v1/s14_first_real_token/executor.py:638-668
+ *   fast16/research/polaris_meridian_v1/local_s14_primitives/final_head.py:113-149
+ * with one stated deviation: logits are accumulated in double (the Python code
+ * leaves the F32 summation order to the BLAS it happens to run on), rounded to
+ * F32 once, so that selection is reproducible on any device.
+ *
+ * Parity pin: the decode tables and matvecs are checked against the reference's
+ * own known-answer vectors (local_s14_primitives/tests/test_primitives.py:37-112)
+ * and against outputs of the importable Python reference committed under
+ * tests/golden/.
+ */
+#include <math.h>
+#include <stddef.h>
+#include <stdint.h>
+#include <string.h>
+#ifdef _OPENMP
+#include <omp.h>
+#endif
+
+#define S14O_API __attribute__((visibility("default")))
+
+/* numeric.rs:1716-1724 */
+S14O_API float s14o_e2m1(uint8_t code) {
+    static const float magnitude[8] = {0.0f, 0.5f, 1.0f, 1.5f, 2.0f, 3.0f, 4.0f, 6.0f};
+    float value = magnitude[code & 7];
+    return (code & 8) ? -value : value;
+}
+
+/* numeric.rs:1726-1728: 2^(code-127); code 0 gives the subnormal 2^-127, 0xFF is
+ * rejected by the caller before any decode (s14_vulkan.rs:143-148). */
+S14O_API float s14o_ue8m0(uint8_t code) { return ldexpf(1.0f, (int)code - 127); }
+
+/* numeric.rs:1730-1743 */
+S14O_API float s14o_e4m3fn(uint8_t code) {
+    unsigned exponent = (code >> 3) & 0x0f;
+    unsigned mantissa = code & 7;
+    float magnitude;
+    if (exponent == 0) {
+        magnitude = (float)mantissa * ldexpf(1.0f, -9);
+    } else {
+        magnitude = (1.0f + (float)mantissa / 8.0f) * ldexpf(1.0f, (int)exponent - 7);
+    }
+    return (code & 0x80) ? -magnitude : magnitude;
+}
+
+S14O_API int s14o_max_threads(void) {
+#ifdef _OPENMP
+    return omp_get_max_threads();
+#else
+    return 1;
+#endif
+}
+
+S14O_API void s14o_set_threads(int n) {
+#ifdef _OPENMP
+    if (n > 0) omp_set_num_threads(n);
+#else
+    (void)n;
+#endif
+}
+
+/* numeric.rs:1669-1696.  W [n, k/2] bytes (low nibble = even k), S [n, k/32]. */
+S14O_API void s14o_mxfp4_matvec(const float *x, const uint8_t *packed_weight,
+                                const uint8_t *scale, uint32_t n_rows, uint32_t k,
+                                float *y) {
+    const size_t packed_k = k / 2, groups = k / 32;
+#pragma omp parallel for schedule(static)
+    for (int64_t n = 0; n < (int64_t)n_rows; ++n) {
+        float sum = 0.0f;
+        for (size_t group = 0; group < groups; ++group) {
+            const float s = s14o_ue8m0(scale[n * groups + group]);
+            const size_t pair_base = group * 16;
+            for (size_t pair_in_group = 0; pair_in_group < 16; ++pair_in_group) {
+                const size_t pair = pair_base + pair_in_group;
+                const uint8_t codes = packed_weight[n * packed_k + pair];
+                const size_t k0 = pair * 2;
+                sum += x[k0] * s14o_e2m1(codes & 0x0f) * s;
+                sum += x[k0 + 1] * s14o_e2m1(codes >> 4) * s;
+            }
+        }
+        y[n] = sum;
+    }
+}
+
+/* Same products, double accumulation, double result ("truth"). */
+S14O_API void s14o_mxfp4_matvec_f64(const double *x, const uint8_t *packed_weight,
+                                    const uint8_t *scale, uint32_t n_rows, uint32_t k,
+                                    double *y) {
+    const size_t packed_k = k / 2, groups = k / 32;
+#pragma omp parallel for schedule(static)
+    for (int64_t n = 0; n < (int64_t)n_rows; ++n) {
+        double sum = 0.0;
+        for (size_t group = 0; group < groups; ++group) {
+            const double s = ldexp(1.0, (int)scale[n * groups + group] - 127);
+            double part = 0.0;
+            for (size_t pair = group * 16; pair < group * 16 + 16; ++pair) {
+                const uint8_t codes = packed_weight[n * packed_k + pair];
+                part += x[pair * 2] * (double)s14o_e2m1(codes & 0x0f);
+                part += x[pair * 2 + 1] * (double)s14o_e2m1(codes >> 4);
+            }
+            sum += part * s;
+        }
+        y[n] = sum;
+    }
+}
+
+/* numeric.rs:1698-1714.  W [n, k] bytes, S [ceil(n/128), ceil(k/128)] UE8M0. */
+S14O_API void s14o_fp8_matvec(const float *x, const uint8_t *weight, const uint8_t *scale,
+                              uint32_t n_rows, uint32_t k, float *y) {
+    const size_t k_groups = ((size_t)k + 127) / 128;
+#pragma omp parallel for schedule(static)
+    for (int64_t n = 0; n < (int64_t)n_rows; ++n) {
+        const size_t scale_row = ((size_t)n / 128) * k_groups;
+        const size_t weight_row = (size_t)n * k;
+        float sum = 0.0f;
+        for (size_t k_index = 0; k_index < k; ++k_index) {
+            const float s = s14o_ue8m0(scale[scale_row + k_index / 128]);
+            sum += x[k_index] * s14o_e4m3fn(weight[weight_row + k_index]) * s;
+        }
+        y[n] = sum;
+    }
+}
+
+/* The same loop with one F32 scale per 128x128 block instead of a UE8M0 byte
+ * (the Python reference accepts either, local_s14_primitives/fp8.py:37-46). */
+S14O_API void s14o_fp8_matvec_f32scale(const float *x, const uint8_t *weight,
+                                       const float *scale, uint32_t n_rows, uint32_t k,
+                                       float *y) {
+    const size_t k_groups = ((size_t)k + 127) / 128;
+#pragma omp parallel for schedule(static)
+    for (int64_t n = 0; n < (int64_t)n_rows; ++n) {
+        const size_t scale_row = ((size_t)n / 128) * k_groups;
+        const size_t weight_row = (size_t)n * k;
+        float sum = 0.0f;
+        for (size_t k_index = 0; k_index < k; ++k_index) {
+            const float s = scale[scale_row + k_index / 128];
+            sum += x[k_index] * s14o_e4m3fn(weight[weight_row + k_index]) * s;
+        }
+        y[n] = sum;
+    }
+}
+
+/* Double-accumulated FP8 matvec; scale_is_f32 selects the scale format. */
+S14O_API void s14o_fp8_matvec_f64(const double *x, const uint8_t *weight, const void *scale,
+                                  int scale_is_f32, uint32_t n_rows, uint32_t k, double *y) {
+    const size_t k_groups = ((size_t)k + 127) / 128;
+#pragma omp parallel for schedule(static)
+    for (int64_t n = 0; n < (int64_t)n_rows; ++n) {
+        const size_t scale_row = ((size_t)n / 128) * k_groups;
+        const size_t weight_row = (size_t)n * k;
+        double sum = 0.0;
+        for (size_t kg = 0; kg < k_groups; ++kg) {
+            const double s = scale_is_f32
+                                 ? (double)((const float *)scale)[scale_row + kg]
+                                 : ldexp(1.0, (int)((const uint8_t *)scale)[scale_row + kg] - 127);
+            const size_t k_end = (kg * 128 + 128 < k) ? kg * 128 + 128 : k;
+            double part = 0.0;
+            for (size_t k_index = kg * 128; k_index < k_end; ++k_index)
+                part += x[k_index] * (double)s14o_e4m3fn(weight[weight_row + k_index]);
+            sum += part * s;
+        }
+        y[n] = sum;
+    }
+}
+
+/* numeric.rs:1543-1556: gate is limited from above only, up on both sides. */
+S14O_API void s14o_swiglu_limit(const float *gate, const float *up, uint32_t n, float *y) {
+    for (uint32_t i = 0; i < n; ++i) {
+        float g = gate[i] < 10.0f ? gate[i] : 10.0f;
+        float u = up[i];
+        if (u < -10.0f) u = -10.0f;
+        if (u > 10.0f) u = 10.0f;
+        y[i] = (g / (1.0f + expf(-g))) * u;
+    }
+}
+
+S14O_API void s14o_swiglu_limit_f64(const double *gate, const double *up, uint32_t n,
+                                    double *y) {
+    for (uint32_t i = 0; i < n; ++i) {
+        double g = gate[i] < 10.0 ? gate[i] : 10.0;
+        double u = up[i];
+        if (u < -10.0) u = -10.0;
+        if (u > 10.0) u = 10.0;
+        y[i] = (g / (1.0 + exp(-g))) * u;
+    }
+}
+
+/* One expert page as the library lays it out in a pool slot:
+ *   [w1 codes n_i*k_h/2][w3 codes][w2 codes n_h*k_i/2][s1][s3][s2]  (MXFP4)
+ *   [w1 n_i*k_h][w3][w2][s1][s3][s2]                                (FP8, UE8M0 128x128)
+ * hidden = k_h, intermediate = n_i. */
+typedef struct {
+    const uint8_t *w1, *w3, *w2, *s1, *s3, *s2;
+} s14o_expert_view;
+
+static s14o_expert_view mxfp4_view(const uint8_t *page, uint32_t hidden, uint32_t inter) {
+    s14o_expert_view v;
+    const size_t wb = (size_t)hidden * inter / 2, sb = (size_t)hidden * inter / 32;
+    v.w1 = page;
+    v.w3 = page + wb;
+    v.w2 = page + 2 * wb;
+    v.s1 = page + 3 * wb;
+    v.s3 = v.s1 + sb;
+    v.s2 = v.s3 + sb;
+    return v;
+}
+
+static size_t fp8_scale_bytes(uint32_t n, uint32_t k) {
+    return (((size_t)n + 127) / 128) * (((size_t)k + 127) / 128);
+}
+
+static s14o_expert_view fp8_view(const uint8_t *page, uint32_t hidden, uint32_t inter) {
+    s14o_expert_view v;
+    const size_t wb = (size_t)hidden * inter;
+    v.w1 = page;
+    v.w3 = page + wb;
+    v.w2 = page + 2 * wb;
+    v.s1 = page + 3 * wb;
+    v.s3 = v.s1 + fp8_scale_bytes(inter, hidden);
+    v.s2 = v.s3 + fp8_scale_bytes(inter, hidden);
+    return v;
+}
+
+/* numeric.rs:1296-1300 (single-expert chain): w1,w3 -> limited SwiGLU -> w2 ->
+ * multiply by the route weight.  work must hold 3*inter floats. */
+S14O_API void s14o_expert_chain_mxfp4(const float *x, const uint8_t *page, uint32_t hidden,
+                                      uint32_t inter, float route_weight, float *work,
+                                      float *down_out, float *y) {
+    s14o_expert_view v = mxfp4_view(page, hidden, inter);
+    float *gate = work, *up = work + inter, *h = work + 2 * (size_t)inter;
+    s14o_mxfp4_matvec(x, v.w1, v.s1, inter, hidden, gate);
+    s14o_mxfp4_matvec(x, v.w3, v.s3, inter, hidden, up);
+    s14o_swiglu_limit(gate, up, inter, h);
+    s14o_mxfp4_matvec(h, v.w2, v.s2, hidden, inter, down_out);
+    if (y)
+        for (uint32_t i = 0; i < hidden; ++i) y[i] = route_weight * down_out[i];
+}
+
+/* numeric.rs:929-947 (layer): acc = 0; for each routed expert in route order
+ * acc += w_e * down_e; then acc += down_shared (weight 1).  shared_kind: 0 =
+ * MXFP4 page, 1 = FP8 page (the reference's shared expert), 2 = no shared expert.
+ * work must hold 3*inter + hidden floats. */
+S14O_API void s14o_moe_layer(const float *x, const uint8_t *const *routed_pages,
+                             const float *route_weights, uint32_t n_routed,
+                             const uint8_t *shared_page, int shared_kind, uint32_t hidden,
+                             uint32_t inter, float *work, float *y) {
+    float *down = work + 3 * (size_t)inter;
+    for (uint32_t i = 0; i < hidden; ++i) y[i] = 0.0f;
+    for (uint32_t e = 0; e < n_routed; ++e) {
+        s14o_expert_chain_mxfp4(x, routed_pages[e], hidden, inter, 0.0f, work, down, NULL);
+        for (uint32_t i = 0; i < hidden; ++i) y[i] += route_weights[e] * down[i];
+    }
+    if (shared_kind == 0) {
+        s14o_expert_chain_mxfp4(x, shared_page, hidden, inter, 0.0f, work, down, NULL);
+        for (uint32_t i = 0; i < hidden; ++i) y[i] += down[i];
+    } else if (shared_kind == 1) {
+        s14o_expert_view v = fp8_view(shared_page, hidden, inter);
+        float *gate = work, *up = work + inter, *h = work + 2 * (size_t)inter;
+        s14o_fp8_matvec(x, v.w1, v.s1, inter, hidden, gate);
+        s14o_fp8_matvec(x, v.w3, v.s3, inter, hidden, up);
+        s14o_swiglu_limit(gate, up, inter, h);
+        s14o_fp8_matvec(h, v.w2, v.s2, hidden, inter, down);
+        for (uint32_t i = 0; i < hidden; ++i) y[i] += down[i];
+    }
+}
+
+/* The layer with every matvec, the activation and the mix carried in double.
+ * work must hold 3*inter + 2*hidden doubles. */
+S14O_API void s14o_moe_layer_f64(const float *x, const uint8_t *const *routed_pages,
+                                 const float *route_weights, uint32_t n_routed,
+                                 const uint8_t *shared_page, int shared_kind, uint32_t hidden,
+                                 uint32_t inter, double *work, double *y) {
+    double *gate = work, *up = work + inter, *h = work + 2 * (size_t)inter;
+    double *down = work + 3 * (size_t)inter, *xd = down + hidden;
+    for (uint32_t i = 0; i < hidden; ++i) {
+        y[i] = 0.0;
+        xd[i] = (double)x[i];
+    }
+    for (uint32_t e = 0; e <= n_routed; ++e) {
+        const int is_shared = (e == n_routed);
+        if (is_shared && shared_kind == 2) break;
+        const uint8_t *page = is_shared ? shared_page : routed_pages[e];
+        const double w = is_shared ? 1.0 : (double)route_weights[e];
+        if (is_shared && shared_kind == 1) {
+            s14o_expert_view v = fp8_view(page, hidden, inter);
+            s14o_fp8_matvec_f64(xd, v.w1, v.s1, 0, inter, hidden, gate);
+            s14o_fp8_matvec_f64(xd, v.w3, v.s3, 0, inter, hidden, up);
+            s14o_swiglu_limit_f64(gate, up, inter, h);
+            s14o_fp8_matvec_f64(h, v.w2, v.s2, 0, hidden, inter, down);
+        } else {
+            s14o_expert_view v = mxfp4_view(page, hidden, inter);
+            s14o_mxfp4_matvec_f64(xd, v.w1, v.s1, inter, hidden, gate);
+            s14o_mxfp4_matvec_f64(xd, v.w3, v.s3, inter, hidden, up);
+            s14o_swiglu_limit_f64(gate, up, inter, h);
+            s14o_mxfp4_matvec_f64(h, v.w2, v.s2, hidden, inter, down);
+        }
+        for (uint32_t i = 0; i < hidden; ++i) y[i] += w * down[i];
+    }
+}
+
+static float bf16_to_f32(uint16_t bits) {
+    uint32_t u = (uint32_t)bits << 16;
+    float f;
+    memcpy(&f, &u, 4);
+    return f;
+}
+
+/* executor.py:638-668.  Wr [n_experts, hidden] BF16 bits, bias [n_experts] F32 (may
+ * be NULL).  score_fn 0: sigmoid(logit); 1: sqrt(softplus(logit)) (the reference's
+ * router, softplus threshold 20 as in torch).  Selection: top_k largest of
+ * score+bias, order = descending value, ties -> lowest index.  Weights: unbiased
+ * score[idx] / sum(score[idx]) * route_scale, F32, summed in selection order.
+ * scores_out / select_out (n_experts each) may be NULL. */
+S14O_API void s14o_router(const float *x, const uint16_t *wr_bf16, const float *bias,
+                          uint32_t n_experts, uint32_t hidden, int score_fn, uint32_t top_k,
+                          float route_scale, int32_t *ids_out, float *weights_out,
+                          float *scores_out, float *select_out) {
+    float scores[4096], select[4096];
+    uint8_t taken[4096];
+    if (n_experts > 4096) n_experts = 4096;
+#pragma omp parallel for schedule(static)
+    for (int64_t e = 0; e < (int64_t)n_experts; ++e) {
+        double acc = 0.0;
+        const uint16_t *row = wr_bf16 + (size_t)e * hidden;
+        for (uint32_t k = 0; k < hidden; ++k) acc += (double)x[k] * (double)bf16_to_f32(row[k]);
+        const float logit = (float)acc;
+        double s;
+        if (score_fn == 0) {
+            s = 1.0 / (1.0 + exp(-(double)logit));
+        } else {
+            const double l = (double)logit;
+            s = sqrt(l > 20.0 ? l : log1p(exp(l)));
+        }
+        scores[e] = (float)s;
+        select[e] = scores[e] + (bias ? bias[e] : 0.0f);
+        taken[e] = 0;
+    }
+    for (uint32_t j = 0; j < top_k; ++j) {
+        int32_t best = -1;
+        for (uint32_t e = 0; e < n_experts; ++e) {
+            if (taken[e]) continue;
+            if (best < 0 || select[e] > select[best]) best = (int32_t)e;
+        }
+        taken[best] = 1;
+        ids_out[j] = best;
+    }
+    float sum = 0.0f;
+    for (uint32_t j = 0; j < top_k; ++j) sum += scores[ids_out[j]];
+    for (uint32_t j = 0; j < top_k; ++j) weights_out[j] = scores[ids_out[j]] / sum * route_scale;
+    if (scores_out) memcpy(scores_out, scores, n_experts * sizeof(float));
+    if (select_out) memcpy(select_out, select, n_experts * sizeof(float));
+}
+
+/* final_head.py:113-149: logits[v] = sum_k x[k] * float(W_bf16[v,k]).  Accumulated
+ * in double and rounded to F32 once (the reference leaves the F32 order to BLAS
+ * and itself accepts rtol 2e-7 / atol 3e-7 between two chunkings,
+ * tests/test_final_head.py:68-70). */
+S14O_API void s14o_head_logits(const float *x, const uint16_t *w_bf16, uint32_t vocab,
+                               uint32_t hidden, float *logits) {
+#pragma omp parallel for schedule(static)
+    for (int64_t v = 0; v < (int64_t)vocab; ++v) {
+        double acc = 0.0;
+        const uint16_t *row = w_bf16 + (size_t)v * hidden;
+        for (uint32_t k = 0; k < hidden; ++k) acc += (double)x[k] * (double)bf16_to_f32(row[k]);
+        logits[v] = (float)acc;
+    }
+}
+
+/* scheduler/s14_runner/src/runner.rs:485-508: greedy argmax over all logits,
+ * lowest id wins ties, any NaN rejects (-1). */
+S14O_API int64_t s14o_greedy_argmax(const float *logits, uint32_t vocab) {
+    int64_t best = -1;
+    for (uint32_t v = 0; v < vocab; ++v) {
+        if (isnan(logits[v])) return -1;
+        if (best < 0 || logits[v] > logits[best]) best = v;
+    }
+    return best;
+}
+
+/* numeric.rs:1745-1771.  out = {max_abs, mean_abs, rmse, max_rel(|ref|>1e-5)};
+ * returns -1 on a shape error or a non-finite value. */
+S14O_API int s14o_error_stats(const float *actual, const float *expected, uint64_t n,
+                              double out[4]) {
+    if (n == 0) return -1;
+    float max_abs = 0.0f, max_rel = 0.0f;
+    double sum_abs = 0.0, sum_square = 0.0;
+    for (uint64_t i = 0; i < n; ++i) {
+        const float a = actual[i], e = expected[i];
+        if (!isfinite(a) || !isfinite(e)) return -1;
+        const float delta = fabsf(a - e);
+        if (delta > max_abs) max_abs = delta;
+        sum_abs += (double)delta;
+        sum_square += (double)delta * (double)delta;
+        if (fabsf(e) > 1.0e-5f) {
+            const float rel = delta / fabsf(e);
+            if (rel > max_rel) max_rel = rel;
+        }
+    }
+    out[0] = max_abs;
+    out[1] = sum_abs / (double)n;
+    out[2] = sqrt(sum_square / (double)n);
+    out[3] = max_rel;
+    return 0;
+}

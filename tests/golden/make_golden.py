@@ -1,0 +1,203 @@
+"""Generates tests/golden/s14_golden.npz by running the reference's importable Python
+code (``fast16/research/polaris_meridian_v1``) on small seeded inputs.
+
+Run from the repository root where the reference checkout is available:
+
+    python tests/golden/make_golden.py /path/to/reference
+
+The resulting file is committed; the tests only read it and never need the reference
+itself.  Small inputs are stored next to the outputs; large random inputs are rebuilt by
+the tests from the same seeds with ``colormlm_b200.synth`` and checked against a SHA-256
+stored here.  Cases:
+
+* decode tables of all E2M1, UE8M0 and E4M3FN codes (``decode_*`` of the reference);
+* the reference's own deterministic MXFP4 fixture
+  (local_s14_primitives/tests/test_primitives.py:58-72) through ``fp4_linear`` with F32
+  and F64 accumulation;
+* a seeded MXFP4 matvec with the benchmark's value distribution through ``fp4_linear``;
+* the reference's FP8 fixture (test_primitives.py:97-112, seed 7) through
+  ``fp8_weight_linear`` with UE8M0 and with F32 block scales;
+* one expert chain and one 6+1 expert layer composed from ``fp4_linear``,
+  ``fp8_weight_linear`` and the reference's ``_limited_swiglu``
+  (s14_first_real_token/executor.py:706-710) in the order of
+  examples/s14_vulkan_numeric.rs:929-947, with F64 accumulation;
+* router outputs from the torch expressions of executor.py:638-668 (both score
+  functions);
+* LM-head logits through ``bf16_checkpoint_head_logits`` on the reference's seed-731
+  fixture (tests/test_final_head.py:22-30).
+"""
+from __future__ import annotations
+
+import hashlib
+import os
+import sys
+
+import numpy as np
+import torch
+import torch.nn.functional as F
+
+HERE = os.path.dirname(os.path.abspath(__file__))
+ROOT = os.path.dirname(os.path.dirname(HERE))
+sys.path.insert(0, ROOT)
+
+
+def _digest(*arrays) -> bytes:
+    h = hashlib.sha256()
+    for a in arrays:
+        h.update(np.ascontiguousarray(a).tobytes())
+    return h.digest()
+
+
+def main(reference_root: str) -> None:
+    sys.path.insert(0, reference_root)
+    from fast16.research.polaris_meridian_v1.local_s14_primitives import (
+        FP4_E2M1_VALUES, decode_fp8_e4m3fn, decode_ue8m0, fp4_linear, fp8_weight_linear)
+    from fast16.research.polaris_meridian_v1.local_s14_primitives.final_head import (
+        bf16_checkpoint_head_logits)
+    from fast16.research.polaris_meridian_v1.s14_first_real_token.executor import (
+        NativeLayerReference)
+
+    from colormlm_b200 import synth
+    from colormlm_b200.pages import ExpertPageLayout
+
+    swiglu = NativeLayerReference._limited_swiglu
+    out = {}
+
+    # decode tables
+    out["e2m1_table"] = np.asarray(FP4_E2M1_VALUES, dtype=np.float32)
+    out["ue8m0_table"] = decode_ue8m0(torch.arange(255, dtype=torch.uint8)).numpy()
+    codes = torch.tensor([c for c in range(256) if c not in (0x7F, 0xFF)], dtype=torch.uint8)
+    out["e4m3_codes"] = codes.numpy()
+    out["e4m3_table"] = decode_fp8_e4m3fn(codes).numpy()
+
+    # the reference's deterministic MXFP4 fixture
+    packed = torch.arange(3 * 64, dtype=torch.uint8).reshape(3, 64)
+    scales = torch.tensor([[126, 127, 128, 129], [127, 128, 126, 127], [128, 126, 127, 128]],
+                          dtype=torch.uint8)
+    x = torch.sin(torch.arange(2 * 128, dtype=torch.float32).reshape(2, 128) * 0.013)
+    out["fx_packed"], out["fx_scales"], out["fx_x"] = packed.numpy(), scales.numpy(), x.numpy()
+    out["fx_y_f32"] = fp4_linear(x, packed, scales, output_dtype=torch.float32).numpy()
+    out["fx_y_f64"] = fp4_linear(x.double(), packed, scales, accumulation_dtype=torch.float64,
+                                 output_dtype=torch.float64).numpy()
+
+    # seeded MXFP4 matvec, benchmark distribution
+    g = synth.rng(1001)
+    n, k = 96, 1024
+    w = synth.mxfp4_codes(g, n, k)
+    s = synth.mxfp4_scales(g, n, k)
+    xv = synth.activations(g, 2, k)
+    out["mx_inputs_sha256"] = np.frombuffer(_digest(w, s, xv), dtype=np.uint8)
+    out["mx_y_f32"] = fp4_linear(torch.from_numpy(xv), torch.from_numpy(w), torch.from_numpy(s),
+                                 output_dtype=torch.float32).numpy()
+    out["mx_y_f64"] = fp4_linear(torch.from_numpy(xv).double(), torch.from_numpy(w), torch.from_numpy(s),
+                                 accumulation_dtype=torch.float64, output_dtype=torch.float64).numpy()
+
+    # the reference's FP8 fixture (seed 7), ragged 129 x 130
+    torch.manual_seed(7)
+    _raw_x = torch.randint(0, 255, (2, 130), dtype=torch.uint8)  # consumed to keep the stream aligned
+    raw_w = torch.randint(0, 255, (129, 130), dtype=torch.uint8)
+    raw_w[raw_w == 0x7F] = 0x7E
+    scale_w = torch.tensor([[127, 128], [126, 127]], dtype=torch.uint8)
+    logical_x = torch.sin(torch.arange(260, dtype=torch.float32).reshape(2, 130) * 0.01)
+    out["f8_w"], out["f8_s"], out["f8_x"] = raw_w.numpy(), scale_w.numpy(), logical_x.numpy()
+    out["f8_y"] = fp8_weight_linear(logical_x, raw_w, scale_w, output_chunk_size=41).numpy()
+    out["f8_y_f64"] = fp8_weight_linear(logical_x.double(), raw_w, scale_w, output_chunk_size=41,
+                                        accumulation_dtype=torch.float64,
+                                        output_dtype=torch.float64).numpy()
+    scale_f = torch.tensor([[0.011, 0.0071], [0.0093, 0.0127]], dtype=torch.float32)
+    out["f8_sf"] = scale_f.numpy()
+    out["f8_y_sf"] = fp8_weight_linear(logical_x, raw_w, scale_f, output_chunk_size=41).numpy()
+
+    # aligned FP8 projection, benchmark distribution (wq_a-like, smaller)
+    g = synth.rng(1002)
+    n8, k8 = 256, 512
+    w8 = synth.e4m3_codes(g, n8, k8)
+    s8 = synth.fp8_block_scales_ue8m0(g, n8, k8)
+    s8f = synth.fp8_block_scales_f32(g, n8, k8)
+    x8 = synth.activations(g, 4, k8)
+    out["p8_inputs_sha256"] = np.frombuffer(_digest(w8, s8, s8f, x8), dtype=np.uint8)
+    out["p8_y"] = fp8_weight_linear(torch.from_numpy(x8), torch.from_numpy(w8), torch.from_numpy(s8)).numpy()
+    out["p8_y_sf"] = fp8_weight_linear(torch.from_numpy(x8), torch.from_numpy(w8), torch.from_numpy(s8f)).numpy()
+
+    # expert chain and layer, F64 accumulation, hidden 1024 / inter 1024
+    hidden, inter = 1024, 1024
+    g = synth.rng(1003)
+    lay4 = ExpertPageLayout(hidden, inter, 0)
+    lay8 = ExpertPageLayout(hidden, inter, 1)
+    pages = [synth.mxfp4_expert_page(g, hidden, inter) for _ in range(7)]
+    page8 = synth.fp8_expert_page(g, hidden, inter)
+    xl = synth.activations(g, 1, hidden)[0]
+    weights = np.asarray([0.31, 0.22, 0.17, 0.13, 0.1, 0.07], dtype=np.float32)
+    # the pages are not stored (random bytes do not compress): the tests regenerate them
+    # from seed 1003 and check this digest
+    out["ly_inputs_sha256"] = np.frombuffer(_digest(*pages, page8, xl), dtype=np.uint8)
+    out["ly_w"] = weights
+
+    def t(a, shape):
+        return torch.from_numpy(np.ascontiguousarray(a)).reshape(shape)
+
+    def chain4(page, xin):
+        p = lay4.split(page)
+        xd = torch.from_numpy(xin).double()
+        kw = dict(accumulation_dtype=torch.float64, output_dtype=torch.float64)
+        gate = fp4_linear(xd, t(p["w1"], (inter, hidden // 2)), t(p["s1"], (inter, hidden // 32)), **kw)
+        up = fp4_linear(xd, t(p["w3"], (inter, hidden // 2)), t(p["s3"], (inter, hidden // 32)), **kw)
+        # the reference's SwiGLU runs in F32 (it calls .float()); keep that
+        h = swiglu(gate.float(), up.float())
+        return fp4_linear(h.double(), t(p["w2"], (hidden, inter // 2)), t(p["s2"], (hidden, inter // 32)), **kw)
+
+    def chain8(page, xin):
+        p = lay8.split(page)
+        xd = torch.from_numpy(xin).double()
+        nb_u = ((inter + 127) // 128, (hidden + 127) // 128)
+        nb_d = ((hidden + 127) // 128, (inter + 127) // 128)
+        gate = fp8_weight_linear(xd, t(p["w1"], (inter, hidden)), t(p["s1"], nb_u), accumulation_dtype=torch.float64, output_dtype=torch.float64)
+        up = fp8_weight_linear(xd, t(p["w3"], (inter, hidden)), t(p["s3"], nb_u), accumulation_dtype=torch.float64, output_dtype=torch.float64)
+        h = swiglu(gate.float(), up.float())
+        return fp8_weight_linear(h.double(), t(p["w2"], (hidden, inter)), t(p["s2"], nb_d), accumulation_dtype=torch.float64,
+                                 output_dtype=torch.float64)
+
+    downs = [chain4(p, xl) for p in pages]
+    out["ly_chain0_down"] = downs[0].numpy()
+    acc = torch.zeros(hidden, dtype=torch.float64)
+    for e in range(6):
+        acc += float(weights[e]) * downs[e]
+    out["ly_y_mxfp4_shared"] = (acc + downs[6]).numpy()
+    out["ly_y_fp8_shared"] = (acc + chain8(page8, xl)).numpy()
+
+    # router: executor.py:638-668 with both score functions, scale 1.5 and 1.0
+    g = synth.rng(1004)
+    n_exp, hid = 256, 1024
+    wr_bits = synth.router_weight_bf16(g, n_exp, hid)
+    bias = synth.router_bias(g, n_exp)
+    xr = synth.activations(g, 4, hid)
+    out["rt_inputs_sha256"] = np.frombuffer(_digest(wr_bits, bias, xr), dtype=np.uint8)
+    wr = torch.from_numpy(synth.bf16_bits_to_f32(wr_bits))
+    logits = F.linear(torch.from_numpy(xr).float(), wr.float())
+    for name, scores in (("sig", torch.sigmoid(logits)), ("ssp", F.softplus(logits).sqrt())):
+        indices = (scores + torch.from_numpy(bias)).topk(6, dim=-1).indices
+        w6 = scores.gather(1, indices)
+        w6 = w6 / w6.sum(dim=-1, keepdim=True) * 1.5
+        out[f"rt_{name}_ids"] = indices.numpy().astype(np.int32)
+        out[f"rt_{name}_w"] = w6.numpy()
+        sel = (scores + torch.from_numpy(bias)).sort(dim=-1, descending=True).values
+        out[f"rt_{name}_gap"] = (sel[:, 5] - sel[:, 6]).numpy()
+
+    # LM head on the reference's seed-731 fixture
+    torch.manual_seed(731)
+    hx = torch.randn(2, 3, 4, 8, dtype=torch.float32).to(torch.bfloat16)
+    _ = torch.randn(4, 32, dtype=torch.float32)
+    head_weight = torch.randn(13, 8, dtype=torch.float32).to(torch.bfloat16)
+    hid_states = hx[:, :, 0]
+    out["hd_x"] = hid_states.float().numpy()
+    out["hd_w"] = head_weight.view(torch.int16).numpy().view(np.uint16)
+    out["hd_logits"] = bf16_checkpoint_head_logits(hid_states, head_weight, full_logits=True,
+                                                   output_chunk_size=5).numpy()
+
+    path = os.path.join(HERE, "s14_golden.npz")
+    np.savez_compressed(path, **out)
+    print(path, os.path.getsize(path), "bytes;", len(out), "arrays")
+
+
+if __name__ == "__main__":
+    main(sys.argv[1] if len(sys.argv) > 1 else "/root/reference")
