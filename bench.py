@@ -1,0 +1,396 @@
+#!/usr/bin/env python
+"""Benchmark of the S14 MoE layer at 1-token decode: router top-6 + six routed MXFP4
+experts + the shared MXFP4 expert, 256 routed experts per layer resident in the page pool.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl reference] [--accum pairwise|reference]
+
+A step is one layer-token: one token through one MoE layer (router, up phase, down phase,
+ordered mix).  14 layers of 257 expert pages each are resident (the S14 stack, 48 GB); the
+steps walk the layers round-robin with a fresh token each, so consecutive steps read
+disjoint pages and the 96 MB a step touches never comes from L2.  Steps are replayed from
+a CUDA graph of 14 layer-steps; time is taken with CUDA events on the launching stream.
+
+One JSON line is printed by rank 0.  `value` is layer-tokens/s with inputs resident in HBM,
+`e2e` the same through the host-buffer C-ABI call (H2D of the token and D2H of the result
+inside the timed region), `roofline` the up-phase kernel against the measured copy
+bandwidth, `cpu_baseline` the CPU oracle on this box's host cores on a bounded sample.
+`--impl reference` times that CPU implementation alone.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import subprocess
+import sys
+import threading
+import time
+
+import numpy as np
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+if ROOT not in sys.path:
+    sys.path.insert(0, ROOT)
+
+HIDDEN, INTER, N_EXPERTS, TOP_K, N_LAYERS = 4096, 2048, 256, 6, 14
+PAGE_BYTES = 13_369_344
+# algorithmic bytes of one layer-token: 7 expert pages + router weights + bias + x + y
+ROUTER_BYTES = N_EXPERTS * HIDDEN * 2 + N_EXPERTS * 4
+STEP_BYTES = 7 * PAGE_BYTES + ROUTER_BYTES + HIDDEN * 4 + HIDDEN * 4
+# up-phase kernel: w1, w3 and their scales of 7 experts, x in, 7 hidden vectors out
+UP_BYTES = 7 * (2 * (HIDDEN * INTER // 2) + 2 * (HIDDEN * INTER // 32)) + HIDDEN * 4 + 7 * INTER * 4
+DOWN_BYTES = 7 * ((HIDDEN * INTER // 2) + (HIDDEN * INTER // 32)) + 7 * INTER * 4 + 7 * HIDDEN * 4
+WORKLOAD = ("moe_layer_decode: 1 token, router top-6 of 256 + 6 routed + 1 shared MXFP4 expert, "
+            "hidden 4096, intermediate 2048")
+
+
+def measured_peaks():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(path):
+        with open(path) as f:
+            return float(json.load(f)["hbm_gbs"]), "measured"
+    return 6650.0, "fallback"
+
+
+class ClockSampler:
+    """nvidia-smi clocks and throttle reasons while the timed region runs."""
+
+    QUERY = ("clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,"
+             "clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+             "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, device: int):
+        self.rows = []
+        self.proc = None
+        self.device = device
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(
+                ["nvidia-smi", f"--id={self.device}", f"--query-gpu={self.QUERY}",
+                 "--format=csv,noheader,nounits", "-lms", "100"],
+                stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+            self.thread = threading.Thread(target=self._read, daemon=True)
+            self.thread.start()
+        except OSError:
+            self.proc = None
+
+    def _read(self):
+        for line in self.proc.stdout:
+            self.rows.append([c.strip() for c in line.split(",")])
+
+    def stop(self) -> dict:
+        if self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        time.sleep(0.15)
+        self.proc.terminate()
+        try:
+            self.proc.wait(timeout=2)
+        except subprocess.TimeoutExpired:
+            self.proc.kill()
+        sm, reasons, mx = [], set(), None
+        for r in self.rows:
+            try:
+                sm.append(float(r[0]))
+                mx = float(r[1])
+            except (ValueError, IndexError):
+                continue
+            for name, col in (("hw_slowdown", 4), ("hw_thermal_slowdown", 5),
+                              ("sw_thermal_slowdown", 6), ("sw_power_cap", 7)):
+                if len(r) > col and r[col].lower().startswith("active"):
+                    reasons.add(name)
+        return {"sm_mhz": float(np.median(sm)) if sm else None, "sm_max_mhz": mx,
+                "reasons": sorted(reasons), "samples": len(sm)}
+
+
+# ------------------------------------------------------------------ CPU reference arm
+
+def cpu_pages(layer: int, ids, cache: dict):
+    """Host copies of the pages a CPU step needs, generated on demand from per-page seeds."""
+    from colormlm_b200 import synth
+
+    out = []
+    for e in list(ids) + [N_EXPERTS]:
+        key = (layer, int(e))
+        if key not in cache:
+            cache[key] = synth.mxfp4_expert_page(synth.rng(10_000 + layer * 1000 + int(e)), HIDDEN, INTER)
+        out.append(cache[key])
+    return out
+
+
+def cpu_step_setup(n_steps: int):
+    """Router weights per layer, tokens, routes and pages for n_steps CPU steps (untimed)."""
+    from colormlm_b200 import synth
+    from oracle import s14_oracle as oracle
+
+    g = synth.rng(77)
+    layers = {}
+    steps = []
+    cache = {}
+    for i in range(n_steps):
+        layer = i % N_LAYERS
+        if layer not in layers:
+            gl = synth.rng(500 + layer)
+            layers[layer] = (synth.router_weight_bf16(gl, N_EXPERTS, HIDDEN), synth.router_bias(gl, N_EXPERTS))
+        x = synth.activations(g, 1, HIDDEN)[0]
+        wr, bias = layers[layer]
+        ids, _, _, _ = oracle.router(x, wr, bias, 0, TOP_K, 1.0)
+        steps.append((x, wr, bias, cpu_pages(layer, ids, cache)))
+        if len(cache) > 64:
+            cache.clear()
+    return steps
+
+
+def cpu_run(steps) -> float:
+    """Seconds for the CPU oracle to run the given layer-token steps (router + layer)."""
+    from oracle import s14_oracle as oracle
+
+    t0 = time.perf_counter()
+    for x, wr, bias, pages in steps:
+        ids, w, _, _ = oracle.router(x, wr, bias, 0, TOP_K, 1.0)
+        oracle.moe_layer(x, pages[:TOP_K], w, pages[TOP_K], 0, HIDDEN, INTER)
+    return time.perf_counter() - t0
+
+
+def run_reference(args) -> None:
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    from oracle import s14_oracle as oracle
+
+    oracle.build()
+    cores = oracle.max_threads()
+    steps = cpu_step_setup(args.warmup + args.steps)
+    cpu_run(steps[:args.warmup])
+    sec = cpu_run(steps[args.warmup:])
+    value = args.steps / sec
+    line = {
+        "impl": "reference", "metric": "moe_layer_tokens_per_s", "value": value, "unit": "layer-tokens/s",
+        "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup,
+        "ms_per_step": 1e3 * sec / args.steps, "higher_is_better": True, "scaling": "weak",
+        "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+        "config": {"workload": WORKLOAD, "layers_resident": N_LAYERS, "device": "host CPU"},
+        "cpu_baseline": {"value": value, "unit": "layer-tokens/s", "cores": cores, "kind": "port",
+                         "sample": f"{args.steps} layer-tokens (router + 7 experts each), OpenMP over rows"},
+        "e2e": {"value": value, "unit": "layer-tokens/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        "gpu_launches": 0,
+        "hbm_gbs_equivalent": value * STEP_BYTES / 1e9,
+    }
+    print(json.dumps(line), flush=True)
+
+
+# ------------------------------------------------------------------------- GPU arm
+
+def make_layer_pages(torch, n_pages: int, gen) -> "torch.Tensor":
+    """[n_pages, PAGE_BYTES] uint8 on the device: uniform E2M1 codes, scale codes in [119, 123]."""
+    wb = 3 * (HIDDEN * INTER // 2)
+    pages = torch.empty((n_pages, PAGE_BYTES), dtype=torch.uint8, device="cuda")
+    pages[:, :wb] = torch.randint(0, 256, (n_pages, wb), dtype=torch.uint8, device="cuda", generator=gen)
+    pages[:, wb:] = torch.randint(119, 124, (n_pages, PAGE_BYTES - wb), dtype=torch.uint8, device="cuda",
+                                  generator=gen)
+    return pages
+
+
+def run_gpu(args) -> None:
+    import torch
+    import torch.distributed as dist
+
+    from colormlm_b200 import _lib as L
+    from colormlm_b200 import build as cuda_build
+    from colormlm_b200 import synth
+    from colormlm_b200.s14 import S14Context
+
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a CUDA device: there is no CPU fallback for the product path")
+    if rank == 0:
+        cuda_build.build()
+    torch.cuda.set_device(local_rank)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
+        dist.barrier()
+
+    ctx = S14Context(local_rank)
+    mode = L.ACCUM_REFERENCE if args.accum == "reference" else L.ACCUM_PAIRWISE
+    ctx.set_accumulation(mode)
+    gen = torch.Generator(device="cuda")
+    gen.manual_seed(1234 + rank)
+
+    # resident state: N_LAYERS x (256 routed + 1 shared) pages, router weights, page tables
+    layers = []
+    for layer in range(N_LAYERS):
+        pages = make_layer_pages(torch, N_EXPERTS + 1, gen)
+        gl = synth.rng(500 + layer)
+        wr = torch.from_numpy(synth.router_weight_bf16(gl, N_EXPERTS, HIDDEN).view(np.int16)).cuda()
+        bias = torch.from_numpy(synth.router_bias(gl, N_EXPERTS)).cuda()
+        base = pages.data_ptr()
+        table = torch.tensor([base + e * PAGE_BYTES for e in range(N_EXPERTS)], dtype=torch.int64, device="cuda")
+        layers.append({"pages": pages, "wr": wr, "bias": bias, "table": table,
+                       "shared": base + N_EXPERTS * PAGE_BYTES})
+    n_tok = 64
+    xs = torch.randn((n_tok, HIDDEN), dtype=torch.float32, device="cuda", generator=gen)
+    ys = torch.empty((N_LAYERS, HIDDEN), dtype=torch.float32, device="cuda")
+    torch.cuda.synchronize()
+
+    def enqueue_step(i: int, stream_handle=None):
+        ly = layers[i % N_LAYERS]
+        ctx.cmd_routed_moe_layer(xs[i % n_tok], ly["wr"], ly["bias"], ly["table"], ly["shared"], L.PAGE_MXFP4,
+                                 INTER, ys[i % N_LAYERS], stream=stream_handle)
+
+    stream = torch.cuda.Stream()
+    kernels_per_step = 5
+
+    def capture(n_steps: int, first: int):
+        g = torch.cuda.CUDAGraph()
+        with torch.cuda.stream(stream):
+            with torch.cuda.graph(g, stream=stream):
+                for i in range(n_steps):
+                    enqueue_step(first + i, stream.cuda_stream)
+        return g
+
+    with torch.cuda.stream(stream):
+        for i in range(3):  # first launches outside capture (module load)
+            enqueue_step(i, stream.cuda_stream)
+    stream.synchronize()
+    graph = capture(N_LAYERS, 0)
+    rem = args.steps % N_LAYERS
+    graph_rem = capture(rem, 0) if rem else None
+    full = args.steps // N_LAYERS
+
+    def replay(n_full: int, with_rem: bool):
+        with torch.cuda.stream(stream):
+            for _ in range(n_full):
+                graph.replay()
+            if with_rem and graph_rem is not None:
+                graph_rem.replay()
+
+    warm_full = max(1, (args.warmup + N_LAYERS - 1) // N_LAYERS)
+    replay(warm_full, False)
+    stream.synchronize()
+    if world > 1:
+        dist.barrier()
+    torch.cuda.synchronize()
+    sampler = ClockSampler(local_rank)
+    if rank == 0:
+        sampler.start()
+        time.sleep(0.25)
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    with torch.cuda.stream(stream):
+        e0.record(stream)
+    replay(full, True)
+    with torch.cuda.stream(stream):
+        e1.record(stream)
+    stream.synchronize()
+    torch.cuda.synchronize()
+    if world > 1:
+        dist.barrier()
+    ms = e0.elapsed_time(e1)
+    if world > 1:
+        t = torch.tensor([ms], dtype=torch.float64, device="cuda")
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        ms = float(t.item())
+    clocks = sampler.stop() if rank == 0 else None
+    value = world * args.steps / (ms / 1e3)
+
+    # per-kernel durations (separate loop, blocking calls, not part of the headline number)
+    ctx.set_kernel_timing(True)
+    with torch.cuda.stream(stream):
+        for i in range(4 * N_LAYERS):
+            enqueue_step(i, stream.cuda_stream)
+    kt, calls = ctx.kernel_times()
+    ctx.set_kernel_timing(False)
+    up_ms = kt["up"] / max(1, calls)
+    peak, peak_kind = measured_peaks()
+    achieved = UP_BYTES / (up_ms * 1e-3) / 1e9 if up_ms > 0 else 0.0
+
+    # end to end through the host-buffer call: pinned x in, y (+ route) out, every step
+    hx = torch.randn((n_tok, HIDDEN), dtype=torch.float32).pin_memory()
+    hy = torch.empty((HIDDEN,), dtype=torch.float32).pin_memory()
+    hx_np, hy_np = hx.numpy(), hy.numpy()
+    ids_np, w_np = np.empty(TOP_K, np.int32), np.empty(TOP_K, np.float32)
+    e2e_steps = min(args.steps, 2000)
+
+    def e2e_step(i):
+        ly = layers[i % N_LAYERS]
+        ctx.routed_moe_layer_host(hx_np[i % n_tok], hy_np, ly["wr"], ly["bias"], ly["table"], ly["shared"],
+                                  L.PAGE_MXFP4, INTER, ids_np, w_np)
+
+    for i in range(max(3, args.warmup)):
+        e2e_step(i)
+    if world > 1:
+        dist.barrier()
+    t0 = time.perf_counter()
+    for i in range(e2e_steps):
+        e2e_step(i)
+    e2e_sec = time.perf_counter() - t0
+    if world > 1:
+        t = torch.tensor([e2e_sec], dtype=torch.float64, device="cuda")
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        e2e_sec = float(t.item())
+    e2e_value = world * e2e_steps / e2e_sec
+
+    if rank == 0:
+        cpu = None
+        if world == 1 and not args.no_cpu_baseline:
+            from oracle import s14_oracle as oracle
+
+            oracle.build()
+            sample = cpu_step_setup(2 + args.cpu_steps)
+            cpu_run(sample[:2])
+            sec = cpu_run(sample[2:])
+            cpu = {"value": args.cpu_steps / sec, "unit": "layer-tokens/s", "cores": oracle.max_threads(),
+                   "kind": "port",
+                   "sample": f"{args.cpu_steps} layer-tokens of the same workload (router + 7 experts), "
+                             f"{sec:.1f} s of CPU work"}
+        line = {
+            "metric": "moe_layer_tokens_per_s", "value": value, "unit": "layer-tokens/s", "n_gpus": world,
+            "steps": args.steps, "warmup": warm_full * N_LAYERS, "ms_per_step": ms / args.steps,
+            "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f32",
+            "data": "synthetic",
+            "config": {"workload": WORKLOAD, "layers_resident": N_LAYERS, "accumulation": args.accum,
+                       "l2": "inputs larger than L2: 14 x 3.4 GB of pages walked round-robin, 96 MB per step",
+                       "parallelism": "replicas" if world > 1 else "single"},
+            "hbm_gbs": value / world * STEP_BYTES / 1e9, "hbm_frac_of_measured_peak": value / world * STEP_BYTES / 1e9 / peak,
+            "algorithmic_bytes_per_step": STEP_BYTES,
+            "roofline": {"bound": "hbm", "kernel": "expert up phase (w1, w3, SwiGLU) of 7 experts",
+                         "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
+                         "peak_kind": peak_kind, "traffic": None, "bytes_per_launch": UP_BYTES,
+                         "ms_per_launch": up_ms,
+                         "other_kernels_ms": {k: v / max(1, calls) for k, v in kt.items() if k != "up"}},
+            "cpu_baseline": cpu,
+            "e2e": {"value": e2e_value, "unit": "layer-tokens/s", "h2d_bytes_per_step": HIDDEN * 4,
+                    "d2h_bytes_per_step": HIDDEN * 4 + TOP_K * 8, "steps": e2e_steps},
+            "gpu_launches": kernels_per_step * args.steps,
+            "clocks": clocks,
+        }
+        print(json.dumps(line), flush=True)
+    if world > 1:
+        dist.barrier()
+        dist.destroy_process_group()
+    ctx.close()
+
+
+def main() -> None:
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=None)
+    ap.add_argument("--warmup", type=int, default=None)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--accum", default="pairwise", choices=["pairwise", "reference"])
+    ap.add_argument("--cpu-steps", type=int, default=60)
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    args = ap.parse_args()
+    if args.impl == "reference":
+        args.steps = args.steps if args.steps is not None else 60
+        args.warmup = args.warmup if args.warmup is not None else 3
+        run_reference(args)
+    else:
+        args.steps = args.steps if args.steps is not None else 28000
+        args.warmup = args.warmup if args.warmup is not None else 140
+        run_gpu(args)
+
+
+if __name__ == "__main__":
+    main()

@@ -114,6 +114,8 @@ SIGNATURES = {
     "s14_ctx_sm_count": (_I32, [_VP]),
     "s14_ctx_device_status": (_I32, [_VP, _P(_U32)]),
     "s14_ctx_launch_count": (_U64, [_VP]),
+    "s14_ctx_set_kernel_timing": (_I32, [_VP, _I32]),
+    "s14_ctx_kernel_times": (_I32, [_VP, _P(C.c_double), _P(_U64)]),
     "s14_shape_new": (_I32, [_U32, _U32, _P(MatvecShape)]),
     "s14_shape_validate_mxfp4": (_I32, [MatvecShape]),
     "s14_shape_validate_fp8": (_I32, [MatvecShape]),
@@ -144,6 +146,7 @@ SIGNATURES = {
     "s14_cmd_moe_layer": (_I32, [_VP, _VP, _P(MoeLayerDesc)]),
     "s14_cmd_router": (_I32, [_VP, _VP, _P(RouterDesc)]),
     "s14_cmd_routed_moe_layer": (_I32, [_VP, _VP, _P(RoutedLayerDesc)]),
+    "s14_routed_moe_layer_host": (_I32, [_VP, _P(RoutedLayerDesc), _VP, _VP, _VP, _VP]),
     "s14_cmd_head_logits": (_I32, [_VP, _VP, _VP, _U32, _VP, _U32, _U32, _VP, _U32]),
     "s14_cmd_greedy_argmax": (_I32, [_VP, _VP, _VP, _U32, _VP]),
     "s14_moe_layer_host": (_I32, [_VP, _P(MoeLayerDesc), _VP, _VP]),

@@ -61,6 +61,12 @@ struct s14_ctx {
     float *x_stage = nullptr, *y_stage = nullptr;  // [kMaxTokens, kMaxDim]
     uint32_t *status = nullptr;
     uint64_t launches = 0;
+    bool timing = false;  // per-kernel timing of routed layer calls (blocks after each call)
+    KernelMarks marks{};
+    double kernel_ms[4] = {0, 0, 0, 0};  // router, up, down, mix
+    uint64_t timed_calls = 0;
+    int32_t *ids_stage = nullptr;  // [8] route ids / weights staging of the host-buffer call
+    float *weights_stage = nullptr;
 };
 
 static cudaStream_t stream_of(s14_ctx *ctx, void *stream) {
@@ -94,6 +100,9 @@ extern "C" int32_t s14_ctx_create(int32_t device, s14_ctx **out) {
     CUDA_OK(cudaMalloc(&ctx->y_stage, sizeof(float) * kMaxTokens * kMaxDim));
     CUDA_OK(cudaMalloc(&ctx->status, sizeof(uint32_t)));
     CUDA_OK(cudaMemset(ctx->status, 0, sizeof(uint32_t)));
+    CUDA_OK(cudaMalloc(&ctx->ids_stage, sizeof(int32_t) * 8));
+    CUDA_OK(cudaMalloc(&ctx->weights_stage, sizeof(float) * 8));
+    for (auto &e : ctx->marks.ev) CUDA_OK(cudaEventCreate(&e));
     *out = ctx.release();
     return S14_OK;
 }
@@ -111,6 +120,10 @@ extern "C" int32_t s14_ctx_destroy(s14_ctx *ctx) {
     cudaFree(ctx->x_stage);
     cudaFree(ctx->y_stage);
     cudaFree(ctx->status);
+    cudaFree(ctx->ids_stage);
+    cudaFree(ctx->weights_stage);
+    for (auto &e : ctx->marks.ev)
+        if (e) cudaEventDestroy(e);
     cudaStreamDestroy(ctx->compute);
     cudaStreamDestroy(ctx->copy);
     delete ctx;
@@ -144,6 +157,21 @@ extern "C" int32_t s14_ctx_device_status(s14_ctx *ctx, uint32_t *status) {
     CUDA_OK(cudaStreamSynchronize(ctx->compute));
     CUDA_OK(cudaMemcpy(status, ctx->status, sizeof(uint32_t), cudaMemcpyDeviceToHost));
     if (*status != 0) CUDA_OK(cudaMemset(ctx->status, 0, sizeof(uint32_t)));
+    return S14_OK;
+}
+
+extern "C" int32_t s14_ctx_set_kernel_timing(s14_ctx *ctx, int32_t enable) {
+    if (!ctx) return fail(S14_ERR_CONTRACT, "ctx is NULL");
+    ctx->timing = enable != 0;
+    for (double &v : ctx->kernel_ms) v = 0.0;
+    ctx->timed_calls = 0;
+    return S14_OK;
+}
+
+extern "C" int32_t s14_ctx_kernel_times(s14_ctx *ctx, double ms_out[4], uint64_t *calls) {
+    if (!ctx || !ms_out || !calls) return fail(S14_ERR_CONTRACT, "s14_ctx_kernel_times: NULL argument");
+    for (int i = 0; i < 4; ++i) ms_out[i] = ctx->kernel_ms[i];
+    *calls = ctx->timed_calls;
     return S14_OK;
 }
 
@@ -551,17 +579,55 @@ extern "C" int32_t s14_cmd_routed_moe_layer(s14_ctx *ctx, void *stream,
         throw ContractError("S14 routed layer: unknown shared page kind");
     cudaStream_t st = stream_of(ctx, stream);
     cudaError_t err;
+    const KernelMarks *km = ctx->timing ? &ctx->marks : nullptr;
     ctx->launches += launch_router(st, r, ctx->scores, ctx->select, ctx->dev_table, desc->page_table,
-                                   desc->shared_page, desc->shared_kind, &err);
+                                   desc->shared_page, desc->shared_kind, &err, km);
     if (err != cudaSuccess) return cuda_fail(err, "S14 router launch");
     JobTable unused;
     unused.n_jobs = 0;
     const uint32_t n_jobs = r.top_k + (desc->shared_page ? 1u : 0u);
     ctx->launches += launch_moe_layer(st, ctx->mode, ctx->sm_count, ctx->dev_table, unused, 1, n_jobs,
-                                      r.hidden, desc->inter, r.x, ctx->h, ctx->d, desc->y, &err);
+                                      r.hidden, desc->inter, r.x, ctx->h, ctx->d, desc->y, &err, km);
     if (err != cudaSuccess) return cuda_fail(err, "S14 MoE layer launch");
+    if (km) {
+        CUDA_OK(cudaStreamSynchronize(st));
+        for (int i = 0; i < 4; ++i) {
+            float ms = 0.0f;
+            CUDA_OK(cudaEventElapsedTime(&ms, km->ev[i], km->ev[i + 1]));
+            ctx->kernel_ms[i] += ms;
+        }
+        ctx->timed_calls += 1;
+    }
     return S14_OK;
     S14_CATCH
+}
+
+extern "C" int32_t s14_routed_moe_layer_host(s14_ctx *ctx, const s14_routed_layer_desc *desc,
+                                             const float *host_x, float *host_y, int32_t *host_ids,
+                                             float *host_weights) {
+    if (!ctx || !desc || !host_x || !host_y)
+        return fail(S14_ERR_CONTRACT, "s14_routed_moe_layer_host: NULL argument");
+    if (desc->router.hidden == 0 || desc->router.hidden > kMaxDim || desc->router.top_k > 8)
+        return fail(S14_ERR_CONTRACT, "s14_routed_moe_layer_host: hidden size or top_k out of range");
+    const size_t bytes = sizeof(float) * desc->router.hidden;
+    s14_routed_layer_desc d = *desc;
+    d.router.x = ctx->x_stage;
+    d.router.n_tokens = 1;
+    d.router.ids_out = ctx->ids_stage;
+    d.router.weights_out = ctx->weights_stage;
+    d.y = ctx->y_stage;
+    CUDA_OK(cudaMemcpyAsync(ctx->x_stage, host_x, bytes, cudaMemcpyHostToDevice, ctx->compute));
+    const int32_t rc = s14_cmd_routed_moe_layer(ctx, ctx->compute, &d);
+    if (rc != S14_OK) return rc;
+    CUDA_OK(cudaMemcpyAsync(host_y, ctx->y_stage, bytes, cudaMemcpyDeviceToHost, ctx->compute));
+    if (host_ids)
+        CUDA_OK(cudaMemcpyAsync(host_ids, ctx->ids_stage, sizeof(int32_t) * d.router.top_k,
+                                cudaMemcpyDeviceToHost, ctx->compute));
+    if (host_weights)
+        CUDA_OK(cudaMemcpyAsync(host_weights, ctx->weights_stage, sizeof(float) * d.router.top_k,
+                                cudaMemcpyDeviceToHost, ctx->compute));
+    CUDA_OK(cudaStreamSynchronize(ctx->compute));
+    return S14_OK;
 }
 
 extern "C" int32_t s14_cmd_head_logits(s14_ctx *ctx, void *stream, const float *x, uint32_t n_tokens,

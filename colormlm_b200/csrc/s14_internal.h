@@ -31,6 +31,12 @@ struct JobTable {
     Job jobs[kMaxJobs];
 };
 
+// Optional per-kernel timing marks of one routed layer call: events are recorded before the
+// router (0), before the up phase (1), between up and down (2), before the mix (3), after it (4).
+struct KernelMarks {
+    cudaEvent_t ev[5];
+};
+
 cudaError_t launch_mxfp4_matvec(cudaStream_t st, uint32_t mode, int sm_count, const float *x,
                                 const uint8_t *w, const uint8_t *s, float *y, uint32_t n, uint32_t k);
 cudaError_t launch_fp8_matvec(cudaStream_t st, uint32_t mode, int sm_count, uint32_t scale_format,
@@ -46,10 +52,10 @@ cudaError_t launch_moe_accumulate(cudaStream_t st, const float *expert, float *a
 int launch_moe_layer(cudaStream_t st, uint32_t mode, int sm_count, const JobTable *dev_table,
                      const JobTable &param_table, uint32_t n_tokens, uint32_t n_jobs_max,
                      uint32_t hidden, uint32_t inter, const float *x, float *h, float *d, float *y,
-                     cudaError_t *err);
+                     cudaError_t *err, const KernelMarks *km = nullptr);
 int launch_router(cudaStream_t st, const s14_router_desc &r, float *scores, float *select,
                   JobTable *table_out, const uint8_t *const *page_table, const uint8_t *shared_page,
-                  uint32_t shared_kind, cudaError_t *err);
+                  uint32_t shared_kind, cudaError_t *err, const KernelMarks *km = nullptr);
 cudaError_t launch_head_logits(cudaStream_t st, int sm_count, const float *x, uint32_t n_tokens,
                                const uint16_t *w, uint32_t n_rows, uint32_t hidden, float *out,
                                uint32_t out_stride);

@@ -974,13 +974,15 @@ static void launch_down_pairwise(cudaStream_t st, const JobTable *dev, const Job
 int launch_moe_layer(cudaStream_t st, uint32_t mode, int sm_count, const JobTable *dev_table,
                      const JobTable &param_table, uint32_t n_tokens, uint32_t n_jobs_max,
                      uint32_t hidden, uint32_t inter, const float *x, float *h, float *d, float *y,
-                     cudaError_t *err) {
+                     cudaError_t *err, const KernelMarks *km) {
     int launches = 0;
     *err = cudaSuccess;
+    if (km) cudaEventRecord(km->ev[1], st);
     if (mode == S14_ACCUM_REFERENCE) {
         dim3 gu(ceil_div(inter, 32), n_jobs_max), gd(ceil_div(hidden, 32), n_jobs_max);
         k_expert_up_reference<<<gu, 32, hidden * sizeof(float), st>>>(dev_table, param_table, x, h,
                                                                       hidden, inter);
+        if (km) cudaEventRecord(km->ev[2], st);
         k_expert_down_reference<<<gd, 32, inter * sizeof(float), st>>>(dev_table, param_table, h, d,
                                                                        hidden, inter);
         launches += 2;
@@ -991,6 +993,7 @@ int launch_moe_layer(cudaStream_t st, uint32_t mode, int sm_count, const JobTabl
         case 2: launch_up_pairwise<2>(st, dev_table, param_table, x, h, inter, n_tokens, ctas_per_token); break;
         default: launch_up_pairwise<4>(st, dev_table, param_table, x, h, inter, n_tokens, ctas_per_token); break;
         }
+        if (km) cudaEventRecord(km->ev[2], st);
         const uint32_t ctas_per_job = max(1u, ceil_div(2u * (uint32_t)sm_count, n_jobs_max));
         switch (inter >> 10) {
         case 1: launch_down_pairwise<1>(st, dev_table, param_table, h, d, hidden, n_jobs_max, ctas_per_job); break;
@@ -999,8 +1002,10 @@ int launch_moe_layer(cudaStream_t st, uint32_t mode, int sm_count, const JobTabl
         }
         launches += 2;
     }
+    if (km) cudaEventRecord(km->ev[3], st);
     dim3 gm(ceil_div(hidden, 256), n_tokens);
     k_moe_mix<<<gm, 256, 0, st>>>(dev_table, param_table, d, y, hidden);
+    if (km) cudaEventRecord(km->ev[4], st);
     launches += 1;
     *err = cudaGetLastError();
     return launches;
@@ -1008,8 +1013,9 @@ int launch_moe_layer(cudaStream_t st, uint32_t mode, int sm_count, const JobTabl
 
 int launch_router(cudaStream_t st, const s14_router_desc &r, float *scores, float *select,
                   JobTable *table_out, const uint8_t *const *page_table, const uint8_t *shared_page,
-                  uint32_t shared_kind, cudaError_t *err) {
+                  uint32_t shared_kind, cudaError_t *err, const KernelMarks *km) {
     const uint32_t warps = r.n_experts * r.n_tokens;
+    if (km) cudaEventRecord(km->ev[0], st);
     k_router_scores<<<ceil_div(warps, 8), 256, 0, st>>>(r.x, r.router_weight_bf16, r.bias, scores,
                                                         select, r.n_experts, r.hidden, r.n_tokens,
                                                         r.score_fn);

@@ -183,6 +183,38 @@ class S14Context:
         check(L.lib().s14_cmd_routed_moe_layer(
             self._h, stream if stream is not None else _torch_stream(), C.byref(d)))
 
+    def routed_moe_layer_host(self, host_x: np.ndarray, host_y: np.ndarray, wr_bf16, bias, page_table,
+                              shared_page: Optional[int], shared_kind: int, inter: int,
+                              host_ids: Optional[np.ndarray] = None,
+                              host_weights: Optional[np.ndarray] = None, *,
+                              score_fn: int = L.SCORE_SIGMOID, top_k: int = 6,
+                              route_scale: float = 1.0) -> None:
+        """One decode token held in host memory: H2D copy, router + layer, D2H copy, wait."""
+        d = L.RoutedLayerDesc()
+        r = L.RouterDesc()
+        r.n_experts, r.hidden, r.n_tokens = wr_bf16.shape[0], wr_bf16.shape[1], 1
+        r.top_k, r.score_fn, r.route_scale = top_k, score_fn, route_scale
+        r.router_weight_bf16 = wr_bf16.data_ptr()
+        r.bias = bias.data_ptr() if bias is not None else None
+        d.router = r
+        d.inter, d.shared_kind = inter, shared_kind
+        d.page_table = page_table.data_ptr()
+        d.shared_page = shared_page
+        check(L.lib().s14_routed_moe_layer_host(
+            self._h, C.byref(d), host_x.ctypes.data, host_y.ctypes.data,
+            host_ids.ctypes.data if host_ids is not None else None,
+            host_weights.ctypes.data if host_weights is not None else None))
+
+    def set_kernel_timing(self, enable: bool) -> None:
+        check(L.lib().s14_ctx_set_kernel_timing(self._h, 1 if enable else 0))
+
+    def kernel_times(self):
+        """({'router','up','down','mix'} total ms, number of timed calls)."""
+        ms = (C.c_double * 4)()
+        calls = C.c_uint64()
+        check(L.lib().s14_ctx_kernel_times(self._h, ms, C.byref(calls)))
+        return dict(zip(("router", "up", "down", "mix"), [float(v) for v in ms])), calls.value
+
     def cmd_head_logits(self, x, weight_bf16, logits_out, *, n_rows: Optional[int] = None,
                         stream: Optional[int] = None) -> None:
         n_tokens = 1 if x.dim() == 1 else x.shape[0]

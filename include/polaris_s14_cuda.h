@@ -94,6 +94,14 @@ S14_API int32_t s14_ctx_device_status(s14_ctx *ctx, uint32_t *status);
 /* Number of kernels this context has launched since creation. */
 S14_API uint64_t s14_ctx_launch_count(const s14_ctx *ctx);
 
+/* Per-kernel timing of s14_cmd_routed_moe_layer for profiling runs: while enabled,
+ * every such call records CUDA events around its kernels, waits for the stream and
+ * accumulates the durations (router, up phase, down phase, mix), the counterpart of
+ * the reference's timestamp queries (examples/s14_vulkan_numeric.rs:1088-1101,
+ * 1220-1260).  Not for timed throughput runs: the call becomes blocking. */
+S14_API int32_t s14_ctx_set_kernel_timing(s14_ctx *ctx, int32_t enable);
+S14_API int32_t s14_ctx_kernel_times(s14_ctx *ctx, double ms_out[4], uint64_t *calls);
+
 /* ---- byte contracts: S14MatvecShape (s14_vulkan.rs:40-114) ------------------- */
 typedef struct {
     uint32_t n;
@@ -268,6 +276,14 @@ typedef struct {
 
 S14_API int32_t s14_cmd_routed_moe_layer(s14_ctx *ctx, void *stream,
                                          const s14_routed_layer_desc *desc);
+
+/* The routed layer for a caller that holds the token in host memory: copies host_x
+ * [hidden] to the device, runs router + layer on the resident pages (desc->router.x,
+ * ids_out, weights_out and desc->y are ignored), copies y [hidden] and, when the
+ * pointers are not NULL, the route (top_k ids and weights) back, and waits. */
+S14_API int32_t s14_routed_moe_layer_host(s14_ctx *ctx, const s14_routed_layer_desc *desc,
+                                          const float *host_x, float *host_y, int32_t *host_ids,
+                                          float *host_weights);
 
 /* LM head (local_s14_primitives/final_head.py:113-149): logits[v] = x . W[v,:]
  * for the rows [row_begin, row_begin + n_rows) of a BF16 [vocab, hidden] matrix

@@ -15,9 +15,10 @@
  * rayon parallel iterator over rows, numeric.rs:1678, 1701) does not change any
  * result bit.
  *
- * The "_f64" variants accumulate the same exact products in double and are used
- * as the order-independent "truth" when reporting how far either F32
- * evaluation order is from the real value.
+ * The "_f64" matvecs and the "_acc64" layer accumulate the same exact products in
+ * double (the accumulator option of the reference's Python code) and serve as the
+ * order-independent value when reporting how far either F32 summation order is
+ * from it.
  *
  * The router and LM-head functions restate the Python reference
  *   fast16/research/polaris_meridian_v1/s14_first_real_token/executor.py:638-668
@@ -196,17 +197,6 @@ S14O_API void s14o_swiglu_limit(const float *gate, const float *up, uint32_t n, 
     }
 }
 
-S14O_API void s14o_swiglu_limit_f64(const double *gate, const double *up, uint32_t n,
-                                    double *y) {
-    for (uint32_t i = 0; i < n; ++i) {
-        double g = gate[i] < 10.0 ? gate[i] : 10.0;
-        double u = up[i];
-        if (u < -10.0) u = -10.0;
-        if (u > 10.0) u = 10.0;
-        y[i] = (g / (1.0 + exp(-g))) * u;
-    }
-}
-
 /* One expert page as the library lays it out in a pool slot:
  *   [w1 codes n_i*k_h/2][w3 codes][w2 codes n_h*k_i/2][s1][s3][s2]  (MXFP4)
  *   [w1 n_i*k_h][w3][w2][s1][s3][s2]                                (FP8, UE8M0 128x128)
@@ -286,37 +276,46 @@ S14O_API void s14o_moe_layer(const float *x, const uint8_t *const *routed_pages,
     }
 }
 
-/* The layer with every matvec, the activation and the mix carried in double.
- * work must hold 3*inter + 2*hidden doubles. */
-S14O_API void s14o_moe_layer_f64(const float *x, const uint8_t *const *routed_pages,
-                                 const float *route_weights, uint32_t n_routed,
-                                 const uint8_t *shared_page, int shared_kind, uint32_t hidden,
-                                 uint32_t inter, double *work, double *y) {
-    double *gate = work, *up = work + inter, *h = work + 2 * (size_t)inter;
-    double *down = work + 3 * (size_t)inter, *xd = down + hidden;
-    for (uint32_t i = 0; i < hidden; ++i) {
-        y[i] = 0.0;
-        xd[i] = (double)x[i];
-    }
+/* The reference's layer with the accumulator of every matvec widened to double: each
+ * matvec sums its exact products in double and rounds the row result to F32 once; gate,
+ * up, the SwiGLU, the hidden vector and the ordered mix stay F32 exactly as in
+ * numeric.rs:929-947.  This is what the reference's Python code computes with
+ * accumulation_dtype=float64 (local_s14_primitives/mxfp4.py:172-275) and it is free of
+ * the summation-order noise of either F32 order.  work: 3*inter + hidden floats,
+ * work64: 2*max(hidden, inter) doubles. */
+static void matvec_acc64(const float *x, const uint8_t *w, const void *s, int kind, uint32_t n,
+                         uint32_t k, double *xd, double *yd, float *y) {
+    for (uint32_t i = 0; i < k; ++i) xd[i] = (double)x[i];
+    if (kind == 0)
+        s14o_mxfp4_matvec_f64(xd, w, (const uint8_t *)s, n, k, yd);
+    else
+        s14o_fp8_matvec_f64(xd, w, s, 0, n, k, yd);
+    for (uint32_t i = 0; i < n; ++i) y[i] = (float)yd[i];
+}
+
+S14O_API void s14o_moe_layer_acc64(const float *x, const uint8_t *const *routed_pages,
+                                   const float *route_weights, uint32_t n_routed,
+                                   const uint8_t *shared_page, int shared_kind, uint32_t hidden,
+                                   uint32_t inter, float *work, double *work64, float *y) {
+    const uint32_t big = hidden > inter ? hidden : inter;
+    float *gate = work, *up = work + inter, *h = work + 2 * (size_t)inter;
+    float *down = work + 3 * (size_t)inter;
+    double *xd = work64, *yd = work64 + big;
+    for (uint32_t i = 0; i < hidden; ++i) y[i] = 0.0f;
     for (uint32_t e = 0; e <= n_routed; ++e) {
         const int is_shared = (e == n_routed);
         if (is_shared && shared_kind == 2) break;
         const uint8_t *page = is_shared ? shared_page : routed_pages[e];
-        const double w = is_shared ? 1.0 : (double)route_weights[e];
-        if (is_shared && shared_kind == 1) {
-            s14o_expert_view v = fp8_view(page, hidden, inter);
-            s14o_fp8_matvec_f64(xd, v.w1, v.s1, 0, inter, hidden, gate);
-            s14o_fp8_matvec_f64(xd, v.w3, v.s3, 0, inter, hidden, up);
-            s14o_swiglu_limit_f64(gate, up, inter, h);
-            s14o_fp8_matvec_f64(h, v.w2, v.s2, 0, hidden, inter, down);
-        } else {
-            s14o_expert_view v = mxfp4_view(page, hidden, inter);
-            s14o_mxfp4_matvec_f64(xd, v.w1, v.s1, inter, hidden, gate);
-            s14o_mxfp4_matvec_f64(xd, v.w3, v.s3, inter, hidden, up);
-            s14o_swiglu_limit_f64(gate, up, inter, h);
-            s14o_mxfp4_matvec_f64(h, v.w2, v.s2, hidden, inter, down);
-        }
-        for (uint32_t i = 0; i < hidden; ++i) y[i] += w * down[i];
+        const int kind = (is_shared && shared_kind == 1) ? 1 : 0;
+        s14o_expert_view v = kind ? fp8_view(page, hidden, inter) : mxfp4_view(page, hidden, inter);
+        matvec_acc64(x, v.w1, v.s1, kind, inter, hidden, xd, yd, gate);
+        matvec_acc64(x, v.w3, v.s3, kind, inter, hidden, xd, yd, up);
+        s14o_swiglu_limit(gate, up, inter, h);
+        matvec_acc64(h, v.w2, v.s2, kind, hidden, inter, xd, yd, down);
+        if (is_shared)
+            for (uint32_t i = 0; i < hidden; ++i) y[i] += down[i];
+        else
+            for (uint32_t i = 0; i < hidden; ++i) y[i] += route_weights[e] * down[i];
     }
 }
 

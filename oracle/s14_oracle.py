@@ -166,17 +166,19 @@ def moe_layer(x, routed_pages, route_weights, shared_page, shared_kind: int, hid
     return y
 
 
-def moe_layer_f64(x, routed_pages, route_weights, shared_page, shared_kind: int, hidden: int,
-                  inter: int) -> np.ndarray:
+def moe_layer_acc64(x, routed_pages, route_weights, shared_page, shared_kind: int, hidden: int,
+                    inter: int) -> np.ndarray:
+    """The layer with double accumulators inside each matvec and F32 everywhere else."""
     x = _f32(x)
     pages, arr = _page_ptrs(routed_pages)
     rw = _f32(route_weights)
     shared = _u8(shared_page) if shared_page is not None else np.zeros(1, np.uint8)
-    work = np.empty(3 * inter + 2 * hidden, np.float64)
-    y = np.empty(hidden, np.float64)
-    lib().s14o_moe_layer_f64(_p(x), arr, _p(rw), C.c_uint32(len(pages)), _p(shared),
-                             C.c_int(shared_kind), C.c_uint32(hidden), C.c_uint32(inter), _p(work),
-                             _p(y))
+    work = np.empty(3 * inter + hidden, np.float32)
+    work64 = np.empty(2 * max(hidden, inter), np.float64)
+    y = np.empty(hidden, np.float32)
+    lib().s14o_moe_layer_acc64(_p(x), arr, _p(rw), C.c_uint32(len(pages)), _p(shared),
+                               C.c_int(shared_kind), C.c_uint32(hidden), C.c_uint32(inter), _p(work),
+                               _p(work64), _p(y))
     return y
 
 

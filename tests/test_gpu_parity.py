@@ -1,0 +1,476 @@
+"""Parity of the CUDA path, called through the C ABI, against the CPU oracle on identical
+seeded inputs.  Reference-order mode must be bit-identical to the oracle's F32 results
+(max_abs = RMSE = 0, inside the stated 2e-5 / 2e-6); pairwise mode is held to the relative
+bound of assert_pairwise_close against the double-accumulated reference."""
+import numpy as np
+import pytest
+
+torch = pytest.importorskip("torch")
+
+from colormlm_b200 import _lib as L
+from colormlm_b200 import synth
+from colormlm_b200.pages import ExpertPageLayout
+from colormlm_b200.s14 import (ExpertKey, RouteDecision, S14Context, S14Error, S14MatvecShape,
+                               S14MoePages, TokenRoute, VramPool)
+
+pytestmark = [pytest.mark.gpu, pytest.mark.usefixtures("cuda_lib")]
+
+MAX_ABS, RMSE = 2e-5, 2e-6  # the stated tolerance per layer; met bit-exactly in reference order
+
+
+def assert_pairwise_close(oracle, y, ref_acc64, ref32=None):
+    """Pairwise order sums F32 products in another order than the reference, so it cannot
+    be held to an absolute bound tighter than the reference's own summation noise (the two
+    F32 orders differ by ~2e-4 at these magnitudes).  It is held to a relative bound against
+    the double-accumulated reference: RMSE <= 1e-6 of the output RMS and max error <= 8e-6 of
+    the largest output (a few F32 ulps), and it must be at least as close to that value as
+    the reference's own F32 order is."""
+    ref = np.asarray(ref_acc64, np.float32)
+    e = oracle.error_stats(np.asarray(y, np.float32), ref)
+    rms = float(np.sqrt(np.mean(ref.astype(np.float64) ** 2)))
+    assert e["rmse"] <= 1e-6 * rms, (e, rms)
+    assert e["max_abs"] <= 8e-6 * float(np.abs(ref).max()), e
+    if ref32 is not None:
+        noise = oracle.error_stats(np.asarray(ref32, np.float32), ref)
+        assert e["rmse"] <= noise["rmse"] + 1e-7 * rms, (e, noise)
+    return e
+
+
+@pytest.fixture(scope="module")
+def ctx():
+    if not torch.cuda.is_available():
+        pytest.skip("needs a CUDA device")
+    c = S14Context(0)
+    yield c
+    c.close()
+
+
+def dev(a):
+    return torch.from_numpy(np.ascontiguousarray(a)).cuda()
+
+
+def run_mxfp4(ctx, x, w, s, n, k):
+    dx, dw, ds = dev(x), dev(w), dev(s)
+    dy = torch.empty(n, dtype=torch.float32, device="cuda")
+    d = ctx.pipelines.bind_mxfp4(S14MatvecShape(n, k), dx, dw, ds, dy)
+    ctx.pipelines.cmd_mxfp4_matvec(d)
+    torch.cuda.synchronize()
+    return dy.cpu().numpy()
+
+
+def run_fp8(ctx, x, w, s, n, k):
+    x = np.atleast_2d(x)
+    dx, dw, ds = dev(x), dev(w), dev(s)
+    dy = torch.empty((x.shape[0], n), dtype=torch.float32, device="cuda")
+    fmt = L.SCALE_UE8M0 if s.dtype == np.uint8 else L.SCALE_F32
+    d = ctx.pipelines.bind_fp8(S14MatvecShape(n, k), dx, dw, ds, dy, scale_format=fmt, n_tokens=x.shape[0])
+    ctx.pipelines.cmd_fp8_matvec(d)
+    torch.cuda.synchronize()
+    return dy.cpu().numpy()
+
+
+def stats(oracle, a, b):
+    return oracle.error_stats(np.asarray(a, np.float32), np.asarray(b, np.float32))
+
+
+@pytest.mark.parametrize("n,k", [(1, 128), (3, 128), (96, 1024), (2048, 4096), (4096, 2048), (7, 8192)])
+def test_mxfp4_matvec_both_orders(ctx, oracle, n, k):
+    g = synth.rng(10 + n + k)
+    w, s, x = synth.mxfp4_codes(g, n, k), synth.mxfp4_scales(g, n, k), synth.activations(g, 1, k)[0]
+    ref32 = oracle.mxfp4_matvec(x, w, s, n, k)
+    ref64 = oracle.mxfp4_matvec_f64(x, w, s, n, k)
+    ctx.set_accumulation(L.ACCUM_REFERENCE)
+    assert np.array_equal(run_mxfp4(ctx, x, w, s, n, k).view(np.uint32), ref32.view(np.uint32))
+    ctx.set_accumulation(L.ACCUM_PAIRWISE)
+    y = run_mxfp4(ctx, x, w, s, n, k)
+    # F32 only inside a 32-element scale block: within a few ulps of the F64 value
+    assert np.abs(y - ref64).max() <= 4 * np.spacing(np.abs(ref64).max().astype(np.float32))
+    if n >= 96:
+        assert_pairwise_close(oracle, y, ref64, ref32)
+
+
+def test_mxfp4_extreme_scales_and_all_codes(ctx, oracle):
+    """Scale codes 0 (2^-127, subnormal) .. 254 (2^127) and every nibble value."""
+    n, k = 16, 256
+    w = np.tile(np.arange(256, dtype=np.uint8), (n, k // 2 // 256 + 1))[:, :k // 2].copy()
+    s = np.array([[0, 1, 2, 60, 126, 127, 128, 200][(r + c) % 8] for r in range(n) for c in range(k // 32)],
+                 np.uint8).reshape(n, k // 32)
+    x = synth.activations(synth.rng(5), 1, k)[0]
+    ref = oracle.mxfp4_matvec(x, w, s, n, k)
+    ctx.set_accumulation(L.ACCUM_REFERENCE)
+    assert np.array_equal(run_mxfp4(ctx, x, w, s, n, k).view(np.uint32), ref.view(np.uint32))
+    ctx.set_accumulation(L.ACCUM_PAIRWISE)
+    ref64 = oracle.mxfp4_matvec_f64(x, w, s, n, k)
+    y = run_mxfp4(ctx, x, w, s, n, k)
+    np.testing.assert_allclose(y, ref64.astype(np.float32), rtol=3e-7, atol=1e-38)
+    s[:] = 254
+    ref = oracle.mxfp4_matvec(x, w, s, n, k)
+    ctx.set_accumulation(L.ACCUM_REFERENCE)
+    assert np.array_equal(run_mxfp4(ctx, x, w, s, n, k).view(np.uint32), ref.view(np.uint32))
+    ctx.set_accumulation(L.ACCUM_PAIRWISE)
+
+
+def test_golden_mxfp4_fixture_on_gpu(ctx, golden):
+    """The reference's own deterministic fixture (test_primitives.py:58-72), its tolerance."""
+    w, s, x = golden["fx_packed"], golden["fx_scales"], golden["fx_x"]
+    for mode in (L.ACCUM_REFERENCE, L.ACCUM_PAIRWISE):
+        ctx.set_accumulation(mode)
+        for t in range(2):
+            np.testing.assert_allclose(run_mxfp4(ctx, x[t], w, s, 3, 128), golden["fx_y_f32"][t],
+                                       rtol=2e-6, atol=2e-6)
+    ctx.set_accumulation(L.ACCUM_PAIRWISE)
+
+
+@pytest.mark.parametrize("n,k,tokens", [(129, 130, 2), (1024, 4096, 1), (1024, 4096, 4), (1024, 4096, 8),
+                                        (5, 16, 3), (256, 512, 4)])
+@pytest.mark.parametrize("f32_scale", [False, True])
+def test_fp8_matvec_both_orders(ctx, oracle, n, k, tokens, f32_scale):
+    g = synth.rng(77 + n + k + tokens)
+    w = synth.e4m3_codes(g, n, k)
+    s = synth.fp8_block_scales_f32(g, n, k) if f32_scale else synth.fp8_block_scales_ue8m0(g, n, k)
+    x = synth.activations(g, tokens, k)
+    ref32 = np.stack([oracle.fp8_matvec(x[t], w, s, n, k) for t in range(tokens)])
+    ref64 = np.stack([oracle.fp8_matvec_f64(x[t], w, s, n, k) for t in range(tokens)])
+    ctx.set_accumulation(L.ACCUM_REFERENCE)
+    assert np.array_equal(run_fp8(ctx, x, w, s, n, k).view(np.uint32), ref32.view(np.uint32))
+    ctx.set_accumulation(L.ACCUM_PAIRWISE)
+    y = run_fp8(ctx, x, w, s, n, k)
+    assert np.abs(y - ref64).max() <= 4 * np.spacing(np.abs(ref64).max().astype(np.float32))
+    # the reference harness's own FP8 gate (examples/s14_vulkan_numeric.rs:1537) against its F32 order
+    e = stats(oracle, y, ref32)
+    assert e["max_abs"] <= 2.5e-5 * max(1.0, np.abs(ref32).max()) and e["rmse"] <= 3.5e-6 * max(1.0, np.abs(ref32).max())
+
+
+def test_golden_fp8_fixture_on_gpu(ctx, golden):
+    w, s, x = golden["f8_w"], golden["f8_s"], golden["f8_x"]
+    ctx.set_accumulation(L.ACCUM_PAIRWISE)
+    y = run_fp8(ctx, x, w, s, 129, 130)
+    np.testing.assert_allclose(y, golden["f8_y_f64"], rtol=3e-7, atol=1e-6)
+
+
+def test_elementwise_operators(ctx, oracle):
+    g = synth.rng(3)
+    n = 2048 + 37
+    gate = (g.standard_normal(n) * 7).astype(np.float32)
+    up = (g.standard_normal(n) * 7).astype(np.float32)
+    gate[:4] = [-20.0, 20.0, 10.0, -10.0]
+    dg, du = dev(gate), dev(up)
+    dy = torch.empty(n, dtype=torch.float32, device="cuda")
+    p = ctx.pipelines
+    p.cmd_swiglu_limit(p.bind_swiglu_limit(n, dg, du, dy))
+    torch.cuda.synchronize()
+    ref = oracle.swiglu_limit(gate, up)
+    assert np.array_equal(dy.cpu().numpy().view(np.uint32), ref.view(np.uint32))
+    routed = torch.empty(n, dtype=torch.float32, device="cuda")
+    p.cmd_route_mix(p.bind_route_mix(n, 0.3, dy, routed))
+    acc = torch.zeros(n, dtype=torch.float32, device="cuda")
+    p.cmd_moe_accumulate(p.bind_moe_accumulate(n, 0.3, dy, acc))
+    p.cmd_moe_accumulate(p.bind_moe_accumulate(n, 1.0, du, acc))
+    torch.cuda.synchronize()
+    assert np.array_equal(routed.cpu().numpy(), np.float32(0.3) * ref)
+    assert np.array_equal(acc.cpu().numpy(), (np.float32(0.0) + np.float32(0.3) * ref) + np.float32(1.0) * up)
+    for bad in (float("nan"), -0.1, float("inf")):
+        with pytest.raises(S14Error):
+            p.bind_route_mix(n, bad, dy, routed)
+        with pytest.raises(S14Error):
+            p.bind_moe_accumulate(n, bad, dy, acc)
+    with pytest.raises(S14Error):
+        p.bind_swiglu_limit(0, dg, du, dy)
+
+
+def test_bind_rejects_short_buffers(ctx):
+    x = torch.zeros(4096, device="cuda")
+    w = torch.zeros(2048 * 2048, dtype=torch.uint8, device="cuda")
+    s = torch.zeros(2048 * 128, dtype=torch.uint8, device="cuda")
+    y = torch.zeros(2048, device="cuda")
+    shape = S14MatvecShape(2048, 4096)
+    ctx.pipelines.bind_mxfp4(shape, x, w, s, y)
+    for bufs in ((x[:4095], w, s, y), (x, w[:-1], s, y), (x, w, s[:-4], y), (x, w, s, y[:2047])):
+        with pytest.raises(S14Error) as e:
+            ctx.pipelines.bind_mxfp4(shape, *bufs)
+        assert e.value.code == L.ERR_CONTRACT
+    with pytest.raises(S14Error):
+        ctx.pipelines.bind_mxfp4(S14MatvecShape(2048, 4000), x, w, s, y)
+
+
+def make_layer(seed, hidden, inter, n_experts, shared_kind):
+    g = synth.rng(seed)
+    pages = [synth.mxfp4_expert_page(g, hidden, inter) for _ in range(n_experts)]
+    shared = (synth.mxfp4_expert_page(g, hidden, inter) if shared_kind == L.PAGE_MXFP4
+              else synth.fp8_expert_page(g, hidden, inter))
+    return g, pages, shared
+
+
+def run_layer(ctx, x, pages_dev, shared_dev, routes, shared_kind, hidden, inter):
+    dx = dev(x)
+    dy = torch.empty_like(dx)
+    tr = [TokenRoute(ids, w, [pages_dev[i].data_ptr() for i in ids]) for ids, w in routes]
+    ctx.cmd_moe_layer(dx, dy, tr, shared_dev.data_ptr() if shared_dev is not None else None, shared_kind,
+                      hidden, inter)
+    torch.cuda.synchronize()
+    return dy.cpu().numpy()
+
+
+@pytest.mark.parametrize("hidden,inter", [(1024, 1024), (2048, 1024), (4096, 2048)])
+@pytest.mark.parametrize("shared_kind", [L.PAGE_MXFP4, L.PAGE_FP8])
+def test_moe_layer_decode(ctx, oracle, hidden, inter, shared_kind):
+    """One token, six routed experts and the shared expert (examples/s14_vulkan_numeric.rs:929-947)."""
+    g, pages, shared = make_layer(200 + hidden + inter + shared_kind, hidden, inter, 9, shared_kind)
+    x = synth.activations(g, 1, hidden)
+    ids = [7, 2, 5, 0, 8, 3]
+    w = np.asarray([0.31, 0.22, 0.17, 0.13, 0.1, 0.07], np.float32)
+    pages_dev, shared_dev = [dev(p) for p in pages], dev(shared)
+    ref32 = oracle.moe_layer(x[0], [pages[i] for i in ids], w, shared, shared_kind, hidden, inter)
+    ref64 = oracle.moe_layer_acc64(x[0], [pages[i] for i in ids], w, shared, shared_kind, hidden, inter)
+    ctx.set_accumulation(L.ACCUM_REFERENCE)
+    y = run_layer(ctx, x, pages_dev, shared_dev, [(ids, w)], shared_kind, hidden, inter)[0]
+    assert np.array_equal(y.view(np.uint32), ref32.view(np.uint32)), stats(oracle, y, ref32)
+    ctx.set_accumulation(L.ACCUM_PAIRWISE)
+    y = run_layer(ctx, x, pages_dev, shared_dev, [(ids, w)], shared_kind, hidden, inter)[0]
+    assert_pairwise_close(oracle, y, ref64, ref32)
+    # against the F32-order oracle the difference is that oracle's own summation noise
+    e32, noise = stats(oracle, y, ref32), stats(oracle, ref32, ref64)
+    assert e32["rmse"] <= 1.5 * noise["rmse"] + RMSE
+
+
+def test_single_expert_chain_route_weight(ctx, oracle):
+    """w1, w3 -> limited SwiGLU -> w2 -> x 0.3 (examples/s14_vulkan_numeric.rs:1296-1300)."""
+    hidden, inter = 4096, 2048
+    g = synth.rng(126)
+    page = synth.mxfp4_expert_page(g, hidden, inter)
+    x = synth.activations(g, 1, hidden)
+    ref, _ = oracle.expert_chain_mxfp4(x[0], page, hidden, inter, 0.3)
+    pd = dev(page)
+    ctx.set_accumulation(L.ACCUM_REFERENCE)
+    y = run_layer(ctx, x, [pd], None, [([0], [0.3])], L.PAGE_MXFP4, hidden, inter)[0]
+    # the layer starts from acc = 0 and adds w * down; 0 + v == v exactly
+    assert np.array_equal(y.view(np.uint32), ref.view(np.uint32))
+    ctx.set_accumulation(L.ACCUM_PAIRWISE)
+
+
+@pytest.mark.parametrize("n_tokens", [2, 4, 8])
+def test_moe_layer_verify_block(ctx, oracle, n_tokens):
+    """K tokens through one layer; tokens share experts; every token equals its own decode."""
+    hidden, inter, n_experts = 2048, 1024, 16
+    g, pages, shared = make_layer(900 + n_tokens, hidden, inter, n_experts, L.PAGE_MXFP4)
+    x = synth.activations(g, n_tokens, hidden)
+    routes = []
+    for t in range(n_tokens):
+        ids = g.permutation(n_experts)[:6].tolist()
+        w = g.uniform(0.05, 0.4, 6).astype(np.float32)
+        routes.append((ids, w))
+    pages_dev, shared_dev = [dev(p) for p in pages], dev(shared)
+    for mode in (L.ACCUM_REFERENCE, L.ACCUM_PAIRWISE):
+        ctx.set_accumulation(mode)
+        y = run_layer(ctx, x, pages_dev, shared_dev, routes, L.PAGE_MXFP4, hidden, inter)
+        for t in range(n_tokens):
+            ids, w = routes[t]
+            if mode == L.ACCUM_REFERENCE:
+                ref = oracle.moe_layer(x[t], [pages[i] for i in ids], w, shared, 0, hidden, inter)
+                assert np.array_equal(y[t].view(np.uint32), ref.view(np.uint32))
+            else:
+                ref = oracle.moe_layer_acc64(x[t], [pages[i] for i in ids], w, shared, 0, hidden, inter)
+                assert_pairwise_close(oracle, y[t], ref)
+            single = run_layer(ctx, x[t:t + 1], pages_dev, shared_dev, [routes[t]], L.PAGE_MXFP4, hidden, inter)[0]
+            assert np.array_equal(single.view(np.uint32), y[t].view(np.uint32))
+    ctx.set_accumulation(L.ACCUM_PAIRWISE)
+
+
+def test_moe_layer_rejects_bad_routes(ctx):
+    hidden, inter = 1024, 1024
+    page = torch.zeros(ExpertPageLayout(hidden, inter).page_bytes, dtype=torch.uint8, device="cuda")
+    x = torch.zeros((1, hidden), device="cuda")
+    y = torch.empty_like(x)
+    ok = TokenRoute([0, 1], [0.5, 0.5], [page.data_ptr()] * 2)
+    ctx.cmd_moe_layer(x, y, [ok], None, L.PAGE_MXFP4, hidden, inter)
+    bad = [TokenRoute([0, 0], [0.5, 0.5], [page.data_ptr()] * 2),
+           TokenRoute([0, 1], [0.5, float("nan")], [page.data_ptr()] * 2),
+           TokenRoute([0, 1], [0.5, -1.0], [page.data_ptr()] * 2),
+           TokenRoute([0, 1], [0.5, 0.5], [page.data_ptr(), 0])]
+    for r in bad:
+        with pytest.raises(S14Error):
+            ctx.cmd_moe_layer(x, y, [r], None, L.PAGE_MXFP4, hidden, inter)
+    with pytest.raises(S14Error):
+        ctx.cmd_moe_layer(x, y, [ok], None, L.PAGE_MXFP4, 1000, inter)
+    with pytest.raises(S14Error):
+        ctx.cmd_moe_layer(x, y, [], None, L.PAGE_MXFP4, hidden, inter)
+    torch.cuda.synchronize()
+
+
+@pytest.mark.parametrize("score_fn", [L.SCORE_SIGMOID, L.SCORE_SQRT_SOFTPLUS])
+def test_router_indices_bit_exact(ctx, oracle, score_fn):
+    g = synth.rng(4242 + score_fn)
+    n_experts, hidden, tokens = 256, 4096, 8
+    wr, bias = synth.router_weight_bf16(g, n_experts, hidden), synth.router_bias(g, n_experts)
+    min_gap = np.inf
+    for rep in range(4):
+        x = synth.activations(g, tokens, hidden)
+        ids = torch.empty((tokens, 6), dtype=torch.int32, device="cuda")
+        wts = torch.empty((tokens, 6), dtype=torch.float32, device="cuda")
+        ctx.cmd_router(dev(x), dev(wr), dev(bias), ids, wts, score_fn=score_fn, top_k=6, route_scale=1.5)
+        torch.cuda.synchronize()
+        for t in range(tokens):
+            rid, rw, _, select = oracle.router(x[t], wr, bias, score_fn=score_fn, top_k=6, route_scale=1.5)
+            srt = np.sort(select)[::-1]
+            min_gap = min(min_gap, float(srt[5] - srt[6]))
+            assert np.array_equal(ids[t].cpu().numpy(), rid)
+            assert np.array_equal(wts[t].cpu().numpy().view(np.uint32), rw.view(np.uint32))
+    assert min_gap > 0
+
+
+def test_golden_router_fixture_on_gpu(ctx, golden):
+    g = synth.rng(1004)
+    wr, bias, x = synth.router_weight_bf16(g, 256, 1024), synth.router_bias(g, 256), synth.activations(g, 4, 1024)
+    for fn, name in ((L.SCORE_SIGMOID, "sig"), (L.SCORE_SQRT_SOFTPLUS, "ssp")):
+        ids = torch.empty((4, 6), dtype=torch.int32, device="cuda")
+        wts = torch.empty((4, 6), dtype=torch.float32, device="cuda")
+        ctx.cmd_router(dev(x), dev(wr), dev(bias), ids, wts, score_fn=fn, top_k=6, route_scale=1.5)
+        torch.cuda.synchronize()
+        assert np.array_equal(ids.cpu().numpy(), golden[f"rt_{name}_ids"])
+        np.testing.assert_allclose(wts.cpu().numpy(), golden[f"rt_{name}_w"], rtol=2e-6)
+
+
+def test_routed_layer_without_host_round_trip(ctx, oracle):
+    """Router and layer chained on the device: same route and same output as the two-step path."""
+    hidden, inter, n_experts = 2048, 1024, 32
+    g, pages, shared = make_layer(31337, hidden, inter, n_experts, L.PAGE_MXFP4)
+    wr, bias = synth.router_weight_bf16(g, n_experts, hidden), synth.router_bias(g, n_experts)
+    x = synth.activations(g, 1, hidden)
+    pages_dev, shared_dev = [dev(p) for p in pages], dev(shared)
+    table = torch.tensor([p.data_ptr() for p in pages_dev], dtype=torch.int64, device="cuda")
+    dx = dev(x)
+    y = torch.empty_like(dx)
+    ids = torch.empty(6, dtype=torch.int32, device="cuda")
+    wts = torch.empty(6, dtype=torch.float32, device="cuda")
+    for mode in (L.ACCUM_REFERENCE, L.ACCUM_PAIRWISE):
+        ctx.set_accumulation(mode)
+        ctx.cmd_routed_moe_layer(dx[0], dev(wr), dev(bias), table, shared_dev.data_ptr(), L.PAGE_MXFP4, inter, y,
+                                 ids, wts)
+        torch.cuda.synchronize()
+        rid, rw, _, _ = oracle.router(x[0], wr, bias, 0, 6, 1.0)
+        assert np.array_equal(ids.cpu().numpy(), rid)
+        assert np.array_equal(wts.cpu().numpy().view(np.uint32), rw.view(np.uint32))
+        if mode == L.ACCUM_REFERENCE:
+            ref = oracle.moe_layer(x[0], [pages[i] for i in rid], rw, shared, 0, hidden, inter)
+            assert np.array_equal(y.cpu().numpy()[0].view(np.uint32), ref.view(np.uint32))
+        else:
+            ref = oracle.moe_layer_acc64(x[0], [pages[i] for i in rid], rw, shared, 0, hidden, inter)
+            assert_pairwise_close(oracle, y.cpu().numpy()[0], ref)
+    ctx.set_accumulation(L.ACCUM_PAIRWISE)
+
+
+def test_head_logits_and_argmax(ctx, oracle, golden):
+    g = synth.rng(99)
+    vocab, hidden = 5003, 4096
+    w = synth.head_weight_bf16(g, vocab, hidden)
+    x = synth.activations(g, 3, hidden)
+    dw, dx = dev(w.view(np.int16)), dev(x)
+    logits = torch.empty((3, vocab), dtype=torch.float32, device="cuda")
+    ctx.cmd_head_logits(dx, dw, logits)
+    res = torch.empty(1, dtype=torch.int64, device="cuda")
+    torch.cuda.synchronize()
+    for t in range(3):
+        ref = oracle.head_logits(x[t], w)
+        # local_s14_primitives/tests/test_final_head.py:68-70 accepts rtol 2e-7 / atol 3e-7
+        np.testing.assert_allclose(logits[t].cpu().numpy(), ref, rtol=2e-7, atol=3e-7)
+        ctx.cmd_greedy_argmax(logits[t], res)
+        torch.cuda.synchronize()
+        assert int(res.item()) == oracle.greedy_argmax(ref)
+    # a vocabulary shard: rows [1000, 3000) written at their place in the full logits
+    part = torch.zeros(vocab, dtype=torch.float32, device="cuda")
+    ctx.cmd_head_logits(dx[0], dw[1000:3000], part[1000:3000], n_rows=2000)
+    torch.cuda.synchronize()
+    assert torch.equal(part[1000:3000], logits[0, 1000:3000]) and float(part[:1000].abs().sum()) == 0.0
+    # ties -> lowest id, NaN -> -1
+    tie = torch.tensor([1.0, 5.0, 5.0, 2.0], device="cuda")
+    ctx.cmd_greedy_argmax(tie, res)
+    torch.cuda.synchronize()
+    assert int(res.item()) == 1
+    tie[3] = float("nan")
+    ctx.cmd_greedy_argmax(tie, res)
+    torch.cuda.synchronize()
+    assert int(res.item()) == -1
+    # the reference's seed-731 head fixture
+    hx, hw = golden["hd_x"], golden["hd_w"]
+    out = torch.empty((1, 13), dtype=torch.float32, device="cuda")
+    for b in range(2):
+        for s in range(3):
+            ctx.cmd_head_logits(dev(hx[b, s]), dev(hw.view(np.int16)), out)
+            torch.cuda.synchronize()
+            np.testing.assert_allclose(out.cpu().numpy()[0], golden["hd_logits"][b, s], rtol=2e-7, atol=3e-7)
+
+
+def test_pool_upload_publish_compute_release(ctx, oracle):
+    """The page transaction end to end: route -> reserve -> pinned async upload on the copy
+    stream -> transfer fence -> publish -> layer on the slot addresses -> release."""
+    hidden, inter = 1024, 1024
+    lay = ExpertPageLayout(hidden, inter)
+    slot_bytes = lay.page_bytes
+    g, pages, shared = make_layer(555, hidden, inter, 256, L.PAGE_MXFP4)
+    routed_pool, shared_pool = VramPool(ctx, 8, slot_bytes), VramPool(ctx, 1, slot_bytes)
+    mp = S14MoePages(routed_pool, shared_pool, min_routed_bytes=slot_bytes, min_shared_bytes=slot_bytes)
+    staging = torch.empty((7, slot_bytes), dtype=torch.uint8).pin_memory()
+    x = synth.activations(g, 1, hidden)
+    dx = dev(x)
+    y = torch.empty_like(dx)
+
+    def step(ids, weights):
+        rd = RouteDecision(layer=42, kind=1, expert_ids=ids, weights=weights)
+        batch = mp.begin_after_official_route(rd)
+        missing = batch.missing()
+        for i, (res, is_shared) in enumerate(missing):
+            src = shared if is_shared else pages[res.key.slot]
+            staging[i].copy_(torch.from_numpy(src))
+            (shared_pool if is_shared else routed_pool).upload_page_async(res, staging[i].data_ptr(), slot_bytes)
+        routed_pool.transfer_fence()
+        routed_pool.wait_transfer_fence()
+        lease = mp.publish_after_transfer_fence(batch)
+        tr = TokenRoute(lease.expert_ids(), lease.route_weights(),
+                        [routed_pool.slot_ptr(b.slot) for b in lease.routed_bindings()])
+        ctx.cmd_moe_layer(dx, y, [tr], shared_pool.slot_ptr(lease.shared_binding().slot), L.PAGE_MXFP4, hidden, inter)
+        torch.cuda.synchronize()
+        mp.release_after_compute_fence(lease)
+        return len(missing), y.cpu().numpy()[0].copy()
+
+    ctx.set_accumulation(L.ACCUM_REFERENCE)
+    w = [0.25] * 6
+    n_up, out = step([126, 12, 205, 149, 227, 174], w)
+    assert n_up == 7
+    ref = oracle.moe_layer(x[0], [pages[i] for i in [126, 12, 205, 149, 227, 174]], np.asarray(w, np.float32),
+                           shared, 0, hidden, inter)
+    assert np.array_equal(out.view(np.uint32), ref.view(np.uint32))
+    n_up, out2 = step([126, 12, 205, 149, 227, 174], w)  # all cached now
+    assert n_up == 0 and np.array_equal(out2, out)
+    n_up, out3 = step([1, 12, 3, 149, 5, 174], w)  # three misses evict the least recently used
+    assert n_up == 3
+    ref = oracle.moe_layer(x[0], [pages[i] for i in [1, 12, 3, 149, 5, 174]], np.asarray(w, np.float32), shared, 0,
+                           hidden, inter)
+    assert np.array_equal(out3.view(np.uint32), ref.view(np.uint32))
+    ctx.set_accumulation(L.ACCUM_PAIRWISE)
+    # a NaN scale code in a payload is refused before upload
+    from colormlm_b200.s14 import validate_ue8m0_codes
+    bad = pages[9].copy()
+    bad[lay.offsets["s1"] + 5] = 0xFF
+    with pytest.raises(S14Error):
+        validate_ue8m0_codes(bad[lay.offsets["s1"]:])
+
+
+def test_moe_layer_host_buffers(ctx, oracle):
+    hidden, inter = 1024, 1024
+    g, pages, shared = make_layer(808, hidden, inter, 7, L.PAGE_MXFP4)
+    pages_dev, shared_dev = [dev(p) for p in pages], dev(shared)
+    x = synth.activations(g, 2, hidden)
+    y = np.empty_like(x)
+    w = np.asarray([0.3, 0.2, 0.2, 0.1, 0.1, 0.1], np.float32)
+    routes = [TokenRoute([0, 1, 2, 3, 4, 5], w, [p.data_ptr() for p in pages_dev[:6]]),
+              TokenRoute([5, 4, 3, 2, 1, 6], w, [pages_dev[i].data_ptr() for i in [5, 4, 3, 2, 1, 6]])]
+    torch.cuda.synchronize()
+    ctx.set_accumulation(L.ACCUM_REFERENCE)
+    before = ctx.launch_count
+    ctx.moe_layer_host(x, y, routes, shared_dev.data_ptr(), L.PAGE_MXFP4, hidden, inter)
+    assert ctx.launch_count - before == 3
+    for t, ids in enumerate(([0, 1, 2, 3, 4, 5], [5, 4, 3, 2, 1, 6])):
+        ref = oracle.moe_layer(x[t], [pages[i] for i in ids], w, shared, 0, hidden, inter)
+        assert np.array_equal(y[t].view(np.uint32), ref.view(np.uint32))
+    ctx.set_accumulation(L.ACCUM_PAIRWISE)
+    assert ctx.device_status() == 0

@@ -1,0 +1,272 @@
+"""Host-side contract of the S14 page pool and operator shapes, through the C ABI, without
+a GPU.  Each test restates a unit test of the reference (file:line in the docstring)."""
+import numpy as np
+import pytest
+
+from colormlm_b200 import _lib as L
+from colormlm_b200.s14 import (ExpertKey, RouteDecision, S14Error, S14MatvecShape, S14MoePages,
+                               VramPool, validate_e4m3fn_codes, validate_ue8m0_codes)
+
+pytestmark = pytest.mark.usefixtures("cuda_lib")
+
+ROUTED, SHARED = L.ROUTED_EXPERT_KIND, L.SHARED_EXPERT_KIND
+
+
+def route(ids, weights=None, layer=42, kind=1):
+    return RouteDecision(layer=layer, kind=kind, expert_ids=list(ids),
+                         weights=list(weights) if weights is not None else [0.25] * 6)
+
+
+def test_real_sample_shapes_have_exact_byte_contracts():
+    """s14_vulkan.rs:835-856"""
+    w1 = S14MatvecShape(2048, 4096).validate_mxfp4()
+    assert w1.mxfp4_weight_bytes() == 4_194_304 and w1.mxfp4_scale_bytes() == 262_144
+    w2 = S14MatvecShape(4096, 2048).validate_mxfp4()
+    assert w2.mxfp4_weight_bytes() == 4_194_304 and w2.mxfp4_scale_bytes() == 262_144
+    wq_a = S14MatvecShape(1024, 4096).validate_fp8()
+    assert wq_a.fp8_weight_bytes() == 4_194_304 and wq_a.fp8_scale_bytes() == 256
+    assert w1.fp32_input_bytes() == 16384 and w1.fp32_output_bytes() == 8192
+    assert 3 * 4_194_304 + 3 * 262_144 == L.EXPERT_PAGE_BYTES
+    shared_up = S14MatvecShape(2048, 4096).validate_fp8()
+    assert 3 * shared_up.fp8_weight_bytes() + 3 * shared_up.fp8_scale_bytes() == L.SHARED_EXPERT_PAGE_BYTES
+
+
+def test_rejects_invalid_quantized_codes():
+    """s14_vulkan.rs:859-865"""
+    validate_ue8m0_codes(bytes([0, 127, 254]))
+    with pytest.raises(S14Error) as e:
+        validate_ue8m0_codes(bytes([127, 255]))
+    assert e.value.code == L.ERR_CODE and "byte 1" in e.value.message
+    validate_e4m3fn_codes(bytes([0x00, 0x01, 0x7E, 0xFE]))
+    for bad in (0x7F, 0xFF):
+        with pytest.raises(S14Error):
+            validate_e4m3fn_codes(bytes([bad]))
+    validate_ue8m0_codes(b"")
+
+
+def test_mxfp4_rejects_non_native_k_alignment_and_zero_shapes():
+    """s14_vulkan.rs:868-873, 46-50"""
+    with pytest.raises(S14Error):
+        S14MatvecShape(1, 32).validate_mxfp4()
+    with pytest.raises(S14Error):
+        S14MatvecShape(0, 128)
+    with pytest.raises(S14Error):
+        S14MatvecShape(4, 0)
+    S14MatvecShape(1, 128).validate_mxfp4()
+    assert S14MatvecShape(129, 130).validate_fp8().fp8_scale_bytes() == 4  # ragged: ceil on both axes
+
+
+def test_reserve_eviction_logic():
+    """vram_pool.rs:437-489"""
+    p = VramPool(None, 3, 1024)
+    k1, k2, k3, k4 = (ExpertKey(0, 0, i) for i in (1, 2, 3, 4))
+    for i, k in enumerate((k1, k2, k3)):
+        slot, evicted = p.reserve_loading(k)
+        assert slot == i and evicted is None
+        assert p.lookup(k) is None  # hidden while Loading
+        p.mark_ready(slot, k)
+    assert p.n_loaded() == 3
+    p.lookup(k2)  # k1 becomes the oldest
+    slot, evicted = p.reserve_loading(k4)
+    assert slot == 0 and (evicted.layer, evicted.kind, evicted.slot) == (0, 0, 1)
+    assert p.lookup(k4) is None
+    p.mark_ready(slot, k4)
+    assert p.n_loaded() == 3
+    assert p.lookup(k1) is None
+    assert p.lookup(k2) is not None and p.lookup(k3) is not None and p.lookup(k4) is not None
+    assert p.capacity() == 3 and p.slot_bytes() == 1024 and p.total_bytes() == 3072
+    assert p.slot_offset(2) == 2048 and p.slot_ptr(2) is None
+
+
+def test_loading_slots_are_hidden_and_never_evicted():
+    """vram_pool.rs:492-522"""
+    p = VramPool(None, 1, 1024)
+    loading, other = ExpertKey(1, 0, 7), ExpertKey(1, 0, 8)
+    slot, _ = p.reserve_loading(loading)
+    assert p.lookup(loading) is None
+    with pytest.raises(S14Error) as e:
+        p.reserve_loading(other)
+    assert e.value.code == L.ERR_POOL
+    with pytest.raises(S14Error):
+        p.reserve_loading(loading)  # already loading
+    p.cancel_loading(slot, loading)
+    replacement, _ = p.reserve_loading(other)
+    assert replacement == slot
+    p.mark_ready(replacement, other)
+    assert p.lookup(other) == slot
+    with pytest.raises(S14Error):
+        p.reserve_loading(other)  # already ready
+
+
+def test_pinned_ready_slot_cannot_be_evicted_until_compute_fence_release():
+    """vram_pool.rs:525-551"""
+    p = VramPool(None, 1, 1024)
+    resident, replacement = ExpertKey(42, ROUTED, 126), ExpertKey(42, ROUTED, 12)
+    lease = p.publish_batch_and_pin([p.reserve_loading_generation(resident)])[0]
+    with pytest.raises(S14Error):
+        p.reserve_loading_generation(replacement)
+    p.release_after_compute_fence(lease)
+    r = p.reserve_loading_generation(replacement)
+    assert r.has_evicted and r.evicted.slot == 126
+
+
+def test_stale_generation_is_rejected_after_slot_reuse():
+    """vram_pool.rs:554-586"""
+    p = VramPool(None, 1, 1024)
+    first, second = ExpertKey(42, ROUTED, 126), ExpertKey(42, ROUTED, 12)
+    lease = p.publish_batch_and_pin([p.reserve_loading_generation(first)])[0]
+    stale = L.SlotBinding.from_buffer_copy(lease)
+    p.release_after_compute_fence(lease)
+    p.publish_batch_and_pin([p.reserve_loading_generation(second)])
+    with pytest.raises(S14Error):
+        p.validate_binding(stale)
+    with pytest.raises(S14Error):
+        p.release_after_compute_fence(stale)
+
+
+def test_batch_publish_preflight_prevents_partial_visibility():
+    """vram_pool.rs:589-616"""
+    p = VramPool(None, 2, 1024)
+    first, second = ExpertKey(42, ROUTED, 126), ExpertKey(42, ROUTED, 12)
+    r1, r2 = p.reserve_loading_generation(first), p.reserve_loading_generation(second)
+    stale2 = L.LoadingReservation.from_buffer_copy(r2)
+    stale2.generation += 1
+    with pytest.raises(S14Error):
+        p.publish_batch_and_pin([r1, stale2])
+    assert p.lookup(first) is None and p.lookup(second) is None
+    with pytest.raises(S14Error):
+        p.publish_batch_and_pin([])  # an empty batch is an error
+    with pytest.raises(S14Error):
+        p.publish_batch_and_pin([r1, r1])  # duplicate slot / key
+    p.cancel_reservation(r1)
+    p.cancel_reservation(r2)
+    with pytest.raises(S14Error):
+        p.cancel_reservation(r1)  # already cancelled
+    assert p.n_loaded() == 0
+
+
+def test_pool_rejects_degenerate_sizes():
+    """vram_pool.rs:77-85"""
+    for n, b in ((0, 1024), (4, 0), (0xFFFFFFFF, 1 << 62)):
+        with pytest.raises(S14Error):
+            VramPool(None, n, b)
+
+
+def test_route_decision_validate_for():
+    """s14_runner/src/runner.rs:128-180"""
+    good = route([126, 12, 205, 149, 227, 174])
+    good.validate_for(L.PROFILE_S14_TOP6)
+    good.validate_for(L.PROFILE_FULL_DEPTH43_NATIVE_TOP6)
+    bad_cases = [
+        route([126, 12, 205, 149, 227, 174], layer=3),             # not an S14 layer
+        route([126, 12, 205, 149, 227]),                           # five ids
+        route([126, 12, 205, 149, 227, 174], kind=0),              # score layer with hash kind
+        route([126, 12, 205, 149, 227, 256]),                      # id out of range
+        route([126, 126, 205, 149, 227, 174]),                     # duplicate
+        route([126, 12, 205, 149, 227, 174], [0.25] * 5 + [float("nan")]),
+        route([126, 12, 205, 149, 227, 174], [0.25] * 5 + [-0.25]),
+        route([126, 12, 205, 149, 227, 174], [0.0] + [0.25] * 5),  # sum 1.25
+    ]
+    for r in bad_cases:
+        with pytest.raises(S14Error) as e:
+            r.validate_for(L.PROFILE_S14_TOP6)
+        assert e.value.code == L.ERR_CONTRACT
+    route([1, 2, 3, 4, 5, 6], layer=3).validate_for(L.PROFILE_FULL_DEPTH43_NATIVE_TOP6)
+    route([1, 2, 3, 4, 5, 6], layer=1, kind=0).validate_for(L.PROFILE_S14_TOP6)  # hash layers 0-2
+
+
+def _pools(n_routed):
+    return (VramPool(None, n_routed, L.EXPERT_PAGE_BYTES), VramPool(None, 1, L.SHARED_EXPERT_PAGE_BYTES))
+
+
+def test_moe_pages_require_full_size_slots():
+    """s14_vulkan.rs:709-734"""
+    small = VramPool(None, 6, L.EXPERT_PAGE_BYTES - 1)
+    shared = VramPool(None, 1, L.SHARED_EXPERT_PAGE_BYTES)
+    with pytest.raises(S14Error):
+        S14MoePages(small, shared)
+    with pytest.raises(S14Error):
+        S14MoePages(VramPool(None, 6, L.EXPERT_PAGE_BYTES), VramPool(None, 1, L.EXPERT_PAGE_BYTES))
+    # an MXFP4 shared expert only needs a routed-size slot
+    S14MoePages(VramPool(None, 6, L.EXPERT_PAGE_BYTES), VramPool(None, 1, L.EXPERT_PAGE_BYTES),
+                min_shared_bytes=L.EXPERT_PAGE_BYTES)
+
+
+def test_route_load_batch_rolls_back_every_reservation_on_capacity_failure():
+    """s14_vulkan.rs:876-889"""
+    routed, shared = _pools(5)
+    pages = S14MoePages(routed, shared)
+    with pytest.raises(S14Error):
+        pages.begin_after_official_route(route([126, 12, 205, 149, 227, 174]))
+    assert routed.n_loaded() == 0 and shared.n_loaded() == 0
+
+
+def test_route_load_batch_rejects_duplicate_or_weight_drift_before_reservation():
+    """s14_vulkan.rs:892-908"""
+    routed, shared = _pools(6)
+    pages = S14MoePages(routed, shared)
+    with pytest.raises(S14Error):
+        pages.begin_after_official_route(route([126, 126, 205, 149, 227, 174]))
+    with pytest.raises(S14Error):
+        pages.begin_after_official_route(route([126, 12, 205, 149, 227, 174], [0.0] + [0.25] * 5))
+    assert routed.n_loaded() == 0 and shared.n_loaded() == 0
+
+
+def test_route_load_batch_capacity_failure_releases_cached_pin():
+    """s14_vulkan.rs:911-939"""
+    resident = ExpertKey(42, ROUTED, 126)
+    routed, shared = _pools(1)
+    lease = routed.publish_batch_and_pin([routed.reserve_loading_generation(resident)])[0]
+    routed.release_after_compute_fence(lease)
+    pages = S14MoePages(routed, shared)
+    with pytest.raises(S14Error):
+        pages.begin_after_official_route(route([126, 12, 205, 149, 227, 174]))
+    routed.reserve_loading_generation(ExpertKey(42, ROUTED, 7))  # the cached pin was given back
+
+
+def test_route_load_batch_publishes_all_then_holds_compute_fence_pins():
+    """s14_vulkan.rs:942-963"""
+    routed, shared = _pools(6)
+    pages = S14MoePages(routed, shared)
+    ids = [126, 12, 205, 149, 227, 174]
+    batch = pages.begin_after_official_route(route(ids))
+    missing = batch.missing()
+    assert len(missing) == 7 and [m[1] for m in missing] == [False] * 6 + [True]
+    compute = pages.publish_after_transfer_fence(batch)
+    assert len(compute.routed_bindings()) == 6 and compute.expert_ids() == ids
+    assert compute.route_weights() == [0.25] * 6
+    assert compute.shared_binding().key.kind == SHARED
+    with pytest.raises(S14Error):
+        pages.begin_after_official_route(route([1, 2, 3, 4, 5, 6]))  # everything is pinned
+    pages.release_after_compute_fence(compute)
+    replacement = pages.begin_after_official_route(route([1, 2, 3, 4, 5, 6]))
+    pages.cancel(replacement)
+    # a second pass over the first route now hits the shared page and misses the evicted ones
+    again = pages.begin_after_official_route(route(ids))
+    assert not any(is_shared for _, is_shared in again.missing())
+    pages.cancel(again)
+
+
+def test_stale_shared_generation_prevents_partial_routed_publication():
+    """s14_vulkan.rs:966-996"""
+    ids = [126, 12, 205, 149, 227, 174]
+    routed, shared = _pools(6)
+    pages = S14MoePages(routed, shared)
+    batch = pages.begin_after_official_route(route(ids))
+    stale_shared = [r for r, is_shared in batch.missing() if is_shared][0]
+    shared.cancel_reservation(stale_shared)
+    unrelated = shared.reserve_loading_generation(ExpertKey(42, SHARED, 1))
+    with pytest.raises(S14Error):
+        pages.publish_after_transfer_fence(batch)
+    for e in ids:
+        assert routed.lookup(ExpertKey(42, ROUTED, e)) is None
+    assert routed.n_loaded() == 0
+    shared.cancel_reservation(unrelated)
+
+
+def test_upload_needs_a_device_pool():
+    p = VramPool(None, 1, 1024)
+    r = p.reserve_loading_generation(ExpertKey(0, ROUTED, 0))
+    buf = np.zeros(16, np.uint8)
+    with pytest.raises(S14Error):
+        p.upload_page_async(r, buf.ctypes.data, 16)

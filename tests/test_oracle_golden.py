@@ -136,7 +136,7 @@ def test_expert_chain_and_layer_against_python_reference(oracle, golden):
     for kind, page, key in ((0, pages[6], "ly_y_mxfp4_shared"), (1, page8, "ly_y_fp8_shared")):
         ref = golden[key]
         scale = np.abs(ref).max()
-        y64 = oracle.moe_layer_f64(x, pages[:6], w, page, kind, hidden, inter)
+        y64 = oracle.moe_layer_acc64(x, pages[:6], w, page, kind, hidden, inter)
         assert np.abs(y64 - ref).max() < 2e-6 * scale
         y32 = oracle.moe_layer(x, pages[:6], w, page, kind, hidden, inter)
         assert np.abs(y32 - ref).max() < 1e-5 * scale
