@@ -220,7 +220,8 @@ def run_gpu(args) -> None:
 
     # resident state: N_LAYERS x (256 routed + 1 shared) pages, router weights, page tables
     layers = []
-    for layer in range(N_LAYERS):
+    n_layers = max(1, args.layers)
+    for layer in range(n_layers):
         pages = make_layer_pages(torch, N_EXPERTS + 1, gen)
         gl = synth.rng(500 + layer)
         wr = torch.from_numpy(synth.router_weight_bf16(gl, N_EXPERTS, HIDDEN).view(np.int16)).cuda()
@@ -235,7 +236,7 @@ def run_gpu(args) -> None:
     torch.cuda.synchronize()
 
     def enqueue_step(i: int, stream_handle=None):
-        ly = layers[i % N_LAYERS]
+        ly = layers[i % n_layers]
         ctx.cmd_routed_moe_layer(xs[i % n_tok], ly["wr"], ly["bias"], ly["table"], ly["shared"], L.PAGE_MXFP4,
                                  INTER, ys[i % N_LAYERS], stream=stream_handle)
 
@@ -310,21 +311,21 @@ def run_gpu(args) -> None:
     hy = torch.empty((HIDDEN,), dtype=torch.float32).pin_memory()
     hx_np, hy_np = hx.numpy(), hy.numpy()
     ids_np, w_np = np.empty(TOP_K, np.int32), np.empty(TOP_K, np.float32)
-    e2e_steps = min(args.steps, 2000)
+    e2e_steps = 0 if args.kernel_only else min(args.steps, 2000)
 
     def e2e_step(i):
-        ly = layers[i % N_LAYERS]
+        ly = layers[i % n_layers]
         ctx.routed_moe_layer_host(hx_np[i % n_tok], hy_np, ly["wr"], ly["bias"], ly["table"], ly["shared"],
                                   L.PAGE_MXFP4, INTER, ids_np, w_np)
 
-    for i in range(max(3, args.warmup)):
+    for i in range(0 if args.kernel_only else max(3, min(args.warmup, 100))):
         e2e_step(i)
     if world > 1:
         dist.barrier()
     t0 = time.perf_counter()
     for i in range(e2e_steps):
         e2e_step(i)
-    e2e_sec = time.perf_counter() - t0
+    e2e_sec = max(time.perf_counter() - t0, 1e-9)
     if world > 1:
         t = torch.tensor([e2e_sec], dtype=torch.float64, device="cuda")
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
@@ -333,7 +334,7 @@ def run_gpu(args) -> None:
 
     if rank == 0:
         cpu = None
-        if world == 1 and not args.no_cpu_baseline:
+        if world == 1 and not args.no_cpu_baseline and not args.kernel_only:
             from oracle import s14_oracle as oracle
 
             oracle.build()
@@ -349,7 +350,7 @@ def run_gpu(args) -> None:
             "steps": args.steps, "warmup": warm_full * N_LAYERS, "ms_per_step": ms / args.steps,
             "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f32",
             "data": "synthetic",
-            "config": {"workload": WORKLOAD, "layers_resident": N_LAYERS, "accumulation": args.accum,
+            "config": {"workload": WORKLOAD, "layers_resident": n_layers, "accumulation": args.accum,
                        "l2": "inputs larger than L2: 14 x 3.4 GB of pages walked round-robin, 96 MB per step",
                        "parallelism": "replicas" if world > 1 else "single"},
             "hbm_gbs": value / world * STEP_BYTES / 1e9, "hbm_frac_of_measured_peak": value / world * STEP_BYTES / 1e9 / peak,
@@ -381,6 +382,10 @@ def main() -> None:
     ap.add_argument("--accum", default="pairwise", choices=["pairwise", "reference"])
     ap.add_argument("--cpu-steps", type=int, default=60)
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--layers", type=int, default=N_LAYERS,
+                    help="resident layers (3.4 GB each); fewer than 14 is for profiler captures only")
+    ap.add_argument("--kernel-only", action="store_true",
+                    help="skip the end-to-end and CPU legs (profiler captures)")
     args = ap.parse_args()
     if args.impl == "reference":
         args.steps = args.steps if args.steps is not None else 60

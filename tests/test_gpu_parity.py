@@ -102,7 +102,7 @@ def test_mxfp4_extreme_scales_and_all_codes(ctx, oracle):
     ctx.set_accumulation(L.ACCUM_PAIRWISE)
     ref64 = oracle.mxfp4_matvec_f64(x, w, s, n, k)
     y = run_mxfp4(ctx, x, w, s, n, k)
-    np.testing.assert_allclose(y, ref64.astype(np.float32), rtol=3e-7, atol=1e-38)
+    assert np.abs(y - ref64).max() <= 4 * np.spacing(np.abs(ref64).max().astype(np.float32))
     s[:] = 254
     ref = oracle.mxfp4_matvec(x, w, s, n, k)
     ctx.set_accumulation(L.ACCUM_REFERENCE)
