@@ -506,9 +506,11 @@ static int32_t enqueue_layer(s14_ctx *ctx, cudaStream_t st, const s14_moe_layer_
     if (!x || !y) throw ContractError("S14 MoE layer: x or y is NULL");
     require_aligned(x, 16, "S14 MoE layer x");
     cudaError_t err;
+    bool all_mxfp4 = true;
+    for (uint32_t j = 0; j < tab.n_jobs; ++j) all_mxfp4 = all_mxfp4 && tab.jobs[j].kind == S14_PAGE_MXFP4;
     const int launched = launch_moe_layer(st, ctx->mode, ctx->sm_count, nullptr, tab, tab.n_tokens,
                                           tab.n_jobs, desc.hidden, desc.inter, x, ctx->h, ctx->d, y,
-                                          &err);
+                                          &err, nullptr, all_mxfp4);
     ctx->launches += launched;
     if (err != cudaSuccess) return cuda_fail(err, "S14 MoE layer launch");
     return S14_OK;
@@ -587,7 +589,8 @@ extern "C" int32_t s14_cmd_routed_moe_layer(s14_ctx *ctx, void *stream,
     unused.n_jobs = 0;
     const uint32_t n_jobs = r.top_k + (desc->shared_page ? 1u : 0u);
     ctx->launches += launch_moe_layer(st, ctx->mode, ctx->sm_count, ctx->dev_table, unused, 1, n_jobs,
-                                      r.hidden, desc->inter, r.x, ctx->h, ctx->d, desc->y, &err, km);
+                                      r.hidden, desc->inter, r.x, ctx->h, ctx->d, desc->y, &err, km,
+                                      !desc->shared_page || desc->shared_kind == S14_PAGE_MXFP4);
     if (err != cudaSuccess) return cuda_fail(err, "S14 MoE layer launch");
     if (km) {
         CUDA_OK(cudaStreamSynchronize(st));

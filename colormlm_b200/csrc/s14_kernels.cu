@@ -11,72 +11,9 @@
 //               (examples/s14_vulkan_numeric.rs:1669-1714), bit-identical to it.
 // The elementwise steps (limit-10 SwiGLU, route mix, ordered accumulate) use
 // separate F32 multiplies and adds in both modes, as the reference does.
-#include "s14_internal.h"
-
-#include <cuda_bf16.h>
-#include <cuda_fp16.h>
-#include <cuda_fp8.h>
+#include "s14_device.cuh"
 
 namespace s14 {
-
-// ---------------------------------------------------------------- decode ----
-
-// Eight E2M1 codes of one 32-bit word (low nibble first) -> four f16x2 words.
-__device__ __forceinline__ void e2m1x8_to_h2x4(uint32_t w, uint32_t &h0, uint32_t &h1,
-                                               uint32_t &h2, uint32_t &h3) {
-    asm("{\n"
-        ".reg .b8 b0, b1, b2, b3;\n"
-        "mov.b32 {b0, b1, b2, b3}, %4;\n"
-        "cvt.rn.f16x2.e2m1x2 %0, b0;\n"
-        "cvt.rn.f16x2.e2m1x2 %1, b1;\n"
-        "cvt.rn.f16x2.e2m1x2 %2, b2;\n"
-        "cvt.rn.f16x2.e2m1x2 %3, b3;\n"
-        "}\n"
-        : "=r"(h0), "=r"(h1), "=r"(h2), "=r"(h3)
-        : "r"(w));
-}
-
-// Four E4M3 codes of one 32-bit word -> two f16x2 words.
-__device__ __forceinline__ void e4m3x4_to_h2x2(uint32_t w, uint32_t &h0, uint32_t &h1) {
-    asm("{\n"
-        ".reg .b16 lo, hi;\n"
-        "mov.b32 {lo, hi}, %2;\n"
-        "cvt.rn.f16x2.e4m3x2 %0, lo;\n"
-        "cvt.rn.f16x2.e4m3x2 %1, hi;\n"
-        "}\n"
-        : "=r"(h0), "=r"(h1)
-        : "r"(w));
-}
-
-__device__ __forceinline__ float2 h2_to_f2(uint32_t h) {
-    __half2 v;
-    *reinterpret_cast<uint32_t *>(&v) = h;
-    return __half22float2(v);
-}
-
-// 2^(code-127) as a double: exact for every code 0..254.
-__device__ __forceinline__ double ue8m0_to_f64(uint32_t code) {
-    return __hiloint2double((int)((code + 896u) << 20), 0);
-}
-
-// 2^(code-127) as a float; code 0 is the subnormal 2^-127.
-__device__ __forceinline__ float ue8m0_to_f32(uint32_t code) {
-    return __uint_as_float(code == 0u ? 0x00400000u : (code << 23));
-}
-
-__device__ __forceinline__ uint4 ldg_stream(const uint4 *p) {
-    uint4 v;
-    asm volatile("ld.global.nc.L1::no_allocate.v4.u32 {%0,%1,%2,%3}, [%4];"
-                 : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w)
-                 : "l"(p));
-    return v;
-}
-
-__device__ __forceinline__ double warp_sum(double v) {
-#pragma unroll
-    for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
-    return v;
-}
 
 // F32 dot of 32 E2M1 codes (one 16-byte piece = one scale block) with 32
 // activations held in registers; two independent even/odd chains on the packed
@@ -108,16 +45,6 @@ __device__ __forceinline__ float dot16_e4m3(const uint4 &q, const float *__restr
         acc = __ffma2_rn(h2_to_f2(h1), make_float2(xr[i * 4 + 2], xr[i * 4 + 3]), acc);
     }
     return acc.x + acc.y;
-}
-
-// The reference's SwiGLU (examples/s14_vulkan_numeric.rs:1543-1556) in F32 with
-// separate operations.  expf is evaluated in double and rounded once, which
-// reproduces a correctly rounded expf.
-__device__ __forceinline__ float swiglu_limit_f32(float gate, float up) {
-    const float g = fminf(gate, 10.0f);
-    const float u = fminf(fmaxf(up, -10.0f), 10.0f);
-    const float e = (float)exp(-(double)g);
-    return __fmul_rn(__fdiv_rn(g, __fadd_rn(1.0f, e)), u);
 }
 
 // ------------------------------------------------- primitive operators ------
@@ -312,38 +239,6 @@ __global__ void k_moe_accumulate(const float *__restrict__ expert, float *__rest
 //   down : d[job, n]    = w2[n,:] . h[job,:]                        n < hidden
 //   mix  : y[t, n]      = sum over the token's jobs, in route order, of
 //                         weight * d[job, n]  (shared last, weight 1)
-
-__device__ __forceinline__ const JobTable &table_of(const JobTable *dev, const JobTable &param) {
-    return dev ? *dev : param;
-}
-
-struct PageView {
-    const uint8_t *w1, *w3, *w2, *s1, *s3, *s2;
-};
-
-__device__ __forceinline__ PageView page_view(const uint8_t *page, uint32_t kind, uint32_t hidden,
-                                              uint32_t inter) {
-    PageView v;
-    const size_t elems = (size_t)hidden * inter;
-    if (kind == S14_PAGE_MXFP4) {
-        const size_t wb = elems >> 1, sb = elems >> 5;
-        v.w1 = page;
-        v.w3 = page + wb;
-        v.w2 = page + 2 * wb;
-        v.s1 = page + 3 * wb;
-        v.s3 = v.s1 + sb;
-        v.s2 = v.s3 + sb;
-    } else {
-        const size_t sb = (size_t)((inter + 127u) >> 7) * ((hidden + 127u) >> 7);
-        v.w1 = page;
-        v.w3 = page + elems;
-        v.w2 = page + 2 * elems;
-        v.s1 = page + 3 * elems;
-        v.s3 = v.s1 + sb;
-        v.s2 = v.s3 + sb;
-    }
-    return v;
-}
 
 // One MXFP4 row against register-resident activations.  KC = K / 1024; lane l
 // owns the 32 elements k = j*1024 + l*32 ... of every 1024-wide slice j, which is
@@ -974,7 +869,7 @@ static void launch_down_pairwise(cudaStream_t st, const JobTable *dev, const Job
 int launch_moe_layer(cudaStream_t st, uint32_t mode, int sm_count, const JobTable *dev_table,
                      const JobTable &param_table, uint32_t n_tokens, uint32_t n_jobs_max,
                      uint32_t hidden, uint32_t inter, const float *x, float *h, float *d, float *y,
-                     cudaError_t *err, const KernelMarks *km) {
+                     cudaError_t *err, const KernelMarks *km, bool all_mxfp4) {
     int launches = 0;
     *err = cudaSuccess;
     if (km) cudaEventRecord(km->ev[1], st);
@@ -985,6 +880,13 @@ int launch_moe_layer(cudaStream_t st, uint32_t mode, int sm_count, const JobTabl
         if (km) cudaEventRecord(km->ev[2], st);
         k_expert_down_reference<<<gd, 32, inter * sizeof(float), st>>>(dev_table, param_table, h, d,
                                                                        hidden, inter);
+        launches += 2;
+    } else if (all_mxfp4) {
+        *err = launch_up_mma(st, sm_count, dev_table, param_table, x, h, hidden, inter, n_tokens);
+        if (km) cudaEventRecord(km->ev[2], st);
+        if (*err == cudaSuccess)
+            *err = launch_down_mma(st, sm_count, dev_table, param_table, h, d, hidden, inter, n_jobs_max);
+        if (*err != cudaSuccess) return launches;
         launches += 2;
     } else {
         const uint32_t ctas_per_token = max(1u, (uint32_t)sm_count / n_tokens);
