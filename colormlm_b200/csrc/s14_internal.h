@@ -55,7 +55,8 @@ int launch_moe_layer(cudaStream_t st, uint32_t mode, int sm_count, const JobTabl
                      cudaError_t *err, const KernelMarks *km = nullptr, bool all_mxfp4 = false);
 // Tensor-core pairwise phases (s14_moe_mma.cu); every job must be an MXFP4 page.
 cudaError_t launch_up_mma(cudaStream_t st, int sm_count, const JobTable *dev, const JobTable &param,
-                          const float *x, float *h, uint32_t hidden, uint32_t inter, uint32_t n_tokens);
+                          const float *x, float *h, uint32_t hidden, uint32_t inter, uint32_t n_tokens,
+                          uint32_t jobs_per_token);
 cudaError_t launch_down_mma(cudaStream_t st, int sm_count, const JobTable *dev, const JobTable &param,
                             const float *h, float *d, uint32_t hidden, uint32_t inter, uint32_t n_jobs);
 int launch_router(cudaStream_t st, const s14_router_desc &r, float *scores, float *select,

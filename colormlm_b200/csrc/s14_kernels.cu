@@ -882,7 +882,8 @@ int launch_moe_layer(cudaStream_t st, uint32_t mode, int sm_count, const JobTabl
                                                                        hidden, inter);
         launches += 2;
     } else if (all_mxfp4) {
-        *err = launch_up_mma(st, sm_count, dev_table, param_table, x, h, hidden, inter, n_tokens);
+        *err = launch_up_mma(st, sm_count, dev_table, param_table, x, h, hidden, inter, n_tokens,
+                             (n_jobs_max + n_tokens - 1) / n_tokens);
         if (km) cudaEventRecord(km->ev[2], st);
         if (*err == cudaSuccess)
             *err = launch_down_mma(st, sm_count, dev_table, param_table, h, d, hidden, inter, n_jobs_max);

@@ -1,10 +1,10 @@
 // Pairwise-order up and down phases of the fused MoE layer for MXFP4 pages, built around
 // the warp-level f16 tensor-core dot product (mma.sync m16n8k16, F32 accumulate).
 //
-// Why tensor cores in a matvec: measured on B200 the F32 path needs a half-to-float
+// Why tensor cores in a matvec: measured on B200, the F32 path needs a half-to-float
 // widening (2 FMA-pipe slots per element) plus a multiply-add per element, which alone
 // takes longer than streaming the weights from HBM.  Feeding the decoded f16x2 words
-// straight into an MMA removes both; the only per-element work left is the hardware
+// straight into an MMA removes both; the per-element work left is the hardware
 // E2M1 -> f16x2 conversion (one instruction per byte).
 //
 // Exactness: the activation vector is split into three f16 limbs (11 + 11 + 2 bits, each
@@ -15,29 +15,33 @@
 // summed in F32 and carried on in F64.  The summation order differs from the reference's
 // sequential F32 order, which is what S14_ACCUM_PAIRWISE means.
 //
-// Data movement: every warp owns 16 MMA rows (up phase: 8 gate rows of w1 and the 8 up
-// rows of w3 with the same indices; down phase: 16 rows of w2) and streams them through a
-// private cp.async ring in shared memory (16-byte coalesced copies, XOR-swizzled 128-byte
-// rows), four stages of 256 K-elements deep, so that loads in flight do not depend on
-// registers.  ldmatrix hands each lane the four bytes of its MMA fragment.
+// Data movement: one CTA per SM.  A warp streams tiles of 16 MMA rows (up phase: 8 gate
+// rows of w1 and the 8 up rows of w3 with the same indices; down phase: 16 rows of w2)
+// through a private cp.async ring in shared memory (16-byte coalesced copies,
+// XOR-swizzled 128-byte rows, stages of 256 K-elements), so that loads in flight do not
+// depend on registers; ldmatrix hands each lane the four bytes of its MMA fragment.  When a
+// CTA has few tiles, its (tile, stage) list is cut into equal runs for the warps and the
+// partial sums of a tile meet in shared memory in a fixed order.
 #include "s14_device.cuh"
 
 namespace s14 {
 
 namespace {
 
-constexpr int kStages = 4;         // cp.async ring depth per warp
-constexpr int kStageGroups = 8;    // scale blocks (32 elements) per stage: 128 B per row
-constexpr int kTileRows = 16;      // MMA rows per warp tile
-constexpr int kWarps = 8;          // warps per CTA
-constexpr int kStageBytes = kTileRows * 128;          // weights of one warp stage
-constexpr int kScaleStageBytes = kTileRows * 8;       // scale bytes of one warp stage
-constexpr int kWarpSmem = kStages * (kStageBytes + kScaleStageBytes);
+constexpr int kStages = 4;                        // cp.async ring depth per warp
+constexpr int kMaxWarps = 16;                     // warps per CTA (one CTA per SM)
+constexpr int kStageBytes = 16 * 128;             // 16 rows x 128 B of codes
+constexpr int kScaleRaw = 16 * 8;                 // 16 rows x 8 scale codes
+constexpr int kConvPitch = 80;                    // bytes per row of converted scales (8 x (f, f) + pad)
+constexpr int kConvBytes = 16 * kConvPitch;
+constexpr int kWarpSmem = kStages * (kStageBytes + kScaleRaw) + kConvBytes;
+constexpr int kSplitTiles = 16;                   // at most this many tiles per CTA are cut into runs
+constexpr int kMaxSeg = 3;                        // runs that can touch one tile
+constexpr int kPartBytes = kSplitTiles * kMaxSeg * 16 * 8;
 
 __device__ __forceinline__ uint32_t smem_u32(const void *p) {
     return (uint32_t)__cvta_generic_to_shared(p);
 }
-
 __device__ __forceinline__ void cp_async16(uint32_t dst, const void *src) {
     asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(dst), "l"(src));
 }
@@ -47,7 +51,7 @@ __device__ __forceinline__ void cp_async8(uint32_t dst, const void *src) {
 __device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;"); }
 template <int N>
 __device__ __forceinline__ void cp_async_wait() {
-    asm volatile("cp.async.wait_group %0;" ::"n"(N));
+    asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory");
 }
 
 __device__ __forceinline__ void ldmatrix_x4(uint32_t addr, uint32_t &r0, uint32_t &r1, uint32_t &r2,
@@ -57,20 +61,22 @@ __device__ __forceinline__ void ldmatrix_x4(uint32_t addr, uint32_t &r0, uint32_
                  : "r"(addr));
 }
 
-__device__ __forceinline__ void mma_f16(float (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2,
-                                        uint32_t a3, uint32_t b0, uint32_t b1) {
-    asm volatile(
-        "mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, "
-        "{%0,%1,%2,%3};"
-        : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
-        : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+// d = a * b + c; not volatile so that independent MMAs can be interleaved by the scheduler.
+__device__ __forceinline__ void mma_f16(float (&d)[4], uint32_t a0, uint32_t a1, uint32_t a2,
+                                        uint32_t a3, uint32_t b0, uint32_t b1, float c0, float c1,
+                                        float c2, float c3) {
+    asm("mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, "
+        "{%10,%11,%12,%13};"
+        : "=f"(d[0]), "=f"(d[1]), "=f"(d[2]), "=f"(d[3])
+        : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1), "f"(c0), "f"(c1), "f"(c2), "f"(c3));
 }
 
-// Shared-memory image of one token's activations as three f16 limbs: limb[j][k], each limb
-// row padded by 64 bytes so that the three rows start in different banks.
+// Shared-memory image of one token's activations: three f16 limb rows and one row of zeros
+// (the B fragment of the five unused MMA columns), each padded by 64 bytes.
 __device__ __forceinline__ uint32_t limb_pitch_bytes(uint32_t k) { return k * 2u + 64u; }
 
-// x = 2^e * (l1 + l2 * 2^-11 + l3 * 2^-22) exactly, |x| * 2^-e < 2.  Returns e.
+// x = 2^e * (l1 + l2 * 2^-11 + l3 * 2^-22) exactly, |x| * 2^-e < 1.  Returns e.  The caller
+// synchronises the CTA before the limbs are read.
 __device__ int build_limbs(const float *__restrict__ x, uint32_t k, uint8_t *limbs, float *red) {
     float m = 0.0f;
     for (uint32_t i = threadIdx.x; i < k; i += blockDim.x) m = fmaxf(m, fabsf(x[i]));
@@ -88,7 +94,7 @@ __device__ int build_limbs(const float *__restrict__ x, uint32_t k, uint8_t *lim
     const float down = ldexpf(1.0f, -e);
     const uint32_t pitch = limb_pitch_bytes(k);
     for (uint32_t i = threadIdx.x; i < k; i += blockDim.x) {
-        const float v = x[i] * down;  // exact: power of two, |v| < 1
+        const float v = x[i] * down;  // exact: power of two
         const __half l1 = __float2half_rn(v);
         const float r1 = (v - __half2float(l1)) * 2048.0f;  // exact
         const __half l2 = __float2half_rn(r1);
@@ -97,250 +103,380 @@ __device__ int build_limbs(const float *__restrict__ x, uint32_t k, uint8_t *lim
         reinterpret_cast<__half *>(limbs)[i] = l1;
         reinterpret_cast<__half *>(limbs + pitch)[i] = l2;
         reinterpret_cast<__half *>(limbs + 2 * pitch)[i] = l3;
+        reinterpret_cast<uint16_t *>(limbs + 3 * pitch)[i] = 0;
     }
-    __syncthreads();
     return e;
 }
 
-// Streams the 16 rows of one warp tile through the warp's ring and accumulates, per lane,
-// the MMA output fragment (rows g and g+8, columns 2t and 2t+1 = limbs) in F64.
-// row_ptr(m) gives the global address of MMA row m's packed codes, scale_ptr(m) its scale row.
+// Rows of one tile: MMA rows 0-7 are rows r0.. of matrix (w0, s0), rows 8-15 rows r1.. of (w1, s1).
 struct TileRows {
-    const uint8_t *w[2];   // base of MMA rows 0-7 and 8-15
-    const uint8_t *s[2];
-    uint32_t row0[2];      // first matrix row of each half
-    uint32_t row_bytes;    // K / 2
-    uint32_t scale_bytes;  // K / 32
+    const uint8_t *w0, *w1, *s0, *s1;
+    uint32_t r0, r1;
 };
 
-__device__ __forceinline__ void issue_stage(const TileRows &tr, uint32_t stage_k, uint32_t wbuf,
-                                            uint32_t sbuf, uint32_t lane) {
-    // 16 rows x 128 B = 128 chunks of 16 B, four per lane; eight consecutive lanes cover one row
+__device__ __forceinline__ void issue_stage(const TileRows &tr, uint32_t row_bytes, uint32_t scale_bytes,
+                                            uint32_t stage_k, uint32_t wbuf, uint32_t sbuf, uint32_t lane) {
+    // 16 rows x 128 B = 128 pieces of 16 B, four per lane; eight consecutive lanes cover one row
 #pragma unroll
     for (int i = 0; i < 4; ++i) {
-        const uint32_t q = i * 32 + lane, m = q >> 3, c = q & 7u;
-        const uint8_t *src = tr.w[m >> 3] + (size_t)(tr.row0[m >> 3] + (m & 7u)) * tr.row_bytes +
-                             (size_t)stage_k * 128u + c * 16u;
+        const uint32_t m = i * 4 + (lane >> 3), c = lane & 7u;  // i < 2: rows 0-7, else rows 8-15
+        const uint8_t *base = (i < 2) ? tr.w0 : tr.w1;
+        const uint32_t row = ((i < 2) ? tr.r0 : tr.r1) + (m & 7u);
+        const uint8_t *src = base + (size_t)row * row_bytes + (size_t)stage_k * 128u + c * 16u;
         cp_async16(wbuf + m * 128u + ((c ^ (m & 7u)) << 4), src);
     }
     if (lane < 16) {
-        const uint32_t m = lane;
-        const uint8_t *src = tr.s[m >> 3] + (size_t)(tr.row0[m >> 3] + (m & 7u)) * tr.scale_bytes +
-                             (size_t)stage_k * 8u;
-        cp_async8(sbuf + m * 8u, src);
+        const uint8_t *base = (lane < 8) ? tr.s0 : tr.s1;
+        const uint32_t row = ((lane < 8) ? tr.r0 : tr.r1) + (lane & 7u);
+        cp_async8(sbuf + lane * 8u, base + (size_t)row * scale_bytes + (size_t)stage_k * 8u);
     }
 }
 
-__device__ __forceinline__ float scale_f32(uint32_t code) {
-    return __uint_as_float(code ? (code << 23) : 0x00400000u);
+// The 128 scale codes of a stage -> (f, f) pairs of 2^(code-127) in the warp's conversion area.
+__device__ __forceinline__ void convert_scales(const uint8_t *raw, uint8_t *conv, uint32_t lane) {
+    const uint32_t w = reinterpret_cast<const uint32_t *>(raw)[lane];  // row lane/2, codes (lane&1)*4..
+    uint32_t b[4];
+    b[0] = (w & 0xffu) << 23;
+    b[1] = (w << 15) & 0x7f800000u;
+    b[2] = (w << 7) & 0x7f800000u;
+    b[3] = (w >> 1) & 0x7f800000u;
+    if (((w - 0x01010101u) & ~w & 0x80808080u) != 0u) {  // code 0 is the subnormal 2^-127
+#pragma unroll
+        for (int i = 0; i < 4; ++i) b[i] = b[i] ? b[i] : 0x00400000u;
+    }
+    uint4 *dst = reinterpret_cast<uint4 *>(conv + (lane >> 1) * kConvPitch + (lane & 1u) * 32u);
+    dst[0] = make_uint4(b[0], b[0], b[1], b[1]);
+    dst[1] = make_uint4(b[2], b[2], b[3], b[3]);
 }
 
-__device__ __forceinline__ void compute_stage(uint32_t wbuf, const uint8_t *sbuf_gen,
-                                              const uint8_t *limbs, uint32_t pitch, uint32_t k0,
+// One stage = eight scale blocks of the warp's 16 rows.  Four blocks at a time: two ldmatrix.x4,
+// four B fragments, eight MMAs (four independent chains of two), then the scale multiply.
+__device__ __forceinline__ void compute_stage(uint32_t wbuf, const uint8_t *conv, const uint8_t *bptr,
                                               uint32_t lane, double (&acc)[4]) {
-    const uint32_t g = lane >> 2, t = lane & 3u;
-    // the eight scale codes of rows g and g+8 for this stage
-    const uint2 sg = *reinterpret_cast<const uint2 *>(sbuf_gen + g * 8u);
-    const uint2 sh = *reinterpret_cast<const uint2 *>(sbuf_gen + (g + 8u) * 8u);
-    float part[4] = {0.f, 0.f, 0.f, 0.f};
+    const uint32_t g = lane >> 2;
+    float2 p_lo = make_float2(0.f, 0.f), p_hi = make_float2(0.f, 0.f);
     const uint32_t mat = lane >> 3, r = lane & 7u;
     const uint32_t lm_row = r + ((mat & 1u) << 3);
     const uint32_t lm_base = wbuf + lm_row * 128u;
-    const bool has_b = g < 3;
-    const uint8_t *bptr = limbs + (has_b ? g : 0u) * pitch + (size_t)(k0 + t * 8u) * 2u;
+    const uint8_t *cg = conv + g * kConvPitch, *ch = conv + (g + 8u) * kConvPitch;
 #pragma unroll
-    for (int cp = 0; cp < kStageGroups; cp += 2) {
-        uint32_t r0, r1, r2, r3;
-        ldmatrix_x4(lm_base + ((((uint32_t)cp + (mat >> 1)) ^ (lm_row & 7u)) << 4), r0, r1, r2, r3);
+    for (int hh = 0; hh < 2; ++hh) {
+        uint32_t raw[8];
+        ldmatrix_x4(lm_base + ((((uint32_t)(4 * hh) + (mat >> 1)) ^ (lm_row & 7u)) << 4), raw[0], raw[1],
+                    raw[2], raw[3]);
+        ldmatrix_x4(lm_base + ((((uint32_t)(4 * hh + 2) + (mat >> 1)) ^ (lm_row & 7u)) << 4), raw[4], raw[5],
+                    raw[6], raw[7]);
+        uint4 b[4];
 #pragma unroll
-        for (int half = 0; half < 2; ++half) {
-            const int c = cp + half;
-            const uint32_t lo = half ? r2 : r0, hi = half ? r3 : r1;
-            uint4 b = make_uint4(0u, 0u, 0u, 0u);
-            if (has_b) b = *reinterpret_cast<const uint4 *>(bptr + c * 64);
-            uint32_t a0, a2, a0b, a2b, a1, a3, a1b, a3b;
-            e2m1x8_to_h2x4(lo, a0, a2, a0b, a2b);
-            e2m1x8_to_h2x4(hi, a1, a3, a1b, a3b);
-            float cfrag[4] = {0.f, 0.f, 0.f, 0.f};
-            mma_f16(cfrag, a0, a1, a2, a3, b.x, b.y);
-            mma_f16(cfrag, a0b, a1b, a2b, a3b, b.z, b.w);
-            const uint32_t cg = (c < 4 ? (sg.x >> (8 * c)) : (sg.y >> (8 * (c - 4)))) & 0xffu;
-            const uint32_t ch = (c < 4 ? (sh.x >> (8 * c)) : (sh.y >> (8 * (c - 4)))) & 0xffu;
-            const float fg = scale_f32(cg), fh = scale_f32(ch);
-            part[0] = fmaf(cfrag[0], fg, part[0]);
-            part[1] = fmaf(cfrag[1], fg, part[1]);
-            part[2] = fmaf(cfrag[2], fh, part[2]);
-            part[3] = fmaf(cfrag[3], fh, part[3]);
+        for (int j = 0; j < 4; ++j) b[j] = *reinterpret_cast<const uint4 *>(bptr + (4 * hh + j) * 64);
+        const float4 sg0 = *reinterpret_cast<const float4 *>(cg + hh * 32);
+        const float4 sg1 = *reinterpret_cast<const float4 *>(cg + hh * 32 + 16);
+        const float4 sh0 = *reinterpret_cast<const float4 *>(ch + hh * 32);
+        const float4 sh1 = *reinterpret_cast<const float4 *>(ch + hh * 32 + 16);
+        float c[4][4];
+        uint32_t a[4][8];
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+            // a[j][0..3]: row g bytes 0..3 of block j; a[j][4..7]: row g+8
+            e2m1x8_to_h2x4(raw[j * 2], a[j][0], a[j][1], a[j][2], a[j][3]);
+            e2m1x8_to_h2x4(raw[j * 2 + 1], a[j][4], a[j][5], a[j][6], a[j][7]);
         }
-    }
 #pragma unroll
-    for (int i = 0; i < 4; ++i) acc[i] += (double)part[i];
+        for (int j = 0; j < 4; ++j)
+            mma_f16(c[j], a[j][0], a[j][4], a[j][1], a[j][5], b[j].x, b[j].y, 0.f, 0.f, 0.f, 0.f);
+#pragma unroll
+        for (int j = 0; j < 4; ++j)
+            mma_f16(c[j], a[j][2], a[j][6], a[j][3], a[j][7], b[j].z, b[j].w, c[j][0], c[j][1], c[j][2],
+                    c[j][3]);
+        p_lo = __ffma2_rn(make_float2(c[0][0], c[0][1]), make_float2(sg0.x, sg0.y), p_lo);
+        p_hi = __ffma2_rn(make_float2(c[0][2], c[0][3]), make_float2(sh0.x, sh0.y), p_hi);
+        p_lo = __ffma2_rn(make_float2(c[1][0], c[1][1]), make_float2(sg0.z, sg0.w), p_lo);
+        p_hi = __ffma2_rn(make_float2(c[1][2], c[1][3]), make_float2(sh0.z, sh0.w), p_hi);
+        p_lo = __ffma2_rn(make_float2(c[2][0], c[2][1]), make_float2(sg1.x, sg1.y), p_lo);
+        p_hi = __ffma2_rn(make_float2(c[2][2], c[2][3]), make_float2(sh1.x, sh1.y), p_hi);
+        p_lo = __ffma2_rn(make_float2(c[3][0], c[3][1]), make_float2(sg1.z, sg1.w), p_lo);
+        p_hi = __ffma2_rn(make_float2(c[3][2], c[3][3]), make_float2(sh1.z, sh1.w), p_hi);
+    }
+    acc[0] += (double)p_lo.x;
+    acc[1] += (double)p_lo.y;
+    acc[2] += (double)p_hi.x;
+    acc[3] += (double)p_hi.y;
 }
 
-// Runs `n_tiles` tiles of this warp (tile ids first, first + stride, ...) as one flat
-// cp.async pipeline; `setup(tile, tr)` fills the row pointers, `finish(tile, v_lo, v_hi)` gets
-// the finished values of rows g (v_lo) and g+8 (v_hi) on the lanes with t == 0.
-template <class Setup, class Finish>
-__device__ __forceinline__ void run_tiles(uint32_t first, uint32_t stride, uint32_t total_tiles,
-                                          uint32_t k, const uint8_t *limbs, int x_exp, uint8_t *ring,
-                                          uint32_t lane, Setup setup, Finish finish) {
-    if (first >= total_tiles) return;
-    const uint32_t n_tiles = (total_tiles - first + stride - 1) / stride;
-    const uint32_t stages_per_tile = k >> 8;
-    const uint32_t total = n_tiles * stages_per_tile;
+// The tiles of one CTA: tile ids first, first + stride, ..., n of them, each `spt` stages long.
+// Short lists are cut into equal runs of stages for the warps (a tile then has up to kMaxSeg
+// partial sums); long lists are dealt out tile by tile.
+struct WorkList {
+    uint32_t first, stride, n, spt;
+    bool split;
+    uint32_t warps_used, total;  // runs (split mode) or warps, and flat length
+};
+
+__device__ __forceinline__ WorkList make_work(uint32_t first, uint32_t stride, uint32_t total_tiles,
+                                              uint32_t spt, uint32_t n_warps) {
+    WorkList wl;
+    wl.first = first;
+    wl.stride = stride;
+    wl.spt = spt;
+    wl.n = first < total_tiles ? (total_tiles - first + stride - 1) / stride : 0u;
+    wl.split = wl.n <= (uint32_t)kSplitTiles;
+    wl.total = wl.n * spt;
+    const uint32_t min_run = (spt + 1u) >> 1;
+    wl.warps_used = wl.split ? max(1u, min(n_warps, wl.total / max(1u, min_run))) : n_warps;
+    return wl;
+}
+
+// Warp that owns flat stage f0 in split mode.
+__device__ __forceinline__ uint32_t run_of(const WorkList &wl, uint32_t f0) {
+    return (uint32_t)((((uint64_t)f0 + 1) * wl.warps_used + wl.total - 1) / wl.total) - 1u;
+}
+__device__ __forceinline__ uint32_t run_begin(const WorkList &wl, uint32_t w) {
+    return (uint32_t)(((uint64_t)w * wl.total) / wl.warps_used);
+}
+// True when one run covers the whole tile, so its result was stored directly.
+__device__ __forceinline__ bool tile_is_whole(const WorkList &wl, uint32_t tl) {
+    const uint32_t f0 = tl * wl.spt, w = run_of(wl, f0);
+    return run_begin(wl, w) <= f0 && run_begin(wl, w + 1) >= f0 + wl.spt;
+}
+
+// Runs this warp's share of the work list as one flat cp.async pipeline.  `setup(tile, tr)`
+// fills the row pointers of a global tile id; finished sums of rows g (lo) and g+8 (hi) are
+// handed, on the lanes with t == 0, to `emit(tile_local, seg, whole, lo, hi)`.
+template <class Setup, class Emit>
+__device__ __forceinline__ void run_tiles(const WorkList &wl, uint32_t warp, uint32_t k, const uint8_t *limbs,
+                                          uint8_t *ring, uint32_t lane, Setup setup, Emit emit) {
+    const uint32_t spt = wl.spt;
+    uint32_t f_lo, f_hi;
+    if (wl.split) {
+        if (warp >= wl.warps_used) return;
+        f_lo = run_begin(wl, warp);
+        f_hi = run_begin(wl, warp + 1);
+    } else {
+        if (warp >= wl.n) return;
+        f_lo = 0;
+        f_hi = ((wl.n - warp + wl.warps_used - 1) / wl.warps_used) * spt;
+    }
+    if (f_lo >= f_hi) return;
+    // flat index f -> local tile
+    auto tile_of = [&](uint32_t f) { return wl.split ? f / spt : warp + (f / spt) * wl.warps_used; };
+    const uint32_t row_bytes = k >> 1, scale_bytes = k >> 5;
     const uint32_t pitch = limb_pitch_bytes(k);
     const uint32_t ring_w = smem_u32(ring);
     const uint32_t ring_s = ring_w + kStages * kStageBytes;
     const uint8_t *ring_s_gen = ring + kStages * kStageBytes;
+    uint8_t *conv = ring + kStages * (kStageBytes + kScaleRaw);
+    const uint32_t g = lane >> 2, t = lane & 3u;
+    const uint8_t *bbase = limbs + (g < 3 ? g : 3u) * pitch + (size_t)(t * 8u) * 2u;
 
     TileRows tr_issue;
     uint32_t issue_tile = 0xffffffffu;
     auto issue = [&](uint32_t f) {
-        if (f < total) {
-            const uint32_t ti = f / stages_per_tile, st = f - ti * stages_per_tile;
-            if (ti != issue_tile) {
-                setup(first + ti * stride, tr_issue);
-                issue_tile = ti;
+        if (f < f_hi) {
+            const uint32_t tl = tile_of(f), st = f % spt;
+            if (tl != issue_tile) {
+                setup(wl.first + tl * wl.stride, tr_issue);
+                issue_tile = tl;
             }
-            const uint32_t slot = f % kStages;
-            issue_stage(tr_issue, st, ring_w + slot * kStageBytes, ring_s + slot * kScaleStageBytes, lane);
+            const uint32_t slot = (f - f_lo) % kStages;
+            issue_stage(tr_issue, row_bytes, scale_bytes, st, ring_w + slot * kStageBytes,
+                        ring_s + slot * kScaleRaw, lane);
         }
         cp_async_commit();
     };
 #pragma unroll
-    for (int f = 0; f < kStages - 1; ++f) issue(f);
+    for (int i = 0; i < kStages - 1; ++i) issue(f_lo + i);
     double acc[4] = {0.0, 0.0, 0.0, 0.0};
-    for (uint32_t f = 0; f < total; ++f) {
+    uint32_t slot = 0;
+    for (uint32_t f = f_lo; f < f_hi; ++f) {
+        const uint32_t st = f % spt;
         cp_async_wait<kStages - 2>();
         __syncwarp();
-        const uint32_t ti = f / stages_per_tile, st = f - ti * stages_per_tile;
-        const uint32_t slot = f % kStages;
-        compute_stage(ring_w + slot * kStageBytes, ring_s_gen + slot * kScaleStageBytes, limbs, pitch,
-                      st << 8, lane, acc);
+        convert_scales(ring_s_gen + slot * kScaleRaw, conv, lane);
+        __syncwarp();
+        compute_stage(ring_w + slot * kStageBytes, conv, bbase + (size_t)(st << 8) * 2u, lane, acc);
         __syncwarp();
         issue(f + kStages - 1);
-        if (st + 1 == stages_per_tile) {
+        slot = (slot + 1 == kStages) ? 0 : slot + 1;
+        if (st + 1 == spt || f + 1 == f_hi) {
             // columns: t == 0 holds limbs 0 and 1, t == 1 holds limb 2 (and an unused column)
             const double l2_lo = __shfl_down_sync(0xffffffffu, acc[0], 1);
             const double l2_hi = __shfl_down_sync(0xffffffffu, acc[2], 1);
-            const double sc = ldexp(1.0, x_exp);
-            const double v_lo = (acc[0] + acc[1] * (1.0 / 2048.0) + l2_lo * (1.0 / 4194304.0)) * sc;
-            const double v_hi = (acc[2] + acc[3] * (1.0 / 2048.0) + l2_hi * (1.0 / 4194304.0)) * sc;
-            finish(first + ti * stride, v_lo, v_hi);
+            const double v_lo = acc[0] + acc[1] * (1.0 / 2048.0) + l2_lo * (1.0 / 4194304.0);
+            const double v_hi = acc[2] + acc[3] * (1.0 / 2048.0) + l2_hi * (1.0 / 4194304.0);
+            const uint32_t tl = tile_of(f);
+            uint32_t seg = 0;
+            bool whole = true;
+            if (wl.split) {
+                seg = warp - run_of(wl, tl * spt);
+                whole = tile_is_whole(wl, tl);
+            }
+            if (t == 0) emit(tl, seg, whole, v_lo, v_hi);
             acc[0] = acc[1] = acc[2] = acc[3] = 0.0;
         }
     }
     cp_async_wait<0>();
 }
 
+__device__ __forceinline__ uint8_t *smem_limbs(uint8_t *smem, uint32_t n_warps) {
+    return smem + n_warps * kWarpSmem + kPartBytes;
+}
+__device__ __forceinline__ double *smem_parts(uint8_t *smem, uint32_t n_warps) {
+    return reinterpret_cast<double *>(smem + n_warps * kWarpSmem);
+}
+
 }  // namespace
 
-// Up phase.  grid = n_tokens * ctas_per_token, block = 256, dynamic smem =
-// 8 * kWarpSmem + 3 * limb pitch.  Tiles of 8 row pairs of the token's jobs, which must all be
-// MXFP4 pages (the launcher routes layers with an FP8 page to the F32 kernels).
-__global__ void __launch_bounds__(256, 2)
+// Up phase.  grid = n_tokens * ctas_per_token, block = 32 * warps, dynamic smem =
+// warps * kWarpSmem + kPartBytes + 4 * limb pitch.  Tiles of 8 row pairs of the token's jobs,
+// which must all be MXFP4 pages (the launcher routes layers with an FP8 page to the F32 kernels).
+__global__ void __launch_bounds__(512, 1)
 k_expert_up_mma(const JobTable *__restrict__ dev_table, const __grid_constant__ JobTable param_table,
                 const float *__restrict__ x, float *__restrict__ h, uint32_t hidden, uint32_t inter,
                 uint32_t ctas_per_token) {
     extern __shared__ __align__(128) uint8_t smem[];
-    __shared__ float red[kWarps];
+    __shared__ float red[kMaxWarps];
     const JobTable &tab = table_of(dev_table, param_table);
-    const uint32_t lane = threadIdx.x & 31u, warp = threadIdx.x >> 5;
+    const uint32_t lane = threadIdx.x & 31u, warp = threadIdx.x >> 5, n_warps = blockDim.x >> 5;
     const uint32_t token = blockIdx.x / ctas_per_token;
     const uint32_t cta_in_token = blockIdx.x - token * ctas_per_token;
-    uint8_t *limbs = smem + kWarps * kWarpSmem;
+    uint8_t *limbs = smem_limbs(smem, n_warps);
+    double *parts = smem_parts(smem, n_warps);
+    for (uint32_t i = threadIdx.x; i < kPartBytes / 8; i += blockDim.x) parts[i] = 0.0;
     const int x_exp = build_limbs(x + (size_t)token * hidden, hidden, limbs, red);
+    __syncthreads();
 
     const uint32_t job0 = tab.token_job_begin[token];
     const uint32_t n_jobs = tab.token_job_begin[token + 1] - job0;
     const uint32_t tiles_per_job = inter >> 3;
-    const uint32_t total_tiles = n_jobs * tiles_per_job;
-    const uint32_t first = cta_in_token * kWarps + warp, stride = ctas_per_token * kWarps;
-    const uint32_t g = lane >> 2, t = lane & 3u;
+    const WorkList wl = make_work(cta_in_token, ctas_per_token, n_jobs * tiles_per_job, hidden >> 8, n_warps);
+    const double sc = ldexp(1.0, x_exp);
+    const uint32_t g = lane >> 2;
 
     auto setup = [&](uint32_t tile, TileRows &tr) {
         const uint32_t jid = tab.token_jobs[job0 + tile / tiles_per_job];
-        const Job jb = tab.jobs[jid];
-        const PageView pv = page_view(jb.page, S14_PAGE_MXFP4, hidden, inter);
-        const uint32_t n0 = (tile % tiles_per_job) << 3;
-        tr.w[0] = pv.w1;
-        tr.w[1] = pv.w3;
-        tr.s[0] = pv.s1;
-        tr.s[1] = pv.s3;
-        tr.row0[0] = tr.row0[1] = n0;
-        tr.row_bytes = hidden >> 1;
-        tr.scale_bytes = hidden >> 5;
+        const PageView pv = page_view(tab.jobs[jid].page, S14_PAGE_MXFP4, hidden, inter);
+        tr.w0 = pv.w1;
+        tr.w1 = pv.w3;
+        tr.s0 = pv.s1;
+        tr.s1 = pv.s3;
+        tr.r0 = tr.r1 = (tile % tiles_per_job) << 3;
     };
-    auto finish = [&](uint32_t tile, double gate, double up) {
-        if (t == 0) {
-            const uint32_t jid = tab.token_jobs[job0 + tile / tiles_per_job];
-            const uint32_t n0 = (tile % tiles_per_job) << 3;
-            h[(size_t)jid * inter + n0 + g] = swiglu_limit_f32((float)gate, (float)up);
+    auto store = [&](uint32_t tile, uint32_t row, double gate, double up) {
+        const uint32_t jid = tab.token_jobs[job0 + tile / tiles_per_job];
+        h[(size_t)jid * inter + ((tile % tiles_per_job) << 3) + row] =
+            swiglu_limit_f32((float)(gate * sc), (float)(up * sc));
+    };
+    auto emit = [&](uint32_t tl, uint32_t seg, bool whole, double lo, double hi) {
+        if (whole) {
+            store(wl.first + tl * wl.stride, g, lo, hi);
+        } else {
+            double *p = parts + ((size_t)tl * kMaxSeg + seg) * 16;
+            p[g] = lo;
+            p[g + 8] = hi;
         }
     };
-    run_tiles(first, stride, total_tiles, hidden, limbs, x_exp, smem + warp * kWarpSmem, lane, setup, finish);
+    run_tiles(wl, warp, hidden, limbs, smem + warp * kWarpSmem, lane, setup, emit);
+    if (!wl.split) return;
+    __syncthreads();
+    // tiles whose stages were shared between warps: add the partial sums in run order
+    for (uint32_t i = threadIdx.x; i < wl.n * 8u; i += blockDim.x) {
+        const uint32_t tl = i >> 3, row = i & 7u;
+        if (tile_is_whole(wl, tl)) continue;
+        const double *p = parts + (size_t)tl * kMaxSeg * 16;
+        double gate = 0.0, up = 0.0;
+#pragma unroll
+        for (int s = 0; s < kMaxSeg; ++s) {
+            gate += p[s * 16 + row];
+            up += p[s * 16 + 8 + row];
+        }
+        store(wl.first + tl * wl.stride, row, gate, up);
+    }
 }
 
 // Down phase.  grid = n_jobs * ctas_per_job; a CTA keeps the limbs of its job's hidden vector.
-__global__ void __launch_bounds__(256, 2)
+__global__ void __launch_bounds__(512, 1)
 k_expert_down_mma(const JobTable *__restrict__ dev_table, const __grid_constant__ JobTable param_table,
                   const float *__restrict__ h, float *__restrict__ d, uint32_t hidden, uint32_t inter,
                   uint32_t ctas_per_job) {
     extern __shared__ __align__(128) uint8_t smem[];
-    __shared__ float red[kWarps];
+    __shared__ float red[kMaxWarps];
     const JobTable &tab = table_of(dev_table, param_table);
-    const uint32_t lane = threadIdx.x & 31u, warp = threadIdx.x >> 5;
+    const uint32_t lane = threadIdx.x & 31u, warp = threadIdx.x >> 5, n_warps = blockDim.x >> 5;
     const uint32_t jid = blockIdx.x / ctas_per_job;
     const uint32_t cta_in_job = blockIdx.x - jid * ctas_per_job;
     if (jid >= tab.n_jobs) return;
     const Job jb = tab.jobs[jid];
     if (jb.kind != S14_PAGE_MXFP4) return;
-    uint8_t *limbs = smem + kWarps * kWarpSmem;
+    uint8_t *limbs = smem_limbs(smem, n_warps);
+    double *parts = smem_parts(smem, n_warps);
+    for (uint32_t i = threadIdx.x; i < kPartBytes / 8; i += blockDim.x) parts[i] = 0.0;
     const int x_exp = build_limbs(h + (size_t)jid * inter, inter, limbs, red);
+    __syncthreads();
     const PageView pv = page_view(jb.page, S14_PAGE_MXFP4, hidden, inter);
-    const uint32_t total_tiles = hidden >> 4;
-    const uint32_t first = cta_in_job * kWarps + warp, stride = ctas_per_job * kWarps;
-    const uint32_t g = lane >> 2, t = lane & 3u;
+    const WorkList wl = make_work(cta_in_job, ctas_per_job, hidden >> 4, inter >> 8, n_warps);
+    const double sc = ldexp(1.0, x_exp);
+    const uint32_t g = lane >> 2;
     float *out = d + (size_t)jid * hidden;
     auto setup = [&](uint32_t tile, TileRows &tr) {
-        tr.w[0] = tr.w[1] = pv.w2;
-        tr.s[0] = tr.s[1] = pv.s2;
-        tr.row0[0] = tile << 4;
-        tr.row0[1] = (tile << 4) + 8u;
-        tr.row_bytes = inter >> 1;
-        tr.scale_bytes = inter >> 5;
+        tr.w0 = tr.w1 = pv.w2;
+        tr.s0 = tr.s1 = pv.s2;
+        tr.r0 = tile << 4;
+        tr.r1 = (tile << 4) + 8u;
     };
-    auto finish = [&](uint32_t tile, double lo, double hi) {
-        if (t == 0) {
-            out[(tile << 4) + g] = (float)lo;
-            out[(tile << 4) + 8u + g] = (float)hi;
+    auto emit = [&](uint32_t tl, uint32_t seg, bool whole, double lo, double hi) {
+        if (whole) {
+            const uint32_t tile = wl.first + tl * wl.stride;
+            out[(tile << 4) + g] = (float)(lo * sc);
+            out[(tile << 4) + 8u + g] = (float)(hi * sc);
+        } else {
+            double *p = parts + ((size_t)tl * kMaxSeg + seg) * 16;
+            p[g] = lo;
+            p[g + 8] = hi;
         }
     };
-    run_tiles(first, stride, total_tiles, inter, limbs, x_exp, smem + warp * kWarpSmem, lane, setup, finish);
+    run_tiles(wl, warp, inter, limbs, smem + warp * kWarpSmem, lane, setup, emit);
+    if (!wl.split) return;
+    __syncthreads();
+    for (uint32_t i = threadIdx.x; i < wl.n * 16u; i += blockDim.x) {
+        const uint32_t tl = i >> 4, row = i & 15u;
+        if (tile_is_whole(wl, tl)) continue;
+        const double *p = parts + (size_t)tl * kMaxSeg * 16;
+        double v = 0.0;
+#pragma unroll
+        for (int s = 0; s < kMaxSeg; ++s) v += p[s * 16 + row];
+        out[((wl.first + tl * wl.stride) << 4) + row] = (float)(v * sc);
+    }
 }
 
-static size_t mma_smem_bytes(uint32_t k) { return (size_t)kWarps * kWarpSmem + 3u * (k * 2u + 64u); }
+static size_t mma_smem_bytes(uint32_t warps, uint32_t k) {
+    return (size_t)warps * kWarpSmem + kPartBytes + 4u * (k * 2u + 64u);
+}
+
+static void configure_once() {
+    static bool configured = false;
+    if (configured) return;
+    const int most = (int)mma_smem_bytes(kMaxWarps, 4096);
+    cudaFuncSetAttribute(k_expert_up_mma, cudaFuncAttributeMaxDynamicSharedMemorySize, most);
+    cudaFuncSetAttribute(k_expert_down_mma, cudaFuncAttributeMaxDynamicSharedMemorySize, most);
+    configured = true;
+}
 
 cudaError_t launch_up_mma(cudaStream_t st, int sm_count, const JobTable *dev, const JobTable &param,
-                          const float *x, float *h, uint32_t hidden, uint32_t inter, uint32_t n_tokens) {
-    static bool configured = false;
-    if (!configured) {
-        cudaFuncSetAttribute(k_expert_up_mma, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                             (int)mma_smem_bytes(4096));
-        cudaFuncSetAttribute(k_expert_down_mma, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                             (int)mma_smem_bytes(4096));
-        configured = true;
-    }
-    const uint32_t ctas_per_token = max(1u, 2u * (uint32_t)sm_count / n_tokens);
-    k_expert_up_mma<<<n_tokens * ctas_per_token, 256, mma_smem_bytes(hidden), st>>>(
+                          const float *x, float *h, uint32_t hidden, uint32_t inter, uint32_t n_tokens,
+                          uint32_t jobs_per_token) {
+    (void)jobs_per_token;
+    configure_once();
+    const uint32_t ctas_per_token = max(1u, (uint32_t)sm_count / n_tokens);
+    k_expert_up_mma<<<n_tokens * ctas_per_token, kMaxWarps * 32, mma_smem_bytes(kMaxWarps, hidden), st>>>(
         dev, param, x, h, hidden, inter, ctas_per_token);
     return cudaGetLastError();
 }
 
 cudaError_t launch_down_mma(cudaStream_t st, int sm_count, const JobTable *dev, const JobTable &param,
                             const float *h, float *d, uint32_t hidden, uint32_t inter, uint32_t n_jobs) {
-    const uint32_t ctas_per_job = max(1u, (2u * (uint32_t)sm_count + n_jobs - 1) / n_jobs);
-    k_expert_down_mma<<<n_jobs * ctas_per_job, 256, mma_smem_bytes(inter), st>>>(
+    configure_once();
+    const uint32_t ctas_per_job = max(1u, (uint32_t)sm_count / n_jobs);
+    k_expert_down_mma<<<n_jobs * ctas_per_job, kMaxWarps * 32, mma_smem_bytes(kMaxWarps, inter), st>>>(
         dev, param, h, d, hidden, inter, ctas_per_job);
     return cudaGetLastError();
 }

@@ -10,7 +10,8 @@
  * (cited per function below as "numeric.rs:<lines>").  The evaluation order is
  * kept exactly: one output row at a time, k ascending, two separate
  * multiply-then-add steps per packed byte, `(x * decode) * scale` association,
- * no fused multiply-add (build with -ffp-contract=off), libm expf for SiLU.
+ * no fused multiply-add (build with -ffp-contract=off), correctly rounded F32 exp for SiLU
+ * (see s14o_swiglu_limit).
  * Rows are independent, so the OpenMP loop over rows (the reference uses a
  * rayon parallel iterator over rows, numeric.rs:1678, 1701) does not change any
  * result bit.
@@ -186,8 +187,24 @@ S14O_API void s14o_fp8_matvec_f64(const double *x, const uint8_t *weight, const 
     }
 }
 
-/* numeric.rs:1543-1556: gate is limited from above only, up on both sides. */
+/* numeric.rs:1543-1556: gate is limited from above only, up on both sides.  The
+ * reference calls its platform's F32 exp, whose last bit differs between C libraries
+ * (glibc's expf returns a value other than the correctly rounded one for about 80
+ * arguments per million).  The oracle pins the platform-independent definition: the
+ * correctly rounded F32 exponential, obtained as a double exp rounded once.
+ * s14o_swiglu_limit_libm keeps the libm call to measure that difference. */
 S14O_API void s14o_swiglu_limit(const float *gate, const float *up, uint32_t n, float *y) {
+    for (uint32_t i = 0; i < n; ++i) {
+        float g = gate[i] < 10.0f ? gate[i] : 10.0f;
+        float u = up[i];
+        if (u < -10.0f) u = -10.0f;
+        if (u > 10.0f) u = 10.0f;
+        const float e = (float)exp(-(double)g);
+        y[i] = (g / (1.0f + e)) * u;
+    }
+}
+
+S14O_API void s14o_swiglu_limit_libm(const float *gate, const float *up, uint32_t n, float *y) {
     for (uint32_t i = 0; i < n; ++i) {
         float g = gate[i] < 10.0f ? gate[i] : 10.0f;
         float u = up[i];

@@ -135,6 +135,14 @@ def swiglu_limit(gate, up) -> np.ndarray:
     return y
 
 
+def swiglu_limit_libm(gate, up) -> np.ndarray:
+    """The same with the C library's expf (not correctly rounded in rare cases)."""
+    gate, up = _f32(gate), _f32(up)
+    y = np.empty(gate.size, np.float32)
+    lib().s14o_swiglu_limit_libm(_p(gate), _p(up), C.c_uint32(gate.size), _p(y))
+    return y
+
+
 def expert_chain_mxfp4(x, page, hidden: int, inter: int, route_weight: float):
     """Returns (route_weight * down, down)."""
     x, page = _f32(x), _u8(page)

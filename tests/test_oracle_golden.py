@@ -154,6 +154,20 @@ def test_swiglu_limit_is_one_sided_on_the_gate(oracle):
     assert y[0] != 0.0 and abs(y[0] - silu(-10.0) * 3.0) > 1e-4  # -20 is NOT clamped to -10
 
 
+def test_swiglu_exp_definition_vs_libm(oracle):
+    """The oracle rounds a double exp once; libm's expf may differ in the last bit for a few
+    arguments per 10^5, which moves the SwiGLU value by at most one ulp."""
+    g = synth.rng(8)
+    gate = (g.standard_normal(400_000) * 6.2).astype(np.float32)
+    up = (g.standard_normal(400_000) * 6.2).astype(np.float32)
+    a, b = oracle.swiglu_limit(gate, up), oracle.swiglu_limit_libm(gate, up)
+    differ = np.nonzero(a != b)[0]
+    assert differ.size < 400  # < 1e-3 of the arguments
+    if differ.size:
+        ulp = np.spacing(np.abs(a[differ]))
+        assert (np.abs(a[differ] - b[differ]) <= 2 * ulp).all()
+
+
 def test_router_against_torch_reference(oracle, golden):
     g = synth.rng(1004)
     wr, bias, x = synth.router_weight_bf16(g, 256, 1024), synth.router_bias(g, 256), synth.activations(g, 4, 1024)
