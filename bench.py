@@ -241,7 +241,7 @@ def run_gpu(args) -> None:
                                  INTER, ys[i % N_LAYERS], stream=stream_handle)
 
     stream = torch.cuda.Stream()
-    kernels_per_step = 5
+    kernels_per_step = 3  # router (scores + select), up phase, down phase + mix
 
     def capture(n_steps: int, first: int):
         g = torch.cuda.CUDAGraph()

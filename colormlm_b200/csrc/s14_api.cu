@@ -47,6 +47,7 @@ extern "C" const char *s14_last_error(void) { return g_last_error.c_str(); }
 // ---- context ----------------------------------------------------------------
 
 static constexpr uint32_t kMaxDim = 4096;  // largest hidden / intermediate of the fused layer
+static constexpr uint32_t kCounters = 2048; // [0]: router; [1 + token * 160 + slice]: down-phase row slices
 
 struct s14_ctx {
     int device = 0;
@@ -65,6 +66,7 @@ struct s14_ctx {
     KernelMarks marks{};
     double kernel_ms[4] = {0, 0, 0, 0};  // router, up, down, mix
     uint64_t timed_calls = 0;
+    unsigned int *counters = nullptr;  // [kCounters] arrival counters of the fused kernels, all zero at rest
     int32_t *ids_stage = nullptr;  // [8] route ids / weights staging of the host-buffer call
     float *weights_stage = nullptr;
 };
@@ -100,6 +102,8 @@ extern "C" int32_t s14_ctx_create(int32_t device, s14_ctx **out) {
     CUDA_OK(cudaMalloc(&ctx->y_stage, sizeof(float) * kMaxTokens * kMaxDim));
     CUDA_OK(cudaMalloc(&ctx->status, sizeof(uint32_t)));
     CUDA_OK(cudaMemset(ctx->status, 0, sizeof(uint32_t)));
+    CUDA_OK(cudaMalloc(&ctx->counters, sizeof(unsigned int) * kCounters));
+    CUDA_OK(cudaMemset(ctx->counters, 0, sizeof(unsigned int) * kCounters));
     CUDA_OK(cudaMalloc(&ctx->ids_stage, sizeof(int32_t) * 8));
     CUDA_OK(cudaMalloc(&ctx->weights_stage, sizeof(float) * 8));
     for (auto &e : ctx->marks.ev) CUDA_OK(cudaEventCreate(&e));
@@ -120,6 +124,7 @@ extern "C" int32_t s14_ctx_destroy(s14_ctx *ctx) {
     cudaFree(ctx->x_stage);
     cudaFree(ctx->y_stage);
     cudaFree(ctx->status);
+    cudaFree(ctx->counters);
     cudaFree(ctx->ids_stage);
     cudaFree(ctx->weights_stage);
     for (auto &e : ctx->marks.ev)
@@ -510,7 +515,7 @@ static int32_t enqueue_layer(s14_ctx *ctx, cudaStream_t st, const s14_moe_layer_
     for (uint32_t j = 0; j < tab.n_jobs; ++j) all_mxfp4 = all_mxfp4 && tab.jobs[j].kind == S14_PAGE_MXFP4;
     const int launched = launch_moe_layer(st, ctx->mode, ctx->sm_count, nullptr, tab, tab.n_tokens,
                                           tab.n_jobs, desc.hidden, desc.inter, x, ctx->h, ctx->d, y,
-                                          &err, nullptr, all_mxfp4);
+                                          &err, nullptr, all_mxfp4, ctx->counters);
     ctx->launches += launched;
     if (err != cudaSuccess) return cuda_fail(err, "S14 MoE layer launch");
     return S14_OK;
@@ -560,7 +565,7 @@ extern "C" int32_t s14_cmd_router(s14_ctx *ctx, void *stream, const s14_router_d
     validate_router(*desc, true);
     cudaError_t err;
     ctx->launches += launch_router(stream_of(ctx, stream), *desc, ctx->scores, ctx->select, nullptr,
-                                   nullptr, nullptr, 0, &err);
+                                   nullptr, nullptr, 0, ctx->counters, &err);
     if (err != cudaSuccess) return cuda_fail(err, "S14 router launch");
     return S14_OK;
     S14_CATCH
@@ -583,14 +588,14 @@ extern "C" int32_t s14_cmd_routed_moe_layer(s14_ctx *ctx, void *stream,
     cudaError_t err;
     const KernelMarks *km = ctx->timing ? &ctx->marks : nullptr;
     ctx->launches += launch_router(st, r, ctx->scores, ctx->select, ctx->dev_table, desc->page_table,
-                                   desc->shared_page, desc->shared_kind, &err, km);
+                                   desc->shared_page, desc->shared_kind, ctx->counters, &err, km);
     if (err != cudaSuccess) return cuda_fail(err, "S14 router launch");
     JobTable unused;
     unused.n_jobs = 0;
     const uint32_t n_jobs = r.top_k + (desc->shared_page ? 1u : 0u);
     ctx->launches += launch_moe_layer(st, ctx->mode, ctx->sm_count, ctx->dev_table, unused, 1, n_jobs,
                                       r.hidden, desc->inter, r.x, ctx->h, ctx->d, desc->y, &err, km,
-                                      !desc->shared_page || desc->shared_kind == S14_PAGE_MXFP4);
+                                      !desc->shared_page || desc->shared_kind == S14_PAGE_MXFP4, ctx->counters);
     if (err != cudaSuccess) return cuda_fail(err, "S14 MoE layer launch");
     if (km) {
         CUDA_OK(cudaStreamSynchronize(st));

@@ -52,16 +52,19 @@ cudaError_t launch_moe_accumulate(cudaStream_t st, const float *expert, float *a
 int launch_moe_layer(cudaStream_t st, uint32_t mode, int sm_count, const JobTable *dev_table,
                      const JobTable &param_table, uint32_t n_tokens, uint32_t n_jobs_max,
                      uint32_t hidden, uint32_t inter, const float *x, float *h, float *d, float *y,
-                     cudaError_t *err, const KernelMarks *km = nullptr, bool all_mxfp4 = false);
+                     cudaError_t *err, const KernelMarks *km = nullptr, bool all_mxfp4 = false,
+                     unsigned int *counters = nullptr);
 // Tensor-core pairwise phases (s14_moe_mma.cu); every job must be an MXFP4 page.
 cudaError_t launch_up_mma(cudaStream_t st, int sm_count, const JobTable *dev, const JobTable &param,
                           const float *x, float *h, uint32_t hidden, uint32_t inter, uint32_t n_tokens,
                           uint32_t jobs_per_token);
 cudaError_t launch_down_mma(cudaStream_t st, int sm_count, const JobTable *dev, const JobTable &param,
-                            const float *h, float *d, uint32_t hidden, uint32_t inter, uint32_t n_jobs);
+                            const float *h, float *d, float *y, unsigned int *counters, uint32_t hidden,
+                            uint32_t inter, uint32_t n_jobs);
 int launch_router(cudaStream_t st, const s14_router_desc &r, float *scores, float *select,
                   JobTable *table_out, const uint8_t *const *page_table, const uint8_t *shared_page,
-                  uint32_t shared_kind, cudaError_t *err, const KernelMarks *km = nullptr);
+                  uint32_t shared_kind, unsigned int *counter, cudaError_t *err,
+                  const KernelMarks *km = nullptr);
 cudaError_t launch_head_logits(cudaStream_t st, int sm_count, const float *x, uint32_t n_tokens,
                                const uint16_t *w, uint32_t n_rows, uint32_t hidden, float *out,
                                uint32_t out_stride);

@@ -567,124 +567,163 @@ k_moe_mix(const JobTable *__restrict__ dev_table, const __grid_constant__ JobTab
 
 // ------------------------------------------------------------- router -------
 
-// logits in double: warp per (token, expert) row of BF16 weights.
-__global__ void __launch_bounds__(256)
-k_router_scores(const float *__restrict__ x, const uint16_t *__restrict__ wr,
-                const float *__restrict__ bias, float *__restrict__ scores,
-                float *__restrict__ select, uint32_t n_experts, uint32_t hidden, uint32_t n_tokens,
-                uint32_t score_fn) {
-    const uint32_t lane = threadIdx.x & 31u;
-    const uint32_t warp = (blockIdx.x * blockDim.x + threadIdx.x) >> 5;
-    if (warp >= n_experts * n_tokens) return;
-    const uint32_t t = warp / n_experts, e = warp - t * n_experts;
-    const uint4 *row = reinterpret_cast<const uint4 *>(wr + (size_t)e * hidden);
-    const float *xt = x + (size_t)t * hidden;
-    double acc = 0.0;
-    for (uint32_t p = lane; p < (hidden >> 3); p += 32u) {
-        const uint4 q = __ldg(row + p);
-        const uint32_t wd[4] = {q.x, q.y, q.z, q.w};
-        const float4 xa = __ldg(reinterpret_cast<const float4 *>(xt + p * 8));
-        const float4 xb = __ldg(reinterpret_cast<const float4 *>(xt + p * 8 + 4));
-        const float xv[8] = {xa.x, xa.y, xa.z, xa.w, xb.x, xb.y, xb.z, xb.w};
-#pragma unroll
-        for (int i = 0; i < 4; ++i) {
-            acc += (double)xv[i * 2] * (double)__uint_as_float(wd[i] << 16);
-            acc += (double)xv[i * 2 + 1] * (double)__uint_as_float(wd[i] & 0xffff0000u);
-        }
-    }
-    acc = warp_sum(acc);
-    if (lane == 0) {
-        const double l = (double)(float)acc;
-        const double sc = (score_fn == S14_SCORE_SIGMOID) ? 1.0 / (1.0 + exp(-l))
-                                                          : sqrt(l > 20.0 ? l : log1p(exp(l)));
-        const float s = (float)sc;
-        scores[(size_t)t * n_experts + e] = s;
-        select[(size_t)t * n_experts + e] = __fadd_rn(s, bias ? bias[e] : 0.0f);
-    }
-}
-
-// top-k of select (descending, ties -> lowest index) with one warp per token, then
-// the normalised weights; optionally writes the decode job table.
-__global__ void __launch_bounds__(32)
-k_router_select(const float *__restrict__ scores, const float *__restrict__ select,
-                uint32_t n_experts, uint32_t top_k, float route_scale, int32_t *__restrict__ ids_out,
-                float *__restrict__ weights_out, JobTable *__restrict__ table_out,
-                const uint8_t *const *__restrict__ page_table, const uint8_t *shared_page,
-                uint32_t shared_kind) {
-    const uint32_t lane = threadIdx.x;
-    const uint32_t t = blockIdx.x;
-    const float *sel = select + (size_t)t * n_experts;
-    const float *sco = scores + (size_t)t * n_experts;
-    float v[8];
+// One warp per (token, expert) row of BF16 weights: logit in double (every product
+// f32 x bf16 is exact in double), score and score + bias in F32.  The last CTA to finish
+// (a counter in global memory, no waiting) selects the top-k of every token, normalises the
+// weights and, for the one-token decode path, writes the job table of the layer.
+__device__ __forceinline__ void router_select(const float *scores, const float *select,
+                                              uint32_t n_experts, uint32_t top_k, float route_scale,
+                                              int32_t *ids_out, float *weights_out, JobTable *table_out,
+                                              const uint8_t *const *page_table, const uint8_t *shared_page,
+                                              uint32_t shared_kind, uint32_t lane) {
+    float v[8], sc[8];
 #pragma unroll
     for (int i = 0; i < 8; ++i) {
         const uint32_t e = i * 32 + lane;
-        v[i] = e < n_experts ? sel[e] : -INFINITY;
+        v[i] = e < n_experts ? __ldcg(select + e) : -INFINITY;
+        sc[i] = e < n_experts ? __ldcg(scores + e) : 0.0f;
     }
     uint32_t taken = 0;
-    int32_t my_ids[8];
-    float my_scores[8];
-    for (uint32_t j = 0; j < top_k; ++j) {
-        float best = -INFINITY;
-        uint32_t best_e = 0xffffffffu;
+    int32_t ids[8];
+    float picked[8];
 #pragma unroll
-        for (int i = 0; i < 8; ++i) {
-            const uint32_t e = i * 32 + lane;
-            if (e < n_experts && !((taken >> i) & 1u) && (best_e == 0xffffffffu || v[i] > best)) {
-                best = v[i];
-                best_e = e;
-            }
-        }
+    for (int j = 0; j < 8; ++j) {
+        ids[j] = -1;
+        picked[j] = 0.0f;
+        if ((uint32_t)j < top_k) {
+            float best = -INFINITY;
+            uint32_t best_e = 0xffffffffu;
+            float best_s = 0.0f;
 #pragma unroll
-        for (int o = 16; o > 0; o >>= 1) {
-            const float ob = __shfl_xor_sync(0xffffffffu, best, o);
-            const uint32_t oe = __shfl_xor_sync(0xffffffffu, best_e, o);
-            if (oe != 0xffffffffu && (best_e == 0xffffffffu || ob > best || (ob == best && oe < best_e))) {
-                best = ob;
-                best_e = oe;
+            for (int i = 0; i < 8; ++i) {
+                const uint32_t e = i * 32 + lane;
+                if (e < n_experts && !((taken >> i) & 1u) && (best_e == 0xffffffffu || v[i] > best)) {
+                    best = v[i];
+                    best_e = e;
+                    best_s = sc[i];
+                }
             }
+#pragma unroll
+            for (int o = 16; o > 0; o >>= 1) {
+                const float ob = __shfl_xor_sync(0xffffffffu, best, o);
+                const uint32_t oe = __shfl_xor_sync(0xffffffffu, best_e, o);
+                const float os = __shfl_xor_sync(0xffffffffu, best_s, o);
+                if (oe != 0xffffffffu && (best_e == 0xffffffffu || ob > best || (ob == best && oe < best_e))) {
+                    best = ob;
+                    best_e = oe;
+                    best_s = os;
+                }
+            }
+            if ((best_e & 31u) == lane) taken |= 1u << (best_e >> 5);
+            ids[j] = (int32_t)best_e;
+            picked[j] = best_s;
         }
-        if ((best_e & 31u) == lane) taken |= 1u << (best_e >> 5);
-        my_ids[j] = (int32_t)best_e;
-        my_scores[j] = sco[best_e];
     }
-    if (lane == 0) {
-        float sum = 0.0f;
-        for (uint32_t j = 0; j < top_k; ++j) sum = __fadd_rn(sum, my_scores[j]);
-        for (uint32_t j = 0; j < top_k; ++j) {
-            const float w = __fmul_rn(__fdiv_rn(my_scores[j], sum), route_scale);
-            if (ids_out) ids_out[(size_t)t * top_k + j] = my_ids[j];
-            if (weights_out) weights_out[(size_t)t * top_k + j] = w;
-            if (table_out) {
-                Job jb;
-                jb.page = page_table[my_ids[j]];
-                jb.kind = S14_PAGE_MXFP4;
-                jb.token = 0;
-                jb.weight = w;
-                jb.is_shared = 0;
-                table_out->jobs[j] = jb;
-                table_out->token_jobs[j] = j;
-            }
-        }
+    if (lane != 0) return;
+    float sum = 0.0f;
+#pragma unroll
+    for (int j = 0; j < 8; ++j)
+        if ((uint32_t)j < top_k) sum = __fadd_rn(sum, picked[j]);
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+        if ((uint32_t)j >= top_k) continue;
+        const float w = __fmul_rn(__fdiv_rn(picked[j], sum), route_scale);
+        if (ids_out) ids_out[j] = ids[j];
+        if (weights_out) weights_out[j] = w;
         if (table_out) {
-            uint32_t n = top_k;
-            if (shared_page) {
-                Job jb;
-                jb.page = shared_page;
-                jb.kind = shared_kind;
-                jb.token = 0;
-                jb.weight = 1.0f;
-                jb.is_shared = 1;
-                table_out->jobs[n] = jb;
-                table_out->token_jobs[n] = n;
-                ++n;
-            }
-            table_out->n_jobs = n;
-            table_out->n_tokens = 1;
-            table_out->token_job_begin[0] = 0;
-            table_out->token_job_begin[1] = n;
+            Job jb;
+            jb.page = page_table[ids[j]];
+            jb.kind = S14_PAGE_MXFP4;
+            jb.token = 0;
+            jb.weight = w;
+            jb.is_shared = 0;
+            table_out->jobs[j] = jb;
+            table_out->token_jobs[j] = (uint8_t)j;
         }
     }
+    if (table_out) {
+        uint32_t n = top_k;
+        if (shared_page) {
+            Job jb;
+            jb.page = shared_page;
+            jb.kind = shared_kind;
+            jb.token = 0;
+            jb.weight = 1.0f;
+            jb.is_shared = 1;
+            table_out->jobs[n] = jb;
+            table_out->token_jobs[n] = (uint8_t)n;
+            ++n;
+        }
+        table_out->n_jobs = n;
+        table_out->n_tokens = 1;
+        table_out->token_job_begin[0] = 0;
+        table_out->token_job_begin[1] = n;
+    }
+}
+
+__global__ void __launch_bounds__(64)
+k_router(const float *__restrict__ x, const uint16_t *__restrict__ wr, const float *__restrict__ bias,
+         float *__restrict__ scores, float *__restrict__ select, uint32_t n_experts, uint32_t hidden,
+         uint32_t n_tokens, uint32_t score_fn, uint32_t top_k, float route_scale,
+         int32_t *__restrict__ ids_out, float *__restrict__ weights_out, JobTable *__restrict__ table_out,
+         const uint8_t *const *__restrict__ page_table, const uint8_t *shared_page, uint32_t shared_kind,
+         unsigned int *__restrict__ counter) {
+    __shared__ bool is_last;
+    const uint32_t lane = threadIdx.x & 31u;
+    const uint32_t warp = (blockIdx.x * blockDim.x + threadIdx.x) >> 5;
+    if (warp < n_experts * n_tokens) {
+        const uint32_t t = warp / n_experts, e = warp - t * n_experts;
+        const uint4 *row = reinterpret_cast<const uint4 *>(wr + (size_t)e * hidden);
+        const float *xt = x + (size_t)t * hidden;
+        double acc0 = 0.0, acc1 = 0.0;
+        const uint32_t pieces = hidden >> 3;  // 8 weights per 16-byte piece
+        for (uint32_t p0 = lane; p0 < pieces; p0 += 32u * 8u) {
+            uint4 q[8];
+            float4 xa[8], xb[8];
+#pragma unroll
+            for (int u = 0; u < 8; ++u) {
+                const uint32_t p = p0 + u * 32u;
+                if (p < pieces) {
+                    q[u] = __ldg(row + p);
+                    xa[u] = __ldg(reinterpret_cast<const float4 *>(xt + p * 8));
+                    xb[u] = __ldg(reinterpret_cast<const float4 *>(xt + p * 8 + 4));
+                }
+            }
+#pragma unroll
+            for (int u = 0; u < 8; ++u) {
+                if (p0 + u * 32u < pieces) {
+                    const uint32_t wd[4] = {q[u].x, q[u].y, q[u].z, q[u].w};
+                    const float xv[8] = {xa[u].x, xa[u].y, xa[u].z, xa[u].w, xb[u].x, xb[u].y, xb[u].z, xb[u].w};
+#pragma unroll
+                    for (int i = 0; i < 4; ++i) {
+                        acc0 += (double)xv[i * 2] * (double)__uint_as_float(wd[i] << 16);
+                        acc1 += (double)xv[i * 2 + 1] * (double)__uint_as_float(wd[i] & 0xffff0000u);
+                    }
+                }
+            }
+        }
+        const double acc = warp_sum(acc0 + acc1);
+        if (lane == 0) {
+            const double l = (double)(float)acc;
+            const double sc = (score_fn == S14_SCORE_SIGMOID) ? 1.0 / (1.0 + exp(-l))
+                                                              : sqrt(l > 20.0 ? l : log1p(exp(l)));
+            const float s = (float)sc;
+            scores[(size_t)t * n_experts + e] = s;
+            select[(size_t)t * n_experts + e] = __fadd_rn(s, bias ? bias[e] : 0.0f);
+        }
+    }
+    __threadfence();
+    __syncthreads();
+    if (threadIdx.x == 0) is_last = atomicAdd(counter, 1u) == gridDim.x - 1u;
+    __syncthreads();
+    if (!is_last) return;
+    __threadfence();
+    for (uint32_t t = threadIdx.x >> 5; t < n_tokens; t += blockDim.x >> 5)
+        router_select(scores + (size_t)t * n_experts, select + (size_t)t * n_experts, n_experts, top_k,
+                      route_scale, ids_out ? ids_out + (size_t)t * top_k : nullptr,
+                      weights_out ? weights_out + (size_t)t * top_k : nullptr, table_out, page_table,
+                      shared_page, shared_kind, lane);
+    if (threadIdx.x == 0) *counter = 0u;  // ready for the next launch
 }
 
 // --------------------------------------------------------------- LM head ----
@@ -869,7 +908,7 @@ static void launch_down_pairwise(cudaStream_t st, const JobTable *dev, const Job
 int launch_moe_layer(cudaStream_t st, uint32_t mode, int sm_count, const JobTable *dev_table,
                      const JobTable &param_table, uint32_t n_tokens, uint32_t n_jobs_max,
                      uint32_t hidden, uint32_t inter, const float *x, float *h, float *d, float *y,
-                     cudaError_t *err, const KernelMarks *km, bool all_mxfp4) {
+                     cudaError_t *err, const KernelMarks *km, bool all_mxfp4, unsigned int *counters) {
     int launches = 0;
     *err = cudaSuccess;
     if (km) cudaEventRecord(km->ev[1], st);
@@ -881,14 +920,19 @@ int launch_moe_layer(cudaStream_t st, uint32_t mode, int sm_count, const JobTabl
         k_expert_down_reference<<<gd, 32, inter * sizeof(float), st>>>(dev_table, param_table, h, d,
                                                                        hidden, inter);
         launches += 2;
-    } else if (all_mxfp4) {
+    } else if (all_mxfp4 && counters) {
         *err = launch_up_mma(st, sm_count, dev_table, param_table, x, h, hidden, inter, n_tokens,
                              (n_jobs_max + n_tokens - 1) / n_tokens);
         if (km) cudaEventRecord(km->ev[2], st);
         if (*err == cudaSuccess)
-            *err = launch_down_mma(st, sm_count, dev_table, param_table, h, d, hidden, inter, n_jobs_max);
-        if (*err != cudaSuccess) return launches;
+            *err = launch_down_mma(st, sm_count, dev_table, param_table, h, d, y, counters, hidden, inter,
+                                   n_jobs_max);
         launches += 2;
+        if (km) {
+            cudaEventRecord(km->ev[3], st);
+            cudaEventRecord(km->ev[4], st);
+        }
+        return launches;  // the down kernel also mixes
     } else {
         const uint32_t ctas_per_token = max(1u, (uint32_t)sm_count / n_tokens);
         switch (hidden >> 10) {
@@ -916,17 +960,15 @@ int launch_moe_layer(cudaStream_t st, uint32_t mode, int sm_count, const JobTabl
 
 int launch_router(cudaStream_t st, const s14_router_desc &r, float *scores, float *select,
                   JobTable *table_out, const uint8_t *const *page_table, const uint8_t *shared_page,
-                  uint32_t shared_kind, cudaError_t *err, const KernelMarks *km) {
+                  uint32_t shared_kind, unsigned int *counter, cudaError_t *err, const KernelMarks *km) {
     const uint32_t warps = r.n_experts * r.n_tokens;
     if (km) cudaEventRecord(km->ev[0], st);
-    k_router_scores<<<ceil_div(warps, 8), 256, 0, st>>>(r.x, r.router_weight_bf16, r.bias, scores,
-                                                        select, r.n_experts, r.hidden, r.n_tokens,
-                                                        r.score_fn);
-    k_router_select<<<r.n_tokens, 32, 0, st>>>(scores, select, r.n_experts, r.top_k, r.route_scale,
-                                               r.ids_out, r.weights_out, table_out, page_table,
-                                               shared_page, shared_kind);
+    k_router<<<ceil_div(warps, 2), 64, 0, st>>>(r.x, r.router_weight_bf16, r.bias, scores, select,
+                                                r.n_experts, r.hidden, r.n_tokens, r.score_fn, r.top_k,
+                                                r.route_scale, r.ids_out, r.weights_out, table_out,
+                                                page_table, shared_page, shared_kind, counter);
     *err = cudaGetLastError();
-    return 2;
+    return 1;
 }
 
 cudaError_t launch_head_logits(cudaStream_t st, int sm_count, const float *x, uint32_t n_tokens,

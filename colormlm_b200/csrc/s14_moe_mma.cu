@@ -393,13 +393,16 @@ k_expert_up_mma(const JobTable *__restrict__ dev_table, const __grid_constant__ 
     }
 }
 
-// Down phase.  grid = n_jobs * ctas_per_job; a CTA keeps the limbs of its job's hidden vector.
+// Down phase and mix.  grid = n_jobs * ctas_per_job; a CTA keeps the limbs of its job's hidden
+// vector and owns the row tiles cta_in_job, cta_in_job + ctas_per_job, ... of that job.
 __global__ void __launch_bounds__(512, 1)
 k_expert_down_mma(const JobTable *__restrict__ dev_table, const __grid_constant__ JobTable param_table,
-                  const float *__restrict__ h, float *__restrict__ d, uint32_t hidden, uint32_t inter,
+                  const float *__restrict__ h, float *__restrict__ d, float *__restrict__ y,
+                  unsigned int *__restrict__ counters, uint32_t hidden, uint32_t inter,
                   uint32_t ctas_per_job) {
     extern __shared__ __align__(128) uint8_t smem[];
     __shared__ float red[kMaxWarps];
+    __shared__ bool is_last;
     const JobTable &tab = table_of(dev_table, param_table);
     const uint32_t lane = threadIdx.x & 31u, warp = threadIdx.x >> 5, n_warps = blockDim.x >> 5;
     const uint32_t jid = blockIdx.x / ctas_per_job;
@@ -435,17 +438,40 @@ k_expert_down_mma(const JobTable *__restrict__ dev_table, const __grid_constant_
         }
     };
     run_tiles(wl, warp, inter, limbs, smem + warp * kWarpSmem, lane, setup, emit);
-    if (!wl.split) return;
-    __syncthreads();
-    for (uint32_t i = threadIdx.x; i < wl.n * 16u; i += blockDim.x) {
-        const uint32_t tl = i >> 4, row = i & 15u;
-        if (tile_is_whole(wl, tl)) continue;
-        const double *p = parts + (size_t)tl * kMaxSeg * 16;
-        double v = 0.0;
+    if (wl.split) {
+        __syncthreads();
+        for (uint32_t i = threadIdx.x; i < wl.n * 16u; i += blockDim.x) {
+            const uint32_t tl = i >> 4, row = i & 15u;
+            if (tile_is_whole(wl, tl)) continue;
+            const double *p = parts + (size_t)tl * kMaxSeg * 16;
+            double v = 0.0;
 #pragma unroll
-        for (int s = 0; s < kMaxSeg; ++s) v += p[s * 16 + row];
-        out[((wl.first + tl * wl.stride) << 4) + row] = (float)(v * sc);
+            for (int s = 0; s < kMaxSeg; ++s) v += p[s * 16 + row];
+            out[((wl.first + tl * wl.stride) << 4) + row] = (float)(v * sc);
+        }
     }
+    // Ordered mix (examples/s14_vulkan_numeric.rs:936-946) by the last CTA of this token to finish
+    // this slice of rows: acc = 0; acc += w * d for the routed jobs in route order; acc += d_shared.
+    __threadfence();
+    __syncthreads();
+    const uint32_t j0 = tab.token_job_begin[jb.token], j1 = tab.token_job_begin[jb.token + 1];
+    unsigned int *counter = counters + 1u + jb.token * 160u + cta_in_job;
+    if (threadIdx.x == 0) is_last = atomicAdd(counter, 1u) == (j1 - j0) - 1u;
+    __syncthreads();
+    if (!is_last) return;
+    __threadfence();
+    for (uint32_t i = threadIdx.x; i < wl.n * 16u; i += blockDim.x) {
+        const uint32_t n = ((wl.first + (i >> 4) * wl.stride) << 4) + (i & 15u);
+        float acc = 0.0f;
+        for (uint32_t j = j0; j < j1; ++j) {
+            const uint32_t other = tab.token_jobs[j];
+            const float v = __ldcg(d + (size_t)other * hidden + n);
+            acc = tab.jobs[other].is_shared ? __fadd_rn(acc, v)
+                                            : __fadd_rn(acc, __fmul_rn(tab.jobs[other].weight, v));
+        }
+        y[(size_t)jb.token * hidden + n] = acc;
+    }
+    if (threadIdx.x == 0) *counter = 0u;  // ready for the next launch
 }
 
 static size_t mma_smem_bytes(uint32_t warps, uint32_t k) {
@@ -473,11 +499,12 @@ cudaError_t launch_up_mma(cudaStream_t st, int sm_count, const JobTable *dev, co
 }
 
 cudaError_t launch_down_mma(cudaStream_t st, int sm_count, const JobTable *dev, const JobTable &param,
-                            const float *h, float *d, uint32_t hidden, uint32_t inter, uint32_t n_jobs) {
+                            const float *h, float *d, float *y, unsigned int *counters, uint32_t hidden,
+                            uint32_t inter, uint32_t n_jobs) {
     configure_once();
     const uint32_t ctas_per_job = max(1u, (uint32_t)sm_count / n_jobs);
     k_expert_down_mma<<<n_jobs * ctas_per_job, kMaxWarps * 32, mma_smem_bytes(kMaxWarps, inter), st>>>(
-        dev, param, h, d, hidden, inter, ctas_per_job);
+        dev, param, h, d, y, counters, hidden, inter, ctas_per_job);
     return cudaGetLastError();
 }
 

@@ -476,7 +476,7 @@ def test_moe_layer_host_buffers(ctx, oracle):
     ctx.set_accumulation(L.ACCUM_REFERENCE)
     before = ctx.launch_count
     ctx.moe_layer_host(x, y, routes, shared_dev.data_ptr(), L.PAGE_MXFP4, hidden, inter)
-    assert ctx.launch_count - before == 3
+    assert ctx.launch_count - before == 3  # reference order: up, down, mix
     for t, ids in enumerate(([0, 1, 2, 3, 4, 5], [5, 4, 3, 2, 1, 6])):
         ref = oracle.moe_layer(x[t], [pages[i] for i in ids], w, shared, 0, hidden, inter)
         assert np.array_equal(y[t].view(np.uint32), ref.view(np.uint32))
