@@ -57,7 +57,7 @@ int launch_moe_layer(cudaStream_t st, uint32_t mode, int sm_count, const JobTabl
 // Tensor-core pairwise phases (s14_moe_mma.cu); every job must be an MXFP4 page.
 cudaError_t launch_up_mma(cudaStream_t st, int sm_count, const JobTable *dev, const JobTable &param,
                           const float *x, float *h, uint32_t hidden, uint32_t inter, uint32_t n_tokens,
-                          uint32_t jobs_per_token);
+                          bool after_router);
 cudaError_t launch_down_mma(cudaStream_t st, int sm_count, const JobTable *dev, const JobTable &param,
                             const float *h, float *d, float *y, unsigned int *counters, uint32_t hidden,
                             uint32_t inter, uint32_t n_jobs);

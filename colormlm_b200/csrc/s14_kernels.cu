@@ -669,6 +669,9 @@ k_router(const float *__restrict__ x, const uint16_t *__restrict__ wr, const flo
          const uint8_t *const *__restrict__ page_table, const uint8_t *shared_page, uint32_t shared_kind,
          unsigned int *__restrict__ counter) {
     __shared__ bool is_last;
+    // a dependent launch (the up phase) may start its own prologue now; it reads what this
+    // kernel writes only after cudaGridDependencySynchronize()
+    cudaTriggerProgrammaticLaunchCompletion();
     const uint32_t lane = threadIdx.x & 31u;
     const uint32_t warp = (blockIdx.x * blockDim.x + threadIdx.x) >> 5;
     if (warp < n_experts * n_tokens) {
@@ -922,7 +925,7 @@ int launch_moe_layer(cudaStream_t st, uint32_t mode, int sm_count, const JobTabl
         launches += 2;
     } else if (all_mxfp4 && counters) {
         *err = launch_up_mma(st, sm_count, dev_table, param_table, x, h, hidden, inter, n_tokens,
-                             (n_jobs_max + n_tokens - 1) / n_tokens);
+                             dev_table != nullptr);
         if (km) cudaEventRecord(km->ev[2], st);
         if (*err == cudaSuccess)
             *err = launch_down_mma(st, sm_count, dev_table, param_table, h, d, y, counters, hidden, inter,

@@ -24,6 +24,7 @@
 // partial sums of a tile meet in shared memory in a fixed order.
 #include "s14_device.cuh"
 
+
 namespace s14 {
 
 namespace {
@@ -114,22 +115,40 @@ struct TileRows {
     uint32_t r0, r1;
 };
 
-__device__ __forceinline__ void issue_stage(const TileRows &tr, uint32_t row_bytes, uint32_t scale_bytes,
-                                            uint32_t stage_k, uint32_t wbuf, uint32_t sbuf, uint32_t lane) {
-    // 16 rows x 128 B = 128 pieces of 16 B, four per lane; eight consecutive lanes cover one row
+// Per-lane source pointers of a tile (stage 0) and destination offsets inside a ring slot: the 16
+// rows x 128 B of a stage are 128 pieces of 16 B, four per lane, eight consecutive lanes per row.
+struct LaneCopy {
+    const uint8_t *src[4];
+    const uint8_t *ssrc;  // scale codes, lanes 0-15
+    uint32_t dst[4];
+};
+
+__device__ __forceinline__ void lane_copy_init(LaneCopy &lc, uint32_t lane) {
 #pragma unroll
     for (int i = 0; i < 4; ++i) {
-        const uint32_t m = i * 4 + (lane >> 3), c = lane & 7u;  // i < 2: rows 0-7, else rows 8-15
+        const uint32_t m = i * 4 + (lane >> 3), c = lane & 7u;
+        lc.dst[i] = m * 128u + ((c ^ (m & 7u)) << 4);
+    }
+}
+
+__device__ __forceinline__ void lane_copy_tile(LaneCopy &lc, const TileRows &tr, uint32_t row_bytes,
+                                               uint32_t scale_bytes, uint32_t lane) {
+    const uint32_t sub = lane >> 3, c = lane & 7u;
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {  // i < 2: MMA rows 0-7, else rows 8-15
         const uint8_t *base = (i < 2) ? tr.w0 : tr.w1;
-        const uint32_t row = ((i < 2) ? tr.r0 : tr.r1) + (m & 7u);
-        const uint8_t *src = base + (size_t)row * row_bytes + (size_t)stage_k * 128u + c * 16u;
-        cp_async16(wbuf + m * 128u + ((c ^ (m & 7u)) << 4), src);
+        const uint32_t row = ((i < 2) ? tr.r0 : tr.r1) + ((i & 1) * 4 + sub);
+        lc.src[i] = base + (size_t)row * row_bytes + c * 16u;
     }
-    if (lane < 16) {
-        const uint8_t *base = (lane < 8) ? tr.s0 : tr.s1;
-        const uint32_t row = ((lane < 8) ? tr.r0 : tr.r1) + (lane & 7u);
-        cp_async8(sbuf + lane * 8u, base + (size_t)row * scale_bytes + (size_t)stage_k * 8u);
-    }
+    const uint8_t *sbase = (lane < 8) ? tr.s0 : tr.s1;
+    lc.ssrc = sbase + (size_t)(((lane < 8) ? tr.r0 : tr.r1) + (lane & 7u)) * scale_bytes;
+}
+
+__device__ __forceinline__ void issue_stage(const LaneCopy &lc, uint32_t stage_k, uint32_t wbuf, uint32_t sbuf,
+                                            uint32_t lane) {
+#pragma unroll
+    for (int i = 0; i < 4; ++i) cp_async16(wbuf + lc.dst[i], lc.src[i] + stage_k * 128u);
+    if (lane < 16) cp_async8(sbuf + lane * 8u, lc.ssrc + stage_k * 8u);
 }
 
 // The 128 scale codes of a stage -> (f, f) pairs of 2^(code-127) in the warp's conversion area.
@@ -242,23 +261,26 @@ __device__ __forceinline__ bool tile_is_whole(const WorkList &wl, uint32_t tl) {
 // Runs this warp's share of the work list as one flat cp.async pipeline.  `setup(tile, tr)`
 // fills the row pointers of a global tile id; finished sums of rows g (lo) and g+8 (hi) are
 // handed, on the lanes with t == 0, to `emit(tile_local, seg, whole, lo, hi)`.
-template <class Setup, class Emit>
+// `before_compute()` runs on every warp of the CTA after the first copies are in flight and
+// before any activation limb is read (the down phase builds its limbs there).
+template <class Setup, class Emit, class Before>
 __device__ __forceinline__ void run_tiles(const WorkList &wl, uint32_t warp, uint32_t k, const uint8_t *limbs,
-                                          uint8_t *ring, uint32_t lane, Setup setup, Emit emit) {
+                                          uint8_t *ring, uint32_t lane, Setup setup, Emit emit,
+                                          Before before_compute) {
     const uint32_t spt = wl.spt;
-    uint32_t f_lo, f_hi;
+    uint32_t count = 0, tl0 = 0, st0 = 0, tl_step = 1;  // stages to run, first local tile and stage, tile step
     if (wl.split) {
-        if (warp >= wl.warps_used) return;
-        f_lo = run_begin(wl, warp);
-        f_hi = run_begin(wl, warp + 1);
-    } else {
-        if (warp >= wl.n) return;
-        f_lo = 0;
-        f_hi = ((wl.n - warp + wl.warps_used - 1) / wl.warps_used) * spt;
+        if (warp < wl.warps_used) {
+            const uint32_t f_lo = run_begin(wl, warp), f_hi = run_begin(wl, warp + 1);
+            count = f_hi - f_lo;
+            tl0 = f_lo / spt;
+            st0 = f_lo - tl0 * spt;
+        }
+    } else if (warp < wl.n) {
+        count = ((wl.n - warp + wl.warps_used - 1) / wl.warps_used) * spt;
+        tl0 = warp;
+        tl_step = wl.warps_used;
     }
-    if (f_lo >= f_hi) return;
-    // flat index f -> local tile
-    auto tile_of = [&](uint32_t f) { return wl.split ? f / spt : warp + (f / spt) * wl.warps_used; };
     const uint32_t row_bytes = k >> 1, scale_bytes = k >> 5;
     const uint32_t pitch = limb_pitch_bytes(k);
     const uint32_t ring_w = smem_u32(ring);
@@ -268,42 +290,51 @@ __device__ __forceinline__ void run_tiles(const WorkList &wl, uint32_t warp, uin
     const uint32_t g = lane >> 2, t = lane & 3u;
     const uint8_t *bbase = limbs + (g < 3 ? g : 3u) * pitch + (size_t)(t * 8u) * 2u;
 
-    TileRows tr_issue;
-    uint32_t issue_tile = 0xffffffffu;
-    auto issue = [&](uint32_t f) {
-        if (f < f_hi) {
-            const uint32_t tl = tile_of(f), st = f % spt;
-            if (tl != issue_tile) {
-                setup(wl.first + tl * wl.stride, tr_issue);
-                issue_tile = tl;
+    // producer side: next stage to copy
+    LaneCopy lc;
+    lane_copy_init(lc, lane);
+    uint32_t i_left = count, i_tl = tl0, i_st = st0, i_slot = 0;
+    bool i_new_tile = true;
+    auto issue = [&]() {
+        if (i_left) {
+            if (i_new_tile) {
+                TileRows tr;
+                setup(wl.first + i_tl * wl.stride, tr);
+                lane_copy_tile(lc, tr, row_bytes, scale_bytes, lane);
+                i_new_tile = false;
             }
-            const uint32_t slot = (f - f_lo) % kStages;
-            issue_stage(tr_issue, row_bytes, scale_bytes, st, ring_w + slot * kStageBytes,
-                        ring_s + slot * kScaleRaw, lane);
+            issue_stage(lc, i_st, ring_w + i_slot * kStageBytes, ring_s + i_slot * kScaleRaw, lane);
+            --i_left;
+            i_slot = (i_slot + 1 == kStages) ? 0 : i_slot + 1;
+            if (++i_st == spt) {
+                i_st = 0;
+                i_tl += tl_step;
+                i_new_tile = true;
+            }
         }
         cp_async_commit();
     };
 #pragma unroll
-    for (int i = 0; i < kStages - 1; ++i) issue(f_lo + i);
+    for (int i = 0; i < kStages - 1; ++i) issue();
+    before_compute();
     double acc[4] = {0.0, 0.0, 0.0, 0.0};
-    uint32_t slot = 0;
-    for (uint32_t f = f_lo; f < f_hi; ++f) {
-        const uint32_t st = f % spt;
+    uint32_t slot = 0, tl = tl0, st = st0;
+    for (uint32_t left = count; left; --left) {
         cp_async_wait<kStages - 2>();
         __syncwarp();
         convert_scales(ring_s_gen + slot * kScaleRaw, conv, lane);
         __syncwarp();
         compute_stage(ring_w + slot * kStageBytes, conv, bbase + (size_t)(st << 8) * 2u, lane, acc);
         __syncwarp();
-        issue(f + kStages - 1);
+        issue();
         slot = (slot + 1 == kStages) ? 0 : slot + 1;
-        if (st + 1 == spt || f + 1 == f_hi) {
+        ++st;
+        if (st == spt || left == 1) {
             // columns: t == 0 holds limbs 0 and 1, t == 1 holds limb 2 (and an unused column)
             const double l2_lo = __shfl_down_sync(0xffffffffu, acc[0], 1);
             const double l2_hi = __shfl_down_sync(0xffffffffu, acc[2], 1);
             const double v_lo = acc[0] + acc[1] * (1.0 / 2048.0) + l2_lo * (1.0 / 4194304.0);
             const double v_hi = acc[2] + acc[3] * (1.0 / 2048.0) + l2_hi * (1.0 / 4194304.0);
-            const uint32_t tl = tile_of(f);
             uint32_t seg = 0;
             bool whole = true;
             if (wl.split) {
@@ -312,6 +343,10 @@ __device__ __forceinline__ void run_tiles(const WorkList &wl, uint32_t warp, uin
             }
             if (t == 0) emit(tl, seg, whole, v_lo, v_hi);
             acc[0] = acc[1] = acc[2] = acc[3] = 0.0;
+            if (st == spt) {
+                st = 0;
+                tl += tl_step;
+            }
         }
     }
     cp_async_wait<0>();
@@ -344,6 +379,11 @@ k_expert_up_mma(const JobTable *__restrict__ dev_table, const __grid_constant__ 
     for (uint32_t i = threadIdx.x; i < kPartBytes / 8; i += blockDim.x) parts[i] = 0.0;
     const int x_exp = build_limbs(x + (size_t)token * hidden, hidden, limbs, red);
     __syncthreads();
+    // When launched as a programmatic dependent of the router, everything above overlapped with
+    // it; the job table is read only after the router has completed.  The down kernel may queue
+    // behind this one from here on (its CTAs start as ours retire and prefetch their weights).
+    cudaGridDependencySynchronize();
+    cudaTriggerProgrammaticLaunchCompletion();
 
     const uint32_t job0 = tab.token_job_begin[token];
     const uint32_t n_jobs = tab.token_job_begin[token + 1] - job0;
@@ -375,7 +415,7 @@ k_expert_up_mma(const JobTable *__restrict__ dev_table, const __grid_constant__ 
             p[g + 8] = hi;
         }
     };
-    run_tiles(wl, warp, hidden, limbs, smem + warp * kWarpSmem, lane, setup, emit);
+    run_tiles(wl, warp, hidden, limbs, smem + warp * kWarpSmem, lane, setup, emit, [] {});
     if (!wl.split) return;
     __syncthreads();
     // tiles whose stages were shared between warps: add the partial sums in run order
@@ -413,11 +453,17 @@ k_expert_down_mma(const JobTable *__restrict__ dev_table, const __grid_constant_
     uint8_t *limbs = smem_limbs(smem, n_warps);
     double *parts = smem_parts(smem, n_warps);
     for (uint32_t i = threadIdx.x; i < kPartBytes / 8; i += blockDim.x) parts[i] = 0.0;
-    const int x_exp = build_limbs(h + (size_t)jid * inter, inter, limbs, red);
-    __syncthreads();
     const PageView pv = page_view(jb.page, S14_PAGE_MXFP4, hidden, inter);
     const WorkList wl = make_work(cta_in_job, ctas_per_job, hidden >> 4, inter >> 8, n_warps);
-    const double sc = ldexp(1.0, x_exp);
+    double sc = 1.0;
+    // The weight copies start before the up phase has finished (programmatic dependent launch);
+    // the hidden vector is read, and split into limbs, only after it has.
+    auto before = [&] {
+        cudaGridDependencySynchronize();
+        const int x_exp = build_limbs(h + (size_t)jid * inter, inter, limbs, red);
+        __syncthreads();
+        sc = ldexp(1.0, x_exp);
+    };
     const uint32_t g = lane >> 2;
     float *out = d + (size_t)jid * hidden;
     auto setup = [&](uint32_t tile, TileRows &tr) {
@@ -437,7 +483,7 @@ k_expert_down_mma(const JobTable *__restrict__ dev_table, const __grid_constant_
             p[g + 8] = hi;
         }
     };
-    run_tiles(wl, warp, inter, limbs, smem + warp * kWarpSmem, lane, setup, emit);
+    run_tiles(wl, warp, inter, limbs, smem + warp * kWarpSmem, lane, setup, emit, before);
     if (wl.split) {
         __syncthreads();
         for (uint32_t i = threadIdx.x; i < wl.n * 16u; i += blockDim.x) {
@@ -487,15 +533,30 @@ static void configure_once() {
     configured = true;
 }
 
+template <class Kernel, class... Args>
+static cudaError_t launch_pdl(Kernel kernel, dim3 grid, dim3 block, size_t smem, cudaStream_t st, bool pdl,
+                              Args... args) {
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = grid;
+    cfg.blockDim = block;
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = st;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = pdl ? 1 : 0;
+    return cudaLaunchKernelEx(&cfg, kernel, args...);
+}
+
 cudaError_t launch_up_mma(cudaStream_t st, int sm_count, const JobTable *dev, const JobTable &param,
                           const float *x, float *h, uint32_t hidden, uint32_t inter, uint32_t n_tokens,
-                          uint32_t jobs_per_token) {
-    (void)jobs_per_token;
+                          bool after_router) {
     configure_once();
     const uint32_t ctas_per_token = max(1u, (uint32_t)sm_count / n_tokens);
-    k_expert_up_mma<<<n_tokens * ctas_per_token, kMaxWarps * 32, mma_smem_bytes(kMaxWarps, hidden), st>>>(
-        dev, param, x, h, hidden, inter, ctas_per_token);
-    return cudaGetLastError();
+    return launch_pdl(k_expert_up_mma, dim3(n_tokens * ctas_per_token), dim3(kMaxWarps * 32),
+                      mma_smem_bytes(kMaxWarps, hidden), st, after_router, dev, param, x, h, hidden, inter,
+                      ctas_per_token);
 }
 
 cudaError_t launch_down_mma(cudaStream_t st, int sm_count, const JobTable *dev, const JobTable &param,
@@ -503,9 +564,9 @@ cudaError_t launch_down_mma(cudaStream_t st, int sm_count, const JobTable *dev, 
                             uint32_t inter, uint32_t n_jobs) {
     configure_once();
     const uint32_t ctas_per_job = max(1u, (uint32_t)sm_count / n_jobs);
-    k_expert_down_mma<<<n_jobs * ctas_per_job, kMaxWarps * 32, mma_smem_bytes(kMaxWarps, inter), st>>>(
-        dev, param, h, d, y, counters, hidden, inter, ctas_per_job);
-    return cudaGetLastError();
+    return launch_pdl(k_expert_down_mma, dim3(n_jobs * ctas_per_job), dim3(kMaxWarps * 32),
+                      mma_smem_bytes(kMaxWarps, inter), st, true, dev, param, h, d, y, counters, hidden, inter,
+                      ctas_per_job);
 }
 
 }  // namespace s14
