@@ -567,7 +567,7 @@ k_moe_mix(const JobTable *__restrict__ dev_table, const __grid_constant__ JobTab
 
 // ------------------------------------------------------------- router -------
 
-// One warp per (token, expert) row of BF16 weights: logit in double (every product
+// One CTA of two warps per (token, expert) row of BF16 weights: logit in double (every product
 // f32 x bf16 is exact in double), score and score + bias in F32.  The last CTA to finish
 // (a counter in global memory, no waiting) selects the top-k of every token, normalises the
 // weights and, for the one-token decode path, writes the job table of the layer.
@@ -576,14 +576,19 @@ __device__ __forceinline__ void router_select(const float *scores, const float *
                                               int32_t *ids_out, float *weights_out, JobTable *table_out,
                                               const uint8_t *const *page_table, const uint8_t *shared_page,
                                               uint32_t shared_kind, uint32_t lane) {
-    float v[8], sc[8];
+    // key = (order-preserving bits of score + bias, ~expert): the largest key is the largest value,
+    // the lowest expert id on ties; one 64-bit shuffle per butterfly step
+    unsigned long long key[8];
 #pragma unroll
     for (int i = 0; i < 8; ++i) {
         const uint32_t e = i * 32 + lane;
-        v[i] = e < n_experts ? __ldcg(select + e) : -INFINITY;
-        sc[i] = e < n_experts ? __ldcg(scores + e) : 0.0f;
+        key[i] = 0ull;
+        if (e < n_experts) {
+            const uint32_t bits = __float_as_uint(__ldcg(select + e));
+            const uint32_t ordered = (bits & 0x80000000u) ? ~bits : (bits | 0x80000000u);
+            key[i] = ((unsigned long long)ordered << 32) | (unsigned long long)(0xffffffffu - e);
+        }
     }
-    uint32_t taken = 0;
     int32_t ids[8];
     float picked[8];
 #pragma unroll
@@ -591,32 +596,20 @@ __device__ __forceinline__ void router_select(const float *scores, const float *
         ids[j] = -1;
         picked[j] = 0.0f;
         if ((uint32_t)j < top_k) {
-            float best = -INFINITY;
-            uint32_t best_e = 0xffffffffu;
-            float best_s = 0.0f;
+            unsigned long long best = key[0];
 #pragma unroll
-            for (int i = 0; i < 8; ++i) {
-                const uint32_t e = i * 32 + lane;
-                if (e < n_experts && !((taken >> i) & 1u) && (best_e == 0xffffffffu || v[i] > best)) {
-                    best = v[i];
-                    best_e = e;
-                    best_s = sc[i];
-                }
-            }
+            for (int i = 1; i < 8; ++i) best = key[i] > best ? key[i] : best;
 #pragma unroll
             for (int o = 16; o > 0; o >>= 1) {
-                const float ob = __shfl_xor_sync(0xffffffffu, best, o);
-                const uint32_t oe = __shfl_xor_sync(0xffffffffu, best_e, o);
-                const float os = __shfl_xor_sync(0xffffffffu, best_s, o);
-                if (oe != 0xffffffffu && (best_e == 0xffffffffu || ob > best || (ob == best && oe < best_e))) {
-                    best = ob;
-                    best_e = oe;
-                    best_s = os;
-                }
+                const unsigned long long other = __shfl_xor_sync(0xffffffffu, best, o);
+                best = other > best ? other : best;
             }
-            if ((best_e & 31u) == lane) taken |= 1u << (best_e >> 5);
-            ids[j] = (int32_t)best_e;
-            picked[j] = best_s;
+            const uint32_t e = 0xffffffffu - (uint32_t)(best & 0xffffffffull);
+#pragma unroll
+            for (int i = 0; i < 8; ++i)
+                if (key[i] == best) key[i] = 0ull;  // taken
+            ids[j] = (int32_t)e;
+            picked[j] = __ldcg(scores + e);
         }
     }
     if (lane != 0) return;
@@ -672,14 +665,14 @@ k_router(const float *__restrict__ x, const uint16_t *__restrict__ wr, const flo
     // a dependent launch (the up phase) may start its own prologue now; it reads what this
     // kernel writes only after cudaGridDependencySynchronize()
     cudaTriggerProgrammaticLaunchCompletion();
-    const uint32_t lane = threadIdx.x & 31u;
-    const uint32_t warp = (blockIdx.x * blockDim.x + threadIdx.x) >> 5;
-    if (warp < n_experts * n_tokens) {
-        const uint32_t t = warp / n_experts, e = warp - t * n_experts;
-        const uint4 *row = reinterpret_cast<const uint4 *>(wr + (size_t)e * hidden);
-        const float *xt = x + (size_t)t * hidden;
+    __shared__ double half_sum[2];
+    const uint32_t lane = threadIdx.x & 31u, half = threadIdx.x >> 5;
+    {
+        const uint32_t t = blockIdx.x / n_experts, e = blockIdx.x - t * n_experts;
+        const uint32_t pieces = hidden >> 4;  // 16-byte pieces (8 weights) per half row
+        const uint4 *row = reinterpret_cast<const uint4 *>(wr + (size_t)e * hidden) + half * pieces;
+        const float *xt = x + (size_t)t * hidden + (size_t)half * (hidden >> 1);
         double acc0 = 0.0, acc1 = 0.0;
-        const uint32_t pieces = hidden >> 3;  // 8 weights per 16-byte piece
         for (uint32_t p0 = lane; p0 < pieces; p0 += 32u * 8u) {
             uint4 q[8];
             float4 xa[8], xb[8];
@@ -705,9 +698,11 @@ k_router(const float *__restrict__ x, const uint16_t *__restrict__ wr, const flo
                 }
             }
         }
-        const double acc = warp_sum(acc0 + acc1);
-        if (lane == 0) {
-            const double l = (double)(float)acc;
+        const double part = warp_sum(acc0 + acc1);
+        if (lane == 0) half_sum[half] = part;
+        __syncthreads();
+        if (threadIdx.x == 0) {
+            const double l = (double)(float)(half_sum[0] + half_sum[1]);
             const double sc = (score_fn == S14_SCORE_SIGMOID) ? 1.0 / (1.0 + exp(-l))
                                                               : sqrt(l > 20.0 ? l : log1p(exp(l)));
             const float s = (float)sc;
@@ -966,7 +961,7 @@ int launch_router(cudaStream_t st, const s14_router_desc &r, float *scores, floa
                   uint32_t shared_kind, unsigned int *counter, cudaError_t *err, const KernelMarks *km) {
     const uint32_t warps = r.n_experts * r.n_tokens;
     if (km) cudaEventRecord(km->ev[0], st);
-    k_router<<<ceil_div(warps, 2), 64, 0, st>>>(r.x, r.router_weight_bf16, r.bias, scores, select,
+    k_router<<<warps, 64, 0, st>>>(r.x, r.router_weight_bf16, r.bias, scores, select,
                                                 r.n_experts, r.hidden, r.n_tokens, r.score_fn, r.top_k,
                                                 r.route_scale, r.ids_out, r.weights_out, table_out,
                                                 page_table, shared_page, shared_kind, counter);
