@@ -149,6 +149,7 @@ SIGNATURES = {
     "s14_routed_moe_layer_host": (_I32, [_VP, _P(RoutedLayerDesc), _VP, _VP, _VP, _VP]),
     "s14_cmd_head_logits": (_I32, [_VP, _VP, _VP, _U32, _VP, _U32, _U32, _VP, _U32]),
     "s14_cmd_greedy_argmax": (_I32, [_VP, _VP, _VP, _U32, _VP]),
+    "s14_moe_layer_noalloc": (_I32, [_I32, _VP, _U32, _P(MoeLayerDesc)]),
     "s14_moe_layer_host": (_I32, [_VP, _P(MoeLayerDesc), _VP, _VP]),
     "s14_pool_create": (_I32, [_VP, _U32, _U64, _P(_VP)]),
     "s14_pool_destroy": (_I32, [_VP]),

@@ -527,6 +527,79 @@ extern "C" int32_t s14_cmd_moe_layer(s14_ctx *ctx, void *stream, const s14_moe_l
     return enqueue_layer(ctx, stream_of(ctx, stream), *desc, desc->x, desc->y);
 }
 
+// ---- allocation-free layer ----------------------------------------------------------
+//
+// Scratch of s14_moe_layer_noalloc: the hidden vectors between the up and down phases, the
+// per-expert down outputs before the mix, and the arrival counters of the fused mix.  File
+// scope, so every GPU that loads this library holds kNoAllocBytes of it until the process exits.
+static constexpr uint32_t kNoAllocJobs = S14_EXPERTS_PER_TOKEN + 1;  // one token: 6 routed + shared
+static __device__ __align__(256) float g_noalloc_h[kNoAllocJobs * kMaxDim];
+static __device__ __align__(256) float g_noalloc_d[kNoAllocJobs * kMaxDim];
+static __device__ __align__(256) unsigned int g_noalloc_counters[kCounters];
+
+struct NoAllocDevice {
+    bool ready = false;
+    int sm_count = 0;
+    float *h = nullptr, *d = nullptr;
+    unsigned int *counters = nullptr;
+};
+static NoAllocDevice g_noalloc[64];
+
+// Resolves the device addresses of the scratch arrays for the current device.  In host code the
+// array names are only handles; the kernels need what cudaGetSymbolAddress returns.
+static int32_t noalloc_setup(int device, NoAllocDevice **out) {
+    if (device < 0 || device >= 64) return fail(S14_ERR_CONTRACT, "s14_moe_layer_noalloc: device out of range");
+    NoAllocDevice &nd = g_noalloc[device];
+    if (!nd.ready) {
+        cudaDeviceProp prop;
+        CUDA_OK(cudaGetDeviceProperties(&prop, device));
+        if (prop.major < 10)
+            return fail(S14_ERR_CONTRACT, "s14_moe_layer_noalloc: the kernels are built for sm_100a only");
+        CUDA_OK(cudaGetSymbolAddress((void **)&nd.h, g_noalloc_h));
+        CUDA_OK(cudaGetSymbolAddress((void **)&nd.d, g_noalloc_d));
+        CUDA_OK(cudaGetSymbolAddress((void **)&nd.counters, g_noalloc_counters));
+        nd.sm_count = prop.multiProcessorCount;
+        nd.ready = true;
+    }
+    *out = &nd;
+    return S14_OK;
+}
+
+extern "C" int32_t s14_moe_layer_noalloc(int32_t device, void *stream, uint32_t accumulation,
+                                         const s14_moe_layer_desc *desc) {
+    S14_TRY
+    if (!desc) throw ContractError("s14_moe_layer_noalloc: desc is NULL");
+    if (accumulation != S14_ACCUM_PAIRWISE && accumulation != S14_ACCUM_REFERENCE)
+        throw ContractError("s14_moe_layer_noalloc: unknown accumulation mode");
+    if (desc->n_tokens != 1)
+        throw ContractError("s14_moe_layer_noalloc: the static scratch holds one token (6 routed + shared "
+                            "experts); got " + std::to_string(desc->n_tokens) + " tokens");
+    if (desc->hidden > kMaxDim || desc->inter > kMaxDim)
+        throw ContractError("s14_moe_layer_noalloc: hidden and intermediate sizes are limited to 4096");
+    int current = -1;
+    CUDA_OK(cudaGetDevice(&current));
+    if (current != device) CUDA_OK(cudaSetDevice(device));
+    NoAllocDevice *nd = nullptr;
+    const int32_t rc = noalloc_setup(device, &nd);
+    if (rc != S14_OK) return rc;
+    JobTable tab;
+    build_job_table(*desc, tab);
+    if (!desc->x || !desc->y) throw ContractError("s14_moe_layer_noalloc: x or y is NULL");
+    require_aligned(desc->x, 16, "S14 MoE layer x");
+    bool all_mxfp4 = true;
+    for (uint32_t j = 0; j < tab.n_jobs; ++j) all_mxfp4 = all_mxfp4 && tab.jobs[j].kind == S14_PAGE_MXFP4;
+    cudaStream_t st = (cudaStream_t)stream;
+    // every call shares the scratch: the counters must start at zero whatever an earlier,
+    // interrupted call left behind; h and d are fully overwritten before they are read
+    CUDA_OK(cudaMemsetAsync(nd->counters, 0, sizeof(unsigned int) * kCounters, st));
+    cudaError_t err;
+    launch_moe_layer(st, accumulation, nd->sm_count, nullptr, tab, tab.n_tokens, tab.n_jobs, desc->hidden,
+                     desc->inter, desc->x, nd->h, nd->d, desc->y, &err, nullptr, all_mxfp4, nd->counters);
+    if (err != cudaSuccess) return cuda_fail(err, "S14 MoE layer launch");
+    return S14_OK;
+    S14_CATCH
+}
+
 extern "C" int32_t s14_moe_layer_host(s14_ctx *ctx, const s14_moe_layer_desc *desc,
                                       const float *host_x, float *host_y) {
     if (!ctx || !desc || !host_x || !host_y)

@@ -298,6 +298,24 @@ S14_API int32_t s14_cmd_head_logits(s14_ctx *ctx, void *stream, const float *x, 
 S14_API int32_t s14_cmd_greedy_argmax(s14_ctx *ctx, void *stream, const float *logits,
                                       uint32_t vocab, int64_t *result);
 
+/* The layer for callers that must not allocate: code that runs where cudaMalloc is off
+ * limits (inside a CUDA graph capture that some other component owns, in a latency-critical
+ * serving loop whose memory plan is frozen after start-up, or under a harness that forbids
+ * device allocation after initialisation) and therefore cannot create an s14_ctx, whose
+ * constructor allocates its scratch.  This entry point has no counterpart in the reference.
+ * It takes no context: the scratch between the up and down phases lives in file-scope device
+ * arrays inside the library (about 230 KB per GPU, held until the process exits), so the limits
+ * are one token per call (desc->n_tokens == 1, at most 6 routed experts plus the shared one)
+ * and hidden, intermediate <= 4096; anything larger is refused with S14_ERR_CONTRACT.  It calls
+ * no cudaMalloc, cudaFree or allocating library routine.  `device` is the ordinal the pointers
+ * in desc belong to; `stream` a stream of that device (NULL = the legacy default stream).
+ * The first call on a device resolves the addresses of the arrays and the kernel attributes;
+ * make that first call before any stream capture.  All calls on a device share the one scratch
+ * and its arrival counters (cleared at the start of every call): calls that overlap on the
+ * GPU - different streams without ordering, or several host threads - race on it. */
+S14_API int32_t s14_moe_layer_noalloc(int32_t device, void *stream, uint32_t accumulation,
+                                      const s14_moe_layer_desc *desc);
+
 /* The same layer for a caller that holds x and y in host memory (pinned or
  * pageable): copies host_x [n_tokens, hidden] to context-owned device staging,
  * runs the layer on the resident pages named by desc (desc->x / desc->y are
