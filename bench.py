@@ -218,30 +218,54 @@ def run_gpu(args) -> None:
     gen = torch.Generator(device="cuda")
     gen.manual_seed(1234 + rank)
 
-    # resident state: N_LAYERS x (256 routed + 1 shared) pages, router weights, page tables
+    # resident state: N_LAYERS x (256 routed + 1 shared) pages, router weights, page tables.
+    # With several GPUs the experts are partitioned (expert e on rank e mod N, the shared expert of
+    # layer l on rank l mod N) and every rank keeps only the pages it owns.
+    from colormlm_b200 import ep
+
     layers = []
     n_layers = max(1, args.layers)
     for layer in range(n_layers):
-        pages = make_layer_pages(torch, N_EXPERTS + 1, gen)
+        owned = ep.owned_experts(rank, world, N_EXPERTS)
+        has_shared = ep.shared_owner(layer, world) == rank
+        pages = make_layer_pages(torch, len(owned) + (1 if has_shared else 0), gen)
         gl = synth.rng(500 + layer)
         wr = torch.from_numpy(synth.router_weight_bf16(gl, N_EXPERTS, HIDDEN).view(np.int16)).cuda()
         bias = torch.from_numpy(synth.router_bias(gl, N_EXPERTS)).cuda()
         base = pages.data_ptr()
-        table = torch.tensor([base + e * PAGE_BYTES for e in range(N_EXPERTS)], dtype=torch.int64, device="cuda")
+        addr = [0] * N_EXPERTS
+        for slot, e in enumerate(owned):
+            addr[e] = base + slot * PAGE_BYTES
+        table = torch.tensor(addr, dtype=torch.int64, device="cuda")
         layers.append({"pages": pages, "wr": wr, "bias": bias, "table": table,
-                       "shared": base + N_EXPERTS * PAGE_BYTES})
+                       "shared": base + len(owned) * PAGE_BYTES if has_shared else None})
     n_tok = 64
-    xs = torch.randn((n_tok, HIDDEN), dtype=torch.float32, device="cuda", generator=gen)
+    xgen = torch.Generator(device="cuda")
+    xgen.manual_seed(99)  # the same tokens on every rank
+    xs = torch.randn((n_tok, HIDDEN), dtype=torch.float32, device="cuda", generator=xgen)
     ys = torch.empty((N_LAYERS, HIDDEN), dtype=torch.float32, device="cuda")
+    slots = torch.zeros((N_LAYERS, TOP_K + 1, HIDDEN), dtype=torch.float32, device="cuda")
+    ep_ids = torch.empty((N_LAYERS, TOP_K), dtype=torch.int32, device="cuda")
+    ep_w = torch.empty((N_LAYERS, TOP_K), dtype=torch.float32, device="cuda")
     torch.cuda.synchronize()
 
     def enqueue_step(i: int, stream_handle=None):
         ly = layers[i % n_layers]
-        ctx.cmd_routed_moe_layer(xs[i % n_tok], ly["wr"], ly["bias"], ly["table"], ly["shared"], L.PAGE_MXFP4,
-                                 INTER, ys[i % N_LAYERS], stream=stream_handle)
+        if world == 1:
+            ctx.cmd_routed_moe_layer(xs[i % n_tok], ly["wr"], ly["bias"], ly["table"], ly["shared"],
+                                     L.PAGE_MXFP4, INTER, ys[i % N_LAYERS], stream=stream_handle)
+        else:
+            k = i % N_LAYERS
+            ly_state = dict(ly)
+            if ly_state["shared"] is None:
+                ly_state["shared"] = ly["pages"].data_ptr()  # never read: this rank is not the owner
+            ep.decode_step(ctx, xs[i % n_tok], ly_state, slots[k], ep_ids[k], ep_w[k], ys[k],
+                           layer=i % n_layers, rank=rank, world=world, inter=INTER, stream=stream_handle)
 
     stream = torch.cuda.Stream()
-    kernels_per_step = 3  # router (scores + select), up phase, down phase + mix
+    # router, up phase, down phase + mix; expert parallel adds the slot memset is not a kernel of ours,
+    # the all-reduce is NCCL's, the mix is one more kernel
+    kernels_per_step = 3 if world == 1 else 4
 
     def capture(n_steps: int, first: int):
         g = torch.cuda.CUDAGraph()
@@ -255,13 +279,25 @@ def run_gpu(args) -> None:
         for i in range(3):  # first launches outside capture (module load)
             enqueue_step(i, stream.cuda_stream)
     stream.synchronize()
-    graph = capture(N_LAYERS, 0)
     rem = args.steps % N_LAYERS
-    graph_rem = capture(rem, 0) if rem else None
     full = args.steps // N_LAYERS
+    launch_mode = "cuda graph of 14 layer-steps"
+    try:
+        graph = capture(N_LAYERS, 0)
+        graph_rem = capture(rem, 0) if rem else None
+    except Exception as exc:  # a collective that cannot be captured: launch step by step
+        if world == 1:
+            raise
+        graph = graph_rem = None
+        launch_mode = f"eager launches (graph capture failed: {type(exc).__name__})"
+        torch.cuda.synchronize()
 
     def replay(n_full: int, with_rem: bool):
         with torch.cuda.stream(stream):
+            if graph is None:
+                for i in range(n_full * N_LAYERS + (rem if with_rem else 0)):
+                    enqueue_step(i, stream.cuda_stream)
+                return
             for _ in range(n_full):
                 graph.replay()
             if with_rem and graph_rem is not None:
@@ -293,7 +329,8 @@ def run_gpu(args) -> None:
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
         ms = float(t.item())
     clocks = sampler.stop() if rank == 0 else None
-    value = world * args.steps / (ms / 1e3)
+    # one token stream: with several GPUs the experts of the same tokens are spread over the ranks
+    value = args.steps / (ms / 1e3)
 
     # per-kernel durations (separate loop, blocking calls, not part of the headline number)
     ctx.set_kernel_timing(True)
@@ -304,19 +341,31 @@ def run_gpu(args) -> None:
     ctx.set_kernel_timing(False)
     up_ms = kt["up"] / max(1, calls)
     peak, peak_kind = measured_peaks()
-    achieved = UP_BYTES / (up_ms * 1e-3) / 1e9 if up_ms > 0 else 0.0
+    achieved = UP_BYTES / (up_ms * 1e-3) / 1e9 if up_ms > 0 else None
 
     # end to end through the host-buffer call: pinned x in, y (+ route) out, every step
     hx = torch.randn((n_tok, HIDDEN), dtype=torch.float32).pin_memory()
     hy = torch.empty((HIDDEN,), dtype=torch.float32).pin_memory()
     hx_np, hy_np = hx.numpy(), hy.numpy()
     ids_np, w_np = np.empty(TOP_K, np.int32), np.empty(TOP_K, np.float32)
+    xd = torch.empty(HIDDEN, dtype=torch.float32, device="cuda")
     e2e_steps = 0 if args.kernel_only else min(args.steps, 2000)
 
     def e2e_step(i):
         ly = layers[i % n_layers]
-        ctx.routed_moe_layer_host(hx_np[i % n_tok], hy_np, ly["wr"], ly["bias"], ly["table"], ly["shared"],
-                                  L.PAGE_MXFP4, INTER, ids_np, w_np)
+        if world == 1:
+            ctx.routed_moe_layer_host(hx_np[i % n_tok], hy_np, ly["wr"], ly["bias"], ly["table"], ly["shared"],
+                                      L.PAGE_MXFP4, INTER, ids_np, w_np)
+        else:
+            with torch.cuda.stream(stream):
+                xd.copy_(hx[i % n_tok], non_blocking=True)
+                ly_state = dict(ly)
+                if ly_state["shared"] is None:
+                    ly_state["shared"] = ly["pages"].data_ptr()
+                ep.decode_step(ctx, xd, ly_state, slots[0], ep_ids[0], ep_w[0], ys[0], layer=i % n_layers,
+                               rank=rank, world=world, inter=INTER, stream=stream.cuda_stream)
+                hy.copy_(ys[0], non_blocking=True)
+            stream.synchronize()
 
     for i in range(0 if args.kernel_only else max(3, min(args.warmup, 100))):
         e2e_step(i)
@@ -330,7 +379,7 @@ def run_gpu(args) -> None:
         t = torch.tensor([e2e_sec], dtype=torch.float64, device="cuda")
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
         e2e_sec = float(t.item())
-    e2e_value = world * e2e_steps / e2e_sec
+    e2e_value = e2e_steps / e2e_sec
 
     if rank == 0:
         cpu = None
@@ -348,15 +397,19 @@ def run_gpu(args) -> None:
         line = {
             "metric": "moe_layer_tokens_per_s", "value": value, "unit": "layer-tokens/s", "n_gpus": world,
             "steps": args.steps, "warmup": warm_full * N_LAYERS, "ms_per_step": ms / args.steps,
-            "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f32",
+            "higher_is_better": True, "scaling": "weak" if world == 1 else "strong", "vs_baseline": None,
+            "dtype": "f32",
             "data": "synthetic",
             "config": {"workload": WORKLOAD, "layers_resident": n_layers, "accumulation": args.accum,
+                       "launch": launch_mode,
                        "l2": "inputs larger than L2: 14 x 3.4 GB of pages walked round-robin, 96 MB per step",
-                       "parallelism": "replicas" if world > 1 else "single"},
-            "hbm_gbs": value / world * STEP_BYTES / 1e9, "hbm_frac_of_measured_peak": value / world * STEP_BYTES / 1e9 / peak,
+                       "parallelism": f"ep{world}: expert e on rank e mod {world}, slot all-reduce + ordered mix"
+                       if world > 1 else "single"},
+            "hbm_gbs": value * STEP_BYTES / 1e9, "hbm_frac_of_measured_peak": value * STEP_BYTES / 1e9 / (peak * world),
             "algorithmic_bytes_per_step": STEP_BYTES,
             "roofline": {"bound": "hbm", "kernel": "expert up phase (w1, w3, SwiGLU) of 7 experts",
-                         "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
+                         "achieved": achieved, "peak": peak, "unit": "GB/s",
+                         "frac": achieved / peak if achieved else None,
                          "peak_kind": peak_kind, "traffic": None, "bytes_per_launch": UP_BYTES,
                          "ms_per_launch": up_ms,
                          "other_kernels_ms": {k: v / max(1, calls) for k, v in kt.items() if k != "up"}},

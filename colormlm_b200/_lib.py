@@ -146,6 +146,8 @@ SIGNATURES = {
     "s14_cmd_moe_layer": (_I32, [_VP, _VP, _P(MoeLayerDesc)]),
     "s14_cmd_router": (_I32, [_VP, _VP, _P(RouterDesc)]),
     "s14_cmd_routed_moe_layer": (_I32, [_VP, _VP, _P(RoutedLayerDesc)]),
+    "s14_cmd_routed_moe_experts_ep": (_I32, [_VP, _VP, _P(RoutedLayerDesc), _U32, _U32, _U32, _VP]),
+    "s14_cmd_moe_mix_slots": (_I32, [_VP, _VP, _VP, _VP, _U32, _I32, _VP, _U32]),
     "s14_routed_moe_layer_host": (_I32, [_VP, _P(RoutedLayerDesc), _VP, _VP, _VP, _VP]),
     "s14_cmd_head_logits": (_I32, [_VP, _VP, _VP, _U32, _VP, _U32, _U32, _VP, _U32]),
     "s14_cmd_greedy_argmax": (_I32, [_VP, _VP, _VP, _U32, _VP]),

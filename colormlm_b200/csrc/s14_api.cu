@@ -473,6 +473,7 @@ static void build_job_table(const s14_moe_layer_desc &desc, JobTable &tab) {
         jb.token = p.token;
         jb.weight = r.weights[p.slot];
         jb.is_shared = 0;
+        jb.out_index = n;
         tab.jobs[n] = jb;
         per_token[p.token][p.slot] = (uint8_t)n;
         ++n;
@@ -487,6 +488,7 @@ static void build_job_table(const s14_moe_layer_desc &desc, JobTable &tab) {
             jb.token = t;
             jb.weight = 1.0f;
             jb.is_shared = 1;
+            jb.out_index = n;
             tab.jobs[n] = jb;
             per_token[t][desc.routes[t].n_routed] = (uint8_t)n;
             ++n;
@@ -681,6 +683,53 @@ extern "C" int32_t s14_cmd_routed_moe_layer(s14_ctx *ctx, void *stream,
     }
     return S14_OK;
     S14_CATCH
+}
+
+extern "C" int32_t s14_cmd_routed_moe_experts_ep(s14_ctx *ctx, void *stream,
+                                                 const s14_routed_layer_desc *desc, uint32_t ep_rank,
+                                                 uint32_t ep_world, uint32_t shared_owner,
+                                                 float *slots_out) {
+    S14_TRY
+    if (!ctx || !desc || !slots_out) throw ContractError("s14_cmd_routed_moe_experts_ep: NULL argument");
+    const s14_router_desc &r = desc->router;
+    validate_router(r, true);
+    if (r.n_tokens != 1) throw ContractError("S14 expert-parallel layer: one decode token per call");
+    if (r.top_k > S14_EXPERTS_PER_TOKEN) throw ContractError("S14 expert-parallel layer: top_k must be <= 6");
+    if (ep_world == 0 || ep_rank >= ep_world || shared_owner >= ep_world)
+        throw ContractError("S14 expert-parallel layer: rank / owner outside the world");
+    if (!fused_dim_ok(r.hidden) || !fused_dim_ok(desc->inter))
+        throw ContractError("S14 expert-parallel layer: hidden and intermediate must be 1024, 2048 or 4096");
+    if (!desc->page_table) throw ContractError("S14 expert-parallel layer: page_table is NULL");
+    if (desc->shared_page && desc->shared_kind != S14_PAGE_MXFP4 && desc->shared_kind != S14_PAGE_FP8)
+        throw ContractError("S14 expert-parallel layer: unknown shared page kind");
+    cudaStream_t st = stream_of(ctx, stream);
+    const uint32_t n_slots = r.top_k + (desc->shared_page ? 1u : 0u);
+    // slots this rank does not own stay zero, so that the ranks' buffers add up exactly
+    CUDA_OK(cudaMemsetAsync(slots_out, 0, sizeof(float) * n_slots * r.hidden, st));
+    cudaError_t err;
+    ctx->launches += launch_router(st, r, ctx->scores, ctx->select, ctx->dev_table, desc->page_table,
+                                   desc->shared_page, desc->shared_kind, ctx->counters, &err, nullptr,
+                                   ep_rank, ep_world, shared_owner);
+    if (err != cudaSuccess) return cuda_fail(err, "S14 router launch");
+    JobTable unused;
+    unused.n_jobs = 0;
+    ctx->launches += launch_moe_layer(st, ctx->mode, ctx->sm_count, ctx->dev_table, unused, 1, n_slots,
+                                      r.hidden, desc->inter, r.x, ctx->h, slots_out, nullptr, &err, nullptr,
+                                      !desc->shared_page || desc->shared_kind == S14_PAGE_MXFP4,
+                                      ctx->counters);
+    if (err != cudaSuccess) return cuda_fail(err, "S14 MoE layer launch");
+    return S14_OK;
+    S14_CATCH
+}
+
+extern "C" int32_t s14_cmd_moe_mix_slots(s14_ctx *ctx, void *stream, const float *slots,
+                                         const float *weights_dev, uint32_t n_routed, int32_t has_shared,
+                                         float *y, uint32_t hidden) {
+    if (!ctx || !slots || !weights_dev || !y || hidden == 0 || n_routed > S14_EXPERTS_PER_TOKEN)
+        return fail(S14_ERR_CONTRACT, "s14_cmd_moe_mix_slots: NULL or out-of-range argument");
+    CUDA_OK(launch_mix_slots(stream_of(ctx, stream), slots, weights_dev, n_routed, has_shared, y, hidden));
+    ctx->launches += 1;
+    return S14_OK;
 }
 
 extern "C" int32_t s14_routed_moe_layer_host(s14_ctx *ctx, const s14_routed_layer_desc *desc,

@@ -16,6 +16,8 @@ struct Job {
     uint32_t token;     // row of x / y
     float weight;       // route weight (unused for the shared expert)
     uint32_t is_shared; // added last with weight 1
+    uint32_t out_index; // row of the per-job down outputs this job writes (its job id unless
+                        // the caller wants route slots, as the expert-parallel exchange does)
 };
 
 constexpr uint32_t kMaxTokens = S14_MAX_BLOCK_TOKENS;
@@ -64,7 +66,10 @@ cudaError_t launch_down_mma(cudaStream_t st, int sm_count, const JobTable *dev, 
 int launch_router(cudaStream_t st, const s14_router_desc &r, float *scores, float *select,
                   JobTable *table_out, const uint8_t *const *page_table, const uint8_t *shared_page,
                   uint32_t shared_kind, unsigned int *counter, cudaError_t *err,
-                  const KernelMarks *km = nullptr);
+                  const KernelMarks *km = nullptr, uint32_t ep_rank = 0, uint32_t ep_world = 1,
+                  uint32_t shared_owner = 0);
+cudaError_t launch_mix_slots(cudaStream_t st, const float *slots, const float *weights, uint32_t n_routed,
+                             int has_shared, float *y, uint32_t hidden);
 cudaError_t launch_head_logits(cudaStream_t st, int sm_count, const float *x, uint32_t n_tokens,
                                const uint16_t *w, uint32_t n_rows, uint32_t hidden, float *out,
                                uint32_t out_stride);

@@ -386,7 +386,7 @@ k_expert_down_pairwise(const JobTable *__restrict__ dev_table,
 
     float xr[KC * 32];
     load_x_regs<KC>(xr, h + (size_t)jid * inter, lane);
-    float *out = d + (size_t)jid * hidden;
+    float *out = d + (size_t)jb.out_index * hidden;
 
     if (jb.kind != S14_PAGE_MXFP4) {
         for (uint32_t row = warp; row < hidden; row += n_warps) {
@@ -542,7 +542,7 @@ k_expert_down_reference(const JobTable *__restrict__ dev_table,
     const float v = (jb.kind == S14_PAGE_MXFP4)
                         ? dot_row_mxfp4_reference(pv.w2, pv.s2, row, inter, xs)
                         : dot_row_fp8_reference(pv.w2, pv.s2, row, inter, xs);
-    d[(size_t)jid * hidden + row] = v;
+    d[(size_t)jb.out_index * hidden + row] = v;
 }
 
 // Ordered mix (examples/s14_vulkan_numeric.rs:936-946): acc = 0; acc += w * d for the
@@ -559,10 +559,24 @@ k_moe_mix(const JobTable *__restrict__ dev_table, const __grid_constant__ JobTab
     for (uint32_t j = j0; j < j1; ++j) {
         const uint32_t jid = tab.token_jobs[j];
         const Job jb = tab.jobs[jid];
-        const float v = d[(size_t)jid * hidden + n];
+        const float v = d[(size_t)jb.out_index * hidden + n];
         acc = jb.is_shared ? __fadd_rn(acc, v) : __fadd_rn(acc, __fmul_rn(jb.weight, v));
     }
     y[(size_t)token * hidden + n] = acc;
+}
+
+// Ordered mix of gathered per-slot expert outputs (expert-parallel combine): slots [n_routed (+1)]
+// [hidden], weights on the device; same operations and order as k_moe_mix.
+__global__ void __launch_bounds__(256)
+k_mix_slots(const float *__restrict__ slots, const float *__restrict__ weights, uint32_t n_routed,
+            int has_shared, float *__restrict__ y, uint32_t hidden) {
+    const uint32_t n = blockIdx.x * blockDim.x + threadIdx.x;
+    if (n >= hidden) return;
+    float acc = 0.0f;
+    for (uint32_t j = 0; j < n_routed; ++j)
+        acc = __fadd_rn(acc, __fmul_rn(weights[j], slots[(size_t)j * hidden + n]));
+    if (has_shared) acc = __fadd_rn(acc, slots[(size_t)n_routed * hidden + n]);
+    y[n] = acc;
 }
 
 // ------------------------------------------------------------- router -------
@@ -575,7 +589,8 @@ __device__ __forceinline__ void router_select(const float *scores, const float *
                                               uint32_t n_experts, uint32_t top_k, float route_scale,
                                               int32_t *ids_out, float *weights_out, JobTable *table_out,
                                               const uint8_t *const *page_table, const uint8_t *shared_page,
-                                              uint32_t shared_kind, uint32_t lane) {
+                                              uint32_t shared_kind, uint32_t lane, uint32_t ep_rank,
+                                              uint32_t ep_world, uint32_t shared_owner) {
     // key = (order-preserving bits of score + bias, ~expert): the largest key is the largest value,
     // the lowest expert id on ties; one 64-bit shuffle per butterfly step
     unsigned long long key[8];
@@ -617,32 +632,38 @@ __device__ __forceinline__ void router_select(const float *scores, const float *
 #pragma unroll
     for (int j = 0; j < 8; ++j)
         if ((uint32_t)j < top_k) sum = __fadd_rn(sum, picked[j]);
+    // Expert parallel: this rank keeps the jobs of the experts it owns (id mod world == rank) and,
+    // if it is the shared expert's owner, the shared job; every job writes the row of its route
+    // slot so that the ranks' outputs add up to the full set.
+    uint32_t n = 0;
 #pragma unroll
     for (int j = 0; j < 8; ++j) {
         if ((uint32_t)j >= top_k) continue;
         const float w = __fmul_rn(__fdiv_rn(picked[j], sum), route_scale);
         if (ids_out) ids_out[j] = ids[j];
         if (weights_out) weights_out[j] = w;
-        if (table_out) {
+        if (table_out && ((uint32_t)ids[j] % ep_world) == ep_rank) {
             Job jb;
             jb.page = page_table[ids[j]];
             jb.kind = S14_PAGE_MXFP4;
             jb.token = 0;
             jb.weight = w;
             jb.is_shared = 0;
-            table_out->jobs[j] = jb;
-            table_out->token_jobs[j] = (uint8_t)j;
+            jb.out_index = (uint32_t)j;
+            table_out->jobs[n] = jb;
+            table_out->token_jobs[n] = (uint8_t)n;
+            ++n;
         }
     }
     if (table_out) {
-        uint32_t n = top_k;
-        if (shared_page) {
+        if (shared_page && shared_owner == ep_rank) {
             Job jb;
             jb.page = shared_page;
             jb.kind = shared_kind;
             jb.token = 0;
             jb.weight = 1.0f;
             jb.is_shared = 1;
+            jb.out_index = top_k;
             table_out->jobs[n] = jb;
             table_out->token_jobs[n] = (uint8_t)n;
             ++n;
@@ -660,7 +681,7 @@ k_router(const float *__restrict__ x, const uint16_t *__restrict__ wr, const flo
          uint32_t n_tokens, uint32_t score_fn, uint32_t top_k, float route_scale,
          int32_t *__restrict__ ids_out, float *__restrict__ weights_out, JobTable *__restrict__ table_out,
          const uint8_t *const *__restrict__ page_table, const uint8_t *shared_page, uint32_t shared_kind,
-         unsigned int *__restrict__ counter) {
+         unsigned int *__restrict__ counter, uint32_t ep_rank, uint32_t ep_world, uint32_t shared_owner) {
     __shared__ bool is_last;
     // a dependent launch (the up phase) may start its own prologue now; it reads what this
     // kernel writes only after cudaGridDependencySynchronize()
@@ -720,7 +741,7 @@ k_router(const float *__restrict__ x, const uint16_t *__restrict__ wr, const flo
         router_select(scores + (size_t)t * n_experts, select + (size_t)t * n_experts, n_experts, top_k,
                       route_scale, ids_out ? ids_out + (size_t)t * top_k : nullptr,
                       weights_out ? weights_out + (size_t)t * top_k : nullptr, table_out, page_table,
-                      shared_page, shared_kind, lane);
+                      shared_page, shared_kind, lane, ep_rank, ep_world, shared_owner);
     if (threadIdx.x == 0) *counter = 0u;  // ready for the next launch
 }
 
@@ -948,6 +969,7 @@ int launch_moe_layer(cudaStream_t st, uint32_t mode, int sm_count, const JobTabl
         launches += 2;
     }
     if (km) cudaEventRecord(km->ev[3], st);
+    if (!y) return launches;  // the caller mixes (expert-parallel combine)
     dim3 gm(ceil_div(hidden, 256), n_tokens);
     k_moe_mix<<<gm, 256, 0, st>>>(dev_table, param_table, d, y, hidden);
     if (km) cudaEventRecord(km->ev[4], st);
@@ -958,15 +980,23 @@ int launch_moe_layer(cudaStream_t st, uint32_t mode, int sm_count, const JobTabl
 
 int launch_router(cudaStream_t st, const s14_router_desc &r, float *scores, float *select,
                   JobTable *table_out, const uint8_t *const *page_table, const uint8_t *shared_page,
-                  uint32_t shared_kind, unsigned int *counter, cudaError_t *err, const KernelMarks *km) {
+                  uint32_t shared_kind, unsigned int *counter, cudaError_t *err, const KernelMarks *km,
+                  uint32_t ep_rank, uint32_t ep_world, uint32_t shared_owner) {
     const uint32_t warps = r.n_experts * r.n_tokens;
     if (km) cudaEventRecord(km->ev[0], st);
     k_router<<<warps, 64, 0, st>>>(r.x, r.router_weight_bf16, r.bias, scores, select,
                                                 r.n_experts, r.hidden, r.n_tokens, r.score_fn, r.top_k,
                                                 r.route_scale, r.ids_out, r.weights_out, table_out,
-                                                page_table, shared_page, shared_kind, counter);
+                                                page_table, shared_page, shared_kind, counter, ep_rank,
+                                                ep_world, shared_owner);
     *err = cudaGetLastError();
     return 1;
+}
+
+cudaError_t launch_mix_slots(cudaStream_t st, const float *slots, const float *weights, uint32_t n_routed,
+                             int has_shared, float *y, uint32_t hidden) {
+    k_mix_slots<<<ceil_div(hidden, 256), 256, 0, st>>>(slots, weights, n_routed, has_shared, y, hidden);
+    return cudaGetLastError();
 }
 
 cudaError_t launch_head_logits(cudaStream_t st, int sm_count, const float *x, uint32_t n_tokens,

@@ -465,7 +465,7 @@ k_expert_down_mma(const JobTable *__restrict__ dev_table, const __grid_constant_
         sc = ldexp(1.0, x_exp);
     };
     const uint32_t g = lane >> 2;
-    float *out = d + (size_t)jid * hidden;
+    float *out = d + (size_t)jb.out_index * hidden;
     auto setup = [&](uint32_t tile, TileRows &tr) {
         tr.w0 = tr.w1 = pv.w2;
         tr.s0 = tr.s1 = pv.s2;
@@ -496,6 +496,7 @@ k_expert_down_mma(const JobTable *__restrict__ dev_table, const __grid_constant_
             out[((wl.first + tl * wl.stride) << 4) + row] = (float)(v * sc);
         }
     }
+    if (!y) return;  // the caller mixes (expert-parallel combine)
     // Ordered mix (examples/s14_vulkan_numeric.rs:936-946) by the last CTA of this token to finish
     // this slice of rows: acc = 0; acc += w * d for the routed jobs in route order; acc += d_shared.
     __threadfence();
@@ -511,7 +512,7 @@ k_expert_down_mma(const JobTable *__restrict__ dev_table, const __grid_constant_
         float acc = 0.0f;
         for (uint32_t j = j0; j < j1; ++j) {
             const uint32_t other = tab.token_jobs[j];
-            const float v = __ldcg(d + (size_t)other * hidden + n);
+            const float v = __ldcg(d + (size_t)tab.jobs[other].out_index * hidden + n);
             acc = tab.jobs[other].is_shared ? __fadd_rn(acc, v)
                                             : __fadd_rn(acc, __fmul_rn(tab.jobs[other].weight, v));
         }

@@ -183,6 +183,28 @@ class S14Context:
         check(L.lib().s14_cmd_routed_moe_layer(
             self._h, stream if stream is not None else _torch_stream(), C.byref(d)))
 
+    def cmd_routed_moe_experts_ep(self, x, wr_bf16, bias, page_table, shared_page: Optional[int],
+                                  shared_kind: int, inter: int, slots_out, ids_out, weights_out, *,
+                                  ep_rank: int, ep_world: int, shared_owner: int,
+                                  score_fn: int = L.SCORE_SIGMOID, top_k: int = 6, route_scale: float = 1.0,
+                                  stream: Optional[int] = None) -> None:
+        """This rank's share of an expert-parallel decode step: route on every rank, own experts
+        only, unmixed outputs by route slot (all-reduce them, then cmd_moe_mix_slots)."""
+        d = L.RoutedLayerDesc()
+        d.router = _router_desc(x, wr_bf16, bias, ids_out, weights_out, score_fn, top_k, route_scale)
+        d.inter, d.shared_kind = inter, shared_kind
+        d.page_table = page_table.data_ptr()
+        d.shared_page = shared_page
+        check(L.lib().s14_cmd_routed_moe_experts_ep(
+            self._h, stream if stream is not None else _torch_stream(), C.byref(d), ep_rank, ep_world,
+            shared_owner, slots_out.data_ptr()))
+
+    def cmd_moe_mix_slots(self, slots, weights_dev, n_routed: int, has_shared: bool, y,
+                          stream: Optional[int] = None) -> None:
+        check(L.lib().s14_cmd_moe_mix_slots(self._h, stream if stream is not None else _torch_stream(),
+                                            slots.data_ptr(), weights_dev.data_ptr(), n_routed,
+                                            1 if has_shared else 0, y.data_ptr(), y.shape[-1]))
+
     def routed_moe_layer_host(self, host_x: np.ndarray, host_y: np.ndarray, wr_bf16, bias, page_table,
                               shared_page: Optional[int], shared_kind: int, inter: int,
                               host_ids: Optional[np.ndarray] = None,

@@ -277,6 +277,23 @@ typedef struct {
 S14_API int32_t s14_cmd_routed_moe_layer(s14_ctx *ctx, void *stream,
                                          const s14_routed_layer_desc *desc);
 
+/* Expert-parallel decode (no counterpart in the reference, which has no multi-GPU code).  Every
+ * rank of `ep_world` runs the replicated router on the same token and computes the experts it
+ * owns - routed expert e belongs to rank e mod ep_world (its page_table entry must be resident
+ * there; other entries are not read), the shared expert to `shared_owner`.  slots_out
+ * [top_k (+1), hidden] receives the unmixed down vector of every owned expert in the row of its
+ * route slot (shared expert last) and zeros elsewhere, so an all-reduce (sum) over the ranks
+ * yields every slot exactly; router.ids_out / weights_out receive the route on every rank.
+ * s14_cmd_moe_mix_slots then performs the reference's ordered mix on the gathered slots, which
+ * makes the result bit-identical to the single-GPU layer for any number of ranks. */
+S14_API int32_t s14_cmd_routed_moe_experts_ep(s14_ctx *ctx, void *stream,
+                                              const s14_routed_layer_desc *desc, uint32_t ep_rank,
+                                              uint32_t ep_world, uint32_t shared_owner,
+                                              float *slots_out);
+S14_API int32_t s14_cmd_moe_mix_slots(s14_ctx *ctx, void *stream, const float *slots,
+                                      const float *weights_dev, uint32_t n_routed, int32_t has_shared,
+                                      float *y, uint32_t hidden);
+
 /* The routed layer for a caller that holds the token in host memory: copies host_x
  * [hidden] to the device, runs router + layer on the resident pages (desc->router.x,
  * ids_out, weights_out and desc->y are ignored), copies y [hidden] and, when the

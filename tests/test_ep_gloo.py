@@ -1,0 +1,70 @@
+"""The expert-parallel exchange with two CPU ranks over gloo: ownership, slot buffers, all-reduce
+and the ordered mix reproduce the single-rank layer bit for bit.  The per-expert arithmetic comes
+from the CPU oracle here (no GPU); on GPUs the same exchange runs over NCCL."""
+import os
+import sys
+
+import numpy as np
+import pytest
+import torch
+import torch.distributed as dist
+import torch.multiprocessing as mp
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+
+def _worker(rank: int, world: int, port: int, out_dir: str) -> None:
+    sys.path.insert(0, ROOT)
+    os.environ["MASTER_ADDR"] = "127.0.0.1"
+    os.environ["MASTER_PORT"] = str(port)
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    from colormlm_b200 import ep, synth
+    from oracle import s14_oracle as oracle
+
+    hidden, inter, n_experts, layer = 1024, 1024, 16, 3
+    g = synth.rng(2468)  # every rank draws the same tensors; a rank only uses the pages it owns
+    pages = [synth.mxfp4_expert_page(g, hidden, inter) for _ in range(n_experts)]
+    shared = synth.mxfp4_expert_page(g, hidden, inter)
+    wr, bias = synth.router_weight_bf16(g, n_experts, hidden), synth.router_bias(g, n_experts)
+    x = synth.activations(g, 1, hidden)[0]
+    ids, w, _, _ = oracle.router(x, wr, bias, 0, 6, 1.0)  # replicated router
+    slots = torch.zeros((7, hidden), dtype=torch.float32)
+    for j, e in enumerate(ids.tolist()):
+        if ep.expert_owner(e, world) == rank:
+            slots[j] = torch.from_numpy(oracle.expert_chain_mxfp4(x, pages[e], hidden, inter, 1.0)[1])
+    if ep.shared_owner(layer, world) == rank:
+        slots[6] = torch.from_numpy(oracle.expert_chain_mxfp4(x, shared, hidden, inter, 1.0)[1])
+    ep.all_reduce_slots(slots)
+    acc = np.zeros(hidden, np.float32)
+    for j in range(6):
+        acc = acc + w[j] * slots[j].numpy()
+    acc = acc + slots[6].numpy()
+    want = oracle.moe_layer(x, [pages[e] for e in ids], w, shared, 0, hidden, inter)
+    ok = np.array_equal(acc.view(np.uint32), want.view(np.uint32))
+    owned = sorted(set(ep.owned_experts(rank, world, n_experts)))
+    with open(os.path.join(out_dir, f"rank{rank}.txt"), "w") as f:
+        f.write(f"{int(ok)} {len(owned)}\n")
+    dist.barrier()
+    dist.destroy_process_group()
+
+
+@pytest.mark.parametrize("world", [2])
+def test_two_rank_exchange_matches_single_rank(tmp_path, world):
+    port = 29500 + (os.getpid() % 2000)
+    mp.spawn(_worker, args=(world, port, str(tmp_path)), nprocs=world, join=True)
+    total_owned = 0
+    for r in range(world):
+        ok, owned = open(tmp_path / f"rank{r}.txt").read().split()
+        assert ok == "1"
+        total_owned += int(owned)
+    assert total_owned == 16
+
+
+def test_ownership_is_a_partition():
+    sys.path.insert(0, ROOT)
+    from colormlm_b200 import ep
+
+    for world in (1, 2, 4, 8):
+        seen = sorted(e for r in range(world) for e in ep.owned_experts(r, world))
+        assert seen == list(range(256))
+        assert all(0 <= ep.shared_owner(layer, world) < world for layer in range(43))

@@ -367,6 +367,48 @@ def test_routed_layer_without_host_round_trip(ctx, oracle):
     ctx.set_accumulation(L.ACCUM_PAIRWISE)
 
 
+@pytest.mark.parametrize("world", [1, 2, 4, 8])
+def test_expert_parallel_slots_add_up_to_the_single_gpu_layer(ctx, world):
+    """Every rank's share is run in turn on one GPU; the slot buffers are summed as the all-reduce
+    would and mixed in route order: bit-identical to the undivided layer for any world size."""
+    from colormlm_b200 import ep
+
+    hidden, inter, n_experts = 2048, 1024, 32
+    g, pages, shared = make_layer(4040, hidden, inter, n_experts, L.PAGE_MXFP4)
+    wr, bias = synth.router_weight_bf16(g, n_experts, hidden), synth.router_bias(g, n_experts)
+    x = dev(synth.activations(g, 1, hidden))
+    pages_dev, shared_dev = [dev(p) for p in pages], dev(shared)
+    table = torch.tensor([p.data_ptr() for p in pages_dev], dtype=torch.int64, device="cuda")
+    dwr, dbias = dev(wr.view(np.int16)), dev(bias)
+    for mode in (L.ACCUM_REFERENCE, L.ACCUM_PAIRWISE):
+        ctx.set_accumulation(mode)
+        want = torch.empty_like(x)
+        ctx.cmd_routed_moe_layer(x[0], dwr, dbias, table, shared_dev.data_ptr(), L.PAGE_MXFP4, inter, want)
+        total = torch.zeros((7, hidden), device="cuda")
+        ids = torch.empty(6, dtype=torch.int32, device="cuda")
+        wts = torch.empty(6, dtype=torch.float32, device="cuda")
+        owned = 0
+        for rank in range(world):
+            slots = torch.full((7, hidden), float("nan"), device="cuda")
+            ctx.cmd_routed_moe_experts_ep(x[0], dwr, dbias, table, shared_dev.data_ptr(), L.PAGE_MXFP4, inter, slots,
+                                          ids, wts, ep_rank=rank, ep_world=world,
+                                          shared_owner=ep.shared_owner(5, world))
+            torch.cuda.synchronize()
+            mine = [j for j, e in enumerate(ids.tolist()) if ep.expert_owner(e, world) == rank]
+            if ep.shared_owner(5, world) == rank:
+                mine.append(6)
+            owned += len(mine)
+            others = [j for j in range(7) if j not in mine]
+            assert float(slots[others].abs().sum()) == 0.0
+            total += slots
+        assert owned == 7
+        got = torch.empty_like(x)
+        ctx.cmd_moe_mix_slots(total, wts, 6, True, got)
+        torch.cuda.synchronize()
+        assert torch.equal(got, want)
+    ctx.set_accumulation(L.ACCUM_PAIRWISE)
+
+
 def test_head_logits_and_argmax(ctx, oracle, golden):
     g = synth.rng(99)
     vocab, hidden = 5003, 4096
