@@ -191,6 +191,12 @@ def make_layer_pages(torch, n_pages: int, gen) -> "torch.Tensor":
     return pages
 
 
+def _note(msg: str) -> None:
+    """Progress lines on stderr when S14_BENCH_VERBOSE is set."""
+    if os.environ.get("S14_BENCH_VERBOSE"):
+        print(f"[bench rank {os.environ.get('RANK', '0')}] {msg}", file=sys.stderr, flush=True)
+
+
 def run_gpu(args) -> None:
     import torch
     import torch.distributed as dist
@@ -212,6 +218,7 @@ def run_gpu(args) -> None:
         dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
         dist.barrier()
 
+    _note("process group ready")
     ctx = S14Context(local_rank)
     mode = L.ACCUM_REFERENCE if args.accum == "reference" else L.ACCUM_PAIRWISE
     ctx.set_accumulation(mode)
@@ -262,6 +269,7 @@ def run_gpu(args) -> None:
             ep.decode_step(ctx, xs[i % n_tok], ly_state, slots[k], ep_ids[k], ep_w[k], ys[k],
                            layer=i % n_layers, rank=rank, world=world, inter=INTER, stream=stream_handle)
 
+    _note("layers resident")
     stream = torch.cuda.Stream()
     # router, up phase, down phase + mix; expert parallel adds the slot memset is not a kernel of ours,
     # the all-reduce is NCCL's, the mix is one more kernel
@@ -279,18 +287,18 @@ def run_gpu(args) -> None:
         for i in range(3):  # first launches outside capture (module load)
             enqueue_step(i, stream.cuda_stream)
     stream.synchronize()
+    _note("eager warm-up steps done")
     rem = args.steps % N_LAYERS
     full = args.steps // N_LAYERS
-    launch_mode = "cuda graph of 14 layer-steps"
-    try:
+    if world == 1:
+        launch_mode = "cuda graph of 14 layer-steps"
         graph = capture(N_LAYERS, 0)
         graph_rem = capture(rem, 0) if rem else None
-    except Exception as exc:  # a collective that cannot be captured: launch step by step
-        if world == 1:
-            raise
+    else:
+        # NCCL all-reduces replayed from a CUDA graph ran ~10x slower than eager ones here
+        # (0.95 ms against 0.1 ms per step at 2 GPUs), so the expert-parallel steps are launched eagerly
+        launch_mode = "eager launches (router, up, down, NCCL all-reduce, mix per step)"
         graph = graph_rem = None
-        launch_mode = f"eager launches (graph capture failed: {type(exc).__name__})"
-        torch.cuda.synchronize()
 
     def replay(n_full: int, with_rem: bool):
         with torch.cuda.stream(stream):
@@ -303,6 +311,7 @@ def run_gpu(args) -> None:
             if with_rem and graph_rem is not None:
                 graph_rem.replay()
 
+    _note(f"launch mode: {launch_mode}")
     warm_full = max(1, (args.warmup + N_LAYERS - 1) // N_LAYERS)
     replay(warm_full, False)
     stream.synchronize()
@@ -329,6 +338,7 @@ def run_gpu(args) -> None:
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
         ms = float(t.item())
     clocks = sampler.stop() if rank == 0 else None
+    _note(f"timed region done: {ms:.3f} ms")
     # one token stream: with several GPUs the experts of the same tokens are spread over the ranks
     value = args.steps / (ms / 1e3)
 
@@ -380,6 +390,7 @@ def run_gpu(args) -> None:
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
         e2e_sec = float(t.item())
     e2e_value = e2e_steps / e2e_sec
+    _note("end-to-end leg done")
 
     if rank == 0:
         cpu = None
@@ -421,8 +432,11 @@ def run_gpu(args) -> None:
         }
         print(json.dumps(line), flush=True)
     if world > 1:
+        torch.cuda.synchronize()
         dist.barrier()
-        dist.destroy_process_group()
+        sys.stdout.flush()
+        sys.stderr.flush()
+        os._exit(0)  # skip NCCL teardown, which did not return here after the run
     ctx.close()
 
 
