@@ -3,6 +3,7 @@
 // page transaction.  No CPU fallback: every cmd_ call launches a CUDA kernel.
 #include <algorithm>
 #include <cmath>
+#include <cstdlib>
 #include <cstring>
 #include <memory>
 #include <new>
@@ -48,6 +49,7 @@ extern "C" const char *s14_last_error(void) { return g_last_error.c_str(); }
 
 static constexpr uint32_t kMaxDim = 4096;  // largest hidden / intermediate of the fused layer
 static constexpr uint32_t kCounters = 2048; // [0]: router; [1 + token * 160 + slice]: down-phase row slices
+static constexpr uint32_t kCtxCounters = 8192;  // a context's array also serves the tcgen05 phases (4609 used)
 
 struct s14_ctx {
     int device = 0;
@@ -66,9 +68,12 @@ struct s14_ctx {
     KernelMarks marks{};
     double kernel_ms[4] = {0, 0, 0, 0};  // router, up, down, mix
     uint64_t timed_calls = 0;
-    unsigned int *counters = nullptr;  // [kCounters] arrival counters of the fused kernels, all zero at rest
+    unsigned int *counters = nullptr;  // [kCtxCounters] arrival counters of the fused kernels, all zero at rest
     int32_t *ids_stage = nullptr;  // [8] route ids / weights staging of the host-buffer call
     float *weights_stage = nullptr;
+    UmmaScratch umma{nullptr, nullptr};  // scratch of the tcgen05 phases
+    bool use_umma = true;                // S14_TENSOR_PATH=mma_sync in the environment turns them off
+    const UmmaScratch *umma_scratch() const { return use_umma ? &umma : nullptr; }
 };
 
 static cudaStream_t stream_of(s14_ctx *ctx, void *stream) {
@@ -102,10 +107,13 @@ extern "C" int32_t s14_ctx_create(int32_t device, s14_ctx **out) {
     CUDA_OK(cudaMalloc(&ctx->y_stage, sizeof(float) * kMaxTokens * kMaxDim));
     CUDA_OK(cudaMalloc(&ctx->status, sizeof(uint32_t)));
     CUDA_OK(cudaMemset(ctx->status, 0, sizeof(uint32_t)));
-    CUDA_OK(cudaMalloc(&ctx->counters, sizeof(unsigned int) * kCounters));
-    CUDA_OK(cudaMemset(ctx->counters, 0, sizeof(unsigned int) * kCounters));
+    CUDA_OK(cudaMalloc(&ctx->counters, sizeof(unsigned int) * kCtxCounters));
+    CUDA_OK(cudaMemset(ctx->counters, 0, sizeof(unsigned int) * kCtxCounters));
     CUDA_OK(cudaMalloc(&ctx->ids_stage, sizeof(int32_t) * 8));
     CUDA_OK(cudaMalloc(&ctx->weights_stage, sizeof(float) * 8));
+    CUDA_OK(cudaMalloc(&ctx->umma.partials, umma_partials_bytes(ctx->sm_count)));
+    ctx->umma.status = ctx->status;
+    if (const char *path = getenv("S14_TENSOR_PATH")) ctx->use_umma = strcmp(path, "mma_sync") != 0;
     for (auto &e : ctx->marks.ev) CUDA_OK(cudaEventCreate(&e));
     *out = ctx.release();
     return S14_OK;
@@ -127,6 +135,7 @@ extern "C" int32_t s14_ctx_destroy(s14_ctx *ctx) {
     cudaFree(ctx->counters);
     cudaFree(ctx->ids_stage);
     cudaFree(ctx->weights_stage);
+    cudaFree(ctx->umma.partials);
     for (auto &e : ctx->marks.ev)
         if (e) cudaEventDestroy(e);
     cudaStreamDestroy(ctx->compute);
@@ -228,6 +237,30 @@ SHAPE_BYTES_FN(s14_shape_mxfp4_weight_bytes, mxfp4_weight_bytes)
 SHAPE_BYTES_FN(s14_shape_mxfp4_scale_bytes, mxfp4_scale_bytes)
 SHAPE_BYTES_FN(s14_shape_fp8_weight_bytes, fp8_weight_bytes)
 SHAPE_BYTES_FN(s14_shape_fp8_scale_bytes, fp8_scale_bytes)
+
+extern "C" int32_t s14_mxfp4_scales_to_page_order(uint32_t n, uint32_t k, const uint8_t *row_major,
+                                                  uint8_t *page_order) {
+    S14_TRY
+    mxfp4_scales_to_page_order(n, k, row_major, page_order);
+    return S14_OK;
+    S14_CATCH
+}
+
+extern "C" int32_t s14_mxfp4_scales_from_page_order(uint32_t n, uint32_t k, const uint8_t *page_order,
+                                                    uint8_t *row_major) {
+    S14_TRY
+    mxfp4_scales_from_page_order(n, k, page_order, row_major);
+    return S14_OK;
+    S14_CATCH
+}
+
+extern "C" int32_t s14_mxfp4_expert_page_from_tensors(uint32_t hidden, uint32_t inter, const uint8_t *tensor_page,
+                                                      uint8_t *page) {
+    S14_TRY
+    mxfp4_expert_page_from_tensors(hidden, inter, tensor_page, page);
+    return S14_OK;
+    S14_CATCH
+}
 
 extern "C" int32_t s14_validate_ue8m0_codes(const uint8_t *codes, uint64_t len, uint64_t *bad_index) {
     try {
@@ -517,7 +550,7 @@ static int32_t enqueue_layer(s14_ctx *ctx, cudaStream_t st, const s14_moe_layer_
     for (uint32_t j = 0; j < tab.n_jobs; ++j) all_mxfp4 = all_mxfp4 && tab.jobs[j].kind == S14_PAGE_MXFP4;
     const int launched = launch_moe_layer(st, ctx->mode, ctx->sm_count, nullptr, tab, tab.n_tokens,
                                           tab.n_jobs, desc.hidden, desc.inter, x, ctx->h, ctx->d, y,
-                                          &err, nullptr, all_mxfp4, ctx->counters);
+                                          &err, nullptr, all_mxfp4, ctx->counters, ctx->umma_scratch());
     ctx->launches += launched;
     if (err != cudaSuccess) return cuda_fail(err, "S14 MoE layer launch");
     return S14_OK;
@@ -670,7 +703,8 @@ extern "C" int32_t s14_cmd_routed_moe_layer(s14_ctx *ctx, void *stream,
     const uint32_t n_jobs = r.top_k + (desc->shared_page ? 1u : 0u);
     ctx->launches += launch_moe_layer(st, ctx->mode, ctx->sm_count, ctx->dev_table, unused, 1, n_jobs,
                                       r.hidden, desc->inter, r.x, ctx->h, ctx->d, desc->y, &err, km,
-                                      !desc->shared_page || desc->shared_kind == S14_PAGE_MXFP4, ctx->counters);
+                                      !desc->shared_page || desc->shared_kind == S14_PAGE_MXFP4, ctx->counters,
+                                      ctx->umma_scratch());
     if (err != cudaSuccess) return cuda_fail(err, "S14 MoE layer launch");
     if (km) {
         CUDA_OK(cudaStreamSynchronize(st));
@@ -716,7 +750,7 @@ extern "C" int32_t s14_cmd_routed_moe_experts_ep(s14_ctx *ctx, void *stream,
     ctx->launches += launch_moe_layer(st, ctx->mode, ctx->sm_count, ctx->dev_table, unused, 1, n_slots,
                                       r.hidden, desc->inter, r.x, ctx->h, slots_out, nullptr, &err, nullptr,
                                       !desc->shared_page || desc->shared_kind == S14_PAGE_MXFP4,
-                                      ctx->counters);
+                                      ctx->counters, ctx->umma_scratch());
     if (err != cudaSuccess) return cuda_fail(err, "S14 MoE layer launch");
     return S14_OK;
     S14_CATCH

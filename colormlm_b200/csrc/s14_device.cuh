@@ -87,6 +87,14 @@ struct PageView {
     const uint8_t *w1, *w3, *w2, *s1, *s3, *s2;
 };
 
+// The MXFP4 scale arrays of a page are stored atom by atom, in the order the block-scaled
+// tensor-core instructions take them into tensor memory: an atom holds the codes of 128 rows x
+// 4 scale blocks (512 B), atoms of a 128-row tile follow each other along K.  The four codes of
+// row n, blocks 4a..4a+3 of an [N, K] matrix are the 32-bit word at this byte offset.
+__device__ __forceinline__ size_t scale_word_offset(uint32_t n, uint32_t a, uint32_t k) {
+    return ((size_t)(n >> 7) * (k >> 7) + a) * 512u + (n & 31u) * 16u + ((n >> 5) & 3u) * 4u;
+}
+
 __device__ __forceinline__ PageView page_view(const uint8_t *page, uint32_t kind, uint32_t hidden,
                                               uint32_t inter) {
     PageView v;

@@ -5,6 +5,7 @@
 
 #include <algorithm>
 #include <cmath>
+#include <cstring>
 #include <limits>
 #include <sstream>
 #include <unordered_set>
@@ -73,6 +74,43 @@ void validate_ue8m0_codes(const uint8_t *codes, uint64_t len) {
     for (uint64_t i = 0; i < len; ++i)
         if (codes[i] == 0xff)
             throw CodeError("UE8M0 scale contains 0xff NaN at byte " + std::to_string(i), i);
+}
+
+uint64_t mxfp4_scale_page_offset(uint32_t n, uint32_t kb, uint32_t k) {
+    return ((uint64_t)(n >> 7) * (k >> 7) + (kb >> 2)) * 512u + (n & 31u) * 16u + ((n >> 5) & 3u) * 4u + (kb & 3u);
+}
+
+static void check_scale_shape(uint32_t n, uint32_t k) {
+    if (n == 0 || k == 0 || (n & 127u) || (k & 127u))
+        throw ContractError("MXFP4 page scales: rows and K must be non-zero multiples of 128");
+}
+
+void mxfp4_scales_to_page_order(uint32_t n, uint32_t k, const uint8_t *row_major, uint8_t *page_order) {
+    check_scale_shape(n, k);
+    if (!row_major || !page_order) throw ContractError("MXFP4 page scales: NULL buffer");
+    const uint32_t groups = k >> 5;
+    for (uint32_t r = 0; r < n; ++r)
+        for (uint32_t kb = 0; kb < groups; kb += 4)
+            std::memcpy(page_order + mxfp4_scale_page_offset(r, kb, k), row_major + (size_t)r * groups + kb, 4);
+}
+
+void mxfp4_scales_from_page_order(uint32_t n, uint32_t k, const uint8_t *page_order, uint8_t *row_major) {
+    check_scale_shape(n, k);
+    if (!row_major || !page_order) throw ContractError("MXFP4 page scales: NULL buffer");
+    const uint32_t groups = k >> 5;
+    for (uint32_t r = 0; r < n; ++r)
+        for (uint32_t kb = 0; kb < groups; kb += 4)
+            std::memcpy(row_major + (size_t)r * groups + kb, page_order + mxfp4_scale_page_offset(r, kb, k), 4);
+}
+
+void mxfp4_expert_page_from_tensors(uint32_t hidden, uint32_t inter, const uint8_t *tensor_page, uint8_t *page) {
+    check_scale_shape(inter, hidden);
+    if (!tensor_page || !page) throw ContractError("MXFP4 expert page: NULL buffer");
+    const size_t wb = (size_t)hidden * inter / 2, sb = (size_t)hidden * inter / 32;
+    std::memcpy(page, tensor_page, 3 * wb);
+    mxfp4_scales_to_page_order(inter, hidden, tensor_page + 3 * wb, page + 3 * wb);           // s1: [inter, hidden]
+    mxfp4_scales_to_page_order(inter, hidden, tensor_page + 3 * wb + sb, page + 3 * wb + sb);  // s3
+    mxfp4_scales_to_page_order(hidden, inter, tensor_page + 3 * wb + 2 * sb, page + 3 * wb + 2 * sb);  // s2: [hidden, inter]
 }
 
 void validate_e4m3fn_codes(const uint8_t *codes, uint64_t len) {

@@ -43,6 +43,18 @@ struct S14MatvecShape {
 // storage_bytes (s14_vulkan.rs:128-130): byte counts rounded up to whole 32-bit words.
 inline uint64_t storage_bytes(uint64_t logical) { return (logical + 3) / 4 * 4; }
 
+// Page order of MXFP4 scale codes.  The checkpoint's tensor is [n, k/32] row-major; an expert page
+// holds it atom by atom, the order the sm_100 block-scaled MMA takes scales into tensor memory:
+// atom (n / 128, kb / 4) is 512 bytes, the code of row n, scale block kb sits at byte
+// (n % 32) * 16 + ((n % 128) / 32) * 4 + kb % 4 of it, atoms of a 128-row tile follow each other
+// along k.  n and k must be multiples of 128.  No counterpart in the reference, which fixes no page layout.
+uint64_t mxfp4_scale_page_offset(uint32_t n, uint32_t kb, uint32_t k);
+void mxfp4_scales_to_page_order(uint32_t n, uint32_t k, const uint8_t *row_major, uint8_t *page_order);
+void mxfp4_scales_from_page_order(uint32_t n, uint32_t k, const uint8_t *page_order, uint8_t *row_major);
+// w1 | w3 | w2 | s1 | s3 | s2 with the tensors as the checkpoint has them -> the same page with the
+// three scale arrays in page order (src and dst must not overlap).
+void mxfp4_expert_page_from_tensors(uint32_t hidden, uint32_t inter, const uint8_t *tensor_page, uint8_t *page);
+
 // validate_ue8m0_codes / validate_e4m3fn_codes (s14_vulkan.rs:143-156).
 void validate_ue8m0_codes(const uint8_t *codes, uint64_t len);
 void validate_e4m3fn_codes(const uint8_t *codes, uint64_t len);

@@ -39,6 +39,8 @@ struct KernelMarks {
     cudaEvent_t ev[5];
 };
 
+struct UmmaScratch;
+
 cudaError_t launch_mxfp4_matvec(cudaStream_t st, uint32_t mode, int sm_count, const float *x,
                                 const uint8_t *w, const uint8_t *s, float *y, uint32_t n, uint32_t k);
 cudaError_t launch_fp8_matvec(cudaStream_t st, uint32_t mode, int sm_count, uint32_t scale_format,
@@ -55,8 +57,23 @@ int launch_moe_layer(cudaStream_t st, uint32_t mode, int sm_count, const JobTabl
                      const JobTable &param_table, uint32_t n_tokens, uint32_t n_jobs_max,
                      uint32_t hidden, uint32_t inter, const float *x, float *h, float *d, float *y,
                      cudaError_t *err, const KernelMarks *km = nullptr, bool all_mxfp4 = false,
-                     unsigned int *counters = nullptr);
-// Tensor-core pairwise phases (s14_moe_mma.cu); every job must be an MXFP4 page.
+                     unsigned int *counters = nullptr, const struct UmmaScratch *umma = nullptr);
+// Scratch of the tcgen05 phases (s14_moe_umma.cu): F64 partial sums of tiles whose K range is
+// shared between CTAs (umma_partials_bytes) and the device status word a timed-out wait sets.
+struct UmmaScratch {
+    double *partials;
+    uint32_t *status;
+};
+size_t umma_partials_bytes(int sm_count);
+// One token, every job an MXFP4 page, hidden and inter multiples of 256 that fit shared memory.
+bool umma_layer_ok(int sm_count, uint32_t n_tokens, uint32_t n_jobs_max, uint32_t hidden, uint32_t inter);
+cudaError_t launch_up_umma(cudaStream_t st, int sm_count, const JobTable *dev, const JobTable &param,
+                           const float *x, float *h, double *partials, unsigned int *counters,
+                           uint32_t *status, uint32_t hidden, uint32_t inter, bool after_router);
+cudaError_t launch_down_umma(cudaStream_t st, int sm_count, const JobTable *dev, const JobTable &param,
+                             const float *h, float *d, float *y, double *partials, unsigned int *counters,
+                             uint32_t *status, uint32_t hidden, uint32_t inter);
+// Warp-level tensor-core pairwise phases (s14_moe_mma.cu); every job must be an MXFP4 page.
 cudaError_t launch_up_mma(cudaStream_t st, int sm_count, const JobTable *dev, const JobTable &param,
                           const float *x, float *h, uint32_t hidden, uint32_t inter, uint32_t n_tokens,
                           bool after_router);

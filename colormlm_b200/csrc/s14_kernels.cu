@@ -253,11 +253,10 @@ template <int KC>
 __device__ __forceinline__ void load_row_mxfp4(RowFrag<KC> &f, const uint8_t *w, const uint8_t *s,
                                                uint32_t row, uint32_t lane) {
     const uint4 *wrow = reinterpret_cast<const uint4 *>(w + (size_t)row * (KC * 512));
-    const uint8_t *srow = s + (size_t)row * (KC * 32);
 #pragma unroll
     for (int j = 0; j < KC; ++j) {
         f.q[j] = ldg_stream(wrow + j * 32 + lane);
-        f.sc[j] = __ldg(srow + j * 32 + lane);
+        f.sc[j] = __ldg(s + scale_word_offset(row, (uint32_t)j * 8u + (lane >> 2), KC * 1024u) + (lane & 3u));
     }
 }
 
@@ -434,14 +433,13 @@ __device__ __forceinline__ float dot_row_mxfp4_reference(const uint8_t *w, const
                                                          const float *__restrict__ xs) {
     const uint32_t groups = k >> 5;
     const uint4 *wrow = reinterpret_cast<const uint4 *>(w + (size_t)row * (k >> 1));
-    const uint8_t *srow = s + (size_t)row * groups;
     float sum = 0.0f;
     for (uint32_t g4 = 0; g4 < groups; g4 += 4) {
         uint4 q[4];
         uint32_t scw;
 #pragma unroll
         for (int j = 0; j < 4; ++j) q[j] = __ldg(wrow + g4 + j);
-        scw = __ldg(reinterpret_cast<const uint32_t *>(srow + g4));
+        scw = __ldg(reinterpret_cast<const uint32_t *>(s + scale_word_offset(row, g4 >> 2, k)));
 #pragma unroll
         for (int j = 0; j < 4; ++j) {
             const float sc = ue8m0_to_f32((scw >> (8 * j)) & 0xffu);
@@ -927,7 +925,8 @@ static void launch_down_pairwise(cudaStream_t st, const JobTable *dev, const Job
 int launch_moe_layer(cudaStream_t st, uint32_t mode, int sm_count, const JobTable *dev_table,
                      const JobTable &param_table, uint32_t n_tokens, uint32_t n_jobs_max,
                      uint32_t hidden, uint32_t inter, const float *x, float *h, float *d, float *y,
-                     cudaError_t *err, const KernelMarks *km, bool all_mxfp4, unsigned int *counters) {
+                     cudaError_t *err, const KernelMarks *km, bool all_mxfp4, unsigned int *counters,
+                     const UmmaScratch *umma) {
     int launches = 0;
     *err = cudaSuccess;
     if (km) cudaEventRecord(km->ev[1], st);
@@ -939,6 +938,19 @@ int launch_moe_layer(cudaStream_t st, uint32_t mode, int sm_count, const JobTabl
         k_expert_down_reference<<<gd, 32, inter * sizeof(float), st>>>(dev_table, param_table, h, d,
                                                                        hidden, inter);
         launches += 2;
+    } else if (all_mxfp4 && counters && umma && umma_layer_ok(sm_count, n_tokens, n_jobs_max, hidden, inter)) {
+        *err = launch_up_umma(st, sm_count, dev_table, param_table, x, h, umma->partials, counters, umma->status,
+                              hidden, inter, dev_table != nullptr);
+        if (km) cudaEventRecord(km->ev[2], st);
+        if (*err == cudaSuccess)
+            *err = launch_down_umma(st, sm_count, dev_table, param_table, h, d, y, umma->partials, counters,
+                                    umma->status, hidden, inter);
+        launches += 2;
+        if (km) {
+            cudaEventRecord(km->ev[3], st);
+            cudaEventRecord(km->ev[4], st);
+        }
+        return launches;  // the down kernel also mixes
     } else if (all_mxfp4 && counters) {
         *err = launch_up_mma(st, sm_count, dev_table, param_table, x, h, hidden, inter, n_tokens,
                              dev_table != nullptr);

@@ -46,8 +46,8 @@ __device__ __forceinline__ uint32_t smem_u32(const void *p) {
 __device__ __forceinline__ void cp_async16(uint32_t dst, const void *src) {
     asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(dst), "l"(src));
 }
-__device__ __forceinline__ void cp_async8(uint32_t dst, const void *src) {
-    asm volatile("cp.async.ca.shared.global [%0], [%1], 8;" ::"r"(dst), "l"(src));
+__device__ __forceinline__ void cp_async4(uint32_t dst, const void *src) {
+    asm volatile("cp.async.ca.shared.global [%0], [%1], 4;" ::"r"(dst), "l"(src));
 }
 __device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;"); }
 template <int N>
@@ -141,14 +141,17 @@ __device__ __forceinline__ void lane_copy_tile(LaneCopy &lc, const TileRows &tr,
         lc.src[i] = base + (size_t)row * row_bytes + c * 16u;
     }
     const uint8_t *sbase = (lane < 8) ? tr.s0 : tr.s1;
-    lc.ssrc = sbase + (size_t)(((lane < 8) ? tr.r0 : tr.r1) + (lane & 7u)) * scale_bytes;
+    lc.ssrc = sbase + scale_word_offset(((lane < 8) ? tr.r0 : tr.r1) + (lane & 7u), 0, scale_bytes << 5);
 }
 
 __device__ __forceinline__ void issue_stage(const LaneCopy &lc, uint32_t stage_k, uint32_t wbuf, uint32_t sbuf,
                                             uint32_t lane) {
 #pragma unroll
     for (int i = 0; i < 4; ++i) cp_async16(wbuf + lc.dst[i], lc.src[i] + stage_k * 128u);
-    if (lane < 16) cp_async8(sbuf + lane * 8u, lc.ssrc + stage_k * 8u);
+    if (lane < 16) {  // eight codes of a row: two words, one per atom
+        cp_async4(sbuf + lane * 8u, lc.ssrc + stage_k * 1024u);
+        cp_async4(sbuf + lane * 8u + 4u, lc.ssrc + stage_k * 1024u + 512u);
+    }
 }
 
 // The 128 scale codes of a stage -> (f, f) pairs of 2^(code-127) in the warp's conversion area.

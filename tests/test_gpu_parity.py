@@ -49,6 +49,11 @@ def dev(a):
     return torch.from_numpy(np.ascontiguousarray(a)).cuda()
 
 
+def dev_page(tensor_page, hidden, inter, kind=L.PAGE_MXFP4):
+    """The oracle reads the page of checkpoint tensors; the GPU reads the expert page made from it."""
+    return dev(ExpertPageLayout(hidden, inter, kind).to_expert_page(tensor_page))
+
+
 def run_mxfp4(ctx, x, w, s, n, k):
     dx, dw, ds = dev(x), dev(w), dev(s)
     dy = torch.empty(n, dtype=torch.float32, device="cuda")
@@ -215,6 +220,7 @@ def run_layer(ctx, x, pages_dev, shared_dev, routes, shared_kind, hidden, inter)
     ctx.cmd_moe_layer(dx, dy, tr, shared_dev.data_ptr() if shared_dev is not None else None, shared_kind,
                       hidden, inter)
     torch.cuda.synchronize()
+    assert ctx.device_status() == 0  # no bounded wait of a fused kernel ran out
     return dy.cpu().numpy()
 
 
@@ -226,7 +232,8 @@ def test_moe_layer_decode(ctx, oracle, hidden, inter, shared_kind):
     x = synth.activations(g, 1, hidden)
     ids = [7, 2, 5, 0, 8, 3]
     w = np.asarray([0.31, 0.22, 0.17, 0.13, 0.1, 0.07], np.float32)
-    pages_dev, shared_dev = [dev(p) for p in pages], dev(shared)
+    pages_dev = [dev_page(p, hidden, inter) for p in pages]
+    shared_dev = dev_page(shared, hidden, inter, shared_kind)
     ref32 = oracle.moe_layer(x[0], [pages[i] for i in ids], w, shared, shared_kind, hidden, inter)
     ref64 = oracle.moe_layer_acc64(x[0], [pages[i] for i in ids], w, shared, shared_kind, hidden, inter)
     ctx.set_accumulation(L.ACCUM_REFERENCE)
@@ -247,7 +254,7 @@ def test_single_expert_chain_route_weight(ctx, oracle):
     page = synth.mxfp4_expert_page(g, hidden, inter)
     x = synth.activations(g, 1, hidden)
     ref, _ = oracle.expert_chain_mxfp4(x[0], page, hidden, inter, 0.3)
-    pd = dev(page)
+    pd = dev_page(page, hidden, inter)
     ctx.set_accumulation(L.ACCUM_REFERENCE)
     y = run_layer(ctx, x, [pd], None, [([0], [0.3])], L.PAGE_MXFP4, hidden, inter)[0]
     # the layer starts from acc = 0 and adds w * down; 0 + v == v exactly
@@ -266,7 +273,7 @@ def test_moe_layer_verify_block(ctx, oracle, n_tokens):
         ids = g.permutation(n_experts)[:6].tolist()
         w = g.uniform(0.05, 0.4, 6).astype(np.float32)
         routes.append((ids, w))
-    pages_dev, shared_dev = [dev(p) for p in pages], dev(shared)
+    pages_dev, shared_dev = [dev_page(p, hidden, inter) for p in pages], dev_page(shared, hidden, inter)
     for mode in (L.ACCUM_REFERENCE, L.ACCUM_PAIRWISE):
         ctx.set_accumulation(mode)
         y = run_layer(ctx, x, pages_dev, shared_dev, routes, L.PAGE_MXFP4, hidden, inter)
@@ -344,7 +351,7 @@ def test_routed_layer_without_host_round_trip(ctx, oracle):
     g, pages, shared = make_layer(31337, hidden, inter, n_experts, L.PAGE_MXFP4)
     wr, bias = synth.router_weight_bf16(g, n_experts, hidden), synth.router_bias(g, n_experts)
     x = synth.activations(g, 1, hidden)
-    pages_dev, shared_dev = [dev(p) for p in pages], dev(shared)
+    pages_dev, shared_dev = [dev_page(p, hidden, inter) for p in pages], dev_page(shared, hidden, inter)
     table = torch.tensor([p.data_ptr() for p in pages_dev], dtype=torch.int64, device="cuda")
     dx = dev(x)
     y = torch.empty_like(dx)
@@ -377,7 +384,7 @@ def test_expert_parallel_slots_add_up_to_the_single_gpu_layer(ctx, world):
     g, pages, shared = make_layer(4040, hidden, inter, n_experts, L.PAGE_MXFP4)
     wr, bias = synth.router_weight_bf16(g, n_experts, hidden), synth.router_bias(g, n_experts)
     x = dev(synth.activations(g, 1, hidden))
-    pages_dev, shared_dev = [dev(p) for p in pages], dev(shared)
+    pages_dev, shared_dev = [dev_page(p, hidden, inter) for p in pages], dev_page(shared, hidden, inter)
     table = torch.tensor([p.data_ptr() for p in pages_dev], dtype=torch.int64, device="cuda")
     dwr, dbias = dev(wr.view(np.int16)), dev(bias)
     for mode in (L.ACCUM_REFERENCE, L.ACCUM_PAIRWISE):
@@ -470,7 +477,7 @@ def test_pool_upload_publish_compute_release(ctx, oracle):
         missing = batch.missing()
         for i, (res, is_shared) in enumerate(missing):
             src = shared if is_shared else pages[res.key.slot]
-            staging[i].copy_(torch.from_numpy(src))
+            staging[i].copy_(torch.from_numpy(lay.to_expert_page(src)))  # reordered once, at load time
             (shared_pool if is_shared else routed_pool).upload_page_async(res, staging[i].data_ptr(), slot_bytes)
         routed_pool.transfer_fence()
         routed_pool.wait_transfer_fence()
@@ -508,7 +515,7 @@ def test_pool_upload_publish_compute_release(ctx, oracle):
 def test_moe_layer_host_buffers(ctx, oracle):
     hidden, inter = 1024, 1024
     g, pages, shared = make_layer(808, hidden, inter, 7, L.PAGE_MXFP4)
-    pages_dev, shared_dev = [dev(p) for p in pages], dev(shared)
+    pages_dev, shared_dev = [dev_page(p, hidden, inter) for p in pages], dev_page(shared, hidden, inter)
     x = synth.activations(g, 2, hidden)
     y = np.empty_like(x)
     w = np.asarray([0.3, 0.2, 0.2, 0.1, 0.1, 0.1], np.float32)

@@ -270,3 +270,52 @@ def test_upload_needs_a_device_pool():
     buf = np.zeros(16, np.uint8)
     with pytest.raises(S14Error):
         p.upload_page_async(r, buf.ctypes.data, 16)
+
+
+def test_mxfp4_scale_page_order_round_trip_and_formula():
+    """The page order of MXFP4 scale codes: the C functions, the numpy mirror and the stated
+    byte formula agree, and the two directions are inverse to each other."""
+    import ctypes as C
+
+    import numpy as np
+
+    from colormlm_b200 import _lib as L
+    from colormlm_b200.pages import ExpertPageLayout
+
+    g = np.random.default_rng(5)
+    for n, k in ((128, 128), (256, 1024), (1024, 2048)):
+        s = g.integers(0, 255, (n, k // 32), dtype=np.uint8)
+        want = ExpertPageLayout.scales_to_page_order(s, n, k)
+        got = np.empty_like(want)
+        L.check(L.lib().s14_mxfp4_scales_to_page_order(n, k, s.ctypes.data_as(C.c_void_p), got.ctypes.data_as(C.c_void_p)))
+        assert np.array_equal(want, got)
+        for r, kb in ((0, 0), (37, 5 % (k // 32)), (n - 1, k // 32 - 1), (n // 2 + 33, 2)):
+            off = ((r // 128) * (k // 128) + kb // 4) * 512 + (r % 32) * 16 + ((r % 128) // 32) * 4 + kb % 4
+            assert got[off] == s[r, kb]
+        back = np.empty_like(s)
+        L.check(L.lib().s14_mxfp4_scales_from_page_order(n, k, got.ctypes.data_as(C.c_void_p), back.ctypes.data_as(C.c_void_p)))
+        assert np.array_equal(back, s)
+        assert np.array_equal(ExpertPageLayout.scales_from_page_order(want, n, k), s)
+    with pytest.raises(L.S14Error):
+        L.check(L.lib().s14_mxfp4_scales_to_page_order(100, 128, None, None))
+
+
+def test_expert_page_from_tensors_matches_the_numpy_mirror():
+    import ctypes as C
+
+    import numpy as np
+
+    from colormlm_b200 import _lib as L
+    from colormlm_b200 import synth
+    from colormlm_b200.pages import ExpertPageLayout
+
+    hidden, inter = 1024, 512 + 512
+    lay = ExpertPageLayout(hidden, inter)
+    tensor_page = synth.mxfp4_expert_page(synth.rng(9), hidden, inter)
+    want = lay.to_expert_page(tensor_page)
+    got = np.empty_like(want)
+    L.check(L.lib().s14_mxfp4_expert_page_from_tensors(hidden, inter, tensor_page.ctypes.data_as(C.c_void_p),
+                                                       got.ctypes.data_as(C.c_void_p)))
+    assert np.array_equal(want, got)
+    assert np.array_equal(want[:3 * lay.weight_bytes], tensor_page[:3 * lay.weight_bytes])  # weights as they are
+    assert not np.array_equal(want, tensor_page)

@@ -4,6 +4,7 @@ what the context-based entry point gives, on repeated calls that reuse the libra
 scratch.  Collected last on purpose: a run that stops at the first failure has then already run
 every other test."""
 import ctypes as C
+import os
 
 import numpy as np
 import pytest
@@ -12,6 +13,7 @@ torch = pytest.importorskip("torch")
 
 from colormlm_b200 import _lib as L
 from colormlm_b200 import synth
+from colormlm_b200.pages import ExpertPageLayout
 from colormlm_b200.s14 import S14Context, S14Error, TokenRoute, _layer_desc
 
 pytestmark = [pytest.mark.gpu, pytest.mark.usefixtures("cuda_lib")]
@@ -29,10 +31,17 @@ def test_noalloc_layer_matches_context_layer_on_repeated_calls(hidden, inter):
     if not torch.cuda.is_available():
         pytest.skip("needs a CUDA device")
     g = synth.rng(4711 + hidden)
-    pages = [torch.from_numpy(synth.mxfp4_expert_page(g, hidden, inter)).cuda() for _ in range(8)]
+    lay = ExpertPageLayout(hidden, inter)
+    pages = [torch.from_numpy(lay.to_expert_page(synth.mxfp4_expert_page(g, hidden, inter))).cuda() for _ in range(8)]
     xs = torch.from_numpy(synth.activations(g, 2, hidden)).cuda()
     w = [0.3, 0.25, 0.15, 0.12, 0.1, 0.08]
-    ctx = S14Context(0)
+    # the entry point without a context runs the warp-level tensor-core kernels; the context it is
+    # compared with is told to run the same ones (it prefers the tcgen05 kernels otherwise)
+    os.environ["S14_TENSOR_PATH"] = "mma_sync"
+    try:
+        ctx = S14Context(0)
+    finally:
+        del os.environ["S14_TENSOR_PATH"]
     try:
         for mode in (L.ACCUM_PAIRWISE, L.ACCUM_REFERENCE):
             ctx.set_accumulation(mode)
