@@ -65,14 +65,13 @@ struct UmmaScratch {
     uint32_t *status;
 };
 size_t umma_partials_bytes(int sm_count);
-// One token, every job an MXFP4 page, hidden and inter multiples of 256 that fit shared memory.
+// Every job an MXFP4 page, hidden and inter multiples of 512 that fit shared and tensor memory.
 bool umma_layer_ok(int sm_count, uint32_t n_tokens, uint32_t n_jobs_max, uint32_t hidden, uint32_t inter);
-cudaError_t launch_up_umma(cudaStream_t st, int sm_count, const JobTable *dev, const JobTable &param,
-                           const float *x, float *h, double *partials, unsigned int *counters,
-                           uint32_t *status, uint32_t hidden, uint32_t inter, bool after_router);
-cudaError_t launch_down_umma(cudaStream_t st, int sm_count, const JobTable *dev, const JobTable &param,
-                             const float *h, float *d, float *y, double *partials, unsigned int *counters,
-                             uint32_t *status, uint32_t hidden, uint32_t inter);
+// Both phases and the mix in one launch (y == nullptr: the caller mixes).
+cudaError_t launch_moe_layer_umma(cudaStream_t st, int sm_count, const JobTable *dev, const JobTable &param,
+                                  uint32_t n_tokens, const float *x, float *h, float *d, float *y, double *partials,
+                                  unsigned int *counters, uint32_t *status, uint32_t hidden, uint32_t inter,
+                                  bool after_router);
 // Warp-level tensor-core pairwise phases (s14_moe_mma.cu); every job must be an MXFP4 page.
 cudaError_t launch_up_mma(cudaStream_t st, int sm_count, const JobTable *dev, const JobTable &param,
                           const float *x, float *h, uint32_t hidden, uint32_t inter, uint32_t n_tokens,

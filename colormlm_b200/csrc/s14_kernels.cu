@@ -939,18 +939,15 @@ int launch_moe_layer(cudaStream_t st, uint32_t mode, int sm_count, const JobTabl
                                                                        hidden, inter);
         launches += 2;
     } else if (all_mxfp4 && counters && umma && umma_layer_ok(sm_count, n_tokens, n_jobs_max, hidden, inter)) {
-        *err = launch_up_umma(st, sm_count, dev_table, param_table, x, h, umma->partials, counters, umma->status,
-                              hidden, inter, dev_table != nullptr);
-        if (km) cudaEventRecord(km->ev[2], st);
-        if (*err == cudaSuccess)
-            *err = launch_down_umma(st, sm_count, dev_table, param_table, h, d, y, umma->partials, counters,
-                                    umma->status, hidden, inter);
-        launches += 2;
-        if (km) {
+        *err = launch_moe_layer_umma(st, sm_count, dev_table, param_table, n_tokens, x, h, d, y, umma->partials,
+                                     counters, umma->status, hidden, inter, dev_table != nullptr);
+        launches += 1;
+        if (km) {  // one kernel runs both phases and the mix: its time is booked as the up phase
+            cudaEventRecord(km->ev[2], st);
             cudaEventRecord(km->ev[3], st);
             cudaEventRecord(km->ev[4], st);
         }
-        return launches;  // the down kernel also mixes
+        return launches;
     } else if (all_mxfp4 && counters) {
         *err = launch_up_mma(st, sm_count, dev_table, param_table, x, h, hidden, inter, n_tokens,
                              dev_table != nullptr);

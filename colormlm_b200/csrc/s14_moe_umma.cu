@@ -39,30 +39,27 @@ constexpr uint32_t kThreads = 512;               // warps 14 and 15 only help wi
 constexpr uint32_t kTmemCols = 512;            // [0,128): 8 accumulators x 16; [128,192): weight scales; [192,512): digit scales
 constexpr uint32_t kSfaCol0 = 128, kSfbCol0 = 192;
 constexpr uint32_t kDigitSlots = 2;            // activation vectors a CTA's run can need
+constexpr uint32_t kMaxBlocks = 160;           // scale blocks per activation vector (K <= 5120)
 constexpr uint32_t kMaxK = (kTmemCols - kSfbCol0) / kDigitSlots / 4 * 128;  // digit scales of both slots fit tensor memory
 constexpr uint32_t kSpin = 1u << 17;           // tries before a wait gives up
 constexpr uint32_t kMaxTiles = 2048;           // tile counters per phase
 constexpr uint32_t kUpCounter0 = 1, kDownCounter0 = 1 + kMaxTiles, kMixCounter0 = 1 + 2 * kMaxTiles;
-static_assert(kMixCounter0 + kMaxTokens * 64 <= 8192, "a context allocates 8192 arrival counters");
+constexpr uint32_t kHReadyCounter0 = kMixCounter0 + kMaxTokens * 64;  // finished up tiles per job
+constexpr uint32_t kExitCounter = kHReadyCounter0 + kMaxJobs;          // CTAs that have left the kernel
+static_assert(kExitCounter < 8192, "a context allocates 8192 arrival counters");
+constexpr uint32_t kSpinGlobal = 1u << 20;     // polls (100 ns apart) of another CTA's progress before giving up
 constexpr uint32_t kMaxRowTiles = 64;             // mix counters: [token][row tile]
 
 // Bar indices in the static barrier array: stage filled, unit multiplied, accumulator read,
 // digit scales in tensor memory, both issuing threads finished.
-constexpr uint32_t kBarFull = 0, kBarDone = kRing, kBarAccFree = 2 * kRing, kBarSfb = 3 * kRing, kBarFin = 3 * kRing + 1,
-                   kBars = 3 * kRing + 2;
+constexpr uint32_t kBarFull = 0, kBarDone = kRing, kBarAccFree = 2 * kRing, kBarDigitsUp = 3 * kRing,
+                   kBarDigitsDown = 3 * kRing + 1, kBarFin = 3 * kRing + 2, kBars = 3 * kRing + 3;
 
 __device__ __forceinline__ uint32_t smem_u32(const void *p) {
     return (uint32_t)__cvta_generic_to_shared(p);
 }
 __device__ __forceinline__ void cp_async16(uint32_t dst, const void *src) {
     asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(dst), "l"(src));
-}
-#ifndef S14_UMMA_PREFETCH
-#define S14_UMMA_PREFETCH 0
-#endif
-constexpr uint32_t kPrefetch = S14_UMMA_PREFETCH;  // units the L2 prefetch runs ahead of the copies
-__device__ __forceinline__ void prefetch_l2(const void *p, uint32_t bytes) {
-    asm volatile("cp.async.bulk.prefetch.L2.global [%0], %1;" ::"l"(p), "r"(bytes) : "memory");
 }
 __device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
     asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count));
@@ -177,11 +174,11 @@ __device__ __forceinline__ void trace_mark(bool up, uint32_t k) {
     asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t));
     g_umma_trace[up ? 1 : 0][blockIdx.x][k] = t;
 }
-#define TRACE(k) trace_mark(kUp, k)
+#define TRACE(k) trace_mark(true, k)
 __device__ long long g_umma_cyc[2][160][8];
 #define CYC_DECL(n) long long cyc_[n] = {}; long long cyc_t_ = clock64()
 #define CYC_LAP(k) do { const long long now_ = clock64(); cyc_[k] += now_ - cyc_t_; cyc_t_ = now_; } while (0)
-#define CYC_STORE(base, n) do { for (int q_ = 0; q_ < (n); ++q_) g_umma_cyc[kUp ? 1 : 0][blockIdx.x][(base) + q_] = cyc_[q_]; } while (0)
+#define CYC_STORE(base, n) do { for (int q_ = 0; q_ < (n); ++q_) g_umma_cyc[1][blockIdx.x][(base) + q_] = cyc_[q_]; } while (0)
 #else
 #define TRACE(k) ((void)0)
 #define CYC_DECL(n) ((void)0)
@@ -196,15 +193,18 @@ constexpr uint32_t kIdesc = (1u << 7) | (1u << 10) | ((16u >> 3) << 17) | (1u <<
 // elements, i.e. one 32-bit word of every digit row; the four lanes of a scale block agree on its
 // exponent E (largest magnitude < 2^E, clamped to [-100, 128]).  With the bias 4 * (8^8 - 1) / 7
 // added, the balanced digits of q are the plain base-8 digits minus 4, so no carry runs through
-// them.  Rows 8-15 of the tile and the scale bytes of unused rows are initialised by the caller.
-__device__ void build_digits(const float *__restrict__ v0, const float *__restrict__ v1, uint32_t n_vec, uint32_t K,
-                             uint8_t *sB, uint32_t b_stride, uint8_t *sSFB, uint32_t sfb_stride) {
+// them.  Rows 8-15 of the tile are zeroed by the caller; the blocks' exponents go to sE, from which
+// store_digit_scales writes the digit rows' scale codes into tensor memory.
+__device__ void build_digits(const float *v0, const float *v1, uint32_t n_vec, uint32_t K,
+                             uint8_t *sB, uint32_t b_stride, uint8_t *sE, uint32_t tid,
+                             uint32_t n_threads) {
     const uint32_t per_vec = K >> 3;
-    for (uint32_t item = threadIdx.x; item < n_vec * per_vec; item += blockDim.x) {
+    for (uint32_t item = tid; item < n_vec * per_vec; item += n_threads) {
         const uint32_t slot = item >= per_vec ? 1u : 0u, g = item - slot * per_vec;
         const float *v = slot ? v1 : v0;
-        const float4 p0 = reinterpret_cast<const float4 *>(v)[2u * g];
-        const float4 p1 = reinterpret_cast<const float4 *>(v)[2u * g + 1u];
+        // read through L2: a hidden vector was written by other CTAs of this launch
+        const float4 p0 = __ldcg(reinterpret_cast<const float4 *>(v) + 2u * g);
+        const float4 p1 = __ldcg(reinterpret_cast<const float4 *>(v) + 2u * g + 1u);
         const float xs[8] = {p0.x, p0.y, p0.z, p0.w, p1.x, p1.y, p1.z, p1.w};
         float bm = 0.0f;
 #pragma unroll
@@ -212,7 +212,7 @@ __device__ void build_digits(const float *__restrict__ v0, const float *__restri
         bm = fmaxf(bm, __shfl_xor_sync(0xffffffffu, bm, 1));
         bm = fmaxf(bm, __shfl_xor_sync(0xffffffffu, bm, 2));
         int E = -100;
-        if (bm > 0.0f) E = min(max((int)((__float_as_uint(bm) >> 23) & 0xFFu) - 126, -100), 128);
+        if (bm > 0.0f) E = min(max((int)((__float_as_uint(bm) >> 23) & 0xFFu) - 126, -100), 127);
         const float up = __uint_as_float((uint32_t)(150 - E) << 23);  // 2^(23-E)
         uint32_t words[8] = {0u, 0u, 0u, 0u, 0u, 0u, 0u, 0u};
 #pragma unroll
@@ -229,12 +229,32 @@ __device__ void build_digits(const float *__restrict__ v0, const float *__restri
 #pragma unroll
         for (uint32_t j = 0; j < 8; ++j)
             *reinterpret_cast<uint32_t *>(chunk + j * 128u + (((kb & 7u) ^ j) << 4)) = words[j];
-#pragma unroll
-        for (uint32_t jj = 0; jj < 2; ++jj) {
-            const uint32_t j = (g & 3u) * 2u + jj;
-            sSFB[slot * sfb_stride + (kb >> 2) * 256u + j * 16u + (kb & 3u)] = (uint8_t)(104 + E + 3 * (int)j);
-        }
+        if ((g & 3u) == 0u) sE[slot * kMaxBlocks + kb] = (uint8_t)(E + 100);  // the block's exponent, biased
     }
+}
+
+// The scale codes of the digit rows, written to tensor memory by the eight epilogue warps (each
+// lane quadrant takes every atom; warps 0-3 the even groups of four atoms, warps 4-7 the odd ones).
+// Column 4a of lane l holds the codes of N-row l for scale blocks 4a..4a+3: digit row l < 8 of a
+// block with exponent E has the code 127 + E - 23 + 3l; rows 8-15 are zero rows, columns 4a+1..4a+3
+// belong to N-rows 32 and up, which a 16-column MMA does not read.
+__device__ __forceinline__ void store_digit_scales(uint32_t tmem_sfb, const uint8_t *sE, uint32_t n_slots, uint32_t K,
+                                                   uint32_t sfb_cols, uint32_t warp, uint32_t lane) {
+    const uint32_t groups = K >> 9;  // groups of four atoms (512 K-elements, 16 blocks)
+    const uint32_t bias = 0x01010101u * (4u + 3u * (lane & 7u));
+    const uint32_t quad = tmem_sfb + (((warp & 3u) * 32u) << 16);
+    for (uint32_t q = warp >> 2; q < n_slots * groups; q += 2u) {
+        const uint32_t b = q / groups, g = q - b * groups;
+        const uint4 e = *reinterpret_cast<const uint4 *>(sE + b * kMaxBlocks + g * 16u);
+        const uint32_t one = 0x7F7F7F7Fu;
+        const uint32_t w0 = lane < 8u ? e.x + bias : one, w1 = lane < 8u ? e.y + bias : one;
+        const uint32_t w2 = lane < 8u ? e.z + bias : one, w3 = lane < 8u ? e.w + bias : one;
+        asm volatile(
+            "tcgen05.st.sync.aligned.32x32b.x16.b32 [%0], {%1,%5,%5,%5,%2,%5,%5,%5,%3,%5,%5,%5,%4,%5,%5,%5};"
+            ::"r"(quad + b * sfb_cols + g * 16u), "r"(w0), "r"(w1), "r"(w2), "r"(w3), "r"(one)
+            : "memory");
+    }
+    asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
 }
 
 // s + e = a + b exactly (Knuth); no operation may be contracted or reordered.
@@ -252,44 +272,87 @@ __device__ __forceinline__ float swiglu_limit_fast(float gate, float up) {
     return __fmul_rn(__fdiv_rn(g, __fadd_rn(1.0f, expf(-g))), u);
 }
 
-template <bool kUp>
+// Shape of one phase: the up phase multiplies [inter, hidden] twice (w1, w3), the down phase
+// [hidden, inter] once (w2).
+struct PhaseShape {
+    uint32_t K, rows, mats, kchunks, upt, tpj;  // upt: units per tile, tpj: tiles per job
+    uint32_t b_stride, sfb_cols;                // digit tile (shared memory), its scale columns (tensor memory)
+};
+__device__ __forceinline__ PhaseShape phase_shape(bool up, uint32_t hidden, uint32_t inter) {
+    PhaseShape ps;
+    ps.K = up ? hidden : inter;
+    ps.rows = up ? inter : hidden;
+    ps.mats = up ? 2u : 1u;
+    ps.kchunks = ps.K >> 8;
+    ps.upt = ps.mats * ps.kchunks;
+    ps.tpj = ps.rows >> 7;
+    ps.b_stride = ps.kchunks * 2048u;
+    ps.sfb_cols = (ps.K >> 7) * 4u;
+    return ps;
+}
+// A CTA's run of a phase: units [u0, u1) of `total`, cut into G equal runs.
+struct Run {
+    uint64_t total;
+    uint32_t G, u0, u1, n, job_first, job_last;
+};
+__device__ __forceinline__ Run make_run(const PhaseShape &ps, uint32_t n_jobs, uint32_t grid, uint32_t cta) {
+    Run r;
+    r.total = (uint64_t)n_jobs * ps.tpj * ps.upt;
+    // every working CTA gets at least one unit, so each tile's contributors are consecutive CTAs
+    r.G = (uint32_t)min((uint64_t)grid, r.total);
+    const bool working = cta < r.G;
+    r.u0 = working ? (uint32_t)(r.total * cta / r.G) : 0u;
+    r.u1 = working ? (uint32_t)(r.total * (cta + 1u) / r.G) : 0u;
+    r.n = r.u1 - r.u0;
+    // a run is at most one job long (the launcher requires n_jobs <= gridDim.x): two jobs at most
+    r.job_first = r.n ? (r.u0 / ps.upt) / ps.tpj : 0u;
+    r.job_last = r.n ? ((r.u1 - 1u) / ps.upt) / ps.tpj : 0u;
+    return r;
+}
+
+__device__ __forceinline__ uint32_t ld_acquire(const unsigned int *p) {
+    uint32_t v;
+    asm volatile("ld.acquire.gpu.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+    return v;
+}
+
+// One launch runs the whole layer.  Every CTA streams its run of the up phase and then its run of
+// the down phase through one ring; the copies of the down phase do not wait for the hidden
+// vectors, only its MMAs do (the vectors of a job are complete when the job's counter says that
+// all its up tiles are finished, whichever CTAs finished them).
 __global__ void __launch_bounds__(kThreads, 1)
-k_expert_umma(const JobTable *__restrict__ dev_table, const __grid_constant__ JobTable param_table,
-              const float *__restrict__ vec_in, float *__restrict__ out, float *__restrict__ y,
-              double *__restrict__ partials, unsigned int *__restrict__ counters,
-              uint32_t *__restrict__ status, uint32_t hidden, uint32_t inter) {
+k_moe_layer_umma(const JobTable *__restrict__ dev_table, const __grid_constant__ JobTable param_table,
+                 const float *__restrict__ x, float *h, float *d, float *__restrict__ y,
+                 double *__restrict__ partials, unsigned int *__restrict__ counters, uint32_t *__restrict__ status,
+                 uint32_t hidden, uint32_t inter, uint32_t b_bytes) {
     extern __shared__ __align__(1024) uint8_t smem[];
     __shared__ __align__(8) uint64_t bars[kBars];
     __shared__ double xchg[kEpiGroup];  // group B's sums of a tile, handed to group A
     __shared__ uint32_t tmem_slot;
     __shared__ int abort_flag;
     __shared__ uint32_t epi_info[3];
+    __shared__ __align__(16) uint8_t sE[kDigitSlots * kMaxBlocks];  // block exponents of the digit tiles
 
     const uint32_t tid = threadIdx.x, warp = tid >> 5, lane = tid & 31u;
     const bool is_producer = warp >= kProdWarp0 && warp < kProdWarp0 + kProdThreads / 32u;
     if (tid == 0) TRACE(0);
-    const uint32_t K = kUp ? hidden : inter, rows = kUp ? inter : hidden;
-    constexpr uint32_t mats = kUp ? 2u : 1u;
-    const uint32_t kchunks = K >> 8, upt = mats * kchunks, tpj = rows >> 7;
-    const uint32_t b_stride = kchunks * 2048u, sfb_stride = (K >> 7) * 256u + 256u, sfb_cols = (K >> 7) * 4u;
+    const PhaseShape PU = phase_shape(true, hidden, inter), PD = phase_shape(false, hidden, inter);
     uint8_t *const sA = smem;
     uint8_t *const sSFA = sA + kRing * kStageA;
     uint8_t *const sB = sSFA + kRing * kStageSf;
-    uint8_t *const sSFB = sB + kDigitSlots * b_stride;
     const uint32_t bar0 = smem_u32(bars);
     auto bar = [&](uint32_t i) { return bar0 + i * 8u; };
 
-    for (uint32_t i = tid; i < (kDigitSlots * b_stride) >> 4; i += kThreads)
-        reinterpret_cast<uint4 *>(sB)[i] = make_uint4(0u, 0u, 0u, 0u);
-    for (uint32_t i = tid; i < (kDigitSlots * sfb_stride) >> 2; i += kThreads)
-        reinterpret_cast<uint32_t *>(sSFB)[i] = 0x7F7F7F7Fu;
+    // rows 8-15 of every digit tile stay zero
+    for (uint32_t i = tid; i < b_bytes >> 4; i += kThreads) reinterpret_cast<uint4 *>(sB)[i] = make_uint4(0u, 0u, 0u, 0u);
     if (tid == 0) {
         for (uint32_t s = 0; s < kRing; ++s) {
             mbar_init(bar(kBarFull + s), kProdThreads);
             mbar_init(bar(kBarDone + s), 1);
             mbar_init(bar(kBarAccFree + s), kEpiGroup);
         }
-        mbar_init(bar(kBarSfb), 1);
+        mbar_init(bar(kBarDigitsUp), 2u * kEpiGroup);
+        mbar_init(bar(kBarDigitsDown), 2u * kEpiGroup);
         mbar_init(bar(kBarFin), 2);
         abort_flag = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
@@ -306,254 +369,250 @@ k_expert_umma(const JobTable *__restrict__ dev_table, const __grid_constant__ Jo
     const uint32_t tmem = tmem_slot;
     if (tid == 0) TRACE(1);
 
-    if (kUp) {
-        if (dev_table) {
-            // One token routed on the device: the token does not depend on the router, so its
-            // digits are built while the router runs; the job table is read only afterwards.
-            build_digits(vec_in, vec_in, 1, K, sB, b_stride, sSFB, sfb_stride);
-        }
-        cudaGridDependencySynchronize();
-        cudaTriggerProgrammaticLaunchCompletion();
+    if (dev_table) {
+        // One token routed on the device: the token does not depend on the router, so its digits
+        // are built while the router runs; the job table is read only afterwards.
+        build_digits(x, x, 1, PU.K, sB, PU.b_stride, sE, tid, kThreads);
     }
+    cudaGridDependencySynchronize();
     const JobTable &tab = table_of(dev_table, param_table);
-    const uint32_t n_jobs = tab.n_jobs;
-    const uint64_t total = (uint64_t)n_jobs * tpj * upt;
-    // every working CTA gets at least one unit, so each tile's contributors are consecutive CTAs
-    const uint32_t G = (uint32_t)min((uint64_t)gridDim.x, total), cta = blockIdx.x;
-    const bool working = cta < G;
-    const uint32_t u0 = working ? (uint32_t)(total * cta / G) : 0u;
-    const uint32_t u1 = working ? (uint32_t)(total * (cta + 1u) / G) : 0u;
-    const uint32_t n_units = u1 - u0;
-    // a run is at most one job long (the launcher requires n_jobs <= gridDim.x): it touches two jobs at most
-    const uint32_t job_first = n_units ? (u0 / upt) / tpj : 0u;
-    const uint32_t job_last = n_units ? ((u1 - 1u) / upt) / tpj : 0u;
-    const uint32_t tok0 = (kUp && !dev_table && n_units) ? tab.jobs[job_first].token : 0u;
-    const uint32_t tok1 = (kUp && !dev_table && n_units) ? tab.jobs[job_last].token : 0u;
-    const uint32_t slots_used = kUp ? (tok1 != tok0 ? 2u : 1u) : job_last - job_first + 1u;
+    const uint32_t n_jobs = tab.n_jobs, cta = blockIdx.x;
+    const Run RU = make_run(PU, n_jobs, gridDim.x, cta), RD = make_run(PD, n_jobs, gridDim.x, cta);
+    const uint32_t tok0 = (!dev_table && RU.n) ? tab.jobs[RU.job_first].token : 0u;
+    const uint32_t tok1 = (!dev_table && RU.n) ? tab.jobs[RU.job_last].token : 0u;
+    const uint32_t up_slots = tok1 != tok0 ? 2u : 1u, down_slots = RD.job_last - RD.job_first + 1u;
     // digit slot of job j: up phase by token, down phase by job
-    auto slot_of = [&](uint32_t j) { return kUp ? (tab.jobs[j].token == tok0 ? 0u : 1u) : j - job_first; };
-
-    // Producer: the copies of the run's unit i, at cursor c, into ring stage i % kRing.
-    auto produce = [&](uint32_t i, const UnitCursor &c) {
-        const uint32_t ks = kUp ? (c.w >> 1) : c.w, mat = kUp ? (c.w & 1u) : 0u;
-        const PageView pv = page_view(tab.jobs[c.j].page, S14_PAGE_MXFP4, hidden, inter);
-        const uint8_t *wp = kUp ? (mat ? pv.w3 : pv.w1) : pv.w2;
-        const uint8_t *sp = kUp ? (mat ? pv.s3 : pv.s1) : pv.s2;
-        const uint32_t s = i % kRing, pt = tid - kProdWarp0 * 32u;
-        const uint32_t r8 = pt >> 3, cc = pt & 7u;
-        const uint8_t *src = wp + (size_t)(c.rt * 128u + r8) * (K >> 1) + ks * 128u + cc * 16u;
-        const uint32_t dst = smem_u32(sA + s * kStageA) + r8 * 128u + ((cc ^ (r8 & 7u)) << 4);
-#pragma unroll
-        for (uint32_t i8 = 0; i8 < 8; ++i8) cp_async16(dst + i8 * 2048u, src + (size_t)i8 * 16u * (K >> 1));
-        // the unit's two scale atoms are 1 KB of consecutive page bytes, already in tensor-memory order
-        if (pt < kStageSf / 16u)
-            cp_async16(smem_u32(sSFA + s * kStageSf) + pt * 16u, sp + scale_word_offset(c.rt * 128u, ks * 2u, K) + pt * 16u);
-        mbar_arrive_after_copies(bar(kBarFull + s));
-    };
-
-    // L2 prefetch of one unit: a thread per row (128 B of codes).  Data in flight from HBM to L2
-    // needs no shared memory, so it can run further ahead than the ring is deep.
-    auto prefetch = [&](const UnitCursor &c) {
-        const uint32_t ks = kUp ? (c.w >> 1) : c.w, mat = kUp ? (c.w & 1u) : 0u;
-        const PageView pv = page_view(tab.jobs[c.j].page, S14_PAGE_MXFP4, hidden, inter);
-        const uint8_t *wp = kUp ? (mat ? pv.w3 : pv.w1) : pv.w2;
-        const uint32_t pt = tid - kProdWarp0 * 32u;
-        prefetch_l2(wp + (size_t)(c.rt * 128u + pt) * (K >> 1) + ks * 128u, 128u);
-    };
-
-    uint32_t prefilled = 0, prefetched = 0;
-    UnitCursor pc = cursor_at(u0, upt, tpj);  // the producer's position
-    UnitCursor fc = pc;                       // the prefetch's position
-    if (!kUp) {
-        // Weight copies start before the up phase has finished; its output is read only after.
-        if (is_producer) {
-            prefilled = min(n_units, kRing);
-            for (uint32_t i = 0; i < prefilled; ++i) {
-                produce(i, pc);
-                cursor_advance(pc, 1, upt, tpj);
-            }
-            fc = pc;
-            for (prefetched = prefilled; prefetched < min(n_units, prefilled + kPrefetch); ++prefetched) {
-                prefetch(fc);
-                cursor_advance(fc, 1, upt, tpj);
-            }
-        }
-        cudaGridDependencySynchronize();
-        if (n_units)
-            build_digits(vec_in + (size_t)job_first * inter, vec_in + (size_t)job_last * inter, slots_used, K, sB,
-                         b_stride, sSFB, sfb_stride);
-    } else if (!dev_table && n_units) {
-        build_digits(vec_in + (size_t)tok0 * hidden, vec_in + (size_t)tok1 * hidden, slots_used, K, sB, b_stride,
-                     sSFB, sfb_stride);
-    }
+    auto slot_up = [&](uint32_t j) { return tab.jobs[j].token == tok0 ? 0u : 1u; };
+    if (!dev_table && RU.n)
+        build_digits(x + (size_t)tok0 * hidden, x + (size_t)tok1 * hidden, up_slots, PU.K, sB, PU.b_stride, sE, tid,
+                     kThreads);
     asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
     __syncthreads();
     if (tid == 0) TRACE(2);
 
+    unsigned int *const h_ready = counters + kHReadyCounter0;
+
     if (is_producer) {
-        if (kPrefetch) {
-            if (prefetched < kRing) {  // the first kRing units are copied at once, not prefetched
-                prefetched = min(n_units, kRing);
-                fc = cursor_at(u0 + prefetched, upt, tpj);
+        // ---- copies: the run of the up phase, then the run of the down phase, through one ring ----
+        const uint32_t pt = tid - kProdWarp0 * 32u, r8 = pt >> 3, cc = pt & 7u;
+        const uint32_t dst0 = smem_u32(sA) + r8 * 128u + ((cc ^ (r8 & 7u)) << 4);
+        uint32_t i = 0;
+        bool ok = true;
+        for (uint32_t ph = 0; ph < 2 && ok; ++ph) {
+            const PhaseShape &ps = ph ? PD : PU;
+            const Run &run = ph ? RD : RU;
+            UnitCursor c = cursor_at(run.u0, ps.upt, ps.tpj);
+            for (uint32_t l = 0; l < run.n; ++l, ++i) {
+                const uint32_t s = i % kRing;
+                if (i >= kRing && !mbar_wait(bar(kBarDone + s), ((i / kRing) - 1u) & 1u, &abort_flag)) {
+                    ok = false;
+                    break;
+                }
+                const uint32_t ks = ph ? c.w : (c.w >> 1), mat = ph ? 0u : (c.w & 1u);
+                const PageView pv = page_view(tab.jobs[c.j].page, S14_PAGE_MXFP4, hidden, inter);
+                const uint8_t *wp = ph ? pv.w2 : (mat ? pv.w3 : pv.w1);
+                const uint8_t *sp = ph ? pv.s2 : (mat ? pv.s3 : pv.s1);
+                const uint8_t *src = wp + (size_t)(c.rt * 128u + r8) * (ps.K >> 1) + ks * 128u + cc * 16u;
+                const uint32_t dst = dst0 + s * kStageA;
+#pragma unroll
+                for (uint32_t i8 = 0; i8 < 8; ++i8) cp_async16(dst + i8 * 2048u, src + (size_t)i8 * 16u * (ps.K >> 1));
+                // the unit's two scale atoms are 1 KB of consecutive page bytes, already in tensor-memory order
+                if (pt < kStageSf / 16u)
+                    cp_async16(smem_u32(sSFA + s * kStageSf) + pt * 16u,
+                               sp + scale_word_offset(c.rt * 128u, ks * 2u, ps.K) + pt * 16u);
+                mbar_arrive_after_copies(bar(kBarFull + s));
+                cursor_advance(c, 1, ps.upt, ps.tpj);
             }
-        }
-        for (uint32_t i = prefilled; i < n_units; ++i) {
-            for (; kPrefetch && prefetched < min(n_units, i + kRing + kPrefetch); ++prefetched) {
-                prefetch(fc);
-                cursor_advance(fc, 1, upt, tpj);
-            }
-            if (i >= kRing && !mbar_wait(bar(kBarDone + i % kRing), ((i / kRing) - 1u) & 1u, &abort_flag)) break;
-            produce(i, pc);
-            cursor_advance(pc, 1, upt, tpj);
         }
         if (tid == kProdWarp0 * 32u) TRACE(8);
         asm volatile("cp.async.wait_all;" ::: "memory");
         if (tid == kProdWarp0 * 32u) TRACE(9);
     } else if (warp == kMmaWarp0 || warp == kMmaWarp0 + 1u) {
-        if (lane == 0 && n_units) {
-            // Two issuing threads take the run's even and odd units.  One accumulator per unit: a
-            // tile's result is the F64 sum of its units' F32 sums, whichever CTAs computed them.
+        if (lane == 0 && (RU.n || RD.n)) {
+            // ---- MMA issue: two threads take the even and the odd ring indices.  One accumulator per
+            // unit: a tile's result is the sum of its units' F32 sums, whichever CTAs computed them. ----
             const uint32_t m = warp - kMmaWarp0;
-            if (m == 0) {
-                // the digit rows' scales stay in tensor memory for the whole run
-                fence_after();
-                for (uint32_t b = 0; b < slots_used; ++b)
-                    for (uint32_t a = 0; a < (K >> 7); ++a)
-                        tmem_copy_scales(tmem + kSfbCol0 + b * sfb_cols + a * 4u,
-                                         smem_desc(smem_u32(sSFB + b * sfb_stride + a * 256u), 0, 8, 0));
-                umma_commit(bar(kBarSfb));
-            }
-            bool ok = mbar_wait(bar(kBarSfb), 0, &abort_flag);
             const uint64_t a_desc0 = smem_desc(smem_u32(sA), 1, 64, 2), b_desc0 = smem_desc(smem_u32(sB), 1, 64, 2);
             const uint64_t sfa_desc0 = smem_desc(smem_u32(sSFA), 0, 8, 0);
-            UnitCursor c = cursor_at(u0 + m, upt, tpj);
-            uint32_t slot_t = ~0u, b = 0;
-            CYC_DECL(4);
-            for (uint32_t i = m; i < n_units && ok; i += 2) {
-                if (c.t != slot_t) {
-                    slot_t = c.t;
-                    b = slot_of(c.j);
-                }
-                const uint32_t ks = kUp ? (c.w >> 1) : c.w;
-                const uint32_t s = i % kRing, ph = (i / kRing) & 1u;
-                CYC_LAP(0);
-                if (!mbar_wait(bar(kBarFull + s), ph, &abort_flag)) break;
-                if (i == 0) TRACE(3);
-                CYC_LAP(1);
-                if (i >= kRing && !mbar_wait(bar(kBarAccFree + s), ph ^ 1u, &abort_flag)) break;
-                CYC_LAP(2);
+            bool ok = true;
+            for (uint32_t ph = 0; ph < 2 && ok; ++ph) {
+                const PhaseShape &ps = ph ? PD : PU;
+                const Run &run = ph ? RD : RU;
+                if (!run.n) continue;
+                const uint32_t i0 = ph ? RU.n : 0u;
+                // the phase's digit rows are in shared memory, their scales in tensor memory
+                ok = mbar_wait(bar(ph ? kBarDigitsDown : kBarDigitsUp), 0, &abort_flag);
+                if (!ok) break;
                 asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
                 fence_after();
-                const uint32_t sfa_t = tmem + kSfaCol0 + s * 8u, sfb_t = tmem + kSfbCol0 + b * sfb_cols + ks * 8u;
-                const uint64_t sfa_d = sfa_desc0 + s * (kStageSf >> 4);
-                tmem_copy_scales(sfa_t, sfa_d);
-                tmem_copy_scales(sfa_t + 4u, sfa_d + (512u >> 4));
-                const uint64_t ad = a_desc0 + s * (kStageA >> 4), bd = b_desc0 + ((b * b_stride + ks * 2048u) >> 4);
+                const uint32_t l0 = (m ^ i0) & 1u;  // first unit of this phase with ring index parity m
+                UnitCursor c = cursor_at(run.u0 + l0, ps.upt, ps.tpj);
+                uint32_t slot_t = ~0u, b = 0;
+                CYC_DECL(4);
+                for (uint32_t l = l0; l < run.n; l += 2) {
+                    const uint32_t i = i0 + l;
+                    if (c.t != slot_t) {
+                        slot_t = c.t;
+                        b = ph ? c.j - RD.job_first : slot_up(c.j);
+                    }
+                    const uint32_t ks = ph ? c.w : (c.w >> 1);
+                    const uint32_t s = i % kRing, par = (i / kRing) & 1u;
+                    CYC_LAP(0);
+                    if (!mbar_wait(bar(kBarFull + s), par, &abort_flag)) { ok = false; break; }
+                    if (i == 0) TRACE(3);
+                    CYC_LAP(1);
+                    if (i >= kRing && !mbar_wait(bar(kBarAccFree + s), par ^ 1u, &abort_flag)) { ok = false; break; }
+                    CYC_LAP(2);
+                    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+                    fence_after();
+                    const uint32_t sfa_t = tmem + kSfaCol0 + s * 8u, sfb_t = tmem + kSfbCol0 + b * ps.sfb_cols + ks * 8u;
+                    const uint64_t sfa_d = sfa_desc0 + s * (kStageSf >> 4);
+                    tmem_copy_scales(sfa_t, sfa_d);
+                    tmem_copy_scales(sfa_t + 4u, sfa_d + (512u >> 4));
+                    const uint64_t ad = a_desc0 + s * (kStageA >> 4), bd = b_desc0 + ((b * ps.b_stride + ks * 2048u) >> 4);
 #pragma unroll
-                for (uint32_t kk = 0; kk < 4; ++kk) {
-                    const uint32_t atom = kk >> 1, sfid = (kk & 1u) * 2u;
-                    umma_mxf4(tmem + s * 16u, ad + kk * 2u, bd + kk * 2u, kIdesc | (sfid << 29) | (sfid << 4),
-                              (sfa_t + atom * 4u) | (sfid << 30), (sfb_t + atom * 4u) | (sfid << 30), kk ? 1u : 0u);
+                    for (uint32_t kk = 0; kk < 4; ++kk) {
+                        const uint32_t atom = kk >> 1, sfid = (kk & 1u) * 2u;
+                        umma_mxf4(tmem + s * 16u, ad + kk * 2u, bd + kk * 2u, kIdesc | (sfid << 29) | (sfid << 4),
+                                  (sfa_t + atom * 4u) | (sfid << 30), (sfb_t + atom * 4u) | (sfid << 30), kk ? 1u : 0u);
+                    }
+                    umma_commit(bar(kBarDone + s));
+                    CYC_LAP(3);
+                    cursor_advance(c, 2, ps.upt, ps.tpj);
                 }
-                umma_commit(bar(kBarDone + s));
-                CYC_LAP(3);
-                cursor_advance(c, 2, upt, tpj);
-            }
-            if (m == 0) {
-                CYC_STORE(0, 4);
-                TRACE(4);
+                if (m == 0 && ph == 0) {
+                    CYC_STORE(0, 4);
+                    TRACE(4);
+                }
             }
             // nothing of this CTA's tensor work is in flight when the tensor memory is freed
             umma_commit(bar(kBarFin));
             mbar_wait(bar(kBarFin), 0, &abort_flag);
             if (m == 0) TRACE(5);
         }
-    } else if (warp < 2u * kEpiGroup / 32u && n_units) {
-        // Epilogue.  Group A (warps 0-3) sums the even units of a tile, group B (warps 4-7) the odd
-        // ones: in the up phase these are the gate and the up projection.
+    } else if (warp < 2u * kEpiGroup / 32u && (RU.n || RD.n)) {
+        // ---- epilogue.  Group A (warps 0-3) sums the even units of a tile, group B (warps 4-7) the
+        // odd ones: in the up phase these are the gate and the up projection. ----
         const uint32_t grp = warp >> 2, row = tid & (kEpiGroup - 1u);
         const uint32_t lane_base = tmem + (((warp & 3u) * 32u) << 16);
-        float hi = 0.0f, lo = 0.0f;  // hi + lo: this group's sum over the tile's units, to about 48 bits
         bool ok = true;
-        UnitCursor c = cursor_at(u0, upt, tpj);
-        CYC_DECL(4);
-        for (uint32_t i = 0; i < n_units; ++i) {
-            const uint32_t s = i % kRing;
-            if ((c.w & 1u) == grp) {
-                CYC_LAP(3);
-                ok = __all_sync(0xffffffffu, ok && mbar_wait(bar(kBarDone + s), (i / kRing) & 1u, &abort_flag));
-                CYC_LAP(0);
-                if (ok) {
-                    if (tid == 0 && i + 2u >= n_units) TRACE(6);
-                    fence_after();
-                    float a[8];
-                    tmem_ld8(lane_base + s * 16u, a);
-                    fence_before();
-                    mbar_arrive(bar(kBarAccFree + s));
-                    CYC_LAP(2);
-#pragma unroll
-                    for (int jj = 0; jj < 8; ++jj) {  // low digits first
-                        float e;
-                        two_sum(hi, a[jj], hi, e);
-                        lo = __fadd_rn(lo, e);
-                    }
-                }
-            }
-            const bool tile_ends = c.w + 1u == upt;
-            if (!tile_ends && i + 1u != n_units) {
-                cursor_advance(c, 1, upt, tpj);
-                continue;
-            }
-
-            // the run's units of tile c.t, [wa, c.w], are summed
-            const double v = (double)hi + (double)lo;
-            if (grp == 1u) xchg[row] = v;
-            if (!epi_bar_and(ok)) break;
-            CYC_LAP(1);
-            if (grp == 0u) {
-                const uint32_t t = c.t, t_begin = t * upt, j = c.j, rt = c.rt;
-                const uint32_t seg_first = max(u0, t_begin), wa = seg_first - t_begin;
-                double v0 = kUp ? v : v + xchg[row], v1 = kUp ? xchg[row] : 0.0;
-                bool finish = (wa == 0u && tile_ends);
-                if (!finish) {
-                    // part of the tile's K range: leave the partial sums, count the arrival
-                    const uint32_t slot = (seg_first == u0) ? 0u : 1u;
-                    double *p = partials + (size_t)(cta * 2u + slot) * mats * 128u + row;
-                    p[0] = v0;
-                    if (kUp) p[128] = v1;
-                    __threadfence();
-                    group_bar_sync();
-                    if (row == 0) {
-                        const uint32_t c_first = (uint32_t)((((uint64_t)t_begin + 1u) * G - 1u) / total);
-                        const uint32_t c_last = (uint32_t)((((uint64_t)t_begin + upt) * G - 1u) / total);
-                        unsigned int *cnt = counters + (kUp ? kUpCounter0 : kDownCounter0) + t;
-                        const bool last = atomicAdd(cnt, 1u) == c_last - c_first;
-                        if (last) *cnt = 0u;  // ready for the next launch
-                        epi_info[0] = last ? 1u : 0u;
-                        epi_info[1] = c_first;
-                        epi_info[2] = c_last;
-                    }
-                    group_bar_sync();
-                    finish = epi_info[0] != 0u;
-                    if (finish) {
-                        __threadfence();
-                        const uint32_t c_first = epi_info[1], c_last = epi_info[2];
-                        v0 = 0.0;
-                        v1 = 0.0;
-                        for (uint32_t cc = c_first; cc <= c_last; ++cc) {  // K order
-                            const uint32_t sl = ((uint32_t)(total * cc / G) >= t_begin) ? 0u : 1u;
-                            const double *q = partials + (size_t)(cc * 2u + sl) * mats * 128u + row;
-                            v0 += __ldcg(q);
-                            if (kUp) v1 += __ldcg(q + 128);
+        uint32_t i = 0;
+        for (uint32_t ph = 0; ph < 2 && ok; ++ph) {
+            const PhaseShape &ps = ph ? PD : PU;
+            const Run &run = ph ? RD : RU;
+            if (!run.n) continue;
+            if (!ph) {
+                store_digit_scales(tmem + kSfbCol0, sE, up_slots, PU.K, PU.sfb_cols, warp, lane);
+                fence_before();
+                mbar_arrive(bar(kBarDigitsUp));
+            } else {
+                // The hidden vectors of this run's jobs: wait until every up tile of them is finished,
+                // then write their digit rows (the token's digits are no longer read: every MMA of
+                // the up phase has completed before its accumulator was read above).
+                if (tid == 0) {
+                    for (uint32_t j = RD.job_first; j <= RD.job_last && ok; ++j) {
+                        uint32_t tries = 0;
+                        while (ld_acquire(h_ready + j) < PU.tpj) {
+                            if (++tries > kSpinGlobal || abort_flag) {
+                                abort_flag = 1;
+                                ok = false;
+                                break;
+                            }
+                            __nanosleep(100);
                         }
                     }
                 }
-                if (finish) {
-                    if (kUp) {
-                        out[(size_t)j * inter + rt * 128u + row] = swiglu_limit_fast((float)v0, (float)v1);
-                    } else {
+                ok = epi_bar_and(ok);
+                if (!ok) break;
+                if (tid == 0) TRACE(6);
+                build_digits(h + (size_t)RD.job_first * inter, h + (size_t)RD.job_last * inter, down_slots, PD.K, sB,
+                             PD.b_stride, sE, tid, 2u * kEpiGroup);
+                asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+                epi_bar_sync();  // every block exponent is written
+                store_digit_scales(tmem + kSfbCol0, sE, down_slots, PD.K, PD.sfb_cols, warp, lane);
+                fence_before();
+                mbar_arrive(bar(kBarDigitsDown));
+            }
+            float hi = 0.0f, lo = 0.0f;  // hi + lo: this group's sum over the tile's units, to about 48 bits
+            UnitCursor c = cursor_at(run.u0, ps.upt, ps.tpj);
+            for (uint32_t l = 0; l < run.n; ++l, ++i) {
+                const uint32_t s = i % kRing;
+                if ((c.w & 1u) == grp) {
+                    ok = __all_sync(0xffffffffu, ok && mbar_wait(bar(kBarDone + s), (i / kRing) & 1u, &abort_flag));
+                    if (ok) {
+                        fence_after();
+                        float a[8];
+                        tmem_ld8(lane_base + s * 16u, a);
+                        fence_before();
+                        mbar_arrive(bar(kBarAccFree + s));
+#pragma unroll
+                        for (int jj = 0; jj < 8; ++jj) {  // low digits first
+                            float e;
+                            two_sum(hi, a[jj], hi, e);
+                            lo = __fadd_rn(lo, e);
+                        }
+                    }
+                }
+                const bool tile_ends = c.w + 1u == ps.upt;
+                if (!tile_ends && l + 1u != run.n) {
+                    cursor_advance(c, 1, ps.upt, ps.tpj);
+                    continue;
+                }
+
+                // the run's units of tile c.t, [wa, c.w], are summed
+                const double v = (double)hi + (double)lo;
+                if (grp == 1u) xchg[row] = v;
+                if (!epi_bar_and(ok)) {
+                    ok = false;
+                    break;
+                }
+                if (grp == 0u) {
+                    const uint32_t t = c.t, t_begin = t * ps.upt, j = c.j, rt = c.rt;
+                    const uint32_t seg_first = max(run.u0, t_begin), wa = seg_first - t_begin;
+                    double v0 = ph ? v + xchg[row] : v, v1 = ph ? 0.0 : xchg[row];
+                    bool finish = (wa == 0u && tile_ends);
+                    double *const part = partials + (ph ? (size_t)gridDim.x * 2u * 2u * 128u : 0u);
+                    if (!finish) {
+                        // part of the tile's K range: leave the partial sums, count the arrival
+                        const uint32_t slot = (seg_first == run.u0) ? 0u : 1u;
+                        double *p = part + (size_t)(cta * 2u + slot) * 2u * 128u + row;
+                        p[0] = v0;
+                        if (!ph) p[128] = v1;
+                        __threadfence();
+                        group_bar_sync();
+                        if (row == 0) {
+                            const uint32_t c_first = (uint32_t)((((uint64_t)t_begin + 1u) * run.G - 1u) / run.total);
+                            const uint32_t c_last = (uint32_t)((((uint64_t)t_begin + ps.upt) * run.G - 1u) / run.total);
+                            unsigned int *cnt = counters + (ph ? kDownCounter0 : kUpCounter0) + t;
+                            const bool last = atomicAdd(cnt, 1u) == c_last - c_first;
+                            if (last) *cnt = 0u;  // ready for the next launch
+                            epi_info[0] = last ? 1u : 0u;
+                            epi_info[1] = c_first;
+                            epi_info[2] = c_last;
+                        }
+                        group_bar_sync();
+                        finish = epi_info[0] != 0u;
+                        if (finish) {
+                            __threadfence();
+                            const uint32_t c_first = epi_info[1], c_last = epi_info[2];
+                            v0 = 0.0;
+                            v1 = 0.0;
+                            for (uint32_t cc = c_first; cc <= c_last; ++cc) {  // K order
+                                const uint32_t sl = ((uint32_t)(run.total * cc / run.G) >= t_begin) ? 0u : 1u;
+                                const double *q = part + (size_t)(cc * 2u + sl) * 2u * 128u + row;
+                                v0 += __ldcg(q);
+                                if (!ph) v1 += __ldcg(q + 128);
+                            }
+                        }
+                    }
+                    if (finish && !ph) {
+                        h[(size_t)j * inter + rt * 128u + row] = swiglu_limit_fast((float)v0, (float)v1);
+                        __threadfence();
+                        group_bar_sync();
+                        if (row == 0) atomicAdd(h_ready + j, 1u);  // one more tile of job j's hidden vector
+                    } else if (finish) {
                         const uint32_t n = rt * 128u + row, tk = tab.jobs[j].token;
-                        out[(size_t)tab.jobs[j].out_index * hidden + n] = (float)v0;
+                        d[(size_t)tab.jobs[j].out_index * hidden + n] = (float)v0;
                         if (y) {
                             // Ordered mix (examples/s14_vulkan_numeric.rs:936-946) by whoever finishes the
                             // token's last job of these 128 rows: acc = 0; acc += w * d in route order;
@@ -573,7 +632,7 @@ k_expert_umma(const JobTable *__restrict__ dev_table, const __grid_constant__ Jo
                                 float acc = 0.0f;
                                 for (uint32_t jj = j0; jj < j1; ++jj) {
                                     const Job &o = tab.jobs[tab.token_jobs[jj]];
-                                    const float dv = __ldcg(out + (size_t)o.out_index * hidden + n);
+                                    const float dv = __ldcg(d + (size_t)o.out_index * hidden + n);
                                     acc = o.is_shared ? __fadd_rn(acc, dv) : __fadd_rn(acc, __fmul_rn(o.weight, dv));
                                 }
                                 y[(size_t)tk * hidden + n] = acc;
@@ -581,16 +640,12 @@ k_expert_umma(const JobTable *__restrict__ dev_table, const __grid_constant__ Jo
                         }
                     }
                 }
+                // xchg and epi_info are rewritten only after every epilogue thread has passed this point
+                epi_bar_sync();
+                hi = 0.0f;
+                lo = 0.0f;
+                cursor_advance(c, 1, ps.upt, ps.tpj);
             }
-            // xchg and epi_info are rewritten only after every epilogue thread has passed this point
-            epi_bar_sync();
-            hi = 0.0f;
-            lo = 0.0f;
-            cursor_advance(c, 1, upt, tpj);
-        }
-        if (tid == 0) {
-            CYC_LAP(3);
-            CYC_STORE(4, 4);
         }
     }
 
@@ -598,16 +653,30 @@ k_expert_umma(const JobTable *__restrict__ dev_table, const __grid_constant__ Jo
     fence_before();
     __syncthreads();
     if (tid == 0) TRACE(10);
-    if (tid == 0 && abort_flag) atomicExch(status, kUp ? 0x5501u : 0x5502u);
+    if (tid == 0) {
+        if (abort_flag) atomicExch(status, 0x5501u);
+        // the last CTA to leave puts the hidden vectors' counters back to zero for the next launch
+        __threadfence();
+        unsigned int *exit_count = counters + kExitCounter;
+        if (atomicAdd(exit_count, 1u) == gridDim.x - 1u) {
+            for (uint32_t j = 0; j < n_jobs; ++j) h_ready[j] = 0u;
+            *exit_count = 0u;
+        }
+    }
     if (warp == kMmaWarp0) {
         __syncwarp();
         asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(kTmemCols) : "memory");
     }
 }
 
-size_t umma_smem_bytes(bool up, uint32_t hidden, uint32_t inter) {
-    const uint32_t K = up ? hidden : inter;
-    return (size_t)kRing * (kStageA + kStageSf) + (size_t)kDigitSlots * ((K >> 8) * 2048u + (K >> 7) * 256u + 256u);
+// Bytes of the digit tiles: two hidden vectors in the down phase, one token (two in a block of
+// several tokens) in the up phase.
+size_t digit_tile_bytes(uint32_t n_tokens, uint32_t hidden, uint32_t inter) {
+    const size_t up = (size_t)(n_tokens > 1u ? 2u : 1u) * (hidden >> 8) * 2048u, down = (size_t)2u * (inter >> 8) * 2048u;
+    return up > down ? up : down;
+}
+size_t umma_smem_bytes(uint32_t n_tokens, uint32_t hidden, uint32_t inter) {
+    return (size_t)kRing * (kStageA + kStageSf) + digit_tile_bytes(n_tokens, hidden, inter);
 }
 
 template <class Kernel, class... Args>
@@ -627,24 +696,18 @@ cudaError_t launch_pdl(Kernel kernel, dim3 grid, dim3 block, size_t smem, cudaSt
 
 constexpr size_t kMaxSmem = 227u * 1024u;  // per CTA, static + dynamic
 
-// Largest dynamic size each kernel may ask for (the limit minus its static part); 0 on failure.
-size_t g_dynamic_limit[2] = {0, 0};
-
-template <class Kernel>
-size_t configure(Kernel kernel) {
-    cudaFuncAttributes fa;
-    if (cudaFuncGetAttributes(&fa, kernel) != cudaSuccess) return 0;
-    const size_t most = kMaxSmem - fa.sharedSizeBytes;
-    if (cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)most) != cudaSuccess) return 0;
-    return most;
-}
+// Largest dynamic size the kernel may ask for (the limit minus its static part); 0 on failure.
+size_t g_dynamic_limit = 0;
 
 void configure_once() {
     static bool configured = false;
     if (configured) return;
-    g_dynamic_limit[0] = configure(k_expert_umma<false>);
-    g_dynamic_limit[1] = configure(k_expert_umma<true>);
     configured = true;
+    cudaFuncAttributes fa;
+    if (cudaFuncGetAttributes(&fa, k_moe_layer_umma) != cudaSuccess) return;
+    const size_t most = kMaxSmem - fa.sharedSizeBytes;
+    if (cudaFuncSetAttribute(k_moe_layer_umma, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)most) != cudaSuccess) return;
+    g_dynamic_limit = most;
 }
 
 }  // namespace
@@ -656,29 +719,21 @@ size_t umma_partials_bytes(int sm_count) {
 
 bool umma_layer_ok(int sm_count, uint32_t n_tokens, uint32_t n_jobs_max, uint32_t hidden, uint32_t inter) {
     if (n_tokens == 0u || n_tokens > kMaxTokens || n_jobs_max == 0u || (int)n_jobs_max > sm_count) return false;
-    if ((hidden & 255u) || (inter & 255u) || hidden < 256u || inter < 256u) return false;
+    if ((hidden & 511u) || (inter & 511u) || hidden < 512u || inter < 512u) return false;
     if (n_jobs_max * (inter >> 7) > kMaxTiles || n_jobs_max * (hidden >> 7) > kMaxTiles) return false;
-    if ((hidden >> 7) > kMaxRowTiles || hidden > kMaxK || inter > kMaxK) return false;
+    if ((hidden >> 7) > kMaxRowTiles || hidden > kMaxK || inter > kMaxK || n_jobs_max > kMaxJobs) return false;
     configure_once();
-    return umma_smem_bytes(true, hidden, inter) <= g_dynamic_limit[1] &&
-           umma_smem_bytes(false, hidden, inter) <= g_dynamic_limit[0];
+    return umma_smem_bytes(n_tokens, hidden, inter) <= g_dynamic_limit;
 }
 
-cudaError_t launch_up_umma(cudaStream_t st, int sm_count, const JobTable *dev, const JobTable &param,
-                           const float *x, float *h, double *partials, unsigned int *counters,
-                           uint32_t *status, uint32_t hidden, uint32_t inter, bool after_router) {
+cudaError_t launch_moe_layer_umma(cudaStream_t st, int sm_count, const JobTable *dev, const JobTable &param,
+                                  uint32_t n_tokens, const float *x, float *h, float *d, float *y, double *partials,
+                                  unsigned int *counters, uint32_t *status, uint32_t hidden, uint32_t inter,
+                                  bool after_router) {
     configure_once();
-    return launch_pdl(k_expert_umma<true>, dim3(sm_count), dim3(kThreads), umma_smem_bytes(true, hidden, inter), st,
-                      after_router, dev, param, x, h, (float *)nullptr, partials, counters, status, hidden, inter);
-}
-
-cudaError_t launch_down_umma(cudaStream_t st, int sm_count, const JobTable *dev, const JobTable &param,
-                             const float *h, float *d, float *y, double *partials, unsigned int *counters,
-                             uint32_t *status, uint32_t hidden, uint32_t inter) {
-    configure_once();
-    double *part_down = partials + (size_t)sm_count * 2 * 2 * 128;
-    return launch_pdl(k_expert_umma<false>, dim3(sm_count), dim3(kThreads), umma_smem_bytes(false, hidden, inter), st,
-                      true, dev, param, h, d, y, part_down, counters, status, hidden, inter);
+    return launch_pdl(k_moe_layer_umma, dim3(sm_count), dim3(kThreads), umma_smem_bytes(n_tokens, hidden, inter), st,
+                      after_router, dev, param, x, h, d, y, partials, counters, status, hidden, inter,
+                      (uint32_t)digit_tile_bytes(n_tokens, hidden, inter));
 }
 
 }  // namespace s14
