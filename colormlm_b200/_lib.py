@@ -125,9 +125,8 @@ SIGNATURES = {
     "s14_shape_mxfp4_scale_bytes": (_I32, [MatvecShape, _P(_U64)]),
     "s14_shape_fp8_weight_bytes": (_I32, [MatvecShape, _P(_U64)]),
     "s14_shape_fp8_scale_bytes": (_I32, [MatvecShape, _P(_U64)]),
-    "s14_mxfp4_scales_to_page_order": (_I32, [_U32, _U32, _VP, _VP]),
-    "s14_mxfp4_scales_from_page_order": (_I32, [_U32, _U32, _VP, _VP]),
     "s14_mxfp4_expert_page_from_tensors": (_I32, [_U32, _U32, _VP, _VP]),
+    "s14_mxfp4_expert_page_to_tensors": (_I32, [_U32, _U32, _VP, _VP]),
     "s14_validate_ue8m0_codes": (_I32, [_VP, _U64, _P(_U64)]),
     "s14_validate_e4m3fn_codes": (_I32, [_VP, _U64, _P(_U64)]),
     "s14_bind_mxfp4": (_I32, [_VP, MatvecShape, _P(Buffer), _P(Buffer), _P(Buffer), _P(Buffer),

@@ -71,8 +71,8 @@ struct s14_ctx {
     unsigned int *counters = nullptr;  // [kCtxCounters] arrival counters of the fused kernels, all zero at rest
     int32_t *ids_stage = nullptr;  // [8] route ids / weights staging of the host-buffer call
     float *weights_stage = nullptr;
-    UmmaScratch umma{nullptr, nullptr};  // scratch of the tcgen05 phases
-    bool use_umma = true;                // S14_TENSOR_PATH=mma_sync in the environment turns them off
+    UmmaScratch umma{nullptr, nullptr};  // scratch of the tcgen05 layer kernel
+    bool use_umma = true;                // S14_TENSOR_PATH=off in the environment turns it off
     const UmmaScratch *umma_scratch() const { return use_umma ? &umma : nullptr; }
 };
 
@@ -111,9 +111,9 @@ extern "C" int32_t s14_ctx_create(int32_t device, s14_ctx **out) {
     CUDA_OK(cudaMemset(ctx->counters, 0, sizeof(unsigned int) * kCtxCounters));
     CUDA_OK(cudaMalloc(&ctx->ids_stage, sizeof(int32_t) * 8));
     CUDA_OK(cudaMalloc(&ctx->weights_stage, sizeof(float) * 8));
-    CUDA_OK(cudaMalloc(&ctx->umma.partials, umma_partials_bytes(ctx->sm_count)));
+    CUDA_OK(cudaMalloc(&ctx->umma.partials, umma_partials_bytes()));
     ctx->umma.status = ctx->status;
-    if (const char *path = getenv("S14_TENSOR_PATH")) ctx->use_umma = strcmp(path, "mma_sync") != 0;
+    if (const char *path = getenv("S14_TENSOR_PATH")) ctx->use_umma = strcmp(path, "off") != 0;
     for (auto &e : ctx->marks.ev) CUDA_OK(cudaEventCreate(&e));
     *out = ctx.release();
     return S14_OK;
@@ -238,26 +238,18 @@ SHAPE_BYTES_FN(s14_shape_mxfp4_scale_bytes, mxfp4_scale_bytes)
 SHAPE_BYTES_FN(s14_shape_fp8_weight_bytes, fp8_weight_bytes)
 SHAPE_BYTES_FN(s14_shape_fp8_scale_bytes, fp8_scale_bytes)
 
-extern "C" int32_t s14_mxfp4_scales_to_page_order(uint32_t n, uint32_t k, const uint8_t *row_major,
-                                                  uint8_t *page_order) {
-    S14_TRY
-    mxfp4_scales_to_page_order(n, k, row_major, page_order);
-    return S14_OK;
-    S14_CATCH
-}
-
-extern "C" int32_t s14_mxfp4_scales_from_page_order(uint32_t n, uint32_t k, const uint8_t *page_order,
-                                                    uint8_t *row_major) {
-    S14_TRY
-    mxfp4_scales_from_page_order(n, k, page_order, row_major);
-    return S14_OK;
-    S14_CATCH
-}
-
 extern "C" int32_t s14_mxfp4_expert_page_from_tensors(uint32_t hidden, uint32_t inter, const uint8_t *tensor_page,
                                                       uint8_t *page) {
     S14_TRY
     mxfp4_expert_page_from_tensors(hidden, inter, tensor_page, page);
+    return S14_OK;
+    S14_CATCH
+}
+
+extern "C" int32_t s14_mxfp4_expert_page_to_tensors(uint32_t hidden, uint32_t inter, const uint8_t *page,
+                                                    uint8_t *tensor_page) {
+    S14_TRY
+    mxfp4_expert_page_to_tensors(hidden, inter, page, tensor_page);
     return S14_OK;
     S14_CATCH
 }

@@ -87,12 +87,31 @@ struct PageView {
     const uint8_t *w1, *w3, *w2, *s1, *s3, *s2;
 };
 
-// The MXFP4 scale arrays of a page are stored atom by atom, in the order the block-scaled
-// tensor-core instructions take them into tensor memory: an atom holds the codes of 128 rows x
-// 4 scale blocks (512 B), atoms of a 128-row tile follow each other along K.  The four codes of
-// row n, blocks 4a..4a+3 of an [N, K] matrix are the 32-bit word at this byte offset.
-__device__ __forceinline__ size_t scale_word_offset(uint32_t n, uint32_t a, uint32_t k) {
-    return ((size_t)(n >> 7) * (k >> 7) + a) * 512u + (n & 31u) * 16u + ((n >> 5) & 3u) * 4u;
+// Byte order inside an MXFP4 expert page (w1 | w3 | w2 | s13 | s2).  The unit of work of the
+// tcgen05 kernel is a slice of 64 intermediate elements of one expert: the 64 rows of w1 and of
+// w3 that produce them (one 128-row MMA tile) and the 64 columns of w2 that consume them.
+//   w1, w3  [inter, hidden/2] bytes, row-major, as the checkpoint has them.
+//   w2      by slice s and row tile rt: 128 rows x 32 B (the 64 codes of the slice), 4 KB per
+//           (s, rt), row tiles of a slice next to each other -- a slice's columns are one
+//           contiguous run of hidden * 32 bytes.
+//   s13     the scale codes of w1 and w3 by slice s and K-atom a (four scale blocks): 512 B in
+//           the order tensor memory takes them, MMA row m = the slice's w1 row m (m < 64) or w3
+//           row m - 64: byte (m % 32) * 16 + (m / 32) * 4 + block % 4.
+//   s2      the scale codes of w2 by slice pair p and row tile rt: 512 B, row r of the tile at
+//           (r % 32) * 16 + (r / 32) * 4, blocks 4p..4p+3 (slice 2p: 0 and 1, slice 2p+1: 2 and 3).
+// hidden and inter are multiples of 128.  The sixteen code bytes (one scale block) of w2 row n:
+__device__ __forceinline__ size_t w2_block_offset(uint32_t n, uint32_t kb, uint32_t hidden) {
+    return (((size_t)(kb >> 1) * (hidden >> 7) + (n >> 7)) * 128u + (n & 127u)) * 32u + (kb & 1u) * 16u;
+}
+// the scale code of row i, block kb of w1 (mat 0) or w3 (mat 1), inside s13
+__device__ __forceinline__ size_t up_scale_offset(uint32_t mat, uint32_t i, uint32_t kb, uint32_t hidden) {
+    const uint32_t m = (i & 63u) + mat * 64u;
+    return ((size_t)(i >> 6) * (hidden >> 7) + (kb >> 2)) * 512u + (m & 31u) * 16u + (m >> 5) * 4u + (kb & 3u);
+}
+// the scale code of row n, block kb of w2, inside s2
+__device__ __forceinline__ size_t down_scale_offset(uint32_t n, uint32_t kb, uint32_t hidden) {
+    const uint32_t r = n & 127u;
+    return ((size_t)(kb >> 2) * (hidden >> 7) + (n >> 7)) * 512u + (r & 31u) * 16u + (r >> 5) * 4u + (kb & 3u);
 }
 
 __device__ __forceinline__ PageView page_view(const uint8_t *page, uint32_t kind, uint32_t hidden,

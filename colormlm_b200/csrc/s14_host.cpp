@@ -76,41 +76,56 @@ void validate_ue8m0_codes(const uint8_t *codes, uint64_t len) {
             throw CodeError("UE8M0 scale contains 0xff NaN at byte " + std::to_string(i), i);
 }
 
-uint64_t mxfp4_scale_page_offset(uint32_t n, uint32_t kb, uint32_t k) {
-    return ((uint64_t)(n >> 7) * (k >> 7) + (kb >> 2)) * 512u + (n & 31u) * 16u + ((n >> 5) & 3u) * 4u + (kb & 3u);
+uint64_t mxfp4_page_w2_offset(uint32_t n, uint32_t kb, uint32_t hidden) {
+    return (((uint64_t)(kb >> 1) * (hidden >> 7) + (n >> 7)) * 128u + (n & 127u)) * 32u + (kb & 1u) * 16u;
+}
+uint64_t mxfp4_page_up_scale_offset(uint32_t mat, uint32_t i, uint32_t kb, uint32_t hidden) {
+    const uint32_t m = (i & 63u) + mat * 64u;
+    return ((uint64_t)(i >> 6) * (hidden >> 7) + (kb >> 2)) * 512u + (m & 31u) * 16u + (m >> 5) * 4u + (kb & 3u);
+}
+uint64_t mxfp4_page_down_scale_offset(uint32_t n, uint32_t kb, uint32_t hidden) {
+    const uint32_t r = n & 127u;
+    return ((uint64_t)(kb >> 2) * (hidden >> 7) + (n >> 7)) * 512u + (r & 31u) * 16u + (r >> 5) * 4u + (kb & 3u);
 }
 
-static void check_scale_shape(uint32_t n, uint32_t k) {
-    if (n == 0 || k == 0 || (n & 127u) || (k & 127u))
-        throw ContractError("MXFP4 page scales: rows and K must be non-zero multiples of 128");
+static void check_page_shape(uint32_t hidden, uint32_t inter, const void *a, const void *b) {
+    if (hidden == 0 || inter == 0 || (hidden & 127u) || (inter & 127u))
+        throw ContractError("MXFP4 expert page: hidden and intermediate must be non-zero multiples of 128");
+    if (!a || !b) throw ContractError("MXFP4 expert page: NULL buffer");
 }
 
-void mxfp4_scales_to_page_order(uint32_t n, uint32_t k, const uint8_t *row_major, uint8_t *page_order) {
-    check_scale_shape(n, k);
-    if (!row_major || !page_order) throw ContractError("MXFP4 page scales: NULL buffer");
-    const uint32_t groups = k >> 5;
-    for (uint32_t r = 0; r < n; ++r)
-        for (uint32_t kb = 0; kb < groups; kb += 4)
-            std::memcpy(page_order + mxfp4_scale_page_offset(r, kb, k), row_major + (size_t)r * groups + kb, 4);
-}
-
-void mxfp4_scales_from_page_order(uint32_t n, uint32_t k, const uint8_t *page_order, uint8_t *row_major) {
-    check_scale_shape(n, k);
-    if (!row_major || !page_order) throw ContractError("MXFP4 page scales: NULL buffer");
-    const uint32_t groups = k >> 5;
-    for (uint32_t r = 0; r < n; ++r)
-        for (uint32_t kb = 0; kb < groups; kb += 4)
-            std::memcpy(row_major + (size_t)r * groups + kb, page_order + mxfp4_scale_page_offset(r, kb, k), 4);
+// forward = true: tensors -> page order; false: page order -> tensors
+static void reorder_page(uint32_t hidden, uint32_t inter, const uint8_t *src, uint8_t *dst, bool forward) {
+    const size_t wb = (size_t)hidden * inter / 2, sb = (size_t)hidden * inter / 32;
+    std::memcpy(dst, src, 2 * wb);  // w1, w3 as they are
+    const uint8_t *w2s = src + 2 * wb, *sc_s = src + 3 * wb;
+    uint8_t *w2d = dst + 2 * wb, *sc_d = dst + 3 * wb;
+    const uint32_t kb_down = inter >> 5, kb_up = hidden >> 5;
+    for (uint32_t n = 0; n < hidden; ++n)
+        for (uint32_t kb = 0; kb < kb_down; ++kb) {
+            const size_t t = (size_t)n * (inter >> 1) + (size_t)kb * 16u, p = mxfp4_page_w2_offset(n, kb, hidden);
+            std::memcpy(forward ? w2d + p : w2d + t, forward ? w2s + t : w2s + p, 16);
+            const size_t ts = 2 * sb + (size_t)n * kb_down + kb, ps = 2 * sb + mxfp4_page_down_scale_offset(n, kb, hidden);
+            if (forward) sc_d[ps] = sc_s[ts];
+            else sc_d[ts] = sc_s[ps];
+        }
+    for (uint32_t mat = 0; mat < 2; ++mat)
+        for (uint32_t i = 0; i < inter; ++i)
+            for (uint32_t kb = 0; kb < kb_up; ++kb) {
+                const size_t ts = (size_t)mat * sb + (size_t)i * kb_up + kb, ps = mxfp4_page_up_scale_offset(mat, i, kb, hidden);
+                if (forward) sc_d[ps] = sc_s[ts];
+                else sc_d[ts] = sc_s[ps];
+            }
 }
 
 void mxfp4_expert_page_from_tensors(uint32_t hidden, uint32_t inter, const uint8_t *tensor_page, uint8_t *page) {
-    check_scale_shape(inter, hidden);
-    if (!tensor_page || !page) throw ContractError("MXFP4 expert page: NULL buffer");
-    const size_t wb = (size_t)hidden * inter / 2, sb = (size_t)hidden * inter / 32;
-    std::memcpy(page, tensor_page, 3 * wb);
-    mxfp4_scales_to_page_order(inter, hidden, tensor_page + 3 * wb, page + 3 * wb);           // s1: [inter, hidden]
-    mxfp4_scales_to_page_order(inter, hidden, tensor_page + 3 * wb + sb, page + 3 * wb + sb);  // s3
-    mxfp4_scales_to_page_order(hidden, inter, tensor_page + 3 * wb + 2 * sb, page + 3 * wb + 2 * sb);  // s2: [hidden, inter]
+    check_page_shape(hidden, inter, tensor_page, page);
+    reorder_page(hidden, inter, tensor_page, page, true);
+}
+
+void mxfp4_expert_page_to_tensors(uint32_t hidden, uint32_t inter, const uint8_t *page, uint8_t *tensor_page) {
+    check_page_shape(hidden, inter, page, tensor_page);
+    reorder_page(hidden, inter, page, tensor_page, false);
 }
 
 void validate_e4m3fn_codes(const uint8_t *codes, uint64_t len) {

@@ -43,17 +43,23 @@ struct S14MatvecShape {
 // storage_bytes (s14_vulkan.rs:128-130): byte counts rounded up to whole 32-bit words.
 inline uint64_t storage_bytes(uint64_t logical) { return (logical + 3) / 4 * 4; }
 
-// Page order of MXFP4 scale codes.  The checkpoint's tensor is [n, k/32] row-major; an expert page
-// holds it atom by atom, the order the sm_100 block-scaled MMA takes scales into tensor memory:
-// atom (n / 128, kb / 4) is 512 bytes, the code of row n, scale block kb sits at byte
-// (n % 32) * 16 + ((n % 128) / 32) * 4 + kb % 4 of it, atoms of a 128-row tile follow each other
-// along k.  n and k must be multiples of 128.  No counterpart in the reference, which fixes no page layout.
-uint64_t mxfp4_scale_page_offset(uint32_t n, uint32_t kb, uint32_t k);
-void mxfp4_scales_to_page_order(uint32_t n, uint32_t k, const uint8_t *row_major, uint8_t *page_order);
-void mxfp4_scales_from_page_order(uint32_t n, uint32_t k, const uint8_t *page_order, uint8_t *row_major);
-// w1 | w3 | w2 | s1 | s3 | s2 with the tensors as the checkpoint has them -> the same page with the
-// three scale arrays in page order (src and dst must not overlap).
+// Byte order of an MXFP4 expert page, w1 | w3 | w2 | s13 | s2.  A page made of the six checkpoint
+// tensors in their own ABI (w1 | w3 | w2 | s1 | s3 | s2, weights [N, K/2] bytes, scales [N, K/32]
+// codes) is the *tensor page*; the page the GPU reads keeps w1 and w3 and stores the rest by slice
+// of 64 intermediate elements, the unit of work of the tcgen05 kernel:
+//   w2   (slice s, row tile rt): 128 rows x 32 bytes -- a slice's columns are contiguous;
+//   s13  (slice s, K-atom a): the codes of the slice's 64 w1 rows and 64 w3 rows for four scale
+//        blocks, 512 bytes in the order tensor memory takes them;
+//   s2   (slice pair p, row tile rt): the codes of 128 rows of w2 for blocks 4p..4p+3, same order.
+// hidden and inter must be multiples of 128.  No counterpart in the reference, which fixes no page
+// layout.  The three offset functions give the position of the 16 code bytes of w2 row n, block
+// kb (inside w2), of a w1 / w3 scale code (inside s13) and of a w2 scale code (inside s2).
+uint64_t mxfp4_page_w2_offset(uint32_t n, uint32_t kb, uint32_t hidden);
+uint64_t mxfp4_page_up_scale_offset(uint32_t mat, uint32_t i, uint32_t kb, uint32_t hidden);
+uint64_t mxfp4_page_down_scale_offset(uint32_t n, uint32_t kb, uint32_t hidden);
+// src and dst must not overlap.
 void mxfp4_expert_page_from_tensors(uint32_t hidden, uint32_t inter, const uint8_t *tensor_page, uint8_t *page);
+void mxfp4_expert_page_to_tensors(uint32_t hidden, uint32_t inter, const uint8_t *page, uint8_t *tensor_page);
 
 // validate_ue8m0_codes / validate_e4m3fn_codes (s14_vulkan.rs:143-156).
 void validate_ue8m0_codes(const uint8_t *codes, uint64_t len);

@@ -58,27 +58,19 @@ int launch_moe_layer(cudaStream_t st, uint32_t mode, int sm_count, const JobTabl
                      uint32_t hidden, uint32_t inter, const float *x, float *h, float *d, float *y,
                      cudaError_t *err, const KernelMarks *km = nullptr, bool all_mxfp4 = false,
                      unsigned int *counters = nullptr, const struct UmmaScratch *umma = nullptr);
-// Scratch of the tcgen05 phases (s14_moe_umma.cu): F64 partial sums of tiles whose K range is
-// shared between CTAs (umma_partials_bytes) and the device status word a timed-out wait sets.
+// Scratch of the tcgen05 layer kernel (s14_moe_umma.cu): every item's share of its expert's output
+// (umma_partials_bytes) and the device status word a timed-out wait sets.
 struct UmmaScratch {
-    double *partials;
+    float *partials;
     uint32_t *status;
 };
-size_t umma_partials_bytes(int sm_count);
-// Every job an MXFP4 page, hidden and inter multiples of 512 that fit shared and tensor memory.
+size_t umma_partials_bytes();
+// One token, every job an MXFP4 page, hidden and inter multiples of 512 that fit shared and tensor memory.
 bool umma_layer_ok(int sm_count, uint32_t n_tokens, uint32_t n_jobs_max, uint32_t hidden, uint32_t inter);
-// Both phases and the mix in one launch (y == nullptr: the caller mixes).
+// Both phases and the mix in one launch (y == nullptr: the expert outputs go to d, the caller mixes).
 cudaError_t launch_moe_layer_umma(cudaStream_t st, int sm_count, const JobTable *dev, const JobTable &param,
-                                  uint32_t n_tokens, const float *x, float *h, float *d, float *y, double *partials,
-                                  unsigned int *counters, uint32_t *status, uint32_t hidden, uint32_t inter,
-                                  bool after_router);
-// Warp-level tensor-core pairwise phases (s14_moe_mma.cu); every job must be an MXFP4 page.
-cudaError_t launch_up_mma(cudaStream_t st, int sm_count, const JobTable *dev, const JobTable &param,
-                          const float *x, float *h, uint32_t hidden, uint32_t inter, uint32_t n_tokens,
-                          bool after_router);
-cudaError_t launch_down_mma(cudaStream_t st, int sm_count, const JobTable *dev, const JobTable &param,
-                            const float *h, float *d, float *y, unsigned int *counters, uint32_t hidden,
-                            uint32_t inter, uint32_t n_jobs);
+                                  const float *x, float *d, float *y, float *partials, unsigned int *counters,
+                                  uint32_t *status, uint32_t hidden, uint32_t inter, bool after_router);
 int launch_router(cudaStream_t st, const s14_router_desc &r, float *scores, float *select,
                   JobTable *table_out, const uint8_t *const *page_table, const uint8_t *shared_page,
                   uint32_t shared_kind, unsigned int *counter, cudaError_t *err,

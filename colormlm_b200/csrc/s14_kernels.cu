@@ -249,14 +249,21 @@ struct RowFrag {
     uint32_t sc[KC];
 };
 
-template <int KC>
-__device__ __forceinline__ void load_row_mxfp4(RowFrag<KC> &f, const uint8_t *w, const uint8_t *s,
-                                               uint32_t row, uint32_t lane) {
-    const uint4 *wrow = reinterpret_cast<const uint4 *>(w + (size_t)row * (KC * 512));
+// MAT: 0 = w1, 1 = w3 (rows of [inter, hidden]), 2 = w2 (rows of [hidden, inter]).
+template <int KC, int MAT>
+__device__ __forceinline__ void load_row_mxfp4(RowFrag<KC> &f, const PageView &pv, uint32_t row, uint32_t lane,
+                                               uint32_t hidden) {
 #pragma unroll
     for (int j = 0; j < KC; ++j) {
-        f.q[j] = ldg_stream(wrow + j * 32 + lane);
-        f.sc[j] = __ldg(s + scale_word_offset(row, (uint32_t)j * 8u + (lane >> 2), KC * 1024u) + (lane & 3u));
+        const uint32_t kb = (uint32_t)j * 32u + lane;
+        if (MAT < 2) {
+            const uint8_t *w = MAT ? pv.w3 : pv.w1;
+            f.q[j] = ldg_stream(reinterpret_cast<const uint4 *>(w + (size_t)row * (KC * 512)) + kb);
+            f.sc[j] = __ldg(pv.s1 + up_scale_offset(MAT, row, kb, hidden));
+        } else {
+            f.q[j] = ldg_stream(reinterpret_cast<const uint4 *>(pv.w2 + w2_block_offset(row, kb, hidden)));
+            f.sc[j] = __ldg(pv.s2 + down_scale_offset(row, kb, hidden));
+        }
     }
 }
 
@@ -330,8 +337,8 @@ k_expert_up_pairwise(const JobTable *__restrict__ dev_table,
         const Job jb = tab.jobs[tab.token_jobs[job]];
         if (jb.kind == S14_PAGE_MXFP4) {
             const PageView pv = page_view(jb.page, jb.kind, hidden, inter);
-            load_row_mxfp4<KC>(g, pv.w1, pv.s1, row, lane);
-            load_row_mxfp4<KC>(u, pv.w3, pv.s3, row, lane);
+            load_row_mxfp4<KC, 0>(g, pv, row, lane, hidden);
+            load_row_mxfp4<KC, 1>(u, pv, row, lane, hidden);
         }
     };
     auto finish = [&](const RowFrag<KC> &g, const RowFrag<KC> &u, uint32_t item) {
@@ -399,8 +406,8 @@ k_expert_down_pairwise(const JobTable *__restrict__ dev_table,
     const uint32_t step = n_warps;
     // two rows per stage, two stages in flight
     auto issue2 = [&](RowFrag<KC> &p, RowFrag<KC> &q, uint32_t r) {
-        if (r < hidden) load_row_mxfp4<KC>(p, pv.w2, pv.s2, r, lane);
-        if (r + step < hidden) load_row_mxfp4<KC>(q, pv.w2, pv.s2, r + step, lane);
+        if (r < hidden) load_row_mxfp4<KC, 2>(p, pv, r, lane, hidden);
+        if (r + step < hidden) load_row_mxfp4<KC, 2>(q, pv, r + step, lane, hidden);
     };
     auto finish2 = [&](const RowFrag<KC> &p, const RowFrag<KC> &q, uint32_t r) {
         if (r < hidden) {
@@ -428,18 +435,22 @@ k_expert_down_pairwise(const JobTable *__restrict__ dev_table,
 
 // Reference-order dot of one MXFP4 row: sequential k, (x*e)*s, separate add.
 // x is read from shared memory (every lane reads the same address: broadcast).
-__device__ __forceinline__ float dot_row_mxfp4_reference(const uint8_t *w, const uint8_t *s,
-                                                         uint32_t row, uint32_t k,
+// MAT: 0 = w1, 1 = w3, 2 = w2 of an expert page.
+template <int MAT>
+__device__ __forceinline__ float dot_row_mxfp4_reference(const PageView &pv, uint32_t row, uint32_t k, uint32_t hidden,
                                                          const float *__restrict__ xs) {
     const uint32_t groups = k >> 5;
-    const uint4 *wrow = reinterpret_cast<const uint4 *>(w + (size_t)row * (k >> 1));
+    const uint4 *wrow = reinterpret_cast<const uint4 *>((MAT == 1 ? pv.w3 : pv.w1) + (size_t)row * (k >> 1));
     float sum = 0.0f;
     for (uint32_t g4 = 0; g4 < groups; g4 += 4) {
         uint4 q[4];
         uint32_t scw;
 #pragma unroll
-        for (int j = 0; j < 4; ++j) q[j] = __ldg(wrow + g4 + j);
-        scw = __ldg(reinterpret_cast<const uint32_t *>(s + scale_word_offset(row, g4 >> 2, k)));
+        for (int j = 0; j < 4; ++j)
+            q[j] = MAT < 2 ? __ldg(wrow + g4 + j)
+                           : __ldg(reinterpret_cast<const uint4 *>(pv.w2 + w2_block_offset(row, g4 + j, hidden)));
+        scw = __ldg(reinterpret_cast<const uint32_t *>(MAT < 2 ? pv.s1 + up_scale_offset(MAT, row, g4, hidden)
+                                                               : pv.s2 + down_scale_offset(row, g4, hidden)));
 #pragma unroll
         for (int j = 0; j < 4; ++j) {
             const float sc = ue8m0_to_f32((scw >> (8 * j)) & 0xffu);
@@ -512,8 +523,8 @@ k_expert_up_reference(const JobTable *__restrict__ dev_table,
     const PageView pv = page_view(jb.page, jb.kind, hidden, inter);
     float gate, up;
     if (jb.kind == S14_PAGE_MXFP4) {
-        gate = dot_row_mxfp4_reference(pv.w1, pv.s1, row, hidden, xs);
-        up = dot_row_mxfp4_reference(pv.w3, pv.s3, row, hidden, xs);
+        gate = dot_row_mxfp4_reference<0>(pv, row, hidden, hidden, xs);
+        up = dot_row_mxfp4_reference<1>(pv, row, hidden, hidden, xs);
     } else {
         gate = dot_row_fp8_reference(pv.w1, pv.s1, row, hidden, xs);
         up = dot_row_fp8_reference(pv.w3, pv.s3, row, hidden, xs);
@@ -538,7 +549,7 @@ k_expert_down_reference(const JobTable *__restrict__ dev_table,
     if (row >= hidden) return;
     const PageView pv = page_view(jb.page, jb.kind, hidden, inter);
     const float v = (jb.kind == S14_PAGE_MXFP4)
-                        ? dot_row_mxfp4_reference(pv.w2, pv.s2, row, inter, xs)
+                        ? dot_row_mxfp4_reference<2>(pv, row, inter, hidden, xs)
                         : dot_row_fp8_reference(pv.w2, pv.s2, row, inter, xs);
     d[(size_t)jb.out_index * hidden + row] = v;
 }
@@ -939,8 +950,8 @@ int launch_moe_layer(cudaStream_t st, uint32_t mode, int sm_count, const JobTabl
                                                                        hidden, inter);
         launches += 2;
     } else if (all_mxfp4 && counters && umma && umma_layer_ok(sm_count, n_tokens, n_jobs_max, hidden, inter)) {
-        *err = launch_moe_layer_umma(st, sm_count, dev_table, param_table, n_tokens, x, h, d, y, umma->partials,
-                                     counters, umma->status, hidden, inter, dev_table != nullptr);
+        *err = launch_moe_layer_umma(st, sm_count, dev_table, param_table, x, d, y, umma->partials, counters,
+                                     umma->status, hidden, inter, dev_table != nullptr);
         launches += 1;
         if (km) {  // one kernel runs both phases and the mix: its time is booked as the up phase
             cudaEventRecord(km->ev[2], st);
@@ -948,19 +959,6 @@ int launch_moe_layer(cudaStream_t st, uint32_t mode, int sm_count, const JobTabl
             cudaEventRecord(km->ev[4], st);
         }
         return launches;
-    } else if (all_mxfp4 && counters) {
-        *err = launch_up_mma(st, sm_count, dev_table, param_table, x, h, hidden, inter, n_tokens,
-                             dev_table != nullptr);
-        if (km) cudaEventRecord(km->ev[2], st);
-        if (*err == cudaSuccess)
-            *err = launch_down_mma(st, sm_count, dev_table, param_table, h, d, y, counters, hidden, inter,
-                                   n_jobs_max);
-        launches += 2;
-        if (km) {
-            cudaEventRecord(km->ev[3], st);
-            cudaEventRecord(km->ev[4], st);
-        }
-        return launches;  // the down kernel also mixes
     } else {
         const uint32_t ctas_per_token = max(1u, (uint32_t)sm_count / n_tokens);
         switch (hidden >> 10) {

@@ -1,59 +1,75 @@
-// Pairwise-order up and down phases of a one-token MoE layer on the fifth-generation tensor
-// cores: tcgen05.mma kind::mxf4.block_scale consumes the page bytes as they are (packed E2M1,
-// one UE8M0 scale per 32 elements along K), so no thread decodes or scales a weight.
+// The pairwise-order MoE layer of one token on the fifth-generation tensor cores:
+// tcgen05.mma kind::mxf4.block_scale consumes the page bytes as they are (packed E2M1, one
+// UE8M0 scale per 32 elements along K), so no thread decodes or scales a weight.
 //
-// The matvec as a block-scaled MMA.  A = 128 weight rows x 64 K-elements per instruction, staged
-// in shared memory K-major with the 128-byte swizzle; its scales go to tensor memory with
-// tcgen05.cp.  B = the activation vector, written once per CTA as eight balanced base-8 digit
-// rows: within a scale block of 32 elements with largest magnitude < 2^E (E >= -100), every element is
-// q * 2^(E-23) with |q| <= 2^23 (rounded to nearest when it has more bits below the block's top
-// bit), q = sum_j d_j 8^j with d_j in [-4, 4] -- all of them E2M1 values -- and digit row j carries
-// the UE8M0 scale 2^(E-23+3j).  Accumulator column j therefore holds the exact digit-j share of
-// the dot product in F32; the eight columns are added in F64 and rounded once.  Measured against
-// a double-precision sum on B200: relative RMSE 1.5e-7, all of it from the 23-bit quantisation of
-// elements far below their block's largest one.  Columns 8-15 of the 16-column MMA are zero rows.
+// The matvec as a block-scaled MMA.  A = 128 weight rows x 64 K-elements per instruction; its
+// scales go to tensor memory with tcgen05.cp.  B = the activation vector as eight balanced
+// base-8 digit rows: within a scale block of 32 elements with largest magnitude < 2^E
+// (E >= -100), every element is q * 2^(E-23) with |q| <= 2^23 (rounded to nearest when it has
+// more bits below the block's top bit), q = sum_j d_j 8^j with d_j in [-4, 4] -- all of them
+// E2M1 values -- and digit row j carries the UE8M0 scale 2^(E-23+3j).  Accumulator column j
+// holds the digit-j share of the dot product in F32; the eight columns are added with
+// error-free F32 additions and rounded once.  Measured against a double-precision sum on B200:
+// relative RMSE 1.5e-7, all of it from the 23-bit quantisation of elements far below their
+// block's largest one.  Columns 8-15 of the 16-column MMA are zero rows.
 //
-// Work split.  A unit is one 128-row x 256-K stage (16 KB of codes + 1 KB of scales).  The units
-// of the launch, ordered job, row tile, K (up phase: w1 and w3 alternate, two accumulators),
-// are cut into gridDim.x equal runs, one CTA per SM.  A run that ends inside a tile leaves F64
-// partial sums in global scratch; whichever CTA arrives last at the tile's counter adds the
-// partials in K order and finishes the rows (no CTA waits for another).  Roles inside a CTA:
-// four producer warps (cp.async into an 8-stage ring, completion through mbarriers), one MMA
-// thread, four epilogue warps (tcgen05.ld, F64 sums, SwiGLU or the ordered mix).  Every mbarrier
-// wait is bounded; a wait that runs out raises the CTA's abort flag, the status word is set and
-// the CTA drains its copies, frees its tensor memory and returns.
+// Work split: by slice.  An item is (expert, 64 intermediate elements): the 64 rows of w1 and
+// the 64 rows of w3 that produce them form one 128-row MMA tile over K = hidden (up phase, one
+// accumulator: lanes 0-63 the gate, 64-127 the up projection), and the 64 columns of w2 that
+// consume them are hidden / 128 MMAs of K = 64 (down phase).  The hidden values of a slice never
+// leave the CTA: SwiGLU, digits and scales are made from the up accumulator and fed to the down
+// MMAs.  Each item leaves its contribution to the expert's output, 4 bytes per row, in global
+// scratch; when every item of the layer is done (one counter, bounded polling; the grid is one
+// CTA per SM, all resident), every CTA adds up its share of the rows in slice order and applies
+// the ordered mix.  Items are handed out in equal numbers, so the result does not depend on how.
+// The expert page stores w2 and all scales by slice for this purpose.
+//
+// Roles inside a CTA: four producer warps (cp.async into an 8-stage ring of 16 KB of codes + 2 KB
+// of scales: up units of all items first, then down stages), two MMA-issuing threads, eight
+// epilogue warps (tcgen05.ld / tcgen05.st).  Every mbarrier wait and the poll of the item
+// counter are bounded; a wait that runs out raises the CTA's abort flag, the status word is set
+// and the CTA drains its copies, frees its tensor memory and returns.
 #include "s14_device.cuh"
 
 namespace s14 {
 
 namespace {
 
-constexpr uint32_t kRing = 8;                  // stages, accumulators and scale slots in flight per CTA
-constexpr uint32_t kStageA = 128 * 128;        // 128 rows x 128 B of codes
-constexpr uint32_t kStageSf = 2 * 512;         // two scale atoms (128 rows x 4 blocks each)
-constexpr uint32_t kEpiGroup = 128;            // two epilogue groups of four warps (even / odd units of a tile)
-constexpr uint32_t kMmaWarp0 = 8;              // warps 8 and 9: one issuing thread each (even / odd units of the run)
+constexpr uint32_t kRing = 8;                  // stages in flight per CTA
+constexpr uint32_t kStageA = 128 * 128;        // 16 KB of codes: an up unit (128 rows x 256 K) or four down blocks (128 rows x 64 K each)
+constexpr uint32_t kStageSf = 4 * 512;         // scale atoms of a stage: two (up unit) or four (down stage)
+constexpr uint32_t kEpiGroup = 128;            // two epilogue groups of four warps
+constexpr uint32_t kMmaWarp0 = 8;              // warps 8 and 9: one issuing thread each
 constexpr uint32_t kProdWarp0 = 10;            // warps 10..13 copy
 constexpr uint32_t kProdThreads = 128;
-constexpr uint32_t kThreads = 512;               // warps 14 and 15 only help with the digits
-constexpr uint32_t kTmemCols = 512;            // [0,128): 8 accumulators x 16; [128,192): weight scales; [192,512): digit scales
-constexpr uint32_t kSfaCol0 = 128, kSfbCol0 = 192;
-constexpr uint32_t kDigitSlots = 2;            // activation vectors a CTA's run can need
-constexpr uint32_t kMaxBlocks = 160;           // scale blocks per activation vector (K <= 5120)
-constexpr uint32_t kMaxK = (kTmemCols - kSfbCol0) / kDigitSlots / 4 * 128;  // digit scales of both slots fit tensor memory
-constexpr uint32_t kSpin = 1u << 17;           // tries before a wait gives up
-constexpr uint32_t kMaxTiles = 2048;           // tile counters per phase
-constexpr uint32_t kUpCounter0 = 1, kDownCounter0 = 1 + kMaxTiles, kMixCounter0 = 1 + 2 * kMaxTiles;
-constexpr uint32_t kHReadyCounter0 = kMixCounter0 + kMaxTokens * 64;  // finished up tiles per job
-constexpr uint32_t kExitCounter = kHReadyCounter0 + kMaxJobs;          // CTAs that have left the kernel
-static_assert(kExitCounter < 8192, "a context allocates 8192 arrival counters");
-constexpr uint32_t kSpinGlobal = 1u << 20;     // polls (100 ns apart) of another CTA's progress before giving up
-constexpr uint32_t kMaxRowTiles = 64;             // mix counters: [token][row tile]
+constexpr uint32_t kThreads = 512;             // warps 14 and 15 only help with the digits and the final sums
+constexpr uint32_t kDRing = 2;                 // down stages whose four accumulators are in flight (one per issuing thread)
+constexpr uint32_t kItemSlots = 4;             // items a CTA can hold (digit tiles of their hidden values)
+// tensor memory columns
+constexpr uint32_t kTmemCols = 512;
+constexpr uint32_t kColD = 0;                  // kDRing x 4 accumulators x 16
+constexpr uint32_t kColU = kColD + kDRing * 64;    // 2 items x 2 issuing threads x 16
+constexpr uint32_t kColSfa = kColU + 64;       // kRing x 16: weight scales of a stage
+constexpr uint32_t kColSfbX = kColSfa + kRing * 16;  // hidden / 32: scales of the token's digit rows
+constexpr uint32_t kColSfbH = kColSfbX + 128;  // kItemSlots x 4: scales of the hidden values' digit rows
+static_assert(kColSfbH + kItemSlots * 4 <= kTmemCols, "tensor memory map");
+constexpr uint32_t kMaxHidden = 4096;          // 128 columns of token digit scales
+constexpr uint32_t kMaxBlocks = kMaxHidden / 32;
+constexpr uint32_t kSpin = 1u << 17;           // tries (a microsecond each at most) before a wait gives up
+constexpr uint32_t kSpinGlobal = 1u << 20;     // polls (100 ns apart) of the item counter before giving up
+constexpr uint32_t kItemCounter = 1, kExitCounter = 2;  // in the context's counter array ([0] is the router's)
 
-// Bar indices in the static barrier array: stage filled, unit multiplied, accumulator read,
-// digit scales in tensor memory, both issuing threads finished.
-constexpr uint32_t kBarFull = 0, kBarDone = kRing, kBarAccFree = 2 * kRing, kBarDigitsUp = 3 * kRing,
-                   kBarDigitsDown = 3 * kRing + 1, kBarFin = 3 * kRing + 2, kBars = 3 * kRing + 3;
+// Bar indices in the static barrier array.
+constexpr uint32_t kBarFull = 0;                      // stage filled (128 copying threads)
+constexpr uint32_t kBarDone = kRing;                  // the stage's MMAs have completed (the copies may reuse it)
+constexpr uint32_t kBarDFree = 2 * kRing;             // a down stage's accumulators have been read
+constexpr uint32_t kBarDDone = kBarDFree + kDRing;    // a down stage's accumulators are complete
+constexpr uint32_t kBarUDone = kBarDDone + kDRing;    // an item's up accumulators are complete
+constexpr uint32_t kBarUFree = kBarUDone + 2;         // ... has been read
+constexpr uint32_t kBarHReady = kBarUFree + 2;        // an item's hidden digits and scales are in place
+constexpr uint32_t kBarXReady = kBarHReady + kItemSlots;  // the token's digit scales are in tensor memory
+constexpr uint32_t kBarFin = kBarXReady + 1;          // both issuing threads have finished
+constexpr uint32_t kBars = kBarFin + 1;
 
 __device__ __forceinline__ uint32_t smem_u32(const void *p) {
     return (uint32_t)__cvta_generic_to_shared(p);
@@ -93,46 +109,8 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatil
     *abort_flag = 1;
     return false;
 }
-// Named barriers of the epilogue: 1 = the 128 threads of group A, 2 = both groups.
+// Named barrier 1: the 128 threads of epilogue group A.
 __device__ __forceinline__ void group_bar_sync() { asm volatile("bar.sync 1, 128;" ::: "memory"); }
-__device__ __forceinline__ void epi_bar_sync() { asm volatile("bar.sync 2, 256;" ::: "memory"); }
-__device__ __forceinline__ bool epi_bar_and(bool v) {
-    uint32_t r;
-    asm volatile(
-        "{\n.reg .pred p, q;\n"
-        "setp.ne.b32 q, %1, 0;\n"
-        "bar.red.and.pred p, 2, 256, q;\n"
-        "selp.b32 %0, 1, 0, p;\n}"
-        : "=r"(r)
-        : "r"((uint32_t)v)
-        : "memory");
-    return r != 0;
-}
-
-// Position of a unit: tile t (job j, row tile rt) and unit w of the tile.
-struct UnitCursor {
-    uint32_t t, w, j, rt;
-};
-__device__ __forceinline__ UnitCursor cursor_at(uint32_t u, uint32_t upt, uint32_t tpj) {
-    UnitCursor c;
-    c.t = u / upt;
-    c.w = u - c.t * upt;
-    c.j = c.t / tpj;
-    c.rt = c.t - c.j * tpj;
-    return c;
-}
-__device__ __forceinline__ void cursor_advance(UnitCursor &c, uint32_t step, uint32_t upt, uint32_t tpj) {
-    c.w += step;
-    while (c.w >= upt) {
-        c.w -= upt;
-        ++c.t;
-        if (++c.rt == tpj) {
-            c.rt = 0;
-            ++c.j;
-        }
-    }
-}
-
 // Shared-memory matrix descriptor of sm_100: start address, leading and stride byte offsets in
 // 16-byte units, descriptor version 1, layout (0 = no swizzle, 2 = 128-byte swizzle).
 __device__ __forceinline__ uint64_t smem_desc(uint32_t addr, uint32_t lbo16, uint32_t sbo16, uint32_t layout) {
@@ -155,15 +133,13 @@ __device__ __forceinline__ void umma_commit(uint32_t bar) {
     asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar)
                  : "memory");
 }
-__device__ __forceinline__ void tmem_ld8(uint32_t addr, float (&v)[8]) {
-    uint32_t r[8];
+// Eight accumulator columns of the warp's 32 lanes; the values may be used after tmem_ld_wait().
+__device__ __forceinline__ void tmem_ld8(uint32_t addr, uint32_t (&r)[8]) {
     asm volatile("tcgen05.ld.sync.aligned.32x32b.x8.b32 {%0,%1,%2,%3,%4,%5,%6,%7}, [%8];"
                  : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7])
                  : "r"(addr));
-    asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
-#pragma unroll
-    for (int j = 0; j < 8; ++j) v[j] = __uint_as_float(r[j]);
 }
+__device__ __forceinline__ void tmem_ld_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
 __device__ __forceinline__ void fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
 __device__ __forceinline__ void fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
 
@@ -272,43 +248,6 @@ __device__ __forceinline__ float swiglu_limit_fast(float gate, float up) {
     return __fmul_rn(__fdiv_rn(g, __fadd_rn(1.0f, expf(-g))), u);
 }
 
-// Shape of one phase: the up phase multiplies [inter, hidden] twice (w1, w3), the down phase
-// [hidden, inter] once (w2).
-struct PhaseShape {
-    uint32_t K, rows, mats, kchunks, upt, tpj;  // upt: units per tile, tpj: tiles per job
-    uint32_t b_stride, sfb_cols;                // digit tile (shared memory), its scale columns (tensor memory)
-};
-__device__ __forceinline__ PhaseShape phase_shape(bool up, uint32_t hidden, uint32_t inter) {
-    PhaseShape ps;
-    ps.K = up ? hidden : inter;
-    ps.rows = up ? inter : hidden;
-    ps.mats = up ? 2u : 1u;
-    ps.kchunks = ps.K >> 8;
-    ps.upt = ps.mats * ps.kchunks;
-    ps.tpj = ps.rows >> 7;
-    ps.b_stride = ps.kchunks * 2048u;
-    ps.sfb_cols = (ps.K >> 7) * 4u;
-    return ps;
-}
-// A CTA's run of a phase: units [u0, u1) of `total`, cut into G equal runs.
-struct Run {
-    uint64_t total;
-    uint32_t G, u0, u1, n, job_first, job_last;
-};
-__device__ __forceinline__ Run make_run(const PhaseShape &ps, uint32_t n_jobs, uint32_t grid, uint32_t cta) {
-    Run r;
-    r.total = (uint64_t)n_jobs * ps.tpj * ps.upt;
-    // every working CTA gets at least one unit, so each tile's contributors are consecutive CTAs
-    r.G = (uint32_t)min((uint64_t)grid, r.total);
-    const bool working = cta < r.G;
-    r.u0 = working ? (uint32_t)(r.total * cta / r.G) : 0u;
-    r.u1 = working ? (uint32_t)(r.total * (cta + 1u) / r.G) : 0u;
-    r.n = r.u1 - r.u0;
-    // a run is at most one job long (the launcher requires n_jobs <= gridDim.x): two jobs at most
-    r.job_first = r.n ? (r.u0 / ps.upt) / ps.tpj : 0u;
-    r.job_last = r.n ? ((r.u1 - 1u) / ps.upt) / ps.tpj : 0u;
-    return r;
-}
 
 __device__ __forceinline__ uint32_t ld_acquire(const unsigned int *p) {
     uint32_t v;
@@ -316,43 +255,54 @@ __device__ __forceinline__ uint32_t ld_acquire(const unsigned int *p) {
     return v;
 }
 
-// One launch runs the whole layer.  Every CTA streams its run of the up phase and then its run of
-// the down phase through one ring; the copies of the down phase do not wait for the hidden
-// vectors, only its MMAs do (the vectors of a job are complete when the job's counter says that
-// all its up tiles are finished, whichever CTAs finished them).
+// No-swizzle K-major tile of 8-row x 16-byte core matrices for K = 64 (32 bytes per row): the two
+// halves of a row are 128 B apart (leading offset), 8-row groups 256 B apart (stride offset).
+__device__ __forceinline__ uint64_t smem_desc_k64(uint32_t addr) { return smem_desc(addr, 8, 16, 0); }
+
 __global__ void __launch_bounds__(kThreads, 1)
 k_moe_layer_umma(const JobTable *__restrict__ dev_table, const __grid_constant__ JobTable param_table,
-                 const float *__restrict__ x, float *h, float *d, float *__restrict__ y,
-                 double *__restrict__ partials, unsigned int *__restrict__ counters, uint32_t *__restrict__ status,
-                 uint32_t hidden, uint32_t inter, uint32_t b_bytes) {
+                 const float *__restrict__ x, float *d_out, float *__restrict__ y, float *part,
+                 unsigned int *counters, uint32_t *__restrict__ status, uint32_t hidden, uint32_t inter) {
     extern __shared__ __align__(1024) uint8_t smem[];
     __shared__ __align__(8) uint64_t bars[kBars];
-    __shared__ double xchg[kEpiGroup];  // group B's sums of a tile, handed to group A
+    __shared__ __align__(16) uint8_t sE[kMaxBlocks];         // block exponents of the token's digits
+    __shared__ __align__(16) uint8_t sBh[kItemSlots * 512];  // digit tiles of the items' hidden values (rows 8-15 zero)
+    __shared__ float s_up[64];                               // an item's up projection, handed to the gate threads
+    __shared__ uint8_t sEh[kItemSlots][2];
     __shared__ uint32_t tmem_slot;
     __shared__ int abort_flag;
-    __shared__ uint32_t epi_info[3];
-    __shared__ __align__(16) uint8_t sE[kDigitSlots * kMaxBlocks];  // block exponents of the digit tiles
 
     const uint32_t tid = threadIdx.x, warp = tid >> 5, lane = tid & 31u;
     const bool is_producer = warp >= kProdWarp0 && warp < kProdWarp0 + kProdThreads / 32u;
     if (tid == 0) TRACE(0);
-    const PhaseShape PU = phase_shape(true, hidden, inter), PD = phase_shape(false, hidden, inter);
+    const uint32_t KU = hidden >> 8;   // up units of an item (256 K-elements each)
+    const uint32_t DS = hidden >> 9;   // down stages of an item (four 128-row tiles each)
+    const uint32_t RT = hidden >> 7;   // row tiles of w2
+    const uint32_t S = inter >> 6;     // slices of an expert
     uint8_t *const sA = smem;
-    uint8_t *const sSFA = sA + kRing * kStageA;
-    uint8_t *const sB = sSFA + kRing * kStageSf;
+    uint8_t *const sSF = sA + kRing * kStageA;
+    uint8_t *const sBx = sSF + kRing * kStageSf;  // the token's digit tile, 2 KB per 256 K-elements
     const uint32_t bar0 = smem_u32(bars);
     auto bar = [&](uint32_t i) { return bar0 + i * 8u; };
 
-    // rows 8-15 of every digit tile stay zero
-    for (uint32_t i = tid; i < b_bytes >> 4; i += kThreads) reinterpret_cast<uint4 *>(sB)[i] = make_uint4(0u, 0u, 0u, 0u);
+    // rows 8-15 of the digit tiles stay zero
+    for (uint32_t i = tid; i < (KU * 2048u) >> 4; i += kThreads) reinterpret_cast<uint4 *>(sBx)[i] = make_uint4(0u, 0u, 0u, 0u);
+    for (uint32_t i = tid; i < sizeof(sBh) / 4u; i += kThreads) reinterpret_cast<uint32_t *>(sBh)[i] = 0u;
     if (tid == 0) {
         for (uint32_t s = 0; s < kRing; ++s) {
             mbar_init(bar(kBarFull + s), kProdThreads);
             mbar_init(bar(kBarDone + s), 1);
-            mbar_init(bar(kBarAccFree + s), kEpiGroup);
         }
-        mbar_init(bar(kBarDigitsUp), 2u * kEpiGroup);
-        mbar_init(bar(kBarDigitsDown), 2u * kEpiGroup);
+        for (uint32_t s = 0; s < kDRing; ++s) {
+            mbar_init(bar(kBarDFree + s), kEpiGroup);
+            mbar_init(bar(kBarDDone + s), 1);
+        }
+        for (uint32_t s = 0; s < 2; ++s) {
+            mbar_init(bar(kBarUDone + s), 2);
+            mbar_init(bar(kBarUFree + s), kEpiGroup);
+        }
+        for (uint32_t s = 0; s < kItemSlots; ++s) mbar_init(bar(kBarHReady + s), kEpiGroup);
+        mbar_init(bar(kBarXReady), 2u * kEpiGroup);
         mbar_init(bar(kBarFin), 2);
         abort_flag = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
@@ -369,120 +319,133 @@ k_moe_layer_umma(const JobTable *__restrict__ dev_table, const __grid_constant__
     const uint32_t tmem = tmem_slot;
     if (tid == 0) TRACE(1);
 
-    if (dev_table) {
-        // One token routed on the device: the token does not depend on the router, so its digits
-        // are built while the router runs; the job table is read only afterwards.
-        build_digits(x, x, 1, PU.K, sB, PU.b_stride, sE, tid, kThreads);
-    }
+    // The token does not depend on the router: its digits are built while the router runs; the
+    // job table is read only after the router has finished.
+    build_digits(x, x, 1, hidden, sBx, 0, sE, tid, kThreads);
     cudaGridDependencySynchronize();
     const JobTable &tab = table_of(dev_table, param_table);
-    const uint32_t n_jobs = tab.n_jobs, cta = blockIdx.x;
-    const Run RU = make_run(PU, n_jobs, gridDim.x, cta), RD = make_run(PD, n_jobs, gridDim.x, cta);
-    const uint32_t tok0 = (!dev_table && RU.n) ? tab.jobs[RU.job_first].token : 0u;
-    const uint32_t tok1 = (!dev_table && RU.n) ? tab.jobs[RU.job_last].token : 0u;
-    const uint32_t up_slots = tok1 != tok0 ? 2u : 1u, down_slots = RD.job_last - RD.job_first + 1u;
-    // digit slot of job j: up phase by token, down phase by job
-    auto slot_up = [&](uint32_t j) { return tab.jobs[j].token == tok0 ? 0u : 1u; };
-    if (!dev_table && RU.n)
-        build_digits(x + (size_t)tok0 * hidden, x + (size_t)tok1 * hidden, up_slots, PU.K, sB, PU.b_stride, sE, tid,
-                     kThreads);
+    const uint32_t n_jobs = tab.n_jobs, n_items = n_jobs * S, grid = gridDim.x, cta = blockIdx.x;
+    // items are dealt in equal shares; with more CTAs than items the last CTAs have none
+    const uint32_t G = min(grid, n_items);
+    const uint32_t q0 = cta < G ? (uint32_t)((uint64_t)n_items * cta / G) : 0u;
+    const uint32_t q1 = cta < G ? (uint32_t)((uint64_t)n_items * (cta + 1u) / G) : 0u;
+    const uint32_t n_it = min(q1 - q0, kItemSlots);  // the launcher keeps the share within kItemSlots
+    const uint32_t nU = n_it * KU, nD = n_it * DS;
     asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
     __syncthreads();
     if (tid == 0) TRACE(2);
 
-    unsigned int *const h_ready = counters + kHReadyCounter0;
-
-    if (is_producer) {
-        // ---- copies: the run of the up phase, then the run of the down phase, through one ring ----
+    if (is_producer && n_it) {
+        // ---- copies: the up units of every item, then the down stages of every item ----
         const uint32_t pt = tid - kProdWarp0 * 32u, r8 = pt >> 3, cc = pt & 7u;
-        const uint32_t dst0 = smem_u32(sA) + r8 * 128u + ((cc ^ (r8 & 7u)) << 4);
-        uint32_t i = 0;
+        const uint32_t dst_up = smem_u32(sA) + r8 * 128u + ((cc ^ (r8 & 7u)) << 4);
         bool ok = true;
-        for (uint32_t ph = 0; ph < 2 && ok; ++ph) {
-            const PhaseShape &ps = ph ? PD : PU;
-            const Run &run = ph ? RD : RU;
-            UnitCursor c = cursor_at(run.u0, ps.upt, ps.tpj);
-            for (uint32_t l = 0; l < run.n; ++l, ++i) {
+        uint32_t i = 0;
+        for (uint32_t l = 0; l < n_it && ok; ++l) {
+            const uint32_t q = q0 + l, j = q / S, sl = q - j * S;
+            const PageView pv = page_view(tab.jobs[j].page, S14_PAGE_MXFP4, hidden, inter);
+            // rows r8, r8 + 16, ... of the tile: the first four are w1 rows of the slice, the last four w3 rows
+            const uint8_t *src1 = pv.w1 + (size_t)(sl * 64u + r8) * (hidden >> 1) + cc * 16u;
+            const uint8_t *src3 = pv.w3 + (size_t)(sl * 64u + r8) * (hidden >> 1) + cc * 16u;
+            const uint8_t *sf = pv.s1 + (size_t)sl * RT * 512u + pt * 16u;
+            for (uint32_t ks = 0; ks < KU; ++ks, ++i) {
                 const uint32_t s = i % kRing;
                 if (i >= kRing && !mbar_wait(bar(kBarDone + s), ((i / kRing) - 1u) & 1u, &abort_flag)) {
                     ok = false;
                     break;
                 }
-                const uint32_t ks = ph ? c.w : (c.w >> 1), mat = ph ? 0u : (c.w & 1u);
-                const PageView pv = page_view(tab.jobs[c.j].page, S14_PAGE_MXFP4, hidden, inter);
-                const uint8_t *wp = ph ? pv.w2 : (mat ? pv.w3 : pv.w1);
-                const uint8_t *sp = ph ? pv.s2 : (mat ? pv.s3 : pv.s1);
-                const uint8_t *src = wp + (size_t)(c.rt * 128u + r8) * (ps.K >> 1) + ks * 128u + cc * 16u;
-                const uint32_t dst = dst0 + s * kStageA;
+                const uint32_t dst = dst_up + s * kStageA;
 #pragma unroll
-                for (uint32_t i8 = 0; i8 < 8; ++i8) cp_async16(dst + i8 * 2048u, src + (size_t)i8 * 16u * (ps.K >> 1));
-                // the unit's two scale atoms are 1 KB of consecutive page bytes, already in tensor-memory order
-                if (pt < kStageSf / 16u)
-                    cp_async16(smem_u32(sSFA + s * kStageSf) + pt * 16u,
-                               sp + scale_word_offset(c.rt * 128u, ks * 2u, ps.K) + pt * 16u);
+                for (uint32_t i8 = 0; i8 < 4; ++i8) {
+                    cp_async16(dst + i8 * 2048u, src1 + (size_t)i8 * 16u * (hidden >> 1) + ks * 128u);
+                    cp_async16(dst + (i8 + 4u) * 2048u, src3 + (size_t)i8 * 16u * (hidden >> 1) + ks * 128u);
+                }
+                // the unit's two scale atoms are 1 KB of consecutive page bytes
+                if (pt < 64u) cp_async16(smem_u32(sSF + s * kStageSf) + pt * 16u, sf + (size_t)ks * 1024u);
                 mbar_arrive_after_copies(bar(kBarFull + s));
-                cursor_advance(c, 1, ps.upt, ps.tpj);
+            }
+        }
+        for (uint32_t l = 0; l < n_it && ok; ++l) {
+            const uint32_t q = q0 + l, j = q / S, sl = q - j * S;
+            const PageView pv = page_view(tab.jobs[j].page, S14_PAGE_MXFP4, hidden, inter);
+            const uint8_t *wsrc = pv.w2 + (size_t)sl * RT * 4096u + pt * 16u;        // the slice's columns, 4 KB per row tile
+            const uint8_t *sf = pv.s2 + (size_t)(sl >> 1) * RT * 512u + pt * 16u;   // the slice pair's atoms
+            for (uint32_t v = 0; v < DS; ++v, ++i) {
+                const uint32_t s = i % kRing;
+                if (i >= kRing && !mbar_wait(bar(kBarDone + s), ((i / kRing) - 1u) & 1u, &abort_flag)) {
+                    ok = false;
+                    break;
+                }
+                const uint32_t dst = smem_u32(sA + s * kStageA);
+#pragma unroll
+                for (uint32_t i8 = 0; i8 < 8; ++i8) {
+                    // piece id: block id / 256, row (id % 256) / 2, half id % 2 -> 8-row x 16-byte core matrices
+                    const uint32_t id = pt + i8 * 128u, r = (id & 255u) >> 1;
+                    cp_async16(dst + (id >> 8) * 4096u + (r >> 3) * 256u + (id & 1u) * 128u + (r & 7u) * 16u,
+                               wsrc + (size_t)v * 16384u + i8 * 2048u);
+                }
+                cp_async16(smem_u32(sSF + s * kStageSf) + pt * 16u, sf + (size_t)v * 2048u);
+                mbar_arrive_after_copies(bar(kBarFull + s));
             }
         }
         if (tid == kProdWarp0 * 32u) TRACE(8);
         asm volatile("cp.async.wait_all;" ::: "memory");
         if (tid == kProdWarp0 * 32u) TRACE(9);
-    } else if (warp == kMmaWarp0 || warp == kMmaWarp0 + 1u) {
-        if (lane == 0 && (RU.n || RD.n)) {
-            // ---- MMA issue: two threads take the even and the odd ring indices.  One accumulator per
-            // unit: a tile's result is the sum of its units' F32 sums, whichever CTAs computed them. ----
+    } else if ((warp == kMmaWarp0 || warp == kMmaWarp0 + 1u) && n_it) {
+        if (lane == 0) {
+            // ---- MMA issue.  The two threads take the even and the odd stages, so each ring slot has one
+            // owner who sees every phase of its barriers.  An item's up units accumulate into two
+            // accumulators, one per thread (hidden / 256 is even); the down stages have accumulators of
+            // their own. ----
             const uint32_t m = warp - kMmaWarp0;
-            const uint64_t a_desc0 = smem_desc(smem_u32(sA), 1, 64, 2), b_desc0 = smem_desc(smem_u32(sB), 1, 64, 2);
-            const uint64_t sfa_desc0 = smem_desc(smem_u32(sSFA), 0, 8, 0);
-            bool ok = true;
-            for (uint32_t ph = 0; ph < 2 && ok; ++ph) {
-                const PhaseShape &ps = ph ? PD : PU;
-                const Run &run = ph ? RD : RU;
-                if (!run.n) continue;
-                const uint32_t i0 = ph ? RU.n : 0u;
-                // the phase's digit rows are in shared memory, their scales in tensor memory
-                ok = mbar_wait(bar(ph ? kBarDigitsDown : kBarDigitsUp), 0, &abort_flag);
-                if (!ok) break;
-                asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
-                fence_after();
-                const uint32_t l0 = (m ^ i0) & 1u;  // first unit of this phase with ring index parity m
-                UnitCursor c = cursor_at(run.u0 + l0, ps.upt, ps.tpj);
-                uint32_t slot_t = ~0u, b = 0;
-                CYC_DECL(4);
-                for (uint32_t l = l0; l < run.n; l += 2) {
-                    const uint32_t i = i0 + l;
-                    if (c.t != slot_t) {
-                        slot_t = c.t;
-                        b = ph ? c.j - RD.job_first : slot_up(c.j);
-                    }
-                    const uint32_t ks = ph ? c.w : (c.w >> 1);
-                    const uint32_t s = i % kRing, par = (i / kRing) & 1u;
-                    CYC_LAP(0);
-                    if (!mbar_wait(bar(kBarFull + s), par, &abort_flag)) { ok = false; break; }
+            const uint64_t a_up0 = smem_desc(smem_u32(sA), 1, 64, 2), b_x0 = smem_desc(smem_u32(sBx), 1, 64, 2);
+            const uint64_t sf_desc0 = smem_desc(smem_u32(sSF), 0, 8, 0);
+            bool ok = mbar_wait(bar(kBarXReady), 0, &abort_flag);
+            for (uint32_t i = m; i < nU + nD && ok; i += 2u) {
+                const uint32_t s = i % kRing, par = (i / kRing) & 1u;
+                const uint32_t sfa_t = tmem + kColSfa + s * 16u;
+                const uint64_t sfd = sf_desc0 + s * (kStageSf >> 4);
+                if (i < nU) {
+                    const uint32_t l = i / KU, ks = i - l * KU;
+                    const bool first = ks < 2u;  // this thread's first unit of the item
+                    if (first && l >= 2u) ok = mbar_wait(bar(kBarUFree + (l & 1u)), ((l >> 1) - 1u) & 1u, &abort_flag);
+                    ok = ok && mbar_wait(bar(kBarFull + s), par, &abort_flag);
+                    if (!ok) break;
                     if (i == 0) TRACE(3);
-                    CYC_LAP(1);
-                    if (i >= kRing && !mbar_wait(bar(kBarAccFree + s), par ^ 1u, &abort_flag)) { ok = false; break; }
-                    CYC_LAP(2);
                     asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
                     fence_after();
-                    const uint32_t sfa_t = tmem + kSfaCol0 + s * 8u, sfb_t = tmem + kSfbCol0 + b * ps.sfb_cols + ks * 8u;
-                    const uint64_t sfa_d = sfa_desc0 + s * (kStageSf >> 4);
-                    tmem_copy_scales(sfa_t, sfa_d);
-                    tmem_copy_scales(sfa_t + 4u, sfa_d + (512u >> 4));
-                    const uint64_t ad = a_desc0 + s * (kStageA >> 4), bd = b_desc0 + ((b * ps.b_stride + ks * 2048u) >> 4);
+                    const uint32_t sfb_t = tmem + kColSfbX + ks * 8u;
+                    tmem_copy_scales(sfa_t, sfd);
+                    tmem_copy_scales(sfa_t + 4u, sfd + (512u >> 4));
+                    const uint64_t ad = a_up0 + s * (kStageA >> 4), bd = b_x0 + ks * (2048u >> 4);
 #pragma unroll
                     for (uint32_t kk = 0; kk < 4; ++kk) {
                         const uint32_t atom = kk >> 1, sfid = (kk & 1u) * 2u;
-                        umma_mxf4(tmem + s * 16u, ad + kk * 2u, bd + kk * 2u, kIdesc | (sfid << 29) | (sfid << 4),
-                                  (sfa_t + atom * 4u) | (sfid << 30), (sfb_t + atom * 4u) | (sfid << 30), kk ? 1u : 0u);
+                        umma_mxf4(tmem + kColU + (l & 1u) * 32u + m * 16u, ad + kk * 2u, bd + kk * 2u,
+                                  kIdesc | (sfid << 29) | (sfid << 4), (sfa_t + atom * 4u) | (sfid << 30),
+                                  (sfb_t + atom * 4u) | (sfid << 30), (first && kk == 0u) ? 0u : 1u);
                     }
                     umma_commit(bar(kBarDone + s));
-                    CYC_LAP(3);
-                    cursor_advance(c, 2, ps.upt, ps.tpj);
-                }
-                if (m == 0 && ph == 0) {
-                    CYC_STORE(0, 4);
-                    TRACE(4);
+                    if (ks + 2u >= KU) umma_commit(bar(kBarUDone + (l & 1u)));
+                    if (m == 0 && i + 2u >= nU) TRACE(4);
+                } else {
+                    // down stage vg: vg and i have the same parity, so accumulator set vg % 2 is this thread's
+                    const uint32_t vg = i - nU, l = vg / DS, sl = (q0 + l) % S, acc = vg & 1u;
+                    ok = mbar_wait(bar(kBarHReady + l), 0, &abort_flag) && mbar_wait(bar(kBarFull + s), par, &abort_flag) &&
+                         (vg < kDRing || mbar_wait(bar(kBarDFree + acc), ((vg >> 1) - 1u) & 1u, &abort_flag));
+                    if (!ok) break;
+                    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+                    fence_after();
+                    const uint32_t asf = (sl & 1u) * 2u;
+                    const uint64_t bd = smem_desc_k64(smem_u32(sBh + l * 512u));
+#pragma unroll
+                    for (uint32_t b = 0; b < 4; ++b) tmem_copy_scales(sfa_t + b * 4u, sfd + b * (512u >> 4));
+#pragma unroll
+                    for (uint32_t b = 0; b < 4; ++b)
+                        umma_mxf4(tmem + kColD + acc * 64u + b * 16u, smem_desc_k64(smem_u32(sA + s * kStageA + b * 4096u)),
+                                  bd, kIdesc | (asf << 29), (sfa_t + b * 4u) | (asf << 30), tmem + kColSfbH + l * 4u, 0u);
+                    umma_commit(bar(kBarDone + s));
+                    umma_commit(bar(kBarDDone + acc));
                 }
             }
             // nothing of this CTA's tensor work is in flight when the tensor memory is freed
@@ -490,194 +453,185 @@ k_moe_layer_umma(const JobTable *__restrict__ dev_table, const __grid_constant__
             mbar_wait(bar(kBarFin), 0, &abort_flag);
             if (m == 0) TRACE(5);
         }
-    } else if (warp < 2u * kEpiGroup / 32u && (RU.n || RD.n)) {
-        // ---- epilogue.  Group A (warps 0-3) sums the even units of a tile, group B (warps 4-7) the
-        // odd ones: in the up phase these are the gate and the up projection. ----
+    } else if (warp < 2u * kEpiGroup / 32u && n_it) {
+        // ---- epilogue: group A (warps 0-3) turns the up accumulators into hidden digits, then both
+        // groups read the down accumulators (alternate stages) ----
         const uint32_t grp = warp >> 2, row = tid & (kEpiGroup - 1u);
         const uint32_t lane_base = tmem + (((warp & 3u) * 32u) << 16);
         bool ok = true;
-        uint32_t i = 0;
-        for (uint32_t ph = 0; ph < 2 && ok; ++ph) {
-            const PhaseShape &ps = ph ? PD : PU;
-            const Run &run = ph ? RD : RU;
-            if (!run.n) continue;
-            if (!ph) {
-                store_digit_scales(tmem + kSfbCol0, sE, up_slots, PU.K, PU.sfb_cols, warp, lane);
-                fence_before();
-                mbar_arrive(bar(kBarDigitsUp));
-            } else {
-                // The hidden vectors of this run's jobs: wait until every up tile of them is finished,
-                // then write their digit rows (the token's digits are no longer read: every MMA of
-                // the up phase has completed before its accumulator was read above).
-                if (tid == 0) {
-                    for (uint32_t j = RD.job_first; j <= RD.job_last && ok; ++j) {
-                        uint32_t tries = 0;
-                        while (ld_acquire(h_ready + j) < PU.tpj) {
-                            if (++tries > kSpinGlobal || abort_flag) {
-                                abort_flag = 1;
-                                ok = false;
-                                break;
-                            }
-                            __nanosleep(100);
-                        }
-                    }
-                }
-                ok = epi_bar_and(ok);
-                if (!ok) break;
-                if (tid == 0) TRACE(6);
-                build_digits(h + (size_t)RD.job_first * inter, h + (size_t)RD.job_last * inter, down_slots, PD.K, sB,
-                             PD.b_stride, sE, tid, 2u * kEpiGroup);
-                asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
-                epi_bar_sync();  // every block exponent is written
-                store_digit_scales(tmem + kSfbCol0, sE, down_slots, PD.K, PD.sfb_cols, warp, lane);
-                fence_before();
-                mbar_arrive(bar(kBarDigitsDown));
-            }
-            float hi = 0.0f, lo = 0.0f;  // hi + lo: this group's sum over the tile's units, to about 48 bits
-            UnitCursor c = cursor_at(run.u0, ps.upt, ps.tpj);
-            for (uint32_t l = 0; l < run.n; ++l, ++i) {
-                const uint32_t s = i % kRing;
-                if ((c.w & 1u) == grp) {
-                    ok = __all_sync(0xffffffffu, ok && mbar_wait(bar(kBarDone + s), (i / kRing) & 1u, &abort_flag));
-                    if (ok) {
-                        fence_after();
-                        float a[8];
-                        tmem_ld8(lane_base + s * 16u, a);
-                        fence_before();
-                        mbar_arrive(bar(kBarAccFree + s));
+        store_digit_scales(tmem + kColSfbX, sE, 1, hidden, 0, warp, lane);
+        fence_before();
+        mbar_arrive(bar(kBarXReady));
+        if (grp == 0u) {
+            for (uint32_t l = 0; l < n_it; ++l) {
+                const uint32_t q = q0 + l, j = q / S;
+                ok = __all_sync(0xffffffffu, ok && mbar_wait(bar(kBarUDone + (l & 1u)), (l >> 1) & 1u, &abort_flag));
+                float v = 0.0f;
+                if (ok) {
+                    fence_after();
+                    uint32_t a[8], b[8];  // even and odd units of the item
+                    tmem_ld8(lane_base + kColU + (l & 1u) * 32u, a);
+                    tmem_ld8(lane_base + kColU + (l & 1u) * 32u + 16u, b);
+                    tmem_ld_wait();
+                    fence_before();
+                    mbar_arrive(bar(kBarUFree + (l & 1u)));
+                    float hi = 0.0f, lo = 0.0f;
 #pragma unroll
-                        for (int jj = 0; jj < 8; ++jj) {  // low digits first
-                            float e;
-                            two_sum(hi, a[jj], hi, e);
-                            lo = __fadd_rn(lo, e);
-                        }
+                    for (int jj = 0; jj < 8; ++jj) {  // low digits first
+                        float e;
+                        two_sum(hi, __uint_as_float(a[jj]), hi, e);
+                        lo = __fadd_rn(lo, e);
+                        two_sum(hi, __uint_as_float(b[jj]), hi, e);
+                        lo = __fadd_rn(lo, e);
                     }
+                    v = __fadd_rn(hi, lo);
                 }
-                const bool tile_ends = c.w + 1u == ps.upt;
-                if (!tile_ends && l + 1u != run.n) {
-                    cursor_advance(c, 1, ps.upt, ps.tpj);
-                    continue;
-                }
-
-                // the run's units of tile c.t, [wa, c.w], are summed
-                const double v = (double)hi + (double)lo;
-                if (grp == 1u) xchg[row] = v;
-                if (!epi_bar_and(ok)) {
-                    ok = false;
-                    break;
-                }
-                if (grp == 0u) {
-                    const uint32_t t = c.t, t_begin = t * ps.upt, j = c.j, rt = c.rt;
-                    const uint32_t seg_first = max(run.u0, t_begin), wa = seg_first - t_begin;
-                    double v0 = ph ? v + xchg[row] : v, v1 = ph ? 0.0 : xchg[row];
-                    bool finish = (wa == 0u && tile_ends);
-                    double *const part = partials + (ph ? (size_t)gridDim.x * 2u * 2u * 128u : 0u);
-                    if (!finish) {
-                        // part of the tile's K range: leave the partial sums, count the arrival
-                        const uint32_t slot = (seg_first == run.u0) ? 0u : 1u;
-                        double *p = part + (size_t)(cta * 2u + slot) * 2u * 128u + row;
-                        p[0] = v0;
-                        if (!ph) p[128] = v1;
-                        __threadfence();
-                        group_bar_sync();
-                        if (row == 0) {
-                            const uint32_t c_first = (uint32_t)((((uint64_t)t_begin + 1u) * run.G - 1u) / run.total);
-                            const uint32_t c_last = (uint32_t)((((uint64_t)t_begin + ps.upt) * run.G - 1u) / run.total);
-                            unsigned int *cnt = counters + (ph ? kDownCounter0 : kUpCounter0) + t;
-                            const bool last = atomicAdd(cnt, 1u) == c_last - c_first;
-                            if (last) *cnt = 0u;  // ready for the next launch
-                            epi_info[0] = last ? 1u : 0u;
-                            epi_info[1] = c_first;
-                            epi_info[2] = c_last;
-                        }
-                        group_bar_sync();
-                        finish = epi_info[0] != 0u;
-                        if (finish) {
-                            __threadfence();
-                            const uint32_t c_first = epi_info[1], c_last = epi_info[2];
-                            v0 = 0.0;
-                            v1 = 0.0;
-                            for (uint32_t cc = c_first; cc <= c_last; ++cc) {  // K order
-                                const uint32_t sl = ((uint32_t)(run.total * cc / run.G) >= t_begin) ? 0u : 1u;
-                                const double *q = part + (size_t)(cc * 2u + sl) * 2u * 128u + row;
-                                v0 += __ldcg(q);
-                                if (!ph) v1 += __ldcg(q + 128);
-                            }
-                        }
+                if (row >= 64u) s_up[row - 64u] = v;
+                group_bar_sync();
+                (void)j;
+                if (row < 64u) {
+                    // hidden value `row` of the slice -> eight digit nibbles, scale block = warp
+                    const float hv = swiglu_limit_fast(v, s_up[row]);
+                    float bm = fabsf(hv);
+#pragma unroll
+                    for (int o = 16; o > 0; o >>= 1) bm = fmaxf(bm, __shfl_xor_sync(0xffffffffu, bm, o));
+                    int E = -100;
+                    if (bm > 0.0f) E = min(max((int)((__float_as_uint(bm) >> 23) & 0xFFu) - 126, -100), 127);
+                    const uint32_t qb = (uint32_t)(__float2int_rn(hv * __uint_as_float((uint32_t)(150 - E) << 23)) + 0x924924);
+                    uint32_t word = 0;
+#pragma unroll
+                    for (int jj = 0; jj < 7; ++jj) word |= ((0x5420ACDEu >> (((qb >> (3 * jj)) & 7u) << 2)) & 0xFu) << (4 * jj);
+                    const uint32_t top = qb >> 21;
+                    word |= (top > 7u ? 6u : ((0x5420ACDEu >> (top << 2)) & 0xFu)) << 28;
+                    const uint32_t other = __shfl_xor_sync(0xffffffffu, word, 1);
+                    const uint32_t lo_w = (lane & 1u) ? other : word, hi_w = (lane & 1u) ? word : other;
+                    uint8_t *chunk = sBh + l * 512u + warp * 128u + (lane >> 1);  // K half = scale block = warp
+#pragma unroll
+                    for (uint32_t jj = 0; jj < 4; ++jj) {
+                        const uint32_t dj = (lane & 1u) * 4u + jj;  // digit row
+                        chunk[dj * 16u] = (uint8_t)(((lo_w >> (4u * dj)) & 0xFu) | (((hi_w >> (4u * dj)) & 0xFu) << 4));
                     }
-                    if (finish && !ph) {
-                        h[(size_t)j * inter + rt * 128u + row] = swiglu_limit_fast((float)v0, (float)v1);
-                        __threadfence();
-                        group_bar_sync();
-                        if (row == 0) atomicAdd(h_ready + j, 1u);  // one more tile of job j's hidden vector
-                    } else if (finish) {
-                        const uint32_t n = rt * 128u + row, tk = tab.jobs[j].token;
-                        d[(size_t)tab.jobs[j].out_index * hidden + n] = (float)v0;
-                        if (y) {
-                            // Ordered mix (examples/s14_vulkan_numeric.rs:936-946) by whoever finishes the
-                            // token's last job of these 128 rows: acc = 0; acc += w * d in route order;
-                            // acc += d_shared.
-                            const uint32_t j0 = tab.token_job_begin[tk], j1 = tab.token_job_begin[tk + 1u];
-                            __threadfence();
-                            group_bar_sync();
-                            if (row == 0) {
-                                unsigned int *cnt = counters + kMixCounter0 + tk * kMaxRowTiles + rt;
-                                const bool last = atomicAdd(cnt, 1u) == j1 - j0 - 1u;
-                                if (last) *cnt = 0u;
-                                epi_info[0] = last ? 1u : 0u;
-                            }
-                            group_bar_sync();
-                            if (epi_info[0]) {
-                                __threadfence();
-                                float acc = 0.0f;
-                                for (uint32_t jj = j0; jj < j1; ++jj) {
-                                    const Job &o = tab.jobs[tab.token_jobs[jj]];
-                                    const float dv = __ldcg(d + (size_t)o.out_index * hidden + n);
-                                    acc = o.is_shared ? __fadd_rn(acc, dv) : __fadd_rn(acc, __fmul_rn(o.weight, dv));
-                                }
-                                y[(size_t)tk * hidden + n] = acc;
-                            }
-                        }
-                    }
+                    if (lane == 0) sEh[l][warp] = (uint8_t)(E + 100);
                 }
-                // xchg and epi_info are rewritten only after every epilogue thread has passed this point
-                epi_bar_sync();
-                hi = 0.0f;
-                lo = 0.0f;
-                cursor_advance(c, 1, ps.upt, ps.tpj);
+                group_bar_sync();
+                {
+                    // scale codes of the eight digit rows for the slice's two blocks (blocks 2, 3 unused)
+                    const uint32_t bias = 4u + 3u * (lane & 7u);
+                    const uint32_t w0 = lane < 8u ? ((sEh[l][0] + bias) | ((sEh[l][1] + bias) << 8) | 0x7F7F0000u) : 0x7F7F7F7Fu;
+                    const uint32_t one = 0x7F7F7F7Fu;
+                    asm volatile("tcgen05.st.sync.aligned.32x32b.x4.b32 [%0], {%1,%2,%2,%2};" ::"r"(lane_base + kColSfbH + l * 4u),
+                                 "r"(w0), "r"(one)
+                                 : "memory");
+                    asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
+                }
+                asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+                fence_before();
+                mbar_arrive(bar(kBarHReady + l));
             }
+            if (tid == 0) TRACE(6);
+        }
+        for (uint32_t vg = grp; vg < nD; vg += 2u) {
+            const uint32_t acc = vg & 1u;
+            const uint32_t l = vg / DS, vloc = vg - l * DS, q = q0 + l;
+            // every phase of this barrier is waited for by this group, in order
+            ok = __all_sync(0xffffffffu, ok && mbar_wait(bar(kBarDDone + acc), (vg >> 1) & 1u, &abort_flag));
+            if (!ok) break;
+            fence_after();
+            uint32_t a[4][8];
+#pragma unroll
+            for (uint32_t b = 0; b < 4; ++b) tmem_ld8(lane_base + kColD + acc * 64u + b * 16u, a[b]);
+            tmem_ld_wait();
+            fence_before();
+            mbar_arrive(bar(kBarDFree + acc));  // the accumulators are in registers: the next stage may overwrite them
+            float out[4];
+#pragma unroll
+            for (uint32_t b = 0; b < 4; ++b) {
+                float hi = 0.0f, lo = 0.0f;
+#pragma unroll
+                for (int jj = 0; jj < 8; ++jj) {
+                    float e;
+                    two_sum(hi, __uint_as_float(a[b][jj]), hi, e);
+                    lo = __fadd_rn(lo, e);
+                }
+                out[b] = __fadd_rn(hi, lo);
+            }
+            // the item's share of rows (4 vloc + b) * 128 + row of its expert's output
+            float *p = part + (size_t)q * hidden + (size_t)vloc * 512u + row;
+#pragma unroll
+            for (uint32_t b = 0; b < 4; ++b) p[b * 128u] = out[b];
         }
     }
 
     if (tid == 0) TRACE(7);
+    // ---- every item's share is in global memory: count the CTA's items, wait for all of them ----
+    __threadfence();
     fence_before();
     __syncthreads();
-    if (tid == 0) TRACE(10);
-    if (tid == 0) {
-        if (abort_flag) atomicExch(status, 0x5501u);
-        // the last CTA to leave puts the hidden vectors' counters back to zero for the next launch
-        __threadfence();
-        unsigned int *exit_count = counters + kExitCounter;
-        if (atomicAdd(exit_count, 1u) == gridDim.x - 1u) {
-            for (uint32_t j = 0; j < n_jobs; ++j) h_ready[j] = 0u;
-            *exit_count = 0u;
-        }
-    }
     if (warp == kMmaWarp0) {
         __syncwarp();
         asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(kTmemCols) : "memory");
     }
+    if (tid == 0) {
+        if (n_it) atomicAdd(counters + kItemCounter, abort_flag ? 0u : n_it);
+        uint32_t tries = 0;
+        while (!abort_flag && ld_acquire(counters + kItemCounter) < n_items) {
+            if (++tries > kSpinGlobal) abort_flag = 1;
+            __nanosleep(100);
+        }
+        if (abort_flag) atomicExch(status, 0x5501u);
+        TRACE(10);
+    }
+    __syncthreads();
+    if (!abort_flag) {
+        // ---- rows [n0, n1) of this CTA: expert outputs as sums over slices in slice order, then the
+        // ordered mix (examples/s14_vulkan_numeric.rs:936-946): acc = 0; acc += w * d in route order;
+        // acc += d_shared.  Scratch: the ring's shared memory. ----
+        const uint32_t n0 = (uint32_t)((uint64_t)hidden * cta / grid), n1 = (uint32_t)((uint64_t)hidden * (cta + 1u) / grid);
+        const uint32_t rows = n1 - n0, chunks = S >> 2;
+        double *red = reinterpret_cast<double *>(smem);                       // [job][chunk][row]
+        float *dj = reinterpret_cast<float *>(smem + (size_t)n_jobs * chunks * rows * 8u);  // [job][row]
+        for (uint32_t t = tid; t < n_jobs * chunks * rows; t += kThreads) {
+            const uint32_t r = t % rows, jc = t / rows;  // jc = job * chunks + chunk: four slices of one job
+            const float *p = part + (size_t)jc * 4u * hidden + n0 + r;
+            double sum = (double)__ldcg(p);
+            sum += (double)__ldcg(p + hidden);
+            sum += (double)__ldcg(p + 2u * (size_t)hidden);
+            sum += (double)__ldcg(p + 3u * (size_t)hidden);
+            red[t] = sum;
+        }
+        __syncthreads();
+        for (uint32_t t = tid; t < n_jobs * rows; t += kThreads) {
+            const uint32_t r = t % rows, j = t / rows;
+            double sum = 0.0;
+            for (uint32_t c = 0; c < chunks; ++c) sum += red[((size_t)j * chunks + c) * rows + r];
+            const float v = (float)sum;
+            dj[t] = v;
+            if (!y) d_out[(size_t)tab.jobs[j].out_index * hidden + n0 + r] = v;  // the caller mixes
+        }
+        __syncthreads();
+        if (y && tid < rows) {
+            const uint32_t j0 = tab.token_job_begin[0], j1 = tab.token_job_begin[1];
+            float acc = 0.0f;
+            for (uint32_t jj = j0; jj < j1; ++jj) {
+                const uint32_t jb = tab.token_jobs[jj];
+                const float dv = dj[(size_t)jb * rows + tid];
+                acc = tab.jobs[jb].is_shared ? __fadd_rn(acc, dv) : __fadd_rn(acc, __fmul_rn(tab.jobs[jb].weight, dv));
+            }
+            y[n0 + tid] = acc;
+        }
+    }
+    // the last CTA to leave puts the counters back to zero for the next launch
+    if (tid == 0) {
+        TRACE(11);
+        __threadfence();
+        if (atomicAdd(counters + kExitCounter, 1u) == grid - 1u) {
+            counters[kItemCounter] = 0u;
+            counters[kExitCounter] = 0u;
+        }
+    }
 }
 
-// Bytes of the digit tiles: two hidden vectors in the down phase, one token (two in a block of
-// several tokens) in the up phase.
-size_t digit_tile_bytes(uint32_t n_tokens, uint32_t hidden, uint32_t inter) {
-    const size_t up = (size_t)(n_tokens > 1u ? 2u : 1u) * (hidden >> 8) * 2048u, down = (size_t)2u * (inter >> 8) * 2048u;
-    return up > down ? up : down;
-}
-size_t umma_smem_bytes(uint32_t n_tokens, uint32_t hidden, uint32_t inter) {
-    return (size_t)kRing * (kStageA + kStageSf) + digit_tile_bytes(n_tokens, hidden, inter);
-}
+size_t umma_smem_bytes(uint32_t hidden) { return (size_t)kRing * (kStageA + kStageSf) + (size_t)(hidden >> 8) * 2048u; }
 
 template <class Kernel, class... Args>
 cudaError_t launch_pdl(Kernel kernel, dim3 grid, dim3 block, size_t smem, cudaStream_t st, bool pdl, Args... args) {
@@ -712,28 +666,29 @@ void configure_once() {
 
 }  // namespace
 
-size_t umma_partials_bytes(int sm_count) {
-    // two phases x (CTA, first or last run) x two accumulators x 128 rows of F64
-    return (size_t)2 * sm_count * 2 * 2 * 128 * sizeof(double);
+size_t umma_partials_bytes() {
+    // one F32 per (item, output row): experts of a token x slices x rows, at the largest shape
+    return (size_t)(S14_EXPERTS_PER_TOKEN + 1) * (4096 / 64) * kMaxHidden * sizeof(float);
 }
 
 bool umma_layer_ok(int sm_count, uint32_t n_tokens, uint32_t n_jobs_max, uint32_t hidden, uint32_t inter) {
-    if (n_tokens == 0u || n_tokens > kMaxTokens || n_jobs_max == 0u || (int)n_jobs_max > sm_count) return false;
-    if ((hidden & 511u) || (inter & 511u) || hidden < 512u || inter < 512u) return false;
-    if (n_jobs_max * (inter >> 7) > kMaxTiles || n_jobs_max * (hidden >> 7) > kMaxTiles) return false;
-    if ((hidden >> 7) > kMaxRowTiles || hidden > kMaxK || inter > kMaxK || n_jobs_max > kMaxJobs) return false;
+    if (n_tokens != 1u || n_jobs_max == 0u || n_jobs_max > S14_EXPERTS_PER_TOKEN + 1u) return false;
+    if ((hidden & 511u) || (inter & 511u) || hidden < 512u || inter < 512u || hidden > kMaxHidden || inter > 4096u) return false;
+    const uint32_t items = n_jobs_max * (inter >> 6);
+    if ((items + (uint32_t)sm_count - 1u) / (uint32_t)sm_count > kItemSlots) return false;
     configure_once();
-    return umma_smem_bytes(n_tokens, hidden, inter) <= g_dynamic_limit;
+    // the final sums reuse the ring: [jobs][slices / 4][rows] doubles + [jobs][rows] floats
+    const size_t rows = (hidden + sm_count - 1) / sm_count + 1;
+    if ((size_t)n_jobs_max * ((inter >> 8) * 8u + 4u) * rows > (size_t)kRing * (kStageA + kStageSf)) return false;
+    return umma_smem_bytes(hidden) <= g_dynamic_limit;
 }
 
 cudaError_t launch_moe_layer_umma(cudaStream_t st, int sm_count, const JobTable *dev, const JobTable &param,
-                                  uint32_t n_tokens, const float *x, float *h, float *d, float *y, double *partials,
-                                  unsigned int *counters, uint32_t *status, uint32_t hidden, uint32_t inter,
-                                  bool after_router) {
+                                  const float *x, float *d, float *y, float *partials, unsigned int *counters,
+                                  uint32_t *status, uint32_t hidden, uint32_t inter, bool after_router) {
     configure_once();
-    return launch_pdl(k_moe_layer_umma, dim3(sm_count), dim3(kThreads), umma_smem_bytes(n_tokens, hidden, inter), st,
-                      after_router, dev, param, x, h, d, y, partials, counters, status, hidden, inter,
-                      (uint32_t)digit_tile_bytes(n_tokens, hidden, inter));
+    return launch_pdl(k_moe_layer_umma, dim3(sm_count), dim3(kThreads), umma_smem_bytes(hidden), st, after_router, dev,
+                      param, x, d, y, partials, counters, status, hidden, inter);
 }
 
 }  // namespace s14

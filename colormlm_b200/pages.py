@@ -2,23 +2,27 @@
 
 The reference uploads an expert's six tensors as six separate buffers and never fixes
 a layout inside a pool slot (examples/s14_vulkan_numeric.rs:331-366), so the layout is
-this library's choice: the three weight matrices first, then the three scale arrays.
-Every tensor starts on a 16-byte boundary for the supported sizes.
+this library's choice.  Two byte orders of the same page exist:
 
-    MXFP4 page: w1 | w3 | w2 | s1 | s3 | s2   (13 369 344 B at hidden 4096 / inter 2048)
-    FP8   page: w1 | w3 | w2 | s1 | s3 | s2   (25 167 360 B at hidden 4096 / inter 2048)
+* the *tensor page* is the six tensors one after the other, each in the reference's tensor
+  ABI: ``w1 | w3 | w2 | s1 | s3 | s2`` with weights ``[N, K/2]`` bytes (low nibble = even k),
+  MXFP4 scales ``[N, K/32]`` UE8M0 bytes, FP8 scales ``[ceil(N/128), ceil(K/128)]``.  The CPU
+  oracle reads this one;
+* the *expert page* is what the GPU reads.  FP8 pages are tensor pages.  An MXFP4 expert page,
+  ``w1 | w3 | w2 | s13 | s2`` (same size: 13 369 344 B at hidden 4096 / inter 2048), is stored
+  for the unit of work of the tcgen05 kernel, a slice of 64 intermediate elements:
 
-Two byte orders of the same page exist:
+  - ``w1``, ``w3``: unchanged;
+  - ``w2``: by (slice s, row tile rt) blocks of 128 rows x 32 bytes, so that the 64 columns a
+    slice needs are ``hidden * 32`` consecutive bytes;
+  - ``s13``: by (slice s, K-atom a) 512-byte atoms holding the codes of the slice's 64 rows of
+    w1 (MMA rows 0-63) and 64 rows of w3 (MMA rows 64-127) for four scale blocks, in the order
+    the sm_100 block-scaled MMA takes scales into tensor memory: byte
+    ``(m % 32) * 16 + (m // 32) * 4 + block % 4``;
+  - ``s2``: by (slice pair p, row tile rt) atoms with the codes of 128 rows of w2 for blocks
+    ``4p .. 4p+3``, same byte order.
 
-* the *tensor page* holds every tensor in the reference's tensor ABI (weights ``[N, K/2]``
-  bytes with the low nibble at even k, MXFP4 scales ``[N, K/32]`` UE8M0 bytes, FP8 scales
-  ``[ceil(N/128), ceil(K/128)]``).  The CPU oracle reads this one;
-* the *expert page* the GPU reads differs for MXFP4 only: each scale array is stored atom by
-  atom, the order the sm_100 block-scaled tensor-core instructions take scales into tensor
-  memory (an atom = 128 rows x 4 scale blocks = 512 bytes; byte ``(n % 32) * 16 +
-  ((n % 128) // 32) * 4 + kb % 4`` of atom ``(n // 128, kb // 4)``; atoms of a 128-row tile follow
-  each other along K).  A unit of the kernel's stream is then 16 KB of codes plus 1 KB of
-  scales, both consecutive bytes.  ``to_expert_page`` converts once, at load time.
+``to_expert_page`` converts once, at load time (hidden and inter multiples of 128).
 """
 from __future__ import annotations
 
@@ -72,30 +76,28 @@ class ExpertPageLayout:
             page[o[name]:o[name] + t.size] = t
         return page
 
-    # ---- MXFP4 scale order of the page the GPU reads --------------------------------------
-    @staticmethod
-    def scales_to_page_order(s: np.ndarray, n: int, k: int) -> np.ndarray:
-        """[n, k/32] row-major codes -> page order (see the module docstring)."""
-        if n % 128 or k % 128:
-            raise ValueError("MXFP4 page scales: rows and K must be multiples of 128")
-        a = np.ascontiguousarray(s, np.uint8).reshape(n // 128, 4, 32, k // 128, 4)  # tile, r/32, r%32, atom, kb%4
-        return np.ascontiguousarray(a.transpose(0, 3, 2, 1, 4)).ravel()
-
-    @staticmethod
-    def scales_from_page_order(s: np.ndarray, n: int, k: int) -> np.ndarray:
-        a = np.ascontiguousarray(s, np.uint8).reshape(n // 128, k // 128, 32, 4, 4)  # tile, atom, r%32, r/32, kb%4
-        return np.ascontiguousarray(a.transpose(0, 3, 2, 1, 4)).reshape(n, k // 32)
-
+    # ---- the page the GPU reads -------------------------------------------------------------
     def to_expert_page(self, tensor_page: np.ndarray) -> np.ndarray:
-        """Tensor page -> the page the GPU kernels read (a copy; FP8 pages are unchanged)."""
+        """Tensor page -> expert page (a copy; FP8 pages are unchanged)."""
         page = np.array(tensor_page, dtype=np.uint8, copy=True)
         if self.kind != PAGE_MXFP4:
             return page
+        h, i = self.hidden, self.inter
+        if h % 128 or i % 128:
+            raise ValueError("MXFP4 expert page: hidden and inter must be multiples of 128")
+        t = self.split(np.asarray(tensor_page, np.uint8))
         o = self.offsets
-        for name, n, k in (("s1", self.inter, self.hidden), ("s3", self.inter, self.hidden),
-                           ("s2", self.hidden, self.inter)):
-            size = n * k // 32
-            page[o[name]:o[name] + size] = self.scales_to_page_order(tensor_page[o[name]:o[name] + size], n, k)
+        # w2 [h, i/2] -> (slice, row tile, row, 32 bytes)
+        w2 = t["w2"].reshape(h // 128, 128, i // 64, 32).transpose(2, 0, 1, 3)
+        page[o["w2"]:o["w2"] + self.weight_bytes] = np.ascontiguousarray(w2).ravel()
+        # s1, s3 [i, h/32] -> (slice, atom, m % 32, m // 32, block % 4), m = row in slice (+ 64 for w3)
+        s13 = np.concatenate([t["s1"].reshape(i // 64, 64, h // 128, 4), t["s3"].reshape(i // 64, 64, h // 128, 4)],
+                             axis=1)  # (slice, m, atom, c)
+        s13 = s13.reshape(i // 64, 4, 32, h // 128, 4).transpose(0, 3, 2, 1, 4)
+        page[o["s1"]:o["s1"] + 2 * self.up_scale_bytes] = np.ascontiguousarray(s13).ravel()
+        # s2 [h, i/32] -> (slice pair, row tile, r % 32, r // 32, block % 4)
+        s2 = t["s2"].reshape(h // 128, 4, 32, i // 128, 4).transpose(3, 0, 2, 1, 4)
+        page[o["s2"]:o["s2"] + self.down_scale_bytes] = np.ascontiguousarray(s2).ravel()
         return page
 
     def split(self, page: np.ndarray) -> dict:

@@ -118,22 +118,23 @@ S14_API int32_t s14_shape_mxfp4_scale_bytes(s14_matvec_shape shape, uint64_t *ou
 S14_API int32_t s14_shape_fp8_weight_bytes(s14_matvec_shape shape, uint64_t *out);
 S14_API int32_t s14_shape_fp8_scale_bytes(s14_matvec_shape shape, uint64_t *out);
 
-/* MXFP4 expert page = w1 | w3 | w2 | s1 | s3 | s2 in one pool slot (S14_EXPERT_PAGE_BYTES at
- * hidden 4096, intermediate 2048).  The weights are the checkpoint's tensors ([N, K/2] bytes,
- * low nibble = even k).  The scale arrays are stored atom by atom, the order in which the
- * sm_100 block-scaled tensor-core instructions take scales into tensor memory: the code of row
- * n, scale block kb of an [N, K] matrix is byte
- *   ((n / 128) * (K / 128) + kb / 4) * 512 + (n % 32) * 16 + ((n % 128) / 32) * 4 + kb % 4
- * of its array (N and K multiples of 128).  These host functions reorder one scale tensor, or
- * turn a page made of the six checkpoint tensors into an expert page, once, at load time.
- * The reference fixes no layout inside a slot (examples/s14_vulkan_numeric.rs:331-366 uploads
- * six buffers), so they have no counterpart there.  FP8 pages keep their tensors unchanged. */
-S14_API int32_t s14_mxfp4_scales_to_page_order(uint32_t n, uint32_t k, const uint8_t *row_major,
-                                               uint8_t *page_order);
-S14_API int32_t s14_mxfp4_scales_from_page_order(uint32_t n, uint32_t k, const uint8_t *page_order,
-                                                 uint8_t *row_major);
+/* MXFP4 expert page = w1 | w3 | w2 | s13 | s2 in one pool slot (S14_EXPERT_PAGE_BYTES at hidden
+ * 4096, intermediate 2048): the bytes of the six checkpoint tensors, stored for the unit of work
+ * of the tcgen05 kernel, a slice of 64 intermediate elements of one expert.
+ *   w1, w3  [inter, hidden/2] bytes as the checkpoint has them (low nibble = even k);
+ *   w2      by (slice s, row tile rt): 128 rows x 32 bytes, so a slice's columns are contiguous;
+ *   s13     by (slice s, four scale blocks): the codes of the slice's 64 rows of w1 and 64 rows of
+ *           w3, 512 bytes in the order the block-scaled MMA takes scales into tensor memory;
+ *   s2      by (slice pair, row tile): the codes of 128 rows of w2 for four scale blocks, same order.
+ * hidden and intermediate must be multiples of 128.  A "tensor page" is the six tensors one after
+ * the other in the checkpoint's ABI (w1 | w3 | w2 | s1 | s3 | s2); these host functions convert
+ * between the two, once, at load time.  The reference fixes no layout inside a slot
+ * (examples/s14_vulkan_numeric.rs:331-366 uploads six buffers), so they have no counterpart
+ * there.  FP8 pages keep their tensors unchanged. */
 S14_API int32_t s14_mxfp4_expert_page_from_tensors(uint32_t hidden, uint32_t inter, const uint8_t *tensor_page,
                                                    uint8_t *page);
+S14_API int32_t s14_mxfp4_expert_page_to_tensors(uint32_t hidden, uint32_t inter, const uint8_t *page,
+                                                 uint8_t *tensor_page);
 
 /* validate_ue8m0_codes / validate_e4m3fn_codes (s14_vulkan.rs:143-156): host
  * bytes, checked before upload.  On failure *bad_index (may be NULL) receives the

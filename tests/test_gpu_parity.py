@@ -286,8 +286,14 @@ def test_moe_layer_verify_block(ctx, oracle, n_tokens):
             else:
                 ref = oracle.moe_layer_acc64(x[t], [pages[i] for i in ids], w, shared, 0, hidden, inter)
                 assert_pairwise_close(oracle, y[t], ref)
+            # a token of a block against its own one-token call: bit-identical in reference order; in
+            # pairwise order the one-token call runs the tcgen05 kernel and the block the F32 kernels,
+            # two summation orders inside the same bound
             single = run_layer(ctx, x[t:t + 1], pages_dev, shared_dev, [routes[t]], L.PAGE_MXFP4, hidden, inter)[0]
-            assert np.array_equal(single.view(np.uint32), y[t].view(np.uint32))
+            if mode == L.ACCUM_REFERENCE:
+                assert np.array_equal(single.view(np.uint32), y[t].view(np.uint32))
+            else:
+                assert_pairwise_close(oracle, single, ref)
     ctx.set_accumulation(L.ACCUM_PAIRWISE)
 
 

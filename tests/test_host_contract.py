@@ -272,35 +272,9 @@ def test_upload_needs_a_device_pool():
         p.upload_page_async(r, buf.ctypes.data, 16)
 
 
-def test_mxfp4_scale_page_order_round_trip_and_formula():
-    """The page order of MXFP4 scale codes: the C functions, the numpy mirror and the stated
-    byte formula agree, and the two directions are inverse to each other."""
-    import ctypes as C
-
-    import numpy as np
-
-    from colormlm_b200 import _lib as L
-    from colormlm_b200.pages import ExpertPageLayout
-
-    g = np.random.default_rng(5)
-    for n, k in ((128, 128), (256, 1024), (1024, 2048)):
-        s = g.integers(0, 255, (n, k // 32), dtype=np.uint8)
-        want = ExpertPageLayout.scales_to_page_order(s, n, k)
-        got = np.empty_like(want)
-        L.check(L.lib().s14_mxfp4_scales_to_page_order(n, k, s.ctypes.data_as(C.c_void_p), got.ctypes.data_as(C.c_void_p)))
-        assert np.array_equal(want, got)
-        for r, kb in ((0, 0), (37, 5 % (k // 32)), (n - 1, k // 32 - 1), (n // 2 + 33, 2)):
-            off = ((r // 128) * (k // 128) + kb // 4) * 512 + (r % 32) * 16 + ((r % 128) // 32) * 4 + kb % 4
-            assert got[off] == s[r, kb]
-        back = np.empty_like(s)
-        L.check(L.lib().s14_mxfp4_scales_from_page_order(n, k, got.ctypes.data_as(C.c_void_p), back.ctypes.data_as(C.c_void_p)))
-        assert np.array_equal(back, s)
-        assert np.array_equal(ExpertPageLayout.scales_from_page_order(want, n, k), s)
-    with pytest.raises(L.S14Error):
-        L.check(L.lib().s14_mxfp4_scales_to_page_order(100, 128, None, None))
-
-
-def test_expert_page_from_tensors_matches_the_numpy_mirror():
+def test_expert_page_from_tensors_matches_the_numpy_mirror_and_the_stated_offsets():
+    """The MXFP4 expert page: the C conversion, the numpy mirror and the byte offsets stated in
+    the header agree, and converting back returns the tensors."""
     import ctypes as C
 
     import numpy as np
@@ -309,13 +283,33 @@ def test_expert_page_from_tensors_matches_the_numpy_mirror():
     from colormlm_b200 import synth
     from colormlm_b200.pages import ExpertPageLayout
 
-    hidden, inter = 1024, 512 + 512
-    lay = ExpertPageLayout(hidden, inter)
-    tensor_page = synth.mxfp4_expert_page(synth.rng(9), hidden, inter)
-    want = lay.to_expert_page(tensor_page)
-    got = np.empty_like(want)
-    L.check(L.lib().s14_mxfp4_expert_page_from_tensors(hidden, inter, tensor_page.ctypes.data_as(C.c_void_p),
-                                                       got.ctypes.data_as(C.c_void_p)))
-    assert np.array_equal(want, got)
-    assert np.array_equal(want[:3 * lay.weight_bytes], tensor_page[:3 * lay.weight_bytes])  # weights as they are
-    assert not np.array_equal(want, tensor_page)
+    for hidden, inter in ((1024, 1024), (2048, 1024), (512, 256)):
+        lay = ExpertPageLayout(hidden, inter)
+        tensor_page = synth.mxfp4_expert_page(synth.rng(9 + hidden), hidden, inter)
+        want = lay.to_expert_page(tensor_page)
+        got = np.empty_like(want)
+        L.check(L.lib().s14_mxfp4_expert_page_from_tensors(hidden, inter, tensor_page.ctypes.data_as(C.c_void_p),
+                                                           got.ctypes.data_as(C.c_void_p)))
+        assert np.array_equal(want, got)
+        assert np.array_equal(want[:2 * lay.weight_bytes], tensor_page[:2 * lay.weight_bytes])  # w1, w3 as they are
+        assert not np.array_equal(want, tensor_page)
+        t, o = lay.split(tensor_page), lay.offsets
+        g = np.random.default_rng(1)
+        for _ in range(200):
+            n, kb = int(g.integers(hidden)), int(g.integers(inter // 32))
+            off = (((kb // 2) * (hidden // 128) + n // 128) * 128 + n % 128) * 32 + (kb % 2) * 16
+            assert np.array_equal(got[o["w2"] + off:o["w2"] + off + 16], t["w2"].reshape(hidden, inter // 2)[n, kb * 16:kb * 16 + 16])
+            r = n % 128
+            off = ((kb // 4) * (hidden // 128) + n // 128) * 512 + (r % 32) * 16 + (r // 32) * 4 + kb % 4
+            assert got[o["s2"] + off] == t["s2"].reshape(hidden, inter // 32)[n, kb]
+            i, kb = int(g.integers(inter)), int(g.integers(hidden // 32))
+            for mat, name in ((0, "s1"), (1, "s3")):
+                m = i % 64 + 64 * mat
+                off = ((i // 64) * (hidden // 128) + kb // 4) * 512 + (m % 32) * 16 + (m // 32) * 4 + kb % 4
+                assert got[o["s1"] + off] == t[name].reshape(inter, hidden // 32)[i, kb]
+        back = np.empty_like(tensor_page)
+        L.check(L.lib().s14_mxfp4_expert_page_to_tensors(hidden, inter, got.ctypes.data_as(C.c_void_p),
+                                                         back.ctypes.data_as(C.c_void_p)))
+        assert np.array_equal(back, tensor_page)
+    with pytest.raises(L.S14Error):
+        L.check(L.lib().s14_mxfp4_expert_page_from_tensors(100, 128, None, None))

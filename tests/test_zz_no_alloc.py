@@ -35,9 +35,9 @@ def test_noalloc_layer_matches_context_layer_on_repeated_calls(hidden, inter):
     pages = [torch.from_numpy(lay.to_expert_page(synth.mxfp4_expert_page(g, hidden, inter))).cuda() for _ in range(8)]
     xs = torch.from_numpy(synth.activations(g, 2, hidden)).cuda()
     w = [0.3, 0.25, 0.15, 0.12, 0.1, 0.08]
-    # the entry point without a context runs the warp-level tensor-core kernels; the context it is
-    # compared with is told to run the same ones (it prefers the tcgen05 kernels otherwise)
-    os.environ["S14_TENSOR_PATH"] = "mma_sync"
+    # the entry point without a context runs the F32 pairwise kernels; the context it is compared
+    # with is told to run the same ones (it prefers the tcgen05 kernel otherwise)
+    os.environ["S14_TENSOR_PATH"] = "off"
     try:
         ctx = S14Context(0)
     finally:
