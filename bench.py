@@ -4,16 +4,16 @@ experts + the shared MXFP4 expert, 256 routed experts per layer resident in the 
 
     python bench.py [--gpus N] [--steps K] [--warmup W] [--impl reference] [--accum pairwise|reference]
 
-A step is one layer-token: one token through one MoE layer (router, up phase, down phase,
-ordered mix).  14 layers of 257 expert pages each are resident (the S14 stack, 48 GB); the
+A step is one layer-token: one token through one MoE layer (router kernel, then the layer
+kernel: up projections, SwiGLU, down projection, sums over slices, ordered mix).  14 layers of 257 expert pages each are resident (the S14 stack, 48 GB); the
 steps walk the layers round-robin with a fresh token each, so consecutive steps read
 disjoint pages and the 96 MB a step touches never comes from L2.  Steps are replayed from
 a CUDA graph of 14 layer-steps; time is taken with CUDA events on the launching stream.
 
 One JSON line is printed by rank 0.  `value` is layer-tokens/s with inputs resident in HBM,
 `e2e` the same through the host-buffer C-ABI call (H2D of the token and D2H of the result
-inside the timed region), `roofline` the up-phase kernel against the measured copy
-bandwidth, `cpu_baseline` the CPU oracle on this box's host cores on a bounded sample.
+inside the timed region), `roofline` the layer kernel (timed alone in a CUDA graph of 14
+launches with fixed routes, over the same resident pages) against the measured copy bandwidth, `cpu_baseline` the CPU oracle on this box's host cores on a bounded sample.
 `--impl reference` times that CPU implementation alone.
 """
 from __future__ import annotations
@@ -37,9 +37,8 @@ PAGE_BYTES = 13_369_344
 # algorithmic bytes of one layer-token: 7 expert pages + router weights + bias + x + y
 ROUTER_BYTES = N_EXPERTS * HIDDEN * 2 + N_EXPERTS * 4
 STEP_BYTES = 7 * PAGE_BYTES + ROUTER_BYTES + HIDDEN * 4 + HIDDEN * 4
-# up-phase kernel: w1, w3 and their scales of 7 experts, x in, 7 hidden vectors out
-UP_BYTES = 7 * (2 * (HIDDEN * INTER // 2) + 2 * (HIDDEN * INTER // 32)) + HIDDEN * 4 + 7 * INTER * 4
-DOWN_BYTES = 7 * ((HIDDEN * INTER // 2) + (HIDDEN * INTER // 32)) + 7 * INTER * 4 + 7 * HIDDEN * 4
+# layer kernel: 7 expert pages, x in, y out
+LAYER_BYTES = 7 * PAGE_BYTES + HIDDEN * 4 + HIDDEN * 4
 WORKLOAD = ("moe_layer_decode: 1 token, router top-6 of 256 + 6 routed + 1 shared MXFP4 expert, "
             "hidden 4096, intermediate 2048")
 
@@ -271,9 +270,10 @@ def run_gpu(args) -> None:
 
     _note("layers resident")
     stream = torch.cuda.Stream()
-    # router, up phase, down phase + mix; expert parallel adds the slot memset is not a kernel of ours,
-    # the all-reduce is NCCL's, the mix is one more kernel
-    kernels_per_step = 3 if world == 1 else 4
+    # pairwise order: router + layer kernel; reference order: router, up, down, mix.  Expert parallel adds
+    # the mix of the exchanged slots (the slot memset is not a kernel of ours, the all-reduce is NCCL's)
+    layer_kernels = 1 if args.accum == "pairwise" else 2
+    kernels_per_step = (1 + layer_kernels + (1 if args.accum != "pairwise" else 0)) if world == 1 else 2 + layer_kernels
 
     def capture(n_steps: int, first: int):
         g = torch.cuda.CUDAGraph()
@@ -297,7 +297,7 @@ def run_gpu(args) -> None:
     else:
         # NCCL all-reduces replayed from a CUDA graph ran ~10x slower than eager ones here
         # (0.95 ms against 0.1 ms per step at 2 GPUs), so the expert-parallel steps are launched eagerly
-        launch_mode = "eager launches (router, up, down, NCCL all-reduce, mix per step)"
+        launch_mode = "eager launches (router, layer kernel, NCCL all-reduce, mix per step)"
         graph = graph_rem = None
 
     def replay(n_full: int, with_rem: bool):
@@ -342,16 +342,48 @@ def run_gpu(args) -> None:
     # one token stream: with several GPUs the experts of the same tokens are spread over the ranks
     value = args.steps / (ms / 1e3)
 
-    # per-kernel durations (separate loop, blocking calls, not part of the headline number)
-    ctx.set_kernel_timing(True)
-    with torch.cuda.stream(stream):
-        for i in range(4 * N_LAYERS):
-            enqueue_step(i, stream.cuda_stream)
-    kt, calls = ctx.kernel_times()
-    ctx.set_kernel_timing(False)
-    up_ms = kt["up"] / max(1, calls)
+    # The layer kernel alone: a CUDA graph of one launch per resident layer with fixed routes (six routed
+    # experts + the shared one, other pages every launch), replayed back to back and timed with CUDA events
+    # on the launching stream.  Not part of the headline number.
+    from colormlm_b200.s14 import TokenRoute
+
+    layer_ms = None
+    if world == 1:
+        rr = np.random.default_rng(7)
+        fixed = []
+        for k in range(N_LAYERS):
+            ly = layers[k % n_layers]
+            ids = rr.permutation(N_EXPERTS)[:TOP_K].tolist()
+            fixed.append(([TokenRoute(ids, [1.0 / TOP_K] * TOP_K, [ly["pages"].data_ptr() + e * PAGE_BYTES for e in ids])],
+                          ly["shared"]))
+
+        def enqueue_layer_only(k):
+            route, shared = fixed[k]
+            ctx.cmd_moe_layer(xs[k:k + 1], ys[k:k + 1], route, shared, L.PAGE_MXFP4, HIDDEN, INTER,
+                              stream=stream.cuda_stream)
+
+        with torch.cuda.stream(stream):
+            for k in range(2):
+                enqueue_layer_only(k)
+        stream.synchronize()
+        g_layer = torch.cuda.CUDAGraph()
+        with torch.cuda.stream(stream):
+            with torch.cuda.graph(g_layer, stream=stream):
+                for k in range(N_LAYERS):
+                    enqueue_layer_only(k)
+        reps = 60
+        with torch.cuda.stream(stream):
+            for _ in range(5):
+                g_layer.replay()
+            k0, k1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            k0.record(stream)
+            for _ in range(reps):
+                g_layer.replay()
+            k1.record(stream)
+        stream.synchronize()
+        layer_ms = k0.elapsed_time(k1) / (reps * N_LAYERS)
     peak, peak_kind = measured_peaks()
-    achieved = UP_BYTES / (up_ms * 1e-3) / 1e9 if up_ms > 0 else None
+    achieved = LAYER_BYTES / (layer_ms * 1e-3) / 1e9 if layer_ms else None
 
     # end to end through the host-buffer call: pinned x in, y (+ route) out, every step
     hx = torch.randn((n_tok, HIDDEN), dtype=torch.float32).pin_memory()
@@ -418,12 +450,15 @@ def run_gpu(args) -> None:
                        if world > 1 else "single"},
             "hbm_gbs": value * STEP_BYTES / 1e9, "hbm_frac_of_measured_peak": value * STEP_BYTES / 1e9 / (peak * world),
             "algorithmic_bytes_per_step": STEP_BYTES,
-            "roofline": {"bound": "hbm", "kernel": "expert up phase (w1, w3, SwiGLU) of 7 experts",
+            "roofline": {"bound": "hbm",
+                         "kernel": ("k_moe_layer_umma: 7 MXFP4 experts, up projections + SwiGLU + down projection + mix"
+                                    if args.accum == "pairwise" else "reference-order layer kernels (up, down, mix)"),
                          "achieved": achieved, "peak": peak, "unit": "GB/s",
                          "frac": achieved / peak if achieved else None,
-                         "peak_kind": peak_kind, "traffic": None, "bytes_per_launch": UP_BYTES,
-                         "ms_per_launch": up_ms,
-                         "other_kernels_ms": {k: v / max(1, calls) for k, v in kt.items() if k != "up"}},
+                         "peak_kind": peak_kind, "traffic": None, "bytes_per_launch": LAYER_BYTES,
+                         "ms_per_launch": layer_ms,
+                         "timed": "CUDA graph of 14 layer launches with fixed routes, 60 replays, CUDA events",
+                         "rest_of_step_ms": (ms / args.steps - layer_ms) if layer_ms else None},
             "cpu_baseline": cpu,
             "e2e": {"value": e2e_value, "unit": "layer-tokens/s", "h2d_bytes_per_step": HIDDEN * 4,
                     "d2h_bytes_per_step": HIDDEN * 4 + TOP_K * 8, "steps": e2e_steps},

@@ -43,14 +43,14 @@ constexpr uint32_t kMmaWarp0 = 8;              // warps 8 and 9: one issuing thr
 constexpr uint32_t kProdWarp0 = 10;            // warps 10..13 copy
 constexpr uint32_t kProdThreads = 128;
 constexpr uint32_t kThreads = 512;             // warps 14 and 15 only help with the digits and the final sums
-constexpr uint32_t kDRing = 2;                 // down stages whose four accumulators are in flight (one per issuing thread)
+constexpr uint32_t kDRing = 4;                 // down stages whose four accumulators are in flight (two per issuing thread)
 constexpr uint32_t kItemSlots = 4;             // items a CTA can hold (digit tiles of their hidden values)
 // tensor memory columns
 constexpr uint32_t kTmemCols = 512;
 constexpr uint32_t kColD = 0;                  // kDRing x 4 accumulators x 16
 constexpr uint32_t kColU = kColD + kDRing * 64;    // 2 items x 2 issuing threads x 16
-constexpr uint32_t kColSfa = kColU + 64;       // kRing x 16: weight scales of a stage
-constexpr uint32_t kColSfbX = kColSfa + kRing * 16;  // hidden / 32: scales of the token's digit rows
+constexpr uint32_t kColSfa = kColU + 64;       // 2 x 16: weight scales of the stage each issuing thread is at
+constexpr uint32_t kColSfbX = kColSfa + 2 * 16;  // hidden / 32: scales of the token's digit rows
 constexpr uint32_t kColSfbH = kColSfbX + 128;  // kItemSlots x 4: scales of the hidden values' digit rows
 static_assert(kColSfbH + kItemSlots * 4 <= kTmemCols, "tensor memory map");
 constexpr uint32_t kMaxHidden = 4096;          // 128 columns of token digit scales
@@ -322,6 +322,12 @@ k_moe_layer_umma(const JobTable *__restrict__ dev_table, const __grid_constant__
     // The token does not depend on the router: its digits are built while the router runs; the
     // job table is read only after the router has finished.
     build_digits(x, x, 1, hidden, sBx, 0, sE, tid, kThreads);
+    __syncthreads();  // every block exponent is written
+    if (warp < 2u * kEpiGroup / 32u) {
+        store_digit_scales(tmem + kColSfbX, sE, 1, hidden, 0, warp, lane);
+        fence_before();
+        mbar_arrive(bar(kBarXReady));
+    }
     cudaGridDependencySynchronize();
     const JobTable &tab = table_of(dev_table, param_table);
     const uint32_t n_jobs = tab.n_jobs, n_items = n_jobs * S, grid = gridDim.x, cta = blockIdx.x;
@@ -401,16 +407,20 @@ k_moe_layer_umma(const JobTable *__restrict__ dev_table, const __grid_constant__
             const uint64_t a_up0 = smem_desc(smem_u32(sA), 1, 64, 2), b_x0 = smem_desc(smem_u32(sBx), 1, 64, 2);
             const uint64_t sf_desc0 = smem_desc(smem_u32(sSF), 0, 8, 0);
             bool ok = mbar_wait(bar(kBarXReady), 0, &abort_flag);
+            CYC_DECL(8);
             for (uint32_t i = m; i < nU + nD && ok; i += 2u) {
                 const uint32_t s = i % kRing, par = (i / kRing) & 1u;
-                const uint32_t sfa_t = tmem + kColSfa + s * 16u;
+                // one scale slot per thread: a thread's copies and MMAs execute in issue order
+                const uint32_t sfa_t = tmem + kColSfa + m * 16u;
                 const uint64_t sfd = sf_desc0 + s * (kStageSf >> 4);
                 if (i < nU) {
                     const uint32_t l = i / KU, ks = i - l * KU;
                     const bool first = ks < 2u;  // this thread's first unit of the item
+                    CYC_LAP(0);
                     if (first && l >= 2u) ok = mbar_wait(bar(kBarUFree + (l & 1u)), ((l >> 1) - 1u) & 1u, &abort_flag);
                     ok = ok && mbar_wait(bar(kBarFull + s), par, &abort_flag);
                     if (!ok) break;
+                    CYC_LAP(1);
                     if (i == 0) TRACE(3);
                     asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
                     fence_after();
@@ -427,12 +437,19 @@ k_moe_layer_umma(const JobTable *__restrict__ dev_table, const __grid_constant__
                     }
                     umma_commit(bar(kBarDone + s));
                     if (ks + 2u >= KU) umma_commit(bar(kBarUDone + (l & 1u)));
+                    CYC_LAP(2);
                     if (m == 0 && i + 2u >= nU) TRACE(4);
                 } else {
-                    // down stage vg: vg and i have the same parity, so accumulator set vg % 2 is this thread's
-                    const uint32_t vg = i - nU, l = vg / DS, sl = (q0 + l) % S, acc = vg & 1u;
-                    ok = mbar_wait(bar(kBarHReady + l), 0, &abort_flag) && mbar_wait(bar(kBarFull + s), par, &abort_flag) &&
-                         (vg < kDRing || mbar_wait(bar(kBarDFree + acc), ((vg >> 1) - 1u) & 1u, &abort_flag));
+                    // down stage vg: vg and i have the same parity, so accumulator sets vg % 4 = m and m + 2 are
+                    // this thread's; the same sets are read by epilogue group m
+                    const uint32_t vg = i - nU, l = vg / DS, sl = (q0 + l) % S, acc = vg & 3u;
+                    CYC_LAP(0);
+                    ok = mbar_wait(bar(kBarHReady + l), 0, &abort_flag);
+                    CYC_LAP(3);
+                    ok = ok && mbar_wait(bar(kBarFull + s), par, &abort_flag);
+                    CYC_LAP(4);
+                    ok = ok && (vg < kDRing || mbar_wait(bar(kBarDFree + acc), ((vg >> 2) - 1u) & 1u, &abort_flag));
+                    CYC_LAP(5);
                     if (!ok) break;
                     asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
                     fence_after();
@@ -446,8 +463,10 @@ k_moe_layer_umma(const JobTable *__restrict__ dev_table, const __grid_constant__
                                   bd, kIdesc | (asf << 29), (sfa_t + b * 4u) | (asf << 30), tmem + kColSfbH + l * 4u, 0u);
                     umma_commit(bar(kBarDone + s));
                     umma_commit(bar(kBarDDone + acc));
+                    CYC_LAP(6);
                 }
             }
+            if (m == 0) CYC_STORE(0, 8);
             // nothing of this CTA's tensor work is in flight when the tensor memory is freed
             umma_commit(bar(kBarFin));
             mbar_wait(bar(kBarFin), 0, &abort_flag);
@@ -459,9 +478,6 @@ k_moe_layer_umma(const JobTable *__restrict__ dev_table, const __grid_constant__
         const uint32_t grp = warp >> 2, row = tid & (kEpiGroup - 1u);
         const uint32_t lane_base = tmem + (((warp & 3u) * 32u) << 16);
         bool ok = true;
-        store_digit_scales(tmem + kColSfbX, sE, 1, hidden, 0, warp, lane);
-        fence_before();
-        mbar_arrive(bar(kBarXReady));
         if (grp == 0u) {
             for (uint32_t l = 0; l < n_it; ++l) {
                 const uint32_t q = q0 + l, j = q / S;
@@ -531,10 +547,10 @@ k_moe_layer_umma(const JobTable *__restrict__ dev_table, const __grid_constant__
             if (tid == 0) TRACE(6);
         }
         for (uint32_t vg = grp; vg < nD; vg += 2u) {
-            const uint32_t acc = vg & 1u;
+            const uint32_t acc = vg & 3u;
             const uint32_t l = vg / DS, vloc = vg - l * DS, q = q0 + l;
             // every phase of this barrier is waited for by this group, in order
-            ok = __all_sync(0xffffffffu, ok && mbar_wait(bar(kBarDDone + acc), (vg >> 1) & 1u, &abort_flag));
+            ok = __all_sync(0xffffffffu, ok && mbar_wait(bar(kBarDDone + acc), (vg >> 2) & 1u, &abort_flag));
             if (!ok) break;
             fence_after();
             uint32_t a[4][8];
@@ -590,14 +606,21 @@ k_moe_layer_umma(const JobTable *__restrict__ dev_table, const __grid_constant__
         const uint32_t rows = n1 - n0, chunks = S >> 2;
         double *red = reinterpret_cast<double *>(smem);                       // [job][chunk][row]
         float *dj = reinterpret_cast<float *>(smem + (size_t)n_jobs * chunks * rows * 8u);  // [job][row]
-        for (uint32_t t = tid; t < n_jobs * chunks * rows; t += kThreads) {
-            const uint32_t r = t % rows, jc = t / rows;  // jc = job * chunks + chunk: four slices of one job
-            const float *p = part + (size_t)jc * 4u * hidden + n0 + r;
-            double sum = (double)__ldcg(p);
-            sum += (double)__ldcg(p + hidden);
-            sum += (double)__ldcg(p + 2u * (size_t)hidden);
-            sum += (double)__ldcg(p + 3u * (size_t)hidden);
-            red[t] = sum;
+        for (uint32_t t0 = tid; t0 < n_jobs * chunks * rows; t0 += 4u * kThreads) {
+            float v[4][4];  // four tasks at a time, so that sixteen loads are in flight per thread
+#pragma unroll
+            for (uint32_t k = 0; k < 4; ++k) {
+                const uint32_t t = min(t0 + k * kThreads, n_jobs * chunks * rows - 1u);
+                const uint32_t r = t % rows, jc = t / rows;  // jc = job * chunks + chunk: four slices of one job
+                const float *p = part + (size_t)jc * 4u * hidden + n0 + r;
+#pragma unroll
+                for (uint32_t c = 0; c < 4; ++c) v[k][c] = __ldcg(p + (size_t)c * hidden);
+            }
+#pragma unroll
+            for (uint32_t k = 0; k < 4; ++k) {
+                const uint32_t t = t0 + k * kThreads;
+                if (t < n_jobs * chunks * rows) red[t] = (((double)v[k][0] + (double)v[k][1]) + (double)v[k][2]) + (double)v[k][3];
+            }
         }
         __syncthreads();
         for (uint32_t t = tid; t < n_jobs * rows; t += kThreads) {
