@@ -39,19 +39,22 @@ constexpr uint32_t kRing = 8;                  // stages in flight per CTA
 constexpr uint32_t kStageA = 128 * 128;        // 16 KB of codes: an up unit (128 rows x 256 K) or four down blocks (128 rows x 64 K each)
 constexpr uint32_t kStageSf = 4 * 512;         // scale atoms of a stage: two (up unit) or four (down stage)
 constexpr uint32_t kEpiGroup = 128;            // two epilogue groups of four warps
-constexpr uint32_t kMmaWarp0 = 8;              // warps 8 and 9: one issuing thread each
+constexpr uint32_t kMmaWarp0 = 8;              // warps 8, 9, 14, 15: one issuing thread each (lane 0)
+constexpr uint32_t kIssuers = 4;
 constexpr uint32_t kProdWarp0 = 10;            // warps 10..13 copy
 constexpr uint32_t kProdThreads = 128;
-constexpr uint32_t kThreads = 512;             // warps 14 and 15 only help with the digits and the final sums
-constexpr uint32_t kDRing = 4;                 // down stages whose four accumulators are in flight (two per issuing thread)
+constexpr uint32_t kThreads = 512;
+constexpr uint32_t kDRing = 4;                 // down stages whose four accumulators are in flight (one per issuing thread)
 constexpr uint32_t kItemSlots = 4;             // items a CTA can hold (digit tiles of their hidden values)
 // tensor memory columns
 constexpr uint32_t kTmemCols = 512;
 constexpr uint32_t kColD = 0;                  // kDRing x 4 accumulators x 16
-constexpr uint32_t kColU = kColD + kDRing * 64;    // 2 items x 2 issuing threads x 16
-constexpr uint32_t kColSfa = kColU + 64;       // 2 x 16: weight scales of the stage each issuing thread is at
-constexpr uint32_t kColSfbX = kColSfa + 2 * 16;  // hidden / 32: scales of the token's digit rows
-constexpr uint32_t kColSfbH = kColSfbX + 128;  // kItemSlots x 4: scales of the hidden values' digit rows
+constexpr uint32_t kColU = kColD + kDRing * 64;    // 2 issuing threads x 16 (one item at a time)
+constexpr uint32_t kColSfa = kColU + 32;       // kIssuers x 16: weight scales of the stage each issuing thread is at
+// Scales of digit rows: an atom (four scale blocks) is four columns (N-rows 0-31, 32-63, ...; a 16-row
+// operand uses the first).  Scale addresses given to the MMA stay atom-aligned.
+constexpr uint32_t kColSfbX = kColSfa + kIssuers * 16;  // hidden / 32: scales of the token's digit rows
+constexpr uint32_t kColSfbH = kColSfbX + 128;           // kItemSlots x 4: scales of the hidden values' digit rows
 static_assert(kColSfbH + kItemSlots * 4 <= kTmemCols, "tensor memory map");
 constexpr uint32_t kMaxHidden = 4096;          // 128 columns of token digit scales
 constexpr uint32_t kMaxBlocks = kMaxHidden / 32;
@@ -60,13 +63,14 @@ constexpr uint32_t kSpinGlobal = 1u << 20;     // polls (100 ns apart) of the it
 constexpr uint32_t kItemCounter = 1, kExitCounter = 2;  // in the context's counter array ([0] is the router's)
 
 // Bar indices in the static barrier array.
-constexpr uint32_t kBarFull = 0;                      // stage filled (128 copying threads)
-constexpr uint32_t kBarDone = kRing;                  // the stage's MMAs have completed (the copies may reuse it)
-constexpr uint32_t kBarDFree = 2 * kRing;             // a down stage's accumulators have been read
+constexpr uint32_t kBarFull = 0;                      // ring slot filled with an up unit (128 copying threads)
+constexpr uint32_t kBarDFull = kRing;                 // ring slot filled with a down stage
+constexpr uint32_t kBarDone = 2 * kRing;              // the slot's MMAs have completed (the copies may reuse it)
+constexpr uint32_t kBarDFree = 3 * kRing;             // a down stage's accumulators have been read
 constexpr uint32_t kBarDDone = kBarDFree + kDRing;    // a down stage's accumulators are complete
 constexpr uint32_t kBarUDone = kBarDDone + kDRing;    // an item's up accumulators are complete
-constexpr uint32_t kBarUFree = kBarUDone + 2;         // ... has been read
-constexpr uint32_t kBarHReady = kBarUFree + 2;        // an item's hidden digits and scales are in place
+constexpr uint32_t kBarUFree = kBarUDone + 1;         // ... have been read
+constexpr uint32_t kBarHReady = kBarUFree + 1;        // an item's hidden digits and scales are in place
 constexpr uint32_t kBarXReady = kBarHReady + kItemSlots;  // the token's digit scales are in tensor memory
 constexpr uint32_t kBarFin = kBarXReady + 1;          // both issuing threads have finished
 constexpr uint32_t kBars = kBarFin + 1;
@@ -213,21 +217,20 @@ __device__ void build_digits(const float *v0, const float *v1, uint32_t n_vec, u
 // lane quadrant takes every atom; warps 0-3 the even groups of four atoms, warps 4-7 the odd ones).
 // Column 4a of lane l holds the codes of N-row l for scale blocks 4a..4a+3: digit row l < 8 of a
 // block with exponent E has the code 127 + E - 23 + 3l; rows 8-15 are zero rows, columns 4a+1..4a+3
-// belong to N-rows 32 and up, which a 16-column MMA does not read.
-__device__ __forceinline__ void store_digit_scales(uint32_t tmem_sfb, const uint8_t *sE, uint32_t n_slots, uint32_t K,
-                                                   uint32_t sfb_cols, uint32_t warp, uint32_t lane) {
+// belong to N-rows 32 and up, which a 16-column MMA does not use.
+__device__ __forceinline__ void store_digit_scales(uint32_t tmem_sfb, const uint8_t *sE, uint32_t K, uint32_t warp,
+                                                   uint32_t lane) {
     const uint32_t groups = K >> 9;  // groups of four atoms (512 K-elements, 16 blocks)
     const uint32_t bias = 0x01010101u * (4u + 3u * (lane & 7u));
     const uint32_t quad = tmem_sfb + (((warp & 3u) * 32u) << 16);
-    for (uint32_t q = warp >> 2; q < n_slots * groups; q += 2u) {
-        const uint32_t b = q / groups, g = q - b * groups;
-        const uint4 e = *reinterpret_cast<const uint4 *>(sE + b * kMaxBlocks + g * 16u);
+    for (uint32_t g = warp >> 2; g < groups; g += 2u) {
+        const uint4 e = *reinterpret_cast<const uint4 *>(sE + g * 16u);
         const uint32_t one = 0x7F7F7F7Fu;
         const uint32_t w0 = lane < 8u ? e.x + bias : one, w1 = lane < 8u ? e.y + bias : one;
         const uint32_t w2 = lane < 8u ? e.z + bias : one, w3 = lane < 8u ? e.w + bias : one;
         asm volatile(
             "tcgen05.st.sync.aligned.32x32b.x16.b32 [%0], {%1,%5,%5,%5,%2,%5,%5,%5,%3,%5,%5,%5,%4,%5,%5,%5};"
-            ::"r"(quad + b * sfb_cols + g * 16u), "r"(w0), "r"(w1), "r"(w2), "r"(w3), "r"(one)
+            ::"r"(quad + g * 16u), "r"(w0), "r"(w1), "r"(w2), "r"(w3), "r"(one)
             : "memory");
     }
     asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
@@ -291,19 +294,18 @@ k_moe_layer_umma(const JobTable *__restrict__ dev_table, const __grid_constant__
     if (tid == 0) {
         for (uint32_t s = 0; s < kRing; ++s) {
             mbar_init(bar(kBarFull + s), kProdThreads);
+            mbar_init(bar(kBarDFull + s), kProdThreads);
             mbar_init(bar(kBarDone + s), 1);
         }
         for (uint32_t s = 0; s < kDRing; ++s) {
             mbar_init(bar(kBarDFree + s), kEpiGroup);
             mbar_init(bar(kBarDDone + s), 1);
         }
-        for (uint32_t s = 0; s < 2; ++s) {
-            mbar_init(bar(kBarUDone + s), 2);
-            mbar_init(bar(kBarUFree + s), kEpiGroup);
-        }
+        mbar_init(bar(kBarUDone), 2);
+        mbar_init(bar(kBarUFree), kEpiGroup);
         for (uint32_t s = 0; s < kItemSlots; ++s) mbar_init(bar(kBarHReady + s), kEpiGroup);
         mbar_init(bar(kBarXReady), 2u * kEpiGroup);
-        mbar_init(bar(kBarFin), 2);
+        mbar_init(bar(kBarFin), kIssuers);
         abort_flag = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
@@ -324,7 +326,7 @@ k_moe_layer_umma(const JobTable *__restrict__ dev_table, const __grid_constant__
     build_digits(x, x, 1, hidden, sBx, 0, sE, tid, kThreads);
     __syncthreads();  // every block exponent is written
     if (warp < 2u * kEpiGroup / 32u) {
-        store_digit_scales(tmem + kColSfbX, sE, 1, hidden, 0, warp, lane);
+        store_digit_scales(tmem + kColSfbX, sE, hidden, warp, lane);
         fence_before();
         mbar_arrive(bar(kBarXReady));
     }
@@ -391,79 +393,95 @@ k_moe_layer_umma(const JobTable *__restrict__ dev_table, const __grid_constant__
                                wsrc + (size_t)v * 16384u + i8 * 2048u);
                 }
                 cp_async16(smem_u32(sSF + s * kStageSf) + pt * 16u, sf + (size_t)v * 2048u);
-                mbar_arrive_after_copies(bar(kBarFull + s));
+                mbar_arrive_after_copies(bar(kBarDFull + s));
             }
         }
         if (tid == kProdWarp0 * 32u) TRACE(8);
         asm volatile("cp.async.wait_all;" ::: "memory");
         if (tid == kProdWarp0 * 32u) TRACE(9);
-    } else if ((warp == kMmaWarp0 || warp == kMmaWarp0 + 1u) && n_it) {
+    } else if ((warp == kMmaWarp0 || warp == kMmaWarp0 + 1u || warp >= 14u) && n_it) {
         if (lane == 0) {
-            // ---- MMA issue.  The two threads take the even and the odd stages, so each ring slot has one
-            // owner who sees every phase of its barriers.  An item's up units accumulate into two
-            // accumulators, one per thread (hidden / 256 is even); the down stages have accumulators of
-            // their own. ----
-            const uint32_t m = warp - kMmaWarp0;
+            // ---- MMA issue.  Issuing a tcgen05 operation costs the thread 70-90 cycles (measured), more
+            // than a 16 KB stage may take once it has up to ten of them, so four threads issue.  Thread 0
+            // issues the up units (one accumulator per item, in order); the down stages have
+            // accumulators of their own and go round the four threads.  The down stages use ring-slot
+            // barriers of their own, so each thread sees every phase of the barriers it waits on. ----
+            const uint32_t m = warp < 14u ? warp - kMmaWarp0 : warp - 12u;
             const uint64_t a_up0 = smem_desc(smem_u32(sA), 1, 64, 2), b_x0 = smem_desc(smem_u32(sBx), 1, 64, 2);
             const uint64_t sf_desc0 = smem_desc(smem_u32(sSF), 0, 8, 0);
-            bool ok = mbar_wait(bar(kBarXReady), 0, &abort_flag);
+            const uint32_t sfa_t = tmem + kColSfa + m * 16u;  // a thread's copies and MMAs execute in issue order
+            bool ok = true;
             CYC_DECL(8);
-            for (uint32_t i = m; i < nU + nD && ok; i += 2u) {
-                const uint32_t s = i % kRing, par = (i / kRing) & 1u;
-                // one scale slot per thread: a thread's copies and MMAs execute in issue order
-                const uint32_t sfa_t = tmem + kColSfa + m * 16u;
-                const uint64_t sfd = sf_desc0 + s * (kStageSf >> 4);
-                if (i < nU) {
-                    const uint32_t l = i / KU, ks = i - l * KU;
-                    const bool first = ks < 2u;  // this thread's first unit of the item
-                    CYC_LAP(0);
-                    if (first && l >= 2u) ok = mbar_wait(bar(kBarUFree + (l & 1u)), ((l >> 1) - 1u) & 1u, &abort_flag);
-                    ok = ok && mbar_wait(bar(kBarFull + s), par, &abort_flag);
-                    if (!ok) break;
-                    CYC_LAP(1);
-                    if (i == 0) TRACE(3);
-                    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
-                    fence_after();
-                    const uint32_t sfb_t = tmem + kColSfbX + ks * 8u;
-                    tmem_copy_scales(sfa_t, sfd);
-                    tmem_copy_scales(sfa_t + 4u, sfd + (512u >> 4));
-                    const uint64_t ad = a_up0 + s * (kStageA >> 4), bd = b_x0 + ks * (2048u >> 4);
+            if (m < 2u) {
+                // up units: threads 0 and 1 take the even and the odd ones (hidden / 256 is even, so the
+                // parity of a unit is the parity of its ring slot) and accumulate into accumulators of their own
+                ok = mbar_wait(bar(kBarXReady), 0, &abort_flag);
+                for (uint32_t l = 0; l < n_it && ok; ++l) {
+                    // the two up accumulators serve one item at a time
+                    if (l >= 1u) ok = mbar_wait(bar(kBarUFree), (l - 1u) & 1u, &abort_flag);
+                    const uint32_t acc = tmem + kColU + m * 16u;
+                    for (uint32_t ks = m; ks < KU && ok; ks += 2u) {
+                        const uint32_t i = l * KU + ks, s = i % kRing;
+                        CYC_LAP(0);
+                        ok = mbar_wait(bar(kBarFull + s), (i / kRing) & 1u, &abort_flag);
+                        if (!ok) break;
+                        if (i == 0) TRACE(3);
+                        CYC_LAP(1);
+                        fence_after();
+                        const uint32_t sfb_t = tmem + kColSfbX + ks * 8u;
+                        const uint64_t sfd = sf_desc0 + s * (kStageSf >> 4);
+                        tmem_copy_scales(sfa_t, sfd);
+                        tmem_copy_scales(sfa_t + 4u, sfd + (512u >> 4));
+                        const uint64_t ad = a_up0 + s * (kStageA >> 4), bd = b_x0 + ks * (2048u >> 4);
 #pragma unroll
-                    for (uint32_t kk = 0; kk < 4; ++kk) {
-                        const uint32_t atom = kk >> 1, sfid = (kk & 1u) * 2u;
-                        umma_mxf4(tmem + kColU + (l & 1u) * 32u + m * 16u, ad + kk * 2u, bd + kk * 2u,
-                                  kIdesc | (sfid << 29) | (sfid << 4), (sfa_t + atom * 4u) | (sfid << 30),
-                                  (sfb_t + atom * 4u) | (sfid << 30), (first && kk == 0u) ? 0u : 1u);
+                        for (uint32_t kk = 0; kk < 4; ++kk) {
+                            const uint32_t atom = kk >> 1, sfid = (kk & 1u) * 2u;
+                            umma_mxf4(acc, ad + kk * 2u, bd + kk * 2u, kIdesc | (sfid << 29) | (sfid << 4),
+                                      (sfa_t + atom * 4u) | (sfid << 30), (sfb_t + atom * 4u) | (sfid << 30),
+                                      (ks >= 2u || kk) ? 1u : 0u);
+                        }
+                        umma_commit(bar(kBarDone + s));
+                        if (ks + 2u >= KU) umma_commit(bar(kBarUDone));
+                        CYC_LAP(2);
                     }
-                    umma_commit(bar(kBarDone + s));
-                    if (ks + 2u >= KU) umma_commit(bar(kBarUDone + (l & 1u)));
-                    CYC_LAP(2);
-                    if (m == 0 && i + 2u >= nU) TRACE(4);
-                } else {
-                    // down stage vg: vg and i have the same parity, so accumulator sets vg % 4 = m and m + 2 are
-                    // this thread's; the same sets are read by epilogue group m
-                    const uint32_t vg = i - nU, l = vg / DS, sl = (q0 + l) % S, acc = vg & 3u;
+                }
+                if (m == 0) TRACE(4);
+            }
+            {
+                // down stage vg (ring slot (nU + vg) % kRing, accumulator set vg % 4 = m)
+                uint32_t l = 0, vloc = m;  // item and stage within the item
+                while (vloc >= DS) {
+                    vloc -= DS;
+                    ++l;
+                }
+                for (uint32_t vg = m; vg < nD && ok; vg += kIssuers) {
+                    const uint32_t s = (nU + vg) % kRing, sl = (q0 + l) % S, asf = (sl & 1u) * 2u;
                     CYC_LAP(0);
                     ok = mbar_wait(bar(kBarHReady + l), 0, &abort_flag);
                     CYC_LAP(3);
-                    ok = ok && mbar_wait(bar(kBarFull + s), par, &abort_flag);
+                    ok = ok && mbar_wait(bar(kBarDFull + s), (vg / kRing) & 1u, &abort_flag);
                     CYC_LAP(4);
-                    ok = ok && (vg < kDRing || mbar_wait(bar(kBarDFree + acc), ((vg >> 2) - 1u) & 1u, &abort_flag));
+                    ok = ok && (vg < kDRing || mbar_wait(bar(kBarDFree + m), ((vg >> 2) - 1u) & 1u, &abort_flag));
                     CYC_LAP(5);
                     if (!ok) break;
-                    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
                     fence_after();
-                    const uint32_t asf = (sl & 1u) * 2u;
+                    const uint64_t sfd = sf_desc0 + s * (kStageSf >> 4);
                     const uint64_t bd = smem_desc_k64(smem_u32(sBh + l * 512u));
+                    const uint64_t ad = smem_desc_k64(smem_u32(sA + s * kStageA));
 #pragma unroll
                     for (uint32_t b = 0; b < 4; ++b) tmem_copy_scales(sfa_t + b * 4u, sfd + b * (512u >> 4));
 #pragma unroll
                     for (uint32_t b = 0; b < 4; ++b)
-                        umma_mxf4(tmem + kColD + acc * 64u + b * 16u, smem_desc_k64(smem_u32(sA + s * kStageA + b * 4096u)),
-                                  bd, kIdesc | (asf << 29), (sfa_t + b * 4u) | (asf << 30), tmem + kColSfbH + l * 4u, 0u);
+                        umma_mxf4(tmem + kColD + m * 64u + b * 16u, ad + b * (4096u >> 4), bd, kIdesc | (asf << 29),
+                                  (sfa_t + b * 4u) | (asf << 30), tmem + kColSfbH + l * 4u, 0u);
                     umma_commit(bar(kBarDone + s));
-                    umma_commit(bar(kBarDDone + acc));
+                    umma_commit(bar(kBarDDone + m));
                     CYC_LAP(6);
+                    vloc += kIssuers;
+                    while (vloc >= DS) {
+                        vloc -= DS;
+                        ++l;
+                    }
                 }
             }
             if (m == 0) CYC_STORE(0, 8);
@@ -481,16 +499,16 @@ k_moe_layer_umma(const JobTable *__restrict__ dev_table, const __grid_constant__
         if (grp == 0u) {
             for (uint32_t l = 0; l < n_it; ++l) {
                 const uint32_t q = q0 + l, j = q / S;
-                ok = __all_sync(0xffffffffu, ok && mbar_wait(bar(kBarUDone + (l & 1u)), (l >> 1) & 1u, &abort_flag));
+                ok = __all_sync(0xffffffffu, ok && mbar_wait(bar(kBarUDone), l & 1u, &abort_flag));
                 float v = 0.0f;
                 if (ok) {
                     fence_after();
                     uint32_t a[8], b[8];  // even and odd units of the item
-                    tmem_ld8(lane_base + kColU + (l & 1u) * 32u, a);
-                    tmem_ld8(lane_base + kColU + (l & 1u) * 32u + 16u, b);
+                    tmem_ld8(lane_base + kColU, a);
+                    tmem_ld8(lane_base + kColU + 16u, b);
                     tmem_ld_wait();
                     fence_before();
-                    mbar_arrive(bar(kBarUFree + (l & 1u)));
+                    mbar_arrive(bar(kBarUFree));
                     float hi = 0.0f, lo = 0.0f;
 #pragma unroll
                     for (int jj = 0; jj < 8; ++jj) {  // low digits first
@@ -604,7 +622,8 @@ k_moe_layer_umma(const JobTable *__restrict__ dev_table, const __grid_constant__
         // acc += d_shared.  Scratch: the ring's shared memory. ----
         const uint32_t n0 = (uint32_t)((uint64_t)hidden * cta / grid), n1 = (uint32_t)((uint64_t)hidden * (cta + 1u) / grid);
         const uint32_t rows = n1 - n0, chunks = S >> 2;
-        double *red = reinterpret_cast<double *>(smem);                       // [job][chunk][row]
+        // sums as (hi, lo) pairs of F32 with error-free additions: FP64 is scarce on this GPU
+        float2 *red = reinterpret_cast<float2 *>(smem);                        // [job][chunk][row]
         float *dj = reinterpret_cast<float *>(smem + (size_t)n_jobs * chunks * rows * 8u);  // [job][row]
         for (uint32_t t0 = tid; t0 < n_jobs * chunks * rows; t0 += 4u * kThreads) {
             float v[4][4];  // four tasks at a time, so that sixteen loads are in flight per thread
@@ -619,15 +638,25 @@ k_moe_layer_umma(const JobTable *__restrict__ dev_table, const __grid_constant__
 #pragma unroll
             for (uint32_t k = 0; k < 4; ++k) {
                 const uint32_t t = t0 + k * kThreads;
-                if (t < n_jobs * chunks * rows) red[t] = (((double)v[k][0] + (double)v[k][1]) + (double)v[k][2]) + (double)v[k][3];
+                float hi = v[k][0], lo = 0.0f, e;
+#pragma unroll
+                for (uint32_t c = 1; c < 4; ++c) {
+                    two_sum(hi, v[k][c], hi, e);
+                    lo = __fadd_rn(lo, e);
+                }
+                if (t < n_jobs * chunks * rows) red[t] = make_float2(hi, lo);
             }
         }
         __syncthreads();
         for (uint32_t t = tid; t < n_jobs * rows; t += kThreads) {
             const uint32_t r = t % rows, j = t / rows;
-            double sum = 0.0;
-            for (uint32_t c = 0; c < chunks; ++c) sum += red[((size_t)j * chunks + c) * rows + r];
-            const float v = (float)sum;
+            float hi = 0.0f, lo = 0.0f, e;
+            for (uint32_t c = 0; c < chunks; ++c) {  // slice order
+                const float2 pr = red[((size_t)j * chunks + c) * rows + r];
+                two_sum(hi, pr.x, hi, e);
+                lo = __fadd_rn(lo, __fadd_rn(e, pr.y));
+            }
+            const float v = __fadd_rn(hi, lo);
             dj[t] = v;
             if (!y) d_out[(size_t)tab.jobs[j].out_index * hidden + n0 + r] = v;  // the caller mixes
         }
