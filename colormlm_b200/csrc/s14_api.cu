@@ -71,6 +71,12 @@ struct s14_ctx {
     unsigned int *counters = nullptr;  // [kCtxCounters] arrival counters of the fused kernels, all zero at rest
     int32_t *ids_stage = nullptr;  // [8] route ids / weights staging of the host-buffer call
     float *weights_stage = nullptr;
+    // Results of the routed host-buffer call: pinned host memory the kernels write through its
+    // device address (16 KB + 64 B per step, posted writes), read by the CPU after the stream
+    // synchronisation -- no device-to-host copy is enqueued.
+    float *y_host = nullptr, *y_host_dev = nullptr;          // [kMaxDim]
+    int32_t *ids_host = nullptr, *ids_host_dev = nullptr;    // [8]
+    float *w_host = nullptr, *w_host_dev = nullptr;          // [8]
     UmmaScratch umma{nullptr, nullptr};  // scratch of the tcgen05 layer kernel
     bool use_umma = true;                // S14_TENSOR_PATH=off in the environment turns it off
     const UmmaScratch *umma_scratch() const { return use_umma ? &umma : nullptr; }
@@ -111,6 +117,12 @@ extern "C" int32_t s14_ctx_create(int32_t device, s14_ctx **out) {
     CUDA_OK(cudaMemset(ctx->counters, 0, sizeof(unsigned int) * kCtxCounters));
     CUDA_OK(cudaMalloc(&ctx->ids_stage, sizeof(int32_t) * 8));
     CUDA_OK(cudaMalloc(&ctx->weights_stage, sizeof(float) * 8));
+    CUDA_OK(cudaHostAlloc(&ctx->y_host, sizeof(float) * kMaxDim, cudaHostAllocMapped));
+    CUDA_OK(cudaHostAlloc(&ctx->ids_host, sizeof(int32_t) * 8, cudaHostAllocMapped));
+    CUDA_OK(cudaHostAlloc(&ctx->w_host, sizeof(float) * 8, cudaHostAllocMapped));
+    CUDA_OK(cudaHostGetDevicePointer(&ctx->y_host_dev, ctx->y_host, 0));
+    CUDA_OK(cudaHostGetDevicePointer(&ctx->ids_host_dev, ctx->ids_host, 0));
+    CUDA_OK(cudaHostGetDevicePointer(&ctx->w_host_dev, ctx->w_host, 0));
     CUDA_OK(cudaMalloc(&ctx->umma.partials, umma_partials_bytes()));
     ctx->umma.status = ctx->status;
     if (const char *path = getenv("S14_TENSOR_PATH")) ctx->use_umma = strcmp(path, "off") != 0;
@@ -136,6 +148,9 @@ extern "C" int32_t s14_ctx_destroy(s14_ctx *ctx) {
     cudaFree(ctx->ids_stage);
     cudaFree(ctx->weights_stage);
     cudaFree(ctx->umma.partials);
+    cudaFreeHost(ctx->y_host);
+    cudaFreeHost(ctx->ids_host);
+    cudaFreeHost(ctx->w_host);
     for (auto &e : ctx->marks.ev)
         if (e) cudaEventDestroy(e);
     cudaStreamDestroy(ctx->compute);
@@ -769,20 +784,16 @@ extern "C" int32_t s14_routed_moe_layer_host(s14_ctx *ctx, const s14_routed_laye
     s14_routed_layer_desc d = *desc;
     d.router.x = ctx->x_stage;
     d.router.n_tokens = 1;
-    d.router.ids_out = ctx->ids_stage;
-    d.router.weights_out = ctx->weights_stage;
-    d.y = ctx->y_stage;
+    d.router.ids_out = ctx->ids_host_dev;
+    d.router.weights_out = ctx->w_host_dev;
+    d.y = ctx->y_host_dev;
     CUDA_OK(cudaMemcpyAsync(ctx->x_stage, host_x, bytes, cudaMemcpyHostToDevice, ctx->compute));
     const int32_t rc = s14_cmd_routed_moe_layer(ctx, ctx->compute, &d);
     if (rc != S14_OK) return rc;
-    CUDA_OK(cudaMemcpyAsync(host_y, ctx->y_stage, bytes, cudaMemcpyDeviceToHost, ctx->compute));
-    if (host_ids)
-        CUDA_OK(cudaMemcpyAsync(host_ids, ctx->ids_stage, sizeof(int32_t) * d.router.top_k,
-                                cudaMemcpyDeviceToHost, ctx->compute));
-    if (host_weights)
-        CUDA_OK(cudaMemcpyAsync(host_weights, ctx->weights_stage, sizeof(float) * d.router.top_k,
-                                cudaMemcpyDeviceToHost, ctx->compute));
     CUDA_OK(cudaStreamSynchronize(ctx->compute));
+    std::memcpy(host_y, ctx->y_host, bytes);
+    if (host_ids) std::memcpy(host_ids, ctx->ids_host, sizeof(int32_t) * d.router.top_k);
+    if (host_weights) std::memcpy(host_weights, ctx->w_host, sizeof(float) * d.router.top_k);
     return S14_OK;
 }
 

@@ -8,10 +8,10 @@
 // (E >= -100), every element is q * 2^(E-23) with |q| <= 2^23 (rounded to nearest when it has
 // more bits below the block's top bit), q = sum_j d_j 8^j with d_j in [-4, 4] -- all of them
 // E2M1 values -- and digit row j carries the UE8M0 scale 2^(E-23+3j).  Accumulator column j
-// holds the digit-j share of the dot product in F32; the eight columns are added with
-// error-free F32 additions and rounded once.  Measured against a double-precision sum on B200:
-// relative RMSE 1.5e-7, all of it from the 23-bit quantisation of elements far below their
-// block's largest one.  Columns 8-15 of the 16-column MMA are zero rows.
+// holds the digit-j share of the dot product in F32; the eight columns are added low digits
+// first.  Measured against a double-precision sum on B200: relative RMSE 1.5e-7, nearly all of it
+// from the 23-bit quantisation of elements far below their block's largest one.  Columns 8-15 of
+// the 16-column MMA are zero rows.
 //
 // Work split: by slice.  An item is (expert, 64 intermediate elements): the 64 rows of w1 and
 // the 64 rows of w3 that produce them form one 128-row MMA tile over K = hidden (up phase, one
@@ -272,6 +272,8 @@ k_moe_layer_umma(const JobTable *__restrict__ dev_table, const __grid_constant__
     __shared__ __align__(16) uint8_t sBh[kItemSlots * 512];  // digit tiles of the items' hidden values (rows 8-15 zero)
     __shared__ float s_up[64];                               // an item's up projection, handed to the gate threads
     __shared__ uint8_t sEh[kItemSlots][2];
+    __shared__ float s_mix_w[S14_EXPERTS_PER_TOKEN + 1];        // the mix, in route order: weight (shared expert: 1)
+    __shared__ uint32_t s_mix_job[S14_EXPERTS_PER_TOKEN + 1];   //   job, bit 31 set for the shared expert
     __shared__ uint32_t tmem_slot;
     __shared__ int abort_flag;
 
@@ -339,6 +341,11 @@ k_moe_layer_umma(const JobTable *__restrict__ dev_table, const __grid_constant__
     const uint32_t q1 = cta < G ? (uint32_t)((uint64_t)n_items * (cta + 1u) / G) : 0u;
     const uint32_t n_it = min(q1 - q0, kItemSlots);  // the launcher keeps the share within kItemSlots
     const uint32_t nU = n_it * KU, nD = n_it * DS;
+    if (tid < tab.token_job_begin[1] - tab.token_job_begin[0] && tid <= S14_EXPERTS_PER_TOKEN) {
+        const uint32_t jb = tab.token_jobs[tab.token_job_begin[0] + tid];  // the job table may live in global memory
+        s_mix_w[tid] = tab.jobs[jb].weight;
+        s_mix_job[tid] = jb | (tab.jobs[jb].is_shared ? 0x80000000u : 0u);
+    }
     asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
     __syncthreads();
     if (tid == 0) TRACE(2);
@@ -396,9 +403,7 @@ k_moe_layer_umma(const JobTable *__restrict__ dev_table, const __grid_constant__
                 mbar_arrive_after_copies(bar(kBarDFull + s));
             }
         }
-        if (tid == kProdWarp0 * 32u) TRACE(8);
         asm volatile("cp.async.wait_all;" ::: "memory");
-        if (tid == kProdWarp0 * 32u) TRACE(9);
     } else if ((warp == kMmaWarp0 || warp == kMmaWarp0 + 1u || warp >= 14u) && n_it) {
         if (lane == 0) {
             // ---- MMA issue.  Issuing a tcgen05 operation costs the thread 70-90 cycles (measured), more
@@ -509,16 +514,15 @@ k_moe_layer_umma(const JobTable *__restrict__ dev_table, const __grid_constant__
                     tmem_ld_wait();
                     fence_before();
                     mbar_arrive(bar(kBarUFree));
-                    float hi = 0.0f, lo = 0.0f;
+                    // Digit columns, low digits first, each column about eight times the one before: plain F32
+                    // additions lose a few 2^-24 of the result, below the 23-bit digits of what follows.
+                    float sa = 0.0f, sb = 0.0f;
 #pragma unroll
-                    for (int jj = 0; jj < 8; ++jj) {  // low digits first
-                        float e;
-                        two_sum(hi, __uint_as_float(a[jj]), hi, e);
-                        lo = __fadd_rn(lo, e);
-                        two_sum(hi, __uint_as_float(b[jj]), hi, e);
-                        lo = __fadd_rn(lo, e);
+                    for (int jj = 0; jj < 8; ++jj) {
+                        sa = __fadd_rn(sa, __uint_as_float(a[jj]));
+                        sb = __fadd_rn(sb, __uint_as_float(b[jj]));
                     }
-                    v = __fadd_rn(hi, lo);
+                    v = __fadd_rn(sa, sb);
                 }
                 if (row >= 64u) s_up[row - 64u] = v;
                 group_bar_sync();
@@ -579,15 +583,11 @@ k_moe_layer_umma(const JobTable *__restrict__ dev_table, const __grid_constant__
             mbar_arrive(bar(kBarDFree + acc));  // the accumulators are in registers: the next stage may overwrite them
             float out[4];
 #pragma unroll
-            for (uint32_t b = 0; b < 4; ++b) {
-                float hi = 0.0f, lo = 0.0f;
+            for (uint32_t b = 0; b < 4; ++b) {  // low digits first; the share is kept as one F32 anyway
+                float sum = 0.0f;
 #pragma unroll
-                for (int jj = 0; jj < 8; ++jj) {
-                    float e;
-                    two_sum(hi, __uint_as_float(a[b][jj]), hi, e);
-                    lo = __fadd_rn(lo, e);
-                }
-                out[b] = __fadd_rn(hi, lo);
+                for (int jj = 0; jj < 8; ++jj) sum = __fadd_rn(sum, __uint_as_float(a[b][jj]));
+                out[b] = sum;
             }
             // the item's share of rows (4 vloc + b) * 128 + row of its expert's output
             float *p = part + (size_t)q * hidden + (size_t)vloc * 512u + row;
@@ -648,6 +648,7 @@ k_moe_layer_umma(const JobTable *__restrict__ dev_table, const __grid_constant__
             }
         }
         __syncthreads();
+        if (tid == 0) TRACE(8);
         for (uint32_t t = tid; t < n_jobs * rows; t += kThreads) {
             const uint32_t r = t % rows, j = t / rows;
             float hi = 0.0f, lo = 0.0f, e;
@@ -661,13 +662,13 @@ k_moe_layer_umma(const JobTable *__restrict__ dev_table, const __grid_constant__
             if (!y) d_out[(size_t)tab.jobs[j].out_index * hidden + n0 + r] = v;  // the caller mixes
         }
         __syncthreads();
+        if (tid == 0) TRACE(9);
         if (y && tid < rows) {
-            const uint32_t j0 = tab.token_job_begin[0], j1 = tab.token_job_begin[1];
             float acc = 0.0f;
-            for (uint32_t jj = j0; jj < j1; ++jj) {
-                const uint32_t jb = tab.token_jobs[jj];
-                const float dv = dj[(size_t)jb * rows + tid];
-                acc = tab.jobs[jb].is_shared ? __fadd_rn(acc, dv) : __fadd_rn(acc, __fmul_rn(tab.jobs[jb].weight, dv));
+            for (uint32_t jj = 0; jj < n_jobs; ++jj) {
+                const uint32_t jb = s_mix_job[jj];
+                const float dv = dj[(size_t)(jb & 0x7FFFFFFFu) * rows + tid];
+                acc = (jb >> 31) ? __fadd_rn(acc, dv) : __fadd_rn(acc, __fmul_rn(s_mix_w[jj], dv));
             }
             y[n0 + tid] = acc;
         }
