@@ -147,24 +147,6 @@ __device__ __forceinline__ void tmem_ld_wait() { asm volatile("tcgen05.wait::ld.
 __device__ __forceinline__ void fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
 __device__ __forceinline__ void fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
 
-#ifdef S14_UMMA_TRACE
-__device__ unsigned long long g_umma_trace[2][160][12];
-__device__ __forceinline__ void trace_mark(bool up, uint32_t k) {
-    unsigned long long t;
-    asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t));
-    g_umma_trace[up ? 1 : 0][blockIdx.x][k] = t;
-}
-#define TRACE(k) trace_mark(true, k)
-__device__ long long g_umma_cyc[2][160][8];
-#define CYC_DECL(n) long long cyc_[n] = {}; long long cyc_t_ = clock64()
-#define CYC_LAP(k) do { const long long now_ = clock64(); cyc_[k] += now_ - cyc_t_; cyc_t_ = now_; } while (0)
-#define CYC_STORE(base, n) do { for (int q_ = 0; q_ < (n); ++q_) g_umma_cyc[1][blockIdx.x][(base) + q_] = cyc_[q_]; } while (0)
-#else
-#define TRACE(k) ((void)0)
-#define CYC_DECL(n) ((void)0)
-#define CYC_LAP(k) ((void)0)
-#define CYC_STORE(base, n) ((void)0)
-#endif
 
 // Instruction descriptor: A and B E2M1 (format 1), both K-major, N = 16, UE8M0 scales, M = 128.
 constexpr uint32_t kIdesc = (1u << 7) | (1u << 10) | ((16u >> 3) << 17) | (1u << 23) | ((128u >> 4) << 24);
@@ -279,7 +261,6 @@ k_moe_layer_umma(const JobTable *__restrict__ dev_table, const __grid_constant__
 
     const uint32_t tid = threadIdx.x, warp = tid >> 5, lane = tid & 31u;
     const bool is_producer = warp >= kProdWarp0 && warp < kProdWarp0 + kProdThreads / 32u;
-    if (tid == 0) TRACE(0);
     const uint32_t KU = hidden >> 8;   // up units of an item (256 K-elements each)
     const uint32_t DS = hidden >> 9;   // down stages of an item (four 128-row tiles each)
     const uint32_t RT = hidden >> 7;   // row tiles of w2
@@ -321,7 +302,6 @@ k_moe_layer_umma(const JobTable *__restrict__ dev_table, const __grid_constant__
     __syncthreads();
     fence_after();
     const uint32_t tmem = tmem_slot;
-    if (tid == 0) TRACE(1);
 
     // The token does not depend on the router: its digits are built while the router runs; the
     // job table is read only after the router has finished.
@@ -348,7 +328,6 @@ k_moe_layer_umma(const JobTable *__restrict__ dev_table, const __grid_constant__
     }
     asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
     __syncthreads();
-    if (tid == 0) TRACE(2);
 
     if (is_producer && n_it) {
         // ---- copies: the up units of every item, then the down stages of every item ----
@@ -416,7 +395,6 @@ k_moe_layer_umma(const JobTable *__restrict__ dev_table, const __grid_constant__
             const uint64_t sf_desc0 = smem_desc(smem_u32(sSF), 0, 8, 0);
             const uint32_t sfa_t = tmem + kColSfa + m * 16u;  // a thread's copies and MMAs execute in issue order
             bool ok = true;
-            CYC_DECL(8);
             if (m < 2u) {
                 // up units: threads 0 and 1 take the even and the odd ones (hidden / 256 is even, so the
                 // parity of a unit is the parity of its ring slot) and accumulate into accumulators of their own
@@ -427,11 +405,8 @@ k_moe_layer_umma(const JobTable *__restrict__ dev_table, const __grid_constant__
                     const uint32_t acc = tmem + kColU + m * 16u;
                     for (uint32_t ks = m; ks < KU && ok; ks += 2u) {
                         const uint32_t i = l * KU + ks, s = i % kRing;
-                        CYC_LAP(0);
                         ok = mbar_wait(bar(kBarFull + s), (i / kRing) & 1u, &abort_flag);
                         if (!ok) break;
-                        if (i == 0) TRACE(3);
-                        CYC_LAP(1);
                         fence_after();
                         const uint32_t sfb_t = tmem + kColSfbX + ks * 8u;
                         const uint64_t sfd = sf_desc0 + s * (kStageSf >> 4);
@@ -447,10 +422,8 @@ k_moe_layer_umma(const JobTable *__restrict__ dev_table, const __grid_constant__
                         }
                         umma_commit(bar(kBarDone + s));
                         if (ks + 2u >= KU) umma_commit(bar(kBarUDone));
-                        CYC_LAP(2);
                     }
                 }
-                if (m == 0) TRACE(4);
             }
             {
                 // down stage vg (ring slot (nU + vg) % kRing, accumulator set vg % 4 = m)
@@ -461,13 +434,9 @@ k_moe_layer_umma(const JobTable *__restrict__ dev_table, const __grid_constant__
                 }
                 for (uint32_t vg = m; vg < nD && ok; vg += kIssuers) {
                     const uint32_t s = (nU + vg) % kRing, sl = (q0 + l) % S, asf = (sl & 1u) * 2u;
-                    CYC_LAP(0);
                     ok = mbar_wait(bar(kBarHReady + l), 0, &abort_flag);
-                    CYC_LAP(3);
                     ok = ok && mbar_wait(bar(kBarDFull + s), (vg / kRing) & 1u, &abort_flag);
-                    CYC_LAP(4);
                     ok = ok && (vg < kDRing || mbar_wait(bar(kBarDFree + m), ((vg >> 2) - 1u) & 1u, &abort_flag));
-                    CYC_LAP(5);
                     if (!ok) break;
                     fence_after();
                     const uint64_t sfd = sf_desc0 + s * (kStageSf >> 4);
@@ -481,7 +450,6 @@ k_moe_layer_umma(const JobTable *__restrict__ dev_table, const __grid_constant__
                                   (sfa_t + b * 4u) | (asf << 30), tmem + kColSfbH + l * 4u, 0u);
                     umma_commit(bar(kBarDone + s));
                     umma_commit(bar(kBarDDone + m));
-                    CYC_LAP(6);
                     vloc += kIssuers;
                     while (vloc >= DS) {
                         vloc -= DS;
@@ -489,11 +457,9 @@ k_moe_layer_umma(const JobTable *__restrict__ dev_table, const __grid_constant__
                     }
                 }
             }
-            if (m == 0) CYC_STORE(0, 8);
             // nothing of this CTA's tensor work is in flight when the tensor memory is freed
             umma_commit(bar(kBarFin));
             mbar_wait(bar(kBarFin), 0, &abort_flag);
-            if (m == 0) TRACE(5);
         }
     } else if (warp < 2u * kEpiGroup / 32u && n_it) {
         // ---- epilogue: group A (warps 0-3) turns the up accumulators into hidden digits, then both
@@ -566,7 +532,6 @@ k_moe_layer_umma(const JobTable *__restrict__ dev_table, const __grid_constant__
                 fence_before();
                 mbar_arrive(bar(kBarHReady + l));
             }
-            if (tid == 0) TRACE(6);
         }
         for (uint32_t vg = grp; vg < nD; vg += 2u) {
             const uint32_t acc = vg & 3u;
@@ -596,7 +561,6 @@ k_moe_layer_umma(const JobTable *__restrict__ dev_table, const __grid_constant__
         }
     }
 
-    if (tid == 0) TRACE(7);
     // ---- every item's share is in global memory: count the CTA's items, wait for all of them ----
     __threadfence();
     fence_before();
@@ -613,7 +577,6 @@ k_moe_layer_umma(const JobTable *__restrict__ dev_table, const __grid_constant__
             __nanosleep(100);
         }
         if (abort_flag) atomicExch(status, 0x5501u);
-        TRACE(10);
     }
     __syncthreads();
     if (!abort_flag) {
@@ -648,7 +611,6 @@ k_moe_layer_umma(const JobTable *__restrict__ dev_table, const __grid_constant__
             }
         }
         __syncthreads();
-        if (tid == 0) TRACE(8);
         for (uint32_t t = tid; t < n_jobs * rows; t += kThreads) {
             const uint32_t r = t % rows, j = t / rows;
             float hi = 0.0f, lo = 0.0f, e;
@@ -662,7 +624,6 @@ k_moe_layer_umma(const JobTable *__restrict__ dev_table, const __grid_constant__
             if (!y) d_out[(size_t)tab.jobs[j].out_index * hidden + n0 + r] = v;  // the caller mixes
         }
         __syncthreads();
-        if (tid == 0) TRACE(9);
         if (y && tid < rows) {
             float acc = 0.0f;
             for (uint32_t jj = 0; jj < n_jobs; ++jj) {
@@ -675,7 +636,6 @@ k_moe_layer_umma(const JobTable *__restrict__ dev_table, const __grid_constant__
     }
     // the last CTA to leave puts the counters back to zero for the next launch
     if (tid == 0) {
-        TRACE(11);
         __threadfence();
         if (atomicAdd(counters + kExitCounter, 1u) == grid - 1u) {
             counters[kItemCounter] = 0u;
