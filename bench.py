@@ -4,16 +4,15 @@ experts + the shared MXFP4 expert, 256 routed experts per layer resident in the 
 
     python bench.py [--gpus N] [--steps K] [--warmup W] [--impl reference] [--accum pairwise|reference]
 
-A step is one layer-token: one token through one MoE layer (router kernel, then the layer
-kernel: up projections, SwiGLU, down projection, sums over slices, ordered mix).  14 layers of 257 expert pages each are resident (the S14 stack, 48 GB); the
+A step is one layer-token: one token through one MoE layer, a single launch in pairwise order
+(expert scores and routes, up projections, SwiGLU, down projection, sums over slices, ordered mix).  14 layers of 257 expert pages each are resident (the S14 stack, 48 GB); the
 steps walk the layers round-robin with a fresh token each, so consecutive steps read
 disjoint pages and the 96 MB a step touches never comes from L2.  Steps are replayed from
 a CUDA graph of 14 layer-steps; time is taken with CUDA events on the launching stream.
 
 One JSON line is printed by rank 0.  `value` is layer-tokens/s with inputs resident in HBM,
 `e2e` the same through the host-buffer C-ABI call (H2D of the token and D2H of the result
-inside the timed region), `roofline` the layer kernel (timed alone in a CUDA graph of 14
-launches with fixed routes, over the same resident pages) against the measured copy bandwidth, `cpu_baseline` the CPU oracle on this box's host cores on a bounded sample.
+inside the timed region), `roofline` the layer kernel (a step is one launch of it) against the measured copy bandwidth, `cpu_baseline` the CPU oracle on this box's host cores on a bounded sample.
 `--impl reference` times that CPU implementation alone.
 """
 from __future__ import annotations
@@ -39,6 +38,9 @@ ROUTER_BYTES = N_EXPERTS * HIDDEN * 2 + N_EXPERTS * 4
 STEP_BYTES = 7 * PAGE_BYTES + ROUTER_BYTES + HIDDEN * 4 + HIDDEN * 4
 # layer kernel: 7 expert pages, x in, y out
 LAYER_BYTES = 7 * PAGE_BYTES + HIDDEN * 4 + HIDDEN * 4
+# DRAM bytes of one launch of the layer kernel at this workload (dram__bytes_read.sum + dram__bytes_write.sum
+# of one ncu capture; the summary of that capture is kept under profiles/)
+NCU_TRAFFIC_BYTES = None
 WORKLOAD = ("moe_layer_decode: 1 token, router top-6 of 256 + 6 routed + 1 shared MXFP4 expert, "
             "hidden 4096, intermediate 2048")
 
@@ -270,10 +272,9 @@ def run_gpu(args) -> None:
 
     _note("layers resident")
     stream = torch.cuda.Stream()
-    # pairwise order: router + layer kernel; reference order: router, up, down, mix.  Expert parallel adds
-    # the mix of the exchanged slots (the slot memset is not a kernel of ours, the all-reduce is NCCL's)
-    layer_kernels = 1 if args.accum == "pairwise" else 2
-    kernels_per_step = (1 + layer_kernels + (1 if args.accum != "pairwise" else 0)) if world == 1 else 2 + layer_kernels
+    # Kernels of ours per step, counted by the context: pairwise order one (the layer kernel scores the
+    # experts and picks the routes itself); reference order router, up, down, mix.  Expert parallel adds
+    # the mix of the exchanged slots (the slot memset is not a kernel of ours, the all-reduce is NCCL's).
 
     def capture(n_steps: int, first: int):
         g = torch.cuda.CUDAGraph()
@@ -283,10 +284,12 @@ def run_gpu(args) -> None:
                     enqueue_step(first + i, stream.cuda_stream)
         return g
 
+    launched_before = ctx.launch_count
     with torch.cuda.stream(stream):
         for i in range(3):  # first launches outside capture (module load)
             enqueue_step(i, stream.cuda_stream)
     stream.synchronize()
+    kernels_per_step = (ctx.launch_count - launched_before) // 3
     _note("eager warm-up steps done")
     rem = args.steps % N_LAYERS
     full = args.steps // N_LAYERS
@@ -297,7 +300,7 @@ def run_gpu(args) -> None:
     else:
         # NCCL all-reduces replayed from a CUDA graph ran ~10x slower than eager ones here
         # (0.95 ms against 0.1 ms per step at 2 GPUs), so the expert-parallel steps are launched eagerly
-        launch_mode = "eager launches (router, layer kernel, NCCL all-reduce, mix per step)"
+        launch_mode = "eager launches (layer kernel with its router, NCCL all-reduce, mix per step)"
         graph = graph_rem = None
 
     def replay(n_full: int, with_rem: bool):
@@ -342,9 +345,10 @@ def run_gpu(args) -> None:
     # one token stream: with several GPUs the experts of the same tokens are spread over the ranks
     value = args.steps / (ms / 1e3)
 
-    # The layer kernel alone: a CUDA graph of one launch per resident layer with fixed routes (six routed
-    # experts + the shared one, other pages every launch), replayed back to back and timed with CUDA events
-    # on the launching stream.  Not part of the headline number.
+    # The layer kernel with the routes given (no expert scoring): a CUDA graph of one launch per resident
+    # layer with fixed routes (six routed experts + the shared one, other pages every launch), replayed back
+    # to back and timed with CUDA events on the launching stream.  Not part of the headline number; it shows
+    # what the routing costs inside the kernel.
     from colormlm_b200.s14 import TokenRoute
 
     layer_ms = None
@@ -383,7 +387,11 @@ def run_gpu(args) -> None:
         stream.synchronize()
         layer_ms = k0.elapsed_time(k1) / (reps * N_LAYERS)
     peak, peak_kind = measured_peaks()
-    achieved = LAYER_BYTES / (layer_ms * 1e-3) / 1e9 if layer_ms else None
+    # pairwise order on one GPU: a step is one launch of the layer kernel (routing included), so the timed
+    # region itself gives the kernel's duration; otherwise the fixed-route launches stand for it
+    one_kernel_step = world == 1 and kernels_per_step == 1
+    roof_ms, roof_bytes = (ms / args.steps, STEP_BYTES) if one_kernel_step else (layer_ms, LAYER_BYTES)
+    achieved = roof_bytes / (roof_ms * 1e-3) / 1e9 if roof_ms else None
 
     # end to end through the host-buffer call: pinned x in, y (+ route) out, every step
     hx = torch.randn((n_tok, HIDDEN), dtype=torch.float32).pin_memory()
@@ -451,14 +459,17 @@ def run_gpu(args) -> None:
             "hbm_gbs": value * STEP_BYTES / 1e9, "hbm_frac_of_measured_peak": value * STEP_BYTES / 1e9 / (peak * world),
             "algorithmic_bytes_per_step": STEP_BYTES,
             "roofline": {"bound": "hbm",
-                         "kernel": ("k_moe_layer_umma: 7 MXFP4 experts, up projections + SwiGLU + down projection + mix"
+                         "kernel": ("k_moe_layer_umma: expert scores + routes, 7 MXFP4 experts (up projections, SwiGLU, "
+                                    "down projection), sums over slices, ordered mix"
                                     if args.accum == "pairwise" else "reference-order layer kernels (up, down, mix)"),
                          "achieved": achieved, "peak": peak, "unit": "GB/s",
                          "frac": achieved / peak if achieved else None,
-                         "peak_kind": peak_kind, "traffic": None, "bytes_per_launch": LAYER_BYTES,
-                         "ms_per_launch": layer_ms,
-                         "timed": "CUDA graph of 14 layer launches with fixed routes, 60 replays, CUDA events",
-                         "rest_of_step_ms": (ms / args.steps - layer_ms) if layer_ms else None},
+                         "peak_kind": peak_kind, "traffic": NCU_TRAFFIC_BYTES if one_kernel_step else None,
+                         "bytes_per_launch": roof_bytes, "ms_per_launch": roof_ms,
+                         "timed": ("the timed region: one launch per step, CUDA events on the launching stream"
+                                   if one_kernel_step else
+                                   "CUDA graph of 14 layer launches with fixed routes, 60 replays, CUDA events"),
+                         "fixed_routes_ms_per_launch": layer_ms},
             "cpu_baseline": cpu,
             "e2e": {"value": e2e_value, "unit": "layer-tokens/s", "h2d_bytes_per_step": HIDDEN * 4,
                     "d2h_bytes_per_step": HIDDEN * 4 + TOP_K * 8, "steps": e2e_steps},

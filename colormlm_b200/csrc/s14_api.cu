@@ -686,6 +686,32 @@ extern "C" int32_t s14_cmd_router(s14_ctx *ctx, void *stream, const s14_router_d
     S14_CATCH
 }
 
+// The router's side of a routed layer call, for launch_moe_layer (which scores the experts inside
+// the layer kernel when that kernel can, and launches k_router otherwise).
+static FusedRouter router_of(const s14_ctx *ctx, const s14_routed_layer_desc *desc, uint32_t ep_rank,
+                             uint32_t ep_world, uint32_t shared_owner) {
+    const s14_router_desc &r = desc->router;
+    FusedRouter f = {};
+    f.weight = r.router_weight_bf16;
+    f.bias = r.bias;
+    f.scores = ctx->scores;
+    f.select = ctx->select;
+    f.n_experts = r.n_experts;
+    f.score_fn = r.score_fn;
+    f.top_k = r.top_k;
+    f.route_scale = r.route_scale;
+    f.ids_out = r.ids_out;
+    f.weights_out = r.weights_out;
+    f.table_out = ctx->dev_table;
+    f.page_table = desc->page_table;
+    f.shared_page = desc->shared_page;
+    f.shared_kind = desc->shared_kind;
+    f.ep_rank = ep_rank;
+    f.ep_world = ep_world;
+    f.shared_owner = shared_owner;
+    return f;
+}
+
 extern "C" int32_t s14_cmd_routed_moe_layer(s14_ctx *ctx, void *stream,
                                             const s14_routed_layer_desc *desc) {
     S14_TRY
@@ -702,17 +728,15 @@ extern "C" int32_t s14_cmd_routed_moe_layer(s14_ctx *ctx, void *stream,
     cudaStream_t st = stream_of(ctx, stream);
     cudaError_t err;
     const KernelMarks *km = ctx->timing ? &ctx->marks : nullptr;
-    ctx->launches += launch_router(st, r, ctx->scores, ctx->select, ctx->dev_table, desc->page_table,
-                                   desc->shared_page, desc->shared_kind, ctx->counters, &err, km);
-    if (err != cudaSuccess) return cuda_fail(err, "S14 router launch");
+    const FusedRouter fr = router_of(ctx, desc, 0, 1, 0);
     JobTable unused;
     unused.n_jobs = 0;
     const uint32_t n_jobs = r.top_k + (desc->shared_page ? 1u : 0u);
     ctx->launches += launch_moe_layer(st, ctx->mode, ctx->sm_count, ctx->dev_table, unused, 1, n_jobs,
                                       r.hidden, desc->inter, r.x, ctx->h, ctx->d, desc->y, &err, km,
                                       !desc->shared_page || desc->shared_kind == S14_PAGE_MXFP4, ctx->counters,
-                                      ctx->umma_scratch());
-    if (err != cudaSuccess) return cuda_fail(err, "S14 MoE layer launch");
+                                      ctx->umma_scratch(), &fr);
+    if (err != cudaSuccess) return cuda_fail(err, "S14 routed MoE layer launch");
     if (km) {
         CUDA_OK(cudaStreamSynchronize(st));
         for (int i = 0; i < 4; ++i) {
@@ -748,17 +772,14 @@ extern "C" int32_t s14_cmd_routed_moe_experts_ep(s14_ctx *ctx, void *stream,
     // slots this rank does not own stay zero, so that the ranks' buffers add up exactly
     CUDA_OK(cudaMemsetAsync(slots_out, 0, sizeof(float) * n_slots * r.hidden, st));
     cudaError_t err;
-    ctx->launches += launch_router(st, r, ctx->scores, ctx->select, ctx->dev_table, desc->page_table,
-                                   desc->shared_page, desc->shared_kind, ctx->counters, &err, nullptr,
-                                   ep_rank, ep_world, shared_owner);
-    if (err != cudaSuccess) return cuda_fail(err, "S14 router launch");
+    const FusedRouter fr = router_of(ctx, desc, ep_rank, ep_world, shared_owner);
     JobTable unused;
     unused.n_jobs = 0;
     ctx->launches += launch_moe_layer(st, ctx->mode, ctx->sm_count, ctx->dev_table, unused, 1, n_slots,
                                       r.hidden, desc->inter, r.x, ctx->h, slots_out, nullptr, &err, nullptr,
                                       !desc->shared_page || desc->shared_kind == S14_PAGE_MXFP4,
-                                      ctx->counters, ctx->umma_scratch());
-    if (err != cudaSuccess) return cuda_fail(err, "S14 MoE layer launch");
+                                      ctx->counters, ctx->umma_scratch(), &fr);
+    if (err != cudaSuccess) return cuda_fail(err, "S14 routed MoE layer launch");
     return S14_OK;
     S14_CATCH
 }

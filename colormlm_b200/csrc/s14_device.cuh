@@ -79,6 +79,14 @@ __device__ __forceinline__ float swiglu_limit_f32(float gate, float up) {
     return __fmul_rn(__fdiv_rn(g, __fadd_rn(1.0f, e)), u);
 }
 
+// An expert's score from its logit (the double-accumulated dot product, rounded to F32 first):
+// sigmoid or sqrt(softplus), evaluated in double and rounded once.
+__device__ __forceinline__ float router_score_f32(double logit_sum, uint32_t score_fn) {
+    const double l = (double)(float)logit_sum;
+    const double sc = (score_fn == S14_SCORE_SIGMOID) ? 1.0 / (1.0 + exp(-l)) : sqrt(l > 20.0 ? l : log1p(exp(l)));
+    return (float)sc;
+}
+
 __device__ __forceinline__ const JobTable &table_of(const JobTable *dev, const JobTable &param) {
     return dev ? *dev : param;
 }

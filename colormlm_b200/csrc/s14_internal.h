@@ -41,6 +41,24 @@ struct KernelMarks {
 
 struct UmmaScratch;
 
+// What the router reads and writes, for a layer call that computes its own routes: the tcgen05
+// layer kernel scores the experts in its first microseconds (every CTA a few of them), and every
+// CTA then picks the routes from the scores; other layer kernels run k_router first.
+struct FusedRouter {
+    const uint16_t *weight;            // [n_experts, hidden] BF16
+    const float *bias;                 // [n_experts] or NULL
+    float *scores, *select;            // [n_experts] scratch: score, score + bias
+    uint32_t n_experts, score_fn, top_k;
+    float route_scale;
+    int32_t *ids_out;                  // [top_k] or NULL
+    float *weights_out;                // [top_k] or NULL
+    JobTable *table_out;               // the device job table k_router fills
+    const uint8_t *const *page_table;  // [n_experts] expert pages (MXFP4)
+    const uint8_t *shared_page;        // or NULL
+    uint32_t shared_kind;
+    uint32_t ep_rank, ep_world, shared_owner;
+};
+
 cudaError_t launch_mxfp4_matvec(cudaStream_t st, uint32_t mode, int sm_count, const float *x,
                                 const uint8_t *w, const uint8_t *s, float *y, uint32_t n, uint32_t k);
 cudaError_t launch_fp8_matvec(cudaStream_t st, uint32_t mode, int sm_count, uint32_t scale_format,
@@ -57,7 +75,8 @@ int launch_moe_layer(cudaStream_t st, uint32_t mode, int sm_count, const JobTabl
                      const JobTable &param_table, uint32_t n_tokens, uint32_t n_jobs_max,
                      uint32_t hidden, uint32_t inter, const float *x, float *h, float *d, float *y,
                      cudaError_t *err, const KernelMarks *km = nullptr, bool all_mxfp4 = false,
-                     unsigned int *counters = nullptr, const struct UmmaScratch *umma = nullptr);
+                     unsigned int *counters = nullptr, const struct UmmaScratch *umma = nullptr,
+                     const FusedRouter *router = nullptr);
 // Scratch of the tcgen05 layer kernel (s14_moe_umma.cu): every item's share of its expert's output
 // (umma_partials_bytes) and the device status word a timed-out wait sets.
 struct UmmaScratch {
@@ -67,10 +86,14 @@ struct UmmaScratch {
 size_t umma_partials_bytes();
 // One token, every job an MXFP4 page, hidden and inter multiples of 512 that fit shared and tensor memory.
 bool umma_layer_ok(int sm_count, uint32_t n_tokens, uint32_t n_jobs_max, uint32_t hidden, uint32_t inter);
+// Whether the tcgen05 layer kernel can score n_experts itself (a CTA scores at most four).
+bool umma_router_ok(int sm_count, uint32_t n_experts);
 // Both phases and the mix in one launch (y == nullptr: the expert outputs go to d, the caller mixes).
+// With a router the kernel computes the routes itself and the job tables are not read.
 cudaError_t launch_moe_layer_umma(cudaStream_t st, int sm_count, const JobTable *dev, const JobTable &param,
                                   const float *x, float *d, float *y, float *partials, unsigned int *counters,
-                                  uint32_t *status, uint32_t hidden, uint32_t inter, bool after_router);
+                                  uint32_t *status, uint32_t hidden, uint32_t inter, bool after_router,
+                                  const FusedRouter *router = nullptr);
 int launch_router(cudaStream_t st, const s14_router_desc &r, float *scores, float *select,
                   JobTable *table_out, const uint8_t *const *page_table, const uint8_t *shared_page,
                   uint32_t shared_kind, unsigned int *counter, cudaError_t *err,

@@ -732,10 +732,7 @@ k_router(const float *__restrict__ x, const uint16_t *__restrict__ wr, const flo
         if (lane == 0) half_sum[half] = part;
         __syncthreads();
         if (threadIdx.x == 0) {
-            const double l = (double)(float)(half_sum[0] + half_sum[1]);
-            const double sc = (score_fn == S14_SCORE_SIGMOID) ? 1.0 / (1.0 + exp(-l))
-                                                              : sqrt(l > 20.0 ? l : log1p(exp(l)));
-            const float s = (float)sc;
+            const float s = router_score_f32(half_sum[0] + half_sum[1], score_fn);
             scores[(size_t)t * n_experts + e] = s;
             select[(size_t)t * n_experts + e] = __fadd_rn(s, bias ? bias[e] : 0.0f);
         }
@@ -937,9 +934,34 @@ int launch_moe_layer(cudaStream_t st, uint32_t mode, int sm_count, const JobTabl
                      const JobTable &param_table, uint32_t n_tokens, uint32_t n_jobs_max,
                      uint32_t hidden, uint32_t inter, const float *x, float *h, float *d, float *y,
                      cudaError_t *err, const KernelMarks *km, bool all_mxfp4, unsigned int *counters,
-                     const UmmaScratch *umma) {
+                     const UmmaScratch *umma, const FusedRouter *router) {
     int launches = 0;
     *err = cudaSuccess;
+    const bool tensor_path = mode != S14_ACCUM_REFERENCE && all_mxfp4 && counters && umma &&
+                             umma_layer_ok(sm_count, n_tokens, n_jobs_max, hidden, inter);
+    if (router && !(tensor_path && umma_router_ok(sm_count, router->n_experts))) {
+        // the routes come from a kernel of their own, which fills the device job table
+        s14_router_desc r = {};
+        r.x = x;
+        r.router_weight_bf16 = router->weight;
+        r.bias = router->bias;
+        r.n_experts = router->n_experts;
+        r.hidden = hidden;
+        r.n_tokens = 1;
+        r.score_fn = router->score_fn;
+        r.top_k = router->top_k;
+        r.route_scale = router->route_scale;
+        r.ids_out = router->ids_out;
+        r.weights_out = router->weights_out;
+        launches += launch_router(st, r, router->scores, router->select, router->table_out, router->page_table,
+                                  router->shared_page, router->shared_kind, counters, err, km, router->ep_rank,
+                                  router->ep_world, router->shared_owner);
+        if (*err != cudaSuccess) return launches;
+        dev_table = router->table_out;
+        router = nullptr;
+    } else if (router && km) {
+        cudaEventRecord(km->ev[0], st);
+    }
     if (km) cudaEventRecord(km->ev[1], st);
     if (mode == S14_ACCUM_REFERENCE) {
         dim3 gu(ceil_div(inter, 32), n_jobs_max), gd(ceil_div(hidden, 32), n_jobs_max);
@@ -949,9 +971,9 @@ int launch_moe_layer(cudaStream_t st, uint32_t mode, int sm_count, const JobTabl
         k_expert_down_reference<<<gd, 32, inter * sizeof(float), st>>>(dev_table, param_table, h, d,
                                                                        hidden, inter);
         launches += 2;
-    } else if (all_mxfp4 && counters && umma && umma_layer_ok(sm_count, n_tokens, n_jobs_max, hidden, inter)) {
+    } else if (tensor_path) {
         *err = launch_moe_layer_umma(st, sm_count, dev_table, param_table, x, d, y, umma->partials, counters,
-                                     umma->status, hidden, inter, dev_table != nullptr);
+                                     umma->status, hidden, inter, dev_table != nullptr, router);
         launches += 1;
         if (km) {  // one kernel runs both phases and the mix: its time is booked as the up phase
             cudaEventRecord(km->ev[2], st);

@@ -61,6 +61,8 @@ constexpr uint32_t kMaxBlocks = kMaxHidden / 32;
 constexpr uint32_t kSpin = 1u << 17;           // tries (a microsecond each at most) before a wait gives up
 constexpr uint32_t kSpinGlobal = 1u << 20;     // polls (100 ns apart) of the item counter before giving up
 constexpr uint32_t kItemCounter = 1, kExitCounter = 2;  // in the context's counter array ([0] is the router's)
+constexpr uint32_t kRouteCounter = 3;          // CTAs whose expert scores are written (routes computed in this kernel)
+constexpr uint32_t kRouterSlots = 4;           // experts a CTA scores at most
 
 // Bar indices in the static barrier array.
 constexpr uint32_t kBarFull = 0;                      // ring slot filled with an up unit (128 copying threads)
@@ -151,48 +153,38 @@ __device__ __forceinline__ void fence_after() { asm volatile("tcgen05.fence::aft
 // Instruction descriptor: A and B E2M1 (format 1), both K-major, N = 16, UE8M0 scales, M = 128.
 constexpr uint32_t kIdesc = (1u << 7) | (1u << 10) | ((16u >> 3) << 17) | (1u << 23) | ((128u >> 4) << 24);
 
-// Writes the eight digit rows of v[0..K) and their scale atoms.  A thread owns eight consecutive
-// elements, i.e. one 32-bit word of every digit row; the four lanes of a scale block agree on its
-// exponent E (largest magnitude < 2^E, clamped to [-100, 128]).  With the bias 4 * (8^8 - 1) / 7
-// added, the balanced digits of q are the plain base-8 digits minus 4, so no carry runs through
-// them.  Rows 8-15 of the tile are zeroed by the caller; the blocks' exponents go to sE, from which
-// store_digit_scales writes the digit rows' scale codes into tensor memory.
-__device__ void build_digits(const float *v0, const float *v1, uint32_t n_vec, uint32_t K,
-                             uint8_t *sB, uint32_t b_stride, uint8_t *sE, uint32_t tid,
-                             uint32_t n_threads) {
-    const uint32_t per_vec = K >> 3;
-    for (uint32_t item = tid; item < n_vec * per_vec; item += n_threads) {
-        const uint32_t slot = item >= per_vec ? 1u : 0u, g = item - slot * per_vec;
-        const float *v = slot ? v1 : v0;
-        // read through L2: a hidden vector was written by other CTAs of this launch
-        const float4 p0 = __ldcg(reinterpret_cast<const float4 *>(v) + 2u * g);
-        const float4 p1 = __ldcg(reinterpret_cast<const float4 *>(v) + 2u * g + 1u);
-        const float xs[8] = {p0.x, p0.y, p0.z, p0.w, p1.x, p1.y, p1.z, p1.w};
-        float bm = 0.0f;
+// Writes the eight digit rows of elements 8g .. 8g+7 of a vector and, for the first thread of a
+// scale block, the block's exponent.  Thread g of the CTA owns group g, i.e. one 32-bit word of
+// every digit row; the four lanes of a scale block agree on its exponent E (largest magnitude
+// < 2^E, clamped to [-100, 127]), so whole warps call this together.  With the bias
+// 4 * (8^8 - 1) / 7 added, the balanced digits of q are the plain base-8 digits minus 4, so no
+// carry runs through them.  Rows 8-15 of the tile are zeroed by the caller; the blocks' exponents
+// go to sE, from which store_digit_scales writes the digit rows' scale codes into tensor memory.
+__device__ __forceinline__ void digits_of8(const float (&xs)[8], uint32_t g, uint8_t *sB, uint8_t *sE) {
+    float bm = 0.0f;
 #pragma unroll
-        for (int i = 0; i < 8; ++i) bm = fmaxf(bm, fabsf(xs[i]));
-        bm = fmaxf(bm, __shfl_xor_sync(0xffffffffu, bm, 1));
-        bm = fmaxf(bm, __shfl_xor_sync(0xffffffffu, bm, 2));
-        int E = -100;
-        if (bm > 0.0f) E = min(max((int)((__float_as_uint(bm) >> 23) & 0xFFu) - 126, -100), 127);
-        const float up = __uint_as_float((uint32_t)(150 - E) << 23);  // 2^(23-E)
-        uint32_t words[8] = {0u, 0u, 0u, 0u, 0u, 0u, 0u, 0u};
+    for (int i = 0; i < 8; ++i) bm = fmaxf(bm, fabsf(xs[i]));
+    bm = fmaxf(bm, __shfl_xor_sync(0xffffffffu, bm, 1));
+    bm = fmaxf(bm, __shfl_xor_sync(0xffffffffu, bm, 2));
+    int E = -100;
+    if (bm > 0.0f) E = min(max((int)((__float_as_uint(bm) >> 23) & 0xFFu) - 126, -100), 127);
+    const float up = __uint_as_float((uint32_t)(150 - E) << 23);  // 2^(23-E)
+    uint32_t words[8] = {0u, 0u, 0u, 0u, 0u, 0u, 0u, 0u};
 #pragma unroll
-        for (int i = 0; i < 8; ++i) {
-            const uint32_t qb = (uint32_t)(__float2int_rn(xs[i] * up) + 0x924924);  // in [0, 8^8 + 8^7) for finite input
+    for (int i = 0; i < 8; ++i) {
+        const uint32_t qb = (uint32_t)(__float2int_rn(xs[i] * up) + 0x924924);  // in [0, 8^8 + 8^7) for finite input
 #pragma unroll
-            for (int j = 0; j < 7; ++j)  // E2M1 codes of -4..3 by digit value 0..7
-                words[j] |= ((0x5420ACDEu >> (((qb >> (3 * j)) & 7u) << 2)) & 0xFu) << (4 * i);
-            const uint32_t top = qb >> 21;  // 0..8 -> -4..4
-            words[7] |= (top > 7u ? 6u : ((0x5420ACDEu >> (top << 2)) & 0xFu)) << (4 * i);
-        }
-        const uint32_t kb = g >> 2;
-        uint8_t *chunk = sB + slot * b_stride + (kb >> 3) * 2048u + (g & 3u) * 4u;
-#pragma unroll
-        for (uint32_t j = 0; j < 8; ++j)
-            *reinterpret_cast<uint32_t *>(chunk + j * 128u + (((kb & 7u) ^ j) << 4)) = words[j];
-        if ((g & 3u) == 0u) sE[slot * kMaxBlocks + kb] = (uint8_t)(E + 100);  // the block's exponent, biased
+        for (int j = 0; j < 7; ++j)  // E2M1 codes of -4..3 by digit value 0..7
+            words[j] |= ((0x5420ACDEu >> (((qb >> (3 * j)) & 7u) << 2)) & 0xFu) << (4 * i);
+        const uint32_t top = qb >> 21;  // 0..8 -> -4..4
+        words[7] |= (top > 7u ? 6u : ((0x5420ACDEu >> (top << 2)) & 0xFu)) << (4 * i);
     }
+    const uint32_t kb = g >> 2;
+    uint8_t *chunk = sB + (kb >> 3) * 2048u + (g & 3u) * 4u;
+#pragma unroll
+    for (uint32_t j = 0; j < 8; ++j)
+        *reinterpret_cast<uint32_t *>(chunk + j * 128u + (((kb & 7u) ^ j) << 4)) = words[j];
+    if ((g & 3u) == 0u) sE[kb] = (uint8_t)(E + 100);  // the block's exponent, biased
 }
 
 // The scale codes of the digit rows, written to tensor memory by the eight epilogue warps (each
@@ -244,10 +236,113 @@ __device__ __forceinline__ uint32_t ld_acquire(const unsigned int *p) {
 // halves of a row are 128 B apart (leading offset), 8-row groups 256 B apart (stride offset).
 __device__ __forceinline__ uint64_t smem_desc_k64(uint32_t addr) { return smem_desc(addr, 8, 16, 0); }
 
+// The routes of the token from the experts' scores, by one warp (the same picks, sums and weights
+// as k_router's last block: largest score + bias first, lowest id on ties; weight = score / sum of
+// the picked scores x route_scale).  Scores, selection values and page addresses come in one round
+// of loads; the picked expert's values come from the lane that holds them.  Lane 0 writes the jobs
+// (route order, the shared expert last) and the mix; `publish` also writes the caller's ids and
+// weights.  Expert parallel: the rank keeps the jobs of the experts it owns and, as the shared
+// expert's owner, the shared job; every job writes the row of its route slot.
+__device__ void route_select(const FusedRouter &rt, uint32_t lane, bool publish, Job *jobs, uint32_t *n_jobs_out,
+                             float *mix_w, uint32_t *mix_job) {
+    unsigned long long key[8], pg[8];
+    float sc[8];
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+        const uint32_t e = i * 32 + lane;
+        key[i] = 0ull;
+        pg[i] = 0ull;
+        sc[i] = 0.0f;
+        if (e < rt.n_experts) {
+            const uint32_t bits = __float_as_uint(__ldcg(rt.select + e));
+            sc[i] = __ldcg(rt.scores + e);
+            pg[i] = __ldg(reinterpret_cast<const unsigned long long *>(rt.page_table) + e);
+            const uint32_t ordered = (bits & 0x80000000u) ? ~bits : (bits | 0x80000000u);
+            key[i] = ((unsigned long long)ordered << 32) | (unsigned long long)(0xffffffffu - e);
+        }
+    }
+    int32_t ids[S14_EXPERTS_PER_TOKEN];
+    float picked[S14_EXPERTS_PER_TOKEN];
+    unsigned long long pages[S14_EXPERTS_PER_TOKEN];
+#pragma unroll
+    for (int j = 0; j < S14_EXPERTS_PER_TOKEN; ++j) {
+        ids[j] = -1;
+        picked[j] = 0.0f;
+        pages[j] = 0ull;
+        if ((uint32_t)j < rt.top_k) {
+            unsigned long long best = key[0];
+#pragma unroll
+            for (int i = 1; i < 8; ++i) best = key[i] > best ? key[i] : best;
+#pragma unroll
+            for (int o = 16; o > 0; o >>= 1) {
+                const unsigned long long other = __shfl_xor_sync(0xffffffffu, best, o);
+                best = other > best ? other : best;
+            }
+            const uint32_t e = 0xffffffffu - (uint32_t)(best & 0xffffffffull);
+            float my_sc = sc[0];
+            unsigned long long my_pg = pg[0];
+#pragma unroll
+            for (int i = 1; i < 8; ++i) {
+                if ((e >> 5) == (uint32_t)i) {
+                    my_sc = sc[i];
+                    my_pg = pg[i];
+                }
+            }
+#pragma unroll
+            for (int i = 0; i < 8; ++i)
+                if (key[i] == best) key[i] = 0ull;  // taken
+            ids[j] = (int32_t)e;
+            picked[j] = __shfl_sync(0xffffffffu, my_sc, e & 31u);
+            pages[j] = __shfl_sync(0xffffffffu, my_pg, e & 31u);
+        }
+    }
+    if (lane != 0) return;
+    float sum = 0.0f;
+#pragma unroll
+    for (int j = 0; j < S14_EXPERTS_PER_TOKEN; ++j)
+        if ((uint32_t)j < rt.top_k) sum = __fadd_rn(sum, picked[j]);
+    uint32_t n = 0;
+#pragma unroll
+    for (int j = 0; j < S14_EXPERTS_PER_TOKEN; ++j) {
+        if ((uint32_t)j >= rt.top_k) continue;
+        const float w = __fmul_rn(__fdiv_rn(picked[j], sum), rt.route_scale);
+        if (publish && rt.ids_out) rt.ids_out[j] = ids[j];
+        if (publish && rt.weights_out) rt.weights_out[j] = w;
+        if (((uint32_t)ids[j] % rt.ep_world) == rt.ep_rank) {
+            Job jb;
+            jb.page = reinterpret_cast<const uint8_t *>(pages[j]);
+            jb.kind = S14_PAGE_MXFP4;
+            jb.token = 0;
+            jb.weight = w;
+            jb.is_shared = 0;
+            jb.out_index = (uint32_t)j;
+            jobs[n] = jb;
+            mix_w[n] = w;
+            mix_job[n] = n;
+            ++n;
+        }
+    }
+    if (rt.shared_page && rt.shared_owner == rt.ep_rank) {
+        Job jb;
+        jb.page = rt.shared_page;
+        jb.kind = rt.shared_kind;
+        jb.token = 0;
+        jb.weight = 1.0f;
+        jb.is_shared = 1;
+        jb.out_index = rt.top_k;
+        jobs[n] = jb;
+        mix_w[n] = 1.0f;
+        mix_job[n] = n | 0x80000000u;
+        ++n;
+    }
+    *n_jobs_out = n;
+}
+
 __global__ void __launch_bounds__(kThreads, 1)
 k_moe_layer_umma(const JobTable *__restrict__ dev_table, const __grid_constant__ JobTable param_table,
                  const float *__restrict__ x, float *d_out, float *__restrict__ y, float *part,
-                 unsigned int *counters, uint32_t *__restrict__ status, uint32_t hidden, uint32_t inter) {
+                 unsigned int *counters, uint32_t *__restrict__ status, uint32_t hidden, uint32_t inter,
+                 const __grid_constant__ FusedRouter rt) {
     extern __shared__ __align__(1024) uint8_t smem[];
     __shared__ __align__(8) uint64_t bars[kBars];
     __shared__ __align__(16) uint8_t sE[kMaxBlocks];         // block exponents of the token's digits
@@ -256,6 +351,8 @@ k_moe_layer_umma(const JobTable *__restrict__ dev_table, const __grid_constant__
     __shared__ uint8_t sEh[kItemSlots][2];
     __shared__ float s_mix_w[S14_EXPERTS_PER_TOKEN + 1];        // the mix, in route order: weight (shared expert: 1)
     __shared__ uint32_t s_mix_job[S14_EXPERTS_PER_TOKEN + 1];   //   job, bit 31 set for the shared expert
+    __shared__ Job s_jobs[S14_EXPERTS_PER_TOKEN + 1];           // the layer's jobs, from the routes or the caller's table
+    __shared__ uint32_t s_n_jobs;
     __shared__ uint32_t tmem_slot;
     __shared__ int abort_flag;
 
@@ -270,6 +367,28 @@ k_moe_layer_umma(const JobTable *__restrict__ dev_table, const __grid_constant__
     uint8_t *const sBx = sSF + kRing * kStageSf;  // the token's digit tile, 2 KB per 256 K-elements
     const uint32_t bar0 = smem_u32(bars);
     auto bar = [&](uint32_t i) { return bar0 + i * 8u; };
+
+    // Thread t owns elements 8t .. 8t+7 of the token (hidden <= 8 x kThreads), for the digits and for
+    // the router's dot products; the router weights of this CTA's experts (cta, cta + grid, ...) are
+    // asked for first, so that they arrive while the CTA sets itself up.
+    const bool routes_here = rt.weight != nullptr;
+    const bool has_x = tid < (hidden >> 3);
+    float xs[8] = {0.0f, 0.0f, 0.0f, 0.0f, 0.0f, 0.0f, 0.0f, 0.0f};
+    uint4 rq[kRouterSlots];
+    if (routes_here) {
+#pragma unroll
+        for (uint32_t k = 0; k < kRouterSlots; ++k) {
+            const uint32_t e = blockIdx.x + k * gridDim.x;
+            rq[k] = make_uint4(0u, 0u, 0u, 0u);
+            if (has_x && e < rt.n_experts) rq[k] = ldg_stream(reinterpret_cast<const uint4 *>(rt.weight + (size_t)e * hidden) + tid);
+        }
+    }
+    if (has_x) {
+        const float4 p0 = __ldcg(reinterpret_cast<const float4 *>(x) + 2u * tid);
+        const float4 p1 = __ldcg(reinterpret_cast<const float4 *>(x) + 2u * tid + 1u);
+        xs[0] = p0.x, xs[1] = p0.y, xs[2] = p0.z, xs[3] = p0.w;
+        xs[4] = p1.x, xs[5] = p1.y, xs[6] = p1.z, xs[7] = p1.w;
+    }
 
     // rows 8-15 of the digit tiles stay zero
     for (uint32_t i = tid; i < (KU * 2048u) >> 4; i += kThreads) reinterpret_cast<uint4 *>(sBx)[i] = make_uint4(0u, 0u, 0u, 0u);
@@ -303,31 +422,83 @@ k_moe_layer_umma(const JobTable *__restrict__ dev_table, const __grid_constant__
     fence_after();
     const uint32_t tmem = tmem_slot;
 
-    // The token does not depend on the router: its digits are built while the router runs; the
-    // job table is read only after the router has finished.
-    build_digits(x, x, 1, hidden, sBx, 0, sE, tid, kThreads);
+    if (routes_here) {
+        // ---- expert scores: logit = x . w in double (warp sums, then the sixteen warps in order),
+        // rounded to F32; score and score + bias go to global memory, then the CTA counts itself ----
+        double *s_red = reinterpret_cast<double *>(smem);  // [slot][warp]; the ring is not in use yet
+#pragma unroll
+        for (uint32_t k = 0; k < kRouterSlots; ++k) {
+            if (blockIdx.x + k * gridDim.x >= rt.n_experts) break;
+            const uint32_t wd[4] = {rq[k].x, rq[k].y, rq[k].z, rq[k].w};
+            double acc0 = 0.0, acc1 = 0.0;
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+                acc0 += (double)xs[i * 2] * (double)__uint_as_float(wd[i] << 16);
+                acc1 += (double)xs[i * 2 + 1] * (double)__uint_as_float(wd[i] & 0xffff0000u);
+            }
+            const double ws = warp_sum(acc0 + acc1);
+            if (lane == 0) s_red[k * (kThreads / 32u) + warp] = ws;
+        }
+        __syncthreads();
+        if (tid < kRouterSlots && blockIdx.x + tid * gridDim.x < rt.n_experts) {
+            const uint32_t e = blockIdx.x + tid * gridDim.x;
+            double sum = 0.0;
+            for (uint32_t w = 0; w < kThreads / 32u; ++w) sum += s_red[tid * (kThreads / 32u) + w];
+            const float sc = router_score_f32(sum, rt.score_fn);
+            rt.scores[e] = sc;
+            rt.select[e] = __fadd_rn(sc, rt.bias ? rt.bias[e] : 0.0f);
+        }
+        __threadfence();
+        __syncthreads();
+        if (tid == 0) atomicAdd(counters + kRouteCounter, 1u);
+    }
+
+    // the token's digits (they do not depend on the routes)
+    if (has_x) digits_of8(xs, tid, sBx, sE);
     __syncthreads();  // every block exponent is written
     if (warp < 2u * kEpiGroup / 32u) {
         store_digit_scales(tmem + kColSfbX, sE, hidden, warp, lane);
         fence_before();
         mbar_arrive(bar(kBarXReady));
     }
-    cudaGridDependencySynchronize();
-    const JobTable &tab = table_of(dev_table, param_table);
-    const uint32_t n_jobs = tab.n_jobs, n_items = n_jobs * S, grid = gridDim.x, cta = blockIdx.x;
+    const uint32_t grid = gridDim.x, cta = blockIdx.x;
+    if (routes_here) {
+        // every CTA's scores are needed: all CTAs are resident (one per SM), the wait is bounded
+        if (tid == 0) {
+            uint32_t tries = 0;
+            while (ld_acquire(counters + kRouteCounter) < grid) {
+                if (++tries > kSpinGlobal) {
+                    abort_flag = 1;
+                    break;
+                }
+                __nanosleep(40);
+            }
+        }
+        __syncthreads();
+        if (warp == 0 && !abort_flag) route_select(rt, lane, cta == 0, s_jobs, &s_n_jobs, s_mix_w, s_mix_job);
+        if (tid == 0 && abort_flag) s_n_jobs = 0;
+    } else {
+        // a router launched before this kernel has finished when this returns
+        cudaGridDependencySynchronize();
+        const JobTable &tab = table_of(dev_table, param_table);
+        const uint32_t nj = min(tab.token_job_begin[1] - tab.token_job_begin[0], (uint32_t)S14_EXPERTS_PER_TOKEN + 1u);
+        if (tid < min(tab.n_jobs, (uint32_t)S14_EXPERTS_PER_TOKEN + 1u)) s_jobs[tid] = tab.jobs[tid];
+        if (tid < nj) {
+            const uint32_t jb = tab.token_jobs[tab.token_job_begin[0] + tid];  // the job table may live in global memory
+            s_mix_w[tid] = tab.jobs[jb].weight;
+            s_mix_job[tid] = jb | (tab.jobs[jb].is_shared ? 0x80000000u : 0u);
+        }
+        if (tid == 0) s_n_jobs = min(tab.n_jobs, (uint32_t)S14_EXPERTS_PER_TOKEN + 1u);
+    }
+    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");  // the digit tiles are read by the tensor cores
+    __syncthreads();
+    const uint32_t n_jobs = s_n_jobs, n_items = n_jobs * S;
     // items are dealt in equal shares; with more CTAs than items the last CTAs have none
     const uint32_t G = min(grid, n_items);
     const uint32_t q0 = cta < G ? (uint32_t)((uint64_t)n_items * cta / G) : 0u;
     const uint32_t q1 = cta < G ? (uint32_t)((uint64_t)n_items * (cta + 1u) / G) : 0u;
     const uint32_t n_it = min(q1 - q0, kItemSlots);  // the launcher keeps the share within kItemSlots
     const uint32_t nU = n_it * KU, nD = n_it * DS;
-    if (tid < tab.token_job_begin[1] - tab.token_job_begin[0] && tid <= S14_EXPERTS_PER_TOKEN) {
-        const uint32_t jb = tab.token_jobs[tab.token_job_begin[0] + tid];  // the job table may live in global memory
-        s_mix_w[tid] = tab.jobs[jb].weight;
-        s_mix_job[tid] = jb | (tab.jobs[jb].is_shared ? 0x80000000u : 0u);
-    }
-    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
-    __syncthreads();
 
     if (is_producer && n_it) {
         // ---- copies: the up units of every item, then the down stages of every item ----
@@ -337,7 +508,7 @@ k_moe_layer_umma(const JobTable *__restrict__ dev_table, const __grid_constant__
         uint32_t i = 0;
         for (uint32_t l = 0; l < n_it && ok; ++l) {
             const uint32_t q = q0 + l, j = q / S, sl = q - j * S;
-            const PageView pv = page_view(tab.jobs[j].page, S14_PAGE_MXFP4, hidden, inter);
+            const PageView pv = page_view(s_jobs[j].page, S14_PAGE_MXFP4, hidden, inter);
             // rows r8, r8 + 16, ... of the tile: the first four are w1 rows of the slice, the last four w3 rows
             const uint8_t *src1 = pv.w1 + (size_t)(sl * 64u + r8) * (hidden >> 1) + cc * 16u;
             const uint8_t *src3 = pv.w3 + (size_t)(sl * 64u + r8) * (hidden >> 1) + cc * 16u;
@@ -361,7 +532,7 @@ k_moe_layer_umma(const JobTable *__restrict__ dev_table, const __grid_constant__
         }
         for (uint32_t l = 0; l < n_it && ok; ++l) {
             const uint32_t q = q0 + l, j = q / S, sl = q - j * S;
-            const PageView pv = page_view(tab.jobs[j].page, S14_PAGE_MXFP4, hidden, inter);
+            const PageView pv = page_view(s_jobs[j].page, S14_PAGE_MXFP4, hidden, inter);
             const uint8_t *wsrc = pv.w2 + (size_t)sl * RT * 4096u + pt * 16u;        // the slice's columns, 4 KB per row tile
             const uint8_t *sf = pv.s2 + (size_t)(sl >> 1) * RT * 512u + pt * 16u;   // the slice pair's atoms
             for (uint32_t v = 0; v < DS; ++v, ++i) {
@@ -621,7 +792,7 @@ k_moe_layer_umma(const JobTable *__restrict__ dev_table, const __grid_constant__
             }
             const float v = __fadd_rn(hi, lo);
             dj[t] = v;
-            if (!y) d_out[(size_t)tab.jobs[j].out_index * hidden + n0 + r] = v;  // the caller mixes
+            if (!y) d_out[(size_t)s_jobs[j].out_index * hidden + n0 + r] = v;  // the caller mixes
         }
         __syncthreads();
         if (y && tid < rows) {
@@ -640,6 +811,7 @@ k_moe_layer_umma(const JobTable *__restrict__ dev_table, const __grid_constant__
         if (atomicAdd(counters + kExitCounter, 1u) == grid - 1u) {
             counters[kItemCounter] = 0u;
             counters[kExitCounter] = 0u;
+            counters[kRouteCounter] = 0u;
         }
     }
 }
@@ -696,12 +868,21 @@ bool umma_layer_ok(int sm_count, uint32_t n_tokens, uint32_t n_jobs_max, uint32_
     return umma_smem_bytes(hidden) <= g_dynamic_limit;
 }
 
+bool umma_router_ok(int sm_count, uint32_t n_experts) {
+    return n_experts > 0u && n_experts <= kRouterSlots * (uint32_t)sm_count;
+}
+
 cudaError_t launch_moe_layer_umma(cudaStream_t st, int sm_count, const JobTable *dev, const JobTable &param,
                                   const float *x, float *d, float *y, float *partials, unsigned int *counters,
-                                  uint32_t *status, uint32_t hidden, uint32_t inter, bool after_router) {
+                                  uint32_t *status, uint32_t hidden, uint32_t inter, bool after_router,
+                                  const FusedRouter *router) {
     configure_once();
-    return launch_pdl(k_moe_layer_umma, dim3(sm_count), dim3(kThreads), umma_smem_bytes(hidden), st, after_router, dev,
-                      param, x, d, y, partials, counters, status, hidden, inter);
+    FusedRouter rt = {};
+    if (router) rt = *router;
+    // with the routes computed here nothing earlier in the stream may still be running when the
+    // kernel starts, so the launch is an ordinary one
+    return launch_pdl(k_moe_layer_umma, dim3(sm_count), dim3(kThreads), umma_smem_bytes(hidden), st,
+                      after_router && !router, dev, param, x, d, y, partials, counters, status, hidden, inter, rt);
 }
 
 }  // namespace s14

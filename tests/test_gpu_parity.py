@@ -247,6 +247,38 @@ def test_moe_layer_decode(ctx, oracle, hidden, inter, shared_kind):
     assert e32["rmse"] <= 1.5 * noise["rmse"] + RMSE
 
 
+def test_moe_layer_decode_wide_range_and_zero_blocks(ctx, oracle):
+    """The tensor-core layer kernel writes activations as digit rows per scale block: blocks of
+    zeros, magnitudes from 1e-6 to 1e3 side by side, exact powers of two and a lone large value
+    in a block of small ones.  Gate and up sums reach 2e4 here while only values inside the +-10
+    clamp pass on, so the input is ill-conditioned: the reference's own F32 order is 3.7e-6 of
+    the output RMS away from the double-accumulated result.  The pairwise result is held to
+    twice that noise instead of the 1e-6 bound of well-conditioned inputs."""
+    hidden, inter = 2048, 1024
+    g, pages, shared = make_layer(4321, hidden, inter, 8, L.PAGE_MXFP4)
+    x = synth.activations(g, 1, hidden)
+    x[0] *= 10.0 ** g.uniform(-6.0, 3.0, hidden).astype(np.float32)
+    x[0, 64:160] = 0.0                      # three scale blocks of zeros
+    x[0, 256:288] = 2.0 ** np.arange(-16, 16, dtype=np.float32)  # powers of two, 2^-16 .. 2^15 in one block
+    x[0, 320:352] = 1e-4
+    x[0, 333] = -7.0e3                      # a lone large value among small ones
+    ids = [1, 6, 3, 0, 7, 4]
+    w = np.asarray([0.4, 0.2, 0.15, 0.1, 0.1, 0.05], np.float32)
+    pages_dev, shared_dev = [dev_page(p, hidden, inter) for p in pages], dev_page(shared, hidden, inter)
+    ref64 = oracle.moe_layer_acc64(x[0], [pages[i] for i in ids], w, shared, 0, hidden, inter)
+    ref32 = oracle.moe_layer(x[0], [pages[i] for i in ids], w, shared, 0, hidden, inter)
+    ctx.set_accumulation(L.ACCUM_PAIRWISE)
+    y = run_layer(ctx, x, pages_dev, shared_dev, [(ids, w)], L.PAGE_MXFP4, hidden, inter)[0]
+    assert np.isfinite(y).all()
+    ref = np.asarray(ref64, np.float32)
+    e, noise = oracle.error_stats(y, ref), oracle.error_stats(ref32, ref)
+    assert e["rmse"] <= 2.0 * noise["rmse"] and e["max_abs"] <= 2.0 * noise["max_abs"], (e, noise)
+    ctx.set_accumulation(L.ACCUM_REFERENCE)
+    y = run_layer(ctx, x, pages_dev, shared_dev, [(ids, w)], L.PAGE_MXFP4, hidden, inter)[0]
+    assert np.array_equal(y.view(np.uint32), ref32.view(np.uint32))
+    ctx.set_accumulation(L.ACCUM_PAIRWISE)
+
+
 def test_single_expert_chain_route_weight(ctx, oracle):
     """w1, w3 -> limited SwiGLU -> w2 -> x 0.3 (examples/s14_vulkan_numeric.rs:1296-1300)."""
     hidden, inter = 4096, 2048
