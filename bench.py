@@ -256,6 +256,12 @@ def run_gpu(args) -> None:
     ep_ids = torch.empty((N_LAYERS, TOP_K), dtype=torch.int32, device="cuda")
     ep_w = torch.empty((N_LAYERS, TOP_K), dtype=torch.float32, device="cuda")
     torch.cuda.synchronize()
+    # several GPUs, pairwise order: the exchange of the down vectors runs inside the layer kernel over
+    # the ranks' mapped slot buffers (one launch per rank and step); --exchange nccl keeps the baseline
+    # (owned experts, NCCL all-reduce of the slot buffer, mix kernel)
+    peer_exchange = world > 1 and args.exchange == "peer" and args.accum == "pairwise"
+    if peer_exchange:
+        ep.connect_exchange(ctx, rank, world, HIDDEN)
 
     def enqueue_step(i: int, stream_handle=None):
         ly = layers[i % n_layers]
@@ -267,8 +273,12 @@ def run_gpu(args) -> None:
             ly_state = dict(ly)
             if ly_state["shared"] is None:
                 ly_state["shared"] = ly["pages"].data_ptr()  # never read: this rank is not the owner
-            ep.decode_step(ctx, xs[i % n_tok], ly_state, slots[k], ep_ids[k], ep_w[k], ys[k],
-                           layer=i % n_layers, rank=rank, world=world, inter=INTER, stream=stream_handle)
+            if peer_exchange:
+                ep.decode_step_fused(ctx, xs[i % n_tok], ly_state, ys[k], layer=i % n_layers, world=world,
+                                     inter=INTER, stream=stream_handle)
+            else:
+                ep.decode_step(ctx, xs[i % n_tok], ly_state, slots[k], ep_ids[k], ep_w[k], ys[k],
+                               layer=i % n_layers, rank=rank, world=world, inter=INTER, stream=stream_handle)
 
     _note("layers resident")
     stream = torch.cuda.Stream()
@@ -293,7 +303,7 @@ def run_gpu(args) -> None:
     _note("eager warm-up steps done")
     rem = args.steps % N_LAYERS
     full = args.steps // N_LAYERS
-    if world == 1:
+    if world == 1 or peer_exchange:
         launch_mode = "cuda graph of 14 layer-steps"
         graph = capture(N_LAYERS, 0)
         graph_rem = capture(rem, 0) if rem else None
@@ -324,7 +334,10 @@ def run_gpu(args) -> None:
     sampler = ClockSampler(local_rank)
     if rank == 0:
         sampler.start()
-        time.sleep(0.25)
+    time.sleep(0.25)
+    if world > 1:
+        dist.barrier()  # the ranks start the timed region together: a rank's kernels wait for the others'
+        torch.cuda.synchronize()
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     with torch.cuda.stream(stream):
         e0.record(stream)
@@ -454,7 +467,10 @@ def run_gpu(args) -> None:
             "config": {"workload": WORKLOAD, "layers_resident": n_layers, "accumulation": args.accum,
                        "launch": launch_mode,
                        "l2": "inputs larger than L2: 14 x 3.4 GB of pages walked round-robin, 96 MB per step",
-                       "parallelism": f"ep{world}: expert e on rank e mod {world}, slot all-reduce + ordered mix"
+                       "parallelism": (f"ep{world}: expert e on rank e mod {world}, "
+                                       + ("down vectors stored into every rank's slot buffer over peer memory by the "
+                                          "layer kernel, flag wait, ordered mix in the same launch" if peer_exchange
+                                          else "NCCL all-reduce of the slot buffer + ordered mix"))
                        if world > 1 else "single"},
             "hbm_gbs": value * STEP_BYTES / 1e9, "hbm_frac_of_measured_peak": value * STEP_BYTES / 1e9 / (peak * world),
             "algorithmic_bytes_per_step": STEP_BYTES,
@@ -493,6 +509,8 @@ def main() -> None:
     ap.add_argument("--warmup", type=int, default=None)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--accum", default="pairwise", choices=["pairwise", "reference"])
+    ap.add_argument("--exchange", default="peer", choices=["peer", "nccl"],
+                    help="several GPUs: down vectors exchanged inside the layer kernel over peer memory, or by NCCL all-reduce")
     ap.add_argument("--cpu-steps", type=int, default=60)
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--layers", type=int, default=N_LAYERS,

@@ -77,6 +77,15 @@ struct s14_ctx {
     float *y_host = nullptr, *y_host_dev = nullptr;          // [kMaxDim]
     int32_t *ids_host = nullptr, *ids_host_dev = nullptr;    // [8]
     float *w_host = nullptr, *w_host_dev = nullptr;          // [8]
+    // Expert-parallel exchange over peer memory: this rank's exchange buffer and the ranks' buffers
+    // as mapped here (own buffer included); peers of other processes are opened CUDA IPC handles.
+    struct {
+        uint8_t *buf = nullptr;
+        uint32_t rank = 0, world = 0, hidden = 0;
+        uint8_t *peer[kMaxEpWorld] = {};
+        bool opened[kMaxEpWorld] = {};
+        bool connected = false;
+    } ep;
     UmmaScratch umma{nullptr, nullptr};  // scratch of the tcgen05 layer kernel
     bool use_umma = true;                // S14_TENSOR_PATH=off in the environment turns it off
     const UmmaScratch *umma_scratch() const { return use_umma ? &umma : nullptr; }
@@ -148,6 +157,7 @@ extern "C" int32_t s14_ctx_destroy(s14_ctx *ctx) {
     cudaFree(ctx->ids_stage);
     cudaFree(ctx->weights_stage);
     cudaFree(ctx->umma.partials);
+    s14_ep_exchange_destroy(ctx);
     cudaFreeHost(ctx->y_host);
     cudaFreeHost(ctx->ids_host);
     cudaFreeHost(ctx->w_host);
@@ -792,6 +802,132 @@ extern "C" int32_t s14_cmd_moe_mix_slots(s14_ctx *ctx, void *stream, const float
     CUDA_OK(launch_mix_slots(stream_of(ctx, stream), slots, weights_dev, n_routed, has_shared, y, hidden));
     ctx->launches += 1;
     return S14_OK;
+}
+
+// ---- expert-parallel exchange over peer memory ------------------------------------------
+
+extern "C" int32_t s14_ep_exchange_destroy(s14_ctx *ctx) {
+    if (!ctx) return S14_OK;
+    for (uint32_t p = 0; p < kMaxEpWorld; ++p) {
+        if (ctx->ep.opened[p]) cudaIpcCloseMemHandle(ctx->ep.peer[p]);
+        ctx->ep.opened[p] = false;
+        ctx->ep.peer[p] = nullptr;
+    }
+    if (ctx->ep.buf) cudaFree(ctx->ep.buf);
+    ctx->ep.buf = nullptr;
+    ctx->ep.connected = false;
+    ctx->ep.world = 0;
+    return S14_OK;
+}
+
+extern "C" int32_t s14_ep_exchange_create(s14_ctx *ctx, uint32_t rank, uint32_t world, uint32_t hidden,
+                                          uint8_t *handle_out) {
+    S14_TRY
+    if (!ctx) throw ContractError("s14_ep_exchange_create: ctx is NULL");
+    if (world < 2 || world > kMaxEpWorld || rank >= world)
+        throw ContractError("S14 expert-parallel exchange: 2..8 ranks, rank inside the world");
+    if (!fused_dim_ok(hidden)) throw ContractError("S14 expert-parallel exchange: hidden must be 1024, 2048 or 4096");
+    if (ctx->ep.buf) throw ContractError("S14 expert-parallel exchange: already created for this context");
+    CUDA_OK(cudaSetDevice(ctx->device));
+    const size_t bytes = ep_exchange_bytes(hidden);
+    CUDA_OK(cudaMalloc(&ctx->ep.buf, bytes));
+    CUDA_OK(cudaMemset(ctx->ep.buf, 0, bytes));
+    CUDA_OK(cudaDeviceSynchronize());
+    ctx->ep.rank = rank;
+    ctx->ep.world = world;
+    ctx->ep.hidden = hidden;
+    if (handle_out) {
+        cudaIpcMemHandle_t h;
+        static_assert(sizeof(h) == S14_EP_HANDLE_BYTES, "IPC handle size");
+        CUDA_OK(cudaIpcGetMemHandle(&h, ctx->ep.buf));
+        std::memcpy(handle_out, &h, sizeof(h));
+    }
+    return S14_OK;
+    S14_CATCH
+}
+
+extern "C" int32_t s14_ep_exchange_connect(s14_ctx *ctx, const uint8_t *handles) {
+    S14_TRY
+    if (!ctx || !handles) throw ContractError("s14_ep_exchange_connect: NULL argument");
+    if (!ctx->ep.buf) throw ContractError("S14 expert-parallel exchange: create it first");
+    if (ctx->ep.connected) throw ContractError("S14 expert-parallel exchange: already connected");
+    CUDA_OK(cudaSetDevice(ctx->device));
+    for (uint32_t p = 0; p < ctx->ep.world; ++p) {
+        if (p == ctx->ep.rank) {
+            ctx->ep.peer[p] = ctx->ep.buf;
+            continue;
+        }
+        cudaIpcMemHandle_t h;
+        std::memcpy(&h, handles + (size_t)p * S14_EP_HANDLE_BYTES, sizeof(h));
+        void *base = nullptr;
+        CUDA_OK(cudaIpcOpenMemHandle(&base, h, cudaIpcMemLazyEnablePeerAccess));
+        ctx->ep.peer[p] = (uint8_t *)base;
+        ctx->ep.opened[p] = true;
+    }
+    ctx->ep.connected = true;
+    return S14_OK;
+    S14_CATCH
+}
+
+extern "C" int32_t s14_ep_exchange_connect_local(s14_ctx *ctx, s14_ctx *const *ranks) {
+    S14_TRY
+    if (!ctx || !ranks) throw ContractError("s14_ep_exchange_connect_local: NULL argument");
+    if (!ctx->ep.buf) throw ContractError("S14 expert-parallel exchange: create it first");
+    if (ctx->ep.connected) throw ContractError("S14 expert-parallel exchange: already connected");
+    for (uint32_t p = 0; p < ctx->ep.world; ++p) {
+        const s14_ctx *o = ranks[p];
+        if (!o || !o->ep.buf || o->ep.world != ctx->ep.world || o->ep.rank != p || o->ep.hidden != ctx->ep.hidden ||
+            o->device != ctx->device)
+            throw ContractError("S14 expert-parallel exchange: rank " + std::to_string(p) +
+                                " is not an exchange of the same world, hidden size and device");
+        ctx->ep.peer[p] = o->ep.buf;
+    }
+    ctx->ep.connected = true;
+    return S14_OK;
+    S14_CATCH
+}
+
+extern "C" int32_t s14_cmd_routed_moe_layer_ep(s14_ctx *ctx, void *stream, const s14_routed_layer_desc *desc,
+                                               uint32_t shared_owner, int32_t wait_and_mix) {
+    S14_TRY
+    if (!ctx || !desc) throw ContractError("s14_cmd_routed_moe_layer_ep: NULL argument");
+    if (!ctx->ep.connected) throw ContractError("S14 expert-parallel layer: the exchange is not connected");
+    const s14_router_desc &r = desc->router;
+    validate_router(r, false);
+    if (r.n_tokens != 1) throw ContractError("S14 expert-parallel layer: one decode token per call");
+    if (r.top_k > S14_EXPERTS_PER_TOKEN) throw ContractError("S14 expert-parallel layer: top_k must be <= 6");
+    if (shared_owner >= ctx->ep.world) throw ContractError("S14 expert-parallel layer: owner outside the world");
+    if (r.hidden != ctx->ep.hidden || !fused_dim_ok(desc->inter))
+        throw ContractError("S14 expert-parallel layer: hidden must be the exchange's, intermediate 1024, 2048 or 4096");
+    if (!desc->page_table || (wait_and_mix && !desc->y))
+        throw ContractError("S14 expert-parallel layer: page_table or y is NULL");
+    if (desc->shared_page && desc->shared_kind != S14_PAGE_MXFP4)
+        throw ContractError("S14 expert-parallel layer: the exchange over peer memory takes MXFP4 pages only");
+    if (ctx->mode != S14_ACCUM_PAIRWISE || !ctx->use_umma)
+        throw ContractError("S14 expert-parallel layer: the exchange over peer memory is part of the pairwise tensor-core kernel");
+    cudaStream_t st = stream_of(ctx, stream);
+    const uint32_t n_slots = r.top_k + (desc->shared_page ? 1u : 0u);
+    const FusedRouter fr = router_of(ctx, desc, ctx->ep.rank, ctx->ep.world, shared_owner);
+    EpExchange ex = {};
+    const size_t slot_bytes = sizeof(float) * 2u * (S14_EXPERTS_PER_TOKEN + 1) * ctx->ep.hidden;
+    for (uint32_t p = 0; p < ctx->ep.world; ++p) {
+        ex.slots[p] = reinterpret_cast<float *>(ctx->ep.peer[p]);
+        ex.flags[p] = reinterpret_cast<uint32_t *>(ctx->ep.peer[p] + slot_bytes);
+    }
+    ex.step = reinterpret_cast<uint32_t *>(ctx->ep.buf + slot_bytes) + kMaxEpWorld;
+    ex.world = ctx->ep.world;
+    ex.rank = ctx->ep.rank;
+    ex.n_slots = n_slots;
+    ex.wait_and_mix = wait_and_mix ? 1u : 0u;
+    JobTable unused;
+    unused.n_jobs = 0;
+    cudaError_t err;
+    ctx->launches += launch_moe_layer(st, ctx->mode, ctx->sm_count, ctx->dev_table, unused, 1, n_slots, r.hidden,
+                                      desc->inter, r.x, ctx->h, ctx->d, desc->y, &err, nullptr, true, ctx->counters,
+                                      ctx->umma_scratch(), &fr, &ex);
+    if (err != cudaSuccess) return cuda_fail(err, "S14 expert-parallel layer launch");
+    return S14_OK;
+    S14_CATCH
 }
 
 extern "C" int32_t s14_routed_moe_layer_host(s14_ctx *ctx, const s14_routed_layer_desc *desc,

@@ -41,6 +41,25 @@ struct KernelMarks {
 
 struct UmmaScratch;
 
+// Expert-parallel exchange of the tcgen05 layer kernel over peer memory.  Every rank holds an
+// exchange buffer: two slot buffers [n_slots, hidden] F32 (steps alternate between them), then
+// kMaxEpWorld arrival flags, then the rank's own step count.  A rank stores the down vectors of the
+// experts it owns into the slot rows of EVERY rank's buffer (plain stores to peer memory), then
+// publishes step + 1 in its flag on every rank; each rank waits (bounded) for all flags in its own
+// buffer and mixes from its own memory.  world <= 1: no exchange.
+constexpr uint32_t kMaxEpWorld = 8;
+struct EpExchange {
+    float *slots[kMaxEpWorld];     // rank p's slot buffers, as mapped on this rank
+    uint32_t *flags[kMaxEpWorld];  // rank p's flags [kMaxEpWorld], as mapped on this rank
+    uint32_t *step;                // this rank's step count (device memory, kept by the kernel)
+    uint32_t world, rank;
+    uint32_t n_slots;              // top_k (+ 1 with a shared expert)
+    uint32_t wait_and_mix;         // 0: publish only (single-GPU emulation of the other ranks)
+};
+inline size_t ep_exchange_bytes(uint32_t hidden) {
+    return sizeof(float) * 2u * (S14_EXPERTS_PER_TOKEN + 1) * hidden + sizeof(uint32_t) * (kMaxEpWorld + 8u);
+}
+
 // What the router reads and writes, for a layer call that computes its own routes: the tcgen05
 // layer kernel scores the experts in its first microseconds (every CTA a few of them), and every
 // CTA then picks the routes from the scores; other layer kernels run k_router first.
@@ -76,7 +95,7 @@ int launch_moe_layer(cudaStream_t st, uint32_t mode, int sm_count, const JobTabl
                      uint32_t hidden, uint32_t inter, const float *x, float *h, float *d, float *y,
                      cudaError_t *err, const KernelMarks *km = nullptr, bool all_mxfp4 = false,
                      unsigned int *counters = nullptr, const struct UmmaScratch *umma = nullptr,
-                     const FusedRouter *router = nullptr);
+                     const FusedRouter *router = nullptr, const EpExchange *ep = nullptr);
 // Scratch of the tcgen05 layer kernel (s14_moe_umma.cu): every item's share of its expert's output
 // (umma_partials_bytes) and the device status word a timed-out wait sets.
 struct UmmaScratch {
@@ -93,7 +112,7 @@ bool umma_router_ok(int sm_count, uint32_t n_experts);
 cudaError_t launch_moe_layer_umma(cudaStream_t st, int sm_count, const JobTable *dev, const JobTable &param,
                                   const float *x, float *d, float *y, float *partials, unsigned int *counters,
                                   uint32_t *status, uint32_t hidden, uint32_t inter, bool after_router,
-                                  const FusedRouter *router = nullptr);
+                                  const FusedRouter *router = nullptr, const EpExchange *ep = nullptr);
 int launch_router(cudaStream_t st, const s14_router_desc &r, float *scores, float *select,
                   JobTable *table_out, const uint8_t *const *page_table, const uint8_t *shared_page,
                   uint32_t shared_kind, unsigned int *counter, cudaError_t *err,

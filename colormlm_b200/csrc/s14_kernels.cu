@@ -934,11 +934,15 @@ int launch_moe_layer(cudaStream_t st, uint32_t mode, int sm_count, const JobTabl
                      const JobTable &param_table, uint32_t n_tokens, uint32_t n_jobs_max,
                      uint32_t hidden, uint32_t inter, const float *x, float *h, float *d, float *y,
                      cudaError_t *err, const KernelMarks *km, bool all_mxfp4, unsigned int *counters,
-                     const UmmaScratch *umma, const FusedRouter *router) {
+                     const UmmaScratch *umma, const FusedRouter *router, const EpExchange *ep) {
     int launches = 0;
     *err = cudaSuccess;
     const bool tensor_path = mode != S14_ACCUM_REFERENCE && all_mxfp4 && counters && umma &&
                              umma_layer_ok(sm_count, n_tokens, n_jobs_max, hidden, inter);
+    if (ep && ep->world > 1u && !(tensor_path && router && umma_router_ok(sm_count, router->n_experts))) {
+        *err = cudaErrorNotSupported;  // the exchange over peer memory is part of the tensor-core layer kernel
+        return launches;
+    }
     if (router && !(tensor_path && umma_router_ok(sm_count, router->n_experts))) {
         // the routes come from a kernel of their own, which fills the device job table
         s14_router_desc r = {};
@@ -973,7 +977,7 @@ int launch_moe_layer(cudaStream_t st, uint32_t mode, int sm_count, const JobTabl
         launches += 2;
     } else if (tensor_path) {
         *err = launch_moe_layer_umma(st, sm_count, dev_table, param_table, x, d, y, umma->partials, counters,
-                                     umma->status, hidden, inter, dev_table != nullptr, router);
+                                     umma->status, hidden, inter, dev_table != nullptr, router, ep);
         launches += 1;
         if (km) {  // one kernel runs both phases and the mix: its time is booked as the up phase
             cudaEventRecord(km->ev[2], st);

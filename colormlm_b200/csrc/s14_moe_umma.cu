@@ -63,6 +63,8 @@ constexpr uint32_t kSpinGlobal = 1u << 20;     // polls (100 ns apart) of the it
 constexpr uint32_t kItemCounter = 1, kExitCounter = 2;  // in the context's counter array ([0] is the router's)
 constexpr uint32_t kRouteCounter = 3;          // CTAs whose expert scores are written (routes computed in this kernel)
 constexpr uint32_t kRouterSlots = 4;           // experts a CTA scores at most
+constexpr uint32_t kEpCounter = 4;             // CTAs whose stores to the peers' slot buffers are fenced
+constexpr uint32_t kSpinEp = 1u << 22;         // polls (about a microsecond each) of the peers' flags: a few seconds
 
 // Bar indices in the static barrier array.
 constexpr uint32_t kBarFull = 0;                      // ring slot filled with an up unit (128 copying threads)
@@ -226,6 +228,14 @@ __device__ __forceinline__ float swiglu_limit_fast(float gate, float up) {
 }
 
 
+__device__ __forceinline__ uint32_t ld_acquire_sys(const uint32_t *p) {
+    uint32_t v;
+    asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+    return v;
+}
+__device__ __forceinline__ void st_release_sys(uint32_t *p, uint32_t v) {
+    asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
+}
 __device__ __forceinline__ uint32_t ld_acquire(const unsigned int *p) {
     uint32_t v;
     asm volatile("ld.acquire.gpu.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
@@ -240,11 +250,11 @@ __device__ __forceinline__ uint64_t smem_desc_k64(uint32_t addr) { return smem_d
 // as k_router's last block: largest score + bias first, lowest id on ties; weight = score / sum of
 // the picked scores x route_scale).  Scores, selection values and page addresses come in one round
 // of loads; the picked expert's values come from the lane that holds them.  Lane 0 writes the jobs
-// (route order, the shared expert last) and the mix; `publish` also writes the caller's ids and
-// weights.  Expert parallel: the rank keeps the jobs of the experts it owns and, as the shared
+// (route order, the shared expert last), the mix and every route's weight; `publish` also writes
+// the caller's ids and weights.  Expert parallel: the rank keeps the jobs of the experts it owns and, as the shared
 // expert's owner, the shared job; every job writes the row of its route slot.
 __device__ void route_select(const FusedRouter &rt, uint32_t lane, bool publish, Job *jobs, uint32_t *n_jobs_out,
-                             float *mix_w, uint32_t *mix_job) {
+                             float *mix_w, uint32_t *mix_job, float *route_w) {
     unsigned long long key[8], pg[8];
     float sc[8];
 #pragma unroll
@@ -308,6 +318,7 @@ __device__ void route_select(const FusedRouter &rt, uint32_t lane, bool publish,
         const float w = __fmul_rn(__fdiv_rn(picked[j], sum), rt.route_scale);
         if (publish && rt.ids_out) rt.ids_out[j] = ids[j];
         if (publish && rt.weights_out) rt.weights_out[j] = w;
+        route_w[j] = w;  // every route's weight, also of experts other ranks own
         if (((uint32_t)ids[j] % rt.ep_world) == rt.ep_rank) {
             Job jb;
             jb.page = reinterpret_cast<const uint8_t *>(pages[j]);
@@ -342,7 +353,7 @@ __global__ void __launch_bounds__(kThreads, 1)
 k_moe_layer_umma(const JobTable *__restrict__ dev_table, const __grid_constant__ JobTable param_table,
                  const float *__restrict__ x, float *d_out, float *__restrict__ y, float *part,
                  unsigned int *counters, uint32_t *__restrict__ status, uint32_t hidden, uint32_t inter,
-                 const __grid_constant__ FusedRouter rt) {
+                 const __grid_constant__ FusedRouter rt, const __grid_constant__ EpExchange ep) {
     extern __shared__ __align__(1024) uint8_t smem[];
     __shared__ __align__(8) uint64_t bars[kBars];
     __shared__ __align__(16) uint8_t sE[kMaxBlocks];         // block exponents of the token's digits
@@ -353,6 +364,7 @@ k_moe_layer_umma(const JobTable *__restrict__ dev_table, const __grid_constant__
     __shared__ uint32_t s_mix_job[S14_EXPERTS_PER_TOKEN + 1];   //   job, bit 31 set for the shared expert
     __shared__ Job s_jobs[S14_EXPERTS_PER_TOKEN + 1];           // the layer's jobs, from the routes or the caller's table
     __shared__ uint32_t s_n_jobs;
+    __shared__ float s_route_w[S14_EXPERTS_PER_TOKEN];         // expert parallel: the weight of every route
     __shared__ uint32_t tmem_slot;
     __shared__ int abort_flag;
 
@@ -372,6 +384,10 @@ k_moe_layer_umma(const JobTable *__restrict__ dev_table, const __grid_constant__
     // the router's dot products; the router weights of this CTA's experts (cta, cta + grid, ...) are
     // asked for first, so that they arrive while the CTA sets itself up.
     const bool routes_here = rt.weight != nullptr;
+    // expert parallel: the step count picks the slot buffer and the flag value; the last CTA to
+    // leave advances it, after every CTA has read it
+    const bool ep_on = ep.world > 1u;
+    const uint32_t ep_step = ep_on ? __ldcg(ep.step) : 0u;
     const bool has_x = tid < (hidden >> 3);
     float xs[8] = {0.0f, 0.0f, 0.0f, 0.0f, 0.0f, 0.0f, 0.0f, 0.0f};
     uint4 rq[kRouterSlots];
@@ -475,7 +491,7 @@ k_moe_layer_umma(const JobTable *__restrict__ dev_table, const __grid_constant__
             }
         }
         __syncthreads();
-        if (warp == 0 && !abort_flag) route_select(rt, lane, cta == 0, s_jobs, &s_n_jobs, s_mix_w, s_mix_job);
+        if (warp == 0 && !abort_flag) route_select(rt, lane, cta == 0, s_jobs, &s_n_jobs, s_mix_w, s_mix_job, s_route_w);
         if (tid == 0 && abort_flag) s_n_jobs = 0;
     } else {
         // a router launched before this kernel has finished when this returns
@@ -792,10 +808,50 @@ k_moe_layer_umma(const JobTable *__restrict__ dev_table, const __grid_constant__
             }
             const float v = __fadd_rn(hi, lo);
             dj[t] = v;
-            if (!y) d_out[(size_t)s_jobs[j].out_index * hidden + n0 + r] = v;  // the caller mixes
+            if (ep_on) {
+                // the expert's rows of this CTA go to the route slot's row in every rank's slot buffer
+                const size_t at = ((size_t)(ep_step & 1u) * ep.n_slots + s_jobs[j].out_index) * hidden + n0 + r;
+                for (uint32_t p = 0; p < ep.world; ++p) ep.slots[p][at] = v;
+            } else if (!y) {
+                d_out[(size_t)s_jobs[j].out_index * hidden + n0 + r] = v;  // the caller mixes
+            }
         }
         __syncthreads();
-        if (y && tid < rows) {
+        if (ep_on) {
+            // ---- exchange: when every CTA's stores are fenced, the rank publishes step + 1 in its flag
+            // on every rank; then it waits (bounded) for all ranks' flags in its own memory and mixes
+            // rows [n0, n1) from its own slot buffer, in route order, the shared expert last ----
+            __threadfence_system();
+            __syncthreads();
+            if (tid == 0 && atomicAdd(counters + kEpCounter, 1u) == grid - 1u) {
+                __threadfence_system();
+                for (uint32_t p = 0; p < ep.world; ++p) st_release_sys(ep.flags[p] + ep.rank, ep_step + 1u);
+                counters[kEpCounter] = 0u;
+                *ep.step = ep_step + 1u;
+            }
+            if (ep.wait_and_mix) {
+                if (tid < ep.world) {
+                    uint32_t tries = 0;
+                    while ((int32_t)(ld_acquire_sys(ep.flags[ep.rank] + tid) - (ep_step + 1u)) < 0) {
+                        if (++tries > kSpinEp) {
+                            abort_flag = 1;
+                            atomicExch(status, 0x5503u);
+                            break;
+                        }
+                        __nanosleep(200);
+                    }
+                }
+                __syncthreads();
+                if (!abort_flag && y && tid < rows) {
+                    const float *slot = ep.slots[ep.rank] + (size_t)(ep_step & 1u) * ep.n_slots * hidden + n0 + tid;
+                    float acc = 0.0f;
+                    for (uint32_t jj = 0; jj < rt.top_k; ++jj)
+                        acc = __fadd_rn(acc, __fmul_rn(s_route_w[jj], __ldcg(slot + (size_t)jj * hidden)));
+                    if (ep.n_slots > rt.top_k) acc = __fadd_rn(acc, __ldcg(slot + (size_t)rt.top_k * hidden));
+                    y[n0 + tid] = acc;
+                }
+            }
+        } else if (y && tid < rows) {
             float acc = 0.0f;
             for (uint32_t jj = 0; jj < n_jobs; ++jj) {
                 const uint32_t jb = s_mix_job[jj];
@@ -875,14 +931,17 @@ bool umma_router_ok(int sm_count, uint32_t n_experts) {
 cudaError_t launch_moe_layer_umma(cudaStream_t st, int sm_count, const JobTable *dev, const JobTable &param,
                                   const float *x, float *d, float *y, float *partials, unsigned int *counters,
                                   uint32_t *status, uint32_t hidden, uint32_t inter, bool after_router,
-                                  const FusedRouter *router) {
+                                  const FusedRouter *router, const EpExchange *ep) {
     configure_once();
     FusedRouter rt = {};
     if (router) rt = *router;
+    EpExchange ex = {};
+    if (ep) ex = *ep;
+    if (ex.world > 1u && !router) return cudaErrorInvalidValue;  // the mix needs every route's weight
     // with the routes computed here nothing earlier in the stream may still be running when the
     // kernel starts, so the launch is an ordinary one
     return launch_pdl(k_moe_layer_umma, dim3(sm_count), dim3(kThreads), umma_smem_bytes(hidden), st,
-                      after_router && !router, dev, param, x, d, y, partials, counters, status, hidden, inter, rt);
+                      after_router && !router, dev, param, x, d, y, partials, counters, status, hidden, inter, rt, ex);
 }
 
 }  // namespace s14

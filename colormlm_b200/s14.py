@@ -199,6 +199,45 @@ class S14Context:
             self._h, stream if stream is not None else _torch_stream(), C.byref(d), ep_rank, ep_world,
             shared_owner, slots_out.data_ptr()))
 
+    EP_HANDLE_BYTES = 64
+
+    def ep_exchange_create(self, rank: int, world: int, hidden: int) -> bytes:
+        """Allocates this rank's exchange buffer of the expert-parallel layer; returns its CUDA IPC
+        handle (64 bytes) for the other ranks' processes."""
+        h = (C.c_uint8 * self.EP_HANDLE_BYTES)()
+        check(L.lib().s14_ep_exchange_create(self._h, rank, world, hidden, C.cast(h, C.c_void_p)))
+        return bytes(h)
+
+    def ep_exchange_connect(self, handles) -> None:
+        """``handles``: every rank's handle in rank order (this rank's own entry is not opened)."""
+        blob = b"".join(bytes(h) for h in handles)
+        buf = (C.c_uint8 * len(blob)).from_buffer_copy(blob)
+        check(L.lib().s14_ep_exchange_connect(self._h, C.cast(buf, C.c_void_p)))
+
+    def ep_exchange_connect_local(self, ranks) -> None:
+        """The ranks are contexts of this process on the same GPU (tests)."""
+        arr = (C.c_void_p * len(ranks))(*[r._h for r in ranks])
+        check(L.lib().s14_ep_exchange_connect_local(self._h, arr))
+
+    def ep_exchange_destroy(self) -> None:
+        check(L.lib().s14_ep_exchange_destroy(self._h))
+
+    def cmd_routed_moe_layer_ep(self, x, y, wr_bf16, bias, page_table, shared_page: Optional[int], inter: int, *,
+                                shared_owner: int, wait_and_mix: bool = True, ids_out=None, weights_out=None,
+                                score_fn: int = L.SCORE_SIGMOID, top_k: int = 6, route_scale: float = 1.0,
+                                stream: Optional[int] = None) -> None:
+        """One expert-parallel decode step in one launch: routes, owned experts, exchange of the
+        down vectors through the ranks' mapped slot buffers, ordered mix into y on every rank."""
+        d = L.RoutedLayerDesc()
+        d.router = _router_desc(x, wr_bf16, bias, ids_out, weights_out, score_fn, top_k, route_scale)
+        d.inter, d.shared_kind = inter, L.PAGE_MXFP4
+        d.page_table = page_table.data_ptr()
+        d.shared_page = shared_page
+        d.y = y.data_ptr() if y is not None else None
+        check(L.lib().s14_cmd_routed_moe_layer_ep(
+            self._h, stream if stream is not None else _torch_stream(), C.byref(d), shared_owner,
+            1 if wait_and_mix else 0))
+
     def cmd_moe_mix_slots(self, slots, weights_dev, n_routed: int, has_shared: bool, y,
                           stream: Optional[int] = None) -> None:
         check(L.lib().s14_cmd_moe_mix_slots(self._h, stream if stream is not None else _torch_stream(),

@@ -312,6 +312,31 @@ S14_API int32_t s14_cmd_moe_mix_slots(s14_ctx *ctx, void *stream, const float *s
                                       const float *weights_dev, uint32_t n_routed, int32_t has_shared,
                                       float *y, uint32_t hidden);
 
+/* Expert-parallel decode with the exchange inside the layer kernel (no counterpart in the
+ * reference).  Same partition as above.  Every rank owns an exchange buffer (two slot buffers
+ * [top_k + 1, hidden], arrival flags, a step count) that the other ranks map: the layer kernel
+ * stores the down vectors of the experts it owns into the route slot's row of EVERY rank's slot
+ * buffer (plain stores to peer memory over NVLink), publishes its step in its flag on every rank,
+ * waits - bounded, a few seconds; a wait that runs out sets the device status word 0x5503 - for
+ * all ranks' flags in its own memory and performs the ordered mix from its own slot buffer.  One
+ * launch per rank and step, no collective call; y is bit-identical to the single-GPU layer on
+ * every rank.  Every rank must issue the same sequence of steps.
+ *   create:   allocates the buffer; handle_out (S14_EP_HANDLE_BYTES, may be NULL) receives the
+ *             CUDA IPC handle to hand to the other ranks' processes.
+ *   connect:  handles = world x S14_EP_HANDLE_BYTES in rank order (own entry ignored).
+ *   connect_local: the ranks are contexts of this process on the same GPU (tests: ranks other
+ *             than the last one run with wait_and_mix = 0 - they publish and return - so that no
+ *             launch waits for a later launch of the same GPU).
+ * Pairwise accumulation and MXFP4 pages only. */
+#define S14_EP_HANDLE_BYTES 64
+S14_API int32_t s14_ep_exchange_create(s14_ctx *ctx, uint32_t rank, uint32_t world, uint32_t hidden,
+                                       uint8_t *handle_out);
+S14_API int32_t s14_ep_exchange_connect(s14_ctx *ctx, const uint8_t *handles);
+S14_API int32_t s14_ep_exchange_connect_local(s14_ctx *ctx, s14_ctx *const *ranks);
+S14_API int32_t s14_ep_exchange_destroy(s14_ctx *ctx);
+S14_API int32_t s14_cmd_routed_moe_layer_ep(s14_ctx *ctx, void *stream, const s14_routed_layer_desc *desc,
+                                            uint32_t shared_owner, int32_t wait_and_mix);
+
 /* The routed layer for a caller that holds the token in host memory: copies host_x
  * [hidden] to the device, runs router + layer on the resident pages (desc->router.x,
  * ids_out, weights_out and desc->y are ignored), copies y [hidden] and, when the

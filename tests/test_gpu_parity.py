@@ -454,6 +454,49 @@ def test_expert_parallel_slots_add_up_to_the_single_gpu_layer(ctx, world):
     ctx.set_accumulation(L.ACCUM_PAIRWISE)
 
 
+@pytest.mark.parametrize("world", [2, 4, 8])
+def test_expert_parallel_exchange_in_the_layer_kernel(ctx, world):
+    """The exchange over mapped slot buffers, every rank a context of this process on one GPU.  Ranks
+    1 .. world-1 publish their down vectors and flags without waiting (no launch waits for a later
+    launch of the same GPU); rank 0 runs last, finds every flag, and mixes: bit-identical to the
+    undivided layer, over several steps (the slot buffers alternate, the step count advances)."""
+    from colormlm_b200 import ep
+    from colormlm_b200.s14 import S14Context
+
+    hidden, inter, n_experts = 2048, 1024, 32
+    g, pages, shared = make_layer(5050, hidden, inter, n_experts, L.PAGE_MXFP4)
+    wr, bias = synth.router_weight_bf16(g, n_experts, hidden), synth.router_bias(g, n_experts)
+    pages_dev, shared_dev = [dev_page(p, hidden, inter) for p in pages], dev_page(shared, hidden, inter)
+    table = torch.tensor([p.data_ptr() for p in pages_dev], dtype=torch.int64, device="cuda")
+    dwr, dbias = dev(wr.view(np.int16)), dev(bias)
+    ranks = [S14Context(0) for _ in range(world)]
+    try:
+        for r, c in enumerate(ranks):
+            c.set_accumulation(L.ACCUM_PAIRWISE)
+            c.ep_exchange_create(r, world, hidden)
+        for c in ranks:
+            c.ep_exchange_connect_local(ranks)
+        ctx.set_accumulation(L.ACCUM_PAIRWISE)
+        for step in range(5):
+            x = dev(synth.activations(g, 1, hidden))
+            want = torch.empty_like(x)
+            ctx.cmd_routed_moe_layer(x[0], dwr, dbias, table, shared_dev.data_ptr(), L.PAGE_MXFP4, inter, want)
+            got = torch.full_like(x, float("nan"))
+            ids = torch.empty(6, dtype=torch.int32, device="cuda")
+            wts = torch.empty(6, dtype=torch.float32, device="cuda")
+            owner = ep.shared_owner(step, world)
+            for r in range(world - 1, -1, -1):
+                ranks[r].cmd_routed_moe_layer_ep(x[0], got if r == 0 else None, dwr, dbias, table, shared_dev.data_ptr(),
+                                                 inter, shared_owner=owner, wait_and_mix=(r == 0),
+                                                 ids_out=ids if r == 0 else None, weights_out=wts if r == 0 else None)
+                torch.cuda.synchronize()
+                assert ranks[r].device_status() == 0
+            assert torch.equal(got, want), step
+    finally:
+        for c in ranks:
+            c.close()
+
+
 def test_head_logits_and_argmax(ctx, oracle, golden):
     g = synth.rng(99)
     vocab, hidden = 5003, 4096
