@@ -909,12 +909,9 @@ extern "C" int32_t s14_cmd_routed_moe_layer_ep(s14_ctx *ctx, void *stream, const
     const uint32_t n_slots = r.top_k + (desc->shared_page ? 1u : 0u);
     const FusedRouter fr = router_of(ctx, desc, ctx->ep.rank, ctx->ep.world, shared_owner);
     EpExchange ex = {};
-    const size_t slot_bytes = sizeof(float) * 2u * (S14_EXPERTS_PER_TOKEN + 1) * ctx->ep.hidden;
-    for (uint32_t p = 0; p < ctx->ep.world; ++p) {
-        ex.slots[p] = reinterpret_cast<float *>(ctx->ep.peer[p]);
-        ex.flags[p] = reinterpret_cast<uint32_t *>(ctx->ep.peer[p] + slot_bytes);
-    }
-    ex.step = reinterpret_cast<uint32_t *>(ctx->ep.buf + slot_bytes) + kMaxEpWorld;
+    for (uint32_t p = 0; p < ctx->ep.world; ++p)
+        ex.slots[p] = reinterpret_cast<unsigned long long *>(ctx->ep.peer[p]);
+    ex.step = reinterpret_cast<uint32_t *>(ctx->ep.buf + ep_exchange_slot_bytes(ctx->ep.hidden));
     ex.world = ctx->ep.world;
     ex.rank = ctx->ep.rank;
     ex.n_slots = n_slots;

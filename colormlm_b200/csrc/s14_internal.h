@@ -42,23 +42,24 @@ struct KernelMarks {
 struct UmmaScratch;
 
 // Expert-parallel exchange of the tcgen05 layer kernel over peer memory.  Every rank holds an
-// exchange buffer: two slot buffers [n_slots, hidden] F32 (steps alternate between them), then
-// kMaxEpWorld arrival flags, then the rank's own step count.  A rank stores the down vectors of the
-// experts it owns into the slot rows of EVERY rank's buffer (plain stores to peer memory), then
-// publishes step + 1 in its flag on every rank; each rank waits (bounded) for all flags in its own
-// buffer and mixes from its own memory.  world <= 1: no exchange.
+// exchange buffer: two slot buffers [n_slots, hidden] of 8-byte words {F32 bits, step + 1} (steps
+// alternate between them), then the rank's own step count.  A rank stores the down vectors of the
+// experts it owns into the slot rows of EVERY rank's buffer, each value with the step's number in
+// one 8-byte store (plain stores to peer memory; an aligned 8-byte store arrives whole, so the
+// number validates the value beside it and no fence or flag is needed); each rank polls (bounded)
+// the words it needs in its own buffer and mixes from them.  world <= 1: no exchange.
 constexpr uint32_t kMaxEpWorld = 8;
 struct EpExchange {
-    float *slots[kMaxEpWorld];     // rank p's slot buffers, as mapped on this rank
-    uint32_t *flags[kMaxEpWorld];  // rank p's flags [kMaxEpWorld], as mapped on this rank
+    unsigned long long *slots[kMaxEpWorld];  // rank p's slot buffers, as mapped on this rank
     uint32_t *step;                // this rank's step count (device memory, kept by the kernel)
     uint32_t world, rank;
     uint32_t n_slots;              // top_k (+ 1 with a shared expert)
     uint32_t wait_and_mix;         // 0: publish only (single-GPU emulation of the other ranks)
 };
-inline size_t ep_exchange_bytes(uint32_t hidden) {
-    return sizeof(float) * 2u * (S14_EXPERTS_PER_TOKEN + 1) * hidden + sizeof(uint32_t) * (kMaxEpWorld + 8u);
+inline size_t ep_exchange_slot_bytes(uint32_t hidden) {
+    return sizeof(unsigned long long) * 2u * (S14_EXPERTS_PER_TOKEN + 1) * hidden;
 }
+inline size_t ep_exchange_bytes(uint32_t hidden) { return ep_exchange_slot_bytes(hidden) + 64u; }
 
 // What the router reads and writes, for a layer call that computes its own routes: the tcgen05
 // layer kernel scores the experts in its first microseconds (every CTA a few of them), and every

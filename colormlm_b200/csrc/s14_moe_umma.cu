@@ -63,8 +63,7 @@ constexpr uint32_t kSpinGlobal = 1u << 20;     // polls (100 ns apart) of the it
 constexpr uint32_t kItemCounter = 1, kExitCounter = 2;  // in the context's counter array ([0] is the router's)
 constexpr uint32_t kRouteCounter = 3;          // CTAs whose expert scores are written (routes computed in this kernel)
 constexpr uint32_t kRouterSlots = 4;           // experts a CTA scores at most
-constexpr uint32_t kEpCounter = 4;             // CTAs whose stores to the peers' slot buffers are fenced
-constexpr uint32_t kSpinEp = 1u << 22;         // polls (about a microsecond each) of the peers' flags: a few seconds
+constexpr uint32_t kSpinEp = 1u << 22;         // polls (about a microsecond each) of a word of the slot buffer: a few seconds
 
 // Bar indices in the static barrier array.
 constexpr uint32_t kBarFull = 0;                      // ring slot filled with an up unit (128 copying threads)
@@ -228,13 +227,13 @@ __device__ __forceinline__ float swiglu_limit_fast(float gate, float up) {
 }
 
 
-__device__ __forceinline__ uint32_t ld_acquire_sys(const uint32_t *p) {
-    uint32_t v;
-    asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+__device__ __forceinline__ unsigned long long ld_relaxed_sys(const unsigned long long *p) {
+    unsigned long long v;
+    asm volatile("ld.relaxed.sys.global.u64 %0, [%1];" : "=l"(v) : "l"(p) : "memory");
     return v;
 }
-__device__ __forceinline__ void st_release_sys(uint32_t *p, uint32_t v) {
-    asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
+__device__ __forceinline__ void st_relaxed_sys(unsigned long long *p, unsigned long long v) {
+    asm volatile("st.relaxed.sys.global.u64 [%0], %1;" ::"l"(p), "l"(v) : "memory");
 }
 __device__ __forceinline__ uint32_t ld_acquire(const unsigned int *p) {
     uint32_t v;
@@ -809,45 +808,46 @@ k_moe_layer_umma(const JobTable *__restrict__ dev_table, const __grid_constant__
             const float v = __fadd_rn(hi, lo);
             dj[t] = v;
             if (ep_on) {
-                // the expert's rows of this CTA go to the route slot's row in every rank's slot buffer
+                // the expert's rows of this CTA go to the route slot's row in every rank's slot buffer,
+                // each value with the step's number in one 8-byte store
                 const size_t at = ((size_t)(ep_step & 1u) * ep.n_slots + s_jobs[j].out_index) * hidden + n0 + r;
-                for (uint32_t p = 0; p < ep.world; ++p) ep.slots[p][at] = v;
+                const unsigned long long word = ((unsigned long long)(ep_step + 1u) << 32) | __float_as_uint(v);
+                for (uint32_t p = 0; p < ep.world; ++p) st_relaxed_sys(ep.slots[p] + at, word);
             } else if (!y) {
                 d_out[(size_t)s_jobs[j].out_index * hidden + n0 + r] = v;  // the caller mixes
             }
         }
         __syncthreads();
         if (ep_on) {
-            // ---- exchange: when every CTA's stores are fenced, the rank publishes step + 1 in its flag
-            // on every rank; then it waits (bounded) for all ranks' flags in its own memory and mixes
-            // rows [n0, n1) from its own slot buffer, in route order, the shared expert last ----
-            __threadfence_system();
-            __syncthreads();
-            if (tid == 0 && atomicAdd(counters + kEpCounter, 1u) == grid - 1u) {
-                __threadfence_system();
-                for (uint32_t p = 0; p < ep.world; ++p) st_release_sys(ep.flags[p] + ep.rank, ep_step + 1u);
-                counters[kEpCounter] = 0u;
-                *ep.step = ep_step + 1u;
-            }
+            // ---- exchange: rows [n0, n1) of every slot arrive in this rank's own buffer from the CTA of
+            // the same number on the slot's owner; a thread polls (bounded) one word until it carries
+            // this step's number, then the rows are mixed in route order, the shared expert last ----
             if (ep.wait_and_mix) {
-                if (tid < ep.world) {
+                float *sv = dj;  // [slot][row]; the experts' sums are not needed any more
+                for (uint32_t t = tid; t < ep.n_slots * rows; t += kThreads) {
+                    const uint32_t r = t % rows, jj = t / rows;
+                    const unsigned long long *w =
+                        ep.slots[ep.rank] + ((size_t)(ep_step & 1u) * ep.n_slots + jj) * hidden + n0 + r;
+                    unsigned long long got = ld_relaxed_sys(w);
                     uint32_t tries = 0;
-                    while ((int32_t)(ld_acquire_sys(ep.flags[ep.rank] + tid) - (ep_step + 1u)) < 0) {
-                        if (++tries > kSpinEp) {
+                    while ((uint32_t)(got >> 32) != ep_step + 1u) {
+                        if (++tries > kSpinEp || abort_flag) {
                             abort_flag = 1;
-                            atomicExch(status, 0x5503u);
                             break;
                         }
-                        __nanosleep(200);
+                        __nanosleep(100);
+                        got = ld_relaxed_sys(w);
                     }
+                    sv[t] = __uint_as_float((uint32_t)got);
                 }
                 __syncthreads();
-                if (!abort_flag && y && tid < rows) {
-                    const float *slot = ep.slots[ep.rank] + (size_t)(ep_step & 1u) * ep.n_slots * hidden + n0 + tid;
+                if (abort_flag) {
+                    if (tid == 0) atomicExch(status, 0x5503u);
+                } else if (y && tid < rows) {
                     float acc = 0.0f;
                     for (uint32_t jj = 0; jj < rt.top_k; ++jj)
-                        acc = __fadd_rn(acc, __fmul_rn(s_route_w[jj], __ldcg(slot + (size_t)jj * hidden)));
-                    if (ep.n_slots > rt.top_k) acc = __fadd_rn(acc, __ldcg(slot + (size_t)rt.top_k * hidden));
+                        acc = __fadd_rn(acc, __fmul_rn(s_route_w[jj], sv[jj * rows + tid]));
+                    if (ep.n_slots > rt.top_k) acc = __fadd_rn(acc, sv[rt.top_k * rows + tid]);
                     y[n0 + tid] = acc;
                 }
             }
@@ -868,6 +868,7 @@ k_moe_layer_umma(const JobTable *__restrict__ dev_table, const __grid_constant__
             counters[kItemCounter] = 0u;
             counters[kExitCounter] = 0u;
             counters[kRouteCounter] = 0u;
+            if (ep_on) *ep.step = ep_step + 1u;  // every CTA has read the count
         }
     }
 }

@@ -314,11 +314,12 @@ S14_API int32_t s14_cmd_moe_mix_slots(s14_ctx *ctx, void *stream, const float *s
 
 /* Expert-parallel decode with the exchange inside the layer kernel (no counterpart in the
  * reference).  Same partition as above.  Every rank owns an exchange buffer (two slot buffers
- * [top_k + 1, hidden], arrival flags, a step count) that the other ranks map: the layer kernel
+ * [top_k + 1, hidden] of 8-byte words, a step count) that the other ranks map: the layer kernel
  * stores the down vectors of the experts it owns into the route slot's row of EVERY rank's slot
- * buffer (plain stores to peer memory over NVLink), publishes its step in its flag on every rank,
- * waits - bounded, a few seconds; a wait that runs out sets the device status word 0x5503 - for
- * all ranks' flags in its own memory and performs the ordered mix from its own slot buffer.  One
+ * buffer, each value together with the step's number in one 8-byte store (plain stores to peer
+ * memory over NVLink), polls - bounded, a few seconds; a wait that runs out sets the device
+ * status word 0x5503 - the words it needs in its own buffer until they carry this step's number,
+ * and performs the ordered mix from them.  No fence, flag or collective call on the way.  One
  * launch per rank and step, no collective call; y is bit-identical to the single-GPU layer on
  * every rank.  Every rank must issue the same sequence of steps.
  *   create:   allocates the buffer; handle_out (S14_EP_HANDLE_BYTES, may be NULL) receives the
