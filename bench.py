@@ -413,20 +413,30 @@ def run_gpu(args) -> None:
     ids_np, w_np = np.empty(TOP_K, np.int32), np.empty(TOP_K, np.float32)
     xd = torch.empty(HIDDEN, dtype=torch.float32, device="cuda")
     e2e_steps = 0 if args.kernel_only else min(args.steps, 2000)
+    # one GPU: every layer's call is bound once (descriptor validated and recorded), a step is the
+    # foreign call alone: pinned x in, y and the route out
+    bound = [ctx.bind_routed_moe_layer_host(ly["wr"], ly["bias"], ly["table"], ly["shared"], L.PAGE_MXFP4, INTER)
+             for ly in layers] if world == 1 else None
+    hx_addr, hy_addr, ids_addr, w_addr = hx.data_ptr(), hy.data_ptr(), ids_np.ctypes.data, w_np.ctypes.data
+    ep_states = []
+    for ly in layers:
+        st_ = dict(ly)
+        if st_["shared"] is None:
+            st_["shared"] = ly["pages"].data_ptr()  # never read: this rank is not the owner
+        ep_states.append(st_)
 
     def e2e_step(i):
-        ly = layers[i % n_layers]
         if world == 1:
-            ctx.routed_moe_layer_host(hx_np[i % n_tok], hy_np, ly["wr"], ly["bias"], ly["table"], ly["shared"],
-                                      L.PAGE_MXFP4, INTER, ids_np, w_np)
+            bound[i % n_layers].run_addresses(hx_addr + (i % n_tok) * HIDDEN * 4, hy_addr, ids_addr, w_addr)
         else:
             with torch.cuda.stream(stream):
                 xd.copy_(hx[i % n_tok], non_blocking=True)
-                ly_state = dict(ly)
-                if ly_state["shared"] is None:
-                    ly_state["shared"] = ly["pages"].data_ptr()
-                ep.decode_step(ctx, xd, ly_state, slots[0], ep_ids[0], ep_w[0], ys[0], layer=i % n_layers,
-                               rank=rank, world=world, inter=INTER, stream=stream.cuda_stream)
+                if peer_exchange:
+                    ep.decode_step_fused(ctx, xd, ep_states[i % n_layers], ys[0], layer=i % n_layers, world=world,
+                                         inter=INTER, stream=stream.cuda_stream)
+                else:
+                    ep.decode_step(ctx, xd, ep_states[i % n_layers], slots[0], ep_ids[0], ep_w[0], ys[0],
+                                   layer=i % n_layers, rank=rank, world=world, inter=INTER, stream=stream.cuda_stream)
                 hy.copy_(ys[0], non_blocking=True)
             stream.synchronize()
 

@@ -244,6 +244,24 @@ class S14Context:
                                             slots.data_ptr(), weights_dev.data_ptr(), n_routed,
                                             1 if has_shared else 0, y.data_ptr(), y.shape[-1]))
 
+    def bind_routed_moe_layer_host(self, wr_bf16, bias, page_table, shared_page: Optional[int], shared_kind: int,
+                                   inter: int, *, score_fn: int = L.SCORE_SIGMOID, top_k: int = 6,
+                                   route_scale: float = 1.0) -> "RoutedLayerHostCall":
+        """Validates and records a layer's routed host-buffer call once (the bind step of the
+        reference's bind / cmd split, s14_vulkan.rs:207-415); the returned object runs it per token
+        with nothing but the foreign call on the way."""
+        d = L.RoutedLayerDesc()
+        r = L.RouterDesc()
+        r.n_experts, r.hidden, r.n_tokens = wr_bf16.shape[0], wr_bf16.shape[1], 1
+        r.top_k, r.score_fn, r.route_scale = top_k, score_fn, route_scale
+        r.router_weight_bf16 = wr_bf16.data_ptr()
+        r.bias = bias.data_ptr() if bias is not None else None
+        d.router = r
+        d.inter, d.shared_kind = inter, shared_kind
+        d.page_table = page_table.data_ptr()
+        d.shared_page = shared_page
+        return RoutedLayerHostCall(self, d, (wr_bf16, bias, page_table))
+
     def routed_moe_layer_host(self, host_x: np.ndarray, host_y: np.ndarray, wr_bf16, bias, page_table,
                               shared_page: Optional[int], shared_kind: int, inter: int,
                               host_ids: Optional[np.ndarray] = None,
@@ -316,6 +334,28 @@ def _layer_desc(routes, shared_page, shared_kind, hidden, inter):
     d.shared_page = shared_page
     d.routes = C.cast(arr, C.POINTER(L.TokenRoute))
     return d, arr
+
+
+class RoutedLayerHostCall:
+    """A bound routed layer call on host buffers (see S14Context.bind_routed_moe_layer_host)."""
+
+    def __init__(self, ctx: "S14Context", desc, keep_alive):
+        self._ctx, self._desc, self._keep = ctx, desc, keep_alive
+        self._ref = C.byref(desc)
+        self._fn = L.lib().s14_routed_moe_layer_host
+
+    def run_addresses(self, host_x: int, host_y: int, host_ids: int = 0, host_weights: int = 0) -> None:
+        """host_x / host_y: addresses of hidden F32 values (pinned memory for speed); host_ids /
+        host_weights: addresses of top_k int32 / F32 values, or 0."""
+        rc = self._fn(self._ctx._h, self._ref, host_x, host_y, host_ids or None, host_weights or None)
+        if rc:
+            check(rc)
+
+    def __call__(self, host_x: np.ndarray, host_y: np.ndarray, host_ids: Optional[np.ndarray] = None,
+                 host_weights: Optional[np.ndarray] = None) -> None:
+        self.run_addresses(host_x.ctypes.data, host_y.ctypes.data,
+                           host_ids.ctypes.data if host_ids is not None else 0,
+                           host_weights.ctypes.data if host_weights is not None else 0)
 
 
 def _router_desc(x, wr_bf16, bias, ids_out, weights_out, score_fn, top_k, route_scale):

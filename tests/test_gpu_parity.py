@@ -412,6 +412,35 @@ def test_routed_layer_without_host_round_trip(ctx, oracle):
     ctx.set_accumulation(L.ACCUM_PAIRWISE)
 
 
+def test_routed_layer_on_host_buffers_and_the_bound_call(ctx, oracle):
+    """The call a host program makes per token: x from host memory, y and the route back.  The bound
+    call (descriptor recorded once) and the one-shot call give the device path's bits."""
+    hidden, inter, n_experts = 2048, 1024, 32
+    g, pages, shared = make_layer(4711, hidden, inter, n_experts, L.PAGE_MXFP4)
+    wr, bias = synth.router_weight_bf16(g, n_experts, hidden), synth.router_bias(g, n_experts)
+    pages_dev, shared_dev = [dev_page(p, hidden, inter) for p in pages], dev_page(shared, hidden, inter)
+    table = torch.tensor([p.data_ptr() for p in pages_dev], dtype=torch.int64, device="cuda")
+    dwr, dbias = dev(wr.view(np.int16)), dev(bias)
+    ctx.set_accumulation(L.ACCUM_PAIRWISE)
+    bound = ctx.bind_routed_moe_layer_host(dwr, dbias, table, shared_dev.data_ptr(), L.PAGE_MXFP4, inter)
+    for step in range(3):
+        x = synth.activations(g, 1, hidden)
+        want = torch.empty((1, hidden), dtype=torch.float32, device="cuda")
+        ctx.cmd_routed_moe_layer(dev(x)[0], dwr, dbias, table, shared_dev.data_ptr(), L.PAGE_MXFP4, inter, want)
+        torch.cuda.synchronize()
+        rid, rw, _, _ = oracle.router(x[0], wr, bias, 0, 6, 1.0)
+        for call in ("bound", "one-shot"):
+            y = np.full(hidden, np.nan, np.float32)
+            ids, wts = np.full(6, -1, np.int32), np.zeros(6, np.float32)
+            if call == "bound":
+                bound(x[0], y, ids, wts)
+            else:
+                ctx.routed_moe_layer_host(x[0], y, dwr, dbias, table, shared_dev.data_ptr(), L.PAGE_MXFP4, inter, ids, wts)
+            assert np.array_equal(ids, rid) and np.array_equal(wts.view(np.uint32), rw.view(np.uint32))
+            assert np.array_equal(y.view(np.uint32), want.cpu().numpy()[0].view(np.uint32)), (step, call)
+    assert ctx.device_status() == 0
+
+
 @pytest.mark.parametrize("world", [1, 2, 4, 8])
 def test_expert_parallel_slots_add_up_to_the_single_gpu_layer(ctx, world):
     """Every rank's share is run in turn on one GPU; the slot buffers are summed as the all-reduce
