@@ -386,7 +386,6 @@ k_moe_layer_umma(const JobTable *__restrict__ dev_table, const __grid_constant__
     // expert parallel: the step count picks the slot buffer and the flag value; the last CTA to
     // leave advances it, after every CTA has read it
     const bool ep_on = ep.world > 1u;
-    const uint32_t ep_step = ep_on ? __ldcg(ep.step) : 0u;
     const bool has_x = tid < (hidden >> 3);
     float xs[8] = {0.0f, 0.0f, 0.0f, 0.0f, 0.0f, 0.0f, 0.0f, 0.0f};
     uint4 rq[kRouterSlots];
@@ -398,6 +397,13 @@ k_moe_layer_umma(const JobTable *__restrict__ dev_table, const __grid_constant__
             if (has_x && e < rt.n_experts) rq[k] = ldg_stream(reinterpret_cast<const uint4 *>(rt.weight + (size_t)e * hidden) + tid);
         }
     }
+    // The kernel is launched as a programmatic dependent of whatever precedes it in the stream: its
+    // CTAs may be placed as soon as SMs are free, and everything an earlier kernel may have written
+    // (the token, the counters, the step count) is read only after this point; in the same way the
+    // next launch may be set up from now on.  Weights and page tables are constant during a step.
+    cudaTriggerProgrammaticLaunchCompletion();
+    cudaGridDependencySynchronize();
+    const uint32_t ep_step = ep_on ? __ldcg(ep.step) : 0u;
     if (has_x) {
         const float4 p0 = __ldcg(reinterpret_cast<const float4 *>(x) + 2u * tid);
         const float4 p1 = __ldcg(reinterpret_cast<const float4 *>(x) + 2u * tid + 1u);
@@ -493,8 +499,6 @@ k_moe_layer_umma(const JobTable *__restrict__ dev_table, const __grid_constant__
         if (warp == 0 && !abort_flag) route_select(rt, lane, cta == 0, s_jobs, &s_n_jobs, s_mix_w, s_mix_job, s_route_w);
         if (tid == 0 && abort_flag) s_n_jobs = 0;
     } else {
-        // a router launched before this kernel has finished when this returns
-        cudaGridDependencySynchronize();
         const JobTable &tab = table_of(dev_table, param_table);
         const uint32_t nj = min(tab.token_job_begin[1] - tab.token_job_begin[0], (uint32_t)S14_EXPERTS_PER_TOKEN + 1u);
         if (tid < min(tab.n_jobs, (uint32_t)S14_EXPERTS_PER_TOKEN + 1u)) s_jobs[tid] = tab.jobs[tid];
@@ -939,10 +943,8 @@ cudaError_t launch_moe_layer_umma(cudaStream_t st, int sm_count, const JobTable 
     EpExchange ex = {};
     if (ep) ex = *ep;
     if (ex.world > 1u && !router) return cudaErrorInvalidValue;  // the mix needs every route's weight
-    // with the routes computed here nothing earlier in the stream may still be running when the
-    // kernel starts, so the launch is an ordinary one
-    return launch_pdl(k_moe_layer_umma, dim3(sm_count), dim3(kThreads), umma_smem_bytes(hidden), st,
-                      after_router && !router, dev, param, x, d, y, partials, counters, status, hidden, inter, rt, ex);
+    (void)after_router;
+    return launch_pdl(k_moe_layer_umma, dim3(sm_count), dim3(kThreads), umma_smem_bytes(hidden), st, true, dev, param, x, d, y, partials, counters, status, hidden, inter, rt, ex);
 }
 
 }  // namespace s14
