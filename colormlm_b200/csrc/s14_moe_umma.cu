@@ -398,18 +398,11 @@ k_moe_layer_umma(const JobTable *__restrict__ dev_table, const __grid_constant__
         }
     }
     // The kernel is launched as a programmatic dependent of whatever precedes it in the stream: its
-    // CTAs may be placed as soon as SMs are free, and everything an earlier kernel may have written
-    // (the token, the counters, the step count) is read only after this point; in the same way the
-    // next launch may be set up from now on.  Weights and page tables are constant during a step.
+    // CTAs may be placed as soon as SMs are free and set themselves up (barriers, tensor memory);
+    // everything an earlier kernel may have written (the token, the counters, the step count) is read
+    // only after cudaGridDependencySynchronize() below.  In the same way the next launch may be set
+    // up from now on.  Weights and page tables are constant during a step.
     cudaTriggerProgrammaticLaunchCompletion();
-    cudaGridDependencySynchronize();
-    const uint32_t ep_step = ep_on ? __ldcg(ep.step) : 0u;
-    if (has_x) {
-        const float4 p0 = __ldcg(reinterpret_cast<const float4 *>(x) + 2u * tid);
-        const float4 p1 = __ldcg(reinterpret_cast<const float4 *>(x) + 2u * tid + 1u);
-        xs[0] = p0.x, xs[1] = p0.y, xs[2] = p0.z, xs[3] = p0.w;
-        xs[4] = p1.x, xs[5] = p1.y, xs[6] = p1.z, xs[7] = p1.w;
-    }
 
     // rows 8-15 of the digit tiles stay zero
     for (uint32_t i = tid; i < (KU * 2048u) >> 4; i += kThreads) reinterpret_cast<uint4 *>(sBx)[i] = make_uint4(0u, 0u, 0u, 0u);
@@ -442,6 +435,15 @@ k_moe_layer_umma(const JobTable *__restrict__ dev_table, const __grid_constant__
     __syncthreads();
     fence_after();
     const uint32_t tmem = tmem_slot;
+
+    cudaGridDependencySynchronize();
+    const uint32_t ep_step = ep_on ? __ldcg(ep.step) : 0u;
+    if (has_x) {
+        const float4 p0 = __ldcg(reinterpret_cast<const float4 *>(x) + 2u * tid);
+        const float4 p1 = __ldcg(reinterpret_cast<const float4 *>(x) + 2u * tid + 1u);
+        xs[0] = p0.x, xs[1] = p0.y, xs[2] = p0.z, xs[3] = p0.w;
+        xs[4] = p1.x, xs[5] = p1.y, xs[6] = p1.z, xs[7] = p1.w;
+    }
 
     if (routes_here) {
         // ---- expert scores: logit = x . w in double (warp sums, then the sixteen warps in order),
