@@ -71,3 +71,69 @@ def decode_step_fused(ctx, x, layer_state: dict, y, *, layer: int, world: int, i
     ctx.cmd_routed_moe_layer_ep(x, y, layer_state["wr"], layer_state["bias"], layer_state["table"],
                                 layer_state["shared"], inter, shared_owner=shared_owner(layer, world),
                                 ids_out=ids, weights_out=weights, stream=stream)
+
+
+# ---- vocabulary-sharded LM head ---------------------------------------------------------------
+# The head weight [vocab, hidden] BF16 is split by rows: rank r holds rows [vocab r / G, vocab (r+1) / G)
+# (final_head.py:113-149 computes all rows on one device; the runner's contract wants the full logits,
+# s14_runner/src/runner.rs:111-117, and picks the greedy token with the lowest id on ties and rejects
+# NaN, runner.rs:485-508).  Every row's logit is the same sum whichever rank computes it, so the
+# gathered logits and the token are identical for every G.
+
+
+def head_rows(rank: int, world: int, vocab: int):
+    return vocab * rank // world, vocab * (rank + 1) // world
+
+
+def gather_head_logits(local_logits, vocab: int, world: int, group=None):
+    """All-gather of the ranks' row shards ([rows of this rank] F32) into the full [vocab] logits."""
+    import torch
+    import torch.distributed as dist
+
+    if world == 1:
+        return local_logits
+    sizes = [head_rows(r, world, vocab)[1] - head_rows(r, world, vocab)[0] for r in range(world)]
+    widest = max(sizes)
+    mine = torch.zeros(widest, dtype=local_logits.dtype, device=local_logits.device)
+    mine[: local_logits.numel()] = local_logits
+    parts = [torch.empty_like(mine) for _ in range(world)]
+    dist.all_gather(parts, mine, group=group)
+    return torch.cat([p[:n] for p, n in zip(parts, sizes)])
+
+
+def combine_greedy(local_best: float, local_token: int, world: int, group=None, device="cpu") -> int:
+    """The greedy token over all shards from every rank's (largest logit, its global id): largest
+    value, lowest id on ties; a rank that met a NaN reports token -1 and the result is -1."""
+    import torch
+    import torch.distributed as dist
+
+    pair = torch.tensor([float(local_best), float(local_token)], dtype=torch.float64, device=device)
+    pairs = [pair]
+    if world > 1:
+        pairs = [torch.empty_like(pair) for _ in range(world)]
+        dist.all_gather(pairs, pair, group=group)
+    best, token = None, -1
+    for p in pairs:
+        v, t = float(p[0]), int(p[1])
+        if t < 0:
+            return -1
+        if best is None or v > best or (v == best and t < token):
+            best, token = v, t
+    return token
+
+
+def sharded_head(ctx, x, w_shard_bf16, vocab: int, rank: int, world: int, group=None, stream: Optional[int] = None):
+    """Full logits [vocab] and the greedy token from this rank's row shard of the head weight (GPU)."""
+    import torch
+
+    row0, row1 = head_rows(rank, world, vocab)
+    local = torch.empty(row1 - row0, dtype=torch.float32, device=x.device)
+    ctx.cmd_head_logits(x, w_shard_bf16, local, stream=stream)
+    arg = torch.empty(1, dtype=torch.int64, device=x.device)
+    ctx.cmd_greedy_argmax(local, arg, stream=stream)
+    logits = gather_head_logits(local, vocab, world, group)
+    torch.cuda.synchronize()
+    a = int(arg.item())
+    token = combine_greedy(float(local[a]) if a >= 0 else 0.0, row0 + a if a >= 0 else -1, world, group,
+                           device=x.device)
+    return logits, token

@@ -60,6 +60,44 @@ def test_two_rank_exchange_matches_single_rank(tmp_path, world):
     assert total_owned == 16
 
 
+def _head_worker(rank: int, world: int, port: int, out_dir: str) -> None:
+    sys.path.insert(0, ROOT)
+    os.environ["MASTER_ADDR"] = "127.0.0.1"
+    os.environ["MASTER_PORT"] = str(port)
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    from colormlm_b200 import ep, synth
+    from oracle import s14_oracle as oracle
+
+    vocab, hidden = 1003, 512  # rows do not divide evenly
+    g = synth.rng(731)
+    w = synth.head_weight_bf16(g, vocab, hidden)
+    x = synth.activations(g, 1, hidden)[0]
+    full = oracle.head_logits(x, w)
+    r0, r1 = ep.head_rows(rank, world, vocab)
+    local = oracle.head_logits(x, w[r0:r1])
+    got = ep.gather_head_logits(torch.from_numpy(local), vocab, world).numpy()
+    ok = np.array_equal(got.view(np.uint32), full.view(np.uint32))
+    cases = []
+    for name, logits in (("plain", full), ("tie", np.where(np.arange(vocab) % 97 == 5, np.float32(99.0), full)),
+                         ("nan", np.where(np.arange(vocab) == vocab - 2, np.float32(np.nan), full))):
+        mine = logits[r0:r1]
+        a = oracle.greedy_argmax(mine)
+        token = ep.combine_greedy(float(mine[a]) if a >= 0 else 0.0, r0 + a if a >= 0 else -1, world)
+        cases.append(token == oracle.greedy_argmax(logits))
+    with open(os.path.join(out_dir, f"head{rank}.txt"), "w") as f:
+        f.write(f"{int(ok)} {int(all(cases))}\n")
+    dist.barrier()
+    dist.destroy_process_group()
+
+
+@pytest.mark.parametrize("world", [2])
+def test_two_rank_sharded_head_gathers_the_full_logits_and_the_greedy_token(tmp_path, world):
+    port = 31500 + (os.getpid() % 2000)
+    mp.spawn(_head_worker, args=(world, port, str(tmp_path)), nprocs=world, join=True)
+    for r in range(world):
+        assert open(tmp_path / f"head{r}.txt").read().split() == ["1", "1"]
+
+
 def test_ownership_is_a_partition():
     sys.path.insert(0, ROOT)
     from colormlm_b200 import ep

@@ -526,6 +526,35 @@ def test_expert_parallel_exchange_in_the_layer_kernel(ctx, world):
             c.close()
 
 
+def test_sharded_head_on_one_rank_and_by_row_shards(ctx, oracle):
+    """ep.sharded_head with one rank, and the row shards of two ranks computed in turn: the pieces are
+    the full logits bit for bit, the combined greedy token is the oracle's."""
+    from colormlm_b200 import ep
+
+    g = synth.rng(732)
+    vocab, hidden = 3001, 2048
+    w = synth.head_weight_bf16(g, vocab, hidden)
+    x = synth.activations(g, 1, hidden)
+    dw, dx = dev(w.view(np.int16)), dev(x)
+    logits, token = ep.sharded_head(ctx, dx[0], dw, vocab, 0, 1)
+    full = logits.cpu().numpy()
+    ref = oracle.head_logits(x[0], w)
+    assert np.allclose(full, ref, rtol=2e-7, atol=3e-7)  # tolerance of tests/test_final_head.py:68-70
+    assert token == oracle.greedy_argmax(full)
+    pieces = []
+    best = []
+    for rank in range(2):
+        r0, r1 = ep.head_rows(rank, 2, vocab)
+        local = torch.empty(r1 - r0, dtype=torch.float32, device="cuda")
+        ctx.cmd_head_logits(dx[0], dw[r0:r1], local)
+        torch.cuda.synchronize()
+        pieces.append(local.cpu().numpy())
+        a = int(np.argmax(pieces[-1]))
+        best.append((float(pieces[-1][a]), r0 + a))
+    assert np.array_equal(np.concatenate(pieces).view(np.uint32), full.view(np.uint32))
+    assert max(best, key=lambda p: (p[0], -p[1]))[1] == token
+
+
 def test_head_logits_and_argmax(ctx, oracle, golden):
     g = synth.rng(99)
     vocab, hidden = 5003, 4096
