@@ -24,8 +24,8 @@
 // the ordered mix.  Items are handed out in equal numbers, so the result does not depend on how.
 // The expert page stores w2 and all scales by slice for this purpose.
 //
-// Roles inside a CTA: four producer warps (cp.async into an 8-stage ring of 16 KB of codes + 2 KB
-// of scales: up units of all items first, then down stages), two MMA-issuing threads, eight
+// Roles inside a CTA: four producer warps (cp.async into a 10-stage ring of 16 KB of codes + 2 KB
+// of scales: up units of all items first, then down stages), four MMA-issuing threads, eight
 // epilogue warps (tcgen05.ld / tcgen05.st).  Every mbarrier wait and the poll of the item
 // counter are bounded; a wait that runs out raises the CTA's abort flag, the status word is set
 // and the CTA drains its copies, frees its tensor memory and returns.
@@ -35,7 +35,7 @@ namespace s14 {
 
 namespace {
 
-constexpr uint32_t kRing = 8;                  // stages in flight per CTA
+constexpr uint32_t kRing = 10;                 // stages in flight per CTA (even: an up unit's parity is its slot's)
 constexpr uint32_t kStageA = 128 * 128;        // 16 KB of codes: an up unit (128 rows x 256 K) or four down blocks (128 rows x 64 K each)
 constexpr uint32_t kStageSf = 4 * 512;         // scale atoms of a stage: two (up unit) or four (down stage)
 constexpr uint32_t kEpiGroup = 128;            // two epilogue groups of four warps
@@ -618,18 +618,19 @@ k_moe_layer_umma(const JobTable *__restrict__ dev_table, const __grid_constant__
                 }
             }
             {
-                // down stage vg (ring slot (nU + vg) % kRing, accumulator set vg % 4 = m)
-                uint32_t l = 0, vloc = m;  // item and stage within the item
-                while (vloc >= DS) {
-                    vloc -= DS;
-                    ++l;
-                }
-                for (uint32_t vg = m; vg < nD && ok; vg += kIssuers) {
-                    const uint32_t s = (nU + vg) % kRing, sl = (q0 + l) % S, asf = (sl & 1u) * 2u;
+                // Down stage vg sits in ring slot s = (nU + vg) % kRing and belongs to the issuing thread and
+                // accumulator set s % 4, so that every slot's barrier has one waiting thread, which sees
+                // each of its phases; j counts this thread's down stages (the phases of its own barriers).
+                uint32_t j = 0;
+                for (uint32_t vg = 0; vg < nD && ok; ++vg) {
+                    const uint32_t s = (nU + vg) % kRing;
+                    if ((s & 3u) != m) continue;
+                    const uint32_t l = vg / DS, sl = (q0 + l) % S, asf = (sl & 1u) * 2u;
                     ok = mbar_wait(bar(kBarHReady + l), 0, &abort_flag);
                     ok = ok && mbar_wait(bar(kBarDFull + s), (vg / kRing) & 1u, &abort_flag);
-                    ok = ok && (vg < kDRing || mbar_wait(bar(kBarDFree + m), ((vg >> 2) - 1u) & 1u, &abort_flag));
+                    ok = ok && (j == 0u || mbar_wait(bar(kBarDFree + m), (j - 1u) & 1u, &abort_flag));
                     if (!ok) break;
+                    ++j;
                     fence_after();
                     const uint64_t sfd = sf_desc0 + s * (kStageSf >> 4);
                     const uint64_t bd = smem_desc_k64(smem_u32(sBh + l * 512u));
@@ -642,11 +643,6 @@ k_moe_layer_umma(const JobTable *__restrict__ dev_table, const __grid_constant__
                                   (sfa_t + b * 4u) | (asf << 30), tmem + kColSfbH + l * 4u, 0u);
                     umma_commit(bar(kBarDone + s));
                     umma_commit(bar(kBarDDone + m));
-                    vloc += kIssuers;
-                    while (vloc >= DS) {
-                        vloc -= DS;
-                        ++l;
-                    }
                 }
             }
             // nothing of this CTA's tensor work is in flight when the tensor memory is freed
@@ -725,11 +721,14 @@ k_moe_layer_umma(const JobTable *__restrict__ dev_table, const __grid_constant__
                 mbar_arrive(bar(kBarHReady + l));
             }
         }
-        for (uint32_t vg = grp; vg < nD; vg += 2u) {
-            const uint32_t acc = vg & 3u;
+        uint32_t seen_lo = 0, seen_hi = 0;  // down stages of the group's two accumulator sets so far
+        for (uint32_t vg = 0; vg < nD; ++vg) {
+            const uint32_t acc = ((nU + vg) % kRing) & 3u;  // the stage's issuing thread and accumulator set
+            if ((acc & 1u) != grp) continue;                // sets 0, 2: group A; sets 1, 3: group B
+            const uint32_t j = (acc & 2u) ? seen_hi++ : seen_lo++;
             const uint32_t l = vg / DS, vloc = vg - l * DS, q = q0 + l;
             // every phase of this barrier is waited for by this group, in order
-            ok = __all_sync(0xffffffffu, ok && mbar_wait(bar(kBarDDone + acc), (vg >> 2) & 1u, &abort_flag));
+            ok = __all_sync(0xffffffffu, ok && mbar_wait(bar(kBarDDone + acc), j & 1u, &abort_flag));
             if (!ok) break;
             fence_after();
             uint32_t a[4][8];
