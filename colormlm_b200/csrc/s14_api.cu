@@ -85,6 +85,7 @@ struct s14_ctx {
         uint8_t *peer[kMaxEpWorld] = {};
         bool opened[kMaxEpWorld] = {};
         bool connected = false;
+        uint32_t wait_limit = 1u << 22;  // polls of about a microsecond: a few seconds
     } ep;
     UmmaScratch umma{nullptr, nullptr};  // scratch of the tcgen05 layer kernel
     bool use_umma = true;                // S14_TENSOR_PATH=off in the environment turns it off
@@ -887,6 +888,12 @@ extern "C" int32_t s14_ep_exchange_connect_local(s14_ctx *ctx, s14_ctx *const *r
     S14_CATCH
 }
 
+extern "C" int32_t s14_ep_exchange_set_wait_limit(s14_ctx *ctx, uint32_t polls) {
+    if (!ctx || polls == 0) return fail(S14_ERR_CONTRACT, "s14_ep_exchange_set_wait_limit: NULL context or zero polls");
+    ctx->ep.wait_limit = polls;
+    return S14_OK;
+}
+
 extern "C" int32_t s14_cmd_routed_moe_layer_ep(s14_ctx *ctx, void *stream, const s14_routed_layer_desc *desc,
                                                uint32_t shared_owner, int32_t wait_and_mix) {
     S14_TRY
@@ -916,6 +923,7 @@ extern "C" int32_t s14_cmd_routed_moe_layer_ep(s14_ctx *ctx, void *stream, const
     ex.rank = ctx->ep.rank;
     ex.n_slots = n_slots;
     ex.wait_and_mix = wait_and_mix ? 1u : 0u;
+    ex.wait_limit = ctx->ep.wait_limit;
     JobTable unused;
     unused.n_jobs = 0;
     cudaError_t err;

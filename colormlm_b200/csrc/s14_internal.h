@@ -55,6 +55,7 @@ struct EpExchange {
     uint32_t world, rank;
     uint32_t n_slots;              // top_k (+ 1 with a shared expert)
     uint32_t wait_and_mix;         // 0: publish only (single-GPU emulation of the other ranks)
+    uint32_t wait_limit;           // polls (about a microsecond each) of one word before the rank gives up
 };
 inline size_t ep_exchange_slot_bytes(uint32_t hidden) {
     return sizeof(unsigned long long) * 2u * (S14_EXPERTS_PER_TOKEN + 1) * hidden;

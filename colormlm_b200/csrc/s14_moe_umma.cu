@@ -63,7 +63,6 @@ constexpr uint32_t kSpinGlobal = 1u << 20;     // polls (100 ns apart) of the it
 constexpr uint32_t kItemCounter = 1, kExitCounter = 2;  // in the context's counter array ([0] is the router's)
 constexpr uint32_t kRouteCounter = 3;          // CTAs whose expert scores are written (routes computed in this kernel)
 constexpr uint32_t kRouterSlots = 4;           // experts a CTA scores at most
-constexpr uint32_t kSpinEp = 1u << 22;         // polls (about a microsecond each) of a word of the slot buffer: a few seconds
 
 // Bar indices in the static barrier array.
 constexpr uint32_t kBarFull = 0;                      // ring slot filled with an up unit (128 copying threads)
@@ -836,7 +835,7 @@ k_moe_layer_umma(const JobTable *__restrict__ dev_table, const __grid_constant__
                     unsigned long long got = ld_relaxed_sys(w);
                     uint32_t tries = 0;
                     while ((uint32_t)(got >> 32) != ep_step + 1u) {
-                        if (++tries > kSpinEp || abort_flag) {
+                        if (++tries > ep.wait_limit || abort_flag) {
                             abort_flag = 1;
                             break;
                         }

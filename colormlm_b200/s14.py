@@ -219,6 +219,9 @@ class S14Context:
         arr = (C.c_void_p * len(ranks))(*[r._h for r in ranks])
         check(L.lib().s14_ep_exchange_connect_local(self._h, arr))
 
+    def ep_exchange_set_wait_limit(self, polls: int) -> None:
+        check(L.lib().s14_ep_exchange_set_wait_limit(self._h, polls))
+
     def ep_exchange_destroy(self) -> None:
         check(L.lib().s14_ep_exchange_destroy(self._h))
 

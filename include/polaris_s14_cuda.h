@@ -334,6 +334,10 @@ S14_API int32_t s14_ep_exchange_create(s14_ctx *ctx, uint32_t rank, uint32_t wor
                                        uint8_t *handle_out);
 S14_API int32_t s14_ep_exchange_connect(s14_ctx *ctx, const uint8_t *handles);
 S14_API int32_t s14_ep_exchange_connect_local(s14_ctx *ctx, s14_ctx *const *ranks);
+/* How long a rank waits for a word of another rank: `polls` of about a microsecond each (default
+ * 2^22, a few seconds).  When it runs out the kernel sets the device status word 0x5503, writes no
+ * y and returns; the context stays usable. */
+S14_API int32_t s14_ep_exchange_set_wait_limit(s14_ctx *ctx, uint32_t polls);
 S14_API int32_t s14_ep_exchange_destroy(s14_ctx *ctx);
 S14_API int32_t s14_cmd_routed_moe_layer_ep(s14_ctx *ctx, void *stream, const s14_routed_layer_desc *desc,
                                             uint32_t shared_owner, int32_t wait_and_mix);

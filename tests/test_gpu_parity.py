@@ -526,6 +526,44 @@ def test_expert_parallel_exchange_in_the_layer_kernel(ctx, world):
             c.close()
 
 
+def test_expert_parallel_wait_runs_out_when_a_rank_never_publishes(ctx):
+    """Failure detection without a fault: rank 1 never runs its step, rank 0's bounded wait (set to
+    a few milliseconds here) runs out, the kernel reports status 0x5503 and returns, and the GPU
+    and the context go on working."""
+    from colormlm_b200.s14 import S14Context
+
+    hidden, inter, n_experts = 2048, 1024, 32
+    g, pages, shared = make_layer(6060, hidden, inter, n_experts, L.PAGE_MXFP4)
+    wr, bias = synth.router_weight_bf16(g, n_experts, hidden), synth.router_bias(g, n_experts)
+    pages_dev, shared_dev = [dev_page(p, hidden, inter) for p in pages], dev_page(shared, hidden, inter)
+    table = torch.tensor([p.data_ptr() for p in pages_dev], dtype=torch.int64, device="cuda")
+    dwr, dbias = dev(wr.view(np.int16)), dev(bias)
+    x = dev(synth.activations(g, 1, hidden))
+    ranks = [S14Context(0) for _ in range(2)]
+    try:
+        for r, c in enumerate(ranks):
+            c.set_accumulation(L.ACCUM_PAIRWISE)
+            c.ep_exchange_create(r, 2, hidden)
+        for c in ranks:
+            c.ep_exchange_connect_local(ranks)
+        ranks[0].ep_exchange_set_wait_limit(3000)
+        got = torch.full_like(x, float("nan"))
+        ranks[0].cmd_routed_moe_layer_ep(x[0], got, dwr, dbias, table, shared_dev.data_ptr(), inter, shared_owner=1)
+        torch.cuda.synchronize()
+        assert ranks[0].device_status() == 0x5503
+        assert ranks[0].device_status() == 0  # reading clears it
+        # the same context computes an undivided layer afterwards, equal to another context's
+        want, again = torch.empty_like(x), torch.empty_like(x)
+        ctx.set_accumulation(L.ACCUM_PAIRWISE)
+        ctx.cmd_routed_moe_layer(x[0], dwr, dbias, table, shared_dev.data_ptr(), L.PAGE_MXFP4, inter, want)
+        ranks[0].cmd_routed_moe_layer(x[0], dwr, dbias, table, shared_dev.data_ptr(), L.PAGE_MXFP4, inter, again)
+        torch.cuda.synchronize()
+        assert torch.equal(again, want) and ranks[0].device_status() == 0
+    finally:
+        for c in ranks:
+            c.close()
+
+
 def test_sharded_head_on_one_rank_and_by_row_shards(ctx, oracle):
     """ep.sharded_head with one rank, and the row shards of two ranks computed in turn: the pieces are
     the full logits bit for bit, the combined greedy token is the oracle's."""
