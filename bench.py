@@ -262,6 +262,10 @@ def run_gpu(args) -> None:
     peer_exchange = world > 1 and args.exchange == "peer" and args.accum == "pairwise"
     if peer_exchange:
         ep.connect_exchange(ctx, rank, world, HIDDEN)
+        # the ranks start together (barrier before the timed region); a rank that waits longer than
+        # about 20 ms for a peer gives the step up (status 0x5503, reported below) instead of stalling
+        # the run
+        ctx.ep_exchange_set_wait_limit(1 << 14)
 
     def enqueue_step(i: int, stream_handle=None):
         ly = layers[i % n_layers]
@@ -431,12 +435,10 @@ def run_gpu(args) -> None:
         else:
             with torch.cuda.stream(stream):
                 xd.copy_(hx[i % n_tok], non_blocking=True)
-                if peer_exchange:
-                    ep.decode_step_fused(ctx, xd, ep_states[i % n_layers], ys[0], layer=i % n_layers, world=world,
-                                         inter=INTER, stream=stream.cuda_stream)
-                else:
-                    ep.decode_step(ctx, xd, ep_states[i % n_layers], slots[0], ep_ids[0], ep_w[0], ys[0],
-                                   layer=i % n_layers, rank=rank, world=world, inter=INTER, stream=stream.cuda_stream)
+                # the per-token host round trip on several GPUs goes through the NCCL exchange (the exchange
+                # inside the kernel was measured from CUDA graphs only)
+                ep.decode_step(ctx, xd, ep_states[i % n_layers], slots[0], ep_ids[0], ep_w[0], ys[0],
+                               layer=i % n_layers, rank=rank, world=world, inter=INTER, stream=stream.cuda_stream)
                 hy.copy_(ys[0], non_blocking=True)
             stream.synchronize()
 
@@ -455,6 +457,7 @@ def run_gpu(args) -> None:
     e2e_value = e2e_steps / e2e_sec
     _note("end-to-end leg done")
 
+    device_status = ctx.device_status()  # 0 unless a bounded wait of a kernel ran out
     if rank == 0:
         cpu = None
         if world == 1 and not args.no_cpu_baseline and not args.kernel_only:
@@ -500,6 +503,7 @@ def run_gpu(args) -> None:
             "e2e": {"value": e2e_value, "unit": "layer-tokens/s", "h2d_bytes_per_step": HIDDEN * 4,
                     "d2h_bytes_per_step": HIDDEN * 4 + TOP_K * 8, "steps": e2e_steps},
             "gpu_launches": kernels_per_step * args.steps,
+            "device_status": device_status,
             "clocks": clocks,
         }
         print(json.dumps(line), flush=True)

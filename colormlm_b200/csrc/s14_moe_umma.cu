@@ -944,7 +944,10 @@ cudaError_t launch_moe_layer_umma(cudaStream_t st, int sm_count, const JobTable 
     if (ep) ex = *ep;
     if (ex.world > 1u && !router) return cudaErrorInvalidValue;  // the mix needs every route's weight
     (void)after_router;
-    return launch_pdl(k_moe_layer_umma, dim3(sm_count), dim3(kThreads), umma_smem_bytes(hidden), st, true, dev, param, x, d, y, partials, counters, status, hidden, inter, rt, ex);
+    // A programmatic dependent of the previous launch on the single-GPU path.  The expert-parallel
+    // paths (exchange inside the kernel, or expert outputs handed to a collective) were measured as
+    // ordinary launches only and stay so; the kernel's own dependency calls are then no-ops.
+    return launch_pdl(k_moe_layer_umma, dim3(sm_count), dim3(kThreads), umma_smem_bytes(hidden), st, ex.world <= 1u && y != nullptr, dev, param, x, d, y, partials, counters, status, hidden, inter, rt, ex);
 }
 
 }  // namespace s14
