@@ -834,7 +834,10 @@ k_moe_layer_umma(const JobTable *__restrict__ dev_table, const __grid_constant__
                         ep.slots[ep.rank] + ((size_t)(ep_step & 1u) * ep.n_slots + jj) * hidden + n0 + r;
                     unsigned long long got = ld_relaxed_sys(w);
                     uint32_t tries = 0;
-                    while ((uint32_t)(got >> 32) != ep_step + 1u) {
+                    // a word with an earlier step's number is waited for; one with a LATER number means that
+                    // the peer ran two steps ahead after giving up on this rank (the value of this step has
+                    // been overwritten): the rank does not wait, reports it, and so catches up again
+                    while ((int32_t)((uint32_t)(got >> 32) - (ep_step + 1u)) < 0) {
                         if (++tries > ep.wait_limit || abort_flag) {
                             abort_flag = 1;
                             break;
@@ -842,6 +845,7 @@ k_moe_layer_umma(const JobTable *__restrict__ dev_table, const __grid_constant__
                         __nanosleep(100);
                         got = ld_relaxed_sys(w);
                     }
+                    if ((int32_t)((uint32_t)(got >> 32) - (ep_step + 1u)) > 0) atomicExch(status, 0x5504u);
                     sv[t] = __uint_as_float((uint32_t)got);
                 }
                 __syncthreads();
