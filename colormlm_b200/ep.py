@@ -6,13 +6,14 @@ resident there).  Exchange: every rank writes the unmixed down vectors of the ex
 into a ``[top_k + 1, hidden]`` slot buffer (zeros elsewhere); one all-reduce (sum) gives every
 rank all slots exactly, because each slot has a single non-zero contributor; the reference's
 ordered mix then runs on every rank, so the result is bit-identical for any world size.  The
-reference has no multi-GPU code; this is the design SURVEY-level analysis asked for, built on the
+reference has no multi-GPU code; the partition is built on the
 reference's per-expert semantics (examples/s14_vulkan_numeric.rs:929-947).
 
 Two exchanges exist.  ``decode_step`` is the baseline: owned experts, one NCCL all-reduce of the
 slot buffer, a mix kernel.  ``decode_step_fused`` is one launch per rank: the layer kernel stores
-the down vectors of the experts it owns into every rank's mapped slot buffer over NVLink, publishes
-a flag, waits (bounded) for the other ranks' flags and mixes; ``connect_exchange`` maps the ranks'
+the down vectors of the experts it owns into every rank's mapped slot buffer over NVLink (each
+value with the step's number in one 8-byte store), waits (bounded) for the other ranks' values and
+mixes; ``connect_exchange`` maps the ranks'
 buffers once (CUDA IPC handles passed through torch.distributed)."""
 from __future__ import annotations
 
