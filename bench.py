@@ -298,6 +298,8 @@ def run_gpu(args) -> None:
                     enqueue_step(first + i, stream.cuda_stream)
         return g
 
+    if world > 1:
+        dist.barrier()  # first launches load the kernels; the ranks enter them together
     launched_before = ctx.launch_count
     with torch.cuda.stream(stream):
         for i in range(3):  # first launches outside capture (module load)
@@ -342,6 +344,7 @@ def run_gpu(args) -> None:
     if world > 1:
         dist.barrier()  # the ranks start the timed region together: a rank's kernels wait for the others'
         torch.cuda.synchronize()
+    ctx.device_status()  # read and clear: what is reported covers the timed region and the host leg
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     with torch.cuda.stream(stream):
         e0.record(stream)
