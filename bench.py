@@ -414,7 +414,9 @@ def run_gpu(args) -> None:
     achieved = roof_bytes / (roof_ms * 1e-3) / 1e9 if roof_ms else None
 
     # end to end through the host-buffer call: pinned x in, y (+ route) out, every step
-    hx = torch.randn((n_tok, HIDDEN), dtype=torch.float32).pin_memory()
+    hgen = torch.Generator()
+    hgen.manual_seed(4242)  # the same host tokens on every rank: the ranks must agree on the routes
+    hx = torch.randn((n_tok, HIDDEN), dtype=torch.float32, generator=hgen).pin_memory()
     hy = torch.empty((HIDDEN,), dtype=torch.float32).pin_memory()
     hx_np, hy_np = hx.numpy(), hy.numpy()
     ids_np, w_np = np.empty(TOP_K, np.int32), np.empty(TOP_K, np.float32)
