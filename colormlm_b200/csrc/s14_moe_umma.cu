@@ -365,6 +365,7 @@ k_moe_layer_umma(const JobTable *__restrict__ dev_table, const __grid_constant__
     __shared__ float s_route_w[S14_EXPERTS_PER_TOKEN];         // expert parallel: the weight of every route
     __shared__ uint32_t tmem_slot;
     __shared__ int abort_flag;
+    __shared__ int s_behind;  // expert parallel: a peer's word carries a later step's number
 
     const uint32_t tid = threadIdx.x, warp = tid >> 5, lane = tid & 31u;
     const bool is_producer = warp >= kProdWarp0 && warp < kProdWarp0 + kProdThreads / 32u;
@@ -422,6 +423,7 @@ k_moe_layer_umma(const JobTable *__restrict__ dev_table, const __grid_constant__
         mbar_init(bar(kBarXReady), 2u * kEpiGroup);
         mbar_init(bar(kBarFin), kIssuers);
         abort_flag = 0;
+        s_behind = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
     if (warp == kMmaWarp0) {
@@ -834,10 +836,12 @@ k_moe_layer_umma(const JobTable *__restrict__ dev_table, const __grid_constant__
                         ep.slots[ep.rank] + ((size_t)(ep_step & 1u) * ep.n_slots + jj) * hidden + n0 + r;
                     unsigned long long got = ld_relaxed_sys(w);
                     uint32_t tries = 0;
-                    // a word with an earlier step's number is waited for; one with a LATER number means that
-                    // the peer ran two steps ahead after giving up on this rank (the value of this step has
-                    // been overwritten): the rank does not wait, reports it, and so catches up again
+                    // A word with an earlier step's number is waited for.  One with a LATER number means that a
+                    // peer gave up on this rank and ran ahead: the words this rank still misses belong to
+                    // steps its peers have left behind and would never come, so it reports that, waits for
+                    // nothing more in this step and runs at full speed until it is level again.
                     while ((int32_t)((uint32_t)(got >> 32) - (ep_step + 1u)) < 0) {
+                        if (s_behind) break;
                         if (++tries > ep.wait_limit || abort_flag) {
                             abort_flag = 1;
                             break;
@@ -845,7 +849,10 @@ k_moe_layer_umma(const JobTable *__restrict__ dev_table, const __grid_constant__
                         __nanosleep(100);
                         got = ld_relaxed_sys(w);
                     }
-                    if ((int32_t)((uint32_t)(got >> 32) - (ep_step + 1u)) > 0) atomicExch(status, 0x5504u);
+                    if ((int32_t)((uint32_t)(got >> 32) - (ep_step + 1u)) > 0) {
+                        s_behind = 1;
+                        atomicExch(status, 0x5504u);
+                    }
                     sv[t] = __uint_as_float((uint32_t)got);
                 }
                 __syncthreads();

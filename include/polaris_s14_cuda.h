@@ -319,7 +319,8 @@ S14_API int32_t s14_cmd_moe_mix_slots(s14_ctx *ctx, void *stream, const float *s
  * buffer, each value together with the step's number in one 8-byte store (plain stores to peer
  * memory over NVLink), polls - bounded, a few seconds; a wait that runs out sets the device
  * status word 0x5503; a word that carries a later step's number, i.e. a peer that gave up on this
- * rank and ran ahead, sets 0x5504 and is not waited for, so that the ranks fall into step again -
+ * rank and ran ahead, sets 0x5504 and ends the waiting of that step, so that the rank catches up
+ * and the ranks fall into step again -
  * the words it needs in its own buffer until they carry this step's number,
  * and performs the ordered mix from them.  No fence, flag or collective call on the way.  One
  * launch per rank and step, no collective call; y is bit-identical to the single-GPU layer on
