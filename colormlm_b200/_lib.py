@@ -114,6 +114,8 @@ SIGNATURES = {
     "s14_ctx_sm_count": (_I32, [_VP]),
     "s14_ctx_device_status": (_I32, [_VP, _P(_U32)]),
     "s14_ctx_launch_count": (_U64, [_VP]),
+    "s14_ctx_set_layer_trace": (_I32, [_VP, _I32]),
+    "s14_ctx_read_layer_trace": (_I32, [_VP, _VP, _U32, _P(_U32), _P(_U32)]),
     "s14_ctx_set_kernel_timing": (_I32, [_VP, _I32]),
     "s14_ctx_kernel_times": (_I32, [_VP, _P(C.c_double), _P(_U64)]),
     "s14_shape_new": (_I32, [_U32, _U32, _P(MatvecShape)]),
@@ -125,6 +127,7 @@ SIGNATURES = {
     "s14_shape_mxfp4_scale_bytes": (_I32, [MatvecShape, _P(_U64)]),
     "s14_shape_fp8_weight_bytes": (_I32, [MatvecShape, _P(_U64)]),
     "s14_shape_fp8_scale_bytes": (_I32, [MatvecShape, _P(_U64)]),
+    "s14_layer_work_list": (_I32, [_U32, _U32, _U32, _U32, _U32, _VP, _U32, _VP]),
     "s14_mxfp4_expert_page_from_tensors": (_I32, [_U32, _U32, _VP, _VP]),
     "s14_mxfp4_expert_page_to_tensors": (_I32, [_U32, _U32, _VP, _VP]),
     "s14_validate_ue8m0_codes": (_I32, [_VP, _U64, _P(_U64)]),

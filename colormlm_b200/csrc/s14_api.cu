@@ -87,7 +87,7 @@ struct s14_ctx {
         bool connected = false;
         uint32_t wait_limit = 1u << 22;  // polls of about a microsecond: a few seconds
     } ep;
-    UmmaScratch umma{nullptr, nullptr};  // scratch of the tcgen05 layer kernel
+    UmmaScratch umma{nullptr, nullptr, nullptr};  // scratch of the tcgen05 layer kernel
     bool use_umma = true;                // S14_TENSOR_PATH=off in the environment turns it off
     const UmmaScratch *umma_scratch() const { return use_umma ? &umma : nullptr; }
 };
@@ -133,7 +133,7 @@ extern "C" int32_t s14_ctx_create(int32_t device, s14_ctx **out) {
     CUDA_OK(cudaHostGetDevicePointer(&ctx->y_host_dev, ctx->y_host, 0));
     CUDA_OK(cudaHostGetDevicePointer(&ctx->ids_host_dev, ctx->ids_host, 0));
     CUDA_OK(cudaHostGetDevicePointer(&ctx->w_host_dev, ctx->w_host, 0));
-    CUDA_OK(cudaMalloc(&ctx->umma.partials, umma_partials_bytes()));
+    CUDA_OK(cudaMalloc(&ctx->umma.tiles, umma_scratch_bytes()));
     ctx->umma.status = ctx->status;
     if (const char *path = getenv("S14_TENSOR_PATH")) ctx->use_umma = strcmp(path, "off") != 0;
     for (auto &e : ctx->marks.ev) CUDA_OK(cudaEventCreate(&e));
@@ -157,7 +157,8 @@ extern "C" int32_t s14_ctx_destroy(s14_ctx *ctx) {
     cudaFree(ctx->counters);
     cudaFree(ctx->ids_stage);
     cudaFree(ctx->weights_stage);
-    cudaFree(ctx->umma.partials);
+    cudaFree(ctx->umma.tiles);
+    cudaFree(ctx->umma.trace);
     s14_ep_exchange_destroy(ctx);
     cudaFreeHost(ctx->y_host);
     cudaFreeHost(ctx->ids_host);
@@ -197,6 +198,33 @@ extern "C" int32_t s14_ctx_device_status(s14_ctx *ctx, uint32_t *status) {
     CUDA_OK(cudaStreamSynchronize(ctx->compute));
     CUDA_OK(cudaMemcpy(status, ctx->status, sizeof(uint32_t), cudaMemcpyDeviceToHost));
     if (*status != 0) CUDA_OK(cudaMemset(ctx->status, 0, sizeof(uint32_t)));
+    return S14_OK;
+}
+
+extern "C" int32_t s14_ctx_set_layer_trace(s14_ctx *ctx, int32_t enable) {
+    if (!ctx) return fail(S14_ERR_CONTRACT, "ctx is NULL");
+    CUDA_OK(cudaStreamSynchronize(ctx->compute));
+    if (enable && !ctx->umma.trace) {
+        CUDA_OK(cudaMalloc(&ctx->umma.trace, umma_trace_bytes(ctx->sm_count)));
+        CUDA_OK(cudaMemset(ctx->umma.trace, 0, umma_trace_bytes(ctx->sm_count)));
+    } else if (!enable && ctx->umma.trace) {
+        CUDA_OK(cudaDeviceSynchronize());
+        CUDA_OK(cudaFree(ctx->umma.trace));
+        ctx->umma.trace = nullptr;
+    }
+    return S14_OK;
+}
+
+extern "C" int32_t s14_ctx_read_layer_trace(s14_ctx *ctx, uint64_t *out, uint32_t cap_words, uint32_t *n_ctas,
+                                            uint32_t *words_per_cta) {
+    if (!ctx || !out || !n_ctas || !words_per_cta) return fail(S14_ERR_CONTRACT, "s14_ctx_read_layer_trace: NULL argument");
+    if (!ctx->umma.trace) return fail(S14_ERR_CONTRACT, "s14_ctx_read_layer_trace: the trace is not enabled");
+    *n_ctas = (uint32_t)ctx->sm_count;
+    *words_per_cta = umma_trace_words();
+    const size_t words = (size_t)ctx->sm_count * umma_trace_words();
+    if (cap_words < words) return fail(S14_ERR_CONTRACT, "s14_ctx_read_layer_trace: buffer too small");
+    CUDA_OK(cudaDeviceSynchronize());
+    CUDA_OK(cudaMemcpy(out, ctx->umma.trace, words * sizeof(uint64_t), cudaMemcpyDeviceToHost));
     return S14_OK;
 }
 
@@ -573,6 +601,15 @@ static int32_t enqueue_layer(s14_ctx *ctx, cudaStream_t st, const s14_moe_layer_
     if (err != cudaSuccess) return cuda_fail(err, "S14 MoE layer launch");
     return S14_OK;
     S14_CATCH
+}
+
+extern "C" int32_t s14_layer_work_list(uint32_t cta, uint32_t n_ctas, uint32_t n_jobs, uint32_t hidden,
+                                       uint32_t inter, uint32_t *items_out, uint32_t cap, uint32_t *count) {
+    if (!count || (cap && !items_out)) return fail(S14_ERR_CONTRACT, "s14_layer_work_list: NULL argument");
+    if (n_ctas == 0 || cta >= n_ctas || (hidden & 511u) || (inter & 511u) || hidden == 0 || inter == 0)
+        return fail(S14_ERR_CONTRACT, "s14_layer_work_list: cta outside the grid, or sizes that are not multiples of 512");
+    *count = layer_work_list(cta, n_ctas, n_jobs, inter >> 6, hidden >> 7, hidden >> 8, inter >> 8, items_out, cap);
+    return S14_OK;
 }
 
 extern "C" int32_t s14_cmd_moe_layer(s14_ctx *ctx, void *stream, const s14_moe_layer_desc *desc) {

@@ -7,6 +7,7 @@
 #include <cuda_fp8.h>
 
 #include "s14_internal.h"
+#include "s14_page_layout.h"
 
 namespace s14 {
 
@@ -91,58 +92,27 @@ __device__ __forceinline__ const JobTable &table_of(const JobTable *dev, const J
     return dev ? *dev : param;
 }
 
+// An expert page as the kernels see it.  FP8 pages are the six tensors one after the other
+// (w1 | w3 | w2 | s1 | s3 | s2, weights [N, K] bytes, one UE8M0 code per 128 x 128 block).  MXFP4
+// pages are read through the offset functions of s14_page_layout.h from `base`.
 struct PageView {
-    const uint8_t *w1, *w3, *w2, *s1, *s3, *s2;
+    const uint8_t *base;
+    const uint8_t *w1, *w3, *w2, *s1, *s3, *s2;  // FP8 pages only
 };
-
-// Byte order inside an MXFP4 expert page (w1 | w3 | w2 | s13 | s2).  The unit of work of the
-// tcgen05 kernel is a slice of 64 intermediate elements of one expert: the 64 rows of w1 and of
-// w3 that produce them (one 128-row MMA tile) and the 64 columns of w2 that consume them.
-//   w1, w3  [inter, hidden/2] bytes, row-major, as the checkpoint has them.
-//   w2      by slice s and row tile rt: 128 rows x 32 B (the 64 codes of the slice), 4 KB per
-//           (s, rt), row tiles of a slice next to each other -- a slice's columns are one
-//           contiguous run of hidden * 32 bytes.
-//   s13     the scale codes of w1 and w3 by slice s and K-atom a (four scale blocks): 512 B in
-//           the order tensor memory takes them, MMA row m = the slice's w1 row m (m < 64) or w3
-//           row m - 64: byte (m % 32) * 16 + (m / 32) * 4 + block % 4.
-//   s2      the scale codes of w2 by slice pair p and row tile rt: 512 B, row r of the tile at
-//           (r % 32) * 16 + (r / 32) * 4, blocks 4p..4p+3 (slice 2p: 0 and 1, slice 2p+1: 2 and 3).
-// hidden and inter are multiples of 128.  The sixteen code bytes (one scale block) of w2 row n:
-__device__ __forceinline__ size_t w2_block_offset(uint32_t n, uint32_t kb, uint32_t hidden) {
-    return (((size_t)(kb >> 1) * (hidden >> 7) + (n >> 7)) * 128u + (n & 127u)) * 32u + (kb & 1u) * 16u;
-}
-// the scale code of row i, block kb of w1 (mat 0) or w3 (mat 1), inside s13
-__device__ __forceinline__ size_t up_scale_offset(uint32_t mat, uint32_t i, uint32_t kb, uint32_t hidden) {
-    const uint32_t m = (i & 63u) + mat * 64u;
-    return ((size_t)(i >> 6) * (hidden >> 7) + (kb >> 2)) * 512u + (m & 31u) * 16u + (m >> 5) * 4u + (kb & 3u);
-}
-// the scale code of row n, block kb of w2, inside s2
-__device__ __forceinline__ size_t down_scale_offset(uint32_t n, uint32_t kb, uint32_t hidden) {
-    const uint32_t r = n & 127u;
-    return ((size_t)(kb >> 2) * (hidden >> 7) + (n >> 7)) * 512u + (r & 31u) * 16u + (r >> 5) * 4u + (kb & 3u);
-}
 
 __device__ __forceinline__ PageView page_view(const uint8_t *page, uint32_t kind, uint32_t hidden,
                                               uint32_t inter) {
     PageView v;
+    v.base = page;
     const size_t elems = (size_t)hidden * inter;
-    if (kind == S14_PAGE_MXFP4) {
-        const size_t wb = elems >> 1, sb = elems >> 5;
-        v.w1 = page;
-        v.w3 = page + wb;
-        v.w2 = page + 2 * wb;
-        v.s1 = page + 3 * wb;
-        v.s3 = v.s1 + sb;
-        v.s2 = v.s3 + sb;
-    } else {
-        const size_t sb = (size_t)((inter + 127u) >> 7) * ((hidden + 127u) >> 7);
-        v.w1 = page;
-        v.w3 = page + elems;
-        v.w2 = page + 2 * elems;
-        v.s1 = page + 3 * elems;
-        v.s3 = v.s1 + sb;
-        v.s2 = v.s3 + sb;
-    }
+    const size_t sb = (size_t)((inter + 127u) >> 7) * ((hidden + 127u) >> 7);
+    v.w1 = page;
+    v.w3 = page + elems;
+    v.w2 = page + 2 * elems;
+    v.s1 = page + 3 * elems;
+    v.s3 = v.s1 + sb;
+    v.s2 = v.s3 + sb;
+    (void)kind;
     return v;
 }
 

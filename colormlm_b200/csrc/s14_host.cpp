@@ -76,45 +76,34 @@ void validate_ue8m0_codes(const uint8_t *codes, uint64_t len) {
             throw CodeError("UE8M0 scale contains 0xff NaN at byte " + std::to_string(i), i);
 }
 
-uint64_t mxfp4_page_w2_offset(uint32_t n, uint32_t kb, uint32_t hidden) {
-    return (((uint64_t)(kb >> 1) * (hidden >> 7) + (n >> 7)) * 128u + (n & 127u)) * 32u + (kb & 1u) * 16u;
-}
-uint64_t mxfp4_page_up_scale_offset(uint32_t mat, uint32_t i, uint32_t kb, uint32_t hidden) {
-    const uint32_t m = (i & 63u) + mat * 64u;
-    return ((uint64_t)(i >> 6) * (hidden >> 7) + (kb >> 2)) * 512u + (m & 31u) * 16u + (m >> 5) * 4u + (kb & 3u);
-}
-uint64_t mxfp4_page_down_scale_offset(uint32_t n, uint32_t kb, uint32_t hidden) {
-    const uint32_t r = n & 127u;
-    return ((uint64_t)(kb >> 2) * (hidden >> 7) + (n >> 7)) * 512u + (r & 31u) * 16u + (r >> 5) * 4u + (kb & 3u);
-}
-
 static void check_page_shape(uint32_t hidden, uint32_t inter, const void *a, const void *b) {
-    if (hidden == 0 || inter == 0 || (hidden & 127u) || (inter & 127u))
-        throw ContractError("MXFP4 expert page: hidden and intermediate must be non-zero multiples of 128");
+    if (hidden == 0 || inter == 0 || (hidden & 255u) || (inter & 255u))
+        throw ContractError("MXFP4 expert page: hidden and intermediate must be non-zero multiples of 256");
     if (!a || !b) throw ContractError("MXFP4 expert page: NULL buffer");
 }
 
 // forward = true: tensors -> page order; false: page order -> tensors
 static void reorder_page(uint32_t hidden, uint32_t inter, const uint8_t *src, uint8_t *dst, bool forward) {
-    const size_t wb = (size_t)hidden * inter / 2, sb = (size_t)hidden * inter / 32;
-    std::memcpy(dst, src, 2 * wb);  // w1, w3 as they are
-    const uint8_t *w2s = src + 2 * wb, *sc_s = src + 3 * wb;
-    uint8_t *w2d = dst + 2 * wb, *sc_d = dst + 3 * wb;
+    const size_t wb = mxfp4_weight_bytes(hidden, inter), sb = (size_t)hidden * inter / 32;
     const uint32_t kb_down = inter >> 5, kb_up = hidden >> 5;
+    auto move16 = [&](size_t tensor_at, size_t page_at) {
+        std::memcpy(forward ? dst + page_at : dst + tensor_at, forward ? src + tensor_at : src + page_at, 16);
+    };
+    auto move1 = [&](size_t tensor_at, size_t page_at) {
+        if (forward) dst[page_at] = src[tensor_at];
+        else dst[tensor_at] = src[page_at];
+    };
     for (uint32_t n = 0; n < hidden; ++n)
         for (uint32_t kb = 0; kb < kb_down; ++kb) {
-            const size_t t = (size_t)n * (inter >> 1) + (size_t)kb * 16u, p = mxfp4_page_w2_offset(n, kb, hidden);
-            std::memcpy(forward ? w2d + p : w2d + t, forward ? w2s + t : w2s + p, 16);
-            const size_t ts = 2 * sb + (size_t)n * kb_down + kb, ps = 2 * sb + mxfp4_page_down_scale_offset(n, kb, hidden);
-            if (forward) sc_d[ps] = sc_s[ts];
-            else sc_d[ts] = sc_s[ps];
+            move16(2 * wb + (size_t)n * (inter >> 1) + (size_t)kb * 16u, mxfp4_down_chunk_offset(n, kb, hidden, inter));
+            move1(3 * wb + 2 * sb + (size_t)n * kb_down + kb, mxfp4_down_scale_offset(n, kb, hidden, inter));
         }
     for (uint32_t mat = 0; mat < 2; ++mat)
         for (uint32_t i = 0; i < inter; ++i)
             for (uint32_t kb = 0; kb < kb_up; ++kb) {
-                const size_t ts = (size_t)mat * sb + (size_t)i * kb_up + kb, ps = mxfp4_page_up_scale_offset(mat, i, kb, hidden);
-                if (forward) sc_d[ps] = sc_s[ts];
-                else sc_d[ts] = sc_s[ps];
+                move16((size_t)mat * wb + (size_t)i * (hidden >> 1) + (size_t)kb * 16u,
+                       mxfp4_up_chunk_offset(mat, i, kb, hidden));
+                move1(3 * wb + (size_t)mat * sb + (size_t)i * kb_up + kb, mxfp4_up_scale_offset(mat, i, kb, hidden, inter));
             }
 }
 

@@ -12,6 +12,8 @@
 #include <unordered_map>
 #include <vector>
 
+#include "s14_page_layout.h"
+
 namespace s14 {
 
 // Error classes map onto the C ABI status codes.
@@ -43,20 +45,10 @@ struct S14MatvecShape {
 // storage_bytes (s14_vulkan.rs:128-130): byte counts rounded up to whole 32-bit words.
 inline uint64_t storage_bytes(uint64_t logical) { return (logical + 3) / 4 * 4; }
 
-// Byte order of an MXFP4 expert page, w1 | w3 | w2 | s13 | s2.  A page made of the six checkpoint
-// tensors in their own ABI (w1 | w3 | w2 | s1 | s3 | s2, weights [N, K/2] bytes, scales [N, K/32]
-// codes) is the *tensor page*; the page the GPU reads keeps w1 and w3 and stores the rest by slice
-// of 64 intermediate elements, the unit of work of the tcgen05 kernel:
-//   w2   (slice s, row tile rt): 128 rows x 32 bytes -- a slice's columns are contiguous;
-//   s13  (slice s, K-atom a): the codes of the slice's 64 w1 rows and 64 w3 rows for four scale
-//        blocks, 512 bytes in the order tensor memory takes them;
-//   s2   (slice pair p, row tile rt): the codes of 128 rows of w2 for blocks 4p..4p+3, same order.
-// hidden and inter must be multiples of 128.  No counterpart in the reference, which fixes no page
-// layout.  The three offset functions give the position of the 16 code bytes of w2 row n, block
-// kb (inside w2), of a w1 / w3 scale code (inside s13) and of a w2 scale code (inside s2).
-uint64_t mxfp4_page_w2_offset(uint32_t n, uint32_t kb, uint32_t hidden);
-uint64_t mxfp4_page_up_scale_offset(uint32_t mat, uint32_t i, uint32_t kb, uint32_t hidden);
-uint64_t mxfp4_page_down_scale_offset(uint32_t n, uint32_t kb, uint32_t hidden);
+// The MXFP4 expert page the GPU reads (byte order: s14_page_layout.h) against the *tensor page*, the
+// six checkpoint tensors in their own ABI one after the other (w1 | w3 | w2 | s1 | s3 | s2, weights
+// [N, K/2] bytes, scales [N, K/32] codes), which the loader receives.  Same size; hidden and
+// intermediate must be multiples of 256.  No counterpart in the reference, which fixes no page layout.
 // src and dst must not overlap.
 void mxfp4_expert_page_from_tensors(uint32_t hidden, uint32_t inter, const uint8_t *tensor_page, uint8_t *page);
 void mxfp4_expert_page_to_tensors(uint32_t hidden, uint32_t inter, const uint8_t *page, uint8_t *tensor_page);

@@ -43,14 +43,17 @@ struct UmmaScratch;
 
 // Expert-parallel exchange of the tcgen05 layer kernel over peer memory.  Every rank holds an
 // exchange buffer: two slot buffers [n_slots, hidden] of 8-byte words {F32 bits, step + 1} (steps
-// alternate between them), then the rank's own step count.  A rank stores the down vectors of the
+// alternate between them), then the rank's own step count (64 bytes), then one 8-byte word per
+// rank: the number of steps that rank has finished.  A rank stores the down vectors of the
 // experts it owns into the slot rows of EVERY rank's buffer, each value with the step's number in
 // one 8-byte store (plain stores to peer memory; an aligned 8-byte store arrives whole, so the
 // number validates the value beside it and no fence or flag is needed); each rank polls (bounded)
-// the words it needs in its own buffer and mixes from them.  world <= 1: no exchange.
+// the words it needs in its own buffer and mixes from them.  Before a rank writes the slot buffer
+// of step s it waits (bounded) until every peer has finished step s - 2, the last reader of that
+// buffer; a rank that owns nothing in a step is waited for in this way too.  world <= 1: no exchange.
 constexpr uint32_t kMaxEpWorld = 8;
 struct EpExchange {
-    unsigned long long *slots[kMaxEpWorld];  // rank p's slot buffers, as mapped on this rank
+    unsigned long long *slots[kMaxEpWorld];  // rank p's exchange buffer, as mapped on this rank
     uint32_t *step;                // this rank's step count (device memory, kept by the kernel)
     uint32_t world, rank;
     uint32_t n_slots;              // top_k (+ 1 with a shared expert)
@@ -60,7 +63,9 @@ struct EpExchange {
 inline size_t ep_exchange_slot_bytes(uint32_t hidden) {
     return sizeof(unsigned long long) * 2u * (S14_EXPERTS_PER_TOKEN + 1) * hidden;
 }
-inline size_t ep_exchange_bytes(uint32_t hidden) { return ep_exchange_slot_bytes(hidden) + 64u; }
+inline size_t ep_exchange_bytes(uint32_t hidden) {
+    return ep_exchange_slot_bytes(hidden) + 64u + sizeof(unsigned long long) * kMaxEpWorld;
+}
 
 // What the router reads and writes, for a layer call that computes its own routes: the tcgen05
 // layer kernel scores the experts in its first microseconds (every CTA a few of them), and every
@@ -98,23 +103,32 @@ int launch_moe_layer(cudaStream_t st, uint32_t mode, int sm_count, const JobTabl
                      cudaError_t *err, const KernelMarks *km = nullptr, bool all_mxfp4 = false,
                      unsigned int *counters = nullptr, const struct UmmaScratch *umma = nullptr,
                      const FusedRouter *router = nullptr, const EpExchange *ep = nullptr);
-// Scratch of the tcgen05 layer kernel (s14_moe_umma.cu): every item's share of its expert's output
-// (umma_partials_bytes) and the device status word a timed-out wait sets.
+// Scratch of the tcgen05 layer kernel (s14_moe_umma.cu): per job the digit tile of its hidden
+// values and the tile's block exponents (umma_scratch_bytes), and the device status word a
+// timed-out wait sets.
 struct UmmaScratch {
-    float *partials;
+    uint8_t *tiles;
     uint32_t *status;
+    unsigned long long *trace;  // per-CTA time marks of the last launch (profiling runs), or nullptr
 };
-size_t umma_partials_bytes();
+size_t umma_scratch_bytes();
+size_t umma_trace_bytes(int sm_count);
+uint32_t umma_trace_words();
 // One token, every job an MXFP4 page, hidden and inter multiples of 512 that fit shared and tensor memory.
+// Sets the kernel's shared-memory attribute for the current device on first use.
 bool umma_layer_ok(int sm_count, uint32_t n_tokens, uint32_t n_jobs_max, uint32_t hidden, uint32_t inter);
 // Whether the tcgen05 layer kernel can score n_experts itself (a CTA scores at most four).
 bool umma_router_ok(int sm_count, uint32_t n_experts);
+// The items CTA c of G runs, in order (see s14_moe_umma.cu); returns their number, writes at most cap.
+__host__ __device__ uint32_t layer_work_list(uint32_t c, uint32_t G, uint32_t n_jobs, uint32_t S, uint32_t RT,
+                                             uint32_t KU, uint32_t KD, uint32_t *items, uint32_t cap);
 // Both phases and the mix in one launch (y == nullptr: the expert outputs go to d, the caller mixes).
 // With a router the kernel computes the routes itself and the job tables are not read.
 cudaError_t launch_moe_layer_umma(cudaStream_t st, int sm_count, const JobTable *dev, const JobTable &param,
-                                  const float *x, float *d, float *y, float *partials, unsigned int *counters,
-                                  uint32_t *status, uint32_t hidden, uint32_t inter, bool after_router,
-                                  const FusedRouter *router = nullptr, const EpExchange *ep = nullptr);
+                                  const float *x, float *d, float *y, uint8_t *tiles, unsigned int *counters,
+                                  uint32_t *status, uint32_t hidden, uint32_t inter,
+                                  const FusedRouter *router = nullptr, const EpExchange *ep = nullptr,
+                                  unsigned long long *trace = nullptr);
 int launch_router(cudaStream_t st, const s14_router_desc &r, float *scores, float *select,
                   JobTable *table_out, const uint8_t *const *page_table, const uint8_t *shared_page,
                   uint32_t shared_kind, unsigned int *counter, cudaError_t *err,

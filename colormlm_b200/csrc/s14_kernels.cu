@@ -249,20 +249,22 @@ struct RowFrag {
     uint32_t sc[KC];
 };
 
-// MAT: 0 = w1, 1 = w3 (rows of [inter, hidden]), 2 = w2 (rows of [hidden, inter]).
+// MAT: 0 = w1, 1 = w3 (rows of [inter, hidden]), 2 = w2 (rows of [hidden, inter]); `other` is the
+// matrix's other dimension (inter for w1 / w3 rows of K = hidden, hidden for w2 rows of K = inter).
 template <int KC, int MAT>
 __device__ __forceinline__ void load_row_mxfp4(RowFrag<KC> &f, const PageView &pv, uint32_t row, uint32_t lane,
-                                               uint32_t hidden) {
+                                               uint32_t other) {
 #pragma unroll
     for (int j = 0; j < KC; ++j) {
         const uint32_t kb = (uint32_t)j * 32u + lane;
         if (MAT < 2) {
-            const uint8_t *w = MAT ? pv.w3 : pv.w1;
-            f.q[j] = ldg_stream(reinterpret_cast<const uint4 *>(w + (size_t)row * (KC * 512)) + kb);
-            f.sc[j] = __ldg(pv.s1 + up_scale_offset(MAT, row, kb, hidden));
+            constexpr uint32_t hidden = KC * 1024;
+            f.q[j] = ldg_stream(reinterpret_cast<const uint4 *>(pv.base + mxfp4_up_chunk_offset(MAT, row, kb, hidden)));
+            f.sc[j] = __ldg(pv.base + mxfp4_up_scale_offset(MAT, row, kb, hidden, other));
         } else {
-            f.q[j] = ldg_stream(reinterpret_cast<const uint4 *>(pv.w2 + w2_block_offset(row, kb, hidden)));
-            f.sc[j] = __ldg(pv.s2 + down_scale_offset(row, kb, hidden));
+            constexpr uint32_t inter = KC * 1024;
+            f.q[j] = ldg_stream(reinterpret_cast<const uint4 *>(pv.base + mxfp4_down_chunk_offset(row, kb, other, inter)));
+            f.sc[j] = __ldg(pv.base + mxfp4_down_scale_offset(row, kb, other, inter));
         }
     }
 }
@@ -337,8 +339,8 @@ k_expert_up_pairwise(const JobTable *__restrict__ dev_table,
         const Job jb = tab.jobs[tab.token_jobs[job]];
         if (jb.kind == S14_PAGE_MXFP4) {
             const PageView pv = page_view(jb.page, jb.kind, hidden, inter);
-            load_row_mxfp4<KC, 0>(g, pv, row, lane, hidden);
-            load_row_mxfp4<KC, 1>(u, pv, row, lane, hidden);
+            load_row_mxfp4<KC, 0>(g, pv, row, lane, inter);
+            load_row_mxfp4<KC, 1>(u, pv, row, lane, inter);
         }
     };
     auto finish = [&](const RowFrag<KC> &g, const RowFrag<KC> &u, uint32_t item) {
@@ -435,22 +437,23 @@ k_expert_down_pairwise(const JobTable *__restrict__ dev_table,
 
 // Reference-order dot of one MXFP4 row: sequential k, (x*e)*s, separate add.
 // x is read from shared memory (every lane reads the same address: broadcast).
-// MAT: 0 = w1, 1 = w3, 2 = w2 of an expert page.
+// MAT: 0 = w1, 1 = w3, 2 = w2 of an expert page; k is the row's length.
 template <int MAT>
 __device__ __forceinline__ float dot_row_mxfp4_reference(const PageView &pv, uint32_t row, uint32_t k, uint32_t hidden,
-                                                         const float *__restrict__ xs) {
+                                                         uint32_t inter, const float *__restrict__ xs) {
     const uint32_t groups = k >> 5;
-    const uint4 *wrow = reinterpret_cast<const uint4 *>((MAT == 1 ? pv.w3 : pv.w1) + (size_t)row * (k >> 1));
     float sum = 0.0f;
     for (uint32_t g4 = 0; g4 < groups; g4 += 4) {
         uint4 q[4];
         uint32_t scw;
 #pragma unroll
         for (int j = 0; j < 4; ++j)
-            q[j] = MAT < 2 ? __ldg(wrow + g4 + j)
-                           : __ldg(reinterpret_cast<const uint4 *>(pv.w2 + w2_block_offset(row, g4 + j, hidden)));
-        scw = __ldg(reinterpret_cast<const uint32_t *>(MAT < 2 ? pv.s1 + up_scale_offset(MAT, row, g4, hidden)
-                                                               : pv.s2 + down_scale_offset(row, g4, hidden)));
+            q[j] = __ldg(reinterpret_cast<const uint4 *>(
+                pv.base + (MAT < 2 ? mxfp4_up_chunk_offset(MAT, row, g4 + j, hidden)
+                                   : mxfp4_down_chunk_offset(row, g4 + j, hidden, inter))));
+        scw = __ldg(reinterpret_cast<const uint32_t *>(
+            pv.base + (MAT < 2 ? mxfp4_up_scale_offset(MAT, row, g4, hidden, inter)
+                               : mxfp4_down_scale_offset(row, g4, hidden, inter))));
 #pragma unroll
         for (int j = 0; j < 4; ++j) {
             const float sc = ue8m0_to_f32((scw >> (8 * j)) & 0xffu);
@@ -523,8 +526,8 @@ k_expert_up_reference(const JobTable *__restrict__ dev_table,
     const PageView pv = page_view(jb.page, jb.kind, hidden, inter);
     float gate, up;
     if (jb.kind == S14_PAGE_MXFP4) {
-        gate = dot_row_mxfp4_reference<0>(pv, row, hidden, hidden, xs);
-        up = dot_row_mxfp4_reference<1>(pv, row, hidden, hidden, xs);
+        gate = dot_row_mxfp4_reference<0>(pv, row, hidden, hidden, inter, xs);
+        up = dot_row_mxfp4_reference<1>(pv, row, hidden, hidden, inter, xs);
     } else {
         gate = dot_row_fp8_reference(pv.w1, pv.s1, row, hidden, xs);
         up = dot_row_fp8_reference(pv.w3, pv.s3, row, hidden, xs);
@@ -549,7 +552,7 @@ k_expert_down_reference(const JobTable *__restrict__ dev_table,
     if (row >= hidden) return;
     const PageView pv = page_view(jb.page, jb.kind, hidden, inter);
     const float v = (jb.kind == S14_PAGE_MXFP4)
-                        ? dot_row_mxfp4_reference<2>(pv, row, inter, hidden, xs)
+                        ? dot_row_mxfp4_reference<2>(pv, row, inter, hidden, inter, xs)
                         : dot_row_fp8_reference(pv.w2, pv.s2, row, inter, xs);
     d[(size_t)jb.out_index * hidden + row] = v;
 }
@@ -976,8 +979,8 @@ int launch_moe_layer(cudaStream_t st, uint32_t mode, int sm_count, const JobTabl
                                                                        hidden, inter);
         launches += 2;
     } else if (tensor_path) {
-        *err = launch_moe_layer_umma(st, sm_count, dev_table, param_table, x, d, y, umma->partials, counters,
-                                     umma->status, hidden, inter, dev_table != nullptr, router, ep);
+        *err = launch_moe_layer_umma(st, sm_count, dev_table, param_table, x, d, y, umma->tiles, counters,
+                                     umma->status, hidden, inter, router, ep, umma->trace);
         launches += 1;
         if (km) {  // one kernel runs both phases and the mix: its time is booked as the up phase
             cudaEventRecord(km->ev[2], st);

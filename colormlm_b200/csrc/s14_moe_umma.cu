@@ -3,85 +3,89 @@
 // UE8M0 scale per 32 elements along K), so no thread decodes or scales a weight.
 //
 // The matvec as a block-scaled MMA.  A = 128 weight rows x 64 K-elements per instruction; its
-// scales go to tensor memory with tcgen05.cp.  B = the activation vector as eight balanced
+// scales go to tensor memory with tcgen05.cp.  B = the activation vector as sixteen balanced
 // base-8 digit rows: within a scale block of 32 elements with largest magnitude < 2^E
-// (E >= -100), every element is q * 2^(E-23) with |q| <= 2^23 (rounded to nearest when it has
-// more bits below the block's top bit), q = sum_j d_j 8^j with d_j in [-4, 4] -- all of them
-// E2M1 values -- and digit row j carries the UE8M0 scale 2^(E-23+3j).  Accumulator column j
-// holds the digit-j share of the dot product in F32; the eight columns are added low digits
-// first.  Measured against a double-precision sum on B200: relative RMSE 1.5e-7, nearly all of it
-// from the 23-bit quantisation of elements far below their block's largest one.  Columns 8-15 of
-// the 16-column MMA are zero rows.
+// (-80 <= E <= 127), every element is q * 2^(E-47) with q a 48-bit integer (exact for every F32
+// value down to 2^-24 of the block's largest), q = hi * 8^8 + lo, and hi, lo are written with eight
+// digits d_j in [-4, 4] each -- all of them E2M1 values.  Row j < 8 holds the digits of hi with the
+// UE8M0 scale 2^(E-23+3j), row 8 + j the digits of lo with 2^(E-47+3j).  Accumulator column j holds
+// the digit-j share of the dot product: a sum of small integers times powers of two, which the F32
+// accumulator in tensor memory holds exactly at the magnitudes of this path, so the sixteen columns
+// added in double and rounded once give the double-accumulated dot product rounded to F32.
 //
-// Work split: by slice.  An item is (expert, 64 intermediate elements): the 64 rows of w1 and
-// the 64 rows of w3 that produce them form one 128-row MMA tile over K = hidden (up phase, one
-// accumulator: lanes 0-63 the gate, 64-127 the up projection), and the 64 columns of w2 that
-// consume them are hidden / 128 MMAs of K = 64 (down phase).  The hidden values of a slice never
-// leave the CTA: SwiGLU, digits and scales are made from the up accumulator and fed to the down
-// MMAs.  Each item leaves its contribution to the expert's output, 4 bytes per row, in global
-// scratch; when every item of the layer is done (one counter, bounded polling; the grid is one
-// CTA per SM, all resident), every CTA adds up its share of the rows in slice order and applies
-// the ordered mix.  Items are handed out in equal numbers, so the result does not depend on how.
-// The expert page stores w2 and all scales by slice for this purpose.
+// Work.  An expert page is stored as units of 128 rows x 256 K-elements (s14_page_layout.h); a unit
+// and its scale atoms are two plain bulk copies (cp.async.bulk, no multicast) into one ring slot.
+//   up item   (job, slice of 64 intermediate elements): hidden / 256 units accumulate into one
+//             accumulator (lanes 0-63 the gate, 64-127 the up projection); the epilogue applies the
+//             limited SwiGLU, writes the 64 hidden values as digit rows into the job's digit tile in
+//             global memory (L2) and counts the slice on the job's counter.
+//   down item (job, tile of 128 output rows): waits (bounded) until the job's counter says that
+//             every slice is there, takes the job's digit tile into shared memory, and accumulates
+//             intermediate / 256 units into one accumulator: the finished rows of the expert's
+//             output.  The last item of a row tile to finish (a counter, no waiting) applies the
+//             ordered mix to that tile.
+// No output passes through partial sums of several CTAs, so the result does not depend on how
+// items are dealt.  Items are dealt to the CTAs (one per SM, all resident) in a fixed pattern that
+// levels the number of units per CTA; a CTA runs its up items first, then its down items.
 //
-// Roles inside a CTA: four producer warps (cp.async into a 10-stage ring of 16 KB of codes + 2 KB
-// of scales: up units of all items first, then down stages), four MMA-issuing threads, eight
-// epilogue warps (tcgen05.ld / tcgen05.st).  Every mbarrier wait and the poll of the item
-// counter are bounded; a wait that runs out raises the CTA's abort flag, the status word is set
-// and the CTA drains its copies, frees its tensor memory and returns.
+// Roles inside a CTA: one copying thread, two MMA-issuing threads (even and odd units of an item,
+// an accumulator each), four epilogue warps (tcgen05.ld, sums, SwiGLU, digits, mix), eight warps
+// that fetch digit tiles for the down items.  Every wait (mbarrier, counter, peer word) is bounded;
+// a wait that runs out raises the CTA's abort flag, the status word is set, and the CTA waits for
+// its copies in flight, frees its tensor memory and returns.
 #include "s14_device.cuh"
 
 namespace s14 {
 
 namespace {
 
-constexpr uint32_t kRing = 10;                 // stages in flight per CTA (even: an up unit's parity is its slot's)
-constexpr uint32_t kStageA = 128 * 128;        // 16 KB of codes: an up unit (128 rows x 256 K) or four down blocks (128 rows x 64 K each)
-constexpr uint32_t kStageSf = 4 * 512;         // scale atoms of a stage: two (up unit) or four (down stage)
-constexpr uint32_t kEpiGroup = 128;            // two epilogue groups of four warps
-constexpr uint32_t kMmaWarp0 = 8;              // warps 8, 9, 14, 15: one issuing thread each (lane 0)
-constexpr uint32_t kIssuers = 4;
-constexpr uint32_t kProdWarp0 = 10;            // warps 10..13 copy
-constexpr uint32_t kProdThreads = 128;
+constexpr uint32_t kUnitSf = 2 * kAtomBytes;       // scale atoms of a unit (256 K-elements = 8 blocks)
+constexpr uint32_t kSlot = kUnitBytes + kUnitSf;   // ring slot: codes, then scales (17 KB, keeps 1 KB alignment)
+constexpr uint32_t kMaxRing = 12;                  // ring slots are an even number: a slot belongs to one issuing thread
 constexpr uint32_t kThreads = 512;
-constexpr uint32_t kDRing = 4;                 // down stages whose four accumulators are in flight (one per issuing thread)
-constexpr uint32_t kItemSlots = 4;             // items a CTA can hold (digit tiles of their hidden values)
+constexpr uint32_t kEpiThreads = 128;              // warps 0-3: one per lane quadrant of tensor memory
+constexpr uint32_t kProdWarp = 4;                  // lane 0 copies
+constexpr uint32_t kMmaWarp0 = 5;                  // warps 5, 6: lane 0 issues
+constexpr uint32_t kLoadWarp0 = 8;                 // warps 8-15 fetch digit tiles
+constexpr uint32_t kLoadThreads = 256;
+constexpr uint32_t kMaxItems = 32;                 // items a CTA can hold
+constexpr uint32_t kJobsMax = S14_EXPERTS_PER_TOKEN + 1;
+constexpr uint32_t kTileMax = 32768;               // digit tile of a 4096-long vector: 16 units of 2 KB
+constexpr uint32_t kExpMax = 128;                  // its block exponents
 // tensor memory columns
 constexpr uint32_t kTmemCols = 512;
-constexpr uint32_t kColD = 0;                  // kDRing x 4 accumulators x 16
-constexpr uint32_t kColU = kColD + kDRing * 64;    // 2 issuing threads x 16 (one item at a time)
-constexpr uint32_t kColSfa = kColU + 32;       // kIssuers x 16: weight scales of the stage each issuing thread is at
-// Scales of digit rows: an atom (four scale blocks) is four columns (N-rows 0-31, 32-63, ...; a 16-row
-// operand uses the first).  Scale addresses given to the MMA stay atom-aligned.
-constexpr uint32_t kColSfbX = kColSfa + kIssuers * 16;  // hidden / 32: scales of the token's digit rows
-constexpr uint32_t kColSfbH = kColSfbX + 128;           // kItemSlots x 4: scales of the hidden values' digit rows
-static_assert(kColSfbH + kItemSlots * 4 <= kTmemCols, "tensor memory map");
-constexpr uint32_t kMaxHidden = 4096;          // 128 columns of token digit scales
-constexpr uint32_t kMaxBlocks = kMaxHidden / 32;
-constexpr uint32_t kSpin = 1u << 17;           // tries (a microsecond each at most) before a wait gives up
-constexpr uint32_t kSpinGlobal = 1u << 20;     // polls (100 ns apart) of the item counter before giving up
-constexpr uint32_t kItemCounter = 1, kExitCounter = 2;  // in the context's counter array ([0] is the router's)
-constexpr uint32_t kRouteCounter = 3;          // CTAs whose expert scores are written (routes computed in this kernel)
-constexpr uint32_t kRouterSlots = 4;           // experts a CTA scores at most
+constexpr uint32_t kColAcc = 0;      // [2 buffers][2 issuing threads][16]
+constexpr uint32_t kColSfa = 64;     // [2 issuing threads][16]: weight scales of the unit each thread is at
+// Scales of digit rows: an atom (four scale blocks) is four columns (N-rows 0-31, 32-63, ...; a
+// 16-row operand uses the first).  Scale addresses given to the MMA stay atom-aligned.
+constexpr uint32_t kColSfbX = 96;    // hidden / 32 columns: the token's digit rows
+constexpr uint32_t kColSfbH = 224;   // [2 tiles][128]: the hidden values' digit rows
+static_assert(kColSfbH + 2 * 128 <= kTmemCols, "tensor memory map");
+constexpr uint32_t kMaxHidden = 4096;
+constexpr uint32_t kSpin = 1u << 17;        // tries (a microsecond each at most) before a wait gives up
+constexpr uint32_t kSpinGlobal = 1u << 20;  // polls (100 ns apart) of a counter before giving up
+// the context's counter array ([0] is the router kernel's); [1, kCntEnd) are zero between launches
+constexpr uint32_t kCntExit = 2, kCntRoute = 3;
+constexpr uint32_t kCntJob0 = 16;                    // slices done per job
+constexpr uint32_t kCntTile0 = kCntJob0 + 64;        // jobs done per row tile
+constexpr uint32_t kCntEnd = kCntTile0 + 64;
+constexpr uint32_t kRouterSlots = 4;                 // experts a CTA scores at most
+constexpr uint32_t kItemDown = 0x80000000u;
+constexpr uint32_t kTraceWords = 64;   // time marks per CTA of a profiling run
 
-// Bar indices in the static barrier array.
-constexpr uint32_t kBarFull = 0;                      // ring slot filled with an up unit (128 copying threads)
-constexpr uint32_t kBarDFull = kRing;                 // ring slot filled with a down stage
-constexpr uint32_t kBarDone = 2 * kRing;              // the slot's MMAs have completed (the copies may reuse it)
-constexpr uint32_t kBarDFree = 3 * kRing;             // a down stage's accumulators have been read
-constexpr uint32_t kBarDDone = kBarDFree + kDRing;    // a down stage's accumulators are complete
-constexpr uint32_t kBarUDone = kBarDDone + kDRing;    // an item's up accumulators are complete
-constexpr uint32_t kBarUFree = kBarUDone + 1;         // ... have been read
-constexpr uint32_t kBarHReady = kBarUFree + 1;        // an item's hidden digits and scales are in place
-constexpr uint32_t kBarXReady = kBarHReady + kItemSlots;  // the token's digit scales are in tensor memory
-constexpr uint32_t kBarFin = kBarXReady + 1;          // both issuing threads have finished
+// Barriers.
+constexpr uint32_t kBarFull = 0;                      // ring slot filled (one arrival + the copies' bytes)
+constexpr uint32_t kBarDone = kMaxRing;               // the slot's MMAs have completed (the copies may reuse it)
+constexpr uint32_t kBarAccDone = 2 * kMaxRing;        // [2] an item's accumulators are complete (both issuing threads)
+constexpr uint32_t kBarAccFree = kBarAccDone + 2;     // [2] ... have been read
+constexpr uint32_t kBarXReady = kBarAccFree + 2;      // the token's digit scales are in tensor memory
+constexpr uint32_t kBarHReady = kBarXReady + 1;       // [2] a digit tile of hidden values is in place
+constexpr uint32_t kBarHFree = kBarHReady + 2;        // [2] ... is not read any more
+constexpr uint32_t kBarFin = kBarHFree + 2;           // both issuing threads have finished
 constexpr uint32_t kBars = kBarFin + 1;
 
 __device__ __forceinline__ uint32_t smem_u32(const void *p) {
     return (uint32_t)__cvta_generic_to_shared(p);
-}
-__device__ __forceinline__ void cp_async16(uint32_t dst, const void *src) {
-    asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(dst), "l"(src));
 }
 __device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
     asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count));
@@ -89,9 +93,15 @@ __device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
 __device__ __forceinline__ void mbar_arrive(uint32_t bar) {
     asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
 }
-// Arrives once the calling thread's earlier cp.async copies have landed.
-__device__ __forceinline__ void mbar_arrive_after_copies(uint32_t bar) {
-    asm volatile("cp.async.mbarrier.arrive.noinc.shared::cta.b64 [%0];" ::"r"(bar) : "memory");
+__device__ __forceinline__ void mbar_arrive_expect(uint32_t bar, uint32_t bytes) {
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
+}
+// Plain bulk copy global -> this CTA's shared memory; both addresses and the size are multiples
+// of 16.  Completion is counted in bytes on the mbarrier.
+__device__ __forceinline__ void bulk_copy(uint32_t dst, const void *src, uint32_t bytes, uint32_t bar) {
+    asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
+                 ::"r"(dst), "l"(src), "r"(bytes), "r"(bar)
+                 : "memory");
 }
 // One bounded hardware wait: returns when the phase completes or after about a microsecond.
 __device__ __forceinline__ bool mbar_try(uint32_t bar, uint32_t parity) {
@@ -115,8 +125,34 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatil
     *abort_flag = 1;
     return false;
 }
-// Named barrier 1: the 128 threads of epilogue group A.
-__device__ __forceinline__ void group_bar_sync() { asm volatile("bar.sync 1, 128;" ::: "memory"); }
+// Named barriers with a vote: every thread of the group executes them, whatever it has seen, so a
+// group never splits in front of a barrier.  1: the 128 epilogue threads; 2: the 256 tile threads.
+__device__ __forceinline__ bool epi_all(bool ok) {
+    uint32_t r;
+    asm volatile(
+        "{\n.reg .pred p, q;\n"
+        "setp.ne.b32 p, %1, 0;\n"
+        "barrier.cta.red.and.pred q, 1, 128, p;\n"
+        "selp.b32 %0, 1, 0, q;\n}"
+        : "=r"(r)
+        : "r"((uint32_t)ok)
+        : "memory");
+    return r != 0;
+}
+__device__ __forceinline__ bool load_all(bool ok) {
+    uint32_t r;
+    asm volatile(
+        "{\n.reg .pred p, q;\n"
+        "setp.ne.b32 p, %1, 0;\n"
+        "barrier.cta.red.and.pred q, 2, 256, p;\n"
+        "selp.b32 %0, 1, 0, q;\n}"
+        : "=r"(r)
+        : "r"((uint32_t)ok)
+        : "memory");
+    return r != 0;
+}
+__device__ __forceinline__ void epi_sync() { asm volatile("bar.sync 1, 128;" ::: "memory"); }
+__device__ __forceinline__ void load_sync() { asm volatile("bar.sync 2, 256;" ::: "memory"); }
 // Shared-memory matrix descriptor of sm_100: start address, leading and stride byte offsets in
 // 16-byte units, descriptor version 1, layout (0 = no swizzle, 2 = 128-byte swizzle).
 __device__ __forceinline__ uint64_t smem_desc(uint32_t addr, uint32_t lbo16, uint32_t sbo16, uint32_t layout) {
@@ -139,92 +175,108 @@ __device__ __forceinline__ void umma_commit(uint32_t bar) {
     asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar)
                  : "memory");
 }
-// Eight accumulator columns of the warp's 32 lanes; the values may be used after tmem_ld_wait().
-__device__ __forceinline__ void tmem_ld8(uint32_t addr, uint32_t (&r)[8]) {
-    asm volatile("tcgen05.ld.sync.aligned.32x32b.x8.b32 {%0,%1,%2,%3,%4,%5,%6,%7}, [%8];"
-                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7])
-                 : "r"(addr));
+// Sixteen accumulator columns of the warp's 32 lanes; the values may be used after tmem_ld_wait().
+__device__ __forceinline__ void tmem_ld16(uint32_t addr, uint32_t (&r)[16]) {
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x16.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15}, [%16];"
+        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
+          "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
+        : "r"(addr));
 }
 __device__ __forceinline__ void tmem_ld_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
 __device__ __forceinline__ void fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
 __device__ __forceinline__ void fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
-
+__device__ __forceinline__ void fence_async_smem() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
 
 // Instruction descriptor: A and B E2M1 (format 1), both K-major, N = 16, UE8M0 scales, M = 128.
 constexpr uint32_t kIdesc = (1u << 7) | (1u << 10) | ((16u >> 3) << 17) | (1u << 23) | ((128u >> 4) << 24);
 
-// Writes the eight digit rows of elements 8g .. 8g+7 of a vector and, for the first thread of a
-// scale block, the block's exponent.  Thread g of the CTA owns group g, i.e. one 32-bit word of
-// every digit row; the four lanes of a scale block agree on its exponent E (largest magnitude
-// < 2^E, clamped to [-100, 127]), so whole warps call this together.  With the bias
-// 4 * (8^8 - 1) / 7 added, the balanced digits of q are the plain base-8 digits minus 4, so no
-// carry runs through them.  Rows 8-15 of the tile are zeroed by the caller; the blocks' exponents
-// go to sE, from which store_digit_scales writes the digit rows' scale codes into tensor memory.
+// E2M1 codes of the eight balanced base-8 digits of q (|q| <= 2^23), digit j in bits 4j .. 4j+3.
+// With the bias 4 * (8^8 - 1) / 7 added, the balanced digits are the plain base-8 digits minus 4,
+// so no carry runs through them; the top digit may reach +4.
+__device__ __forceinline__ uint32_t digit_codes(int q) {
+    const uint32_t qb = (uint32_t)(q + 0x924924);  // in [0, 8^8 + 8^7)
+    uint32_t w = 0;
+#pragma unroll
+    for (int j = 0; j < 7; ++j)  // E2M1 codes of -4..3 by digit value 0..7
+        w |= ((0x5420ACDEu >> (((qb >> (3 * j)) & 7u) << 2)) & 0xFu) << (4 * j);
+    const uint32_t top = qb >> 21;  // 0..8 -> -4..4
+    return w | ((top > 7u ? 6u : ((0x5420ACDEu >> (top << 2)) & 0xFu)) << 28);
+}
+// v * 2^(23-E) = hi + lo * 2^-24 with integers |hi|, |lo| <= 2^23 (|v| < 2^E); digit codes of both.
+__device__ __forceinline__ void digit_codes16(float v, float up, uint32_t &hi_w, uint32_t &lo_w) {
+    const float t = v * up;  // exact: a power of two
+    const int hi = __float2int_rn(t);
+    const float rem = __fsub_rn(t, (float)hi);  // exact
+    hi_w = digit_codes(hi);
+    lo_w = digit_codes(__float2int_rn(rem * 16777216.0f));
+}
+// The exponent E of a scale block from its largest magnitude: bm < 2^E, clamped to [-80, 127] (row
+// 8 of a block carries the scale 2^(E-47), whose UE8M0 code must not fall below zero).
+__device__ __forceinline__ int block_exponent(float bm) {
+    int E = -80;
+    if (bm > 0.0f) E = min(max((int)((__float_as_uint(bm) >> 23) & 0xFFu) - 126, -80), 127);
+    return E;
+}
+
+// Writes the sixteen digit rows of elements 8g .. 8g+7 of a vector into a digit tile (2 KB per 256
+// elements: sixteen rows of 128 bytes, the 16-byte chunk of scale block kb at position
+// (kb % 8) ^ (row % 8)) and, for the first thread of a scale block, the block's exponent.  Thread g
+// owns one 32-bit word of every digit row; the four lanes of a scale block agree on its exponent,
+// so whole warps call this together.
 __device__ __forceinline__ void digits_of8(const float (&xs)[8], uint32_t g, uint8_t *sB, uint8_t *sE) {
     float bm = 0.0f;
 #pragma unroll
     for (int i = 0; i < 8; ++i) bm = fmaxf(bm, fabsf(xs[i]));
     bm = fmaxf(bm, __shfl_xor_sync(0xffffffffu, bm, 1));
     bm = fmaxf(bm, __shfl_xor_sync(0xffffffffu, bm, 2));
-    int E = -100;
-    if (bm > 0.0f) E = min(max((int)((__float_as_uint(bm) >> 23) & 0xFFu) - 126, -100), 127);
+    const int E = block_exponent(bm);
     const float up = __uint_as_float((uint32_t)(150 - E) << 23);  // 2^(23-E)
-    uint32_t words[8] = {0u, 0u, 0u, 0u, 0u, 0u, 0u, 0u};
+    uint32_t words[16];
+#pragma unroll
+    for (int j = 0; j < 16; ++j) words[j] = 0u;
 #pragma unroll
     for (int i = 0; i < 8; ++i) {
-        const uint32_t qb = (uint32_t)(__float2int_rn(xs[i] * up) + 0x924924);  // in [0, 8^8 + 8^7) for finite input
+        uint32_t hw, lw;
+        digit_codes16(xs[i], up, hw, lw);
 #pragma unroll
-        for (int j = 0; j < 7; ++j)  // E2M1 codes of -4..3 by digit value 0..7
-            words[j] |= ((0x5420ACDEu >> (((qb >> (3 * j)) & 7u) << 2)) & 0xFu) << (4 * i);
-        const uint32_t top = qb >> 21;  // 0..8 -> -4..4
-        words[7] |= (top > 7u ? 6u : ((0x5420ACDEu >> (top << 2)) & 0xFu)) << (4 * i);
+        for (int j = 0; j < 8; ++j) {
+            words[j] |= ((hw >> (4 * j)) & 0xFu) << (4 * i);
+            words[8 + j] |= ((lw >> (4 * j)) & 0xFu) << (4 * i);
+        }
     }
     const uint32_t kb = g >> 2;
     uint8_t *chunk = sB + (kb >> 3) * 2048u + (g & 3u) * 4u;
 #pragma unroll
-    for (uint32_t j = 0; j < 8; ++j)
-        *reinterpret_cast<uint32_t *>(chunk + j * 128u + (((kb & 7u) ^ j) << 4)) = words[j];
+    for (uint32_t j = 0; j < 16; ++j)
+        *reinterpret_cast<uint32_t *>(chunk + j * 128u + (((kb & 7u) ^ (j & 7u)) << 4)) = words[j];
     if ((g & 3u) == 0u) sE[kb] = (uint8_t)(E + 100);  // the block's exponent, biased
 }
 
-// The scale codes of the digit rows, written to tensor memory by the eight epilogue warps (each
-// lane quadrant takes every atom; warps 0-3 the even groups of four atoms, warps 4-7 the odd ones).
-// Column 4a of lane l holds the codes of N-row l for scale blocks 4a..4a+3: digit row l < 8 of a
-// block with exponent E has the code 127 + E - 23 + 3l; rows 8-15 are zero rows, columns 4a+1..4a+3
-// belong to N-rows 32 and up, which a 16-column MMA does not use.
-__device__ __forceinline__ void store_digit_scales(uint32_t tmem_sfb, const uint8_t *sE, uint32_t K, uint32_t warp,
-                                                   uint32_t lane) {
+// The scale codes of the sixteen digit rows of a vector of K elements, written to tensor memory by
+// the warp that owns lane quadrant `quad` (every quadrant holds all of them); the warp takes the
+// groups of four atoms g0, g0 + gstep, ...  Column 4a of lane l holds the codes of N-row l for scale
+// blocks 4a..4a+3: digit row l < 8 of a block with exponent E has the code 127 + E - 23 + 3l, row
+// 8 + l the code 127 + E - 47 + 3l; columns 4a+1..4a+3 belong to N-rows 32 and up, which a 16-column
+// MMA does not use.  sE holds E + 100 per block.
+__device__ __forceinline__ void store_digit_scales(uint32_t tmem_sfb, const uint8_t *sE, uint32_t K, uint32_t quad,
+                                                   uint32_t g0, uint32_t gstep, uint32_t lane) {
     const uint32_t groups = K >> 9;  // groups of four atoms (512 K-elements, 16 blocks)
-    const uint32_t bias = 0x01010101u * (4u + 3u * (lane & 7u));
-    const uint32_t quad = tmem_sfb + (((warp & 3u) * 32u) << 16);
-    for (uint32_t g = warp >> 2; g < groups; g += 2u) {
+    const int shift = lane < 8u ? 4 + 3 * (int)lane : 3 * (int)(lane & 7u) - 20;
+    const uint32_t bias = 0x01010101u * (uint32_t)shift;  // no byte borrows: E + 100 >= 20
+    const uint32_t base = tmem_sfb + ((quad * 32u) << 16);
+    const uint32_t one = 0x7F7F7F7Fu;
+    for (uint32_t g = g0; g < groups; g += gstep) {
         const uint4 e = *reinterpret_cast<const uint4 *>(sE + g * 16u);
-        const uint32_t one = 0x7F7F7F7Fu;
-        const uint32_t w0 = lane < 8u ? e.x + bias : one, w1 = lane < 8u ? e.y + bias : one;
-        const uint32_t w2 = lane < 8u ? e.z + bias : one, w3 = lane < 8u ? e.w + bias : one;
+        const uint32_t w0 = lane < 16u ? e.x + bias : one, w1 = lane < 16u ? e.y + bias : one;
+        const uint32_t w2 = lane < 16u ? e.z + bias : one, w3 = lane < 16u ? e.w + bias : one;
         asm volatile(
             "tcgen05.st.sync.aligned.32x32b.x16.b32 [%0], {%1,%5,%5,%5,%2,%5,%5,%5,%3,%5,%5,%5,%4,%5,%5,%5};"
-            ::"r"(quad + g * 16u), "r"(w0), "r"(w1), "r"(w2), "r"(w3), "r"(one)
+            ::"r"(base + g * 16u), "r"(w0), "r"(w1), "r"(w2), "r"(w3), "r"(one)
             : "memory");
     }
     asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
 }
-
-// s + e = a + b exactly (Knuth); no operation may be contracted or reordered.
-__device__ __forceinline__ void two_sum(float a, float b, float &s, float &e) {
-    s = __fadd_rn(a, b);
-    const float bb = __fsub_rn(s, a);
-    e = __fadd_rn(__fsub_rn(a, __fsub_rn(s, bb)), __fsub_rn(b, bb));
-}
-
-// SwiGLU of the pairwise path: the same expression as swiglu_limit_f32 with the F32 library
-// exponential (FP64 is scarce on this GPU; the bit-exact order keeps the correctly rounded one).
-__device__ __forceinline__ float swiglu_limit_fast(float gate, float up) {
-    const float g = fminf(gate, 10.0f);
-    const float u = fminf(fmaxf(up, -10.0f), 10.0f);
-    return __fmul_rn(__fdiv_rn(g, __fadd_rn(1.0f, expf(-g))), u);
-}
-
 
 __device__ __forceinline__ unsigned long long ld_relaxed_sys(const unsigned long long *p) {
     unsigned long long v;
@@ -240,19 +292,53 @@ __device__ __forceinline__ uint32_t ld_acquire(const unsigned int *p) {
     return v;
 }
 
-// No-swizzle K-major tile of 8-row x 16-byte core matrices for K = 64 (32 bytes per row): the two
-// halves of a row are 128 B apart (leading offset), 8-row groups 256 B apart (stride offset).
-__device__ __forceinline__ uint64_t smem_desc_k64(uint32_t addr) { return smem_desc(addr, 8, 16, 0); }
+}  // namespace
+
+// The items of CTA c of G: its up items (job j, slice) first, then its down items (job j, row tile),
+// each as down-bit | j << 8 | index.  Up items q = j * S + slice go round the CTAs (q mod G).  The
+// CTAs with one up item fewer take KU / KD down items each of the jobs whose slices are finished
+// when they get there; the rest of the down items p = j * RT + tile go round all CTAs from the last
+// CTA down.  KU, KD: units of an up and of a down item.  Writes at most `cap` items, returns the
+// CTA's number of items.
+__host__ __device__ uint32_t layer_work_list(uint32_t c, uint32_t G, uint32_t n_jobs, uint32_t S, uint32_t RT,
+                                             uint32_t KU, uint32_t KD, uint32_t *items, uint32_t cap) {
+    const uint32_t U = n_jobs * S, D = n_jobs * RT;
+    uint32_t n = 0;
+    if (U == 0u || G == 0u) return 0u;
+    for (uint32_t q = c; q < U; q += G, ++n)
+        if (n < cap) items[n] = ((q / S) << 8) | (q % S);
+    const uint32_t a_max = (U + G - 1u) / G, r = U - (a_max - 1u) * G;  // CTAs 0 .. r-1 hold a_max up items
+    const uint32_t n_light = G - r, k0 = KU / KD;
+    const uint32_t ready = RT * (((a_max - 1u) * G) / S);  // down items of jobs finished one round of up items earlier
+    uint32_t D1 = n_light * k0;
+    if (D1 > ready) D1 = ready;
+    if (D1 > D) D1 = D;
+    if (c >= r)
+        for (uint32_t i = 0; i < k0; ++i) {
+            const uint32_t p = (c - r) + i * n_light;
+            if (p < D1) {
+                if (n < cap) items[n] = 0x80000000u | ((p / RT) << 8) | (p % RT);
+                ++n;
+            }
+        }
+    for (uint32_t p = D1 + (G - 1u - c); p < D; p += G, ++n)
+        if (n < cap) items[n] = 0x80000000u | ((p / RT) << 8) | (p % RT);
+    return n;
+}
+
+namespace {
 
 // The routes of the token from the experts' scores, by one warp (the same picks, sums and weights
 // as k_router's last block: largest score + bias first, lowest id on ties; weight = score / sum of
 // the picked scores x route_scale).  Scores, selection values and page addresses come in one round
 // of loads; the picked expert's values come from the lane that holds them.  Lane 0 writes the jobs
-// (route order, the shared expert last), the mix and every route's weight; `publish` also writes
-// the caller's ids and weights.  Expert parallel: the rank keeps the jobs of the experts it owns and, as the shared
-// expert's owner, the shared job; every job writes the row of its route slot.
+// (the shared expert first, so that its page can be asked for before the routes exist, then the
+// routed experts in route order), the mix (route order, the shared expert last) and every route's
+// weight; `publish` also writes the caller's ids and weights.  Expert parallel: the rank keeps the
+// jobs of the experts it owns and, as the shared expert's owner, the shared job; every job writes
+// the row of its route slot.
 __device__ void route_select(const FusedRouter &rt, uint32_t lane, bool publish, Job *jobs, uint32_t *n_jobs_out,
-                             float *mix_w, uint32_t *mix_job, float *route_w) {
+                             float *mix_w, uint32_t *mix_slot, uint32_t *n_mix_out) {
     unsigned long long key[8], pg[8];
     float sc[8];
 #pragma unroll
@@ -310,13 +396,25 @@ __device__ void route_select(const FusedRouter &rt, uint32_t lane, bool publish,
     for (int j = 0; j < S14_EXPERTS_PER_TOKEN; ++j)
         if ((uint32_t)j < rt.top_k) sum = __fadd_rn(sum, picked[j]);
     uint32_t n = 0;
+    const bool shared_here = rt.shared_page && rt.shared_owner == rt.ep_rank;
+    if (shared_here) {
+        Job jb;
+        jb.page = rt.shared_page;
+        jb.kind = rt.shared_kind;
+        jb.token = 0;
+        jb.weight = 1.0f;
+        jb.is_shared = 1;
+        jb.out_index = rt.top_k;
+        jobs[n++] = jb;
+    }
 #pragma unroll
     for (int j = 0; j < S14_EXPERTS_PER_TOKEN; ++j) {
         if ((uint32_t)j >= rt.top_k) continue;
         const float w = __fmul_rn(__fdiv_rn(picked[j], sum), rt.route_scale);
         if (publish && rt.ids_out) rt.ids_out[j] = ids[j];
         if (publish && rt.weights_out) rt.weights_out[j] = w;
-        route_w[j] = w;  // every route's weight, also of experts other ranks own
+        mix_w[j] = w;  // every route's weight, also of experts other ranks own
+        mix_slot[j] = (uint32_t)j;
         if (((uint32_t)ids[j] % rt.ep_world) == rt.ep_rank) {
             Job jb;
             jb.page = reinterpret_cast<const uint8_t *>(pages[j]);
@@ -325,105 +423,149 @@ __device__ void route_select(const FusedRouter &rt, uint32_t lane, bool publish,
             jb.weight = w;
             jb.is_shared = 0;
             jb.out_index = (uint32_t)j;
-            jobs[n] = jb;
-            mix_w[n] = w;
-            mix_job[n] = n;
-            ++n;
+            jobs[n++] = jb;
         }
     }
-    if (rt.shared_page && rt.shared_owner == rt.ep_rank) {
-        Job jb;
-        jb.page = rt.shared_page;
-        jb.kind = rt.shared_kind;
-        jb.token = 0;
-        jb.weight = 1.0f;
-        jb.is_shared = 1;
-        jb.out_index = rt.top_k;
-        jobs[n] = jb;
-        mix_w[n] = 1.0f;
-        mix_job[n] = n | 0x80000000u;
-        ++n;
+    uint32_t nm = rt.top_k;
+    if (rt.shared_page) {
+        mix_w[nm] = 1.0f;
+        mix_slot[nm] = rt.top_k | 0x80000000u;
+        ++nm;
     }
+    *n_mix_out = nm;
     *n_jobs_out = n;
 }
 
 __global__ void __launch_bounds__(kThreads, 1)
 k_moe_layer_umma(const JobTable *__restrict__ dev_table, const __grid_constant__ JobTable param_table,
-                 const float *__restrict__ x, float *d_out, float *__restrict__ y, float *part,
+                 const float *__restrict__ x, float *d_out, float *__restrict__ y, uint8_t *tiles,
                  unsigned int *counters, uint32_t *__restrict__ status, uint32_t hidden, uint32_t inter,
-                 const __grid_constant__ FusedRouter rt, const __grid_constant__ EpExchange ep) {
+                 uint32_t ring, unsigned long long *trace, const __grid_constant__ FusedRouter rt,
+                 const __grid_constant__ EpExchange ep) {
     extern __shared__ __align__(1024) uint8_t smem[];
     __shared__ __align__(8) uint64_t bars[kBars];
-    __shared__ __align__(16) uint8_t sE[kMaxBlocks];         // block exponents of the token's digits
-    __shared__ __align__(16) uint8_t sBh[kItemSlots * 512];  // digit tiles of the items' hidden values (rows 8-15 zero)
-    __shared__ float s_up[64];                               // an item's up projection, handed to the gate threads
-    __shared__ uint8_t sEh[kItemSlots][2];
-    __shared__ float s_mix_w[S14_EXPERTS_PER_TOKEN + 1];        // the mix, in route order: weight (shared expert: 1)
-    __shared__ uint32_t s_mix_job[S14_EXPERTS_PER_TOKEN + 1];   //   job, bit 31 set for the shared expert
-    __shared__ Job s_jobs[S14_EXPERTS_PER_TOKEN + 1];           // the layer's jobs, from the routes or the caller's table
-    __shared__ uint32_t s_n_jobs;
-    __shared__ float s_route_w[S14_EXPERTS_PER_TOKEN];         // expert parallel: the weight of every route
+    __shared__ __align__(16) uint8_t sE[kExpMax];        // block exponents of the token's digits
+    __shared__ __align__(16) uint8_t sEh[2][kExpMax];    // ... of the digit tiles of hidden values
+    __shared__ __align__(16) uint8_t s_hst[16 * 2 * 16]; // an up item's digit chunks: [row][block][16 bytes]
+    __shared__ float s_up[64];                           // an item's up projection, handed to the gate threads
+    __shared__ float s_mix_w[kJobsMax];                  // the mix, in route order: weight (shared expert: 1)
+    __shared__ uint32_t s_mix_slot[kJobsMax];            //   row of the expert outputs, bit 31 set for the shared expert
+    __shared__ uint32_t s_n_mix;
+    __shared__ Job s_jobs[kJobsMax];                     // the layer's jobs, from the routes or the caller's table
+    __shared__ uint32_t s_n_jobs, s_n_static;
+    __shared__ uint32_t s_items[kMaxItems];
+    __shared__ uint32_t s_n_items;
     __shared__ uint32_t tmem_slot;
     __shared__ int abort_flag;
-    __shared__ int s_behind;  // expert parallel: a peer's word carries a later step's number
+    __shared__ int s_behind;   // expert parallel: a peer's word carries a later step's number
+    __shared__ int s_last;     // this CTA finished the last job of a row tile / is the last CTA to leave
+    __shared__ uint32_t s_abort_code;
 
     const uint32_t tid = threadIdx.x, warp = tid >> 5, lane = tid & 31u;
-    const bool is_producer = warp >= kProdWarp0 && warp < kProdWarp0 + kProdThreads / 32u;
-    const uint32_t KU = hidden >> 8;   // up units of an item (256 K-elements each)
-    const uint32_t DS = hidden >> 9;   // down stages of an item (four 128-row tiles each)
+    const uint32_t grid = gridDim.x, cta = blockIdx.x;
+    const uint32_t KU = hidden >> 8;   // units of an up item
+    const uint32_t KD = inter >> 8;    // units of a down item
     const uint32_t RT = hidden >> 7;   // row tiles of w2
     const uint32_t S = inter >> 6;     // slices of an expert
-    uint8_t *const sA = smem;
-    uint8_t *const sSF = sA + kRing * kStageA;
-    uint8_t *const sBx = sSF + kRing * kStageSf;  // the token's digit tile, 2 KB per 256 K-elements
+    uint8_t *const sRing = smem;
+    uint8_t *const sBx = smem + ring * kSlot;   // the token's digit tile, 2 KB per 256 K-elements
+    uint8_t *const sBh = sBx + KU * 2048u;      // two digit tiles of hidden values
+    const uint32_t tile_bytes = KD * 2048u;
+    uint8_t *const tile_exps = tiles + (size_t)kJobsMax * kTileMax;  // [job][kExpMax] after the tiles
     const uint32_t bar0 = smem_u32(bars);
     auto bar = [&](uint32_t i) { return bar0 + i * 8u; };
+    volatile int *const abortp = &abort_flag;
+    // Optional per-CTA time marks (SM clock) for profiling runs: kTraceWords words per CTA, word 0 the
+    // global timer at entry.  One designated thread writes each mark.
+    unsigned long long *const tr = trace ? trace + (size_t)cta * kTraceWords : nullptr;
+    auto mark = [&](uint32_t i) {
+        if (tr && i < kTraceWords) tr[i] = (unsigned long long)clock64();
+    };
+    if (tr && tid == 0) {
+        unsigned long long gt;
+        asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(gt));
+        tr[0] = gt;
+        mark(1);
+    }
 
     // Thread t owns elements 8t .. 8t+7 of the token (hidden <= 8 x kThreads), for the digits and for
     // the router's dot products; the router weights of this CTA's experts (cta, cta + grid, ...) are
     // asked for first, so that they arrive while the CTA sets itself up.
     const bool routes_here = rt.weight != nullptr;
-    // expert parallel: the step count picks the slot buffer and the flag value; the last CTA to
-    // leave advances it, after every CTA has read it
     const bool ep_on = ep.world > 1u;
+    const bool table_param = !routes_here && dev_table == nullptr;
+    // the CTA's items are known at once unless the number of jobs depends on the routes (expert
+    // parallel: a rank keeps the experts it owns) or the table comes from an earlier kernel
+    const bool early = table_param || (routes_here && rt.ep_world <= 1u);
     const bool has_x = tid < (hidden >> 3);
     float xs[8] = {0.0f, 0.0f, 0.0f, 0.0f, 0.0f, 0.0f, 0.0f, 0.0f};
     uint4 rq[kRouterSlots];
     if (routes_here) {
 #pragma unroll
         for (uint32_t k = 0; k < kRouterSlots; ++k) {
-            const uint32_t e = blockIdx.x + k * gridDim.x;
+            const uint32_t e = cta + k * grid;
             rq[k] = make_uint4(0u, 0u, 0u, 0u);
             if (has_x && e < rt.n_experts) rq[k] = ldg_stream(reinterpret_cast<const uint4 *>(rt.weight + (size_t)e * hidden) + tid);
         }
     }
     // The kernel is launched as a programmatic dependent of whatever precedes it in the stream: its
-    // CTAs may be placed as soon as SMs are free and set themselves up (barriers, tensor memory);
-    // everything an earlier kernel may have written (the token, the counters, the step count) is read
-    // only after cudaGridDependencySynchronize() below.  In the same way the next launch may be set
-    // up from now on.  Weights and page tables are constant during a step.
+    // CTAs may be placed as soon as SMs are free and set themselves up (barriers, tensor memory, the
+    // first copies of pages whose addresses are launch arguments); everything an earlier kernel may
+    // have written (the token, the counters, a device job table, the step count) is read only after
+    // cudaGridDependencySynchronize() below.  In the same way the next launch may be set up from now
+    // on.  Weights and page tables are constant during a step.
     cudaTriggerProgrammaticLaunchCompletion();
 
-    // rows 8-15 of the digit tiles stay zero
-    for (uint32_t i = tid; i < (KU * 2048u) >> 4; i += kThreads) reinterpret_cast<uint4 *>(sBx)[i] = make_uint4(0u, 0u, 0u, 0u);
-    for (uint32_t i = tid; i < sizeof(sBh) / 4u; i += kThreads) reinterpret_cast<uint32_t *>(sBh)[i] = 0u;
     if (tid == 0) {
-        for (uint32_t s = 0; s < kRing; ++s) {
-            mbar_init(bar(kBarFull + s), kProdThreads);
-            mbar_init(bar(kBarDFull + s), kProdThreads);
+        for (uint32_t s = 0; s < kMaxRing; ++s) {
+            mbar_init(bar(kBarFull + s), 1);
             mbar_init(bar(kBarDone + s), 1);
         }
-        for (uint32_t s = 0; s < kDRing; ++s) {
-            mbar_init(bar(kBarDFree + s), kEpiGroup);
-            mbar_init(bar(kBarDDone + s), 1);
+        for (uint32_t b = 0; b < 2; ++b) {
+            mbar_init(bar(kBarAccDone + b), 2);
+            mbar_init(bar(kBarAccFree + b), kEpiThreads);
+            mbar_init(bar(kBarHReady + b), kLoadThreads);
+            mbar_init(bar(kBarHFree + b), 2);
         }
-        mbar_init(bar(kBarUDone), 2);
-        mbar_init(bar(kBarUFree), kEpiGroup);
-        for (uint32_t s = 0; s < kItemSlots; ++s) mbar_init(bar(kBarHReady + s), kEpiGroup);
-        mbar_init(bar(kBarXReady), 2u * kEpiGroup);
-        mbar_init(bar(kBarFin), kIssuers);
+        mbar_init(bar(kBarXReady), 256);
+        mbar_init(bar(kBarFin), 2);
         abort_flag = 0;
         s_behind = 0;
+        s_last = 0;
+        s_abort_code = 0x5501u;
+        s_n_items = 0;
+        s_n_jobs = 0;
+        s_n_static = 0;
+        s_n_mix = 0;
+        if (table_param) {
+            const uint32_t nj = min(param_table.n_jobs, kJobsMax);
+            for (uint32_t j = 0; j < nj; ++j) s_jobs[j] = param_table.jobs[j];
+            const uint32_t m0 = param_table.token_job_begin[0];
+            const uint32_t nm = min(param_table.token_job_begin[1] - m0, kJobsMax);
+            for (uint32_t j = 0; j < nm; ++j) {
+                const Job &jb = param_table.jobs[param_table.token_jobs[m0 + j]];
+                s_mix_w[j] = jb.weight;
+                s_mix_slot[j] = jb.out_index | (jb.is_shared ? 0x80000000u : 0u);
+            }
+            s_n_mix = nm;
+            s_n_jobs = nj;
+            s_n_static = nj;
+        } else if (early) {
+            const uint32_t nj = rt.top_k + (rt.shared_page ? 1u : 0u);
+            if (rt.shared_page) {
+                Job jb;
+                jb.page = rt.shared_page;
+                jb.kind = rt.shared_kind;
+                jb.token = 0;
+                jb.weight = 1.0f;
+                jb.is_shared = 1;
+                jb.out_index = rt.top_k;
+                s_jobs[0] = jb;
+                s_n_static = 1;
+            }
+            s_n_jobs = nj;
+        }
+        if (early) s_n_items = min(layer_work_list(cta, grid, s_n_jobs, S, RT, KU, KD, s_items, kMaxItems), kMaxItems);
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
     if (warp == kMmaWarp0) {
@@ -436,6 +578,46 @@ k_moe_layer_umma(const JobTable *__restrict__ dev_table, const __grid_constant__
     __syncthreads();
     fence_after();
     const uint32_t tmem = tmem_slot;
+    if (tid == 0) mark(2);
+
+    // ---- the copying thread: the units of the CTA's items in order, each one bulk copy of 16 KB of
+    // codes and one of 1 KB of scales into the next ring slot ----
+    uint32_t p_units = 0, p_item = 0, p_unit = 0;  // state of the copying thread
+    bool p_ok = true;
+    auto produce = [&](bool static_only) {
+        const uint32_t n_items = s_n_items, n_static = s_n_static;
+        while (p_ok && p_item < n_items) {
+            const uint32_t item = s_items[p_item], j = (item >> 8) & 0xFFu, idx = item & 0xFFu;
+            if (static_only && (j >= n_static || p_units >= ring)) return;
+            const uint8_t *page = s_jobs[j].page;
+            const bool down = (item & kItemDown) != 0u;
+            const uint32_t nu = down ? KD : KU;
+            const uint8_t *a0 = page + (down ? mxfp4_down_offset(hidden, inter) : 0u) + (size_t)idx * nu * kUnitBytes;
+            const uint8_t *sf0 = page + (down ? mxfp4_s2_offset(hidden, inter) + (size_t)idx * (inter >> 7) * kAtomBytes
+                                              : mxfp4_s13_offset(hidden, inter) + (size_t)idx * (hidden >> 7) * kAtomBytes);
+            while (p_unit < nu) {
+                if (static_only && p_units >= ring) return;
+                const uint32_t s = p_units % ring;
+                if (p_units >= ring && !mbar_wait(bar(kBarDone + s), ((p_units / ring) - 1u) & 1u, abortp)) {
+                    p_ok = false;
+                    return;
+                }
+                const uint32_t dst = smem_u32(sRing + s * kSlot), full = bar(kBarFull + s);
+                mbar_arrive_expect(full, kSlot);
+                bulk_copy(dst, a0 + (size_t)p_unit * kUnitBytes, kUnitBytes, full);
+                bulk_copy(dst + kUnitBytes, sf0 + (size_t)p_unit * kUnitSf, kUnitSf, full);
+                ++p_unit;
+                ++p_units;
+            }
+            p_unit = 0;
+            ++p_item;
+        }
+    };
+    const bool is_producer = tid == kProdWarp * 32u;
+    if (is_producer && early) {
+        produce(true);
+        mark(3);
+    }
 
     cudaGridDependencySynchronize();
     const uint32_t ep_step = ep_on ? __ldcg(ep.step) : 0u;
@@ -445,14 +627,15 @@ k_moe_layer_umma(const JobTable *__restrict__ dev_table, const __grid_constant__
         xs[0] = p0.x, xs[1] = p0.y, xs[2] = p0.z, xs[3] = p0.w;
         xs[4] = p1.x, xs[5] = p1.y, xs[6] = p1.z, xs[7] = p1.w;
     }
+    if (tid == 0) mark(4);
 
     if (routes_here) {
         // ---- expert scores: logit = x . w in double (warp sums, then the sixteen warps in order),
         // rounded to F32; score and score + bias go to global memory, then the CTA counts itself ----
-        double *s_red = reinterpret_cast<double *>(smem);  // [slot][warp]; the ring is not in use yet
+        double *s_red = reinterpret_cast<double *>(sBh);  // [slot][warp]; no digit tile is in use yet
 #pragma unroll
         for (uint32_t k = 0; k < kRouterSlots; ++k) {
-            if (blockIdx.x + k * gridDim.x >= rt.n_experts) break;
+            if (cta + k * grid >= rt.n_experts) break;
             const uint32_t wd[4] = {rq[k].x, rq[k].y, rq[k].z, rq[k].w};
             double acc0 = 0.0, acc1 = 0.0;
 #pragma unroll
@@ -464,8 +647,8 @@ k_moe_layer_umma(const JobTable *__restrict__ dev_table, const __grid_constant__
             if (lane == 0) s_red[k * (kThreads / 32u) + warp] = ws;
         }
         __syncthreads();
-        if (tid < kRouterSlots && blockIdx.x + tid * gridDim.x < rt.n_experts) {
-            const uint32_t e = blockIdx.x + tid * gridDim.x;
+        if (tid < kRouterSlots && cta + tid * grid < rt.n_experts) {
+            const uint32_t e = cta + tid * grid;
             double sum = 0.0;
             for (uint32_t w = 0; w < kThreads / 32u; ++w) sum += s_red[tid * (kThreads / 32u) + w];
             const float sc = router_score_f32(sum, rt.score_fn);
@@ -474,421 +657,371 @@ k_moe_layer_umma(const JobTable *__restrict__ dev_table, const __grid_constant__
         }
         __threadfence();
         __syncthreads();
-        if (tid == 0) atomicAdd(counters + kRouteCounter, 1u);
+        if (tid == 0) {
+            atomicAdd(counters + kCntRoute, 1u);
+            mark(5);
+        }
     }
 
     // the token's digits (they do not depend on the routes)
     if (has_x) digits_of8(xs, tid, sBx, sE);
     __syncthreads();  // every block exponent is written
-    if (warp < 2u * kEpiGroup / 32u) {
-        store_digit_scales(tmem + kColSfbX, sE, hidden, warp, lane);
+    if (warp < 8u) {
+        store_digit_scales(tmem + kColSfbX, sE, hidden, warp & 3u, warp >> 2, 2u, lane);
         fence_before();
         mbar_arrive(bar(kBarXReady));
     }
-    const uint32_t grid = gridDim.x, cta = blockIdx.x;
+    if (tid == 0) mark(6);
     if (routes_here) {
         // every CTA's scores are needed: all CTAs are resident (one per SM), the wait is bounded
         if (tid == 0) {
             uint32_t tries = 0;
-            while (ld_acquire(counters + kRouteCounter) < grid) {
+            while (ld_acquire(counters + kCntRoute) < grid) {
                 if (++tries > kSpinGlobal) {
                     abort_flag = 1;
                     break;
                 }
                 __nanosleep(40);
             }
+            mark(7);
         }
         __syncthreads();
-        if (warp == 0 && !abort_flag) route_select(rt, lane, cta == 0, s_jobs, &s_n_jobs, s_mix_w, s_mix_job, s_route_w);
-        if (tid == 0 && abort_flag) s_n_jobs = 0;
-    } else {
-        const JobTable &tab = table_of(dev_table, param_table);
-        const uint32_t nj = min(tab.token_job_begin[1] - tab.token_job_begin[0], (uint32_t)S14_EXPERTS_PER_TOKEN + 1u);
-        if (tid < min(tab.n_jobs, (uint32_t)S14_EXPERTS_PER_TOKEN + 1u)) s_jobs[tid] = tab.jobs[tid];
-        if (tid < nj) {
-            const uint32_t jb = tab.token_jobs[tab.token_job_begin[0] + tid];  // the job table may live in global memory
+        if (warp == 0 && !abort_flag) {
+            route_select(rt, lane, cta == 0, s_jobs, &s_n_jobs, s_mix_w, s_mix_slot, &s_n_mix);
+            if (lane == 0 && !early)
+                s_n_items = min(layer_work_list(cta, grid, s_n_jobs, S, RT, KU, KD, s_items, kMaxItems), kMaxItems);
+        }
+        if (tid == 0 && abort_flag) s_n_items = 0;
+    } else if (!table_param) {
+        const JobTable &tab = *dev_table;
+        const uint32_t nj = min(tab.n_jobs, kJobsMax);
+        const uint32_t m0 = tab.token_job_begin[0], nm = min(tab.token_job_begin[1] - m0, kJobsMax);
+        if (tid < nj) s_jobs[tid] = tab.jobs[tid];
+        if (tid < nm) {
+            const uint32_t jb = tab.token_jobs[m0 + tid];
             s_mix_w[tid] = tab.jobs[jb].weight;
-            s_mix_job[tid] = jb | (tab.jobs[jb].is_shared ? 0x80000000u : 0u);
+            s_mix_slot[tid] = tab.jobs[jb].out_index | (tab.jobs[jb].is_shared ? 0x80000000u : 0u);
         }
-        if (tid == 0) s_n_jobs = min(tab.n_jobs, (uint32_t)S14_EXPERTS_PER_TOKEN + 1u);
+        if (tid == 0) {
+            s_n_jobs = nj;
+            s_n_mix = nm;
+            s_n_items = min(layer_work_list(cta, grid, nj, S, RT, KU, KD, s_items, kMaxItems), kMaxItems);
+        }
     }
-    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");  // the digit tiles are read by the tensor cores
+    fence_async_smem();  // the digit tile is read by the tensor cores
     __syncthreads();
-    const uint32_t n_jobs = s_n_jobs, n_items = n_jobs * S;
-    // items are dealt in equal shares; with more CTAs than items the last CTAs have none
-    const uint32_t G = min(grid, n_items);
-    const uint32_t q0 = cta < G ? (uint32_t)((uint64_t)n_items * cta / G) : 0u;
-    const uint32_t q1 = cta < G ? (uint32_t)((uint64_t)n_items * (cta + 1u) / G) : 0u;
-    const uint32_t n_it = min(q1 - q0, kItemSlots);  // the launcher keeps the share within kItemSlots
-    const uint32_t nU = n_it * KU, nD = n_it * DS;
+    const uint32_t n_jobs = s_n_jobs, n_items = s_n_items;
+    if (tid == 0) {
+        mark(8);
+        if (tr) tr[15] = n_items | (ring << 8) | (n_jobs << 16);
+    }
 
-    if (is_producer && n_it) {
-        // ---- copies: the up units of every item, then the down stages of every item ----
-        const uint32_t pt = tid - kProdWarp0 * 32u, r8 = pt >> 3, cc = pt & 7u;
-        const uint32_t dst_up = smem_u32(sA) + r8 * 128u + ((cc ^ (r8 & 7u)) << 4);
-        bool ok = true;
-        uint32_t i = 0;
-        for (uint32_t l = 0; l < n_it && ok; ++l) {
-            const uint32_t q = q0 + l, j = q / S, sl = q - j * S;
-            const PageView pv = page_view(s_jobs[j].page, S14_PAGE_MXFP4, hidden, inter);
-            // rows r8, r8 + 16, ... of the tile: the first four are w1 rows of the slice, the last four w3 rows
-            const uint8_t *src1 = pv.w1 + (size_t)(sl * 64u + r8) * (hidden >> 1) + cc * 16u;
-            const uint8_t *src3 = pv.w3 + (size_t)(sl * 64u + r8) * (hidden >> 1) + cc * 16u;
-            const uint8_t *sf = pv.s1 + (size_t)sl * RT * 512u + pt * 16u;
-            for (uint32_t ks = 0; ks < KU; ++ks, ++i) {
-                const uint32_t s = i % kRing;
-                if (i >= kRing && !mbar_wait(bar(kBarDone + s), ((i / kRing) - 1u) & 1u, &abort_flag)) {
-                    ok = false;
-                    break;
+    if (is_producer) {
+        produce(false);  // every page address is known now
+        mark(12);
+    } else if ((warp == kMmaWarp0 || warp == kMmaWarp0 + 1u) && lane == 0) {
+        // ---- MMA issue.  Issuing a tcgen05 operation costs the thread 70-90 cycles (measured), more
+        // than a 16 KB unit may take, so two threads issue: thread m takes units m, m + 2, ... of every
+        // item (every item has an even number of units and the ring an even number of slots, so a slot
+        // always belongs to the same thread, which sees each phase of its barrier) and accumulates
+        // into an accumulator of its own.  Items alternate between two accumulator buffers. ----
+        const uint32_t m = warp - kMmaWarp0;
+        const uint64_t a_desc0 = smem_desc(smem_u32(sRing), 1, 64, 2);
+        const uint64_t sf_desc0 = smem_desc(smem_u32(sRing) + kUnitBytes, 0, 8, 0);
+        const uint64_t bx_desc0 = smem_desc(smem_u32(sBx), 1, 64, 2);
+        const uint32_t sfa_t = tmem + kColSfa + m * 16u;  // a thread's copies and MMAs execute in issue order
+        bool ok = n_items == 0u || mbar_wait(bar(kBarXReady), 0, abortp);
+        uint32_t g0 = 0, n_loaded = 0, cur_job = 0xFFFFFFFFu, hb = 0;
+        for (uint32_t i = 0; i < n_items && ok; ++i) {
+            const uint32_t item = s_items[i], j = (item >> 8) & 0xFFu, buf = i & 1u;
+            const bool down = (item & kItemDown) != 0u;
+            const uint32_t nu = down ? KD : KU;
+            if (i >= 2u) ok = mbar_wait(bar(kBarAccFree + buf), ((i - 2u) >> 1) & 1u, abortp);
+            uint64_t b_desc0 = bx_desc0;
+            uint32_t sfb0 = tmem + kColSfbX;
+            bool last_user = false;
+            if (down) {
+                if (j != cur_job) {
+                    hb = n_loaded & 1u;
+                    ok = ok && mbar_wait(bar(kBarHReady + hb), (n_loaded >> 1) & 1u, abortp);
+                    cur_job = j;
+                    ++n_loaded;
                 }
-                const uint32_t dst = dst_up + s * kStageA;
-#pragma unroll
-                for (uint32_t i8 = 0; i8 < 4; ++i8) {
-                    cp_async16(dst + i8 * 2048u, src1 + (size_t)i8 * 16u * (hidden >> 1) + ks * 128u);
-                    cp_async16(dst + (i8 + 4u) * 2048u, src3 + (size_t)i8 * 16u * (hidden >> 1) + ks * 128u);
-                }
-                // the unit's two scale atoms are 1 KB of consecutive page bytes
-                if (pt < 64u) cp_async16(smem_u32(sSF + s * kStageSf) + pt * 16u, sf + (size_t)ks * 1024u);
-                mbar_arrive_after_copies(bar(kBarFull + s));
+                b_desc0 = smem_desc(smem_u32(sBh + hb * tile_bytes), 1, 64, 2);
+                sfb0 = tmem + kColSfbH + hb * 128u;
+                last_user = i + 1u >= n_items || ((s_items[i + 1u] >> 8) & 0xFFu) != j;
             }
-        }
-        for (uint32_t l = 0; l < n_it && ok; ++l) {
-            const uint32_t q = q0 + l, j = q / S, sl = q - j * S;
-            const PageView pv = page_view(s_jobs[j].page, S14_PAGE_MXFP4, hidden, inter);
-            const uint8_t *wsrc = pv.w2 + (size_t)sl * RT * 4096u + pt * 16u;        // the slice's columns, 4 KB per row tile
-            const uint8_t *sf = pv.s2 + (size_t)(sl >> 1) * RT * 512u + pt * 16u;   // the slice pair's atoms
-            for (uint32_t v = 0; v < DS; ++v, ++i) {
-                const uint32_t s = i % kRing;
-                if (i >= kRing && !mbar_wait(bar(kBarDone + s), ((i / kRing) - 1u) & 1u, &abort_flag)) {
-                    ok = false;
-                    break;
-                }
-                const uint32_t dst = smem_u32(sA + s * kStageA);
-#pragma unroll
-                for (uint32_t i8 = 0; i8 < 8; ++i8) {
-                    // piece id: block id / 256, row (id % 256) / 2, half id % 2 -> 8-row x 16-byte core matrices
-                    const uint32_t id = pt + i8 * 128u, r = (id & 255u) >> 1;
-                    cp_async16(dst + (id >> 8) * 4096u + (r >> 3) * 256u + (id & 1u) * 128u + (r & 7u) * 16u,
-                               wsrc + (size_t)v * 16384u + i8 * 2048u);
-                }
-                cp_async16(smem_u32(sSF + s * kStageSf) + pt * 16u, sf + (size_t)v * 2048u);
-                mbar_arrive_after_copies(bar(kBarDFull + s));
-            }
-        }
-        asm volatile("cp.async.wait_all;" ::: "memory");
-    } else if ((warp == kMmaWarp0 || warp == kMmaWarp0 + 1u || warp >= 14u) && n_it) {
-        if (lane == 0) {
-            // ---- MMA issue.  Issuing a tcgen05 operation costs the thread 70-90 cycles (measured), more
-            // than a 16 KB stage may take once it has up to ten of them, so four threads issue.  Thread 0
-            // issues the up units (one accumulator per item, in order); the down stages have
-            // accumulators of their own and go round the four threads.  The down stages use ring-slot
-            // barriers of their own, so each thread sees every phase of the barriers it waits on. ----
-            const uint32_t m = warp < 14u ? warp - kMmaWarp0 : warp - 12u;
-            const uint64_t a_up0 = smem_desc(smem_u32(sA), 1, 64, 2), b_x0 = smem_desc(smem_u32(sBx), 1, 64, 2);
-            const uint64_t sf_desc0 = smem_desc(smem_u32(sSF), 0, 8, 0);
-            const uint32_t sfa_t = tmem + kColSfa + m * 16u;  // a thread's copies and MMAs execute in issue order
-            bool ok = true;
-            if (m < 2u) {
-                // up units: threads 0 and 1 take the even and the odd ones (hidden / 256 is even, so the
-                // parity of a unit is the parity of its ring slot) and accumulate into accumulators of their own
-                ok = mbar_wait(bar(kBarXReady), 0, &abort_flag);
-                for (uint32_t l = 0; l < n_it && ok; ++l) {
-                    // the two up accumulators serve one item at a time
-                    if (l >= 1u) ok = mbar_wait(bar(kBarUFree), (l - 1u) & 1u, &abort_flag);
-                    const uint32_t acc = tmem + kColU + m * 16u;
-                    for (uint32_t ks = m; ks < KU && ok; ks += 2u) {
-                        const uint32_t i = l * KU + ks, s = i % kRing;
-                        ok = mbar_wait(bar(kBarFull + s), (i / kRing) & 1u, &abort_flag);
-                        if (!ok) break;
-                        fence_after();
-                        const uint32_t sfb_t = tmem + kColSfbX + ks * 8u;
-                        const uint64_t sfd = sf_desc0 + s * (kStageSf >> 4);
-                        tmem_copy_scales(sfa_t, sfd);
-                        tmem_copy_scales(sfa_t + 4u, sfd + (512u >> 4));
-                        const uint64_t ad = a_up0 + s * (kStageA >> 4), bd = b_x0 + ks * (2048u >> 4);
-#pragma unroll
-                        for (uint32_t kk = 0; kk < 4; ++kk) {
-                            const uint32_t atom = kk >> 1, sfid = (kk & 1u) * 2u;
-                            umma_mxf4(acc, ad + kk * 2u, bd + kk * 2u, kIdesc | (sfid << 29) | (sfid << 4),
-                                      (sfa_t + atom * 4u) | (sfid << 30), (sfb_t + atom * 4u) | (sfid << 30),
-                                      (ks >= 2u || kk) ? 1u : 0u);
-                        }
-                        umma_commit(bar(kBarDone + s));
-                        if (ks + 2u >= KU) umma_commit(bar(kBarUDone));
-                    }
-                }
-            }
-            {
-                // Down stage vg sits in ring slot s = (nU + vg) % kRing and belongs to the issuing thread and
-                // accumulator set s % 4, so that every slot's barrier has one waiting thread, which sees
-                // each of its phases; j counts this thread's down stages (the phases of its own barriers).
-                uint32_t j = 0;
-                for (uint32_t vg = 0; vg < nD && ok; ++vg) {
-                    const uint32_t s = (nU + vg) % kRing;
-                    if ((s & 3u) != m) continue;
-                    const uint32_t l = vg / DS, sl = (q0 + l) % S, asf = (sl & 1u) * 2u;
-                    ok = mbar_wait(bar(kBarHReady + l), 0, &abort_flag);
-                    ok = ok && mbar_wait(bar(kBarDFull + s), (vg / kRing) & 1u, &abort_flag);
-                    ok = ok && (j == 0u || mbar_wait(bar(kBarDFree + m), (j - 1u) & 1u, &abort_flag));
-                    if (!ok) break;
-                    ++j;
-                    fence_after();
-                    const uint64_t sfd = sf_desc0 + s * (kStageSf >> 4);
-                    const uint64_t bd = smem_desc_k64(smem_u32(sBh + l * 512u));
-                    const uint64_t ad = smem_desc_k64(smem_u32(sA + s * kStageA));
-#pragma unroll
-                    for (uint32_t b = 0; b < 4; ++b) tmem_copy_scales(sfa_t + b * 4u, sfd + b * (512u >> 4));
-#pragma unroll
-                    for (uint32_t b = 0; b < 4; ++b)
-                        umma_mxf4(tmem + kColD + m * 64u + b * 16u, ad + b * (4096u >> 4), bd, kIdesc | (asf << 29),
-                                  (sfa_t + b * 4u) | (asf << 30), tmem + kColSfbH + l * 4u, 0u);
-                    umma_commit(bar(kBarDone + s));
-                    umma_commit(bar(kBarDDone + m));
-                }
-            }
-            // nothing of this CTA's tensor work is in flight when the tensor memory is freed
-            umma_commit(bar(kBarFin));
-            mbar_wait(bar(kBarFin), 0, &abort_flag);
-        }
-    } else if (warp < 2u * kEpiGroup / 32u && n_it) {
-        // ---- epilogue: group A (warps 0-3) turns the up accumulators into hidden digits, then both
-        // groups read the down accumulators (alternate stages) ----
-        const uint32_t grp = warp >> 2, row = tid & (kEpiGroup - 1u);
-        const uint32_t lane_base = tmem + (((warp & 3u) * 32u) << 16);
-        bool ok = true;
-        if (grp == 0u) {
-            for (uint32_t l = 0; l < n_it; ++l) {
-                const uint32_t q = q0 + l, j = q / S;
-                ok = __all_sync(0xffffffffu, ok && mbar_wait(bar(kBarUDone), l & 1u, &abort_flag));
-                float v = 0.0f;
-                if (ok) {
-                    fence_after();
-                    uint32_t a[8], b[8];  // even and odd units of the item
-                    tmem_ld8(lane_base + kColU, a);
-                    tmem_ld8(lane_base + kColU + 16u, b);
-                    tmem_ld_wait();
-                    fence_before();
-                    mbar_arrive(bar(kBarUFree));
-                    // Digit columns, low digits first, each column about eight times the one before: plain F32
-                    // additions lose a few 2^-24 of the result, below the 23-bit digits of what follows.
-                    float sa = 0.0f, sb = 0.0f;
-#pragma unroll
-                    for (int jj = 0; jj < 8; ++jj) {
-                        sa = __fadd_rn(sa, __uint_as_float(a[jj]));
-                        sb = __fadd_rn(sb, __uint_as_float(b[jj]));
-                    }
-                    v = __fadd_rn(sa, sb);
-                }
-                if (row >= 64u) s_up[row - 64u] = v;
-                group_bar_sync();
-                (void)j;
-                if (row < 64u) {
-                    // hidden value `row` of the slice -> eight digit nibbles, scale block = warp
-                    const float hv = swiglu_limit_fast(v, s_up[row]);
-                    float bm = fabsf(hv);
-#pragma unroll
-                    for (int o = 16; o > 0; o >>= 1) bm = fmaxf(bm, __shfl_xor_sync(0xffffffffu, bm, o));
-                    int E = -100;
-                    if (bm > 0.0f) E = min(max((int)((__float_as_uint(bm) >> 23) & 0xFFu) - 126, -100), 127);
-                    const uint32_t qb = (uint32_t)(__float2int_rn(hv * __uint_as_float((uint32_t)(150 - E) << 23)) + 0x924924);
-                    uint32_t word = 0;
-#pragma unroll
-                    for (int jj = 0; jj < 7; ++jj) word |= ((0x5420ACDEu >> (((qb >> (3 * jj)) & 7u) << 2)) & 0xFu) << (4 * jj);
-                    const uint32_t top = qb >> 21;
-                    word |= (top > 7u ? 6u : ((0x5420ACDEu >> (top << 2)) & 0xFu)) << 28;
-                    const uint32_t other = __shfl_xor_sync(0xffffffffu, word, 1);
-                    const uint32_t lo_w = (lane & 1u) ? other : word, hi_w = (lane & 1u) ? word : other;
-                    uint8_t *chunk = sBh + l * 512u + warp * 128u + (lane >> 1);  // K half = scale block = warp
-#pragma unroll
-                    for (uint32_t jj = 0; jj < 4; ++jj) {
-                        const uint32_t dj = (lane & 1u) * 4u + jj;  // digit row
-                        chunk[dj * 16u] = (uint8_t)(((lo_w >> (4u * dj)) & 0xFu) | (((hi_w >> (4u * dj)) & 0xFu) << 4));
-                    }
-                    if (lane == 0) sEh[l][warp] = (uint8_t)(E + 100);
-                }
-                group_bar_sync();
-                {
-                    // scale codes of the eight digit rows for the slice's two blocks (blocks 2, 3 unused)
-                    const uint32_t bias = 4u + 3u * (lane & 7u);
-                    const uint32_t w0 = lane < 8u ? ((sEh[l][0] + bias) | ((sEh[l][1] + bias) << 8) | 0x7F7F0000u) : 0x7F7F7F7Fu;
-                    const uint32_t one = 0x7F7F7F7Fu;
-                    asm volatile("tcgen05.st.sync.aligned.32x32b.x4.b32 [%0], {%1,%2,%2,%2};" ::"r"(lane_base + kColSfbH + l * 4u),
-                                 "r"(w0), "r"(one)
-                                 : "memory");
-                    asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
-                }
-                asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
-                fence_before();
-                mbar_arrive(bar(kBarHReady + l));
-            }
-        }
-        uint32_t seen_lo = 0, seen_hi = 0;  // down stages of the group's two accumulator sets so far
-        for (uint32_t vg = 0; vg < nD; ++vg) {
-            const uint32_t acc = ((nU + vg) % kRing) & 3u;  // the stage's issuing thread and accumulator set
-            if ((acc & 1u) != grp) continue;                // sets 0, 2: group A; sets 1, 3: group B
-            const uint32_t j = (acc & 2u) ? seen_hi++ : seen_lo++;
-            const uint32_t l = vg / DS, vloc = vg - l * DS, q = q0 + l;
-            // every phase of this barrier is waited for by this group, in order
-            ok = __all_sync(0xffffffffu, ok && mbar_wait(bar(kBarDDone + acc), j & 1u, &abort_flag));
             if (!ok) break;
             fence_after();
-            uint32_t a[4][8];
+            const uint32_t acc = tmem + kColAcc + (buf * 2u + m) * 16u;
+            for (uint32_t ku = m; ku < nu; ku += 2u) {
+                const uint32_t gu = g0 + ku, s = gu % ring;
+                ok = mbar_wait(bar(kBarFull + s), (gu / ring) & 1u, abortp);
+                if (!ok) break;
+                if (ku == 0u) mark(16u + i * 4u);
+                fence_after();
+                const uint64_t sfd = sf_desc0 + s * (kSlot >> 4);
+                tmem_copy_scales(sfa_t, sfd);
+                tmem_copy_scales(sfa_t + 4u, sfd + (kAtomBytes >> 4));
+                const uint64_t ad = a_desc0 + s * (kSlot >> 4), bd = b_desc0 + ku * (2048u >> 4);
+                const uint32_t sfb_t = sfb0 + ku * 8u;
 #pragma unroll
-            for (uint32_t b = 0; b < 4; ++b) tmem_ld8(lane_base + kColD + acc * 64u + b * 16u, a[b]);
-            tmem_ld_wait();
-            fence_before();
-            mbar_arrive(bar(kBarDFree + acc));  // the accumulators are in registers: the next stage may overwrite them
-            float out[4];
-#pragma unroll
-            for (uint32_t b = 0; b < 4; ++b) {  // low digits first; the share is kept as one F32 anyway
-                float sum = 0.0f;
-#pragma unroll
-                for (int jj = 0; jj < 8; ++jj) sum = __fadd_rn(sum, __uint_as_float(a[b][jj]));
-                out[b] = sum;
-            }
-            // the item's share of rows (4 vloc + b) * 128 + row of its expert's output
-            float *p = part + (size_t)q * hidden + (size_t)vloc * 512u + row;
-#pragma unroll
-            for (uint32_t b = 0; b < 4; ++b) p[b * 128u] = out[b];
-        }
-    }
-
-    // ---- every item's share is in global memory: count the CTA's items, wait for all of them ----
-    __threadfence();
-    fence_before();
-    __syncthreads();
-    if (warp == kMmaWarp0) {
-        __syncwarp();
-        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(kTmemCols) : "memory");
-    }
-    if (tid == 0) {
-        if (n_it) atomicAdd(counters + kItemCounter, abort_flag ? 0u : n_it);
-        uint32_t tries = 0;
-        while (!abort_flag && ld_acquire(counters + kItemCounter) < n_items) {
-            if (++tries > kSpinGlobal) abort_flag = 1;
-            __nanosleep(100);
-        }
-        if (abort_flag) atomicExch(status, 0x5501u);
-    }
-    __syncthreads();
-    if (!abort_flag) {
-        // ---- rows [n0, n1) of this CTA: expert outputs as sums over slices in slice order, then the
-        // ordered mix (examples/s14_vulkan_numeric.rs:936-946): acc = 0; acc += w * d in route order;
-        // acc += d_shared.  Scratch: the ring's shared memory. ----
-        const uint32_t n0 = (uint32_t)((uint64_t)hidden * cta / grid), n1 = (uint32_t)((uint64_t)hidden * (cta + 1u) / grid);
-        const uint32_t rows = n1 - n0, chunks = S >> 2;
-        // sums as (hi, lo) pairs of F32 with error-free additions: FP64 is scarce on this GPU
-        float2 *red = reinterpret_cast<float2 *>(smem);                        // [job][chunk][row]
-        float *dj = reinterpret_cast<float *>(smem + (size_t)n_jobs * chunks * rows * 8u);  // [job][row]
-        for (uint32_t t0 = tid; t0 < n_jobs * chunks * rows; t0 += 4u * kThreads) {
-            float v[4][4];  // four tasks at a time, so that sixteen loads are in flight per thread
-#pragma unroll
-            for (uint32_t k = 0; k < 4; ++k) {
-                const uint32_t t = min(t0 + k * kThreads, n_jobs * chunks * rows - 1u);
-                const uint32_t r = t % rows, jc = t / rows;  // jc = job * chunks + chunk: four slices of one job
-                const float *p = part + (size_t)jc * 4u * hidden + n0 + r;
-#pragma unroll
-                for (uint32_t c = 0; c < 4; ++c) v[k][c] = __ldcg(p + (size_t)c * hidden);
-            }
-#pragma unroll
-            for (uint32_t k = 0; k < 4; ++k) {
-                const uint32_t t = t0 + k * kThreads;
-                float hi = v[k][0], lo = 0.0f, e;
-#pragma unroll
-                for (uint32_t c = 1; c < 4; ++c) {
-                    two_sum(hi, v[k][c], hi, e);
-                    lo = __fadd_rn(lo, e);
+                for (uint32_t kk = 0; kk < 4; ++kk) {
+                    const uint32_t atom = kk >> 1, sfid = (kk & 1u) * 2u;
+                    umma_mxf4(acc, ad + kk * 2u, bd + kk * 2u, kIdesc | (sfid << 29) | (sfid << 4),
+                              (sfa_t + atom * 4u) | (sfid << 30), (sfb_t + atom * 4u) | (sfid << 30),
+                              (ku >= 2u || kk) ? 1u : 0u);
                 }
-                if (t < n_jobs * chunks * rows) red[t] = make_float2(hi, lo);
+                umma_commit(bar(kBarDone + s));
             }
+            if (!ok) break;
+            umma_commit(bar(kBarAccDone + buf));
+            if (down && last_user) umma_commit(bar(kBarHFree + hb));
+            g0 += nu;
         }
-        __syncthreads();
-        for (uint32_t t = tid; t < n_jobs * rows; t += kThreads) {
-            const uint32_t r = t % rows, j = t / rows;
-            float hi = 0.0f, lo = 0.0f, e;
-            for (uint32_t c = 0; c < chunks; ++c) {  // slice order
-                const float2 pr = red[((size_t)j * chunks + c) * rows + r];
-                two_sum(hi, pr.x, hi, e);
-                lo = __fadd_rn(lo, __fadd_rn(e, pr.y));
-            }
-            const float v = __fadd_rn(hi, lo);
-            dj[t] = v;
-            if (ep_on) {
-                // the expert's rows of this CTA go to the route slot's row in every rank's slot buffer,
-                // each value with the step's number in one 8-byte store
-                const size_t at = ((size_t)(ep_step & 1u) * ep.n_slots + s_jobs[j].out_index) * hidden + n0 + r;
-                const unsigned long long word = ((unsigned long long)(ep_step + 1u) << 32) | __float_as_uint(v);
-                for (uint32_t p = 0; p < ep.world; ++p) st_relaxed_sys(ep.slots[p] + at, word);
-            } else if (!y) {
-                d_out[(size_t)s_jobs[j].out_index * hidden + n0 + r] = v;  // the caller mixes
-            }
-        }
-        __syncthreads();
-        if (ep_on) {
-            // ---- exchange: rows [n0, n1) of every slot arrive in this rank's own buffer from the CTA of
-            // the same number on the slot's owner; a thread polls (bounded) one word until it carries
-            // this step's number, then the rows are mixed in route order, the shared expert last ----
-            if (ep.wait_and_mix) {
-                float *sv = dj;  // [slot][row]; the experts' sums are not needed any more
-                for (uint32_t t = tid; t < ep.n_slots * rows; t += kThreads) {
-                    const uint32_t r = t % rows, jj = t / rows;
-                    const unsigned long long *w =
-                        ep.slots[ep.rank] + ((size_t)(ep_step & 1u) * ep.n_slots + jj) * hidden + n0 + r;
-                    unsigned long long got = ld_relaxed_sys(w);
+        // nothing of this CTA's tensor work is in flight when the tensor memory is freed
+        umma_commit(bar(kBarFin));
+        mbar_wait(bar(kBarFin), 0, abortp);
+    } else if (warp < kEpiThreads / 32u) {
+        // ---- epilogue: the item's two accumulators (sixteen digit columns each) are added in double
+        // and rounded once ----
+        const uint32_t row = tid;
+        const uint32_t lane_base = tmem + ((warp * 32u) << 16);
+        bool ok = true;
+        if (ep_on && n_items) {
+            // A slot buffer may be written for step s only when every peer has finished reading step
+            // s - 2 from it: each rank tells every other rank the number of steps it has finished
+            // (one 8-byte word per rank in the exchange buffer).
+            if (tid == 0) {
+                const unsigned long long *mine = ep.slots[ep.rank] + 2u * (size_t)(S14_EXPERTS_PER_TOKEN + 1) * hidden + 8u;
+                for (uint32_t p = 0; p < ep.world && ok; ++p) {
+                    if (p == ep.rank) continue;
                     uint32_t tries = 0;
-                    // A word with an earlier step's number is waited for.  One with a LATER number means that a
-                    // peer gave up on this rank and ran ahead: the words this rank still misses belong to
-                    // steps its peers have left behind and would never come, so it reports that, waits for
-                    // nothing more in this step and runs at full speed until it is level again.
-                    while ((int32_t)((uint32_t)(got >> 32) - (ep_step + 1u)) < 0) {
-                        if (s_behind) break;
+                    while ((int32_t)((uint32_t)ld_relaxed_sys(mine + p) - ep_step + 1u) < 0) {
                         if (++tries > ep.wait_limit || abort_flag) {
+                            ok = false;
+                            s_abort_code = 0x5505u;
                             abort_flag = 1;
                             break;
                         }
                         __nanosleep(100);
-                        got = ld_relaxed_sys(w);
                     }
-                    if ((int32_t)((uint32_t)(got >> 32) - (ep_step + 1u)) > 0) {
-                        s_behind = 1;
-                        atomicExch(status, 0x5504u);
-                    }
-                    sv[t] = __uint_as_float((uint32_t)got);
-                }
-                __syncthreads();
-                if (abort_flag) {
-                    if (tid == 0) atomicExch(status, 0x5503u);
-                } else if (y && tid < rows) {
-                    float acc = 0.0f;
-                    for (uint32_t jj = 0; jj < rt.top_k; ++jj)
-                        acc = __fadd_rn(acc, __fmul_rn(s_route_w[jj], sv[jj * rows + tid]));
-                    if (ep.n_slots > rt.top_k) acc = __fadd_rn(acc, sv[rt.top_k * rows + tid]);
-                    y[n0 + tid] = acc;
                 }
             }
-        } else if (y && tid < rows) {
-            float acc = 0.0f;
-            for (uint32_t jj = 0; jj < n_jobs; ++jj) {
-                const uint32_t jb = s_mix_job[jj];
-                const float dv = dj[(size_t)(jb & 0x7FFFFFFFu) * rows + tid];
-                acc = (jb >> 31) ? __fadd_rn(acc, dv) : __fadd_rn(acc, __fmul_rn(s_mix_w[jj], dv));
+            ok = epi_all(ok);
+        }
+        for (uint32_t i = 0; i < n_items && ok; ++i) {
+            const uint32_t item = s_items[i], j = (item >> 8) & 0xFFu, idx = item & 0xFFu, buf = i & 1u;
+            const bool down = (item & kItemDown) != 0u;
+            ok = epi_all(mbar_wait(bar(kBarAccDone + buf), (i >> 1) & 1u, abortp));
+            if (!ok) break;
+            if (tid == 0) mark(17u + i * 4u);
+            fence_after();
+            uint32_t a[16], b[16];  // even and odd units of the item
+            tmem_ld16(lane_base + kColAcc + (buf * 2u) * 16u, a);
+            tmem_ld16(lane_base + kColAcc + (buf * 2u + 1u) * 16u, b);
+            tmem_ld_wait();
+            fence_before();
+            mbar_arrive(bar(kBarAccFree + buf));
+            double sum = 0.0;
+#pragma unroll
+            for (int c = 15; c >= 8; --c) sum += (double)__uint_as_float(a[c]) + (double)__uint_as_float(b[c]);
+#pragma unroll
+            for (int c = 7; c >= 0; --c) sum += (double)__uint_as_float(a[c]) + (double)__uint_as_float(b[c]);
+            const float v = (float)sum;
+            if (!down) {
+                // lanes 0-63: gate of the slice's element `row`; lanes 64-127: its up projection
+                if (row >= 64u) s_up[row - 64u] = v;
+                epi_sync();
+                int E = -80;
+                if (row < 64u) {
+                    // hidden value `row` of the slice -> sixteen digit nibbles; scale block = warp
+                    const float hv = swiglu_limit_f32(v, s_up[row]);
+                    float bm = fabsf(hv);
+#pragma unroll
+                    for (int o = 16; o > 0; o >>= 1) bm = fmaxf(bm, __shfl_xor_sync(0xffffffffu, bm, o));
+                    E = block_exponent(bm);
+                    uint32_t hw, lw;
+                    digit_codes16(hv, __uint_as_float((uint32_t)(150 - E) << 23), hw, lw);
+                    const uint32_t ohw = __shfl_xor_sync(0xffffffffu, hw, 1), olw = __shfl_xor_sync(0xffffffffu, lw, 1);
+                    // byte lane / 2 of every row's chunk holds the nibbles of lanes 2b (low) and 2b + 1; even
+                    // lanes write digit rows 0-3 and 8-11, odd lanes 4-7 and 12-15
+                    const uint32_t e_hw = (lane & 1u) ? ohw : hw, o_hw = (lane & 1u) ? hw : ohw;
+                    const uint32_t e_lw = (lane & 1u) ? olw : lw, o_lw = (lane & 1u) ? lw : olw;
+#pragma unroll
+                    for (uint32_t jj = 0; jj < 4; ++jj) {
+                        const uint32_t dj = (lane & 1u) * 4u + jj;
+                        s_hst[(dj * 2u + warp) * 16u + (lane >> 1)] =
+                            (uint8_t)(((e_hw >> (4u * dj)) & 0xFu) | (((o_hw >> (4u * dj)) & 0xFu) << 4));
+                        s_hst[((8u + dj) * 2u + warp) * 16u + (lane >> 1)] =
+                            (uint8_t)(((e_lw >> (4u * dj)) & 0xFu) | (((o_lw >> (4u * dj)) & 0xFu) << 4));
+                    }
+                }
+                epi_sync();
+                uint8_t *tile = tiles + (size_t)j * kTileMax;
+                if (tid < 32u) {
+                    // chunk (digit row, block) of the slice -> its place in the job's digit tile
+                    const uint32_t dj = tid >> 1, blk = tid & 1u, cc = (idx & 3u) * 2u + blk;
+                    const uint4 c16 = *reinterpret_cast<const uint4 *>(s_hst + (dj * 2u + blk) * 16u);
+                    __stcg(reinterpret_cast<uint4 *>(tile + (idx >> 2) * 2048u + dj * 128u + ((cc ^ (dj & 7u)) << 4)), c16);
+                }
+                if (row < 64u && lane == 0) tile_exps[(size_t)j * kExpMax + idx * 2u + warp] = (uint8_t)(E + 100);
+                __threadfence();
+                epi_sync();
+                if (tid == 0) atomicAdd(counters + kCntJob0 + j, 1u);
+            } else {
+                // row idx * 128 + `row` of the expert's output
+                const uint32_t n = idx * 128u + row, slot = s_jobs[j].out_index;
+                if (ep_on) {
+                    // into the route slot's row of every rank's slot buffer, the value with the step's
+                    // number in one 8-byte store
+                    const size_t at = ((size_t)(ep_step & 1u) * ep.n_slots + slot) * hidden + n;
+                    const unsigned long long word = ((unsigned long long)(ep_step + 1u) << 32) | __float_as_uint(v);
+                    for (uint32_t p = 0; p < ep.world; ++p) st_relaxed_sys(ep.slots[p] + at, word);
+                } else {
+                    __stcg(d_out + (size_t)slot * hidden + n, v);
+                    if (y) {
+                        // ---- the last job of the row tile to finish applies the ordered mix
+                        // (examples/s14_vulkan_numeric.rs:936-946): acc = 0; acc += w * d in route order;
+                        // acc += d_shared ----
+                        __threadfence();
+                        epi_sync();
+                        if (tid == 0) s_last = atomicAdd(counters + kCntTile0 + idx, 1u) == n_jobs - 1u;
+                        epi_sync();
+                        if (s_last) {
+                            __threadfence();
+                            const uint32_t nm = s_n_mix;
+                            float acc = 0.0f;
+                            for (uint32_t jj = 0; jj < nm; ++jj) {
+                                const uint32_t ms = s_mix_slot[jj];
+                                const float dv = __ldcg(d_out + (size_t)(ms & 0x7FFFFFFFu) * hidden + n);
+                                acc = (ms >> 31) ? __fadd_rn(acc, dv) : __fadd_rn(acc, __fmul_rn(s_mix_w[jj], dv));
+                            }
+                            y[n] = acc;
+                        }
+                        epi_sync();  // s_last is read before the next item writes it
+                    }
+                }
             }
-            y[n0 + tid] = acc;
+            if (tid == 0) mark(18u + i * 4u);
+        }
+    } else if (warp >= kLoadWarp0) {
+        // ---- digit tiles of the down items: wait (bounded) until every slice of the job has been
+        // counted, then take the job's tile from global memory (L2) into one of two tile buffers
+        // and its scale codes into tensor memory ----
+        const uint32_t lt = tid - kLoadWarp0 * 32u;
+        uint32_t n_loaded = 0, cur_job = 0xFFFFFFFFu;
+        bool ok = true;
+        for (uint32_t i = 0; i < n_items && ok; ++i) {
+            const uint32_t item = s_items[i], j = (item >> 8) & 0xFFu;
+            if (!(item & kItemDown) || j == cur_job) continue;
+            const uint32_t hb = n_loaded & 1u;
+            bool mine = true;
+            if (lt == 0) {
+                if (n_loaded >= 2u) mine = mbar_wait(bar(kBarHFree + hb), ((n_loaded >> 1) - 1u) & 1u, abortp);
+                uint32_t tries = 0;
+                while (mine && ld_acquire(counters + kCntJob0 + j) < S) {
+                    if (++tries > kSpinGlobal || abort_flag) {
+                        abort_flag = 1;
+                        mine = false;
+                    }
+                    __nanosleep(100);
+                }
+            }
+            ok = load_all(mine);
+            if (!ok) break;
+            const uint8_t *src = tiles + (size_t)j * kTileMax;
+            uint8_t *dst = sBh + hb * tile_bytes;
+            for (uint32_t o = lt * 16u; o < tile_bytes; o += kLoadThreads * 16u)
+                *reinterpret_cast<uint4 *>(dst + o) = __ldcg(reinterpret_cast<const uint4 *>(src + o));
+            if (lt < (inter >> 7))
+                reinterpret_cast<uint32_t *>(sEh[hb])[lt] = __ldcg(reinterpret_cast<const uint32_t *>(tile_exps + (size_t)j * kExpMax) + lt);
+            fence_async_smem();
+            load_sync();
+            if (warp < kLoadWarp0 + 4u) {
+                store_digit_scales(tmem + kColSfbH + hb * 128u, sEh[hb], inter, warp & 3u, 0u, 1u, lane);
+                fence_before();
+            }
+            mbar_arrive(bar(kBarHReady + hb));
+            if (lt == 0) mark(19u + i * 4u);
+            cur_job = j;
+            ++n_loaded;
         }
     }
+
+    // ---- the CTA's items are done (or given up) ----
+    if (is_producer) {
+        // copies in flight land in this CTA's shared memory: wait for them before leaving
+        const uint32_t first = p_units > ring ? p_units - ring : 0u;
+        for (uint32_t u = first; u < p_units; ++u) {
+            const uint32_t s = u % ring, parity = (u / ring) & 1u;
+            uint32_t tries = 0;
+            while (!mbar_try(bar(kBarFull + s), parity) && ++tries < kSpin) {
+            }
+        }
+    }
+    fence_before();
+    __syncthreads();
+    if (tid == 0) mark(13);
+    if (warp == kMmaWarp0) {
+        __syncwarp();
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(kTmemCols) : "memory");
+    }
+    if (ep_on && ep.wait_and_mix && cta < RT && tid < kEpiThreads && !abort_flag) {
+        // ---- exchange: row tile `cta` of every slot arrives in this rank's own buffer from the slot's
+        // owner; a thread polls (bounded) one word per slot until it carries this step's number, then
+        // the row is mixed in route order, the shared expert last ----
+        const uint32_t n = cta * 128u + tid;
+        float acc = 0.0f;
+        bool ok = true;
+        for (uint32_t jj = 0; jj < ep.n_slots && ok; ++jj) {
+            const unsigned long long *w = ep.slots[ep.rank] + ((size_t)(ep_step & 1u) * ep.n_slots + jj) * hidden + n;
+            unsigned long long got = ld_relaxed_sys(w);
+            uint32_t tries = 0;
+            // A word with an earlier step's number is waited for.  One with a LATER number means that a
+            // peer gave up on this rank and ran ahead: the words this rank still misses belong to
+            // steps its peers have left behind and would never come, so it reports that, waits for
+            // nothing more in this step and runs at full speed until it is level again.
+            while ((int32_t)((uint32_t)(got >> 32) - (ep_step + 1u)) < 0) {
+                if (s_behind) break;
+                if (++tries > ep.wait_limit || abort_flag) {
+                    s_abort_code = 0x5503u;
+                    abort_flag = 1;
+                    ok = false;
+                    break;
+                }
+                __nanosleep(100);
+                got = ld_relaxed_sys(w);
+            }
+            if ((int32_t)((uint32_t)(got >> 32) - (ep_step + 1u)) > 0) {
+                s_behind = 1;
+                atomicExch(status, 0x5504u);
+            }
+            const float dv = __uint_as_float((uint32_t)got);
+            acc = jj < rt.top_k ? __fadd_rn(acc, __fmul_rn(s_mix_w[jj], dv)) : __fadd_rn(acc, dv);
+        }
+        if (ok && y) y[n] = acc;
+    }
+    __syncthreads();
     // the last CTA to leave puts the counters back to zero for the next launch
     if (tid == 0) {
+        if (abort_flag) atomicExch(status, s_abort_code);
         __threadfence();
-        if (atomicAdd(counters + kExitCounter, 1u) == grid - 1u) {
-            counters[kItemCounter] = 0u;
-            counters[kExitCounter] = 0u;
-            counters[kRouteCounter] = 0u;
-            if (ep_on) *ep.step = ep_step + 1u;  // every CTA has read the count
+        s_last = atomicAdd(counters + kCntExit, 1u) == grid - 1u;
+        mark(14);
+    }
+    __syncthreads();
+    if (s_last) {
+        for (uint32_t i = 1u + tid; i < kCntEnd; i += kThreads) counters[i] = 0u;
+        if (ep_on && tid == 0) {
+            // every CTA has read the step count and finished reading this step's words
+            *ep.step = ep_step + 1u;
+            const size_t credit = 2u * (size_t)(S14_EXPERTS_PER_TOKEN + 1) * hidden + 8u;
+            for (uint32_t p = 0; p < ep.world; ++p)
+                if (p != ep.rank) st_relaxed_sys(ep.slots[p] + credit + ep.rank, (unsigned long long)(ep_step + 1u));
         }
     }
 }
-
-size_t umma_smem_bytes(uint32_t hidden) { return (size_t)kRing * (kStageA + kStageSf) + (size_t)(hidden >> 8) * 2048u; }
 
 template <class Kernel, class... Args>
 cudaError_t launch_pdl(Kernel kernel, dim3 grid, dim3 block, size_t smem, cudaStream_t st, bool pdl, Args... args) {
@@ -906,38 +1039,54 @@ cudaError_t launch_pdl(Kernel kernel, dim3 grid, dim3 block, size_t smem, cudaSt
 }
 
 constexpr size_t kMaxSmem = 227u * 1024u;  // per CTA, static + dynamic
+constexpr int kMaxDevices = 64;
 
-// Largest dynamic size the kernel may ask for (the limit minus its static part); 0 on failure.
-size_t g_dynamic_limit = 0;
+// Largest dynamic size the kernel may ask for on a device (the limit minus its static part); 0:
+// not configured yet or failed.  The attribute belongs to a device, so it is set once per device,
+// with that device current.
+size_t g_dynamic_limit[kMaxDevices] = {};
 
-void configure_once() {
-    static bool configured = false;
-    if (configured) return;
-    configured = true;
+size_t dynamic_limit() {
+    int dev = -1;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= kMaxDevices) return 0;
+    if (g_dynamic_limit[dev]) return g_dynamic_limit[dev];
     cudaFuncAttributes fa;
-    if (cudaFuncGetAttributes(&fa, k_moe_layer_umma) != cudaSuccess) return;
+    if (cudaFuncGetAttributes(&fa, k_moe_layer_umma) != cudaSuccess) return 0;
     const size_t most = kMaxSmem - fa.sharedSizeBytes;
-    if (cudaFuncSetAttribute(k_moe_layer_umma, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)most) != cudaSuccess) return;
-    g_dynamic_limit = most;
+    if (cudaFuncSetAttribute(k_moe_layer_umma, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)most) != cudaSuccess) return 0;
+    g_dynamic_limit[dev] = most;
+    return most;
+}
+
+// Ring slots that fit beside the token's digit tile and two tiles of hidden values: an even number.
+uint32_t ring_slots(uint32_t hidden, uint32_t inter, size_t limit) {
+    const size_t fixed = (size_t)(hidden >> 8) * 2048u + 2u * (size_t)(inter >> 8) * 2048u;
+    if (limit < fixed + 2u * kSlot) return 0;
+    uint32_t r = (uint32_t)((limit - fixed) / kSlot);
+    if (r > kMaxRing) r = kMaxRing;
+    return r & ~1u;
 }
 
 }  // namespace
 
-size_t umma_partials_bytes() {
-    // one F32 per (item, output row): experts of a token x slices x rows, at the largest shape
-    return (size_t)(S14_EXPERTS_PER_TOKEN + 1) * (4096 / 64) * kMaxHidden * sizeof(float);
+size_t umma_trace_bytes(int sm_count) { return (size_t)sm_count * kTraceWords * sizeof(unsigned long long); }
+uint32_t umma_trace_words() { return kTraceWords; }
+
+size_t umma_scratch_bytes() {
+    // a digit tile and its block exponents per job
+    return (size_t)kJobsMax * (kTileMax + kExpMax);
 }
 
 bool umma_layer_ok(int sm_count, uint32_t n_tokens, uint32_t n_jobs_max, uint32_t hidden, uint32_t inter) {
-    if (n_tokens != 1u || n_jobs_max == 0u || n_jobs_max > S14_EXPERTS_PER_TOKEN + 1u) return false;
+    if (n_tokens != 1u || n_jobs_max == 0u || n_jobs_max > kJobsMax || sm_count <= 0) return false;
     if ((hidden & 511u) || (inter & 511u) || hidden < 512u || inter < 512u || hidden > kMaxHidden || inter > 4096u) return false;
-    const uint32_t items = n_jobs_max * (inter >> 6);
-    if ((items + (uint32_t)sm_count - 1u) / (uint32_t)sm_count > kItemSlots) return false;
-    configure_once();
-    // the final sums reuse the ring: [jobs][slices / 4][rows] doubles + [jobs][rows] floats
-    const size_t rows = (hidden + sm_count - 1) / sm_count + 1;
-    if ((size_t)n_jobs_max * ((inter >> 8) * 8u + 4u) * rows > (size_t)kRing * (kStageA + kStageSf)) return false;
-    return umma_smem_bytes(hidden) <= g_dynamic_limit;
+    // no CTA's share may exceed the item list
+    uint32_t items[1];
+    for (uint32_t c = 0; c < (uint32_t)sm_count; ++c)
+        if (layer_work_list(c, (uint32_t)sm_count, n_jobs_max, inter >> 6, hidden >> 7, hidden >> 8, inter >> 8, items, 0) >
+            kMaxItems)
+            return false;
+    return ring_slots(hidden, inter, dynamic_limit()) >= 2u;
 }
 
 bool umma_router_ok(int sm_count, uint32_t n_experts) {
@@ -945,20 +1094,22 @@ bool umma_router_ok(int sm_count, uint32_t n_experts) {
 }
 
 cudaError_t launch_moe_layer_umma(cudaStream_t st, int sm_count, const JobTable *dev, const JobTable &param,
-                                  const float *x, float *d, float *y, float *partials, unsigned int *counters,
-                                  uint32_t *status, uint32_t hidden, uint32_t inter, bool after_router,
-                                  const FusedRouter *router, const EpExchange *ep) {
-    configure_once();
+                                  const float *x, float *d, float *y, uint8_t *tiles, unsigned int *counters,
+                                  uint32_t *status, uint32_t hidden, uint32_t inter, const FusedRouter *router,
+                                  const EpExchange *ep, unsigned long long *trace) {
+    const uint32_t ring = ring_slots(hidden, inter, dynamic_limit());
+    if (ring < 2u) return cudaErrorInvalidConfiguration;
     FusedRouter rt = {};
     if (router) rt = *router;
     EpExchange ex = {};
     if (ep) ex = *ep;
     if (ex.world > 1u && !router) return cudaErrorInvalidValue;  // the mix needs every route's weight
-    (void)after_router;
+    const size_t smem = (size_t)ring * kSlot + (size_t)(hidden >> 8) * 2048u + 2u * (size_t)(inter >> 8) * 2048u;
     // A programmatic dependent of the previous launch on the single-GPU path.  The expert-parallel
-    // paths (exchange inside the kernel, or expert outputs handed to a collective) were measured as
-    // ordinary launches only and stay so; the kernel's own dependency calls are then no-ops.
-    return launch_pdl(k_moe_layer_umma, dim3(sm_count), dim3(kThreads), umma_smem_bytes(hidden), st, ex.world <= 1u && y != nullptr, dev, param, x, d, y, partials, counters, status, hidden, inter, rt, ex);
+    // paths (exchange inside the kernel, or expert outputs handed to a collective) are ordinary
+    // launches; the kernel's own dependency calls are then no-ops.
+    return launch_pdl(k_moe_layer_umma, dim3(sm_count), dim3(kThreads), smem, st, ex.world <= 1u && y != nullptr, dev,
+                      param, x, d, y, tiles, counters, status, hidden, inter, ring, trace, rt, ex);
 }
 
 }  // namespace s14

@@ -93,9 +93,14 @@ def _buf(t) -> L.Buffer:
 
 
 def _torch_stream() -> int:
+    """The handle of torch's current stream.  torch reports its default stream as 0, which the C ABI
+    reads as "the context's own stream"; the legacy default stream is passed by its own handle
+    (cudaStreamLegacy) instead, so that a call without an explicit stream is ordered with the
+    torch work around it."""
     import torch
 
-    return torch.cuda.current_stream().cuda_stream
+    h = torch.cuda.current_stream().cuda_stream
+    return h if h else 1
 
 
 class S14Context:
@@ -286,6 +291,20 @@ class S14Context:
             self._h, C.byref(d), host_x.ctypes.data, host_y.ctypes.data,
             host_ids.ctypes.data if host_ids is not None else None,
             host_weights.ctypes.data if host_weights is not None else None))
+
+    def set_layer_trace(self, enable: bool) -> None:
+        """Time marks inside the tensor-core layer kernel (profiling runs)."""
+        check(L.lib().s14_ctx_set_layer_trace(self._h, 1 if enable else 0))
+
+    def read_layer_trace(self):
+        """[n_ctas, 64] uint64 marks of the last launch of the layer kernel (see the header)."""
+        import numpy as np
+
+        cap = 1024 * 64
+        out = np.zeros(cap, np.uint64)
+        n, w = C.c_uint32(), C.c_uint32()
+        check(L.lib().s14_ctx_read_layer_trace(self._h, out.ctypes.data, cap, C.byref(n), C.byref(w)))
+        return out[: n.value * w.value].reshape(n.value, w.value)
 
     def set_kernel_timing(self, enable: bool) -> None:
         check(L.lib().s14_ctx_set_kernel_timing(self._h, 1 if enable else 0))

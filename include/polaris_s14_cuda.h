@@ -53,9 +53,15 @@ extern "C" {
 #define S14_PAGE_FP8 1u   /* [w1][w3][w2] E4M3 codes, then [s1][s3][s2] UE8M0 per 128x128 */
 
 /* Summation order of every matvec of a context.
- *   S14_ACCUM_PAIRWISE  : lanes of a warp split K; products are accumulated in F32
- *                         inside one scale block and in F64 across blocks, lanes
- *                         and warps, then rounded to F32 once (the fast path).
+ *   S14_ACCUM_PAIRWISE  : the fast path.  Every product x * w is exact and the products of a row
+ *                         are added in a wider format than F32, then rounded to F32 once per
+ *                         row: the result is the reference's dot product with the accumulator
+ *                         widened to double (what the reference's Python code computes with
+ *                         accumulation_dtype=float64, local_s14_primitives/mxfp4.py:172-275).
+ *                         One-token layers of MXFP4 pages run on the tensor cores (activations
+ *                         as sixteen base-8 digit rows, tcgen05 block-scaled MMA, columns added
+ *                         in double); everything else on F32 / F64 register kernels (a warp per
+ *                         row, F32 inside a scale block, F64 across blocks and lanes).
  *   S14_ACCUM_REFERENCE : one thread per output row, k ascending, two separate
  *                         multiply-then-add steps per packed byte, (x*w)*s - the
  *                         exact evaluation order of the reference's F32 CPU code
@@ -102,6 +108,16 @@ S14_API uint64_t s14_ctx_launch_count(const s14_ctx *ctx);
 S14_API int32_t s14_ctx_set_kernel_timing(s14_ctx *ctx, int32_t enable);
 S14_API int32_t s14_ctx_kernel_times(s14_ctx *ctx, double ms_out[4], uint64_t *calls);
 
+/* Time marks inside the tensor-core layer kernel, for profiling runs (no counterpart in the
+ * reference): while enabled, every CTA of the kernel's next launches writes 64 words - word 0 the
+ * GPU's global timer (ns) at entry, then SM clock values at the kernel's stages (set-up, first
+ * copies, token read, digits, routes known, per item: first unit arrived, accumulators complete,
+ * epilogue done, digit tile in place; copies issued, items done, exit), word 15 = items | ring slots
+ * << 8 | jobs << 16.  read copies the marks of the last launch ([n_ctas][words_per_cta]). */
+S14_API int32_t s14_ctx_set_layer_trace(s14_ctx *ctx, int32_t enable);
+S14_API int32_t s14_ctx_read_layer_trace(s14_ctx *ctx, uint64_t *out, uint32_t cap_words, uint32_t *n_ctas,
+                                         uint32_t *words_per_cta);
+
 /* ---- byte contracts: S14MatvecShape (s14_vulkan.rs:40-114) ------------------- */
 typedef struct {
     uint32_t n;
@@ -118,15 +134,20 @@ S14_API int32_t s14_shape_mxfp4_scale_bytes(s14_matvec_shape shape, uint64_t *ou
 S14_API int32_t s14_shape_fp8_weight_bytes(s14_matvec_shape shape, uint64_t *out);
 S14_API int32_t s14_shape_fp8_scale_bytes(s14_matvec_shape shape, uint64_t *out);
 
-/* MXFP4 expert page = w1 | w3 | w2 | s13 | s2 in one pool slot (S14_EXPERT_PAGE_BYTES at hidden
- * 4096, intermediate 2048): the bytes of the six checkpoint tensors, stored for the unit of work
- * of the tcgen05 kernel, a slice of 64 intermediate elements of one expert.
- *   w1, w3  [inter, hidden/2] bytes as the checkpoint has them (low nibble = even k);
- *   w2      by (slice s, row tile rt): 128 rows x 32 bytes, so a slice's columns are contiguous;
- *   s13     by (slice s, four scale blocks): the codes of the slice's 64 rows of w1 and 64 rows of
- *           w3, 512 bytes in the order the block-scaled MMA takes scales into tensor memory;
- *   s2      by (slice pair, row tile): the codes of 128 rows of w2 for four scale blocks, same order.
- * hidden and intermediate must be multiples of 128.  A "tensor page" is the six tensors one after
+/* MXFP4 expert page = up | down | s13 | s2 in one pool slot (S14_EXPERT_PAGE_BYTES at hidden
+ * 4096, intermediate 2048): the bytes of the six checkpoint tensors, stored so that everything the
+ * tcgen05 layer kernel fetches in one step is one contiguous run, already in the order the tensor
+ * cores read shared memory.  A unit is 128 matrix rows x 256 K-elements of E2M1 codes: 16 KB, 128
+ * rows of 128 bytes, the 16-byte chunk (one scale block, low nibble = even k) number c of row m at
+ * position c ^ (m % 8).
+ *   up      [inter/64 slices][hidden/256 units]: rows 0-63 of a unit are w1 rows of the slice,
+ *           rows 64-127 the same rows of w3;
+ *   down    [hidden/128 row tiles][inter/256 units] of w2;
+ *   s13     by (slice, four scale blocks): the codes of the slice's 64 rows of w1 and 64 rows of
+ *           w3, 512 bytes in the order the block-scaled MMA takes scales into tensor memory:
+ *           byte (m % 32) * 16 + (m / 32) * 4 + block % 4;
+ *   s2      by (row tile, four scale blocks): the codes of 128 rows of w2, same order.
+ * hidden and intermediate must be multiples of 256.  A "tensor page" is the six tensors one after
  * the other in the checkpoint's ABI (w1 | w3 | w2 | s1 | s3 | s2); these host functions convert
  * between the two, once, at load time.  The reference fixes no layout inside a slot
  * (examples/s14_vulkan_numeric.rs:331-366 uploads six buffers), so they have no counterpart
@@ -258,6 +279,15 @@ typedef struct {
  * route order, then the shared output is added with weight 1
  * (examples/s14_vulkan_numeric.rs:929-947).  Uses the context's scratch. */
 S14_API int32_t s14_cmd_moe_layer(s14_ctx *ctx, void *stream, const s14_moe_layer_desc *desc);
+
+/* Which work the CTA `cta` of `n_ctas` (one per SM) does in a one-token layer of `n_jobs` experts on
+ * the tensor-core path, in the order it does it: items_out[i] = down << 31 | job << 8 | index, where
+ * an up item is (job, slice of 64 intermediate elements: w1 / w3 rows, SwiGLU) and a down item
+ * (job, tile of 128 rows of w2).  Writes at most `cap` items; *count receives the CTA's number of
+ * items.  Host arithmetic only, for tests and for reading profiles; no counterpart in the
+ * reference. */
+S14_API int32_t s14_layer_work_list(uint32_t cta, uint32_t n_ctas, uint32_t n_jobs, uint32_t hidden,
+                                    uint32_t inter, uint32_t *items_out, uint32_t cap, uint32_t *count);
 
 /* Router (s14_first_real_token/executor.py:638-668): logits = x . Wr^T with Wr
  * BF16 [n_experts, hidden]; score = sigmoid | sqrt(softplus); select top_k of

@@ -412,6 +412,87 @@ def test_routed_layer_without_host_round_trip(ctx, oracle):
     ctx.set_accumulation(L.ACCUM_PAIRWISE)
 
 
+def near_tie_bias(oracle, x, wr, bias, score_fn):
+    """A copy of `bias` in which the seventh-best expert's selection value is moved to within 1e-5
+    below the sixth-best one (the seventh expert has the lower id when possible, so that a kernel
+    that confused the two would pick it)."""
+    _, _, scores, select = oracle.router(x, wr, bias, score_fn, 6, 1.0)
+    order = np.lexsort((np.arange(select.size), -select.astype(np.float64)))
+    sixth, seventh = int(order[5]), int(order[6])
+    b = bias.copy()
+    want = np.float32(select[sixth]) - np.float32(3e-6)
+    b[seventh] = np.float32(np.float64(want) - np.float64(scores[seventh]))
+    return b, sixth, seventh
+
+
+@pytest.mark.parametrize("score_fn", [L.SCORE_SIGMOID, L.SCORE_SQRT_SOFTPLUS])
+def test_routed_layer_at_the_benchmark_shape(ctx, oracle, score_fn):
+    """The configuration the benchmark times: 256 routed experts, hidden 4096, intermediate 2048,
+    MXFP4 shared expert, the router inside the layer kernel (every CTA scores two experts).  Eight
+    tokens over two layers; ids and weights bit-exact against the oracle's router, y bit-exact in
+    reference order and, in pairwise order, inside the stated tolerance (max-abs 2e-5, RMSE 2e-6)
+    against the double-accumulated oracle.  One token per layer has a sixth / seventh selection gap
+    below 1e-5.  Only the pages a token selects are generated; every other table entry points at a
+    page of other bytes, so a wrong pick cannot go unnoticed."""
+    hidden, inter, n_experts, tokens_per_layer = 4096, 2048, 256, 4
+    worst = {"max_abs": 0.0, "rmse": 0.0, "bit_equal": 1.0}
+    for layer in range(2):
+        g = synth.rng(7100 + 10 * layer + score_fn)
+        wr, bias0 = synth.router_weight_bf16(g, n_experts, hidden), synth.router_bias(g, n_experts)
+        xs = synth.activations(g, tokens_per_layer, hidden)
+        biases, gaps = [], []
+        for t in range(tokens_per_layer):
+            b = bias0
+            if t == 1:
+                b, sixth, seventh = near_tie_bias(oracle, xs[t], wr, bias0, score_fn)
+            _, _, _, select = oracle.router(xs[t], wr, b, score_fn, 6, 1.0)
+            srt = np.sort(select)[::-1]
+            gaps.append(float(srt[5] - srt[6]))
+            biases.append(b)
+        assert 0.0 < gaps[1] < 1e-5, gaps
+        routes = [oracle.router(xs[t], wr, biases[t], score_fn, 6, 1.0) for t in range(tokens_per_layer)]
+        needed = sorted({int(e) for r in routes for e in r[0]})
+        pages = {e: synth.mxfp4_expert_page(synth.rng(90_000 + 1000 * layer + e), hidden, inter) for e in needed}
+        shared = synth.mxfp4_expert_page(synth.rng(95_000 + layer), hidden, inter)
+        other = dev_page(synth.mxfp4_expert_page(synth.rng(96_000 + layer), hidden, inter), hidden, inter)
+        pages_dev = {e: dev_page(p, hidden, inter) for e, p in pages.items()}
+        shared_dev = dev_page(shared, hidden, inter)
+        table = torch.tensor([pages_dev[e].data_ptr() if e in pages_dev else other.data_ptr() for e in range(n_experts)],
+                             dtype=torch.int64, device="cuda")
+        dwr = dev(wr.view(np.int16))
+        ids = torch.empty(6, dtype=torch.int32, device="cuda")
+        wts = torch.empty(6, dtype=torch.float32, device="cuda")
+        for t in range(tokens_per_layer):
+            rid, rw, _, _ = routes[t]
+            dx, dbias = dev(xs[t:t + 1]), dev(biases[t])
+            y = torch.empty_like(dx)
+            sel = [pages[int(e)] for e in rid]
+            for mode in ((L.ACCUM_PAIRWISE, L.ACCUM_REFERENCE) if t < 2 else (L.ACCUM_PAIRWISE,)):
+                ctx.set_accumulation(mode)
+                before = ctx.launch_count
+                ctx.cmd_routed_moe_layer(dx[0], dwr, dbias, table, shared_dev.data_ptr(), L.PAGE_MXFP4, inter, y,
+                                         ids, wts, score_fn=score_fn)
+                torch.cuda.synchronize()
+                assert ctx.device_status() == 0
+                assert np.array_equal(ids.cpu().numpy(), rid), (layer, t, mode)
+                assert np.array_equal(wts.cpu().numpy().view(np.uint32), rw.view(np.uint32)), (layer, t, mode)
+                got = y.cpu().numpy()[0]
+                if mode == L.ACCUM_REFERENCE:
+                    ref = oracle.moe_layer(xs[t], sel, rw, shared, 0, hidden, inter)
+                    assert np.array_equal(got.view(np.uint32), ref.view(np.uint32)), stats(oracle, got, ref)
+                else:
+                    assert ctx.launch_count - before == 1  # scores, routes and the layer in one launch
+                    ref = oracle.moe_layer_acc64(xs[t], sel, rw, shared, 0, hidden, inter)
+                    e = stats(oracle, got, ref)
+                    assert e["max_abs"] <= MAX_ABS and e["rmse"] <= RMSE, (layer, t, e)
+                    worst["max_abs"] = max(worst["max_abs"], e["max_abs"])
+                    worst["rmse"] = max(worst["rmse"], e["rmse"])
+                    worst["bit_equal"] = min(worst["bit_equal"], float((got.view(np.uint32) == ref.view(np.uint32)).mean()))
+        del pages_dev, shared_dev, other
+    ctx.set_accumulation(L.ACCUM_PAIRWISE)
+    print("benchmark-shape parity, pairwise vs double-accumulated oracle:", worst)
+
+
 def test_routed_layer_on_host_buffers_and_the_bound_call(ctx, oracle):
     """The call a host program makes per token: x from host memory, y and the route back.  The bound
     call (descriptor recorded once) and the one-shot call give the device path's bits."""

@@ -291,25 +291,30 @@ def test_expert_page_from_tensors_matches_the_numpy_mirror_and_the_stated_offset
         L.check(L.lib().s14_mxfp4_expert_page_from_tensors(hidden, inter, tensor_page.ctypes.data_as(C.c_void_p),
                                                            got.ctypes.data_as(C.c_void_p)))
         assert np.array_equal(want, got)
-        assert np.array_equal(want[:2 * lay.weight_bytes], tensor_page[:2 * lay.weight_bytes])  # w1, w3 as they are
         assert not np.array_equal(want, tensor_page)
         t, o = lay.split(tensor_page), lay.offsets
         g = np.random.default_rng(1)
+
+        def in_unit(m, kb):  # 128 rows of 128 bytes, the 16-byte chunks of row m at chunk ^ (m % 8)
+            return m * 128 + (((kb % 8) ^ (m % 8)) << 4)
+
         for _ in range(200):
             n, kb = int(g.integers(hidden)), int(g.integers(inter // 32))
-            off = (((kb // 2) * (hidden // 128) + n // 128) * 128 + n % 128) * 32 + (kb % 2) * 16
+            off = ((n // 128) * (inter // 256) + kb // 8) * 16384 + in_unit(n % 128, kb)
             assert np.array_equal(got[o["w2"] + off:o["w2"] + off + 16], t["w2"].reshape(hidden, inter // 2)[n, kb * 16:kb * 16 + 16])
             r = n % 128
-            off = ((kb // 4) * (hidden // 128) + n // 128) * 512 + (r % 32) * 16 + (r // 32) * 4 + kb % 4
+            off = ((n // 128) * (inter // 128) + kb // 4) * 512 + (r % 32) * 16 + (r // 32) * 4 + kb % 4
             assert got[o["s2"] + off] == t["s2"].reshape(hidden, inter // 32)[n, kb]
             i, kb = int(g.integers(inter)), int(g.integers(hidden // 32))
-            for mat, name in ((0, "s1"), (1, "s3")):
+            for mat, name, wname in ((0, "s1", "w1"), (1, "s3", "w3")):
                 m = i % 64 + 64 * mat
                 off = ((i // 64) * (hidden // 128) + kb // 4) * 512 + (m % 32) * 16 + (m // 32) * 4 + kb % 4
                 assert got[o["s1"] + off] == t[name].reshape(inter, hidden // 32)[i, kb]
+                off = ((i // 64) * (hidden // 256) + kb // 8) * 16384 + in_unit(m, kb)
+                assert np.array_equal(got[off:off + 16], t[wname].reshape(inter, hidden // 2)[i, kb * 16:kb * 16 + 16])
         back = np.empty_like(tensor_page)
         L.check(L.lib().s14_mxfp4_expert_page_to_tensors(hidden, inter, got.ctypes.data_as(C.c_void_p),
                                                          back.ctypes.data_as(C.c_void_p)))
         assert np.array_equal(back, tensor_page)
     with pytest.raises(L.S14Error):
-        L.check(L.lib().s14_mxfp4_expert_page_from_tensors(100, 128, None, None))
+        L.check(L.lib().s14_mxfp4_expert_page_from_tensors(100, 256, None, None))
