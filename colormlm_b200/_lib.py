@@ -80,6 +80,18 @@ class RoutedLayerDesc(C.Structure):
                 ("page_table", C.c_void_p), ("shared_page", C.c_void_p), ("y", C.c_void_p)]
 
 
+class StackLayer(C.Structure):
+    _fields_ = [("router_weight_bf16", C.c_void_p), ("bias", C.c_void_p), ("page_table", C.c_void_p),
+                ("shared_page", C.c_void_p), ("ids_out", C.c_void_p), ("weights_out", C.c_void_p),
+                ("y_out", C.c_void_p)]
+
+
+class StackConfig(C.Structure):
+    _fields_ = [("n_layers", C.c_uint32), ("n_experts", C.c_uint32), ("hidden", C.c_uint32), ("inter", C.c_uint32),
+                ("top_k", C.c_uint32), ("score_fn", C.c_uint32), ("route_scale", C.c_float),
+                ("shared_kind", C.c_uint32), ("residual", C.c_uint32)]
+
+
 class ExpertKey(C.Structure):
     _fields_ = [("layer", C.c_uint32), ("kind", C.c_uint8), ("slot", C.c_uint32)]
 
@@ -127,6 +139,10 @@ SIGNATURES = {
     "s14_shape_mxfp4_scale_bytes": (_I32, [MatvecShape, _P(_U64)]),
     "s14_shape_fp8_weight_bytes": (_I32, [MatvecShape, _P(_U64)]),
     "s14_shape_fp8_scale_bytes": (_I32, [MatvecShape, _P(_U64)]),
+    "s14_stack_create": (_I32, [_VP, _P(StackConfig), _P(StackLayer), _P(_VP)]),
+    "s14_stack_destroy": (_I32, [_VP]),
+    "s14_cmd_stack_decode": (_I32, [_VP, _VP, _VP, _VP, _VP]),
+    "s14_stack_decode_host": (_I32, [_VP, _VP, _VP, _VP]),
     "s14_layer_work_list": (_I32, [_U32, _U32, _U32, _U32, _U32, _VP, _U32, _VP]),
     "s14_mxfp4_expert_page_from_tensors": (_I32, [_U32, _U32, _VP, _VP]),
     "s14_mxfp4_expert_page_to_tensors": (_I32, [_U32, _U32, _VP, _VP]),

@@ -798,6 +798,158 @@ extern "C" int32_t s14_cmd_routed_moe_layer(s14_ctx *ctx, void *stream,
     S14_CATCH
 }
 
+// ---- decode stack ---------------------------------------------------------------------
+
+struct s14_stack {
+    s14_ctx *ctx = nullptr;
+    s14_stack_config cfg{};
+    std::vector<StackLayer> layers;
+    StackLayer *dev_layers = nullptr;
+    float *hbuf = nullptr;  // [2][hidden]: the tokens between layers
+    float *ybuf = nullptr;  // [hidden]: a layer's output when the layers are launched one by one
+};
+
+extern "C" int32_t s14_stack_create(s14_ctx *ctx, const s14_stack_config *config, const s14_stack_layer *layers,
+                                    s14_stack **out) {
+    S14_TRY
+    if (!ctx || !config || !layers || !out) throw ContractError("s14_stack_create: NULL argument");
+    *out = nullptr;
+    const s14_stack_config &c = *config;
+    if (c.n_layers == 0 || c.n_layers > 64) throw ContractError("S14 stack: 1..64 layers");
+    if (c.n_experts == 0 || c.n_experts > S14_N_ROUTED_EXPERTS) throw ContractError("S14 stack: 1..256 experts");
+    if (!fused_dim_ok(c.hidden) || !fused_dim_ok(c.inter))
+        throw ContractError("S14 stack: hidden and intermediate must be 1024, 2048 or 4096");
+    if (c.top_k == 0 || c.top_k > S14_EXPERTS_PER_TOKEN || c.top_k > c.n_experts)
+        throw ContractError("S14 stack: top_k must be 1..6");
+    if (c.score_fn != S14_SCORE_SIGMOID && c.score_fn != S14_SCORE_SQRT_SOFTPLUS)
+        throw ContractError("S14 stack: unknown score function");
+    if (!std::isfinite(c.route_scale) || c.route_scale <= 0.0f)
+        throw ContractError("S14 stack: route_scale must be finite and positive");
+    if (c.shared_kind != S14_PAGE_MXFP4 && c.shared_kind != S14_PAGE_FP8)
+        throw ContractError("S14 stack: unknown shared page kind");
+    std::unique_ptr<s14_stack> st(new s14_stack());
+    st->ctx = ctx;
+    st->cfg = c;
+    const bool has_shared = layers[0].shared_page != nullptr;
+    for (uint32_t l = 0; l < c.n_layers; ++l) {
+        const s14_stack_layer &in = layers[l];
+        if (!in.router_weight_bf16 || !in.page_table) throw ContractError("S14 stack: router weight or page table is NULL");
+        if ((in.shared_page != nullptr) != has_shared)
+            throw ContractError("S14 stack: either every layer has a shared expert or none has");
+        require_aligned(in.router_weight_bf16, 16, "S14 stack router weight");
+        if (in.shared_page) require_aligned(in.shared_page, 16, "S14 stack shared page");
+        StackLayer v;
+        v.router_weight = in.router_weight_bf16;
+        v.bias = in.bias;
+        v.page_table = in.page_table;
+        v.shared_page = in.shared_page;
+        v.ids_out = in.ids_out;
+        v.weights_out = in.weights_out;
+        v.y_out = in.y_out;
+        st->layers.push_back(v);
+    }
+    CUDA_OK(cudaSetDevice(ctx->device));
+    CUDA_OK(cudaMalloc(&st->dev_layers, sizeof(StackLayer) * c.n_layers));
+    CUDA_OK(cudaMemcpy(st->dev_layers, st->layers.data(), sizeof(StackLayer) * c.n_layers, cudaMemcpyHostToDevice));
+    CUDA_OK(cudaMalloc(&st->hbuf, sizeof(float) * 2 * c.hidden));
+    CUDA_OK(cudaMalloc(&st->ybuf, sizeof(float) * c.hidden));
+    *out = st.release();
+    return S14_OK;
+    S14_CATCH
+}
+
+extern "C" int32_t s14_stack_destroy(s14_stack *stack) {
+    if (!stack) return S14_OK;
+    if (stack->ctx) {
+        cudaSetDevice(stack->ctx->device);
+        cudaStreamSynchronize(stack->ctx->compute);
+    }
+    cudaFree(stack->dev_layers);
+    cudaFree(stack->hbuf);
+    cudaFree(stack->ybuf);
+    delete stack;
+    return S14_OK;
+}
+
+static FusedRouter stack_router(const s14_ctx *ctx, const s14_stack *stack, uint32_t layer) {
+    const s14_stack_config &c = stack->cfg;
+    const StackLayer &ly = stack->layers[layer];
+    FusedRouter f = {};
+    f.weight = ly.router_weight;
+    f.bias = ly.bias;
+    f.scores = ctx->scores;
+    f.select = ctx->select;
+    f.n_experts = c.n_experts;
+    f.score_fn = c.score_fn;
+    f.top_k = c.top_k;
+    f.route_scale = c.route_scale;
+    f.ids_out = ly.ids_out;
+    f.weights_out = ly.weights_out;
+    f.table_out = ctx->dev_table;
+    f.page_table = ly.page_table;
+    f.shared_page = ly.shared_page;
+    f.shared_kind = c.shared_kind;
+    f.ep_rank = 0;
+    f.ep_world = 1;
+    f.shared_owner = 0;
+    f.has_shared = ly.shared_page != nullptr;
+    return f;
+}
+
+extern "C" int32_t s14_cmd_stack_decode(s14_ctx *ctx, void *stream, s14_stack *stack, const float *x, float *h_out) {
+    S14_TRY
+    if (!ctx || !stack || !x || !h_out) throw ContractError("s14_cmd_stack_decode: NULL argument");
+    if (stack->ctx != ctx) throw ContractError("S14 stack: created for another context");
+    require_aligned(x, 16, "S14 stack x");
+    const s14_stack_config &c = stack->cfg;
+    cudaStream_t st = stream_of(ctx, stream);
+    const bool has_shared = stack->layers[0].shared_page != nullptr;
+    const uint32_t n_jobs = c.top_k + (has_shared ? 1u : 0u);
+    JobTable unused;
+    unused.n_jobs = 0;
+    const bool tensor_path = ctx->mode == S14_ACCUM_PAIRWISE && ctx->use_umma && (!has_shared || c.shared_kind == S14_PAGE_MXFP4) &&
+                             umma_layer_ok(ctx->sm_count, 1, n_jobs, c.hidden, c.inter) &&
+                             umma_router_ok(ctx->sm_count, c.n_experts);
+    if (tensor_path) {
+        FusedRouter fr = stack_router(ctx, stack, 0);
+        fr.has_shared = has_shared;
+        const cudaError_t err = launch_moe_layer_umma(st, ctx->sm_count, nullptr, unused, x, ctx->d, h_out, ctx->umma.tiles,
+                                                      ctx->counters, ctx->status, c.hidden, c.inter, &fr, nullptr,
+                                                      ctx->umma.trace, stack->dev_layers, c.n_layers, stack->hbuf,
+                                                      c.residual != 0);
+        ctx->launches += 1;
+        if (err != cudaSuccess) return cuda_fail(err, "S14 stack launch");
+        return S14_OK;
+    }
+    // the layers one by one: router and layer kernels into ybuf, then the step to the next token
+    const float *cur = x;
+    for (uint32_t l = 0; l < c.n_layers; ++l) {
+        const FusedRouter fr = stack_router(ctx, stack, l);
+        cudaError_t err;
+        ctx->launches += launch_moe_layer(st, ctx->mode, ctx->sm_count, ctx->dev_table, unused, 1, n_jobs, c.hidden, c.inter,
+                                          cur, ctx->h, ctx->d, stack->ybuf, &err, nullptr,
+                                          !has_shared || c.shared_kind == S14_PAGE_MXFP4, ctx->counters, ctx->umma_scratch(), &fr);
+        if (err != cudaSuccess) return cuda_fail(err, "S14 stack layer launch");
+        float *next = (l + 1 == c.n_layers) ? h_out : stack->hbuf + (size_t)((l + 1) & 1u) * c.hidden;
+        CUDA_OK(launch_stack_step(st, cur, stack->ybuf, next, stack->layers[l].y_out, c.hidden, c.residual != 0));
+        ctx->launches += 1;
+        cur = next;
+    }
+    return S14_OK;
+    S14_CATCH
+}
+
+extern "C" int32_t s14_stack_decode_host(s14_ctx *ctx, s14_stack *stack, const float *host_x, float *host_h) {
+    if (!ctx || !stack || !host_x || !host_h) return fail(S14_ERR_CONTRACT, "s14_stack_decode_host: NULL argument");
+    const size_t bytes = sizeof(float) * stack->cfg.hidden;
+    CUDA_OK(cudaMemcpyAsync(ctx->x_stage, host_x, bytes, cudaMemcpyHostToDevice, ctx->compute));
+    const int32_t rc = s14_cmd_stack_decode(ctx, ctx->compute, stack, ctx->x_stage, ctx->y_host_dev);
+    if (rc != S14_OK) return rc;
+    CUDA_OK(cudaStreamSynchronize(ctx->compute));
+    std::memcpy(host_h, ctx->y_host, bytes);
+    return S14_OK;
+}
+
 extern "C" int32_t s14_cmd_routed_moe_experts_ep(s14_ctx *ctx, void *stream,
                                                  const s14_routed_layer_desc *desc, uint32_t ep_rank,
                                                  uint32_t ep_world, uint32_t shared_owner,

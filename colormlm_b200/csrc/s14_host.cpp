@@ -84,7 +84,7 @@ static void check_page_shape(uint32_t hidden, uint32_t inter, const void *a, con
 
 // forward = true: tensors -> page order; false: page order -> tensors
 static void reorder_page(uint32_t hidden, uint32_t inter, const uint8_t *src, uint8_t *dst, bool forward) {
-    const size_t wb = mxfp4_weight_bytes(hidden, inter), sb = (size_t)hidden * inter / 32;
+    const size_t wb = (size_t)hidden * inter / 2, sb = (size_t)hidden * inter / 32;
     const uint32_t kb_down = inter >> 5, kb_up = hidden >> 5;
     auto move16 = [&](size_t tensor_at, size_t page_at) {
         std::memcpy(forward ? dst + page_at : dst + tensor_at, forward ? src + tensor_at : src + page_at, 16);

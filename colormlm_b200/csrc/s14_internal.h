@@ -83,6 +83,21 @@ struct FusedRouter {
     const uint8_t *shared_page;        // or NULL
     uint32_t shared_kind;
     uint32_t ep_rank, ep_world, shared_owner;
+    uint32_t has_shared;               // every layer has a shared expert (a stack's layers say where)
+};
+
+// What one layer of a decode stack brings of its own (device memory, constant during a step): the
+// tcgen05 layer kernel walks an array of these in one launch, the output of a layer (plus its input,
+// if the stack keeps a residual) being the next layer's token.  Router shape, score function, top_k
+// and page kind are the stack's and come with FusedRouter.
+struct StackLayer {
+    const uint16_t *router_weight;     // [n_experts, hidden] BF16
+    const float *bias;                 // [n_experts] or NULL
+    const uint8_t *const *page_table;  // [n_experts] expert pages (MXFP4)
+    const uint8_t *shared_page;        // MXFP4 page; NULL only if no layer of the stack has one
+    int32_t *ids_out;                  // [top_k] or NULL: the layer's route
+    float *weights_out;                // [top_k] or NULL
+    float *y_out;                      // [hidden] or NULL: the layer's MoE output before the residual
 };
 
 cudaError_t launch_mxfp4_matvec(cudaStream_t st, uint32_t mode, int sm_count, const float *x,
@@ -128,12 +143,16 @@ cudaError_t launch_moe_layer_umma(cudaStream_t st, int sm_count, const JobTable 
                                   const float *x, float *d, float *y, uint8_t *tiles, unsigned int *counters,
                                   uint32_t *status, uint32_t hidden, uint32_t inter,
                                   const FusedRouter *router = nullptr, const EpExchange *ep = nullptr,
-                                  unsigned long long *trace = nullptr);
+                                  unsigned long long *trace = nullptr, const StackLayer *stack = nullptr,
+                                  uint32_t n_layers = 1, float *hbuf = nullptr, bool residual = false);
 int launch_router(cudaStream_t st, const s14_router_desc &r, float *scores, float *select,
                   JobTable *table_out, const uint8_t *const *page_table, const uint8_t *shared_page,
                   uint32_t shared_kind, unsigned int *counter, cudaError_t *err,
                   const KernelMarks *km = nullptr, uint32_t ep_rank = 0, uint32_t ep_world = 1,
                   uint32_t shared_owner = 0);
+// out[i] = residual ? x[i] + y[i] : y[i]; y_copy (or NULL) also receives y (a stack's layers launched one by one).
+cudaError_t launch_stack_step(cudaStream_t st, const float *x, const float *y, float *out, float *y_copy,
+                              uint32_t n, bool residual);
 cudaError_t launch_mix_slots(cudaStream_t st, const float *slots, const float *weights, uint32_t n_routed,
                              int has_shared, float *y, uint32_t hidden);
 cudaError_t launch_head_logits(cudaStream_t st, int sm_count, const float *x, uint32_t n_tokens,

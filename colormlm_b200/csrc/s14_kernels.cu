@@ -1029,6 +1029,22 @@ int launch_router(cudaStream_t st, const s14_router_desc &r, float *scores, floa
     return 1;
 }
 
+__global__ void __launch_bounds__(256)
+k_stack_step(const float *__restrict__ x, const float *__restrict__ y, float *out, float *y_copy, uint32_t n,
+             uint32_t residual) {
+    const uint32_t i = blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= n) return;
+    const float v = y[i];
+    if (y_copy) y_copy[i] = v;
+    out[i] = residual ? __fadd_rn(x[i], v) : v;
+}
+
+cudaError_t launch_stack_step(cudaStream_t st, const float *x, const float *y, float *out, float *y_copy,
+                              uint32_t n, bool residual) {
+    k_stack_step<<<ceil_div(n, 256), 256, 0, st>>>(x, y, out, y_copy, n, residual ? 1u : 0u);
+    return cudaGetLastError();
+}
+
 cudaError_t launch_mix_slots(cudaStream_t st, const float *slots, const float *weights, uint32_t n_routed,
                              int has_shared, float *y, uint32_t hidden) {
     k_mix_slots<<<ceil_div(hidden, 256), 256, 0, st>>>(slots, weights, n_routed, has_shared, y, hidden);

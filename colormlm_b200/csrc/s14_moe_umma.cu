@@ -39,15 +39,15 @@ namespace s14 {
 
 namespace {
 
-constexpr uint32_t kUnitSf = 2 * kAtomBytes;       // scale atoms of a unit (256 K-elements = 8 blocks)
-constexpr uint32_t kSlot = kUnitBytes + kUnitSf;   // ring slot: codes, then scales (17 KB, keeps 1 KB alignment)
+constexpr uint32_t kSlot = kUnitStride;             // ring slot: a unit's codes, then its scales (17 KB, keeps 1 KB alignment)
 constexpr uint32_t kMaxRing = 12;                  // ring slots are an even number: a slot belongs to one issuing thread
-constexpr uint32_t kThreads = 512;
+constexpr uint32_t kThreads = 544;                 // sixteen warps that share the token, one warp that copies
+constexpr uint32_t kTokenThreads = 512;
 constexpr uint32_t kEpiThreads = 128;              // warps 0-3: one per lane quadrant of tensor memory
-constexpr uint32_t kProdWarp = 4;                  // lane 0 copies
 constexpr uint32_t kMmaWarp0 = 5;                  // warps 5, 6: lane 0 issues
-constexpr uint32_t kLoadWarp0 = 8;                 // warps 8-15 fetch digit tiles
+constexpr uint32_t kLoadWarp0 = 8;                 // warps 8-15 fetch digit tiles (and pick the routes)
 constexpr uint32_t kLoadThreads = 256;
+constexpr uint32_t kProdWarp = 16;                 // lane 0 copies
 constexpr uint32_t kMaxItems = 32;                 // items a CTA can hold
 constexpr uint32_t kJobsMax = S14_EXPERTS_PER_TOKEN + 1;
 constexpr uint32_t kTileMax = 32768;               // digit tile of a 4096-long vector: 16 units of 2 KB
@@ -66,12 +66,13 @@ constexpr uint32_t kSpin = 1u << 17;        // tries (a microsecond each at most
 constexpr uint32_t kSpinGlobal = 1u << 20;  // polls (100 ns apart) of a counter before giving up
 // the context's counter array ([0] is the router kernel's); [1, kCntEnd) are zero between launches
 constexpr uint32_t kCntExit = 2, kCntRoute = 3;
+constexpr uint32_t kCntMixed = 4;                    // row tiles mixed (a stack's next layer waits for all of them)
 constexpr uint32_t kCntJob0 = 16;                    // slices done per job
 constexpr uint32_t kCntTile0 = kCntJob0 + 64;        // jobs done per row tile
 constexpr uint32_t kCntEnd = kCntTile0 + 64;
-constexpr uint32_t kRouterSlots = 4;                 // experts a CTA scores at most
+constexpr uint32_t kRouterSlots = 2;                 // experts a CTA scores at most
 constexpr uint32_t kItemDown = 0x80000000u;
-constexpr uint32_t kTraceWords = 64;   // time marks per CTA of a profiling run
+constexpr uint32_t kTraceWords = 96;   // time marks per CTA of a profiling run
 
 // Barriers.
 constexpr uint32_t kBarFull = 0;                      // ring slot filled (one arrival + the copies' bytes)
@@ -82,7 +83,10 @@ constexpr uint32_t kBarXReady = kBarAccFree + 2;      // the token's digit scale
 constexpr uint32_t kBarHReady = kBarXReady + 1;       // [2] a digit tile of hidden values is in place
 constexpr uint32_t kBarHFree = kBarHReady + 2;        // [2] ... is not read any more
 constexpr uint32_t kBarFin = kBarHFree + 2;           // both issuing threads have finished
-constexpr uint32_t kBars = kBarFin + 1;
+constexpr uint32_t kBarRoutes = kBarFin + 1;          // the jobs and the CTA's items are in shared memory
+constexpr uint32_t kBarWr = kBarRoutes + 1;           // the layer's router rows of this CTA are in shared memory
+constexpr uint32_t kBars = kBarWr + 1;
+constexpr uint32_t kRouteWarp = 15;                   // the warp that publishes the CTA's expert scores
 
 __device__ __forceinline__ uint32_t smem_u32(const void *p) {
     return (uint32_t)__cvta_generic_to_shared(p);
@@ -125,34 +129,36 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatil
     *abort_flag = 1;
     return false;
 }
-// Named barriers with a vote: every thread of the group executes them, whatever it has seen, so a
-// group never splits in front of a barrier.  1: the 128 epilogue threads; 2: the 256 tile threads.
-__device__ __forceinline__ bool epi_all(bool ok) {
+// Named barriers, plain and with a vote.  Every thread of the group executes them, whatever it has
+// seen, so a group never splits in front of a barrier; and every one starts by bringing the warp
+// back together, because a lane that has been polling or issuing on its own may still be behind its
+// warp, and a warp counts as arrived as soon as some of its lanes get there.  1: the 128 epilogue
+// threads; 2: the 256 tile threads; 3: the 512 threads that share the token.
+template <int ID, int N>
+__device__ __forceinline__ bool named_all(bool ok) {
     uint32_t r;
+    __syncwarp();
     asm volatile(
         "{\n.reg .pred p, q;\n"
         "setp.ne.b32 p, %1, 0;\n"
-        "barrier.cta.red.and.pred q, 1, 128, p;\n"
+        "barrier.cta.red.and.pred q, %2, %3, p;\n"
         "selp.b32 %0, 1, 0, q;\n}"
         : "=r"(r)
-        : "r"((uint32_t)ok)
+        : "r"((uint32_t)ok), "n"(ID), "n"(N)
         : "memory");
     return r != 0;
 }
-__device__ __forceinline__ bool load_all(bool ok) {
-    uint32_t r;
-    asm volatile(
-        "{\n.reg .pred p, q;\n"
-        "setp.ne.b32 p, %1, 0;\n"
-        "barrier.cta.red.and.pred q, 2, 256, p;\n"
-        "selp.b32 %0, 1, 0, q;\n}"
-        : "=r"(r)
-        : "r"((uint32_t)ok)
-        : "memory");
-    return r != 0;
+template <int ID, int N>
+__device__ __forceinline__ void named_sync() {
+    __syncwarp();
+    asm volatile("bar.sync %0, %1;" ::"n"(ID), "n"(N) : "memory");
 }
-__device__ __forceinline__ void epi_sync() { asm volatile("bar.sync 1, 128;" ::: "memory"); }
-__device__ __forceinline__ void load_sync() { asm volatile("bar.sync 2, 256;" ::: "memory"); }
+__device__ __forceinline__ bool epi_all(bool ok) { return named_all<1, 128>(ok); }
+__device__ __forceinline__ bool load_all(bool ok) { return named_all<2, 256>(ok); }
+__device__ __forceinline__ bool token_all(bool ok) { return named_all<3, 512>(ok); }
+__device__ __forceinline__ void epi_sync() { named_sync<1, 128>(); }
+__device__ __forceinline__ void load_sync() { named_sync<2, 256>(); }
+__device__ __forceinline__ void token_sync() { named_sync<3, 512>(); }
 // Shared-memory matrix descriptor of sm_100: start address, leading and stride byte offsets in
 // 16-byte units, descriptor version 1, layout (0 = no swizzle, 2 = 128-byte swizzle).
 __device__ __forceinline__ uint64_t smem_desc(uint32_t addr, uint32_t lbo16, uint32_t sbo16, uint32_t layout) {
@@ -191,25 +197,58 @@ __device__ __forceinline__ void fence_async_smem() { asm volatile("fence.proxy.a
 // Instruction descriptor: A and B E2M1 (format 1), both K-major, N = 16, UE8M0 scales, M = 128.
 constexpr uint32_t kIdesc = (1u << 7) | (1u << 10) | ((16u >> 3) << 17) | (1u << 23) | ((128u >> 4) << 24);
 
-// E2M1 codes of the eight balanced base-8 digits of q (|q| <= 2^23), digit j in bits 4j .. 4j+3.
-// With the bias 4 * (8^8 - 1) / 7 added, the balanced digits are the plain base-8 digits minus 4,
-// so no carry runs through them; the top digit may reach +4.
-__device__ __forceinline__ uint32_t digit_codes(int q) {
-    const uint32_t qb = (uint32_t)(q + 0x924924);  // in [0, 8^8 + 8^7)
-    uint32_t w = 0;
-#pragma unroll
-    for (int j = 0; j < 7; ++j)  // E2M1 codes of -4..3 by digit value 0..7
-        w |= ((0x5420ACDEu >> (((qb >> (3 * j)) & 7u) << 2)) & 0xFu) << (4 * j);
-    const uint32_t top = qb >> 21;  // 0..8 -> -4..4
-    return w | ((top > 7u ? 6u : ((0x5420ACDEu >> (top << 2)) & 0xFu)) << 28);
+__device__ __forceinline__ uint32_t prmt(uint32_t a, uint32_t b, uint32_t sel) {
+    uint32_t r;
+    asm("prmt.b32 %0, %1, %2, %3;" : "=r"(r) : "r"(a), "r"(b), "r"(sel));
+    return r;
 }
-// v * 2^(23-E) = hi + lo * 2^-24 with integers |hi|, |lo| <= 2^23 (|v| < 2^E); digit codes of both.
-__device__ __forceinline__ void digit_codes16(float v, float up, uint32_t &hi_w, uint32_t &lo_w) {
+// E2M1 codes of the eight balanced base-8 digits of q (|q| <= 2^23), one code per byte: digit j in
+// byte j of c03 (j < 4) or byte j - 4 of c47.  With the bias 4 * (8^8 - 1) / 7 added, the balanced
+// digits are the plain base-8 digits minus 4, so no carry runs through them; the top digit may
+// reach +4.  The 3-bit fields are spread to nibbles and looked up four at a time with prmt.
+__device__ __forceinline__ void digit_code_bytes(int q, uint32_t &c03, uint32_t &c47) {
+    const uint32_t qb = (uint32_t)(q + 0x924924);  // in [0, 8^8 + 8^7)
+    uint32_t x = qb & 0xFFFFFFu;
+    x = (x & 0x00000FFFu) | ((x & 0x00FFF000u) << 4);
+    x = (x & 0x003F003Fu) | ((x & 0x0FC00FC0u) << 2);
+    x = (x & 0x07070707u) | ((x & 0x38383838u) << 1);  // digit value j (0..7) in nibble j
+    // codes of -4, -3, -2, -1 | 0, 1, 2, 3 by digit value
+    c03 = prmt(0x0A0C0D0Eu, 0x05040200u, x);
+    c47 = prmt(0x0A0C0D0Eu, 0x05040200u, x >> 16);
+    if (qb >> 24) c47 = (c47 & 0x00FFFFFFu) | 0x06000000u;  // top digit +4
+}
+// Four code bytes (each < 16) -> four nibbles in the low 16 bits of byte lanes 0 and 2 of the result
+// (use with pack_pairs).
+__device__ __forceinline__ uint32_t pair_nibbles(uint32_t c) { return c | (c >> 4); }
+// nibbles of eight codes: a = pair_nibbles of codes 0-3, b = of codes 4-7
+__device__ __forceinline__ uint32_t pack_pairs(uint32_t a, uint32_t b) { return prmt(a, b, 0x6420u); }
+// E2M1 codes of the eight digits of q, digit j in bits 4j .. 4j+3.
+__device__ __forceinline__ uint32_t digit_codes(int q) {
+    uint32_t c03, c47;
+    digit_code_bytes(q, c03, c47);
+    return pack_pairs(pair_nibbles(c03), pair_nibbles(c47));
+}
+// v * 2^(23-E) = hi + lo * 2^-24 with integers |hi|, |lo| <= 2^23 (|v| < 2^E).
+__device__ __forceinline__ void split_hi_lo(float v, float up, int &hi, int &lo) {
     const float t = v * up;  // exact: a power of two
-    const int hi = __float2int_rn(t);
+    hi = __float2int_rn(t);
     const float rem = __fsub_rn(t, (float)hi);  // exact
+    lo = __float2int_rn(rem * 16777216.0f);
+}
+__device__ __forceinline__ void digit_codes16(float v, float up, uint32_t &hi_w, uint32_t &lo_w) {
+    int hi, lo;
+    split_hi_lo(v, up, hi, lo);
     hi_w = digit_codes(hi);
-    lo_w = digit_codes(__float2int_rn(rem * 16777216.0f));
+    lo_w = digit_codes(lo);
+}
+// Transposes four registers of four bytes: out k = byte k of r0, r1, r2, r3.
+__device__ __forceinline__ void transpose4(uint32_t r0, uint32_t r1, uint32_t r2, uint32_t r3, uint32_t (&o)[4]) {
+    const uint32_t t0 = prmt(r0, r1, 0x5140u), t1 = prmt(r0, r1, 0x7362u);
+    const uint32_t t2 = prmt(r2, r3, 0x5140u), t3 = prmt(r2, r3, 0x7362u);
+    o[0] = prmt(t0, t2, 0x5410u);
+    o[1] = prmt(t0, t2, 0x7632u);
+    o[2] = prmt(t1, t3, 0x5410u);
+    o[3] = prmt(t1, t3, 0x7632u);
 }
 // The exponent E of a scale block from its largest magnitude: bm < 2^E, clamped to [-80, 127] (row
 // 8 of a block carries the scale 2^(E-47), whose UE8M0 code must not fall below zero).
@@ -232,19 +271,32 @@ __device__ __forceinline__ void digits_of8(const float (&xs)[8], uint32_t g, uin
     bm = fmaxf(bm, __shfl_xor_sync(0xffffffffu, bm, 2));
     const int E = block_exponent(bm);
     const float up = __uint_as_float((uint32_t)(150 - E) << 23);  // 2^(23-E)
-    uint32_t words[16];
+    // Four elements at a time: their code bytes [element][hi digits 0-3, hi 4-7, lo 0-3, lo 4-7] are
+    // transposed to [digit row][element] and squeezed to nibbles; the two halves of a row's word are
+    // joined at the end.
+    uint32_t half[2][16];
 #pragma unroll
-    for (int j = 0; j < 16; ++j) words[j] = 0u;
+    for (int h = 0; h < 2; ++h) {
+        uint32_t c[4][4];
 #pragma unroll
-    for (int i = 0; i < 8; ++i) {
-        uint32_t hw, lw;
-        digit_codes16(xs[i], up, hw, lw);
+        for (int i = 0; i < 4; ++i) {
+            int hi, lo;
+            split_hi_lo(xs[h * 4 + i], up, hi, lo);
+            digit_code_bytes(hi, c[i][0], c[i][1]);
+            digit_code_bytes(lo, c[i][2], c[i][3]);
+        }
 #pragma unroll
-        for (int j = 0; j < 8; ++j) {
-            words[j] |= ((hw >> (4 * j)) & 0xFu) << (4 * i);
-            words[8 + j] |= ((lw >> (4 * j)) & 0xFu) << (4 * i);
+        for (int q4 = 0; q4 < 4; ++q4) {  // four digit rows at a time
+            uint32_t a[4];
+            transpose4(c[0][q4], c[1][q4], c[2][q4], c[3][q4], a);
+#pragma unroll
+            for (int k = 0; k < 4; ++k) half[h][q4 * 4 + k] = pair_nibbles(a[k]);
         }
     }
+    // word of digit row j: the codes of elements 0..7 in nibbles 0..7
+    uint32_t words[16];
+#pragma unroll
+    for (int j = 0; j < 16; ++j) words[j] = pack_pairs(half[0][j], half[1][j]);
     const uint32_t kb = g >> 2;
     uint8_t *chunk = sB + (kb >> 3) * 2048u + (g & 3u) * 4u;
 #pragma unroll
@@ -295,11 +347,9 @@ __device__ __forceinline__ uint32_t ld_acquire(const unsigned int *p) {
 }  // namespace
 
 // The items of CTA c of G: its up items (job j, slice) first, then its down items (job j, row tile),
-// each as down-bit | j << 8 | index.  Up items q = j * S + slice go round the CTAs (q mod G).  The
-// CTAs with one up item fewer take KU / KD down items each of the jobs whose slices are finished
-// when they get there; the rest of the down items p = j * RT + tile go round all CTAs from the last
-// CTA down.  KU, KD: units of an up and of a down item.  Writes at most `cap` items, returns the
-// CTA's number of items.
+// each as down-bit | j << 8 | index.  Up items q = j * S + slice go round the CTAs (q mod G); the down
+// items p = j * RT + tile are dealt as described below.  KU, KD: units of an up and of a down item.
+// Writes at most `cap` items, returns the CTA's number of items.
 __host__ __device__ uint32_t layer_work_list(uint32_t c, uint32_t G, uint32_t n_jobs, uint32_t S, uint32_t RT,
                                              uint32_t KU, uint32_t KD, uint32_t *items, uint32_t cap) {
     const uint32_t U = n_jobs * S, D = n_jobs * RT;
@@ -308,158 +358,147 @@ __host__ __device__ uint32_t layer_work_list(uint32_t c, uint32_t G, uint32_t n_
     for (uint32_t q = c; q < U; q += G, ++n)
         if (n < cap) items[n] = ((q / S) << 8) | (q % S);
     const uint32_t a_max = (U + G - 1u) / G, r = U - (a_max - 1u) * G;  // CTAs 0 .. r-1 hold a_max up items
-    const uint32_t n_light = G - r, k0 = KU / KD;
+    // The CTAs with one up item fewer are free a whole up item earlier, but a job's down items can start
+    // only some microseconds after its last slice (SwiGLU, digits, publication, the tile's way into shared
+    // memory), which is about what a down item itself takes: each of them takes ONE down item of the jobs
+    // that are finished by then; the rest goes round all CTAs, the others first.
+    const uint32_t n_light = G - r;
     const uint32_t ready = RT * (((a_max - 1u) * G) / S);  // down items of jobs finished one round of up items earlier
-    uint32_t D1 = n_light * k0;
+    uint32_t D1 = n_light;
     if (D1 > ready) D1 = ready;
     if (D1 > D) D1 = D;
-    if (c >= r)
-        for (uint32_t i = 0; i < k0; ++i) {
-            const uint32_t p = (c - r) + i * n_light;
-            if (p < D1) {
-                if (n < cap) items[n] = 0x80000000u | ((p / RT) << 8) | (p % RT);
-                ++n;
-            }
-        }
-    for (uint32_t p = D1 + (G - 1u - c); p < D; p += G, ++n)
+    (void)KU;
+    (void)KD;
+    if (c >= r && c - r < D1) {
+        const uint32_t p = c - r;
         if (n < cap) items[n] = 0x80000000u | ((p / RT) << 8) | (p % RT);
+        ++n;
+    }
+    // first round: CTAs 0 .. G-1 (those with more up items get the jobs that finish first); further
+    // rounds start with the CTAs that have fewer up items
+    for (uint32_t k = 0;; ++k) {
+        const uint32_t pos = k == 0u ? c : (c + G - r) % G;
+        const uint32_t p = D1 + k * G + pos;
+        if (D1 + k * G >= D) break;
+        if (p < D) {
+            if (n < cap) items[n] = 0x80000000u | ((p / RT) << 8) | (p % RT);
+            ++n;
+        }
+    }
     return n;
 }
 
 namespace {
 
-// The routes of the token from the experts' scores, by one warp (the same picks, sums and weights
-// as k_router's last block: largest score + bias first, lowest id on ties; weight = score / sum of
-// the picked scores x route_scale).  Scores, selection values and page addresses come in one round
-// of loads; the picked expert's values come from the lane that holds them.  Lane 0 writes the jobs
-// (the shared expert first, so that its page can be asked for before the routes exist, then the
-// routed experts in route order), the mix (route order, the shared expert last) and every route's
-// weight; `publish` also writes the caller's ids and weights.  Expert parallel: the rank keeps the
-// jobs of the experts it owns and, as the shared expert's owner, the shared job; every job writes
-// the row of its route slot.
-__device__ void route_select(const FusedRouter &rt, uint32_t lane, bool publish, Job *jobs, uint32_t *n_jobs_out,
-                             float *mix_w, uint32_t *mix_slot, uint32_t *n_mix_out) {
-    unsigned long long key[8], pg[8];
-    float sc[8];
-#pragma unroll
-    for (int i = 0; i < 8; ++i) {
-        const uint32_t e = i * 32 + lane;
-        key[i] = 0ull;
-        pg[i] = 0ull;
-        sc[i] = 0.0f;
-        if (e < rt.n_experts) {
-            const uint32_t bits = __float_as_uint(__ldcg(rt.select + e));
-            sc[i] = __ldcg(rt.scores + e);
-            pg[i] = __ldg(reinterpret_cast<const unsigned long long *>(rt.page_table) + e);
-            const uint32_t ordered = (bits & 0x80000000u) ? ~bits : (bits | 0x80000000u);
-            key[i] = ((unsigned long long)ordered << 32) | (unsigned long long)(0xffffffffu - e);
-        }
-    }
-    int32_t ids[S14_EXPERTS_PER_TOKEN];
-    float picked[S14_EXPERTS_PER_TOKEN];
-    unsigned long long pages[S14_EXPERTS_PER_TOKEN];
-#pragma unroll
-    for (int j = 0; j < S14_EXPERTS_PER_TOKEN; ++j) {
-        ids[j] = -1;
-        picked[j] = 0.0f;
-        pages[j] = 0ull;
-        if ((uint32_t)j < rt.top_k) {
-            unsigned long long best = key[0];
-#pragma unroll
-            for (int i = 1; i < 8; ++i) best = key[i] > best ? key[i] : best;
-#pragma unroll
-            for (int o = 16; o > 0; o >>= 1) {
-                const unsigned long long other = __shfl_xor_sync(0xffffffffu, best, o);
-                best = other > best ? other : best;
-            }
-            const uint32_t e = 0xffffffffu - (uint32_t)(best & 0xffffffffull);
-            float my_sc = sc[0];
-            unsigned long long my_pg = pg[0];
-#pragma unroll
-            for (int i = 1; i < 8; ++i) {
-                if ((e >> 5) == (uint32_t)i) {
-                    my_sc = sc[i];
-                    my_pg = pg[i];
-                }
-            }
-#pragma unroll
-            for (int i = 0; i < 8; ++i)
-                if (key[i] == best) key[i] = 0ull;  // taken
-            ids[j] = (int32_t)e;
-            picked[j] = __shfl_sync(0xffffffffu, my_sc, e & 31u);
-            pages[j] = __shfl_sync(0xffffffffu, my_pg, e & 31u);
-        }
-    }
-    if (lane != 0) return;
+// The routes of the token from the picked experts (rank order = largest score + bias first, lowest
+// id on ties), by one warp: lane j takes route j.  The same sums and weights as k_router's last block:
+// weight = score / sum of the picked scores x route_scale.  Writes the jobs (the shared expert first,
+// so that its page can be asked for before the routes exist, then the routed experts in route
+// order), the mix (route order, the shared expert last) and every route's weight; `publish` also
+// writes the caller's ids and weights.  Expert parallel: the rank keeps the jobs of the experts it
+// owns and, as the shared expert's owner, the shared job; every job writes the row of its route slot.
+struct RouteConsts {  // what the route records need of the router, by value
+    uint32_t top_k, has_shared, shared_here, shared_kind, ep_rank, ep_world;
+    float route_scale;
+};
+__device__ __forceinline__ void routes_from_picks(const RouteConsts rc, const uint8_t *shared_page, int32_t *ids_out,
+                                                  float *weights_out, uint32_t lane, const uint32_t *ids, const float *picked,
+                                                  const unsigned long long *pages, bool publish, Job *jobs,
+                                                  uint32_t *n_jobs_out, float *mix_w, uint32_t *mix_slot, uint32_t *n_mix_out) {
     float sum = 0.0f;
-#pragma unroll
-    for (int j = 0; j < S14_EXPERTS_PER_TOKEN; ++j)
-        if ((uint32_t)j < rt.top_k) sum = __fadd_rn(sum, picked[j]);
-    uint32_t n = 0;
-    const bool shared_here = rt.shared_page && rt.shared_owner == rt.ep_rank;
-    if (shared_here) {
-        Job jb;
-        jb.page = rt.shared_page;
-        jb.kind = rt.shared_kind;
-        jb.token = 0;
-        jb.weight = 1.0f;
-        jb.is_shared = 1;
-        jb.out_index = rt.top_k;
-        jobs[n++] = jb;
-    }
-#pragma unroll
-    for (int j = 0; j < S14_EXPERTS_PER_TOKEN; ++j) {
-        if ((uint32_t)j >= rt.top_k) continue;
-        const float w = __fmul_rn(__fdiv_rn(picked[j], sum), rt.route_scale);
-        if (publish && rt.ids_out) rt.ids_out[j] = ids[j];
-        if (publish && rt.weights_out) rt.weights_out[j] = w;
-        mix_w[j] = w;  // every route's weight, also of experts other ranks own
-        mix_slot[j] = (uint32_t)j;
-        if (((uint32_t)ids[j] % rt.ep_world) == rt.ep_rank) {
-            Job jb;
-            jb.page = reinterpret_cast<const uint8_t *>(pages[j]);
-            jb.kind = S14_PAGE_MXFP4;
-            jb.token = 0;
-            jb.weight = w;
-            jb.is_shared = 0;
-            jb.out_index = (uint32_t)j;
-            jobs[n++] = jb;
+    for (uint32_t j = 0; j < rc.top_k; ++j) sum = __fadd_rn(sum, picked[j]);  // every lane, the same order
+    const bool is_route = lane < rc.top_k;
+    const uint32_t id = is_route ? ids[lane] : 0u;
+    const bool owned = is_route && (rc.ep_world <= 1u || (id % rc.ep_world) == rc.ep_rank);
+    const uint32_t owned_mask = __ballot_sync(0xffffffffu, owned);
+    const uint32_t pos = rc.shared_here + __popc(owned_mask & ((1u << lane) - 1u));
+    if (is_route) {
+        const float w = __fmul_rn(__fdiv_rn(picked[lane], sum), rc.route_scale);
+        if (publish && ids_out) ids_out[lane] = (int32_t)id;
+        if (publish && weights_out) weights_out[lane] = w;
+        mix_w[lane] = w;  // every route's weight, also of experts other ranks own
+        mix_slot[lane] = lane;
+        if (owned) {
+            jobs[pos].page = reinterpret_cast<const uint8_t *>(pages[lane]);
+            jobs[pos].kind = S14_PAGE_MXFP4;
+            jobs[pos].token = 0;
+            jobs[pos].weight = w;
+            jobs[pos].is_shared = 0;
+            jobs[pos].out_index = lane;
         }
+    } else if (lane == rc.top_k) {
+        if (rc.shared_here) {
+            jobs[0].page = shared_page;
+            jobs[0].kind = rc.shared_kind;
+            jobs[0].token = 0;
+            jobs[0].weight = 1.0f;
+            jobs[0].is_shared = 1;
+            jobs[0].out_index = rc.top_k;
+        }
+        if (rc.has_shared) {
+            mix_w[rc.top_k] = 1.0f;
+            mix_slot[rc.top_k] = rc.top_k | 0x80000000u;
+        }
+        *n_mix_out = rc.top_k + (rc.has_shared ? 1u : 0u);
+        *n_jobs_out = rc.shared_here + __popc(owned_mask);
     }
-    uint32_t nm = rt.top_k;
-    if (rt.shared_page) {
-        mix_w[nm] = 1.0f;
-        mix_slot[nm] = rt.top_k | 0x80000000u;
-        ++nm;
-    }
-    *n_mix_out = nm;
-    *n_jobs_out = n;
 }
 
+// One round of a warp's selection: the largest key among the lanes' keys (0 = none), as the largest
+// upper word, then the largest lower word among the lanes that have it.
+__device__ __forceinline__ unsigned long long warp_max_key(unsigned long long key) {
+    const uint32_t hi = (uint32_t)(key >> 32), lo = (uint32_t)key;
+    const uint32_t best_hi = __reduce_max_sync(0xffffffffu, hi);
+    const uint32_t best_lo = __reduce_max_sync(0xffffffffu, hi == best_hi ? lo : 0u);
+    return ((unsigned long long)best_hi << 32) | best_lo;
+}
+
+// the one device copy of the deal (its divisions make it long; a CTA calls it once)
+__device__ __noinline__ uint32_t work_list_once(uint32_t c, uint32_t G, uint32_t n_jobs, uint32_t S, uint32_t RT, uint32_t KU,
+                                                uint32_t KD, uint32_t *items) {
+    const uint32_t n = layer_work_list(c, G, n_jobs, S, RT, KU, KD, items, kMaxItems);
+    return n < kMaxItems ? n : kMaxItems;
+}
+// Nothing on the kernel's paths may live in local memory: nearly all of the SM's L1 is carved out as
+// shared memory, so the 544 threads' stack frames would miss it and every local access would cost
+// an L2 round trip (measured: a 100-instruction block went from 0.25 to 3 microseconds).  Helpers are
+// inlined, arrays are indexed by unrolled loops, and only code that runs once per launch or layer
+// with little live state (the deal, the route records) is kept out of line.
+
+// 544 threads = 17 warps: one sub-partition of the SM holds five of them, so 96 registers per thread
+// is the most the launch can have.
 __global__ void __launch_bounds__(kThreads, 1)
 k_moe_layer_umma(const JobTable *__restrict__ dev_table, const __grid_constant__ JobTable param_table,
                  const float *__restrict__ x, float *d_out, float *__restrict__ y, uint8_t *tiles,
                  unsigned int *counters, uint32_t *__restrict__ status, uint32_t hidden, uint32_t inter,
                  uint32_t ring, unsigned long long *trace, const __grid_constant__ FusedRouter rt,
-                 const __grid_constant__ EpExchange ep) {
+                 const __grid_constant__ EpExchange ep, const StackLayer *__restrict__ stack, uint32_t n_layers,
+                 float *hbuf, uint32_t residual) {
     extern __shared__ __align__(1024) uint8_t smem[];
     __shared__ __align__(8) uint64_t bars[kBars];
     __shared__ __align__(16) uint8_t sE[kExpMax];        // block exponents of the token's digits
     __shared__ __align__(16) uint8_t sEh[2][kExpMax];    // ... of the digit tiles of hidden values
     __shared__ __align__(16) uint8_t s_hst[16 * 2 * 16]; // an up item's digit chunks: [row][block][16 bytes]
     __shared__ float s_up[64];                           // an item's up projection, handed to the gate threads
-    __shared__ float s_mix_w[kJobsMax];                  // the mix, in route order: weight (shared expert: 1)
-    __shared__ uint32_t s_mix_slot[kJobsMax];            //   row of the expert outputs, bit 31 set for the shared expert
-    __shared__ uint32_t s_n_mix;
-    __shared__ Job s_jobs[kJobsMax];                     // the layer's jobs, from the routes or the caller's table
-    __shared__ uint32_t s_n_jobs, s_n_static;
+    // per layer parity: the mix, in route order: weight (shared expert: 1) and row of the expert
+    // outputs, bit 31 set for the shared expert; the layer's jobs, from the routes or the caller's table
+    __shared__ float s_mix_w[2][kJobsMax];
+    __shared__ uint32_t s_mix_slot[2][kJobsMax];
+    __shared__ Job s_jobs[2][kJobsMax];
+    __shared__ uint32_t s_n_mix, s_n_jobs;
     __shared__ uint32_t s_items[kMaxItems];
     __shared__ uint32_t s_n_items;
+    __shared__ unsigned long long s_page[S14_N_ROUTED_EXPERTS];  // the layer's page table, parked a layer ahead
+    __shared__ float s_bias[kRouterSlots];               // the bias of this CTA's experts, likewise
+    __shared__ uint32_t s_pick_id[8];                    // the picked experts by rank, their scores and pages
+    __shared__ float s_pick_score[8];
+    __shared__ unsigned long long s_pick_page[8];
     __shared__ uint32_t tmem_slot;
     __shared__ int abort_flag;
     __shared__ int s_behind;   // expert parallel: a peer's word carries a later step's number
     __shared__ int s_last;     // this CTA finished the last job of a row tile / is the last CTA to leave
     __shared__ uint32_t s_abort_code;
+    __shared__ uint32_t s_dbg;
 
     const uint32_t tid = threadIdx.x, warp = tid >> 5, lane = tid & 31u;
     const uint32_t grid = gridDim.x, cta = blockIdx.x;
@@ -467,47 +506,43 @@ k_moe_layer_umma(const JobTable *__restrict__ dev_table, const __grid_constant__
     const uint32_t KD = inter >> 8;    // units of a down item
     const uint32_t RT = hidden >> 7;   // row tiles of w2
     const uint32_t S = inter >> 6;     // slices of an expert
+    const uint32_t L = n_layers ? n_layers : 1u;
     uint8_t *const sRing = smem;
     uint8_t *const sBx = smem + ring * kSlot;   // the token's digit tile, 2 KB per 256 K-elements
     uint8_t *const sBh = sBx + KU * 2048u;      // two digit tiles of hidden values
     const uint32_t tile_bytes = KD * 2048u;
+    uint8_t *const sWr = sBh + 2u * tile_bytes; // the router rows of this CTA's experts (BF16), a layer ahead
     uint8_t *const tile_exps = tiles + (size_t)kJobsMax * kTileMax;  // [job][kExpMax] after the tiles
     const uint32_t bar0 = smem_u32(bars);
     auto bar = [&](uint32_t i) { return bar0 + i * 8u; };
     volatile int *const abortp = &abort_flag;
     // Optional per-CTA time marks (SM clock) for profiling runs: kTraceWords words per CTA, word 0 the
-    // global timer at entry.  One designated thread writes each mark.
-    unsigned long long *const tr = trace ? trace + (size_t)cta * kTraceWords : nullptr;
+    // global timer at entry; taken in the second layer of a stack (its code has run before), else in
+    // the only one.  One designated thread writes each mark.
+    unsigned long long *const tr_base = trace ? trace + (size_t)cta * kTraceWords : nullptr;
+    const uint32_t trace_layer = L > 1u ? 1u : 0u;
+    unsigned long long *tr = trace_layer == 0u ? tr_base : nullptr;
     auto mark = [&](uint32_t i) {
         if (tr && i < kTraceWords) tr[i] = (unsigned long long)clock64();
     };
-    if (tr && tid == 0) {
+    if (tr_base && tid == 0) {
         unsigned long long gt;
         asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(gt));
-        tr[0] = gt;
-        mark(1);
+        tr_base[0] = gt;
+        tr_base[1] = (unsigned long long)clock64();
     }
 
-    // Thread t owns elements 8t .. 8t+7 of the token (hidden <= 8 x kThreads), for the digits and for
-    // the router's dot products; the router weights of this CTA's experts (cta, cta + grid, ...) are
-    // asked for first, so that they arrive while the CTA sets itself up.
-    const bool routes_here = rt.weight != nullptr;
+    // Thread t < 512 owns elements 8t .. 8t+7 of the token (hidden <= 4096), for the digits and for
+    // the router's dot products.
+    const bool routes_here = rt.weight != nullptr || stack != nullptr;
     const bool ep_on = ep.world > 1u;
     const bool table_param = !routes_here && dev_table == nullptr;
     // the CTA's items are known at once unless the number of jobs depends on the routes (expert
     // parallel: a rank keeps the experts it owns) or the table comes from an earlier kernel
     const bool early = table_param || (routes_here && rt.ep_world <= 1u);
+    const bool token_thread = tid < kTokenThreads;
     const bool has_x = tid < (hidden >> 3);
-    float xs[8] = {0.0f, 0.0f, 0.0f, 0.0f, 0.0f, 0.0f, 0.0f, 0.0f};
-    uint4 rq[kRouterSlots];
-    if (routes_here) {
-#pragma unroll
-        for (uint32_t k = 0; k < kRouterSlots; ++k) {
-            const uint32_t e = cta + k * grid;
-            rq[k] = make_uint4(0u, 0u, 0u, 0u);
-            if (has_x && e < rt.n_experts) rq[k] = ldg_stream(reinterpret_cast<const uint4 *>(rt.weight + (size_t)e * hidden) + tid);
-        }
-    }
+    const bool is_producer = tid == kProdWarp * 32u;
     // The kernel is launched as a programmatic dependent of whatever precedes it in the stream: its
     // CTAs may be placed as soon as SMs are free and set themselves up (barriers, tensor memory, the
     // first copies of pages whose addresses are launch arguments); everything an earlier kernel may
@@ -516,438 +551,662 @@ k_moe_layer_umma(const JobTable *__restrict__ dev_table, const __grid_constant__
     // on.  Weights and page tables are constant during a step.
     cudaTriggerProgrammaticLaunchCompletion();
 
-    if (tid == 0) {
-        for (uint32_t s = 0; s < kMaxRing; ++s) {
-            mbar_init(bar(kBarFull + s), 1);
-            mbar_init(bar(kBarDone + s), 1);
-        }
-        for (uint32_t b = 0; b < 2; ++b) {
-            mbar_init(bar(kBarAccDone + b), 2);
-            mbar_init(bar(kBarAccFree + b), kEpiThreads);
-            mbar_init(bar(kBarHReady + b), kLoadThreads);
-            mbar_init(bar(kBarHFree + b), 2);
-        }
-        mbar_init(bar(kBarXReady), 256);
-        mbar_init(bar(kBarFin), 2);
-        abort_flag = 0;
-        s_behind = 0;
-        s_last = 0;
-        s_abort_code = 0x5501u;
-        s_n_items = 0;
-        s_n_jobs = 0;
-        s_n_static = 0;
-        s_n_mix = 0;
-        if (table_param) {
-            const uint32_t nj = min(param_table.n_jobs, kJobsMax);
-            for (uint32_t j = 0; j < nj; ++j) s_jobs[j] = param_table.jobs[j];
-            const uint32_t m0 = param_table.token_job_begin[0];
-            const uint32_t nm = min(param_table.token_job_begin[1] - m0, kJobsMax);
-            for (uint32_t j = 0; j < nm; ++j) {
-                const Job &jb = param_table.jobs[param_table.token_jobs[m0 + j]];
-                s_mix_w[j] = jb.weight;
-                s_mix_slot[j] = jb.out_index | (jb.is_shared ? 0x80000000u : 0u);
-            }
-            s_n_mix = nm;
-            s_n_jobs = nj;
-            s_n_static = nj;
-        } else if (early) {
-            const uint32_t nj = rt.top_k + (rt.shared_page ? 1u : 0u);
-            if (rt.shared_page) {
-                Job jb;
-                jb.page = rt.shared_page;
-                jb.kind = rt.shared_kind;
-                jb.token = 0;
-                jb.weight = 1.0f;
-                jb.is_shared = 1;
-                jb.out_index = rt.top_k;
-                s_jobs[0] = jb;
-                s_n_static = 1;
-            }
-            s_n_jobs = nj;
-        }
-        if (early) s_n_items = min(layer_work_list(cta, grid, s_n_jobs, S, RT, KU, KD, s_items, kMaxItems), kMaxItems);
+    // ---- set-up: the barriers by the first threads, the jobs and items that are known at launch
+    // by warp 1 ----
+    if (tid < kBars) {
+        uint32_t count = 1u;  // ring slots, routes
+        if (tid >= kBarAccDone && tid < kBarAccDone + 2u) count = 2u;
+        else if (tid >= kBarAccFree && tid < kBarAccFree + 2u) count = kEpiThreads;
+        else if (tid == kBarXReady) count = 256u;
+        else if (tid >= kBarHReady && tid < kBarHReady + 2u) count = kLoadThreads;
+        else if (tid >= kBarHFree && tid < kBarHFree + 2u) count = 2u;
+        else if (tid == kBarFin) count = 2u;
+        mbar_init(bar(tid), count);
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
-    if (warp == kMmaWarp0) {
-        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(&tmem_slot)),
-                     "r"(kTmemCols)
-                     : "memory");
-        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    if (warp == 1u) {
+        uint32_t nj = 0;
+        if (lane == 0) {
+            abort_flag = 0;
+            s_behind = 0;
+            s_last = 0;
+            s_abort_code = 0x5501u;
+            s_dbg = 0;
+            s_n_items = 0;
+            s_n_jobs = 0;
+            s_n_mix = 0;
+        }
+        __syncwarp();
+        if (table_param) {
+            nj = min(param_table.n_jobs, kJobsMax);
+            const uint32_t m0 = param_table.token_job_begin[0];
+            const uint32_t nm = min(param_table.token_job_begin[1] - m0, kJobsMax);
+            if (lane < nj) s_jobs[0][lane] = param_table.jobs[lane];
+            if (lane < nm) {
+                const Job &jb = param_table.jobs[param_table.token_jobs[m0 + lane]];
+                s_mix_w[0][lane] = jb.weight;
+                s_mix_slot[0][lane] = jb.out_index | (jb.is_shared ? 0x80000000u : 0u);
+            }
+            if (lane == 0) {
+                s_n_mix = nm;
+                s_n_jobs = nj;
+            }
+        } else if (early) {
+            nj = rt.top_k + (rt.has_shared ? 1u : 0u);
+            if (lane == 0) s_n_jobs = nj;
+        }
+        if (early && lane == 1u) s_n_items = work_list_once(cta, grid, nj, S, RT, KU, KD, s_items);
     }
-    fence_before();
+    __syncwarp();
     __syncthreads();
-    fence_after();
-    const uint32_t tmem = tmem_slot;
     if (tid == 0) mark(2);
+    // a caller's table is complete now; otherwise the routes barrier opens when the routes are picked
+    if (tid == 32u && table_param) mbar_arrive(bar(kBarRoutes));
 
-    // ---- the copying thread: the units of the CTA's items in order, each one bulk copy of 16 KB of
-    // codes and one of 1 KB of scales into the next ring slot ----
-    uint32_t p_units = 0, p_item = 0, p_unit = 0;  // state of the copying thread
-    bool p_ok = true;
-    auto produce = [&](bool static_only) {
-        const uint32_t n_items = s_n_items, n_static = s_n_static;
-        while (p_ok && p_item < n_items) {
-            const uint32_t item = s_items[p_item], j = (item >> 8) & 0xFFu, idx = item & 0xFFu;
-            if (static_only && (j >= n_static || p_units >= ring)) return;
-            const uint8_t *page = s_jobs[j].page;
-            const bool down = (item & kItemDown) != 0u;
-            const uint32_t nu = down ? KD : KU;
-            const uint8_t *a0 = page + (down ? mxfp4_down_offset(hidden, inter) : 0u) + (size_t)idx * nu * kUnitBytes;
-            const uint8_t *sf0 = page + (down ? mxfp4_s2_offset(hidden, inter) + (size_t)idx * (inter >> 7) * kAtomBytes
-                                              : mxfp4_s13_offset(hidden, inter) + (size_t)idx * (hidden >> 7) * kAtomBytes);
-            while (p_unit < nu) {
-                if (static_only && p_units >= ring) return;
-                const uint32_t s = p_units % ring;
-                if (p_units >= ring && !mbar_wait(bar(kBarDone + s), ((p_units / ring) - 1u) & 1u, abortp)) {
-                    p_ok = false;
-                    return;
-                }
-                const uint32_t dst = smem_u32(sRing + s * kSlot), full = bar(kBarFull + s);
-                mbar_arrive_expect(full, kSlot);
-                bulk_copy(dst, a0 + (size_t)p_unit * kUnitBytes, kUnitBytes, full);
-                bulk_copy(dst + kUnitBytes, sf0 + (size_t)p_unit * kUnitSf, kUnitSf, full);
-                ++p_unit;
-                ++p_units;
-            }
-            p_unit = 0;
-            ++p_item;
-        }
-    };
-    const bool is_producer = tid == kProdWarp * 32u;
-    if (is_producer && early) {
-        produce(true);
-        mark(3);
-    }
-
-    cudaGridDependencySynchronize();
-    const uint32_t ep_step = ep_on ? __ldcg(ep.step) : 0u;
-    if (has_x) {
-        const float4 p0 = __ldcg(reinterpret_cast<const float4 *>(x) + 2u * tid);
-        const float4 p1 = __ldcg(reinterpret_cast<const float4 *>(x) + 2u * tid + 1u);
-        xs[0] = p0.x, xs[1] = p0.y, xs[2] = p0.z, xs[3] = p0.w;
-        xs[4] = p1.x, xs[5] = p1.y, xs[6] = p1.z, xs[7] = p1.w;
-    }
-    if (tid == 0) mark(4);
-
-    if (routes_here) {
-        // ---- expert scores: logit = x . w in double (warp sums, then the sixteen warps in order),
-        // rounded to F32; score and score + bias go to global memory, then the CTA counts itself ----
-        double *s_red = reinterpret_cast<double *>(sBh);  // [slot][warp]; no digit tile is in use yet
-#pragma unroll
-        for (uint32_t k = 0; k < kRouterSlots; ++k) {
-            if (cta + k * grid >= rt.n_experts) break;
-            const uint32_t wd[4] = {rq[k].x, rq[k].y, rq[k].z, rq[k].w};
-            double acc0 = 0.0, acc1 = 0.0;
-#pragma unroll
-            for (int i = 0; i < 4; ++i) {
-                acc0 += (double)xs[i * 2] * (double)__uint_as_float(wd[i] << 16);
-                acc1 += (double)xs[i * 2 + 1] * (double)__uint_as_float(wd[i] & 0xffff0000u);
-            }
-            const double ws = warp_sum(acc0 + acc1);
-            if (lane == 0) s_red[k * (kThreads / 32u) + warp] = ws;
-        }
-        __syncthreads();
-        if (tid < kRouterSlots && cta + tid * grid < rt.n_experts) {
-            const uint32_t e = cta + tid * grid;
-            double sum = 0.0;
-            for (uint32_t w = 0; w < kThreads / 32u; ++w) sum += s_red[tid * (kThreads / 32u) + w];
-            const float sc = router_score_f32(sum, rt.score_fn);
-            rt.scores[e] = sc;
-            rt.select[e] = __fadd_rn(sc, rt.bias ? rt.bias[e] : 0.0f);
-        }
-        __threadfence();
-        __syncthreads();
-        if (tid == 0) {
-            atomicAdd(counters + kCntRoute, 1u);
-            mark(5);
-        }
-    }
-
-    // the token's digits (they do not depend on the routes)
-    if (has_x) digits_of8(xs, tid, sBx, sE);
-    __syncthreads();  // every block exponent is written
-    if (warp < 8u) {
-        store_digit_scales(tmem + kColSfbX, sE, hidden, warp & 3u, warp >> 2, 2u, lane);
-        fence_before();
-        mbar_arrive(bar(kBarXReady));
-    }
-    if (tid == 0) mark(6);
-    if (routes_here) {
-        // every CTA's scores are needed: all CTAs are resident (one per SM), the wait is bounded
-        if (tid == 0) {
-            uint32_t tries = 0;
-            while (ld_acquire(counters + kCntRoute) < grid) {
-                if (++tries > kSpinGlobal) {
-                    abort_flag = 1;
-                    break;
-                }
-                __nanosleep(40);
-            }
-            mark(7);
-        }
-        __syncthreads();
-        if (warp == 0 && !abort_flag) {
-            route_select(rt, lane, cta == 0, s_jobs, &s_n_jobs, s_mix_w, s_mix_slot, &s_n_mix);
-            if (lane == 0 && !early)
-                s_n_items = min(layer_work_list(cta, grid, s_n_jobs, S, RT, KU, KD, s_items, kMaxItems), kMaxItems);
-        }
-        if (tid == 0 && abort_flag) s_n_items = 0;
-    } else if (!table_param) {
-        const JobTable &tab = *dev_table;
-        const uint32_t nj = min(tab.n_jobs, kJobsMax);
-        const uint32_t m0 = tab.token_job_begin[0], nm = min(tab.token_job_begin[1] - m0, kJobsMax);
-        if (tid < nj) s_jobs[tid] = tab.jobs[tid];
-        if (tid < nm) {
-            const uint32_t jb = tab.token_jobs[m0 + tid];
-            s_mix_w[tid] = tab.jobs[jb].weight;
-            s_mix_slot[tid] = tab.jobs[jb].out_index | (tab.jobs[jb].is_shared ? 0x80000000u : 0u);
-        }
-        if (tid == 0) {
-            s_n_jobs = nj;
-            s_n_mix = nm;
-            s_n_items = min(layer_work_list(cta, grid, nj, S, RT, KU, KD, s_items, kMaxItems), kMaxItems);
-        }
-    }
-    fence_async_smem();  // the digit tile is read by the tensor cores
-    __syncthreads();
-    const uint32_t n_jobs = s_n_jobs, n_items = s_n_items;
-    if (tid == 0) {
-        mark(8);
-        if (tr) tr[15] = n_items | (ring << 8) | (n_jobs << 16);
-    }
+    uint32_t p_units = 0;  // units the copying thread has issued
+    uint32_t tmem = 0;
+    const uint32_t ep_step_unused = 0;
+    (void)ep_step_unused;
+    uint32_t ep_step = 0;
 
     if (is_producer) {
-        produce(false);  // every page address is known now
+        // ---- the copying thread: the units of the CTA's items in order, layer after layer, each one
+        // bulk copy (codes and scales, 17 KB of consecutive page bytes) into the next ring slot.  The
+        // items of a layer's shared expert that lead the list are asked for before the layer's routes
+        // exist (its page address is a launch argument); the rest wait (bounded) for the routes. ----
+        uint32_t p_slot = 0, p_round = 0;
+        bool p_ok = true;
+#pragma unroll 1
+        for (uint32_t l = 0; l < L && p_ok; ++l) {
+            const uint32_t par = l & 1u;
+            const uint8_t *shared_page = stack ? stack[l].shared_page : rt.shared_page;
+            const uint32_t n_static = table_param ? s_n_jobs : ((early && rt.has_shared) ? 1u : 0u);
+            if (routes_here && l == 0u) {
+                // the first layer's router rows; those of layer l + 1 follow when layer l's routes are known
+                const uint16_t *wr0 = stack ? stack[0].router_weight : rt.weight;
+                const uint32_t rows = (cta < rt.n_experts ? 1u : 0u) + (cta + grid < rt.n_experts ? 1u : 0u);
+                mbar_arrive_expect(bar(kBarWr), rows * hidden * 2u);
+                for (uint32_t k = 0; k < rows; ++k)
+                    bulk_copy(smem_u32(sWr) + k * hidden * 2u, wr0 + (size_t)(cta + k * grid) * hidden, hidden * 2u, bar(kBarWr));
+            }
+            bool routes_known = table_param;
+            const uint32_t n_items = early ? s_n_items : 0u;  // late lists are read after the routes barrier
+            uint32_t n_it = n_items;
+            for (uint32_t i = 0; p_ok; ++i) {
+                if (!routes_known) {
+                    const bool is_static = i < n_it && ((s_items[i] >> 8) & 0xFFu) < n_static;
+                    if (!is_static) {
+                        if (l == 0u) mark(3);
+                        if (!mbar_wait(bar(kBarRoutes), par, abortp)) {
+                            p_ok = false;
+                            break;
+                        }
+                        routes_known = true;
+                        n_it = s_n_items;
+                        if (routes_here && l + 1u < L) {
+                            // this layer's scores are done: its router rows make room for the next layer's
+                            const uint16_t *wrn = stack[l + 1u].router_weight;
+                            const uint32_t rows = (cta < rt.n_experts ? 1u : 0u) + (cta + grid < rt.n_experts ? 1u : 0u);
+                            mbar_arrive_expect(bar(kBarWr), rows * hidden * 2u);
+                            for (uint32_t k = 0; k < rows; ++k)
+                                bulk_copy(smem_u32(sWr) + k * hidden * 2u, wrn + (size_t)(cta + k * grid) * hidden, hidden * 2u, bar(kBarWr));
+                        }
+                    }
+                }
+                if (i >= n_it) break;
+                const uint32_t item = s_items[i], j = (item >> 8) & 0xFFu, idx = item & 0xFFu;
+                const bool down = (item & kItemDown) != 0u;
+                const uint32_t nu = down ? KD : KU;
+                const uint8_t *page = (!routes_known && !table_param) ? shared_page : s_jobs[par][j].page;
+                const uint8_t *a = page + (down ? mxfp4_down_offset(hidden, inter) : 0u) + (size_t)idx * nu * kUnitStride;
+                for (uint32_t u = 0; u < nu; ++u) {
+                    if (p_round && !mbar_wait(bar(kBarDone + p_slot), (p_round - 1u) & 1u, abortp)) {
+                        p_ok = false;
+                        break;
+                    }
+                    const uint32_t full = bar(kBarFull + p_slot);
+                    mbar_arrive_expect(full, kSlot);
+                    bulk_copy(smem_u32(sRing) + p_slot * kSlot, a, kSlot, full);
+                    a += kUnitStride;
+                    ++p_units;
+                    if (++p_slot == ring) {
+                        p_slot = 0;
+                        ++p_round;
+                    }
+                }
+            }
+        }
         mark(12);
-    } else if ((warp == kMmaWarp0 || warp == kMmaWarp0 + 1u) && lane == 0) {
-        // ---- MMA issue.  Issuing a tcgen05 operation costs the thread 70-90 cycles (measured), more
-        // than a 16 KB unit may take, so two threads issue: thread m takes units m, m + 2, ... of every
-        // item (every item has an even number of units and the ring an even number of slots, so a slot
-        // always belongs to the same thread, which sees each phase of its barrier) and accumulates
-        // into an accumulator of its own.  Items alternate between two accumulator buffers. ----
-        const uint32_t m = warp - kMmaWarp0;
-        const uint64_t a_desc0 = smem_desc(smem_u32(sRing), 1, 64, 2);
-        const uint64_t sf_desc0 = smem_desc(smem_u32(sRing) + kUnitBytes, 0, 8, 0);
-        const uint64_t bx_desc0 = smem_desc(smem_u32(sBx), 1, 64, 2);
-        const uint32_t sfa_t = tmem + kColSfa + m * 16u;  // a thread's copies and MMAs execute in issue order
-        bool ok = n_items == 0u || mbar_wait(bar(kBarXReady), 0, abortp);
-        uint32_t g0 = 0, n_loaded = 0, cur_job = 0xFFFFFFFFu, hb = 0;
-        for (uint32_t i = 0; i < n_items && ok; ++i) {
-            const uint32_t item = s_items[i], j = (item >> 8) & 0xFFu, buf = i & 1u;
-            const bool down = (item & kItemDown) != 0u;
-            const uint32_t nu = down ? KD : KU;
-            if (i >= 2u) ok = mbar_wait(bar(kBarAccFree + buf), ((i - 2u) >> 1) & 1u, abortp);
-            uint64_t b_desc0 = bx_desc0;
-            uint32_t sfb0 = tmem + kColSfbX;
-            bool last_user = false;
-            if (down) {
-                if (j != cur_job) {
-                    hb = n_loaded & 1u;
-                    ok = ok && mbar_wait(bar(kBarHReady + hb), (n_loaded >> 1) & 1u, abortp);
+    } else if (token_thread) {
+        uint32_t gi0 = 0;                       // items of earlier layers
+        uint32_t m_slot = warp - kMmaWarp0, m_round = 0;  // issuing threads: position in the CTA's sequence of units
+        uint32_t n_loaded = 0;                  // digit tiles of hidden values so far (issuing and tile threads)
+        bool alive = true;
+#pragma unroll 1
+        for (uint32_t l = 0; l < L; ++l) {
+            const uint32_t par = l & 1u;
+            tr = (l == trace_layer) ? tr_base : nullptr;
+            // what a layer of a stack brings of its own; a single layer takes it from the launch arguments
+            const uint16_t *const l_wr = stack ? stack[l].router_weight : rt.weight;
+            const float *const l_bias = stack ? stack[l].bias : rt.bias;
+            const uint8_t *const *const l_table = stack ? stack[l].page_table : rt.page_table;
+            const uint8_t *const l_shared = stack ? stack[l].shared_page : rt.shared_page;
+            int32_t *const l_ids = stack ? stack[l].ids_out : rt.ids_out;
+            float *const l_weights = stack ? stack[l].weights_out : rt.weights_out;
+            float *const l_y = stack ? stack[l].y_out : nullptr;
+            float *const scores = rt.scores + par * S14_N_ROUTED_EXPERTS, *const select = rt.select + par * S14_N_ROUTED_EXPERTS;
+            const float *xsrc = l == 0u ? x : hbuf + (size_t)par * hidden;
+            float *const xdst = (l + 1u == L) ? y : hbuf + (size_t)(par ^ 1u) * hidden;
+            // The layer's router rows of this CTA's experts (cta, cta + grid) come into shared memory by
+            // bulk copies a layer ahead; the bias of those experts and the page table are parked in shared
+            // memory by the threads that need them, right after the routing of the layer before (the first
+            // layer's before the token is waited for): with the weight stream saturating the memory, such
+            // a load takes microseconds, which nobody may wait for once the token is there.
+            float xs[8] = {0.0f, 0.0f, 0.0f, 0.0f, 0.0f, 0.0f, 0.0f, 0.0f};
+            (void)l_wr;
+            if (routes_here && l == 0u) {
+                if (warp == kRouteWarp && lane < kRouterSlots)
+                    s_bias[lane] = (cta + lane * grid < rt.n_experts && l_bias) ? __ldg(l_bias + cta + lane * grid) : 0.0f;
+                if (warp >= kLoadWarp0 && tid - kLoadWarp0 * 32u < rt.n_experts)
+                    s_page[tid - kLoadWarp0 * 32u] = __ldg(reinterpret_cast<const unsigned long long *>(l_table) + (tid - kLoadWarp0 * 32u));
+            }
+            if (l == 0u) {
+                cudaGridDependencySynchronize();
+                ep_step = ep_on ? __ldcg(ep.step) : 0u;
+            } else {
+                // the token of this layer is the output of the one before: every row tile must be mixed
+                bool ok = alive;
+                if (tid == 0 && ok) {
+                    uint32_t tries = 0;
+                    while (ld_acquire(counters + kCntMixed) < RT * l) {
+                        if (++tries > kSpinGlobal || abort_flag) {
+                            abort_flag = 1;
+                            ok = false;
+                            break;
+                        }
+                        __nanosleep(20);
+                    }
+                }
+                alive = token_all(ok && !abort_flag);
+                if (!alive) break;
+            }
+            if (has_x) {
+                const float4 p0 = __ldcg(reinterpret_cast<const float4 *>(xsrc) + 2u * tid);
+                const float4 p1 = __ldcg(reinterpret_cast<const float4 *>(xsrc) + 2u * tid + 1u);
+                xs[0] = p0.x, xs[1] = p0.y, xs[2] = p0.z, xs[3] = p0.w;
+                xs[4] = p1.x, xs[5] = p1.y, xs[6] = p1.z, xs[7] = p1.w;
+            }
+            if (tid == 0) mark(4);
+            // tensor memory, while the first token is on its way
+            if (l == 0u && warp == kMmaWarp0) {
+                asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(&tmem_slot)),
+                             "r"(kTmemCols)
+                             : "memory");
+                asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+                fence_before();
+            }
+
+            if (routes_here) {
+                // ---- expert scores: logit = x . w in double (warp sums, then the sixteen warps in order),
+                // rounded to F32; score and score + bias go to global memory, then the CTA counts itself ----
+                double *s_red = reinterpret_cast<double *>(sBh);  // [slot][warp]; no digit tile is in use now
+                const bool wr_ok = mbar_wait(bar(kBarWr), par, abortp);
+#pragma unroll
+                for (uint32_t k = 0; k < kRouterSlots; ++k) {
+                    if (cta + k * grid < rt.n_experts) {  // uniform in the CTA
+                        uint4 q = make_uint4(0u, 0u, 0u, 0u);
+                        if (has_x && wr_ok) q = reinterpret_cast<const uint4 *>(sWr + k * hidden * 2u)[tid];
+                        const uint32_t wd[4] = {q.x, q.y, q.z, q.w};
+                        double acc0 = 0.0, acc1 = 0.0;
+#pragma unroll
+                        for (int i = 0; i < 4; ++i) {
+                            acc0 += (double)xs[i * 2] * (double)__uint_as_float(wd[i] << 16);
+                            acc1 += (double)xs[i * 2 + 1] * (double)__uint_as_float(wd[i] & 0xffff0000u);
+                        }
+                        const double ws = warp_sum(acc0 + acc1);
+                        if (lane == 0) s_red[k * (kTokenThreads / 32u) + warp] = ws;
+                    }
+                }
+                if (tid == 0) mark(64);
+                if (trace && l == trace_layer) atomicAdd(&s_dbg, 1u);
+                token_sync();
+                if (tid == kRouteWarp * 32u) {
+                    mark(65);
+                    if (tr) tr[80] = s_dbg;
+                }
+                // one warp finishes the scores, publishes them and counts the CTA while the other warps
+                // turn to the digits
+                if (warp == kRouteWarp) {
+                    if (lane < kRouterSlots && cta + lane * grid < rt.n_experts) {
+                        const uint32_t e = cta + lane * grid;
+                        double sum = 0.0;
+                        for (uint32_t w = 0; w < kTokenThreads / 32u; ++w) sum += s_red[lane * (kTokenThreads / 32u) + w];
+                        const float sc = router_score_f32(sum, rt.score_fn);
+                        scores[e] = sc;
+                        select[e] = __fadd_rn(sc, s_bias[lane]);
+                    }
+                    __syncwarp();
+                    if (lane == 0) {
+                        mark(66);
+                        __threadfence();
+                        mark(67);
+                        atomicAdd(counters + kCntRoute, 1u);
+                        mark(5);
+                    }
+                    __syncwarp();
+                    if (l + 1u < L && lane < kRouterSlots) {
+                        const float *nb = stack[l + 1u].bias;
+                        s_bias[lane] = (cta + lane * grid < rt.n_experts && nb) ? __ldg(nb + cta + lane * grid) : 0.0f;
+                    }
+                }
+            }
+
+            // the token's digits (they do not depend on the routes)
+            if (has_x) digits_of8(xs, tid, sBx, sE);
+            fence_async_smem();  // the digit tile is read by the tensor cores
+            if (tid == 0) mark(9);
+            token_sync();        // every block exponent is written, the tensor memory address too; s_red is not read any more
+            fence_after();
+            tmem = tmem_slot;
+            if (tid == 0) mark(10);
+            if (warp < 8u) {
+                store_digit_scales(tmem + kColSfbX, sE, hidden, warp & 3u, warp >> 2, 2u, lane);
+                fence_before();
+                mbar_arrive(bar(kBarXReady));
+            }
+            if (tid == 0) mark(6);
+            if (routes_here && warp >= kLoadWarp0) {
+                // ---- the routes, by the 256 tile threads: thread e takes expert e.  Every CTA's scores are
+                // needed: all CTAs are resident (one per SM), the wait is bounded.  An expert's rank is the
+                // number of experts that come before it (larger score + bias, or the same and a lower id);
+                // the experts of rank < top_k are the routes, in rank order. ----
+                const uint32_t lt = tid - kLoadWarp0 * 32u;
+                bool ok = true;
+                if (lt == 0) {
+                    uint32_t tries = 0;
+                    while (ld_acquire(counters + kCntRoute) < grid * (l + 1u)) {
+                        if (++tries > kSpinGlobal || abort_flag) {
+                            ok = false;
+                            break;
+                        }
+                        __nanosleep(20);
+                    }
+                    mark(7);
+                }
+                ok = load_all(ok);
+                if (ok) {
+                    // every warp picks the top_k of its 32 experts (one hardware reduction per word and
+                    // round), then the first warp picks the top_k of the 8 x top_k candidates
+                    unsigned long long *s_cand = reinterpret_cast<unsigned long long *>(sBh);   // [8 warps][8]
+                    float *s_cand_score = reinterpret_cast<float *>(sBh + 512);                 // [64]
+                    unsigned long long *s_cand_page = reinterpret_cast<unsigned long long *>(sBh + 1024);  // [64]
+                    const uint32_t wl = warp - kLoadWarp0;
+                    unsigned long long key = 0ull;
+                    float sc = 0.0f;
+                    if (lt < rt.n_experts) {
+                        const uint32_t bits = __float_as_uint(__ldcg(select + lt));
+                        sc = __ldcg(scores + lt);
+                        const uint32_t ordered = (bits & 0x80000000u) ? ~bits : (bits | 0x80000000u);
+                        key = ((unsigned long long)ordered << 32) | (unsigned long long)(0xffffffffu - lt);
+                    }
+                    if (lt == 0) mark(68);
+                    for (uint32_t r = 0; r < rt.top_k; ++r) {
+                        const unsigned long long best = warp_max_key(key);
+                        if (key == best && key != 0ull) {
+                            s_cand_score[wl * 8u + r] = sc;
+                            s_cand_page[wl * 8u + r] = s_page[lt];
+                            key = 0ull;
+                        }
+                        if (lane == 0) s_cand[wl * 8u + r] = best;
+                    }
+                    if (lt == 0) mark(69);
+                    load_sync();
+                    if (wl == 0u) {
+                        // lanes 0-31: candidates lane and lane + 32 (slot = warp * 8 + round; rounds >= top_k are empty)
+                        unsigned long long k0 = (lane & 7u) < rt.top_k ? s_cand[lane] : 0ull;
+                        unsigned long long k1 = (lane & 7u) < rt.top_k ? s_cand[lane + 32u] : 0ull;
+                        for (uint32_t r = 0; r < rt.top_k; ++r) {
+                            const unsigned long long best = warp_max_key(k0 > k1 ? k0 : k1);
+                            if (best != 0ull && (k0 == best || k1 == best)) {
+                                const uint32_t slot = k0 == best ? lane : lane + 32u;
+                                s_pick_id[r] = 0xffffffffu - (uint32_t)best;
+                                s_pick_score[r] = s_cand_score[slot];
+                                s_pick_page[r] = s_cand_page[slot];
+                                if (k0 == best) k0 = 0ull;
+                                else k1 = 0ull;
+                            }
+                        }
+                        __syncwarp();
+                        if (lane == 0) mark(71);
+                        RouteConsts rc;
+                        rc.top_k = rt.top_k;
+                        rc.has_shared = rt.has_shared;
+                        rc.shared_here = (rt.has_shared && rt.shared_owner == rt.ep_rank) ? 1u : 0u;
+                        rc.shared_kind = rt.shared_kind;
+                        rc.ep_rank = rt.ep_rank;
+                        rc.ep_world = rt.ep_world;
+                        rc.route_scale = rt.route_scale;
+                        routes_from_picks(rc, l_shared, l_ids, l_weights, lane, s_pick_id, s_pick_score, s_pick_page, cta == 0, s_jobs[par], &s_n_jobs,
+                                          s_mix_w[par], s_mix_slot[par], &s_n_mix);
+                        __syncwarp();
+                        if (lane == 0 && !early)
+                            s_n_items = work_list_once(cta, grid, s_n_jobs, S, RT, KU, KD, s_items);
+                        __syncwarp();
+                    }
+                } else if (lt == 0) {
+                    abort_flag = 1;
+                    s_n_items = 0;
+                }
+                if (lt == 0) {
+                    mark(72);
+                    mbar_arrive(bar(kBarRoutes));
+                }
+                if (l + 1u < L) {
+                    load_sync();  // every candidate's page has been read
+                    if (lt < rt.n_experts)
+                        s_page[lt] = __ldg(reinterpret_cast<const unsigned long long *>(stack[l + 1u].page_table) + lt);
+                }
+            } else if (!routes_here && !table_param && warp == kRouteWarp) {
+                const JobTable &tab = *dev_table;
+                const uint32_t nj = min(tab.n_jobs, kJobsMax);
+                const uint32_t m0 = tab.token_job_begin[0], nm = min(tab.token_job_begin[1] - m0, kJobsMax);
+                if (lane < nj) s_jobs[0][lane] = tab.jobs[lane];
+                if (lane < nm) {
+                    const uint32_t jb = tab.token_jobs[m0 + lane];
+                    s_mix_w[0][lane] = tab.jobs[jb].weight;
+                    s_mix_slot[0][lane] = tab.jobs[jb].out_index | (tab.jobs[jb].is_shared ? 0x80000000u : 0u);
+                }
+                if (lane == 0) {
+                    s_n_jobs = nj;
+                    s_n_mix = nm;
+                    s_n_items = work_list_once(cta, grid, nj, S, RT, KU, KD, s_items);
+                }
+                __syncwarp();
+                if (lane == 0) mbar_arrive(bar(kBarRoutes));
+            }
+
+            // ---- roles.  Each waits (bounded) until the jobs and the CTA's items are there ----
+            const bool is_issuer = (warp == kMmaWarp0 || warp == kMmaWarp0 + 1u) && lane == 0;
+            const bool role_thread = is_issuer || warp < kEpiThreads / 32u || warp >= kLoadWarp0;
+            bool routes_ok = true;
+            if (role_thread) routes_ok = mbar_wait(bar(kBarRoutes), par, abortp);
+            const uint32_t n_jobs = routes_ok ? s_n_jobs : 0u, n_items = routes_ok ? s_n_items : 0u;
+            if (tid == 0) {
+                mark(8);
+                if (tr) tr[15] = n_items | (ring << 8) | (n_jobs << 16);
+            }
+
+            if (is_issuer) {
+                // ---- MMA issue.  Issuing a tcgen05 operation costs the thread 70-90 cycles (measured), more
+                // than a 16 KB unit may take, so two threads issue: thread m takes units m, m + 2, ... of every
+                // item (every item has an even number of units and the ring an even number of slots, so a slot
+                // always belongs to the same thread, which sees each phase of its barrier) and accumulates
+                // into an accumulator of its own.  Items alternate between two accumulator buffers. ----
+                const uint32_t m = warp - kMmaWarp0;
+                const uint64_t a_desc0 = smem_desc(smem_u32(sRing), 1, 64, 2);
+                const uint64_t sf_desc0 = smem_desc(smem_u32(sRing) + kUnitBytes, 0, 8, 0);
+                const uint64_t bx_desc0 = smem_desc(smem_u32(sBx), 1, 64, 2);
+                const uint32_t sfa_t = tmem + kColSfa + m * 16u;  // a thread's copies and MMAs execute in issue order
+                bool ok = n_items == 0u || mbar_wait(bar(kBarXReady), par, abortp);
+                uint32_t cur_job = 0xFFFFFFFFu, hb = 0;
+#pragma unroll 1
+                for (uint32_t i = 0; i < n_items && ok; ++i) {
+                    const uint32_t gi = gi0 + i;
+                    const uint32_t item = s_items[i], j = (item >> 8) & 0xFFu, buf = gi & 1u;
+                    const bool down = (item & kItemDown) != 0u;
+                    const uint32_t nu = down ? KD : KU;
+                    if (gi >= 2u) ok = mbar_wait(bar(kBarAccFree + buf), ((gi - 2u) >> 1) & 1u, abortp);
+                    uint64_t b_desc0 = bx_desc0;
+                    uint32_t sfb0 = tmem + kColSfbX;
+                    bool last_user = false;
+                    if (down) {
+                        if (j != cur_job) {
+                            hb = n_loaded & 1u;
+                            ok = ok && mbar_wait(bar(kBarHReady + hb), (n_loaded >> 1) & 1u, abortp);
+                            cur_job = j;
+                            ++n_loaded;
+                        }
+                        b_desc0 = smem_desc(smem_u32(sBh + hb * tile_bytes), 1, 64, 2);
+                        sfb0 = tmem + kColSfbH + hb * 128u;
+                        last_user = i + 1u >= n_items || ((s_items[i + 1u] >> 8) & 0xFFu) != j;
+                    }
+                    if (!ok) break;
+                    fence_after();
+                    const uint32_t acc = tmem + kColAcc + (buf * 2u + m) * 16u;
+#pragma unroll 1
+                    for (uint32_t ku = m; ku < nu; ku += 2u) {
+                        const uint32_t s = m_slot;
+                        ok = mbar_wait(bar(kBarFull + s), m_round & 1u, abortp);
+                        if (!ok) break;
+                        m_slot += 2u;
+                        if (m_slot >= ring) {
+                            m_slot -= ring;
+                            ++m_round;
+                        }
+                        if (ku == 0u) mark(16u + i * 4u);
+                        fence_after();
+                        const uint64_t sfd = sf_desc0 + s * (kSlot >> 4);
+                        tmem_copy_scales(sfa_t, sfd);
+                        tmem_copy_scales(sfa_t + 4u, sfd + (kAtomBytes >> 4));
+                        const uint64_t ad = a_desc0 + s * (kSlot >> 4), bd = b_desc0 + ku * (2048u >> 4);
+                        const uint32_t sfb_t = sfb0 + ku * 8u;
+#pragma unroll
+                        for (uint32_t kk = 0; kk < 4; ++kk) {
+                            const uint32_t atom = kk >> 1, sfid = (kk & 1u) * 2u;
+                            umma_mxf4(acc, ad + kk * 2u, bd + kk * 2u, kIdesc | (sfid << 29) | (sfid << 4),
+                                      (sfa_t + atom * 4u) | (sfid << 30), (sfb_t + atom * 4u) | (sfid << 30),
+                                      (ku >= 2u || kk) ? 1u : 0u);
+                        }
+                        umma_commit(bar(kBarDone + s));
+                    }
+                    if (!ok) break;
+                    umma_commit(bar(kBarAccDone + buf));
+                    if (down && last_user) umma_commit(bar(kBarHFree + hb));
+                }
+            } else if (warp < kEpiThreads / 32u) {
+                // ---- epilogue: the item's two accumulators (sixteen digit columns each) are added in double
+                // and rounded once ----
+                const uint32_t row = tid;
+                const uint32_t lane_base = tmem + ((warp * 32u) << 16);
+                bool ok = true;
+                if (ep_on && n_items) {
+                    // A slot buffer may be written for step s only when every peer has finished reading step
+                    // s - 2 from it: each rank tells every other rank the number of steps it has finished
+                    // (one 8-byte word per rank in the exchange buffer).
+                    if (tid == 0) {
+                        const unsigned long long *mine = ep.slots[ep.rank] + 2u * (size_t)(S14_EXPERTS_PER_TOKEN + 1) * hidden + 8u;
+                        for (uint32_t p = 0; p < ep.world && ok; ++p) {
+                            if (p == ep.rank) continue;
+                            uint32_t tries = 0;
+                            while ((int32_t)((uint32_t)ld_relaxed_sys(mine + p) - ep_step + 1u) < 0) {
+                                if (++tries > ep.wait_limit || abort_flag) {
+                                    ok = false;
+                                    s_abort_code = 0x5505u;
+                                    abort_flag = 1;
+                                    break;
+                                }
+                                __nanosleep(100);
+                            }
+                        }
+                    }
+                    ok = epi_all(ok);
+                }
+#pragma unroll 1
+                for (uint32_t i = 0; i < n_items && ok; ++i) {
+                    const uint32_t gi = gi0 + i;
+                    const uint32_t item = s_items[i], j = (item >> 8) & 0xFFu, idx = item & 0xFFu, buf = gi & 1u;
+                    const bool down = (item & kItemDown) != 0u;
+                    ok = epi_all(mbar_wait(bar(kBarAccDone + buf), (gi >> 1) & 1u, abortp));
+                    if (!ok) break;
+                    if (tid == 0) mark(17u + i * 4u);
+                    fence_after();
+                    // the accumulators of the even and of the odd units, one after the other (sixteen registers at a time)
+                    double sum = 0.0;
+#pragma unroll
+                    for (uint32_t half = 0; half < 2; ++half) {
+                        uint32_t a[16];
+                        tmem_ld16(lane_base + kColAcc + (buf * 2u + half) * 16u, a);
+                        tmem_ld_wait();
+                        double lo = 0.0, hi = 0.0;  // the digits of lo (columns 8-15) and of hi (0-7): two chains
+#pragma unroll
+                        for (int c = 0; c < 8; ++c) {
+                            lo += (double)__uint_as_float(a[8 + c]);
+                            hi += (double)__uint_as_float(a[c]);
+                        }
+                        sum += lo + hi;
+                    }
+                    fence_before();
+                    mbar_arrive(bar(kBarAccFree + buf));
+                    if (tid == 0) mark(52u + i);
+                    const float v = (float)sum;
+                    if (!down) {
+                        // lanes 0-63: gate of the slice's element `row`; lanes 64-127: its up projection
+                        if (row >= 64u) s_up[row - 64u] = v;
+                        epi_sync();
+                        int E = -80;
+                        if (row < 64u) {
+                            // hidden value `row` of the slice -> sixteen digit nibbles; scale block = warp
+                            const float hv = swiglu_limit_f32(v, s_up[row]);
+                            float bm = fabsf(hv);
+#pragma unroll
+                            for (int o = 16; o > 0; o >>= 1) bm = fmaxf(bm, __shfl_xor_sync(0xffffffffu, bm, o));
+                            E = block_exponent(bm);
+                            uint32_t hw, lw;
+                            digit_codes16(hv, __uint_as_float((uint32_t)(150 - E) << 23), hw, lw);
+                            const uint32_t ohw = __shfl_xor_sync(0xffffffffu, hw, 1), olw = __shfl_xor_sync(0xffffffffu, lw, 1);
+                            // byte lane / 2 of every row's chunk holds the nibbles of lanes 2b (low) and 2b + 1; even
+                            // lanes write digit rows 0-3 and 8-11, odd lanes 4-7 and 12-15
+                            const uint32_t e_hw = (lane & 1u) ? ohw : hw, o_hw = (lane & 1u) ? hw : ohw;
+                            const uint32_t e_lw = (lane & 1u) ? olw : lw, o_lw = (lane & 1u) ? lw : olw;
+#pragma unroll
+                            for (uint32_t jj = 0; jj < 4; ++jj) {
+                                const uint32_t dj = (lane & 1u) * 4u + jj;
+                                s_hst[(dj * 2u + warp) * 16u + (lane >> 1)] =
+                                    (uint8_t)(((e_hw >> (4u * dj)) & 0xFu) | (((o_hw >> (4u * dj)) & 0xFu) << 4));
+                                s_hst[((8u + dj) * 2u + warp) * 16u + (lane >> 1)] =
+                                    (uint8_t)(((e_lw >> (4u * dj)) & 0xFu) | (((o_lw >> (4u * dj)) & 0xFu) << 4));
+                            }
+                        }
+                        epi_sync();
+                        if (tid == 0) mark(58u + i);
+                        uint8_t *tile = tiles + (size_t)j * kTileMax;
+                        if (tid < 32u) {
+                            // chunk (digit row, block) of the slice -> its place in the job's digit tile
+                            const uint32_t dj = tid >> 1, blk = tid & 1u, cc = (idx & 3u) * 2u + blk;
+                            const uint4 c16 = *reinterpret_cast<const uint4 *>(s_hst + (dj * 2u + blk) * 16u);
+                            __stcg(reinterpret_cast<uint4 *>(tile + (idx >> 2) * 2048u + dj * 128u + ((cc ^ (dj & 7u)) << 4)), c16);
+                        }
+                        if (row < 64u && lane == 0) tile_exps[(size_t)j * kExpMax + idx * 2u + warp] = (uint8_t)(E + 100);
+                        epi_sync();  // the group's stores are ordered before thread 0's fence, which publishes them
+                        if (tid == 0) {
+                            __threadfence();
+                            atomicAdd(counters + kCntJob0 + j, 1u);
+                        }
+                    } else {
+                        // row idx * 128 + `row` of the expert's output
+                        const uint32_t n = idx * 128u + row, slot = s_jobs[par][j].out_index;
+                        if (ep_on) {
+                            // into the route slot's row of every rank's slot buffer, the value with the step's
+                            // number in one 8-byte store
+                            const size_t at = ((size_t)(ep_step & 1u) * ep.n_slots + slot) * hidden + n;
+                            const unsigned long long word = ((unsigned long long)(ep_step + 1u) << 32) | __float_as_uint(v);
+                            for (uint32_t p = 0; p < ep.world; ++p) st_relaxed_sys(ep.slots[p] + at, word);
+                        } else {
+                            __stcg(d_out + (size_t)slot * hidden + n, v);
+                            if (xdst) {
+                                // ---- the last job of the row tile to finish applies the ordered mix
+                                // (examples/s14_vulkan_numeric.rs:936-946): acc = 0; acc += w * d in route order;
+                                // acc += d_shared.  In a stack the result, plus the layer's input if the stack
+                                // keeps a residual, is the next layer's token. ----
+                                epi_sync();
+                                if (tid == 0) {
+                                    __threadfence();
+                                    s_last = atomicAdd(counters + kCntTile0 + idx, 1u) == n_jobs * (l + 1u) - 1u;
+                                }
+                                epi_sync();
+                                if (s_last) {
+                                    __threadfence();
+                                    const uint32_t nm = s_n_mix;
+                                    float acc = 0.0f;
+                                    for (uint32_t jj = 0; jj < nm; ++jj) {
+                                        const uint32_t ms = s_mix_slot[par][jj];
+                                        const float dv = __ldcg(d_out + (size_t)(ms & 0x7FFFFFFFu) * hidden + n);
+                                        acc = (ms >> 31) ? __fadd_rn(acc, dv) : __fadd_rn(acc, __fmul_rn(s_mix_w[par][jj], dv));
+                                    }
+                                    if (l_y) l_y[n] = acc;
+                                    xdst[n] = residual ? __fadd_rn(__ldcg(xsrc + n), acc) : acc;
+                                    if (L > 1u) {
+                                        epi_sync();
+                                        if (tid == 0) {
+                                            __threadfence();
+                                            atomicAdd(counters + kCntMixed, 1u);
+                                        }
+                                    }
+                                }
+                                epi_sync();  // s_last is read before the next item writes it
+                            }
+                        }
+                    }
+                    if (tid == 0) mark(18u + i * 4u);
+                }
+            } else if (warp >= kLoadWarp0) {
+                // ---- digit tiles of the down items: wait (bounded) until every slice of the job has been
+                // counted, then take the job's tile from global memory (L2) into one of two tile buffers
+                // and its scale codes into tensor memory ----
+                const uint32_t lt = tid - kLoadWarp0 * 32u;
+                uint32_t cur_job = 0xFFFFFFFFu;
+                bool ok = true;
+                for (uint32_t i = 0; i < n_items && ok; ++i) {
+                    const uint32_t item = s_items[i], j = (item >> 8) & 0xFFu;
+                    if (!(item & kItemDown) || j == cur_job) continue;
+                    const uint32_t hb = n_loaded & 1u;
+                    bool mine = true;
+                    if (lt == 0) {
+                        if (n_loaded >= 2u) mine = mbar_wait(bar(kBarHFree + hb), ((n_loaded >> 1) - 1u) & 1u, abortp);
+                        uint32_t tries = 0;
+                        while (mine && ld_acquire(counters + kCntJob0 + j) < S * (l + 1u)) {
+                            if (++tries > kSpinGlobal || abort_flag) {
+                                abort_flag = 1;
+                                mine = false;
+                            }
+                            __nanosleep(20);
+                        }
+                    }
+                    ok = load_all(mine);
+                    if (!ok) break;
+                    if (lt == 0) mark(40u + i);
+                    const uint8_t *src = tiles + (size_t)j * kTileMax;
+                    uint8_t *dst = sBh + hb * tile_bytes;
+                    for (uint32_t o = lt * 16u; o < tile_bytes; o += kLoadThreads * 16u)
+                        *reinterpret_cast<uint4 *>(dst + o) = __ldcg(reinterpret_cast<const uint4 *>(src + o));
+                    if (lt < (inter >> 7))
+                        reinterpret_cast<uint32_t *>(sEh[hb])[lt] = __ldcg(reinterpret_cast<const uint32_t *>(tile_exps + (size_t)j * kExpMax) + lt);
+                    fence_async_smem();
+                    load_sync();
+                    if (lt == 0) mark(46u + i);
+                    if (warp < kLoadWarp0 + 4u) {
+                        store_digit_scales(tmem + kColSfbH + hb * 128u, sEh[hb], inter, warp & 3u, 0u, 1u, lane);
+                        fence_before();
+                    }
+                    mbar_arrive(bar(kBarHReady + hb));
+                    if (lt == 0) mark(19u + i * 4u);
                     cur_job = j;
                     ++n_loaded;
                 }
-                b_desc0 = smem_desc(smem_u32(sBh + hb * tile_bytes), 1, 64, 2);
-                sfb0 = tmem + kColSfbH + hb * 128u;
-                last_user = i + 1u >= n_items || ((s_items[i + 1u] >> 8) & 0xFFu) != j;
             }
-            if (!ok) break;
-            fence_after();
-            const uint32_t acc = tmem + kColAcc + (buf * 2u + m) * 16u;
-            for (uint32_t ku = m; ku < nu; ku += 2u) {
-                const uint32_t gu = g0 + ku, s = gu % ring;
-                ok = mbar_wait(bar(kBarFull + s), (gu / ring) & 1u, abortp);
-                if (!ok) break;
-                if (ku == 0u) mark(16u + i * 4u);
-                fence_after();
-                const uint64_t sfd = sf_desc0 + s * (kSlot >> 4);
-                tmem_copy_scales(sfa_t, sfd);
-                tmem_copy_scales(sfa_t + 4u, sfd + (kAtomBytes >> 4));
-                const uint64_t ad = a_desc0 + s * (kSlot >> 4), bd = b_desc0 + ku * (2048u >> 4);
-                const uint32_t sfb_t = sfb0 + ku * 8u;
-#pragma unroll
-                for (uint32_t kk = 0; kk < 4; ++kk) {
-                    const uint32_t atom = kk >> 1, sfid = (kk & 1u) * 2u;
-                    umma_mxf4(acc, ad + kk * 2u, bd + kk * 2u, kIdesc | (sfid << 29) | (sfid << 4),
-                              (sfa_t + atom * 4u) | (sfid << 30), (sfb_t + atom * 4u) | (sfid << 30),
-                              (ku >= 2u || kk) ? 1u : 0u);
-                }
-                umma_commit(bar(kBarDone + s));
+            // the issuing threads count the tiles too (the other threads of their warps do not care)
+            if (!(warp >= kLoadWarp0) && !is_issuer) {
+                // nothing: only the issuing and the tile threads track n_loaded
             }
-            if (!ok) break;
-            umma_commit(bar(kBarAccDone + buf));
-            if (down && last_user) umma_commit(bar(kBarHFree + hb));
-            g0 += nu;
+            gi0 += n_items;
         }
-        // nothing of this CTA's tensor work is in flight when the tensor memory is freed
-        umma_commit(bar(kBarFin));
-        mbar_wait(bar(kBarFin), 0, abortp);
-    } else if (warp < kEpiThreads / 32u) {
-        // ---- epilogue: the item's two accumulators (sixteen digit columns each) are added in double
-        // and rounded once ----
-        const uint32_t row = tid;
-        const uint32_t lane_base = tmem + ((warp * 32u) << 16);
-        bool ok = true;
-        if (ep_on && n_items) {
-            // A slot buffer may be written for step s only when every peer has finished reading step
-            // s - 2 from it: each rank tells every other rank the number of steps it has finished
-            // (one 8-byte word per rank in the exchange buffer).
-            if (tid == 0) {
-                const unsigned long long *mine = ep.slots[ep.rank] + 2u * (size_t)(S14_EXPERTS_PER_TOKEN + 1) * hidden + 8u;
-                for (uint32_t p = 0; p < ep.world && ok; ++p) {
-                    if (p == ep.rank) continue;
-                    uint32_t tries = 0;
-                    while ((int32_t)((uint32_t)ld_relaxed_sys(mine + p) - ep_step + 1u) < 0) {
-                        if (++tries > ep.wait_limit || abort_flag) {
-                            ok = false;
-                            s_abort_code = 0x5505u;
-                            abort_flag = 1;
-                            break;
-                        }
-                        __nanosleep(100);
-                    }
-                }
-            }
-            ok = epi_all(ok);
-        }
-        for (uint32_t i = 0; i < n_items && ok; ++i) {
-            const uint32_t item = s_items[i], j = (item >> 8) & 0xFFu, idx = item & 0xFFu, buf = i & 1u;
-            const bool down = (item & kItemDown) != 0u;
-            ok = epi_all(mbar_wait(bar(kBarAccDone + buf), (i >> 1) & 1u, abortp));
-            if (!ok) break;
-            if (tid == 0) mark(17u + i * 4u);
-            fence_after();
-            uint32_t a[16], b[16];  // even and odd units of the item
-            tmem_ld16(lane_base + kColAcc + (buf * 2u) * 16u, a);
-            tmem_ld16(lane_base + kColAcc + (buf * 2u + 1u) * 16u, b);
-            tmem_ld_wait();
-            fence_before();
-            mbar_arrive(bar(kBarAccFree + buf));
-            double sum = 0.0;
-#pragma unroll
-            for (int c = 15; c >= 8; --c) sum += (double)__uint_as_float(a[c]) + (double)__uint_as_float(b[c]);
-#pragma unroll
-            for (int c = 7; c >= 0; --c) sum += (double)__uint_as_float(a[c]) + (double)__uint_as_float(b[c]);
-            const float v = (float)sum;
-            if (!down) {
-                // lanes 0-63: gate of the slice's element `row`; lanes 64-127: its up projection
-                if (row >= 64u) s_up[row - 64u] = v;
-                epi_sync();
-                int E = -80;
-                if (row < 64u) {
-                    // hidden value `row` of the slice -> sixteen digit nibbles; scale block = warp
-                    const float hv = swiglu_limit_f32(v, s_up[row]);
-                    float bm = fabsf(hv);
-#pragma unroll
-                    for (int o = 16; o > 0; o >>= 1) bm = fmaxf(bm, __shfl_xor_sync(0xffffffffu, bm, o));
-                    E = block_exponent(bm);
-                    uint32_t hw, lw;
-                    digit_codes16(hv, __uint_as_float((uint32_t)(150 - E) << 23), hw, lw);
-                    const uint32_t ohw = __shfl_xor_sync(0xffffffffu, hw, 1), olw = __shfl_xor_sync(0xffffffffu, lw, 1);
-                    // byte lane / 2 of every row's chunk holds the nibbles of lanes 2b (low) and 2b + 1; even
-                    // lanes write digit rows 0-3 and 8-11, odd lanes 4-7 and 12-15
-                    const uint32_t e_hw = (lane & 1u) ? ohw : hw, o_hw = (lane & 1u) ? hw : ohw;
-                    const uint32_t e_lw = (lane & 1u) ? olw : lw, o_lw = (lane & 1u) ? lw : olw;
-#pragma unroll
-                    for (uint32_t jj = 0; jj < 4; ++jj) {
-                        const uint32_t dj = (lane & 1u) * 4u + jj;
-                        s_hst[(dj * 2u + warp) * 16u + (lane >> 1)] =
-                            (uint8_t)(((e_hw >> (4u * dj)) & 0xFu) | (((o_hw >> (4u * dj)) & 0xFu) << 4));
-                        s_hst[((8u + dj) * 2u + warp) * 16u + (lane >> 1)] =
-                            (uint8_t)(((e_lw >> (4u * dj)) & 0xFu) | (((o_lw >> (4u * dj)) & 0xFu) << 4));
-                    }
-                }
-                epi_sync();
-                uint8_t *tile = tiles + (size_t)j * kTileMax;
-                if (tid < 32u) {
-                    // chunk (digit row, block) of the slice -> its place in the job's digit tile
-                    const uint32_t dj = tid >> 1, blk = tid & 1u, cc = (idx & 3u) * 2u + blk;
-                    const uint4 c16 = *reinterpret_cast<const uint4 *>(s_hst + (dj * 2u + blk) * 16u);
-                    __stcg(reinterpret_cast<uint4 *>(tile + (idx >> 2) * 2048u + dj * 128u + ((cc ^ (dj & 7u)) << 4)), c16);
-                }
-                if (row < 64u && lane == 0) tile_exps[(size_t)j * kExpMax + idx * 2u + warp] = (uint8_t)(E + 100);
-                __threadfence();
-                epi_sync();
-                if (tid == 0) atomicAdd(counters + kCntJob0 + j, 1u);
-            } else {
-                // row idx * 128 + `row` of the expert's output
-                const uint32_t n = idx * 128u + row, slot = s_jobs[j].out_index;
-                if (ep_on) {
-                    // into the route slot's row of every rank's slot buffer, the value with the step's
-                    // number in one 8-byte store
-                    const size_t at = ((size_t)(ep_step & 1u) * ep.n_slots + slot) * hidden + n;
-                    const unsigned long long word = ((unsigned long long)(ep_step + 1u) << 32) | __float_as_uint(v);
-                    for (uint32_t p = 0; p < ep.world; ++p) st_relaxed_sys(ep.slots[p] + at, word);
-                } else {
-                    __stcg(d_out + (size_t)slot * hidden + n, v);
-                    if (y) {
-                        // ---- the last job of the row tile to finish applies the ordered mix
-                        // (examples/s14_vulkan_numeric.rs:936-946): acc = 0; acc += w * d in route order;
-                        // acc += d_shared ----
-                        __threadfence();
-                        epi_sync();
-                        if (tid == 0) s_last = atomicAdd(counters + kCntTile0 + idx, 1u) == n_jobs - 1u;
-                        epi_sync();
-                        if (s_last) {
-                            __threadfence();
-                            const uint32_t nm = s_n_mix;
-                            float acc = 0.0f;
-                            for (uint32_t jj = 0; jj < nm; ++jj) {
-                                const uint32_t ms = s_mix_slot[jj];
-                                const float dv = __ldcg(d_out + (size_t)(ms & 0x7FFFFFFFu) * hidden + n);
-                                acc = (ms >> 31) ? __fadd_rn(acc, dv) : __fadd_rn(acc, __fmul_rn(s_mix_w[jj], dv));
-                            }
-                            y[n] = acc;
-                        }
-                        epi_sync();  // s_last is read before the next item writes it
-                    }
-                }
-            }
-            if (tid == 0) mark(18u + i * 4u);
-        }
-    } else if (warp >= kLoadWarp0) {
-        // ---- digit tiles of the down items: wait (bounded) until every slice of the job has been
-        // counted, then take the job's tile from global memory (L2) into one of two tile buffers
-        // and its scale codes into tensor memory ----
-        const uint32_t lt = tid - kLoadWarp0 * 32u;
-        uint32_t n_loaded = 0, cur_job = 0xFFFFFFFFu;
-        bool ok = true;
-        for (uint32_t i = 0; i < n_items && ok; ++i) {
-            const uint32_t item = s_items[i], j = (item >> 8) & 0xFFu;
-            if (!(item & kItemDown) || j == cur_job) continue;
-            const uint32_t hb = n_loaded & 1u;
-            bool mine = true;
-            if (lt == 0) {
-                if (n_loaded >= 2u) mine = mbar_wait(bar(kBarHFree + hb), ((n_loaded >> 1) - 1u) & 1u, abortp);
-                uint32_t tries = 0;
-                while (mine && ld_acquire(counters + kCntJob0 + j) < S) {
-                    if (++tries > kSpinGlobal || abort_flag) {
-                        abort_flag = 1;
-                        mine = false;
-                    }
-                    __nanosleep(100);
-                }
-            }
-            ok = load_all(mine);
-            if (!ok) break;
-            const uint8_t *src = tiles + (size_t)j * kTileMax;
-            uint8_t *dst = sBh + hb * tile_bytes;
-            for (uint32_t o = lt * 16u; o < tile_bytes; o += kLoadThreads * 16u)
-                *reinterpret_cast<uint4 *>(dst + o) = __ldcg(reinterpret_cast<const uint4 *>(src + o));
-            if (lt < (inter >> 7))
-                reinterpret_cast<uint32_t *>(sEh[hb])[lt] = __ldcg(reinterpret_cast<const uint32_t *>(tile_exps + (size_t)j * kExpMax) + lt);
-            fence_async_smem();
-            load_sync();
-            if (warp < kLoadWarp0 + 4u) {
-                store_digit_scales(tmem + kColSfbH + hb * 128u, sEh[hb], inter, warp & 3u, 0u, 1u, lane);
-                fence_before();
-            }
-            mbar_arrive(bar(kBarHReady + hb));
-            if (lt == 0) mark(19u + i * 4u);
-            cur_job = j;
-            ++n_loaded;
+        if ((warp == kMmaWarp0 || warp == kMmaWarp0 + 1u) && lane == 0) {
+            // nothing of this CTA's tensor work is in flight when the tensor memory is freed
+            umma_commit(bar(kBarFin));
+            mbar_wait(bar(kBarFin), 0, abortp);
         }
     }
+    tr = tr_base;
 
     // ---- the CTA's items are done (or given up) ----
     if (is_producer) {
@@ -961,11 +1220,12 @@ k_moe_layer_umma(const JobTable *__restrict__ dev_table, const __grid_constant__
         }
     }
     fence_before();
+    __syncwarp();  // the copying and the issuing threads rejoin their warps
     __syncthreads();
     if (tid == 0) mark(13);
     if (warp == kMmaWarp0) {
         __syncwarp();
-        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(kTmemCols) : "memory");
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_slot), "r"(kTmemCols) : "memory");
     }
     if (ep_on && ep.wait_and_mix && cta < RT && tid < kEpiThreads && !abort_flag) {
         // ---- exchange: row tile `cta` of every slot arrives in this rank's own buffer from the slot's
@@ -998,10 +1258,11 @@ k_moe_layer_umma(const JobTable *__restrict__ dev_table, const __grid_constant__
                 atomicExch(status, 0x5504u);
             }
             const float dv = __uint_as_float((uint32_t)got);
-            acc = jj < rt.top_k ? __fadd_rn(acc, __fmul_rn(s_mix_w[jj], dv)) : __fadd_rn(acc, dv);
+            acc = jj < rt.top_k ? __fadd_rn(acc, __fmul_rn(s_mix_w[0][jj], dv)) : __fadd_rn(acc, dv);
         }
         if (ok && y) y[n] = acc;
     }
+    __syncwarp();
     __syncthreads();
     // the last CTA to leave puts the counters back to zero for the next launch
     if (tid == 0) {
@@ -1010,6 +1271,7 @@ k_moe_layer_umma(const JobTable *__restrict__ dev_table, const __grid_constant__
         s_last = atomicAdd(counters + kCntExit, 1u) == grid - 1u;
         mark(14);
     }
+    __syncwarp();
     __syncthreads();
     if (s_last) {
         for (uint32_t i = 1u + tid; i < kCntEnd; i += kThreads) counters[i] = 0u;
@@ -1058,9 +1320,14 @@ size_t dynamic_limit() {
     return most;
 }
 
-// Ring slots that fit beside the token's digit tile and two tiles of hidden values: an even number.
+// shared memory beside the ring: the token's digit tile, two tiles of hidden values, two router rows
+size_t umma_fixed_smem(uint32_t hidden, uint32_t inter) {
+    return (size_t)(hidden >> 8) * 2048u + 2u * (size_t)(inter >> 8) * 2048u + (size_t)kRouterSlots * hidden * 2u;
+}
+
+// Ring slots that fit beside them: an even number.
 uint32_t ring_slots(uint32_t hidden, uint32_t inter, size_t limit) {
-    const size_t fixed = (size_t)(hidden >> 8) * 2048u + 2u * (size_t)(inter >> 8) * 2048u;
+    const size_t fixed = umma_fixed_smem(hidden, inter);
     if (limit < fixed + 2u * kSlot) return 0;
     uint32_t r = (uint32_t)((limit - fixed) / kSlot);
     if (r > kMaxRing) r = kMaxRing;
@@ -1096,20 +1363,25 @@ bool umma_router_ok(int sm_count, uint32_t n_experts) {
 cudaError_t launch_moe_layer_umma(cudaStream_t st, int sm_count, const JobTable *dev, const JobTable &param,
                                   const float *x, float *d, float *y, uint8_t *tiles, unsigned int *counters,
                                   uint32_t *status, uint32_t hidden, uint32_t inter, const FusedRouter *router,
-                                  const EpExchange *ep, unsigned long long *trace) {
+                                  const EpExchange *ep, unsigned long long *trace, const StackLayer *stack,
+                                  uint32_t n_layers, float *hbuf, bool residual) {
     const uint32_t ring = ring_slots(hidden, inter, dynamic_limit());
     if (ring < 2u) return cudaErrorInvalidConfiguration;
     FusedRouter rt = {};
     if (router) rt = *router;
+    if (!stack) rt.has_shared = rt.shared_page != nullptr;
     EpExchange ex = {};
     if (ep) ex = *ep;
     if (ex.world > 1u && !router) return cudaErrorInvalidValue;  // the mix needs every route's weight
-    const size_t smem = (size_t)ring * kSlot + (size_t)(hidden >> 8) * 2048u + 2u * (size_t)(inter >> 8) * 2048u;
+    if (stack && (!router || n_layers == 0u || (n_layers > 1u && !hbuf) || ex.world > 1u || rt.ep_world > 1u))
+        return cudaErrorInvalidValue;  // a stack routes its own layers on one GPU
+    const size_t smem = (size_t)ring * kSlot + umma_fixed_smem(hidden, inter);
     // A programmatic dependent of the previous launch on the single-GPU path.  The expert-parallel
     // paths (exchange inside the kernel, or expert outputs handed to a collective) are ordinary
     // launches; the kernel's own dependency calls are then no-ops.
     return launch_pdl(k_moe_layer_umma, dim3(sm_count), dim3(kThreads), smem, st, ex.world <= 1u && y != nullptr, dev,
-                      param, x, d, y, tiles, counters, status, hidden, inter, ring, trace, rt, ex);
+                      param, x, d, y, tiles, counters, status, hidden, inter, ring, trace, rt, ex, stack,
+                      stack ? n_layers : 1u, hbuf, residual ? 1u : 0u);
 }
 
 }  // namespace s14

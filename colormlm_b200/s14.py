@@ -22,7 +22,7 @@ from ._lib import S14Error, check
 
 __all__ = [
     "S14Error", "S14MatvecShape", "validate_ue8m0_codes", "validate_e4m3fn_codes", "S14Context",
-    "S14NumericPipelines", "VramPool", "S14MoePages", "RouteDecision", "TokenRoute",
+    "S14NumericPipelines", "VramPool", "S14MoePages", "RouteDecision", "TokenRoute", "DecodeStack",
 ]
 
 
@@ -297,10 +297,10 @@ class S14Context:
         check(L.lib().s14_ctx_set_layer_trace(self._h, 1 if enable else 0))
 
     def read_layer_trace(self):
-        """[n_ctas, 64] uint64 marks of the last launch of the layer kernel (see the header)."""
+        """[n_ctas, words] uint64 marks of the last launch of the layer kernel (see the header)."""
         import numpy as np
 
-        cap = 1024 * 64
+        cap = 1024 * 128
         out = np.zeros(cap, np.uint64)
         n, w = C.c_uint32(), C.c_uint32()
         check(L.lib().s14_ctx_read_layer_trace(self._h, out.ctypes.data, cap, C.byref(n), C.byref(w)))
@@ -356,6 +356,59 @@ def _layer_desc(routes, shared_page, shared_kind, hidden, inter):
     d.shared_page = shared_page
     d.routes = C.cast(arr, C.POINTER(L.TokenRoute))
     return d, arr
+
+
+class DecodeStack:
+    """The MoE layers of a token step, bound once (see the header: s14_stack_create).  ``layers`` is a
+    list of dicts with the device tensors ``wr`` (BF16 router weight as int16 / uint16), ``bias``,
+    ``table`` (int64 page addresses), the device address ``shared`` (or None) and, optionally,
+    ``ids``, ``weights`` ([top_k]) and ``y`` ([hidden]) outputs."""
+
+    def __init__(self, ctx: "S14Context", layers, *, inter: int, shared_kind: int = L.PAGE_MXFP4,
+                 score_fn: int = L.SCORE_SIGMOID, top_k: int = 6, route_scale: float = 1.0, residual: bool = True):
+        self._ctx = ctx
+        self._keep = layers
+        cfg = L.StackConfig()
+        cfg.n_layers = len(layers)
+        cfg.n_experts, cfg.hidden = layers[0]["wr"].shape[0], layers[0]["wr"].shape[1]
+        cfg.inter, cfg.top_k, cfg.score_fn, cfg.route_scale = inter, top_k, score_fn, route_scale
+        cfg.shared_kind, cfg.residual = shared_kind, 1 if residual else 0
+        arr = (L.StackLayer * len(layers))()
+        for i, ly in enumerate(layers):
+            arr[i].router_weight_bf16 = ly["wr"].data_ptr()
+            arr[i].bias = ly["bias"].data_ptr() if ly.get("bias") is not None else None
+            arr[i].page_table = ly["table"].data_ptr()
+            arr[i].shared_page = ly.get("shared")
+            for field, key in (("ids_out", "ids"), ("weights_out", "weights"), ("y_out", "y")):
+                t = ly.get(key)
+                setattr(arr[i], field, t.data_ptr() if t is not None else None)
+        h = C.c_void_p()
+        check(L.lib().s14_stack_create(ctx._h, C.byref(cfg), arr, C.byref(h)))
+        self._h = h
+        self.hidden, self.n_layers = cfg.hidden, cfg.n_layers
+
+    def cmd_decode(self, x, h_out, stream: Optional[int] = None) -> None:
+        check(L.lib().s14_cmd_stack_decode(self._ctx._h, stream if stream is not None else _torch_stream(), self._h,
+                                           x.data_ptr(), h_out.data_ptr()))
+
+    def decode_host(self, host_x: np.ndarray, host_h: np.ndarray) -> None:
+        check(L.lib().s14_stack_decode_host(self._ctx._h, self._h, host_x.ctypes.data, host_h.ctypes.data))
+
+    def decode_host_addresses(self, host_x: int, host_h: int) -> None:
+        rc = L.lib().s14_stack_decode_host(self._ctx._h, self._h, host_x, host_h)
+        if rc:
+            check(rc)
+
+    def close(self) -> None:
+        if self._h:
+            L.lib().s14_stack_destroy(self._h)
+            self._h = None
+
+    def __del__(self):
+        try:
+            self.close()
+        except Exception:
+            pass
 
 
 class RoutedLayerHostCall:

@@ -134,19 +134,17 @@ S14_API int32_t s14_shape_mxfp4_scale_bytes(s14_matvec_shape shape, uint64_t *ou
 S14_API int32_t s14_shape_fp8_weight_bytes(s14_matvec_shape shape, uint64_t *out);
 S14_API int32_t s14_shape_fp8_scale_bytes(s14_matvec_shape shape, uint64_t *out);
 
-/* MXFP4 expert page = up | down | s13 | s2 in one pool slot (S14_EXPERT_PAGE_BYTES at hidden
- * 4096, intermediate 2048): the bytes of the six checkpoint tensors, stored so that everything the
+/* MXFP4 expert page = up | down in one pool slot (S14_EXPERT_PAGE_BYTES at hidden 4096,
+ * intermediate 2048): the bytes of the six checkpoint tensors, stored so that everything the
  * tcgen05 layer kernel fetches in one step is one contiguous run, already in the order the tensor
- * cores read shared memory.  A unit is 128 matrix rows x 256 K-elements of E2M1 codes: 16 KB, 128
+ * cores read shared memory.  A unit is 128 matrix rows x 256 K-elements: 16 KB of E2M1 codes, 128
  * rows of 128 bytes, the 16-byte chunk (one scale block, low nibble = even k) number c of row m at
- * position c ^ (m % 8).
+ * position c ^ (m % 8), then the rows' UE8M0 codes for the unit's eight scale blocks as two atoms of
+ * 512 bytes (four blocks each) in the order the block-scaled MMA takes scales into tensor memory:
+ * byte (m % 32) * 16 + (m / 32) * 4 + block % 4.  17 408 bytes per unit.
  *   up      [inter/64 slices][hidden/256 units]: rows 0-63 of a unit are w1 rows of the slice,
  *           rows 64-127 the same rows of w3;
- *   down    [hidden/128 row tiles][inter/256 units] of w2;
- *   s13     by (slice, four scale blocks): the codes of the slice's 64 rows of w1 and 64 rows of
- *           w3, 512 bytes in the order the block-scaled MMA takes scales into tensor memory:
- *           byte (m % 32) * 16 + (m / 32) * 4 + block % 4;
- *   s2      by (row tile, four scale blocks): the codes of 128 rows of w2, same order.
+ *   down    [hidden/128 row tiles][inter/256 units] of w2.
  * hidden and intermediate must be multiples of 256.  A "tensor page" is the six tensors one after
  * the other in the checkpoint's ABI (w1 | w3 | w2 | s1 | s3 | s2); these host functions convert
  * between the two, once, at load time.  The reference fixes no layout inside a slot
@@ -324,6 +322,52 @@ typedef struct {
 
 S14_API int32_t s14_cmd_routed_moe_layer(s14_ctx *ctx, void *stream,
                                          const s14_routed_layer_desc *desc);
+
+/* A decode stack: the MoE layers of a token step one after the other, the output of a layer being
+ * the next layer's token - h <- h + moe_l(h) with `residual`, h <- moe_l(h) without - which is what
+ * the runner's token step asks of its executor layer by layer
+ * (scheduler/s14_runner/src/runner.rs:312-358: routed_and_shared_moe_then_hc_post per layer, with
+ * the attention and hyper-connection steps taken as the identity) and what the reference's own
+ * prefill / decode loop does with its layers (ssd_inference/src/forward.rs:544-549).  In pairwise
+ * order with MXFP4 pages the whole stack is ONE launch of the tensor-core layer kernel, which walks
+ * the layers itself (one CTA per SM stays resident, the next layer's shared expert is asked for
+ * while the last rows of the layer before are mixed); otherwise the layers are launched one by one.
+ * Every layer's result is the one s14_cmd_routed_moe_layer gives for the same token.
+ *   create:  copies the layers' descriptors to the device once (the bind step).  All pointers are
+ *            device addresses that stay valid while the stack is used; ids_out / weights_out
+ *            ([top_k], the layer's route) and y_out ([hidden], the layer's MoE output before the
+ *            residual) may be NULL.  Either every layer has a shared expert or none has.
+ *   decode:  x [hidden] -> h_out [hidden], both device memory; x and h_out may be the same buffer. */
+typedef struct {
+    const uint16_t *router_weight_bf16;
+    const float *bias;
+    const uint8_t *const *page_table;
+    const uint8_t *shared_page;
+    int32_t *ids_out;
+    float *weights_out;
+    float *y_out;
+} s14_stack_layer;
+
+typedef struct {
+    uint32_t n_layers;   /* 1..64 */
+    uint32_t n_experts;  /* <= 256 */
+    uint32_t hidden;     /* 1024, 2048 or 4096 */
+    uint32_t inter;      /* 1024, 2048 or 4096 */
+    uint32_t top_k;      /* 1..6 */
+    uint32_t score_fn;
+    float route_scale;
+    uint32_t shared_kind; /* S14_PAGE_MXFP4 | S14_PAGE_FP8 */
+    uint32_t residual;    /* 1: h <- h + moe(h) */
+} s14_stack_config;
+
+typedef struct s14_stack s14_stack;
+S14_API int32_t s14_stack_create(s14_ctx *ctx, const s14_stack_config *config, const s14_stack_layer *layers,
+                                 s14_stack **out);
+S14_API int32_t s14_stack_destroy(s14_stack *stack);
+S14_API int32_t s14_cmd_stack_decode(s14_ctx *ctx, void *stream, s14_stack *stack, const float *x, float *h_out);
+/* The same for a caller that holds the token in host memory: copies host_x [hidden] to the device,
+ * runs the stack, copies h [hidden] back and waits. */
+S14_API int32_t s14_stack_decode_host(s14_ctx *ctx, s14_stack *stack, const float *host_x, float *host_h);
 
 /* Expert-parallel decode (no counterpart in the reference, which has no multi-GPU code).  Every
  * rank of `ep_world` runs the replicated router on the same token and computes the experts it

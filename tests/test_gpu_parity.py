@@ -493,6 +493,163 @@ def test_routed_layer_at_the_benchmark_shape(ctx, oracle, score_fn):
     print("benchmark-shape parity, pairwise vs double-accumulated oracle:", worst)
 
 
+def assert_chain_close(oracle, got, ref, what):
+    """A chain of layers without normalisation grows (outputs reach the hundreds after a few layers),
+    so the stated absolute tolerance (max-abs 2e-5, RMSE 2e-6, written for outputs of magnitude ~100
+    and RMS ~27, i.e. about three F32 ulps of the largest value and one ulp of the RMS) is kept in
+    those units: max error <= max(2e-5, 3 ulps of the largest reference value), RMSE <= max(2e-6,
+    one ulp of the reference RMS)."""
+    ref = np.asarray(ref, np.float32)
+    e = stats(oracle, got, ref)
+    rms = np.float32(np.sqrt(np.mean(ref.astype(np.float64) ** 2)))
+    assert e["max_abs"] <= max(MAX_ABS, 3.0 * float(np.spacing(np.abs(ref).max()))), (what, e)
+    assert e["rmse"] <= max(RMSE, float(np.spacing(rms))), (what, e)
+    return e
+
+
+def oracle_stack(oracle, x, layers, hidden, inter, residual, acc64, score_fn=0):
+    """The chain h <- h + moe_l(h) on the CPU: every layer routed by the oracle's router on the
+    layer's own input; returns the final h, the per-layer outputs and routes."""
+    h = np.asarray(x, np.float32).copy()
+    ys, routes = [], []
+    for ly in layers:
+        rid, rw, _, _ = oracle.router(h, ly["wr"], ly["bias"], score_fn, 6, 1.0)
+        sel = [ly["page"](int(e)) for e in rid]
+        fn = oracle.moe_layer_acc64 if acc64 else oracle.moe_layer
+        yl = fn(h, sel, rw, ly["shared"], 0, hidden, inter)
+        ys.append(yl)
+        routes.append((rid, rw))
+        h = (h + yl).astype(np.float32) if residual else yl
+    return h, ys, routes
+
+
+@pytest.mark.parametrize("residual", [True, False])
+def test_decode_stack_small(ctx, oracle, residual):
+    """Four chained layers (hidden 2048, intermediate 1024, 32 experts) in one launch: routes of every
+    layer bit-exact, every layer's output and the final token equal to the same layers run one by one
+    and inside the stated tolerance against the double-accumulated oracle chain; reference order
+    (layers launched one by one) bit-identical to the F32 oracle chain."""
+    from colormlm_b200.s14 import DecodeStack
+
+    hidden, inter, n_experts, n_layers = 2048, 1024, 32, 4
+    host_layers, dev_layers, keep = [], [], []
+    for l in range(n_layers):
+        g, pages, shared = make_layer(8800 + l, hidden, inter, n_experts, L.PAGE_MXFP4)
+        wr, bias = synth.router_weight_bf16(g, n_experts, hidden), synth.router_bias(g, n_experts)
+        host_layers.append({"wr": wr, "bias": bias, "shared": shared, "page": (lambda e, p=pages: p[e])})
+        pd, sd = [dev_page(p, hidden, inter) for p in pages], dev_page(shared, hidden, inter)
+        keep.append((pd, sd))
+        dev_layers.append({"wr": dev(wr.view(np.int16)), "bias": dev(bias),
+                           "table": torch.tensor([p.data_ptr() for p in pd], dtype=torch.int64, device="cuda"),
+                           "shared": sd.data_ptr(),
+                           "ids": torch.empty(6, dtype=torch.int32, device="cuda"),
+                           "weights": torch.empty(6, dtype=torch.float32, device="cuda"),
+                           "y": torch.empty(hidden, dtype=torch.float32, device="cuda")})
+    x = synth.activations(synth.rng(8899), 1, hidden)[0] * np.float32(0.25)
+    dx = dev(x)
+    stack = DecodeStack(ctx, dev_layers, inter=inter, residual=residual)
+    try:
+        for mode, acc64 in ((L.ACCUM_PAIRWISE, True), (L.ACCUM_REFERENCE, False)):
+            ctx.set_accumulation(mode)
+            want_h, want_y, want_routes = oracle_stack(oracle, x, host_layers, hidden, inter, residual, acc64)
+            h = torch.full((hidden,), float("nan"), device="cuda")
+            before = ctx.launch_count
+            stack.cmd_decode(dx, h)
+            torch.cuda.synchronize()
+            assert ctx.device_status() == 0
+            if mode == L.ACCUM_PAIRWISE:
+                assert ctx.launch_count - before == 1  # the whole stack is one launch
+            for l in range(n_layers):
+                rid, rw = want_routes[l]
+                assert np.array_equal(dev_layers[l]["ids"].cpu().numpy(), rid), (mode, l)
+                assert np.array_equal(dev_layers[l]["weights"].cpu().numpy().view(np.uint32), rw.view(np.uint32)), (mode, l)
+                got = dev_layers[l]["y"].cpu().numpy()
+                if mode == L.ACCUM_REFERENCE:
+                    assert np.array_equal(got.view(np.uint32), want_y[l].view(np.uint32)), (l, stats(oracle, got, want_y[l]))
+                else:
+                    assert_chain_close(oracle, got, want_y[l], ("layer", l))
+            got_h = h.cpu().numpy()
+            if mode == L.ACCUM_REFERENCE:
+                assert np.array_equal(got_h.view(np.uint32), want_h.view(np.uint32))
+            else:
+                assert_chain_close(oracle, got_h, want_h, "final token")
+                # the same layers one by one, the step between them on the host side of the call
+                cur = dx.clone()
+                for l in range(n_layers):
+                    yl = torch.empty(1, hidden, device="cuda")
+                    ly = dev_layers[l]
+                    ctx.cmd_routed_moe_layer(cur, ly["wr"], ly["bias"], ly["table"], ly["shared"], L.PAGE_MXFP4, inter, yl)
+                    cur = cur + yl[0] if residual else yl[0].clone()
+                torch.cuda.synchronize()
+                assert torch.equal(cur, h)
+        # a second token through the same stack (the counters are back at zero, the barriers start again)
+        ctx.set_accumulation(L.ACCUM_PAIRWISE)
+        x2 = synth.activations(synth.rng(8900), 1, hidden)[0] * np.float32(0.25)
+        want_h, _, _ = oracle_stack(oracle, x2, host_layers, hidden, inter, residual, True)
+        h = torch.empty(hidden, device="cuda")
+        stack.cmd_decode(dev(x2), h)
+        torch.cuda.synchronize()
+        assert ctx.device_status() == 0
+        assert_chain_close(oracle, h.cpu().numpy(), want_h, "second token")
+    finally:
+        stack.close()
+        ctx.set_accumulation(L.ACCUM_PAIRWISE)
+
+
+def test_decode_stack_at_the_benchmark_shape(ctx, oracle):
+    """Three chained layers of 256 experts, hidden 4096, intermediate 2048 with the residual, one
+    launch: routes bit-exact, outputs inside the stated tolerance against the double-accumulated
+    oracle chain.  Only the pages the chain selects are generated (the oracle chain is run first)."""
+    from colormlm_b200.s14 import DecodeStack
+
+    hidden, inter, n_experts, n_layers = 4096, 2048, 256, 3
+    cache = {}
+
+    def page(layer, e):
+        if (layer, e) not in cache:
+            cache[(layer, e)] = synth.mxfp4_expert_page(synth.rng(70_000 + 1000 * layer + e), hidden, inter)
+        return cache[(layer, e)]
+
+    host_layers = []
+    for l in range(n_layers):
+        g = synth.rng(7700 + l)
+        host_layers.append({"wr": synth.router_weight_bf16(g, n_experts, hidden), "bias": synth.router_bias(g, n_experts),
+                            "shared": synth.mxfp4_expert_page(synth.rng(79_000 + l), hidden, inter),
+                            "page": (lambda e, l=l: page(l, e))})
+    x = synth.activations(synth.rng(7799), 1, hidden)[0]
+    want_h, want_y, want_routes = oracle_stack(oracle, x, host_layers, hidden, inter, True, True)
+    dev_layers, keep = [], []
+    for l in range(n_layers):
+        other = dev_page(synth.mxfp4_expert_page(synth.rng(78_000 + l), hidden, inter), hidden, inter)
+        pd = {int(e): dev_page(page(l, int(e)), hidden, inter) for e in want_routes[l][0]}
+        sd = dev_page(host_layers[l]["shared"], hidden, inter)
+        keep.append((other, pd, sd))
+        dev_layers.append({"wr": dev(host_layers[l]["wr"].view(np.int16)), "bias": dev(host_layers[l]["bias"]),
+                           "table": torch.tensor([pd[e].data_ptr() if e in pd else other.data_ptr() for e in range(n_experts)],
+                                                 dtype=torch.int64, device="cuda"),
+                           "shared": sd.data_ptr(),
+                           "ids": torch.empty(6, dtype=torch.int32, device="cuda"),
+                           "weights": torch.empty(6, dtype=torch.float32, device="cuda"),
+                           "y": torch.empty(hidden, dtype=torch.float32, device="cuda")})
+    ctx.set_accumulation(L.ACCUM_PAIRWISE)
+    stack = DecodeStack(ctx, dev_layers, inter=inter, residual=True)
+    try:
+        h = torch.empty(hidden, device="cuda")
+        for rep in range(2):
+            before = ctx.launch_count
+            stack.cmd_decode(dev(x), h)
+            torch.cuda.synchronize()
+            assert ctx.device_status() == 0 and ctx.launch_count - before == 1
+            for l in range(n_layers):
+                rid, rw = want_routes[l]
+                assert np.array_equal(dev_layers[l]["ids"].cpu().numpy(), rid), l
+                assert np.array_equal(dev_layers[l]["weights"].cpu().numpy().view(np.uint32), rw.view(np.uint32)), l
+                assert_chain_close(oracle, dev_layers[l]["y"].cpu().numpy(), want_y[l], ("layer", l))
+            assert_chain_close(oracle, h.cpu().numpy(), want_h, "final token")
+    finally:
+        stack.close()
+
+
 def test_routed_layer_on_host_buffers_and_the_bound_call(ctx, oracle):
     """The call a host program makes per token: x from host memory, y and the route back.  The bound
     call (descriptor recorded once) and the one-shot call give the device path's bits."""

@@ -295,22 +295,27 @@ def test_expert_page_from_tensors_matches_the_numpy_mirror_and_the_stated_offset
         t, o = lay.split(tensor_page), lay.offsets
         g = np.random.default_rng(1)
 
+        unit = 16384 + 1024  # codes, then two scale atoms
+
         def in_unit(m, kb):  # 128 rows of 128 bytes, the 16-byte chunks of row m at chunk ^ (m % 8)
             return m * 128 + (((kb % 8) ^ (m % 8)) << 4)
 
+        def scale_in_unit(m, kb):
+            return 16384 + ((kb // 4) % 2) * 512 + (m % 32) * 16 + (m // 32) * 4 + kb % 4
+
+        down0 = (inter // 64) * (hidden // 256) * unit
         for _ in range(200):
             n, kb = int(g.integers(hidden)), int(g.integers(inter // 32))
-            off = ((n // 128) * (inter // 256) + kb // 8) * 16384 + in_unit(n % 128, kb)
-            assert np.array_equal(got[o["w2"] + off:o["w2"] + off + 16], t["w2"].reshape(hidden, inter // 2)[n, kb * 16:kb * 16 + 16])
-            r = n % 128
-            off = ((n // 128) * (inter // 128) + kb // 4) * 512 + (r % 32) * 16 + (r // 32) * 4 + kb % 4
-            assert got[o["s2"] + off] == t["s2"].reshape(hidden, inter // 32)[n, kb]
+            base = down0 + ((n // 128) * (inter // 256) + kb // 8) * unit
+            off = base + in_unit(n % 128, kb)
+            assert np.array_equal(got[off:off + 16], t["w2"].reshape(hidden, inter // 2)[n, kb * 16:kb * 16 + 16])
+            assert got[base + scale_in_unit(n % 128, kb)] == t["s2"].reshape(hidden, inter // 32)[n, kb]
             i, kb = int(g.integers(inter)), int(g.integers(hidden // 32))
             for mat, name, wname in ((0, "s1", "w1"), (1, "s3", "w3")):
                 m = i % 64 + 64 * mat
-                off = ((i // 64) * (hidden // 128) + kb // 4) * 512 + (m % 32) * 16 + (m // 32) * 4 + kb % 4
-                assert got[o["s1"] + off] == t[name].reshape(inter, hidden // 32)[i, kb]
-                off = ((i // 64) * (hidden // 256) + kb // 8) * 16384 + in_unit(m, kb)
+                base = ((i // 64) * (hidden // 256) + kb // 8) * unit
+                assert got[base + scale_in_unit(m, kb)] == t[name].reshape(inter, hidden // 32)[i, kb]
+                off = base + in_unit(m, kb)
                 assert np.array_equal(got[off:off + 16], t[wname].reshape(inter, hidden // 2)[i, kb * 16:kb * 16 + 16])
         back = np.empty_like(tensor_page)
         L.check(L.lib().s14_mxfp4_expert_page_to_tensors(hidden, inter, got.ctypes.data_as(C.c_void_p),
