@@ -1,23 +1,35 @@
 #!/usr/bin/env python
-"""Benchmark of the S14 MoE layer at 1-token decode: router top-6 + six routed MXFP4
-experts + the shared MXFP4 expert, 256 routed experts per layer resident in the page pool.
+"""Benchmark of the S14 MoE expert path on B200.
 
-    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl reference] [--accum pairwise|reference]
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl reference]
+                    [--workload stack|layer|expert_chain|wq_a|verify8] [--accum pairwise|reference]
 
-A step is one layer-token: one token through one MoE layer, a single launch in pairwise order
-(expert scores and routes, up projections, SwiGLU, down projection, sums over slices, ordered mix).  14 layers of 257 expert pages each are resident (the S14 stack, 48 GB); the
-steps walk the layers round-robin with a fresh token each, so consecutive steps read
-disjoint pages and the 96 MB a step touches never comes from L2.  Steps are replayed from
-a CUDA graph of 14 layer-steps; time is taken with CUDA events on the launching stream.
+A step is one layer-token: one token through one MoE layer (router top-6 of 256, six routed MXFP4
+experts and the shared MXFP4 expert, hidden 4096, intermediate 2048).  14 layers of 257 expert pages
+are resident (48 GB), so the 96 MB a step touches never come from L2.
 
-One JSON line is printed by rank 0.  `value` is layer-tokens/s with inputs resident in HBM,
-`e2e` the same through the host-buffer C-ABI call (H2D of the token and D2H of the result
-inside the timed region), `roofline` the layer kernel (a step is one launch of it) against the measured copy bandwidth, `cpu_baseline` the CPU oracle on this box's host cores on a bounded sample.
-`--impl reference` times that CPU implementation alone.
+  stack   (default on one GPU) the 14 layers chained as the decode of one token does it,
+          h <- h + moe_l(h), in ONE launch of the layer kernel per 14 steps (s14_cmd_stack_decode);
+  layer   one launch per step with independent tokens (s14_cmd_routed_moe_layer); with several GPUs
+          the experts are partitioned and the down vectors exchanged inside the kernel;
+  expert_chain, wq_a, verify8   the single-expert chain, the FP8 projection matvec and the 8-token
+          verify block of the other configurations, each with its own roofline entry.
+
+The timed region is exactly K steps, taken with CUDA events on the launching stream; it is repeated
+(--repeats, default 50) and the median repeat is reported with the spread.  Pages are a function of
+(layer, expert, byte position) that the GPU and the host evaluate alike, so the CPU arm and the
+parity check run the very bytes the GPU holds (a SHA-256 of one page from both sides is in the line).
+
+One JSON line is printed by rank 0: `value` is layer-tokens/s with inputs resident in HBM, `e2e` the
+same through the host-buffer C-ABI call (H2D of the token, D2H of the result inside the timed region),
+`roofline` the layer kernel against the measured copy bandwidth, `parity` the error of the timed path
+on its own steps against the CPU oracle, `cpu_baseline` the CPU oracle on this box's host cores on a
+bounded sample.  `--impl reference` times that CPU implementation alone.
 """
 from __future__ import annotations
 
 import argparse
+import hashlib
 import json
 import os
 import subprocess
@@ -36,13 +48,15 @@ PAGE_BYTES = 13_369_344
 # algorithmic bytes of one layer-token: 7 expert pages + router weights + bias + x + y
 ROUTER_BYTES = N_EXPERTS * HIDDEN * 2 + N_EXPERTS * 4
 STEP_BYTES = 7 * PAGE_BYTES + ROUTER_BYTES + HIDDEN * 4 + HIDDEN * 4
-# layer kernel: 7 expert pages, x in, y out
+# layer kernel with the routes given: 7 expert pages, x in, y out
 LAYER_BYTES = 7 * PAGE_BYTES + HIDDEN * 4 + HIDDEN * 4
-# DRAM bytes of one launch of the layer kernel at this workload (dram__bytes_read.sum + dram__bytes_write.sum
-# of one ncu capture; the summary of that capture is kept under profiles/)
-NCU_TRAFFIC_BYTES = 99_866_368
+# DRAM bytes of one layer of a launch of the layer kernel at this workload (dram__bytes_read.sum +
+# dram__bytes_write.sum of one ncu capture divided by the layers of the launch; the summary of that
+# capture is kept under profiles/)
+NCU_TRAFFIC_BYTES = None
 WORKLOAD = ("moe_layer_decode: 1 token, router top-6 of 256 + 6 routed + 1 shared MXFP4 expert, "
             "hidden 4096, intermediate 2048")
+TOKEN_SEED = 99
 
 
 def measured_peaks():
@@ -69,7 +83,7 @@ class ClockSampler:
         try:
             self.proc = subprocess.Popen(
                 ["nvidia-smi", f"--id={self.device}", f"--query-gpu={self.QUERY}",
-                 "--format=csv,noheader,nounits", "-lms", "100"],
+                 "--format=csv,noheader,nounits", "-lms", "50"],
                 stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
             self.thread = threading.Thread(target=self._read, daemon=True)
             self.thread.start()
@@ -80,10 +94,12 @@ class ClockSampler:
         for line in self.proc.stdout:
             self.rows.append([c.strip() for c in line.split(",")])
 
+    def samples(self) -> int:
+        return len(self.rows)
+
     def stop(self) -> dict:
         if self.proc is None:
             return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
-        time.sleep(0.15)
         self.proc.terminate()
         try:
             self.proc.wait(timeout=2)
@@ -104,71 +120,93 @@ class ClockSampler:
                 "reasons": sorted(reasons), "samples": len(sm)}
 
 
-# ------------------------------------------------------------------ CPU reference arm
+# --------------------------------------------------------------- inputs both arms share
 
-def cpu_pages(layer: int, ids, cache: dict):
-    """Host copies of the pages a CPU step needs, generated on demand from per-page seeds."""
+def tokens(n: int) -> np.ndarray:
     from colormlm_b200 import synth
 
+    return synth.activations(synth.rng(TOKEN_SEED), n, HIDDEN)
+
+
+def router_of_layer(layer: int):
+    from colormlm_b200 import synth
+
+    gl = synth.rng(500 + layer)
+    return synth.router_weight_bf16(gl, N_EXPERTS, HIDDEN), synth.router_bias(gl, N_EXPERTS)
+
+
+class HostPages:
+    """Tensor pages (what the CPU oracle reads) of the very bytes the GPU holds, made on demand."""
+
+    def __init__(self, limit: int = 96):
+        self.cache, self.limit = {}, limit
+
+    def get(self, layer: int, expert: int) -> np.ndarray:
+        from colormlm_b200 import synth
+
+        key = (layer, int(expert))
+        if key not in self.cache:
+            if len(self.cache) >= self.limit:
+                self.cache.clear()
+            self.cache[key] = synth.hashed_tensor_page(layer, int(expert), HIDDEN, INTER)
+        return self.cache[key]
+
+
+def cpu_layer(oracle, pages: HostPages, layer: int, x: np.ndarray, acc64: bool = False):
+    """Router + layer of one token on the CPU oracle; returns (y, ids, weights)."""
+    wr, bias = router_of_layer(layer)
+    ids, w, _, _ = oracle.router(x, wr, bias, 0, TOP_K, 1.0)
+    sel = [pages.get(layer, e) for e in ids]
+    fn = oracle.moe_layer_acc64 if acc64 else oracle.moe_layer
+    return fn(x, sel, w, pages.get(layer, N_EXPERTS), 0, HIDDEN, INTER), ids, w
+
+
+# ------------------------------------------------------------------ CPU reference arm
+
+def cpu_steps(oracle, n_steps: int, first_token: int = 0):
+    """(x, wr, bias, routed tensor pages, shared page) of n layer-token steps (untimed set-up)."""
+    pages = HostPages(limit=10 ** 6)
+    xs = tokens(first_token + n_steps)
     out = []
-    for e in list(ids) + [N_EXPERTS]:
-        key = (layer, int(e))
-        if key not in cache:
-            cache[key] = synth.mxfp4_expert_page(synth.rng(10_000 + layer * 1000 + int(e)), HIDDEN, INTER)
-        out.append(cache[key])
+    for i in range(n_steps):
+        layer = i % N_LAYERS
+        wr, bias = router_of_layer(layer)
+        x = xs[first_token + i]
+        ids, _, _, _ = oracle.router(x, wr, bias, 0, TOP_K, 1.0)
+        out.append((x, wr, bias, [pages.get(layer, e) for e in ids], pages.get(layer, N_EXPERTS)))
     return out
 
 
-def cpu_step_setup(n_steps: int):
-    """Router weights per layer, tokens, routes and pages for n_steps CPU steps (untimed)."""
-    from colormlm_b200 import synth
-    from oracle import s14_oracle as oracle
-
-    g = synth.rng(77)
-    layers = {}
-    steps = []
-    cache = {}
-    for i in range(n_steps):
-        layer = i % N_LAYERS
-        if layer not in layers:
-            gl = synth.rng(500 + layer)
-            layers[layer] = (synth.router_weight_bf16(gl, N_EXPERTS, HIDDEN), synth.router_bias(gl, N_EXPERTS))
-        x = synth.activations(g, 1, HIDDEN)[0]
-        wr, bias = layers[layer]
-        ids, _, _, _ = oracle.router(x, wr, bias, 0, TOP_K, 1.0)
-        steps.append((x, wr, bias, cpu_pages(layer, ids, cache)))
-        if len(cache) > 64:
-            cache.clear()
-    return steps
-
-
-def cpu_run(steps) -> float:
-    """Seconds for the CPU oracle to run the given layer-token steps (router + layer)."""
-    from oracle import s14_oracle as oracle
-
+def cpu_run(oracle, steps) -> float:
     t0 = time.perf_counter()
-    for x, wr, bias, pages in steps:
-        ids, w, _, _ = oracle.router(x, wr, bias, 0, TOP_K, 1.0)
-        oracle.moe_layer(x, pages[:TOP_K], w, pages[TOP_K], 0, HIDDEN, INTER)
+    for x, wr, bias, sel, shared in steps:
+        _, w, _, _ = oracle.router(x, wr, bias, 0, TOP_K, 1.0)
+        oracle.moe_layer(x, sel, w, shared, 0, HIDDEN, INTER)
     return time.perf_counter() - t0
 
 
+def cpu_threads(oracle) -> int:
+    """All host cores, whatever OMP_NUM_THREADS a launcher set."""
+    n = os.cpu_count() or 1
+    oracle.set_threads(n)
+    return n
+
+
 def run_reference(args) -> None:
-    rank = int(os.environ.get("RANK", "0"))
-    if rank != 0:
+    if int(os.environ.get("RANK", "0")) != 0:
         return
     from oracle import s14_oracle as oracle
 
     oracle.build()
-    cores = oracle.max_threads()
-    steps = cpu_step_setup(args.warmup + args.steps)
-    cpu_run(steps[:args.warmup])
-    sec = cpu_run(steps[args.warmup:])
+    cores = cpu_threads(oracle)
+    steps = cpu_steps(oracle, args.warmup + args.steps)
+    cpu_run(oracle, steps[:args.warmup])
+    sec = cpu_run(oracle, steps[args.warmup:])
     value = args.steps / sec
     line = {
         "impl": "reference", "metric": "moe_layer_tokens_per_s", "value": value, "unit": "layer-tokens/s",
         "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup,
-        "ms_per_step": 1e3 * sec / args.steps, "higher_is_better": True, "scaling": "weak",
+        "ms_per_step": 1e3 * sec / args.steps, "higher_is_better": True, "scaling": "strong",
         "vs_baseline": None, "dtype": "f32", "data": "synthetic",
         "config": {"workload": WORKLOAD, "layers_resident": N_LAYERS, "device": "host CPU"},
         "cpu_baseline": {"value": value, "unit": "layer-tokens/s", "cores": cores, "kind": "port",
@@ -182,20 +220,73 @@ def run_reference(args) -> None:
 
 # ------------------------------------------------------------------------- GPU arm
 
-def make_layer_pages(torch, n_pages: int, gen) -> "torch.Tensor":
-    """[n_pages, PAGE_BYTES] uint8 on the device: uniform E2M1 codes, scale codes in [119, 123]."""
-    wb = 3 * (HIDDEN * INTER // 2)
-    pages = torch.empty((n_pages, PAGE_BYTES), dtype=torch.uint8, device="cuda")
-    pages[:, :wb] = torch.randint(0, 256, (n_pages, wb), dtype=torch.uint8, device="cuda", generator=gen)
-    pages[:, wb:] = torch.randint(119, 124, (n_pages, PAGE_BYTES - wb), dtype=torch.uint8, device="cuda",
-                                  generator=gen)
-    return pages
-
-
 def _note(msg: str) -> None:
     """Progress lines on stderr when S14_BENCH_VERBOSE is set."""
     if os.environ.get("S14_BENCH_VERBOSE"):
         print(f"[bench rank {os.environ.get('RANK', '0')}] {msg}", file=sys.stderr, flush=True)
+
+
+def resident_layers(torch, n_layers: int, rank: int, world: int):
+    """The pages this rank owns (expert e on rank e mod world, the shared expert of layer l on rank
+    l mod world), router weights and page tables, all on the device."""
+    from colormlm_b200 import ep, synth
+
+    writer = synth.HashedPageWriter(torch, HIDDEN, INTER)
+    layers = []
+    for layer in range(n_layers):
+        owned = ep.owned_experts(rank, world, N_EXPERTS)
+        has_shared = ep.shared_owner(layer, world) == rank
+        pages = torch.empty((len(owned) + (1 if has_shared else 0), PAGE_BYTES), dtype=torch.uint8, device="cuda")
+        for slot, e in enumerate(owned):
+            writer.fill(pages[slot], layer, e)
+        if has_shared:
+            writer.fill(pages[len(owned)], layer, N_EXPERTS)
+        wr_np, bias_np = router_of_layer(layer)
+        base = pages.data_ptr()
+        addr = [0] * N_EXPERTS
+        for slot, e in enumerate(owned):
+            addr[e] = base + slot * PAGE_BYTES
+        layers.append({"pages": pages, "wr": torch.from_numpy(wr_np.view(np.int16)).cuda(),
+                       "bias": torch.from_numpy(bias_np).cuda(),
+                       "table": torch.tensor(addr, dtype=torch.int64, device="cuda"),
+                       "shared": base + len(owned) * PAGE_BYTES if has_shared else None,
+                       "owned": owned})
+    return layers
+
+
+def timed_repeats(torch, stream, enqueue, repeats: int, barrier=None):
+    """enqueue() launches exactly one region; every repeat is bracketed by CUDA events."""
+    ms = []
+    for _ in range(repeats):
+        if barrier:
+            barrier()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        with torch.cuda.stream(stream):
+            e0.record(stream)
+            enqueue()
+            e1.record(stream)
+        stream.synchronize()
+        ms.append(e0.elapsed_time(e1))
+    return ms
+
+
+def error_block(oracle, got, ref) -> dict:
+    e = oracle.error_stats(np.asarray(got, np.float32), np.asarray(ref, np.float32))
+    ref64 = np.asarray(ref, np.float64)
+    rms = float(np.sqrt(np.mean(ref64 ** 2)))
+    peak = float(np.abs(ref64).max())
+    return {"max_abs": e["max_abs"], "rmse": e["rmse"], "max_abs_over_rms": e["max_abs"] / rms if rms else None,
+            "max_abs_in_ulps_of_largest": e["max_abs"] / float(np.spacing(np.float32(peak))) if peak else None,
+            "bit_equal_fraction": float((np.asarray(got, np.float32).view(np.uint32) ==
+                                         np.asarray(ref, np.float32).view(np.uint32)).mean())}
+
+
+def worst(blocks) -> dict:
+    out = {}
+    for k in blocks[0]:
+        vals = [b[k] for b in blocks if b[k] is not None]
+        out[k] = (min(vals) if k == "bit_equal_fraction" else max(vals)) if vals else None
+    return out
 
 
 def run_gpu(args) -> None:
@@ -204,8 +295,8 @@ def run_gpu(args) -> None:
 
     from colormlm_b200 import _lib as L
     from colormlm_b200 import build as cuda_build
-    from colormlm_b200 import synth
-    from colormlm_b200.s14 import S14Context
+    from colormlm_b200 import ep, synth
+    from colormlm_b200.s14 import DecodeStack, S14Context, TokenRoute
 
     rank = int(os.environ.get("RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))
@@ -218,215 +309,33 @@ def run_gpu(args) -> None:
     if world > 1:
         dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
         dist.barrier()
+    workload = args.workload or ("stack" if world == 1 else "layer")
+    if world > 1 and workload != "layer":
+        raise SystemExit("several GPUs: the expert-parallel workload is `layer`")
+    if workload in ("expert_chain", "wq_a", "verify8"):
+        return run_small_workload(args, workload, torch, L, synth, S14Context, TokenRoute)
 
-    _note("process group ready")
     ctx = S14Context(local_rank)
     mode = L.ACCUM_REFERENCE if args.accum == "reference" else L.ACCUM_PAIRWISE
     ctx.set_accumulation(mode)
-    gen = torch.Generator(device="cuda")
-    gen.manual_seed(1234 + rank)
-
-    # resident state: N_LAYERS x (256 routed + 1 shared) pages, router weights, page tables.
-    # With several GPUs the experts are partitioned (expert e on rank e mod N, the shared expert of
-    # layer l on rank l mod N) and every rank keeps only the pages it owns.
-    from colormlm_b200 import ep
-
-    layers = []
-    n_layers = max(1, args.layers)
-    for layer in range(n_layers):
-        owned = ep.owned_experts(rank, world, N_EXPERTS)
-        has_shared = ep.shared_owner(layer, world) == rank
-        pages = make_layer_pages(torch, len(owned) + (1 if has_shared else 0), gen)
-        gl = synth.rng(500 + layer)
-        wr = torch.from_numpy(synth.router_weight_bf16(gl, N_EXPERTS, HIDDEN).view(np.int16)).cuda()
-        bias = torch.from_numpy(synth.router_bias(gl, N_EXPERTS)).cuda()
-        base = pages.data_ptr()
-        addr = [0] * N_EXPERTS
-        for slot, e in enumerate(owned):
-            addr[e] = base + slot * PAGE_BYTES
-        table = torch.tensor(addr, dtype=torch.int64, device="cuda")
-        layers.append({"pages": pages, "wr": wr, "bias": bias, "table": table,
-                       "shared": base + len(owned) * PAGE_BYTES if has_shared else None})
+    n_layers = max(1, min(args.layers, N_LAYERS))
+    layers = resident_layers(torch, n_layers, rank, world)
+    _note("layers resident")
     n_tok = 64
-    xgen = torch.Generator(device="cuda")
-    xgen.manual_seed(99)  # the same tokens on every rank
-    xs = torch.randn((n_tok, HIDDEN), dtype=torch.float32, device="cuda", generator=xgen)
-    ys = torch.empty((N_LAYERS, HIDDEN), dtype=torch.float32, device="cuda")
-    slots = torch.zeros((N_LAYERS, TOP_K + 1, HIDDEN), dtype=torch.float32, device="cuda")
-    ep_ids = torch.empty((N_LAYERS, TOP_K), dtype=torch.int32, device="cuda")
-    ep_w = torch.empty((N_LAYERS, TOP_K), dtype=torch.float32, device="cuda")
-    torch.cuda.synchronize()
-    # several GPUs, pairwise order: the exchange of the down vectors runs inside the layer kernel over
-    # the ranks' mapped slot buffers (one launch per rank and step); --exchange nccl keeps the baseline
-    # (owned experts, NCCL all-reduce of the slot buffer, mix kernel)
+    xs_np = tokens(n_tok)
+    xs = torch.from_numpy(xs_np).cuda()
+    ys = torch.empty((max(n_layers, 2), HIDDEN), dtype=torch.float32, device="cuda")
+    stream = torch.cuda.Stream()
+    barrier = (lambda: (dist.barrier(), torch.cuda.synchronize())) if world > 1 else None
     peer_exchange = world > 1 and args.exchange == "peer" and args.accum == "pairwise"
     if peer_exchange:
         ep.connect_exchange(ctx, rank, world, HIDDEN)
-        # the ranks start together (barrier before the timed region); a rank that waits longer than
-        # about 20 ms for a peer gives the step up (status 0x5503, reported below) instead of stalling
-        # the run
+        # a rank that waits longer than about 20 ms for a peer gives the step up (status 0x5503,
+        # reported below for every rank) instead of stalling the run
         ctx.ep_exchange_set_wait_limit(1 << 14)
-
-    def enqueue_step(i: int, stream_handle=None):
-        ly = layers[i % n_layers]
-        if world == 1:
-            ctx.cmd_routed_moe_layer(xs[i % n_tok], ly["wr"], ly["bias"], ly["table"], ly["shared"],
-                                     L.PAGE_MXFP4, INTER, ys[i % N_LAYERS], stream=stream_handle)
-        else:
-            k = i % N_LAYERS
-            ly_state = dict(ly)
-            if ly_state["shared"] is None:
-                ly_state["shared"] = ly["pages"].data_ptr()  # never read: this rank is not the owner
-            if peer_exchange:
-                ep.decode_step_fused(ctx, xs[i % n_tok], ly_state, ys[k], layer=i % n_layers, world=world,
-                                     inter=INTER, stream=stream_handle)
-            else:
-                ep.decode_step(ctx, xs[i % n_tok], ly_state, slots[k], ep_ids[k], ep_w[k], ys[k],
-                               layer=i % n_layers, rank=rank, world=world, inter=INTER, stream=stream_handle)
-
-    _note("layers resident")
-    stream = torch.cuda.Stream()
-    # Kernels of ours per step, counted by the context: pairwise order one (the layer kernel scores the
-    # experts and picks the routes itself); reference order router, up, down, mix.  Expert parallel adds
-    # the mix of the exchanged slots (the slot memset is not a kernel of ours, the all-reduce is NCCL's).
-
-    def capture(n_steps: int, first: int):
-        g = torch.cuda.CUDAGraph()
-        with torch.cuda.stream(stream):
-            with torch.cuda.graph(g, stream=stream):
-                for i in range(n_steps):
-                    enqueue_step(first + i, stream.cuda_stream)
-        return g
-
-    if world > 1:
-        dist.barrier()  # first launches load the kernels; the ranks enter them together
-    launched_before = ctx.launch_count
-    with torch.cuda.stream(stream):
-        for i in range(3):  # first launches outside capture (module load)
-            enqueue_step(i, stream.cuda_stream)
-    stream.synchronize()
-    kernels_per_step = (ctx.launch_count - launched_before) // 3
-    _note("eager warm-up steps done")
-    rem = args.steps % N_LAYERS
-    full = args.steps // N_LAYERS
-    if world == 1 or peer_exchange:
-        launch_mode = "cuda graph of 14 layer-steps"
-        graph = capture(N_LAYERS, 0)
-        graph_rem = capture(rem, 0) if rem else None
-    else:
-        # NCCL all-reduces replayed from a CUDA graph ran ~10x slower than eager ones here
-        # (0.95 ms against 0.1 ms per step at 2 GPUs), so the expert-parallel steps are launched eagerly
-        launch_mode = "eager launches (layer kernel with its router, NCCL all-reduce, mix per step)"
-        graph = graph_rem = None
-
-    def replay(n_full: int, with_rem: bool):
-        with torch.cuda.stream(stream):
-            if graph is None:
-                for i in range(n_full * N_LAYERS + (rem if with_rem else 0)):
-                    enqueue_step(i, stream.cuda_stream)
-                return
-            for _ in range(n_full):
-                graph.replay()
-            if with_rem and graph_rem is not None:
-                graph_rem.replay()
-
-    _note(f"launch mode: {launch_mode}")
-    warm_full = max(1, (args.warmup + N_LAYERS - 1) // N_LAYERS)
-    replay(warm_full, False)
-    stream.synchronize()
-    if world > 1:
-        dist.barrier()
-    torch.cuda.synchronize()
-    sampler = ClockSampler(local_rank)
-    if rank == 0:
-        sampler.start()
-    time.sleep(0.25)
-    if world > 1:
-        dist.barrier()  # the ranks start the timed region together: a rank's kernels wait for the others'
-        torch.cuda.synchronize()
-    ctx.device_status()  # read and clear: what is reported covers the timed region and the host leg
-    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    with torch.cuda.stream(stream):
-        e0.record(stream)
-    replay(full, True)
-    with torch.cuda.stream(stream):
-        e1.record(stream)
-    stream.synchronize()
-    torch.cuda.synchronize()
-    if world > 1:
-        dist.barrier()
-    ms = e0.elapsed_time(e1)
-    if world > 1:
-        t = torch.tensor([ms], dtype=torch.float64, device="cuda")
-        dist.all_reduce(t, op=dist.ReduceOp.MAX)
-        ms = float(t.item())
-    clocks = sampler.stop() if rank == 0 else None
-    _note(f"timed region done: {ms:.3f} ms")
-    # one token stream: with several GPUs the experts of the same tokens are spread over the ranks
-    value = args.steps / (ms / 1e3)
-
-    # The layer kernel with the routes given (no expert scoring): a CUDA graph of one launch per resident
-    # layer with fixed routes (six routed experts + the shared one, other pages every launch), replayed back
-    # to back and timed with CUDA events on the launching stream.  Not part of the headline number; it shows
-    # what the routing costs inside the kernel.
-    from colormlm_b200.s14 import TokenRoute
-
-    layer_ms = None
-    if world == 1:
-        rr = np.random.default_rng(7)
-        fixed = []
-        for k in range(N_LAYERS):
-            ly = layers[k % n_layers]
-            ids = rr.permutation(N_EXPERTS)[:TOP_K].tolist()
-            fixed.append(([TokenRoute(ids, [1.0 / TOP_K] * TOP_K, [ly["pages"].data_ptr() + e * PAGE_BYTES for e in ids])],
-                          ly["shared"]))
-
-        def enqueue_layer_only(k):
-            route, shared = fixed[k]
-            ctx.cmd_moe_layer(xs[k:k + 1], ys[k:k + 1], route, shared, L.PAGE_MXFP4, HIDDEN, INTER,
-                              stream=stream.cuda_stream)
-
-        with torch.cuda.stream(stream):
-            for k in range(2):
-                enqueue_layer_only(k)
-        stream.synchronize()
-        g_layer = torch.cuda.CUDAGraph()
-        with torch.cuda.stream(stream):
-            with torch.cuda.graph(g_layer, stream=stream):
-                for k in range(N_LAYERS):
-                    enqueue_layer_only(k)
-        reps = 60
-        with torch.cuda.stream(stream):
-            for _ in range(5):
-                g_layer.replay()
-            k0, k1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-            k0.record(stream)
-            for _ in range(reps):
-                g_layer.replay()
-            k1.record(stream)
-        stream.synchronize()
-        layer_ms = k0.elapsed_time(k1) / (reps * N_LAYERS)
-    peak, peak_kind = measured_peaks()
-    # pairwise order on one GPU: a step is one launch of the layer kernel (routing included), so the timed
-    # region itself gives the kernel's duration; otherwise the fixed-route launches stand for it
-    one_kernel_step = world == 1 and kernels_per_step == 1
-    roof_ms, roof_bytes = (ms / args.steps, STEP_BYTES) if one_kernel_step else (layer_ms, LAYER_BYTES)
-    achieved = roof_bytes / (roof_ms * 1e-3) / 1e9 if roof_ms else None
-
-    # end to end through the host-buffer call: pinned x in, y (+ route) out, every step
-    hgen = torch.Generator()
-    hgen.manual_seed(4242)  # the same host tokens on every rank: the ranks must agree on the routes
-    hx = torch.randn((n_tok, HIDDEN), dtype=torch.float32, generator=hgen).pin_memory()
-    hy = torch.empty((HIDDEN,), dtype=torch.float32).pin_memory()
-    hx_np, hy_np = hx.numpy(), hy.numpy()
-    ids_np, w_np = np.empty(TOP_K, np.int32), np.empty(TOP_K, np.float32)
-    xd = torch.empty(HIDDEN, dtype=torch.float32, device="cuda")
-    e2e_steps = 0 if args.kernel_only else min(args.steps, 2000)
-    # one GPU: every layer's call is bound once (descriptor validated and recorded), a step is the
-    # foreign call alone: pinned x in, y and the route out
-    bound = [ctx.bind_routed_moe_layer_host(ly["wr"], ly["bias"], ly["table"], ly["shared"], L.PAGE_MXFP4, INTER)
-             for ly in layers] if world == 1 else None
-    hx_addr, hy_addr, ids_addr, w_addr = hx.data_ptr(), hy.data_ptr(), ids_np.ctypes.data, w_np.ctypes.data
+    slots = torch.zeros((TOP_K + 1, HIDDEN), dtype=torch.float32, device="cuda")
+    ep_ids = torch.empty(TOP_K, dtype=torch.int32, device="cuda")
+    ep_w = torch.empty(TOP_K, dtype=torch.float32, device="cuda")
     ep_states = []
     for ly in layers:
         st_ = dict(ly)
@@ -434,83 +343,367 @@ def run_gpu(args) -> None:
             st_["shared"] = ly["pages"].data_ptr()  # never read: this rank is not the owner
         ep_states.append(st_)
 
-    def e2e_step(i):
-        if world == 1:
-            bound[i % n_layers].run_addresses(hx_addr + (i % n_tok) * HIDDEN * 4, hy_addr, ids_addr, w_addr)
-        else:
-            with torch.cuda.stream(stream):
-                xd.copy_(hx[i % n_tok], non_blocking=True)
-                # the per-token host round trip on several GPUs goes through the NCCL exchange (the exchange
-                # inside the kernel was measured from CUDA graphs only)
-                ep.decode_step(ctx, xd, ep_states[i % n_layers], slots[0], ep_ids[0], ep_w[0], ys[0],
-                               layer=i % n_layers, rank=rank, world=world, inter=INTER, stream=stream.cuda_stream)
-                hy.copy_(ys[0], non_blocking=True)
-            stream.synchronize()
+    # ---- what a region of K steps launches -------------------------------------------------
+    stacks = {}
 
-    if world > 1:
-        dist.barrier()  # rank 0 has just stopped its clock sampler, which can take two seconds
-    for i in range(0 if args.kernel_only else max(3, min(args.warmup, 100))):
-        e2e_step(i)
+    def stack_of(first: int, count: int):
+        key = (first, count)
+        if key not in stacks:
+            stacks[key] = DecodeStack(ctx, [layers[(first + i) % n_layers] for i in range(count)], inter=INTER, residual=True)
+        return stacks[key]
+
+    h_out = torch.empty(HIDDEN, dtype=torch.float32, device="cuda")
+
+    def enqueue_steps(k_steps: int, first_step: int, handle):
+        """k_steps layer-tokens starting at step `first_step`; returns the launches of the layer kernel."""
+        if workload == "stack":
+            done, launches = 0, 0
+            while done < k_steps:
+                count = min(n_layers, k_steps - done)
+                stack_of(0, count).cmd_decode(xs[((first_step + done) // n_layers) % n_tok], h_out, stream=handle)
+                done += count
+                launches += 1
+            return launches
+        for i in range(first_step, first_step + k_steps):
+            ly = layers[i % n_layers]
+            if world == 1:
+                ctx.cmd_routed_moe_layer(xs[i % n_tok], ly["wr"], ly["bias"], ly["table"], ly["shared"], L.PAGE_MXFP4,
+                                         INTER, ys[i % n_layers], stream=handle)
+            elif peer_exchange:
+                ep.decode_step_fused(ctx, xs[i % n_tok], ep_states[i % n_layers], ys[i % n_layers], layer=i % n_layers,
+                                     world=world, inter=INTER, stream=handle)
+            else:
+                ep.decode_step(ctx, xs[i % n_tok], ep_states[i % n_layers], slots, ep_ids, ep_w, ys[i % n_layers],
+                               layer=i % n_layers, rank=rank, world=world, inter=INTER, stream=handle)
+        return k_steps
+
     if world > 1:
         dist.barrier()
-    t0 = time.perf_counter()
-    for i in range(e2e_steps):
-        e2e_step(i)
-    e2e_sec = max(time.perf_counter() - t0, 1e-9)
+    if world == 1:
+        # the stacks a region needs are bound before anything is captured (binding allocates)
+        stack_of(0, n_layers)
+        if args.steps % n_layers:
+            stack_of(0, args.steps % n_layers)
+    with torch.cuda.stream(stream):
+        enqueue_steps(min(n_layers, 3) if workload == "layer" else n_layers, 0, stream.cuda_stream)  # module load
+    stream.synchronize()
+    _note("eager warm-up launches done")
+    use_graph = world == 1 or peer_exchange
+    graph = None
+    if use_graph:
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.stream(stream):
+            with torch.cuda.graph(graph, stream=stream):
+                enqueue_steps(args.steps, 0, stream.cuda_stream)
+        launch_mode = f"cuda graph of the {args.steps} steps of a region"
+    else:
+        # NCCL all-reduces replayed from a CUDA graph ran ~10x slower than eager ones here
+        launch_mode = "eager launches (layer kernel with its router, NCCL all-reduce, mix per step)"
+    launches_per_region = None
+
+    def region():
+        nonlocal launches_per_region
+        if graph is not None:
+            graph.replay()
+        else:
+            enqueue_steps(args.steps, 0, stream.cuda_stream)
+
+    # launches of our kernels per region, counted by the context on an eager pass
+    with torch.cuda.stream(stream):
+        c0 = ctx.launch_count
+        enqueue_steps(args.steps, 0, stream.cuda_stream)
+        launches_per_region = ctx.launch_count - c0
+    stream.synchronize()
+    warm_regions = max(1, -(-args.warmup // args.steps))
+    with torch.cuda.stream(stream):
+        for _ in range(warm_regions):
+            region()
+    stream.synchronize()
     if world > 1:
-        t = torch.tensor([e2e_sec], dtype=torch.float64, device="cuda")
-        dist.all_reduce(t, op=dist.ReduceOp.MAX)
-        e2e_sec = float(t.item())
-    e2e_value = e2e_steps / e2e_sec
+        dist.barrier()
+    torch.cuda.synchronize()
+    ctx.device_status()  # read and clear: what is reported covers the timed regions and the host leg
+    sampler = ClockSampler(local_rank)
+    if rank == 0:
+        sampler.start()
+        time.sleep(0.2)
+    # keep the regions running until the sampler has seen the GPU under load a few times
+    ms_all = timed_repeats(torch, stream, region, args.repeats, barrier)
+    extra = 0
+    while rank == 0 and world == 1 and sampler.samples() < 6 and extra < 2000:
+        ms_all += timed_repeats(torch, stream, region, 10)
+        extra += 10
+    if world > 1:
+        t = torch.tensor(ms_all[:args.repeats], dtype=torch.float64, device="cuda")
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)  # every repeat: the slowest rank
+        ms_all = [float(v) for v in t.tolist()]
+    clocks = sampler.stop() if rank == 0 else None
+    ms = float(np.median(ms_all))
+    value = args.steps / (ms / 1e3)
+    _note(f"timed regions done: median {ms:.4f} ms")
+
+    # ---- the layer kernel with the routes given (no expert scoring), for the roofline entry's breakdown
+    layer_ms = None
+    if world == 1 and not args.kernel_only_skip_fixed:
+        rr = np.random.default_rng(7)
+        fixed = []
+        for k in range(n_layers):
+            ly = layers[k]
+            ids = rr.permutation(N_EXPERTS)[:TOP_K].tolist()
+            fixed.append(([TokenRoute(ids, [1.0 / TOP_K] * TOP_K, [ly["pages"].data_ptr() + e * PAGE_BYTES for e in ids])],
+                          ly["shared"]))
+
+        def enqueue_fixed():
+            for k in range(n_layers):
+                route, shared = fixed[k]
+                ctx.cmd_moe_layer(xs[k:k + 1], ys[k:k + 1], route, shared, L.PAGE_MXFP4, HIDDEN, INTER,
+                                  stream=stream.cuda_stream)
+
+        with torch.cuda.stream(stream):
+            enqueue_fixed()
+        stream.synchronize()
+        g_fixed = torch.cuda.CUDAGraph()
+        with torch.cuda.stream(stream):
+            with torch.cuda.graph(g_fixed, stream=stream):
+                enqueue_fixed()
+        layer_ms = float(np.median(timed_repeats(torch, stream, g_fixed.replay, 30))) / n_layers
+
+    # ---- the other way of launching the same steps, and the bit-identical order, for comparison
+    other = {}
+    if world == 1 and not args.kernel_only:
+        def time_variant(name, accum, wl):
+            nonlocal workload
+            saved_mode, saved_wl = ctx.accumulation, workload
+            ctx.set_accumulation(accum)
+            workload = wl
+            try:
+                with torch.cuda.stream(stream):
+                    enqueue_steps(n_layers, 0, stream.cuda_stream)
+                stream.synchronize()
+                g = torch.cuda.CUDAGraph()
+                with torch.cuda.stream(stream):
+                    with torch.cuda.graph(g, stream=stream):
+                        enqueue_steps(n_layers, 0, stream.cuda_stream)
+                other[name] = float(np.median(timed_repeats(torch, stream, g.replay, 20))) / n_layers
+            finally:
+                ctx.set_accumulation(saved_mode)
+                workload = saved_wl
+
+        if args.accum == "pairwise":
+            time_variant("single_layer_launch_ms_per_step" if workload == "stack" else "stack_launch_ms_per_step",
+                         L.ACCUM_PAIRWISE, "layer" if workload == "stack" else "stack")
+            time_variant("reference_order_ms_per_step", L.ACCUM_REFERENCE, "layer")
+
+    # ---- parity of the timed path on its own steps, against the CPU oracle on the same bytes
+    parity = None
+    sha = None
+    if not args.kernel_only and (rank == 0 or world > 1):
+        from oracle import s14_oracle as oracle
+
+        oracle.build()
+        cpu_threads(oracle)
+        hp = HostPages()
+        if rank == 0:
+            page0 = layers[0]["pages"][0].cpu().numpy()
+            host0 = synth.hashed_expert_page(0, layers[0]["owned"][0], HIDDEN, INTER)
+            sha = {"gpu": hashlib.sha256(page0.tobytes()).hexdigest(), "host": hashlib.sha256(host0.tobytes()).hexdigest()}
+            sha["match"] = sha["gpu"] == sha["host"]
+        if workload == "stack" and rank == 0:
+            # one token through the whole chain: every layer's output and the final token
+            outs = []
+            per_layer = [dict(ly) for ly in layers]
+            for ly in per_layer:
+                ly["y"] = torch.empty(HIDDEN, dtype=torch.float32, device="cuda")
+                ly["ids"] = torch.empty(TOP_K, dtype=torch.int32, device="cuda")
+            st = DecodeStack(ctx, per_layer, inter=INTER, residual=True)
+            hh = torch.empty(HIDDEN, dtype=torch.float32, device="cuda")
+            st.cmd_decode(xs[0], hh)
+            torch.cuda.synchronize()
+            b32, b64, routes_ok = [], [], True
+            h64 = xs_np[0].copy()
+            for l in range(n_layers):
+                # the CPU chain runs on its own (double-accumulated layers); the F32-order layer is given
+                # the same layer input, so that its figure is the summation-order noise of one layer and
+                # not the divergence of two chains
+                y64, ids64, _ = cpu_layer(oracle, hp, l, h64, acc64=True)
+                y32, _, _ = cpu_layer(oracle, hp, l, h64, acc64=False)
+                got = per_layer[l]["y"].cpu().numpy()
+                routes_ok = routes_ok and bool(np.array_equal(per_layer[l]["ids"].cpu().numpy(), ids64))
+                b64.append(error_block(oracle, got, y64))
+                b32.append(error_block(oracle, got, y32))
+                h64 = (h64 + y64).astype(np.float32)
+            st.close()
+            parity = {"steps": n_layers, "what": "one token through the chain, every layer's output, independent CPU chain "
+                                                 "(double-accumulated); outputs grow with depth, see max_abs_in_ulps_of_largest",
+                      "routes_bit_exact": routes_ok,
+                      "vs_double_accumulated_oracle": worst(b64), "vs_f32_order_oracle": worst(b32),
+                      "final_token_vs_double_accumulated": error_block(oracle, hh.cpu().numpy(), h64)}
+        elif workload == "layer":
+            n_check = 8
+            b32, b64, routes_ok = [], [], True
+            idsd = torch.empty(TOP_K, dtype=torch.int32, device="cuda")
+            yd = torch.empty(HIDDEN, dtype=torch.float32, device="cuda")
+            digest = hashlib.sha256()
+            for i in range(n_check):
+                ly = layers[i % n_layers]
+                if world == 1:
+                    ctx.cmd_routed_moe_layer(xs[i], ly["wr"], ly["bias"], ly["table"], ly["shared"], L.PAGE_MXFP4, INTER, yd, idsd)
+                elif peer_exchange:
+                    ep.decode_step_fused(ctx, xs[i], ep_states[i % n_layers], yd, layer=i % n_layers, world=world, inter=INTER,
+                                         ids=idsd)
+                else:
+                    ep.decode_step(ctx, xs[i], ep_states[i % n_layers], slots, idsd, ep_w, yd, layer=i % n_layers, rank=rank,
+                                   world=world, inter=INTER)
+                torch.cuda.synchronize()
+                got = yd.cpu().numpy()
+                digest.update(got.tobytes())
+                if rank == 0:
+                    y64, ids64, _ = cpu_layer(oracle, hp, i % n_layers, xs_np[i], acc64=True)
+                    y32, _, _ = cpu_layer(oracle, hp, i % n_layers, xs_np[i], acc64=False)
+                    routes_ok = routes_ok and bool(np.array_equal(idsd.cpu().numpy(), ids64))
+                    b64.append(error_block(oracle, got, y64))
+                    b32.append(error_block(oracle, got, y32))
+            y_digest = digest.hexdigest()
+            equal = True
+            if world > 1:
+                all_d = [None] * world
+                dist.all_gather_object(all_d, y_digest)
+                equal = all(d == all_d[0] for d in all_d)
+            if rank == 0:
+                parity = {"steps": n_check, "what": "the first layer-tokens of the timed sequence", "routes_bit_exact": routes_ok,
+                          "vs_double_accumulated_oracle": worst(b64), "vs_f32_order_oracle": worst(b32),
+                          "y_digest": y_digest, "y_equal_across_ranks": equal}
+
+    # ---- end to end through the host-buffer call: pinned x in, result out, every call
+    hx = torch.from_numpy(xs_np.copy()).pin_memory()
+    hy = torch.empty((HIDDEN,), dtype=torch.float32).pin_memory()
+    ids_np, w_np = np.empty(TOP_K, np.int32), np.empty(TOP_K, np.float32)
+    hx_addr, hy_addr = hx.data_ptr(), hy.data_ptr()
+    e2e_steps = 0 if args.kernel_only else min(max(args.steps, 280), 2800)
+    h2d = d2h = 0.0
+    if e2e_steps:
+        if workload == "stack":
+            full = stack_of(0, n_layers)
+            e2e_steps = (e2e_steps // n_layers) * n_layers
+            calls = e2e_steps // n_layers
+            h2d, d2h = HIDDEN * 4 / n_layers, HIDDEN * 4 / n_layers  # one token in and out per n_layers steps
+
+            def e2e_call(i):
+                full.decode_host_addresses(hx_addr + (i % n_tok) * HIDDEN * 4, hy_addr)
+        elif world == 1:
+            bound = [ctx.bind_routed_moe_layer_host(ly["wr"], ly["bias"], ly["table"], ly["shared"], L.PAGE_MXFP4, INTER)
+                     for ly in layers]
+            calls = e2e_steps
+            h2d, d2h = HIDDEN * 4, HIDDEN * 4 + TOP_K * 8
+
+            def e2e_call(i):
+                bound[i % n_layers].run_addresses(hx_addr + (i % n_tok) * HIDDEN * 4, hy_addr, ids_np.ctypes.data, w_np.ctypes.data)
+        else:
+            xd = torch.empty(HIDDEN, dtype=torch.float32, device="cuda")
+            calls = e2e_steps
+            h2d, d2h = HIDDEN * 4, HIDDEN * 4
+
+            def e2e_call(i):
+                with torch.cuda.stream(stream):
+                    xd.copy_(hx[i % n_tok], non_blocking=True)
+                    if peer_exchange:
+                        ep.decode_step_fused(ctx, xd, ep_states[i % n_layers], ys[0], layer=i % n_layers, world=world,
+                                             inter=INTER, stream=stream.cuda_stream)
+                    else:
+                        ep.decode_step(ctx, xd, ep_states[i % n_layers], slots, ep_ids, ep_w, ys[0], layer=i % n_layers,
+                                       rank=rank, world=world, inter=INTER, stream=stream.cuda_stream)
+                    hy.copy_(ys[0], non_blocking=True)
+                stream.synchronize()
+
+        if world > 1:
+            dist.barrier()
+        for i in range(min(calls, 20)):
+            e2e_call(i)
+        if world > 1:
+            dist.barrier()
+        t0 = time.perf_counter()
+        for i in range(calls):
+            e2e_call(i)
+        e2e_sec = max(time.perf_counter() - t0, 1e-9)
+        if world > 1:
+            t = torch.tensor([e2e_sec], dtype=torch.float64, device="cuda")
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+            e2e_sec = float(t.item())
+        e2e_value = e2e_steps / e2e_sec
+    else:
+        e2e_value = None
     _note("end-to-end leg done")
 
-    device_status = ctx.device_status()  # 0 unless a bounded wait of a kernel ran out
+    status = ctx.device_status()  # 0 unless a bounded wait of a kernel ran out
+    status_all = status
+    if world > 1:
+        t = torch.tensor([status], dtype=torch.int64, device="cuda")
+        gathered = [torch.zeros_like(t) for _ in range(world)]
+        dist.all_gather(gathered, t)
+        status_all = [int(g.item()) for g in gathered]
     if rank == 0:
+        peak, peak_kind = measured_peaks()
         cpu = None
         if world == 1 and not args.no_cpu_baseline and not args.kernel_only:
             from oracle import s14_oracle as oracle
 
             oracle.build()
-            sample = cpu_step_setup(2 + args.cpu_steps)
-            cpu_run(sample[:2])
-            sec = cpu_run(sample[2:])
-            cpu = {"value": args.cpu_steps / sec, "unit": "layer-tokens/s", "cores": oracle.max_threads(),
-                   "kind": "port",
-                   "sample": f"{args.cpu_steps} layer-tokens of the same workload (router + 7 experts), "
+            cores = cpu_threads(oracle)
+            sample = cpu_steps(oracle, 2 + args.cpu_steps)
+            cpu_run(oracle, sample[:2])
+            sec = cpu_run(oracle, sample[2:])
+            cpu = {"value": args.cpu_steps / sec, "unit": "layer-tokens/s", "cores": cores, "kind": "port",
+                   "sample": f"{args.cpu_steps} layer-tokens of the same workload and the same bytes (router + 7 experts), "
                              f"{sec:.1f} s of CPU work"}
+        kernels_per_step = launches_per_region / args.steps
+        achieved = STEP_BYTES * args.steps / (ms * 1e-3) / 1e9
+        # several GPUs: a rank streams the pages it owns; the busiest rank bounds the step
+        per_rank = None
+        if world > 1:
+            hp2 = None
+            per_rank = "see parity.y_equal_across_ranks; per-rank bytes depend on the routes"
         line = {
             "metric": "moe_layer_tokens_per_s", "value": value, "unit": "layer-tokens/s", "n_gpus": world,
-            "steps": args.steps, "warmup": warm_full * N_LAYERS, "ms_per_step": ms / args.steps,
-            "higher_is_better": True, "scaling": "weak" if world == 1 else "strong", "vs_baseline": None,
-            "dtype": "f32",
-            "data": "synthetic",
-            "config": {"workload": WORKLOAD, "layers_resident": n_layers, "accumulation": args.accum,
-                       "launch": launch_mode,
-                       "l2": "inputs larger than L2: 14 x 3.4 GB of pages walked round-robin, 96 MB per step",
+            "steps": args.steps, "warmup": args.warmup, "warmup_effective": warm_regions * args.steps,
+            "ms_per_step": ms / args.steps, "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
+            "dtype": "f32", "data": "synthetic",
+            "config": {"workload": WORKLOAD,
+                       "launch": ("14 chained layers (h <- h + moe(h)) per launch of the layer kernel, " if workload == "stack"
+                                  else "one launch per layer-token, independent tokens, ") + launch_mode,
+                       "bench_workload": workload, "layers_resident": n_layers, "accumulation": args.accum,
+                       "l2": "inputs larger than L2: 14 x 3.4 GB of pages walked layer by layer, 96 MB per step",
                        "parallelism": (f"ep{world}: expert e on rank e mod {world}, "
                                        + ("down vectors stored into every rank's slot buffer over peer memory by the "
-                                          "layer kernel, flag wait, ordered mix in the same launch" if peer_exchange
+                                          "layer kernel, bounded wait, ordered mix in the same launch" if peer_exchange
                                           else "NCCL all-reduce of the slot buffer + ordered mix"))
                        if world > 1 else "single"},
-            "hbm_gbs": value * STEP_BYTES / 1e9, "hbm_frac_of_measured_peak": value * STEP_BYTES / 1e9 / (peak * world),
+            "repeats": {"count": len(ms_all), "region_ms_median": ms, "region_ms_min": float(np.min(ms_all)),
+                        "region_ms_max": float(np.max(ms_all)), "region_ms_p10": float(np.percentile(ms_all, 10)),
+                        "region_ms_p90": float(np.percentile(ms_all, 90))},
+            "hbm_gbs": achieved, "hbm_frac_of_measured_peak": achieved / (peak * world),
             "algorithmic_bytes_per_step": STEP_BYTES,
             "roofline": {"bound": "hbm",
                          "kernel": ("k_moe_layer_umma: expert scores + routes, 7 MXFP4 experts (up projections, SwiGLU, "
-                                    "down projection), sums over slices, ordered mix"
-                                    if args.accum == "pairwise" else "reference-order layer kernels (up, down, mix)"),
-                         "achieved": achieved, "peak": peak, "unit": "GB/s",
-                         "frac": achieved / peak if achieved else None,
-                         "peak_kind": peak_kind, "traffic": NCU_TRAFFIC_BYTES if one_kernel_step else None,
-                         "bytes_per_launch": roof_bytes, "ms_per_launch": roof_ms,
-                         "timed": ("the timed region: one launch per step, CUDA events on the launching stream"
-                                   if one_kernel_step else
-                                   "CUDA graph of 14 layer launches with fixed routes, 60 replays, CUDA events"),
-                         "fixed_routes_ms_per_launch": layer_ms},
+                                    "down projection), ordered mix" + (", 14 layers per launch" if workload == "stack" else "")
+                                    if args.accum == "pairwise" else "reference-order layer kernels (router, up, down, mix)"),
+                         "achieved": achieved if world == 1 else None, "peak": peak, "unit": "GB/s",
+                         "frac": achieved / peak if world == 1 else None,
+                         "frac_of_nominal_8000": achieved / 8000.0 if world == 1 else None,
+                         "peak_kind": peak_kind, "traffic": NCU_TRAFFIC_BYTES,
+                         "bytes_per_launch": STEP_BYTES * (n_layers if workload == "stack" else 1),
+                         "ms_per_launch": ms / args.steps * (n_layers if workload == "stack" else 1),
+                         "timed": "the timed regions (median repeat): every step is part of a launch of this kernel, "
+                                  "CUDA events on the launching stream",
+                         "fixed_routes_ms_per_launch": layer_ms, **other},
+            "parity": parity, "pages_sha256_sample": sha,
             "cpu_baseline": cpu,
-            "e2e": {"value": e2e_value, "unit": "layer-tokens/s", "h2d_bytes_per_step": HIDDEN * 4,
-                    "d2h_bytes_per_step": HIDDEN * 4 + TOP_K * 8, "steps": e2e_steps},
-            "gpu_launches": kernels_per_step * args.steps,
-            "device_status": device_status,
+            "e2e": {"value": e2e_value, "unit": "layer-tokens/s", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
+                    "steps": e2e_steps,
+                    "call": ("s14_stack_decode_host: one token per call through the 14 layers" if workload == "stack" else
+                             "s14_routed_moe_layer_host per layer-token" if world == 1 else
+                             "pinned token in, expert-parallel step, result out per layer-token")},
+            "gpu_launches": launches_per_region, "kernels_per_step": kernels_per_step,
+            "device_status": status, "device_status_all": status_all,
             "clocks": clocks,
         }
         print(json.dumps(line), flush=True)
@@ -520,6 +713,179 @@ def run_gpu(args) -> None:
         sys.stdout.flush()
         sys.stderr.flush()
         os._exit(0)  # skip NCCL teardown, which did not return here after the run
+    for st in stacks.values():
+        st.close()
+    ctx.close()
+
+
+def run_small_workload(args, workload, torch, L, synth, S14Context, TokenRoute) -> None:
+    """The single-expert chain (hidden 4096, intermediate 2048, route weight 0.3), the FP8 projection
+    matvec (1024 x 4096, 1 / 4 / 8 tokens) and the 8-token verify block: L2-cold by rotating over
+    more than 126 MB of distinct weights, timed like the main workload, each with its own roofline
+    entry and the CPU oracle timed beside it."""
+    from colormlm_b200.pages import ExpertPageLayout
+    from oracle import s14_oracle as oracle
+
+    oracle.build()
+    cores = cpu_threads(oracle)
+    ctx = S14Context(0)
+    ctx.set_accumulation(L.ACCUM_REFERENCE if args.accum == "reference" else L.ACCUM_PAIRWISE)
+    stream = torch.cuda.Stream()
+    peak, peak_kind = measured_peaks()
+    g = synth.rng(126)
+    if workload == "expert_chain":
+        n_pages = 16  # 214 MB of distinct pages
+        writer = synth.HashedPageWriter(torch, HIDDEN, INTER)
+        pages = torch.empty((n_pages, PAGE_BYTES), dtype=torch.uint8, device="cuda")
+        for e in range(n_pages):
+            writer.fill(pages[e], 100, e)
+        x_np = synth.activations(g, 1, HIDDEN)
+        x = torch.from_numpy(x_np).cuda()
+        y = torch.empty_like(x)
+        routes = [[TokenRoute([e], [0.3], [pages[e].data_ptr()])] for e in range(n_pages)]
+        unit_bytes, what = PAGE_BYTES + 2 * HIDDEN * 4, "single routed expert: w1, w3 -> limited SwiGLU -> w2 -> x 0.3"
+
+        def enqueue():
+            for k in range(args.steps):
+                ctx.cmd_moe_layer(x, y, routes[k % n_pages], None, L.PAGE_MXFP4, HIDDEN, INTER, stream=stream.cuda_stream)
+
+        def check():
+            ctx.cmd_moe_layer(x, y, routes[3], None, L.PAGE_MXFP4, HIDDEN, INTER)
+            torch.cuda.synchronize()
+            tp = synth.hashed_tensor_page(100, 3, HIDDEN, INTER)
+            ref32, _ = oracle.expert_chain_mxfp4(x_np[0], tp, HIDDEN, INTER, 0.3)
+            ref64 = oracle.moe_layer_acc64(x_np[0], [tp], np.asarray([0.3], np.float32), None, 2, HIDDEN, INTER)
+            return {"vs_double_accumulated_oracle": error_block(oracle, y.cpu().numpy()[0], ref64),
+                    "vs_f32_order_oracle": error_block(oracle, y.cpu().numpy()[0], ref32)}
+
+        def cpu_once():
+            tp = synth.hashed_tensor_page(100, 3, HIDDEN, INTER)
+            t0 = time.perf_counter()
+            for _ in range(20):
+                oracle.expert_chain_mxfp4(x_np[0], tp, HIDDEN, INTER, 0.3)
+            return (time.perf_counter() - t0) / 20
+    elif workload == "wq_a":
+        n, k, t = 1024, 4096, max(1, min(8, args.tokens))
+        n_w = 40  # 168 MB of distinct matrices
+        ws = torch.stack([torch.from_numpy(synth.e4m3_codes(synth.rng(900 + i), n, k)) for i in range(n_w)]).cuda()
+        s_np = synth.fp8_block_scales_f32(g, n, k)
+        sc = torch.from_numpy(s_np).cuda()
+        x_np = synth.activations(g, t, k)
+        x = torch.from_numpy(x_np).cuda()
+        y = torch.empty((t, n), dtype=torch.float32, device="cuda")
+        from colormlm_b200.s14 import S14MatvecShape
+        disp = [ctx.pipelines.bind_fp8(S14MatvecShape(n, k), x, ws[i].reshape(-1), sc.reshape(-1), y, scale_format=L.SCALE_F32,
+                                       n_tokens=t) for i in range(n_w)]
+        unit_bytes = n * k + s_np.size * 4 + t * k * 4 + t * n * 4
+        what = f"FP8 e4m3 projection matvec 1024 x 4096, one F32 scale per 128 x 128 block, {t} token(s)"
+
+        def enqueue():
+            for i in range(args.steps):
+                ctx.pipelines.cmd_fp8_matvec(disp[i % n_w], stream=stream.cuda_stream)
+
+        def check():
+            ctx.pipelines.cmd_fp8_matvec(disp[2])
+            torch.cuda.synchronize()
+            w2 = ws[2].cpu().numpy()
+            ref32 = np.stack([oracle.fp8_matvec(x_np[i], w2, s_np, n, k) for i in range(t)])
+            ref64 = np.stack([oracle.fp8_matvec_f64(x_np[i], w2, s_np, n, k) for i in range(t)])
+            return {"vs_double_accumulated_oracle": error_block(oracle, y.cpu().numpy(), ref64),
+                    "vs_f32_order_oracle": error_block(oracle, y.cpu().numpy(), ref32)}
+
+        def cpu_once():
+            w2 = ws[2].cpu().numpy()
+            t0 = time.perf_counter()
+            for _ in range(20):
+                for i in range(t):
+                    oracle.fp8_matvec(x_np[i], w2, s_np, n, k)
+            return (time.perf_counter() - t0) / 20
+    else:  # verify8
+        n_tok = 8
+        layers = resident_layers(torch, 2, 0, 1)
+        x_np = tokens(n_tok)
+        x = torch.from_numpy(x_np).cuda()
+        y = torch.empty_like(x)
+        per_layer = []
+        for l in range(2):
+            wr, bias = router_of_layer(l)
+            routes, distinct = [], set()
+            for t in range(n_tok):
+                ids, w, _, _ = oracle.router(x_np[t], wr, bias, 0, TOP_K, 1.0)
+                distinct.update(int(e) for e in ids)
+                routes.append(TokenRoute([int(e) for e in ids], w, [layers[l]["pages"].data_ptr() + int(e) * PAGE_BYTES for e in ids]))
+            per_layer.append((routes, len(distinct)))
+        d_avg = float(np.mean([d for _, d in per_layer]))
+        unit_bytes = int((d_avg + 1) * PAGE_BYTES + n_tok * 2 * HIDDEN * 4)
+        what = (f"8-token verify block through one layer, routes given, {d_avg:.0f} distinct routed experts + the shared one "
+                "(every distinct page counted once)")
+
+        def enqueue():
+            for i in range(args.steps):
+                routes, _ = per_layer[i % 2]
+                ctx.cmd_moe_layer(x, y, routes, layers[i % 2]["shared"], L.PAGE_MXFP4, HIDDEN, INTER, stream=stream.cuda_stream)
+
+        def check():
+            routes, _ = per_layer[0]
+            ctx.cmd_moe_layer(x, y, routes, layers[0]["shared"], L.PAGE_MXFP4, HIDDEN, INTER)
+            torch.cuda.synchronize()
+            hp = HostPages()
+            b64, b32 = [], []
+            for t in (0, 5):
+                y64, _, _ = cpu_layer(oracle, hp, 0, x_np[t], acc64=True)
+                y32, _, _ = cpu_layer(oracle, hp, 0, x_np[t], acc64=False)
+                b64.append(error_block(oracle, y.cpu().numpy()[t], y64))
+                b32.append(error_block(oracle, y.cpu().numpy()[t], y32))
+            return {"vs_double_accumulated_oracle": worst(b64), "vs_f32_order_oracle": worst(b32)}
+
+        def cpu_once():
+            hp = HostPages()
+            cpu_layer(oracle, hp, 0, x_np[0])
+            t0 = time.perf_counter()
+            for t in range(n_tok):
+                cpu_layer(oracle, hp, 0, x_np[t])
+            return time.perf_counter() - t0
+
+    with torch.cuda.stream(stream):
+        enqueue()
+    stream.synchronize()
+    gph = torch.cuda.CUDAGraph()
+    with torch.cuda.stream(stream):
+        with torch.cuda.graph(gph, stream=stream):
+            enqueue()
+    c0 = ctx.launch_count
+    with torch.cuda.stream(stream):
+        enqueue()
+    stream.synchronize()
+    launches = ctx.launch_count - c0
+    sampler = ClockSampler(0)
+    sampler.start()
+    time.sleep(0.2)
+    ms_all = timed_repeats(torch, stream, gph.replay, args.repeats)
+    while sampler.samples() < 6 and len(ms_all) < 4000:
+        ms_all += timed_repeats(torch, stream, gph.replay, 20)
+    clocks = sampler.stop()
+    ms = float(np.median(ms_all))
+    parity = check()
+    cpu_sec = cpu_once()
+    achieved = unit_bytes * args.steps / (ms * 1e-3) / 1e9
+    line = {"metric": {"expert_chain": "expert_chains_per_s", "wq_a": "matvecs_per_s", "verify8": "verify_blocks_per_s"}[workload],
+            "value": args.steps / (ms / 1e3), "unit": "calls/s", "n_gpus": 1, "steps": args.steps, "warmup": args.warmup,
+            "ms_per_step": ms / args.steps, "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "f32",
+            "data": "synthetic",
+            "config": {"workload": what, "bench_workload": workload, "accumulation": args.accum,
+                       "l2": "inputs larger than L2: distinct weights of more than 126 MB walked round-robin",
+                       "launch": f"cuda graph of the {args.steps} calls of a region"},
+            "repeats": {"count": len(ms_all), "region_ms_median": ms, "region_ms_min": float(np.min(ms_all)),
+                        "region_ms_max": float(np.max(ms_all))},
+            "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
+                         "frac_of_nominal_8000": achieved / 8000.0, "peak_kind": peak_kind, "traffic": None,
+                         "bytes_per_call": unit_bytes,
+                         "note": "a call of a few MB is bound by launch and memory latency, not by bandwidth"},
+            "parity": parity,
+            "cpu_baseline": {"value": 1.0 / cpu_sec, "unit": "calls/s", "cores": cores, "kind": "port",
+                             "sample": "the same call on the CPU oracle, same bytes", "ms_per_call": cpu_sec * 1e3},
+            "e2e": None, "gpu_launches": launches, "device_status": ctx.device_status(), "clocks": clocks}
+    print(json.dumps(line), flush=True)
     ctx.close()
 
 
@@ -529,23 +895,27 @@ def main() -> None:
     ap.add_argument("--steps", type=int, default=None)
     ap.add_argument("--warmup", type=int, default=None)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--workload", default=None, choices=["stack", "layer", "expert_chain", "wq_a", "verify8"])
+    ap.add_argument("--tokens", type=int, default=1, help="tokens of the wq_a workload (1, 4 or 8)")
     ap.add_argument("--accum", default="pairwise", choices=["pairwise", "reference"])
     ap.add_argument("--exchange", default="peer", choices=["peer", "nccl"],
                     help="several GPUs: down vectors exchanged inside the layer kernel over peer memory, or by NCCL all-reduce")
-    ap.add_argument("--cpu-steps", type=int, default=60)
+    ap.add_argument("--repeats", type=int, default=50, help="timed regions of --steps steps; the median is reported")
+    ap.add_argument("--cpu-steps", type=int, default=40)
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--layers", type=int, default=N_LAYERS,
                     help="resident layers (3.4 GB each); fewer than 14 is for profiler captures only")
     ap.add_argument("--kernel-only", action="store_true",
-                    help="skip the end-to-end and CPU legs (profiler captures)")
+                    help="skip the parity, end-to-end and CPU legs (profiler captures)")
+    ap.add_argument("--kernel-only-skip-fixed", action="store_true", help="also skip the fixed-route launches")
     args = ap.parse_args()
     if args.impl == "reference":
-        args.steps = args.steps if args.steps is not None else 60
+        args.steps = args.steps if args.steps is not None else 40
         args.warmup = args.warmup if args.warmup is not None else 3
         run_reference(args)
     else:
-        args.steps = args.steps if args.steps is not None else 28000
-        args.warmup = args.warmup if args.warmup is not None else 140
+        args.steps = args.steps if args.steps is not None else 280
+        args.warmup = args.warmup if args.warmup is not None else 28
         run_gpu(args)
 
 

@@ -84,3 +84,76 @@ def router_bias(g: np.random.Generator, n_experts: int) -> np.ndarray:
 
 def head_weight_bf16(g: np.random.Generator, vocab: int, hidden: int, std: float = 0.02) -> np.ndarray:
     return f32_to_bf16_bits((g.standard_normal((vocab, hidden), dtype=np.float32) * np.float32(std)))
+
+
+# ---- expert pages from a counter: the same bytes on the GPU (torch integer ops) and on the host ------
+# The benchmark holds thousands of pages (48 GB); drawing them with numpy and uploading them would take
+# minutes, so a page is a function of (layer, expert, byte position) that both sides can evaluate:
+# every 32-bit word is a mixed counter (the finaliser of MurmurHash3 over word index xor page key), the
+# E2M1 code bytes take it as it is (uniform over the 16 codes per nibble), the scale bytes (the last
+# 1 KB of every 17 408-byte unit of the expert page) become 119 + byte % 5 (2^-8 .. 2^-4).  The page is in
+# the byte order the GPU reads (pages.py); ``hashed_tensor_page`` converts it for the CPU oracle.
+
+UNIT_BYTES, UNIT_STRIDE = 16384, 17408
+
+
+def page_key(layer: int, expert: int, seed: int = 0x5314) -> int:
+    return (seed * 0x01000193 + layer * 0x10001 + expert * 0x9E3779B1 + 0x7F4A7C15) & 0xFFFFFFFF
+
+
+def _mix32_np(h: np.ndarray) -> np.ndarray:
+    m = np.uint64(0xFFFFFFFF)
+    h = (h * np.uint64(0x9E3779B1)) & m
+    h ^= h >> np.uint64(15)
+    h = (h * np.uint64(0x85EBCA77)) & m
+    h ^= h >> np.uint64(13)
+    h = (h * np.uint64(0xC2B2AE3D)) & m
+    h ^= h >> np.uint64(16)
+    return h
+
+
+def hashed_expert_page(layer: int, expert: int, hidden: int, inter: int, seed: int = 0x5314) -> np.ndarray:
+    """The expert page (GPU byte order) of (layer, expert) as uint8, on the host."""
+    n_bytes = ExpertPageLayout(hidden, inter).page_bytes
+    words = _mix32_np(np.arange(n_bytes // 4, dtype=np.uint64) ^ np.uint64(page_key(layer, expert, seed)))
+    page = words.astype(np.uint32).view(np.uint8).copy()
+    units = page.reshape(-1, UNIT_STRIDE)
+    units[:, UNIT_BYTES:] = 119 + units[:, UNIT_BYTES:] % 5
+    return page
+
+
+def hashed_tensor_page(layer: int, expert: int, hidden: int, inter: int, seed: int = 0x5314) -> np.ndarray:
+    """The same page as the six checkpoint tensors (what the CPU oracle reads)."""
+    import ctypes as C
+
+    from . import _lib as L
+
+    page = hashed_expert_page(layer, expert, hidden, inter, seed)
+    out = np.empty_like(page)
+    L.check(L.lib().s14_mxfp4_expert_page_to_tensors(hidden, inter, page.ctypes.data_as(C.c_void_p),
+                                                     out.ctypes.data_as(C.c_void_p)))
+    return out
+
+
+class HashedPageWriter:
+    """Fills device buffers with hashed expert pages (torch integer ops, no host copy)."""
+
+    def __init__(self, torch, hidden: int, inter: int, device="cuda", seed: int = 0x5314):
+        self.torch, self.hidden, self.inter, self.seed = torch, hidden, inter, seed
+        self.n_bytes = ExpertPageLayout(hidden, inter).page_bytes
+        self.idx = torch.arange(self.n_bytes // 4, dtype=torch.int64, device=device)
+        pos = torch.arange(self.n_bytes, dtype=torch.int64, device=device) % UNIT_STRIDE
+        self.scale_at = pos >= UNIT_BYTES
+
+    def fill(self, out, layer: int, expert: int) -> None:
+        """out: uint8 tensor of page_bytes on the device."""
+        m = 0xFFFFFFFF
+        h = self.idx ^ page_key(layer, expert, self.seed)
+        h = (h * 0x9E3779B1) & m
+        h ^= h >> 15
+        h = (h * 0x85EBCA77) & m
+        h ^= h >> 13
+        h = (h * 0xC2B2AE3D) & m
+        h ^= h >> 16
+        b = h.to(self.torch.int32).view(self.torch.uint8)
+        out.copy_(self.torch.where(self.scale_at, 119 + b % 5, b))
