@@ -390,69 +390,6 @@ __host__ __device__ uint32_t layer_work_list(uint32_t c, uint32_t G, uint32_t n_
 
 namespace {
 
-// The routes of the token from the picked experts (rank order = largest score + bias first, lowest
-// id on ties), by one warp: lane j takes route j.  The same sums and weights as k_router's last block:
-// weight = score / sum of the picked scores x route_scale.  Writes the jobs (the shared expert first,
-// so that its page can be asked for before the routes exist, then the routed experts in route
-// order), the mix (route order, the shared expert last) and every route's weight; `publish` also
-// writes the caller's ids and weights.  Expert parallel: the rank keeps the jobs of the experts it
-// owns and, as the shared expert's owner, the shared job; every job writes the row of its route slot.
-struct RouteConsts {  // what the route records need of the router, by value
-    uint32_t top_k, has_shared, shared_here, shared_kind, ep_rank, ep_world;
-    float route_scale;
-};
-__device__ __forceinline__ void routes_from_picks(const RouteConsts rc, const uint8_t *shared_page, int32_t *ids_out,
-                                                  float *weights_out, uint32_t lane, const uint32_t *ids, const float *picked,
-                                                  const unsigned long long *pages, bool publish, Job *jobs,
-                                                  uint32_t *n_jobs_out, float *mix_w, uint32_t *mix_slot, uint32_t *n_mix_out) {
-    float sum = 0.0f;
-    for (uint32_t j = 0; j < rc.top_k; ++j) sum = __fadd_rn(sum, picked[j]);  // every lane, the same order
-    const bool is_route = lane < rc.top_k;
-    const uint32_t id = is_route ? ids[lane] : 0u;
-    const bool owned = is_route && (rc.ep_world <= 1u || (id % rc.ep_world) == rc.ep_rank);
-    const uint32_t owned_mask = __ballot_sync(0xffffffffu, owned);
-    const uint32_t pos = rc.shared_here + __popc(owned_mask & ((1u << lane) - 1u));
-    if (is_route) {
-        const float w = __fmul_rn(__fdiv_rn(picked[lane], sum), rc.route_scale);
-        if (publish && ids_out) ids_out[lane] = (int32_t)id;
-        if (publish && weights_out) weights_out[lane] = w;
-        mix_w[lane] = w;  // every route's weight, also of experts other ranks own
-        mix_slot[lane] = lane;
-        if (owned) {
-            jobs[pos].page = reinterpret_cast<const uint8_t *>(pages[lane]);
-            jobs[pos].kind = S14_PAGE_MXFP4;
-            jobs[pos].token = 0;
-            jobs[pos].weight = w;
-            jobs[pos].is_shared = 0;
-            jobs[pos].out_index = lane;
-        }
-    } else if (lane == rc.top_k) {
-        if (rc.shared_here) {
-            jobs[0].page = shared_page;
-            jobs[0].kind = rc.shared_kind;
-            jobs[0].token = 0;
-            jobs[0].weight = 1.0f;
-            jobs[0].is_shared = 1;
-            jobs[0].out_index = rc.top_k;
-        }
-        if (rc.has_shared) {
-            mix_w[rc.top_k] = 1.0f;
-            mix_slot[rc.top_k] = rc.top_k | 0x80000000u;
-        }
-        *n_mix_out = rc.top_k + (rc.has_shared ? 1u : 0u);
-        *n_jobs_out = rc.shared_here + __popc(owned_mask);
-    }
-}
-
-// One round of a warp's selection: the largest key among the lanes' keys (0 = none), as the largest
-// upper word, then the largest lower word among the lanes that have it.
-__device__ __forceinline__ unsigned long long warp_max_key(unsigned long long key) {
-    const uint32_t hi = (uint32_t)(key >> 32), lo = (uint32_t)key;
-    const uint32_t best_hi = __reduce_max_sync(0xffffffffu, hi);
-    const uint32_t best_lo = __reduce_max_sync(0xffffffffu, hi == best_hi ? lo : 0u);
-    return ((unsigned long long)best_hi << 32) | best_lo;
-}
-
 // the one device copy of the deal (its divisions make it long; a CTA calls it once)
 __device__ __noinline__ uint32_t work_list_once(uint32_t c, uint32_t G, uint32_t n_jobs, uint32_t S, uint32_t RT, uint32_t KU,
                                                 uint32_t KD, uint32_t *items) {
@@ -467,6 +404,7 @@ __device__ __noinline__ uint32_t work_list_once(uint32_t c, uint32_t G, uint32_t
 
 // 544 threads = 17 warps: one sub-partition of the SM holds five of them, so 96 registers per thread
 // is the most the launch can have.
+template <bool kTrace>
 __global__ void __launch_bounds__(kThreads, 1)
 k_moe_layer_umma(const JobTable *__restrict__ dev_table, const __grid_constant__ JobTable param_table,
                  const float *__restrict__ x, float *d_out, float *__restrict__ y, uint8_t *tiles,
@@ -498,7 +436,6 @@ k_moe_layer_umma(const JobTable *__restrict__ dev_table, const __grid_constant__
     __shared__ int s_behind;   // expert parallel: a peer's word carries a later step's number
     __shared__ int s_last;     // this CTA finished the last job of a row tile / is the last CTA to leave
     __shared__ uint32_t s_abort_code;
-    __shared__ uint32_t s_dbg;
 
     const uint32_t tid = threadIdx.x, warp = tid >> 5, lane = tid & 31u;
     const uint32_t grid = gridDim.x, cta = blockIdx.x;
@@ -519,13 +456,16 @@ k_moe_layer_umma(const JobTable *__restrict__ dev_table, const __grid_constant__
     // Optional per-CTA time marks (SM clock) for profiling runs: kTraceWords words per CTA, word 0 the
     // global timer at entry; taken in the second layer of a stack (its code has run before), else in
     // the only one.  One designated thread writes each mark.
-    unsigned long long *const tr_base = trace ? trace + (size_t)cta * kTraceWords : nullptr;
+    // The kernel is compiled twice: the marks exist in the profiling build only.
+    unsigned long long *const tr_base = (kTrace && trace) ? trace + (size_t)cta * kTraceWords : nullptr;
     const uint32_t trace_layer = L > 1u ? 1u : 0u;
     unsigned long long *tr = trace_layer == 0u ? tr_base : nullptr;
     auto mark = [&](uint32_t i) {
-        if (tr && i < kTraceWords) tr[i] = (unsigned long long)clock64();
+        if constexpr (kTrace) {
+            if (tr && i < kTraceWords) tr[i] = (unsigned long long)clock64();
+        }
     };
-    if (tr_base && tid == 0) {
+    if (kTrace && tr_base && tid == 0) {
         unsigned long long gt;
         asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(gt));
         tr_base[0] = gt;
@@ -571,7 +511,6 @@ k_moe_layer_umma(const JobTable *__restrict__ dev_table, const __grid_constant__
             s_behind = 0;
             s_last = 0;
             s_abort_code = 0x5501u;
-            s_dbg = 0;
             s_n_items = 0;
             s_n_jobs = 0;
             s_n_mix = 0;
@@ -685,7 +624,7 @@ k_moe_layer_umma(const JobTable *__restrict__ dev_table, const __grid_constant__
 #pragma unroll 1
         for (uint32_t l = 0; l < L; ++l) {
             const uint32_t par = l & 1u;
-            tr = (l == trace_layer) ? tr_base : nullptr;
+            if constexpr (kTrace) tr = (l == trace_layer) ? tr_base : nullptr;
             // what a layer of a stack brings of its own; a single layer takes it from the launch arguments
             const uint16_t *const l_wr = stack ? stack[l].router_weight : rt.weight;
             const float *const l_bias = stack ? stack[l].bias : rt.bias;
@@ -768,11 +707,9 @@ k_moe_layer_umma(const JobTable *__restrict__ dev_table, const __grid_constant__
                     }
                 }
                 if (tid == 0) mark(64);
-                if (trace && l == trace_layer) atomicAdd(&s_dbg, 1u);
                 token_sync();
                 if (tid == kRouteWarp * 32u) {
                     mark(65);
-                    if (tr) tr[80] = s_dbg;
                 }
                 // one warp finishes the scores, publishes them and counts the CTA while the other warps
                 // turn to the digits
@@ -835,27 +772,31 @@ k_moe_layer_umma(const JobTable *__restrict__ dev_table, const __grid_constant__
                 }
                 ok = load_all(ok);
                 if (ok) {
-                    // every warp picks the top_k of its 32 experts (one hardware reduction per word and
-                    // round), then the first warp picks the top_k of the 8 x top_k candidates
-                    unsigned long long *s_cand = reinterpret_cast<unsigned long long *>(sBh);   // [8 warps][8]
+                    // every warp picks the top_k of its 32 experts (a hardware maximum and a vote per round:
+                    // the lowest lane with the largest key is the lowest id), then the first warp picks the
+                    // top_k of the 8 x top_k candidates.  Among candidates with equal keys the one in the
+                    // lowest slot (warp, then round) has the lowest id.  Keys are 32-bit: 0 = none.
+                    uint32_t *s_cand = reinterpret_cast<uint32_t *>(sBh);                       // [8 warps][8] keys
+                    uint32_t *s_cand_id = reinterpret_cast<uint32_t *>(sBh + 256);              // [64]
                     float *s_cand_score = reinterpret_cast<float *>(sBh + 512);                 // [64]
                     unsigned long long *s_cand_page = reinterpret_cast<unsigned long long *>(sBh + 1024);  // [64]
                     const uint32_t wl = warp - kLoadWarp0;
-                    unsigned long long key = 0ull;
+                    uint32_t key = 0u;
                     float sc = 0.0f;
                     if (lt < rt.n_experts) {
                         const uint32_t bits = __float_as_uint(__ldcg(select + lt));
                         sc = __ldcg(scores + lt);
-                        const uint32_t ordered = (bits & 0x80000000u) ? ~bits : (bits | 0x80000000u);
-                        key = ((unsigned long long)ordered << 32) | (unsigned long long)(0xffffffffu - lt);
+                        key = (bits & 0x80000000u) ? ~bits : (bits | 0x80000000u);
                     }
                     if (lt == 0) mark(68);
                     for (uint32_t r = 0; r < rt.top_k; ++r) {
-                        const unsigned long long best = warp_max_key(key);
-                        if (key == best && key != 0ull) {
+                        const uint32_t best = __reduce_max_sync(0xffffffffu, key);
+                        const uint32_t win = __ffs(__ballot_sync(0xffffffffu, key == best)) - 1u;
+                        if (lane == win && best != 0u) {
                             s_cand_score[wl * 8u + r] = sc;
                             s_cand_page[wl * 8u + r] = s_page[lt];
-                            key = 0ull;
+                            s_cand_id[wl * 8u + r] = lt;
+                            key = 0u;
                         }
                         if (lane == 0) s_cand[wl * 8u + r] = best;
                     }
@@ -863,31 +804,71 @@ k_moe_layer_umma(const JobTable *__restrict__ dev_table, const __grid_constant__
                     load_sync();
                     if (wl == 0u) {
                         // lanes 0-31: candidates lane and lane + 32 (slot = warp * 8 + round; rounds >= top_k are empty)
-                        unsigned long long k0 = (lane & 7u) < rt.top_k ? s_cand[lane] : 0ull;
-                        unsigned long long k1 = (lane & 7u) < rt.top_k ? s_cand[lane + 32u] : 0ull;
+                        uint32_t k0 = (lane & 7u) < rt.top_k ? s_cand[lane] : 0u;
+                        uint32_t k1 = (lane & 7u) < rt.top_k ? s_cand[lane + 32u] : 0u;
                         for (uint32_t r = 0; r < rt.top_k; ++r) {
-                            const unsigned long long best = warp_max_key(k0 > k1 ? k0 : k1);
-                            if (best != 0ull && (k0 == best || k1 == best)) {
-                                const uint32_t slot = k0 == best ? lane : lane + 32u;
-                                s_pick_id[r] = 0xffffffffu - (uint32_t)best;
+                            const uint32_t best = __reduce_max_sync(0xffffffffu, k0 > k1 ? k0 : k1);
+                            const uint32_t b0 = __ballot_sync(0xffffffffu, k0 == best);
+                            const uint32_t b1 = __ballot_sync(0xffffffffu, k1 == best);
+                            const uint32_t slot = b0 ? __ffs(b0) - 1u : 32u + __ffs(b1) - 1u;
+                            if (best != 0u && lane == (slot & 31u)) {
+                                s_pick_id[r] = s_cand_id[slot];
                                 s_pick_score[r] = s_cand_score[slot];
                                 s_pick_page[r] = s_cand_page[slot];
-                                if (k0 == best) k0 = 0ull;
-                                else k1 = 0ull;
+                                if (slot < 32u) k0 = 0u;
+                                else k1 = 0u;
                             }
                         }
                         __syncwarp();
                         if (lane == 0) mark(71);
-                        RouteConsts rc;
-                        rc.top_k = rt.top_k;
-                        rc.has_shared = rt.has_shared;
-                        rc.shared_here = (rt.has_shared && rt.shared_owner == rt.ep_rank) ? 1u : 0u;
-                        rc.shared_kind = rt.shared_kind;
-                        rc.ep_rank = rt.ep_rank;
-                        rc.ep_world = rt.ep_world;
-                        rc.route_scale = rt.route_scale;
-                        routes_from_picks(rc, l_shared, l_ids, l_weights, lane, s_pick_id, s_pick_score, s_pick_page, cta == 0, s_jobs[par], &s_n_jobs,
-                                          s_mix_w[par], s_mix_slot[par], &s_n_mix);
+                        // The routes from the picked experts (rank order = largest score + bias first, lowest
+                        // id on ties): lane j takes route j.  The same sums and weights as k_router's last
+                        // block: weight = score / sum of the picked scores x route_scale.  The jobs are the
+                        // shared expert first (its page can be asked for before the routes exist), then the
+                        // routed experts in route order; the mix is in route order, the shared expert last.
+                        // Expert parallel: the rank keeps the jobs of the experts it owns and, as the shared
+                        // expert's owner, the shared job; every job writes the row of its route slot.
+                        {
+                            const uint32_t top_k = rt.top_k;
+                            const uint32_t shared_here = (rt.has_shared && rt.shared_owner == rt.ep_rank) ? 1u : 0u;
+                            float sum = 0.0f;
+                            for (uint32_t j = 0; j < top_k; ++j) sum = __fadd_rn(sum, s_pick_score[j]);  // every lane, the same order
+                            const bool is_route = lane < top_k;
+                            const uint32_t id = is_route ? s_pick_id[lane] : 0u;
+                            const bool owned = is_route && (rt.ep_world <= 1u || (id % rt.ep_world) == rt.ep_rank);
+                            const uint32_t owned_mask = __ballot_sync(0xffffffffu, owned);
+                            const uint32_t pos = shared_here + __popc(owned_mask & ((1u << lane) - 1u));
+                            if (is_route) {
+                                const float w = __fmul_rn(__fdiv_rn(s_pick_score[lane], sum), rt.route_scale);
+                                if (cta == 0u && l_ids) l_ids[lane] = (int32_t)id;
+                                if (cta == 0u && l_weights) l_weights[lane] = w;
+                                s_mix_w[par][lane] = w;  // every route's weight, also of experts other ranks own
+                                s_mix_slot[par][lane] = lane;
+                                if (owned) {
+                                    s_jobs[par][pos].page = reinterpret_cast<const uint8_t *>(s_pick_page[lane]);
+                                    s_jobs[par][pos].kind = S14_PAGE_MXFP4;
+                                    s_jobs[par][pos].token = 0;
+                                    s_jobs[par][pos].weight = w;
+                                    s_jobs[par][pos].is_shared = 0;
+                                    s_jobs[par][pos].out_index = lane;
+                                }
+                            } else if (lane == top_k) {
+                                if (shared_here) {
+                                    s_jobs[par][0].page = l_shared;
+                                    s_jobs[par][0].kind = rt.shared_kind;
+                                    s_jobs[par][0].token = 0;
+                                    s_jobs[par][0].weight = 1.0f;
+                                    s_jobs[par][0].is_shared = 1;
+                                    s_jobs[par][0].out_index = top_k;
+                                }
+                                if (rt.has_shared) {
+                                    s_mix_w[par][top_k] = 1.0f;
+                                    s_mix_slot[par][top_k] = top_k | 0x80000000u;
+                                }
+                                s_n_mix = top_k + (rt.has_shared ? 1u : 0u);
+                                s_n_jobs = shared_here + __popc(owned_mask);
+                            }
+                        }
                         __syncwarp();
                         if (lane == 0 && !early)
                             s_n_items = work_list_once(cta, grid, s_n_jobs, S, RT, KU, KD, s_items);
@@ -933,7 +914,7 @@ k_moe_layer_umma(const JobTable *__restrict__ dev_table, const __grid_constant__
             const uint32_t n_jobs = routes_ok ? s_n_jobs : 0u, n_items = routes_ok ? s_n_items : 0u;
             if (tid == 0) {
                 mark(8);
-                if (tr) tr[15] = n_items | (ring << 8) | (n_jobs << 16);
+                if (kTrace && tr) tr[15] = n_items | (ring << 8) | (n_jobs << 16);
             }
 
             if (is_issuer) {
@@ -1206,7 +1187,7 @@ k_moe_layer_umma(const JobTable *__restrict__ dev_table, const __grid_constant__
             mbar_wait(bar(kBarFin), 0, abortp);
         }
     }
-    tr = tr_base;
+    if constexpr (kTrace) tr = tr_base;
 
     // ---- the CTA's items are done (or given up) ----
     if (is_producer) {
@@ -1312,10 +1293,12 @@ size_t dynamic_limit() {
     int dev = -1;
     if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= kMaxDevices) return 0;
     if (g_dynamic_limit[dev]) return g_dynamic_limit[dev];
-    cudaFuncAttributes fa;
-    if (cudaFuncGetAttributes(&fa, k_moe_layer_umma) != cudaSuccess) return 0;
-    const size_t most = kMaxSmem - fa.sharedSizeBytes;
-    if (cudaFuncSetAttribute(k_moe_layer_umma, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)most) != cudaSuccess) return 0;
+    cudaFuncAttributes fa, fb;
+    if (cudaFuncGetAttributes(&fa, k_moe_layer_umma<false>) != cudaSuccess) return 0;
+    if (cudaFuncGetAttributes(&fb, k_moe_layer_umma<true>) != cudaSuccess) return 0;
+    const size_t most = kMaxSmem - (fa.sharedSizeBytes > fb.sharedSizeBytes ? fa.sharedSizeBytes : fb.sharedSizeBytes);
+    if (cudaFuncSetAttribute(k_moe_layer_umma<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)most) != cudaSuccess) return 0;
+    if (cudaFuncSetAttribute(k_moe_layer_umma<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)most) != cudaSuccess) return 0;
     g_dynamic_limit[dev] = most;
     return most;
 }
@@ -1379,9 +1362,14 @@ cudaError_t launch_moe_layer_umma(cudaStream_t st, int sm_count, const JobTable 
     // A programmatic dependent of the previous launch on the single-GPU path.  The expert-parallel
     // paths (exchange inside the kernel, or expert outputs handed to a collective) are ordinary
     // launches; the kernel's own dependency calls are then no-ops.
-    return launch_pdl(k_moe_layer_umma, dim3(sm_count), dim3(kThreads), smem, st, ex.world <= 1u && y != nullptr, dev,
-                      param, x, d, y, tiles, counters, status, hidden, inter, ring, trace, rt, ex, stack,
-                      stack ? n_layers : 1u, hbuf, residual ? 1u : 0u);
+    const bool pdl = ex.world <= 1u && y != nullptr;
+    if (trace)
+        return launch_pdl(k_moe_layer_umma<true>, dim3(sm_count), dim3(kThreads), smem, st, pdl, dev, param, x, d, y, tiles,
+                          counters, status, hidden, inter, ring, trace, rt, ex, stack, stack ? n_layers : 1u, hbuf,
+                          residual ? 1u : 0u);
+    return launch_pdl(k_moe_layer_umma<false>, dim3(sm_count), dim3(kThreads), smem, st, pdl, dev, param, x, d, y, tiles,
+                      counters, status, hidden, inter, ring, trace, rt, ex, stack, stack ? n_layers : 1u, hbuf,
+                      residual ? 1u : 0u);
 }
 
 }  // namespace s14
