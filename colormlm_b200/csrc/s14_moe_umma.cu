@@ -122,6 +122,7 @@ __device__ __forceinline__ bool mbar_try(uint32_t bar, uint32_t parity) {
 // Bounded wait: false when the phase did not complete in kSpin tries (each suspends the thread
 // for a microsecond at most, so about 0.1 s) or another role gave up.
 __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int *abort_flag) {
+#pragma unroll 1
     for (uint32_t i = 0; i < kSpin; ++i) {
         if (mbar_try(bar, parity)) return true;
         if (*abort_flag) return false;
@@ -318,6 +319,7 @@ __device__ __forceinline__ void store_digit_scales(uint32_t tmem_sfb, const uint
     const uint32_t bias = 0x01010101u * (uint32_t)shift;  // no byte borrows: E + 100 >= 20
     const uint32_t base = tmem_sfb + ((quad * 32u) << 16);
     const uint32_t one = 0x7F7F7F7Fu;
+#pragma unroll 1
     for (uint32_t g = g0; g < groups; g += gstep) {
         const uint4 e = *reinterpret_cast<const uint4 *>(sE + g * 16u);
         const uint32_t w0 = lane < 16u ? e.x + bias : one, w1 = lane < 16u ? e.y + bias : one;
@@ -355,6 +357,7 @@ __host__ __device__ uint32_t layer_work_list(uint32_t c, uint32_t G, uint32_t n_
     const uint32_t U = n_jobs * S, D = n_jobs * RT;
     uint32_t n = 0;
     if (U == 0u || G == 0u) return 0u;
+#pragma unroll 1
     for (uint32_t q = c; q < U; q += G, ++n)
         if (n < cap) items[n] = ((q / S) << 8) | (q % S);
     const uint32_t a_max = (U + G - 1u) / G, r = U - (a_max - 1u) * G;  // CTAs 0 .. r-1 hold a_max up items
@@ -376,6 +379,7 @@ __host__ __device__ uint32_t layer_work_list(uint32_t c, uint32_t G, uint32_t n_
     }
     // first round: CTAs 0 .. G-1 (those with more up items get the jobs that finish first); further
     // rounds start with the CTAs that have fewer up items
+#pragma unroll 1
     for (uint32_t k = 0;; ++k) {
         const uint32_t pos = k == 0u ? c : (c + G - r) % G;
         const uint32_t p = D1 + k * G + pos;
@@ -565,12 +569,14 @@ k_moe_layer_umma(const JobTable *__restrict__ dev_table, const __grid_constant__
                 const uint16_t *wr0 = stack ? stack[0].router_weight : rt.weight;
                 const uint32_t rows = (cta < rt.n_experts ? 1u : 0u) + (cta + grid < rt.n_experts ? 1u : 0u);
                 mbar_arrive_expect(bar(kBarWr), rows * hidden * 2u);
+#pragma unroll 1
                 for (uint32_t k = 0; k < rows; ++k)
                     bulk_copy(smem_u32(sWr) + k * hidden * 2u, wr0 + (size_t)(cta + k * grid) * hidden, hidden * 2u, bar(kBarWr));
             }
             bool routes_known = table_param;
             const uint32_t n_items = early ? s_n_items : 0u;  // late lists are read after the routes barrier
             uint32_t n_it = n_items;
+#pragma unroll 1
             for (uint32_t i = 0; p_ok; ++i) {
                 if (!routes_known) {
                     const bool is_static = i < n_it && ((s_items[i] >> 8) & 0xFFu) < n_static;
@@ -587,6 +593,7 @@ k_moe_layer_umma(const JobTable *__restrict__ dev_table, const __grid_constant__
                             const uint16_t *wrn = stack[l + 1u].router_weight;
                             const uint32_t rows = (cta < rt.n_experts ? 1u : 0u) + (cta + grid < rt.n_experts ? 1u : 0u);
                             mbar_arrive_expect(bar(kBarWr), rows * hidden * 2u);
+#pragma unroll 1
                             for (uint32_t k = 0; k < rows; ++k)
                                 bulk_copy(smem_u32(sWr) + k * hidden * 2u, wrn + (size_t)(cta + k * grid) * hidden, hidden * 2u, bar(kBarWr));
                         }
@@ -598,6 +605,7 @@ k_moe_layer_umma(const JobTable *__restrict__ dev_table, const __grid_constant__
                 const uint32_t nu = down ? KD : KU;
                 const uint8_t *page = (!routes_known && !table_param) ? shared_page : s_jobs[par][j].page;
                 const uint8_t *a = page + (down ? mxfp4_down_offset(hidden, inter) : 0u) + (size_t)idx * nu * kUnitStride;
+#pragma unroll 1
                 for (uint32_t u = 0; u < nu; ++u) {
                     if (p_round && !mbar_wait(bar(kBarDone + p_slot), (p_round - 1u) & 1u, abortp)) {
                         p_ok = false;
@@ -657,6 +665,7 @@ k_moe_layer_umma(const JobTable *__restrict__ dev_table, const __grid_constant__
                 bool ok = alive;
                 if (tid == 0 && ok) {
                     uint32_t tries = 0;
+#pragma unroll 1
                     while (ld_acquire(counters + kCntMixed) < RT * l) {
                         if (++tries > kSpinGlobal || abort_flag) {
                             abort_flag = 1;
@@ -761,6 +770,7 @@ k_moe_layer_umma(const JobTable *__restrict__ dev_table, const __grid_constant__
                 bool ok = true;
                 if (lt == 0) {
                     uint32_t tries = 0;
+#pragma unroll 1
                     while (ld_acquire(counters + kCntRoute) < grid * (l + 1u)) {
                         if (++tries > kSpinGlobal || abort_flag) {
                             ok = false;
@@ -789,6 +799,7 @@ k_moe_layer_umma(const JobTable *__restrict__ dev_table, const __grid_constant__
                         key = (bits & 0x80000000u) ? ~bits : (bits | 0x80000000u);
                     }
                     if (lt == 0) mark(68);
+#pragma unroll 1
                     for (uint32_t r = 0; r < rt.top_k; ++r) {
                         const uint32_t best = __reduce_max_sync(0xffffffffu, key);
                         const uint32_t win = __ffs(__ballot_sync(0xffffffffu, key == best)) - 1u;
@@ -806,6 +817,7 @@ k_moe_layer_umma(const JobTable *__restrict__ dev_table, const __grid_constant__
                         // lanes 0-31: candidates lane and lane + 32 (slot = warp * 8 + round; rounds >= top_k are empty)
                         uint32_t k0 = (lane & 7u) < rt.top_k ? s_cand[lane] : 0u;
                         uint32_t k1 = (lane & 7u) < rt.top_k ? s_cand[lane + 32u] : 0u;
+#pragma unroll 1
                         for (uint32_t r = 0; r < rt.top_k; ++r) {
                             const uint32_t best = __reduce_max_sync(0xffffffffu, k0 > k1 ? k0 : k1);
                             const uint32_t b0 = __ballot_sync(0xffffffffu, k0 == best);
@@ -832,6 +844,7 @@ k_moe_layer_umma(const JobTable *__restrict__ dev_table, const __grid_constant__
                             const uint32_t top_k = rt.top_k;
                             const uint32_t shared_here = (rt.has_shared && rt.shared_owner == rt.ep_rank) ? 1u : 0u;
                             float sum = 0.0f;
+#pragma unroll 1
                             for (uint32_t j = 0; j < top_k; ++j) sum = __fadd_rn(sum, s_pick_score[j]);  // every lane, the same order
                             const bool is_route = lane < top_k;
                             const uint32_t id = is_route ? s_pick_id[lane] : 0u;
@@ -996,9 +1009,11 @@ k_moe_layer_umma(const JobTable *__restrict__ dev_table, const __grid_constant__
                     // (one 8-byte word per rank in the exchange buffer).
                     if (tid == 0) {
                         const unsigned long long *mine = ep.slots[ep.rank] + 2u * (size_t)(S14_EXPERTS_PER_TOKEN + 1) * hidden + 8u;
+#pragma unroll 1
                         for (uint32_t p = 0; p < ep.world && ok; ++p) {
                             if (p == ep.rank) continue;
                             uint32_t tries = 0;
+#pragma unroll 1
                             while ((int32_t)((uint32_t)ld_relaxed_sys(mine + p) - ep_step + 1u) < 0) {
                                 if (++tries > ep.wait_limit || abort_flag) {
                                     ok = false;
@@ -1091,6 +1106,7 @@ k_moe_layer_umma(const JobTable *__restrict__ dev_table, const __grid_constant__
                             // number in one 8-byte store
                             const size_t at = ((size_t)(ep_step & 1u) * ep.n_slots + slot) * hidden + n;
                             const unsigned long long word = ((unsigned long long)(ep_step + 1u) << 32) | __float_as_uint(v);
+#pragma unroll 1
                             for (uint32_t p = 0; p < ep.world; ++p) st_relaxed_sys(ep.slots[p] + at, word);
                         } else {
                             __stcg(d_out + (size_t)slot * hidden + n, v);
@@ -1137,6 +1153,7 @@ k_moe_layer_umma(const JobTable *__restrict__ dev_table, const __grid_constant__
                 const uint32_t lt = tid - kLoadWarp0 * 32u;
                 uint32_t cur_job = 0xFFFFFFFFu;
                 bool ok = true;
+#pragma unroll 1
                 for (uint32_t i = 0; i < n_items && ok; ++i) {
                     const uint32_t item = s_items[i], j = (item >> 8) & 0xFFu;
                     if (!(item & kItemDown) || j == cur_job) continue;
@@ -1145,6 +1162,7 @@ k_moe_layer_umma(const JobTable *__restrict__ dev_table, const __grid_constant__
                     if (lt == 0) {
                         if (n_loaded >= 2u) mine = mbar_wait(bar(kBarHFree + hb), ((n_loaded >> 1) - 1u) & 1u, abortp);
                         uint32_t tries = 0;
+#pragma unroll 1
                         while (mine && ld_acquire(counters + kCntJob0 + j) < S * (l + 1u)) {
                             if (++tries > kSpinGlobal || abort_flag) {
                                 abort_flag = 1;
@@ -1193,9 +1211,11 @@ k_moe_layer_umma(const JobTable *__restrict__ dev_table, const __grid_constant__
     if (is_producer) {
         // copies in flight land in this CTA's shared memory: wait for them before leaving
         const uint32_t first = p_units > ring ? p_units - ring : 0u;
+#pragma unroll 1
         for (uint32_t u = first; u < p_units; ++u) {
             const uint32_t s = u % ring, parity = (u / ring) & 1u;
             uint32_t tries = 0;
+#pragma unroll 1
             while (!mbar_try(bar(kBarFull + s), parity) && ++tries < kSpin) {
             }
         }
@@ -1215,6 +1235,7 @@ k_moe_layer_umma(const JobTable *__restrict__ dev_table, const __grid_constant__
         const uint32_t n = cta * 128u + tid;
         float acc = 0.0f;
         bool ok = true;
+#pragma unroll 1
         for (uint32_t jj = 0; jj < ep.n_slots && ok; ++jj) {
             const unsigned long long *w = ep.slots[ep.rank] + ((size_t)(ep_step & 1u) * ep.n_slots + jj) * hidden + n;
             unsigned long long got = ld_relaxed_sys(w);
@@ -1223,6 +1244,7 @@ k_moe_layer_umma(const JobTable *__restrict__ dev_table, const __grid_constant__
             // peer gave up on this rank and ran ahead: the words this rank still misses belong to
             // steps its peers have left behind and would never come, so it reports that, waits for
             // nothing more in this step and runs at full speed until it is level again.
+#pragma unroll 1
             while ((int32_t)((uint32_t)(got >> 32) - (ep_step + 1u)) < 0) {
                 if (s_behind) break;
                 if (++tries > ep.wait_limit || abort_flag) {
@@ -1255,11 +1277,13 @@ k_moe_layer_umma(const JobTable *__restrict__ dev_table, const __grid_constant__
     __syncwarp();
     __syncthreads();
     if (s_last) {
+#pragma unroll 1
         for (uint32_t i = 1u + tid; i < kCntEnd; i += kThreads) counters[i] = 0u;
         if (ep_on && tid == 0) {
             // every CTA has read the step count and finished reading this step's words
             *ep.step = ep_step + 1u;
             const size_t credit = 2u * (size_t)(S14_EXPERTS_PER_TOKEN + 1) * hidden + 8u;
+#pragma unroll 1
             for (uint32_t p = 0; p < ep.world; ++p)
                 if (p != ep.rank) st_relaxed_sys(ep.slots[p] + credit + ep.rank, (unsigned long long)(ep_step + 1u));
         }
