@@ -782,55 +782,61 @@ k_moe_layer_umma(const JobTable *__restrict__ dev_table, const __grid_constant__
                 }
                 ok = load_all(ok);
                 if (ok) {
-                    // every warp picks the top_k of its 32 experts (a hardware maximum and a vote per round:
-                    // the lowest lane with the largest key is the lowest id), then the first warp picks the
-                    // top_k of the 8 x top_k candidates.  Among candidates with equal keys the one in the
-                    // lowest slot (warp, then round) has the lowest id.  Keys are 32-bit: 0 = none.
-                    uint32_t *s_cand = reinterpret_cast<uint32_t *>(sBh);                       // [8 warps][8] keys
-                    uint32_t *s_cand_id = reinterpret_cast<uint32_t *>(sBh + 256);              // [64]
-                    float *s_cand_score = reinterpret_cast<float *>(sBh + 512);                 // [64]
+                    // Selection by counting, no serial rounds.  A key is (score + bias as an ordered integer,
+                    // ~id): all keys differ, a larger key comes first.  Thread e counts the keys of its warp's
+                    // 32 experts that beat its own; the experts of rank < top_k within a warp are the warp's
+                    // candidates (slot = warp * 8 + rank).  Then one thread per candidate slot counts the
+                    // candidates that beat it: rank < top_k among the candidates = the route of that rank.
+                    unsigned long long *s_cand = reinterpret_cast<unsigned long long *>(sBh);              // [64] keys, 0 = none
+                    float *s_cand_score = reinterpret_cast<float *>(sBh + 512);                            // [64]
                     unsigned long long *s_cand_page = reinterpret_cast<unsigned long long *>(sBh + 1024);  // [64]
+                    unsigned long long *s_keys = reinterpret_cast<unsigned long long *>(sBh + 2048);       // [256]
                     const uint32_t wl = warp - kLoadWarp0;
-                    uint32_t key = 0u;
+                    unsigned long long key = 0ull;
                     float sc = 0.0f;
                     if (lt < rt.n_experts) {
                         const uint32_t bits = __float_as_uint(__ldcg(select + lt));
                         sc = __ldcg(scores + lt);
-                        key = (bits & 0x80000000u) ? ~bits : (bits | 0x80000000u);
+                        const uint32_t ordered = (bits & 0x80000000u) ? ~bits : (bits | 0x80000000u);
+                        key = ((unsigned long long)ordered << 32) | (unsigned long long)(0xffffffffu - lt);
                     }
                     if (lt == 0) mark(68);
-#pragma unroll 1
-                    for (uint32_t r = 0; r < rt.top_k; ++r) {
-                        const uint32_t best = __reduce_max_sync(0xffffffffu, key);
-                        const uint32_t win = __ffs(__ballot_sync(0xffffffffu, key == best)) - 1u;
-                        if (lane == win && best != 0u) {
-                            s_cand_score[wl * 8u + r] = sc;
-                            s_cand_page[wl * 8u + r] = s_page[lt];
-                            s_cand_id[wl * 8u + r] = lt;
-                            key = 0u;
+                    s_keys[lt] = key;
+                    if (lane < 8u) s_cand[wl * 8u + lane] = 0ull;
+                    __syncwarp();
+                    {
+                        uint32_t rank = 0;
+                        const ulonglong2 *row = reinterpret_cast<const ulonglong2 *>(s_keys + wl * 32u);
+#pragma unroll
+                        for (uint32_t i = 0; i < 16; ++i) {
+                            const ulonglong2 v = row[i];
+                            rank += (v.x > key ? 1u : 0u) + (v.y > key ? 1u : 0u);
                         }
-                        if (lane == 0) s_cand[wl * 8u + r] = best;
+                        if (key != 0ull && rank < rt.top_k) {
+                            s_cand[wl * 8u + rank] = key;
+                            s_cand_score[wl * 8u + rank] = sc;
+                            s_cand_page[wl * 8u + rank] = s_page[lt];
+                        }
                     }
                     if (lt == 0) mark(69);
                     load_sync();
-                    if (wl == 0u) {
-                        // lanes 0-31: candidates lane and lane + 32 (slot = warp * 8 + round; rounds >= top_k are empty)
-                        uint32_t k0 = (lane & 7u) < rt.top_k ? s_cand[lane] : 0u;
-                        uint32_t k1 = (lane & 7u) < rt.top_k ? s_cand[lane + 32u] : 0u;
-#pragma unroll 1
-                        for (uint32_t r = 0; r < rt.top_k; ++r) {
-                            const uint32_t best = __reduce_max_sync(0xffffffffu, k0 > k1 ? k0 : k1);
-                            const uint32_t b0 = __ballot_sync(0xffffffffu, k0 == best);
-                            const uint32_t b1 = __ballot_sync(0xffffffffu, k1 == best);
-                            const uint32_t slot = b0 ? __ffs(b0) - 1u : 32u + __ffs(b1) - 1u;
-                            if (best != 0u && lane == (slot & 31u)) {
-                                s_pick_id[r] = s_cand_id[slot];
-                                s_pick_score[r] = s_cand_score[slot];
-                                s_pick_page[r] = s_cand_page[slot];
-                                if (slot < 32u) k0 = 0u;
-                                else k1 = 0u;
-                            }
+                    if (lt < 64u) {
+                        const unsigned long long mine = s_cand[lt];
+                        uint32_t rank = 0;
+                        const ulonglong2 *row = reinterpret_cast<const ulonglong2 *>(s_cand);
+#pragma unroll
+                        for (uint32_t i = 0; i < 32; ++i) {
+                            const ulonglong2 v = row[i];
+                            rank += (v.x > mine ? 1u : 0u) + (v.y > mine ? 1u : 0u);
                         }
+                        if (mine != 0ull && rank < rt.top_k) {
+                            s_pick_id[rank] = 0xffffffffu - (uint32_t)mine;
+                            s_pick_score[rank] = s_cand_score[lt];
+                            s_pick_page[rank] = s_cand_page[lt];
+                        }
+                    }
+                    load_sync();  // the picks are written; every candidate's page has been read
+                    if (wl == 0u) {
                         __syncwarp();
                         if (lane == 0) mark(71);
                         // The routes from the picked experts (rank order = largest score + bias first, lowest
@@ -896,7 +902,6 @@ k_moe_layer_umma(const JobTable *__restrict__ dev_table, const __grid_constant__
                     mbar_arrive(bar(kBarRoutes));
                 }
                 if (l + 1u < L) {
-                    load_sync();  // every candidate's page has been read
                     if (lt < rt.n_experts)
                         s_page[lt] = __ldg(reinterpret_cast<const unsigned long long *>(stack[l + 1u].page_table) + lt);
                 }
