@@ -134,6 +134,7 @@ extern "C" int32_t s14_ctx_create(int32_t device, s14_ctx **out) {
     CUDA_OK(cudaHostGetDevicePointer(&ctx->ids_host_dev, ctx->ids_host, 0));
     CUDA_OK(cudaHostGetDevicePointer(&ctx->w_host_dev, ctx->w_host, 0));
     CUDA_OK(cudaMalloc(&ctx->umma.tiles, umma_scratch_bytes()));
+    CUDA_OK(cudaMemset(ctx->umma.tiles, 0, umma_scratch_bytes()));  // no word carries a stamp yet
     ctx->umma.status = ctx->status;
     if (const char *path = getenv("S14_TENSOR_PATH")) ctx->use_umma = strcmp(path, "off") != 0;
     for (auto &e : ctx->marks.ev) CUDA_OK(cudaEventCreate(&e));
@@ -815,7 +816,7 @@ extern "C" int32_t s14_stack_create(s14_ctx *ctx, const s14_stack_config *config
     if (!ctx || !config || !layers || !out) throw ContractError("s14_stack_create: NULL argument");
     *out = nullptr;
     const s14_stack_config &c = *config;
-    if (c.n_layers == 0 || c.n_layers > 64) throw ContractError("S14 stack: 1..64 layers");
+    if (c.n_layers == 0 || c.n_layers > 62) throw ContractError("S14 stack: 1..62 layers");
     if (c.n_experts == 0 || c.n_experts > S14_N_ROUTED_EXPERTS) throw ContractError("S14 stack: 1..256 experts");
     if (!fused_dim_ok(c.hidden) || !fused_dim_ok(c.inter))
         throw ContractError("S14 stack: hidden and intermediate must be 1024, 2048 or 4096");

@@ -65,7 +65,7 @@ constexpr uint32_t kMaxHidden = 4096;
 constexpr uint32_t kSpin = 1u << 17;        // tries (a microsecond each at most) before a wait gives up
 constexpr uint32_t kSpinGlobal = 1u << 20;  // polls (100 ns apart) of a counter before giving up
 // the context's counter array ([0] is the router kernel's); [1, kCntEnd) are zero between launches
-constexpr uint32_t kCntExit = 2, kCntRoute = 3;
+constexpr uint32_t kCntExit = 2;
 constexpr uint32_t kCntMixed = 4;                    // row tiles mixed (a stack's next layer waits for all of them)
 constexpr uint32_t kCntJob0 = 16;                    // slices done per job
 constexpr uint32_t kCntTile0 = kCntJob0 + 64;        // jobs done per row tile
@@ -73,6 +73,11 @@ constexpr uint32_t kCntEnd = kCntTile0 + 64;
 constexpr uint32_t kRouterSlots = 2;                 // experts a CTA scores at most
 constexpr uint32_t kItemDown = 0x80000000u;
 constexpr uint32_t kTraceWords = 96;   // time marks per CTA of a profiling run
+// The kernel's scratch in global memory: a head (the launch count, then the expert scores as stamped
+// words, [2 layer parities][256]), then a digit tile per job and the tiles' block exponents.
+constexpr uint32_t kScratchScores = 256;
+constexpr uint32_t kScratchHead = 8192;
+constexpr uint32_t kMaxLayers = 62;    // a stamp is launch count * 64 + layer + 1
 
 // Barriers.
 constexpr uint32_t kBarFull = 0;                      // ring slot filled (one arrival + the copies' bytes)
@@ -340,6 +345,14 @@ __device__ __forceinline__ unsigned long long ld_relaxed_sys(const unsigned long
 __device__ __forceinline__ void st_relaxed_sys(unsigned long long *p, unsigned long long v) {
     asm volatile("st.relaxed.sys.global.u64 [%0], %1;" ::"l"(p), "l"(v) : "memory");
 }
+__device__ __forceinline__ unsigned long long ld_relaxed_gpu(const unsigned long long *p) {
+    unsigned long long v;
+    asm volatile("ld.relaxed.gpu.global.u64 %0, [%1];" : "=l"(v) : "l"(p) : "memory");
+    return v;
+}
+__device__ __forceinline__ void st_relaxed_gpu(unsigned long long *p, unsigned long long v) {
+    asm volatile("st.relaxed.gpu.global.u64 [%0], %1;" ::"l"(p), "l"(v) : "memory");
+}
 __device__ __forceinline__ uint32_t ld_acquire(const unsigned int *p) {
     uint32_t v;
     asm volatile("ld.acquire.gpu.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
@@ -431,7 +444,7 @@ k_moe_layer_umma(const JobTable *__restrict__ dev_table, const __grid_constant__
     __shared__ uint32_t s_items[kMaxItems];
     __shared__ uint32_t s_n_items;
     __shared__ unsigned long long s_page[S14_N_ROUTED_EXPERTS];  // the layer's page table, parked a layer ahead
-    __shared__ float s_bias[kRouterSlots];               // the bias of this CTA's experts, likewise
+    __shared__ float s_bias[S14_N_ROUTED_EXPERTS];       // the layer's bias, likewise
     __shared__ uint32_t s_pick_id[8];                    // the picked experts by rank, their scores and pages
     __shared__ float s_pick_score[8];
     __shared__ unsigned long long s_pick_page[8];
@@ -453,7 +466,12 @@ k_moe_layer_umma(const JobTable *__restrict__ dev_table, const __grid_constant__
     uint8_t *const sBh = sBx + KU * 2048u;      // two digit tiles of hidden values
     const uint32_t tile_bytes = KD * 2048u;
     uint8_t *const sWr = sBh + 2u * tile_bytes; // the router rows of this CTA's experts (BF16), a layer ahead
-    uint8_t *const tile_exps = tiles + (size_t)kJobsMax * kTileMax;  // [job][kExpMax] after the tiles
+    // Values that cross CTAs inside a layer travel as 8-byte words {stamp, value}: the reader polls the
+    // word itself until it carries the stamp of this launch and layer, so no fence, counter or vote
+    // stands between the writer's store and the reader's load.
+    unsigned long long *const score_words = reinterpret_cast<unsigned long long *>(tiles + kScratchScores);
+    uint8_t *const tile0 = tiles + kScratchHead;
+    uint8_t *const tile_exps = tile0 + (size_t)kJobsMax * kTileMax;  // [job][kExpMax] after the tiles
     const uint32_t bar0 = smem_u32(bars);
     auto bar = [&](uint32_t i) { return bar0 + i * 8u; };
     volatile int *const abortp = &abort_flag;
@@ -551,6 +569,7 @@ k_moe_layer_umma(const JobTable *__restrict__ dev_table, const __grid_constant__
     const uint32_t ep_step_unused = 0;
     (void)ep_step_unused;
     uint32_t ep_step = 0;
+    uint32_t stamp0 = 0;   // the launch count, shifted: a layer's stamp is stamp0 + layer + 1
 
     if (is_producer) {
         // ---- the copying thread: the units of the CTA's items in order, layer after layer, each one
@@ -641,7 +660,7 @@ k_moe_layer_umma(const JobTable *__restrict__ dev_table, const __grid_constant__
             int32_t *const l_ids = stack ? stack[l].ids_out : rt.ids_out;
             float *const l_weights = stack ? stack[l].weights_out : rt.weights_out;
             float *const l_y = stack ? stack[l].y_out : nullptr;
-            float *const scores = rt.scores + par * S14_N_ROUTED_EXPERTS, *const select = rt.select + par * S14_N_ROUTED_EXPERTS;
+            unsigned long long *const scores = score_words + par * S14_N_ROUTED_EXPERTS;
             const float *xsrc = l == 0u ? x : hbuf + (size_t)par * hidden;
             float *const xdst = (l + 1u == L) ? y : hbuf + (size_t)(par ^ 1u) * hidden;
             // The layer's router rows of this CTA's experts (cta, cta + grid) come into shared memory by
@@ -652,14 +671,15 @@ k_moe_layer_umma(const JobTable *__restrict__ dev_table, const __grid_constant__
             float xs[8] = {0.0f, 0.0f, 0.0f, 0.0f, 0.0f, 0.0f, 0.0f, 0.0f};
             (void)l_wr;
             if (routes_here && l == 0u) {
-                if (warp == kRouteWarp && lane < kRouterSlots)
-                    s_bias[lane] = (cta + lane * grid < rt.n_experts && l_bias) ? __ldg(l_bias + cta + lane * grid) : 0.0f;
-                if (warp >= kLoadWarp0 && tid - kLoadWarp0 * 32u < rt.n_experts)
+                if (warp >= kLoadWarp0 && tid - kLoadWarp0 * 32u < rt.n_experts) {
                     s_page[tid - kLoadWarp0 * 32u] = __ldg(reinterpret_cast<const unsigned long long *>(l_table) + (tid - kLoadWarp0 * 32u));
+                    s_bias[tid - kLoadWarp0 * 32u] = l_bias ? __ldg(l_bias + (tid - kLoadWarp0 * 32u)) : 0.0f;
+                }
             }
             if (l == 0u) {
                 cudaGridDependencySynchronize();
                 ep_step = ep_on ? __ldcg(ep.step) : 0u;
+                stamp0 = __ldcg(reinterpret_cast<const uint32_t *>(tiles)) << 6;
             } else {
                 // the token of this layer is the output of the one before: every row tile must be mixed
                 bool ok = alive;
@@ -723,27 +743,21 @@ k_moe_layer_umma(const JobTable *__restrict__ dev_table, const __grid_constant__
                 // one warp finishes the scores, publishes them and counts the CTA while the other warps
                 // turn to the digits
                 if (warp == kRouteWarp) {
-                    if (lane < kRouterSlots && cta + lane * grid < rt.n_experts) {
+                    // every CTA writes the word of expert `cta`, whether that expert exists or not: its
+                    // stamp also tells the other CTAs that this one has reached the layer
+                    if (lane < kRouterSlots && (lane == 0u || cta + lane * grid < rt.n_experts)) {
                         const uint32_t e = cta + lane * grid;
-                        double sum = 0.0;
-                        for (uint32_t w = 0; w < kTokenThreads / 32u; ++w) sum += s_red[lane * (kTokenThreads / 32u) + w];
-                        const float sc = router_score_f32(sum, rt.score_fn);
-                        scores[e] = sc;
-                        select[e] = __fadd_rn(sc, s_bias[lane]);
+                        float sc = 0.0f;
+                        if (e < rt.n_experts) {
+                            double sum = 0.0;
+#pragma unroll
+                            for (uint32_t w = 0; w < kTokenThreads / 32u; ++w) sum += s_red[lane * (kTokenThreads / 32u) + w];
+                            sc = router_score_f32(sum, rt.score_fn);
+                        }
+                        if (e < S14_N_ROUTED_EXPERTS)
+                            st_relaxed_gpu(scores + e, ((unsigned long long)(stamp0 + l + 1u) << 32) | __float_as_uint(sc));
                     }
-                    __syncwarp();
-                    if (lane == 0) {
-                        mark(66);
-                        __threadfence();
-                        mark(67);
-                        atomicAdd(counters + kCntRoute, 1u);
-                        mark(5);
-                    }
-                    __syncwarp();
-                    if (l + 1u < L && lane < kRouterSlots) {
-                        const float *nb = stack[l + 1u].bias;
-                        s_bias[lane] = (cta + lane * grid < rt.n_experts && nb) ? __ldg(nb + cta + lane * grid) : 0.0f;
-                    }
+                    if (lane == 0) mark(5);
                 }
             }
 
@@ -767,19 +781,23 @@ k_moe_layer_umma(const JobTable *__restrict__ dev_table, const __grid_constant__
                 // number of experts that come before it (larger score + bias, or the same and a lower id);
                 // the experts of rank < top_k are the routes, in rank order. ----
                 const uint32_t lt = tid - kLoadWarp0 * 32u;
+                // thread e polls (bounded) the word of expert e; the words of experts that do not exist
+                // but whose number is a CTA's are waited for as well, so that no CTA is a layer behind
                 bool ok = true;
-                if (lt == 0) {
+                unsigned long long word = 0ull;
+                if (lt < rt.n_experts || lt < grid) {
+                    const uint32_t want = stamp0 + l + 1u;
                     uint32_t tries = 0;
 #pragma unroll 1
-                    while (ld_acquire(counters + kCntRoute) < grid * (l + 1u)) {
+                    while ((uint32_t)((word = ld_relaxed_gpu(scores + lt)) >> 32) != want) {
                         if (++tries > kSpinGlobal || abort_flag) {
                             ok = false;
                             break;
                         }
                         __nanosleep(20);
                     }
-                    mark(7);
                 }
+                if (lt == 0) mark(7);
                 ok = load_all(ok);
                 if (ok) {
                     // Selection by counting, no serial rounds.  A key is (score + bias as an ordered integer,
@@ -795,8 +813,8 @@ k_moe_layer_umma(const JobTable *__restrict__ dev_table, const __grid_constant__
                     unsigned long long key = 0ull;
                     float sc = 0.0f;
                     if (lt < rt.n_experts) {
-                        const uint32_t bits = __float_as_uint(__ldcg(select + lt));
-                        sc = __ldcg(scores + lt);
+                        sc = __uint_as_float((uint32_t)word);
+                        const uint32_t bits = __float_as_uint(__fadd_rn(sc, s_bias[lt]));
                         const uint32_t ordered = (bits & 0x80000000u) ? ~bits : (bits | 0x80000000u);
                         key = ((unsigned long long)ordered << 32) | (unsigned long long)(0xffffffffu - lt);
                     }
@@ -901,9 +919,11 @@ k_moe_layer_umma(const JobTable *__restrict__ dev_table, const __grid_constant__
                     mark(72);
                     mbar_arrive(bar(kBarRoutes));
                 }
-                if (l + 1u < L) {
-                    if (lt < rt.n_experts)
-                        s_page[lt] = __ldg(reinterpret_cast<const unsigned long long *>(stack[l + 1u].page_table) + lt);
+                if (l + 1u < L && lt < rt.n_experts) {
+                    // the next layer's page table and bias (thread e alone reads and writes entry e)
+                    const float *nb = stack[l + 1u].bias;
+                    s_page[lt] = __ldg(reinterpret_cast<const unsigned long long *>(stack[l + 1u].page_table) + lt);
+                    s_bias[lt] = nb ? __ldg(nb + lt) : 0.0f;
                 }
             } else if (!routes_here && !table_param && warp == kRouteWarp) {
                 const JobTable &tab = *dev_table;
@@ -1090,7 +1110,7 @@ k_moe_layer_umma(const JobTable *__restrict__ dev_table, const __grid_constant__
                         }
                         epi_sync();
                         if (tid == 0) mark(58u + i);
-                        uint8_t *tile = tiles + (size_t)j * kTileMax;
+                        uint8_t *tile = tile0 + (size_t)j * kTileMax;
                         if (tid < 32u) {
                             // chunk (digit row, block) of the slice -> its place in the job's digit tile
                             const uint32_t dj = tid >> 1, blk = tid & 1u, cc = (idx & 3u) * 2u + blk;
@@ -1179,7 +1199,7 @@ k_moe_layer_umma(const JobTable *__restrict__ dev_table, const __grid_constant__
                     ok = load_all(mine);
                     if (!ok) break;
                     if (lt == 0) mark(40u + i);
-                    const uint8_t *src = tiles + (size_t)j * kTileMax;
+                    const uint8_t *src = tile0 + (size_t)j * kTileMax;
                     uint8_t *dst = sBh + hb * tile_bytes;
                     for (uint32_t o = lt * 16u; o < tile_bytes; o += kLoadThreads * 16u)
                         *reinterpret_cast<uint4 *>(dst + o) = __ldcg(reinterpret_cast<const uint4 *>(src + o));
@@ -1284,6 +1304,7 @@ k_moe_layer_umma(const JobTable *__restrict__ dev_table, const __grid_constant__
     if (s_last) {
 #pragma unroll 1
         for (uint32_t i = 1u + tid; i < kCntEnd; i += kThreads) counters[i] = 0u;
+        if (tid == 0) *reinterpret_cast<uint32_t *>(tiles) = (stamp0 >> 6) + 1u;  // the next launch's stamps differ
         if (ep_on && tid == 0) {
             // every CTA has read the step count and finished reading this step's words
             *ep.step = ep_step + 1u;
@@ -1352,8 +1373,8 @@ size_t umma_trace_bytes(int sm_count) { return (size_t)sm_count * kTraceWords * 
 uint32_t umma_trace_words() { return kTraceWords; }
 
 size_t umma_scratch_bytes() {
-    // a digit tile and its block exponents per job
-    return (size_t)kJobsMax * (kTileMax + kExpMax);
+    // the head, then a digit tile and its block exponents per job; zero when the context is created
+    return (size_t)kScratchHead + (size_t)kJobsMax * (kTileMax + kExpMax);
 }
 
 bool umma_layer_ok(int sm_count, uint32_t n_tokens, uint32_t n_jobs_max, uint32_t hidden, uint32_t inter) {
@@ -1385,7 +1406,7 @@ cudaError_t launch_moe_layer_umma(cudaStream_t st, int sm_count, const JobTable 
     EpExchange ex = {};
     if (ep) ex = *ep;
     if (ex.world > 1u && !router) return cudaErrorInvalidValue;  // the mix needs every route's weight
-    if (stack && (!router || n_layers == 0u || (n_layers > 1u && !hbuf) || ex.world > 1u || rt.ep_world > 1u))
+    if (stack && (!router || n_layers == 0u || n_layers > kMaxLayers || (n_layers > 1u && !hbuf) || ex.world > 1u || rt.ep_world > 1u))
         return cudaErrorInvalidValue;  // a stack routes its own layers on one GPU
     const size_t smem = (size_t)ring * kSlot + umma_fixed_smem(hidden, inter);
     // A programmatic dependent of the previous launch on the single-GPU path.  The expert-parallel

@@ -349,7 +349,7 @@ typedef struct {
 } s14_stack_layer;
 
 typedef struct {
-    uint32_t n_layers;   /* 1..64 */
+    uint32_t n_layers;   /* 1..62 */
     uint32_t n_experts;  /* <= 256 */
     uint32_t hidden;     /* 1024, 2048 or 4096 */
     uint32_t inter;      /* 1024, 2048 or 4096 */
