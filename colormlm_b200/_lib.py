@@ -143,7 +143,7 @@ SIGNATURES = {
     "s14_stack_destroy": (_I32, [_VP]),
     "s14_cmd_stack_decode": (_I32, [_VP, _VP, _VP, _VP, _VP]),
     "s14_stack_decode_host": (_I32, [_VP, _VP, _VP, _VP]),
-    "s14_layer_work_list": (_I32, [_U32, _U32, _U32, _U32, _U32, _VP, _U32, _VP]),
+    "s14_layer_work_list": (_I32, [_U32, _U32, _U32, _U32, _U32, _U32, _VP, _U32, _VP]),
     "s14_mxfp4_expert_page_from_tensors": (_I32, [_U32, _U32, _VP, _VP]),
     "s14_mxfp4_expert_page_to_tensors": (_I32, [_U32, _U32, _VP, _VP]),
     "s14_validate_ue8m0_codes": (_I32, [_VP, _U64, _P(_U64)]),

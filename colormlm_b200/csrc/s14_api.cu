@@ -604,12 +604,14 @@ static int32_t enqueue_layer(s14_ctx *ctx, cudaStream_t st, const s14_moe_layer_
     S14_CATCH
 }
 
-extern "C" int32_t s14_layer_work_list(uint32_t cta, uint32_t n_ctas, uint32_t n_jobs, uint32_t hidden,
-                                       uint32_t inter, uint32_t *items_out, uint32_t cap, uint32_t *count) {
+extern "C" int32_t s14_layer_work_list(uint32_t cta, uint32_t n_ctas, uint32_t n_jobs, uint32_t n_early_jobs,
+                                       uint32_t hidden, uint32_t inter, uint32_t *items_out, uint32_t cap,
+                                       uint32_t *count) {
     if (!count || (cap && !items_out)) return fail(S14_ERR_CONTRACT, "s14_layer_work_list: NULL argument");
     if (n_ctas == 0 || cta >= n_ctas || (hidden & 511u) || (inter & 511u) || hidden == 0 || inter == 0)
         return fail(S14_ERR_CONTRACT, "s14_layer_work_list: cta outside the grid, or sizes that are not multiples of 512");
-    *count = layer_work_list(cta, n_ctas, n_jobs, inter >> 6, hidden >> 7, hidden >> 8, inter >> 8, items_out, cap);
+    *count = layer_work_list(cta, n_ctas, n_jobs, inter >> 6, hidden >> 7, hidden >> 8, inter >> 8, items_out, cap,
+                             n_early_jobs);
     return S14_OK;
 }
 

@@ -132,11 +132,11 @@ uint32_t umma_trace_words();
 // One token, every job an MXFP4 page, hidden and inter multiples of 512 that fit shared and tensor memory.
 // Sets the kernel's shared-memory attribute for the current device on first use.
 bool umma_layer_ok(int sm_count, uint32_t n_tokens, uint32_t n_jobs_max, uint32_t hidden, uint32_t inter);
-// Whether the tcgen05 layer kernel can score n_experts itself (a CTA scores at most four).
+// Whether the tcgen05 layer kernel can score n_experts itself (a CTA scores at most two; at most 256 CTAs).
 bool umma_router_ok(int sm_count, uint32_t n_experts);
 // The items CTA c of G runs, in order (see s14_moe_umma.cu); returns their number, writes at most cap.
 __host__ __device__ uint32_t layer_work_list(uint32_t c, uint32_t G, uint32_t n_jobs, uint32_t S, uint32_t RT,
-                                             uint32_t KU, uint32_t KD, uint32_t *items, uint32_t cap);
+                                             uint32_t KU, uint32_t KD, uint32_t *items, uint32_t cap, uint32_t n_early);
 // Both phases and the mix in one launch (y == nullptr: the expert outputs go to d, the caller mixes).
 // With a router the kernel computes the routes itself and the job tables are not read.
 cudaError_t launch_moe_layer_umma(cudaStream_t st, int sm_count, const JobTable *dev, const JobTable &param,

@@ -362,39 +362,49 @@ __device__ __forceinline__ uint32_t ld_acquire(const unsigned int *p) {
 }  // namespace
 
 // The items of CTA c of G: its up items (job j, slice) first, then its down items (job j, row tile),
-// each as down-bit | j << 8 | index.  Up items q = j * S + slice go round the CTAs (q mod G); the down
-// items p = j * RT + tile are dealt as described below.  KU, KD: units of an up and of a down item.
-// Writes at most `cap` items, returns the CTA's number of items.
+// each as down-bit | j << 8 | index.  KU, KD: units of an up and of a down item.  Writes at most
+// `cap` items, returns the CTA's number of items.
+//
+// n_early: the first n_early jobs' pages are known before the token's routes are (the shared expert
+// of a routed layer).  Their up items run while the routes are being picked, when the memory is idle,
+// and do not count in the levelling.  All up items q = j * S + slice go round the CTAs (q mod G); the
+// CTAs are then numbered from the one after the last early item (c_rot), so that the CTAs that hold an
+// early item are among those with fewer of the other up items.  The down items p = j * RT + tile are
+// dealt as described below.
 __host__ __device__ uint32_t layer_work_list(uint32_t c, uint32_t G, uint32_t n_jobs, uint32_t S, uint32_t RT,
-                                             uint32_t KU, uint32_t KD, uint32_t *items, uint32_t cap) {
+                                             uint32_t KU, uint32_t KD, uint32_t *items, uint32_t cap, uint32_t n_early) {
     const uint32_t U = n_jobs * S, D = n_jobs * RT;
     uint32_t n = 0;
     if (U == 0u || G == 0u) return 0u;
-#pragma unroll 1
+    if (n_early > n_jobs) n_early = n_jobs;
+    const uint32_t F = n_early * S, UR = U - F;
     for (uint32_t q = c; q < U; q += G, ++n)
         if (n < cap) items[n] = ((q / S) << 8) | (q % S);
-    const uint32_t a_max = (U + G - 1u) / G, r = U - (a_max - 1u) * G;  // CTAs 0 .. r-1 hold a_max up items
+    const uint32_t c_rot = (c + G - F % G) % G;
+    // CTAs c_rot = 0 .. r-1 hold a_max of the levelled up items, the others one fewer
+    const uint32_t a_max = UR ? (UR + G - 1u) / G : 1u, r = UR - (a_max - 1u) * G;
     // The CTAs with one up item fewer are free a whole up item earlier, but a job's down items can start
     // only some microseconds after its last slice (SwiGLU, digits, publication, the tile's way into shared
     // memory), which is about what a down item itself takes: each of them takes ONE down item of the jobs
-    // that are finished by then; the rest goes round all CTAs, the others first.
+    // that are finished by then (the early jobs, and the jobs whose slices all lie one round of up
+    // items earlier); the rest goes round all CTAs.
     const uint32_t n_light = G - r;
-    const uint32_t ready = RT * (((a_max - 1u) * G) / S);  // down items of jobs finished one round of up items earlier
+    const uint32_t ready = RT * (n_early + ((a_max - 1u) * G) / S);
     uint32_t D1 = n_light;
     if (D1 > ready) D1 = ready;
     if (D1 > D) D1 = D;
     (void)KU;
     (void)KD;
-    if (c >= r && c - r < D1) {
-        const uint32_t p = c - r;
+    if (c_rot >= r && c_rot - r < D1) {
+        const uint32_t p = c_rot - r;
         if (n < cap) items[n] = 0x80000000u | ((p / RT) << 8) | (p % RT);
         ++n;
     }
-    // first round: CTAs 0 .. G-1 (those with more up items get the jobs that finish first); further
-    // rounds start with the CTAs that have fewer up items
-#pragma unroll 1
+    // Without early jobs the first round starts at CTA 0 (the CTAs with more up items get the jobs that
+    // finish first) and further rounds with the CTAs that have fewer up items.  With early jobs the
+    // up items are level already, and every round starts with the CTAs that have fewer of them.
     for (uint32_t k = 0;; ++k) {
-        const uint32_t pos = k == 0u ? c : (c + G - r) % G;
+        const uint32_t pos = (k == 0u && n_early == 0u) ? c : (c_rot + G - r) % G;
         const uint32_t p = D1 + k * G + pos;
         if (D1 + k * G >= D) break;
         if (p < D) {
@@ -409,8 +419,8 @@ namespace {
 
 // the one device copy of the deal (its divisions make it long; a CTA calls it once)
 __device__ __noinline__ uint32_t work_list_once(uint32_t c, uint32_t G, uint32_t n_jobs, uint32_t S, uint32_t RT, uint32_t KU,
-                                                uint32_t KD, uint32_t *items) {
-    const uint32_t n = layer_work_list(c, G, n_jobs, S, RT, KU, KD, items, kMaxItems);
+                                                uint32_t KD, uint32_t *items, uint32_t n_early) {
+    const uint32_t n = layer_work_list(c, G, n_jobs, S, RT, KU, KD, items, kMaxItems, n_early);
     return n < kMaxItems ? n : kMaxItems;
 }
 // Nothing on the kernel's paths may live in local memory: nearly all of the SM's L1 is carved out as
@@ -502,6 +512,8 @@ k_moe_layer_umma(const JobTable *__restrict__ dev_table, const __grid_constant__
     // the CTA's items are known at once unless the number of jobs depends on the routes (expert
     // parallel: a rank keeps the experts it owns) or the table comes from an earlier kernel
     const bool early = table_param || (routes_here && rt.ep_world <= 1u);
+    // the shared expert of a layer that picks its own routes: its up items run while the routes are picked
+    const uint32_t n_early_jobs = (early && routes_here && rt.has_shared) ? 1u : 0u;
     const bool token_thread = tid < kTokenThreads;
     const bool has_x = tid < (hidden >> 3);
     const bool is_producer = tid == kProdWarp * 32u;
@@ -556,7 +568,7 @@ k_moe_layer_umma(const JobTable *__restrict__ dev_table, const __grid_constant__
             nj = rt.top_k + (rt.has_shared ? 1u : 0u);
             if (lane == 0) s_n_jobs = nj;
         }
-        if (early && lane == 1u) s_n_items = work_list_once(cta, grid, nj, S, RT, KU, KD, s_items);
+        if (early && lane == 1u) s_n_items = work_list_once(cta, grid, nj, S, RT, KU, KD, s_items, n_early_jobs);
     }
     __syncwarp();
     __syncthreads();
@@ -908,7 +920,7 @@ k_moe_layer_umma(const JobTable *__restrict__ dev_table, const __grid_constant__
                         }
                         __syncwarp();
                         if (lane == 0 && !early)
-                            s_n_items = work_list_once(cta, grid, s_n_jobs, S, RT, KU, KD, s_items);
+                            s_n_items = work_list_once(cta, grid, s_n_jobs, S, RT, KU, KD, s_items, 0u);
                         __syncwarp();
                     }
                 } else if (lt == 0) {
@@ -938,7 +950,7 @@ k_moe_layer_umma(const JobTable *__restrict__ dev_table, const __grid_constant__
                 if (lane == 0) {
                     s_n_jobs = nj;
                     s_n_mix = nm;
-                    s_n_items = work_list_once(cta, grid, nj, S, RT, KU, KD, s_items);
+                    s_n_items = work_list_once(cta, grid, nj, S, RT, KU, KD, s_items, 0u);
                 }
                 __syncwarp();
                 if (lane == 0) mbar_arrive(bar(kBarRoutes));
@@ -947,13 +959,16 @@ k_moe_layer_umma(const JobTable *__restrict__ dev_table, const __grid_constant__
             // ---- roles.  Each waits (bounded) until the jobs and the CTA's items are there ----
             const bool is_issuer = (warp == kMmaWarp0 || warp == kMmaWarp0 + 1u) && lane == 0;
             const bool role_thread = is_issuer || warp < kEpiThreads / 32u || warp >= kLoadWarp0;
-            bool routes_ok = true;
-            if (role_thread) routes_ok = mbar_wait(bar(kBarRoutes), par, abortp);
-            const uint32_t n_jobs = routes_ok ? s_n_jobs : 0u, n_items = routes_ok ? s_n_items : 0u;
-            if (tid == 0) {
-                mark(8);
-                if (kTrace && tr) tr[15] = n_items | (ring << 8) | (n_jobs << 16);
+            // Where the list is known from the start (`early`), only what needs the routes waits for
+            // them: the tile threads (which pick them) here, the epilogue before its first item of a
+            // routed expert or down item; the issuing threads follow the ring and the tiles.
+            bool routes_ok = true, routes_known = early;
+            if (role_thread && (!early || warp >= kLoadWarp0)) {
+                routes_ok = mbar_wait(bar(kBarRoutes), par, abortp);
+                routes_known = true;
             }
+            const uint32_t n_jobs = routes_ok ? s_n_jobs : 0u, n_items = routes_ok ? s_n_items : 0u;
+            if (kTrace && tid == 0 && tr) tr[15] = n_items | (ring << 8) | (n_jobs << 16);
 
             if (is_issuer) {
                 // ---- MMA issue.  Issuing a tcgen05 operation costs the thread 70-90 cycles (measured), more
@@ -1057,7 +1072,13 @@ k_moe_layer_umma(const JobTable *__restrict__ dev_table, const __grid_constant__
                     const uint32_t gi = gi0 + i;
                     const uint32_t item = s_items[i], j = (item >> 8) & 0xFFu, idx = item & 0xFFu, buf = gi & 1u;
                     const bool down = (item & kItemDown) != 0u;
-                    ok = epi_all(mbar_wait(bar(kBarAccDone + buf), (gi >> 1) & 1u, abortp));
+                    bool seen = true;
+                    if (!routes_known && (down || j >= n_early_jobs)) {
+                        seen = mbar_wait(bar(kBarRoutes), par, abortp);
+                        routes_known = true;
+                        if (tid == 0) mark(8);
+                    }
+                    ok = epi_all(seen && mbar_wait(bar(kBarAccDone + buf), (gi >> 1) & 1u, abortp));
                     if (!ok) break;
                     if (tid == 0) mark(17u + i * 4u);
                     fence_after();
@@ -1383,14 +1404,16 @@ bool umma_layer_ok(int sm_count, uint32_t n_tokens, uint32_t n_jobs_max, uint32_
     // no CTA's share may exceed the item list
     uint32_t items[1];
     for (uint32_t c = 0; c < (uint32_t)sm_count; ++c)
-        if (layer_work_list(c, (uint32_t)sm_count, n_jobs_max, inter >> 6, hidden >> 7, hidden >> 8, inter >> 8, items, 0) >
-            kMaxItems)
-            return false;
+        for (uint32_t n_early = 0; n_early < 2u; ++n_early)
+            if (layer_work_list(c, (uint32_t)sm_count, n_jobs_max, inter >> 6, hidden >> 7, hidden >> 8, inter >> 8, items, 0,
+                                n_early) > kMaxItems)
+                return false;
     return ring_slots(hidden, inter, dynamic_limit()) >= 2u;
 }
 
 bool umma_router_ok(int sm_count, uint32_t n_experts) {
-    return n_experts > 0u && n_experts <= kRouterSlots * (uint32_t)sm_count;
+    return n_experts > 0u && n_experts <= kRouterSlots * (uint32_t)sm_count && n_experts <= S14_N_ROUTED_EXPERTS &&
+           sm_count <= (int)kLoadThreads;  // one selecting thread per expert and per CTA's word
 }
 
 cudaError_t launch_moe_layer_umma(cudaStream_t st, int sm_count, const JobTable *dev, const JobTable &param,

@@ -281,11 +281,14 @@ S14_API int32_t s14_cmd_moe_layer(s14_ctx *ctx, void *stream, const s14_moe_laye
 /* Which work the CTA `cta` of `n_ctas` (one per SM) does in a one-token layer of `n_jobs` experts on
  * the tensor-core path, in the order it does it: items_out[i] = down << 31 | job << 8 | index, where
  * an up item is (job, slice of 64 intermediate elements: w1 / w3 rows, SwiGLU) and a down item
- * (job, tile of 128 rows of w2).  Writes at most `cap` items; *count receives the CTA's number of
- * items.  Host arithmetic only, for tests and for reading profiles; no counterpart in the
- * reference. */
-S14_API int32_t s14_layer_work_list(uint32_t cta, uint32_t n_ctas, uint32_t n_jobs, uint32_t hidden,
-                                    uint32_t inter, uint32_t *items_out, uint32_t cap, uint32_t *count);
+ * (job, tile of 128 rows of w2).  n_early_jobs: the leading jobs whose pages are known before the
+ * token's routes are (1 for a layer that picks its routes itself and has a shared expert, which is job
+ * 0; else 0): their up items lead the lists and run while the routes are being picked.  Writes at
+ * most `cap` items; *count receives the CTA's number of items.  Host arithmetic only, for tests and
+ * for reading profiles; no counterpart in the reference. */
+S14_API int32_t s14_layer_work_list(uint32_t cta, uint32_t n_ctas, uint32_t n_jobs, uint32_t n_early_jobs,
+                                    uint32_t hidden, uint32_t inter, uint32_t *items_out, uint32_t cap,
+                                    uint32_t *count);
 
 /* Router (s14_first_real_token/executor.py:638-668): logits = x . Wr^T with Wr
  * BF16 [n_experts, hidden]; score = sigmoid | sqrt(softplus); select top_k of
