@@ -359,8 +359,9 @@ def run_gpu(args) -> None:
         if workload == "stack":
             done, launches = 0, 0
             while done < k_steps:
-                count = min(n_layers, k_steps - done)
-                stack_of(0, count).cmd_decode(xs[((first_step + done) // n_layers) % n_tok], h_out, stream=handle)
+                # a launch walks N_LAYERS layers; with fewer resident layers (profiler captures) it cycles through them
+                count = min(N_LAYERS, k_steps - done)
+                stack_of(0, count).cmd_decode(xs[((first_step + done) // N_LAYERS) % n_tok], h_out, stream=handle)
                 done += count
                 launches += 1
             return launches
@@ -381,11 +382,11 @@ def run_gpu(args) -> None:
         dist.barrier()
     if world == 1:
         # the stacks a region needs are bound before anything is captured (binding allocates)
-        stack_of(0, n_layers)
-        if args.steps % n_layers:
-            stack_of(0, args.steps % n_layers)
+        stack_of(0, N_LAYERS)
+        if args.steps % N_LAYERS:
+            stack_of(0, args.steps % N_LAYERS)
     with torch.cuda.stream(stream):
-        enqueue_steps(min(n_layers, 3) if workload == "layer" else n_layers, 0, stream.cuda_stream)  # module load
+        enqueue_steps(min(n_layers, 3) if workload == "layer" else N_LAYERS, 0, stream.cuda_stream)  # module load
     stream.synchronize()
     _note("eager warm-up launches done")
     use_graph = world == 1 or peer_exchange
@@ -690,8 +691,8 @@ def run_gpu(args) -> None:
                          "frac": achieved / peak if world == 1 else None,
                          "frac_of_nominal_8000": achieved / 8000.0 if world == 1 else None,
                          "peak_kind": peak_kind, "traffic": NCU_TRAFFIC_BYTES,
-                         "bytes_per_launch": STEP_BYTES * (n_layers if workload == "stack" else 1),
-                         "ms_per_launch": ms / args.steps * (n_layers if workload == "stack" else 1),
+                         "bytes_per_launch": STEP_BYTES * (N_LAYERS if workload == "stack" else 1),
+                         "ms_per_launch": ms / args.steps * (N_LAYERS if workload == "stack" else 1),
                          "timed": "the timed regions (median repeat): every step is part of a launch of this kernel, "
                                   "CUDA events on the launching stream",
                          "fixed_routes_ms_per_launch": layer_ms, **other},
@@ -890,6 +891,7 @@ def run_small_workload(args, workload, torch, L, synth, S14Context, TokenRoute) 
 
 
 def main() -> None:
+    global N_EXPERTS, ROUTER_BYTES, STEP_BYTES, WORKLOAD
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=None)
@@ -905,10 +907,19 @@ def main() -> None:
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--layers", type=int, default=N_LAYERS,
                     help="resident layers (3.4 GB each); fewer than 14 is for profiler captures only")
+    ap.add_argument("--experts", type=int, default=N_EXPERTS,
+                    help="routed experts per layer; fewer than 256 is for profiler captures only (13.4 MB each)")
     ap.add_argument("--kernel-only", action="store_true",
                     help="skip the parity, end-to-end and CPU legs (profiler captures)")
     ap.add_argument("--kernel-only-skip-fixed", action="store_true", help="also skip the fixed-route launches")
     args = ap.parse_args()
+    if args.experts != N_EXPERTS:
+        if not 8 <= args.experts <= 256:
+            raise SystemExit("--experts: 8..256")
+        N_EXPERTS = args.experts
+        ROUTER_BYTES = N_EXPERTS * HIDDEN * 2 + N_EXPERTS * 4
+        STEP_BYTES = 7 * PAGE_BYTES + ROUTER_BYTES + HIDDEN * 4 + HIDDEN * 4
+        WORKLOAD = WORKLOAD.replace("top-6 of 256", f"top-6 of {N_EXPERTS} (reduced pool, not the benchmark)")
     if args.impl == "reference":
         args.steps = args.steps if args.steps is not None else 40
         args.warmup = args.warmup if args.warmup is not None else 3

@@ -72,12 +72,18 @@ __device__ __forceinline__ double warp_sum(double v) {
 
 // The reference's SwiGLU (examples/s14_vulkan_numeric.rs:1543-1556) in F32 with
 // separate operations.  expf is evaluated in double and rounded once, which
-// reproduces a correctly rounded expf.
+// reproduces a correctly rounded expf.  The F32 quotient g / (1 + e) is taken in double and rounded
+// to F32: with 53 >= 2 * 24 + 2 bits the second rounding changes nothing, so this is the correctly
+// rounded F32 division; unlike the F32 division, the double one never leaves its inline path for
+// operands of F32 range (the F32 one calls a subroutine whenever 1 + e is huge or infinite, which a
+// strongly negative gate makes it, and that subroutine's first call in a layer cost the tensor-core
+// layer kernel up to a microsecond of instruction fetch while the weights stream).
 __device__ __forceinline__ float swiglu_limit_f32(float gate, float up) {
     const float g = fminf(gate, 10.0f);
     const float u = fminf(fmaxf(up, -10.0f), 10.0f);
     const float e = (float)exp(-(double)g);
-    return __fmul_rn(__fdiv_rn(g, __fadd_rn(1.0f, e)), u);
+    const float q = (float)((double)g / (double)__fadd_rn(1.0f, e));
+    return __fmul_rn(q, u);
 }
 
 // An expert's score from its logit (the double-accumulated dot product, rounded to F32 first):

@@ -41,13 +41,13 @@ namespace {
 
 constexpr uint32_t kSlot = kUnitStride;             // ring slot: a unit's codes, then its scales (17 KB, keeps 1 KB alignment)
 constexpr uint32_t kMaxRing = 12;                  // ring slots are an even number: a slot belongs to one issuing thread
-constexpr uint32_t kThreads = 544;                 // sixteen warps that share the token, one warp that copies
+constexpr uint32_t kThreads = 512;                 // sixteen warps; every thread owns eight elements of the token
 constexpr uint32_t kTokenThreads = 512;
 constexpr uint32_t kEpiThreads = 128;              // warps 0-3: one per lane quadrant of tensor memory
 constexpr uint32_t kMmaWarp0 = 5;                  // warps 5, 6: lane 0 issues
 constexpr uint32_t kLoadWarp0 = 8;                 // warps 8-15 fetch digit tiles (and pick the routes)
 constexpr uint32_t kLoadThreads = 256;
-constexpr uint32_t kProdWarp = 16;                 // lane 0 copies
+constexpr uint32_t kProdWarp = 4;                  // lane 0 copies (the warp has no other role after the top of a layer)
 constexpr uint32_t kMaxItems = 32;                 // items a CTA can hold
 constexpr uint32_t kJobsMax = S14_EXPERTS_PER_TOKEN + 1;
 constexpr uint32_t kTileMax = 32768;               // digit tile of a 4096-long vector: 16 units of 2 KB
@@ -66,17 +66,19 @@ constexpr uint32_t kSpin = 1u << 17;        // tries (a microsecond each at most
 constexpr uint32_t kSpinGlobal = 1u << 20;  // polls (100 ns apart) of a counter before giving up
 // the context's counter array ([0] is the router kernel's); [1, kCntEnd) are zero between launches
 constexpr uint32_t kCntExit = 2;
-constexpr uint32_t kCntMixed = 4;                    // row tiles mixed (a stack's next layer waits for all of them)
-constexpr uint32_t kCntJob0 = 16;                    // slices done per job
-constexpr uint32_t kCntTile0 = kCntJob0 + 64;        // jobs done per row tile
-constexpr uint32_t kCntEnd = kCntTile0 + 64;
+constexpr uint32_t kCntEnd = 4;
 constexpr uint32_t kRouterSlots = 2;                 // experts a CTA scores at most
 constexpr uint32_t kItemDown = 0x80000000u;
 constexpr uint32_t kTraceWords = 96;   // time marks per CTA of a profiling run
-// The kernel's scratch in global memory: a head (the launch count, then the expert scores as stamped
-// words, [2 layer parities][256]), then a digit tile per job and the tiles' block exponents.
+// The kernel's scratch in global memory, all of it stamped words but the launch count: a head (the
+// launch count, then the expert scores, [2 layer parities][256]), then per job a digit tile (a word
+// per four bytes of the tile) and the tile's block exponents (a word each).
 constexpr uint32_t kScratchScores = 256;
 constexpr uint32_t kScratchHead = 8192;
+constexpr uint32_t kTileWordBytes = 2u * kTileMax;   // a job's tile as words
+constexpr uint32_t kExpWordBytes = 8u * kExpMax;     // its block exponents as words
+// after them: the experts' outputs [job slot][kMaxHidden] and the token between the layers of a
+// stack [2 layer parities][kMaxHidden], a word per value
 constexpr uint32_t kMaxLayers = 62;    // a stamp is launch count * 64 + layer + 1
 
 // Barriers.
@@ -353,6 +355,14 @@ __device__ __forceinline__ unsigned long long ld_relaxed_gpu(const unsigned long
 __device__ __forceinline__ void st_relaxed_gpu(unsigned long long *p, unsigned long long v) {
     asm volatile("st.relaxed.gpu.global.u64 [%0], %1;" ::"l"(p), "l"(v) : "memory");
 }
+__device__ __forceinline__ ulonglong2 ld_relaxed_gpu2(const void *p) {
+    ulonglong2 v;
+    asm volatile("ld.relaxed.gpu.global.v2.u64 {%0, %1}, [%2];" : "=l"(v.x), "=l"(v.y) : "l"(p) : "memory");
+    return v;
+}
+__device__ __forceinline__ void st_relaxed_gpu2(void *p, unsigned long long a, unsigned long long b) {
+    asm volatile("st.relaxed.gpu.global.v2.u64 [%0], {%1, %2};" ::"l"(p), "l"(a), "l"(b) : "memory");
+}
 __device__ __forceinline__ uint32_t ld_acquire(const unsigned int *p) {
     uint32_t v;
     asm volatile("ld.acquire.gpu.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
@@ -429,8 +439,7 @@ __device__ __noinline__ uint32_t work_list_once(uint32_t c, uint32_t G, uint32_t
 // inlined, arrays are indexed by unrolled loops, and only code that runs once per launch or layer
 // with little live state (the deal, the route records) is kept out of line.
 
-// 544 threads = 17 warps: one sub-partition of the SM holds five of them, so 96 registers per thread
-// is the most the launch can have.
+// 512 threads = 16 warps, four per sub-partition of the SM: up to 128 registers per thread.
 template <bool kTrace>
 __global__ void __launch_bounds__(kThreads, 1)
 k_moe_layer_umma(const JobTable *__restrict__ dev_table, const __grid_constant__ JobTable param_table,
@@ -455,6 +464,9 @@ k_moe_layer_umma(const JobTable *__restrict__ dev_table, const __grid_constant__
     __shared__ uint32_t s_n_items;
     __shared__ unsigned long long s_page[S14_N_ROUTED_EXPERTS];  // the layer's page table, parked a layer ahead
     __shared__ float s_bias[S14_N_ROUTED_EXPERTS];       // the layer's bias, likewise
+    __shared__ StackLayer s_layer[2];                    // the layer's own pointers, by layer parity
+    __shared__ uint32_t s_prod[8];                       // the copying thread's position between its steps
+    __shared__ uint32_t s_ep_step, s_stamp0;
     __shared__ uint32_t s_pick_id[8];                    // the picked experts by rank, their scores and pages
     __shared__ float s_pick_score[8];
     __shared__ unsigned long long s_pick_page[8];
@@ -480,8 +492,11 @@ k_moe_layer_umma(const JobTable *__restrict__ dev_table, const __grid_constant__
     // word itself until it carries the stamp of this launch and layer, so no fence, counter or vote
     // stands between the writer's store and the reader's load.
     unsigned long long *const score_words = reinterpret_cast<unsigned long long *>(tiles + kScratchScores);
-    uint8_t *const tile0 = tiles + kScratchHead;
-    uint8_t *const tile_exps = tile0 + (size_t)kJobsMax * kTileMax;  // [job][kExpMax] after the tiles
+    uint8_t *const tile0 = tiles + kScratchHead;                           // [job][kTileWordBytes]
+    unsigned long long *const tile_exps =
+        reinterpret_cast<unsigned long long *>(tile0 + (size_t)kJobsMax * kTileWordBytes);  // [job][kExpMax] after the tiles
+    unsigned long long *const d_words = tile_exps + (size_t)kJobsMax * kExpMax;            // [slot][kMaxHidden]
+    unsigned long long *const x_words = d_words + (size_t)kJobsMax * kMaxHidden;            // [2][kMaxHidden]
     const uint32_t bar0 = smem_u32(bars);
     auto bar = [&](uint32_t i) { return bar0 + i * 8u; };
     volatile int *const abortp = &abort_flag;
@@ -489,19 +504,29 @@ k_moe_layer_umma(const JobTable *__restrict__ dev_table, const __grid_constant__
     // global timer at entry; taken in the second layer of a stack (its code has run before), else in
     // the only one.  One designated thread writes each mark.
     // The kernel is compiled twice: the marks exist in the profiling build only.
-    unsigned long long *const tr_base = (kTrace && trace) ? trace + (size_t)cta * kTraceWords : nullptr;
+    auto trace_base = [&]() -> unsigned long long * { return (kTrace && trace) ? trace + (size_t)cta * kTraceWords : nullptr; };
     const uint32_t trace_layer = L > 1u ? 1u : 0u;
-    unsigned long long *tr = trace_layer == 0u ? tr_base : nullptr;
+    unsigned long long *tr = trace_layer == 0u ? trace_base() : nullptr;
     auto mark = [&](uint32_t i) {
         if constexpr (kTrace) {
             if (tr && i < kTraceWords) tr[i] = (unsigned long long)clock64();
         }
     };
-    if (kTrace && tr_base && tid == 0) {
+    // a mark that is taken only when `dep` has been computed
+    auto mark_after = [&](uint32_t i, uint32_t dep) {
+        if constexpr (kTrace) {
+            if (tr && i < kTraceWords) {
+                unsigned long long t;
+                asm volatile("mov.u64 %0, %%clock64;" : "=l"(t) : "r"(dep) : "memory");
+                tr[i] = t;
+            }
+        }
+    };
+    if (kTrace && trace && tid == 0) {
         unsigned long long gt;
         asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(gt));
-        tr_base[0] = gt;
-        tr_base[1] = (unsigned long long)clock64();
+        trace_base()[0] = gt;
+        trace_base()[1] = (unsigned long long)clock64();
     }
 
     // Thread t < 512 owns elements 8t .. 8t+7 of the token (hidden <= 4096), for the digits and for
@@ -514,7 +539,6 @@ k_moe_layer_umma(const JobTable *__restrict__ dev_table, const __grid_constant__
     const bool early = table_param || (routes_here && rt.ep_world <= 1u);
     // the shared expert of a layer that picks its own routes: its up items run while the routes are picked
     const uint32_t n_early_jobs = (early && routes_here && rt.has_shared) ? 1u : 0u;
-    const bool token_thread = tid < kTokenThreads;
     const bool has_x = tid < (hidden >> 3);
     const bool is_producer = tid == kProdWarp * 32u;
     // The kernel is launched as a programmatic dependent of whatever precedes it in the stream: its
@@ -538,6 +562,18 @@ k_moe_layer_umma(const JobTable *__restrict__ dev_table, const __grid_constant__
         mbar_init(bar(tid), count);
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
+    if (warp == 2u && lane < sizeof(StackLayer) / 8u) {
+        // the first layer's pointers (launch arguments, or the stack's table, which no kernel writes)
+        unsigned long long v = 0ull;
+        if (stack) v = __ldg(reinterpret_cast<const unsigned long long *>(stack) + lane);
+        else if (lane == 0u) v = (unsigned long long)rt.weight;
+        else if (lane == 1u) v = (unsigned long long)rt.bias;
+        else if (lane == 2u) v = (unsigned long long)rt.page_table;
+        else if (lane == 3u) v = (unsigned long long)rt.shared_page;
+        else if (lane == 4u) v = (unsigned long long)rt.ids_out;
+        else if (lane == 5u) v = (unsigned long long)rt.weights_out;
+        reinterpret_cast<unsigned long long *>(&s_layer[0])[lane] = v;
+    }
     if (warp == 1u) {
         uint32_t nj = 0;
         if (lane == 0) {
@@ -549,6 +585,7 @@ k_moe_layer_umma(const JobTable *__restrict__ dev_table, const __grid_constant__
             s_n_jobs = 0;
             s_n_mix = 0;
         }
+        if (lane < 8u) s_prod[lane] = lane == 6u ? 1u : 0u;  // nothing issued yet, no wait has run out
         __syncwarp();
         if (table_param) {
             nj = min(param_table.n_jobs, kJobsMax);
@@ -576,86 +613,106 @@ k_moe_layer_umma(const JobTable *__restrict__ dev_table, const __grid_constant__
     // a caller's table is complete now; otherwise the routes barrier opens when the routes are picked
     if (tid == 32u && table_param) mbar_arrive(bar(kBarRoutes));
 
-    uint32_t p_units = 0;  // units the copying thread has issued
     uint32_t tmem = 0;
-    const uint32_t ep_step_unused = 0;
-    (void)ep_step_unused;
-    uint32_t ep_step = 0;
-    uint32_t stamp0 = 0;   // the launch count, shifted: a layer's stamp is stamp0 + layer + 1
+    // (s_ep_step: the exchange's step count; s_stamp0: the launch count, shifted: a layer's stamp is
+    // s_stamp0 + layer + 1.  Both are read once, by one thread, after the dependency wait of the first
+    // layer; the other threads see them after the layer's first barrier.)
 
-    if (is_producer) {
-        // ---- the copying thread: the units of the CTA's items in order, layer after layer, each one
-        // bulk copy (codes and scales, 17 KB of consecutive page bytes) into the next ring slot.  The
-        // items of a layer's shared expert that lead the list are asked for before the layer's routes
-        // exist (its page address is a launch argument); the rest wait (bounded) for the routes. ----
-        uint32_t p_slot = 0, p_round = 0;
-        bool p_ok = true;
+    // ---- the copying thread: the units of the CTA's items in order, layer after layer, each one
+    // bulk copy (codes and scales, 17 KB of consecutive page bytes) into the next ring slot.  It shares
+    // the top of every layer with the other threads (its eight elements of the token), so it works in
+    // two steps per layer: after the top of layer l, the rest of layer l's list (waiting, bounded, for the
+    // routes where an item needs them), then the head of layer l + 1's list: at most `ring` units of the
+    // leading items whose page is known without the routes (the shared expert; every job of a caller's
+    // table), which wait only for slots that layer l's own MMAs free.  The head of the first layer is
+    // asked for before the token is there.  (p_layer, p_i, p_u): the next unit to ask for. ----
+    // Its position lives in shared memory between the steps (one thread reads and writes it), so that
+    // it does not hold registers of every thread for the whole kernel.
+    auto produce = [&](uint32_t ll, bool head) {
+        uint32_t p_slot = s_prod[0], p_round = s_prod[1], p_layer = s_prod[2], p_i = s_prod[3], p_u = s_prod[4];
+        uint32_t p_units = s_prod[5];
+        bool p_ok = s_prod[6] != 0u;
+        auto leave = [&]() {
+            s_prod[0] = p_slot, s_prod[1] = p_round, s_prod[2] = p_layer, s_prod[3] = p_i, s_prod[4] = p_u;
+            s_prod[5] = p_units, s_prod[6] = p_ok ? 1u : 0u;
+        };
+        if (p_layer > ll || !p_ok) return;
+        const uint32_t par_l = ll & 1u;
+        const uint32_t n_static = table_param ? s_n_jobs : n_early_jobs;
+        bool routes_known = table_param;
+        uint32_t n_it = early ? s_n_items : 0u;  // late lists are read after the routes barrier
+        uint32_t budget = ring;
 #pragma unroll 1
-        for (uint32_t l = 0; l < L && p_ok; ++l) {
-            const uint32_t par = l & 1u;
-            const uint8_t *shared_page = stack ? stack[l].shared_page : rt.shared_page;
-            const uint32_t n_static = table_param ? s_n_jobs : ((early && rt.has_shared) ? 1u : 0u);
-            if (routes_here && l == 0u) {
-                // the first layer's router rows; those of layer l + 1 follow when layer l's routes are known
-                const uint16_t *wr0 = stack ? stack[0].router_weight : rt.weight;
-                const uint32_t rows = (cta < rt.n_experts ? 1u : 0u) + (cta + grid < rt.n_experts ? 1u : 0u);
-                mbar_arrive_expect(bar(kBarWr), rows * hidden * 2u);
-#pragma unroll 1
-                for (uint32_t k = 0; k < rows; ++k)
-                    bulk_copy(smem_u32(sWr) + k * hidden * 2u, wr0 + (size_t)(cta + k * grid) * hidden, hidden * 2u, bar(kBarWr));
-            }
-            bool routes_known = table_param;
-            const uint32_t n_items = early ? s_n_items : 0u;  // late lists are read after the routes barrier
-            uint32_t n_it = n_items;
-#pragma unroll 1
-            for (uint32_t i = 0; p_ok; ++i) {
-                if (!routes_known) {
-                    const bool is_static = i < n_it && ((s_items[i] >> 8) & 0xFFu) < n_static;
-                    if (!is_static) {
-                        if (l == 0u) mark(3);
-                        if (!mbar_wait(bar(kBarRoutes), par, abortp)) {
-                            p_ok = false;
-                            break;
-                        }
-                        routes_known = true;
-                        n_it = s_n_items;
-                        if (routes_here && l + 1u < L) {
-                            // this layer's scores are done: its router rows make room for the next layer's
-                            const uint16_t *wrn = stack[l + 1u].router_weight;
-                            const uint32_t rows = (cta < rt.n_experts ? 1u : 0u) + (cta + grid < rt.n_experts ? 1u : 0u);
-                            mbar_arrive_expect(bar(kBarWr), rows * hidden * 2u);
-#pragma unroll 1
-                            for (uint32_t k = 0; k < rows; ++k)
-                                bulk_copy(smem_u32(sWr) + k * hidden * 2u, wrn + (size_t)(cta + k * grid) * hidden, hidden * 2u, bar(kBarWr));
-                        }
-                    }
-                }
-                if (i >= n_it) break;
-                const uint32_t item = s_items[i], j = (item >> 8) & 0xFFu, idx = item & 0xFFu;
-                const bool down = (item & kItemDown) != 0u;
-                const uint32_t nu = down ? KD : KU;
-                const uint8_t *page = (!routes_known && !table_param) ? shared_page : s_jobs[par][j].page;
-                const uint8_t *a = page + (down ? mxfp4_down_offset(hidden, inter) : 0u) + (size_t)idx * nu * kUnitStride;
-#pragma unroll 1
-                for (uint32_t u = 0; u < nu; ++u) {
-                    if (p_round && !mbar_wait(bar(kBarDone + p_slot), (p_round - 1u) & 1u, abortp)) {
+        for (;;) {
+            if (!routes_known) {
+                const bool is_static = p_i < n_it && ((s_items[p_i] >> 8) & 0xFFu) < n_static;
+                if (!is_static) {
+                    if (head) return leave();
+                    if (ll == 0u) mark(3);
+                    if (!mbar_wait(bar(kBarRoutes), par_l, abortp)) {
                         p_ok = false;
-                        break;
+                        return leave();
                     }
-                    const uint32_t full = bar(kBarFull + p_slot);
-                    mbar_arrive_expect(full, kSlot);
-                    bulk_copy(smem_u32(sRing) + p_slot * kSlot, a, kSlot, full);
-                    a += kUnitStride;
-                    ++p_units;
-                    if (++p_slot == ring) {
-                        p_slot = 0;
-                        ++p_round;
+                    routes_known = true;
+                    n_it = s_n_items;
+                    if (routes_here && ll + 1u < L) {
+                        // this layer's scores are done: its router rows make room for the next layer's
+                        const uint16_t *wrn = s_layer[par_l ^ 1u].router_weight;
+                        const uint32_t rows = (cta < rt.n_experts ? 1u : 0u) + (cta + grid < rt.n_experts ? 1u : 0u);
+                        mbar_arrive_expect(bar(kBarWr), rows * hidden * 2u);
+#pragma unroll 1
+                        for (uint32_t k = 0; k < rows; ++k)
+                            bulk_copy(smem_u32(sWr) + k * hidden * 2u, wrn + (size_t)(cta + k * grid) * hidden, hidden * 2u, bar(kBarWr));
                     }
                 }
             }
+            if (p_i >= n_it) break;
+            const uint32_t item = s_items[p_i], j = (item >> 8) & 0xFFu, idx = item & 0xFFu;
+            const bool down = (item & kItemDown) != 0u;
+            const uint32_t nu = down ? KD : KU;
+            const uint8_t *page = (!routes_known && !table_param) ? s_layer[par_l].shared_page : s_jobs[par_l][j].page;
+            const uint8_t *a = page + (down ? mxfp4_down_offset(hidden, inter) : 0u) + ((size_t)idx * nu + p_u) * kUnitStride;
+#pragma unroll 1
+            for (; p_u < nu; ++p_u) {
+                if (head) {
+                    if (budget == 0u) return leave();
+                    --budget;
+                }
+                if (p_round && !mbar_wait(bar(kBarDone + p_slot), (p_round - 1u) & 1u, abortp)) {
+                    p_ok = false;
+                    return leave();
+                }
+                const uint32_t full = bar(kBarFull + p_slot);
+                mbar_arrive_expect(full, kSlot);
+                bulk_copy(smem_u32(sRing) + p_slot * kSlot, a, kSlot, full);
+                a += kUnitStride;
+                ++p_units;
+                if (++p_slot == ring) {
+                    p_slot = 0;
+                    ++p_round;
+                }
+            }
+            p_u = 0;
+            ++p_i;
         }
-        mark(12);
-    } else if (token_thread) {
+        p_layer = ll + 1u;  // the list is done
+        p_i = 0;
+        leave();
+    };
+    if (is_producer) {
+        if (routes_here) {
+            // the first layer's router rows; those of layer l + 1 follow when layer l's routes are known
+            const uint16_t *wr0 = s_layer[0].router_weight;
+            const uint32_t rows = (cta < rt.n_experts ? 1u : 0u) + (cta + grid < rt.n_experts ? 1u : 0u);
+            mbar_arrive_expect(bar(kBarWr), rows * hidden * 2u);
+#pragma unroll 1
+            for (uint32_t k = 0; k < rows; ++k)
+                bulk_copy(smem_u32(sWr) + k * hidden * 2u, wr0 + (size_t)(cta + k * grid) * hidden, hidden * 2u, bar(kBarWr));
+        }
+        produce(0u, true);
+    }
+    __syncwarp();
+    {
         uint32_t gi0 = 0;                       // items of earlier layers
         uint32_t m_slot = warp - kMmaWarp0, m_round = 0;  // issuing threads: position in the CTA's sequence of units
         uint32_t n_loaded = 0;                  // digit tiles of hidden values so far (issuing and tile threads)
@@ -663,58 +720,80 @@ k_moe_layer_umma(const JobTable *__restrict__ dev_table, const __grid_constant__
 #pragma unroll 1
         for (uint32_t l = 0; l < L; ++l) {
             const uint32_t par = l & 1u;
-            if constexpr (kTrace) tr = (l == trace_layer) ? tr_base : nullptr;
+            if constexpr (kTrace) tr = (l == trace_layer) ? trace_base() : nullptr;
             // what a layer of a stack brings of its own; a single layer takes it from the launch arguments
-            const uint16_t *const l_wr = stack ? stack[l].router_weight : rt.weight;
-            const float *const l_bias = stack ? stack[l].bias : rt.bias;
-            const uint8_t *const *const l_table = stack ? stack[l].page_table : rt.page_table;
-            const uint8_t *const l_shared = stack ? stack[l].shared_page : rt.shared_page;
-            int32_t *const l_ids = stack ? stack[l].ids_out : rt.ids_out;
-            float *const l_weights = stack ? stack[l].weights_out : rt.weights_out;
-            float *const l_y = stack ? stack[l].y_out : nullptr;
-            unsigned long long *const scores = score_words + par * S14_N_ROUTED_EXPERTS;
-            const float *xsrc = l == 0u ? x : hbuf + (size_t)par * hidden;
-            float *const xdst = (l + 1u == L) ? y : hbuf + (size_t)(par ^ 1u) * hidden;
+            // (s_layer[par]: what the layer brings of its own, in shared memory since the layer before)
+            // the token: the caller's for the first layer, then stamped words written by the mix of the layer before
+            // (x_words + par * kMaxHidden: this layer's; the other half: the next layer's)
             // The layer's router rows of this CTA's experts (cta, cta + grid) come into shared memory by
             // bulk copies a layer ahead; the bias of those experts and the page table are parked in shared
             // memory by the threads that need them, right after the routing of the layer before (the first
             // layer's before the token is waited for): with the weight stream saturating the memory, such
             // a load takes microseconds, which nobody may wait for once the token is there.
             float xs[8] = {0.0f, 0.0f, 0.0f, 0.0f, 0.0f, 0.0f, 0.0f, 0.0f};
-            (void)l_wr;
             if (routes_here && l == 0u) {
                 if (warp >= kLoadWarp0 && tid - kLoadWarp0 * 32u < rt.n_experts) {
+                    const float *l_bias = stack ? stack[0].bias : rt.bias;
+                    const uint8_t *const *l_table = stack ? stack[0].page_table : rt.page_table;
                     s_page[tid - kLoadWarp0 * 32u] = __ldg(reinterpret_cast<const unsigned long long *>(l_table) + (tid - kLoadWarp0 * 32u));
                     s_bias[tid - kLoadWarp0 * 32u] = l_bias ? __ldg(l_bias + (tid - kLoadWarp0 * 32u)) : 0.0f;
                 }
             }
             if (l == 0u) {
                 cudaGridDependencySynchronize();
-                ep_step = ep_on ? __ldcg(ep.step) : 0u;
-                stamp0 = __ldcg(reinterpret_cast<const uint32_t *>(tiles)) << 6;
+                if (tid == 0) {
+                    s_ep_step = ep_on ? __ldcg(ep.step) : 0u;
+                    s_stamp0 = __ldcg(reinterpret_cast<const uint32_t *>(tiles)) << 6;
+                }
+            }
+            if (l == 0u) {
+                if (has_x) {
+                    const float4 p0 = __ldcg(reinterpret_cast<const float4 *>(x) + 2u * tid);
+                    const float4 p1 = __ldcg(reinterpret_cast<const float4 *>(x) + 2u * tid + 1u);
+                    xs[0] = p0.x, xs[1] = p0.y, xs[2] = p0.z, xs[3] = p0.w;
+                    xs[4] = p1.x, xs[5] = p1.y, xs[6] = p1.z, xs[7] = p1.w;
+                }
             } else {
-                // the token of this layer is the output of the one before: every row tile must be mixed
+                // The token of this layer is the output of the one before, as stamped words.  One lane of
+                // a warp polls (bounded) one word -- warps that have nothing else to do wait here for most
+                // of the layer before, and 75 000 polling threads would flood the L2 --; then every thread
+                // takes the words of its eight elements, four loads in flight together, and repeats
+                // (bounded) while one of them is not there yet.
                 bool ok = alive;
-                if (tid == 0 && ok) {
+                if (has_x && ok) {
+                    const uint32_t want = s_stamp0 + l + 1u;
+                    const unsigned long long *mine = x_words + (size_t)par * kMaxHidden + 8u * tid;
                     uint32_t tries = 0;
+                    if (lane == 0) {
 #pragma unroll 1
-                    while (ld_acquire(counters + kCntMixed) < RT * l) {
-                        if (++tries > kSpinGlobal || abort_flag) {
-                            abort_flag = 1;
-                            ok = false;
-                            break;
+                        while ((uint32_t)(ld_relaxed_gpu(mine) >> 32) != want) {
+                            if (++tries > kSpinGlobal || abort_flag) {
+                                ok = false;
+                                break;
+                            }
+                            __nanosleep(100);
                         }
-                        __nanosleep(20);
                     }
+                    ok = __shfl_sync(0xffffffffu, ok ? 1 : 0, 0) != 0;  // (has_x is uniform in a warp)
+#pragma unroll 1
+                    while (ok) {
+                        ulonglong2 w[4];
+                        bool all = true;
+#pragma unroll
+                        for (uint32_t q = 0; q < 4; ++q) {
+                            w[q] = ld_relaxed_gpu2(mine + 2u * q);
+                            all = all && (uint32_t)(w[q].x >> 32) == want && (uint32_t)(w[q].y >> 32) == want;
+                            xs[2 * q] = __uint_as_float((uint32_t)w[q].x);
+                            xs[2 * q + 1] = __uint_as_float((uint32_t)w[q].y);
+                        }
+                        if (all) break;
+                        if (++tries > kSpinGlobal || abort_flag) ok = false;
+                        __nanosleep(100);
+                    }
+                    if (!ok) abort_flag = 1;
                 }
                 alive = token_all(ok && !abort_flag);
                 if (!alive) break;
-            }
-            if (has_x) {
-                const float4 p0 = __ldcg(reinterpret_cast<const float4 *>(xsrc) + 2u * tid);
-                const float4 p1 = __ldcg(reinterpret_cast<const float4 *>(xsrc) + 2u * tid + 1u);
-                xs[0] = p0.x, xs[1] = p0.y, xs[2] = p0.z, xs[3] = p0.w;
-                xs[4] = p1.x, xs[5] = p1.y, xs[6] = p1.z, xs[7] = p1.w;
             }
             if (tid == 0) mark(4);
             // tensor memory, while the first token is on its way
@@ -767,7 +846,7 @@ k_moe_layer_umma(const JobTable *__restrict__ dev_table, const __grid_constant__
                             sc = router_score_f32(sum, rt.score_fn);
                         }
                         if (e < S14_N_ROUTED_EXPERTS)
-                            st_relaxed_gpu(scores + e, ((unsigned long long)(stamp0 + l + 1u) << 32) | __float_as_uint(sc));
+                            st_relaxed_gpu(score_words + par * S14_N_ROUTED_EXPERTS + e, ((unsigned long long)(s_stamp0 + l + 1u) << 32) | __float_as_uint(sc));
                     }
                     if (lane == 0) mark(5);
                 }
@@ -777,6 +856,9 @@ k_moe_layer_umma(const JobTable *__restrict__ dev_table, const __grid_constant__
             if (has_x) digits_of8(xs, tid, sBx, sE);
             fence_async_smem();  // the digit tile is read by the tensor cores
             if (tid == 0) mark(9);
+            if (warp == 4u && l + 1u < L && lane < sizeof(StackLayer) / 8u)
+                reinterpret_cast<unsigned long long *>(&s_layer[par ^ 1u])[lane] =
+                    __ldg(reinterpret_cast<const unsigned long long *>(stack + l + 1u) + lane);  // read from the next layer's top on
             token_sync();        // every block exponent is written, the tensor memory address too; s_red is not read any more
             fence_after();
             tmem = tmem_slot;
@@ -798,10 +880,10 @@ k_moe_layer_umma(const JobTable *__restrict__ dev_table, const __grid_constant__
                 bool ok = true;
                 unsigned long long word = 0ull;
                 if (lt < rt.n_experts || lt < grid) {
-                    const uint32_t want = stamp0 + l + 1u;
+                    const uint32_t want = s_stamp0 + l + 1u;
                     uint32_t tries = 0;
 #pragma unroll 1
-                    while ((uint32_t)((word = ld_relaxed_gpu(scores + lt)) >> 32) != want) {
+                    while ((uint32_t)((word = ld_relaxed_gpu(score_words + par * S14_N_ROUTED_EXPERTS + lt)) >> 32) != want) {
                         if (++tries > kSpinGlobal || abort_flag) {
                             ok = false;
                             break;
@@ -889,8 +971,8 @@ k_moe_layer_umma(const JobTable *__restrict__ dev_table, const __grid_constant__
                             const uint32_t pos = shared_here + __popc(owned_mask & ((1u << lane) - 1u));
                             if (is_route) {
                                 const float w = __fmul_rn(__fdiv_rn(s_pick_score[lane], sum), rt.route_scale);
-                                if (cta == 0u && l_ids) l_ids[lane] = (int32_t)id;
-                                if (cta == 0u && l_weights) l_weights[lane] = w;
+                                if (cta == 0u && s_layer[par].ids_out) s_layer[par].ids_out[lane] = (int32_t)id;
+                                if (cta == 0u && s_layer[par].weights_out) s_layer[par].weights_out[lane] = w;
                                 s_mix_w[par][lane] = w;  // every route's weight, also of experts other ranks own
                                 s_mix_slot[par][lane] = lane;
                                 if (owned) {
@@ -903,7 +985,7 @@ k_moe_layer_umma(const JobTable *__restrict__ dev_table, const __grid_constant__
                                 }
                             } else if (lane == top_k) {
                                 if (shared_here) {
-                                    s_jobs[par][0].page = l_shared;
+                                    s_jobs[par][0].page = s_layer[par].shared_page;
                                     s_jobs[par][0].kind = rt.shared_kind;
                                     s_jobs[par][0].token = 0;
                                     s_jobs[par][0].weight = 1.0f;
@@ -1054,7 +1136,7 @@ k_moe_layer_umma(const JobTable *__restrict__ dev_table, const __grid_constant__
                             if (p == ep.rank) continue;
                             uint32_t tries = 0;
 #pragma unroll 1
-                            while ((int32_t)((uint32_t)ld_relaxed_sys(mine + p) - ep_step + 1u) < 0) {
+                            while ((int32_t)((uint32_t)ld_relaxed_sys(mine + p) - s_ep_step + 1u) < 0) {
                                 if (++tries > ep.wait_limit || abort_flag) {
                                     ok = false;
                                     s_abort_code = 0x5505u;
@@ -1105,16 +1187,21 @@ k_moe_layer_umma(const JobTable *__restrict__ dev_table, const __grid_constant__
                         // lanes 0-63: gate of the slice's element `row`; lanes 64-127: its up projection
                         if (row >= 64u) s_up[row - 64u] = v;
                         epi_sync();
+                        if (tid == 0 && i == 0u) mark(73);
                         int E = -80;
                         if (row < 64u) {
                             // hidden value `row` of the slice -> sixteen digit nibbles; scale block = warp
+                            if (tid == 0 && i == 0u) mark_after(77, __float_as_uint(v) ^ __float_as_uint(s_up[row]));
                             const float hv = swiglu_limit_f32(v, s_up[row]);
+                            if (tid == 0 && i == 0u) mark_after(78, __float_as_uint(hv));
                             float bm = fabsf(hv);
 #pragma unroll
                             for (int o = 16; o > 0; o >>= 1) bm = fmaxf(bm, __shfl_xor_sync(0xffffffffu, bm, o));
                             E = block_exponent(bm);
+                            if (tid == 0 && i == 0u) mark_after(79, (uint32_t)E);
                             uint32_t hw, lw;
                             digit_codes16(hv, __uint_as_float((uint32_t)(150 - E) << 23), hw, lw);
+                            if (tid == 0 && i == 0u) mark_after(74, hw ^ lw);
                             const uint32_t ohw = __shfl_xor_sync(0xffffffffu, hw, 1), olw = __shfl_xor_sync(0xffffffffu, lw, 1);
                             // byte lane / 2 of every row's chunk holds the nibbles of lanes 2b (low) and 2b + 1; even
                             // lanes write digit rows 0-3 and 8-11, odd lanes 4-7 and 12-15
@@ -1131,62 +1218,81 @@ k_moe_layer_umma(const JobTable *__restrict__ dev_table, const __grid_constant__
                         }
                         epi_sync();
                         if (tid == 0) mark(58u + i);
-                        uint8_t *tile = tile0 + (size_t)j * kTileMax;
-                        if (tid < 32u) {
-                            // chunk (digit row, block) of the slice -> its place in the job's digit tile
-                            const uint32_t dj = tid >> 1, blk = tid & 1u, cc = (idx & 3u) * 2u + blk;
-                            const uint4 c16 = *reinterpret_cast<const uint4 *>(s_hst + (dj * 2u + blk) * 16u);
-                            __stcg(reinterpret_cast<uint4 *>(tile + (idx >> 2) * 2048u + dj * 128u + ((cc ^ (dj & 7u)) << 4)), c16);
+                        // The slice's 32 chunks (digit row, block) go to their places in the job's digit tile as
+                        // stamped words, four bytes of the tile each: thread t < 64 writes half a chunk with one
+                        // 16-byte store.  The readers poll the words themselves, so nothing else is published.
+                        const unsigned long long stamp_hi = (unsigned long long)(s_stamp0 + l + 1u) << 32;
+                        if (tid < 64u) {
+                            const uint32_t ch = tid >> 1, half = tid & 1u, dj = ch >> 1, blk = ch & 1u, cc = (idx & 3u) * 2u + blk;
+                            const uint2 c8 = *reinterpret_cast<const uint2 *>(s_hst + (dj * 2u + blk) * 16u + half * 8u);
+                            const uint32_t o = (idx >> 2) * 2048u + dj * 128u + ((cc ^ (dj & 7u)) << 4) + half * 8u;
+                            st_relaxed_gpu2(tile0 + (size_t)j * kTileWordBytes + 2u * o, stamp_hi | c8.x, stamp_hi | c8.y);
                         }
-                        if (row < 64u && lane == 0) tile_exps[(size_t)j * kExpMax + idx * 2u + warp] = (uint8_t)(E + 100);
-                        epi_sync();  // the group's stores are ordered before thread 0's fence, which publishes them
-                        if (tid == 0) {
-                            __threadfence();
-                            atomicAdd(counters + kCntJob0 + j, 1u);
-                        }
+                        if (row < 64u && lane == 0)
+                            st_relaxed_gpu(tile_exps + (size_t)j * kExpMax + idx * 2u + warp, stamp_hi | (uint32_t)(E + 100));
                     } else {
                         // row idx * 128 + `row` of the expert's output
                         const uint32_t n = idx * 128u + row, slot = s_jobs[par][j].out_index;
                         if (ep_on) {
                             // into the route slot's row of every rank's slot buffer, the value with the step's
                             // number in one 8-byte store
-                            const size_t at = ((size_t)(ep_step & 1u) * ep.n_slots + slot) * hidden + n;
-                            const unsigned long long word = ((unsigned long long)(ep_step + 1u) << 32) | __float_as_uint(v);
+                            const size_t at = ((size_t)(s_ep_step & 1u) * ep.n_slots + slot) * hidden + n;
+                            const unsigned long long word = ((unsigned long long)(s_ep_step + 1u) << 32) | __float_as_uint(v);
 #pragma unroll 1
                             for (uint32_t p = 0; p < ep.world; ++p) st_relaxed_sys(ep.slots[p] + at, word);
                         } else {
                             __stcg(d_out + (size_t)slot * hidden + n, v);
-                            if (xdst) {
-                                // ---- the last job of the row tile to finish applies the ordered mix
-                                // (examples/s14_vulkan_numeric.rs:936-946): acc = 0; acc += w * d in route order;
-                                // acc += d_shared.  In a stack the result, plus the layer's input if the stack
-                                // keeps a residual, is the next layer's token. ----
-                                epi_sync();
-                                if (tid == 0) {
-                                    __threadfence();
-                                    s_last = atomicAdd(counters + kCntTile0 + idx, 1u) == n_jobs * (l + 1u) - 1u;
-                                }
-                                epi_sync();
-                                if (s_last) {
-                                    __threadfence();
+                            if (y) {
+                                // ---- the ordered mix (examples/s14_vulkan_numeric.rs:936-946): acc = 0; acc += w * d
+                                // in route order; acc += d_shared.  Every expert's output row travels as stamped
+                                // words; the CTA that holds the row tile of the last job mixes the tile: its
+                                // threads poll (bounded) the words of all the jobs, all loads in flight together.
+                                // In a stack the result, plus the layer's input if the stack keeps a residual, is
+                                // the next layer's token, again as stamped words. ----
+                                const uint32_t want = s_stamp0 + l + 1u;
+                                st_relaxed_gpu(d_words + (size_t)slot * kMaxHidden + n, ((unsigned long long)want << 32) | __float_as_uint(v));
+                                if (j + 1u == n_jobs) {
                                     const uint32_t nm = s_n_mix;
-                                    float acc = 0.0f;
-                                    for (uint32_t jj = 0; jj < nm; ++jj) {
-                                        const uint32_t ms = s_mix_slot[par][jj];
-                                        const float dv = __ldcg(d_out + (size_t)(ms & 0x7FFFFFFFu) * hidden + n);
-                                        acc = (ms >> 31) ? __fadd_rn(acc, dv) : __fadd_rn(acc, __fmul_rn(s_mix_w[par][jj], dv));
-                                    }
-                                    if (l_y) l_y[n] = acc;
-                                    xdst[n] = residual ? __fadd_rn(__ldcg(xsrc + n), acc) : acc;
-                                    if (L > 1u) {
-                                        epi_sync();
-                                        if (tid == 0) {
-                                            __threadfence();
-                                            atomicAdd(counters + kCntMixed, 1u);
+                                    const unsigned long long *dw = d_words + n;
+                                    uint32_t vals[kJobsMax];
+                                    uint32_t tries = 0;
+                                    bool got = true;
+#pragma unroll 1
+                                    for (;;) {
+                                        uint32_t missing = 0u;
+#pragma unroll
+                                        for (uint32_t jj = 0; jj < kJobsMax; ++jj) {
+                                            // (rows past the mix are not used: any row will do)
+                                            const uint32_t r = jj < nm ? (s_mix_slot[par][jj] & 0x7FFFFFFFu) : slot;
+                                            const unsigned long long t = ld_relaxed_gpu(dw + (size_t)r * kMaxHidden);
+                                            missing |= (uint32_t)(t >> 32) ^ want;
+                                            vals[jj] = (uint32_t)t;
                                         }
+                                        if (missing == 0u) break;
+                                        if (++tries > kSpinGlobal || abort_flag) {
+                                            abort_flag = 1;
+                                            got = false;
+                                            break;
+                                        }
+                                        __nanosleep(40);
+                                    }
+                                    if (got) {
+                                        float acc = 0.0f;
+#pragma unroll
+                                        for (uint32_t jj = 0; jj < kJobsMax; ++jj) {
+                                            if (jj < nm) {
+                                                const float dv = __uint_as_float(vals[jj]);
+                                                acc = (s_mix_slot[par][jj] >> 31) ? __fadd_rn(acc, dv) : __fadd_rn(acc, __fmul_rn(s_mix_w[par][jj], dv));
+                                            }
+                                        }
+                                        float out = acc;
+                                        if (residual)
+                                            out = __fadd_rn(l == 0u ? __ldcg(x + n) : __uint_as_float((uint32_t)x_words[(size_t)par * kMaxHidden + n]), acc);
+                                        if (l + 1u == L) y[n] = out;
+                                        else st_relaxed_gpu(x_words + (size_t)(par ^ 1u) * kMaxHidden + n, ((unsigned long long)(want + 1u) << 32) | __float_as_uint(out));
+                                        if (s_layer[par].y_out) s_layer[par].y_out[n] = acc;
                                     }
                                 }
-                                epi_sync();  // s_last is read before the next item writes it
                             }
                         }
                     }
@@ -1205,29 +1311,59 @@ k_moe_layer_umma(const JobTable *__restrict__ dev_table, const __grid_constant__
                     if (!(item & kItemDown) || j == cur_job) continue;
                     const uint32_t hb = n_loaded & 1u;
                     bool mine = true;
-                    if (lt == 0) {
-                        if (n_loaded >= 2u) mine = mbar_wait(bar(kBarHFree + hb), ((n_loaded >> 1) - 1u) & 1u, abortp);
-                        uint32_t tries = 0;
+                    if (lt == 0 && n_loaded >= 2u) mine = mbar_wait(bar(kBarHFree + hb), ((n_loaded >> 1) - 1u) & 1u, abortp);
+                    ok = load_all(mine);  // the tile buffer is free
+                    if (!ok) break;
+                    // The job's tile and block exponents arrive as stamped words from the CTAs that run its
+                    // up items.  Every thread asks for all its words at once (a round trip to the L2 costs
+                    // a microsecond while the weights stream, so the loads must not follow one another):
+                    // eight 16-byte loads of the tile and one exponent; then it asks again (bounded, a
+                    // pause between tries) for those that did not carry this layer's stamp yet.
+                    const uint32_t want = s_stamp0 + l + 1u;
+                    const uint8_t *src = tile0 + (size_t)j * kTileWordBytes;
+                    uint8_t *dst = sBh + hb * tile_bytes;
+                    if (lt == 0) mark(40u + i);
 #pragma unroll 1
-                        while (mine && ld_acquire(counters + kCntJob0 + j) < S * (l + 1u)) {
+                    for (uint32_t k0 = 0; k0 < KD && mine; k0 += 8u) {
+                        ulonglong2 v[8];
+                        unsigned long long ew = (unsigned long long)want << 32;
+                        const bool has_exp = k0 == 0u && lt < (inter >> 5);
+                        uint32_t tries = 0;
+#pragma unroll
+                        for (uint32_t q = 0; q < 8; ++q)
+                            if (k0 + q < KD) v[q] = ld_relaxed_gpu2(src + ((size_t)(k0 + q) * kLoadThreads + lt) * 16u);
+                        if (has_exp) ew = ld_relaxed_gpu(tile_exps + (size_t)j * kExpMax + lt);
+#pragma unroll 1
+                        for (;;) {
+                            bool all = (uint32_t)(ew >> 32) == want;
+#pragma unroll
+                            for (uint32_t q = 0; q < 8; ++q)
+                                if (k0 + q < KD) all = all && (uint32_t)(v[q].x >> 32) == want && (uint32_t)(v[q].y >> 32) == want;
+                            if (all) break;
                             if (++tries > kSpinGlobal || abort_flag) {
-                                abort_flag = 1;
                                 mine = false;
+                                break;
                             }
-                            __nanosleep(20);
+                            __nanosleep(200);
+                            // what is missing, again: all of it in flight together
+#pragma unroll
+                            for (uint32_t q = 0; q < 8; ++q)
+                                if (k0 + q < KD && ((uint32_t)(v[q].x >> 32) != want || (uint32_t)(v[q].y >> 32) != want))
+                                    v[q] = ld_relaxed_gpu2(src + ((size_t)(k0 + q) * kLoadThreads + lt) * 16u);
+                            if ((uint32_t)(ew >> 32) != want) ew = ld_relaxed_gpu(tile_exps + (size_t)j * kExpMax + lt);
+                        }
+                        if (mine) {
+#pragma unroll
+                            for (uint32_t q = 0; q < 8; ++q)
+                                if (k0 + q < KD)
+                                    *reinterpret_cast<uint2 *>(dst + ((k0 + q) * kLoadThreads + lt) * 8u) = make_uint2((uint32_t)v[q].x, (uint32_t)v[q].y);
+                            if (has_exp) sEh[hb][lt] = (uint8_t)ew;
                         }
                     }
+                    if (!mine) abort_flag = 1;
+                    fence_async_smem();
                     ok = load_all(mine);
                     if (!ok) break;
-                    if (lt == 0) mark(40u + i);
-                    const uint8_t *src = tile0 + (size_t)j * kTileMax;
-                    uint8_t *dst = sBh + hb * tile_bytes;
-                    for (uint32_t o = lt * 16u; o < tile_bytes; o += kLoadThreads * 16u)
-                        *reinterpret_cast<uint4 *>(dst + o) = __ldcg(reinterpret_cast<const uint4 *>(src + o));
-                    if (lt < (inter >> 7))
-                        reinterpret_cast<uint32_t *>(sEh[hb])[lt] = __ldcg(reinterpret_cast<const uint32_t *>(tile_exps + (size_t)j * kExpMax) + lt);
-                    fence_async_smem();
-                    load_sync();
                     if (lt == 0) mark(46u + i);
                     if (warp < kLoadWarp0 + 4u) {
                         store_digit_scales(tmem + kColSfbH + hb * 128u, sEh[hb], inter, warp & 3u, 0u, 1u, lane);
@@ -1239,10 +1375,14 @@ k_moe_layer_umma(const JobTable *__restrict__ dev_table, const __grid_constant__
                     ++n_loaded;
                 }
             }
-            // the issuing threads count the tiles too (the other threads of their warps do not care)
-            if (!(warp >= kLoadWarp0) && !is_issuer) {
-                // nothing: only the issuing and the tile threads track n_loaded
+            if (is_producer) {
+                produce(l, false);
+                if (l + 1u < L) produce(l + 1u, true);
+                if (l + 1u == L) mark(12);
             }
+            // the other lanes of its warp wait here (a warp barrier, no polling) until it has finished:
+            // a lane that polls for the next layer's token would take the warp's issue slots from it
+            if (warp == kProdWarp) __syncwarp();
             gi0 += n_items;
         }
         if ((warp == kMmaWarp0 || warp == kMmaWarp0 + 1u) && lane == 0) {
@@ -1251,11 +1391,12 @@ k_moe_layer_umma(const JobTable *__restrict__ dev_table, const __grid_constant__
             mbar_wait(bar(kBarFin), 0, abortp);
         }
     }
-    if constexpr (kTrace) tr = tr_base;
+    if constexpr (kTrace) tr = trace_base();
 
     // ---- the CTA's items are done (or given up) ----
     if (is_producer) {
         // copies in flight land in this CTA's shared memory: wait for them before leaving
+        const uint32_t p_units = s_prod[5];  // units the copying thread has issued
         const uint32_t first = p_units > ring ? p_units - ring : 0u;
 #pragma unroll 1
         for (uint32_t u = first; u < p_units; ++u) {
@@ -1283,7 +1424,7 @@ k_moe_layer_umma(const JobTable *__restrict__ dev_table, const __grid_constant__
         bool ok = true;
 #pragma unroll 1
         for (uint32_t jj = 0; jj < ep.n_slots && ok; ++jj) {
-            const unsigned long long *w = ep.slots[ep.rank] + ((size_t)(ep_step & 1u) * ep.n_slots + jj) * hidden + n;
+            const unsigned long long *w = ep.slots[ep.rank] + ((size_t)(s_ep_step & 1u) * ep.n_slots + jj) * hidden + n;
             unsigned long long got = ld_relaxed_sys(w);
             uint32_t tries = 0;
             // A word with an earlier step's number is waited for.  One with a LATER number means that a
@@ -1291,7 +1432,7 @@ k_moe_layer_umma(const JobTable *__restrict__ dev_table, const __grid_constant__
             // steps its peers have left behind and would never come, so it reports that, waits for
             // nothing more in this step and runs at full speed until it is level again.
 #pragma unroll 1
-            while ((int32_t)((uint32_t)(got >> 32) - (ep_step + 1u)) < 0) {
+            while ((int32_t)((uint32_t)(got >> 32) - (s_ep_step + 1u)) < 0) {
                 if (s_behind) break;
                 if (++tries > ep.wait_limit || abort_flag) {
                     s_abort_code = 0x5503u;
@@ -1302,7 +1443,7 @@ k_moe_layer_umma(const JobTable *__restrict__ dev_table, const __grid_constant__
                 __nanosleep(100);
                 got = ld_relaxed_sys(w);
             }
-            if ((int32_t)((uint32_t)(got >> 32) - (ep_step + 1u)) > 0) {
+            if ((int32_t)((uint32_t)(got >> 32) - (s_ep_step + 1u)) > 0) {
                 s_behind = 1;
                 atomicExch(status, 0x5504u);
             }
@@ -1325,14 +1466,14 @@ k_moe_layer_umma(const JobTable *__restrict__ dev_table, const __grid_constant__
     if (s_last) {
 #pragma unroll 1
         for (uint32_t i = 1u + tid; i < kCntEnd; i += kThreads) counters[i] = 0u;
-        if (tid == 0) *reinterpret_cast<uint32_t *>(tiles) = (stamp0 >> 6) + 1u;  // the next launch's stamps differ
+        if (tid == 0) *reinterpret_cast<uint32_t *>(tiles) = (s_stamp0 >> 6) + 1u;  // the next launch's stamps differ
         if (ep_on && tid == 0) {
             // every CTA has read the step count and finished reading this step's words
-            *ep.step = ep_step + 1u;
+            *ep.step = s_ep_step + 1u;
             const size_t credit = 2u * (size_t)(S14_EXPERTS_PER_TOKEN + 1) * hidden + 8u;
 #pragma unroll 1
             for (uint32_t p = 0; p < ep.world; ++p)
-                if (p != ep.rank) st_relaxed_sys(ep.slots[p] + credit + ep.rank, (unsigned long long)(ep_step + 1u));
+                if (p != ep.rank) st_relaxed_sys(ep.slots[p] + credit + ep.rank, (unsigned long long)(s_ep_step + 1u));
         }
     }
 }
@@ -1395,7 +1536,8 @@ uint32_t umma_trace_words() { return kTraceWords; }
 
 size_t umma_scratch_bytes() {
     // the head, then a digit tile and its block exponents per job; zero when the context is created
-    return (size_t)kScratchHead + (size_t)kJobsMax * (kTileMax + kExpMax);
+    return (size_t)kScratchHead + (size_t)kJobsMax * (kTileWordBytes + kExpWordBytes) +
+           (size_t)(kJobsMax + 2u) * kMaxHidden * sizeof(unsigned long long);
 }
 
 bool umma_layer_ok(int sm_count, uint32_t n_tokens, uint32_t n_jobs_max, uint32_t hidden, uint32_t inter) {
