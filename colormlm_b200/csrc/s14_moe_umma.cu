@@ -1344,7 +1344,7 @@ k_moe_layer_umma(const JobTable *__restrict__ dev_table, const __grid_constant__
                                 mine = false;
                                 break;
                             }
-                            __nanosleep(200);
+                            __nanosleep(64);
                             // what is missing, again: all of it in flight together
 #pragma unroll
                             for (uint32_t q = 0; q < 8; ++q)
