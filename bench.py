@@ -710,6 +710,9 @@ def run_gpu(args) -> None:
         print(json.dumps(line), flush=True)
     if world > 1:
         torch.cuda.synchronize()
+        if peer_exchange:
+            # teardown of the exchange in its order: every rank disconnects, host barrier, buffers freed
+            ep.disconnect_exchange(ctx)
         dist.barrier()
         sys.stdout.flush()
         sys.stderr.flush()

@@ -173,6 +173,7 @@ SIGNATURES = {
     "s14_ep_exchange_connect": (_I32, [_VP, _VP]),
     "s14_ep_exchange_connect_local": (_I32, [_VP, _P(_VP)]),
     "s14_ep_exchange_destroy": (_I32, [_VP]),
+    "s14_ep_exchange_disconnect": (_I32, [_VP]),
     "s14_ep_exchange_set_wait_limit": (_I32, [_VP, _U32]),
     "s14_cmd_routed_moe_layer_ep": (_I32, [_VP, _VP, _P(RoutedLayerDesc), _U32, _I32]),
     "s14_routed_moe_layer_host": (_I32, [_VP, _P(RoutedLayerDesc), _VP, _VP, _VP, _VP]),

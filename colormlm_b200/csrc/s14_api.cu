@@ -6,6 +6,7 @@
 #include <cstdlib>
 #include <cstring>
 #include <memory>
+#include <mutex>
 #include <new>
 #include <string>
 #include <vector>
@@ -144,6 +145,12 @@ extern "C" int32_t s14_ctx_create(int32_t device, s14_ctx **out) {
 
 extern "C" int32_t s14_ctx_destroy(s14_ctx *ctx) {
     if (!ctx) return S14_OK;
+    // a context whose expert-parallel exchange is still connected is not destroyed: its peers may
+    // still write into its buffer (see s14_ep_exchange_disconnect for the order of a teardown)
+    if (ctx->ep.connected)
+        return fail(S14_ERR_CONTRACT,
+                    "s14_ctx_destroy: the expert-parallel exchange is still connected; every rank calls "
+                    "s14_ep_exchange_disconnect, the ranks pass a host barrier, then the contexts are destroyed");
     cudaSetDevice(ctx->device);
     cudaStreamSynchronize(ctx->compute);
     cudaStreamSynchronize(ctx->copy);
@@ -631,32 +638,56 @@ static __device__ __align__(256) float g_noalloc_d[kNoAllocJobs * kMaxDim];
 static __device__ __align__(256) unsigned int g_noalloc_counters[kCounters];
 
 struct NoAllocDevice {
-    bool ready = false;
+    std::once_flag once;    // several host threads may make a device's first call together
+    int32_t rc = S14_OK;    // what the one initialisation returned
     int sm_count = 0;
     float *h = nullptr, *d = nullptr;
     unsigned int *counters = nullptr;
 };
 static NoAllocDevice g_noalloc[64];
 
-// Resolves the device addresses of the scratch arrays for the current device.  In host code the
-// array names are only handles; the kernels need what cudaGetSymbolAddress returns.
+// Resolves the device addresses of the scratch arrays for `device`, which is current.  In host
+// code the array names are only handles; the kernels need what cudaGetSymbolAddress returns.
+static int32_t noalloc_resolve(int device, NoAllocDevice &nd) {
+    cudaDeviceProp prop;
+    CUDA_OK(cudaGetDeviceProperties(&prop, device));
+    if (prop.major < 10)
+        return fail(S14_ERR_CONTRACT, "s14_moe_layer_noalloc: the kernels are built for sm_100a only");
+    CUDA_OK(cudaGetSymbolAddress((void **)&nd.h, g_noalloc_h));
+    CUDA_OK(cudaGetSymbolAddress((void **)&nd.d, g_noalloc_d));
+    CUDA_OK(cudaGetSymbolAddress((void **)&nd.counters, g_noalloc_counters));
+    nd.sm_count = prop.multiProcessorCount;
+    return S14_OK;
+}
+
+// Once per device and process; every later call (and every thread that lost the race) reads the
+// result of that one initialisation.
 static int32_t noalloc_setup(int device, NoAllocDevice **out) {
     if (device < 0 || device >= 64) return fail(S14_ERR_CONTRACT, "s14_moe_layer_noalloc: device out of range");
     NoAllocDevice &nd = g_noalloc[device];
-    if (!nd.ready) {
-        cudaDeviceProp prop;
-        CUDA_OK(cudaGetDeviceProperties(&prop, device));
-        if (prop.major < 10)
-            return fail(S14_ERR_CONTRACT, "s14_moe_layer_noalloc: the kernels are built for sm_100a only");
-        CUDA_OK(cudaGetSymbolAddress((void **)&nd.h, g_noalloc_h));
-        CUDA_OK(cudaGetSymbolAddress((void **)&nd.d, g_noalloc_d));
-        CUDA_OK(cudaGetSymbolAddress((void **)&nd.counters, g_noalloc_counters));
-        nd.sm_count = prop.multiProcessorCount;
-        nd.ready = true;
-    }
+    std::call_once(nd.once, [&] { nd.rc = noalloc_resolve(device, nd); });
+    if (nd.rc != S14_OK) return fail(nd.rc, "s14_moe_layer_noalloc: the device could not be set up on its first call");
     *out = &nd;
     return S14_OK;
 }
+
+// Makes `device` current for the duration of a call and puts the caller's device back afterwards.
+struct DeviceScope {
+    int previous = -1;
+    bool switched = false;
+    cudaError_t enter(int device) {
+        cudaError_t e = cudaGetDevice(&previous);
+        if (e != cudaSuccess) return e;
+        if (previous != device) {
+            e = cudaSetDevice(device);
+            switched = e == cudaSuccess;
+        }
+        return e;
+    }
+    ~DeviceScope() {
+        if (switched) cudaSetDevice(previous);
+    }
+};
 
 extern "C" int32_t s14_moe_layer_noalloc(int32_t device, void *stream, uint32_t accumulation,
                                          const s14_moe_layer_desc *desc) {
@@ -667,11 +698,10 @@ extern "C" int32_t s14_moe_layer_noalloc(int32_t device, void *stream, uint32_t 
     if (desc->n_tokens != 1)
         throw ContractError("s14_moe_layer_noalloc: the static scratch holds one token (6 routed + shared "
                             "experts); got " + std::to_string(desc->n_tokens) + " tokens");
-    if (desc->hidden > kMaxDim || desc->inter > kMaxDim)
-        throw ContractError("s14_moe_layer_noalloc: hidden and intermediate sizes are limited to 4096");
-    int current = -1;
-    CUDA_OK(cudaGetDevice(&current));
-    if (current != device) CUDA_OK(cudaSetDevice(device));
+    if (!fused_dim_ok(desc->hidden) || !fused_dim_ok(desc->inter))
+        throw ContractError("s14_moe_layer_noalloc: hidden and intermediate must be 1024, 2048 or 4096");
+    DeviceScope scope;  // the caller's current device is restored on every way out
+    CUDA_OK(scope.enter(device));
     NoAllocDevice *nd = nullptr;
     const int32_t rc = noalloc_setup(device, &nd);
     if (rc != S14_OK) return rc;
@@ -999,16 +1029,40 @@ extern "C" int32_t s14_cmd_moe_mix_slots(s14_ctx *ctx, void *stream, const float
 
 // ---- expert-parallel exchange over peer memory ------------------------------------------
 
-extern "C" int32_t s14_ep_exchange_destroy(s14_ctx *ctx) {
-    if (!ctx) return S14_OK;
+// Teardown of the exchange is a contract between the ranks, because every rank's layer kernel stores
+// into every other rank's buffer and freeing memory that a peer still has mapped, or still writes
+// to, is undefined:
+//   1. every rank calls s14_ep_exchange_disconnect: it waits for all work of its device (its own
+//      steps, whatever stream they ran on) and closes its mappings of the other ranks' buffers;
+//   2. a host barrier over the ranks: after it no rank writes into, or maps, another rank's buffer;
+//   3. every rank calls s14_ep_exchange_destroy (or s14_ctx_destroy), which frees its own buffer.
+// destroy refuses (S14_ERR_CONTRACT) while the exchange is still connected.
+extern "C" int32_t s14_ep_exchange_disconnect(s14_ctx *ctx) {
+    if (!ctx) return fail(S14_ERR_CONTRACT, "s14_ep_exchange_disconnect: ctx is NULL");
+    if (!ctx->ep.buf) return S14_OK;
+    CUDA_OK(cudaSetDevice(ctx->device));
+    CUDA_OK(cudaDeviceSynchronize());  // steps may have run on the caller's streams
     for (uint32_t p = 0; p < kMaxEpWorld; ++p) {
-        if (ctx->ep.opened[p]) cudaIpcCloseMemHandle(ctx->ep.peer[p]);
+        if (ctx->ep.opened[p]) CUDA_OK(cudaIpcCloseMemHandle(ctx->ep.peer[p]));
         ctx->ep.opened[p] = false;
         ctx->ep.peer[p] = nullptr;
     }
-    if (ctx->ep.buf) cudaFree(ctx->ep.buf);
-    ctx->ep.buf = nullptr;
     ctx->ep.connected = false;
+    return S14_OK;
+}
+
+extern "C" int32_t s14_ep_exchange_destroy(s14_ctx *ctx) {
+    if (!ctx) return S14_OK;
+    if (ctx->ep.connected)
+        return fail(S14_ERR_CONTRACT,
+                    "S14 expert-parallel exchange: still connected; every rank calls s14_ep_exchange_disconnect, the "
+                    "ranks pass a host barrier, and only then is a buffer freed");
+    if (ctx->ep.buf) {
+        CUDA_OK(cudaSetDevice(ctx->device));
+        CUDA_OK(cudaDeviceSynchronize());
+        CUDA_OK(cudaFree(ctx->ep.buf));
+    }
+    ctx->ep.buf = nullptr;
     ctx->ep.world = 0;
     return S14_OK;
 }

@@ -1129,18 +1129,28 @@ k_moe_layer_umma(const JobTable *__restrict__ dev_table, const __grid_constant__
                     // A slot buffer may be written for step s only when every peer has finished reading step
                     // s - 2 from it: each rank tells every other rank the number of steps it has finished
                     // (one 8-byte word per rank in the exchange buffer).
+                    // A wait that runs out is reported (status 0x5505) and the step goes on all the same:
+                    // the peer whose buffer is then overwritten is hopelessly late, finds later steps' numbers
+                    // there (0x5504) and catches up at full speed.  A rank that wrote nothing after such a
+                    // wait would leave the late rank waiting for words that never come, and the two would
+                    // stay apart for good.
                     if (tid == 0) {
                         const unsigned long long *mine = ep.slots[ep.rank] + 2u * (size_t)(S14_EXPERTS_PER_TOKEN + 1) * hidden + 8u;
+                        bool waiting = true;
 #pragma unroll 1
-                        for (uint32_t p = 0; p < ep.world && ok; ++p) {
+                        for (uint32_t p = 0; p < ep.world && waiting; ++p) {
                             if (p == ep.rank) continue;
                             uint32_t tries = 0;
 #pragma unroll 1
                             while ((int32_t)((uint32_t)ld_relaxed_sys(mine + p) - s_ep_step + 1u) < 0) {
-                                if (++tries > ep.wait_limit || abort_flag) {
+                                if (abort_flag) {
                                     ok = false;
-                                    s_abort_code = 0x5505u;
-                                    abort_flag = 1;
+                                    waiting = false;
+                                    break;
+                                }
+                                if (++tries > ep.wait_limit) {
+                                    atomicExch(status, 0x5505u);
+                                    waiting = false;
                                     break;
                                 }
                                 __nanosleep(100);

@@ -65,6 +65,20 @@ def connect_exchange(ctx, rank: int, world: int, hidden: int, group=None) -> Non
     dist.barrier(group=group)  # every rank has mapped every buffer before the first step
 
 
+def disconnect_exchange(ctx, group=None, barrier=None) -> None:
+    """The teardown of the exchange, on every rank: wait for this rank's work and close its mappings
+    of the other ranks' buffers, pass a host barrier (after it no rank writes into or maps another
+    rank's buffer), then free this rank's buffer.  `barrier` replaces `dist.barrier` (tests)."""
+    ctx.ep_exchange_disconnect()
+    if barrier is not None:
+        barrier()
+    else:
+        import torch.distributed as dist
+
+        dist.barrier(group=group)
+    ctx.ep_exchange_destroy()
+
+
 def decode_step_fused(ctx, x, layer_state: dict, y, *, layer: int, world: int, inter: int, ids=None, weights=None,
                       stream: Optional[int] = None) -> None:
     """One expert-parallel layer-token on this rank in one launch (exchange inside the kernel).
@@ -132,6 +146,12 @@ def sharded_head(ctx, x, w_shard_bf16, vocab: int, rank: int, world: int, group=
     ctx.cmd_head_logits(x, w_shard_bf16, local, stream=stream)
     arg = torch.empty(1, dtype=torch.int64, device=x.device)
     ctx.cmd_greedy_argmax(local, arg, stream=stream)
+    # Without `stream` the head kernels ran on torch's current stream, like the gather below.  With
+    # one, the gather (which reads `local` on torch's current stream) is ordered after them by an event.
+    if stream is not None:
+        done = torch.cuda.Event()
+        done.record(torch.cuda.ExternalStream(stream))
+        torch.cuda.current_stream().wait_event(done)
     logits = gather_head_logits(local, vocab, world, group)
     torch.cuda.synchronize()
     a = int(arg.item())

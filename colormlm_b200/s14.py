@@ -114,8 +114,13 @@ class S14Context:
         self.pipelines = S14NumericPipelines(self)
 
     def close(self) -> None:
+        """Destroys the context.  A context whose expert-parallel exchange is connected is disconnected
+        first (device synchronise, peer mappings closed); the ranks' host barrier between that and the
+        freeing of the buffers is the caller's: use `ep.disconnect_exchange` on every rank before
+        `close`, which includes it."""
         if self._h:
-            L.lib().s14_ctx_destroy(self._h)
+            L.lib().s14_ep_exchange_disconnect(self._h)
+            check(L.lib().s14_ctx_destroy(self._h))
             self._h = None
 
     def __del__(self):
@@ -226,6 +231,9 @@ class S14Context:
 
     def ep_exchange_set_wait_limit(self, polls: int) -> None:
         check(L.lib().s14_ep_exchange_set_wait_limit(self._h, polls))
+
+    def ep_exchange_disconnect(self) -> None:
+        check(L.lib().s14_ep_exchange_disconnect(self._h))
 
     def ep_exchange_destroy(self) -> None:
         check(L.lib().s14_ep_exchange_destroy(self._h))

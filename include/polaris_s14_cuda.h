@@ -262,8 +262,8 @@ typedef struct {
 } s14_token_route;
 
 typedef struct {
-    uint32_t hidden;       /* K of w1/w3, N of w2 (multiple of 1024, <= 8192) */
-    uint32_t inter;        /* N of w1/w3, K of w2 (multiple of 1024, <= 8192) */
+    uint32_t hidden;       /* K of w1/w3, N of w2: 1024, 2048 or 4096 */
+    uint32_t inter;        /* N of w1/w3, K of w2: 1024, 2048 or 4096 */
     uint32_t n_tokens;     /* 1..S14_MAX_BLOCK_TOKENS */
     uint32_t shared_kind;  /* S14_PAGE_MXFP4 | S14_PAGE_FP8 */
     const uint8_t *shared_page; /* device address, NULL = no shared expert */
@@ -408,6 +408,18 @@ S14_API int32_t s14_cmd_moe_mix_slots(s14_ctx *ctx, void *stream, const float *s
  *   connect_local: the ranks are contexts of this process on the same GPU (tests: ranks other
  *             than the last one run with wait_and_mix = 0 - they publish and return - so that no
  *             launch waits for a later launch of the same GPU).
+ *   A rank may write a slot buffer for step s only when every peer has finished reading step
+ *   s - 2 from it: behind the slot buffers every exchange buffer holds one 8-byte word per rank, the
+ *   number of steps that rank has finished, which the rank's last CTA of a step stores into every
+ *   peer's buffer; a step starts by waiting (bounded) until every peer's word in its own buffer
+ *   says at least s - 1.  A wait that runs out sets status 0x5505 and the step goes on all the same:
+ *   the peer that is then overwritten is far behind, finds later steps' numbers in its buffer
+ *   (0x5504) and catches up without waiting, so that the ranks fall into step again.
+ *   Teardown is a contract between the ranks, because every rank's kernel stores into every other
+ *   rank's buffer: (1) every rank calls s14_ep_exchange_disconnect, which waits for all work of its
+ *   device and closes its mappings of the other ranks' buffers; (2) the ranks pass a host barrier;
+ *   (3) every rank calls s14_ep_exchange_destroy or s14_ctx_destroy, which frees its own buffer.
+ *   Both destroy calls return S14_ERR_CONTRACT, and free nothing, while the exchange is connected.
  * Pairwise accumulation and MXFP4 pages only. */
 #define S14_EP_HANDLE_BYTES 64
 S14_API int32_t s14_ep_exchange_create(s14_ctx *ctx, uint32_t rank, uint32_t world, uint32_t hidden,
@@ -418,6 +430,7 @@ S14_API int32_t s14_ep_exchange_connect_local(s14_ctx *ctx, s14_ctx *const *rank
  * 2^22, a few seconds).  When it runs out the kernel sets the device status word 0x5503, writes no
  * y and returns; the context stays usable. */
 S14_API int32_t s14_ep_exchange_set_wait_limit(s14_ctx *ctx, uint32_t polls);
+S14_API int32_t s14_ep_exchange_disconnect(s14_ctx *ctx);
 S14_API int32_t s14_ep_exchange_destroy(s14_ctx *ctx);
 S14_API int32_t s14_cmd_routed_moe_layer_ep(s14_ctx *ctx, void *stream, const s14_routed_layer_desc *desc,
                                             uint32_t shared_owner, int32_t wait_and_mix);
@@ -451,10 +464,14 @@ S14_API int32_t s14_cmd_greedy_argmax(s14_ctx *ctx, void *stream, const float *l
  * It takes no context: the scratch between the up and down phases lives in file-scope device
  * arrays inside the library (about 230 KB per GPU, held until the process exits), so the limits
  * are one token per call (desc->n_tokens == 1, at most 6 routed experts plus the shared one)
- * and hidden, intermediate <= 4096; anything larger is refused with S14_ERR_CONTRACT.  It calls
+ * and hidden, intermediate each one of 1024, 2048 or 4096 (the sizes the layer kernels are built
+ * for); anything else is refused with S14_ERR_CONTRACT.  It calls
  * no cudaMalloc, cudaFree or allocating library routine.  `device` is the ordinal the pointers
- * in desc belong to; `stream` a stream of that device (NULL = the legacy default stream).
- * The first call on a device resolves the addresses of the arrays and the kernel attributes;
+ * in desc belong to; `stream` a stream of that device (NULL = the legacy default stream).  The
+ * device is made current for the call and the caller's current device is put back before it
+ * returns, on success and on failure.
+ * The first call on a device resolves the addresses of the arrays and the kernel attributes (once
+ * per device and process, also when several host threads make it together);
  * make that first call before any stream capture.  All calls on a device share the one scratch
  * and its arrival counters (cleared at the start of every call): calls that overlap on the
  * GPU - different streams without ordering, or several host threads - race on it. */

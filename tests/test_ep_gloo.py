@@ -106,3 +106,46 @@ def test_ownership_is_a_partition():
         seen = sorted(e for r in range(world) for e in ep.owned_experts(r, world))
         assert seen == list(range(256))
         assert all(0 <= ep.shared_owner(layer, world) < world for layer in range(43))
+
+
+class _RecordingContext:
+    """Stands in for an S14Context in the teardown: counts, in the ranks' shared store, how many ranks
+    have disconnected, and on destroy reads how many had when this rank freed its buffer."""
+
+    def __init__(self, store, rank):
+        self.store, self.rank, self.seen_at_destroy = store, rank, None
+
+    def ep_exchange_disconnect(self):
+        import time
+
+        time.sleep(0.05 * self.rank)  # the ranks reach the teardown at different times
+        self.store.add("disconnected", 1)
+
+    def ep_exchange_destroy(self):
+        self.seen_at_destroy = self.store.add("disconnected", 0)
+
+
+def _teardown_worker(rank: int, world: int, port: int, out_dir: str) -> None:
+    sys.path.insert(0, ROOT)
+    os.environ["MASTER_ADDR"] = "127.0.0.1"
+    os.environ["MASTER_PORT"] = str(port)
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    from colormlm_b200 import ep
+
+    store = dist.distributed_c10d._get_default_store()
+    ctx = _RecordingContext(store, rank)
+    ep.disconnect_exchange(ctx)
+    with open(os.path.join(out_dir, f"rank{rank}.txt"), "w") as f:
+        f.write(f"{ctx.seen_at_destroy}\n")
+    dist.barrier()
+    dist.destroy_process_group()
+
+
+@pytest.mark.parametrize("world", [2])
+def test_no_rank_frees_its_exchange_buffer_before_every_rank_has_disconnected(tmp_path, world):
+    """ep.disconnect_exchange: disconnect, host barrier, destroy.  Every rank, at the moment it frees
+    its buffer, finds that all ranks have closed their mappings of it."""
+    port = 29500 + ((os.getpid() + 7) % 2000)
+    mp.spawn(_teardown_worker, args=(world, port, str(tmp_path)), nprocs=world, join=True)
+    for r in range(world):
+        assert int(open(tmp_path / f"rank{r}.txt").read()) == world

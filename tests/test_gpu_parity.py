@@ -764,6 +764,28 @@ def test_expert_parallel_exchange_in_the_layer_kernel(ctx, world):
             c.close()
 
 
+def test_exchange_teardown_order_is_enforced():
+    """A context whose exchange is connected is not destroyed, and its buffer is not freed: both calls
+    return the contract error until the rank has disconnected (which waits for its device's work and
+    closes its mappings).  Two ranks of this process on one GPU."""
+    from colormlm_b200.s14 import S14Context
+
+    ranks = [S14Context(0) for _ in range(2)]
+    for r, c in enumerate(ranks):
+        c.ep_exchange_create(r, 2, 1024)
+    for c in ranks:
+        c.ep_exchange_connect_local(ranks)
+    lib = L.lib()
+    assert lib.s14_ep_exchange_destroy(ranks[0]._h) == L.ERR_CONTRACT
+    assert lib.s14_ctx_destroy(ranks[0]._h) == L.ERR_CONTRACT
+    for c in ranks:  # step 1 on every rank; no host barrier is needed inside one process
+        c.ep_exchange_disconnect()
+    for c in ranks:  # step 3
+        c.ep_exchange_destroy()
+        c.close()
+    assert all(c._h is None for c in ranks)
+
+
 def test_expert_parallel_wait_runs_out_when_a_rank_never_publishes(ctx):
     """Failure detection without a fault: rank 1 never runs its step, rank 0's bounded wait (set to
     a few milliseconds here) runs out, the kernel reports status 0x5503 and returns, and the GPU

@@ -74,3 +74,47 @@ def test_noalloc_layer_refuses_what_does_not_fit():
     with pytest.raises(S14Error):
         _noalloc(two_tokens[:1], None, 8192, inter, x, y, L.ACCUM_PAIRWISE)
     torch.cuda.synchronize()
+
+
+def test_noalloc_layer_names_the_sizes_it_takes():
+    """hidden and intermediate are 1024, 2048 or 4096, as the header says; 3072 fits the scratch but
+    no layer kernel is built for it, and the refusal says which sizes are taken."""
+    if not torch.cuda.is_available():
+        pytest.skip("needs a CUDA device")
+    page = torch.zeros(1 << 20, dtype=torch.uint8, device="cuda")
+    x = torch.zeros((1, 4096), device="cuda")
+    y = torch.empty_like(x)
+    one = [TokenRoute([0], [1.0], [page.data_ptr()])]
+    for hidden, inter in ((3072, 1024), (1024, 3072), (512, 1024)):
+        with pytest.raises(S14Error) as e:
+            _noalloc(one, None, hidden, inter, x, y, L.ACCUM_PAIRWISE)
+        assert e.value.code == L.ERR_CONTRACT and "1024, 2048 or 4096" in e.value.message
+
+
+def test_noalloc_layer_leaves_the_current_device_as_it_was():
+    """The call makes `device` current for itself only: afterwards cudaGetDevice gives what it gave
+    before, after a good call and after a refused one.  With two GPUs the call goes to the other one."""
+    if not torch.cuda.is_available():
+        pytest.skip("needs a CUDA device")
+    target = 1 if torch.cuda.device_count() > 1 else 0
+    before = torch.cuda.current_device()
+    hidden, inter = 1024, 1024
+    lay = ExpertPageLayout(hidden, inter)
+    with torch.cuda.device(target):
+        page = torch.from_numpy(synth.mxfp4_expert_page(synth.rng(5), hidden, inter)).cuda()
+        x = torch.randn((1, hidden), device="cuda")
+        y = torch.empty_like(x)
+        torch.cuda.synchronize()
+    assert lay.page_bytes == page.numel()
+    desc, keep = _layer_desc([TokenRoute([0], [1.0], [page.data_ptr()])], None, L.PAGE_MXFP4, hidden, inter)
+    desc.x, desc.y = x.data_ptr(), y.data_ptr()
+    assert torch.cuda.current_device() == before
+    L.check(L.lib().s14_moe_layer_noalloc(target, None, L.ACCUM_PAIRWISE, C.byref(desc)))
+    assert torch.cuda.current_device() == before
+    desc.n_tokens = 2  # refused
+    assert L.lib().s14_moe_layer_noalloc(target, None, L.ACCUM_PAIRWISE, C.byref(desc)) == L.ERR_CONTRACT
+    assert torch.cuda.current_device() == before
+    with torch.cuda.device(target):
+        torch.cuda.synchronize()
+        assert bool(torch.isfinite(y).all())
+    del keep
