@@ -443,6 +443,12 @@ def run_gpu(args) -> None:
     value = args.steps / (ms / 1e3)
     _note(f"timed regions done: median {ms:.4f} ms")
 
+    # ---- optional: one launch of the profiling build, time marks of its second layer
+    layer_trace = None
+    if args.trace and world == 1 and workload == "stack":
+        layer_trace = trace_of_a_launch(torch, ctx, stack_of(0, N_LAYERS), xs[0], h_out, stream,
+                                        (clocks or {}).get("sm_mhz") or 1965.0)
+
     # ---- the layer kernel with the routes given (no expert scoring), for the roofline entry's breakdown
     layer_ms = None
     if world == 1 and not args.kernel_only_skip_fixed:
@@ -703,6 +709,7 @@ def run_gpu(args) -> None:
                     "call": ("s14_stack_decode_host: one token per call through the 14 layers" if workload == "stack" else
                              "s14_routed_moe_layer_host per layer-token" if world == 1 else
                              "pinned token in, expert-parallel step, result out per layer-token")},
+            "layer_trace": layer_trace,
             "gpu_launches": launches_per_region, "kernels_per_step": kernels_per_step,
             "device_status": status, "device_status_all": status_all,
             "clocks": clocks,
@@ -720,6 +727,41 @@ def run_gpu(args) -> None:
     for st in stacks.values():
         st.close()
     ctx.close()
+
+
+TRACE_MARKS = [(64, "router dot products"), (5, "scores written"), (7, "all scores seen"), (9, "token digits written"),
+               (6, "token digit scales in tensor memory"), (69, "selection, first level"), (71, "selection, second level"),
+               (72, "routes written"), (16, "item 0: first unit in shared memory"), (17, "item 0: accumulators complete"),
+               (18, "item 0: epilogue done"), (20, "item 1: first unit"), (21, "item 1: accumulators complete"),
+               (22, "item 1: epilogue done"), (47, "item 1: digit tile in shared memory"),
+               (24, "item 2: first unit"), (25, "item 2: accumulators complete"), (26, "item 2: epilogue done"),
+               (48, "item 2: digit tile in shared memory")]
+
+
+def trace_of_a_launch(torch, ctx, stack, x, h_out, stream, sm_mhz: float):
+    """Medians over the CTAs (and min, max) of the kernel's time marks in the second layer of one
+    14-layer launch, in microseconds after the CTA read that layer's token; CTA classes by their place
+    in the deal (0-31 hold a shared-expert up item first, 32-75 two routed up items, the others one)."""
+    ctx.set_layer_trace(True)
+    with torch.cuda.stream(stream):
+        stack.cmd_decode(x, h_out, stream=stream.cuda_stream)
+    stream.synchronize()
+    tr = ctx.read_layer_trace().astype(np.int64)
+    ctx.set_layer_trace(False)
+    t0 = tr[:, 4]
+    out = {"unit": "us after the token of the launch's second layer was read; min/median/max over the CTAs of a class",
+           "sm_mhz": sm_mhz, "classes": {}}
+    classes = {"ctas 0-31": range(0, 32), "ctas 32-75": range(32, 76), "ctas 76-147": range(76, tr.shape[0])}
+    for cname, rng_ in classes.items():
+        rows = np.array([c for c in rng_ if c < tr.shape[0]])
+        marks = {}
+        for col, name in TRACE_MARKS:
+            ok = (tr[rows, col] > 0) & (t0[rows] > 0)
+            if ok.any():
+                v = (tr[rows, col] - t0[rows])[ok] / sm_mhz
+                marks[name] = [round(float(v.min()), 2), round(float(np.median(v)), 2), round(float(v.max()), 2)]
+        out["classes"][cname] = marks
+    return out
 
 
 def run_small_workload(args, workload, torch, L, synth, S14Context, TokenRoute) -> None:
@@ -915,6 +957,8 @@ def main() -> None:
     ap.add_argument("--kernel-only", action="store_true",
                     help="skip the parity, end-to-end and CPU legs (profiler captures)")
     ap.add_argument("--kernel-only-skip-fixed", action="store_true", help="also skip the fixed-route launches")
+    ap.add_argument("--trace", action="store_true",
+                    help="stack workload, one GPU: one more launch with the kernel's time marks; their medians go into the line")
     args = ap.parse_args()
     if args.experts != N_EXPERTS:
         if not 8 <= args.experts <= 256:

@@ -109,11 +109,17 @@ S14_API int32_t s14_ctx_set_kernel_timing(s14_ctx *ctx, int32_t enable);
 S14_API int32_t s14_ctx_kernel_times(s14_ctx *ctx, double ms_out[4], uint64_t *calls);
 
 /* Time marks inside the tensor-core layer kernel, for profiling runs (no counterpart in the
- * reference): while enabled, every CTA of the kernel's next launches writes 64 words - word 0 the
- * GPU's global timer (ns) at entry, then SM clock values at the kernel's stages (set-up, first
- * copies, token read, digits, routes known, per item: first unit arrived, accumulators complete,
- * epilogue done, digit tile in place; copies issued, items done, exit), word 15 = items | ring slots
- * << 8 | jobs << 16.  read copies the marks of the last launch ([n_ctas][words_per_cta]). */
+ * reference): while enabled, the kernel's launches run a second build of the kernel in which every
+ * CTA writes words_per_cta (96) words: word 0 the GPU's global timer (ns) at entry, the others SM
+ * clock values taken in the second layer of a stack (in the only layer of a single-layer launch):
+ * 2 set-up done, 4 token read, 64 router dot products, 5 scores written, 9 token digits written,
+ * 6 their scales in tensor memory, 7 all scores seen, 68 keys made, 69 first selection level,
+ * 71 second level, 72 routes written, 8 routes known to the epilogue; per item i of the CTA's list
+ * (i < 5): 16+4i first unit in shared memory, 17+4i accumulators complete, 52+i accumulators read,
+ * 58+i hidden digits made (up items), 18+4i epilogue done, 40+i digit tile asked for, 46+i tile in
+ * shared memory, 19+4i tile ready (down items); 12 all copies issued, 13 items done, 14 exit;
+ * word 15 = items | ring slots << 8 | jobs << 16.  A word that was not written is 0.  read copies
+ * the marks of the last launch ([n_ctas][words_per_cta]). */
 S14_API int32_t s14_ctx_set_layer_trace(s14_ctx *ctx, int32_t enable);
 S14_API int32_t s14_ctx_read_layer_trace(s14_ctx *ctx, uint64_t *out, uint32_t cap_words, uint32_t *n_ctas,
                                          uint32_t *words_per_cta);

@@ -101,11 +101,10 @@ def test_noalloc_layer_leaves_the_current_device_as_it_was():
     hidden, inter = 1024, 1024
     lay = ExpertPageLayout(hidden, inter)
     with torch.cuda.device(target):
-        page = torch.from_numpy(synth.mxfp4_expert_page(synth.rng(5), hidden, inter)).cuda()
-        x = torch.randn((1, hidden), device="cuda")
+        page = torch.from_numpy(lay.to_expert_page(synth.mxfp4_expert_page(synth.rng(5), hidden, inter))).cuda()
+        x = torch.from_numpy(synth.activations(synth.rng(6), 1, hidden)).cuda()
         y = torch.empty_like(x)
         torch.cuda.synchronize()
-    assert lay.page_bytes == page.numel()
     desc, keep = _layer_desc([TokenRoute([0], [1.0], [page.data_ptr()])], None, L.PAGE_MXFP4, hidden, inter)
     desc.x, desc.y = x.data_ptr(), y.data_ptr()
     assert torch.cuda.current_device() == before
