@@ -970,6 +970,48 @@ int launch_moe_layer(cudaStream_t st, uint32_t mode, int sm_count, const JobTabl
         cudaEventRecord(km->ev[0], st);
     }
     if (km) cudaEventRecord(km->ev[1], st);
+    // A block of several tokens whose routes the caller gives (a verify block of up to eight tokens):
+    // the tensor-core kernel takes one token per launch, so the block is one launch per token, each
+    // with the token's own jobs in its mix order.  Launches follow one another in the stream (each a
+    // programmatic dependent of the one before), a page that several tokens of the block use (the
+    // shared expert always) is read from HBM by the first and found in the L2 by the others, and every
+    // token's result is, bit for bit, that of its own one-token call.
+    const bool block_on_tensor_path = mode != S14_ACCUM_REFERENCE && all_mxfp4 && counters && umma && n_tokens > 1u &&
+                                      !router && !ep && !dev_table && y &&
+                                      umma_layer_ok(sm_count, 1u, S14_EXPERTS_PER_TOKEN + 1u, hidden, inter);
+    if (block_on_tensor_path) {
+        bool fits = true;
+        for (uint32_t t = 0; t < n_tokens; ++t)
+            fits = fits && param_table.token_job_begin[t + 1] - param_table.token_job_begin[t] <= S14_EXPERTS_PER_TOKEN + 1u &&
+                   param_table.token_job_begin[t + 1] > param_table.token_job_begin[t];
+        if (fits) {
+            for (uint32_t t = 0; t < n_tokens && *err == cudaSuccess; ++t) {
+                JobTable one = {};
+                const uint32_t b = param_table.token_job_begin[t], e = param_table.token_job_begin[t + 1];
+                one.n_jobs = e - b;
+                one.n_tokens = 1;
+                one.token_job_begin[0] = 0;
+                one.token_job_begin[1] = e - b;
+                for (uint32_t i = b; i < e; ++i) {
+                    Job jb = param_table.jobs[param_table.token_jobs[i]];
+                    jb.token = 0;
+                    jb.out_index = i - b;
+                    one.jobs[i - b] = jb;
+                    one.token_jobs[i - b] = (uint8_t)(i - b);
+                }
+                *err = launch_moe_layer_umma(st, sm_count, nullptr, one, x + (size_t)t * hidden, d, y + (size_t)t * hidden,
+                                             umma->tiles, counters, umma->status, hidden, inter, nullptr, nullptr,
+                                             umma->trace);
+                launches += 1;
+            }
+            if (km) {
+                cudaEventRecord(km->ev[2], st);
+                cudaEventRecord(km->ev[3], st);
+                cudaEventRecord(km->ev[4], st);
+            }
+            return launches;
+        }
+    }
     if (mode == S14_ACCUM_REFERENCE) {
         dim3 gu(ceil_div(inter, 32), n_jobs_max), gd(ceil_div(hidden, 32), n_jobs_max);
         k_expert_up_reference<<<gu, 32, hidden * sizeof(float), st>>>(dev_table, param_table, x, h,
