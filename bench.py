@@ -442,6 +442,13 @@ def run_gpu(args) -> None:
     ms = float(np.median(ms_all))
     value = args.steps / (ms / 1e3)
     _note(f"timed regions done: median {ms:.4f} ms")
+    # the status word of every rank after the timed regions alone (reading clears it)
+    status_timed = ctx.device_status()
+    if world > 1:
+        t = torch.tensor([status_timed], dtype=torch.int64, device="cuda")
+        gathered = [torch.zeros_like(t) for _ in range(world)]
+        dist.all_gather(gathered, t)
+        status_timed = [int(g.item()) for g in gathered]
 
     # ---- optional: one launch of the profiling build, time marks of its second layer
     layer_trace = None
@@ -551,6 +558,11 @@ def run_gpu(args) -> None:
             idsd = torch.empty(TOP_K, dtype=torch.int32, device="cuda")
             yd = torch.empty(HIDDEN, dtype=torch.float32, device="cuda")
             digest = hashlib.sha256()
+            # the GPU steps first, all ranks in step (a rank that waited for rank 0's CPU check between the
+            # steps would run out of its wait limit); the CPU oracle afterwards
+            gots, got_ids = [], []
+            if world > 1:
+                dist.barrier()
             for i in range(n_check):
                 ly = layers[i % n_layers]
                 if world == 1:
@@ -562,14 +574,15 @@ def run_gpu(args) -> None:
                     ep.decode_step(ctx, xs[i], ep_states[i % n_layers], slots, idsd, ep_w, yd, layer=i % n_layers, rank=rank,
                                    world=world, inter=INTER)
                 torch.cuda.synchronize()
-                got = yd.cpu().numpy()
-                digest.update(got.tobytes())
-                if rank == 0:
-                    y64, ids64, _ = cpu_layer(oracle, hp, i % n_layers, xs_np[i], acc64=True)
-                    y32, _, _ = cpu_layer(oracle, hp, i % n_layers, xs_np[i], acc64=False)
-                    routes_ok = routes_ok and bool(np.array_equal(idsd.cpu().numpy(), ids64))
-                    b64.append(error_block(oracle, got, y64))
-                    b32.append(error_block(oracle, got, y32))
+                gots.append(yd.cpu().numpy().copy())
+                got_ids.append(idsd.cpu().numpy().copy())
+                digest.update(gots[-1].tobytes())
+            for i in range(n_check if rank == 0 else 0):
+                y64, ids64, _ = cpu_layer(oracle, hp, i % n_layers, xs_np[i], acc64=True)
+                y32, _, _ = cpu_layer(oracle, hp, i % n_layers, xs_np[i], acc64=False)
+                routes_ok = routes_ok and bool(np.array_equal(got_ids[i], ids64))
+                b64.append(error_block(oracle, gots[i], y64))
+                b32.append(error_block(oracle, gots[i], y32))
             y_digest = digest.hexdigest()
             equal = True
             if world > 1:
@@ -711,7 +724,7 @@ def run_gpu(args) -> None:
                              "pinned token in, expert-parallel step, result out per layer-token")},
             "layer_trace": layer_trace,
             "gpu_launches": launches_per_region, "kernels_per_step": kernels_per_step,
-            "device_status": status, "device_status_all": status_all,
+            "device_status": status, "device_status_all": status_all, "device_status_timed_regions": status_timed,
             "clocks": clocks,
         }
         print(json.dumps(line), flush=True)
