@@ -19,6 +19,8 @@ EXPERTS_PER_TOKEN = 6
 MAX_BLOCK_TOKENS = 8
 PAGE_MXFP4, PAGE_FP8 = 0, 1
 ACCUM_PAIRWISE, ACCUM_REFERENCE = 0, 1
+LAYER_PATH_TENSOR, LAYER_PATH_TENSOR_PER_TOKEN, LAYER_PATH_TENSOR_STACK, LAYER_PATH_F32, LAYER_PATH_REFERENCE = 1, 2, 3, 4, 5
+LAYER_PATH_ROUTER_KERNEL = 0x100
 SCORE_SIGMOID, SCORE_SQRT_SOFTPLUS = 0, 1
 SCALE_UE8M0, SCALE_F32 = 0, 1
 PROFILE_S14_TOP6, PROFILE_FULL_DEPTH43_NATIVE_TOP6 = 0, 1
@@ -126,6 +128,7 @@ SIGNATURES = {
     "s14_ctx_sm_count": (_I32, [_VP]),
     "s14_ctx_device_status": (_I32, [_VP, _P(_U32)]),
     "s14_ctx_launch_count": (_U64, [_VP]),
+    "s14_ctx_last_layer_path": (_U32, [_VP]),
     "s14_ctx_set_layer_trace": (_I32, [_VP, _I32]),
     "s14_ctx_read_layer_trace": (_I32, [_VP, _VP, _U32, _P(_U32), _P(_U32)]),
     "s14_ctx_set_kernel_timing": (_I32, [_VP, _I32]),
@@ -182,7 +185,16 @@ SIGNATURES = {
     "s14_moe_layer_noalloc": (_I32, [_I32, _VP, _U32, _P(MoeLayerDesc)]),
     "s14_moe_layer_host": (_I32, [_VP, _P(MoeLayerDesc), _VP, _VP]),
     "s14_pool_create": (_I32, [_VP, _U32, _U64, _P(_VP)]),
+    "s14_pool_create_host": (_I32, [_U32, _U64, _P(_VP)]),
     "s14_pool_destroy": (_I32, [_VP]),
+    "s14_loader_create": (_I32, [_VP, _U32, _P(_VP)]),
+    "s14_loader_destroy": (_I32, [_VP]),
+    "s14_loader_enqueue_from_buf": (_I32, [_VP, ExpertKey, _VP, _U64, _P(_U32)]),
+    "s14_loader_batch_enqueue_from_bufs": (_I32, [_VP, _VP, _VP, _VP, _U32, _VP]),
+    "s14_loader_wait_all": (_I32, [_VP]),
+    "s14_loader_in_flight": (_U32, [_VP]),
+    "s14_loader_stat_loads": (_U64, [_VP]),
+    "s14_loader_stat_bytes": (_U64, [_VP]),
     "s14_pool_capacity": (_U32, [_VP]),
     "s14_pool_slot_bytes": (_U64, [_VP]),
     "s14_pool_n_loaded": (_U32, [_VP]),

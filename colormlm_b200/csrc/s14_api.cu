@@ -29,11 +29,20 @@ static int32_t cuda_fail(cudaError_t e, const char *what) {
     return fail(S14_ERR_CUDA, std::string(what) + ": " + cudaGetErrorString(e));
 }
 
+// a CUDA error inside host-side classes that report by exception
+struct CudaError : std::runtime_error {
+    using std::runtime_error::runtime_error;
+};
+static void cuda_check(cudaError_t e, const char *what) {
+    if (e != cudaSuccess) throw CudaError(std::string(what) + ": " + cudaGetErrorString(e));
+}
+
 #define S14_TRY try {
 #define S14_CATCH                                                      \
     }                                                                  \
     catch (const ContractError &e) { return fail(S14_ERR_CONTRACT, e.what()); } \
     catch (const PoolError &e) { return fail(S14_ERR_POOL, e.what()); }         \
+    catch (const CudaError &e) { return fail(S14_ERR_CUDA, e.what()); }         \
     catch (const CodeError &e) { return fail(S14_ERR_CODE, e.what()); }         \
     catch (const std::bad_alloc &) { return fail(S14_ERR_CONTRACT, "out of host memory"); } \
     catch (const std::exception &e) { return fail(S14_ERR_CONTRACT, e.what()); }
@@ -65,6 +74,7 @@ struct s14_ctx {
     float *x_stage = nullptr, *y_stage = nullptr;  // [kMaxTokens, kMaxDim]
     uint32_t *status = nullptr;
     uint64_t launches = 0;
+    uint32_t last_path = 0;   // S14_LAYER_PATH_* of the last layer or stack call
     bool timing = false;  // per-kernel timing of routed layer calls (blocks after each call)
     KernelMarks marks{};
     double kernel_ms[4] = {0, 0, 0, 0};  // router, up, down, mix
@@ -200,6 +210,7 @@ extern "C" int32_t s14_ctx_set_accumulation(s14_ctx *ctx, uint32_t mode) {
 extern "C" uint32_t s14_ctx_accumulation(const s14_ctx *ctx) { return ctx ? ctx->mode : 0; }
 extern "C" int32_t s14_ctx_sm_count(const s14_ctx *ctx) { return ctx ? ctx->sm_count : 0; }
 extern "C" uint64_t s14_ctx_launch_count(const s14_ctx *ctx) { return ctx ? ctx->launches : 0; }
+extern "C" uint32_t s14_ctx_last_layer_path(const s14_ctx *ctx) { return ctx ? ctx->last_path : 0; }
 
 extern "C" int32_t s14_ctx_device_status(s14_ctx *ctx, uint32_t *status) {
     if (!ctx || !status) return fail(S14_ERR_CONTRACT, "ctx or status is NULL");
@@ -605,6 +616,7 @@ static int32_t enqueue_layer(s14_ctx *ctx, cudaStream_t st, const s14_moe_layer_
     const int launched = launch_moe_layer(st, ctx->mode, ctx->sm_count, nullptr, tab, tab.n_tokens,
                                           tab.n_jobs, desc.hidden, desc.inter, x, ctx->h, ctx->d, y,
                                           &err, nullptr, all_mxfp4, ctx->counters, ctx->umma_scratch());
+    ctx->last_path = last_layer_path();
     ctx->launches += launched;
     if (err != cudaSuccess) return cuda_fail(err, "S14 MoE layer launch");
     return S14_OK;
@@ -817,6 +829,7 @@ extern "C" int32_t s14_cmd_routed_moe_layer(s14_ctx *ctx, void *stream,
                                       r.hidden, desc->inter, r.x, ctx->h, ctx->d, desc->y, &err, km,
                                       !desc->shared_page || desc->shared_kind == S14_PAGE_MXFP4, ctx->counters,
                                       ctx->umma_scratch(), &fr);
+    ctx->last_path = last_layer_path();
     if (err != cudaSuccess) return cuda_fail(err, "S14 routed MoE layer launch");
     if (km) {
         CUDA_OK(cudaStreamSynchronize(st));
@@ -951,6 +964,7 @@ extern "C" int32_t s14_cmd_stack_decode(s14_ctx *ctx, void *stream, s14_stack *s
                                                       ctx->umma.trace, stack->dev_layers, c.n_layers, stack->hbuf,
                                                       c.residual != 0);
         ctx->launches += 1;
+        ctx->last_path = S14_LAYER_PATH_TENSOR_STACK;
         if (err != cudaSuccess) return cuda_fail(err, "S14 stack launch");
         return S14_OK;
     }
@@ -962,6 +976,7 @@ extern "C" int32_t s14_cmd_stack_decode(s14_ctx *ctx, void *stream, s14_stack *s
         ctx->launches += launch_moe_layer(st, ctx->mode, ctx->sm_count, ctx->dev_table, unused, 1, n_jobs, c.hidden, c.inter,
                                           cur, ctx->h, ctx->d, stack->ybuf, &err, nullptr,
                                           !has_shared || c.shared_kind == S14_PAGE_MXFP4, ctx->counters, ctx->umma_scratch(), &fr);
+        ctx->last_path = last_layer_path();
         if (err != cudaSuccess) return cuda_fail(err, "S14 stack layer launch");
         float *next = (l + 1 == c.n_layers) ? h_out : stack->hbuf + (size_t)((l + 1) & 1u) * c.hidden;
         CUDA_OK(launch_stack_step(st, cur, stack->ybuf, next, stack->layers[l].y_out, c.hidden, c.residual != 0));
@@ -1012,6 +1027,7 @@ extern "C" int32_t s14_cmd_routed_moe_experts_ep(s14_ctx *ctx, void *stream,
                                       r.hidden, desc->inter, r.x, ctx->h, slots_out, nullptr, &err, nullptr,
                                       !desc->shared_page || desc->shared_kind == S14_PAGE_MXFP4,
                                       ctx->counters, ctx->umma_scratch(), &fr);
+    ctx->last_path = last_layer_path();
     if (err != cudaSuccess) return cuda_fail(err, "S14 routed MoE layer launch");
     return S14_OK;
     S14_CATCH
@@ -1176,6 +1192,7 @@ extern "C" int32_t s14_cmd_routed_moe_layer_ep(s14_ctx *ctx, void *stream, const
     ctx->launches += launch_moe_layer(st, ctx->mode, ctx->sm_count, ctx->dev_table, unused, 1, n_slots, r.hidden,
                                       desc->inter, r.x, ctx->h, ctx->d, desc->y, &err, nullptr, true, ctx->counters,
                                       ctx->umma_scratch(), &fr, &ex);
+    ctx->last_path = last_layer_path();
     if (err != cudaSuccess) return cuda_fail(err, "S14 expert-parallel layer launch");
     return S14_OK;
     S14_CATCH
@@ -1237,6 +1254,7 @@ extern "C" int32_t s14_cmd_greedy_argmax(s14_ctx *ctx, void *stream, const float
 struct s14_pool {
     s14_ctx *ctx = nullptr;
     uint8_t *device_base = nullptr;
+    std::vector<uint8_t> host_base;  // s14_pool_create_host
     std::unique_ptr<VramPool> pool;
     cudaEvent_t transfer_fence = nullptr;
     bool fence_recorded = false;
@@ -1295,6 +1313,21 @@ extern "C" int32_t s14_pool_create(s14_ctx *ctx, uint32_t n_slots, uint64_t slot
         p->ctx = ctx;
         CUDA_OK(cudaEventCreateWithFlags(&p->transfer_fence, cudaEventDisableTiming));
     }
+    *out = p.release();
+    return S14_OK;
+    S14_CATCH
+}
+
+// A pool whose slots are host memory: the bookkeeping of s14_pool_create with memory a CPU test can
+// read (the expert loader's tests); no kernel can use it.
+extern "C" int32_t s14_pool_create_host(uint32_t n_slots, uint64_t slot_bytes, s14_pool **out) {
+    S14_TRY
+    if (!out) throw ContractError("s14_pool_create_host: out is NULL");
+    *out = nullptr;
+    std::unique_ptr<s14_pool> p(new s14_pool());
+    p->pool.reset(new VramPool(n_slots, slot_bytes, nullptr));  // validates sizes first
+    p->host_base.assign((size_t)n_slots * slot_bytes, 0);
+    p->pool.reset(new VramPool(n_slots, slot_bytes, p->host_base.data()));
     *out = p.release();
     return S14_OK;
     S14_CATCH
@@ -1467,6 +1500,130 @@ extern "C" int32_t s14_host_free_pinned(void *ptr) {
     if (ptr) CUDA_OK(cudaFreeHost(ptr));
     return S14_OK;
 }
+
+// ---- expert loader ------------------------------------------------------------------
+
+// Pinned staging buffers, one cudaMemcpyAsync per page on the context's copy stream, one event per
+// ring entry.
+struct CudaTransferEngine : TransferEngine {
+    s14_ctx *ctx;
+    std::vector<uint8_t *> bufs;
+    std::vector<cudaEvent_t> fences;
+    CudaTransferEngine(s14_ctx *c, uint32_t depth, uint64_t bytes) : ctx(c) {
+        cuda_check(cudaSetDevice(c->device), "expert loader");
+        for (uint32_t i = 0; i < depth; ++i) {
+            void *p = nullptr;
+            cuda_check(cudaHostAlloc(&p, bytes, cudaHostAllocDefault), "expert loader staging buffer");
+            bufs.push_back((uint8_t *)p);
+            cudaEvent_t e = nullptr;
+            cuda_check(cudaEventCreateWithFlags(&e, cudaEventDisableTiming), "expert loader fence");
+            fences.push_back(e);
+        }
+    }
+    ~CudaTransferEngine() override {
+        for (auto e : fences) cudaEventDestroy(e);
+        for (auto b : bufs) cudaFreeHost(b);
+    }
+    uint8_t *staging(uint32_t entry) override { return bufs[entry]; }
+    void submit(uint32_t entry, uint8_t *dst, uint64_t bytes) override {
+        cuda_check(cudaMemcpyAsync(dst, bufs[entry], bytes, cudaMemcpyHostToDevice, ctx->copy), "expert page upload");
+        cuda_check(cudaEventRecord(fences[entry], ctx->copy), "expert page fence");
+    }
+    void wait(uint32_t entry) override { cuda_check(cudaEventSynchronize(fences[entry]), "expert page fence wait"); }
+};
+
+// For a pool in host memory (s14_pool_create_host; tests without a GPU): the copy runs when it is
+// waited for, the latest moment a real transfer may still read its staging buffer.
+struct HostTransferEngine : TransferEngine {
+    struct Job {
+        uint8_t *dst = nullptr;
+        uint64_t bytes = 0;
+    };
+    std::vector<std::vector<uint8_t>> bufs;
+    std::vector<Job> jobs;
+    HostTransferEngine(uint32_t depth, uint64_t bytes) : bufs(depth, std::vector<uint8_t>(bytes)), jobs(depth) {}
+    uint8_t *staging(uint32_t entry) override { return bufs[entry].data(); }
+    void submit(uint32_t entry, uint8_t *dst, uint64_t bytes) override {
+        if (!dst) throw PoolError("this pool has no memory (bookkeeping-only pool)");
+        jobs[entry] = Job{dst, bytes};
+    }
+    void wait(uint32_t entry) override {
+        if (jobs[entry].dst) std::memcpy(jobs[entry].dst, bufs[entry].data(), jobs[entry].bytes);
+        jobs[entry] = Job{};
+    }
+};
+
+struct s14_loader {
+    s14_pool *pool = nullptr;
+    std::unique_ptr<TransferEngine> engine;
+    std::unique_ptr<ExpertLoader> loader;
+};
+
+extern "C" int32_t s14_loader_create(s14_pool *pool, uint32_t pipeline_depth, s14_loader **out) {
+    S14_TRY
+    if (!pool || !out) throw ContractError("s14_loader_create: NULL argument");
+    *out = nullptr;
+    if (pipeline_depth == 0 || pipeline_depth > 64) throw PoolError("expert loader: pipeline depth must be 1..64");
+    if (!pool->pool->base()) throw PoolError("this pool has no memory (bookkeeping-only pool)");
+    std::unique_ptr<s14_loader> l(new s14_loader());
+    l->pool = pool;
+    if (pool->ctx) l->engine.reset(new CudaTransferEngine(pool->ctx, pipeline_depth, pool->pool->slot_bytes()));
+    else l->engine.reset(new HostTransferEngine(pipeline_depth, pool->pool->slot_bytes()));
+    l->loader.reset(new ExpertLoader(*pool->pool, *l->engine, pipeline_depth, pool->pool->slot_bytes()));
+    *out = l.release();
+    return S14_OK;
+    S14_CATCH
+}
+
+extern "C" int32_t s14_loader_destroy(s14_loader *loader) {
+    if (!loader) return S14_OK;
+    S14_TRY
+    std::unique_ptr<s14_loader> own(loader);
+    own->loader->wait_all();  // only submitted transfers are waited for
+    return S14_OK;
+    S14_CATCH
+}
+
+extern "C" int32_t s14_loader_enqueue_from_buf(s14_loader *loader, s14_expert_key key, const void *data, uint64_t bytes,
+                                               uint32_t *slot_out) {
+    S14_TRY
+    if (!loader || !slot_out) throw ContractError("s14_loader_enqueue_from_buf: NULL argument");
+    *slot_out = loader->loader->enqueue_from_buf(key_of(key), (const uint8_t *)data, bytes);
+    return S14_OK;
+    S14_CATCH
+}
+
+extern "C" int32_t s14_loader_batch_enqueue_from_bufs(s14_loader *loader, const s14_expert_key *keys,
+                                                      const void *const *datas, const uint64_t *sizes, uint32_t n,
+                                                      uint32_t *slots_out) {
+    S14_TRY
+    if (!loader || (n && (!keys || !datas || !sizes || !slots_out)))
+        throw ContractError("s14_loader_batch_enqueue_from_bufs: NULL argument");
+    std::vector<ExpertKey> k;
+    std::vector<const uint8_t *> d;
+    std::vector<uint64_t> z;
+    for (uint32_t i = 0; i < n; ++i) {
+        k.push_back(key_of(keys[i]));
+        d.push_back((const uint8_t *)datas[i]);
+        z.push_back(sizes[i]);
+    }
+    const std::vector<uint32_t> slots = loader->loader->batch_enqueue_from_bufs(k, d, z);
+    for (uint32_t i = 0; i < n; ++i) slots_out[i] = slots[i];
+    return S14_OK;
+    S14_CATCH
+}
+
+extern "C" int32_t s14_loader_wait_all(s14_loader *loader) {
+    S14_TRY
+    if (!loader) throw ContractError("s14_loader_wait_all: loader is NULL");
+    loader->loader->wait_all();
+    return S14_OK;
+    S14_CATCH
+}
+
+extern "C" uint32_t s14_loader_in_flight(const s14_loader *loader) { return loader ? loader->loader->in_flight() : 0; }
+extern "C" uint64_t s14_loader_stat_loads(const s14_loader *loader) { return loader ? loader->loader->stat_loads : 0; }
+extern "C" uint64_t s14_loader_stat_bytes(const s14_loader *loader) { return loader ? loader->loader->stat_bytes : 0; }
 
 // ---- route page transaction ---------------------------------------------------------
 

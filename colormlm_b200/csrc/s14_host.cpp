@@ -296,6 +296,97 @@ void VramPool::cancel_reservation(const LoadingReservation &r) {
 
 // ---- RouteDecision ----------------------------------------------------------
 
+// ---- ExpertLoader ---------------------------------------------------------------------
+
+ExpertLoader::ExpertLoader(VramPool &pool, TransferEngine &engine, uint32_t pipeline_depth, uint64_t staging_bytes)
+    : pool_(pool), engine_(engine), depth_(pipeline_depth), staging_bytes_(staging_bytes), pending_(pipeline_depth) {
+    if (pipeline_depth == 0) throw PoolError("expert loader needs a staging ring of at least one buffer");
+    if (staging_bytes == 0 || staging_bytes > pool.slot_bytes())
+        throw PoolError("staging buffers must hold one page and no more than a VRAM slot: " + std::to_string(staging_bytes) +
+                        " bytes against slots of " + std::to_string(pool.slot_bytes()));
+}
+
+uint32_t ExpertLoader::in_flight() const {
+    uint32_t n = 0;
+    for (const Pending &p : pending_) n += p.active ? 1u : 0u;
+    return n;
+}
+
+// Waits for the entry's transfer and publishes its page.
+void ExpertLoader::complete_entry(uint32_t entry) {
+    Pending &p = pending_[entry];
+    if (!p.active) return;
+    engine_.wait(entry);
+    p.active = false;  // whatever mark_ready says, the entry is free again
+    pool_.mark_ready(p.slot, p.key);
+}
+
+uint32_t ExpertLoader::enqueue_from_buf(const ExpertKey &key, const uint8_t *data, uint64_t bytes) {
+    if (auto slot = pool_.lookup(key)) return *slot;
+    for (uint32_t e = 0; e < depth_; ++e) {
+        if (pending_[e].active && pending_[e].key == key) {  // in flight already: settle it
+            complete_entry(e);
+            if (auto slot = pool_.lookup(key)) return *slot;
+        }
+    }
+    if (!data) throw PoolError("expert page bytes are NULL");
+    if (bytes == 0 || bytes > staging_bytes_ || bytes > pool_.slot_bytes())
+        throw PoolError("expert page of " + std::to_string(bytes) + " bytes does not fit a staging buffer of " +
+                        std::to_string(staging_bytes_) + " / a VRAM slot of " + std::to_string(pool_.slot_bytes()));
+    const uint32_t entry = next_;
+    next_ = (next_ + 1) % depth_;
+    complete_entry(entry);  // the ring entry's earlier transfer no longer reads its staging buffer
+    const LoadingReservation r = pool_.reserve_loading_generation(key);  // may evict; hidden until published
+    try {
+        std::memcpy(engine_.staging(entry), data, bytes);
+        engine_.submit(entry, pool_.slot_ptr(r.slot), bytes);
+    } catch (...) {
+        pool_.cancel_loading(r.slot, key);
+        throw;
+    }
+    pending_[entry].active = true;
+    pending_[entry].key = key;
+    pending_[entry].slot = r.slot;
+    ++stat_loads;
+    stat_bytes += bytes;
+    return r.slot;
+}
+
+void ExpertLoader::wait_all() {
+    for (uint32_t e = 0; e < depth_; ++e) complete_entry(e);
+}
+
+std::vector<uint32_t> ExpertLoader::batch_enqueue_from_bufs(const std::vector<ExpertKey> &keys,
+                                                            const std::vector<const uint8_t *> &datas,
+                                                            const std::vector<uint64_t> &sizes) {
+    if (keys.size() != datas.size() || keys.size() != sizes.size())
+        throw PoolError("expert loader batch: keys, buffers and sizes differ in number");
+    if (keys.empty()) return {};
+    wait_all();  // earlier work is Ready before duplicates are looked for
+    std::vector<size_t> unique;             // first input index of every distinct key
+    std::vector<size_t> to_unique(keys.size());
+    for (size_t i = 0; i < keys.size(); ++i) {
+        size_t u = 0;
+        while (u < unique.size() && !(keys[unique[u]] == keys[i])) ++u;
+        if (u == unique.size()) unique.push_back(i);
+        to_unique[i] = u;
+    }
+    if (unique.size() > pool_.capacity())
+        throw PoolError("batch requests " + std::to_string(unique.size()) + " distinct experts but VRAM pool has only " +
+                        std::to_string(pool_.capacity()) + " slots");
+    std::vector<uint32_t> slots(unique.size());
+    for (size_t base = 0; base < unique.size(); base += depth_) {
+        const size_t end = std::min(unique.size(), base + depth_);
+        for (size_t u = base; u < end; ++u) slots[u] = enqueue_from_buf(keys[unique[u]], datas[unique[u]], sizes[unique[u]]);
+        // the next wave reuses the staging buffers: this one is published and drained first; the last
+        // wave stays in flight until the caller's wait_all
+        if (end < unique.size()) wait_all();
+    }
+    std::vector<uint32_t> out(keys.size());
+    for (size_t i = 0; i < keys.size(); ++i) out[i] = slots[to_unique[i]];
+    return out;
+}
+
 void RouteDecision::validate_for(GraphProfile profile) const {
     bool in_profile = false;
     if (profile == GraphProfile::S14Top6) {

@@ -139,6 +139,54 @@ private:
     uint32_t n_loaded_ = 0;
 };
 
+// ExpertLoader (ssd_inference/src/expert_loader.rs:163-442): expert pages go to pool slots through a
+// ring of `pipeline_depth` staging buffers, each with a fence of its own.  An entry of the ring is
+// reused only after its transfer has completed and its page has been published (Loading -> Ready); a
+// page is not visible through VramPool::lookup before that.  batch_enqueue works in waves no deeper
+// than the ring, so that a later page never overwrites staging memory an earlier transfer still
+// reads (expert_loader.rs:299-358).  The transfers themselves are behind an interface: CUDA copies
+// on the context's copy stream in the library, host copies that run as late as the wait in the CPU
+// tests (which is what shows a staging buffer that was reused too early).
+struct TransferEngine {
+    virtual ~TransferEngine() = default;
+    virtual uint8_t *staging(uint32_t entry) = 0;                          // host memory of the ring entry
+    virtual void submit(uint32_t entry, uint8_t *dst, uint64_t bytes) = 0; // start staging -> dst; throws on failure
+    virtual void wait(uint32_t entry) = 0;                                 // that entry's last transfer is complete
+};
+
+class ExpertLoader {
+public:
+    ExpertLoader(VramPool &pool, TransferEngine &engine, uint32_t pipeline_depth, uint64_t staging_bytes);
+    // The page of `key` from bytes in host memory: returns the pool slot.  A page that is Ready, or
+    // in flight (its entry is completed first), is not loaded again.  Blocks only to reclaim the
+    // ring entry it takes (enqueue_from_buf, expert_loader.rs:362-442).
+    uint32_t enqueue_from_buf(const ExpertKey &key, const uint8_t *data, uint64_t bytes);
+    // Several pages: earlier work is settled, duplicates are loaded once, more distinct pages than
+    // the pool has slots are refused before anything is issued; waves of pipeline_depth, every wave but
+    // the last drained before the next one starts (batch_enqueue, expert_loader.rs:299-358).
+    std::vector<uint32_t> batch_enqueue_from_bufs(const std::vector<ExpertKey> &keys,
+                                                  const std::vector<const uint8_t *> &datas,
+                                                  const std::vector<uint64_t> &sizes);
+    void wait_all();  // every transfer complete, every page published (expert_loader.rs:291-297)
+    uint32_t in_flight() const;
+    uint32_t pipeline_depth() const { return depth_; }
+    uint64_t stat_loads = 0, stat_bytes = 0;
+
+private:
+    struct Pending {
+        bool active = false;
+        ExpertKey key;
+        uint32_t slot = 0;
+    };
+    void complete_entry(uint32_t entry);
+    VramPool &pool_;
+    TransferEngine &engine_;
+    uint32_t depth_;
+    uint64_t staging_bytes_;
+    uint32_t next_ = 0;
+    std::vector<Pending> pending_;
+};
+
 // RouterKind / GraphProfile / RouteDecision (s14_runner/src/contract.rs:27-52,
 // runner.rs:121-180).
 enum class RouterKind : uint8_t { Hash = 0, Score = 1 };

@@ -111,6 +111,8 @@ cudaError_t launch_route_mix(cudaStream_t st, const float *expert, float *routed
                              float weight);
 cudaError_t launch_moe_accumulate(cudaStream_t st, const float *expert, float *acc, uint32_t n,
                                   float weight);
+// Which implementation the calling thread's last launch_moe_layer chose (S14_LAYER_PATH_* of the header).
+uint32_t last_layer_path();
 // Returns the number of kernels launched.  h: [kMaxJobs, inter], d: [kMaxJobs, hidden].
 int launch_moe_layer(cudaStream_t st, uint32_t mode, int sm_count, const JobTable *dev_table,
                      const JobTable &param_table, uint32_t n_tokens, uint32_t n_jobs_max,

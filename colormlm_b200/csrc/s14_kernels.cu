@@ -933,6 +933,10 @@ static void launch_down_pairwise(cudaStream_t st, const JobTable *dev, const Job
                                                                       ctas_per_job);
 }
 
+// which implementation the calling thread's last launch_moe_layer chose (S14_LAYER_PATH_*)
+static thread_local uint32_t t_last_layer_path = 0;
+uint32_t last_layer_path() { return t_last_layer_path; }
+
 int launch_moe_layer(cudaStream_t st, uint32_t mode, int sm_count, const JobTable *dev_table,
                      const JobTable &param_table, uint32_t n_tokens, uint32_t n_jobs_max,
                      uint32_t hidden, uint32_t inter, const float *x, float *h, float *d, float *y,
@@ -940,6 +944,7 @@ int launch_moe_layer(cudaStream_t st, uint32_t mode, int sm_count, const JobTabl
                      const UmmaScratch *umma, const FusedRouter *router, const EpExchange *ep) {
     int launches = 0;
     *err = cudaSuccess;
+    t_last_layer_path = 0;
     const bool tensor_path = mode != S14_ACCUM_REFERENCE && all_mxfp4 && counters && umma &&
                              umma_layer_ok(sm_count, n_tokens, n_jobs_max, hidden, inter);
     if (ep && ep->world > 1u && !(tensor_path && router && umma_router_ok(sm_count, router->n_experts))) {
@@ -966,6 +971,7 @@ int launch_moe_layer(cudaStream_t st, uint32_t mode, int sm_count, const JobTabl
         if (*err != cudaSuccess) return launches;
         dev_table = router->table_out;
         router = nullptr;
+        t_last_layer_path |= S14_LAYER_PATH_ROUTER_KERNEL;
     } else if (router && km) {
         cudaEventRecord(km->ev[0], st);
     }
@@ -1009,6 +1015,7 @@ int launch_moe_layer(cudaStream_t st, uint32_t mode, int sm_count, const JobTabl
                 cudaEventRecord(km->ev[3], st);
                 cudaEventRecord(km->ev[4], st);
             }
+            t_last_layer_path |= S14_LAYER_PATH_TENSOR_PER_TOKEN;
             return launches;
         }
     }
@@ -1020,10 +1027,12 @@ int launch_moe_layer(cudaStream_t st, uint32_t mode, int sm_count, const JobTabl
         k_expert_down_reference<<<gd, 32, inter * sizeof(float), st>>>(dev_table, param_table, h, d,
                                                                        hidden, inter);
         launches += 2;
+        t_last_layer_path |= S14_LAYER_PATH_REFERENCE;
     } else if (tensor_path) {
         *err = launch_moe_layer_umma(st, sm_count, dev_table, param_table, x, d, y, umma->tiles, counters,
                                      umma->status, hidden, inter, router, ep, umma->trace);
         launches += 1;
+        t_last_layer_path |= S14_LAYER_PATH_TENSOR;
         if (km) {  // one kernel runs both phases and the mix: its time is booked as the up phase
             cudaEventRecord(km->ev[2], st);
             cudaEventRecord(km->ev[3], st);
@@ -1045,6 +1054,7 @@ int launch_moe_layer(cudaStream_t st, uint32_t mode, int sm_count, const JobTabl
         default: launch_down_pairwise<4>(st, dev_table, param_table, h, d, hidden, n_jobs_max, ctas_per_job); break;
         }
         launches += 2;
+        t_last_layer_path |= S14_LAYER_PATH_F32;
     }
     if (km) cudaEventRecord(km->ev[3], st);
     if (!y) return launches;  // the caller mixes (expert-parallel combine)

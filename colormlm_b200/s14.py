@@ -148,6 +148,11 @@ class S14Context:
     def launch_count(self) -> int:
         return L.lib().s14_ctx_launch_count(self._h)
 
+    @property
+    def last_layer_path(self) -> int:
+        """Which implementation the last layer or stack call ran (L.LAYER_PATH_*)."""
+        return L.lib().s14_ctx_last_layer_path(self._h)
+
     def synchronize(self) -> None:
         check(L.lib().s14_ctx_synchronize(self._h))
 

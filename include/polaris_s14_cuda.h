@@ -99,6 +99,17 @@ S14_API int32_t s14_ctx_sm_count(const s14_ctx *ctx);
 S14_API int32_t s14_ctx_device_status(s14_ctx *ctx, uint32_t *status);
 /* Number of kernels this context has launched since creation. */
 S14_API uint64_t s14_ctx_launch_count(const s14_ctx *ctx);
+/* Which implementation the context's last MoE layer or stack call ran (the library chooses by
+ * accumulation mode, page kinds, token count and sizes; no counterpart in the reference):
+ * exactly one of the first five values, ORed with ROUTER_KERNEL if the routes came from a kernel
+ * launch of their own instead of being picked inside the layer kernel.  0: no such call yet. */
+#define S14_LAYER_PATH_TENSOR 1u           /* tcgen05 layer kernel, one launch per layer-token */
+#define S14_LAYER_PATH_TENSOR_PER_TOKEN 2u /* a block of tokens: one launch of it per token */
+#define S14_LAYER_PATH_TENSOR_STACK 3u     /* a whole stack of layers in one launch of it */
+#define S14_LAYER_PATH_F32 4u              /* F32 register kernels, pairwise order */
+#define S14_LAYER_PATH_REFERENCE 5u        /* reference-order kernels */
+#define S14_LAYER_PATH_ROUTER_KERNEL 0x100u
+S14_API uint32_t s14_ctx_last_layer_path(const s14_ctx *ctx);
 
 /* Per-kernel timing of s14_cmd_routed_moe_layer for profiling runs: while enabled,
  * every such call records CUDA events around its kernels, waits for the stream and
@@ -516,6 +527,9 @@ typedef struct {
  * ctx == NULL builds the bookkeeping-only pool the reference's unit tests use
  * (new_for_tests, vram_pool.rs:408-421): no device memory, slot addresses NULL. */
 S14_API int32_t s14_pool_create(s14_ctx *ctx, uint32_t n_slots, uint64_t slot_bytes, s14_pool **out);
+/* The same bookkeeping over slots in host memory (no device, no kernels): for tests of the loader
+ * below on a machine without a GPU. */
+S14_API int32_t s14_pool_create_host(uint32_t n_slots, uint64_t slot_bytes, s14_pool **out);
 S14_API int32_t s14_pool_destroy(s14_pool *pool);
 S14_API uint32_t s14_pool_capacity(const s14_pool *pool);
 S14_API uint64_t s14_pool_slot_bytes(const s14_pool *pool);
@@ -560,6 +574,34 @@ S14_API int32_t s14_pool_upload_page_async(s14_pool *pool, const s14_loading_res
 S14_API int32_t s14_pool_transfer_fence(s14_pool *pool);
 S14_API int32_t s14_pool_wait_transfer_fence(s14_pool *pool);
 S14_API int32_t s14_pool_compute_wait_transfer(s14_pool *pool, void *compute_stream);
+/* ExpertLoader (ssd_inference/src/expert_loader.rs:163-442): pages go to pool slots through a ring
+ * of pipeline_depth pinned staging buffers with a fence each (one cudaMemcpyAsync per page on the
+ * context's copy stream).  A ring entry is reused only after its transfer has completed and its
+ * page has been published; a page is not visible through s14_pool_lookup before that.
+ *   enqueue_from_buf (:362-442): a page that is Ready or in flight is not loaded again; otherwise
+ *     the next ring entry is reclaimed (this is the only wait), a slot is reserved (may evict), the
+ *     bytes are copied to the entry's staging buffer and the transfer is started; *slot_out is the
+ *     pool slot.  A failure cancels the reservation.
+ *   batch_enqueue_from_bufs (batch_enqueue, :299-358): earlier work is settled first, duplicates are
+ *     loaded once, more distinct pages than the pool has slots are refused before anything is
+ *     issued; waves of pipeline_depth pages, every wave but the last drained before the next one
+ *     starts, so that no page overwrites staging memory an earlier transfer still reads.
+ *   wait_all (:291-297): every transfer complete, every page Ready.
+ * The reference's reader-based enqueue (file range reads into the staging buffer) is not mirrored:
+ * the page source is the caller's. */
+typedef struct s14_loader s14_loader;
+S14_API int32_t s14_loader_create(s14_pool *pool, uint32_t pipeline_depth, s14_loader **out);
+S14_API int32_t s14_loader_destroy(s14_loader *loader);
+S14_API int32_t s14_loader_enqueue_from_buf(s14_loader *loader, s14_expert_key key, const void *data, uint64_t bytes,
+                                            uint32_t *slot_out);
+S14_API int32_t s14_loader_batch_enqueue_from_bufs(s14_loader *loader, const s14_expert_key *keys,
+                                                   const void *const *datas, const uint64_t *sizes, uint32_t n,
+                                                   uint32_t *slots_out);
+S14_API int32_t s14_loader_wait_all(s14_loader *loader);
+S14_API uint32_t s14_loader_in_flight(const s14_loader *loader);
+S14_API uint64_t s14_loader_stat_loads(const s14_loader *loader);
+S14_API uint64_t s14_loader_stat_bytes(const s14_loader *loader);
+
 /* Pinned host staging memory (GpuBuffer::new_staging, buffer.rs:56-75). */
 S14_API int32_t s14_host_alloc_pinned(uint64_t bytes, void **out);
 S14_API int32_t s14_host_free_pinned(void *ptr);

@@ -2,6 +2,8 @@
 seeded inputs.  Reference-order mode must be bit-identical to the oracle's F32 results
 (max_abs = RMSE = 0, inside the stated 2e-5 / 2e-6); pairwise mode is held to the relative
 bound of assert_pairwise_close against the double-accumulated reference."""
+import ctypes as C
+
 import numpy as np
 import pytest
 
@@ -309,6 +311,7 @@ def test_moe_layer_verify_block(ctx, oracle, n_tokens):
     for mode in (L.ACCUM_REFERENCE, L.ACCUM_PAIRWISE):
         ctx.set_accumulation(mode)
         y = run_layer(ctx, x, pages_dev, shared_dev, routes, L.PAGE_MXFP4, hidden, inter)
+        assert ctx.last_layer_path == (L.LAYER_PATH_REFERENCE if mode == L.ACCUM_REFERENCE else L.LAYER_PATH_TENSOR_PER_TOKEN)
         for t in range(n_tokens):
             ids, w = routes[t]
             if mode == L.ACCUM_REFERENCE:
@@ -322,9 +325,38 @@ def test_moe_layer_verify_block(ctx, oracle, n_tokens):
             # pairwise order a block of MXFP4 experts is one launch of the tcgen05 kernel per token, and
             # the result is the double-accumulated oracle's, bit for bit)
             single = run_layer(ctx, x[t:t + 1], pages_dev, shared_dev, [routes[t]], L.PAGE_MXFP4, hidden, inter)[0]
+            assert ctx.last_layer_path == (L.LAYER_PATH_REFERENCE if mode == L.ACCUM_REFERENCE else L.LAYER_PATH_TENSOR)
             assert np.array_equal(single.view(np.uint32), y[t].view(np.uint32))
             if mode == L.ACCUM_PAIRWISE:
                 assert np.array_equal(y[t].view(np.uint32), ref.view(np.uint32))
+    ctx.set_accumulation(L.ACCUM_PAIRWISE)
+
+
+def test_moe_layer_verify_block_at_the_benchmark_shape(ctx, oracle):
+    """Eight tokens, 4096 x 2048, 48 experts of which the block uses more than 30 distinct ones: in
+    pairwise order every token is its own one-token call and the double-accumulated oracle, bit for
+    bit; in reference order the F32 oracle."""
+    hidden, inter, n_experts, n_tokens = 4096, 2048, 48, 8
+    g, pages, shared = make_layer(977, hidden, inter, n_experts, L.PAGE_MXFP4)
+    x = synth.activations(g, n_tokens, hidden)
+    routes = []
+    for t in range(n_tokens):
+        routes.append((g.permutation(n_experts)[:6].tolist(), g.uniform(0.05, 0.4, 6).astype(np.float32)))
+    assert len({e for ids, _ in routes for e in ids}) > 30
+    pages_dev, shared_dev = [dev_page(p, hidden, inter) for p in pages], dev_page(shared, hidden, inter)
+    ctx.set_accumulation(L.ACCUM_PAIRWISE)
+    y = run_layer(ctx, x, pages_dev, shared_dev, routes, L.PAGE_MXFP4, hidden, inter)
+    assert ctx.last_layer_path == L.LAYER_PATH_TENSOR_PER_TOKEN
+    for t in range(n_tokens):
+        ids, w = routes[t]
+        ref = oracle.moe_layer_acc64(x[t], [pages[i] for i in ids], w, shared, 0, hidden, inter)
+        assert np.array_equal(y[t].view(np.uint32), ref.view(np.uint32)), (t, stats(oracle, y[t], ref))
+    ctx.set_accumulation(L.ACCUM_REFERENCE)
+    y = run_layer(ctx, x[:2], pages_dev, shared_dev, routes[:2], L.PAGE_MXFP4, hidden, inter)
+    for t in range(2):
+        ids, w = routes[t]
+        ref = oracle.moe_layer(x[t], [pages[i] for i in ids], w, shared, 0, hidden, inter)
+        assert np.array_equal(y[t].view(np.uint32), ref.view(np.uint32))
     ctx.set_accumulation(L.ACCUM_PAIRWISE)
 
 
@@ -761,6 +793,41 @@ def test_expert_parallel_exchange_in_the_layer_kernel(ctx, world):
     finally:
         for c in ranks:
             c.close()
+
+
+def test_expert_loader_ring_on_the_device(ctx):
+    """Five pages through a ring of two pinned staging buffers into a device pool
+    (expert_loader.rs:299-442): hidden until published, every page intact in its slot afterwards."""
+    from cuda import cudart
+
+    slot_bytes = 1 << 20
+    pool, ld = C.c_void_p(), C.c_void_p()
+    L.check(L.lib().s14_pool_create(ctx._h, 6, slot_bytes, C.byref(pool)))
+    try:
+        L.check(L.lib().s14_loader_create(pool, 2, C.byref(ld)))
+        g = synth.rng(55)
+        ids = [3, 8, 3, 1, 9, 4]
+        pages = {i: g.integers(0, 256, slot_bytes, dtype=np.uint8) for i in set(ids)}
+        keys = (L.ExpertKey * len(ids))(*[L.ExpertKey(2, 0, i) for i in ids])
+        datas = (C.c_void_p * len(ids))(*[pages[i].ctypes.data for i in ids])
+        sizes = (C.c_uint64 * len(ids))(*[slot_bytes] * len(ids))
+        slots = (C.c_uint32 * len(ids))()
+        L.check(L.lib().s14_loader_batch_enqueue_from_bufs(ld, keys, datas, sizes, len(ids), slots))
+        assert L.lib().s14_loader_stat_loads(ld) == 5 and slots[0] == slots[2]
+        found, slot = C.c_int32(), C.c_uint32()
+        L.check(L.lib().s14_pool_lookup(pool, L.ExpertKey(2, 0, 4), C.byref(found), C.byref(slot)))
+        assert found.value == 0  # the last wave is in flight: not visible yet
+        L.check(L.lib().s14_loader_wait_all(ld))
+        assert L.lib().s14_loader_in_flight(ld) == 0
+        for pos, i in enumerate(ids):
+            back = np.empty(slot_bytes, np.uint8)
+            (err,) = cudart.cudaMemcpy(back.ctypes.data, L.lib().s14_pool_slot_ptr(pool, slots[pos]), slot_bytes,
+                                       cudart.cudaMemcpyKind.cudaMemcpyDeviceToHost)
+            assert err == cudart.cudaError_t.cudaSuccess
+            assert np.array_equal(back, pages[i]), i
+    finally:
+        L.lib().s14_loader_destroy(ld)
+        L.lib().s14_pool_destroy(pool)
 
 
 def test_exchange_teardown_order_is_enforced():

@@ -1,5 +1,7 @@
 """Host-side contract of the S14 page pool and operator shapes, through the C ABI, without
 a GPU.  Each test restates a unit test of the reference (file:line in the docstring)."""
+import ctypes as C
+
 import numpy as np
 import pytest
 
@@ -323,3 +325,147 @@ def test_expert_page_from_tensors_matches_the_numpy_mirror_and_the_stated_offset
         assert np.array_equal(back, tensor_page)
     with pytest.raises(L.S14Error):
         L.check(L.lib().s14_mxfp4_expert_page_from_tensors(100, 256, None, None))
+
+
+# ---- ExpertLoader (expert_loader.rs:163-442): staging ring, per-entry fences, waves ------------
+
+def _host_pool(n_slots, slot_bytes):
+    pool = C.c_void_p()
+    L.check(L.lib().s14_pool_create_host(n_slots, slot_bytes, C.byref(pool)))
+    return pool
+
+
+def _loader(pool, depth):
+    ld = C.c_void_p()
+    L.check(L.lib().s14_loader_create(pool, depth, C.byref(ld)))
+    return ld
+
+
+def _page(tag, nbytes):
+    return (np.arange(nbytes, dtype=np.uint32) * 2654435761 + tag * 97).astype(np.uint8)
+
+
+def _slot_bytes_of(pool, slot, nbytes):
+    ptr = L.lib().s14_pool_slot_ptr(pool, slot)
+    return np.ctypeslib.as_array(C.cast(ptr, C.POINTER(C.c_uint8)), shape=(nbytes,)).copy()
+
+
+def _lookup(pool, key):
+    slot = C.c_uint32()
+    found = C.c_int32()
+    L.check(L.lib().s14_pool_lookup(pool, key, C.byref(found), C.byref(slot)))
+    return slot.value if found.value else None
+
+
+def test_loader_page_is_hidden_until_its_transfer_is_complete(cuda_lib):
+    slot_bytes = 256
+    pool, ld = _host_pool(4, slot_bytes), None
+    try:
+        ld = _loader(pool, 2)
+        key = L.ExpertKey(3, 0, 17)
+        data = _page(1, slot_bytes)
+        slot = C.c_uint32()
+        L.check(L.lib().s14_loader_enqueue_from_buf(ld, key, data.ctypes.data, data.size, C.byref(slot)))
+        assert L.lib().s14_loader_in_flight(ld) == 1
+        assert _lookup(pool, key) is None  # Loading: not visible
+        L.check(L.lib().s14_loader_wait_all(ld))
+        assert L.lib().s14_loader_in_flight(ld) == 0
+        assert _lookup(pool, key) == slot.value
+        assert np.array_equal(_slot_bytes_of(pool, slot.value, slot_bytes), data)
+        # a page that is Ready is not loaded again
+        again = C.c_uint32()
+        L.check(L.lib().s14_loader_enqueue_from_buf(ld, key, data.ctypes.data, data.size, C.byref(again)))
+        assert again.value == slot.value and L.lib().s14_loader_stat_loads(ld) == 1
+        assert L.lib().s14_loader_stat_bytes(ld) == slot_bytes
+    finally:
+        L.lib().s14_loader_destroy(ld)
+        L.lib().s14_pool_destroy(pool)
+
+
+def test_loader_reclaims_a_ring_entry_before_reusing_its_staging_buffer(cuda_lib):
+    """Three pages through a ring of two: the third takes the first entry again, which publishes the
+    first page; every page arrives intact although the host engine copies as late as the wait."""
+    slot_bytes = 128
+    pool, ld = _host_pool(8, slot_bytes), None
+    try:
+        ld = _loader(pool, 2)
+        keys = [L.ExpertKey(0, 0, i) for i in range(3)]
+        pages = [_page(10 + i, slot_bytes) for i in range(3)]
+        slots = []
+        for k, p in zip(keys, pages):
+            s = C.c_uint32()
+            L.check(L.lib().s14_loader_enqueue_from_buf(ld, k, p.ctypes.data, p.size, C.byref(s)))
+            slots.append(s.value)
+        assert _lookup(pool, keys[0]) == slots[0]      # published when its entry was reclaimed
+        assert _lookup(pool, keys[1]) is None and _lookup(pool, keys[2]) is None
+        assert L.lib().s14_loader_in_flight(ld) == 2
+        # asking for a page that is in flight settles it instead of loading it twice
+        s = C.c_uint32()
+        L.check(L.lib().s14_loader_enqueue_from_buf(ld, keys[1], pages[1].ctypes.data, slot_bytes, C.byref(s)))
+        assert s.value == slots[1] and _lookup(pool, keys[1]) == slots[1]
+        L.check(L.lib().s14_loader_wait_all(ld))
+        for k, p, sl in zip(keys, pages, slots):
+            assert _lookup(pool, k) == sl
+            assert np.array_equal(_slot_bytes_of(pool, sl, slot_bytes), p)
+        assert L.lib().s14_loader_stat_loads(ld) == 3
+    finally:
+        L.lib().s14_loader_destroy(ld)
+        L.lib().s14_pool_destroy(pool)
+
+
+def test_loader_batch_runs_in_waves_no_deeper_than_the_ring(cuda_lib):
+    """Seven requests with two duplicates through a ring of two (expert_loader.rs:299-358): five
+    loads, every input gets its page's slot, all but the last wave are Ready on return, and no page
+    was overwritten in a staging buffer."""
+    slot_bytes = 64
+    pool, ld = _host_pool(8, slot_bytes), None
+    try:
+        ld = _loader(pool, 2)
+        ids = [4, 1, 4, 9, 2, 1, 7]
+        keys = (L.ExpertKey * len(ids))(*[L.ExpertKey(5, 0, i) for i in ids])
+        pages = {i: _page(i, slot_bytes) for i in set(ids)}
+        datas = (C.c_void_p * len(ids))(*[pages[i].ctypes.data for i in ids])
+        sizes = (C.c_uint64 * len(ids))(*[slot_bytes] * len(ids))
+        slots = (C.c_uint32 * len(ids))()
+        L.check(L.lib().s14_loader_batch_enqueue_from_bufs(ld, keys, datas, sizes, len(ids), slots))
+        assert L.lib().s14_loader_stat_loads(ld) == 5
+        assert slots[0] == slots[2] and slots[1] == slots[5] and len({slots[i] for i in range(len(ids))}) == 5
+        assert L.lib().s14_loader_in_flight(ld) == 1  # the last wave (one page) is still in flight
+        assert _lookup(pool, L.ExpertKey(5, 0, 7)) is None and _lookup(pool, L.ExpertKey(5, 0, 2)) is not None
+        L.check(L.lib().s14_loader_wait_all(ld))
+        for pos, i in enumerate(ids):
+            assert np.array_equal(_slot_bytes_of(pool, slots[pos], slot_bytes), pages[i]), i
+    finally:
+        L.lib().s14_loader_destroy(ld)
+        L.lib().s14_pool_destroy(pool)
+
+
+def test_loader_refusals_leave_the_pool_as_it_was(cuda_lib):
+    slot_bytes = 64
+    pool, ld = _host_pool(2, slot_bytes), None
+    try:
+        ld = _loader(pool, 2)
+        big = _page(1, 2 * slot_bytes)
+        s = C.c_uint32()
+        rc = L.lib().s14_loader_enqueue_from_buf(ld, L.ExpertKey(0, 0, 1), big.ctypes.data, big.size, C.byref(s))
+        assert rc == L.ERR_POOL and L.lib().s14_pool_n_loaded(pool) == 0 and L.lib().s14_loader_in_flight(ld) == 0
+        # more distinct pages than the pool has slots: refused before anything is issued
+        ids = [1, 2, 3]
+        keys = (L.ExpertKey * 3)(*[L.ExpertKey(0, 0, i) for i in ids])
+        pages = [_page(i, slot_bytes) for i in ids]
+        datas = (C.c_void_p * 3)(*[p.ctypes.data for p in pages])
+        sizes = (C.c_uint64 * 3)(*[slot_bytes] * 3)
+        slots = (C.c_uint32 * 3)()
+        rc = L.lib().s14_loader_batch_enqueue_from_bufs(ld, keys, datas, sizes, 3, slots)
+        assert rc == L.ERR_POOL and b"distinct experts" in L.lib().s14_last_error()
+        assert L.lib().s14_loader_stat_loads(ld) == 0 and L.lib().s14_pool_n_loaded(pool) == 0
+        # a loader on a bookkeeping-only pool is refused
+        bare = C.c_void_p()
+        L.check(L.lib().s14_pool_create(None, 2, slot_bytes, C.byref(bare)))
+        none = C.c_void_p()
+        assert L.lib().s14_loader_create(bare, 2, C.byref(none)) == L.ERR_POOL
+        L.lib().s14_pool_destroy(bare)
+        assert L.lib().s14_loader_create(pool, 0, C.byref(none)) == L.ERR_POOL
+    finally:
+        L.lib().s14_loader_destroy(ld)
+        L.lib().s14_pool_destroy(pool)
