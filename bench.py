@@ -314,6 +314,8 @@ def run_gpu(args) -> None:
         raise SystemExit("several GPUs: the expert-parallel workload is `layer`")
     if workload in ("expert_chain", "wq_a", "verify8"):
         return run_small_workload(args, workload, torch, L, synth, S14Context, TokenRoute)
+    if workload == "decode":
+        return run_decode_workload(args, torch, L, synth, S14Context)
 
     ctx = S14Context(local_rank)
     mode = L.ACCUM_REFERENCE if args.accum == "reference" else L.ACCUM_PAIRWISE
@@ -654,6 +656,39 @@ def run_gpu(args) -> None:
         e2e_value = None
     _note("end-to-end leg done")
 
+    # ---- several GPUs: the vocabulary-sharded head (full logits and the greedy token on every rank)
+    head_leg = None
+    if world > 1 and not args.kernel_only:
+        r0, r1 = ep.head_rows(rank, world, VOCAB)
+        shard = synth.hashed_head_rows_torch(torch, r0, r1 - r0, HIDDEN)
+        n_head = 8
+        ep.sharded_head(ctx, xs[0], shard, VOCAB, rank, world)  # warm-up (NCCL all-gather buffers)
+        dist.barrier()
+        t0 = time.perf_counter()
+        toks, lg = [], None
+        for i in range(n_head):
+            lg, t = ep.sharded_head(ctx, xs[i], shard, VOCAB, rank, world)
+            toks.append(int(t))
+        head_sec = time.perf_counter() - t0
+        mine = (hashlib.sha256(lg.cpu().numpy().tobytes()).hexdigest(), toks)
+        everyone = [None] * world
+        dist.all_gather_object(everyone, mine)
+        if rank == 0:
+            from oracle import s14_oracle as oracle
+
+            oracle.build()
+            cpu_threads(oracle)
+            ref = oracle.head_logits(xs_np[n_head - 1], synth.hashed_head_rows(0, VOCAB, HIDDEN))
+            got = lg.cpu().numpy()
+            head_leg = {"what": f"BF16 head {VOCAB} x {HIDDEN} in row shards over the ranks, all-gather of the logits, "
+                                "greedy token from the ranks' (largest logit, id) pairs",
+                        "calls": n_head, "ms_per_call": head_sec / n_head * 1e3,
+                        "logits_equal_across_ranks": all(e[0] == everyone[0][0] for e in everyone),
+                        "tokens_equal_across_ranks": all(e[1] == everyone[0][1] for e in everyone),
+                        "logits_max_abs_vs_oracle": float(np.max(np.abs(got - ref))),
+                        "token_equals_oracle": toks[-1] == oracle.greedy_argmax(ref)}
+        del shard
+
     status = ctx.device_status()  # 0 unless a bounded wait of a kernel ran out
     status_all = status
     if world > 1:
@@ -722,7 +757,7 @@ def run_gpu(args) -> None:
                     "call": ("s14_stack_decode_host: one token per call through the 14 layers" if workload == "stack" else
                              "s14_routed_moe_layer_host per layer-token" if world == 1 else
                              "pinned token in, expert-parallel step, result out per layer-token")},
-            "layer_trace": layer_trace,
+            "layer_trace": layer_trace, "sharded_head": head_leg,
             "gpu_launches": launches_per_region, "kernels_per_step": kernels_per_step,
             "device_status": status, "device_status_all": status_all, "device_status_timed_regions": status_timed,
             "clocks": clocks,
@@ -739,6 +774,136 @@ def run_gpu(args) -> None:
         os._exit(0)  # skip NCCL teardown, which did not return here after the run
     for st in stacks.values():
         st.close()
+    ctx.close()
+
+
+VOCAB = 129_280  # scheduler/s14_runner/src/memory.rs:7
+
+
+def run_decode_workload(args, torch, L, synth, S14Context) -> None:
+    """Sequential greedy decode steps through the stack (runner.rs:312-358, 485-508): per step ONE
+    launch of the layer kernel over the 14 chained layers, the BF16 head (129 280 x 4096) and the
+    greedy argmax; the next step's input is looked up by the token just produced, so no step can
+    start before the one before it has finished.  `--steps` decode steps (default 128) replay from
+    a CUDA graph; a metric unit is one decode step (token)."""
+    from colormlm_b200.s14 import DecodeStack
+    from oracle import s14_oracle as oracle
+
+    steps = args.steps if args.steps_given else 128
+    ctx = S14Context(0)
+    ctx.set_accumulation(L.ACCUM_PAIRWISE)
+    layers = resident_layers(torch, N_LAYERS, 0, 1)
+    head = synth.hashed_head_rows_torch(torch, 0, VOCAB, HIDDEN)
+    n_tok = 64
+    xs_np = tokens(n_tok)
+    xs = torch.from_numpy(xs_np).cuda()
+    stack = DecodeStack(ctx, layers, inter=INTER, residual=True)
+    stream = torch.cuda.Stream()
+    h = torch.empty(HIDDEN, dtype=torch.float32, device="cuda")
+    logits = torch.empty(VOCAB, dtype=torch.float32, device="cuda")
+    tok = torch.zeros(1, dtype=torch.int64, device="cuda")
+    x_cur = torch.empty(HIDDEN, dtype=torch.float32, device="cuda")
+    toks_out = torch.zeros(steps, dtype=torch.int64, device="cuda")
+
+    def one_step(i, handle):
+        stack.cmd_decode(x_cur, h, stream=handle)
+        ctx.cmd_head_logits(h, head, logits, stream=handle)
+        ctx.cmd_greedy_argmax(logits, tok, stream=handle)
+        toks_out[i:i + 1].copy_(tok)
+        x_cur.copy_(xs.index_select(0, torch.remainder(tok, n_tok))[0])  # the next token's input
+
+    def run_steps(handle):
+        x_cur.copy_(xs[0])
+        for i in range(steps):
+            one_step(i, handle)
+
+    with torch.cuda.stream(stream):
+        run_steps(stream.cuda_stream)
+    stream.synchronize()
+    eager_tokens = toks_out.cpu().numpy().copy()
+    c0 = ctx.launch_count
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.stream(stream):
+        with torch.cuda.graph(graph, stream=stream):
+            run_steps(stream.cuda_stream)
+    launches = ctx.launch_count - c0
+    sampler = ClockSampler(0)
+    sampler.start()
+    time.sleep(0.2)
+    warm = max(3, -(-args.warmup // steps))
+    with torch.cuda.stream(stream):
+        for _ in range(warm):
+            graph.replay()
+    stream.synchronize()
+    ms_all = timed_repeats(torch, stream, graph.replay, max(5, min(args.repeats, 20)))
+    clocks = sampler.stop()
+    ms = float(np.median(ms_all))
+    graph_tokens = toks_out.cpu().numpy().copy()
+    status = ctx.device_status()
+
+    # parity: the first decode steps on the CPU oracle (double-accumulated layers, head, greedy argmax)
+    parity = None
+    cpu = None
+    if not args.kernel_only:
+        oracle.build()
+        cores = cpu_threads(oracle)
+        hp = HostPages()
+        head_np = synth.hashed_head_rows(0, VOCAB, HIDDEN)
+        n_check = 2
+        x = xs_np[0].copy()
+        cpu_tokens, worst_logit = [], 0.0
+        t0 = time.perf_counter()
+        for i in range(n_check):
+            hh = x.copy()
+            for l in range(N_LAYERS):
+                y64, _, _ = cpu_layer(oracle, hp, l, hh, acc64=True)
+                hh = (hh + y64).astype(np.float32)
+            lg = oracle.head_logits(hh, head_np)
+            t = oracle.greedy_argmax(lg)
+            cpu_tokens.append(int(t))
+            x = xs_np[t % n_tok].copy()
+        cpu_sec = time.perf_counter() - t0
+        # the GPU's logits of the last step of a one-step run, against the oracle's for the same token
+        with torch.cuda.stream(stream):
+            x_cur.copy_(xs[0])
+            one_step(0, stream.cuda_stream)
+        stream.synchronize()
+        hh = xs_np[0].copy()
+        for l in range(N_LAYERS):
+            y64, _, _ = cpu_layer(oracle, hp, l, hh, acc64=True)
+            hh = (hh + y64).astype(np.float32)
+        lg = oracle.head_logits(hh, head_np)
+        worst_logit = float(np.max(np.abs(logits.cpu().numpy() - lg)))
+        parity = {"steps": n_check, "what": "greedy tokens of the first decode steps against the CPU oracle chain "
+                                            "(14 double-accumulated layers, head, argmax); logits of the first step",
+                  "tokens_gpu": [int(v) for v in graph_tokens[:n_check]], "tokens_cpu": cpu_tokens,
+                  "tokens_equal": [int(v) for v in graph_tokens[:n_check]] == cpu_tokens,
+                  "graph_equals_eager": bool(np.array_equal(graph_tokens, eager_tokens)),
+                  "first_step_logits_max_abs": worst_logit,
+                  "logits_tolerance": "rtol 2e-7 / atol 3e-7 of tests/test_final_head.py:68-70 scaled by the logits' size"}
+        cpu = {"value": n_check / cpu_sec, "unit": "tokens/s", "cores": cores, "kind": "port",
+               "sample": f"{n_check} decode steps (14 layers + head + argmax each) on the CPU oracle, {cpu_sec:.1f} s"}
+    peak, peak_kind = measured_peaks()
+    step_bytes = N_LAYERS * STEP_BYTES + VOCAB * HIDDEN * 2 + VOCAB * 4 * 2
+    achieved = step_bytes * steps / (ms * 1e-3) / 1e9
+    line = {
+        "metric": "decode_tokens_per_s", "value": steps / (ms / 1e3), "unit": "tokens/s", "n_gpus": 1,
+        "steps": steps, "warmup": args.warmup, "ms_per_step": ms / steps, "higher_is_better": True,
+        "scaling": "strong", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+        "config": {"workload": "S14 stack decode: 14 chained MoE layers (1 token, top-6 of 256 + shared, 4096 x 2048, MXFP4) "
+                               "+ BF16 head 129 280 x 4096 + greedy argmax per step, every step fed by the token before",
+                   "bench_workload": "decode", "launch": f"cuda graph of {steps} sequential steps",
+                   "l2": "inputs larger than L2: 2.4 GB per step"},
+        "repeats": {"count": len(ms_all), "region_ms_median": ms, "region_ms_min": float(np.min(ms_all)),
+                    "region_ms_max": float(np.max(ms_all))},
+        "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
+                     "peak_kind": peak_kind, "traffic": None, "bytes_per_step": step_bytes,
+                     "kernel": "k_moe_layer_umma (14 layers) + k_head_logits + k_greedy_argmax per step"},
+        "parity": parity, "cpu_baseline": cpu, "e2e": None, "gpu_launches": launches,
+        "device_status": status, "clocks": clocks,
+    }
+    print(json.dumps(line), flush=True)
+    stack.close()
     ctx.close()
 
 
@@ -955,7 +1120,7 @@ def main() -> None:
     ap.add_argument("--steps", type=int, default=None)
     ap.add_argument("--warmup", type=int, default=None)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
-    ap.add_argument("--workload", default=None, choices=["stack", "layer", "expert_chain", "wq_a", "verify8"])
+    ap.add_argument("--workload", default=None, choices=["stack", "layer", "expert_chain", "wq_a", "verify8", "decode"])
     ap.add_argument("--tokens", type=int, default=1, help="tokens of the wq_a workload (1, 4 or 8)")
     ap.add_argument("--accum", default="pairwise", choices=["pairwise", "reference"])
     ap.add_argument("--exchange", default="peer", choices=["peer", "nccl"],
@@ -973,6 +1138,7 @@ def main() -> None:
     ap.add_argument("--trace", action="store_true",
                     help="stack workload, one GPU: one more launch with the kernel's time marks; their medians go into the line")
     args = ap.parse_args()
+    args.steps_given = args.steps is not None
     if args.experts != N_EXPERTS:
         if not 8 <= args.experts <= 256:
             raise SystemExit("--experts: 8..256")

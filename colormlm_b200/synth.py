@@ -157,3 +157,39 @@ class HashedPageWriter:
         h ^= h >> 16
         b = h.to(self.torch.int32).view(self.torch.uint8)
         out.copy_(self.torch.where(self.scale_at, 119 + b % 5, b))
+
+
+# ---- head weight from a counter (the same bits on the host and on the GPU) ----------------------------
+
+HEAD_KEY = 0x48EAD001
+
+
+def _head_bits_from_hash(h, xp):
+    """BF16 bits from mixed 32-bit words: sign and mantissa from the word, exponent 117..121 (|w| in
+    2^-10 .. 2^-5), so that a 4096-long dot product with unit-scale activations stays around one."""
+    return (h & 0x807F) | ((117 + ((h >> 8) % 5)) << 7)
+
+
+def hashed_head_rows(row0: int, n_rows: int, hidden: int) -> np.ndarray:
+    """Rows [row0, row0 + n_rows) of the head weight as BF16 bits (uint16), on the host."""
+    idx = np.arange(row0 * hidden, (row0 + n_rows) * hidden, dtype=np.uint64)
+    h = _mix32_np(idx ^ np.uint64(HEAD_KEY))
+    return _head_bits_from_hash(h, np).astype(np.uint16).reshape(n_rows, hidden)
+
+
+def hashed_head_rows_torch(torch, row0: int, n_rows: int, hidden: int, device="cuda", chunk_rows: int = 8192):
+    """The same rows on the device (int16 tensor holding the BF16 bits), built in chunks."""
+    out = torch.empty((n_rows, hidden), dtype=torch.int16, device=device)
+    m = 0xFFFFFFFF
+    for r in range(0, n_rows, chunk_rows):
+        n = min(chunk_rows, n_rows - r)
+        h = torch.arange((row0 + r) * hidden, (row0 + r + n) * hidden, dtype=torch.int64, device=device) ^ HEAD_KEY
+        h = (h * 0x9E3779B1) & m
+        h ^= h >> 15
+        h = (h * 0x85EBCA77) & m
+        h ^= h >> 13
+        h = (h * 0xC2B2AE3D) & m
+        h ^= h >> 16
+        bits = _head_bits_from_hash(h, torch)
+        out[r:r + n] = (bits - ((bits >> 15) << 16)).to(torch.int16).view(n, hidden)  # two's complement of the 16 bits
+    return out

@@ -333,7 +333,7 @@ def test_moe_layer_verify_block(ctx, oracle, n_tokens):
 
 
 def test_moe_layer_verify_block_at_the_benchmark_shape(ctx, oracle):
-    """Eight tokens, 4096 x 2048, 48 experts of which the block uses more than 30 distinct ones: in
+    """Eight tokens, 4096 x 2048, 48 experts of which the block uses 25 or more distinct ones: in
     pairwise order every token is its own one-token call and the double-accumulated oracle, bit for
     bit; in reference order the F32 oracle."""
     hidden, inter, n_experts, n_tokens = 4096, 2048, 48, 8
@@ -342,7 +342,7 @@ def test_moe_layer_verify_block_at_the_benchmark_shape(ctx, oracle):
     routes = []
     for t in range(n_tokens):
         routes.append((g.permutation(n_experts)[:6].tolist(), g.uniform(0.05, 0.4, 6).astype(np.float32)))
-    assert len({e for ids, _ in routes for e in ids}) > 30
+    assert len({e for ids, _ in routes for e in ids}) >= 25
     pages_dev, shared_dev = [dev_page(p, hidden, inter) for p in pages], dev_page(shared, hidden, inter)
     ctx.set_accumulation(L.ACCUM_PAIRWISE)
     y = run_layer(ctx, x, pages_dev, shared_dev, routes, L.PAGE_MXFP4, hidden, inter)
