@@ -770,25 +770,35 @@ k_head_logits(const float *__restrict__ x, const uint16_t *__restrict__ w, float
         double acc[NT];
 #pragma unroll
         for (int t = 0; t < NT; ++t) acc[t] = 0.0;
-        for (uint32_t p = lane; p < (hidden >> 3); p += 32u) {
-            const uint4 q = ldg_stream(row + p);
-            const uint32_t wd[4] = {q.x, q.y, q.z, q.w};
-            float wf[8];
+        // four 16-byte loads of the row in flight per lane (the row is read once, from HBM); the sums
+        // are taken in the order of the chunks, as before
+        for (uint32_t p0 = lane; p0 < (hidden >> 3); p0 += 128u) {
+            uint4 q4[4];
 #pragma unroll
-            for (int i = 0; i < 4; ++i) {
-                wf[i * 2] = __uint_as_float(wd[i] << 16);
-                wf[i * 2 + 1] = __uint_as_float(wd[i] & 0xffff0000u);
-            }
+            for (int u = 0; u < 4; ++u)
+                q4[u] = (p0 + 32u * u < (hidden >> 3)) ? ldg_stream(row + p0 + 32u * u) : make_uint4(0u, 0u, 0u, 0u);
 #pragma unroll
-            for (int t = 0; t < NT; ++t) {
-                const float4 xa = __ldg(reinterpret_cast<const float4 *>(x + (size_t)t * hidden + p * 8));
-                const float4 xb = __ldg(reinterpret_cast<const float4 *>(x + (size_t)t * hidden + p * 8 + 4));
-                float2 part = make_float2(0.f, 0.f);
-                part = __ffma2_rn(make_float2(wf[0], wf[1]), make_float2(xa.x, xa.y), part);
-                part = __ffma2_rn(make_float2(wf[2], wf[3]), make_float2(xa.z, xa.w), part);
-                part = __ffma2_rn(make_float2(wf[4], wf[5]), make_float2(xb.x, xb.y), part);
-                part = __ffma2_rn(make_float2(wf[6], wf[7]), make_float2(xb.z, xb.w), part);
-                acc[t] += (double)part.x + (double)part.y;
+            for (int u = 0; u < 4; ++u) {
+                const uint32_t p = p0 + 32u * u;
+                if (p >= (hidden >> 3)) break;
+                const uint32_t wd[4] = {q4[u].x, q4[u].y, q4[u].z, q4[u].w};
+                float wf[8];
+#pragma unroll
+                for (int i = 0; i < 4; ++i) {
+                    wf[i * 2] = __uint_as_float(wd[i] << 16);
+                    wf[i * 2 + 1] = __uint_as_float(wd[i] & 0xffff0000u);
+                }
+#pragma unroll
+                for (int t = 0; t < NT; ++t) {
+                    const float4 xa = __ldg(reinterpret_cast<const float4 *>(x + (size_t)t * hidden + p * 8));
+                    const float4 xb = __ldg(reinterpret_cast<const float4 *>(x + (size_t)t * hidden + p * 8 + 4));
+                    float2 part = make_float2(0.f, 0.f);
+                    part = __ffma2_rn(make_float2(wf[0], wf[1]), make_float2(xa.x, xa.y), part);
+                    part = __ffma2_rn(make_float2(wf[2], wf[3]), make_float2(xa.z, xa.w), part);
+                    part = __ffma2_rn(make_float2(wf[4], wf[5]), make_float2(xb.x, xb.y), part);
+                    part = __ffma2_rn(make_float2(wf[6], wf[7]), make_float2(xb.z, xb.w), part);
+                    acc[t] += (double)part.x + (double)part.y;
+                }
             }
         }
 #pragma unroll
@@ -810,12 +820,31 @@ k_greedy_argmax(const float *__restrict__ logits, uint32_t vocab, int64_t *__res
     float best = -INFINITY;
     uint32_t best_i = 0xffffffffu;
     bool nan = false;
-    for (uint32_t i = threadIdx.x; i < vocab; i += blockDim.x) {
-        const float v = logits[i];
-        nan |= (v != v);
-        if (best_i == 0xffffffffu || v > best) {
-            best = v;
-            best_i = i;
+    // four logits per load where the array allows it (a thread meets its indices in ascending order, so
+    // "first largest" stays "lowest index" within a thread)
+    const bool vec = (vocab & 3u) == 0u && (reinterpret_cast<uintptr_t>(logits) & 15u) == 0u;
+    if (vec) {
+        for (uint32_t i = threadIdx.x * 4u; i < vocab; i += blockDim.x * 4u) {
+            const float4 q = *reinterpret_cast<const float4 *>(logits + i);
+            const float vs[4] = {q.x, q.y, q.z, q.w};
+#pragma unroll
+            for (uint32_t k = 0; k < 4; ++k) {
+                const float v = vs[k];
+                nan |= (v != v);
+                if (best_i == 0xffffffffu || v > best) {
+                    best = v;
+                    best_i = i + k;
+                }
+            }
+        }
+    } else {
+        for (uint32_t i = threadIdx.x; i < vocab; i += blockDim.x) {
+            const float v = logits[i];
+            nan |= (v != v);
+            if (best_i == 0xffffffffu || v > best) {
+                best = v;
+                best_i = i;
+            }
         }
     }
     if (nan) snan = 1;
