@@ -88,6 +88,20 @@ def decode_step_fused(ctx, x, layer_state: dict, y, *, layer: int, world: int, i
                                 ids_out=ids, weights_out=weights, stream=stream)
 
 
+def verify_block_fused(ctx, xs, layer_state: dict, ys, *, layer: int, world: int, inter: int, ids=None, weights=None,
+                       stream: Optional[int] = None) -> None:
+    """A block of K tokens (a verify block, K <= 8) through one expert-parallel layer: xs, ys are
+    [K, hidden]; ids, weights [K, top_k] or None.  Tokens are replicated, experts are sharded: every rank
+    holds all K tokens (16 KB each), routes each of them itself and computes the experts it owns, so no
+    token has to be dispatched; the experts' outputs of a token are combined inside its step's kernel.
+    K steps, one launch each, on every rank; a token's result is that of its own decode step."""
+    for t in range(xs.shape[0]):
+        ctx.cmd_routed_moe_layer_ep(xs[t], ys[t], layer_state["wr"], layer_state["bias"], layer_state["table"],
+                                    layer_state["shared"], inter, shared_owner=shared_owner(layer, world),
+                                    ids_out=None if ids is None else ids[t],
+                                    weights_out=None if weights is None else weights[t], stream=stream)
+
+
 # ---- vocabulary-sharded LM head ---------------------------------------------------------------
 # The head weight [vocab, hidden] BF16 is split by rows: rank r holds rows [vocab r / G, vocab (r+1) / G)
 # (final_head.py:113-149 computes all rows on one device; the runner's contract wants the full logits,

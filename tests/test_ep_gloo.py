@@ -149,3 +149,28 @@ def test_no_rank_frees_its_exchange_buffer_before_every_rank_has_disconnected(tm
     mp.spawn(_teardown_worker, args=(world, port, str(tmp_path)), nprocs=world, join=True)
     for r in range(world):
         assert int(open(tmp_path / f"rank{r}.txt").read()) == world
+
+
+def test_verify_block_is_one_expert_parallel_step_per_token():
+    """ep.verify_block_fused: K tokens are K steps of the fused exchange, in token order, each with the
+    token's own rows of the outputs and the layer's shared-expert owner (tokens are replicated, experts
+    are sharded, so nothing is dispatched)."""
+    sys.path.insert(0, ROOT)
+    from colormlm_b200 import ep
+
+    calls = []
+
+    class Ctx:
+        def cmd_routed_moe_layer_ep(self, x, y, wr, bias, table, shared, inter, **kw):
+            calls.append((x, y, wr, bias, table, shared, inter, kw))
+
+    xs, ys = torch.arange(12.0).reshape(3, 4), torch.zeros(3, 4)
+    ids, wts = torch.zeros((3, 6), dtype=torch.int32), torch.zeros((3, 6))
+    state = {"wr": "WR", "bias": "B", "table": "T", "shared": 77}
+    ep.verify_block_fused(Ctx(), xs, state, ys, layer=5, world=4, inter=2048, ids=ids, weights=wts, stream=9)
+    assert len(calls) == 3
+    for t, (x, y, wr, bias, table, shared, inter, kw) in enumerate(calls):
+        assert torch.equal(x, xs[t]) and y.data_ptr() == ys[t].data_ptr()
+        assert (wr, bias, table, shared, inter) == ("WR", "B", "T", 77, 2048)
+        assert kw["shared_owner"] == ep.shared_owner(5, 4) and kw["stream"] == 9
+        assert kw["ids_out"].data_ptr() == ids[t].data_ptr() and kw["weights_out"].data_ptr() == wts[t].data_ptr()
