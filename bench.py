@@ -659,6 +659,25 @@ def run_gpu(args) -> None:
         e2e_value = None
     _note("end-to-end leg done")
 
+    # ---- several GPUs: what every rank streams in a region (the pages of the experts it owns among the
+    # steps' routes, its router weights, the token), from the routes of one eager pass over the region
+    rank_bytes = None
+    if world > 1 and peer_exchange:
+        ids_all = torch.zeros((args.steps, TOP_K), dtype=torch.int32, device="cuda")
+        dist.barrier()
+        with torch.cuda.stream(stream):
+            for i in range(args.steps):
+                ep.decode_step_fused(ctx, xs[i % n_tok], ep_states[i % n_layers], ys[i % n_layers], layer=i % n_layers,
+                                     world=world, inter=INTER, ids=ids_all[i], stream=stream.cuda_stream)
+        stream.synchronize()
+        ids_np = ids_all.cpu().numpy()
+        owned = int(np.sum(ids_np % world == rank)) + sum(1 for i in range(args.steps) if ep.shared_owner(i % n_layers, world) == rank)
+        mine = owned * PAGE_BYTES + args.steps * (ROUTER_BYTES + 2 * HIDDEN * 4)
+        t = torch.tensor([mine], dtype=torch.int64, device="cuda")
+        gathered = [torch.zeros_like(t) for _ in range(world)]
+        dist.all_gather(gathered, t)
+        rank_bytes = [int(g.item()) for g in gathered]
+
     # ---- several GPUs: the vocabulary-sharded head (full logits and the greedy token on every rank)
     head_leg = None
     if world > 1 and not args.kernel_only:
@@ -715,6 +734,8 @@ def run_gpu(args) -> None:
                              f"{sec:.1f} s of CPU work"}
         kernels_per_step = launches_per_region / args.steps
         achieved = STEP_BYTES * args.steps / (ms * 1e-3) / 1e9
+        if world > 1:  # one rank's memory system: the busiest rank's bytes over the same time
+            achieved = (max(rank_bytes) if rank_bytes else STEP_BYTES * args.steps / world) / (ms * 1e-3) / 1e9
         # several GPUs: a rank streams the pages it owns; the busiest rank bounds the step
         per_rank = None
         if world > 1:
@@ -744,9 +765,13 @@ def run_gpu(args) -> None:
                          "kernel": ("k_moe_layer_umma: expert scores + routes, 7 MXFP4 experts (up projections, SwiGLU, "
                                     "down projection), ordered mix" + (", 14 layers per launch" if workload == "stack" else "")
                                     if args.accum == "pairwise" else "reference-order layer kernels (router, up, down, mix)"),
-                         "achieved": achieved if world == 1 else None, "peak": peak, "unit": "GB/s",
-                         "frac": achieved / peak if world == 1 else None,
-                         "frac_of_nominal_8000": achieved / 8000.0 if world == 1 else None,
+                         "achieved": achieved, "peak": peak, "unit": "GB/s",
+                         "frac": achieved / peak,
+                         "frac_of_nominal_8000": achieved / 8000.0,
+                         **({} if world == 1 else {
+                             "what": "the busiest rank: the bytes it streams in a region (pages of the experts it owns "
+                                     "among the routes, its router weights, the tokens) over the region's time",
+                             "per_rank_bytes_per_step": None if rank_bytes is None else [b / args.steps for b in rank_bytes]}),
                          "peak_kind": peak_kind, "traffic": NCU_TRAFFIC_BYTES,
                          "bytes_per_launch": STEP_BYTES * (N_LAYERS if workload == "stack" else 1),
                          "ms_per_launch": ms / args.steps * (N_LAYERS if workload == "stack" else 1),
