@@ -1297,7 +1297,9 @@ k_moe_layer_umma(const JobTable *__restrict__ dev_table, const __grid_constant__
                                         }
                                         float out = acc;
                                         if (residual)
-                                            out = __fadd_rn(l == 0u ? __ldcg(x + n) : __uint_as_float((uint32_t)x_words[(size_t)par * kMaxHidden + n]), acc);
+                                            out = __fadd_rn(l == 0u ? __ldcg(x + n)
+                                                            : __uint_as_float((uint32_t)ld_relaxed_gpu(x_words + (size_t)par * kMaxHidden + n)),
+                                                    acc);  // (from the L2: the L1 may hold this word's value of two layers ago)
                                         if (l + 1u == L) y[n] = out;
                                         else st_relaxed_gpu(x_words + (size_t)(par ^ 1u) * kMaxHidden + n, ((unsigned long long)(want + 1u) << 32) | __float_as_uint(out));
                                         if (s_layer[par].y_out) s_layer[par].y_out[n] = acc;
