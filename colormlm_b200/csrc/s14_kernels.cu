@@ -186,6 +186,77 @@ k_fp8_matvec_pairwise(const float *__restrict__ x, const uint8_t *__restrict__ w
     }
 }
 
+// The same product for a block of tokens and a matrix of few rows (the 1024 x 4096 projection of
+// the decode step, 1 / 4 / 8 tokens): with a warp per row every warp would fetch the activations of
+// all tokens for itself (134 MB of L2 reads for 4 MB of weights at 8 tokens).  Here a CTA of sixteen
+// warps takes eight rows, two warps per row (the halves of K), the tokens' activations are staged
+// once per CTA in shared memory, a 16-byte piece of weights is decoded once for all tokens, and the
+// two halves of a row are added through shared memory.  k a multiple of 32, 16-byte aligned operands.
+constexpr uint32_t kFp8BlockRows = 8, kFp8BlockThreads = 512;
+template <int NT, bool F32_SCALE>
+__global__ void __launch_bounds__(kFp8BlockThreads)
+k_fp8_matvec_block(const float *__restrict__ x, const uint8_t *__restrict__ w, const void *__restrict__ scale,
+                   float *__restrict__ y, uint32_t n_rows, uint32_t k) {
+    extern __shared__ __align__(16) float sx[];  // [NT][k]
+    __shared__ double red[kFp8BlockRows][NT];
+    const uint32_t lane = threadIdx.x & 31u, warp = threadIdx.x >> 5;
+    const uint32_t r = warp & (kFp8BlockRows - 1u), half = warp >> 3;
+    const uint32_t n = blockIdx.x * kFp8BlockRows + r;
+    // staged as [token][quarter of a piece][piece]: the lanes of a warp, which hold consecutive pieces,
+    // then read consecutive 16 bytes (no bank conflicts)
+    const uint32_t pieces = k >> 4, per = pieces >> 1;
+    for (uint32_t i = threadIdx.x; i < (NT * k) >> 2; i += kFp8BlockThreads) {
+        const uint32_t t = i / (k >> 2), j = i % (k >> 2);
+        reinterpret_cast<float4 *>(sx)[(size_t)t * (k >> 2) + (j & 3u) * pieces + (j >> 2)] =
+            __ldg(reinterpret_cast<const float4 *>(x) + i);
+    }
+    __syncthreads();
+    const uint32_t k_groups = (k + 127u) >> 7;
+    double acc[NT];
+#pragma unroll
+    for (int t = 0; t < NT; ++t) acc[t] = 0.0;
+    if (n < n_rows) {
+        const uint4 *wrow = reinterpret_cast<const uint4 *>(w + (size_t)n * k);
+        const size_t srow = (size_t)(n >> 7) * k_groups;
+        for (uint32_t p = half * per + lane; p < (half + 1u) * per; p += 32u) {
+            const uint4 q = ldg_stream(wrow + p);
+            const double sc = fp8_block_scale_f64<F32_SCALE>(scale, srow + (p >> 3));
+            const uint32_t wd[4] = {q.x, q.y, q.z, q.w};
+            float2 wf[8];
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+                uint32_t h0, h1;
+                e4m3x4_to_h2x2(wd[i], h0, h1);
+                wf[i * 2] = h2_to_f2(h0);
+                wf[i * 2 + 1] = h2_to_f2(h1);
+            }
+#pragma unroll
+            for (int t = 0; t < NT; ++t) {
+                const float4 *xp = reinterpret_cast<const float4 *>(sx) + (size_t)t * (k >> 2) + p;
+                float2 part = make_float2(0.f, 0.f);
+#pragma unroll
+                for (int i = 0; i < 4; ++i) {
+                    const float4 v = xp[(size_t)i * pieces];
+                    part = __ffma2_rn(wf[i * 2], make_float2(v.x, v.y), part);
+                    part = __ffma2_rn(wf[i * 2 + 1], make_float2(v.z, v.w), part);
+                }
+                acc[t] += (double)(part.x + part.y) * sc;
+            }
+        }
+    }
+#pragma unroll
+    for (int t = 0; t < NT; ++t) {
+        const double v = warp_sum(acc[t]);
+        if (lane == 0 && half == 1u) red[r][t] = v;
+        acc[t] = v;
+    }
+    __syncthreads();
+    if (lane == 0 && half == 0u && n < n_rows) {
+#pragma unroll
+        for (int t = 0; t < NT; ++t) y[(size_t)t * n_rows + n] = (float)(acc[t] + red[r][t]);
+    }
+}
+
 // Reference order: thread per (row, token), k ascending, (x*e)*s then add
 // (examples/s14_vulkan_numeric.rs:1698-1714).
 template <bool F32_SCALE>
@@ -894,9 +965,46 @@ cudaError_t launch_mxfp4_matvec(cudaStream_t st, uint32_t mode, int sm_count, co
     return cudaGetLastError();
 }
 
+// Largest dynamic shared memory k_fp8_matvec_block may ask for on the current device (0: not set).
+template <int NT, bool F32S>
+static bool fp8_block_smem_ok(size_t bytes) {
+    static int configured[64] = {};
+    int dev = -1;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return false;
+    if (!configured[dev]) {
+        configured[dev] = cudaFuncSetAttribute(k_fp8_matvec_block<NT, F32S>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                               160 * 1024) == cudaSuccess ? 1 : -1;
+    }
+    return configured[dev] == 1 && bytes <= 160u * 1024u;
+}
+
+template <int NT, bool F32S>
+static bool try_fp8_block(cudaStream_t st, int sm_count, const float *x, const uint8_t *w, const void *s, float *y,
+                          uint32_t n, uint32_t k) {
+    // few rows (a warp per row would leave most SMs with a handful of warps), k in whole scale
+    // blocks, 16-byte aligned operands, the tokens' activations fit shared memory
+    const size_t bytes = (size_t)NT * k * sizeof(float);
+    if (n > (uint32_t)sm_count * 32u || (k & 31u) || ((uintptr_t)w & 15u) || ((uintptr_t)x & 15u)) return false;
+    if (!fp8_block_smem_ok<NT, F32S>(bytes)) return false;
+    k_fp8_matvec_block<NT, F32S><<<(n + kFp8BlockRows - 1) / kFp8BlockRows, kFp8BlockThreads, bytes, st>>>(x, w, s, y, n, k);
+    return true;
+}
+
 template <bool F32S>
-static void launch_fp8_pairwise_nt(cudaStream_t st, uint32_t blocks, uint32_t nt, const float *x,
+static void launch_fp8_pairwise_nt(cudaStream_t st, int sm_count, uint32_t blocks, uint32_t nt, const float *x,
                                    const uint8_t *w, const void *s, float *y, uint32_t n, uint32_t k) {
+    bool done = false;
+    switch (nt) {
+    case 1: done = try_fp8_block<1, F32S>(st, sm_count, x, w, s, y, n, k); break;
+    case 2: done = try_fp8_block<2, F32S>(st, sm_count, x, w, s, y, n, k); break;
+    case 3: done = try_fp8_block<3, F32S>(st, sm_count, x, w, s, y, n, k); break;
+    case 4: done = try_fp8_block<4, F32S>(st, sm_count, x, w, s, y, n, k); break;
+    case 5: done = try_fp8_block<5, F32S>(st, sm_count, x, w, s, y, n, k); break;
+    case 6: done = try_fp8_block<6, F32S>(st, sm_count, x, w, s, y, n, k); break;
+    case 7: done = try_fp8_block<7, F32S>(st, sm_count, x, w, s, y, n, k); break;
+    default: done = try_fp8_block<8, F32S>(st, sm_count, x, w, s, y, n, k); break;
+    }
+    if (done) return;
     switch (nt) {
     case 1: k_fp8_matvec_pairwise<1, F32S><<<blocks, 256, 0, st>>>(x, w, s, y, n, k); break;
     case 2: k_fp8_matvec_pairwise<2, F32S><<<blocks, 256, 0, st>>>(x, w, s, y, n, k); break;
@@ -921,9 +1029,9 @@ cudaError_t launch_fp8_matvec(cudaStream_t st, uint32_t mode, int sm_count, uint
     } else {
         const uint32_t blocks = min(ceil_div(n, 8), (uint32_t)sm_count * 8u);
         if (scale_format == S14_SCALE_F32)
-            launch_fp8_pairwise_nt<true>(st, blocks, n_tokens, x, w, s, y, n, k);
+            launch_fp8_pairwise_nt<true>(st, sm_count, blocks, n_tokens, x, w, s, y, n, k);
         else
-            launch_fp8_pairwise_nt<false>(st, blocks, n_tokens, x, w, s, y, n, k);
+            launch_fp8_pairwise_nt<false>(st, sm_count, blocks, n_tokens, x, w, s, y, n, k);
     }
     return cudaGetLastError();
 }
