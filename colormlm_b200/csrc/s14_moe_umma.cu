@@ -114,6 +114,24 @@ __device__ __forceinline__ void bulk_copy(uint32_t dst, const void *src, uint32_
                  ::"r"(dst), "l"(src), "r"(bytes), "r"(bar)
                  : "memory");
 }
+// The same copy for page bytes that are read once: the lines go first when the L2 needs room, so that
+// they do not displace what was fetched ahead (the next layer's shared expert).
+__device__ __forceinline__ void bulk_copy_stream(uint32_t dst, const void *src, uint32_t bytes, uint32_t bar,
+                                                 unsigned long long policy) {
+    asm volatile(
+        "cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes.L2::cache_hint [%0], [%1], %2, [%3], %4;"
+        ::"r"(dst), "l"(src), "r"(bytes), "r"(bar), "l"(policy)
+        : "memory");
+}
+__device__ __forceinline__ unsigned long long l2_policy_evict_first() {
+    unsigned long long p;
+    asm volatile("createpolicy.fractional.L2::evict_first.b64 %0, 1.0;" : "=l"(p));
+    return p;
+}
+// Asks the L2 for bytes of this GPU's memory that a later copy will read (size a multiple of 16).
+__device__ __forceinline__ void l2_prefetch(const void *src, uint32_t bytes) {
+    asm volatile("cp.async.bulk.prefetch.L2.global [%0], %1;" ::"l"(src), "r"(bytes) : "memory");
+}
 // One bounded hardware wait: returns when the phase completes or after about a microsecond.
 __device__ __forceinline__ bool mbar_try(uint32_t bar, uint32_t parity) {
     uint32_t ok;
@@ -637,6 +655,7 @@ k_moe_layer_umma(const JobTable *__restrict__ dev_table, const __grid_constant__
             s_prod[5] = p_units, s_prod[6] = p_ok ? 1u : 0u;
         };
         if (p_layer > ll || !p_ok) return;
+        const unsigned long long stream_policy = l2_policy_evict_first();
         const uint32_t par_l = ll & 1u;
         const uint32_t n_static = table_param ? s_n_jobs : n_early_jobs;
         bool routes_known = table_param;
@@ -684,7 +703,7 @@ k_moe_layer_umma(const JobTable *__restrict__ dev_table, const __grid_constant__
                 }
                 const uint32_t full = bar(kBarFull + p_slot);
                 mbar_arrive_expect(full, kSlot);
-                bulk_copy(smem_u32(sRing) + p_slot * kSlot, a, kSlot, full);
+                bulk_copy_stream(smem_u32(sRing) + p_slot * kSlot, a, kSlot, full, stream_policy);
                 a += kUnitStride;
                 ++p_units;
                 if (++p_slot == ring) {
@@ -699,7 +718,15 @@ k_moe_layer_umma(const JobTable *__restrict__ dev_table, const __grid_constant__
         p_i = 0;
         leave();
     };
+    // This CTA's share of a shared expert's page into the L2: units cta, cta + grid, ...
+    auto prefetch_shared = [&](const uint8_t *page) {
+        if (!page) return;
+        const uint32_t units = (uint32_t)(mxfp4_page_bytes(hidden, inter) / kUnitStride);
+#pragma unroll 1
+        for (uint32_t u = cta; u < units; u += grid) l2_prefetch(page + (size_t)u * kUnitStride, kUnitStride);
+    };
     if (is_producer) {
+        if (n_early_jobs) prefetch_shared(s_layer[0].shared_page);  // the first layer's, before the token is there
         if (routes_here) {
             // the first layer's router rows; those of layer l + 1 follow when layer l's routes are known
             const uint16_t *wr0 = s_layer[0].router_weight;
@@ -1388,6 +1415,10 @@ k_moe_layer_umma(const JobTable *__restrict__ dev_table, const __grid_constant__
                 }
             }
             if (is_producer) {
+                // While the routes are being picked the memory is idle: this CTA's share of the NEXT layer's
+                // shared expert (its address is known) is asked into the L2, where that layer's copies find
+                // it a layer-time later instead of taking HBM time from the routed experts' stream.
+                if (n_early_jobs && l + 1u < L) prefetch_shared(s_layer[par ^ 1u].shared_page);
                 produce(l, false);
                 if (l + 1u < L) produce(l + 1u, true);
                 if (l + 1u == L) mark(12);
