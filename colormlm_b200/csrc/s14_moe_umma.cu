@@ -92,7 +92,8 @@ constexpr uint32_t kBarHFree = kBarHReady + 2;        // [2] ... is not read any
 constexpr uint32_t kBarFin = kBarHFree + 2;           // both issuing threads have finished
 constexpr uint32_t kBarRoutes = kBarFin + 1;          // the jobs and the CTA's items are in shared memory
 constexpr uint32_t kBarWr = kBarRoutes + 1;           // the layer's router rows of this CTA are in shared memory
-constexpr uint32_t kBars = kBarWr + 1;
+constexpr uint32_t kBarPages = kBarWr + 1;            // the picked experts' pages are in the job records (early lists)
+constexpr uint32_t kBars = kBarPages + 1;
 constexpr uint32_t kRouteWarp = 15;                   // the warp that publishes the CTA's expert scores
 
 __device__ __forceinline__ uint32_t smem_u32(const void *p) {
@@ -668,7 +669,9 @@ k_moe_layer_umma(const JobTable *__restrict__ dev_table, const __grid_constant__
                 if (!is_static) {
                     if (head) return leave();
                     if (ll == 0u) mark(3);
-                    if (!mbar_wait(bar(kBarRoutes), par_l, abortp)) {
+                    // with a list known from the start the copies need only the picked experts' pages, which
+                    // are in the job records half a microsecond before the routes' weights are
+                    if (!mbar_wait(bar((early && routes_here) ? kBarPages : kBarRoutes), par_l, abortp)) {
                         p_ok = false;
                         return leave();
                     }
@@ -972,9 +975,12 @@ k_moe_layer_umma(const JobTable *__restrict__ dev_table, const __grid_constant__
                             s_pick_id[rank] = 0xffffffffu - (uint32_t)mine;
                             s_pick_score[rank] = s_cand_score[lt];
                             s_pick_page[rank] = s_cand_page[lt];
+                            // (no expert parallelism: the job of route `rank` follows the shared expert's)
+                            if (early) s_jobs[par][n_early_jobs + rank].page = reinterpret_cast<const uint8_t *>(s_cand_page[lt]);
                         }
                     }
                     load_sync();  // the picks are written; every candidate's page has been read
+                    if (early && lt == 0) mbar_arrive(bar(kBarPages));
                     if (wl == 0u) {
                         __syncwarp();
                         if (lane == 0) mark(71);
