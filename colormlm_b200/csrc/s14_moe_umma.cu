@@ -1297,6 +1297,12 @@ k_moe_layer_umma(const JobTable *__restrict__ dev_table, const __grid_constant__
                                 if (j + 1u == n_jobs) {
                                     const uint32_t nm = s_n_mix;
                                     const unsigned long long *dw = d_words + n;
+                                    // the layer's input for the residual: asked for now, not after the wait below
+                                    // (from the L2: the L1 may hold this word's value of two layers ago)
+                                    float x_in = 0.0f;
+                                    if (residual)
+                                        x_in = l == 0u ? __ldcg(x + n)
+                                                       : __uint_as_float((uint32_t)ld_relaxed_gpu(x_words + (size_t)par * kMaxHidden + n));
                                     uint32_t vals[kJobsMax];
                                     uint32_t tries = 0;
                                     bool got = true;
@@ -1307,9 +1313,11 @@ k_moe_layer_umma(const JobTable *__restrict__ dev_table, const __grid_constant__
                                         for (uint32_t jj = 0; jj < kJobsMax; ++jj) {
                                             // (rows past the mix are not used: any row will do)
                                             const uint32_t r = jj < nm ? (s_mix_slot[par][jj] & 0x7FFFFFFFu) : slot;
+                                            // (no branch between the loads: they must all be in flight together)
                                             const unsigned long long t = ld_relaxed_gpu(dw + (size_t)r * kMaxHidden);
-                                            missing |= (uint32_t)(t >> 32) ^ want;
-                                            vals[jj] = (uint32_t)t;
+                                            const bool own = r == slot;  // this item's own row: the value is at hand
+                                            missing |= own ? 0u : ((uint32_t)(t >> 32) ^ want);
+                                            vals[jj] = own ? __float_as_uint(v) : (uint32_t)t;
                                         }
                                         if (missing == 0u) break;
                                         if (++tries > kSpinGlobal || abort_flag) {
@@ -1328,11 +1336,7 @@ k_moe_layer_umma(const JobTable *__restrict__ dev_table, const __grid_constant__
                                                 acc = (s_mix_slot[par][jj] >> 31) ? __fadd_rn(acc, dv) : __fadd_rn(acc, __fmul_rn(s_mix_w[par][jj], dv));
                                             }
                                         }
-                                        float out = acc;
-                                        if (residual)
-                                            out = __fadd_rn(l == 0u ? __ldcg(x + n)
-                                                            : __uint_as_float((uint32_t)ld_relaxed_gpu(x_words + (size_t)par * kMaxHidden + n)),
-                                                    acc);  // (from the L2: the L1 may hold this word's value of two layers ago)
+                                        const float out = residual ? __fadd_rn(x_in, acc) : acc;
                                         if (l + 1u == L) y[n] = out;
                                         else st_relaxed_gpu(x_words + (size_t)(par ^ 1u) * kMaxHidden + n, ((unsigned long long)(want + 1u) << 32) | __float_as_uint(out));
                                         if (s_layer[par].y_out) s_layer[par].y_out[n] = acc;
