@@ -805,6 +805,12 @@ k_moe_layer_umma(const JobTable *__restrict__ dev_table, const __grid_constant__
                         }
                     }
                     ok = __shfl_sync(0xffffffffu, ok ? 1 : 0, 0) != 0;  // (has_x is uniform in a warp)
+                    if constexpr (kTrace) {
+                        if (l == trace_layer + 1u && lane == 0 && (warp == 0u || warp == 15u)) {
+                            unsigned long long *t2 = trace_base();
+                            if (t2) t2[85u + (warp ? 2u : 0u)] = (unsigned long long)clock64();
+                        }
+                    }
 #pragma unroll 1
                     while (ok) {
                         ulonglong2 w[4];
@@ -821,9 +827,21 @@ k_moe_layer_umma(const JobTable *__restrict__ dev_table, const __grid_constant__
                         __nanosleep(100);
                     }
                     if (!ok) abort_flag = 1;
+                    if constexpr (kTrace) {
+                        if (l == trace_layer + 1u && lane == 0 && (warp == 0u || warp == 15u)) {
+                            unsigned long long *t2 = trace_base();
+                            if (t2) t2[86u + (warp ? 2u : 0u)] = (unsigned long long)clock64();
+                        }
+                    }
                 }
                 alive = token_all(ok && !abort_flag);
                 if (!alive) break;
+                if constexpr (kTrace) {
+                    if (l == trace_layer + 1u && tid == 0) {
+                        unsigned long long *t2 = trace_base();
+                        if (t2) t2[89] = (unsigned long long)clock64();
+                    }
+                }
             }
             if (tid == 0) mark(4);
             // tensor memory, while the first token is on its way

@@ -129,6 +129,8 @@ S14_API int32_t s14_ctx_kernel_times(s14_ctx *ctx, double ms_out[4], uint64_t *c
  * (i < 5): 16+4i first unit in shared memory, 17+4i accumulators complete, 52+i accumulators read,
  * 58+i hidden digits made (up items), 18+4i epilogue done, 40+i digit tile asked for, 46+i tile in
  * shared memory, 19+4i tile ready (down items); 12 all copies issued, 13 items done, 14 exit;
+ * 85/86 (warp 0) and 87/88 (warp 15): the NEXT layer's token: first word seen, all words taken; 89
+ * every warp has its words;
  * word 15 = items | ring slots << 8 | jobs << 16.  A word that was not written is 0.  read copies
  * the marks of the last launch ([n_ctas][words_per_cta]). */
 S14_API int32_t s14_ctx_set_layer_trace(s14_ctx *ctx, int32_t enable);
