@@ -51,12 +51,12 @@ STEP_BYTES = 7 * PAGE_BYTES + ROUTER_BYTES + HIDDEN * 4 + HIDDEN * 4
 # layer kernel with the routes given: 7 expert pages, x in, y out
 LAYER_BYTES = 7 * PAGE_BYTES + HIDDEN * 4 + HIDDEN * 4
 # DRAM bytes of one layer of a launch of the layer kernel at this workload: dram__bytes_read.sum +
-# dram__bytes_write.sum of one ncu capture of a 14-layer launch (1 309.806 MB read + 9.094 MB written) divided by 14 = 94 207 153 B
-# per layer.  The capture ran on a reduced pool (64 routed experts per layer, 1.7 GB resident: the full
-# workload holds 48 GB, more than a capture may); a layer's traffic differs from the full workload's only by
-# the router rows it reads (64 instead of 256), which are added here.  The summary of the capture is kept
-# under profiles/.
-NCU_TRAFFIC_BYTES = 94_207_153 - (64 * HIDDEN * 2 + 64 * 4) + (256 * HIDDEN * 2 + 256 * 4)
+# dram__bytes_write.sum of one ncu capture of a 14-layer launch (1 312.389 MB read + 3.994 MB written)
+# divided by 14 = 94 027 346 B per layer.  The capture ran on a reduced pool (14 layers of 16 routed experts,
+# 3.2 GB resident: the full workload holds 48 GB, more than a capture may); a layer's traffic differs from
+# the full workload's only by the router rows it reads (16 instead of 256), which are added here.  The
+# summary of the capture is kept under profiles/.
+NCU_TRAFFIC_BYTES = 94_027_346 - (16 * HIDDEN * 2 + 16 * 4) + (256 * HIDDEN * 2 + 256 * 4)
 WORKLOAD = ("moe_layer_decode: 1 token, router top-6 of 256 + 6 routed + 1 shared MXFP4 expert, "
             "hidden 4096, intermediate 2048")
 TOKEN_SEED = 99
