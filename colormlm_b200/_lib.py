@@ -21,6 +21,7 @@ PAGE_MXFP4, PAGE_FP8 = 0, 1
 ACCUM_PAIRWISE, ACCUM_REFERENCE = 0, 1
 LAYER_PATH_TENSOR, LAYER_PATH_TENSOR_PER_TOKEN, LAYER_PATH_TENSOR_STACK, LAYER_PATH_F32, LAYER_PATH_REFERENCE = 1, 2, 3, 4, 5
 LAYER_PATH_ROUTER_KERNEL = 0x100
+LAYER_PATH_TENSOR_BLOCK = 6
 SCORE_SIGMOID, SCORE_SQRT_SOFTPLUS = 0, 1
 SCALE_UE8M0, SCALE_F32 = 0, 1
 PROFILE_S14_TOP6, PROFILE_FULL_DEPTH43_NATIVE_TOP6 = 0, 1
@@ -146,6 +147,11 @@ SIGNATURES = {
     "s14_stack_destroy": (_I32, [_VP]),
     "s14_cmd_stack_decode": (_I32, [_VP, _VP, _VP, _VP, _VP]),
     "s14_stack_decode_host": (_I32, [_VP, _VP, _VP, _VP]),
+    "s14_block_create": (_I32, [_VP, _U32, _U32, _U32, _P(_VP)]),
+    "s14_block_destroy": (_I32, [_VP]),
+    "s14_cmd_moe_block": (_I32, [_VP, _VP, _VP, _P(MoeLayerDesc)]),
+    "s14_cmd_routed_moe_block": (_I32, [_VP, _VP, _VP, _P(RoutedLayerDesc)]),
+    "s14_block_last_counts": (_I32, [_VP, _P(_U32)]),
     "s14_layer_work_list": (_I32, [_U32, _U32, _U32, _U32, _U32, _U32, _VP, _U32, _VP]),
     "s14_mxfp4_expert_page_from_tensors": (_I32, [_U32, _U32, _VP, _VP]),
     "s14_mxfp4_expert_page_to_tensors": (_I32, [_U32, _U32, _VP, _VP]),

@@ -1765,3 +1765,195 @@ extern "C" int32_t s14_moe_pages_cancel(s14_moe_pages *pages, s14_route_load_bat
     return S14_OK;
     S14_CATCH
 }
+
+// ---- a block of tokens through one layer, grouped by expert ----------------------------
+//
+// The workspace of the grouped tensor-core kernels (s14_moe_block.cu) for up to max_tokens tokens:
+// chunk and item tables, the tokens' and the (token, route) pairs' digit tiles, the pairs' expert
+// outputs, router scratch, and a pinned staging buffer for routes that come from the host.
+struct s14_block {
+    s14_ctx *ctx = nullptr;
+    uint32_t hidden = 0, inter = 0, max_tokens = 0;
+    BlockWork w{};
+    float *scores = nullptr, *select = nullptr;   // [max_tokens, 256]
+    unsigned int *counter = nullptr;              // the router kernel's arrival counter
+    int32_t *ids = nullptr;                       // [max_tokens, 6] routes of the host-route call, on the device
+    float *weights = nullptr;
+    const uint8_t **pages = nullptr;
+    uint8_t *stage = nullptr;                     // pinned: ids | weights | pages of one call
+    cudaEvent_t staged = nullptr;                 // the staging buffer's last copy has left it
+    bool stage_busy = false;
+};
+
+static constexpr uint32_t kBlockMaxTokens = 1024;
+
+extern "C" int32_t s14_block_destroy(s14_block *blk) {
+    if (!blk) return S14_OK;
+    cudaSetDevice(blk->ctx->device);
+    cudaDeviceSynchronize();
+    cudaFree(blk->w.chunks);
+    cudaFree(blk->w.items_up);
+    cudaFree(blk->w.items_down);
+    cudaFree(blk->w.counts);
+    cudaFree(blk->w.xdig);
+    cudaFree(blk->w.xexp);
+    cudaFree(blk->w.hdig);
+    cudaFree(blk->w.hexp);
+    cudaFree(blk->w.d);
+    cudaFree(blk->scores);
+    cudaFree(blk->select);
+    cudaFree(blk->counter);
+    cudaFree(blk->ids);
+    cudaFree(blk->weights);
+    cudaFree(blk->pages);
+    cudaFreeHost(blk->stage);
+    if (blk->staged) cudaEventDestroy(blk->staged);
+    delete blk;
+    return S14_OK;
+}
+
+extern "C" int32_t s14_block_create(s14_ctx *ctx, uint32_t hidden, uint32_t inter, uint32_t max_tokens, s14_block **out) {
+    if (!ctx || !out) return fail(S14_ERR_CONTRACT, "s14_block_create: NULL argument");
+    *out = nullptr;
+    if (max_tokens == 0 || max_tokens > kBlockMaxTokens)
+        return fail(S14_ERR_CONTRACT, "s14_block_create: 1..1024 tokens");
+    CUDA_OK(cudaSetDevice(ctx->device));
+    if (!moe_block_ok(ctx->sm_count, hidden, inter, S14_N_ROUTED_EXPERTS, S14_EXPERTS_PER_TOKEN))
+        return fail(S14_ERR_CONTRACT, "s14_block_create: hidden and intermediate must be multiples of 512 up to 4096");
+    std::unique_ptr<s14_block, int32_t (*)(s14_block *)> blk(new s14_block(), s14_block_destroy);
+    blk->ctx = ctx;
+    blk->hidden = hidden;
+    blk->inter = inter;
+    blk->max_tokens = max_tokens;
+    const size_t T = max_tokens, P = T * (S14_EXPERTS_PER_TOKEN + 1), C = moe_block_max_chunks(max_tokens);
+    const size_t S = inter >> 6, RT = hidden >> 7, R = S14_EXPERTS_PER_TOKEN;
+    CUDA_OK(cudaMalloc((void **)&blk->w.chunks, C * sizeof(BlockChunk)));
+    CUDA_OK(cudaMalloc((void **)&blk->w.items_up, C * S * sizeof(uint32_t)));
+    CUDA_OK(cudaMalloc((void **)&blk->w.items_down, C * RT * sizeof(uint32_t)));
+    CUDA_OK(cudaMalloc((void **)&blk->w.counts, 64));
+    CUDA_OK(cudaMalloc((void **)&blk->w.xdig, T * (hidden >> 8) * 2048u));
+    CUDA_OK(cudaMalloc((void **)&blk->w.xexp, T * (hidden >> 5)));
+    CUDA_OK(cudaMalloc((void **)&blk->w.hdig, P * (inter >> 8) * 2048u));
+    CUDA_OK(cudaMalloc((void **)&blk->w.hexp, P * (inter >> 5)));
+    CUDA_OK(cudaMalloc((void **)&blk->w.d, P * hidden * sizeof(float)));
+    CUDA_OK(cudaMalloc((void **)&blk->scores, T * S14_N_ROUTED_EXPERTS * sizeof(float)));
+    CUDA_OK(cudaMalloc((void **)&blk->select, T * S14_N_ROUTED_EXPERTS * sizeof(float)));
+    CUDA_OK(cudaMalloc((void **)&blk->counter, 64));
+    CUDA_OK(cudaMalloc((void **)&blk->ids, T * R * sizeof(int32_t)));
+    CUDA_OK(cudaMalloc((void **)&blk->weights, T * R * sizeof(float)));
+    CUDA_OK(cudaMalloc((void **)&blk->pages, T * R * sizeof(uint8_t *)));
+    CUDA_OK(cudaHostAlloc((void **)&blk->stage, T * R * 16u, cudaHostAllocDefault));
+    CUDA_OK(cudaEventCreateWithFlags(&blk->staged, cudaEventDisableTiming));
+    CUDA_OK(cudaMemset(blk->w.counts, 0, 64));
+    CUDA_OK(cudaMemset(blk->counter, 0, 64));
+    *out = blk.release();
+    return S14_OK;
+}
+
+// After the stream is synchronised: counts[3] of the last call (an expert id outside the table).
+static int32_t block_launch(s14_block *blk, cudaStream_t st, const float *x, float *y, const int32_t *ids,
+                            const float *weights, const uint8_t *const *pages, const uint8_t *const *page_table,
+                            const uint8_t *shared_page, uint32_t n_tokens, uint32_t top_k, uint32_t n_experts) {
+    s14_ctx *ctx = blk->ctx;
+    cudaError_t err;
+    ctx->launches += launch_moe_block(st, ctx->sm_count, blk->w, x, y, ids, weights, pages, page_table, shared_page, n_tokens,
+                                      top_k, n_experts, blk->hidden, blk->inter, ctx->status, &err);
+    ctx->last_path = S14_LAYER_PATH_TENSOR_BLOCK;
+    if (err != cudaSuccess) return cuda_fail(err, "S14 MoE block launch");
+    return S14_OK;
+}
+
+extern "C" int32_t s14_cmd_moe_block(s14_ctx *ctx, void *stream, s14_block *blk, const s14_moe_layer_desc *desc) {
+    S14_TRY
+    if (!ctx || !blk || !desc) throw ContractError("s14_cmd_moe_block: NULL argument");
+    if (blk->ctx != ctx) throw ContractError("s14_cmd_moe_block: the block object belongs to another context");
+    if (desc->hidden != blk->hidden || desc->inter != blk->inter)
+        throw ContractError("s14_cmd_moe_block: sizes differ from the block object's");
+    if (desc->n_tokens == 0 || desc->n_tokens > blk->max_tokens)
+        throw ContractError("s14_cmd_moe_block: more tokens than the block object was created for");
+    if (!desc->routes || !desc->x || !desc->y) throw ContractError("s14_cmd_moe_block: routes, x or y is NULL");
+    if (desc->shared_page && desc->shared_kind != S14_PAGE_MXFP4)
+        throw ContractError("s14_cmd_moe_block: the grouped kernels take MXFP4 pages only");
+    require_aligned(desc->x, 16, "S14 MoE block x");
+    if (desc->shared_page) require_aligned(desc->shared_page, 16, "S14 MoE block shared page");
+    const uint32_t T = desc->n_tokens, R = S14_EXPERTS_PER_TOKEN;
+    CUDA_OK(cudaSetDevice(ctx->device));
+    if (blk->stage_busy) CUDA_OK(cudaEventSynchronize(blk->staged));
+    int32_t *h_ids = reinterpret_cast<int32_t *>(blk->stage);
+    float *h_w = reinterpret_cast<float *>(blk->stage + (size_t)T * R * 4u);
+    const uint8_t **h_pages = reinterpret_cast<const uint8_t **>(blk->stage + (size_t)T * R * 8u);
+    for (uint32_t t = 0; t < T; ++t) {
+        const s14_token_route &r = desc->routes[t];
+        if (r.n_routed > R) throw ContractError("s14_cmd_moe_block: a token has more than 6 routed experts");
+        if (r.n_routed == 0 && !desc->shared_page) throw ContractError("s14_cmd_moe_block: a token has no expert at all");
+        for (uint32_t j = 0; j < R; ++j) {
+            h_ids[t * R + j] = -1;
+            h_w[t * R + j] = 0.0f;
+            h_pages[t * R + j] = nullptr;
+            if (j >= r.n_routed) continue;
+            if (!r.pages[j] || reinterpret_cast<uintptr_t>(r.pages[j]) % 16 != 0)
+                throw ContractError("s14_cmd_moe_block: a routed page address is NULL or not 16-byte aligned");
+            if (!std::isfinite(r.weights[j]) || r.weights[j] < 0.0f)
+                throw ContractError("s14_cmd_moe_block: route weight must be finite and non-negative");
+            if (r.expert_ids[j] >= S14_N_ROUTED_EXPERTS) throw ContractError("s14_cmd_moe_block: expert id above 255");
+            for (uint32_t i = 0; i < j; ++i)
+                if (r.expert_ids[i] == r.expert_ids[j]) throw ContractError("s14_cmd_moe_block: route expert repeated");
+            h_ids[t * R + j] = r.expert_ids[j];
+            h_w[t * R + j] = r.weights[j];
+            h_pages[t * R + j] = r.pages[j];
+        }
+    }
+    cudaStream_t st = stream_of(ctx, stream);
+    CUDA_OK(cudaMemcpyAsync(blk->ids, h_ids, (size_t)T * R * 4u, cudaMemcpyHostToDevice, st));
+    CUDA_OK(cudaMemcpyAsync(blk->weights, h_w, (size_t)T * R * 4u, cudaMemcpyHostToDevice, st));
+    CUDA_OK(cudaMemcpyAsync(blk->pages, h_pages, (size_t)T * R * 8u, cudaMemcpyHostToDevice, st));
+    CUDA_OK(cudaEventRecord(blk->staged, st));
+    blk->stage_busy = true;
+    return block_launch(blk, st, desc->x, desc->y, blk->ids, blk->weights, blk->pages, nullptr, desc->shared_page, T, R,
+                        S14_N_ROUTED_EXPERTS);
+    S14_CATCH
+}
+
+extern "C" int32_t s14_cmd_routed_moe_block(s14_ctx *ctx, void *stream, s14_block *blk, const s14_routed_layer_desc *desc) {
+    S14_TRY
+    if (!ctx || !blk || !desc) throw ContractError("s14_cmd_routed_moe_block: NULL argument");
+    if (blk->ctx != ctx) throw ContractError("s14_cmd_routed_moe_block: the block object belongs to another context");
+    const s14_router_desc &r = desc->router;
+    if (r.hidden != blk->hidden || desc->inter != blk->inter)
+        throw ContractError("s14_cmd_routed_moe_block: sizes differ from the block object's");
+    if (r.n_tokens == 0 || r.n_tokens > blk->max_tokens)
+        throw ContractError("s14_cmd_routed_moe_block: more tokens than the block object was created for");
+    if (r.n_experts == 0 || r.n_experts > S14_N_ROUTED_EXPERTS) throw ContractError("S14 router: 1..256 experts");
+    if (r.top_k == 0 || r.top_k > S14_EXPERTS_PER_TOKEN || r.top_k > r.n_experts)
+        throw ContractError("s14_cmd_routed_moe_block: top_k must be 1..6");
+    if (r.score_fn != S14_SCORE_SIGMOID && r.score_fn != S14_SCORE_SQRT_SOFTPLUS)
+        throw ContractError("S14 router: unknown score function");
+    if (!std::isfinite(r.route_scale) || r.route_scale <= 0.0f)
+        throw ContractError("S14 router: route_scale must be finite and positive");
+    if (!r.x || !r.router_weight_bf16 || !desc->page_table || !desc->y)
+        throw ContractError("s14_cmd_routed_moe_block: x, router weight, page table or y is NULL");
+    if (desc->shared_page && desc->shared_kind != S14_PAGE_MXFP4)
+        throw ContractError("s14_cmd_routed_moe_block: the grouped kernels take MXFP4 pages only");
+    require_aligned(r.x, 16, "S14 router x");
+    require_aligned(r.router_weight_bf16, 16, "S14 router weight");
+    CUDA_OK(cudaSetDevice(ctx->device));
+    cudaStream_t st = stream_of(ctx, stream);
+    s14_router_desc rd = r;
+    if (!rd.ids_out) rd.ids_out = blk->ids;
+    if (!rd.weights_out) rd.weights_out = blk->weights;
+    cudaError_t err;
+    ctx->launches += launch_router(st, rd, blk->scores, blk->select, nullptr, nullptr, nullptr, 0, blk->counter, &err);
+    if (err != cudaSuccess) return cuda_fail(err, "S14 router launch");
+    return block_launch(blk, st, r.x, desc->y, rd.ids_out, rd.weights_out, nullptr, desc->page_table, desc->shared_page,
+                        r.n_tokens, r.top_k, r.n_experts);
+    S14_CATCH
+}
+
+// counts of the last call's grouping (after the stream is synchronised): chunks, up items, down
+// items, and 1 if an expert id was outside the table (the call then did nothing).
+extern "C" int32_t s14_block_last_counts(s14_block *blk, uint32_t counts_out[4]) {
+    if (!blk || !counts_out) return fail(S14_ERR_CONTRACT, "s14_block_last_counts: NULL argument");
+    CUDA_OK(cudaSetDevice(blk->ctx->device));
+    CUDA_OK(cudaMemcpy(counts_out, blk->w.counts, 16, cudaMemcpyDeviceToHost));
+    return S14_OK;
+}

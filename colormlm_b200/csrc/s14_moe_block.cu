@@ -1,0 +1,529 @@
+// The MoE layer of a BLOCK of tokens (a verify block of up to 8 tokens, a prefill of hundreds) on
+// the fifth-generation tensor cores, with the tokens grouped by expert so that an expert's page is
+// streamed once for all the tokens routed to it.  Semantics: the reference's per-token layer loop
+// (examples/s14_vulkan_numeric.rs:929-947) applied to every token of the block, which is all the
+// reference's own prefill does (ssd_inference/src/forward.rs:544-549 walks the tokens one by one).
+//
+// The contraction is the one of the one-token layer kernel (s14_moe_umma.cu), widened along N:
+// tcgen05.mma kind::mxf4.block_scale with A = 128 weight rows x 64 K-elements of page bytes as they
+// are, and B = the sixteen balanced base-8 digit rows of EVERY token of a chunk (up to kBlockNt tokens
+// that share the expert: N = 16 * tokens).  Accumulator columns 16 t .. 16 t + 15 hold the digit
+// shares of token t's dot products; added in double and rounded once they give the double-accumulated
+// dot product rounded to F32, so every token's result is bit-identical to what the one-token kernel
+// and the double-accumulating CPU restatement give for that token alone.
+//
+// Five launches per layer, all plain stream order:
+//   k_block_digits   x [T, hidden] -> digit tiles (2 KB per token and 256 elements) + block exponents
+//   k_block_group    routes [T, top_k] -> chunks (expert page, <= kBlockNt tokens), item lists
+//   k_block_gemm<0>  up items (chunk, slice of 64 intermediate elements): w1 | w3 units x the chunk's
+//                    token tiles; epilogue: limited SwiGLU, digit tiles of the hidden values per
+//                    (token, route) pair
+//   k_block_gemm<1>  down items (chunk, tile of 128 rows of w2) x the pairs' digit tiles -> the
+//                    pairs' expert outputs [pair, hidden]
+//   k_block_mix      per token the ordered mix: routes in order, shared expert last
+// Items are dealt round robin to one persistent CTA per SM, the chunks of one expert next to each
+// other, so that the second and later chunks of an expert find its units in the L2.
+//
+// Roles inside a GEMM CTA: one copying thread (a unit of 17 KB page bytes plus the chunk's token
+// tiles of that K range into one ring stage: plain bulk copies, no multicast), two MMA-issuing
+// threads (even and odd units of an item, an accumulator each), four epilogue warps, eight warps
+// that lay out the digit rows' scale codes of the next item in shared memory (tcgen05.cp brings
+// them to tensor memory unit by unit, like the weights' scales).  Every wait is bounded; a wait that
+// runs out raises the CTA's abort flag, the status word is set, and the CTA waits for its copies in
+// flight, frees its tensor memory and returns.
+#include "s14_umma.cuh"
+
+namespace s14 {
+
+namespace {
+
+constexpr uint32_t kNt = kBlockNt;
+constexpr uint32_t kStageA = kUnitStride;                  // a unit's codes, then its scales
+constexpr uint32_t kStage = kStageA + kNt * 2048u;         // ... then the chunk's token tiles of the unit's K range
+static_assert(kStage % 1024u == 0u && kStageA % 1024u == 0u, "operand tiles keep the 1 KB alignment of the 128-byte swizzle");
+constexpr uint32_t kGThreads = 512;
+constexpr uint32_t kGRingMax = 8;
+constexpr uint32_t kSfbBytes = 16u * 1024u;                // an item's digit-row scale atoms: K / 256 units x 1 KB, K <= 4096
+constexpr uint32_t kGProdWarp = 4, kGMmaWarp0 = 5, kGLayWarp0 = 8;
+constexpr uint32_t kGLayThreads = 256;
+// tensor memory columns
+constexpr uint32_t kGColAcc = 0;                           // [2 buffers][2 issuing threads][16 * kNt]
+constexpr uint32_t kGColSfa = 4u * 16u * kNt;              // [2 issuing threads][16]: weight scales of the unit at hand
+constexpr uint32_t kGColSfb = kGColSfa + 32u;              // [2 issuing threads][16]: digit-row scales of that unit
+static_assert(kGColSfb + 32u <= 512u, "tensor memory map");
+// barriers
+constexpr uint32_t kGBarFull = 0;
+constexpr uint32_t kGBarDone = kGRingMax;
+constexpr uint32_t kGBarAccDone = 2 * kGRingMax;           // [2] an item's accumulators are complete (both issuing threads)
+constexpr uint32_t kGBarAccFree = kGBarAccDone + 2;        // [2] ... have been read
+constexpr uint32_t kGBarSfb = kGBarAccFree + 2;            // [2] an item's digit-row scales are laid out
+constexpr uint32_t kGBarFin = kGBarSfb + 2;
+constexpr uint32_t kGBars = kGBarFin + 1;
+constexpr uint32_t kPairsPerToken = S14_EXPERTS_PER_TOKEN + 1;   // pair = token * 7 + position in the mix (6: shared)
+
+struct GemmArgs {
+    const BlockChunk *chunks;
+    const uint32_t *items;      // chunk << 8 | slice (up) or row tile (down)
+    const uint32_t *n_items;    // device memory: written by the grouping kernel
+    const uint8_t *dig;         // digit tiles of the B vectors [vector][K / 256][2048]
+    const uint8_t *exps;        // their block exponents + 100, [vector][K / 32]
+    float *out;                 // down: the pairs' expert outputs [pair][hidden]
+    uint8_t *hdig, *hexp;       // up: digit tiles and exponents of the pairs' hidden values
+    uint32_t hidden, inter, ring;
+};
+
+// The digit tiles and block exponents of n vectors of K elements (one CTA per vector).
+__global__ void __launch_bounds__(512)
+k_block_digits(const float *__restrict__ x, uint32_t K, uint8_t *__restrict__ dig, uint8_t *__restrict__ exps) {
+    const uint32_t v = blockIdx.x, g = threadIdx.x;
+    if (g >= (K >> 3)) return;  // whole warps leave: K is a multiple of 256
+    const float4 p0 = __ldg(reinterpret_cast<const float4 *>(x + (size_t)v * K) + 2u * g);
+    const float4 p1 = __ldg(reinterpret_cast<const float4 *>(x + (size_t)v * K) + 2u * g + 1u);
+    const float xs[8] = {p0.x, p0.y, p0.z, p0.w, p1.x, p1.y, p1.z, p1.w};
+    digits_of8(xs, g, dig + (size_t)v * (K >> 8) * 2048u, exps + (size_t)v * (K >> 5));
+}
+
+// Groups the block's (token, route) pairs by expert.  Group 0 is the shared expert (every token, mix
+// position 6), group 1 + e the routed expert e; a group's members are taken in ascending (token,
+// position) order and cut into chunks of kBlockNt.  ids: [T, top_k] expert ids, negative = no route.
+// The page of a routed group is page_table[e], or, with per-route pages, the page of its first
+// member.  counts: [0] chunks, [1] up items, [2] down items, [3] 1 if an id was out of range.
+// One CTA of 1024 threads.
+__global__ void __launch_bounds__(1024)
+k_block_group(const int32_t *__restrict__ ids, const uint8_t *const *__restrict__ pages,
+              const uint8_t *const *__restrict__ page_table, const uint8_t *shared_page, uint32_t T, uint32_t top_k,
+              uint32_t n_experts, uint32_t S, uint32_t RT, BlockChunk *__restrict__ chunks,
+              uint32_t *__restrict__ items_up, uint32_t *__restrict__ items_down, uint32_t *__restrict__ counts) {
+    __shared__ uint32_t cnt[S14_N_ROUTED_EXPERTS + 1];
+    __shared__ uint32_t chunk0[S14_N_ROUTED_EXPERTS + 2];
+    __shared__ uint32_t bad;
+    const uint32_t tid = threadIdx.x, G = n_experts + 1u, n = T * top_k;
+    if (tid <= S14_N_ROUTED_EXPERTS) cnt[tid] = 0u;
+    if (tid == 0) bad = 0u;
+    __syncthreads();
+    for (uint32_t i = tid; i < n; i += blockDim.x) {
+        const int32_t e = __ldg(ids + i);
+        if (e >= (int32_t)n_experts) bad = 1u;
+        else if (e >= 0) atomicAdd(&cnt[1 + e], 1u);
+    }
+    if (tid == 0 && shared_page) cnt[0] = T;
+    __syncthreads();
+    if (tid == 0) {
+        uint32_t c = 0;
+        for (uint32_t g = 0; g < G; ++g) {
+            chunk0[g] = c;
+            c += (cnt[g] + kNt - 1u) / kNt;
+        }
+        chunk0[G] = c;
+        if (bad) c = 0;  // the contraction kernels find no item and the mix writes nothing
+        counts[0] = c;
+        counts[1] = c * S;
+        counts[2] = c * RT;
+        counts[3] = bad;
+    }
+    __syncthreads();
+    if (tid >= G || cnt[tid] == 0u || bad) return;
+    const uint32_t g = tid, c0 = chunk0[g], nch = chunk0[g + 1u] - c0, members = cnt[g];
+    const uint8_t *page = g == 0u ? shared_page : (page_table ? page_table[g - 1u] : nullptr);
+    if (g == 0u) {
+        for (uint32_t t = 0; t < T; ++t) {
+            BlockChunk *ch = chunks + c0 + t / kNt;
+            ch->tok[t % kNt] = t;
+            ch->pair[t % kNt] = t * kPairsPerToken + S14_EXPERTS_PER_TOKEN;
+        }
+    } else {
+        uint32_t k = 0;
+        for (uint32_t i = 0; i < n && k < members; ++i) {
+            if (__ldg(ids + i) != (int32_t)(g - 1u)) continue;
+            const uint32_t t = i / top_k, m = i - t * top_k;
+            if (k == 0u && !page_table) page = pages[i];
+            BlockChunk *ch = chunks + c0 + k / kNt;
+            ch->tok[k % kNt] = t;
+            ch->pair[k % kNt] = t * kPairsPerToken + m;
+            ++k;
+        }
+    }
+    for (uint32_t k = 0; k < nch; ++k) {
+        BlockChunk *ch = chunks + c0 + k;
+        ch->page = page;
+        ch->nt = k + 1u < nch ? kNt : members - k * kNt;
+        ch->multi = nch > 1u ? 1u : 0u;
+    }
+    for (uint32_t r = 0; r < S; ++r)
+        for (uint32_t k = 0; k < nch; ++k) items_up[(size_t)c0 * S + r * nch + k] = ((c0 + k) << 8) | r;
+    for (uint32_t r = 0; r < RT; ++r)
+        for (uint32_t k = 0; k < nch; ++k) items_down[(size_t)c0 * RT + r * nch + k] = ((c0 + k) << 8) | r;
+}
+
+template <bool kDown>
+__global__ void __launch_bounds__(kGThreads, 1)
+k_block_gemm(const __grid_constant__ GemmArgs a, uint32_t *status) {
+    extern __shared__ __align__(1024) uint8_t smem[];
+    __shared__ __align__(8) uint64_t bars[kGBars];
+    __shared__ float s_up[kNt][64];                          // an item's up projections, handed to the gate threads
+    __shared__ __align__(16) uint8_t s_hst[kNt][16 * 2 * 16]; // an up item's digit chunks per token: [row][block][16 bytes]
+    __shared__ uint32_t tmem_slot, s_units;
+    __shared__ int abort_flag;
+
+    const uint32_t tid = threadIdx.x, warp = tid >> 5, lane = tid & 31u;
+    const uint32_t grid = gridDim.x, cta = blockIdx.x;
+    const uint32_t K = kDown ? a.inter : a.hidden;
+    const uint32_t nu = K >> 8;                      // units of an item
+    const uint32_t KD = a.inter >> 8;
+    const uint32_t ring = a.ring;
+    uint8_t *const sRing = smem;
+    uint8_t *const sSfb = smem + ring * kStage;      // [2][kSfbBytes]
+    const size_t page_off = kDown ? mxfp4_down_offset(a.hidden, a.inter) : 0u;
+    const uint32_t bar0 = smem_u32(bars);
+    auto bar = [&](uint32_t i) { return bar0 + i * 8u; };
+    volatile int *const abortp = &abort_flag;
+
+    if (tid < kGBars) {
+        uint32_t count = 1u;
+        if (tid >= kGBarAccDone && tid < kGBarAccDone + 2u) count = 2u;
+        else if (tid >= kGBarAccFree && tid < kGBarAccFree + 2u) count = 128u;
+        else if (tid >= kGBarSfb && tid < kGBarSfb + 2u) count = kGLayThreads;
+        else if (tid == kGBarFin) count = 2u;
+        mbar_init(bar(tid), count);
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    if (tid == 0) {
+        abort_flag = 0;
+        s_units = 0;
+    }
+    if (warp == kGMmaWarp0) {
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(&tmem_slot)), "r"(512u)
+                     : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+        fence_before();
+    }
+    __syncthreads();
+    fence_after();
+    const uint32_t tmem = tmem_slot;
+    const uint32_t n_items = __ldcg(a.n_items);
+
+    if (tid == kGProdWarp * 32u) {
+        // ---- the copying thread: per unit of every item one ring stage ----
+        const unsigned long long once = l2_policy_evict_first();
+        uint32_t slot = 0, round = 0, units = 0;
+        bool ok = true;
+#pragma unroll 1
+        for (uint32_t q = cta; q < n_items && ok; q += grid) {
+            const uint32_t item = __ldg(a.items + q), r = item & 0xFFu;
+            const BlockChunk *ch = a.chunks + (item >> 8);
+            const uint32_t nt = __ldg(&ch->nt), multi = __ldg(&ch->multi);
+            uint32_t vec[kNt];
+#pragma unroll
+            for (uint32_t t = 0; t < kNt; ++t) vec[t] = kDown ? __ldg(&ch->pair[t]) : __ldg(&ch->tok[t]);
+            const uint8_t *src = reinterpret_cast<const uint8_t *>(__ldg(reinterpret_cast<const unsigned long long *>(&ch->page))) +
+                                 page_off + (size_t)r * nu * kUnitStride;
+#pragma unroll 1
+            for (uint32_t u = 0; u < nu; ++u) {
+                if (round && !mbar_wait(bar(kGBarDone + slot), (round - 1u) & 1u, abortp)) {
+                    ok = false;
+                    break;
+                }
+                const uint32_t full = bar(kGBarFull + slot), dst = smem_u32(sRing) + slot * kStage;
+                mbar_arrive_expect(full, kStageA + nt * 2048u);
+                // an expert with one chunk is read once; with more, its later chunks want the units in the L2
+                if (multi) bulk_copy(dst, src, kStageA, full);
+                else bulk_copy_stream(dst, src, kStageA, full, once);
+#pragma unroll
+                for (uint32_t t = 0; t < kNt; ++t)
+                    if (t < nt) bulk_copy(dst + kStageA + t * 2048u, a.dig + ((size_t)vec[t] * nu + u) * 2048u, 2048u, full);
+                src += kUnitStride;
+                ++units;
+                if (++slot == ring) {
+                    slot = 0;
+                    ++round;
+                }
+            }
+        }
+        s_units = units;
+    } else if ((warp == kGMmaWarp0 || warp == kGMmaWarp0 + 1u) && lane == 0) {
+        // ---- MMA issue: thread m takes units m, m + 2, ... of every item (a ring slot always belongs
+        // to the same thread: items have an even number of units and the ring an even number of slots)
+        // and accumulates into an accumulator of its own; items alternate between two buffers ----
+        const uint32_t m = warp - kGMmaWarp0;
+        const uint64_t a_desc0 = smem_desc(smem_u32(sRing), 1, 64, 2);
+        const uint64_t sf_desc0 = smem_desc(smem_u32(sRing) + kUnitBytes, 0, 8, 0);
+        const uint64_t b_desc0 = smem_desc(smem_u32(sRing) + kStageA, 1, 64, 2);
+        const uint32_t sfa_t = tmem + kGColSfa + m * 16u, sfb_t = tmem + kGColSfb + m * 16u;
+        uint32_t m_slot = m, m_round = 0, gi = 0;
+        bool ok = true;
+#pragma unroll 1
+        for (uint32_t q = cta; q < n_items && ok; q += grid, ++gi) {
+            const uint32_t item = __ldg(a.items + q), buf = gi & 1u;
+            const uint32_t nt = __ldg(&a.chunks[item >> 8].nt);
+            const uint32_t idesc = umma_idesc_mxf4(16u * nt);
+            if (gi >= 2u) ok = mbar_wait(bar(kGBarAccFree + buf), ((gi - 2u) >> 1) & 1u, abortp);
+            ok = ok && mbar_wait(bar(kGBarSfb + buf), (gi >> 1) & 1u, abortp);
+            if (!ok) break;
+            fence_after();
+            const uint32_t acc = tmem + kGColAcc + (buf * 2u + m) * (16u * kNt);
+            const uint64_t sfb_desc0 = smem_desc(smem_u32(sSfb) + buf * kSfbBytes, 0, 8, 0);
+#pragma unroll 1
+            for (uint32_t ku = m; ku < nu; ku += 2u) {
+                const uint32_t s = m_slot;
+                ok = mbar_wait(bar(kGBarFull + s), m_round & 1u, abortp);
+                if (!ok) break;
+                m_slot += 2u;
+                if (m_slot >= ring) {
+                    m_slot -= ring;
+                    ++m_round;
+                }
+                fence_after();
+                const uint64_t sfd = sf_desc0 + s * (kStage >> 4), sbd = sfb_desc0 + ku * (1024u >> 4);
+                tmem_copy_scales(sfa_t, sfd);
+                tmem_copy_scales(sfa_t + 4u, sfd + (kAtomBytes >> 4));
+                tmem_copy_scales(sfb_t, sbd);
+                tmem_copy_scales(sfb_t + 4u, sbd + (kAtomBytes >> 4));
+                const uint64_t ad = a_desc0 + s * (kStage >> 4), bd = b_desc0 + s * (kStage >> 4);
+#pragma unroll
+                for (uint32_t kk = 0; kk < 4; ++kk) {
+                    const uint32_t atom = kk >> 1, sfid = (kk & 1u) * 2u;
+                    umma_mxf4(acc, ad + kk * 2u, bd + kk * 2u, idesc | (sfid << 29) | (sfid << 4),
+                              (sfa_t + atom * 4u) | (sfid << 30), (sfb_t + atom * 4u) | (sfid << 30), (ku >= 2u || kk) ? 1u : 0u);
+                }
+                umma_commit(bar(kGBarDone + s));
+            }
+            if (!ok) break;
+            umma_commit(bar(kGBarAccDone + buf));
+        }
+        // nothing of this CTA's tensor work is in flight when the tensor memory is freed
+        umma_commit(bar(kGBarFin));
+        mbar_wait(bar(kGBarFin), 0, abortp);
+    } else if (warp < 4u) {
+        // ---- epilogue: per token of the chunk the two accumulators' sixteen digit columns, added in
+        // double and rounded once ----
+        const uint32_t row = tid;
+        const uint32_t lane_base = tmem + ((warp * 32u) << 16);
+        uint32_t gi = 0;
+        bool ok = true;
+#pragma unroll 1
+        for (uint32_t q = cta; q < n_items && ok; q += grid, ++gi) {
+            const uint32_t item = __ldg(a.items + q), idx = item & 0xFFu, buf = gi & 1u;
+            const BlockChunk *ch = a.chunks + (item >> 8);
+            const uint32_t nt = __ldg(&ch->nt);
+            uint32_t pair[kNt];
+#pragma unroll
+            for (uint32_t t = 0; t < kNt; ++t) pair[t] = __ldg(&ch->pair[t]);
+            ok = epi_all(mbar_wait(bar(kGBarAccDone + buf), (gi >> 1) & 1u, abortp));
+            if (!ok) break;
+            fence_after();
+            float v[kNt];
+#pragma unroll
+            for (uint32_t t = 0; t < kNt; ++t) {
+                v[t] = 0.0f;
+                if (t < nt) {  // uniform in the CTA
+                    double sum = 0.0;
+#pragma unroll
+                    for (uint32_t half = 0; half < 2; ++half) {
+                        uint32_t r[16];
+                        tmem_ld16(lane_base + kGColAcc + (buf * 2u + half) * (16u * kNt) + 16u * t, r);
+                        tmem_ld_wait();
+                        double lo = 0.0, hi = 0.0;
+#pragma unroll
+                        for (int c = 0; c < 8; ++c) {
+                            lo += (double)__uint_as_float(r[8 + c]);
+                            hi += (double)__uint_as_float(r[c]);
+                        }
+                        sum += lo + hi;
+                    }
+                    v[t] = (float)sum;
+                }
+            }
+            fence_before();
+            mbar_arrive(bar(kGBarAccFree + buf));
+            if constexpr (kDown) {
+                // row idx * 128 + `row` of the pairs' expert outputs
+#pragma unroll
+                for (uint32_t t = 0; t < kNt; ++t)
+                    if (t < nt) a.out[(size_t)pair[t] * a.hidden + idx * 128u + row] = v[t];
+            } else {
+                // lanes 0-63: gate of the slice's element `row`; lanes 64-127: its up projection
+#pragma unroll
+                for (uint32_t t = 0; t < kNt; ++t)
+                    if (t < nt && row >= 64u) s_up[t][row - 64u] = v[t];
+                epi_sync();
+#pragma unroll
+                for (uint32_t t = 0; t < kNt; ++t) {
+                    if (t < nt && row < 64u) {
+                        // hidden value `row` of the slice -> sixteen digit nibbles; scale block = warp
+                        const float hv = swiglu_limit_f32(v[t], s_up[t][row]);
+                        float bm = fabsf(hv);
+#pragma unroll
+                        for (int o = 16; o > 0; o >>= 1) bm = fmaxf(bm, __shfl_xor_sync(0xffffffffu, bm, o));
+                        const int E = block_exponent(bm);
+                        uint32_t hw, lw;
+                        digit_codes16(hv, __uint_as_float((uint32_t)(150 - E) << 23), hw, lw);
+                        const uint32_t ohw = __shfl_xor_sync(0xffffffffu, hw, 1), olw = __shfl_xor_sync(0xffffffffu, lw, 1);
+                        // byte lane / 2 of every row's chunk holds the nibbles of lanes 2b (low) and 2b + 1; even
+                        // lanes write digit rows 0-3 and 8-11, odd lanes 4-7 and 12-15
+                        const uint32_t e_hw = (lane & 1u) ? ohw : hw, o_hw = (lane & 1u) ? hw : ohw;
+                        const uint32_t e_lw = (lane & 1u) ? olw : lw, o_lw = (lane & 1u) ? lw : olw;
+#pragma unroll
+                        for (uint32_t jj = 0; jj < 4; ++jj) {
+                            const uint32_t dj = (lane & 1u) * 4u + jj;
+                            s_hst[t][(dj * 2u + warp) * 16u + (lane >> 1)] =
+                                (uint8_t)(((e_hw >> (4u * dj)) & 0xFu) | (((o_hw >> (4u * dj)) & 0xFu) << 4));
+                            s_hst[t][((8u + dj) * 2u + warp) * 16u + (lane >> 1)] =
+                                (uint8_t)(((e_lw >> (4u * dj)) & 0xFu) | (((o_lw >> (4u * dj)) & 0xFu) << 4));
+                        }
+                        if (lane == 0) a.hexp[(size_t)pair[t] * (a.inter >> 5) + idx * 2u + warp] = (uint8_t)(E + 100);
+                    }
+                }
+                epi_sync();
+                // the slice's 32 chunks (digit row, block) of every token go to their places in the pair's
+                // digit tile: 64 threads write half a chunk each; the two halves of the CTA take the
+                // tokens alternately
+                const uint32_t t64 = tid & 63u, ch16 = t64 >> 1, half = t64 & 1u, dj = ch16 >> 1, blk = ch16 & 1u;
+                const uint32_t cc = (idx & 3u) * 2u + blk;
+                const uint32_t o = (idx >> 2) * 2048u + dj * 128u + ((cc ^ (dj & 7u)) << 4) + half * 8u;
+#pragma unroll
+                for (uint32_t t = 0; t < kNt; ++t) {
+                    if (t < nt && (t & 1u) == (tid >> 6)) {
+                        const uint2 c8 = *reinterpret_cast<const uint2 *>(&s_hst[t][(dj * 2u + blk) * 16u + half * 8u]);
+                        *reinterpret_cast<uint2 *>(a.hdig + (size_t)pair[t] * KD * 2048u + o) = c8;
+                    }
+                }
+            }
+        }
+    } else if (warp >= kGLayWarp0) {
+        // ---- the scale codes of the chunk's digit rows, as the atoms tensor memory takes (row n of
+        // the operand = 16 * token + digit row: byte (n % 32) * 16 + (n / 32) * 4 + block % 4 of the atom
+        // of four scale blocks); digit row j < 8 of a block with exponent E has the code
+        // 127 + E - 23 + 3 j, row 8 + j the code 127 + E - 47 + 3 j; the exponents are stored as E + 100 ----
+        const uint32_t lt = tid - kGLayWarp0 * 32u;
+        const uint32_t atom = lt >> 7, r32 = (lt >> 2) & 31u, col = lt & 3u;
+        const uint32_t t = 2u * col + (r32 >> 4), j = r32 & 15u;
+        const int shift = j < 8u ? 4 + 3 * (int)j : 3 * (int)(j & 7u) - 20;
+        const uint32_t bias = 0x01010101u * (uint32_t)shift;
+        uint32_t gi = 0;
+        bool ok = true;
+#pragma unroll 1
+        for (uint32_t q = cta; q < n_items && ok; q += grid, ++gi) {
+            const uint32_t item = __ldg(a.items + q), buf = gi & 1u;
+            const BlockChunk *ch = a.chunks + (item >> 8);
+            const uint32_t nt = __ldg(&ch->nt);
+            // the buffer's last readers were the copies of item gi - 2
+            if (gi >= 2u) ok = mbar_wait(bar(kGBarAccDone + buf), ((gi - 2u) >> 1) & 1u, abortp);
+            if (!ok) break;
+            uint8_t *dst = sSfb + buf * kSfbBytes + atom * kAtomBytes + r32 * 16u + col * 4u;
+            if (t < nt && t < kNt) {
+                const uint32_t vec = kDown ? __ldg(&ch->pair[t]) : __ldg(&ch->tok[t]);
+                const uint32_t *e4 = reinterpret_cast<const uint32_t *>(a.exps + (size_t)vec * (K >> 5)) + atom;
+#pragma unroll 4
+                for (uint32_t u = 0; u < nu; ++u) *reinterpret_cast<uint32_t *>(dst + u * 1024u) = __ldcg(e4 + u * 2u) + bias;
+            } else {
+#pragma unroll 4
+                for (uint32_t u = 0; u < nu; ++u) *reinterpret_cast<uint32_t *>(dst + u * 1024u) = 0x7F7F7F7Fu;
+            }
+            fence_async_smem();  // tcgen05.cp reads the atoms
+            mbar_arrive(bar(kGBarSfb + buf));
+        }
+    }
+    __syncwarp();
+    if (tid == kGProdWarp * 32u) {
+        // copies in flight land in this CTA's shared memory: wait for them before leaving
+        const uint32_t units = s_units, first = units > ring ? units - ring : 0u;
+#pragma unroll 1
+        for (uint32_t u = first; u < units; ++u) {
+            const uint32_t s = u % ring, parity = (u / ring) & 1u;
+            uint32_t tries = 0;
+#pragma unroll 1
+            while (!mbar_try(bar(kGBarFull + s), parity) && ++tries < kSpin) {
+            }
+        }
+    }
+    fence_before();
+    __syncwarp();
+    __syncthreads();
+    if (warp == kGMmaWarp0) {
+        __syncwarp();
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_slot), "r"(512u) : "memory");
+    }
+    if (tid == 0 && abort_flag) atomicExch(status, 0x5507u);
+}
+
+// y[t, n]: the ordered mix of token t (examples/s14_vulkan_numeric.rs:936-946): acc = 0; acc += w * d
+// over the routes in order; acc += d of the shared expert.
+__global__ void __launch_bounds__(256)
+k_block_mix(const float *__restrict__ d, const int32_t *__restrict__ ids, const float *__restrict__ weights,
+            uint32_t top_k, int has_shared, float *__restrict__ y, uint32_t hidden, const uint32_t *__restrict__ counts) {
+    const uint32_t n = blockIdx.x * blockDim.x + threadIdx.x, t = blockIdx.y;
+    if (n >= hidden || __ldcg(counts + 3)) return;
+    const float *dt = d + (size_t)t * kPairsPerToken * hidden + n;
+    float acc = 0.0f;
+    for (uint32_t m = 0; m < top_k; ++m)
+        if (__ldg(ids + t * top_k + m) >= 0)
+            acc = __fadd_rn(acc, __fmul_rn(__ldg(weights + t * top_k + m), __ldcg(dt + (size_t)m * hidden)));
+    if (has_shared) acc = __fadd_rn(acc, __ldcg(dt + (size_t)S14_EXPERTS_PER_TOKEN * hidden));
+    y[(size_t)t * hidden + n] = acc;
+}
+
+constexpr int kMaxDevices = 64;
+size_t g_block_limit[kMaxDevices] = {};
+
+// The dynamic shared memory the GEMM kernels may ask for on the current device (set once per device).
+size_t block_dynamic_limit() {
+    int dev = -1;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= kMaxDevices) return 0;
+    if (g_block_limit[dev]) return g_block_limit[dev];
+    cudaFuncAttributes fa, fb;
+    if (cudaFuncGetAttributes(&fa, k_block_gemm<false>) != cudaSuccess) return 0;
+    if (cudaFuncGetAttributes(&fb, k_block_gemm<true>) != cudaSuccess) return 0;
+    int optin = 0;
+    if (cudaDeviceGetAttribute(&optin, cudaDevAttrMaxSharedMemoryPerBlockOptin, dev) != cudaSuccess) return 0;
+    const size_t fixed = fa.sharedSizeBytes > fb.sharedSizeBytes ? fa.sharedSizeBytes : fb.sharedSizeBytes;
+    if ((size_t)optin <= fixed) return 0;
+    const size_t most = (size_t)optin - fixed;
+    if (cudaFuncSetAttribute(k_block_gemm<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)most) != cudaSuccess) return 0;
+    if (cudaFuncSetAttribute(k_block_gemm<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)most) != cudaSuccess) return 0;
+    g_block_limit[dev] = most;
+    return most;
+}
+
+uint32_t block_ring(size_t limit) {
+    if (limit < 2u * kSfbBytes + 2u * kStage) return 0;
+    uint32_t r = (uint32_t)((limit - 2u * kSfbBytes) / kStage);
+    if (r > kGRingMax) r = kGRingMax;
+    return r & ~1u;
+}
+
+}  // namespace
+
+bool moe_block_ok(int sm_count, uint32_t hidden, uint32_t inter, uint32_t n_experts, uint32_t top_k) {
+    if (sm_count <= 0 || n_experts == 0u || n_experts > S14_N_ROUTED_EXPERTS || top_k == 0u || top_k > S14_EXPERTS_PER_TOKEN)
+        return false;
+    if ((hidden & 511u) || (inter & 511u) || hidden < 512u || inter < 512u || hidden > 4096u || inter > 4096u) return false;
+    return block_ring(block_dynamic_limit()) >= 2u;
+}
+
+size_t moe_block_max_chunks(uint32_t max_tokens) {
+    // every expert may end with a chunk that is not full; the shared expert's chunks hold every token once
+    return (size_t)S14_N_ROUTED_EXPERTS + 1u + ((size_t)max_tokens * kPairsPerToken + kNt - 1u) / kNt;
+}
+
+int launch_moe_block(cudaStream_t st, int sm_count, const BlockWork &w, const float *x, float *y, const int32_t *ids,
+                     const float *weights, const uint8_t *const *pages, const uint8_t *const *page_table,
+                     const uint8_t *shared_page, uint32_t n_tokens, uint32_t top_k, uint32_t n_experts, uint32_t hidden,
+                     uint32_t inter, uint32_t *status, cudaError_t *err) {
+    const uint32_t ring = block_ring(block_dynamic_limit());
+    *err = cudaErrorInvalidConfiguration;
+    if (ring < 2u || n_tokens == 0u) return 0;
+    const uint32_t S = inter >> 6, RT = hidden >> 7;
+    const size_t smem = (size_t)ring * kStage + 2u * kSfbBytes;
+    k_block_digits<<<n_tokens, 512, 0, st>>>(x, hidden, w.xdig, w.xexp);
+    k_block_group<<<1, 1024, 0, st>>>(ids, pages, page_table, shared_page, n_tokens, top_k, n_experts, S, RT, w.chunks,
+                                     w.items_up, w.items_down, w.counts);
+    GemmArgs up = {w.chunks, w.items_up, w.counts + 1, w.xdig, w.xexp, nullptr, w.hdig, w.hexp, hidden, inter, ring};
+    k_block_gemm<false><<<sm_count, kGThreads, smem, st>>>(up, status);
+    GemmArgs down = {w.chunks, w.items_down, w.counts + 2, w.hdig, w.hexp, w.d, nullptr, nullptr, hidden, inter, ring};
+    k_block_gemm<true><<<sm_count, kGThreads, smem, st>>>(down, status);
+    k_block_mix<<<dim3((hidden + 255u) / 256u, n_tokens), 256, 0, st>>>(w.d, ids, weights, top_k, shared_page != nullptr, y, hidden, w.counts);
+    *err = cudaGetLastError();
+    return 5;
+}
+
+}  // namespace s14

@@ -424,6 +424,58 @@ class DecodeStack:
             pass
 
 
+class MoeBlock:
+    """A block of tokens (a verify block, a prefill) through one MoE layer with the tokens grouped by
+    expert: every distinct expert's page is streamed once (see the header: s14_block_create)."""
+
+    def __init__(self, ctx: "S14Context", hidden: int, inter: int, max_tokens: int):
+        self._ctx = ctx
+        self.hidden, self.inter, self.max_tokens = hidden, inter, max_tokens
+        h = C.c_void_p()
+        check(L.lib().s14_block_create(ctx.handle, hidden, inter, max_tokens, C.byref(h)))
+        self._h = h
+
+    def cmd_moe_block(self, x, y, routes: Sequence["TokenRoute"], shared_page: Optional[int],
+                      stream: Optional[int] = None) -> None:
+        """Routes from the host: x, y device [n_tokens, hidden]."""
+        desc, keep = _layer_desc(routes, shared_page, L.PAGE_MXFP4, self.hidden, self.inter)
+        desc.x, desc.y = x.data_ptr(), y.data_ptr()
+        check(L.lib().s14_cmd_moe_block(self._ctx.handle, stream if stream is not None else _torch_stream(),
+                                        self._h, C.byref(desc)))
+        del keep
+
+    def cmd_routed_moe_block(self, x, wr_bf16, bias, page_table, shared_page: Optional[int], y, ids_out=None,
+                             weights_out=None, *, score_fn: int = L.SCORE_SIGMOID, top_k: int = 6,
+                             route_scale: float = 1.0, stream: Optional[int] = None) -> None:
+        """Router on the device: x, y device [n_tokens, hidden]; ids_out / weights_out [n_tokens, top_k]."""
+        d = L.RoutedLayerDesc()
+        d.router = _router_desc(x, wr_bf16, bias, ids_out, weights_out, score_fn, top_k, route_scale)
+        d.inter = self.inter
+        d.shared_kind = L.PAGE_MXFP4
+        d.page_table = page_table.data_ptr()
+        d.shared_page = shared_page
+        d.y = y.data_ptr()
+        check(L.lib().s14_cmd_routed_moe_block(self._ctx.handle, stream if stream is not None else _torch_stream(),
+                                               self._h, C.byref(d)))
+
+    def last_counts(self):
+        """(chunks, up items, down items, bad id flag) of the last call; synchronise the stream first."""
+        out = (C.c_uint32 * 4)()
+        check(L.lib().s14_block_last_counts(self._h, out))
+        return tuple(int(v) for v in out)
+
+    def close(self) -> None:
+        if getattr(self, "_h", None):
+            check(L.lib().s14_block_destroy(self._h))
+            self._h = None
+
+    def __del__(self):
+        try:
+            self.close()
+        except Exception:
+            pass
+
+
 class RoutedLayerHostCall:
     """A bound routed layer call on host buffers (see S14Context.bind_routed_moe_layer_host)."""
 

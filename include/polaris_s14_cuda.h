@@ -108,6 +108,7 @@ S14_API uint64_t s14_ctx_launch_count(const s14_ctx *ctx);
 #define S14_LAYER_PATH_TENSOR_STACK 3u     /* a whole stack of layers in one launch of it */
 #define S14_LAYER_PATH_F32 4u              /* F32 register kernels, pairwise order */
 #define S14_LAYER_PATH_REFERENCE 5u        /* reference-order kernels */
+#define S14_LAYER_PATH_TENSOR_BLOCK 6u     /* grouped tcgen05 kernels: every expert page streamed once per block */
 #define S14_LAYER_PATH_ROUTER_KERNEL 0x100u
 S14_API uint32_t s14_ctx_last_layer_path(const s14_ctx *ctx);
 
@@ -461,6 +462,34 @@ S14_API int32_t s14_cmd_routed_moe_layer_ep(s14_ctx *ctx, void *stream, const s1
 S14_API int32_t s14_routed_moe_layer_host(s14_ctx *ctx, const s14_routed_layer_desc *desc,
                                           const float *host_x, float *host_y, int32_t *host_ids,
                                           float *host_weights);
+
+/* A block of tokens through one MoE layer with the tokens GROUPED BY EXPERT: a verify block (K = 2..8,
+ * s14_runner/src/cascade.rs:19) or a prefill of hundreds of tokens (the reference's prefill walks
+ * its tokens one by one through the same layer loop, ssd_inference/src/forward.rs:544-549; the
+ * semantics are that loop, examples/s14_vulkan_numeric.rs:929-947, applied to every token).  Every
+ * distinct expert's page is streamed once for all the tokens routed to it (in chunks of six tokens;
+ * an expert's later chunks find the page in the L2): per layer five launches - digit rows of the
+ * tokens, grouping of the (token, route) pairs by expert, the w1 | w3 contraction with SwiGLU, the w2
+ * contraction, the ordered mix - the two contractions on tcgen05 kind::mxf4.block_scale with
+ * N = 16 digit rows per token of a chunk.  Every token's y is bit-identical to what
+ * s14_cmd_moe_layer / s14_cmd_routed_moe_layer give for that token alone in pairwise order.
+ * MXFP4 pages only (routed and shared); hidden and intermediate multiples of 512 up to 4096.
+ *   create:  allocates the workspace for up to max_tokens (<= 1024) tokens:
+ *            about max_tokens * (28 * hidden + 57 * intermediate + 8 * hidden) bytes.
+ *   s14_cmd_moe_block:        routes from the host (desc->n_tokens up to max_tokens; expert_ids < 256
+ *            identify the groups, a group's page is the page of its first member).
+ *   s14_cmd_routed_moe_block: router on the device (desc->router.n_tokens up to max_tokens, top_k <= 6);
+ *            ids_out / weights_out [n_tokens, top_k] may be NULL.
+ *   One call at a time per block object (calls on one stream are ordered).  A wait that runs out
+ *   inside a kernel sets the context's device status word to 0x5507. */
+typedef struct s14_block s14_block;
+S14_API int32_t s14_block_create(s14_ctx *ctx, uint32_t hidden, uint32_t inter, uint32_t max_tokens, s14_block **out);
+S14_API int32_t s14_block_destroy(s14_block *blk);
+S14_API int32_t s14_cmd_moe_block(s14_ctx *ctx, void *stream, s14_block *blk, const s14_moe_layer_desc *desc);
+S14_API int32_t s14_cmd_routed_moe_block(s14_ctx *ctx, void *stream, s14_block *blk, const s14_routed_layer_desc *desc);
+/* After the stream is synchronised: the last call's number of chunks, up items, down items, and 1 if
+ * an expert id was outside the table (the call then wrote no result). */
+S14_API int32_t s14_block_last_counts(s14_block *blk, uint32_t counts_out[4]);
 
 /* LM head (local_s14_primitives/final_head.py:113-149): logits[v] = x . W[v,:]
  * for the rows [row_begin, row_begin + n_rows) of a BF16 [vocab, hidden] matrix

@@ -1,0 +1,180 @@
+"""Parity of the grouped block path (s14_cmd_moe_block / s14_cmd_routed_moe_block): a block of
+tokens through one MoE layer with the tokens grouped by expert must give, for EVERY token, the bits
+of the double-accumulated CPU oracle for that token alone -- the reference's per-token layer loop
+(examples/s14_vulkan_numeric.rs:929-947) applied to each token of the block -- and the bits of the
+one-token tensor-core call."""
+import numpy as np
+import pytest
+
+torch = pytest.importorskip("torch")
+
+from colormlm_b200 import _lib as L
+from colormlm_b200 import synth
+from colormlm_b200.s14 import MoeBlock, S14Context, S14Error, TokenRoute
+
+from .test_gpu_parity import dev, dev_page, make_layer, run_layer
+
+pytestmark = [pytest.mark.gpu, pytest.mark.usefixtures("cuda_lib")]
+
+
+@pytest.fixture(scope="module")
+def ctx():
+    if not torch.cuda.is_available():
+        pytest.skip("needs a CUDA device")
+    c = S14Context(0)
+    yield c
+    c.close()
+
+
+def run_block(ctx, blk, x, pages_dev, shared_dev, routes):
+    dx = dev(x)
+    dy = torch.full_like(dx, float("nan"))
+    tr = [TokenRoute(ids, w, [pages_dev[i].data_ptr() for i in ids]) for ids, w in routes]
+    blk.cmd_moe_block(dx, dy, tr, shared_dev.data_ptr() if shared_dev is not None else None)
+    torch.cuda.synchronize()
+    assert ctx.device_status() == 0  # no bounded wait ran out
+    assert ctx.last_layer_path == L.LAYER_PATH_TENSOR_BLOCK
+    return dy.cpu().numpy()
+
+
+def random_routes(g, n_tokens, n_experts, ragged=False):
+    routes = []
+    for t in range(n_tokens):
+        k = 6 if not ragged else int(g.integers(1, 7))
+        routes.append((g.permutation(n_experts)[:k].tolist(), g.uniform(0.05, 0.4, k).astype(np.float32)))
+    return routes
+
+
+@pytest.mark.parametrize("n_tokens", [1, 5, 8, 13])
+def test_block_equals_every_tokens_own_layer(ctx, oracle, n_tokens):
+    """2048 x 1024, 16 experts: with 13 tokens every expert has several tokens, some more than one
+    chunk of six; the shared expert has three chunks.  Ragged routes (1..6 experts per token)."""
+    hidden, inter, n_experts = 2048, 1024, 16
+    g, pages, shared = make_layer(1200 + n_tokens, hidden, inter, n_experts, L.PAGE_MXFP4)
+    x = synth.activations(g, n_tokens, hidden)
+    routes = random_routes(g, n_tokens, n_experts, ragged=n_tokens == 5)
+    pages_dev, shared_dev = [dev_page(p, hidden, inter) for p in pages], dev_page(shared, hidden, inter)
+    blk = MoeBlock(ctx, hidden, inter, 16)
+    try:
+        y = run_block(ctx, blk, x, pages_dev, shared_dev, routes)
+        chunks, n_up, n_down, bad = blk.last_counts()
+        assert bad == 0 and n_up == chunks * (inter // 64) and n_down == chunks * (hidden // 128)
+        members = {}
+        for ids, _ in routes:
+            for e in ids:
+                members[e] = members.get(e, 0) + 1
+        assert chunks == sum(-(-m // 6) for m in members.values()) + -(-n_tokens // 6)
+        ctx.set_accumulation(L.ACCUM_PAIRWISE)
+        for t in range(n_tokens):
+            ids, w = routes[t]
+            ref = oracle.moe_layer_acc64(x[t], [pages[i] for i in ids], w, shared, 0, hidden, inter)
+            bad_at = np.nonzero(y[t].view(np.uint32) != ref.view(np.uint32))[0]
+            assert bad_at.size == 0, (t, bad_at.size, bad_at[:8], y[t][bad_at[:4]], ref[bad_at[:4]])
+            single = run_layer(ctx, x[t:t + 1], pages_dev, shared_dev, [routes[t]], L.PAGE_MXFP4, hidden, inter)[0]
+            assert np.array_equal(single.view(np.uint32), y[t].view(np.uint32))
+        # the same block again on the same object, and without a shared expert
+        y2 = run_block(ctx, blk, x, pages_dev, shared_dev, routes)
+        assert np.array_equal(y2.view(np.uint32), y.view(np.uint32))
+        full = [r for r in routes if len(r[0]) > 0]
+        y3 = run_block(ctx, blk, x, pages_dev, None, full)
+        for t in (0, n_tokens - 1):
+            single = run_layer(ctx, x[t:t + 1], pages_dev, None, [routes[t]], L.PAGE_MXFP4, hidden, inter)[0]
+            assert np.array_equal(single.view(np.uint32), y3[t].view(np.uint32))
+    finally:
+        blk.close()
+
+
+def test_block_at_the_benchmark_shape(ctx, oracle):
+    """4096 x 2048, 48 experts.  A verify block of 8 tokens against the oracle, bit for bit; 40 tokens
+    (every expert several tokens, the shared expert seven chunks) against every token's own one-token
+    call, which the other tests pin to the oracle."""
+    hidden, inter, n_experts = 4096, 2048, 48
+    g, pages, shared = make_layer(1977, hidden, inter, n_experts, L.PAGE_MXFP4)
+    pages_dev, shared_dev = [dev_page(p, hidden, inter) for p in pages], dev_page(shared, hidden, inter)
+    blk = MoeBlock(ctx, hidden, inter, 64)
+    try:
+        x = synth.activations(g, 8, hidden)
+        routes = random_routes(g, 8, n_experts)
+        y = run_block(ctx, blk, x, pages_dev, shared_dev, routes)
+        for t in range(8):
+            ids, w = routes[t]
+            ref = oracle.moe_layer_acc64(x[t], [pages[i] for i in ids], w, shared, 0, hidden, inter)
+            assert np.array_equal(y[t].view(np.uint32), ref.view(np.uint32)), t
+        x = synth.activations(g, 40, hidden)
+        routes = random_routes(g, 40, n_experts)
+        y = run_block(ctx, blk, x, pages_dev, shared_dev, routes)
+        ctx.set_accumulation(L.ACCUM_PAIRWISE)
+        for t in range(40):
+            single = run_layer(ctx, x[t:t + 1], pages_dev, shared_dev, [routes[t]], L.PAGE_MXFP4, hidden, inter)[0]
+            assert np.array_equal(single.view(np.uint32), y[t].view(np.uint32)), t
+    finally:
+        blk.close()
+
+
+@pytest.mark.parametrize("score_fn", [L.SCORE_SIGMOID, L.SCORE_SQRT_SOFTPLUS])
+def test_routed_block_picks_the_oracles_routes(ctx, oracle, score_fn):
+    """Router on the device for 24 tokens over 32 experts: ids and weights are the oracle's, every
+    token's y is the oracle's layer for those routes, bit for bit."""
+    hidden, inter, n_experts, n_tokens = 2048, 1024, 32, 24
+    g, pages, shared = make_layer(1300 + score_fn, hidden, inter, n_experts, L.PAGE_MXFP4)
+    wr, bias = synth.router_weight_bf16(g, n_experts, hidden), synth.router_bias(g, n_experts)
+    x = synth.activations(g, n_tokens, hidden)
+    pages_dev, shared_dev = [dev_page(p, hidden, inter) for p in pages], dev_page(shared, hidden, inter)
+    table = torch.tensor([p.data_ptr() for p in pages_dev], dtype=torch.int64, device="cuda")
+    ids = torch.empty((n_tokens, 6), dtype=torch.int32, device="cuda")
+    wts = torch.empty((n_tokens, 6), dtype=torch.float32, device="cuda")
+    dx = dev(x)
+    dy = torch.full_like(dx, float("nan"))
+    blk = MoeBlock(ctx, hidden, inter, 32)
+    try:
+        blk.cmd_routed_moe_block(dx, dev(wr), dev(bias), table, shared_dev.data_ptr(), dy, ids, wts,
+                                 score_fn=score_fn, top_k=6, route_scale=1.5)
+        torch.cuda.synchronize()
+        assert ctx.device_status() == 0
+        y = dy.cpu().numpy()
+        for t in range(n_tokens):
+            rid, rw, _, _ = oracle.router(x[t], wr, bias, score_fn=score_fn, top_k=6, route_scale=1.5)
+            assert np.array_equal(ids[t].cpu().numpy(), rid)
+            assert np.array_equal(wts[t].cpu().numpy().view(np.uint32), rw.view(np.uint32))
+            ref = oracle.moe_layer_acc64(x[t], [pages[i] for i in rid], rw, shared, 0, hidden, inter)
+            assert np.array_equal(y[t].view(np.uint32), ref.view(np.uint32)), t
+        # without the optional outputs the object's own buffers hold the routes
+        dy2 = torch.full_like(dx, float("nan"))
+        blk.cmd_routed_moe_block(dx, dev(wr), dev(bias), table, shared_dev.data_ptr(), dy2,
+                                 score_fn=score_fn, top_k=6, route_scale=1.5)
+        torch.cuda.synchronize()
+        assert np.array_equal(dy2.cpu().numpy().view(np.uint32), y.view(np.uint32))
+    finally:
+        blk.close()
+
+
+def test_block_rejects_what_it_cannot_run(ctx):
+    hidden, inter = 1024, 1024
+    with pytest.raises(S14Error):
+        MoeBlock(ctx, 1000, inter, 8)
+    with pytest.raises(S14Error):
+        MoeBlock(ctx, hidden, inter, 0)
+    with pytest.raises(S14Error):
+        MoeBlock(ctx, hidden, inter, 5000)
+    blk = MoeBlock(ctx, hidden, inter, 4)
+    try:
+        from colormlm_b200.pages import ExpertPageLayout
+        page = torch.zeros(ExpertPageLayout(hidden, inter).page_bytes, dtype=torch.uint8, device="cuda")
+        x = torch.zeros((5, hidden), device="cuda")
+        y = torch.empty_like(x)
+        ok = TokenRoute([0, 1], [0.5, 0.5], [page.data_ptr()] * 2)
+        with pytest.raises(S14Error):   # more tokens than the object holds
+            blk.cmd_moe_block(x, y, [ok] * 5, None)
+        for r in (TokenRoute([0, 0], [0.5, 0.5], [page.data_ptr()] * 2),
+                  TokenRoute([0, 300], [0.5, 0.5], [page.data_ptr()] * 2),
+                  TokenRoute([0, 1], [0.5, float("nan")], [page.data_ptr()] * 2),
+                  TokenRoute([0, 1], [0.5, 0.5], [page.data_ptr(), 0]),
+                  TokenRoute([], [], [])):
+            with pytest.raises(S14Error):
+                blk.cmd_moe_block(x[:1], y[:1], [r], None)
+        blk.cmd_moe_block(x[:2], y[:2], [ok, ok], None)
+        torch.cuda.synchronize()
+        assert ctx.device_status() == 0
+        assert torch.count_nonzero(y[:2]).item() == 0   # zero pages: every output is +0
+    finally:
+        blk.close()
