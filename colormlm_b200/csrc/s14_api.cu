@@ -1792,8 +1792,6 @@ extern "C" int32_t s14_block_destroy(s14_block *blk) {
     cudaSetDevice(blk->ctx->device);
     cudaDeviceSynchronize();
     cudaFree(blk->w.chunks);
-    cudaFree(blk->w.items_up);
-    cudaFree(blk->w.items_down);
     cudaFree(blk->w.counts);
     cudaFree(blk->w.xdig);
     cudaFree(blk->w.xexp);
@@ -1826,10 +1824,8 @@ extern "C" int32_t s14_block_create(s14_ctx *ctx, uint32_t hidden, uint32_t inte
     blk->inter = inter;
     blk->max_tokens = max_tokens;
     const size_t T = max_tokens, P = T * (S14_EXPERTS_PER_TOKEN + 1), C = moe_block_max_chunks(max_tokens);
-    const size_t S = inter >> 6, RT = hidden >> 7, R = S14_EXPERTS_PER_TOKEN;
+    const size_t R = S14_EXPERTS_PER_TOKEN;
     CUDA_OK(cudaMalloc((void **)&blk->w.chunks, C * sizeof(BlockChunk)));
-    CUDA_OK(cudaMalloc((void **)&blk->w.items_up, C * S * sizeof(uint32_t)));
-    CUDA_OK(cudaMalloc((void **)&blk->w.items_down, C * RT * sizeof(uint32_t)));
     CUDA_OK(cudaMalloc((void **)&blk->w.counts, 64));
     CUDA_OK(cudaMalloc((void **)&blk->w.xdig, T * (hidden >> 8) * 2048u));
     CUDA_OK(cudaMalloc((void **)&blk->w.xexp, T * (hidden >> 5)));
@@ -1921,6 +1917,7 @@ extern "C" int32_t s14_cmd_routed_moe_block(s14_ctx *ctx, void *stream, s14_bloc
     const s14_router_desc &r = desc->router;
     if (r.hidden != blk->hidden || desc->inter != blk->inter)
         throw ContractError("s14_cmd_routed_moe_block: sizes differ from the block object's");
+    if (r.hidden > 8192u) throw ContractError("s14_cmd_routed_moe_block: hidden above 8192");
     if (r.n_tokens == 0 || r.n_tokens > blk->max_tokens)
         throw ContractError("s14_cmd_routed_moe_block: more tokens than the block object was created for");
     if (r.n_experts == 0 || r.n_experts > S14_N_ROUTED_EXPERTS) throw ContractError("S14 router: 1..256 experts");
@@ -1942,7 +1939,7 @@ extern "C" int32_t s14_cmd_routed_moe_block(s14_ctx *ctx, void *stream, s14_bloc
     if (!rd.ids_out) rd.ids_out = blk->ids;
     if (!rd.weights_out) rd.weights_out = blk->weights;
     cudaError_t err;
-    ctx->launches += launch_router(st, rd, blk->scores, blk->select, nullptr, nullptr, nullptr, 0, blk->counter, &err);
+    ctx->launches += launch_router_batch(st, rd, blk->scores, blk->select, &err);
     if (err != cudaSuccess) return cuda_fail(err, "S14 router launch");
     return block_launch(blk, st, r.x, desc->y, rd.ids_out, rd.weights_out, nullptr, desc->page_table, desc->shared_page,
                         r.n_tokens, r.top_k, r.n_experts);

@@ -164,19 +164,20 @@ cudaError_t launch_greedy_argmax(cudaStream_t st, const float *logits, uint32_t 
                                  int64_t *result);
 
 // ---- a block of tokens through one layer, grouped by expert (s14_moe_block.cu) ----
-constexpr uint32_t kBlockNt = 6;  // tokens of one chunk: the MMA's N is 16 per token
-// Up to kBlockNt (token, route) pairs that share an expert page.
+constexpr uint32_t kBlockNt = 6;  // most tokens of one chunk: the MMA's N is 16 per token
+// Up to kBlockNt (token, route) pairs that share an expert page.  The chunks of one expert follow
+// one another: c0 is the first of them, nch their number.
 struct BlockChunk {
     const uint8_t *page;
     uint32_t nt;               // pairs in the chunk
-    uint32_t multi;            // the expert has more than one chunk
+    uint32_t c0, nch;
     uint32_t tok[kBlockNt];    // the pairs' tokens (rows of x)
     uint32_t pair[kBlockNt];   // token * 7 + position in the mix (6: the shared expert)
+    uint32_t pad;
 };
 // Device workspace of a block object, sized for max_tokens at creation.
 struct BlockWork {
     BlockChunk *chunks;
-    uint32_t *items_up, *items_down;
     uint32_t *counts;          // [0] chunks, [1] up items, [2] down items, [3] an expert id was out of range
     uint8_t *xdig, *xexp;      // the tokens' digit tiles and block exponents
     uint8_t *hdig, *hexp;      // the pairs' hidden values likewise
@@ -190,7 +191,11 @@ size_t moe_block_max_chunks(uint32_t max_tokens);
 int launch_moe_block(cudaStream_t st, int sm_count, const BlockWork &w, const float *x, float *y, const int32_t *ids,
                      const float *weights, const uint8_t *const *pages, const uint8_t *const *page_table,
                      const uint8_t *shared_page, uint32_t n_tokens, uint32_t top_k, uint32_t n_experts, uint32_t hidden,
-                     uint32_t inter, uint32_t *status, cudaError_t *err);
+                     uint32_t inter, uint32_t *status, cudaError_t *err, uint32_t nt_cap = 0);
+// Scores and routes of many tokens (s14_kernels.cu): the tokens of a tile share the router rows in
+// shared memory; one warp per token selects.  Same arithmetic as launch_router.  Returns the number
+// of kernels launched.
+int launch_router_batch(cudaStream_t st, const s14_router_desc &r, float *scores, float *select, cudaError_t *err);
 
 }  // namespace s14
 

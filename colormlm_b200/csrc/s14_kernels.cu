@@ -1228,6 +1228,98 @@ k_stack_step(const float *__restrict__ x, const float *__restrict__ y, float *ou
     out[i] = residual ? __fadd_rn(x[i], v) : v;
 }
 
+// ---- the router for many tokens ----
+// Scores: a CTA holds the BF16 rows of eight experts in shared memory and walks a tile of 32 tokens,
+// one warp per token at a time: logit in double (every product f32 x bf16 is exact in double), score
+// and score + bias in F32 -- the arithmetic of k_router.
+constexpr uint32_t kRbTokens = 32;
+template <uint32_t kRbExperts>
+__global__ void __launch_bounds__(256)
+k_router_scores_batch(const float *__restrict__ x, const uint16_t *__restrict__ wr, const float *__restrict__ bias,
+                      float *__restrict__ scores, float *__restrict__ select, uint32_t n_experts, uint32_t hidden,
+                      uint32_t n_tokens, uint32_t score_fn) {
+    extern __shared__ __align__(16) uint16_t s_w[];  // [kRbExperts][hidden]
+    const uint32_t e0 = blockIdx.x * kRbExperts, t0 = blockIdx.y * kRbTokens;
+    const uint32_t warp = threadIdx.x >> 5, lane = threadIdx.x & 31u;
+    const uint32_t pieces = hidden >> 3;  // 16-byte pieces (8 weights) per row
+    for (uint32_t i = threadIdx.x; i < kRbExperts * pieces; i += blockDim.x) {
+        const uint32_t e = i / pieces, p = i - e * pieces;
+        uint4 q = make_uint4(0u, 0u, 0u, 0u);
+        if (e0 + e < n_experts) q = __ldg(reinterpret_cast<const uint4 *>(wr + (size_t)(e0 + e) * hidden) + p);
+        reinterpret_cast<uint4 *>(s_w)[i] = q;
+    }
+    __syncthreads();
+    for (uint32_t t = t0 + warp; t < t0 + kRbTokens && t < n_tokens; t += 8u) {
+        const float *xt = x + (size_t)t * hidden;
+        double acc[kRbExperts];
+#pragma unroll
+        for (uint32_t e = 0; e < kRbExperts; ++e) acc[e] = 0.0;
+        for (uint32_t p = lane; p < pieces; p += 32u) {
+            const float4 xa = __ldg(reinterpret_cast<const float4 *>(xt + p * 8u));
+            const float4 xb = __ldg(reinterpret_cast<const float4 *>(xt + p * 8u + 4u));
+            const double xv[8] = {xa.x, xa.y, xa.z, xa.w, xb.x, xb.y, xb.z, xb.w};
+#pragma unroll
+            for (uint32_t e = 0; e < kRbExperts; ++e) {
+                const uint4 q = reinterpret_cast<const uint4 *>(s_w + (size_t)e * hidden)[p];
+                const uint32_t wd[4] = {q.x, q.y, q.z, q.w};
+                double a0 = 0.0, a1 = 0.0;
+#pragma unroll
+                for (int i = 0; i < 4; ++i) {
+                    a0 += xv[i * 2] * (double)__uint_as_float(wd[i] << 16);
+                    a1 += xv[i * 2 + 1] * (double)__uint_as_float(wd[i] & 0xffff0000u);
+                }
+                acc[e] += a0 + a1;
+            }
+        }
+#pragma unroll
+        for (uint32_t e = 0; e < kRbExperts; ++e) {
+            const double sum = warp_sum(acc[e]);
+            if (lane == 0 && e0 + e < n_experts) {
+                const float sc = router_score_f32(sum, score_fn);
+                scores[(size_t)t * n_experts + e0 + e] = sc;
+                select[(size_t)t * n_experts + e0 + e] = __fadd_rn(sc, bias ? bias[e0 + e] : 0.0f);
+            }
+        }
+    }
+}
+
+// One warp per token picks the routes from the scores.
+__global__ void __launch_bounds__(256)
+k_router_select_batch(const float *__restrict__ scores, const float *__restrict__ select, uint32_t n_experts, uint32_t n_tokens,
+                      uint32_t top_k, float route_scale, int32_t *__restrict__ ids_out, float *__restrict__ weights_out) {
+    const uint32_t t = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+    if (t >= n_tokens) return;
+    router_select(scores + (size_t)t * n_experts, select + (size_t)t * n_experts, n_experts, top_k, route_scale,
+                  ids_out + (size_t)t * top_k, weights_out + (size_t)t * top_k, nullptr, nullptr, nullptr, 0, threadIdx.x & 31u, 0,
+                  1, 0);
+}
+
+int launch_router_batch(cudaStream_t st, const s14_router_desc &r, float *scores, float *select, cudaError_t *err) {
+    // few tokens: two experts per CTA, so that the grid covers the SMs; many: eight, which share a token's loads
+    const uint32_t per_cta = r.n_tokens <= kRbTokens ? 2u : 8u;
+    const size_t smem = (size_t)per_cta * r.hidden * sizeof(uint16_t);
+    static bool attr_set[64] = {};
+    int dev = 0;
+    *err = cudaGetDevice(&dev);
+    if (*err != cudaSuccess) return 0;
+    if (dev >= 0 && dev < 64 && !attr_set[dev]) {
+        *err = cudaFuncSetAttribute(k_router_scores_batch<8>, cudaFuncAttributeMaxDynamicSharedMemorySize, 8 * 8192 * 2);
+        if (*err != cudaSuccess) return 0;
+        attr_set[dev] = true;
+    }
+    const dim3 grid(ceil_div(r.n_experts, per_cta), ceil_div(r.n_tokens, kRbTokens));
+    if (per_cta == 2u)
+        k_router_scores_batch<2><<<grid, 256, smem, st>>>(r.x, r.router_weight_bf16, r.bias, scores, select, r.n_experts, r.hidden,
+                                                         r.n_tokens, r.score_fn);
+    else
+        k_router_scores_batch<8><<<grid, 256, smem, st>>>(r.x, r.router_weight_bf16, r.bias, scores, select, r.n_experts, r.hidden,
+                                                         r.n_tokens, r.score_fn);
+    k_router_select_batch<<<ceil_div(r.n_tokens, 8), 256, 0, st>>>(scores, select, r.n_experts, r.n_tokens, r.top_k,
+                                                                  r.route_scale, r.ids_out, r.weights_out);
+    *err = cudaGetLastError();
+    return 2;
+}
+
 cudaError_t launch_stack_step(cudaStream_t st, const float *x, const float *y, float *out, float *y_copy,
                               uint32_t n, bool residual) {
     k_stack_step<<<ceil_div(n, 256), 256, 0, st>>>(x, y, out, y_copy, n, residual ? 1u : 0u);

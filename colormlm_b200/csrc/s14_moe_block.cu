@@ -39,12 +39,12 @@ namespace {
 
 constexpr uint32_t kNt = kBlockNt;
 constexpr uint32_t kStageA = kUnitStride;                  // a unit's codes, then its scales
-constexpr uint32_t kStage = kStageA + kNt * 2048u;         // ... then the chunk's token tiles of the unit's K range
-static_assert(kStage % 1024u == 0u && kStageA % 1024u == 0u, "operand tiles keep the 1 KB alignment of the 128-byte swizzle");
+// a ring stage: a unit, then the token tiles (2 KB each) of the unit's K range for as many tokens as a chunk may hold
+static_assert(kStageA % 1024u == 0u && 2048u % 1024u == 0u, "operand tiles keep the 1 KB alignment of the 128-byte swizzle");
 constexpr uint32_t kGThreads = 512;
-constexpr uint32_t kGRingMax = 8;
+constexpr uint32_t kGRingMax = 12;
 constexpr uint32_t kSfbBytes = 16u * 1024u;                // an item's digit-row scale atoms: K / 256 units x 1 KB, K <= 4096
-constexpr uint32_t kGProdWarp = 4, kGMmaWarp0 = 5, kGLayWarp0 = 8;
+constexpr uint32_t kGProdWarp = 4, kGMmaWarp0 = 5, kGTileWarp = 7, kGLayWarp0 = 8;
 constexpr uint32_t kGLayThreads = 256;
 // tensor memory columns
 constexpr uint32_t kGColAcc = 0;                           // [2 buffers][2 issuing threads][16 * kNt]
@@ -63,13 +63,12 @@ constexpr uint32_t kPairsPerToken = S14_EXPERTS_PER_TOKEN + 1;   // pair = token
 
 struct GemmArgs {
     const BlockChunk *chunks;
-    const uint32_t *items;      // chunk << 8 | slice (up) or row tile (down)
-    const uint32_t *n_items;    // device memory: written by the grouping kernel
+    const uint32_t *n_items;    // device memory: written by the grouping kernel (chunks x slices or row tiles)
     const uint8_t *dig;         // digit tiles of the B vectors [vector][K / 256][2048]
     const uint8_t *exps;        // their block exponents + 100, [vector][K / 32]
     float *out;                 // down: the pairs' expert outputs [pair][hidden]
     uint8_t *hdig, *hexp;       // up: digit tiles and exponents of the pairs' hidden values
-    uint32_t hidden, inter, ring;
+    uint32_t hidden, inter, ring, stage;   // stage: bytes of a ring stage (a unit and nt_cap token tiles)
 };
 
 // The digit tiles and block exponents of n vectors of K elements (one CTA per vector).
@@ -84,21 +83,28 @@ k_block_digits(const float *__restrict__ x, uint32_t K, uint8_t *__restrict__ di
 }
 
 // Groups the block's (token, route) pairs by expert.  Group 0 is the shared expert (every token, mix
-// position 6), group 1 + e the routed expert e; a group's members are taken in ascending (token,
-// position) order and cut into chunks of kBlockNt.  ids: [T, top_k] expert ids, negative = no route.
-// The page of a routed group is page_table[e], or, with per-route pages, the page of its first
-// member.  counts: [0] chunks, [1] up items, [2] down items, [3] 1 if an id was out of range.
-// One CTA of 1024 threads.
+// position 6), group 1 + e the routed expert e; a group's members are cut into chunks of nt_cap (the
+// shared expert's in token order, a routed expert's in the order its members arrive: every pair's
+// result depends on that pair alone, so the order changes no bit of the output).  ids: [T, top_k]
+// expert ids, negative = no route.  The page of a routed group is page_table[e], or, with per-route
+// pages, the page of one of its members.  counts: [0] chunks, [1] up items, [2] down items, [3] 1 if
+// an id was out of range (then no chunk is made).  One CTA of 1024 threads.
 __global__ void __launch_bounds__(1024)
 k_block_group(const int32_t *__restrict__ ids, const uint8_t *const *__restrict__ pages,
               const uint8_t *const *__restrict__ page_table, const uint8_t *shared_page, uint32_t T, uint32_t top_k,
-              uint32_t n_experts, uint32_t S, uint32_t RT, BlockChunk *__restrict__ chunks,
-              uint32_t *__restrict__ items_up, uint32_t *__restrict__ items_down, uint32_t *__restrict__ counts) {
-    __shared__ uint32_t cnt[S14_N_ROUTED_EXPERTS + 1];
-    __shared__ uint32_t chunk0[S14_N_ROUTED_EXPERTS + 2];
+              uint32_t n_experts, uint32_t S, uint32_t RT, uint32_t nt_cap, BlockChunk *__restrict__ chunks,
+              uint32_t *__restrict__ counts) {
+    constexpr uint32_t kG = S14_N_ROUTED_EXPERTS + 1;
+    __shared__ uint32_t cnt[kG], fill[kG], chunk0[kG + 1];
+    __shared__ unsigned long long gpage[kG];
     __shared__ uint32_t bad;
-    const uint32_t tid = threadIdx.x, G = n_experts + 1u, n = T * top_k;
-    if (tid <= S14_N_ROUTED_EXPERTS) cnt[tid] = 0u;
+    const uint32_t tid = threadIdx.x, lane = tid & 31u, G = n_experts + 1u, n = T * top_k;
+    if (tid < kG) {
+        cnt[tid] = 0u;
+        fill[tid] = 0u;
+        gpage[tid] = tid == 0u ? (unsigned long long)shared_page
+                               : ((page_table && tid < G) ? (unsigned long long)page_table[tid - 1u] : 0ull);
+    }
     if (tid == 0) bad = 0u;
     __syncthreads();
     for (uint32_t i = tid; i < n; i += blockDim.x) {
@@ -108,58 +114,91 @@ k_block_group(const int32_t *__restrict__ ids, const uint8_t *const *__restrict_
     }
     if (tid == 0 && shared_page) cnt[0] = T;
     __syncthreads();
-    if (tid == 0) {
-        uint32_t c = 0;
-        for (uint32_t g = 0; g < G; ++g) {
-            chunk0[g] = c;
-            c += (cnt[g] + kNt - 1u) / kNt;
+    if (tid < 32u) {
+        // exclusive scan of the groups' chunk counts: nine groups per lane
+        constexpr uint32_t kPer = (kG + 31u) / 32u;
+        uint32_t mine = 0;
+        for (uint32_t k = 0; k < kPer; ++k) {
+            const uint32_t g = lane * kPer + k;
+            if (g < G) mine += (cnt[g] + nt_cap - 1u) / nt_cap;
         }
-        chunk0[G] = c;
-        if (bad) c = 0;  // the contraction kernels find no item and the mix writes nothing
-        counts[0] = c;
-        counts[1] = c * S;
-        counts[2] = c * RT;
-        counts[3] = bad;
+        uint32_t incl = mine;
+#pragma unroll
+        for (int o = 1; o < 32; o <<= 1) {
+            const uint32_t v = __shfl_up_sync(0xffffffffu, incl, o);
+            if ((int)lane >= o) incl += v;
+        }
+        uint32_t c = incl - mine;
+        for (uint32_t k = 0; k < kPer; ++k) {
+            const uint32_t g = lane * kPer + k;
+            if (g < G) {
+                chunk0[g] = c;
+                c += (cnt[g] + nt_cap - 1u) / nt_cap;
+            }
+        }
+        const uint32_t total = __shfl_sync(0xffffffffu, incl, 31);
+        if (lane == 0) {
+            chunk0[G] = total;
+            const uint32_t c_all = bad ? 0u : total;  // with a bad id the contraction kernels find no item, the mix writes nothing
+            counts[0] = c_all;
+            counts[1] = c_all * S;
+            counts[2] = c_all * RT;
+            counts[3] = bad;
+        }
     }
     __syncthreads();
-    if (tid >= G || cnt[tid] == 0u || bad) return;
-    const uint32_t g = tid, c0 = chunk0[g], nch = chunk0[g + 1u] - c0, members = cnt[g];
-    const uint8_t *page = g == 0u ? shared_page : (page_table ? page_table[g - 1u] : nullptr);
-    if (g == 0u) {
-        for (uint32_t t = 0; t < T; ++t) {
-            BlockChunk *ch = chunks + c0 + t / kNt;
-            ch->tok[t % kNt] = t;
-            ch->pair[t % kNt] = t * kPairsPerToken + S14_EXPERTS_PER_TOKEN;
-        }
-    } else {
-        uint32_t k = 0;
-        for (uint32_t i = 0; i < n && k < members; ++i) {
-            if (__ldg(ids + i) != (int32_t)(g - 1u)) continue;
-            const uint32_t t = i / top_k, m = i - t * top_k;
-            if (k == 0u && !page_table) page = pages[i];
-            BlockChunk *ch = chunks + c0 + k / kNt;
-            ch->tok[k % kNt] = t;
-            ch->pair[k % kNt] = t * kPairsPerToken + m;
-            ++k;
+    if (bad) return;
+    for (uint32_t i = tid; i < n; i += blockDim.x) {
+        const int32_t e = __ldg(ids + i);
+        if (e < 0) continue;
+        const uint32_t g = 1u + (uint32_t)e, t = i / top_k, m = i - t * top_k;
+        const uint32_t k = atomicAdd(&fill[g], 1u);
+        if (k == 0u && !page_table) gpage[g] = (unsigned long long)pages[i];
+        BlockChunk *ch = chunks + chunk0[g] + k / nt_cap;
+        ch->tok[k % nt_cap] = t;
+        ch->pair[k % nt_cap] = t * kPairsPerToken + m;
+    }
+    if (shared_page) {
+        for (uint32_t t = tid; t < T; t += blockDim.x) {
+            BlockChunk *ch = chunks + chunk0[0] + t / nt_cap;
+            ch->tok[t % nt_cap] = t;
+            ch->pair[t % nt_cap] = t * kPairsPerToken + S14_EXPERTS_PER_TOKEN;
         }
     }
-    for (uint32_t k = 0; k < nch; ++k) {
-        BlockChunk *ch = chunks + c0 + k;
-        ch->page = page;
-        ch->nt = k + 1u < nch ? kNt : members - k * kNt;
-        ch->multi = nch > 1u ? 1u : 0u;
+    __syncthreads();
+    const uint32_t total = chunk0[G];
+    for (uint32_t c = tid; c < total; c += blockDim.x) {
+        // the chunk's group: the last g with chunk0[g] <= c
+        uint32_t lo = 0, hi = G;
+        while (hi - lo > 1u) {
+            const uint32_t mid = (lo + hi) >> 1;
+            if (chunk0[mid] <= c) lo = mid;
+            else hi = mid;
+        }
+        const uint32_t g = lo, c0 = chunk0[g], nch = chunk0[g + 1u] - c0;
+        BlockChunk *ch = chunks + c;
+        ch->page = reinterpret_cast<const uint8_t *>(gpage[g]);
+        ch->nt = c + 1u < c0 + nch ? nt_cap : cnt[g] - (c - c0) * nt_cap;
+        ch->c0 = c0;
+        ch->nch = nch;
     }
-    for (uint32_t r = 0; r < S; ++r)
-        for (uint32_t k = 0; k < nch; ++k) items_up[(size_t)c0 * S + r * nch + k] = ((c0 + k) << 8) | r;
-    for (uint32_t r = 0; r < RT; ++r)
-        for (uint32_t k = 0; k < nch; ++k) items_down[(size_t)c0 * RT + r * nch + k] = ((c0 + k) << 8) | r;
 }
+
+// An item as the CTA's roles read it, decoded once per batch into shared memory.
+struct ItemRec {
+    unsigned long long page;
+    uint32_t nt, r;            // pairs of the chunk; slice (up) or row tile (down)
+    uint32_t tok[kNt];
+    uint32_t pair[kNt];
+};
+constexpr uint32_t kBatch = 192;   // items decoded at a time
 
 template <bool kDown>
 __global__ void __launch_bounds__(kGThreads, 1)
 k_block_gemm(const __grid_constant__ GemmArgs a, uint32_t *status) {
     extern __shared__ __align__(1024) uint8_t smem[];
     __shared__ __align__(8) uint64_t bars[kGBars];
+    __shared__ __align__(16) ItemRec s_rec[kBatch];
     __shared__ float s_up[kNt][64];                          // an item's up projections, handed to the gate threads
     __shared__ __align__(16) uint8_t s_hst[kNt][16 * 2 * 16]; // an up item's digit chunks per token: [row][block][16 bytes]
     __shared__ uint32_t tmem_slot, s_units;
@@ -172,7 +211,7 @@ k_block_gemm(const __grid_constant__ GemmArgs a, uint32_t *status) {
     const uint32_t KD = a.inter >> 8;
     const uint32_t ring = a.ring;
     uint8_t *const sRing = smem;
-    uint8_t *const sSfb = smem + ring * kStage;      // [2][kSfbBytes]
+    uint8_t *const sSfb = smem + ring * a.stage;     // [2][kSfbBytes]
     const size_t page_off = kDown ? mxfp4_down_offset(a.hidden, a.inter) : 0u;
     const uint32_t bar0 = smem_u32(bars);
     auto bar = [&](uint32_t i) { return bar0 + i * 8u; };
@@ -201,231 +240,282 @@ k_block_gemm(const __grid_constant__ GemmArgs a, uint32_t *status) {
     fence_after();
     const uint32_t tmem = tmem_slot;
     const uint32_t n_items = __ldcg(a.n_items);
+    // The CTA's items are q = cta, cta + grid, ...  The chunks of one expert follow one another and so
+    // do their items, a row tile's chunks side by side (so that CTAs that run at the same time share
+    // the expert's units in the L2).
+    const uint32_t R = kDown ? (a.hidden >> 7) : (a.inter >> 6);
+    const uint32_t n_local = n_items > cta ? (n_items - cta + grid - 1u) / grid : 0u;
 
-    if (tid == kGProdWarp * 32u) {
-        // ---- the copying thread: per unit of every item one ring stage ----
-        const unsigned long long once = l2_policy_evict_first();
-        uint32_t slot = 0, round = 0, units = 0;
-        bool ok = true;
+    const bool is_prod_a = tid == kGProdWarp * 32u, is_prod_b = tid == kGTileWarp * 32u;
+    const bool is_issuer = (warp == kGMmaWarp0 || warp == kGMmaWarp0 + 1u) && lane == 0;
+    // what the roles carry from item to item
+    uint32_t p_slot = 0, p_round = 0, p_units = 0;             // the copying threads: next stage
+    uint32_t m_slot = warp - kGMmaWarp0, m_round = 0;          // the issuing threads: next stage of their own
+    uint32_t gi = 0;                                           // items so far
+    bool ok = true;
+    const unsigned long long once = l2_policy_evict_first();
+
 #pragma unroll 1
-        for (uint32_t q = cta; q < n_items && ok; q += grid) {
-            const uint32_t item = __ldg(a.items + q), r = item & 0xFFu;
-            const BlockChunk *ch = a.chunks + (item >> 8);
-            const uint32_t nt = __ldg(&ch->nt), multi = __ldg(&ch->multi);
-            uint32_t vec[kNt];
+    for (uint32_t base = 0; base < n_local; base += kBatch) {
+        const uint32_t nb = n_local - base < kBatch ? n_local - base : kBatch;
+        // ---- the batch's items into shared memory: every thread decodes one (two dependent loads and
+        // the chunk's record, all threads' in flight together), so that no role waits for global
+        // memory at an item's start ----
+        for (uint32_t i = tid; i < nb; i += kGThreads) {
+            const uint32_t q = cta + (base + i) * grid;
+            const BlockChunk *g = a.chunks + q / R;
+            const uint32_t c0 = __ldg(&g->c0), nch = __ldg(&g->nch), j = q - c0 * R;
+            const uint32_t r = j / nch;
+            const BlockChunk *ch = a.chunks + c0 + (j - r * nch);
+            ItemRec rec;
+            rec.page = __ldg(reinterpret_cast<const unsigned long long *>(&ch->page));
+            rec.nt = __ldg(&ch->nt) | (nch > 1u ? 0x100u : 0u);
+            rec.r = r;
 #pragma unroll
-            for (uint32_t t = 0; t < kNt; ++t) vec[t] = kDown ? __ldg(&ch->pair[t]) : __ldg(&ch->tok[t]);
-            const uint8_t *src = reinterpret_cast<const uint8_t *>(__ldg(reinterpret_cast<const unsigned long long *>(&ch->page))) +
-                                 page_off + (size_t)r * nu * kUnitStride;
+            for (uint32_t t = 0; t < kNt; ++t) {
+                rec.tok[t] = __ldg(&ch->tok[t]);
+                rec.pair[t] = __ldg(&ch->pair[t]);
+            }
+            s_rec[i] = rec;
+        }
+        __syncthreads();
+
+        if (is_prod_a) {
+            // ---- the copying thread of the pages: per unit of every item one ring stage; it arms the
+            // stage's barrier with the bytes of the unit and of the token tiles ----
 #pragma unroll 1
-            for (uint32_t u = 0; u < nu; ++u) {
-                if (round && !mbar_wait(bar(kGBarDone + slot), (round - 1u) & 1u, abortp)) {
-                    ok = false;
-                    break;
-                }
-                const uint32_t full = bar(kGBarFull + slot), dst = smem_u32(sRing) + slot * kStage;
-                mbar_arrive_expect(full, kStageA + nt * 2048u);
-                // an expert with one chunk is read once; with more, its later chunks want the units in the L2
-                if (multi) bulk_copy(dst, src, kStageA, full);
-                else bulk_copy_stream(dst, src, kStageA, full, once);
-#pragma unroll
-                for (uint32_t t = 0; t < kNt; ++t)
-                    if (t < nt) bulk_copy(dst + kStageA + t * 2048u, a.dig + ((size_t)vec[t] * nu + u) * 2048u, 2048u, full);
-                src += kUnitStride;
-                ++units;
-                if (++slot == ring) {
-                    slot = 0;
-                    ++round;
+            for (uint32_t i = 0; i < nb && ok; ++i) {
+                const uint32_t nt = s_rec[i].nt & 0xFFu, multi = s_rec[i].nt >> 8;
+                const uint8_t *src = reinterpret_cast<const uint8_t *>(s_rec[i].page) + page_off + (size_t)s_rec[i].r * nu * kUnitStride;
+#pragma unroll 1
+                for (uint32_t u = 0; u < nu; ++u) {
+                    if (p_round && !mbar_wait(bar(kGBarDone + p_slot), (p_round - 1u) & 1u, abortp)) {
+                        ok = false;
+                        break;
+                    }
+                    const uint32_t full = bar(kGBarFull + p_slot), dst = smem_u32(sRing) + p_slot * a.stage;
+                    mbar_arrive_expect(full, kStageA + nt * 2048u);
+                    // an expert with one chunk is read once; with more, its later chunks want the units in the L2
+                    if (multi) bulk_copy(dst, src, kStageA, full);
+                    else bulk_copy_stream(dst, src, kStageA, full, once);
+                    src += kUnitStride;
+                    ++p_units;
+                    if (++p_slot == ring) {
+                        p_slot = 0;
+                        ++p_round;
+                    }
                 }
             }
-        }
-        s_units = units;
-    } else if ((warp == kGMmaWarp0 || warp == kGMmaWarp0 + 1u) && lane == 0) {
-        // ---- MMA issue: thread m takes units m, m + 2, ... of every item (a ring slot always belongs
-        // to the same thread: items have an even number of units and the ring an even number of slots)
-        // and accumulates into an accumulator of its own; items alternate between two buffers ----
-        const uint32_t m = warp - kGMmaWarp0;
-        const uint64_t a_desc0 = smem_desc(smem_u32(sRing), 1, 64, 2);
-        const uint64_t sf_desc0 = smem_desc(smem_u32(sRing) + kUnitBytes, 0, 8, 0);
-        const uint64_t b_desc0 = smem_desc(smem_u32(sRing) + kStageA, 1, 64, 2);
-        const uint32_t sfa_t = tmem + kGColSfa + m * 16u, sfb_t = tmem + kGColSfb + m * 16u;
-        uint32_t m_slot = m, m_round = 0, gi = 0;
-        bool ok = true;
+            s_units = p_units;
+        } else if (is_prod_b) {
+            // ---- the copying thread of the token tiles: the chunk's tiles of the unit's K range behind the
+            // unit, counted on the same barrier (bytes that land before the barrier is armed are
+            // counted all the same) ----
 #pragma unroll 1
-        for (uint32_t q = cta; q < n_items && ok; q += grid, ++gi) {
-            const uint32_t item = __ldg(a.items + q), buf = gi & 1u;
-            const uint32_t nt = __ldg(&a.chunks[item >> 8].nt);
-            const uint32_t idesc = umma_idesc_mxf4(16u * nt);
-            if (gi >= 2u) ok = mbar_wait(bar(kGBarAccFree + buf), ((gi - 2u) >> 1) & 1u, abortp);
-            ok = ok && mbar_wait(bar(kGBarSfb + buf), (gi >> 1) & 1u, abortp);
-            if (!ok) break;
-            fence_after();
-            const uint32_t acc = tmem + kGColAcc + (buf * 2u + m) * (16u * kNt);
-            const uint64_t sfb_desc0 = smem_desc(smem_u32(sSfb) + buf * kSfbBytes, 0, 8, 0);
+            for (uint32_t i = 0; i < nb && ok; ++i) {
+                const uint32_t nt = s_rec[i].nt & 0xFFu;
+                uint32_t vec[kNt];
+#pragma unroll
+                for (uint32_t t = 0; t < kNt; ++t) vec[t] = kDown ? s_rec[i].pair[t] : s_rec[i].tok[t];
 #pragma unroll 1
-            for (uint32_t ku = m; ku < nu; ku += 2u) {
-                const uint32_t s = m_slot;
-                ok = mbar_wait(bar(kGBarFull + s), m_round & 1u, abortp);
+                for (uint32_t u = 0; u < nu; ++u) {
+                    if (p_round && !mbar_wait(bar(kGBarDone + p_slot), (p_round - 1u) & 1u, abortp)) {
+                        ok = false;
+                        break;
+                    }
+                    const uint32_t full = bar(kGBarFull + p_slot), dst = smem_u32(sRing) + p_slot * a.stage + kStageA;
+#pragma unroll
+                    for (uint32_t t = 0; t < kNt; ++t)
+                        if (t < nt) bulk_copy(dst + t * 2048u, a.dig + ((size_t)vec[t] * nu + u) * 2048u, 2048u, full);
+                    if (++p_slot == ring) {
+                        p_slot = 0;
+                        ++p_round;
+                    }
+                }
+            }
+        } else if (is_issuer) {
+            // ---- MMA issue: thread m takes units m, m + 2, ... of every item (a ring slot always belongs
+            // to the same thread: items have an even number of units and the ring an even number of slots)
+            // and accumulates into an accumulator of its own; items alternate between two buffers ----
+            const uint32_t m = warp - kGMmaWarp0;
+            const uint64_t a_desc0 = smem_desc(smem_u32(sRing), 1, 64, 2);
+            const uint64_t sf_desc0 = smem_desc(smem_u32(sRing) + kUnitBytes, 0, 8, 0);
+            const uint64_t b_desc0 = smem_desc(smem_u32(sRing) + kStageA, 1, 64, 2);
+            const uint32_t sfa_t = tmem + kGColSfa + m * 16u, sfb_t = tmem + kGColSfb + m * 16u;
+#pragma unroll 1
+            for (uint32_t i = 0; i < nb && ok; ++i, ++gi) {
+                const uint32_t buf = gi & 1u;
+                const uint32_t idesc = umma_idesc_mxf4(16u * (s_rec[i].nt & 0xFFu));
+                if (gi >= 2u) ok = mbar_wait(bar(kGBarAccFree + buf), ((gi - 2u) >> 1) & 1u, abortp);
+                ok = ok && mbar_wait(bar(kGBarSfb + buf), (gi >> 1) & 1u, abortp);
                 if (!ok) break;
-                m_slot += 2u;
-                if (m_slot >= ring) {
-                    m_slot -= ring;
-                    ++m_round;
-                }
                 fence_after();
-                const uint64_t sfd = sf_desc0 + s * (kStage >> 4), sbd = sfb_desc0 + ku * (1024u >> 4);
-                tmem_copy_scales(sfa_t, sfd);
-                tmem_copy_scales(sfa_t + 4u, sfd + (kAtomBytes >> 4));
-                tmem_copy_scales(sfb_t, sbd);
-                tmem_copy_scales(sfb_t + 4u, sbd + (kAtomBytes >> 4));
-                const uint64_t ad = a_desc0 + s * (kStage >> 4), bd = b_desc0 + s * (kStage >> 4);
+                const uint32_t acc = tmem + kGColAcc + (buf * 2u + m) * (16u * kNt);
+                const uint64_t sfb_desc0 = smem_desc(smem_u32(sSfb) + buf * kSfbBytes, 0, 8, 0);
+#pragma unroll 1
+                for (uint32_t ku = m; ku < nu; ku += 2u) {
+                    const uint32_t s = m_slot;
+                    ok = mbar_wait(bar(kGBarFull + s), m_round & 1u, abortp);
+                    if (!ok) break;
+                    m_slot += 2u;
+                    if (m_slot >= ring) {
+                        m_slot -= ring;
+                        ++m_round;
+                    }
+                    fence_after();
+                    const uint64_t sfd = sf_desc0 + s * (a.stage >> 4), sbd = sfb_desc0 + ku * (1024u >> 4);
+                    tmem_copy_scales(sfa_t, sfd);
+                    tmem_copy_scales(sfa_t + 4u, sfd + (kAtomBytes >> 4));
+                    tmem_copy_scales(sfb_t, sbd);
+                    tmem_copy_scales(sfb_t + 4u, sbd + (kAtomBytes >> 4));
+                    const uint64_t ad = a_desc0 + s * (a.stage >> 4), bd = b_desc0 + s * (a.stage >> 4);
 #pragma unroll
-                for (uint32_t kk = 0; kk < 4; ++kk) {
-                    const uint32_t atom = kk >> 1, sfid = (kk & 1u) * 2u;
-                    umma_mxf4(acc, ad + kk * 2u, bd + kk * 2u, idesc | (sfid << 29) | (sfid << 4),
-                              (sfa_t + atom * 4u) | (sfid << 30), (sfb_t + atom * 4u) | (sfid << 30), (ku >= 2u || kk) ? 1u : 0u);
+                    for (uint32_t kk = 0; kk < 4; ++kk) {
+                        const uint32_t atom = kk >> 1, sfid = (kk & 1u) * 2u;
+                        umma_mxf4(acc, ad + kk * 2u, bd + kk * 2u, idesc | (sfid << 29) | (sfid << 4),
+                                  (sfa_t + atom * 4u) | (sfid << 30), (sfb_t + atom * 4u) | (sfid << 30), (ku >= 2u || kk) ? 1u : 0u);
+                    }
+                    umma_commit(bar(kGBarDone + s));
                 }
-                umma_commit(bar(kGBarDone + s));
+                if (!ok) break;
+                umma_commit(bar(kGBarAccDone + buf));
             }
-            if (!ok) break;
-            umma_commit(bar(kGBarAccDone + buf));
+        } else if (warp < 4u) {
+            // ---- epilogue: per token of the chunk the two accumulators' sixteen digit columns, added in
+            // double and rounded once ----
+            const uint32_t row = tid;
+            const uint32_t lane_base = tmem + ((warp * 32u) << 16);
+#pragma unroll 1
+            for (uint32_t i = 0; i < nb && ok; ++i, ++gi) {
+                const uint32_t idx = s_rec[i].r, buf = gi & 1u, nt = s_rec[i].nt & 0xFFu;
+                uint32_t pair[kNt];
+#pragma unroll
+                for (uint32_t t = 0; t < kNt; ++t) pair[t] = s_rec[i].pair[t];
+                ok = epi_all(mbar_wait(bar(kGBarAccDone + buf), (gi >> 1) & 1u, abortp));
+                if (!ok) break;
+                fence_after();
+                float v[kNt];
+#pragma unroll
+                for (uint32_t t = 0; t < kNt; ++t) {
+                    v[t] = 0.0f;
+                    if (t < nt) {  // uniform in the CTA
+                        double sum = 0.0;
+#pragma unroll
+                        for (uint32_t half = 0; half < 2; ++half) {
+                            uint32_t r[16];
+                            tmem_ld16(lane_base + kGColAcc + (buf * 2u + half) * (16u * kNt) + 16u * t, r);
+                            tmem_ld_wait();
+                            double lo = 0.0, hi = 0.0;
+#pragma unroll
+                            for (int c = 0; c < 8; ++c) {
+                                lo += (double)__uint_as_float(r[8 + c]);
+                                hi += (double)__uint_as_float(r[c]);
+                            }
+                            sum += lo + hi;
+                        }
+                        v[t] = (float)sum;
+                    }
+                }
+                fence_before();
+                mbar_arrive(bar(kGBarAccFree + buf));
+                if constexpr (kDown) {
+                    // row idx * 128 + `row` of the pairs' expert outputs
+#pragma unroll
+                    for (uint32_t t = 0; t < kNt; ++t)
+                        if (t < nt) a.out[(size_t)pair[t] * a.hidden + idx * 128u + row] = v[t];
+                } else {
+                    // lanes 0-63: gate of the slice's element `row`; lanes 64-127: its up projection
+#pragma unroll
+                    for (uint32_t t = 0; t < kNt; ++t)
+                        if (t < nt && row >= 64u) s_up[t][row - 64u] = v[t];
+                    epi_sync();
+#pragma unroll
+                    for (uint32_t t = 0; t < kNt; ++t) {
+                        if (t < nt && row < 64u) {
+                            // hidden value `row` of the slice -> sixteen digit nibbles; scale block = warp
+                            const float hv = swiglu_limit_f32(v[t], s_up[t][row]);
+                            float bm = fabsf(hv);
+#pragma unroll
+                            for (int o = 16; o > 0; o >>= 1) bm = fmaxf(bm, __shfl_xor_sync(0xffffffffu, bm, o));
+                            const int E = block_exponent(bm);
+                            uint32_t hw, lw;
+                            digit_codes16(hv, __uint_as_float((uint32_t)(150 - E) << 23), hw, lw);
+                            const uint32_t ohw = __shfl_xor_sync(0xffffffffu, hw, 1), olw = __shfl_xor_sync(0xffffffffu, lw, 1);
+                            // byte lane / 2 of every row's chunk holds the nibbles of lanes 2b (low) and 2b + 1; even
+                            // lanes write digit rows 0-3 and 8-11, odd lanes 4-7 and 12-15
+                            const uint32_t e_hw = (lane & 1u) ? ohw : hw, o_hw = (lane & 1u) ? hw : ohw;
+                            const uint32_t e_lw = (lane & 1u) ? olw : lw, o_lw = (lane & 1u) ? lw : olw;
+#pragma unroll
+                            for (uint32_t jj = 0; jj < 4; ++jj) {
+                                const uint32_t dj = (lane & 1u) * 4u + jj;
+                                s_hst[t][(dj * 2u + warp) * 16u + (lane >> 1)] =
+                                    (uint8_t)(((e_hw >> (4u * dj)) & 0xFu) | (((o_hw >> (4u * dj)) & 0xFu) << 4));
+                                s_hst[t][((8u + dj) * 2u + warp) * 16u + (lane >> 1)] =
+                                    (uint8_t)(((e_lw >> (4u * dj)) & 0xFu) | (((o_lw >> (4u * dj)) & 0xFu) << 4));
+                            }
+                            if (lane == 0) a.hexp[(size_t)pair[t] * (a.inter >> 5) + idx * 2u + warp] = (uint8_t)(E + 100);
+                        }
+                    }
+                    epi_sync();
+                    // the slice's 32 chunks (digit row, block) of every token go to their places in the pair's
+                    // digit tile: 64 threads write half a chunk each; the two halves of the CTA take the
+                    // tokens alternately
+                    const uint32_t t64 = tid & 63u, ch16 = t64 >> 1, half = t64 & 1u, dj = ch16 >> 1, blk = ch16 & 1u;
+                    const uint32_t cc = (idx & 3u) * 2u + blk;
+                    const uint32_t o = (idx >> 2) * 2048u + dj * 128u + ((cc ^ (dj & 7u)) << 4) + half * 8u;
+#pragma unroll
+                    for (uint32_t t = 0; t < kNt; ++t) {
+                        if (t < nt && (t & 1u) == (tid >> 6)) {
+                            const uint2 c8 = *reinterpret_cast<const uint2 *>(&s_hst[t][(dj * 2u + blk) * 16u + half * 8u]);
+                            *reinterpret_cast<uint2 *>(a.hdig + (size_t)pair[t] * KD * 2048u + o) = c8;
+                        }
+                    }
+                }
+            }
+        } else if (warp >= kGLayWarp0) {
+            // ---- the scale codes of the chunk's digit rows, as the atoms tensor memory takes (row n of
+            // the operand = 16 * token + digit row: byte (n % 32) * 16 + (n / 32) * 4 + block % 4 of the atom
+            // of four scale blocks); digit row j < 8 of a block with exponent E has the code
+            // 127 + E - 23 + 3 j, row 8 + j the code 127 + E - 47 + 3 j; the exponents are stored as E + 100.
+            // A thread fetches its words of the item before it waits for the buffer. ----
+            const uint32_t lt = tid - kGLayWarp0 * 32u;
+            const uint32_t atom = lt >> 7, r32 = (lt >> 2) & 31u, col = lt & 3u;
+            const uint32_t t = 2u * col + (r32 >> 4), j = r32 & 15u;
+            const int shift = j < 8u ? 4 + 3 * (int)j : 3 * (int)(j & 7u) - 20;
+            const uint32_t bias = 0x01010101u * (uint32_t)shift;
+#pragma unroll 1
+            for (uint32_t i = 0; i < nb && ok; ++i, ++gi) {
+                const uint32_t buf = gi & 1u, nt = s_rec[i].nt & 0xFFu;
+                uint32_t ew[16];
+                const bool mine = t < nt && t < kNt;
+                const uint32_t vec = mine ? (kDown ? s_rec[i].pair[t] : s_rec[i].tok[t]) : 0u;
+                const uint32_t *e4 = reinterpret_cast<const uint32_t *>(a.exps + (size_t)vec * (K >> 5)) + atom;
+#pragma unroll
+                for (uint32_t u = 0; u < 16; ++u) ew[u] = (mine && u < nu) ? __ldcg(e4 + u * 2u) + bias : 0x7F7F7F7Fu;
+                // the buffer's last readers were the copies of item gi - 2
+                if (gi >= 2u) ok = mbar_wait(bar(kGBarAccDone + buf), ((gi - 2u) >> 1) & 1u, abortp);
+                if (!ok) break;
+                uint8_t *dst = sSfb + buf * kSfbBytes + atom * kAtomBytes + r32 * 16u + col * 4u;
+#pragma unroll
+                for (uint32_t u = 0; u < 16; ++u)
+                    if (u < nu) *reinterpret_cast<uint32_t *>(dst + u * 1024u) = ew[u];
+                fence_async_smem();  // tcgen05.cp reads the atoms
+                mbar_arrive(bar(kGBarSfb + buf));
+            }
         }
+        __syncwarp();
+        __syncthreads();  // the records are rewritten; a role that gave up has raised the flag
+        if (abort_flag) break;
+    }
+    if (is_issuer) {
         // nothing of this CTA's tensor work is in flight when the tensor memory is freed
         umma_commit(bar(kGBarFin));
         mbar_wait(bar(kGBarFin), 0, abortp);
-    } else if (warp < 4u) {
-        // ---- epilogue: per token of the chunk the two accumulators' sixteen digit columns, added in
-        // double and rounded once ----
-        const uint32_t row = tid;
-        const uint32_t lane_base = tmem + ((warp * 32u) << 16);
-        uint32_t gi = 0;
-        bool ok = true;
-#pragma unroll 1
-        for (uint32_t q = cta; q < n_items && ok; q += grid, ++gi) {
-            const uint32_t item = __ldg(a.items + q), idx = item & 0xFFu, buf = gi & 1u;
-            const BlockChunk *ch = a.chunks + (item >> 8);
-            const uint32_t nt = __ldg(&ch->nt);
-            uint32_t pair[kNt];
-#pragma unroll
-            for (uint32_t t = 0; t < kNt; ++t) pair[t] = __ldg(&ch->pair[t]);
-            ok = epi_all(mbar_wait(bar(kGBarAccDone + buf), (gi >> 1) & 1u, abortp));
-            if (!ok) break;
-            fence_after();
-            float v[kNt];
-#pragma unroll
-            for (uint32_t t = 0; t < kNt; ++t) {
-                v[t] = 0.0f;
-                if (t < nt) {  // uniform in the CTA
-                    double sum = 0.0;
-#pragma unroll
-                    for (uint32_t half = 0; half < 2; ++half) {
-                        uint32_t r[16];
-                        tmem_ld16(lane_base + kGColAcc + (buf * 2u + half) * (16u * kNt) + 16u * t, r);
-                        tmem_ld_wait();
-                        double lo = 0.0, hi = 0.0;
-#pragma unroll
-                        for (int c = 0; c < 8; ++c) {
-                            lo += (double)__uint_as_float(r[8 + c]);
-                            hi += (double)__uint_as_float(r[c]);
-                        }
-                        sum += lo + hi;
-                    }
-                    v[t] = (float)sum;
-                }
-            }
-            fence_before();
-            mbar_arrive(bar(kGBarAccFree + buf));
-            if constexpr (kDown) {
-                // row idx * 128 + `row` of the pairs' expert outputs
-#pragma unroll
-                for (uint32_t t = 0; t < kNt; ++t)
-                    if (t < nt) a.out[(size_t)pair[t] * a.hidden + idx * 128u + row] = v[t];
-            } else {
-                // lanes 0-63: gate of the slice's element `row`; lanes 64-127: its up projection
-#pragma unroll
-                for (uint32_t t = 0; t < kNt; ++t)
-                    if (t < nt && row >= 64u) s_up[t][row - 64u] = v[t];
-                epi_sync();
-#pragma unroll
-                for (uint32_t t = 0; t < kNt; ++t) {
-                    if (t < nt && row < 64u) {
-                        // hidden value `row` of the slice -> sixteen digit nibbles; scale block = warp
-                        const float hv = swiglu_limit_f32(v[t], s_up[t][row]);
-                        float bm = fabsf(hv);
-#pragma unroll
-                        for (int o = 16; o > 0; o >>= 1) bm = fmaxf(bm, __shfl_xor_sync(0xffffffffu, bm, o));
-                        const int E = block_exponent(bm);
-                        uint32_t hw, lw;
-                        digit_codes16(hv, __uint_as_float((uint32_t)(150 - E) << 23), hw, lw);
-                        const uint32_t ohw = __shfl_xor_sync(0xffffffffu, hw, 1), olw = __shfl_xor_sync(0xffffffffu, lw, 1);
-                        // byte lane / 2 of every row's chunk holds the nibbles of lanes 2b (low) and 2b + 1; even
-                        // lanes write digit rows 0-3 and 8-11, odd lanes 4-7 and 12-15
-                        const uint32_t e_hw = (lane & 1u) ? ohw : hw, o_hw = (lane & 1u) ? hw : ohw;
-                        const uint32_t e_lw = (lane & 1u) ? olw : lw, o_lw = (lane & 1u) ? lw : olw;
-#pragma unroll
-                        for (uint32_t jj = 0; jj < 4; ++jj) {
-                            const uint32_t dj = (lane & 1u) * 4u + jj;
-                            s_hst[t][(dj * 2u + warp) * 16u + (lane >> 1)] =
-                                (uint8_t)(((e_hw >> (4u * dj)) & 0xFu) | (((o_hw >> (4u * dj)) & 0xFu) << 4));
-                            s_hst[t][((8u + dj) * 2u + warp) * 16u + (lane >> 1)] =
-                                (uint8_t)(((e_lw >> (4u * dj)) & 0xFu) | (((o_lw >> (4u * dj)) & 0xFu) << 4));
-                        }
-                        if (lane == 0) a.hexp[(size_t)pair[t] * (a.inter >> 5) + idx * 2u + warp] = (uint8_t)(E + 100);
-                    }
-                }
-                epi_sync();
-                // the slice's 32 chunks (digit row, block) of every token go to their places in the pair's
-                // digit tile: 64 threads write half a chunk each; the two halves of the CTA take the
-                // tokens alternately
-                const uint32_t t64 = tid & 63u, ch16 = t64 >> 1, half = t64 & 1u, dj = ch16 >> 1, blk = ch16 & 1u;
-                const uint32_t cc = (idx & 3u) * 2u + blk;
-                const uint32_t o = (idx >> 2) * 2048u + dj * 128u + ((cc ^ (dj & 7u)) << 4) + half * 8u;
-#pragma unroll
-                for (uint32_t t = 0; t < kNt; ++t) {
-                    if (t < nt && (t & 1u) == (tid >> 6)) {
-                        const uint2 c8 = *reinterpret_cast<const uint2 *>(&s_hst[t][(dj * 2u + blk) * 16u + half * 8u]);
-                        *reinterpret_cast<uint2 *>(a.hdig + (size_t)pair[t] * KD * 2048u + o) = c8;
-                    }
-                }
-            }
-        }
-    } else if (warp >= kGLayWarp0) {
-        // ---- the scale codes of the chunk's digit rows, as the atoms tensor memory takes (row n of
-        // the operand = 16 * token + digit row: byte (n % 32) * 16 + (n / 32) * 4 + block % 4 of the atom
-        // of four scale blocks); digit row j < 8 of a block with exponent E has the code
-        // 127 + E - 23 + 3 j, row 8 + j the code 127 + E - 47 + 3 j; the exponents are stored as E + 100 ----
-        const uint32_t lt = tid - kGLayWarp0 * 32u;
-        const uint32_t atom = lt >> 7, r32 = (lt >> 2) & 31u, col = lt & 3u;
-        const uint32_t t = 2u * col + (r32 >> 4), j = r32 & 15u;
-        const int shift = j < 8u ? 4 + 3 * (int)j : 3 * (int)(j & 7u) - 20;
-        const uint32_t bias = 0x01010101u * (uint32_t)shift;
-        uint32_t gi = 0;
-        bool ok = true;
-#pragma unroll 1
-        for (uint32_t q = cta; q < n_items && ok; q += grid, ++gi) {
-            const uint32_t item = __ldg(a.items + q), buf = gi & 1u;
-            const BlockChunk *ch = a.chunks + (item >> 8);
-            const uint32_t nt = __ldg(&ch->nt);
-            // the buffer's last readers were the copies of item gi - 2
-            if (gi >= 2u) ok = mbar_wait(bar(kGBarAccDone + buf), ((gi - 2u) >> 1) & 1u, abortp);
-            if (!ok) break;
-            uint8_t *dst = sSfb + buf * kSfbBytes + atom * kAtomBytes + r32 * 16u + col * 4u;
-            if (t < nt && t < kNt) {
-                const uint32_t vec = kDown ? __ldg(&ch->pair[t]) : __ldg(&ch->tok[t]);
-                const uint32_t *e4 = reinterpret_cast<const uint32_t *>(a.exps + (size_t)vec * (K >> 5)) + atom;
-#pragma unroll 4
-                for (uint32_t u = 0; u < nu; ++u) *reinterpret_cast<uint32_t *>(dst + u * 1024u) = __ldcg(e4 + u * 2u) + bias;
-            } else {
-#pragma unroll 4
-                for (uint32_t u = 0; u < nu; ++u) *reinterpret_cast<uint32_t *>(dst + u * 1024u) = 0x7F7F7F7Fu;
-            }
-            fence_async_smem();  // tcgen05.cp reads the atoms
-            mbar_arrive(bar(kGBarSfb + buf));
-        }
     }
     __syncwarp();
-    if (tid == kGProdWarp * 32u) {
-        // copies in flight land in this CTA's shared memory: wait for them before leaving
+    if (is_prod_a) {
+        // copies in flight land in this CTA's shared memory: wait for them before leaving (a stage's
+        // barrier completes when the unit and the token tiles are there)
         const uint32_t units = s_units, first = units > ring ? units - ring : 0u;
 #pragma unroll 1
         for (uint32_t u = first; u < units; ++u) {
@@ -484,9 +574,9 @@ size_t block_dynamic_limit() {
     return most;
 }
 
-uint32_t block_ring(size_t limit) {
-    if (limit < 2u * kSfbBytes + 2u * kStage) return 0;
-    uint32_t r = (uint32_t)((limit - 2u * kSfbBytes) / kStage);
+uint32_t block_ring(size_t limit, uint32_t stage) {
+    if (limit < 2u * kSfbBytes + 2u * stage) return 0;
+    uint32_t r = (uint32_t)((limit - 2u * kSfbBytes) / stage);
     if (r > kGRingMax) r = kGRingMax;
     return r & ~1u;
 }
@@ -497,31 +587,38 @@ bool moe_block_ok(int sm_count, uint32_t hidden, uint32_t inter, uint32_t n_expe
     if (sm_count <= 0 || n_experts == 0u || n_experts > S14_N_ROUTED_EXPERTS || top_k == 0u || top_k > S14_EXPERTS_PER_TOKEN)
         return false;
     if ((hidden & 511u) || (inter & 511u) || hidden < 512u || inter < 512u || hidden > 4096u || inter > 4096u) return false;
-    return block_ring(block_dynamic_limit()) >= 2u;
+    return block_ring(block_dynamic_limit(), kStageA + kNt * 2048u) >= 2u;
 }
 
 size_t moe_block_max_chunks(uint32_t max_tokens) {
-    // every expert may end with a chunk that is not full; the shared expert's chunks hold every token once
-    return (size_t)S14_N_ROUTED_EXPERTS + 1u + ((size_t)max_tokens * kPairsPerToken + kNt - 1u) / kNt;
+    // no more chunks than pairs (chunks of one token)
+    return (size_t)max_tokens * kPairsPerToken;
 }
 
 int launch_moe_block(cudaStream_t st, int sm_count, const BlockWork &w, const float *x, float *y, const int32_t *ids,
                      const float *weights, const uint8_t *const *pages, const uint8_t *const *page_table,
                      const uint8_t *shared_page, uint32_t n_tokens, uint32_t top_k, uint32_t n_experts, uint32_t hidden,
-                     uint32_t inter, uint32_t *status, cudaError_t *err) {
-    const uint32_t ring = block_ring(block_dynamic_limit());
+                     uint32_t inter, uint32_t *status, cudaError_t *err, uint32_t nt_cap) {
+    // Tokens per chunk.  A small block is bound by the memory's latency: most experts have one token,
+    // and short stages make the ring deeper (more page bytes in flight); the shared expert's extra
+    // chunks come from the L2.  A large block wants few passes over every expert.
+    if (nt_cap == 0u) nt_cap = n_tokens <= 12u ? 2u : kNt;
+    if (nt_cap > kNt) nt_cap = kNt;
+    const uint32_t stage = kStageA + nt_cap * 2048u;
+    const uint32_t ring = block_ring(block_dynamic_limit(), stage);
     *err = cudaErrorInvalidConfiguration;
     if (ring < 2u || n_tokens == 0u) return 0;
     const uint32_t S = inter >> 6, RT = hidden >> 7;
-    const size_t smem = (size_t)ring * kStage + 2u * kSfbBytes;
+    const size_t smem = (size_t)ring * stage + 2u * kSfbBytes;
     k_block_digits<<<n_tokens, 512, 0, st>>>(x, hidden, w.xdig, w.xexp);
-    k_block_group<<<1, 1024, 0, st>>>(ids, pages, page_table, shared_page, n_tokens, top_k, n_experts, S, RT, w.chunks,
-                                     w.items_up, w.items_down, w.counts);
-    GemmArgs up = {w.chunks, w.items_up, w.counts + 1, w.xdig, w.xexp, nullptr, w.hdig, w.hexp, hidden, inter, ring};
+    k_block_group<<<1, 1024, 0, st>>>(ids, pages, page_table, shared_page, n_tokens, top_k, n_experts, S, RT, nt_cap, w.chunks,
+                                     w.counts);
+    GemmArgs up = {w.chunks, w.counts + 1, w.xdig, w.xexp, nullptr, w.hdig, w.hexp, hidden, inter, ring, stage};
     k_block_gemm<false><<<sm_count, kGThreads, smem, st>>>(up, status);
-    GemmArgs down = {w.chunks, w.items_down, w.counts + 2, w.hdig, w.hexp, w.d, nullptr, nullptr, hidden, inter, ring};
+    GemmArgs down = {w.chunks, w.counts + 2, w.hdig, w.hexp, w.d, nullptr, nullptr, hidden, inter, ring, stage};
     k_block_gemm<true><<<sm_count, kGThreads, smem, st>>>(down, status);
-    k_block_mix<<<dim3((hidden + 255u) / 256u, n_tokens), 256, 0, st>>>(w.d, ids, weights, top_k, shared_page != nullptr, y, hidden, w.counts);
+    k_block_mix<<<dim3((hidden + 255u) / 256u, n_tokens), 256, 0, st>>>(w.d, ids, weights, top_k, shared_page != nullptr, y, hidden,
+                                                                       w.counts);
     *err = cudaGetLastError();
     return 5;
 }
