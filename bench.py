@@ -2,7 +2,7 @@
 """Benchmark of the S14 MoE expert path on B200.
 
     python bench.py [--gpus N] [--steps K] [--warmup W] [--impl reference]
-                    [--workload stack|layer|expert_chain|wq_a|verify8] [--accum pairwise|reference]
+                    [--workload stack|layer|expert_chain|wq_a|verify8|prefill|decode] [--accum pairwise|reference]
 
 A step is one layer-token: one token through one MoE layer (router top-6 of 256, six routed MXFP4
 experts and the shared MXFP4 expert, hidden 4096, intermediate 2048).  14 layers of 257 expert pages
@@ -12,8 +12,10 @@ are resident (48 GB), so the 96 MB a step touches never come from L2.
           h <- h + moe_l(h), in ONE launch of the layer kernel per 14 steps (s14_cmd_stack_decode);
   layer   one launch per step with independent tokens (s14_cmd_routed_moe_layer); with several GPUs
           the experts are partitioned and the down vectors exchanged inside the kernel;
-  expert_chain, wq_a, verify8   the single-expert chain, the FP8 projection matvec and the 8-token
-          verify block of the other configurations, each with its own roofline entry.
+  expert_chain, wq_a   the single-expert chain and the FP8 projection matvec of the other
+          configurations, each with its own roofline entry;
+  verify8, prefill   a block of tokens (8; 370, or --tokens N) through one layer with the tokens
+          grouped by expert, every distinct expert page streamed once (s14_cmd_routed_moe_block).
 
 The timed region is exactly K steps, taken with CUDA events on the launching stream; it is repeated
 (--repeats, default 50) and the median repeat is reported with the spread.  Pages are a function of
@@ -44,6 +46,7 @@ if ROOT not in sys.path:
     sys.path.insert(0, ROOT)
 
 HIDDEN, INTER, N_EXPERTS, TOP_K, N_LAYERS = 4096, 2048, 256, 6, 14
+PREFILL_TOKENS = 370   # the reference's prefill length (README.md:139)
 PAGE_BYTES = 13_369_344
 # algorithmic bytes of one layer-token: 7 expert pages + router weights + bias + x + y
 ROUTER_BYTES = N_EXPERTS * HIDDEN * 2 + N_EXPERTS * 4
@@ -315,7 +318,7 @@ def run_gpu(args) -> None:
     workload = args.workload or ("stack" if world == 1 else "layer")
     if world > 1 and workload != "layer":
         raise SystemExit("several GPUs: the expert-parallel workload is `layer`")
-    if workload in ("expert_chain", "wq_a", "verify8"):
+    if workload in ("expert_chain", "wq_a", "verify8", "prefill"):
         return run_small_workload(args, workload, torch, L, synth, S14Context, TokenRoute)
     if workload == "decode":
         return run_decode_workload(args, torch, L, synth, S14Context)
@@ -980,11 +983,14 @@ def run_small_workload(args, workload, torch, L, synth, S14Context, TokenRoute) 
 
     oracle.build()
     cores = cpu_threads(oracle)
+    if workload == "prefill" and not args.steps_given:
+        args.steps = 10   # a region of ten prefills (some 15 ms)
     ctx = S14Context(0)
     ctx.set_accumulation(L.ACCUM_REFERENCE if args.accum == "reference" else L.ACCUM_PAIRWISE)
     stream = torch.cuda.Stream()
     peak, peak_kind = measured_peaks()
     g = synth.rng(126)
+    n_tok = 1
     if workload == "expert_chain":
         n_pages = 16  # 214 MB of distinct pages
         writer = synth.HashedPageWriter(torch, HIDDEN, INTER)
@@ -1051,51 +1057,67 @@ def run_small_workload(args, workload, torch, L, synth, S14Context, TokenRoute) 
                 for i in range(t):
                     oracle.fp8_matvec(x_np[i], w2, s_np, n, k)
             return (time.perf_counter() - t0) / 20
-    else:  # verify8
-        n_tok = 8
+    else:  # verify8, prefill: a block of tokens through one layer, grouped by expert
+        from colormlm_b200.s14 import MoeBlock
+
+        n_tok = 8 if workload == "verify8" else max(1, min(1024, args.tokens if args.tokens > 8 else PREFILL_TOKENS))
         layers = resident_layers(torch, 2, 0, 1)
         x_np = tokens(n_tok)
         x = torch.from_numpy(x_np).cuda()
         y = torch.empty_like(x)
-        per_layer = []
+        ids_dev = torch.empty((n_tok, TOP_K), dtype=torch.int32, device="cuda")
+        w_dev = torch.empty((n_tok, TOP_K), dtype=torch.float32, device="cuda")
+        blk = MoeBlock(ctx, HIDDEN, INTER, n_tok)
+        distinct = []
         for l in range(2):
             wr, bias = router_of_layer(l)
-            routes, distinct = [], set()
+            seen = set()
             for t in range(n_tok):
-                ids, w, _, _ = oracle.router(x_np[t], wr, bias, 0, TOP_K, 1.0)
-                distinct.update(int(e) for e in ids)
-                routes.append(TokenRoute([int(e) for e in ids], w, [layers[l]["pages"].data_ptr() + int(e) * PAGE_BYTES for e in ids]))
-            per_layer.append((routes, len(distinct)))
-        d_avg = float(np.mean([d for _, d in per_layer]))
-        unit_bytes = int((d_avg + 1) * PAGE_BYTES + n_tok * 2 * HIDDEN * 4)
-        what = (f"8-token verify block through one layer, routes given, {d_avg:.0f} distinct routed experts + the shared one "
-                "(every distinct page counted once)")
+                ids, _, _, _ = oracle.router(x_np[t], wr, bias, 0, TOP_K, 1.0)
+                seen.update(int(e) for e in ids)
+            distinct.append(len(seen))
+        d_avg = float(np.mean(distinct))
+        unit_bytes = int((d_avg + 1) * PAGE_BYTES + ROUTER_BYTES + n_tok * 2 * HIDDEN * 4)
+        what = (f"{n_tok}-token {'verify block' if workload == 'verify8' else 'prefill'} through one layer, routes picked on the "
+                f"device, tokens grouped by expert: {d_avg:.0f} distinct routed experts + the shared one (every distinct page "
+                "counted once), router weights, x and y")
+
+        def block_call(l, st):
+            lay = layers[l]
+            blk.cmd_routed_moe_block(x, lay["wr"], lay["bias"], lay["table"], lay["shared"], y, ids_dev, w_dev,
+                                     score_fn=L.SCORE_SIGMOID, top_k=TOP_K, route_scale=1.0, stream=st)
 
         def enqueue():
             for i in range(args.steps):
-                routes, _ = per_layer[i % 2]
-                ctx.cmd_moe_layer(x, y, routes, layers[i % 2]["shared"], L.PAGE_MXFP4, HIDDEN, INTER, stream=stream.cuda_stream)
+                block_call(i % 2, stream.cuda_stream)
+
+        sample = (0, 5) if workload == "verify8" else (0, n_tok // 2, n_tok - 1)
 
         def check():
-            routes, _ = per_layer[0]
-            ctx.cmd_moe_layer(x, y, routes, layers[0]["shared"], L.PAGE_MXFP4, HIDDEN, INTER)
+            block_call(0, None)
             torch.cuda.synchronize()
+            assert ctx.last_layer_path == L.LAYER_PATH_TENSOR_BLOCK
             hp = HostPages()
             b64, b32 = [], []
-            for t in (0, 5):
-                y64, _, _ = cpu_layer(oracle, hp, 0, x_np[t], acc64=True)
+            for t in sample:
+                y64, ids64, _ = cpu_layer(oracle, hp, 0, x_np[t], acc64=True)
                 y32, _, _ = cpu_layer(oracle, hp, 0, x_np[t], acc64=False)
+                assert np.array_equal(ids_dev[t].cpu().numpy(), ids64), "the device's routes differ from the oracle's"
                 b64.append(error_block(oracle, y.cpu().numpy()[t], y64))
                 b32.append(error_block(oracle, y.cpu().numpy()[t], y32))
-            return {"vs_double_accumulated_oracle": worst(b64), "vs_f32_order_oracle": worst(b32)}
+            return {"vs_double_accumulated_oracle": worst(b64), "vs_f32_order_oracle": worst(b32), "tokens_checked": list(sample)}
+
+        n_cpu = 8
 
         def cpu_once():
+            # the reference's way through a block: token after token (forward.rs:544-549); a bounded sample of
+            # n_cpu tokens, scaled to the block
             hp = HostPages()
             cpu_layer(oracle, hp, 0, x_np[0])
             t0 = time.perf_counter()
-            for t in range(n_tok):
-                cpu_layer(oracle, hp, 0, x_np[t])
-            return time.perf_counter() - t0
+            for t in range(n_cpu):
+                cpu_layer(oracle, hp, 0, x_np[t % n_tok])
+            return (time.perf_counter() - t0) * n_tok / n_cpu
 
     with torch.cuda.stream(stream):
         enqueue()
@@ -1120,8 +1142,10 @@ def run_small_workload(args, workload, torch, L, synth, S14Context, TokenRoute) 
     parity = check()
     cpu_sec = cpu_once()
     achieved = unit_bytes * args.steps / (ms * 1e-3) / 1e9
-    line = {"metric": {"expert_chain": "expert_chains_per_s", "wq_a": "matvecs_per_s", "verify8": "verify_blocks_per_s"}[workload],
-            "value": args.steps / (ms / 1e3), "unit": "calls/s", "n_gpus": 1, "steps": args.steps, "warmup": args.warmup,
+    per_call = n_tok if workload == "prefill" else 1   # a prefill is counted in tokens
+    line = {"metric": {"expert_chain": "expert_chains_per_s", "wq_a": "matvecs_per_s", "verify8": "verify_blocks_per_s",
+                       "prefill": "prefill_tokens_per_s"}[workload],
+            "value": per_call * args.steps / (ms / 1e3), "unit": "tokens/s" if workload == "prefill" else "calls/s", "n_gpus": 1, "steps": args.steps, "warmup": args.warmup,
             "ms_per_step": ms / args.steps, "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "f32",
             "data": "synthetic",
             "config": {"workload": what, "bench_workload": workload, "accumulation": args.accum,
@@ -1134,8 +1158,11 @@ def run_small_workload(args, workload, torch, L, synth, S14Context, TokenRoute) 
                          "bytes_per_call": unit_bytes,
                          "note": "a call of a few MB is bound by launch and memory latency, not by bandwidth"},
             "parity": parity,
-            "cpu_baseline": {"value": 1.0 / cpu_sec, "unit": "calls/s", "cores": cores, "kind": "port",
-                             "sample": "the same call on the CPU oracle, same bytes", "ms_per_call": cpu_sec * 1e3},
+            "cpu_baseline": {"value": per_call / cpu_sec, "unit": "tokens/s" if workload == "prefill" else "calls/s", "cores": cores,
+                             "kind": "port",
+                             "sample": ("8 tokens of the block, token after token, scaled to the block" if workload in ("verify8", "prefill")
+                                        else "the same call on the CPU oracle, same bytes"),
+                             "ms_per_call": cpu_sec * 1e3},
             "e2e": None, "gpu_launches": launches, "device_status": ctx.device_status(), "clocks": clocks}
     print(json.dumps(line), flush=True)
     ctx.close()
@@ -1148,8 +1175,8 @@ def main() -> None:
     ap.add_argument("--steps", type=int, default=None)
     ap.add_argument("--warmup", type=int, default=None)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
-    ap.add_argument("--workload", default=None, choices=["stack", "layer", "expert_chain", "wq_a", "verify8", "decode"])
-    ap.add_argument("--tokens", type=int, default=1, help="tokens of the wq_a workload (1, 4 or 8)")
+    ap.add_argument("--workload", default=None, choices=["stack", "layer", "expert_chain", "wq_a", "verify8", "prefill", "decode"])
+    ap.add_argument("--tokens", type=int, default=1, help="tokens of the wq_a workload (1, 4 or 8); of the prefill workload (default 370)")
     ap.add_argument("--accum", default="pairwise", choices=["pairwise", "reference"])
     ap.add_argument("--exchange", default="peer", choices=["peer", "nccl"],
                     help="several GPUs: down vectors exchanged inside the layer kernel over peer memory, or by NCCL all-reduce")
