@@ -830,6 +830,46 @@ def run_decode_workload(args, torch, L, synth, S14Context) -> None:
     xs = torch.from_numpy(xs_np).cuda()
     stack = DecodeStack(ctx, layers, inter=INTER, residual=True)
     stream = torch.cuda.Stream()
+
+    # ---- the prefill that precedes the decode steps: PREFILL_TOKENS tokens through the 14 chained layers,
+    # h <- h + moe_l(h) for every token, each layer one call of the grouped block path ----
+    from colormlm_b200.s14 import MoeBlock
+
+    n_pre = PREFILL_TOKENS
+    blk = MoeBlock(ctx, HIDDEN, INTER, n_pre)
+    blk.set_residual(True)
+    xp_np = tokens(n_pre)
+    xp = torch.from_numpy(xp_np).cuda()
+    hp_buf = torch.empty_like(xp)
+
+    def run_prefill(handle):
+        hp_buf.copy_(xp)
+        for lay in layers:
+            blk.cmd_routed_moe_block(hp_buf, lay["wr"], lay["bias"], lay["table"], lay["shared"], hp_buf,
+                                     score_fn=L.SCORE_SIGMOID, top_k=TOP_K, route_scale=1.0, stream=handle)
+
+    with torch.cuda.stream(stream):
+        run_prefill(stream.cuda_stream)
+    stream.synchronize()
+    prefill_h = hp_buf.cpu().numpy().copy()
+    prefill_status = ctx.device_status()
+    c0 = ctx.launch_count
+    gpre = torch.cuda.CUDAGraph()
+    with torch.cuda.stream(stream):
+        with torch.cuda.graph(gpre, stream=stream):
+            run_prefill(stream.cuda_stream)
+    prefill_launches = ctx.launch_count - c0
+    with torch.cuda.stream(stream):
+        for _ in range(3):
+            gpre.replay()
+    stream.synchronize()
+    pre_ms = timed_repeats(torch, stream, gpre.replay, 10)
+    prefill_graph_equal = bool(np.array_equal(hp_buf.cpu().numpy().view(np.uint32), prefill_h.view(np.uint32)))
+    prefill = {"tokens": n_pre, "layers": N_LAYERS, "ms_median": float(np.median(pre_ms)), "ms_min": float(np.min(pre_ms)),
+               "tokens_per_s": n_pre / (float(np.median(pre_ms)) / 1e3), "layer_tokens_per_s": n_pre * N_LAYERS / (float(np.median(pre_ms)) / 1e3),
+               "gpu_launches": prefill_launches, "device_status": prefill_status, "graph_equals_eager": prefill_graph_equal,
+               "path": "s14_cmd_routed_moe_block with residual, one call per layer (router, digit rows, grouping, two tcgen05 "
+                       "contractions, mix)"}
     h = torch.empty(HIDDEN, dtype=torch.float32, device="cuda")
     logits = torch.empty(VOCAB, dtype=torch.float32, device="cuda")
     tok = torch.zeros(1, dtype=torch.int64, device="cuda")
@@ -905,6 +945,16 @@ def run_decode_workload(args, torch, L, synth, S14Context) -> None:
             hh = (hh + y64).astype(np.float32)
         lg = oracle.head_logits(hh, head_np)
         worst_logit = float(np.max(np.abs(logits.cpu().numpy() - lg)))
+        # the prefill: the last token's (and the first's) state after the 14 layers against the CPU oracle chain
+        pre_blocks = []
+        for t in (0, n_pre - 1):
+            hh = xp_np[t].copy()
+            for l in range(N_LAYERS):
+                y64, _, _ = cpu_layer(oracle, hp, l, hh, acc64=True)
+                hh = (hh + y64).astype(np.float32)
+            pre_blocks.append(error_block(oracle, prefill_h[t], hh))
+        prefill["parity"] = {"what": "tokens 0 and 369 after the 14 chained layers against the CPU oracle chain (double-accumulated layers)",
+                             "vs_double_accumulated_oracle": worst(pre_blocks)}
         parity = {"steps": n_check, "what": "greedy tokens of the first decode steps against the CPU oracle chain "
                                             "(14 double-accumulated layers, head, argmax); logits of the first step",
                   "tokens_gpu": [int(v) for v in graph_tokens[:n_check]], "tokens_cpu": cpu_tokens,
@@ -931,9 +981,10 @@ def run_decode_workload(args, torch, L, synth, S14Context) -> None:
                      "peak_kind": peak_kind, "traffic": None, "bytes_per_step": step_bytes,
                      "kernel": "k_moe_layer_umma (14 layers) + k_head_logits + k_greedy_argmax per step"},
         "parity": parity, "cpu_baseline": cpu, "e2e": None, "gpu_launches": launches,
-        "device_status": status, "clocks": clocks,
+        "device_status": status, "clocks": clocks, "prefill": prefill,
     }
     print(json.dumps(line), flush=True)
+    blk.close()
     stack.close()
     ctx.close()
 

@@ -1783,6 +1783,7 @@ struct s14_block {
     uint8_t *stage = nullptr;                     // pinned: ids | weights | pages of one call
     cudaEvent_t staged = nullptr;                 // the staging buffer's last copy has left it
     bool stage_busy = false;
+    bool residual = false;                        // y = x + moe(x)
 };
 
 static constexpr uint32_t kBlockMaxTokens = 1024;
@@ -1853,7 +1854,7 @@ static int32_t block_launch(s14_block *blk, cudaStream_t st, const float *x, flo
     s14_ctx *ctx = blk->ctx;
     cudaError_t err;
     ctx->launches += launch_moe_block(st, ctx->sm_count, blk->w, x, y, ids, weights, pages, page_table, shared_page, n_tokens,
-                                      top_k, n_experts, blk->hidden, blk->inter, ctx->status, &err);
+                                      top_k, n_experts, blk->hidden, blk->inter, ctx->status, &err, 0, blk->residual);
     ctx->last_path = S14_LAYER_PATH_TENSOR_BLOCK;
     if (err != cudaSuccess) return cuda_fail(err, "S14 MoE block launch");
     return S14_OK;
@@ -1900,6 +1901,11 @@ extern "C" int32_t s14_cmd_moe_block(s14_ctx *ctx, void *stream, s14_block *blk,
         }
     }
     cudaStream_t st = stream_of(ctx, stream);
+    cudaStreamCaptureStatus cap = cudaStreamCaptureStatusNone;
+    CUDA_OK(cudaStreamIsCapturing(st, &cap));
+    if (cap != cudaStreamCaptureStatusNone)
+        throw ContractError("s14_cmd_moe_block: the routes are staged through one host buffer per block object, so the call "
+                            "cannot be captured into a CUDA graph; s14_cmd_routed_moe_block can");
     CUDA_OK(cudaMemcpyAsync(blk->ids, h_ids, (size_t)T * R * 4u, cudaMemcpyHostToDevice, st));
     CUDA_OK(cudaMemcpyAsync(blk->weights, h_w, (size_t)T * R * 4u, cudaMemcpyHostToDevice, st));
     CUDA_OK(cudaMemcpyAsync(blk->pages, h_pages, (size_t)T * R * 8u, cudaMemcpyHostToDevice, st));
@@ -1944,6 +1950,12 @@ extern "C" int32_t s14_cmd_routed_moe_block(s14_ctx *ctx, void *stream, s14_bloc
     return block_launch(blk, st, r.x, desc->y, rd.ids_out, rd.weights_out, nullptr, desc->page_table, desc->shared_page,
                         r.n_tokens, r.top_k, r.n_experts);
     S14_CATCH
+}
+
+extern "C" int32_t s14_block_set_residual(s14_block *blk, int32_t residual) {
+    if (!blk) return fail(S14_ERR_CONTRACT, "s14_block_set_residual: blk is NULL");
+    blk->residual = residual != 0;
+    return S14_OK;
 }
 
 // counts of the last call's grouping (after the stream is synchronised): chunks, up items, down

@@ -191,7 +191,7 @@ size_t moe_block_max_chunks(uint32_t max_tokens);
 int launch_moe_block(cudaStream_t st, int sm_count, const BlockWork &w, const float *x, float *y, const int32_t *ids,
                      const float *weights, const uint8_t *const *pages, const uint8_t *const *page_table,
                      const uint8_t *shared_page, uint32_t n_tokens, uint32_t top_k, uint32_t n_experts, uint32_t hidden,
-                     uint32_t inter, uint32_t *status, cudaError_t *err, uint32_t nt_cap = 0);
+                     uint32_t inter, uint32_t *status, cudaError_t *err, uint32_t nt_cap = 0, bool residual = false);
 // Scores and routes of many tokens (s14_kernels.cu): the tokens of a tile share the router rows in
 // shared memory; one warp per token selects.  Same arithmetic as launch_router.  Returns the number
 // of kernels launched.

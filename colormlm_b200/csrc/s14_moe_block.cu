@@ -537,10 +537,12 @@ k_block_gemm(const __grid_constant__ GemmArgs a, uint32_t *status) {
 }
 
 // y[t, n]: the ordered mix of token t (examples/s14_vulkan_numeric.rs:936-946): acc = 0; acc += w * d
-// over the routes in order; acc += d of the shared expert.
+// over the routes in order; acc += d of the shared expert.  With `residual` the layer's input is added
+// (y = x + acc, what a layer of a stack hands to the next); y may be x.
 __global__ void __launch_bounds__(256)
 k_block_mix(const float *__restrict__ d, const int32_t *__restrict__ ids, const float *__restrict__ weights,
-            uint32_t top_k, int has_shared, float *__restrict__ y, uint32_t hidden, const uint32_t *__restrict__ counts) {
+            uint32_t top_k, int has_shared, float *y, uint32_t hidden, const uint32_t *__restrict__ counts,
+            const float *x, uint32_t residual) {
     const uint32_t n = blockIdx.x * blockDim.x + threadIdx.x, t = blockIdx.y;
     if (n >= hidden || __ldcg(counts + 3)) return;
     const float *dt = d + (size_t)t * kPairsPerToken * hidden + n;
@@ -549,7 +551,7 @@ k_block_mix(const float *__restrict__ d, const int32_t *__restrict__ ids, const 
         if (__ldg(ids + t * top_k + m) >= 0)
             acc = __fadd_rn(acc, __fmul_rn(__ldg(weights + t * top_k + m), __ldcg(dt + (size_t)m * hidden)));
     if (has_shared) acc = __fadd_rn(acc, __ldcg(dt + (size_t)S14_EXPERTS_PER_TOKEN * hidden));
-    y[(size_t)t * hidden + n] = acc;
+    y[(size_t)t * hidden + n] = residual ? __fadd_rn(x[(size_t)t * hidden + n], acc) : acc;
 }
 
 constexpr int kMaxDevices = 64;
@@ -598,7 +600,7 @@ size_t moe_block_max_chunks(uint32_t max_tokens) {
 int launch_moe_block(cudaStream_t st, int sm_count, const BlockWork &w, const float *x, float *y, const int32_t *ids,
                      const float *weights, const uint8_t *const *pages, const uint8_t *const *page_table,
                      const uint8_t *shared_page, uint32_t n_tokens, uint32_t top_k, uint32_t n_experts, uint32_t hidden,
-                     uint32_t inter, uint32_t *status, cudaError_t *err, uint32_t nt_cap) {
+                     uint32_t inter, uint32_t *status, cudaError_t *err, uint32_t nt_cap, bool residual) {
     // Tokens per chunk.  A small block is bound by the memory's latency: most experts have one token,
     // and short stages make the ring deeper (more page bytes in flight); the shared expert's extra
     // chunks come from the L2.  A large block wants few passes over every expert.
@@ -618,7 +620,7 @@ int launch_moe_block(cudaStream_t st, int sm_count, const BlockWork &w, const fl
     GemmArgs down = {w.chunks, w.counts + 2, w.hdig, w.hexp, w.d, nullptr, nullptr, hidden, inter, ring, stage};
     k_block_gemm<true><<<sm_count, kGThreads, smem, st>>>(down, status);
     k_block_mix<<<dim3((hidden + 255u) / 256u, n_tokens), 256, 0, st>>>(w.d, ids, weights, top_k, shared_page != nullptr, y, hidden,
-                                                                       w.counts);
+                                                                       w.counts, x, residual ? 1u : 0u);
     *err = cudaGetLastError();
     return 5;
 }

@@ -458,6 +458,10 @@ class MoeBlock:
         check(L.lib().s14_cmd_routed_moe_block(self._ctx.handle, stream if stream is not None else _torch_stream(),
                                                self._h, C.byref(d)))
 
+    def set_residual(self, residual: bool) -> None:
+        """The calls that follow write y = x + moe(x); y may then be x."""
+        check(L.lib().s14_block_set_residual(self._h, 1 if residual else 0))
+
     def last_counts(self):
         """(chunks, up items, down items, bad id flag) of the last call; synchronise the stream first."""
         out = (C.c_uint32 * 4)()

@@ -467,17 +467,19 @@ S14_API int32_t s14_routed_moe_layer_host(s14_ctx *ctx, const s14_routed_layer_d
  * s14_runner/src/cascade.rs:19) or a prefill of hundreds of tokens (the reference's prefill walks
  * its tokens one by one through the same layer loop, ssd_inference/src/forward.rs:544-549; the
  * semantics are that loop, examples/s14_vulkan_numeric.rs:929-947, applied to every token).  Every
- * distinct expert's page is streamed once for all the tokens routed to it (in chunks of six tokens;
- * an expert's later chunks find the page in the L2): per layer five launches - digit rows of the
- * tokens, grouping of the (token, route) pairs by expert, the w1 | w3 contraction with SwiGLU, the w2
- * contraction, the ordered mix - the two contractions on tcgen05 kind::mxf4.block_scale with
- * N = 16 digit rows per token of a chunk.  Every token's y is bit-identical to what
+ * distinct expert's page is streamed once from memory for all the tokens routed to it (in chunks of
+ * six tokens, of two for blocks of up to 12 tokens; an expert's later chunks find the page in the
+ * L2): per layer five launches - digit rows of the tokens, grouping of the (token, route) pairs by
+ * expert, the w1 | w3 contraction with SwiGLU, the w2 contraction, the ordered mix - the two
+ * contractions on tcgen05 kind::mxf4.block_scale with N = 16 digit rows per token of a chunk; the
+ * routed call runs two router launches first (scores of all tokens, one warp per token selects).  Every token's y is bit-identical to what
  * s14_cmd_moe_layer / s14_cmd_routed_moe_layer give for that token alone in pairwise order.
  * MXFP4 pages only (routed and shared); hidden and intermediate multiples of 512 up to 4096.
  *   create:  allocates the workspace for up to max_tokens (<= 1024) tokens:
  *            about max_tokens * (28 * hidden + 57 * intermediate + 8 * hidden) bytes.
  *   s14_cmd_moe_block:        routes from the host (desc->n_tokens up to max_tokens; expert_ids < 256
- *            identify the groups, a group's page is the page of its first member).
+ *            identify the groups, a group's page is the page of one of its members).  The routes are
+ *            staged through one pinned buffer of the block object: not for stream capture.
  *   s14_cmd_routed_moe_block: router on the device (desc->router.n_tokens up to max_tokens, top_k <= 6);
  *            ids_out / weights_out [n_tokens, top_k] may be NULL.
  *   One call at a time per block object (calls on one stream are ordered).  A wait that runs out
@@ -485,6 +487,9 @@ S14_API int32_t s14_routed_moe_layer_host(s14_ctx *ctx, const s14_routed_layer_d
 typedef struct s14_block s14_block;
 S14_API int32_t s14_block_create(s14_ctx *ctx, uint32_t hidden, uint32_t inter, uint32_t max_tokens, s14_block **out);
 S14_API int32_t s14_block_destroy(s14_block *blk);
+/* residual != 0: the calls that follow write y = x + moe(x), the step of a stack of layers
+ * (h <- h + moe_l(h), as s14_stack_create's `residual`); y may then be the same buffer as x. */
+S14_API int32_t s14_block_set_residual(s14_block *blk, int32_t residual);
 S14_API int32_t s14_cmd_moe_block(s14_ctx *ctx, void *stream, s14_block *blk, const s14_moe_layer_desc *desc);
 S14_API int32_t s14_cmd_routed_moe_block(s14_ctx *ctx, void *stream, s14_block *blk, const s14_routed_layer_desc *desc);
 /* After the stream is synchronised: the last call's number of chunks, up items, down items, and 1 if

@@ -149,6 +149,29 @@ def test_routed_block_picks_the_oracles_routes(ctx, oracle, score_fn):
         blk.close()
 
 
+def test_block_with_residual_in_place(ctx):
+    """y = x + moe(x), written over x: the step of a stack of layers."""
+    hidden, inter, n_experts, n_tokens = 2048, 1024, 16, 9
+    g, pages, shared = make_layer(1400, hidden, inter, n_experts, L.PAGE_MXFP4)
+    x = synth.activations(g, n_tokens, hidden)
+    routes = random_routes(g, n_tokens, n_experts)
+    pages_dev, shared_dev = [dev_page(p, hidden, inter) for p in pages], dev_page(shared, hidden, inter)
+    blk = MoeBlock(ctx, hidden, inter, 16)
+    try:
+        y = run_block(ctx, blk, x, pages_dev, shared_dev, routes)
+        blk.set_residual(True)
+        buf = dev(x)
+        tr = [TokenRoute(ids, w, [pages_dev[i].data_ptr() for i in ids]) for ids, w in routes]
+        blk.cmd_moe_block(buf, buf, tr, shared_dev.data_ptr())
+        torch.cuda.synchronize()
+        assert ctx.device_status() == 0
+        assert np.array_equal(buf.cpu().numpy().view(np.uint32), (x + y).astype(np.float32).view(np.uint32))
+        blk.set_residual(False)
+        assert np.array_equal(run_block(ctx, blk, x, pages_dev, shared_dev, routes).view(np.uint32), y.view(np.uint32))
+    finally:
+        blk.close()
+
+
 def test_block_rejects_what_it_cannot_run(ctx):
     hidden, inter = 1024, 1024
     with pytest.raises(S14Error):
