@@ -316,8 +316,10 @@ def run_gpu(args) -> None:
         dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
         dist.barrier()
     workload = args.workload or ("stack" if world == 1 else "layer")
+    if world > 1 and workload == "prefill":
+        return run_prefill_ep(args, torch, dist, L, ep, S14Context, rank, world, local_rank)
     if world > 1 and workload != "layer":
-        raise SystemExit("several GPUs: the expert-parallel workload is `layer`")
+        raise SystemExit("several GPUs: the expert-parallel workloads are `layer` and `prefill`")
     if workload in ("expert_chain", "wq_a", "verify8", "prefill"):
         return run_small_workload(args, workload, torch, L, synth, S14Context, TokenRoute)
     if workload == "decode":
@@ -1022,6 +1024,104 @@ def trace_of_a_launch(torch, ctx, stack, x, h_out, stream, sm_mhz: float):
                 marks[name] = [round(float(v.min()), 2), round(float(np.median(v)), 2), round(float(v.max()), 2)]
         out["classes"][cname] = marks
     return out
+
+
+def run_prefill_ep(args, torch, dist, L, ep, S14Context, rank: int, world: int, local_rank: int) -> None:
+    """The prefill block (PREFILL_TOKENS tokens through one layer) expert-parallel over `world` GPUs: tokens
+    on every rank, experts sharded (expert e on rank e mod world), every rank runs the grouped block path on
+    the experts it owns, one NCCL all-reduce adds the pair buffers up, every rank mixes.  Timed with CUDA
+    events between barriers, max over ranks; y must be the same bits on every rank and equal the CPU
+    oracle's for the sampled tokens."""
+    from colormlm_b200.s14 import MoeBlock
+
+    steps = args.steps if args.steps_given else 10
+    n_tok = max(1, min(1024, args.tokens if args.tokens > 8 else PREFILL_TOKENS))
+    ctx = S14Context(local_rank)
+    ctx.set_accumulation(L.ACCUM_PAIRWISE)
+    layers = resident_layers(torch, 2, rank, world)
+    states = []
+    for ly in layers:
+        st_ = dict(ly)
+        if st_["shared"] is None:
+            st_["shared"] = ly["pages"].data_ptr()  # never read: this rank is not the owner
+        states.append(st_)
+    x_np = tokens(n_tok)
+    x = torch.from_numpy(x_np).cuda()
+    y = torch.empty_like(x)
+    pairs = torch.empty((n_tok * (TOP_K + 1), HIDDEN), dtype=torch.float32, device="cuda")
+    ids = torch.empty((n_tok, TOP_K), dtype=torch.int32, device="cuda")
+    wts = torch.empty((n_tok, TOP_K), dtype=torch.float32, device="cuda")
+    blk = MoeBlock(ctx, HIDDEN, INTER, n_tok)
+
+    def step(i):
+        ep.block_layer(blk, x, states[i % 2], pairs, ids, wts, y, layer=i % 2, rank=rank, world=world)
+
+    for i in range(max(3, args.warmup // 4)):
+        step(i)
+    torch.cuda.synchronize()
+    sampler = ClockSampler(local_rank) if rank == 0 else None
+    if sampler:
+        sampler.start()
+    ms_all = []
+    for _ in range(max(5, min(args.repeats, 20))):
+        dist.barrier()
+        torch.cuda.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for i in range(steps):
+            step(i)
+        e1.record()
+        torch.cuda.synchronize()
+        t = torch.tensor([e0.elapsed_time(e1)], dtype=torch.float64, device="cuda")
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        ms_all.append(float(t.item()))
+    clocks = sampler.stop() if sampler else None
+    step(0)
+    torch.cuda.synchronize()
+    y_np = y.cpu().numpy()
+    digest = hashlib.sha256(y_np.tobytes()).hexdigest()
+    digests = [None] * world
+    dist.all_gather_object(digests, digest)
+    statuses = [None] * world
+    dist.all_gather_object(statuses, ctx.device_status())
+    if rank == 0:
+        from oracle import s14_oracle as oracle
+
+        oracle.build()
+        cores = cpu_threads(oracle)
+        hp = HostPages()
+        sample = (0, n_tok // 2, n_tok - 1)
+        b64 = []
+        t0 = time.perf_counter()
+        for t_ in sample:
+            y64, ids64, _ = cpu_layer(oracle, hp, 0, x_np[t_], acc64=True)
+            assert np.array_equal(ids[t_].cpu().numpy(), ids64), "the device's routes differ from the oracle's"
+            b64.append(error_block(oracle, y_np[t_], y64))
+        cpu_sec = (time.perf_counter() - t0) / len(sample)
+        ms = float(np.median(ms_all))
+        peak, peak_kind = measured_peaks()
+        line = {"metric": "prefill_tokens_per_s", "value": n_tok * steps / (ms / 1e3), "unit": "tokens/s", "n_gpus": world,
+                "steps": steps, "warmup": args.warmup, "ms_per_step": ms / steps, "higher_is_better": True, "scaling": "strong",
+                "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+                "config": {"workload": f"{n_tok}-token prefill through one layer, expert parallel over {world} GPUs: tokens on every "
+                                       "rank, experts sharded, grouped block path per rank, one NCCL all-reduce of the pair "
+                                       "buffers, mix on every rank",
+                           "bench_workload": "prefill", "l2": "inputs larger than L2: two layers of pages alternate",
+                           "launch": "eager launches; CUDA events between barriers, max over ranks"},
+                "repeats": {"count": len(ms_all), "region_ms_median": ms, "region_ms_min": float(np.min(ms_all)),
+                            "region_ms_max": float(np.max(ms_all))},
+                "roofline": None,
+                "parity": {"vs_double_accumulated_oracle": worst(b64), "tokens_checked": list(sample),
+                           "y_sha256_per_rank_equal": len(set(digests)) == 1, "y_sha256": digest},
+                "cpu_baseline": {"value": 1.0 / cpu_sec, "unit": "tokens/s", "cores": cores, "kind": "port",
+                                 "sample": f"{len(sample)} tokens of the block on the CPU oracle"},
+                "e2e": None, "gpu_launches": None, "device_status_per_rank": statuses, "clocks": clocks,
+                "exchange_bytes_per_step": int(pairs.numel() * 4)}
+        print(json.dumps(line), flush=True)
+    dist.barrier()
+    blk.close()
+    ctx.close()
+    dist.destroy_process_group()
 
 
 def run_small_workload(args, workload, torch, L, synth, S14Context, TokenRoute) -> None:

@@ -153,6 +153,8 @@ SIGNATURES = {
     "s14_cmd_moe_block": (_I32, [_VP, _VP, _VP, _P(MoeLayerDesc)]),
     "s14_cmd_routed_moe_block": (_I32, [_VP, _VP, _VP, _P(RoutedLayerDesc)]),
     "s14_block_last_counts": (_I32, [_VP, _P(_U32)]),
+    "s14_cmd_routed_moe_block_experts_ep": (_I32, [_VP, _VP, _VP, _P(RoutedLayerDesc), _U32, _U32, _U32, _VP]),
+    "s14_cmd_moe_block_mix": (_I32, [_VP, _VP, _VP, _VP, _VP, _VP, _U32, _U32, _I32, _VP, _VP]),
     "s14_layer_work_list": (_I32, [_U32, _U32, _U32, _U32, _U32, _U32, _VP, _U32, _VP]),
     "s14_mxfp4_expert_page_from_tensors": (_I32, [_U32, _U32, _VP, _VP]),
     "s14_mxfp4_expert_page_to_tensors": (_I32, [_U32, _U32, _VP, _VP]),

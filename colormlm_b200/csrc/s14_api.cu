@@ -1916,40 +1916,85 @@ extern "C" int32_t s14_cmd_moe_block(s14_ctx *ctx, void *stream, s14_block *blk,
     S14_CATCH
 }
 
-extern "C" int32_t s14_cmd_routed_moe_block(s14_ctx *ctx, void *stream, s14_block *blk, const s14_routed_layer_desc *desc) {
+// What the routed block calls share: checks, the router's two launches; rd receives the router with its outputs set.
+static int32_t routed_block_router(s14_ctx *ctx, cudaStream_t st, s14_block *blk, const s14_routed_layer_desc *desc,
+                                   s14_router_desc *rd, bool need_outputs) {
     S14_TRY
-    if (!ctx || !blk || !desc) throw ContractError("s14_cmd_routed_moe_block: NULL argument");
-    if (blk->ctx != ctx) throw ContractError("s14_cmd_routed_moe_block: the block object belongs to another context");
+    if (blk->ctx != ctx) throw ContractError("S14 MoE block: the block object belongs to another context");
     const s14_router_desc &r = desc->router;
-    if (r.hidden != blk->hidden || desc->inter != blk->inter)
-        throw ContractError("s14_cmd_routed_moe_block: sizes differ from the block object's");
-    if (r.hidden > 8192u) throw ContractError("s14_cmd_routed_moe_block: hidden above 8192");
+    if (r.hidden != blk->hidden || desc->inter != blk->inter) throw ContractError("S14 MoE block: sizes differ from the block object's");
+    if (r.hidden > 8192u) throw ContractError("S14 MoE block: hidden above 8192");
     if (r.n_tokens == 0 || r.n_tokens > blk->max_tokens)
-        throw ContractError("s14_cmd_routed_moe_block: more tokens than the block object was created for");
+        throw ContractError("S14 MoE block: more tokens than the block object was created for");
     if (r.n_experts == 0 || r.n_experts > S14_N_ROUTED_EXPERTS) throw ContractError("S14 router: 1..256 experts");
     if (r.top_k == 0 || r.top_k > S14_EXPERTS_PER_TOKEN || r.top_k > r.n_experts)
-        throw ContractError("s14_cmd_routed_moe_block: top_k must be 1..6");
+        throw ContractError("S14 MoE block: top_k must be 1..6");
     if (r.score_fn != S14_SCORE_SIGMOID && r.score_fn != S14_SCORE_SQRT_SOFTPLUS)
         throw ContractError("S14 router: unknown score function");
     if (!std::isfinite(r.route_scale) || r.route_scale <= 0.0f)
         throw ContractError("S14 router: route_scale must be finite and positive");
-    if (!r.x || !r.router_weight_bf16 || !desc->page_table || !desc->y)
-        throw ContractError("s14_cmd_routed_moe_block: x, router weight, page table or y is NULL");
+    if (!r.x || !r.router_weight_bf16 || !desc->page_table) throw ContractError("S14 MoE block: x, router weight or page table is NULL");
+    if (need_outputs && (!r.ids_out || !r.weights_out)) throw ContractError("S14 MoE block: ids_out or weights_out is NULL");
     if (desc->shared_page && desc->shared_kind != S14_PAGE_MXFP4)
-        throw ContractError("s14_cmd_routed_moe_block: the grouped kernels take MXFP4 pages only");
+        throw ContractError("S14 MoE block: the grouped kernels take MXFP4 pages only");
     require_aligned(r.x, 16, "S14 router x");
     require_aligned(r.router_weight_bf16, 16, "S14 router weight");
     CUDA_OK(cudaSetDevice(ctx->device));
-    cudaStream_t st = stream_of(ctx, stream);
-    s14_router_desc rd = r;
-    if (!rd.ids_out) rd.ids_out = blk->ids;
-    if (!rd.weights_out) rd.weights_out = blk->weights;
+    *rd = r;
+    if (!rd->ids_out) rd->ids_out = blk->ids;
+    if (!rd->weights_out) rd->weights_out = blk->weights;
     cudaError_t err;
-    ctx->launches += launch_router_batch(st, rd, blk->scores, blk->select, &err);
+    ctx->launches += launch_router_batch(st, *rd, blk->scores, blk->select, &err);
     if (err != cudaSuccess) return cuda_fail(err, "S14 router launch");
-    return block_launch(blk, st, r.x, desc->y, rd.ids_out, rd.weights_out, nullptr, desc->page_table, desc->shared_page,
-                        r.n_tokens, r.top_k, r.n_experts);
+    return S14_OK;
     S14_CATCH
+}
+
+extern "C" int32_t s14_cmd_routed_moe_block(s14_ctx *ctx, void *stream, s14_block *blk, const s14_routed_layer_desc *desc) {
+    if (!ctx || !blk || !desc) return fail(S14_ERR_CONTRACT, "s14_cmd_routed_moe_block: NULL argument");
+    if (!desc->y) return fail(S14_ERR_CONTRACT, "s14_cmd_routed_moe_block: y is NULL");
+    cudaStream_t st = stream_of(ctx, stream);
+    s14_router_desc rd;
+    const int32_t rc = routed_block_router(ctx, st, blk, desc, &rd, false);
+    if (rc != S14_OK) return rc;
+    return block_launch(blk, st, rd.x, desc->y, rd.ids_out, rd.weights_out, nullptr, desc->page_table, desc->shared_page,
+                        rd.n_tokens, rd.top_k, rd.n_experts);
+}
+
+// Expert parallel: the block's pairs of the experts this rank owns (expert e on rank e mod world, the shared
+// expert on shared_owner) into pairs_out [n_tokens * 7, hidden], zeros elsewhere; no mix.
+extern "C" int32_t s14_cmd_routed_moe_block_experts_ep(s14_ctx *ctx, void *stream, s14_block *blk,
+                                                       const s14_routed_layer_desc *desc, uint32_t ep_rank, uint32_t ep_world,
+                                                       uint32_t shared_owner, float *pairs_out) {
+    if (!ctx || !blk || !desc || !pairs_out) return fail(S14_ERR_CONTRACT, "s14_cmd_routed_moe_block_experts_ep: NULL argument");
+    if (ep_world == 0 || ep_world > kMaxEpWorld || ep_rank >= ep_world || shared_owner >= ep_world)
+        return fail(S14_ERR_CONTRACT, "s14_cmd_routed_moe_block_experts_ep: rank or shared owner outside the world (1..8 ranks)");
+    cudaStream_t st = stream_of(ctx, stream);
+    s14_router_desc rd;
+    const int32_t rc = routed_block_router(ctx, st, blk, desc, &rd, true);
+    if (rc != S14_OK) return rc;
+    cudaError_t err;
+    ctx->launches += launch_moe_block(st, ctx->sm_count, blk->w, rd.x, nullptr, rd.ids_out, rd.weights_out, nullptr, desc->page_table,
+                                      shared_owner == ep_rank ? desc->shared_page : nullptr, rd.n_tokens, rd.top_k, rd.n_experts,
+                                      blk->hidden, blk->inter, ctx->status, &err, 0, false, ep_rank, ep_world, pairs_out);
+    ctx->last_path = S14_LAYER_PATH_TENSOR_BLOCK;
+    if (err != cudaSuccess) return cuda_fail(err, "S14 MoE block launch");
+    return S14_OK;
+}
+
+// The ordered mix of a block from a pairs buffer (after the ranks' buffers have been added up).
+extern "C" int32_t s14_cmd_moe_block_mix(s14_ctx *ctx, void *stream, s14_block *blk, const float *pairs, const int32_t *ids,
+                                         const float *weights, uint32_t n_tokens, uint32_t top_k, int32_t has_shared,
+                                         const float *x_residual, float *y) {
+    if (!ctx || !blk || !pairs || !ids || !weights || !y) return fail(S14_ERR_CONTRACT, "s14_cmd_moe_block_mix: NULL argument");
+    if (n_tokens == 0 || n_tokens > blk->max_tokens || top_k == 0 || top_k > S14_EXPERTS_PER_TOKEN)
+        return fail(S14_ERR_CONTRACT, "s14_cmd_moe_block_mix: token count or top_k out of range");
+    CUDA_OK(cudaSetDevice(ctx->device));
+    const cudaError_t err = launch_block_mix(stream_of(ctx, stream), pairs, ids, weights, n_tokens, top_k, has_shared != 0, x_residual, y,
+                                             blk->hidden, blk->w.counts);
+    ctx->launches += 1;
+    if (err != cudaSuccess) return cuda_fail(err, "S14 MoE block mix launch");
+    return S14_OK;
 }
 
 extern "C" int32_t s14_block_set_residual(s14_block *blk, int32_t residual) {

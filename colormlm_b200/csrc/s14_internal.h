@@ -191,7 +191,13 @@ size_t moe_block_max_chunks(uint32_t max_tokens);
 int launch_moe_block(cudaStream_t st, int sm_count, const BlockWork &w, const float *x, float *y, const int32_t *ids,
                      const float *weights, const uint8_t *const *pages, const uint8_t *const *page_table,
                      const uint8_t *shared_page, uint32_t n_tokens, uint32_t top_k, uint32_t n_experts, uint32_t hidden,
-                     uint32_t inter, uint32_t *status, cudaError_t *err, uint32_t nt_cap = 0, bool residual = false);
+                     uint32_t inter, uint32_t *status, cudaError_t *err, uint32_t nt_cap = 0, bool residual = false,
+                     uint32_t ep_rank = 0, uint32_t ep_world = 1, float *pairs_out = nullptr);
+// With pairs_out (expert parallel: rank ep_rank of ep_world computes the experts e with e mod world == rank) the
+// pairs' expert outputs [n_tokens * 7, hidden] go there, zero where another rank owns the expert, and no mix runs;
+// launch_block_mix mixes such a buffer once the ranks' buffers have been added up (x: the layer's input for a residual, or NULL).
+cudaError_t launch_block_mix(cudaStream_t st, const float *pairs, const int32_t *ids, const float *weights, uint32_t n_tokens,
+                             uint32_t top_k, bool has_shared, const float *x, float *y, uint32_t hidden, const uint32_t *counts);
 // Scores and routes of many tokens (s14_kernels.cu): the tokens of a tile share the router rows in
 // shared memory; one warp per token selects.  Same arithmetic as launch_router.  Returns the number
 // of kernels launched.

@@ -93,7 +93,7 @@ __global__ void __launch_bounds__(1024)
 k_block_group(const int32_t *__restrict__ ids, const uint8_t *const *__restrict__ pages,
               const uint8_t *const *__restrict__ page_table, const uint8_t *shared_page, uint32_t T, uint32_t top_k,
               uint32_t n_experts, uint32_t S, uint32_t RT, uint32_t nt_cap, BlockChunk *__restrict__ chunks,
-              uint32_t *__restrict__ counts) {
+              uint32_t *__restrict__ counts, uint32_t ep_rank, uint32_t ep_world) {
     constexpr uint32_t kG = S14_N_ROUTED_EXPERTS + 1;
     __shared__ uint32_t cnt[kG], fill[kG], chunk0[kG + 1];
     __shared__ unsigned long long gpage[kG];
@@ -110,7 +110,7 @@ k_block_group(const int32_t *__restrict__ ids, const uint8_t *const *__restrict_
     for (uint32_t i = tid; i < n; i += blockDim.x) {
         const int32_t e = __ldg(ids + i);
         if (e >= (int32_t)n_experts) bad = 1u;
-        else if (e >= 0) atomicAdd(&cnt[1 + e], 1u);
+        else if (e >= 0 && (uint32_t)e % ep_world == ep_rank) atomicAdd(&cnt[1 + e], 1u);  // expert parallel: the experts this rank owns
     }
     if (tid == 0 && shared_page) cnt[0] = T;
     __syncthreads();
@@ -150,7 +150,7 @@ k_block_group(const int32_t *__restrict__ ids, const uint8_t *const *__restrict_
     if (bad) return;
     for (uint32_t i = tid; i < n; i += blockDim.x) {
         const int32_t e = __ldg(ids + i);
-        if (e < 0) continue;
+        if (e < 0 || (uint32_t)e % ep_world != ep_rank) continue;
         const uint32_t g = 1u + (uint32_t)e, t = i / top_k, m = i - t * top_k;
         const uint32_t k = atomicAdd(&fill[g], 1u);
         if (k == 0u && !page_table) gpage[g] = (unsigned long long)pages[i];
@@ -600,7 +600,8 @@ size_t moe_block_max_chunks(uint32_t max_tokens) {
 int launch_moe_block(cudaStream_t st, int sm_count, const BlockWork &w, const float *x, float *y, const int32_t *ids,
                      const float *weights, const uint8_t *const *pages, const uint8_t *const *page_table,
                      const uint8_t *shared_page, uint32_t n_tokens, uint32_t top_k, uint32_t n_experts, uint32_t hidden,
-                     uint32_t inter, uint32_t *status, cudaError_t *err, uint32_t nt_cap, bool residual) {
+                     uint32_t inter, uint32_t *status, cudaError_t *err, uint32_t nt_cap, bool residual, uint32_t ep_rank,
+                     uint32_t ep_world, float *pairs_out) {
     // Tokens per chunk.  A small block is bound by the memory's latency: most experts have one token,
     // and short stages make the ring deeper (more page bytes in flight); the shared expert's extra
     // chunks come from the L2.  A large block wants few passes over every expert.
@@ -613,16 +614,33 @@ int launch_moe_block(cudaStream_t st, int sm_count, const BlockWork &w, const fl
     const uint32_t S = inter >> 6, RT = hidden >> 7;
     const size_t smem = (size_t)ring * stage + 2u * kSfbBytes;
     k_block_digits<<<n_tokens, 512, 0, st>>>(x, hidden, w.xdig, w.xexp);
+    if (ep_world == 0u) ep_world = 1u;
     k_block_group<<<1, 1024, 0, st>>>(ids, pages, page_table, shared_page, n_tokens, top_k, n_experts, S, RT, nt_cap, w.chunks,
-                                     w.counts);
+                                     w.counts, ep_rank, ep_world);
+    if (pairs_out) {
+        // expert parallel: the pairs of the experts this rank owns; the others stay zero for the sum over the ranks
+        *err = cudaMemsetAsync(pairs_out, 0, (size_t)n_tokens * kPairsPerToken * hidden * sizeof(float), st);
+        if (*err != cudaSuccess) return 2;
+    }
     GemmArgs up = {w.chunks, w.counts + 1, w.xdig, w.xexp, nullptr, w.hdig, w.hexp, hidden, inter, ring, stage};
     k_block_gemm<false><<<sm_count, kGThreads, smem, st>>>(up, status);
-    GemmArgs down = {w.chunks, w.counts + 2, w.hdig, w.hexp, w.d, nullptr, nullptr, hidden, inter, ring, stage};
+    GemmArgs down = {w.chunks, w.counts + 2, w.hdig, w.hexp, pairs_out ? pairs_out : w.d, nullptr, nullptr, hidden, inter, ring, stage};
     k_block_gemm<true><<<sm_count, kGThreads, smem, st>>>(down, status);
+    if (pairs_out) {
+        *err = cudaGetLastError();
+        return 4;
+    }
     k_block_mix<<<dim3((hidden + 255u) / 256u, n_tokens), 256, 0, st>>>(w.d, ids, weights, top_k, shared_page != nullptr, y, hidden,
                                                                        w.counts, x, residual ? 1u : 0u);
     *err = cudaGetLastError();
     return 5;
+}
+
+cudaError_t launch_block_mix(cudaStream_t st, const float *pairs, const int32_t *ids, const float *weights, uint32_t n_tokens,
+                             uint32_t top_k, bool has_shared, const float *x, float *y, uint32_t hidden, const uint32_t *counts) {
+    k_block_mix<<<dim3((hidden + 255u) / 256u, n_tokens), 256, 0, st>>>(pairs, ids, weights, top_k, has_shared, y, hidden, counts, x,
+                                                                       x ? 1u : 0u);
+    return cudaGetLastError();
 }
 
 }  // namespace s14

@@ -102,6 +102,21 @@ def verify_block_fused(ctx, xs, layer_state: dict, ys, *, layer: int, world: int
                                     weights_out=None if weights is None else weights[t], stream=stream)
 
 
+def block_layer(blk, xs, layer_state: dict, pairs, ids, weights, ys, *, layer: int, rank: int, world: int,
+                residual: bool = False, stream: Optional[int] = None, group=None) -> None:
+    """A block of tokens (a verify block, a prefill) through one expert-parallel layer on the grouped block
+    path: xs, ys [T, hidden]; pairs [T * 7, hidden], ids, weights [T, top_k] device buffers.  Tokens are
+    replicated, experts sharded: every rank routes all tokens, runs the grouped contractions of the experts
+    it owns (each of their pages streamed once for all its tokens), one all-reduce adds the ranks' pair
+    buffers up (every row has one non-zero contributor, so the sum is exact), and the ordered mix runs on
+    every rank: ys is bit-identical to the single-GPU block for any world size."""
+    blk.cmd_routed_moe_block_experts_ep(xs, layer_state["wr"], layer_state["bias"], layer_state["table"],
+                                        layer_state["shared"], pairs, ids, weights, ep_rank=rank, ep_world=world,
+                                        shared_owner=shared_owner(layer, world), stream=stream)
+    all_reduce_slots(pairs, group)
+    blk.cmd_mix(pairs, ids, weights, ys, has_shared=True, x_residual=xs if residual else None, stream=stream)
+
+
 # ---- vocabulary-sharded LM head ---------------------------------------------------------------
 # The head weight [vocab, hidden] BF16 is split by rows: rank r holds rows [vocab r / G, vocab (r+1) / G)
 # (final_head.py:113-149 computes all rows on one device; the runner's contract wants the full logits,

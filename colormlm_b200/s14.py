@@ -458,6 +458,30 @@ class MoeBlock:
         check(L.lib().s14_cmd_routed_moe_block(self._ctx.handle, stream if stream is not None else _torch_stream(),
                                                self._h, C.byref(d)))
 
+    def cmd_routed_moe_block_experts_ep(self, x, wr_bf16, bias, page_table, shared_page: Optional[int], pairs_out, ids_out,
+                                        weights_out, *, ep_rank: int, ep_world: int, shared_owner: int,
+                                        score_fn: int = L.SCORE_SIGMOID, top_k: int = 6, route_scale: float = 1.0,
+                                        stream: Optional[int] = None) -> None:
+        """Expert parallel: the pairs of the experts this rank owns into pairs_out [n_tokens * 7, hidden]."""
+        d = L.RoutedLayerDesc()
+        d.router = _router_desc(x, wr_bf16, bias, ids_out, weights_out, score_fn, top_k, route_scale)
+        d.inter = self.inter
+        d.shared_kind = L.PAGE_MXFP4
+        d.page_table = page_table.data_ptr()
+        d.shared_page = shared_page
+        d.y = None
+        check(L.lib().s14_cmd_routed_moe_block_experts_ep(
+            self._ctx.handle, stream if stream is not None else _torch_stream(), self._h, C.byref(d), ep_rank, ep_world,
+            shared_owner, pairs_out.data_ptr()))
+
+    def cmd_mix(self, pairs, ids, weights, y, *, has_shared: bool = True, x_residual=None,
+                stream: Optional[int] = None) -> None:
+        """The ordered mix of every token from a pairs buffer (after the ranks' buffers were added up)."""
+        check(L.lib().s14_cmd_moe_block_mix(
+            self._ctx.handle, stream if stream is not None else _torch_stream(), self._h, pairs.data_ptr(), ids.data_ptr(),
+            weights.data_ptr(), ids.shape[0], ids.shape[1], 1 if has_shared else 0,
+            x_residual.data_ptr() if x_residual is not None else None, y.data_ptr()))
+
     def set_residual(self, residual: bool) -> None:
         """The calls that follow write y = x + moe(x); y may then be x."""
         check(L.lib().s14_block_set_residual(self._h, 1 if residual else 0))

@@ -492,6 +492,21 @@ S14_API int32_t s14_block_destroy(s14_block *blk);
 S14_API int32_t s14_block_set_residual(s14_block *blk, int32_t residual);
 S14_API int32_t s14_cmd_moe_block(s14_ctx *ctx, void *stream, s14_block *blk, const s14_moe_layer_desc *desc);
 S14_API int32_t s14_cmd_routed_moe_block(s14_ctx *ctx, void *stream, s14_block *blk, const s14_routed_layer_desc *desc);
+/* Expert parallel (no counterpart in the reference; partition as s14_cmd_routed_moe_experts_ep: expert e
+ * on rank e mod world, the shared expert on shared_owner; the tokens are on every rank).  Every rank
+ * routes all tokens itself, groups the (token, route) pairs of the experts IT owns and writes their
+ * expert outputs into pairs_out [n_tokens * 7, hidden] (pair = token * 7 + position in the route,
+ * 6: the shared expert), zeros where another rank owns the expert; ids_out / weights_out are
+ * required.  The caller adds the ranks' buffers up (one all-reduce: every row has one non-zero
+ * contributor, so the sum is exact) and calls s14_cmd_moe_block_mix on every rank: y is then
+ * bit-identical to the single-GPU block for any number of ranks.  x_residual: the layer's input to
+ * add (y = x + moe(x)), or NULL. */
+S14_API int32_t s14_cmd_routed_moe_block_experts_ep(s14_ctx *ctx, void *stream, s14_block *blk,
+                                                    const s14_routed_layer_desc *desc, uint32_t ep_rank,
+                                                    uint32_t ep_world, uint32_t shared_owner, float *pairs_out);
+S14_API int32_t s14_cmd_moe_block_mix(s14_ctx *ctx, void *stream, s14_block *blk, const float *pairs, const int32_t *ids,
+                                      const float *weights, uint32_t n_tokens, uint32_t top_k, int32_t has_shared,
+                                      const float *x_residual, float *y);
 /* After the stream is synchronised: the last call's number of chunks, up items, down items, and 1 if
  * an expert id was outside the table (the call then wrote no result). */
 S14_API int32_t s14_block_last_counts(s14_block *blk, uint32_t counts_out[4]);

@@ -149,6 +149,48 @@ def test_routed_block_picks_the_oracles_routes(ctx, oracle, score_fn):
         blk.close()
 
 
+@pytest.mark.parametrize("world", [2, 4])
+def test_block_expert_parallel_ranks_add_up_to_the_single_gpu_block(ctx, world):
+    """The ranks of an expert-parallel block, run one after the other on this GPU: the sum of their pair
+    buffers (every row has one owner) mixed is the single-GPU block, bit for bit; with and without residual."""
+    from colormlm_b200 import ep
+
+    hidden, inter, n_experts, n_tokens = 2048, 1024, 32, 20
+    g, pages, shared = make_layer(1500 + world, hidden, inter, n_experts, L.PAGE_MXFP4)
+    wr, bias = dev(synth.router_weight_bf16(g, n_experts, hidden)), dev(synth.router_bias(g, n_experts))
+    dx = dev(synth.activations(g, n_tokens, hidden))
+    pages_dev, shared_dev = [dev_page(p, hidden, inter) for p in pages], dev_page(shared, hidden, inter)
+    table = torch.tensor([p.data_ptr() for p in pages_dev], dtype=torch.int64, device="cuda")
+    blk = MoeBlock(ctx, hidden, inter, 32)
+    try:
+        want = torch.full_like(dx, float("nan"))
+        blk.cmd_routed_moe_block(dx, wr, bias, table, shared_dev.data_ptr(), want)
+        torch.cuda.synchronize()
+        ids = torch.empty((n_tokens, 6), dtype=torch.int32, device="cuda")
+        wts = torch.empty((n_tokens, 6), dtype=torch.float32, device="cuda")
+        total = torch.zeros((n_tokens * 7, hidden), dtype=torch.float32, device="cuda")
+        owners = torch.zeros(n_tokens * 7, dtype=torch.int32, device="cuda")
+        for rank in range(world):
+            part = torch.full_like(total, float("nan"))
+            blk.cmd_routed_moe_block_experts_ep(dx, wr, bias, table, shared_dev.data_ptr(), part, ids, wts, ep_rank=rank,
+                                                ep_world=world, shared_owner=ep.shared_owner(3, world))
+            torch.cuda.synchronize()
+            assert ctx.device_status() == 0
+            assert not torch.isnan(part).any()
+            owners += (part != 0).any(dim=1).int()
+            total += part
+        assert int(owners.max().item()) == 1   # no row has two contributors
+        got = torch.full_like(dx, float("nan"))
+        blk.cmd_mix(total, ids, wts, got, has_shared=True)
+        torch.cuda.synchronize()
+        assert np.array_equal(got.cpu().numpy().view(np.uint32), want.cpu().numpy().view(np.uint32))
+        blk.cmd_mix(total, ids, wts, got, has_shared=True, x_residual=dx)
+        torch.cuda.synchronize()
+        assert np.array_equal(got.cpu().numpy().view(np.uint32), (dx + want).cpu().numpy().view(np.uint32))
+    finally:
+        blk.close()
+
+
 def test_block_with_residual_in_place(ctx):
     """y = x + moe(x), written over x: the step of a stack of layers."""
     hidden, inter, n_experts, n_tokens = 2048, 1024, 16, 9
