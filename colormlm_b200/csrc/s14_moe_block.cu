@@ -24,11 +24,12 @@
 // Items are dealt round robin to one persistent CTA per SM, the chunks of one expert next to each
 // other, so that the second and later chunks of an expert find its units in the L2.
 //
-// Roles inside a GEMM CTA: one copying thread (a unit of 17 KB page bytes plus the chunk's token
-// tiles of that K range into one ring stage: plain bulk copies, no multicast), two MMA-issuing
-// threads (even and odd units of an item, an accumulator each), four epilogue warps, eight warps
-// that lay out the digit rows' scale codes of the next item in shared memory (tcgen05.cp brings
-// them to tensor memory unit by unit, like the weights' scales).  Every wait is bounded; a wait that
+// Roles inside a GEMM CTA: one copying thread (a unit of 17 KB page bytes per ring stage: a plain
+// bulk copy, no multicast), two MMA-issuing threads (even and odd units of an item, an accumulator
+// each), four epilogue warps, eight warps that lay out the digit rows' scale codes of an item in
+// shared memory (tcgen05.cp brings them to tensor memory unit by unit, like the weights' scales) and
+// then, for large blocks, fetch the chunk's token tiles of every unit into the unit's stage (cp.async,
+// 16 bytes a thread; for small blocks a second copying thread brings them by bulk copies).  Every wait is bounded; a wait that
 // runs out raises the CTA's abort flag, the status word is set, and the CTA waits for its copies in
 // flight, frees its tensor memory and returns.
 #include "s14_umma.cuh"
@@ -68,6 +69,7 @@ struct GemmArgs {
     const uint8_t *exps;        // their block exponents + 100, [vector][K / 32]
     float *out;                 // down: the pairs' expert outputs [pair][hidden]
     uint8_t *hdig, *hexp;       // up: digit tiles and exponents of the pairs' hidden values
+    uint32_t by_threads;        // the token tiles come by the tile threads' own copies (large blocks), else by bulk copies
     uint32_t hidden, inter, ring, stage;   // stage: bytes of a ring stage (a unit and nt_cap token tiles)
 };
 
@@ -219,7 +221,8 @@ k_block_gemm(const __grid_constant__ GemmArgs a, uint32_t *status) {
 
     if (tid < kGBars) {
         uint32_t count = 1u;
-        if (tid >= kGBarAccDone && tid < kGBarAccDone + 2u) count = 2u;
+        if (tid < kGRingMax) count = a.by_threads ? 1u + kGLayThreads : 1u;   // a stage: the page copy's arrival (and the tile threads' copies)
+        else if (tid >= kGBarAccDone && tid < kGBarAccDone + 2u) count = 2u;
         else if (tid >= kGBarAccFree && tid < kGBarAccFree + 2u) count = 128u;
         else if (tid >= kGBarSfb && tid < kGBarSfb + 2u) count = kGLayThreads;
         else if (tid == kGBarFin) count = 2u;
@@ -246,7 +249,7 @@ k_block_gemm(const __grid_constant__ GemmArgs a, uint32_t *status) {
     const uint32_t R = kDown ? (a.hidden >> 7) : (a.inter >> 6);
     const uint32_t n_local = n_items > cta ? (n_items - cta + grid - 1u) / grid : 0u;
 
-    const bool is_prod_a = tid == kGProdWarp * 32u, is_prod_b = tid == kGTileWarp * 32u;
+    const bool is_prod_a = tid == kGProdWarp * 32u, is_prod_b = tid == kGTileWarp * 32u && !a.by_threads;
     const bool is_issuer = (warp == kGMmaWarp0 || warp == kGMmaWarp0 + 1u) && lane == 0;
     // what the roles carry from item to item
     uint32_t p_slot = 0, p_round = 0, p_units = 0;             // the copying threads: next stage
@@ -281,11 +284,11 @@ k_block_gemm(const __grid_constant__ GemmArgs a, uint32_t *status) {
         __syncthreads();
 
         if (is_prod_a) {
-            // ---- the copying thread of the pages: per unit of every item one ring stage; it arms the
-            // stage's barrier with the bytes of the unit and of the token tiles ----
+            // ---- the copying thread of the pages: per unit of every item one ring stage (a bulk copy of
+            // 17 KB of page bytes, counted in bytes on the stage's barrier) ----
 #pragma unroll 1
             for (uint32_t i = 0; i < nb && ok; ++i) {
-                const uint32_t nt = s_rec[i].nt & 0xFFu, multi = s_rec[i].nt >> 8;
+                const uint32_t multi = s_rec[i].nt >> 8;
                 const uint8_t *src = reinterpret_cast<const uint8_t *>(s_rec[i].page) + page_off + (size_t)s_rec[i].r * nu * kUnitStride;
 #pragma unroll 1
                 for (uint32_t u = 0; u < nu; ++u) {
@@ -294,7 +297,7 @@ k_block_gemm(const __grid_constant__ GemmArgs a, uint32_t *status) {
                         break;
                     }
                     const uint32_t full = bar(kGBarFull + p_slot), dst = smem_u32(sRing) + p_slot * a.stage;
-                    mbar_arrive_expect(full, kStageA + nt * 2048u);
+                    mbar_arrive_expect(full, kStageA + (a.by_threads ? 0u : (s_rec[i].nt & 0xFFu) * 2048u));
                     // an expert with one chunk is read once; with more, its later chunks want the units in the L2
                     if (multi) bulk_copy(dst, src, kStageA, full);
                     else bulk_copy_stream(dst, src, kStageA, full, once);
@@ -308,9 +311,9 @@ k_block_gemm(const __grid_constant__ GemmArgs a, uint32_t *status) {
             }
             s_units = p_units;
         } else if (is_prod_b) {
-            // ---- the copying thread of the token tiles: the chunk's tiles of the unit's K range behind the
-            // unit, counted on the same barrier (bytes that land before the barrier is armed are
-            // counted all the same) ----
+            // ---- small blocks: a second copying thread brings the chunk's token tiles of the unit's K range
+            // behind the unit by bulk copies, counted on the same barrier (bytes that land before the barrier
+            // is armed are counted all the same) ----
 #pragma unroll 1
             for (uint32_t i = 0; i < nb && ok; ++i) {
                 const uint32_t nt = s_rec[i].nt & 0xFFu;
@@ -362,6 +365,7 @@ k_block_gemm(const __grid_constant__ GemmArgs a, uint32_t *status) {
                         m_slot -= ring;
                         ++m_round;
                     }
+                    fence_async_smem();  // the token tiles came by the threads' own copies: the tensor cores read them
                     fence_after();
                     const uint64_t sfd = sf_desc0 + s * (a.stage >> 4), sbd = sfb_desc0 + ku * (1024u >> 4);
                     tmem_copy_scales(sfa_t, sfd);
@@ -501,7 +505,34 @@ k_block_gemm(const __grid_constant__ GemmArgs a, uint32_t *status) {
                     if (u < nu) *reinterpret_cast<uint32_t *>(dst + u * 1024u) = ew[u];
                 fence_async_smem();  // tcgen05.cp reads the atoms
                 mbar_arrive(bar(kGBarSfb + buf));
+                // ---- large blocks: the chunk's token tiles of every unit of the item, behind the unit in its
+                // ring stage: sixteen bytes per copy and thread (cp.async: these bytes do not pass through the
+                // bulk-copy unit that brings the pages; measured 1.83 -> 1.65 ms for 370 tokens, but 151 -> 165 us
+                // for 8), the copies' completion counted on the stage's barrier ----
+                if (!a.by_threads) continue;   // (small blocks: the second copying thread brings them)
+                const uint32_t n16 = nt * 128u;   // sixteen-byte pieces of the chunk's tiles of one unit
+                const uint32_t *vecs = kDown ? s_rec[i].pair : s_rec[i].tok;
+#pragma unroll 1
+                for (uint32_t u = 0; u < nu; ++u) {
+                    if (p_round && !mbar_wait(bar(kGBarDone + p_slot), (p_round - 1u) & 1u, abortp)) {
+                        ok = false;
+                        break;
+                    }
+                    const uint32_t dst0 = smem_u32(sRing) + p_slot * a.stage + kStageA;
+#pragma unroll 1
+                    for (uint32_t c = lt; c < n16; c += kGLayThreads) {
+                        const uint32_t tt = c >> 7, off = (c & 127u) << 4;
+                        const uint8_t *src = a.dig + ((size_t)vecs[tt] * nu + u) * 2048u + off;
+                        asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(dst0 + tt * 2048u + off), "l"(src) : "memory");
+                    }
+                    asm volatile("cp.async.mbarrier.arrive.noinc.shared::cta.b64 [%0];" ::"r"(bar(kGBarFull + p_slot)) : "memory");
+                    if (++p_slot == ring) {
+                        p_slot = 0;
+                        ++p_round;
+                    }
+                }
             }
+            asm volatile("cp.async.wait_all;" ::: "memory");
         }
         __syncwarp();
         __syncthreads();  // the records are rewritten; a role that gave up has raised the flag
@@ -622,9 +653,10 @@ int launch_moe_block(cudaStream_t st, int sm_count, const BlockWork &w, const fl
         *err = cudaMemsetAsync(pairs_out, 0, (size_t)n_tokens * kPairsPerToken * hidden * sizeof(float), st);
         if (*err != cudaSuccess) return 2;
     }
-    GemmArgs up = {w.chunks, w.counts + 1, w.xdig, w.xexp, nullptr, w.hdig, w.hexp, hidden, inter, ring, stage};
+    const uint32_t by_threads = nt_cap > 2u ? 1u : 0u;
+    GemmArgs up = {w.chunks, w.counts + 1, w.xdig, w.xexp, nullptr, w.hdig, w.hexp, by_threads, hidden, inter, ring, stage};
     k_block_gemm<false><<<sm_count, kGThreads, smem, st>>>(up, status);
-    GemmArgs down = {w.chunks, w.counts + 2, w.hdig, w.hexp, pairs_out ? pairs_out : w.d, nullptr, nullptr, hidden, inter, ring, stage};
+    GemmArgs down = {w.chunks, w.counts + 2, w.hdig, w.hexp, pairs_out ? pairs_out : w.d, nullptr, nullptr, by_threads, hidden, inter, ring, stage};
     k_block_gemm<true><<<sm_count, kGThreads, smem, st>>>(down, status);
     if (pairs_out) {
         *err = cudaGetLastError();
