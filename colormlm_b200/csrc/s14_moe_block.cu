@@ -193,13 +193,16 @@ struct ItemRec {
     uint32_t tok[kNt];
     uint32_t pair[kNt];
 };
-constexpr uint32_t kBatch = 192;   // items decoded at a time
-
-template <bool kDown>
+// kMt: row tiles (slices of the up phase) per item.  With two, the chunk's token tiles of a K range are
+// fetched once for two units of page bytes (a stage holds both units, then the tiles), which halves the
+// tile bytes an SM takes in; every issuing thread then holds two accumulators and there is no second
+// accumulator buffer (the next item's MMAs wait until the epilogue has read the accumulators).
+template <bool kDown, uint32_t kMt>
 __global__ void __launch_bounds__(kGThreads, 1)
 k_block_gemm(const __grid_constant__ GemmArgs a, uint32_t *status) {
     extern __shared__ __align__(1024) uint8_t smem[];
     __shared__ __align__(8) uint64_t bars[kGBars];
+    constexpr uint32_t kBatch = kMt == 1u ? 192u : 96u;   // items decoded at a time
     __shared__ __align__(16) ItemRec s_rec[kBatch];
     __shared__ float s_up[kNt][64];                          // an item's up projections, handed to the gate threads
     __shared__ __align__(16) uint8_t s_hst[kNt][16 * 2 * 16]; // an up item's digit chunks per token: [row][block][16 bytes]
@@ -246,7 +249,7 @@ k_block_gemm(const __grid_constant__ GemmArgs a, uint32_t *status) {
     // The CTA's items are q = cta, cta + grid, ...  The chunks of one expert follow one another and so
     // do their items, a row tile's chunks side by side (so that CTAs that run at the same time share
     // the expert's units in the L2).
-    const uint32_t R = kDown ? (a.hidden >> 7) : (a.inter >> 6);
+    const uint32_t R = (kDown ? (a.hidden >> 7) : (a.inter >> 6)) / kMt;   // items per chunk
     const uint32_t n_local = n_items > cta ? (n_items - cta + grid - 1u) / grid : 0u;
 
     const bool is_prod_a = tid == kGProdWarp * 32u, is_prod_b = tid == kGTileWarp * 32u && !a.by_threads;
@@ -289,7 +292,8 @@ k_block_gemm(const __grid_constant__ GemmArgs a, uint32_t *status) {
 #pragma unroll 1
             for (uint32_t i = 0; i < nb && ok; ++i) {
                 const uint32_t multi = s_rec[i].nt >> 8;
-                const uint8_t *src = reinterpret_cast<const uint8_t *>(s_rec[i].page) + page_off + (size_t)s_rec[i].r * nu * kUnitStride;
+                const uint8_t *src = reinterpret_cast<const uint8_t *>(s_rec[i].page) + page_off +
+                                     (size_t)s_rec[i].r * kMt * nu * kUnitStride;
 #pragma unroll 1
                 for (uint32_t u = 0; u < nu; ++u) {
                     if (p_round && !mbar_wait(bar(kGBarDone + p_slot), (p_round - 1u) & 1u, abortp)) {
@@ -297,10 +301,13 @@ k_block_gemm(const __grid_constant__ GemmArgs a, uint32_t *status) {
                         break;
                     }
                     const uint32_t full = bar(kGBarFull + p_slot), dst = smem_u32(sRing) + p_slot * a.stage;
-                    mbar_arrive_expect(full, kStageA + (a.by_threads ? 0u : (s_rec[i].nt & 0xFFu) * 2048u));
+                    mbar_arrive_expect(full, kMt * kStageA + (a.by_threads ? 0u : (s_rec[i].nt & 0xFFu) * 2048u));
                     // an expert with one chunk is read once; with more, its later chunks want the units in the L2
-                    if (multi) bulk_copy(dst, src, kStageA, full);
-                    else bulk_copy_stream(dst, src, kStageA, full, once);
+#pragma unroll
+                    for (uint32_t mt = 0; mt < kMt; ++mt) {
+                        if (multi) bulk_copy(dst + mt * kStageA, src + (size_t)mt * nu * kUnitStride, kStageA, full);
+                        else bulk_copy_stream(dst + mt * kStageA, src + (size_t)mt * nu * kUnitStride, kStageA, full, once);
+                    }
                     src += kUnitStride;
                     ++p_units;
                     if (++p_slot == ring) {
@@ -326,7 +333,7 @@ k_block_gemm(const __grid_constant__ GemmArgs a, uint32_t *status) {
                         ok = false;
                         break;
                     }
-                    const uint32_t full = bar(kGBarFull + p_slot), dst = smem_u32(sRing) + p_slot * a.stage + kStageA;
+                    const uint32_t full = bar(kGBarFull + p_slot), dst = smem_u32(sRing) + p_slot * a.stage + kMt * kStageA;
 #pragma unroll
                     for (uint32_t t = 0; t < kNt; ++t)
                         if (t < nt) bulk_copy(dst + t * 2048u, a.dig + ((size_t)vec[t] * nu + u) * 2048u, 2048u, full);
@@ -343,17 +350,22 @@ k_block_gemm(const __grid_constant__ GemmArgs a, uint32_t *status) {
             const uint32_t m = warp - kGMmaWarp0;
             const uint64_t a_desc0 = smem_desc(smem_u32(sRing), 1, 64, 2);
             const uint64_t sf_desc0 = smem_desc(smem_u32(sRing) + kUnitBytes, 0, 8, 0);
-            const uint64_t b_desc0 = smem_desc(smem_u32(sRing) + kStageA, 1, 64, 2);
+            const uint64_t b_desc0 = smem_desc(smem_u32(sRing) + kMt * kStageA, 1, 64, 2);
             const uint32_t sfa_t = tmem + kGColSfa + m * 16u, sfb_t = tmem + kGColSfb + m * 16u;
 #pragma unroll 1
             for (uint32_t i = 0; i < nb && ok; ++i, ++gi) {
                 const uint32_t buf = gi & 1u;
                 const uint32_t idesc = umma_idesc_mxf4(16u * (s_rec[i].nt & 0xFFu));
-                if (gi >= 2u) ok = mbar_wait(bar(kGBarAccFree + buf), ((gi - 2u) >> 1) & 1u, abortp);
+                // one row tile per item: the accumulators of item gi - 2 have been read; two: those of item gi - 1
+                if (kMt == 1u) {
+                    if (gi >= 2u) ok = mbar_wait(bar(kGBarAccFree + buf), ((gi - 2u) >> 1) & 1u, abortp);
+                } else if (gi >= 1u) {
+                    ok = mbar_wait(bar(kGBarAccFree + ((gi - 1u) & 1u)), ((gi - 1u) >> 1) & 1u, abortp);
+                }
                 ok = ok && mbar_wait(bar(kGBarSfb + buf), (gi >> 1) & 1u, abortp);
                 if (!ok) break;
                 fence_after();
-                const uint32_t acc = tmem + kGColAcc + (buf * 2u + m) * (16u * kNt);
+                const uint32_t acc = tmem + kGColAcc + ((kMt == 1u ? buf : 0u) * 2u + m) * (16u * kNt);   // row tile mt: + 2 * mt accumulators
                 const uint64_t sfb_desc0 = smem_desc(smem_u32(sSfb) + buf * kSfbBytes, 0, 8, 0);
 #pragma unroll 1
                 for (uint32_t ku = m; ku < nu; ku += 2u) {
@@ -368,16 +380,23 @@ k_block_gemm(const __grid_constant__ GemmArgs a, uint32_t *status) {
                     fence_async_smem();  // the token tiles came by the threads' own copies: the tensor cores read them
                     fence_after();
                     const uint64_t sfd = sf_desc0 + s * (a.stage >> 4), sbd = sfb_desc0 + ku * (1024u >> 4);
-                    tmem_copy_scales(sfa_t, sfd);
-                    tmem_copy_scales(sfa_t + 4u, sfd + (kAtomBytes >> 4));
+#pragma unroll
+                    for (uint32_t mt = 0; mt < kMt; ++mt) {
+                        tmem_copy_scales(sfa_t + mt * 8u, sfd + mt * (kStageA >> 4));
+                        tmem_copy_scales(sfa_t + mt * 8u + 4u, sfd + mt * (kStageA >> 4) + (kAtomBytes >> 4));
+                    }
                     tmem_copy_scales(sfb_t, sbd);
                     tmem_copy_scales(sfb_t + 4u, sbd + (kAtomBytes >> 4));
                     const uint64_t ad = a_desc0 + s * (a.stage >> 4), bd = b_desc0 + s * (a.stage >> 4);
 #pragma unroll
-                    for (uint32_t kk = 0; kk < 4; ++kk) {
-                        const uint32_t atom = kk >> 1, sfid = (kk & 1u) * 2u;
-                        umma_mxf4(acc, ad + kk * 2u, bd + kk * 2u, idesc | (sfid << 29) | (sfid << 4),
-                                  (sfa_t + atom * 4u) | (sfid << 30), (sfb_t + atom * 4u) | (sfid << 30), (ku >= 2u || kk) ? 1u : 0u);
+                    for (uint32_t mt = 0; mt < kMt; ++mt) {
+#pragma unroll
+                        for (uint32_t kk = 0; kk < 4; ++kk) {
+                            const uint32_t atom = kk >> 1, sfid = (kk & 1u) * 2u;
+                            umma_mxf4(acc + mt * 2u * (16u * kNt), ad + mt * (kStageA >> 4) + kk * 2u, bd + kk * 2u,
+                                      idesc | (sfid << 29) | (sfid << 4), (sfa_t + mt * 8u + atom * 4u) | (sfid << 30),
+                                      (sfb_t + atom * 4u) | (sfid << 30), (ku >= 2u || kk) ? 1u : 0u);
+                        }
                     }
                     umma_commit(bar(kGBarDone + s));
                 }
@@ -391,87 +410,95 @@ k_block_gemm(const __grid_constant__ GemmArgs a, uint32_t *status) {
             const uint32_t lane_base = tmem + ((warp * 32u) << 16);
 #pragma unroll 1
             for (uint32_t i = 0; i < nb && ok; ++i, ++gi) {
-                const uint32_t idx = s_rec[i].r, buf = gi & 1u, nt = s_rec[i].nt & 0xFFu;
+                const uint32_t idx0 = s_rec[i].r, buf = gi & 1u, nt = s_rec[i].nt & 0xFFu;
                 uint32_t pair[kNt];
 #pragma unroll
                 for (uint32_t t = 0; t < kNt; ++t) pair[t] = s_rec[i].pair[t];
                 ok = epi_all(mbar_wait(bar(kGBarAccDone + buf), (gi >> 1) & 1u, abortp));
                 if (!ok) break;
                 fence_after();
-                float v[kNt];
+                float v[kMt][kNt];
 #pragma unroll
-                for (uint32_t t = 0; t < kNt; ++t) {
-                    v[t] = 0.0f;
-                    if (t < nt) {  // uniform in the CTA
-                        double sum = 0.0;
+                for (uint32_t mt = 0; mt < kMt; ++mt) {
 #pragma unroll
-                        for (uint32_t half = 0; half < 2; ++half) {
-                            uint32_t r[16];
-                            tmem_ld16(lane_base + kGColAcc + (buf * 2u + half) * (16u * kNt) + 16u * t, r);
-                            tmem_ld_wait();
-                            double lo = 0.0, hi = 0.0;
+                    for (uint32_t t = 0; t < kNt; ++t) {
+                        v[mt][t] = 0.0f;
+                        if (t < nt) {  // uniform in the CTA
+                            double sum = 0.0;
 #pragma unroll
-                            for (int c = 0; c < 8; ++c) {
-                                lo += (double)__uint_as_float(r[8 + c]);
-                                hi += (double)__uint_as_float(r[c]);
+                            for (uint32_t half = 0; half < 2; ++half) {
+                                uint32_t r[16];
+                                tmem_ld16(lane_base + kGColAcc + ((kMt == 1u ? buf : mt) * 2u + half) * (16u * kNt) + 16u * t, r);
+                                tmem_ld_wait();
+                                double lo = 0.0, hi = 0.0;
+#pragma unroll
+                                for (int c = 0; c < 8; ++c) {
+                                    lo += (double)__uint_as_float(r[8 + c]);
+                                    hi += (double)__uint_as_float(r[c]);
+                                }
+                                sum += lo + hi;
                             }
-                            sum += lo + hi;
+                            v[mt][t] = (float)sum;
                         }
-                        v[t] = (float)sum;
                     }
                 }
                 fence_before();
                 mbar_arrive(bar(kGBarAccFree + buf));
-                if constexpr (kDown) {
-                    // row idx * 128 + `row` of the pairs' expert outputs
 #pragma unroll
-                    for (uint32_t t = 0; t < kNt; ++t)
-                        if (t < nt) a.out[(size_t)pair[t] * a.hidden + idx * 128u + row] = v[t];
-                } else {
-                    // lanes 0-63: gate of the slice's element `row`; lanes 64-127: its up projection
+                for (uint32_t mt = 0; mt < kMt; ++mt) {
+                    const uint32_t idx = idx0 * kMt + mt;   // the slice (up) or row tile (down)
+                    if constexpr (kDown) {
+                        // row idx * 128 + `row` of the pairs' expert outputs
 #pragma unroll
-                    for (uint32_t t = 0; t < kNt; ++t)
-                        if (t < nt && row >= 64u) s_up[t][row - 64u] = v[t];
-                    epi_sync();
+                        for (uint32_t t = 0; t < kNt; ++t)
+                            if (t < nt) a.out[(size_t)pair[t] * a.hidden + idx * 128u + row] = v[mt][t];
+                    } else {
+                        // lanes 0-63: gate of the slice's element `row`; lanes 64-127: its up projection
+                        if (mt) epi_sync();  // the row tile before has been written out
 #pragma unroll
-                    for (uint32_t t = 0; t < kNt; ++t) {
-                        if (t < nt && row < 64u) {
-                            // hidden value `row` of the slice -> sixteen digit nibbles; scale block = warp
-                            const float hv = swiglu_limit_f32(v[t], s_up[t][row]);
-                            float bm = fabsf(hv);
+                        for (uint32_t t = 0; t < kNt; ++t)
+                            if (t < nt && row >= 64u) s_up[t][row - 64u] = v[mt][t];
+                        epi_sync();
 #pragma unroll
-                            for (int o = 16; o > 0; o >>= 1) bm = fmaxf(bm, __shfl_xor_sync(0xffffffffu, bm, o));
-                            const int E = block_exponent(bm);
-                            uint32_t hw, lw;
-                            digit_codes16(hv, __uint_as_float((uint32_t)(150 - E) << 23), hw, lw);
-                            const uint32_t ohw = __shfl_xor_sync(0xffffffffu, hw, 1), olw = __shfl_xor_sync(0xffffffffu, lw, 1);
-                            // byte lane / 2 of every row's chunk holds the nibbles of lanes 2b (low) and 2b + 1; even
-                            // lanes write digit rows 0-3 and 8-11, odd lanes 4-7 and 12-15
-                            const uint32_t e_hw = (lane & 1u) ? ohw : hw, o_hw = (lane & 1u) ? hw : ohw;
-                            const uint32_t e_lw = (lane & 1u) ? olw : lw, o_lw = (lane & 1u) ? lw : olw;
+                        for (uint32_t t = 0; t < kNt; ++t) {
+                            if (t < nt && row < 64u) {
+                                // hidden value `row` of the slice -> sixteen digit nibbles; scale block = warp
+                                const float hv = swiglu_limit_f32(v[mt][t], s_up[t][row]);
+                                float bm = fabsf(hv);
 #pragma unroll
-                            for (uint32_t jj = 0; jj < 4; ++jj) {
-                                const uint32_t dj = (lane & 1u) * 4u + jj;
-                                s_hst[t][(dj * 2u + warp) * 16u + (lane >> 1)] =
-                                    (uint8_t)(((e_hw >> (4u * dj)) & 0xFu) | (((o_hw >> (4u * dj)) & 0xFu) << 4));
-                                s_hst[t][((8u + dj) * 2u + warp) * 16u + (lane >> 1)] =
-                                    (uint8_t)(((e_lw >> (4u * dj)) & 0xFu) | (((o_lw >> (4u * dj)) & 0xFu) << 4));
+                                for (int o = 16; o > 0; o >>= 1) bm = fmaxf(bm, __shfl_xor_sync(0xffffffffu, bm, o));
+                                const int E = block_exponent(bm);
+                                uint32_t hw, lw;
+                                digit_codes16(hv, __uint_as_float((uint32_t)(150 - E) << 23), hw, lw);
+                                const uint32_t ohw = __shfl_xor_sync(0xffffffffu, hw, 1), olw = __shfl_xor_sync(0xffffffffu, lw, 1);
+                                // byte lane / 2 of every row's chunk holds the nibbles of lanes 2b (low) and 2b + 1; even
+                                // lanes write digit rows 0-3 and 8-11, odd lanes 4-7 and 12-15
+                                const uint32_t e_hw = (lane & 1u) ? ohw : hw, o_hw = (lane & 1u) ? hw : ohw;
+                                const uint32_t e_lw = (lane & 1u) ? olw : lw, o_lw = (lane & 1u) ? lw : olw;
+#pragma unroll
+                                for (uint32_t jj = 0; jj < 4; ++jj) {
+                                    const uint32_t dj = (lane & 1u) * 4u + jj;
+                                    s_hst[t][(dj * 2u + warp) * 16u + (lane >> 1)] =
+                                        (uint8_t)(((e_hw >> (4u * dj)) & 0xFu) | (((o_hw >> (4u * dj)) & 0xFu) << 4));
+                                    s_hst[t][((8u + dj) * 2u + warp) * 16u + (lane >> 1)] =
+                                        (uint8_t)(((e_lw >> (4u * dj)) & 0xFu) | (((o_lw >> (4u * dj)) & 0xFu) << 4));
+                                }
+                                if (lane == 0) a.hexp[(size_t)pair[t] * (a.inter >> 5) + idx * 2u + warp] = (uint8_t)(E + 100);
                             }
-                            if (lane == 0) a.hexp[(size_t)pair[t] * (a.inter >> 5) + idx * 2u + warp] = (uint8_t)(E + 100);
                         }
-                    }
-                    epi_sync();
-                    // the slice's 32 chunks (digit row, block) of every token go to their places in the pair's
-                    // digit tile: 64 threads write half a chunk each; the two halves of the CTA take the
-                    // tokens alternately
-                    const uint32_t t64 = tid & 63u, ch16 = t64 >> 1, half = t64 & 1u, dj = ch16 >> 1, blk = ch16 & 1u;
-                    const uint32_t cc = (idx & 3u) * 2u + blk;
-                    const uint32_t o = (idx >> 2) * 2048u + dj * 128u + ((cc ^ (dj & 7u)) << 4) + half * 8u;
+                        epi_sync();
+                        // the slice's 32 chunks (digit row, block) of every token go to their places in the pair's
+                        // digit tile: 64 threads write half a chunk each; the two halves of the CTA take the
+                        // tokens alternately
+                        const uint32_t t64 = tid & 63u, ch16 = t64 >> 1, half = t64 & 1u, dj = ch16 >> 1, blk = ch16 & 1u;
+                        const uint32_t cc = (idx & 3u) * 2u + blk;
+                        const uint32_t o = (idx >> 2) * 2048u + dj * 128u + ((cc ^ (dj & 7u)) << 4) + half * 8u;
 #pragma unroll
-                    for (uint32_t t = 0; t < kNt; ++t) {
-                        if (t < nt && (t & 1u) == (tid >> 6)) {
-                            const uint2 c8 = *reinterpret_cast<const uint2 *>(&s_hst[t][(dj * 2u + blk) * 16u + half * 8u]);
-                            *reinterpret_cast<uint2 *>(a.hdig + (size_t)pair[t] * KD * 2048u + o) = c8;
+                        for (uint32_t t = 0; t < kNt; ++t) {
+                            if (t < nt && (t & 1u) == (tid >> 6)) {
+                                const uint2 c8 = *reinterpret_cast<const uint2 *>(&s_hst[t][(dj * 2u + blk) * 16u + half * 8u]);
+                                *reinterpret_cast<uint2 *>(a.hdig + (size_t)pair[t] * KD * 2048u + o) = c8;
+                            }
                         }
                     }
                 }
@@ -518,7 +545,7 @@ k_block_gemm(const __grid_constant__ GemmArgs a, uint32_t *status) {
                         ok = false;
                         break;
                     }
-                    const uint32_t dst0 = smem_u32(sRing) + p_slot * a.stage + kStageA;
+                    const uint32_t dst0 = smem_u32(sRing) + p_slot * a.stage + kMt * kStageA;
 #pragma unroll 1
                     for (uint32_t c = lt; c < n16; c += kGLayThreads) {
                         const uint32_t tt = c >> 7, off = (c & 127u) << 4;
@@ -586,24 +613,29 @@ k_block_mix(const float *__restrict__ d, const int32_t *__restrict__ ids, const 
 }
 
 constexpr int kMaxDevices = 64;
-size_t g_block_limit[kMaxDevices] = {};
+size_t g_block_limit[kMaxDevices][2] = {};
 
-// The dynamic shared memory the GEMM kernels may ask for on the current device (set once per device).
-size_t block_dynamic_limit() {
+// The dynamic shared memory the contraction kernels with `mt` row tiles per item may ask for on the
+// current device (set once per device; the variants with two row tiles hold fewer item records).
+size_t block_dynamic_limit(uint32_t mt) {
     int dev = -1;
-    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= kMaxDevices) return 0;
-    if (g_block_limit[dev]) return g_block_limit[dev];
-    cudaFuncAttributes fa, fb;
-    if (cudaFuncGetAttributes(&fa, k_block_gemm<false>) != cudaSuccess) return 0;
-    if (cudaFuncGetAttributes(&fb, k_block_gemm<true>) != cudaSuccess) return 0;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= kMaxDevices || mt < 1u || mt > 2u) return 0;
+    if (g_block_limit[dev][mt - 1u]) return g_block_limit[dev][mt - 1u];
     int optin = 0;
     if (cudaDeviceGetAttribute(&optin, cudaDevAttrMaxSharedMemoryPerBlockOptin, dev) != cudaSuccess) return 0;
-    const size_t fixed = fa.sharedSizeBytes > fb.sharedSizeBytes ? fa.sharedSizeBytes : fb.sharedSizeBytes;
-    if ((size_t)optin <= fixed) return 0;
-    const size_t most = (size_t)optin - fixed;
-    if (cudaFuncSetAttribute(k_block_gemm<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)most) != cudaSuccess) return 0;
-    if (cudaFuncSetAttribute(k_block_gemm<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)most) != cudaSuccess) return 0;
-    g_block_limit[dev] = most;
+    auto set_up = [&](auto up, auto down) -> size_t {
+        cudaFuncAttributes fa, fb;
+        if (cudaFuncGetAttributes(&fa, up) != cudaSuccess || cudaFuncGetAttributes(&fb, down) != cudaSuccess) return 0;
+        const size_t fixed = fa.sharedSizeBytes > fb.sharedSizeBytes ? fa.sharedSizeBytes : fb.sharedSizeBytes;
+        if ((size_t)optin <= fixed) return 0;
+        const size_t most = (size_t)optin - fixed;
+        if (cudaFuncSetAttribute(up, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)most) != cudaSuccess) return 0;
+        if (cudaFuncSetAttribute(down, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)most) != cudaSuccess) return 0;
+        return most;
+    };
+    const size_t most = mt == 1u ? set_up(k_block_gemm<false, 1>, k_block_gemm<true, 1>)
+                                 : set_up(k_block_gemm<false, 2>, k_block_gemm<true, 2>);
+    g_block_limit[dev][mt - 1u] = most;
     return most;
 }
 
@@ -620,7 +652,7 @@ bool moe_block_ok(int sm_count, uint32_t hidden, uint32_t inter, uint32_t n_expe
     if (sm_count <= 0 || n_experts == 0u || n_experts > S14_N_ROUTED_EXPERTS || top_k == 0u || top_k > S14_EXPERTS_PER_TOKEN)
         return false;
     if ((hidden & 511u) || (inter & 511u) || hidden < 512u || inter < 512u || hidden > 4096u || inter > 4096u) return false;
-    return block_ring(block_dynamic_limit(), kStageA + kNt * 2048u) >= 2u;
+    return block_ring(block_dynamic_limit(1), kStageA + kNt * 2048u) >= 2u && block_ring(block_dynamic_limit(2), 2u * kStageA + kNt * 2048u) >= 2u;
 }
 
 size_t moe_block_max_chunks(uint32_t max_tokens) {
@@ -638,16 +670,19 @@ int launch_moe_block(cudaStream_t st, int sm_count, const BlockWork &w, const fl
     // chunks come from the L2.  A large block wants few passes over every expert.
     if (nt_cap == 0u) nt_cap = n_tokens <= 12u ? 2u : kNt;
     if (nt_cap > kNt) nt_cap = kNt;
-    const uint32_t stage = kStageA + nt_cap * 2048u;
-    const uint32_t ring = block_ring(block_dynamic_limit(), stage);
+    // Row tiles per item: a large block fetches a K range's token tiles once for two units (half the tile
+    // bytes); a small block has too few items for that (its items would not level out over the SMs).
+    const uint32_t mt = nt_cap > 2u ? 2u : 1u;
+    const uint32_t stage = mt * kStageA + nt_cap * 2048u;
+    const uint32_t ring = block_ring(block_dynamic_limit(mt), stage);
     *err = cudaErrorInvalidConfiguration;
     if (ring < 2u || n_tokens == 0u) return 0;
     const uint32_t S = inter >> 6, RT = hidden >> 7;
     const size_t smem = (size_t)ring * stage + 2u * kSfbBytes;
     k_block_digits<<<n_tokens, 512, 0, st>>>(x, hidden, w.xdig, w.xexp);
     if (ep_world == 0u) ep_world = 1u;
-    k_block_group<<<1, 1024, 0, st>>>(ids, pages, page_table, shared_page, n_tokens, top_k, n_experts, S, RT, nt_cap, w.chunks,
-                                     w.counts, ep_rank, ep_world);
+    k_block_group<<<1, 1024, 0, st>>>(ids, pages, page_table, shared_page, n_tokens, top_k, n_experts, S / mt, RT / mt, nt_cap,
+                                     w.chunks, w.counts, ep_rank, ep_world);
     if (pairs_out) {
         // expert parallel: the pairs of the experts this rank owns; the others stay zero for the sum over the ranks
         *err = cudaMemsetAsync(pairs_out, 0, (size_t)n_tokens * kPairsPerToken * hidden * sizeof(float), st);
@@ -655,9 +690,14 @@ int launch_moe_block(cudaStream_t st, int sm_count, const BlockWork &w, const fl
     }
     const uint32_t by_threads = nt_cap > 2u ? 1u : 0u;
     GemmArgs up = {w.chunks, w.counts + 1, w.xdig, w.xexp, nullptr, w.hdig, w.hexp, by_threads, hidden, inter, ring, stage};
-    k_block_gemm<false><<<sm_count, kGThreads, smem, st>>>(up, status);
     GemmArgs down = {w.chunks, w.counts + 2, w.hdig, w.hexp, pairs_out ? pairs_out : w.d, nullptr, nullptr, by_threads, hidden, inter, ring, stage};
-    k_block_gemm<true><<<sm_count, kGThreads, smem, st>>>(down, status);
+    if (mt == 1u) {
+        k_block_gemm<false, 1><<<sm_count, kGThreads, smem, st>>>(up, status);
+        k_block_gemm<true, 1><<<sm_count, kGThreads, smem, st>>>(down, status);
+    } else {
+        k_block_gemm<false, 2><<<sm_count, kGThreads, smem, st>>>(up, status);
+        k_block_gemm<true, 2><<<sm_count, kGThreads, smem, st>>>(down, status);
+    }
     if (pairs_out) {
         *err = cudaGetLastError();
         return 4;
