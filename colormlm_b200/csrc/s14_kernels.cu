@@ -1233,7 +1233,7 @@ k_stack_step(const float *__restrict__ x, const float *__restrict__ y, float *ou
 // one warp per token at a time: logit in double (every product f32 x bf16 is exact in double), score
 // and score + bias in F32 -- the arithmetic of k_router.
 constexpr uint32_t kRbTokens = 32;
-template <uint32_t kRbExperts>
+template <uint32_t kRbExperts, uint32_t kRbPerWarp>
 __global__ void __launch_bounds__(256)
 k_router_scores_batch(const float *__restrict__ x, const uint16_t *__restrict__ wr, const float *__restrict__ bias,
                       float *__restrict__ scores, float *__restrict__ select, uint32_t n_experts, uint32_t hidden,
@@ -1249,36 +1249,126 @@ k_router_scores_batch(const float *__restrict__ x, const uint16_t *__restrict__ 
         reinterpret_cast<uint4 *>(s_w)[i] = q;
     }
     __syncthreads();
-    for (uint32_t t = t0 + warp; t < t0 + kRbTokens && t < n_tokens; t += 8u) {
-        const float *xt = x + (size_t)t * hidden;
-        double acc[kRbExperts];
+    // A warp takes kRbPerWarp tokens at a time: a weight is converted to double once (the conversion, not the
+    // FMA, is the slow operation) and multiplied with that element of each of them.
+    for (uint32_t tb = t0 + warp * kRbPerWarp; tb < t0 + kRbTokens && tb < n_tokens; tb += 8u * kRbPerWarp) {
+        double acc[kRbPerWarp][kRbExperts];
 #pragma unroll
-        for (uint32_t e = 0; e < kRbExperts; ++e) acc[e] = 0.0;
+        for (uint32_t j = 0; j < kRbPerWarp; ++j)
+#pragma unroll
+            for (uint32_t e = 0; e < kRbExperts; ++e) acc[j][e] = 0.0;
         for (uint32_t p = lane; p < pieces; p += 32u) {
-            const float4 xa = __ldg(reinterpret_cast<const float4 *>(xt + p * 8u));
-            const float4 xb = __ldg(reinterpret_cast<const float4 *>(xt + p * 8u + 4u));
-            const double xv[8] = {xa.x, xa.y, xa.z, xa.w, xb.x, xb.y, xb.z, xb.w};
+            double xv[kRbPerWarp][8];
+#pragma unroll
+            for (uint32_t j = 0; j < kRbPerWarp; ++j) {
+                // (a token past the block's end reads the last token again; its result is not written)
+                const float *xt = x + (size_t)min(tb + j, n_tokens - 1u) * hidden;
+                const float4 xa = __ldg(reinterpret_cast<const float4 *>(xt + p * 8u));
+                const float4 xb = __ldg(reinterpret_cast<const float4 *>(xt + p * 8u + 4u));
+                xv[j][0] = xa.x, xv[j][1] = xa.y, xv[j][2] = xa.z, xv[j][3] = xa.w;
+                xv[j][4] = xb.x, xv[j][5] = xb.y, xv[j][6] = xb.z, xv[j][7] = xb.w;
+            }
 #pragma unroll
             for (uint32_t e = 0; e < kRbExperts; ++e) {
                 const uint4 q = reinterpret_cast<const uint4 *>(s_w + (size_t)e * hidden)[p];
                 const uint32_t wd[4] = {q.x, q.y, q.z, q.w};
-                double a0 = 0.0, a1 = 0.0;
+                double w[8];
 #pragma unroll
                 for (int i = 0; i < 4; ++i) {
-                    a0 += xv[i * 2] * (double)__uint_as_float(wd[i] << 16);
-                    a1 += xv[i * 2 + 1] * (double)__uint_as_float(wd[i] & 0xffff0000u);
+                    w[i * 2] = (double)__uint_as_float(wd[i] << 16);
+                    w[i * 2 + 1] = (double)__uint_as_float(wd[i] & 0xffff0000u);
                 }
-                acc[e] += a0 + a1;
+#pragma unroll
+                for (uint32_t j = 0; j < kRbPerWarp; ++j) {
+                    double a0 = 0.0, a1 = 0.0;
+#pragma unroll
+                    for (int i = 0; i < 4; ++i) {
+                        a0 += xv[j][i * 2] * w[i * 2];
+                        a1 += xv[j][i * 2 + 1] * w[i * 2 + 1];
+                    }
+                    acc[j][e] += a0 + a1;
+                }
             }
         }
 #pragma unroll
-        for (uint32_t e = 0; e < kRbExperts; ++e) {
-            const double sum = warp_sum(acc[e]);
-            if (lane == 0 && e0 + e < n_experts) {
-                const float sc = router_score_f32(sum, score_fn);
-                scores[(size_t)t * n_experts + e0 + e] = sc;
-                select[(size_t)t * n_experts + e0 + e] = __fadd_rn(sc, bias ? bias[e0 + e] : 0.0f);
+        for (uint32_t j = 0; j < kRbPerWarp; ++j) {
+#pragma unroll
+            for (uint32_t e = 0; e < kRbExperts; ++e) {
+                const double sum = warp_sum(acc[j][e]);
+                if (lane == 0 && e0 + e < n_experts && tb + j < n_tokens) {
+                    const float sc = router_score_f32(sum, score_fn);
+                    scores[(size_t)(tb + j) * n_experts + e0 + e] = sc;
+                    select[(size_t)(tb + j) * n_experts + e0 + e] = __fadd_rn(sc, bias ? bias[e0 + e] : 0.0f);
+                }
             }
+        }
+    }
+}
+
+// The same scores on the FP64 tensor path (B200 runs FP64 FMAs of the vector pipe at a sixteenth of
+// the FP32 rate, and a block of hundreds of tokens needs 0.4 G of them): a CTA takes 32 tokens x 16
+// experts, stages 256 elements of K at a time in shared memory as doubles (every f32 and bf16 value is
+// exact in double, every product of the two exact, the accumulation in double as before, in another order),
+// and its eight warps run mma.m8n8k4.f64 on 8 tokens x 8 experts each.
+constexpr uint32_t kRdTokens = 32, kRdExperts = 16, kRdK = 256, kRdPitch = kRdK + 4;  // pitch: rows 32 bytes apart mod 128
+__global__ void __launch_bounds__(256)
+k_router_scores_dmma(const float *__restrict__ x, const uint16_t *__restrict__ wr, const float *__restrict__ bias,
+                     float *__restrict__ scores, float *__restrict__ select, uint32_t n_experts, uint32_t hidden,
+                     uint32_t n_tokens, uint32_t score_fn) {
+    extern __shared__ __align__(16) double s_d[];
+    double *sx = s_d;                           // [kRdTokens][kRdPitch]
+    double *sw = s_d + kRdTokens * kRdPitch;    // [kRdExperts][kRdPitch]
+    const uint32_t e0 = blockIdx.x * kRdExperts, t0 = blockIdx.y * kRdTokens;
+    const uint32_t tid = threadIdx.x, warp = tid >> 5, lane = tid & 31u;
+    const uint32_t tg = warp & 3u, eg = warp >> 2;
+    double c0 = 0.0, c1 = 0.0;
+    for (uint32_t k0 = 0; k0 < hidden; k0 += kRdK) {
+        __syncthreads();
+#pragma unroll
+        for (uint32_t i = 0; i < kRdTokens * kRdK / 4u / 256u; ++i) {
+            const uint32_t idx = tid + 256u * i, t = idx / (kRdK / 4u), f4 = idx % (kRdK / 4u);
+            // (a token past the block's end reads the last token again; its scores are not written)
+            const float4 v = __ldg(reinterpret_cast<const float4 *>(x + (size_t)min(t0 + t, n_tokens - 1u) * hidden + k0) + f4);
+            double *d = sx + t * kRdPitch + f4 * 4u;
+            *reinterpret_cast<double2 *>(d) = make_double2((double)v.x, (double)v.y);
+            *reinterpret_cast<double2 *>(d + 2) = make_double2((double)v.z, (double)v.w);
+        }
+#pragma unroll
+        for (uint32_t i = 0; i < kRdExperts * kRdK / 8u / 256u; ++i) {
+            const uint32_t idx = tid + 256u * i, e = idx / (kRdK / 8u), p8 = idx % (kRdK / 8u);
+            const uint4 q = __ldg(reinterpret_cast<const uint4 *>(wr + (size_t)min(e0 + e, n_experts - 1u) * hidden + k0) + p8);
+            const uint32_t wd[4] = {q.x, q.y, q.z, q.w};
+            double *d = sw + e * kRdPitch + p8 * 8u;
+#pragma unroll
+            for (int j = 0; j < 4; ++j)
+                *reinterpret_cast<double2 *>(d + 2 * j) =
+                    make_double2((double)__uint_as_float(wd[j] << 16), (double)__uint_as_float(wd[j] & 0xffff0000u));
+        }
+        __syncthreads();
+        // A (8 tokens x 4 k, row major): lane holds (row lane / 4, column lane % 4); B (4 k x 8 experts, column
+        // major): lane holds (row lane % 4, column lane / 4), i.e. the expert's row at the same k
+        const double *pa = sx + (tg * 8u + (lane >> 2)) * kRdPitch + (lane & 3u);
+        const double *pb = sw + (eg * 8u + (lane >> 2)) * kRdPitch + (lane & 3u);
+#pragma unroll 8
+        for (uint32_t k = 0; k < kRdK; k += 4u) {
+            const double a = pa[k], b = pb[k];
+            asm volatile("mma.sync.aligned.m8n8k4.row.col.f64.f64.f64.f64 {%0, %1}, {%2}, {%3}, {%0, %1};"
+                         : "+d"(c0), "+d"(c1)
+                         : "d"(a), "d"(b));
+        }
+    }
+    // C (8 x 8): lane holds row lane / 4, columns 2 (lane % 4) and 2 (lane % 4) + 1
+    const uint32_t t = t0 + tg * 8u + (lane >> 2), e = e0 + eg * 8u + (lane & 3u) * 2u;
+    if (t < n_tokens) {
+        if (e < n_experts) {
+            const float sc = router_score_f32(c0, score_fn);
+            scores[(size_t)t * n_experts + e] = sc;
+            select[(size_t)t * n_experts + e] = __fadd_rn(sc, bias ? bias[e] : 0.0f);
+        }
+        if (e + 1u < n_experts) {
+            const float sc = router_score_f32(c1, score_fn);
+            scores[(size_t)t * n_experts + e + 1u] = sc;
+            select[(size_t)t * n_experts + e + 1u] = __fadd_rn(sc, bias ? bias[e + 1u] : 0.0f);
         }
     }
 }
@@ -1295,25 +1385,26 @@ k_router_select_batch(const float *__restrict__ scores, const float *__restrict_
 }
 
 int launch_router_batch(cudaStream_t st, const s14_router_desc &r, float *scores, float *select, cudaError_t *err) {
-    // few tokens: two experts per CTA, so that the grid covers the SMs; many: eight, which share a token's loads
-    const uint32_t per_cta = r.n_tokens <= kRbTokens ? 2u : 8u;
-    const size_t smem = (size_t)per_cta * r.hidden * sizeof(uint16_t);
+    // few tokens: two experts per CTA on the vector pipe, so that the grid covers the SMs; many: the FP64 tensor path
     static bool attr_set[64] = {};
     int dev = 0;
     *err = cudaGetDevice(&dev);
     if (*err != cudaSuccess) return 0;
+    const size_t smem_d = (size_t)(kRdTokens + kRdExperts) * kRdPitch * sizeof(double);
     if (dev >= 0 && dev < 64 && !attr_set[dev]) {
-        *err = cudaFuncSetAttribute(k_router_scores_batch<8>, cudaFuncAttributeMaxDynamicSharedMemorySize, 8 * 8192 * 2);
+        *err = cudaFuncSetAttribute(k_router_scores_dmma, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem_d);
         if (*err != cudaSuccess) return 0;
         attr_set[dev] = true;
     }
-    const dim3 grid(ceil_div(r.n_experts, per_cta), ceil_div(r.n_tokens, kRbTokens));
-    if (per_cta == 2u)
-        k_router_scores_batch<2><<<grid, 256, smem, st>>>(r.x, r.router_weight_bf16, r.bias, scores, select, r.n_experts, r.hidden,
-                                                         r.n_tokens, r.score_fn);
-    else
-        k_router_scores_batch<8><<<grid, 256, smem, st>>>(r.x, r.router_weight_bf16, r.bias, scores, select, r.n_experts, r.hidden,
-                                                         r.n_tokens, r.score_fn);
+    if (r.n_tokens <= kRbTokens) {
+        const dim3 grid(ceil_div(r.n_experts, 2u), ceil_div(r.n_tokens, kRbTokens));
+        k_router_scores_batch<2, 1><<<grid, 256, (size_t)2u * r.hidden * sizeof(uint16_t), st>>>(
+            r.x, r.router_weight_bf16, r.bias, scores, select, r.n_experts, r.hidden, r.n_tokens, r.score_fn);
+    } else {
+        const dim3 grid(ceil_div(r.n_experts, kRdExperts), ceil_div(r.n_tokens, kRdTokens));
+        k_router_scores_dmma<<<grid, 256, smem_d, st>>>(r.x, r.router_weight_bf16, r.bias, scores, select, r.n_experts, r.hidden,
+                                                       r.n_tokens, r.score_fn);
+    }
     k_router_select_batch<<<ceil_div(r.n_tokens, 8), 256, 0, st>>>(scores, select, r.n_experts, r.n_tokens, r.top_k,
                                                                   r.route_scale, r.ids_out, r.weights_out);
     *err = cudaGetLastError();

@@ -113,11 +113,13 @@ def test_block_at_the_benchmark_shape(ctx, oracle):
         blk.close()
 
 
+@pytest.mark.parametrize("n_tokens,n_experts", [(24, 32), (41, 24)])
 @pytest.mark.parametrize("score_fn", [L.SCORE_SIGMOID, L.SCORE_SQRT_SOFTPLUS])
-def test_routed_block_picks_the_oracles_routes(ctx, oracle, score_fn):
-    """Router on the device for 24 tokens over 32 experts: ids and weights are the oracle's, every
-    token's y is the oracle's layer for those routes, bit for bit."""
-    hidden, inter, n_experts, n_tokens = 2048, 1024, 32, 24
+def test_routed_block_picks_the_oracles_routes(ctx, oracle, score_fn, n_tokens, n_experts):
+    """Router on the device: ids and weights are the oracle's, every token's y is the oracle's layer for
+    those routes, bit for bit.  24 tokens take the vector-pipe scores, 41 the FP64 tensor path (a ragged
+    last tile of tokens, a ragged last tile of experts)."""
+    hidden, inter = 2048, 1024
     g, pages, shared = make_layer(1300 + score_fn, hidden, inter, n_experts, L.PAGE_MXFP4)
     wr, bias = synth.router_weight_bf16(g, n_experts, hidden), synth.router_bias(g, n_experts)
     x = synth.activations(g, n_tokens, hidden)
@@ -127,7 +129,7 @@ def test_routed_block_picks_the_oracles_routes(ctx, oracle, score_fn):
     wts = torch.empty((n_tokens, 6), dtype=torch.float32, device="cuda")
     dx = dev(x)
     dy = torch.full_like(dx, float("nan"))
-    blk = MoeBlock(ctx, hidden, inter, 32)
+    blk = MoeBlock(ctx, hidden, inter, 48)
     try:
         blk.cmd_routed_moe_block(dx, dev(wr), dev(bias), table, shared_dev.data_ptr(), dy, ids, wts,
                                  score_fn=score_fn, top_k=6, route_scale=1.5)
