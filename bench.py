@@ -1307,7 +1307,10 @@ def run_small_workload(args, workload, torch, L, synth, S14Context, TokenRoute) 
             "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
                          "frac_of_nominal_8000": achieved / 8000.0, "peak_kind": peak_kind, "traffic": None,
                          "bytes_per_call": unit_bytes,
-                         "note": "a call of a few MB is bound by launch and memory latency, not by bandwidth"},
+                         "note": ("every distinct expert page counted once; the contraction kernels take in 2-3 x these bytes per SM "
+                                  "(later chunks of an expert and the token tiles come from the L2), which is what bounds them"
+                                  if workload in ("verify8", "prefill") else
+                                  "a call of a few MB is bound by launch and memory latency, not by bandwidth")},
             "parity": parity,
             "cpu_baseline": {"value": per_call / cpu_sec, "unit": "tokens/s" if workload == "prefill" else "calls/s", "cores": cores,
                              "kind": "port",
