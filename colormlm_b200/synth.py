@@ -82,6 +82,20 @@ def router_bias(g: np.random.Generator, n_experts: int) -> np.ndarray:
     return g.uniform(-0.1, 0.1, size=n_experts).astype(np.float32)
 
 
+def hc_params(g: np.random.Generator, hidden: int, hc: int = 4, head: bool = False):
+    """Hyper-connection parameters of one site: (fn [(2 + hc) * hc or hc, hc * hidden], scale [3 or 1], base)."""
+    rows = hc if head else (2 + hc) * hc
+    fn = g.standard_normal((rows, hc * hidden), dtype=np.float32) * np.float32(0.02)
+    scale = g.uniform(0.2, 0.8, size=1 if head else 3).astype(np.float32)
+    base = g.uniform(-1.0, 1.0, size=rows).astype(np.float32)
+    return fn, scale, base
+
+
+def hc_streams(g: np.random.Generator, n_tokens: int, hidden: int, hc: int = 4) -> np.ndarray:
+    """The state of a token: hc streams [n_tokens, hc, hidden], F32."""
+    return g.standard_normal((n_tokens, hc, hidden), dtype=np.float32)
+
+
 def head_weight_bf16(g: np.random.Generator, vocab: int, hidden: int, std: float = 0.02) -> np.ndarray:
     return f32_to_bf16_bits((g.standard_normal((vocab, hidden), dtype=np.float32) * np.float32(std)))
 

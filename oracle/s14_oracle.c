@@ -440,3 +440,165 @@ S14O_API int s14o_error_stats(const float *actual, const float *expected, uint64
     out[3] = max_rel;
     return 0;
 }
+
+/* ---- the steps on either side of the MoE inside one layer --------------------------------------
+ * Hyper-connection reduce / expand, RMSNorm and the head's reduce, restating
+ *   fast16/research/polaris_meridian_v1/local_s14_primitives/hc.py:19-148
+ *   fast16/research/polaris_meridian_v1/local_s14_primitives/final_head.py:43-110
+ * The Python code computes in F32 with torch's CPU kernels, whose summation order inside
+ * F.linear / mean and whose exp are not fixed; here the long sums (mean of squares, the dot
+ * products with hc_fn) are accumulated in double and rounded to F32 once, exp is evaluated in
+ * double and rounded once, and everything else follows the Python expressions operation by
+ * operation in F32 (sums over the four streams in stream order).  The golden vectors made by the
+ * Python code itself are met within a few F32 ulps (tests/test_oracle_golden.py states the bound).
+ * dtype 0: F32 streams; 1: BF16 streams (the reference's state is BF16 [1,1,4,4096]; results are
+ * rounded to BF16 where the Python code casts back with .to(original_dtype) / type_as). */
+static inline float bf16_round(float v) {
+    uint32_t b;
+    memcpy(&b, &v, 4);
+    if ((b & 0x7F800000u) == 0x7F800000u) return v; /* inf / nan as they are */
+    b += 0x7FFFu + ((b >> 16) & 1u);
+    b &= 0xFFFF0000u;
+    memcpy(&v, &b, 4);
+    return v;
+}
+static inline float stream_get(const void *p, size_t i, int dtype) {
+    return dtype ? bf16_to_f32(((const uint16_t *)p)[i]) : ((const float *)p)[i];
+}
+static inline void stream_put(void *p, size_t i, int dtype, float v) {
+    if (dtype) {
+        const float r = bf16_round(v);
+        uint32_t b;
+        memcpy(&b, &r, 4);
+        ((uint16_t *)p)[i] = (uint16_t)(b >> 16);
+    } else {
+        ((float *)p)[i] = v;
+    }
+}
+static inline float sigmoid_f32(float v) { return (float)(1.0 / (1.0 + exp(-(double)v))); }
+
+/* hc.py:19-84.  mixes [(2 + hc) * hc], scale [3], base like mixes -> pre [hc], post [hc], comb [hc][hc]. */
+S14O_API void s14o_hc_split_sinkhorn(const float *mixes, const float *scale, const float *base, uint32_t hc,
+                                     uint32_t iters, float eps, float *pre, float *post, float *comb) {
+    for (uint32_t h = 0; h < hc; ++h) {
+        pre[h] = sigmoid_f32(mixes[h] * scale[0] + base[h]) + eps;
+        post[h] = 2.0f * sigmoid_f32(mixes[hc + h] * scale[1] + base[hc + h]);
+    }
+    for (uint32_t i = 0; i < hc * hc; ++i) comb[i] = mixes[2 * hc + i] * scale[2] + base[2 * hc + i];
+    for (uint32_t i = 0; i < hc; ++i) { /* stable row softmax, + eps */
+        float m = comb[i * hc];
+        for (uint32_t j = 1; j < hc; ++j) m = comb[i * hc + j] > m ? comb[i * hc + j] : m;
+        float s = 0.0f;
+        for (uint32_t j = 0; j < hc; ++j) {
+            comb[i * hc + j] = (float)exp((double)(comb[i * hc + j] - m));
+            s += comb[i * hc + j];
+        }
+        for (uint32_t j = 0; j < hc; ++j) comb[i * hc + j] = comb[i * hc + j] / s + eps;
+    }
+    for (uint32_t it = 0; it < iters; ++it) {
+        if (it) { /* rows */
+            for (uint32_t i = 0; i < hc; ++i) {
+                float s = 0.0f;
+                for (uint32_t j = 0; j < hc; ++j) s += comb[i * hc + j];
+                for (uint32_t j = 0; j < hc; ++j) comb[i * hc + j] = comb[i * hc + j] / (s + eps);
+            }
+        }
+        for (uint32_t j = 0; j < hc; ++j) { /* columns */
+            float s = 0.0f;
+            for (uint32_t i = 0; i < hc; ++i) s += comb[i * hc + j];
+            for (uint32_t i = 0; i < hc; ++i) comb[i * hc + j] = comb[i * hc + j] / (s + eps);
+        }
+    }
+}
+
+/* mixes[m] = (x_flat . fn[m]) * rsqrt(mean(x_flat^2) + norm_eps) for n_mix rows of fn [n_mix][hc * hidden]. */
+static void hc_mixes(const void *x, int dtype, const float *fn, uint32_t n_mix, uint32_t n, float norm_eps, float *mixes) {
+    double ss = 0.0;
+    for (uint32_t i = 0; i < n; ++i) {
+        const double v = (double)stream_get(x, i, dtype);
+        ss += v * v;
+    }
+    const float ms = (float)(ss / (double)n);
+    const float rs = (float)(1.0 / sqrt((double)(ms + norm_eps)));
+    for (uint32_t m = 0; m < n_mix; ++m) {
+        double acc = 0.0;
+        for (uint32_t i = 0; i < n; ++i) acc += (double)stream_get(x, i, dtype) * (double)fn[(size_t)m * n + i];
+        mixes[m] = (float)acc * rs;
+    }
+}
+
+/* hc.py:87-124 for one token: x [hc][hidden] -> reduced [hidden] (stream dtype), post [hc], comb [hc][hc]. */
+S14O_API void s14o_hc_pre(const void *x, int dtype, const float *hc_fn, const float *hc_scale, const float *hc_base,
+                          uint32_t hc, uint32_t hidden, float norm_eps, uint32_t iters, float hc_eps, void *reduced,
+                          float *post, float *comb) {
+    float mixes[64], pre[8];
+    if (hc > 6) return;
+    hc_mixes(x, dtype, hc_fn, (2 + hc) * hc, hc * hidden, norm_eps, mixes);
+    s14o_hc_split_sinkhorn(mixes, hc_scale, hc_base, hc, iters, hc_eps, pre, post, comb);
+    for (uint32_t d = 0; d < hidden; ++d) {
+        float acc = pre[0] * stream_get(x, d, dtype);
+        for (uint32_t h = 1; h < hc; ++h) acc += pre[h] * stream_get(x, (size_t)h * hidden + d, dtype);
+        stream_put(reduced, d, dtype, acc);
+    }
+}
+
+/* hc.py:127-148 for one token: merged[h'] = post[h'] * branch + sum_h comb[h][h'] * residual[h]. */
+S14O_API void s14o_hc_post(const void *branch, const void *residual, int dtype, const float *post, const float *comb,
+                           uint32_t hc, uint32_t hidden, void *merged) {
+    for (uint32_t o = 0; o < hc; ++o) {
+        for (uint32_t d = 0; d < hidden; ++d) {
+            float s = comb[o] * stream_get(residual, d, dtype);
+            for (uint32_t h = 1; h < hc; ++h) s += comb[h * hc + o] * stream_get(residual, (size_t)h * hidden + d, dtype);
+            const float v = post[o] * stream_get(branch, d, dtype) + s;
+            stream_put(merged, (size_t)o * hidden + d, dtype, v);
+        }
+    }
+}
+
+/* final_head.py:84-110 (and l42_reference.py:421-426): out = w * (x * rsqrt(mean(x^2) + eps)). */
+S14O_API void s14o_rms_norm(const void *x, int dtype, const float *w, uint32_t hidden, float eps, void *out) {
+    double ss = 0.0;
+    for (uint32_t i = 0; i < hidden; ++i) {
+        const double v = (double)stream_get(x, i, dtype);
+        ss += v * v;
+    }
+    const float ms = (float)(ss / (double)hidden);
+    const float rs = (float)(1.0 / sqrt((double)(ms + eps)));
+    for (uint32_t i = 0; i < hidden; ++i) stream_put(out, i, dtype, w[i] * (stream_get(x, i, dtype) * rs));
+}
+
+/* final_head.py:43-81 for one token: pre = sigmoid(mixes * scale + base) + eps, reduced = sum_h pre[h] x[h]. */
+S14O_API void s14o_hc_head_reduce(const void *x, int dtype, const float *fn, const float *scale, const float *base,
+                                  uint32_t hc, uint32_t hidden, float norm_eps, float hc_eps, void *reduced, float *pre) {
+    float mixes[8];
+    if (hc > 8) return;
+    hc_mixes(x, dtype, fn, hc, hc * hidden, norm_eps, mixes);
+    for (uint32_t h = 0; h < hc; ++h) pre[h] = sigmoid_f32(mixes[h] * scale[0] + base[h]) + hc_eps;
+    for (uint32_t d = 0; d < hidden; ++d) {
+        float acc = pre[0] * stream_get(x, d, dtype);
+        for (uint32_t h = 1; h < hc; ++h) acc += pre[h] * stream_get(x, (size_t)h * hidden + d, dtype);
+        stream_put(reduced, d, dtype, acc);
+    }
+}
+
+/* executor.py:638-668 for the hash-routed layers (0-2): the ids come from the token's row of
+ * tid2eid; the weights are the router's scores of those experts, normalised and scaled. */
+S14O_API void s14o_router_hash(const float *x, const uint16_t *wr_bf16, uint32_t n_experts, uint32_t hidden, int score_fn,
+                               uint32_t top_k, float route_scale, const int64_t *tid2eid_row, int32_t *ids_out,
+                               float *weights_out) {
+    float sc[8];
+    float sum = 0.0f;
+    for (uint32_t j = 0; j < top_k && j < 8; ++j) {
+        const int64_t e = tid2eid_row[j];
+        ids_out[j] = (int32_t)e;
+        double acc = 0.0;
+        if (e >= 0 && (uint64_t)e < n_experts) {
+            const uint16_t *row = wr_bf16 + (size_t)e * hidden;
+            for (uint32_t k = 0; k < hidden; ++k) acc += (double)x[k] * (double)bf16_to_f32(row[k]);
+        }
+        const double l = (double)(float)acc;
+        sc[j] = (float)(score_fn == 0 ? 1.0 / (1.0 + exp(-l)) : sqrt(l > 20.0 ? l : log1p(exp(l))));
+        sum += sc[j];
+    }
+    for (uint32_t j = 0; j < top_k && j < 8; ++j) weights_out[j] = sc[j] / sum * route_scale;
+}

@@ -230,3 +230,77 @@ def error_stats(actual, expected) -> dict:
     if rc != 0:
         raise ValueError("error_stats: empty input or non-finite value")
     return {"max_abs": out[0], "mean_abs": out[1], "rmse": out[2], "max_rel": out[3]}
+
+
+# ---- the steps on either side of the MoE inside one layer (hc.py, final_head.py) ----------------
+# Streams are F32 arrays, or BF16 bit patterns in uint16 arrays (dtype=1), as the reference's state is.
+
+def _stream(a, dtype: int) -> np.ndarray:
+    return np.ascontiguousarray(a, dtype=np.uint16 if dtype else np.float32)
+
+
+def hc_split_sinkhorn(mixes, scale, base, hc: int = 4, iters: int = 20, eps: float = 1e-6):
+    """mixes [(2 + hc) * hc] -> (pre [hc], post [hc], comb [hc, hc])."""
+    mixes, scale, base = _f32(mixes), _f32(scale), _f32(base)
+    pre, post, comb = np.empty(hc, np.float32), np.empty(hc, np.float32), np.empty((hc, hc), np.float32)
+    lib().s14o_hc_split_sinkhorn(_p(mixes), _p(scale), _p(base), C.c_uint32(hc), C.c_uint32(iters), C.c_float(eps),
+                                 _p(pre), _p(post), _p(comb))
+    return pre, post, comb
+
+
+def hc_pre(x, hc_fn, hc_scale, hc_base, dtype: int = 0, norm_eps: float = 1e-6, iters: int = 20, hc_eps: float = 1e-6):
+    """x [T, hc, hidden] -> (reduced [T, hidden], post [T, hc], comb [T, hc, hc])."""
+    x = _stream(x, dtype)
+    n_tok, hc, hidden = x.shape
+    fn, sc, ba = _f32(hc_fn), _f32(hc_scale), _f32(hc_base)
+    assert fn.shape == ((2 + hc) * hc, hc * hidden)
+    red = np.empty((n_tok, hidden), x.dtype)
+    post, comb = np.empty((n_tok, hc), np.float32), np.empty((n_tok, hc, hc), np.float32)
+    for t in range(n_tok):
+        lib().s14o_hc_pre(_p(x[t]), C.c_int(dtype), _p(fn), _p(sc), _p(ba), C.c_uint32(hc), C.c_uint32(hidden),
+                          C.c_float(norm_eps), C.c_uint32(iters), C.c_float(hc_eps), _p(red[t]), _p(post[t]), _p(comb[t]))
+    return red, post, comb
+
+
+def hc_post(branch, residual, post, comb, dtype: int = 0):
+    """branch [T, hidden], residual [T, hc, hidden], post [T, hc], comb [T, hc, hc] -> merged [T, hc, hidden]."""
+    branch, residual = _stream(branch, dtype), _stream(residual, dtype)
+    n_tok, hc, hidden = residual.shape
+    post, comb = _f32(post), _f32(comb)
+    out = np.empty_like(residual)
+    for t in range(n_tok):
+        lib().s14o_hc_post(_p(branch[t]), _p(residual[t]), C.c_int(dtype), _p(post[t]), _p(comb[t]), C.c_uint32(hc),
+                           C.c_uint32(hidden), _p(out[t]))
+    return out
+
+
+def rms_norm(x, w, dtype: int = 0, eps: float = 1e-6):
+    """x [T, hidden] -> w * x * rsqrt(mean(x^2) + eps)."""
+    x, w = _stream(x, dtype), _f32(w)
+    out = np.empty_like(x)
+    for t in range(x.shape[0]):
+        lib().s14o_rms_norm(_p(x[t]), C.c_int(dtype), _p(w), C.c_uint32(x.shape[1]), C.c_float(eps), _p(out[t]))
+    return out
+
+
+def hc_head_reduce(x, fn, scale, base, dtype: int = 0, norm_eps: float = 1e-6, hc_eps: float = 1e-6):
+    """x [T, hc, hidden] -> (reduced [T, hidden], pre [T, hc])."""
+    x = _stream(x, dtype)
+    n_tok, hc, hidden = x.shape
+    fn, sc, ba = _f32(fn), _f32(scale), _f32(base)
+    red, pre = np.empty((n_tok, hidden), x.dtype), np.empty((n_tok, hc), np.float32)
+    for t in range(n_tok):
+        lib().s14o_hc_head_reduce(_p(x[t]), C.c_int(dtype), _p(fn), _p(sc), _p(ba), C.c_uint32(hc), C.c_uint32(hidden),
+                                  C.c_float(norm_eps), C.c_float(hc_eps), _p(red[t]), _p(pre[t]))
+    return red, pre
+
+
+def router_hash(x, wr_bf16_bits, tid2eid_row, score_fn: int = 1, route_scale: float = 1.5):
+    """The hash-routed layers: ids from the token's tid2eid row, weights from the router's scores of them."""
+    x = _f32(x)
+    wr = np.ascontiguousarray(wr_bf16_bits, dtype=np.uint16)
+    row = np.ascontiguousarray(tid2eid_row, dtype=np.int64)
+    ids, w = np.empty(row.size, np.int32), np.empty(row.size, np.float32)
+    lib().s14o_router_hash(_p(x), _p(wr), C.c_uint32(wr.shape[0]), C.c_uint32(wr.shape[1]), C.c_int(score_fn),
+                           C.c_uint32(row.size), C.c_float(route_scale), _p(row), _p(ids), _p(w))
+    return ids, w

@@ -24,7 +24,12 @@ stored here.  Cases:
 * router outputs from the torch expressions of executor.py:638-668 (both score
   functions);
 * LM-head logits through ``bf16_checkpoint_head_logits`` on the reference's seed-731
-  fixture (tests/test_final_head.py:22-30).
+  fixture (tests/test_final_head.py:22-30);
+* the hyper-connection reduce / expand, RMSNorm and the head's reduce (``hc_split_sinkhorn``,
+  ``hc_pre``, ``hc_post``, ``hc_head_reduce``, ``official_rms_norm``) on the reference's own
+  fixtures (tests/test_primitives.py:126-141, tests/test_final_head.py:22-46) and on seeded streams
+  of the model's size in F32 and BF16; the hash-routed layers' weights from the torch expressions
+  of executor.py:638-668.
 """
 from __future__ import annotations
 
@@ -193,6 +198,64 @@ def main(reference_root: str) -> None:
     out["hd_w"] = head_weight.view(torch.int16).numpy().view(np.uint16)
     out["hd_logits"] = bf16_checkpoint_head_logits(hid_states, head_weight, full_logits=True,
                                                    output_chunk_size=5).numpy()
+
+    # ---- the steps on either side of the MoE: hc.py:19-148, final_head.py:43-110 ----
+    from fast16.research.polaris_meridian_v1.local_s14_primitives.hc import hc_post, hc_pre, hc_split_sinkhorn
+    from fast16.research.polaris_meridian_v1.local_s14_primitives.final_head import hc_head_reduce, official_rms_norm
+
+    # the reference's own deterministic fixture (tests/test_primitives.py:126-141)
+    mixes = torch.linspace(-1000, 1000, 24, dtype=torch.float32).reshape(1, 1, 24)
+    hscale = torch.tensor([0.5, -0.25, 0.01])
+    hbase = torch.linspace(-1, 1, 24)
+    pre, post, comb = hc_split_sinkhorn(mixes, hscale, hbase, sinkhorn_iters=20)
+    out["hcf_pre"], out["hcf_post"], out["hcf_comb"] = pre.numpy().ravel(), post.numpy().ravel(), comb.numpy().reshape(4, 4)
+    fx = torch.sin(torch.arange(32, dtype=torch.float32) * 0.1).reshape(1, 1, 4, 8)
+    ffn = torch.linspace(-0.2, 0.2, 24 * 32).reshape(24, 32)
+    red, post2, comb2 = hc_pre(fx, ffn, hscale, hbase)
+    fbranch = torch.cos(torch.arange(8, dtype=torch.float32)).reshape(1, 1, 8)
+    out["hcf_reduced"], out["hcf_post2"], out["hcf_comb2"] = red.numpy().reshape(8), post2.numpy().ravel(), comb2.numpy().reshape(4, 4)
+    out["hcf_merged"] = hc_post(fbranch, fx, post2, comb2).numpy().reshape(4, 8)
+    out["hcf_mixes"], out["hcf_base"], out["hcf_fn"] = mixes.numpy().ravel(), hbase.numpy(), ffn.numpy()   # torch's linspace
+    out["hcf_x"], out["hcf_branch"] = fx.numpy().reshape(1, 4, 8), fbranch.numpy().reshape(1, 8)
+    # the reference's seed-731 fixture of the head (tests/test_final_head.py:22-46): BF16 streams
+    torch.manual_seed(731)
+    hx = torch.randn(2, 3, 4, 8, dtype=torch.float32).to(torch.bfloat16)
+    hfn = torch.randn(4, 32, dtype=torch.float32) * 0.1
+    hsc = torch.tensor([0.7], dtype=torch.float32)
+    hba = torch.linspace(-0.3, 0.3, 4, dtype=torch.float32)
+    nw = torch.linspace(0.8, 1.2, 8, dtype=torch.float32)
+    hred, hpre = hc_head_reduce(hx, hfn, hsc, hba)
+    out["hh_x"] = hx.view(torch.int16).numpy().view(np.uint16).reshape(6, 4, 8)
+    out["hh_fn"], out["hh_base"], out["hh_nw"] = hfn.numpy(), hba.numpy(), nw.numpy()
+    out["hh_reduced"] = hred.view(torch.int16).numpy().view(np.uint16).reshape(6, 8)
+    out["hh_pre"] = hpre.numpy().reshape(6, 4)
+    out["hh_norm"] = official_rms_norm(hx[:, :, 0], nw).view(torch.int16).numpy().view(np.uint16).reshape(6, 8)
+    # seeded streams of the model's size (3 tokens x 4 x 4096), F32 and BF16
+    g = synth.rng(1005)
+    hfn_np, hsc_np, hba_np = synth.hc_params(g, 4096)
+    xs_np = synth.hc_streams(g, 3, 4096)
+    br_np = synth.activations(g, 3, 4096)
+    nw_np = g.uniform(0.5, 1.5, size=4096).astype(np.float32)
+    out["hc_inputs_sha256"] = np.frombuffer(_digest(hfn_np, hsc_np, hba_np, xs_np, br_np, nw_np), dtype=np.uint8)
+    for name, dt in (("f32", torch.float32), ("bf16", torch.bfloat16)):
+        xs_t = torch.from_numpy(xs_np).to(dt).reshape(1, 3, 4, 4096)
+        br_t = torch.from_numpy(br_np).to(dt).reshape(1, 3, 4096)
+        red, post, comb = hc_pre(xs_t, torch.from_numpy(hfn_np), torch.from_numpy(hsc_np), torch.from_numpy(hba_np))
+        merged = hc_post(br_t, xs_t, post, comb)
+        normed = official_rms_norm(red, torch.from_numpy(nw_np))
+        out[f"hc_{name}_reduced"] = red.float().numpy().reshape(3, 4096)
+        out[f"hc_{name}_post"], out[f"hc_{name}_comb"] = post.numpy().reshape(3, 4), comb.numpy().reshape(3, 4, 4)
+        out[f"hc_{name}_merged"] = merged.float().numpy().reshape(3, 4, 4096)
+        out[f"hc_{name}_normed"] = normed.float().numpy().reshape(3, 4096)
+    # the hash-routed layers (executor.py:638-668 with layer < 3): ids from tid2eid, weights from the scores
+    g = synth.rng(1006)
+    wr_bits = synth.router_weight_bf16(g, 256, 1024)
+    xr = synth.activations(g, 3, 1024)
+    tid2eid = np.stack([g.permutation(256)[:6] for _ in range(3)]).astype(np.int64)
+    out["rh_inputs_sha256"] = np.frombuffer(_digest(wr_bits, xr, tid2eid), dtype=np.uint8)
+    scores = F.softplus(F.linear(torch.from_numpy(xr).float(), torch.from_numpy(synth.bf16_bits_to_f32(wr_bits)).float())).sqrt()
+    w6 = scores.gather(1, torch.from_numpy(tid2eid))
+    out["rh_w"] = (w6 / w6.sum(dim=-1, keepdim=True) * 1.5).numpy()
 
     path = os.path.join(HERE, "s14_golden.npz")
     np.savez_compressed(path, **out)
