@@ -22,6 +22,7 @@ ACCUM_PAIRWISE, ACCUM_REFERENCE = 0, 1
 LAYER_PATH_TENSOR, LAYER_PATH_TENSOR_PER_TOKEN, LAYER_PATH_TENSOR_STACK, LAYER_PATH_F32, LAYER_PATH_REFERENCE = 1, 2, 3, 4, 5
 LAYER_PATH_ROUTER_KERNEL = 0x100
 LAYER_PATH_TENSOR_BLOCK = 6
+STREAM_F32, STREAM_BF16 = 0, 1
 SCORE_SIGMOID, SCORE_SQRT_SOFTPLUS = 0, 1
 SCALE_UE8M0, SCALE_F32 = 0, 1
 PROFILE_S14_TOP6, PROFILE_FULL_DEPTH43_NATIVE_TOP6 = 0, 1
@@ -76,6 +77,12 @@ class RouterDesc(C.Structure):
                 ("top_k", C.c_uint32), ("score_fn", C.c_uint32), ("route_scale", C.c_float),
                 ("x", C.c_void_p), ("router_weight_bf16", C.c_void_p), ("bias", C.c_void_p),
                 ("ids_out", C.c_void_p), ("weights_out", C.c_void_p)]
+
+
+class HcParams(C.Structure):
+    _fields_ = [("n_tokens", C.c_uint32), ("hc", C.c_uint32), ("hidden", C.c_uint32), ("dtype", C.c_uint32),
+                ("sinkhorn_iters", C.c_uint32), ("norm_eps", C.c_float), ("hc_eps", C.c_float),
+                ("hc_fn", C.c_void_p), ("hc_scale", C.c_void_p), ("hc_base", C.c_void_p)]
 
 
 class RoutedLayerDesc(C.Structure):
@@ -155,6 +162,11 @@ SIGNATURES = {
     "s14_block_last_counts": (_I32, [_VP, _P(_U32)]),
     "s14_cmd_routed_moe_block_experts_ep": (_I32, [_VP, _VP, _VP, _P(RoutedLayerDesc), _U32, _U32, _U32, _VP]),
     "s14_cmd_moe_block_mix": (_I32, [_VP, _VP, _VP, _VP, _VP, _VP, _U32, _U32, _I32, _VP, _VP]),
+    "s14_cmd_hc_pre": (_I32, [_VP, _VP, _P(HcParams), _VP, _VP, _VP, _VP]),
+    "s14_cmd_hc_post": (_I32, [_VP, _VP, _U32, _U32, _U32, _U32, _VP, _VP, _VP, _VP, _VP]),
+    "s14_cmd_rms_norm": (_I32, [_VP, _VP, _U32, _U32, _U32, _VP, _VP, _F32, _VP]),
+    "s14_cmd_hc_head_reduce": (_I32, [_VP, _VP, _P(HcParams), _VP, _VP, _VP]),
+    "s14_cmd_router_hash": (_I32, [_VP, _VP, _P(RouterDesc), _VP]),
     "s14_layer_work_list": (_I32, [_U32, _U32, _U32, _U32, _U32, _U32, _VP, _U32, _VP]),
     "s14_mxfp4_expert_page_from_tensors": (_I32, [_U32, _U32, _VP, _VP]),
     "s14_mxfp4_expert_page_to_tensors": (_I32, [_U32, _U32, _VP, _VP]),

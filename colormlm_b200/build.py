@@ -14,7 +14,7 @@ HERE = os.path.dirname(os.path.abspath(__file__))
 CSRC = os.path.join(HERE, "csrc")
 LIB_NAME = "libpolaris_s14_cuda.so"
 LIB_PATH = os.path.join(HERE, LIB_NAME)
-SOURCES = ["s14_kernels.cu", "s14_moe_umma.cu", "s14_moe_block.cu", "s14_api.cu", "s14_host.cpp"]
+SOURCES = ["s14_kernels.cu", "s14_moe_umma.cu", "s14_moe_block.cu", "s14_glue.cu", "s14_api.cu", "s14_host.cpp"]
 HEADERS = ["s14_internal.h", "s14_device.cuh", "s14_umma.cuh", "s14_host.hpp", os.path.join("..", "..", "include", "polaris_s14_cuda.h")]
 
 

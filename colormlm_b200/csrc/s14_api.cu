@@ -59,6 +59,7 @@ extern "C" const char *s14_last_error(void) { return g_last_error.c_str(); }
 
 static constexpr uint32_t kMaxDim = 4096;  // largest hidden / intermediate of the fused layer
 static constexpr uint32_t kCounters = 2048; // [0]: router; [1 + token * 160 + slice]: down-phase row slices
+static constexpr uint32_t kGlueTokens = 1024;   // most tokens of a hyper-connection / RMSNorm / hash-route call
 static constexpr uint32_t kCtxCounters = 8192;  // a context's array also serves the tcgen05 phases (4609 used)
 
 struct s14_ctx {
@@ -98,6 +99,7 @@ struct s14_ctx {
         bool connected = false;
         uint32_t wait_limit = 1u << 22;  // polls of about a microsecond: a few seconds
     } ep;
+    float *glue = nullptr;    // [kGlueTokens, 25] dot products and mean squares of the hyper-connection calls
     UmmaScratch umma{nullptr, nullptr, nullptr};  // scratch of the tcgen05 layer kernel
     bool use_umma = true;                // S14_TENSOR_PATH=off in the environment turns it off
     const UmmaScratch *umma_scratch() const { return use_umma ? &umma : nullptr; }
@@ -130,6 +132,7 @@ extern "C" int32_t s14_ctx_create(int32_t device, s14_ctx **out) {
     CUDA_OK(cudaMalloc(&ctx->scores, sizeof(float) * kMaxTokens * S14_N_ROUTED_EXPERTS));
     CUDA_OK(cudaMalloc(&ctx->select, sizeof(float) * kMaxTokens * S14_N_ROUTED_EXPERTS));
     CUDA_OK(cudaMalloc(&ctx->dev_table, sizeof(JobTable)));
+    CUDA_OK(cudaMalloc(&ctx->glue, sizeof(float) * kGlueTokens * 25));
     CUDA_OK(cudaMalloc(&ctx->x_stage, sizeof(float) * kMaxTokens * kMaxDim));
     CUDA_OK(cudaMalloc(&ctx->y_stage, sizeof(float) * kMaxTokens * kMaxDim));
     CUDA_OK(cudaMalloc(&ctx->status, sizeof(uint32_t)));
@@ -168,6 +171,7 @@ extern "C" int32_t s14_ctx_destroy(s14_ctx *ctx) {
     cudaFree(ctx->d);
     cudaFree(ctx->scores);
     cudaFree(ctx->select);
+    cudaFree(ctx->glue);
     cudaFree(ctx->dev_table);
     cudaFree(ctx->x_stage);
     cudaFree(ctx->y_stage);
@@ -2010,4 +2014,91 @@ extern "C" int32_t s14_block_last_counts(s14_block *blk, uint32_t counts_out[4])
     CUDA_OK(cudaSetDevice(blk->ctx->device));
     CUDA_OK(cudaMemcpy(counts_out, blk->w.counts, 16, cudaMemcpyDeviceToHost));
     return S14_OK;
+}
+
+
+// ---- the steps on either side of the MoE inside one layer ---------------------------------------
+static void check_streams(const char *what, uint32_t n_tokens, uint32_t hc, uint32_t hidden, uint32_t dtype) {
+    if (n_tokens == 0 || n_tokens > kGlueTokens) throw ContractError(std::string(what) + ": 1..1024 tokens");
+    if (hc != 4) throw ContractError(std::string(what) + ": the state has four streams");
+    if (hidden == 0 || hidden % 256 != 0 || hidden > 8192) throw ContractError(std::string(what) + ": hidden must be a multiple of 256 up to 8192");
+    if (dtype != S14_STREAM_F32 && dtype != S14_STREAM_BF16) throw ContractError(std::string(what) + ": unknown stream type");
+}
+
+static int32_t hc_reduce_call(s14_ctx *ctx, void *stream, const s14_hc_params *p, bool head, const void *x, void *reduced,
+                              float *post, float *comb, float *pre, const char *what) {
+    S14_TRY
+    if (!ctx || !p || !x || !reduced) throw ContractError(std::string(what) + ": NULL argument");
+    check_streams(what, p->n_tokens, p->hc, p->hidden, p->dtype);
+    if (!p->hc_fn || !p->hc_scale || !p->hc_base) throw ContractError(std::string(what) + ": hc_fn, hc_scale or hc_base is NULL");
+    if (!head && (!post || !comb)) throw ContractError(std::string(what) + ": post or comb is NULL");
+    if (head && !pre) throw ContractError(std::string(what) + ": pre is NULL");
+    if (!head && p->sinkhorn_iters == 0) throw ContractError(std::string(what) + ": at least one Sinkhorn round");
+    if (!std::isfinite(p->norm_eps) || p->norm_eps <= 0.0f || !std::isfinite(p->hc_eps) || p->hc_eps <= 0.0f)
+        throw ContractError(std::string(what) + ": norm_eps and hc_eps must be finite and positive");
+    CUDA_OK(cudaSetDevice(ctx->device));
+    cudaError_t err;
+    ctx->launches += launch_hc_pre(stream_of(ctx, stream), p->dtype == S14_STREAM_BF16, head, p->n_tokens, p->hidden, x, p->hc_fn,
+                                   p->hc_scale, p->hc_base, p->norm_eps, p->sinkhorn_iters, p->hc_eps, ctx->glue,
+                                   ctx->glue + (size_t)kGlueTokens * 24, reduced, post, comb, pre, &err);
+    if (err != cudaSuccess) return cuda_fail(err, what);
+    return S14_OK;
+    S14_CATCH
+}
+
+extern "C" int32_t s14_cmd_hc_pre(s14_ctx *ctx, void *stream, const s14_hc_params *params, const void *x, void *reduced,
+                                  float *post, float *comb) {
+    return hc_reduce_call(ctx, stream, params, false, x, reduced, post, comb, nullptr, "s14_cmd_hc_pre");
+}
+
+extern "C" int32_t s14_cmd_hc_head_reduce(s14_ctx *ctx, void *stream, const s14_hc_params *params, const void *x, void *reduced,
+                                          float *pre) {
+    return hc_reduce_call(ctx, stream, params, true, x, reduced, nullptr, nullptr, pre, "s14_cmd_hc_head_reduce");
+}
+
+extern "C" int32_t s14_cmd_hc_post(s14_ctx *ctx, void *stream, uint32_t n_tokens, uint32_t hc, uint32_t hidden, uint32_t dtype,
+                                   const void *branch, const void *residual, const float *post, const float *comb, void *merged) {
+    S14_TRY
+    if (!ctx || !branch || !residual || !post || !comb || !merged) throw ContractError("s14_cmd_hc_post: NULL argument");
+    check_streams("s14_cmd_hc_post", n_tokens, hc, hidden, dtype);
+    CUDA_OK(cudaSetDevice(ctx->device));
+    const cudaError_t err = launch_hc_post(stream_of(ctx, stream), dtype == S14_STREAM_BF16, n_tokens, hidden, branch, residual, post,
+                                           comb, merged);
+    ctx->launches += 1;
+    if (err != cudaSuccess) return cuda_fail(err, "s14_cmd_hc_post");
+    return S14_OK;
+    S14_CATCH
+}
+
+extern "C" int32_t s14_cmd_rms_norm(s14_ctx *ctx, void *stream, uint32_t n_tokens, uint32_t hidden, uint32_t dtype, const void *x,
+                                    const float *weight, float eps, void *out) {
+    S14_TRY
+    if (!ctx || !x || !weight || !out) throw ContractError("s14_cmd_rms_norm: NULL argument");
+    check_streams("s14_cmd_rms_norm", n_tokens, 4, hidden, dtype);
+    if (!std::isfinite(eps) || eps <= 0.0f) throw ContractError("s14_cmd_rms_norm: eps must be finite and positive");
+    CUDA_OK(cudaSetDevice(ctx->device));
+    const cudaError_t err = launch_rms_norm(stream_of(ctx, stream), dtype == S14_STREAM_BF16, n_tokens, hidden, x, weight, eps, out);
+    ctx->launches += 1;
+    if (err != cudaSuccess) return cuda_fail(err, "s14_cmd_rms_norm");
+    return S14_OK;
+    S14_CATCH
+}
+
+extern "C" int32_t s14_cmd_router_hash(s14_ctx *ctx, void *stream, const s14_router_desc *desc, const int64_t *tid2eid_rows) {
+    S14_TRY
+    if (!ctx || !desc || !tid2eid_rows) throw ContractError("s14_cmd_router_hash: NULL argument");
+    const s14_router_desc &r = *desc;
+    if (r.n_experts == 0 || r.n_experts > S14_N_ROUTED_EXPERTS) throw ContractError("S14 router: 1..256 experts");
+    if (r.hidden == 0 || r.hidden % 256 != 0) throw ContractError("S14 router: hidden must be a multiple of 256");
+    if (r.n_tokens == 0 || r.n_tokens > kGlueTokens) throw ContractError("s14_cmd_router_hash: 1..1024 tokens");
+    if (r.top_k == 0 || r.top_k > 8) throw ContractError("S14 router: top_k must be 1..8");
+    if (r.score_fn != S14_SCORE_SIGMOID && r.score_fn != S14_SCORE_SQRT_SOFTPLUS) throw ContractError("S14 router: unknown score function");
+    if (!std::isfinite(r.route_scale) || r.route_scale <= 0.0f) throw ContractError("S14 router: route_scale must be finite and positive");
+    if (!r.x || !r.router_weight_bf16 || !r.ids_out || !r.weights_out) throw ContractError("S14 router: x, weight, ids_out or weights_out is NULL");
+    CUDA_OK(cudaSetDevice(ctx->device));
+    const cudaError_t err = launch_router_hash(stream_of(ctx, stream), r, tid2eid_rows);
+    ctx->launches += 1;
+    if (err != cudaSuccess) return cuda_fail(err, "s14_cmd_router_hash");
+    return S14_OK;
+    S14_CATCH
 }

@@ -203,6 +203,17 @@ cudaError_t launch_block_mix(cudaStream_t st, const float *pairs, const int32_t 
 // of kernels launched.
 int launch_router_batch(cudaStream_t st, const s14_router_desc &r, float *scores, float *select, cudaError_t *err);
 
+// ---- the steps on either side of the MoE inside one layer (s14_glue.cu) ----
+// dots: [n_tokens, 24] scratch, mean_sq: [n_tokens] scratch.  Returns the number of kernels launched.
+int launch_hc_pre(cudaStream_t st, bool bf16, bool head, uint32_t n_tokens, uint32_t hidden, const void *x, const float *fn,
+                  const float *scale, const float *base, float norm_eps, uint32_t iters, float hc_eps, float *dots, float *mean_sq,
+                  void *reduced, float *post, float *comb, float *pre, cudaError_t *err);
+cudaError_t launch_hc_post(cudaStream_t st, bool bf16, uint32_t n_tokens, uint32_t hidden, const void *branch, const void *residual,
+                           const float *post, const float *comb, void *merged);
+cudaError_t launch_rms_norm(cudaStream_t st, bool bf16, uint32_t n_tokens, uint32_t hidden, const void *x, const float *w, float eps,
+                            void *out);
+cudaError_t launch_router_hash(cudaStream_t st, const s14_router_desc &r, const int64_t *tid2eid);
+
 }  // namespace s14
 
 

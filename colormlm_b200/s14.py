@@ -329,6 +329,37 @@ class S14Context:
         check(L.lib().s14_ctx_kernel_times(self._h, ms, C.byref(calls)))
         return dict(zip(("router", "up", "down", "mix"), [float(v) for v in ms])), calls.value
 
+    # ---- the steps on either side of the MoE inside one layer (see the header) ---------
+    def cmd_hc_pre(self, x, hc_fn, hc_scale, hc_base, reduced, post, comb, *, iters: int = 20, norm_eps: float = 1e-6,
+                   hc_eps: float = 1e-6, stream: Optional[int] = None) -> None:
+        """x [T, 4, hidden] (float32 or bfloat16) -> reduced [T, hidden], post [T, 4], comb [T, 4, 4]."""
+        p = _hc_params(x, hc_fn, hc_scale, hc_base, iters, norm_eps, hc_eps)
+        check(L.lib().s14_cmd_hc_pre(self._h, stream if stream is not None else _torch_stream(), C.byref(p), x.data_ptr(),
+                                     reduced.data_ptr(), post.data_ptr(), comb.data_ptr()))
+
+    def cmd_hc_post(self, branch, residual, post, comb, merged, stream: Optional[int] = None) -> None:
+        """merged [T, 4, hidden] = post * branch + sum_h comb[h] * residual[h]."""
+        check(L.lib().s14_cmd_hc_post(self._h, stream if stream is not None else _torch_stream(), residual.shape[0],
+                                      residual.shape[1], residual.shape[2], _stream_type(residual), branch.data_ptr(),
+                                      residual.data_ptr(), post.data_ptr(), comb.data_ptr(), merged.data_ptr()))
+
+    def cmd_rms_norm(self, x, weight, out, *, eps: float = 1e-6, stream: Optional[int] = None) -> None:
+        check(L.lib().s14_cmd_rms_norm(self._h, stream if stream is not None else _torch_stream(), x.shape[0], x.shape[1],
+                                       _stream_type(x), x.data_ptr(), weight.data_ptr(), eps, out.data_ptr()))
+
+    def cmd_hc_head_reduce(self, x, hc_fn, hc_scale, hc_base, reduced, pre, *, norm_eps: float = 1e-6, hc_eps: float = 1e-6,
+                           stream: Optional[int] = None) -> None:
+        p = _hc_params(x, hc_fn, hc_scale, hc_base, 1, norm_eps, hc_eps)
+        check(L.lib().s14_cmd_hc_head_reduce(self._h, stream if stream is not None else _torch_stream(), C.byref(p),
+                                             x.data_ptr(), reduced.data_ptr(), pre.data_ptr()))
+
+    def cmd_router_hash(self, x, wr_bf16, tid2eid_rows, ids_out, weights_out, *, score_fn: int = L.SCORE_SQRT_SOFTPLUS,
+                        route_scale: float = 1.5, stream: Optional[int] = None) -> None:
+        """The hash-routed layers: ids from the tokens' tid2eid rows (int64 [T, top_k]), weights from the scores."""
+        d = _router_desc(x, wr_bf16, None, ids_out, weights_out, score_fn, tid2eid_rows.shape[-1], route_scale)
+        check(L.lib().s14_cmd_router_hash(self._h, stream if stream is not None else _torch_stream(), C.byref(d),
+                                          tid2eid_rows.data_ptr()))
+
     def cmd_head_logits(self, x, weight_bf16, logits_out, *, n_rows: Optional[int] = None,
                         stream: Optional[int] = None) -> None:
         n_tokens = 1 if x.dim() == 1 else x.shape[0]
@@ -341,6 +372,25 @@ class S14Context:
     def cmd_greedy_argmax(self, logits, result, stream: Optional[int] = None) -> None:
         check(L.lib().s14_cmd_greedy_argmax(self._h, stream if stream is not None else _torch_stream(),
                                             logits.data_ptr(), logits.numel(), result.data_ptr()))
+
+
+def _stream_type(t) -> int:
+    import torch
+
+    if t.dtype == torch.float32:
+        return L.STREAM_F32
+    if t.dtype == torch.bfloat16:
+        return L.STREAM_BF16
+    raise S14Error(L.ERR_CONTRACT, "a token's streams are float32 or bfloat16 tensors")
+
+
+def _hc_params(x, hc_fn, hc_scale, hc_base, iters, norm_eps, hc_eps) -> "L.HcParams":
+    p = L.HcParams()
+    p.n_tokens, p.hc, p.hidden = x.shape[0], x.shape[1], x.shape[2]
+    p.dtype = _stream_type(x)
+    p.sinkhorn_iters, p.norm_eps, p.hc_eps = iters, norm_eps, hc_eps
+    p.hc_fn, p.hc_scale, p.hc_base = hc_fn.data_ptr(), hc_scale.data_ptr(), hc_base.data_ptr()
+    return p
 
 
 @dataclass

@@ -511,6 +511,45 @@ S14_API int32_t s14_cmd_moe_block_mix(s14_ctx *ctx, void *stream, s14_block *blk
  * an expert id was outside the table (the call then wrote no result). */
 S14_API int32_t s14_block_last_counts(s14_block *blk, uint32_t counts_out[4]);
 
+/* ---- the steps on either side of the MoE inside one layer ------------------------------------
+ * Hyper-connection reduce and expand, RMSNorm, the head's reduce and the hash route of the first
+ * layers (local_s14_primitives/hc.py:19-148, final_head.py:43-110,
+ * s14_first_real_token/executor.py:638-668, 712-743: hc_pre -> RMSNorm -> route -> experts -> hc_post).
+ * A token's state is hc = 4 streams of `hidden` values, F32 or BF16 (the reference's state is BF16
+ * [1, 1, 4, 4096]); results are rounded to the streams' type where the Python code casts back.  The
+ * long sums (mean of squares, the 24 dot products with hc_fn) are accumulated in double and rounded
+ * to F32 once, exp is evaluated in double; everything else is the Python expressions' F32
+ * arithmetic in their order.  1..1024 tokens, hidden a multiple of 256 up to 8192.
+ *   hc_pre:   x [T, 4, hidden] -> reduced [T, hidden] (stream type), post [T, 4], comb [T, 4, 4] (F32)
+ *   hc_post:  merged[t][o] = post[t][o] * branch[t] + sum_h comb[t][h][o] * residual[t][h]  ([T, 4, hidden])
+ *   rms_norm: out = weight * (x * rsqrt(mean(x^2) + eps)), x [T, hidden]
+ *   hc_head_reduce: hc_fn [4, 4 * hidden], hc_scale [1], hc_base [4] -> reduced [T, hidden], pre [T, 4]
+ *   router_hash: ids_out[t] = tid2eid_rows[t] (device int64 [T, top_k], the current token's row of the
+ *            layer's tid2eid), weights_out = the router's scores of those experts / their sum * route_scale;
+ *            desc->bias is not used. */
+#define S14_STREAM_F32 0u
+#define S14_STREAM_BF16 1u
+typedef struct {
+    uint32_t n_tokens;
+    uint32_t hc;             /* 4 */
+    uint32_t hidden;
+    uint32_t dtype;          /* S14_STREAM_* of x and reduced */
+    uint32_t sinkhorn_iters; /* the reference: 20 */
+    float norm_eps, hc_eps;  /* the reference: 1e-6 both */
+    const float *hc_fn;      /* [(2 + hc) * hc, hc * hidden] F32 */
+    const float *hc_scale;   /* [3] */
+    const float *hc_base;    /* [(2 + hc) * hc] */
+} s14_hc_params;
+S14_API int32_t s14_cmd_hc_pre(s14_ctx *ctx, void *stream, const s14_hc_params *params, const void *x, void *reduced,
+                               float *post, float *comb);
+S14_API int32_t s14_cmd_hc_post(s14_ctx *ctx, void *stream, uint32_t n_tokens, uint32_t hc, uint32_t hidden, uint32_t dtype,
+                                const void *branch, const void *residual, const float *post, const float *comb, void *merged);
+S14_API int32_t s14_cmd_rms_norm(s14_ctx *ctx, void *stream, uint32_t n_tokens, uint32_t hidden, uint32_t dtype, const void *x,
+                                 const float *weight, float eps, void *out);
+S14_API int32_t s14_cmd_hc_head_reduce(s14_ctx *ctx, void *stream, const s14_hc_params *params, const void *x, void *reduced,
+                                       float *pre);
+S14_API int32_t s14_cmd_router_hash(s14_ctx *ctx, void *stream, const s14_router_desc *desc, const int64_t *tid2eid_rows);
+
 /* LM head (local_s14_primitives/final_head.py:113-149): logits[v] = x . W[v,:]
  * for the rows [row_begin, row_begin + n_rows) of a BF16 [vocab, hidden] matrix
  * whose first stored row is row_begin (a vocabulary shard); logits_out points at
