@@ -2,7 +2,7 @@
 """Benchmark of the S14 MoE expert path on B200.
 
     python bench.py [--gpus N] [--steps K] [--warmup W] [--impl reference]
-                    [--workload stack|layer|expert_chain|wq_a|verify8|prefill|decode] [--accum pairwise|reference]
+                    [--workload stack|layer|expert_chain|wq_a|verify8|prefill|glue|decode] [--accum pairwise|reference]
 
 A step is one layer-token: one token through one MoE layer (router top-6 of 256, six routed MXFP4
 experts and the shared MXFP4 expert, hidden 4096, intermediate 2048).  14 layers of 257 expert pages
@@ -15,7 +15,9 @@ are resident (48 GB), so the 96 MB a step touches never come from L2.
   expert_chain, wq_a   the single-expert chain and the FP8 projection matvec of the other
           configurations, each with its own roofline entry;
   verify8, prefill   a block of tokens (8; 370, or --tokens N) through one layer with the tokens
-          grouped by expert, every distinct expert page streamed once (s14_cmd_routed_moe_block).
+          grouped by expert, every distinct expert page streamed once (s14_cmd_routed_moe_block);
+  glue    the steps on either side of the MoE at one site of a layer (hc_pre -> RMSNorm -> hc_post,
+          --tokens N tokens, BF16 streams).
 
 The timed region is exactly K steps, taken with CUDA events on the launching stream; it is repeated
 (--repeats, default 50) and the median repeat is reported with the spread.  Pages are a function of
@@ -320,7 +322,7 @@ def run_gpu(args) -> None:
         return run_prefill_ep(args, torch, dist, L, ep, S14Context, rank, world, local_rank)
     if world > 1 and workload != "layer":
         raise SystemExit("several GPUs: the expert-parallel workloads are `layer` and `prefill`")
-    if workload in ("expert_chain", "wq_a", "verify8", "prefill"):
+    if workload in ("expert_chain", "wq_a", "verify8", "prefill", "glue"):
         return run_small_workload(args, workload, torch, L, synth, S14Context, TokenRoute)
     if workload == "decode":
         return run_decode_workload(args, torch, L, synth, S14Context)
@@ -1208,6 +1210,61 @@ def run_small_workload(args, workload, torch, L, synth, S14Context, TokenRoute) 
                 for i in range(t):
                     oracle.fp8_matvec(x_np[i], w2, s_np, n, k)
             return (time.perf_counter() - t0) / 20
+    elif workload == "glue":
+        # the steps on either side of the MoE at one site of a layer: hc_pre -> RMSNorm -> (branch) -> hc_post,
+        # BF16 streams [T, 4, 4096] as the reference's state; L2-cold by walking 96 distinct hc_fn (151 MB)
+        n_tok = max(1, min(1024, args.tokens))
+        n_fn = 96
+        fn_np, sc_np, ba_np = synth.hc_params(g, HIDDEN)
+        fns = torch.from_numpy(fn_np).cuda().unsqueeze(0).repeat(n_fn, 1, 1)
+        fns += torch.arange(n_fn, device="cuda", dtype=torch.float32).view(-1, 1, 1) * 1e-4   # distinct matrices
+        sc, ba = torch.from_numpy(sc_np).cuda(), torch.from_numpy(ba_np).cuda()
+        xs_np = synth.hc_streams(g, n_tok, HIDDEN)
+        xs = torch.from_numpy(xs_np).cuda().to(torch.bfloat16)
+        nw_np = g.uniform(0.5, 1.5, size=HIDDEN).astype(np.float32)
+        nw = torch.from_numpy(nw_np).cuda()
+        red = torch.empty((n_tok, HIDDEN), dtype=torch.bfloat16, device="cuda")
+        normed, merged = torch.empty_like(red), torch.empty_like(xs)
+        post = torch.empty((n_tok, 4), dtype=torch.float32, device="cuda")
+        comb = torch.empty((n_tok, 4, 4), dtype=torch.float32, device="cuda")
+        unit_bytes = fn_np.nbytes + n_tok * (4 * HIDDEN * 2 * 3 + HIDDEN * 2 * 4) + HIDDEN * 4
+        what = (f"layer glue at one site, {n_tok} token(s): hc_pre (24 x 16 384 F32 mixing matrix, Sinkhorn 20) -> RMSNorm -> "
+                "hc_post, BF16 streams [T, 4, 4096]")
+
+        def glue_call(i, st):
+            ctx.cmd_hc_pre(xs, fns[i % n_fn], sc, ba, red, post, comb, stream=st)
+            ctx.cmd_rms_norm(red, nw, normed, stream=st)
+            ctx.cmd_hc_post(normed, xs, post, comb, merged, stream=st)
+
+        def enqueue():
+            for i in range(args.steps):
+                glue_call(i, stream.cuda_stream)
+
+        def _bits(t):
+            return t.view(torch.int16).cpu().numpy().view(np.uint16)
+
+        def _f(a):
+            return (np.asarray(a, np.uint16).astype(np.uint32) << 16).view(np.float32)
+
+        def check():
+            glue_call(2, None)
+            torch.cuda.synchronize()
+            fn2 = fns[2].cpu().numpy()
+            r_ref, p_ref, c_ref = oracle.hc_pre(_bits(xs), fn2, sc_np, ba_np, dtype=1)
+            n_ref = oracle.rms_norm(r_ref, nw_np, dtype=1)
+            m_ref = oracle.hc_post(n_ref, _bits(xs), p_ref, c_ref, dtype=1)
+            blk_ = error_block(oracle, merged.float().cpu().numpy().ravel(), _f(m_ref).ravel())
+            blk_["coefficients_max_abs"] = float(max(np.abs(post.cpu().numpy() - p_ref).max(), np.abs(comb.cpu().numpy() - c_ref).max()))
+            return {"vs_oracle": blk_, "vs_double_accumulated_oracle": blk_}
+
+        def cpu_once():
+            fn2 = fns[2].cpu().numpy()
+            xb = _bits(xs)
+            t0 = time.perf_counter()
+            r_ref, p_ref, c_ref = oracle.hc_pre(xb, fn2, sc_np, ba_np, dtype=1)
+            n_ref = oracle.rms_norm(r_ref, nw_np, dtype=1)
+            oracle.hc_post(n_ref, xb, p_ref, c_ref, dtype=1)
+            return time.perf_counter() - t0
     else:  # verify8, prefill: a block of tokens through one layer, grouped by expert
         from colormlm_b200.s14 import MoeBlock
 
@@ -1295,7 +1352,7 @@ def run_small_workload(args, workload, torch, L, synth, S14Context, TokenRoute) 
     achieved = unit_bytes * args.steps / (ms * 1e-3) / 1e9
     per_call = n_tok if workload == "prefill" else 1   # a prefill is counted in tokens
     line = {"metric": {"expert_chain": "expert_chains_per_s", "wq_a": "matvecs_per_s", "verify8": "verify_blocks_per_s",
-                       "prefill": "prefill_tokens_per_s"}[workload],
+                       "prefill": "prefill_tokens_per_s", "glue": "layer_glue_calls_per_s"}[workload],
             "value": per_call * args.steps / (ms / 1e3), "unit": "tokens/s" if workload == "prefill" else "calls/s", "n_gpus": 1, "steps": args.steps, "warmup": args.warmup,
             "ms_per_step": ms / args.steps, "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "f32",
             "data": "synthetic",
@@ -1329,7 +1386,7 @@ def main() -> None:
     ap.add_argument("--steps", type=int, default=None)
     ap.add_argument("--warmup", type=int, default=None)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
-    ap.add_argument("--workload", default=None, choices=["stack", "layer", "expert_chain", "wq_a", "verify8", "prefill", "decode"])
+    ap.add_argument("--workload", default=None, choices=["stack", "layer", "expert_chain", "wq_a", "verify8", "prefill", "glue", "decode"])
     ap.add_argument("--tokens", type=int, default=1, help="tokens of the wq_a workload (1, 4 or 8); of the prefill workload (default 370)")
     ap.add_argument("--accum", default="pairwise", choices=["pairwise", "reference"])
     ap.add_argument("--exchange", default="peer", choices=["peer", "nccl"],

@@ -55,12 +55,28 @@ k_hc_mixes(const void *__restrict__ x, const float *__restrict__ fn, uint32_t n,
            float *__restrict__ mean_sq, uint32_t n_mix) {
     __shared__ double red[8];
     const uint32_t m = blockIdx.x, t = blockIdx.y;
-    const float *row = fn + (size_t)m * n;
+    const float4 *row = reinterpret_cast<const float4 *>(fn + (size_t)m * n);
     double acc = 0.0, ss = 0.0;
-    for (uint32_t i = threadIdx.x; i < n; i += 256u) {
-        const double v = (double)stream_ld<kBf16>(x, (size_t)t * n + i);
-        acc += v * (double)__ldg(row + i);
-        ss += v * v;
+    // four elements per thread and step, four steps' loads in flight (n is a multiple of 1024)
+#pragma unroll 4
+    for (uint32_t i = threadIdx.x; i < (n >> 2); i += 256u) {
+        float v[4];
+        if constexpr (kBf16) {
+            const uint2 q = __ldg(reinterpret_cast<const uint2 *>(reinterpret_cast<const uint16_t *>(x) + (size_t)t * n) + i);
+            v[0] = __uint_as_float(q.x << 16), v[1] = __uint_as_float(q.x & 0xffff0000u);
+            v[2] = __uint_as_float(q.y << 16), v[3] = __uint_as_float(q.y & 0xffff0000u);
+        } else {
+            const float4 q = __ldg(reinterpret_cast<const float4 *>(reinterpret_cast<const float *>(x) + (size_t)t * n) + i);
+            v[0] = q.x, v[1] = q.y, v[2] = q.z, v[3] = q.w;
+        }
+        const float4 w = __ldg(row + i);
+        const float wv[4] = {w.x, w.y, w.z, w.w};
+#pragma unroll
+        for (int k = 0; k < 4; ++k) {
+            const double d = (double)v[k];
+            acc += d * (double)wv[k];
+            ss += d * d;
+        }
     }
     const double dot = block_sum_256(acc, red);
     if (m == 0u) {
@@ -70,56 +86,38 @@ k_hc_mixes(const void *__restrict__ x, const float *__restrict__ fn, uint32_t n,
     if (threadIdx.x == 0) dots[(size_t)t * n_mix + m] = (float)dot;
 }
 
-// hc.py:19-84 by one thread: 24 logits -> pre [4], post [4], comb [4][4], F32 in the reference's order.
-__device__ void split_sinkhorn(const float *mixes, const float *scale, const float *base, uint32_t iters, float eps, float *pre,
-                               float *post, float *comb) {
-#pragma unroll
-    for (uint32_t h = 0; h < kHc; ++h) {
-        pre[h] = __fadd_rn(sigmoid_f32(__fadd_rn(__fmul_rn(mixes[h], scale[0]), base[h])), eps);
-        post[h] = __fmul_rn(2.0f, sigmoid_f32(__fadd_rn(__fmul_rn(mixes[kHc + h], scale[1]), base[kHc + h])));
-    }
-#pragma unroll
-    for (uint32_t i = 0; i < kHc * kHc; ++i) comb[i] = __fadd_rn(__fmul_rn(mixes[2 * kHc + i], scale[2]), base[2 * kHc + i]);
-#pragma unroll
-    for (uint32_t i = 0; i < kHc; ++i) {  // stable row softmax, + eps
-        float mx = comb[i * kHc];
-#pragma unroll
-        for (uint32_t j = 1; j < kHc; ++j) mx = comb[i * kHc + j] > mx ? comb[i * kHc + j] : mx;
-        float s = 0.0f;
-#pragma unroll
-        for (uint32_t j = 0; j < kHc; ++j) {
-            comb[i * kHc + j] = (float)exp((double)__fsub_rn(comb[i * kHc + j], mx));
-            s = __fadd_rn(s, comb[i * kHc + j]);
-        }
-#pragma unroll
-        for (uint32_t j = 0; j < kHc; ++j) comb[i * kHc + j] = __fadd_rn(__fdiv_rn(comb[i * kHc + j], s), eps);
-    }
+// hc.py:19-84 by one warp: 24 logits -> pre [4], post [4], comb [4][4], F32 in the reference's order.  Lane
+// l < 16 owns comb[l / 4][l % 4]; a row's or column's four values are fetched with shuffles and added in
+// index order, as the Python sums do; lanes 0-3 also make pre and post.  All 32 lanes call it.
+__device__ __forceinline__ void split_sinkhorn_warp(const float *mixes, const float *scale, const float *base, uint32_t iters,
+                                                    float eps, uint32_t lane, float &pre, float &post, float &comb) {
+    const uint32_t l = lane & 15u, i = l >> 2, j = l & 3u, h = lane & 3u;
+    pre = __fadd_rn(sigmoid_f32(__fadd_rn(__fmul_rn(mixes[h], scale[0]), base[h])), eps);
+    post = __fmul_rn(2.0f, sigmoid_f32(__fadd_rn(__fmul_rn(mixes[kHc + h], scale[1]), base[kHc + h])));
+    float c = __fadd_rn(__fmul_rn(mixes[2 * kHc + l], scale[2]), base[2 * kHc + l]);
+    auto row_sum = [&](float v, bool is_max) {
+        const float r0 = __shfl_sync(0xffffffffu, v, i * 4u), r1 = __shfl_sync(0xffffffffu, v, i * 4u + 1u);
+        const float r2 = __shfl_sync(0xffffffffu, v, i * 4u + 2u), r3 = __shfl_sync(0xffffffffu, v, i * 4u + 3u);
+        if (is_max) return fmaxf(fmaxf(fmaxf(r0, r1), r2), r3);
+        return __fadd_rn(__fadd_rn(__fadd_rn(r0, r1), r2), r3);
+    };
+    auto col_sum = [&](float v) {
+        const float r0 = __shfl_sync(0xffffffffu, v, j), r1 = __shfl_sync(0xffffffffu, v, 4u + j);
+        const float r2 = __shfl_sync(0xffffffffu, v, 8u + j), r3 = __shfl_sync(0xffffffffu, v, 12u + j);
+        return __fadd_rn(__fadd_rn(__fadd_rn(r0, r1), r2), r3);
+    };
+    // stable row softmax, + eps
+    c = (float)exp((double)__fsub_rn(c, row_sum(c, true)));
+    c = __fadd_rn(__fdiv_rn(c, row_sum(c, false)), eps);
 #pragma unroll 1
     for (uint32_t it = 0; it < iters; ++it) {
-        if (it) {  // rows
-#pragma unroll
-            for (uint32_t i = 0; i < kHc; ++i) {
-                float s = 0.0f;
-#pragma unroll
-                for (uint32_t j = 0; j < kHc; ++j) s = __fadd_rn(s, comb[i * kHc + j]);
-                const float d = __fadd_rn(s, eps);
-#pragma unroll
-                for (uint32_t j = 0; j < kHc; ++j) comb[i * kHc + j] = __fdiv_rn(comb[i * kHc + j], d);
-            }
-        }
-#pragma unroll
-        for (uint32_t j = 0; j < kHc; ++j) {  // columns
-            float s = 0.0f;
-#pragma unroll
-            for (uint32_t i = 0; i < kHc; ++i) s = __fadd_rn(s, comb[i * kHc + j]);
-            const float d = __fadd_rn(s, eps);
-#pragma unroll
-            for (uint32_t i = 0; i < kHc; ++i) comb[i * kHc + j] = __fdiv_rn(comb[i * kHc + j], d);
-        }
+        if (it) c = __fdiv_rn(c, __fadd_rn(row_sum(c, false), eps));
+        c = __fdiv_rn(c, __fadd_rn(col_sum(c), eps));
     }
+    comb = c;
 }
 
-// One CTA per token: the coefficients from the dots (one thread), then reduced[d] = sum_h pre[h] x[h][d].
+// One CTA per token: the coefficients from the dots (one warp), then reduced[d] = sum_h pre[h] x[h][d].
 // kHead: the head's reduce (final_head.py:43-81): hc logits, pre = sigmoid(mix * scale + base) + eps only.
 template <bool kBf16, bool kHead>
 __global__ void __launch_bounds__(256)
@@ -127,30 +125,26 @@ k_hc_reduce(const void *__restrict__ x, const float *__restrict__ dots, const fl
             const float *__restrict__ scale, const float *__restrict__ base, uint32_t hidden, float norm_eps, uint32_t iters,
             float hc_eps, void *__restrict__ reduced, float *__restrict__ post_out, float *__restrict__ comb_out,
             float *__restrict__ pre_out) {
-    __shared__ float s_pre[kHc];
-    const uint32_t t = blockIdx.x;
+    __shared__ float s_pre[kHc], s_mix[kMixMax];
+    const uint32_t t = blockIdx.x, lane = threadIdx.x & 31u;
     constexpr uint32_t n_mix = kHead ? kHc : kMixMax;
-    if (threadIdx.x == 0) {
+    if (threadIdx.x < 32u) {
         const float rs = (float)(1.0 / sqrt((double)__fadd_rn(mean_sq[t], norm_eps)));
-        float mixes[n_mix], pre[kHc];
-#pragma unroll
-        for (uint32_t m = 0; m < n_mix; ++m) mixes[m] = __fmul_rn(dots[(size_t)t * n_mix + m], rs);
+        if (lane < n_mix) s_mix[lane] = __fmul_rn(dots[(size_t)t * n_mix + lane], rs);
+        __syncwarp();
+        float pre;
         if constexpr (kHead) {
-#pragma unroll
-            for (uint32_t h = 0; h < kHc; ++h)
-                pre[h] = __fadd_rn(sigmoid_f32(__fadd_rn(__fmul_rn(mixes[h], scale[0]), base[h])), hc_eps);
+            const uint32_t h = lane & 3u;
+            pre = __fadd_rn(sigmoid_f32(__fadd_rn(__fmul_rn(s_mix[h], scale[0]), base[h])), hc_eps);
         } else {
-            float post[kHc], comb[kHc * kHc];
-            split_sinkhorn(mixes, scale, base, iters, hc_eps, pre, post, comb);
-#pragma unroll
-            for (uint32_t h = 0; h < kHc; ++h) post_out[(size_t)t * kHc + h] = post[h];
-#pragma unroll
-            for (uint32_t i = 0; i < kHc * kHc; ++i) comb_out[(size_t)t * kHc * kHc + i] = comb[i];
+            float post, comb;
+            split_sinkhorn_warp(s_mix, scale, base, iters, hc_eps, lane, pre, post, comb);
+            if (lane < kHc) post_out[(size_t)t * kHc + lane] = post;
+            if (lane < kHc * kHc) comb_out[(size_t)t * kHc * kHc + lane] = comb;
         }
-#pragma unroll
-        for (uint32_t h = 0; h < kHc; ++h) {
-            s_pre[h] = pre[h];
-            if (pre_out) pre_out[(size_t)t * kHc + h] = pre[h];
+        if (lane < kHc) {
+            s_pre[lane] = pre;
+            if (pre_out) pre_out[(size_t)t * kHc + lane] = pre;
         }
     }
     __syncthreads();
