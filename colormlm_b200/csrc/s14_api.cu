@@ -1777,6 +1777,7 @@ extern "C" int32_t s14_moe_pages_cancel(s14_moe_pages *pages, s14_route_load_bat
 // outputs, router scratch, and a pinned staging buffer for routes that come from the host.
 struct s14_block {
     s14_ctx *ctx = nullptr;
+    int device = 0;           // the context's device (the object may outlive the context; its calls may not)
     uint32_t hidden = 0, inter = 0, max_tokens = 0;
     BlockWork w{};
     float *scores = nullptr, *select = nullptr;   // [max_tokens, 256]
@@ -1794,7 +1795,7 @@ static constexpr uint32_t kBlockMaxTokens = 1024;
 
 extern "C" int32_t s14_block_destroy(s14_block *blk) {
     if (!blk) return S14_OK;
-    cudaSetDevice(blk->ctx->device);
+    cudaSetDevice(blk->device);
     cudaDeviceSynchronize();
     cudaFree(blk->w.chunks);
     cudaFree(blk->w.counts);
@@ -1825,6 +1826,7 @@ extern "C" int32_t s14_block_create(s14_ctx *ctx, uint32_t hidden, uint32_t inte
         return fail(S14_ERR_CONTRACT, "s14_block_create: hidden and intermediate must be multiples of 512 up to 4096");
     std::unique_ptr<s14_block, int32_t (*)(s14_block *)> blk(new s14_block(), s14_block_destroy);
     blk->ctx = ctx;
+    blk->device = ctx->device;
     blk->hidden = hidden;
     blk->inter = inter;
     blk->max_tokens = max_tokens;
@@ -2011,7 +2013,7 @@ extern "C" int32_t s14_block_set_residual(s14_block *blk, int32_t residual) {
 // items, and 1 if an expert id was outside the table (the call then did nothing).
 extern "C" int32_t s14_block_last_counts(s14_block *blk, uint32_t counts_out[4]) {
     if (!blk || !counts_out) return fail(S14_ERR_CONTRACT, "s14_block_last_counts: NULL argument");
-    CUDA_OK(cudaSetDevice(blk->ctx->device));
+    CUDA_OK(cudaSetDevice(blk->device));
     CUDA_OK(cudaMemcpy(counts_out, blk->w.counts, 16, cudaMemcpyDeviceToHost));
     return S14_OK;
 }

@@ -483,7 +483,8 @@ S14_API int32_t s14_routed_moe_layer_host(s14_ctx *ctx, const s14_routed_layer_d
  *   s14_cmd_routed_moe_block: router on the device (desc->router.n_tokens up to max_tokens, top_k <= 6);
  *            ids_out / weights_out [n_tokens, top_k] may be NULL.
  *   One call at a time per block object (calls on one stream are ordered).  A wait that runs out
- *   inside a kernel sets the context's device status word to 0x5507. */
+ *   inside a kernel sets the context's device status word to 0x5507.  A block object is used only
+ *   while its context lives; destroying it afterwards is allowed. */
 typedef struct s14_block s14_block;
 S14_API int32_t s14_block_create(s14_ctx *ctx, uint32_t hidden, uint32_t inter, uint32_t max_tokens, s14_block **out);
 S14_API int32_t s14_block_destroy(s14_block *blk);

@@ -86,6 +86,27 @@ def test_block_equals_every_tokens_own_layer(ctx, oracle, n_tokens):
         blk.close()
 
 
+@pytest.mark.parametrize("hidden,inter", [(1024, 1024), (1024, 4096), (4096, 4096)])
+def test_block_at_the_other_sizes(ctx, oracle, hidden, inter):
+    """The smallest and the largest sizes the kernels take, a small block (chunks of two, one row tile per
+    item) and a large one (chunks of six, two row tiles per item)."""
+    n_experts = 8
+    g, pages, shared = make_layer(1600 + hidden + inter, hidden, inter, n_experts, L.PAGE_MXFP4)
+    pages_dev, shared_dev = [dev_page(p, hidden, inter) for p in pages], dev_page(shared, hidden, inter)
+    blk = MoeBlock(ctx, hidden, inter, 32)
+    try:
+        for n_tokens in (3, 17):
+            x = synth.activations(g, n_tokens, hidden)
+            routes = random_routes(g, n_tokens, n_experts, ragged=True)
+            y = run_block(ctx, blk, x, pages_dev, shared_dev, routes)
+            for t in range(n_tokens):
+                ids, w = routes[t]
+                ref = oracle.moe_layer_acc64(x[t], [pages[i] for i in ids], w, shared, 0, hidden, inter)
+                assert np.array_equal(y[t].view(np.uint32), ref.view(np.uint32)), (n_tokens, t)
+    finally:
+        blk.close()
+
+
 def test_block_at_the_benchmark_shape(ctx, oracle):
     """4096 x 2048, 48 experts.  A verify block of 8 tokens against the oracle, bit for bit; 40 tokens
     (every expert several tokens, the shared expert seven chunks) against every token's own one-token
