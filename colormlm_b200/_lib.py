@@ -85,6 +85,13 @@ class HcParams(C.Structure):
                 ("hc_fn", C.c_void_p), ("hc_scale", C.c_void_p), ("hc_base", C.c_void_p)]
 
 
+class ExecMoeDesc(C.Structure):
+    _fields_ = [("hidden", C.c_uint32), ("inter", C.c_uint32), ("shared_kind", C.c_uint32), ("route", C.c_void_p),
+                ("shared_page", C.c_void_p), ("ffn_input_bf16", C.c_void_p), ("residual_bf16", C.c_void_p),
+                ("post", C.c_void_p), ("comb", C.c_void_p), ("state_out_bf16", C.c_void_p),
+                ("moe_branch_out_bf16", C.c_void_p)]
+
+
 class RoutedLayerDesc(C.Structure):
     _fields_ = [("router", RouterDesc), ("inter", C.c_uint32), ("shared_kind", C.c_uint32),
                 ("page_table", C.c_void_p), ("shared_page", C.c_void_p), ("y", C.c_void_p)]
@@ -167,6 +174,8 @@ SIGNATURES = {
     "s14_cmd_rms_norm": (_I32, [_VP, _VP, _U32, _U32, _U32, _VP, _VP, _F32, _VP]),
     "s14_cmd_hc_head_reduce": (_I32, [_VP, _VP, _P(HcParams), _VP, _VP, _VP]),
     "s14_cmd_router_hash": (_I32, [_VP, _VP, _P(RouterDesc), _VP]),
+    "s14_exec_routed_and_shared_moe_then_hc_post": (_I32, [_VP, _VP, _P(ExecMoeDesc)]),
+    "s14_exec_hc_head_norm_full_logits": (_I32, [_VP, _VP, _P(HcParams), _VP, _VP, _U32, _VP, _VP]),
     "s14_layer_work_list": (_I32, [_U32, _U32, _U32, _U32, _U32, _U32, _VP, _U32, _VP]),
     "s14_mxfp4_expert_page_from_tensors": (_I32, [_U32, _U32, _VP, _VP]),
     "s14_mxfp4_expert_page_to_tensors": (_I32, [_U32, _U32, _VP, _VP]),

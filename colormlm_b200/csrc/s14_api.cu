@@ -100,6 +100,7 @@ struct s14_ctx {
         uint32_t wait_limit = 1u << 22;  // polls of about a microsecond: a few seconds
     } ep;
     float *glue = nullptr;    // [kGlueTokens, 25] dot products and mean squares of the hyper-connection calls
+    uint16_t *glue16 = nullptr;  // [4, 8192] BF16 vectors between the steps of the executor calls
     UmmaScratch umma{nullptr, nullptr, nullptr};  // scratch of the tcgen05 layer kernel
     bool use_umma = true;                // S14_TENSOR_PATH=off in the environment turns it off
     const UmmaScratch *umma_scratch() const { return use_umma ? &umma : nullptr; }
@@ -133,6 +134,7 @@ extern "C" int32_t s14_ctx_create(int32_t device, s14_ctx **out) {
     CUDA_OK(cudaMalloc(&ctx->select, sizeof(float) * kMaxTokens * S14_N_ROUTED_EXPERTS));
     CUDA_OK(cudaMalloc(&ctx->dev_table, sizeof(JobTable)));
     CUDA_OK(cudaMalloc(&ctx->glue, sizeof(float) * kGlueTokens * 25));
+    CUDA_OK(cudaMalloc(&ctx->glue16, sizeof(uint16_t) * 4 * 8192));
     CUDA_OK(cudaMalloc(&ctx->x_stage, sizeof(float) * kMaxTokens * kMaxDim));
     CUDA_OK(cudaMalloc(&ctx->y_stage, sizeof(float) * kMaxTokens * kMaxDim));
     CUDA_OK(cudaMalloc(&ctx->status, sizeof(uint32_t)));
@@ -172,6 +174,7 @@ extern "C" int32_t s14_ctx_destroy(s14_ctx *ctx) {
     cudaFree(ctx->scores);
     cudaFree(ctx->select);
     cudaFree(ctx->glue);
+    cudaFree(ctx->glue16);
     cudaFree(ctx->dev_table);
     cudaFree(ctx->x_stage);
     cudaFree(ctx->y_stage);
@@ -2101,6 +2104,64 @@ extern "C" int32_t s14_cmd_router_hash(s14_ctx *ctx, void *stream, const s14_rou
     const cudaError_t err = launch_router_hash(stream_of(ctx, stream), r, tid2eid_rows);
     ctx->launches += 1;
     if (err != cudaSuccess) return cuda_fail(err, "s14_cmd_router_hash");
+    return S14_OK;
+    S14_CATCH
+}
+
+
+// ---- the executor's two device steps (s14_runner/src/runner.rs:86-118) as single calls ------------
+//
+// NativeS14Executor::routed_and_shared_moe_then_hc_post: the FFN site's input (BF16, after hc_pre and
+// RMSNorm) through the routed and shared experts, the branch rounded to BF16, expanded into the four
+// streams with the site's post / comb.  One token.
+extern "C" int32_t s14_exec_routed_and_shared_moe_then_hc_post(s14_ctx *ctx, void *stream, const s14_exec_moe_desc *d) {
+    S14_TRY
+    if (!ctx || !d) throw ContractError("s14_exec_routed_and_shared_moe_then_hc_post: NULL argument");
+    if (!d->route || !d->ffn_input_bf16 || !d->residual_bf16 || !d->post || !d->comb || !d->state_out_bf16)
+        throw ContractError("s14_exec_routed_and_shared_moe_then_hc_post: NULL pointer in the descriptor");
+    if (!fused_dim_ok(d->hidden) || !fused_dim_ok(d->inter))
+        throw ContractError("s14_exec_routed_and_shared_moe_then_hc_post: hidden and intermediate must be 1024, 2048 or 4096");
+    CUDA_OK(cudaSetDevice(ctx->device));
+    cudaStream_t st = stream_of(ctx, stream);
+    CUDA_OK(launch_bf16_to_f32(st, d->ffn_input_bf16, ctx->x_stage, d->hidden));
+    s14_moe_layer_desc ld = {};
+    ld.hidden = d->hidden;
+    ld.inter = d->inter;
+    ld.n_tokens = 1;
+    ld.shared_kind = d->shared_kind;
+    ld.shared_page = d->shared_page;
+    ld.routes = d->route;
+    const int32_t rc = enqueue_layer(ctx, st, ld, ctx->x_stage, ctx->y_stage);
+    if (rc != S14_OK) return rc;
+    uint16_t *branch = d->moe_branch_out_bf16 ? d->moe_branch_out_bf16 : ctx->glue16;
+    CUDA_OK(launch_f32_to_bf16(st, ctx->y_stage, branch, d->hidden));
+    CUDA_OK(launch_hc_post(st, true, 1, d->hidden, branch, d->residual_bf16, d->post, d->comb, d->state_out_bf16));
+    ctx->launches += 3;
+    return S14_OK;
+    S14_CATCH
+}
+
+// NativeS14Executor::hc_head_norm_full_logits (final_head.py:152-191): the head's reduce of the four
+// streams, RMSNorm, the BF16 head's logits for rows [row_begin, row_begin + n_rows) of the vocabulary.
+extern "C" int32_t s14_exec_hc_head_norm_full_logits(s14_ctx *ctx, void *stream, const s14_hc_params *head, const float *norm_weight,
+                                                     const uint16_t *head_weight_bf16, uint32_t n_rows, const uint16_t *state_bf16,
+                                                     float *logits_out) {
+    S14_TRY
+    if (!ctx || !head || !norm_weight || !head_weight_bf16 || !state_bf16 || !logits_out)
+        throw ContractError("s14_exec_hc_head_norm_full_logits: NULL argument");
+    if (head->n_tokens != 1 || head->dtype != S14_STREAM_BF16)
+        throw ContractError("s14_exec_hc_head_norm_full_logits: one token, BF16 state");
+    if (n_rows == 0) throw ContractError("s14_exec_hc_head_norm_full_logits: no vocabulary rows");
+    if (head->hidden > kMaxDim) throw ContractError("s14_exec_hc_head_norm_full_logits: hidden above 4096");
+    uint16_t *reduced = ctx->glue16 + 8192, *normed = ctx->glue16 + 2 * 8192;
+    float *pre = ctx->glue + (size_t)kGlueTokens * 24 + 512;
+    int32_t rc = hc_reduce_call(ctx, stream, head, true, state_bf16, reduced, nullptr, nullptr, pre, "s14_exec_hc_head_norm_full_logits");
+    if (rc != S14_OK) return rc;
+    cudaStream_t st = stream_of(ctx, stream);
+    CUDA_OK(launch_rms_norm(st, true, 1, head->hidden, reduced, norm_weight, head->norm_eps, normed));
+    CUDA_OK(launch_bf16_to_f32(st, normed, ctx->x_stage, head->hidden));
+    CUDA_OK(launch_head_logits(st, ctx->sm_count, ctx->x_stage, 1, head_weight_bf16, n_rows, head->hidden, logits_out, n_rows));
+    ctx->launches += 3;
     return S14_OK;
     S14_CATCH
 }

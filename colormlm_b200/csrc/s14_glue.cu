@@ -229,7 +229,25 @@ k_router_hash(const float *__restrict__ x, const uint16_t *__restrict__ wr, cons
     }
 }
 
+__global__ void __launch_bounds__(256) k_bf16_to_f32(const uint16_t *__restrict__ in, float *__restrict__ out, uint32_t n) {
+    const uint32_t i = blockIdx.x * 256u + threadIdx.x;
+    if (i < n) out[i] = __uint_as_float((uint32_t)__ldg(in + i) << 16);
+}
+__global__ void __launch_bounds__(256) k_f32_to_bf16(const float *__restrict__ in, __nv_bfloat16 *__restrict__ out, uint32_t n) {
+    const uint32_t i = blockIdx.x * 256u + threadIdx.x;
+    if (i < n) out[i] = __float2bfloat16_rn(__ldg(in + i));
+}
+
 }  // namespace
+
+cudaError_t launch_bf16_to_f32(cudaStream_t st, const uint16_t *in, float *out, uint32_t n) {
+    k_bf16_to_f32<<<(n + 255u) / 256u, 256, 0, st>>>(in, out, n);
+    return cudaGetLastError();
+}
+cudaError_t launch_f32_to_bf16(cudaStream_t st, const float *in, uint16_t *out, uint32_t n) {
+    k_f32_to_bf16<<<(n + 255u) / 256u, 256, 0, st>>>(in, reinterpret_cast<__nv_bfloat16 *>(out), n);
+    return cudaGetLastError();
+}
 
 // dots: [n_tokens, 24] scratch, mean_sq: [n_tokens] scratch.  Returns the number of kernels launched.
 int launch_hc_pre(cudaStream_t st, bool bf16, bool head, uint32_t n_tokens, uint32_t hidden, const void *x, const float *fn,

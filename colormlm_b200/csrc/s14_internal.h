@@ -213,6 +213,8 @@ cudaError_t launch_hc_post(cudaStream_t st, bool bf16, uint32_t n_tokens, uint32
 cudaError_t launch_rms_norm(cudaStream_t st, bool bf16, uint32_t n_tokens, uint32_t hidden, const void *x, const float *w, float eps,
                             void *out);
 cudaError_t launch_router_hash(cudaStream_t st, const s14_router_desc &r, const int64_t *tid2eid);
+cudaError_t launch_bf16_to_f32(cudaStream_t st, const uint16_t *in, float *out, uint32_t n);
+cudaError_t launch_f32_to_bf16(cudaStream_t st, const float *in, uint16_t *out, uint32_t n);
 
 }  // namespace s14
 

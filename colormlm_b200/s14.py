@@ -360,6 +360,32 @@ class S14Context:
         check(L.lib().s14_cmd_router_hash(self._h, stream if stream is not None else _torch_stream(), C.byref(d),
                                           tid2eid_rows.data_ptr()))
 
+    # ---- the executor's two device steps as single calls (see the header) -------------
+    def exec_routed_and_shared_moe_then_hc_post(self, ffn_input, residual, post, comb, route: "TokenRoute",
+                                                shared_page: Optional[int], shared_kind: int, inter: int, state_out,
+                                                moe_branch_out=None, stream: Optional[int] = None) -> None:
+        """ffn_input bfloat16 [hidden], residual bfloat16 [4, hidden] -> state_out bfloat16 [4, hidden]."""
+        ld, keep = _layer_desc([route], shared_page, shared_kind, ffn_input.shape[-1], inter)
+        d = L.ExecMoeDesc()
+        d.hidden, d.inter, d.shared_kind = ffn_input.shape[-1], inter, shared_kind
+        d.route = C.cast(ld.routes, C.c_void_p)
+        d.shared_page = shared_page
+        d.ffn_input_bf16, d.residual_bf16 = ffn_input.data_ptr(), residual.data_ptr()
+        d.post, d.comb = post.data_ptr(), comb.data_ptr()
+        d.state_out_bf16 = state_out.data_ptr()
+        d.moe_branch_out_bf16 = moe_branch_out.data_ptr() if moe_branch_out is not None else None
+        check(L.lib().s14_exec_routed_and_shared_moe_then_hc_post(
+            self._h, stream if stream is not None else _torch_stream(), C.byref(d)))
+        del keep
+
+    def exec_hc_head_norm_full_logits(self, state, hc_fn, hc_scale, hc_base, norm_weight, head_weight_bf16, logits_out, *,
+                                      norm_eps: float = 1e-6, hc_eps: float = 1e-6, stream: Optional[int] = None) -> None:
+        """state bfloat16 [1, 4, hidden] -> logits_out float32 [rows of head_weight_bf16]."""
+        p = _hc_params(state, hc_fn, hc_scale, hc_base, 1, norm_eps, hc_eps)
+        check(L.lib().s14_exec_hc_head_norm_full_logits(
+            self._h, stream if stream is not None else _torch_stream(), C.byref(p), norm_weight.data_ptr(),
+            head_weight_bf16.data_ptr(), head_weight_bf16.shape[0], state.data_ptr(), logits_out.data_ptr()))
+
     def cmd_head_logits(self, x, weight_bf16, logits_out, *, n_rows: Optional[int] = None,
                         stream: Optional[int] = None) -> None:
         n_tokens = 1 if x.dim() == 1 else x.shape[0]

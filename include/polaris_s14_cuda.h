@@ -551,6 +551,32 @@ S14_API int32_t s14_cmd_hc_head_reduce(s14_ctx *ctx, void *stream, const s14_hc_
                                        float *pre);
 S14_API int32_t s14_cmd_router_hash(s14_ctx *ctx, void *stream, const s14_router_desc *desc, const int64_t *tid2eid_rows);
 
+/* The executor's two device steps (NativeS14Executor, s14_runner/src/runner.rs:86-118) as single
+ * calls on a token's BF16 state, composed of the calls above (no new arithmetic):
+ *   routed_and_shared_moe_then_hc_post: ffn_input (BF16 [hidden], the FFN site's hc_pre + RMSNorm
+ *     output) -> F32 -> the MoE layer of s14_cmd_moe_layer with the route's pages -> the branch rounded
+ *     to BF16 -> hc_post with the site's post / comb over the post-attention state -> state_out.
+ *     (The experts run this library's F32 semantics - exact sums, one rounding -, not the official
+ *     BF16 / FP8-requantised intermediate roundings of executor.py:712-743.)
+ *   hc_head_norm_full_logits (final_head.py:152-191): head reduce -> RMSNorm -> the BF16 head's
+ *     logits for n_rows vocabulary rows (the full logits, or a shard's); the caller takes the argmax
+ *     (s14_cmd_greedy_argmax), as the runner does. */
+typedef struct {
+    uint32_t hidden, inter;
+    uint32_t shared_kind;
+    const s14_token_route *route;      /* host: the token's route with its pages */
+    const uint8_t *shared_page;
+    const uint16_t *ffn_input_bf16;    /* device [hidden] */
+    const uint16_t *residual_bf16;     /* device [4, hidden]: the post-attention state */
+    const float *post, *comb;          /* device [4], [4, 4]: the FFN site's */
+    uint16_t *state_out_bf16;          /* device [4, hidden] */
+    uint16_t *moe_branch_out_bf16;     /* device [hidden], or NULL */
+} s14_exec_moe_desc;
+S14_API int32_t s14_exec_routed_and_shared_moe_then_hc_post(s14_ctx *ctx, void *stream, const s14_exec_moe_desc *desc);
+S14_API int32_t s14_exec_hc_head_norm_full_logits(s14_ctx *ctx, void *stream, const s14_hc_params *head,
+                                                  const float *norm_weight, const uint16_t *head_weight_bf16,
+                                                  uint32_t n_rows, const uint16_t *state_bf16, float *logits_out);
+
 /* LM head (local_s14_primitives/final_head.py:113-149): logits[v] = x . W[v,:]
  * for the rows [row_begin, row_begin + n_rows) of a BF16 [vocab, hidden] matrix
  * whose first stored row is row_begin (a vocabulary shard); logits_out points at

@@ -257,6 +257,23 @@ def main(reference_root: str) -> None:
     w6 = scores.gather(1, torch.from_numpy(tid2eid))
     out["rh_w"] = (w6 / w6.sum(dim=-1, keepdim=True) * 1.5).numpy()
 
+    # the final path (final_head.py:152-191: head reduce -> RMSNorm -> BF16 head) at hidden 1024, vocabulary 768
+    from fast16.research.polaris_meridian_v1.local_s14_primitives.final_head import native_final_logits
+
+    g = synth.rng(1007)
+    nfn, nsc, nba = synth.hc_params(g, 1024, head=True)
+    nx = synth.hc_streams(g, 2, 1024)
+    nnw = g.uniform(0.5, 1.5, size=1024).astype(np.float32)
+    nhw = synth.head_weight_bf16(g, 768, 1024)
+    out["nf_inputs_sha256"] = np.frombuffer(_digest(nfn, nsc, nba, nx, nnw, nhw), dtype=np.uint8)
+    head_t = torch.from_numpy(synth.bf16_bits_to_f32(nhw)).to(torch.bfloat16)
+    logits, normalized, npre = native_final_logits(
+        torch.from_numpy(nx).to(torch.bfloat16).reshape(1, 2, 4, 1024), torch.from_numpy(nfn), torch.from_numpy(nsc),
+        torch.from_numpy(nba), torch.from_numpy(nnw), head_t, full_logits=True, enforce_official_shape=False)
+    out["nf_logits"] = logits.numpy().reshape(2, 768)
+    out["nf_normalized"] = normalized.float().numpy().reshape(2, 1024)
+    out["nf_pre"] = npre.numpy().reshape(2, 4)
+
     path = os.path.join(HERE, "s14_golden.npz")
     np.savez_compressed(path, **out)
     print(path, os.path.getsize(path), "bytes;", len(out), "arrays")

@@ -160,3 +160,56 @@ def test_glue_rejects_what_it_cannot_run(ctx):
     with pytest.raises(S14Error):
         ctx.cmd_rms_norm(red, torch.ones(1024, device="cuda"), red, eps=0.0)
     torch.cuda.synchronize()
+
+
+def test_exec_hc_head_norm_full_logits(ctx, oracle, golden):
+    """The executor's final step (runner.rs:86-118, final_head.py:152-191) as one call, against the oracle's
+    composition and against native_final_logits' own output."""
+    g = synth.rng(1007)
+    fn, sc, ba = synth.hc_params(g, 1024, head=True)
+    x = synth.hc_streams(g, 2, 1024)
+    nw = g.uniform(0.5, 1.5, size=1024).astype(np.float32)
+    hw = synth.head_weight_bf16(g, 768, 1024)
+    d_hw = dev(hw.view(np.int16))
+    for t in range(2):
+        state = dev(x[t:t + 1], bf16=True)
+        logits = torch.empty(768, dtype=torch.float32, device="cuda")
+        ctx.exec_hc_head_norm_full_logits(state, dev(fn), dev(sc), dev(ba), dev(nw), d_hw, logits)
+        torch.cuda.synchronize()
+        red, _ = oracle.hc_head_reduce(bits16(state), fn, sc, ba, dtype=1)
+        normed = oracle.rms_norm(red, nw, dtype=1)
+        want = oracle.head_logits(f32_of_bits(normed[0]), hw)
+        got = logits.cpu().numpy()
+        # the head kernel carries 8 products in F32 before its double sum: a few ulps against the double-accumulated oracle
+        assert np.abs(got - want).max() <= 4e-6 * np.abs(want).max()
+        assert np.abs(got - golden["nf_logits"][t]).max() <= 2e-3 * np.abs(golden["nf_logits"][t]).max()
+
+
+def test_exec_routed_and_shared_moe_then_hc_post(ctx, oracle):
+    """The executor's MoE step as one call: BF16 FFN input -> experts -> BF16 branch -> hc_post over the
+    post-attention state, against the oracle's composition, bit for bit."""
+    from colormlm_b200.s14 import TokenRoute
+    from .test_gpu_parity import dev_page, make_layer
+
+    hidden, inter = 2048, 1024
+    g, pages, shared = make_layer(3300, hidden, inter, 8, L.PAGE_MXFP4)
+    pages_dev, shared_dev = [dev_page(p, hidden, inter) for p in pages], dev_page(shared, hidden, inter)
+    ffn_in = dev(synth.activations(g, 1, hidden)[0], bf16=True)
+    residual = dev(synth.hc_streams(g, 1, hidden)[0], bf16=True)
+    post_np = g.uniform(0.2, 1.8, size=4).astype(np.float32)
+    comb_np = g.uniform(0.05, 0.6, size=(4, 4)).astype(np.float32)
+    ids = [5, 1, 7, 0, 3, 6]
+    w = np.asarray([0.4, 0.3, 0.25, 0.2, 0.2, 0.15], np.float32)
+    route = TokenRoute(ids, w, [pages_dev[i].data_ptr() for i in ids])
+    state_out = torch.empty((4, hidden), dtype=torch.bfloat16, device="cuda")
+    branch_out = torch.empty(hidden, dtype=torch.bfloat16, device="cuda")
+    ctx.set_accumulation(L.ACCUM_PAIRWISE)
+    ctx.exec_routed_and_shared_moe_then_hc_post(ffn_in, residual, dev(post_np), dev(comb_np), route, shared_dev.data_ptr(),
+                                                L.PAGE_MXFP4, inter, state_out, branch_out)
+    torch.cuda.synchronize()
+    assert ctx.device_status() == 0
+    y = oracle.moe_layer_acc64(f32_of_bits(bits16(ffn_in)), [pages[i] for i in ids], w, shared, 0, hidden, inter)
+    branch_ref = synth.f32_to_bf16_bits(y)
+    assert np.array_equal(bits16(branch_out), branch_ref)
+    merged = oracle.hc_post(branch_ref[None], bits16(residual)[None], post_np[None], comb_np[None], dtype=1)
+    assert np.array_equal(bits16(state_out), merged[0])

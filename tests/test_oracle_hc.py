@@ -109,3 +109,24 @@ def test_hash_route_weights(oracle, golden):
         assert np.array_equal(ids, tid2eid[t].astype(np.int32))
         np.testing.assert_allclose(w, golden["rh_w"][t], rtol=2e-6, atol=0)
         assert abs(float(w.sum()) - 1.5) <= 2e-7 * 6   # executor.py:665-667 checks the sum
+
+
+def test_final_path_composition(oracle, golden):
+    """final_head.py:152-191 (head reduce -> RMSNorm -> BF16 head) composed from the oracle's pieces, against
+    native_final_logits itself."""
+    g = synth.rng(1007)
+    fn, sc, ba = synth.hc_params(g, 1024, head=True)
+    x = synth.hc_streams(g, 2, 1024)
+    nw = g.uniform(0.5, 1.5, size=1024).astype(np.float32)
+    hw = synth.head_weight_bf16(g, 768, 1024)
+    assert _digest(fn, sc, ba, x, nw, hw) == golden["nf_inputs_sha256"].tobytes()
+    red, pre = oracle.hc_head_reduce(synth.f32_to_bf16_bits(x), fn, sc, ba, dtype=1)
+    np.testing.assert_allclose(pre, golden["nf_pre"], rtol=0, atol=2e-6)
+    normed = oracle.rms_norm(red, nw, dtype=1)
+    assert (_bf16(normed) == golden["nf_normalized"]).mean() >= 0.995
+    for t in range(2):
+        logits = oracle.head_logits(_bf16(normed[t]), hw)
+        # a BF16 ulp of one normalized element moves a logit by up to 2^-8 * |x_k w_k|
+        assert np.abs(logits - golden["nf_logits"][t]).max() <= 2e-3 * np.abs(golden["nf_logits"][t]).max()
+        exact = oracle.head_logits(golden["nf_normalized"][t], hw)   # from the reference's own normalized vector
+        np.testing.assert_allclose(exact, golden["nf_logits"][t], rtol=2e-6, atol=2e-6)
