@@ -167,6 +167,12 @@ SIGNATURES = {
     "s14_cmd_moe_block": (_I32, [_VP, _VP, _VP, _P(MoeLayerDesc)]),
     "s14_cmd_routed_moe_block": (_I32, [_VP, _VP, _VP, _P(RoutedLayerDesc)]),
     "s14_block_last_counts": (_I32, [_VP, _P(_U32)]),
+    "s14_block_ep_create": (_I32, [_VP, _U32, _U32, _VP]),
+    "s14_block_ep_connect": (_I32, [_VP, _VP]),
+    "s14_block_ep_connect_local": (_I32, [_VP, _P(_VP)]),
+    "s14_block_ep_set_wait_limit": (_I32, [_VP, _U32]),
+    "s14_block_ep_disconnect": (_I32, [_VP]),
+    "s14_cmd_routed_moe_block_ep": (_I32, [_VP, _VP, _VP, _P(RoutedLayerDesc), _U32, _I32]),
     "s14_cmd_routed_moe_block_experts_ep": (_I32, [_VP, _VP, _VP, _P(RoutedLayerDesc), _U32, _U32, _U32, _VP]),
     "s14_cmd_moe_block_mix": (_I32, [_VP, _VP, _VP, _VP, _VP, _VP, _U32, _U32, _I32, _VP, _VP]),
     "s14_cmd_hc_pre": (_I32, [_VP, _VP, _P(HcParams), _VP, _VP, _VP, _VP]),

@@ -1792,12 +1792,27 @@ struct s14_block {
     cudaEvent_t staged = nullptr;                 // the staging buffer's last copy has left it
     bool stage_busy = false;
     bool residual = false;                        // y = x + moe(x)
+    // expert-parallel exchange inside the block kernels: this rank's buffer (two pair buffers, then two rows of
+    // flag words) and the ranks' buffers as mapped here
+    struct {
+        uint8_t *buf = nullptr;
+        size_t pair_bytes = 0;
+        uint32_t rank = 0, world = 0, calls = 0, wait_limit = 1u << 22;
+        uint8_t *peer[kMaxEpWorld] = {};
+        bool opened[kMaxEpWorld] = {};
+        bool connected = false;
+        unsigned int *counter = nullptr;
+    } ep;
 };
 
 static constexpr uint32_t kBlockMaxTokens = 1024;
 
 extern "C" int32_t s14_block_destroy(s14_block *blk) {
     if (!blk) return S14_OK;
+    if (blk->ep.connected)
+        return fail(S14_ERR_CONTRACT,
+                    "s14_block_destroy: the expert-parallel exchange is still connected; every rank calls "
+                    "s14_block_ep_disconnect, the ranks pass a host barrier, then the objects are destroyed");
     cudaSetDevice(blk->device);
     cudaDeviceSynchronize();
     cudaFree(blk->w.chunks);
@@ -1814,6 +1829,8 @@ extern "C" int32_t s14_block_destroy(s14_block *blk) {
     cudaFree(blk->weights);
     cudaFree(blk->pages);
     cudaFreeHost(blk->stage);
+    cudaFree(blk->ep.buf);
+    cudaFree(blk->ep.counter);
     if (blk->staged) cudaEventDestroy(blk->staged);
     delete blk;
     return S14_OK;
@@ -1988,6 +2005,136 @@ extern "C" int32_t s14_cmd_routed_moe_block_experts_ep(s14_ctx *ctx, void *strea
                                       blk->hidden, blk->inter, ctx->status, &err, 0, false, ep_rank, ep_world, pairs_out);
     ctx->last_path = S14_LAYER_PATH_TENSOR_BLOCK;
     if (err != cudaSuccess) return cuda_fail(err, "S14 MoE block launch");
+    return S14_OK;
+}
+
+// ---- expert parallel with the exchange inside the block kernels ----
+static size_t block_ep_bytes(const s14_block *blk) { return 2u * blk->ep.pair_bytes + 2u * 8u * kMaxEpWorld; }
+
+extern "C" int32_t s14_block_ep_create(s14_block *blk, uint32_t rank, uint32_t world, uint8_t *handle_out) {
+    S14_TRY
+    if (!blk) throw ContractError("s14_block_ep_create: blk is NULL");
+    if (world < 2 || world > kMaxEpWorld || rank >= world) throw ContractError("s14_block_ep_create: 2..8 ranks, rank inside the world");
+    if (blk->ep.buf) throw ContractError("s14_block_ep_create: already created for this block object");
+    CUDA_OK(cudaSetDevice(blk->device));
+    blk->ep.pair_bytes = ((size_t)blk->max_tokens * (S14_EXPERTS_PER_TOKEN + 1) * blk->hidden * sizeof(float) + 255u) & ~(size_t)255u;
+    CUDA_OK(cudaMalloc(&blk->ep.buf, block_ep_bytes(blk)));
+    CUDA_OK(cudaMemset(blk->ep.buf, 0, block_ep_bytes(blk)));
+    CUDA_OK(cudaMalloc(&blk->ep.counter, 64));
+    CUDA_OK(cudaMemset(blk->ep.counter, 0, 64));
+    CUDA_OK(cudaDeviceSynchronize());
+    blk->ep.rank = rank;
+    blk->ep.world = world;
+    blk->ep.calls = 0;
+    if (handle_out) {
+        cudaIpcMemHandle_t h;
+        static_assert(sizeof(h) == S14_EP_HANDLE_BYTES, "IPC handle size");
+        CUDA_OK(cudaIpcGetMemHandle(&h, blk->ep.buf));
+        std::memcpy(handle_out, &h, sizeof(h));
+    }
+    return S14_OK;
+    S14_CATCH
+}
+
+extern "C" int32_t s14_block_ep_connect(s14_block *blk, const uint8_t *handles) {
+    S14_TRY
+    if (!blk || !handles) throw ContractError("s14_block_ep_connect: NULL argument");
+    if (!blk->ep.buf) throw ContractError("s14_block_ep_connect: create the exchange first");
+    if (blk->ep.connected) throw ContractError("s14_block_ep_connect: already connected");
+    CUDA_OK(cudaSetDevice(blk->device));
+    for (uint32_t p = 0; p < blk->ep.world; ++p) {
+        if (p == blk->ep.rank) {
+            blk->ep.peer[p] = blk->ep.buf;
+            continue;
+        }
+        cudaIpcMemHandle_t h;
+        std::memcpy(&h, handles + (size_t)p * S14_EP_HANDLE_BYTES, sizeof(h));
+        void *base = nullptr;
+        CUDA_OK(cudaIpcOpenMemHandle(&base, h, cudaIpcMemLazyEnablePeerAccess));
+        blk->ep.peer[p] = (uint8_t *)base;
+        blk->ep.opened[p] = true;
+    }
+    blk->ep.connected = true;
+    return S14_OK;
+    S14_CATCH
+}
+
+// The ranks are block objects of this process on the same GPU (tests: every rank but the last runs with
+// wait_and_mix = 0 - it publishes and returns - so that no launch waits for a later launch of the same GPU).
+extern "C" int32_t s14_block_ep_connect_local(s14_block *blk, s14_block *const *ranks) {
+    S14_TRY
+    if (!blk || !ranks) throw ContractError("s14_block_ep_connect_local: NULL argument");
+    if (!blk->ep.buf) throw ContractError("s14_block_ep_connect_local: create the exchange first");
+    for (uint32_t p = 0; p < blk->ep.world; ++p) {
+        if (!ranks[p] || !ranks[p]->ep.buf || ranks[p]->ep.world != blk->ep.world || ranks[p]->ep.rank != p ||
+            ranks[p]->device != blk->device || ranks[p]->ep.pair_bytes != blk->ep.pair_bytes)
+            throw ContractError("s14_block_ep_connect_local: the ranks' objects must be created alike, in rank order, on this GPU");
+        blk->ep.peer[p] = ranks[p]->ep.buf;
+    }
+    blk->ep.connected = true;
+    return S14_OK;
+    S14_CATCH
+}
+
+extern "C" int32_t s14_block_ep_set_wait_limit(s14_block *blk, uint32_t polls) {
+    if (!blk || polls == 0) return fail(S14_ERR_CONTRACT, "s14_block_ep_set_wait_limit: NULL object or zero polls");
+    blk->ep.wait_limit = polls;
+    return S14_OK;
+}
+
+// Teardown as for the one-token exchange: every rank disconnects (waits for its device's work, closes its mappings),
+// the ranks pass a host barrier, then the objects are destroyed.
+extern "C" int32_t s14_block_ep_disconnect(s14_block *blk) {
+    if (!blk) return fail(S14_ERR_CONTRACT, "s14_block_ep_disconnect: blk is NULL");
+    if (!blk->ep.buf) return S14_OK;
+    CUDA_OK(cudaSetDevice(blk->device));
+    CUDA_OK(cudaDeviceSynchronize());
+    for (uint32_t p = 0; p < kMaxEpWorld; ++p) {
+        if (blk->ep.opened[p]) CUDA_OK(cudaIpcCloseMemHandle(blk->ep.peer[p]));
+        blk->ep.opened[p] = false;
+        blk->ep.peer[p] = nullptr;
+    }
+    blk->ep.connected = false;
+    return S14_OK;
+}
+
+// One call per rank and block: router, grouping of the owned experts' pairs, the two contractions - the down kernel
+// stores its rows into every rank's pair buffer and publishes the call's number -, and (wait_and_mix) the mix,
+// which waits (bounded; status 0x5508 and no result if it runs out) for every rank's number.
+extern "C" int32_t s14_cmd_routed_moe_block_ep(s14_ctx *ctx, void *stream, s14_block *blk, const s14_routed_layer_desc *desc,
+                                               uint32_t shared_owner, int32_t wait_and_mix) {
+    if (!ctx || !blk || !desc) return fail(S14_ERR_CONTRACT, "s14_cmd_routed_moe_block_ep: NULL argument");
+    if (!blk->ep.connected) return fail(S14_ERR_CONTRACT, "s14_cmd_routed_moe_block_ep: the exchange is not connected");
+    if (shared_owner >= blk->ep.world) return fail(S14_ERR_CONTRACT, "s14_cmd_routed_moe_block_ep: shared owner outside the world");
+    if (wait_and_mix && !desc->y) return fail(S14_ERR_CONTRACT, "s14_cmd_routed_moe_block_ep: y is NULL");
+    cudaStream_t st = stream_of(ctx, stream);
+    s14_router_desc rd;
+    const int32_t rc = routed_block_router(ctx, st, blk, desc, &rd, false);
+    if (rc != S14_OK) return rc;
+    const uint32_t call = ++blk->ep.calls, parity = call & 1u;
+    BlockEp ep = {};
+    for (uint32_t p = 0; p < blk->ep.world; ++p) {
+        ep.pairs_peer[p] = reinterpret_cast<float *>(blk->ep.peer[p] + parity * blk->ep.pair_bytes);
+        ep.flags_peer[p] = reinterpret_cast<unsigned long long *>(blk->ep.peer[p] + 2u * blk->ep.pair_bytes + parity * 8u * kMaxEpWorld);
+    }
+    ep.flags = ep.flags_peer[blk->ep.rank];
+    ep.counter = blk->ep.counter;
+    ep.world = blk->ep.world;
+    ep.rank = blk->ep.rank;
+    ep.call = call;
+    ep.wait_limit = blk->ep.wait_limit;
+    cudaError_t err;
+    ctx->launches += launch_moe_block(st, ctx->sm_count, blk->w, rd.x, nullptr, rd.ids_out, rd.weights_out, nullptr, desc->page_table,
+                                      shared_owner == blk->ep.rank ? desc->shared_page : nullptr, rd.n_tokens, rd.top_k, rd.n_experts,
+                                      blk->hidden, blk->inter, ctx->status, &err, 0, false, blk->ep.rank, blk->ep.world,
+                                      ep.pairs_peer[blk->ep.rank], &ep);
+    ctx->last_path = S14_LAYER_PATH_TENSOR_BLOCK;
+    if (err != cudaSuccess) return cuda_fail(err, "S14 MoE block launch");
+    if (!wait_and_mix) return S14_OK;
+    err = launch_block_mix(st, ep.pairs_peer[blk->ep.rank], rd.ids_out, rd.weights_out, rd.n_tokens, rd.top_k, desc->shared_page != nullptr,
+                           blk->residual ? rd.x : nullptr, desc->y, blk->hidden, blk->w.counts, &ep, ctx->status);
+    ctx->launches += 1;
+    if (err != cudaSuccess) return cuda_fail(err, "S14 MoE block mix launch");
     return S14_OK;
 }
 

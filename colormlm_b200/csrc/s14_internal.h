@@ -183,6 +183,20 @@ struct BlockWork {
     uint8_t *hdig, *hexp;      // the pairs' hidden values likewise
     float *d;                  // the pairs' expert outputs [pair, hidden]
 };
+// Expert-parallel exchange of the block kernels over peer memory: every rank holds two pair buffers
+// [pairs, hidden] F32 (calls alternate between them) and, per buffer, one 8-byte word per rank: the number
+// of the last call whose rows that rank has written there.  The down kernel stores the rows of the experts it
+// owns into every rank's buffer (plain stores to peer memory) and its last CTA publishes the call's number;
+// the mix waits (bounded) until every rank's word says this call.  A rank writes call s + 1 only after its own
+// mix of call s, which waited for every rank's rows of call s; so a rank that writes into a buffer for call
+// s + 2 knows that every rank has finished reading call s from it: two buffers are enough.
+struct BlockEp {
+    float *pairs_peer[kMaxEpWorld];               // the call's pair buffer of rank p, as mapped on this rank
+    unsigned long long *flags_peer[kMaxEpWorld];  // ... its flag words [world]
+    const unsigned long long *flags;              // this rank's own flag words of the call's buffer
+    unsigned int *counter;                        // arrival counter of the down kernel's CTAs (zero at rest)
+    uint32_t world, rank, call, wait_limit;
+};
 // Whether the grouped tensor-core kernels can run these sizes on the current device.
 bool moe_block_ok(int sm_count, uint32_t hidden, uint32_t inter, uint32_t n_experts, uint32_t top_k);
 size_t moe_block_max_chunks(uint32_t max_tokens);
@@ -192,12 +206,13 @@ int launch_moe_block(cudaStream_t st, int sm_count, const BlockWork &w, const fl
                      const float *weights, const uint8_t *const *pages, const uint8_t *const *page_table,
                      const uint8_t *shared_page, uint32_t n_tokens, uint32_t top_k, uint32_t n_experts, uint32_t hidden,
                      uint32_t inter, uint32_t *status, cudaError_t *err, uint32_t nt_cap = 0, bool residual = false,
-                     uint32_t ep_rank = 0, uint32_t ep_world = 1, float *pairs_out = nullptr);
+                     uint32_t ep_rank = 0, uint32_t ep_world = 1, float *pairs_out = nullptr, const BlockEp *ep = nullptr);
 // With pairs_out (expert parallel: rank ep_rank of ep_world computes the experts e with e mod world == rank) the
 // pairs' expert outputs [n_tokens * 7, hidden] go there, zero where another rank owns the expert, and no mix runs;
 // launch_block_mix mixes such a buffer once the ranks' buffers have been added up (x: the layer's input for a residual, or NULL).
 cudaError_t launch_block_mix(cudaStream_t st, const float *pairs, const int32_t *ids, const float *weights, uint32_t n_tokens,
-                             uint32_t top_k, bool has_shared, const float *x, float *y, uint32_t hidden, const uint32_t *counts);
+                             uint32_t top_k, bool has_shared, const float *x, float *y, uint32_t hidden, const uint32_t *counts,
+                             const BlockEp *ep = nullptr, uint32_t *status = nullptr);
 // Scores and routes of many tokens (s14_kernels.cu): the tokens of a tile share the router rows in
 // shared memory; one warp per token selects.  Same arithmetic as launch_router.  Returns the number
 // of kernels launched.

@@ -71,6 +71,13 @@ struct GemmArgs {
     uint8_t *hdig, *hexp;       // up: digit tiles and exponents of the pairs' hidden values
     uint32_t by_threads;        // the token tiles come by the tile threads' own copies (large blocks), else by bulk copies
     uint32_t hidden, inter, ring, stage;   // stage: bytes of a ring stage (a unit and nt_cap token tiles)
+    // Expert parallel with the exchange inside the kernel: the pairs' outputs go into every rank's buffer
+    // (plain stores to peer memory), and the last CTA to finish tells every rank that this rank's rows of
+    // call `ep_call` are there (flags[rank] of the call's parity in every rank's buffer).
+    float *out_peer[kMaxEpWorld];
+    unsigned long long *flag_peer[kMaxEpWorld];
+    unsigned int *ep_counter;   // this GPU's arrival counter, zero at rest
+    uint32_t ep_world, ep_rank, ep_call;
 };
 
 // The digit tiles and block exponents of n vectors of K elements (one CTA per vector).
@@ -450,8 +457,17 @@ k_block_gemm(const __grid_constant__ GemmArgs a, uint32_t *status) {
                     if constexpr (kDown) {
                         // row idx * 128 + `row` of the pairs' expert outputs
 #pragma unroll
-                        for (uint32_t t = 0; t < kNt; ++t)
-                            if (t < nt) a.out[(size_t)pair[t] * a.hidden + idx * 128u + row] = v[mt][t];
+                        for (uint32_t t = 0; t < kNt; ++t) {
+                            if (t < nt) {
+                                const size_t at = (size_t)pair[t] * a.hidden + idx * 128u + row;
+                                if (a.ep_world > 1u) {
+#pragma unroll 1
+                                    for (uint32_t p = 0; p < a.ep_world; ++p) a.out_peer[p][at] = v[mt][t];
+                                } else {
+                                    a.out[at] = v[mt][t];
+                                }
+                            }
+                        }
                     } else {
                         // lanes 0-63: gate of the slice's element `row`; lanes 64-127: its up projection
                         if (mt) epi_sync();  // the row tile before has been written out
@@ -592,6 +608,25 @@ k_block_gemm(const __grid_constant__ GemmArgs a, uint32_t *status) {
         asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_slot), "r"(512u) : "memory");
     }
     if (tid == 0 && abort_flag) atomicExch(status, 0x5507u);
+    if constexpr (kDown) {
+        if (a.ep_world > 1u) {
+            // every store of this CTA to the peers' buffers is ordered before the count; the last CTA of the
+            // grid publishes the call's number to every rank
+            if (warp < 4u) __threadfence_system();
+            __syncthreads();
+            if (tid == 0) {
+                __threadfence_system();
+                if (atomicAdd(a.ep_counter, 1u) == grid - 1u) {
+                    *a.ep_counter = 0u;
+                    __threadfence_system();
+                    const unsigned long long word = abort_flag ? 0ull : (unsigned long long)a.ep_call;
+#pragma unroll 1
+                    for (uint32_t p = 0; p < a.ep_world; ++p)
+                        asm volatile("st.release.sys.global.u64 [%0], %1;" ::"l"(a.flag_peer[p] + a.ep_rank), "l"(word) : "memory");
+                }
+            }
+        }
+    }
 }
 
 // y[t, n]: the ordered mix of token t (examples/s14_vulkan_numeric.rs:936-946): acc = 0; acc += w * d
@@ -600,8 +635,34 @@ k_block_gemm(const __grid_constant__ GemmArgs a, uint32_t *status) {
 __global__ void __launch_bounds__(256)
 k_block_mix(const float *__restrict__ d, const int32_t *__restrict__ ids, const float *__restrict__ weights,
             uint32_t top_k, int has_shared, float *y, uint32_t hidden, const uint32_t *__restrict__ counts,
-            const float *x, uint32_t residual) {
+            const float *x, uint32_t residual, const unsigned long long *flags, uint32_t ep_world, uint32_t ep_call,
+            uint32_t wait_limit, uint32_t *status) {
     const uint32_t n = blockIdx.x * blockDim.x + threadIdx.x, t = blockIdx.y;
+    if (flags) {
+        // expert parallel, exchange inside the kernels: every rank's rows of this call are in this rank's buffer
+        // when its flag carries the call's number (bounded wait: about a microsecond per poll)
+        __shared__ int s_ok;
+        if (threadIdx.x == 0) {
+            int ok = 1;
+            for (uint32_t p = 0; p < ep_world && ok; ++p) {
+                uint32_t tries = 0;
+                for (;;) {
+                    unsigned long long v;
+                    asm volatile("ld.acquire.sys.global.u64 %0, [%1];" : "=l"(v) : "l"(flags + p) : "memory");
+                    if (v >= (unsigned long long)ep_call) break;
+                    if (++tries > wait_limit) {
+                        ok = 0;
+                        atomicExch(status, 0x5508u);
+                        break;
+                    }
+                    __nanosleep(1000);
+                }
+            }
+            s_ok = ok;
+        }
+        __syncthreads();
+        if (!s_ok) return;
+    }
     if (n >= hidden || __ldcg(counts + 3)) return;
     const float *dt = d + (size_t)t * kPairsPerToken * hidden + n;
     float acc = 0.0f;
@@ -664,7 +725,7 @@ int launch_moe_block(cudaStream_t st, int sm_count, const BlockWork &w, const fl
                      const float *weights, const uint8_t *const *pages, const uint8_t *const *page_table,
                      const uint8_t *shared_page, uint32_t n_tokens, uint32_t top_k, uint32_t n_experts, uint32_t hidden,
                      uint32_t inter, uint32_t *status, cudaError_t *err, uint32_t nt_cap, bool residual, uint32_t ep_rank,
-                     uint32_t ep_world, float *pairs_out) {
+                     uint32_t ep_world, float *pairs_out, const BlockEp *ep) {
     // Tokens per chunk.  A small block is bound by the memory's latency: most experts have one token,
     // and short stages make the ring deeper (more page bytes in flight); the shared expert's extra
     // chunks come from the L2.  A large block wants few passes over every expert.
@@ -683,7 +744,7 @@ int launch_moe_block(cudaStream_t st, int sm_count, const BlockWork &w, const fl
     if (ep_world == 0u) ep_world = 1u;
     k_block_group<<<1, 1024, 0, st>>>(ids, pages, page_table, shared_page, n_tokens, top_k, n_experts, S / mt, RT / mt, nt_cap,
                                      w.chunks, w.counts, ep_rank, ep_world);
-    if (pairs_out) {
+    if (pairs_out && !ep) {
         // expert parallel: the pairs of the experts this rank owns; the others stay zero for the sum over the ranks
         *err = cudaMemsetAsync(pairs_out, 0, (size_t)n_tokens * kPairsPerToken * hidden * sizeof(float), st);
         if (*err != cudaSuccess) return 2;
@@ -691,6 +752,17 @@ int launch_moe_block(cudaStream_t st, int sm_count, const BlockWork &w, const fl
     const uint32_t by_threads = nt_cap > 2u ? 1u : 0u;
     GemmArgs up = {w.chunks, w.counts + 1, w.xdig, w.xexp, nullptr, w.hdig, w.hexp, by_threads, hidden, inter, ring, stage};
     GemmArgs down = {w.chunks, w.counts + 2, w.hdig, w.hexp, pairs_out ? pairs_out : w.d, nullptr, nullptr, by_threads, hidden, inter, ring, stage};
+    if (ep) {
+        // exchange inside the kernel: the owned pairs' rows into every rank's buffer of the call's parity
+        for (uint32_t p = 0; p < ep->world; ++p) {
+            down.out_peer[p] = ep->pairs_peer[p];
+            down.flag_peer[p] = ep->flags_peer[p];
+        }
+        down.ep_counter = ep->counter;
+        down.ep_world = ep->world;
+        down.ep_rank = ep->rank;
+        down.ep_call = ep->call;
+    }
     if (mt == 1u) {
         k_block_gemm<false, 1><<<sm_count, kGThreads, smem, st>>>(up, status);
         k_block_gemm<true, 1><<<sm_count, kGThreads, smem, st>>>(down, status);
@@ -703,15 +775,17 @@ int launch_moe_block(cudaStream_t st, int sm_count, const BlockWork &w, const fl
         return 4;
     }
     k_block_mix<<<dim3((hidden + 255u) / 256u, n_tokens), 256, 0, st>>>(w.d, ids, weights, top_k, shared_page != nullptr, y, hidden,
-                                                                       w.counts, x, residual ? 1u : 0u);
+                                                                       w.counts, x, residual ? 1u : 0u, nullptr, 1u, 0u, 0u, status);
     *err = cudaGetLastError();
     return 5;
 }
 
 cudaError_t launch_block_mix(cudaStream_t st, const float *pairs, const int32_t *ids, const float *weights, uint32_t n_tokens,
-                             uint32_t top_k, bool has_shared, const float *x, float *y, uint32_t hidden, const uint32_t *counts) {
+                             uint32_t top_k, bool has_shared, const float *x, float *y, uint32_t hidden, const uint32_t *counts,
+                             const BlockEp *ep, uint32_t *status) {
     k_block_mix<<<dim3((hidden + 255u) / 256u, n_tokens), 256, 0, st>>>(pairs, ids, weights, top_k, has_shared, y, hidden, counts, x,
-                                                                       x ? 1u : 0u);
+                                                                       x ? 1u : 0u, ep ? ep->flags : nullptr, ep ? ep->world : 1u,
+                                                                       ep ? ep->call : 0u, ep ? ep->wait_limit : 0u, status);
     return cudaGetLastError();
 }
 

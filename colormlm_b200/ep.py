@@ -117,6 +117,38 @@ def block_layer(blk, xs, layer_state: dict, pairs, ids, weights, ys, *, layer: i
     blk.cmd_mix(pairs, ids, weights, ys, has_shared=True, x_residual=xs if residual else None, stream=stream)
 
 
+def connect_block(blk, rank: int, world: int, group=None) -> None:
+    """Creates this rank's pair buffers of the block exchange and maps every other rank's (one process per GPU)."""
+    import torch.distributed as dist
+
+    handle = blk.ep_create(rank, world)
+    handles = [None] * world
+    dist.all_gather_object(handles, handle, group=group)
+    blk.ep_connect(handles)
+    dist.barrier(group=group)
+
+
+def disconnect_block(blk, group=None, barrier=None) -> None:
+    """The block exchange's teardown: disconnect on every rank, a host barrier, then the object may be destroyed."""
+    blk.ep_disconnect()
+    if barrier is not None:
+        barrier()
+    else:
+        import torch.distributed as dist
+
+        if dist.is_initialized():
+            dist.barrier(group=group)
+
+
+def block_layer_fused(blk, xs, layer_state: dict, ys, *, layer: int, world: int, ids=None, weights=None,
+                      stream: Optional[int] = None) -> None:
+    """``block_layer`` with the exchange inside the kernels: one call per rank, no collective; the w2 kernel stores the
+    rows of the experts this rank owns into every rank's pair buffer over NVLink, the mix waits (bounded) for every
+    rank's rows.  ys is bit-identical to the single-GPU block on every rank."""
+    blk.cmd_routed_moe_block_ep(xs, layer_state["wr"], layer_state["bias"], layer_state["table"], layer_state["shared"], ys,
+                                ids, weights, shared_owner=shared_owner(layer, world), stream=stream)
+
+
 # ---- vocabulary-sharded LM head ---------------------------------------------------------------
 # The head weight [vocab, hidden] BF16 is split by rows: rank r holds rows [vocab r / G, vocab (r+1) / G)
 # (final_head.py:113-149 computes all rows on one device; the runner's contract wants the full logits,

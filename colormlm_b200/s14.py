@@ -550,6 +550,43 @@ class MoeBlock:
             self._ctx.handle, stream if stream is not None else _torch_stream(), self._h, C.byref(d), ep_rank, ep_world,
             shared_owner, pairs_out.data_ptr()))
 
+    # ---- expert parallel with the exchange inside the block kernels ----
+    def ep_create(self, rank: int, world: int) -> bytes:
+        handle = (C.c_uint8 * S14Context.EP_HANDLE_BYTES)()
+        check(L.lib().s14_block_ep_create(self._h, rank, world, C.cast(handle, C.c_void_p)))
+        return bytes(handle)
+
+    def ep_connect(self, handles) -> None:
+        blob = b"".join(handles)
+        buf = (C.c_uint8 * len(blob)).from_buffer_copy(blob)
+        check(L.lib().s14_block_ep_connect(self._h, C.cast(buf, C.c_void_p)))
+
+    def ep_connect_local(self, ranks) -> None:
+        arr = (C.c_void_p * len(ranks))(*[r._h for r in ranks])
+        check(L.lib().s14_block_ep_connect_local(self._h, arr))
+
+    def ep_set_wait_limit(self, polls: int) -> None:
+        check(L.lib().s14_block_ep_set_wait_limit(self._h, polls))
+
+    def ep_disconnect(self) -> None:
+        check(L.lib().s14_block_ep_disconnect(self._h))
+
+    def cmd_routed_moe_block_ep(self, x, wr_bf16, bias, page_table, shared_page: Optional[int], y, ids_out=None,
+                                weights_out=None, *, shared_owner: int, wait_and_mix: bool = True,
+                                score_fn: int = L.SCORE_SIGMOID, top_k: int = 6, route_scale: float = 1.0,
+                                stream: Optional[int] = None) -> None:
+        """One call per rank: the owned experts' rows go into every rank's pair buffer inside the w2 kernel, the mix waits
+        for every rank's rows (see the header)."""
+        d = L.RoutedLayerDesc()
+        d.router = _router_desc(x, wr_bf16, bias, ids_out, weights_out, score_fn, top_k, route_scale)
+        d.inter = self.inter
+        d.shared_kind = L.PAGE_MXFP4
+        d.page_table = page_table.data_ptr()
+        d.shared_page = shared_page
+        d.y = y.data_ptr() if y is not None else None
+        check(L.lib().s14_cmd_routed_moe_block_ep(self._ctx.handle, stream if stream is not None else _torch_stream(), self._h,
+                                                  C.byref(d), shared_owner, 1 if wait_and_mix else 0))
+
     def cmd_mix(self, pairs, ids, weights, y, *, has_shared: bool = True, x_residual=None,
                 stream: Optional[int] = None) -> None:
         """The ordered mix of every token from a pairs buffer (after the ranks' buffers were added up)."""
@@ -570,6 +607,9 @@ class MoeBlock:
 
     def close(self) -> None:
         if getattr(self, "_h", None):
+            # a connected exchange is closed here (the process is leaving); ranks that go on after this one
+            # follow the order of the header: disconnect everywhere, a host barrier, then destroy
+            L.lib().s14_block_ep_disconnect(self._h)
             check(L.lib().s14_block_destroy(self._h))
             self._h = None
 

@@ -508,6 +508,26 @@ S14_API int32_t s14_cmd_routed_moe_block_experts_ep(s14_ctx *ctx, void *stream, 
 S14_API int32_t s14_cmd_moe_block_mix(s14_ctx *ctx, void *stream, s14_block *blk, const float *pairs, const int32_t *ids,
                                       const float *weights, uint32_t n_tokens, uint32_t top_k, int32_t has_shared,
                                       const float *x_residual, float *y);
+/* The same partition with the exchange INSIDE the block kernels (no collective call): every rank owns
+ * two pair buffers [max_tokens * 7, hidden] F32 (calls alternate between them) that the other ranks
+ * map (CUDA IPC); the w2 kernel stores the rows of the experts it owns into EVERY rank's buffer (plain
+ * stores to peer memory over NVLink) and its last CTA publishes the call's number to every rank (one
+ * 8-byte word per rank and buffer); the mix waits - bounded, about a microsecond per poll, default 2^22
+ * polls; a wait that runs out sets the device status word 0x5508 and writes no y - until every rank's
+ * word carries this call's number.  A rank writes call s + 1 only after its own mix of call s, which
+ * waited for every rank, so two buffers are enough.  Every rank issues the same sequence of calls; y
+ * is bit-identical to the single-GPU block on every rank.
+ *   create / connect / connect_local / disconnect: as s14_ep_exchange_* (connect_local: the ranks are
+ *   block objects of this process on one GPU; tests run every rank but the last with wait_and_mix = 0).
+ *   Teardown: every rank s14_block_ep_disconnect, a host barrier, then s14_block_destroy (which refuses
+ *   while connected). */
+S14_API int32_t s14_block_ep_create(s14_block *blk, uint32_t rank, uint32_t world, uint8_t *handle_out);
+S14_API int32_t s14_block_ep_connect(s14_block *blk, const uint8_t *handles);
+S14_API int32_t s14_block_ep_connect_local(s14_block *blk, s14_block *const *ranks);
+S14_API int32_t s14_block_ep_set_wait_limit(s14_block *blk, uint32_t polls);
+S14_API int32_t s14_block_ep_disconnect(s14_block *blk);
+S14_API int32_t s14_cmd_routed_moe_block_ep(s14_ctx *ctx, void *stream, s14_block *blk, const s14_routed_layer_desc *desc,
+                                            uint32_t shared_owner, int32_t wait_and_mix);
 /* After the stream is synchronised: the last call's number of chunks, up items, down items, and 1 if
  * an expert id was outside the table (the call then wrote no result). */
 S14_API int32_t s14_block_last_counts(s14_block *blk, uint32_t counts_out[4]);

@@ -215,6 +215,57 @@ def test_block_expert_parallel_ranks_add_up_to_the_single_gpu_block(ctx, world):
         blk.close()
 
 
+@pytest.mark.parametrize("world", [2, 4])
+def test_block_exchange_inside_the_kernels(ctx, world):
+    """The ranks as block objects on this GPU, connected to one another: ranks 0 .. G-2 publish their rows into every
+    rank's pair buffer and return, the last rank waits for all of them and mixes; several calls in a row (the
+    two buffers alternate) with different tokens; the result is the single-GPU block's, bit for bit."""
+    from colormlm_b200 import ep
+
+    hidden, inter, n_experts, n_tokens = 2048, 1024, 32, 20
+    g, pages, shared = make_layer(1700 + world, hidden, inter, n_experts, L.PAGE_MXFP4)
+    wr, bias = dev(synth.router_weight_bf16(g, n_experts, hidden)), dev(synth.router_bias(g, n_experts))
+    pages_dev, shared_dev = [dev_page(p, hidden, inter) for p in pages], dev_page(shared, hidden, inter)
+    table = torch.tensor([p.data_ptr() for p in pages_dev], dtype=torch.int64, device="cuda")
+    single = MoeBlock(ctx, hidden, inter, 32)
+    ranks = [MoeBlock(ctx, hidden, inter, 32) for _ in range(world)]
+    try:
+        for r, b in enumerate(ranks):
+            b.ep_create(r, world)
+        for b in ranks:
+            b.ep_connect_local(ranks)
+            b.ep_set_wait_limit(1 << 12)
+        for call in range(3):
+            dx = dev(synth.activations(g, n_tokens, hidden))
+            want = torch.full_like(dx, float("nan"))
+            single.cmd_routed_moe_block(dx, wr, bias, table, shared_dev.data_ptr(), want)
+            got = torch.full_like(dx, float("nan"))
+            for r, b in enumerate(ranks):
+                last = r == world - 1
+                b.cmd_routed_moe_block_ep(dx, wr, bias, table, shared_dev.data_ptr(), got if last else None,
+                                          shared_owner=ep.shared_owner(call, world), wait_and_mix=last)
+            torch.cuda.synchronize()
+            assert ctx.device_status() == 0
+            assert np.array_equal(got.cpu().numpy().view(np.uint32), want.cpu().numpy().view(np.uint32)), call
+        # a rank whose peers never publish does not hang: the wait runs out, the status says so, the context goes on
+        lonely = ranks[world - 1]
+        dx = dev(synth.activations(g, n_tokens, hidden))
+        got = torch.full_like(dx, float("nan"))
+        lonely.ep_set_wait_limit(200)
+        lonely.cmd_routed_moe_block_ep(dx, wr, bias, table, shared_dev.data_ptr(), got, shared_owner=0, wait_and_mix=True)
+        torch.cuda.synchronize()
+        assert ctx.device_status() == 0x5508
+        assert torch.isnan(got).all()
+        single.cmd_routed_moe_block(dx, wr, bias, table, shared_dev.data_ptr(), got)
+        torch.cuda.synchronize()
+        assert ctx.device_status() == 0 and not torch.isnan(got).any()
+    finally:
+        for b in ranks:
+            b.ep_disconnect()
+        for b in ranks + [single]:
+            b.close()
+
+
 def test_block_with_residual_in_place(ctx):
     """y = x + moe(x), written over x: the step of a stack of layers."""
     hidden, inter, n_experts, n_tokens = 2048, 1024, 16, 9
