@@ -1054,9 +1054,16 @@ def run_prefill_ep(args, torch, dist, L, ep, S14Context, rank: int, world: int, 
     ids = torch.empty((n_tok, TOP_K), dtype=torch.int32, device="cuda")
     wts = torch.empty((n_tok, TOP_K), dtype=torch.float32, device="cuda")
     blk = MoeBlock(ctx, HIDDEN, INTER, n_tok)
+    peer = args.exchange == "peer"
+    if peer:
+        ep.connect_block(blk, rank, world)
+        blk.ep_set_wait_limit(1 << 16)   # a rank that waits longer than about 0.1 s for a peer gives the call up (status 0x5508)
 
     def step(i):
-        ep.block_layer(blk, x, states[i % 2], pairs, ids, wts, y, layer=i % 2, rank=rank, world=world)
+        if peer:
+            ep.block_layer_fused(blk, x, states[i % 2], y, layer=i % 2, world=world, ids=ids, weights=wts)
+        else:
+            ep.block_layer(blk, x, states[i % 2], pairs, ids, wts, y, layer=i % 2, rank=rank, world=world)
 
     for i in range(max(3, args.warmup // 4)):
         step(i)
@@ -1106,8 +1113,11 @@ def run_prefill_ep(args, torch, dist, L, ep, S14Context, rank: int, world: int, 
                 "steps": steps, "warmup": args.warmup, "ms_per_step": ms / steps, "higher_is_better": True, "scaling": "strong",
                 "vs_baseline": None, "dtype": "f32", "data": "synthetic",
                 "config": {"workload": f"{n_tok}-token prefill through one layer, expert parallel over {world} GPUs: tokens on every "
-                                       "rank, experts sharded, grouped block path per rank, one NCCL all-reduce of the pair "
-                                       "buffers, mix on every rank",
+                                       "rank, experts sharded, grouped block path per rank, " +
+                                       ("the w2 kernel stores the owned rows into every rank's pair buffer over NVLink, the mix "
+                                        "waits for every rank's rows (no collective call)" if peer else
+                                        "one NCCL all-reduce of the pair buffers, mix on every rank"),
+                           "exchange": args.exchange,
                            "bench_workload": "prefill", "l2": "inputs larger than L2: two layers of pages alternate",
                            "launch": "eager launches; CUDA events between barriers, max over ranks"},
                 "repeats": {"count": len(ms_all), "region_ms_median": ms, "region_ms_min": float(np.min(ms_all)),
@@ -1121,9 +1131,12 @@ def run_prefill_ep(args, torch, dist, L, ep, S14Context, rank: int, world: int, 
                 "exchange_bytes_per_step": int(pairs.numel() * 4)}
         print(json.dumps(line), flush=True)
     dist.barrier()
+    if peer:
+        ep.disconnect_block(blk)
     blk.close()
     ctx.close()
-    dist.destroy_process_group()
+    sys.stdout.flush()
+    os._exit(0)   # as the layer workload: NCCL's communicator teardown took minutes on this pool
 
 
 def run_small_workload(args, workload, torch, L, synth, S14Context, TokenRoute) -> None:
