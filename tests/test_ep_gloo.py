@@ -174,3 +174,92 @@ def test_verify_block_is_one_expert_parallel_step_per_token():
         assert (wr, bias, table, shared, inter) == ("WR", "B", "T", 77, 2048)
         assert kw["shared_owner"] == ep.shared_owner(5, 4) and kw["stream"] == 9
         assert kw["ids_out"].data_ptr() == ids[t].data_ptr() and kw["weights_out"].data_ptr() == wts[t].data_ptr()
+
+
+def _block_worker(rank: int, world: int, port: int, out_dir: str) -> None:
+    """ep.block_layer's host side with a stand-in for the block object: the rank fills the pair rows of the experts
+    it owns from the CPU oracle (zeros elsewhere), the all-reduce adds the ranks' buffers up, every rank mixes."""
+    sys.path.insert(0, ROOT)
+    os.environ["MASTER_ADDR"] = "127.0.0.1"
+    os.environ["MASTER_PORT"] = str(port)
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    from colormlm_b200 import ep, synth
+    from oracle import s14_oracle as oracle
+
+    hidden, inter, n_experts, layer, n_tok = 1024, 1024, 16, 3, 5
+    g = synth.rng(2469)
+    pages = [synth.mxfp4_expert_page(g, hidden, inter) for _ in range(n_experts)]
+    shared = synth.mxfp4_expert_page(g, hidden, inter)
+    wr, bias = synth.router_weight_bf16(g, n_experts, hidden), synth.router_bias(g, n_experts)
+    xs_np = synth.activations(g, n_tok, hidden)
+
+    class Block:
+        """What MoeBlock does for ep.block_layer, on the CPU oracle."""
+
+        def cmd_routed_moe_block_experts_ep(self, xs, wr_, bias_, table, shared_page, pairs, ids, weights, *, ep_rank, ep_world,
+                                            shared_owner, stream=None):
+            pairs.zero_()
+            for t in range(n_tok):
+                rid, rw, _, _ = oracle.router(xs[t].numpy(), wr, bias, 0, 6, 1.0)
+                ids[t] = torch.from_numpy(rid)
+                weights[t] = torch.from_numpy(rw)
+                for m, e in enumerate(rid.tolist()):
+                    if ep.expert_owner(e, ep_world) == ep_rank:
+                        pairs[t * 7 + m] = torch.from_numpy(oracle.expert_chain_mxfp4(xs[t].numpy(), pages[e], hidden, inter, 1.0)[1])
+                if shared_owner == ep_rank:
+                    pairs[t * 7 + 6] = torch.from_numpy(oracle.expert_chain_mxfp4(xs[t].numpy(), shared, hidden, inter, 1.0)[1])
+
+        def cmd_mix(self, pairs, ids, weights, ys, *, has_shared=True, x_residual=None, stream=None):
+            for t in range(n_tok):
+                acc = np.zeros(hidden, np.float32)
+                for m in range(6):
+                    acc = acc + weights[t, m].numpy() * pairs[t * 7 + m].numpy()
+                acc = acc + pairs[t * 7 + 6].numpy()
+                ys[t] = torch.from_numpy(acc if x_residual is None else (x_residual[t].numpy() + acc).astype(np.float32))
+
+    xs = torch.from_numpy(xs_np)
+    pairs = torch.full((n_tok * 7, hidden), float("nan"))
+    ids, wts = torch.zeros((n_tok, 6), dtype=torch.int32), torch.zeros((n_tok, 6))
+    ys = torch.zeros((n_tok, hidden))
+    ep.block_layer(Block(), xs, {"wr": None, "bias": None, "table": None, "shared": 1}, pairs, ids, wts, ys, layer=layer,
+                   rank=rank, world=world)
+    ok = True
+    for t in range(n_tok):
+        rid, rw, _, _ = oracle.router(xs_np[t], wr, bias, 0, 6, 1.0)
+        want = oracle.moe_layer(xs_np[t], [pages[e] for e in rid], rw, shared, 0, hidden, inter)
+        ok = ok and np.array_equal(ys[t].numpy().view(np.uint32), want.view(np.uint32))
+    with open(os.path.join(out_dir, f"rank{rank}.txt"), "w") as f:
+        f.write(f"{int(ok)}\n")
+    dist.barrier()
+    dist.destroy_process_group()
+
+
+@pytest.mark.parametrize("world", [2])
+def test_two_rank_block_combine_matches_the_single_rank_layer(tmp_path, world):
+    port = 29500 + ((os.getpid() + 13) % 2000)
+    mp.spawn(_block_worker, args=(world, port, str(tmp_path)), nprocs=world, join=True)
+    for r in range(world):
+        assert open(tmp_path / f"rank{r}.txt").read().strip() == "1"
+
+
+def test_block_exchange_calls_and_teardown_order():
+    """ep.block_layer_fused is one call per rank with the layer's shared-expert owner; ep.disconnect_block disconnects
+    before the barrier (the object is destroyed only afterwards, by its owner)."""
+    sys.path.insert(0, ROOT)
+    from colormlm_b200 import ep
+
+    log = []
+
+    class Block:
+        def cmd_routed_moe_block_ep(self, xs, wr, bias, table, shared, ys, ids, weights, **kw):
+            log.append(("call", xs, ys, wr, bias, table, shared, ids, weights, kw))
+
+        def ep_disconnect(self):
+            log.append(("disconnect",))
+
+    state = {"wr": "WR", "bias": "B", "table": "T", "shared": 5}
+    ep.block_layer_fused(Block(), "X", state, "Y", layer=6, world=4, ids="I", weights="W", stream=3)
+    assert log[0][:9] == ("call", "X", "Y", "WR", "B", "T", 5, "I", "W")
+    assert log[0][9] == {"shared_owner": ep.shared_owner(6, 4), "stream": 3}
+    ep.disconnect_block(Block(), barrier=lambda: log.append(("barrier",)))
+    assert [e[0] for e in log[1:]] == ["disconnect", "barrier"]
