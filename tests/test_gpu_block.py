@@ -107,6 +107,27 @@ def test_block_at_the_other_sizes(ctx, oracle, hidden, inter):
         blk.close()
 
 
+def test_block_sweep_of_block_sizes_against_the_one_token_kernel(ctx):
+    """Block sizes around every boundary of the chunking (1, 2, 6, 7, 12, 13 tokens; 33 and 64 with experts of
+    many chunks), ragged routes, few experts so that groups are large: every token equals its own one-token call
+    (which the other tests pin to the oracle)."""
+    hidden, inter, n_experts = 2048, 1024, 10
+    g, pages, shared = make_layer(1800, hidden, inter, n_experts, L.PAGE_MXFP4)
+    pages_dev, shared_dev = [dev_page(p, hidden, inter) for p in pages], dev_page(shared, hidden, inter)
+    blk = MoeBlock(ctx, hidden, inter, 64)
+    ctx.set_accumulation(L.ACCUM_PAIRWISE)
+    try:
+        for n_tokens in (1, 2, 6, 7, 12, 13, 33, 64):
+            x = synth.activations(g, n_tokens, hidden)
+            routes = random_routes(g, n_tokens, n_experts, ragged=True)
+            y = run_block(ctx, blk, x, pages_dev, shared_dev, routes)
+            for t in range(n_tokens):
+                single = run_layer(ctx, x[t:t + 1], pages_dev, shared_dev, [routes[t]], L.PAGE_MXFP4, hidden, inter)[0]
+                assert np.array_equal(single.view(np.uint32), y[t].view(np.uint32)), (n_tokens, t)
+    finally:
+        blk.close()
+
+
 def test_block_at_the_benchmark_shape(ctx, oracle):
     """4096 x 2048, 48 experts.  A verify block of 8 tokens against the oracle, bit for bit; 40 tokens
     (every expert several tokens, the shared expert seven chunks) against every token's own one-token
