@@ -234,16 +234,16 @@ def _note(msg: str) -> None:
         print(f"[bench rank {os.environ.get('RANK', '0')}] {msg}", file=sys.stderr, flush=True)
 
 
-def resident_layers(torch, n_layers: int, rank: int, world: int):
+def resident_layers(torch, n_layers: int, rank: int, world: int, shared_everywhere: bool = False):
     """The pages this rank owns (expert e on rank e mod world, the shared expert of layer l on rank
-    l mod world), router weights and page tables, all on the device."""
+    l mod world, or on every rank), router weights and page tables, all on the device."""
     from colormlm_b200 import ep, synth
 
     writer = synth.HashedPageWriter(torch, HIDDEN, INTER)
     layers = []
     for layer in range(n_layers):
         owned = ep.owned_experts(rank, world, N_EXPERTS)
-        has_shared = ep.shared_owner(layer, world) == rank
+        has_shared = shared_everywhere or ep.shared_owner(layer, world) == rank
         pages = torch.empty((len(owned) + (1 if has_shared else 0), PAGE_BYTES), dtype=torch.uint8, device="cuda")
         for slot, e in enumerate(owned):
             writer.fill(pages[slot], layer, e)
@@ -1040,7 +1040,8 @@ def run_prefill_ep(args, torch, dist, L, ep, S14Context, rank: int, world: int, 
     n_tok = max(1, min(1024, args.tokens if args.tokens > 8 else PREFILL_TOKENS))
     ctx = S14Context(local_rank)
     ctx.set_accumulation(L.ACCUM_PAIRWISE)
-    layers = resident_layers(torch, 2, rank, world)
+    by_token = args.exchange == "peer" and not args.shared_on_owner
+    layers = resident_layers(torch, 2, rank, world, shared_everywhere=by_token)
     states = []
     for ly in layers:
         st_ = dict(ly)
@@ -1061,7 +1062,7 @@ def run_prefill_ep(args, torch, dist, L, ep, S14Context, rank: int, world: int, 
 
     def step(i):
         if peer:
-            ep.block_layer_fused(blk, x, states[i % 2], y, layer=i % 2, world=world, ids=ids, weights=wts)
+            ep.block_layer_fused(blk, x, states[i % 2], y, layer=i % 2, world=world, ids=ids, weights=wts, shared_by_token=by_token)
         else:
             ep.block_layer(blk, x, states[i % 2], pairs, ids, wts, y, layer=i % 2, rank=rank, world=world)
 
@@ -1118,6 +1119,8 @@ def run_prefill_ep(args, torch, dist, L, ep, S14Context, rank: int, world: int, 
                                         "waits for every rank's rows (no collective call)" if peer else
                                         "one NCCL all-reduce of the pair buffers, mix on every rank"),
                            "exchange": args.exchange,
+                           "shared_expert": ("its page on every rank, rank r takes the tokens t with t mod world == r" if by_token
+                                             else "on the rank layer mod world"),
                            "bench_workload": "prefill", "l2": "inputs larger than L2: two layers of pages alternate",
                            "launch": "eager launches; CUDA events between barriers, max over ranks"},
                 "repeats": {"count": len(ms_all), "region_ms_median": ms, "region_ms_min": float(np.min(ms_all)),
@@ -1404,6 +1407,8 @@ def main() -> None:
     ap.add_argument("--accum", default="pairwise", choices=["pairwise", "reference"])
     ap.add_argument("--exchange", default="peer", choices=["peer", "nccl"],
                     help="several GPUs: down vectors exchanged inside the layer kernel over peer memory, or by NCCL all-reduce")
+    ap.add_argument("--shared-on-owner", action="store_true",
+                    help="prefill on several GPUs: the shared expert on one rank (layer mod world) instead of dealt by token")
     ap.add_argument("--repeats", type=int, default=50, help="timed regions of --steps steps; the median is reported")
     ap.add_argument("--cpu-steps", type=int, default=40)
     ap.add_argument("--no-cpu-baseline", action="store_true")

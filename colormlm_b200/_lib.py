@@ -23,6 +23,7 @@ LAYER_PATH_TENSOR, LAYER_PATH_TENSOR_PER_TOKEN, LAYER_PATH_TENSOR_STACK, LAYER_P
 LAYER_PATH_ROUTER_KERNEL = 0x100
 LAYER_PATH_TENSOR_BLOCK = 6
 STREAM_F32, STREAM_BF16 = 0, 1
+EP_SHARED_BY_TOKEN = 0xFFFFFFFF
 SCORE_SIGMOID, SCORE_SQRT_SOFTPLUS = 0, 1
 SCALE_UE8M0, SCALE_F32 = 0, 1
 PROFILE_S14_TOP6, PROFILE_FULL_DEPTH43_NATIVE_TOP6 = 0, 1

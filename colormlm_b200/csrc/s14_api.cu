@@ -1993,7 +1993,8 @@ extern "C" int32_t s14_cmd_routed_moe_block_experts_ep(s14_ctx *ctx, void *strea
                                                        const s14_routed_layer_desc *desc, uint32_t ep_rank, uint32_t ep_world,
                                                        uint32_t shared_owner, float *pairs_out) {
     if (!ctx || !blk || !desc || !pairs_out) return fail(S14_ERR_CONTRACT, "s14_cmd_routed_moe_block_experts_ep: NULL argument");
-    if (ep_world == 0 || ep_world > kMaxEpWorld || ep_rank >= ep_world || shared_owner >= ep_world)
+    const bool by_token = shared_owner == S14_EP_SHARED_BY_TOKEN;
+    if (ep_world == 0 || ep_world > kMaxEpWorld || ep_rank >= ep_world || (!by_token && shared_owner >= ep_world))
         return fail(S14_ERR_CONTRACT, "s14_cmd_routed_moe_block_experts_ep: rank or shared owner outside the world (1..8 ranks)");
     cudaStream_t st = stream_of(ctx, stream);
     s14_router_desc rd;
@@ -2001,8 +2002,9 @@ extern "C" int32_t s14_cmd_routed_moe_block_experts_ep(s14_ctx *ctx, void *strea
     if (rc != S14_OK) return rc;
     cudaError_t err;
     ctx->launches += launch_moe_block(st, ctx->sm_count, blk->w, rd.x, nullptr, rd.ids_out, rd.weights_out, nullptr, desc->page_table,
-                                      shared_owner == ep_rank ? desc->shared_page : nullptr, rd.n_tokens, rd.top_k, rd.n_experts,
-                                      blk->hidden, blk->inter, ctx->status, &err, 0, false, ep_rank, ep_world, pairs_out);
+                                      (by_token || shared_owner == ep_rank) ? desc->shared_page : nullptr, rd.n_tokens, rd.top_k,
+                                      rd.n_experts, blk->hidden, blk->inter, ctx->status, &err, 0, false, ep_rank, ep_world, pairs_out,
+                                      nullptr, by_token);
     ctx->last_path = S14_LAYER_PATH_TENSOR_BLOCK;
     if (err != cudaSuccess) return cuda_fail(err, "S14 MoE block launch");
     return S14_OK;
@@ -2105,7 +2107,9 @@ extern "C" int32_t s14_cmd_routed_moe_block_ep(s14_ctx *ctx, void *stream, s14_b
                                                uint32_t shared_owner, int32_t wait_and_mix) {
     if (!ctx || !blk || !desc) return fail(S14_ERR_CONTRACT, "s14_cmd_routed_moe_block_ep: NULL argument");
     if (!blk->ep.connected) return fail(S14_ERR_CONTRACT, "s14_cmd_routed_moe_block_ep: the exchange is not connected");
-    if (shared_owner >= blk->ep.world) return fail(S14_ERR_CONTRACT, "s14_cmd_routed_moe_block_ep: shared owner outside the world");
+    const bool by_token = shared_owner == S14_EP_SHARED_BY_TOKEN;
+    if (!by_token && shared_owner >= blk->ep.world)
+        return fail(S14_ERR_CONTRACT, "s14_cmd_routed_moe_block_ep: shared owner outside the world");
     if (wait_and_mix && !desc->y) return fail(S14_ERR_CONTRACT, "s14_cmd_routed_moe_block_ep: y is NULL");
     cudaStream_t st = stream_of(ctx, stream);
     s14_router_desc rd;
@@ -2125,9 +2129,9 @@ extern "C" int32_t s14_cmd_routed_moe_block_ep(s14_ctx *ctx, void *stream, s14_b
     ep.wait_limit = blk->ep.wait_limit;
     cudaError_t err;
     ctx->launches += launch_moe_block(st, ctx->sm_count, blk->w, rd.x, nullptr, rd.ids_out, rd.weights_out, nullptr, desc->page_table,
-                                      shared_owner == blk->ep.rank ? desc->shared_page : nullptr, rd.n_tokens, rd.top_k, rd.n_experts,
-                                      blk->hidden, blk->inter, ctx->status, &err, 0, false, blk->ep.rank, blk->ep.world,
-                                      ep.pairs_peer[blk->ep.rank], &ep);
+                                      (by_token || shared_owner == blk->ep.rank) ? desc->shared_page : nullptr, rd.n_tokens, rd.top_k,
+                                      rd.n_experts, blk->hidden, blk->inter, ctx->status, &err, 0, false, blk->ep.rank, blk->ep.world,
+                                      ep.pairs_peer[blk->ep.rank], &ep, by_token);
     ctx->last_path = S14_LAYER_PATH_TENSOR_BLOCK;
     if (err != cudaSuccess) return cuda_fail(err, "S14 MoE block launch");
     if (!wait_and_mix) return S14_OK;

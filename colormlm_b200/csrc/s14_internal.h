@@ -206,7 +206,8 @@ int launch_moe_block(cudaStream_t st, int sm_count, const BlockWork &w, const fl
                      const float *weights, const uint8_t *const *pages, const uint8_t *const *page_table,
                      const uint8_t *shared_page, uint32_t n_tokens, uint32_t top_k, uint32_t n_experts, uint32_t hidden,
                      uint32_t inter, uint32_t *status, cudaError_t *err, uint32_t nt_cap = 0, bool residual = false,
-                     uint32_t ep_rank = 0, uint32_t ep_world = 1, float *pairs_out = nullptr, const BlockEp *ep = nullptr);
+                     uint32_t ep_rank = 0, uint32_t ep_world = 1, float *pairs_out = nullptr, const BlockEp *ep = nullptr,
+                     bool shared_by_token = false);
 // With pairs_out (expert parallel: rank ep_rank of ep_world computes the experts e with e mod world == rank) the
 // pairs' expert outputs [n_tokens * 7, hidden] go there, zero where another rank owns the expert, and no mix runs;
 // launch_block_mix mixes such a buffer once the ranks' buffers have been added up (x: the layer's input for a residual, or NULL).

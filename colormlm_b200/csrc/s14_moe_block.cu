@@ -102,7 +102,7 @@ __global__ void __launch_bounds__(1024)
 k_block_group(const int32_t *__restrict__ ids, const uint8_t *const *__restrict__ pages,
               const uint8_t *const *__restrict__ page_table, const uint8_t *shared_page, uint32_t T, uint32_t top_k,
               uint32_t n_experts, uint32_t S, uint32_t RT, uint32_t nt_cap, BlockChunk *__restrict__ chunks,
-              uint32_t *__restrict__ counts, uint32_t ep_rank, uint32_t ep_world) {
+              uint32_t *__restrict__ counts, uint32_t ep_rank, uint32_t ep_world, uint32_t shared_by_token) {
     constexpr uint32_t kG = S14_N_ROUTED_EXPERTS + 1;
     __shared__ uint32_t cnt[kG], fill[kG], chunk0[kG + 1];
     __shared__ unsigned long long gpage[kG];
@@ -121,7 +121,10 @@ k_block_group(const int32_t *__restrict__ ids, const uint8_t *const *__restrict_
         if (e >= (int32_t)n_experts) bad = 1u;
         else if (e >= 0 && (uint32_t)e % ep_world == ep_rank) atomicAdd(&cnt[1 + e], 1u);  // expert parallel: the experts this rank owns
     }
-    if (tid == 0 && shared_page) cnt[0] = T;
+    // the shared expert's members: every token; expert parallel with the shared page on every rank: the tokens
+    // t with t mod world == rank (its work is a fifth of a large block's: on one rank it would bound the scaling)
+    const uint32_t sh_step = shared_by_token ? ep_world : 1u, sh_first = shared_by_token ? ep_rank : 0u;
+    if (tid == 0 && shared_page) cnt[0] = T > sh_first ? (T - sh_first + sh_step - 1u) / sh_step : 0u;
     __syncthreads();
     if (tid < 32u) {
         // exclusive scan of the groups' chunk counts: nine groups per lane
@@ -168,10 +171,11 @@ k_block_group(const int32_t *__restrict__ ids, const uint8_t *const *__restrict_
         ch->pair[k % nt_cap] = t * kPairsPerToken + m;
     }
     if (shared_page) {
-        for (uint32_t t = tid; t < T; t += blockDim.x) {
-            BlockChunk *ch = chunks + chunk0[0] + t / nt_cap;
-            ch->tok[t % nt_cap] = t;
-            ch->pair[t % nt_cap] = t * kPairsPerToken + S14_EXPERTS_PER_TOKEN;
+        for (uint32_t k = tid; sh_first + k * sh_step < T; k += blockDim.x) {
+            const uint32_t t = sh_first + k * sh_step;
+            BlockChunk *ch = chunks + chunk0[0] + k / nt_cap;
+            ch->tok[k % nt_cap] = t;
+            ch->pair[k % nt_cap] = t * kPairsPerToken + S14_EXPERTS_PER_TOKEN;
         }
     }
     __syncthreads();
@@ -725,7 +729,7 @@ int launch_moe_block(cudaStream_t st, int sm_count, const BlockWork &w, const fl
                      const float *weights, const uint8_t *const *pages, const uint8_t *const *page_table,
                      const uint8_t *shared_page, uint32_t n_tokens, uint32_t top_k, uint32_t n_experts, uint32_t hidden,
                      uint32_t inter, uint32_t *status, cudaError_t *err, uint32_t nt_cap, bool residual, uint32_t ep_rank,
-                     uint32_t ep_world, float *pairs_out, const BlockEp *ep) {
+                     uint32_t ep_world, float *pairs_out, const BlockEp *ep, bool shared_by_token) {
     // Tokens per chunk.  A small block is bound by the memory's latency: most experts have one token,
     // and short stages make the ring deeper (more page bytes in flight); the shared expert's extra
     // chunks come from the L2.  A large block wants few passes over every expert.
@@ -743,7 +747,7 @@ int launch_moe_block(cudaStream_t st, int sm_count, const BlockWork &w, const fl
     k_block_digits<<<n_tokens, 512, 0, st>>>(x, hidden, w.xdig, w.xexp);
     if (ep_world == 0u) ep_world = 1u;
     k_block_group<<<1, 1024, 0, st>>>(ids, pages, page_table, shared_page, n_tokens, top_k, n_experts, S / mt, RT / mt, nt_cap,
-                                     w.chunks, w.counts, ep_rank, ep_world);
+                                     w.chunks, w.counts, ep_rank, ep_world, (shared_by_token && ep_world > 1u) ? 1u : 0u);
     if (pairs_out && !ep) {
         // expert parallel: the pairs of the experts this rank owns; the others stay zero for the sum over the ranks
         *err = cudaMemsetAsync(pairs_out, 0, (size_t)n_tokens * kPairsPerToken * hidden * sizeof(float), st);

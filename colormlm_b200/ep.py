@@ -141,12 +141,14 @@ def disconnect_block(blk, group=None, barrier=None) -> None:
 
 
 def block_layer_fused(blk, xs, layer_state: dict, ys, *, layer: int, world: int, ids=None, weights=None,
-                      stream: Optional[int] = None) -> None:
+                      shared_by_token: bool = False, stream: Optional[int] = None) -> None:
     """``block_layer`` with the exchange inside the kernels: one call per rank, no collective; the w2 kernel stores the
     rows of the experts this rank owns into every rank's pair buffer over NVLink, the mix waits (bounded) for every
     rank's rows.  ys is bit-identical to the single-GPU block on every rank."""
+    # shared_by_token: the shared page is resident on every rank and rank r takes the tokens t with t mod world == r
+    owner = 0xFFFFFFFF if shared_by_token else shared_owner(layer, world)
     blk.cmd_routed_moe_block_ep(xs, layer_state["wr"], layer_state["bias"], layer_state["table"], layer_state["shared"], ys,
-                                ids, weights, shared_owner=shared_owner(layer, world), stream=stream)
+                                ids, weights, shared_owner=owner, stream=stream)
 
 
 # ---- vocabulary-sharded LM head ---------------------------------------------------------------

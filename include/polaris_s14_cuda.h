@@ -502,6 +502,11 @@ S14_API int32_t s14_cmd_routed_moe_block(s14_ctx *ctx, void *stream, s14_block *
  * contributor, so the sum is exact) and calls s14_cmd_moe_block_mix on every rank: y is then
  * bit-identical to the single-GPU block for any number of ranks.  x_residual: the layer's input to
  * add (y = x + moe(x)), or NULL. */
+/* shared_owner of the two expert-parallel block calls: a rank, or S14_EP_SHARED_BY_TOKEN - the shared
+ * page is resident on EVERY rank and rank r runs the shared expert for the tokens t with
+ * t mod world == r (in a large block the shared expert is a fifth of the work; on one rank it bounds
+ * the scaling). */
+#define S14_EP_SHARED_BY_TOKEN 0xFFFFFFFFu
 S14_API int32_t s14_cmd_routed_moe_block_experts_ep(s14_ctx *ctx, void *stream, s14_block *blk,
                                                     const s14_routed_layer_desc *desc, uint32_t ep_rank,
                                                     uint32_t ep_world, uint32_t shared_owner, float *pairs_out);

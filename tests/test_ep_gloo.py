@@ -261,5 +261,7 @@ def test_block_exchange_calls_and_teardown_order():
     ep.block_layer_fused(Block(), "X", state, "Y", layer=6, world=4, ids="I", weights="W", stream=3)
     assert log[0][:9] == ("call", "X", "Y", "WR", "B", "T", 5, "I", "W")
     assert log[0][9] == {"shared_owner": ep.shared_owner(6, 4), "stream": 3}
+    ep.block_layer_fused(Block(), "X", state, "Y", layer=6, world=4, shared_by_token=True)
+    assert log.pop()[9]["shared_owner"] == 0xFFFFFFFF
     ep.disconnect_block(Block(), barrier=lambda: log.append(("barrier",)))
     assert [e[0] for e in log[1:]] == ["disconnect", "barrier"]

@@ -236,8 +236,9 @@ def test_block_expert_parallel_ranks_add_up_to_the_single_gpu_block(ctx, world):
         blk.close()
 
 
+@pytest.mark.parametrize("by_token", [False, True])
 @pytest.mark.parametrize("world", [2, 4])
-def test_block_exchange_inside_the_kernels(ctx, world):
+def test_block_exchange_inside_the_kernels(ctx, world, by_token):
     """The ranks as block objects on this GPU, connected to one another: ranks 0 .. G-2 publish their rows into every
     rank's pair buffer and return, the last rank waits for all of them and mixes; several calls in a row (the
     two buffers alternate) with different tokens; the result is the single-GPU block's, bit for bit."""
@@ -263,8 +264,10 @@ def test_block_exchange_inside_the_kernels(ctx, world):
             got = torch.full_like(dx, float("nan"))
             for r, b in enumerate(ranks):
                 last = r == world - 1
+                # (by_token: the shared expert's tokens are dealt to the ranks, t mod world)
                 b.cmd_routed_moe_block_ep(dx, wr, bias, table, shared_dev.data_ptr(), got if last else None,
-                                          shared_owner=ep.shared_owner(call, world), wait_and_mix=last)
+                                          shared_owner=L.EP_SHARED_BY_TOKEN if by_token else ep.shared_owner(call, world),
+                                          wait_and_mix=last)
             torch.cuda.synchronize()
             assert ctx.device_status() == 0
             assert np.array_equal(got.cpu().numpy().view(np.uint32), want.cpu().numpy().view(np.uint32)), call
