@@ -1086,6 +1086,10 @@ def run_prefill_ep(args, torch, dist, L, ep, S14Context, rank: int, world: int, 
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
         ms_all.append(float(t.item()))
     clocks = sampler.stop() if sampler else None
+    # the checked call: the ranks enter it together (rank 0 has just spent a while stopping its clock sampler, and
+    # a rank that waits longer than its limit for a peer gives the call up)
+    dist.barrier()
+    torch.cuda.synchronize()
     step(0)
     torch.cuda.synchronize()
     y_np = y.cpu().numpy()
