@@ -318,10 +318,10 @@ def run_gpu(args) -> None:
         dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
         dist.barrier()
     workload = args.workload or ("stack" if world == 1 else "layer")
-    if world > 1 and workload == "prefill":
-        return run_prefill_ep(args, torch, dist, L, ep, S14Context, rank, world, local_rank)
+    if world > 1 and workload in ("prefill", "verify8"):
+        return run_prefill_ep(args, torch, dist, L, ep, S14Context, rank, world, local_rank, 8 if workload == "verify8" else None)
     if world > 1 and workload != "layer":
-        raise SystemExit("several GPUs: the expert-parallel workloads are `layer` and `prefill`")
+        raise SystemExit("several GPUs: the expert-parallel workloads are `layer`, `prefill` and `verify8`")
     if workload in ("expert_chain", "wq_a", "verify8", "prefill", "glue"):
         return run_small_workload(args, workload, torch, L, synth, S14Context, TokenRoute)
     if workload == "decode":
@@ -1028,7 +1028,7 @@ def trace_of_a_launch(torch, ctx, stack, x, h_out, stream, sm_mhz: float):
     return out
 
 
-def run_prefill_ep(args, torch, dist, L, ep, S14Context, rank: int, world: int, local_rank: int) -> None:
+def run_prefill_ep(args, torch, dist, L, ep, S14Context, rank: int, world: int, local_rank: int, block_tokens=None) -> None:
     """The prefill block (PREFILL_TOKENS tokens through one layer) expert-parallel over `world` GPUs: tokens
     on every rank, experts sharded (expert e on rank e mod world), every rank runs the grouped block path on
     the experts it owns, one NCCL all-reduce adds the pair buffers up, every rank mixes.  Timed with CUDA
@@ -1036,8 +1036,8 @@ def run_prefill_ep(args, torch, dist, L, ep, S14Context, rank: int, world: int, 
     oracle's for the sampled tokens."""
     from colormlm_b200.s14 import MoeBlock
 
-    steps = args.steps if args.steps_given else 10
-    n_tok = max(1, min(1024, args.tokens if args.tokens > 8 else PREFILL_TOKENS))
+    steps = args.steps if args.steps_given else (10 if block_tokens is None else 100)
+    n_tok = block_tokens or max(1, min(1024, args.tokens if args.tokens > 8 else PREFILL_TOKENS))
     ctx = S14Context(local_rank)
     ctx.set_accumulation(L.ACCUM_PAIRWISE)
     by_token = args.exchange == "peer" and not args.shared_on_owner
@@ -1098,13 +1098,15 @@ def run_prefill_ep(args, torch, dist, L, ep, S14Context, rank: int, world: int, 
     dist.all_gather_object(digests, digest)
     statuses = [None] * world
     dist.all_gather_object(statuses, ctx.device_status())
+    chunks = [None] * world   # the ranks' load of the checked call: chunks (expert page, <= 2 or 6 tokens) each runs
+    dist.all_gather_object(chunks, blk.last_counts()[0])
     if rank == 0:
         from oracle import s14_oracle as oracle
 
         oracle.build()
         cores = cpu_threads(oracle)
         hp = HostPages()
-        sample = (0, n_tok // 2, n_tok - 1)
+        sample = sorted({0, n_tok // 2, n_tok - 1})
         b64 = []
         t0 = time.perf_counter()
         for t_ in sample:
@@ -1114,7 +1116,8 @@ def run_prefill_ep(args, torch, dist, L, ep, S14Context, rank: int, world: int, 
         cpu_sec = (time.perf_counter() - t0) / len(sample)
         ms = float(np.median(ms_all))
         peak, peak_kind = measured_peaks()
-        line = {"metric": "prefill_tokens_per_s", "value": n_tok * steps / (ms / 1e3), "unit": "tokens/s", "n_gpus": world,
+        line = {"metric": "prefill_tokens_per_s" if block_tokens is None else "verify_block_tokens_per_s",
+                "value": n_tok * steps / (ms / 1e3), "unit": "tokens/s", "n_gpus": world,
                 "steps": steps, "warmup": args.warmup, "ms_per_step": ms / steps, "higher_is_better": True, "scaling": "strong",
                 "vs_baseline": None, "dtype": "f32", "data": "synthetic",
                 "config": {"workload": f"{n_tok}-token prefill through one layer, expert parallel over {world} GPUs: tokens on every "
@@ -1125,7 +1128,8 @@ def run_prefill_ep(args, torch, dist, L, ep, S14Context, rank: int, world: int, 
                            "exchange": args.exchange,
                            "shared_expert": ("its page on every rank, rank r takes the tokens t with t mod world == r" if by_token
                                              else "on the rank layer mod world"),
-                           "bench_workload": "prefill", "l2": "inputs larger than L2: two layers of pages alternate",
+                           "bench_workload": "prefill" if block_tokens is None else "verify8",
+                           "l2": "inputs larger than L2: two layers of pages alternate",
                            "launch": "eager launches; CUDA events between barriers, max over ranks"},
                 "repeats": {"count": len(ms_all), "region_ms_median": ms, "region_ms_min": float(np.min(ms_all)),
                             "region_ms_max": float(np.max(ms_all))},
@@ -1135,7 +1139,7 @@ def run_prefill_ep(args, torch, dist, L, ep, S14Context, rank: int, world: int, 
                 "cpu_baseline": {"value": 1.0 / cpu_sec, "unit": "tokens/s", "cores": cores, "kind": "port",
                                  "sample": f"{len(sample)} tokens of the block on the CPU oracle"},
                 "e2e": None, "gpu_launches": None, "device_status_per_rank": statuses, "clocks": clocks,
-                "exchange_bytes_per_step": int(pairs.numel() * 4)}
+                "exchange_bytes_per_step": int(pairs.numel() * 4), "chunks_per_rank": chunks}
         print(json.dumps(line), flush=True)
     dist.barrier()
     if peer:
