@@ -128,6 +128,37 @@ def test_block_sweep_of_block_sizes_against_the_one_token_kernel(ctx):
         blk.close()
 
 
+def test_block_of_the_largest_size(ctx):
+    """1024 tokens (the most a block object takes) over 16 experts: every expert has hundreds of tokens, the
+    contraction kernels walk several batches of items; sampled tokens against their own one-token call."""
+    hidden, inter, n_experts, n_tokens = 1024, 1024, 16, 1024
+    g, pages, shared = make_layer(1900, hidden, inter, n_experts, L.PAGE_MXFP4)
+    wr, bias = dev(synth.router_weight_bf16(g, n_experts, hidden)), dev(synth.router_bias(g, n_experts))
+    pages_dev, shared_dev = [dev_page(p, hidden, inter) for p in pages], dev_page(shared, hidden, inter)
+    table = torch.tensor([p.data_ptr() for p in pages_dev], dtype=torch.int64, device="cuda")
+    x = synth.activations(g, n_tokens, hidden)
+    dx = dev(x)
+    dy = torch.full_like(dx, float("nan"))
+    ids = torch.empty((n_tokens, 6), dtype=torch.int32, device="cuda")
+    wts = torch.empty((n_tokens, 6), dtype=torch.float32, device="cuda")
+    blk = MoeBlock(ctx, hidden, inter, n_tokens)
+    ctx.set_accumulation(L.ACCUM_PAIRWISE)
+    try:
+        blk.cmd_routed_moe_block(dx, wr, bias, table, shared_dev.data_ptr(), dy, ids, wts)
+        torch.cuda.synchronize()
+        assert ctx.device_status() == 0
+        chunks, n_up, n_down, bad = blk.last_counts()
+        assert bad == 0 and chunks >= (7 * n_tokens) // 6 and n_up == chunks * (inter // 64) // 2
+        assert not torch.isnan(dy).any()
+        y = dy.cpu().numpy()
+        ids_np, w_np = ids.cpu().numpy(), wts.cpu().numpy()
+        for t in (0, 1, 511, 777, 1023):
+            single = run_layer(ctx, x[t:t + 1], pages_dev, shared_dev, [(ids_np[t].tolist(), w_np[t])], L.PAGE_MXFP4, hidden, inter)[0]
+            assert np.array_equal(single.view(np.uint32), y[t].view(np.uint32)), t
+    finally:
+        blk.close()
+
+
 def test_block_at_the_benchmark_shape(ctx, oracle):
     """4096 x 2048, 48 experts.  A verify block of 8 tokens against the oracle, bit for bit; 40 tokens
     (every expert several tokens, the shared expert seven chunks) against every token's own one-token
