@@ -129,9 +129,10 @@ def test_block_sweep_of_block_sizes_against_the_one_token_kernel(ctx):
 
 
 def test_block_of_the_largest_size(ctx):
-    """1024 tokens (the most a block object takes) over 16 experts: every expert has hundreds of tokens, the
-    contraction kernels walk several batches of items; sampled tokens against their own one-token call."""
-    hidden, inter, n_experts, n_tokens = 1024, 1024, 16, 1024
+    """1024 tokens (the most a block object takes) over 16 experts: every expert has hundreds of tokens, and with
+    64 slices per chunk a CTA of the up kernel holds some 260 items, i.e. walks three batches of item records;
+    sampled tokens against their own one-token call."""
+    hidden, inter, n_experts, n_tokens = 1024, 4096, 16, 1024
     g, pages, shared = make_layer(1900, hidden, inter, n_experts, L.PAGE_MXFP4)
     wr, bias = dev(synth.router_weight_bf16(g, n_experts, hidden)), dev(synth.router_bias(g, n_experts))
     pages_dev, shared_dev = [dev_page(p, hidden, inter) for p in pages], dev_page(shared, hidden, inter)
