@@ -1371,10 +1371,28 @@ def run_small_workload(args, workload, torch, L, synth, S14Context, TokenRoute) 
         ms_all += timed_repeats(torch, stream, gph.replay, 20)
     clocks = sampler.stop()
     ms = float(np.median(ms_all))
+    per_call = n_tok if workload == "prefill" else 1   # a prefill is counted in tokens
+    e2e = None
+    if workload in ("verify8", "prefill"):
+        # the same calls with the block's tokens in pinned host memory and its result read back, inside the timed region
+        x_host = torch.from_numpy(x_np).pin_memory()
+        y_host = torch.empty_like(x_host).pin_memory()
+        n_e2e = min(args.steps, 20)
+
+        def e2e_region():
+            for i in range(n_e2e):
+                x.copy_(x_host, non_blocking=True)
+                block_call(i % 2, stream.cuda_stream)
+                y_host.copy_(y, non_blocking=True)
+
+        timed_repeats(torch, stream, e2e_region, 2)
+        e2e_ms = float(np.median(timed_repeats(torch, stream, e2e_region, 10)))
+        e2e = {"value": per_call * n_e2e / (e2e_ms / 1e3), "unit": "tokens/s" if workload == "prefill" else "calls/s",
+               "h2d_bytes_per_step": int(x_host.numel() * 4), "d2h_bytes_per_step": int(y_host.numel() * 4),
+               "calls_per_region": n_e2e, "launch": "eager calls, pinned host buffers, copies on the calls' stream"}
     parity = check()
     cpu_sec = cpu_once()
     achieved = unit_bytes * args.steps / (ms * 1e-3) / 1e9
-    per_call = n_tok if workload == "prefill" else 1   # a prefill is counted in tokens
     line = {"metric": {"expert_chain": "expert_chains_per_s", "wq_a": "matvecs_per_s", "verify8": "verify_blocks_per_s",
                        "prefill": "prefill_tokens_per_s", "glue": "layer_glue_calls_per_s"}[workload],
             "value": per_call * args.steps / (ms / 1e3), "unit": "tokens/s" if workload == "prefill" else "calls/s", "n_gpus": 1, "steps": args.steps, "warmup": args.warmup,
@@ -1398,7 +1416,7 @@ def run_small_workload(args, workload, torch, L, synth, S14Context, TokenRoute) 
                              "sample": ("8 tokens of the block, token after token, scaled to the block" if workload in ("verify8", "prefill")
                                         else "the same call on the CPU oracle, same bytes"),
                              "ms_per_call": cpu_sec * 1e3},
-            "e2e": None, "gpu_launches": launches, "device_status": ctx.device_status(), "clocks": clocks}
+            "e2e": e2e, "gpu_launches": launches, "device_status": ctx.device_status(), "clocks": clocks}
     print(json.dumps(line), flush=True)
     ctx.close()
 
