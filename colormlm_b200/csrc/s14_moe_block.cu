@@ -12,26 +12,30 @@
 // dot product rounded to F32, so every token's result is bit-identical to what the one-token kernel
 // and the double-accumulating CPU restatement give for that token alone.
 //
-// Five launches per layer, all plain stream order:
+// Five launches per layer, all plain stream order (the routed calls run the router's two launches first):
 //   k_block_digits   x [T, hidden] -> digit tiles (2 KB per token and 256 elements) + block exponents
-//   k_block_group    routes [T, top_k] -> chunks (expert page, <= kBlockNt tokens), item lists
-//   k_block_gemm<0>  up items (chunk, slice of 64 intermediate elements): w1 | w3 units x the chunk's
-//                    token tiles; epilogue: limited SwiGLU, digit tiles of the hidden values per
+//   k_block_group    routes [T, top_k] -> chunks (expert page, <= nt_cap tokens: 2 for small blocks, else 6);
+//                    an item index decodes to (chunk, slice or row tile) from the chunk records
+//   k_block_gemm<0>  up items (chunk, one or two slices of 64 intermediate elements): w1 | w3 units x the
+//                    chunk's token tiles; epilogue: limited SwiGLU, digit tiles of the hidden values per
 //                    (token, route) pair
-//   k_block_gemm<1>  down items (chunk, tile of 128 rows of w2) x the pairs' digit tiles -> the
-//                    pairs' expert outputs [pair, hidden]
-//   k_block_mix      per token the ordered mix: routes in order, shared expert last
+//   k_block_gemm<1>  down items (chunk, one or two tiles of 128 rows of w2) x the pairs' digit tiles -> the
+//                    pairs' expert outputs [pair, hidden] (expert parallel: into every rank's pair buffer)
+//   k_block_mix      per token the ordered mix: routes in order, shared expert last (expert parallel: after
+//                    every rank's rows have arrived)
 // Items are dealt round robin to one persistent CTA per SM, the chunks of one expert next to each
 // other, so that the second and later chunks of an expert find its units in the L2.
 //
-// Roles inside a GEMM CTA: one copying thread (a unit of 17 KB page bytes per ring stage: a plain
-// bulk copy, no multicast), two MMA-issuing threads (even and odd units of an item, an accumulator
-// each), four epilogue warps, eight warps that lay out the digit rows' scale codes of an item in
-// shared memory (tcgen05.cp brings them to tensor memory unit by unit, like the weights' scales) and
-// then, for large blocks, fetch the chunk's token tiles of every unit into the unit's stage (cp.async,
-// 16 bytes a thread; for small blocks a second copying thread brings them by bulk copies).  Every wait is bounded; a wait that
-// runs out raises the CTA's abort flag, the status word is set, and the CTA waits for its copies in
-// flight, frees its tensor memory and returns.
+// Roles inside a GEMM CTA: all threads decode the CTA's items of a batch into shared-memory records; one
+// copying thread (the units of 17 KB page bytes of a ring stage: plain bulk copies, no multicast), two
+// MMA-issuing threads (even and odd stages of an item, accumulators of their own), four epilogue warps, eight
+// warps that lay out the digit rows' scale codes of an item in shared memory (tcgen05.cp brings them to
+// tensor memory stage by stage, like the weights' scales) and then, for large blocks, fetch the chunk's token
+// tiles of every stage (cp.async, 16 bytes a thread; for small blocks a second copying thread brings them by
+// bulk copies).  What bounds the kernels is the number of bytes an SM takes in (45-50 GB/s per SM, whether
+// from memory or from the L2), so a large block takes TWO slices or row tiles per item: the token tiles of a
+// K range are fetched once for two units.  Every wait is bounded; a wait that runs out raises the CTA's abort
+// flag, the status word is set, and the CTA waits for its copies in flight, frees its tensor memory and returns.
 #include "s14_umma.cuh"
 
 namespace s14 {
@@ -48,7 +52,7 @@ constexpr uint32_t kSfbBytes = 16u * 1024u;                // an item's digit-ro
 constexpr uint32_t kGProdWarp = 4, kGMmaWarp0 = 5, kGTileWarp = 7, kGLayWarp0 = 8;
 constexpr uint32_t kGLayThreads = 256;
 // tensor memory columns
-constexpr uint32_t kGColAcc = 0;                           // [2 buffers][2 issuing threads][16 * kNt]
+constexpr uint32_t kGColAcc = 0;                           // [2 buffers or 2 row tiles][2 issuing threads][16 * kNt]
 constexpr uint32_t kGColSfa = 4u * 16u * kNt;              // [2 issuing threads][16]: weight scales of the unit at hand
 constexpr uint32_t kGColSfb = kGColSfa + 32u;              // [2 issuing threads][16]: digit-row scales of that unit
 static_assert(kGColSfb + 32u <= 512u, "tensor memory map");
