@@ -164,7 +164,7 @@ cudaError_t launch_greedy_argmax(cudaStream_t st, const float *logits, uint32_t 
                                  int64_t *result);
 
 // ---- a block of tokens through one layer, grouped by expert (s14_moe_block.cu) ----
-constexpr uint32_t kBlockNt = 6;  // most tokens of one chunk: the MMA's N is 16 per token
+constexpr uint32_t kBlockNt = 12;  // most tokens of one chunk (two MMAs of N = 96: sixteen digit rows per token)
 // Up to kBlockNt (token, route) pairs that share an expert page.  The chunks of one expert follow
 // one another: c0 is the first of them, nch their number.
 struct BlockChunk {

@@ -42,7 +42,10 @@ namespace s14 {
 
 namespace {
 
-constexpr uint32_t kNt = kBlockNt;
+constexpr uint32_t kNt = kBlockNt;          // most tokens of a chunk
+constexpr uint32_t kNtHalf = 6;             // tokens of one MMA: N = 96 accumulator columns
+constexpr uint32_t kAccCols = 16u * kNtHalf;
+static_assert(kNt == 2u * kNtHalf, "a wide chunk is two halves, one per issuing thread");
 constexpr uint32_t kStageA = kUnitStride;                  // a unit's codes, then its scales
 // a ring stage: a unit, then the token tiles (2 KB each) of the unit's K range for as many tokens as a chunk may hold
 static_assert(kStageA % 1024u == 0u && 2048u % 1024u == 0u, "operand tiles keep the 1 KB alignment of the 128-byte swizzle");
@@ -52,8 +55,8 @@ constexpr uint32_t kSfbBytes = 16u * 1024u;                // an item's digit-ro
 constexpr uint32_t kGProdWarp = 4, kGMmaWarp0 = 5, kGTileWarp = 7, kGLayWarp0 = 8;
 constexpr uint32_t kGLayThreads = 256;
 // tensor memory columns
-constexpr uint32_t kGColAcc = 0;                           // [2 buffers or 2 row tiles][2 issuing threads][16 * kNt]
-constexpr uint32_t kGColSfa = 4u * 16u * kNt;              // [2 issuing threads][16]: weight scales of the unit at hand
+constexpr uint32_t kGColAcc = 0;                           // [2 buffers or 2 row tiles][2 issuing threads][kAccCols]
+constexpr uint32_t kGColSfa = 4u * kAccCols;              // [2 issuing threads][16]: weight scales of the unit at hand
 constexpr uint32_t kGColSfb = kGColSfa + 32u;              // [2 issuing threads][16]: digit-row scales of that unit
 static_assert(kGColSfb + 32u <= 512u, "tensor memory map");
 // barriers
@@ -208,19 +211,27 @@ struct ItemRec {
     uint32_t tok[kNt];
     uint32_t pair[kNt];
 };
-// kMt: row tiles (slices of the up phase) per item.  With two, the chunk's token tiles of a K range are
-// fetched once for two units of page bytes (a stage holds both units, then the tiles), which halves the
-// tile bytes an SM takes in; every issuing thread then holds two accumulators and there is no second
-// accumulator buffer (the next item's MMAs wait until the epilogue has read the accumulators).
-template <bool kDown, uint32_t kMt>
+// kMt: row tiles (slices of the up phase) per item.
+//   1 (small blocks): chunks of up to six tokens (the host uses two); the two issuing threads take the even and
+//     the odd units of an item, each into an accumulator of its own, and items alternate between two
+//     accumulator buffers, so that an item's epilogue runs under the next item's MMAs.
+//   2 (larger blocks): the chunk's token tiles of a K range are fetched once for two units of page bytes (a
+//     stage holds both units, then the tiles): half the tile bytes, and what an SM takes in is what bounds
+//     these kernels.  Every issuing thread holds an accumulator per row tile and there is no second accumulator
+//     buffer (the next item's MMAs wait until the epilogue has read the accumulators, while the ring keeps filling).
+//     kWide (many tokens per expert): a chunk holds up to TWELVE tokens; issuing thread m takes the tokens
+//     6 m .. 6 m + 5 (its own rows of the tile region, its own scale atoms, N = 96) for EVERY stage: fewer
+//     passes over an expert's page.  Otherwise chunks of six and even / odd stages as with one row tile.
+template <bool kDown, uint32_t kMt, bool kWide>
 __global__ void __launch_bounds__(kGThreads, 1)
 k_block_gemm(const __grid_constant__ GemmArgs a, uint32_t *status) {
     extern __shared__ __align__(1024) uint8_t smem[];
     __shared__ __align__(8) uint64_t bars[kGBars];
-    constexpr uint32_t kBatch = kMt == 1u ? 192u : 96u;   // items decoded at a time
+    constexpr uint32_t kTok = kWide ? kNt : kNtHalf;   // most tokens of a chunk in this shape
+    constexpr uint32_t kBatch = kWide ? 96u : 48u;     // items decoded at a time (the records share the static shared memory with the ring)
     __shared__ __align__(16) ItemRec s_rec[kBatch];
-    __shared__ float s_up[kNt][64];                          // an item's up projections, handed to the gate threads
-    __shared__ __align__(16) uint8_t s_hst[kNt][16 * 2 * 16]; // an up item's digit chunks per token: [row][block][16 bytes]
+    __shared__ float s_up[kTok][64];                          // an item's up projections, handed to the gate threads
+    __shared__ __align__(16) uint8_t s_hst[kTok][16 * 2 * 16]; // an up item's digit chunks per token: [row][block][16 bytes]
     __shared__ uint32_t tmem_slot, s_units;
     __shared__ int abort_flag;
 
@@ -240,6 +251,7 @@ k_block_gemm(const __grid_constant__ GemmArgs a, uint32_t *status) {
     if (tid < kGBars) {
         uint32_t count = 1u;
         if (tid < kGRingMax) count = a.by_threads ? 1u + kGLayThreads : 1u;   // a stage: the page copy's arrival (and the tile threads' copies)
+        else if (tid >= kGBarDone && tid < kGBarDone + kGRingMax) count = kWide ? 2u : 1u;   // wide chunks: both issuing threads read every stage
         else if (tid >= kGBarAccDone && tid < kGBarAccDone + 2u) count = 2u;
         else if (tid >= kGBarAccFree && tid < kGBarAccFree + 2u) count = 128u;
         else if (tid >= kGBarSfb && tid < kGBarSfb + 2u) count = kGLayThreads;
@@ -271,7 +283,7 @@ k_block_gemm(const __grid_constant__ GemmArgs a, uint32_t *status) {
     const bool is_issuer = (warp == kGMmaWarp0 || warp == kGMmaWarp0 + 1u) && lane == 0;
     // what the roles carry from item to item
     uint32_t p_slot = 0, p_round = 0, p_units = 0;             // the copying threads: next stage
-    uint32_t m_slot = warp - kGMmaWarp0, m_round = 0;          // the issuing threads: next stage of their own
+    uint32_t m_slot = kWide ? 0u : warp - kGMmaWarp0, m_round = 0;   // the issuing threads: their next stage
     uint32_t gi = 0;                                           // items so far
     bool ok = true;
     const unsigned long long once = l2_policy_evict_first();
@@ -339,9 +351,9 @@ k_block_gemm(const __grid_constant__ GemmArgs a, uint32_t *status) {
 #pragma unroll 1
             for (uint32_t i = 0; i < nb && ok; ++i) {
                 const uint32_t nt = s_rec[i].nt & 0xFFu;
-                uint32_t vec[kNt];
+                uint32_t vec[kNtHalf];   // (small blocks: chunks of up to six tokens)
 #pragma unroll
-                for (uint32_t t = 0; t < kNt; ++t) vec[t] = kDown ? s_rec[i].pair[t] : s_rec[i].tok[t];
+                for (uint32_t t = 0; t < kNtHalf; ++t) vec[t] = kDown ? s_rec[i].pair[t] : s_rec[i].tok[t];
 #pragma unroll 1
                 for (uint32_t u = 0; u < nu; ++u) {
                     if (p_round && !mbar_wait(bar(kGBarDone + p_slot), (p_round - 1u) & 1u, abortp)) {
@@ -350,7 +362,7 @@ k_block_gemm(const __grid_constant__ GemmArgs a, uint32_t *status) {
                     }
                     const uint32_t full = bar(kGBarFull + p_slot), dst = smem_u32(sRing) + p_slot * a.stage + kMt * kStageA;
 #pragma unroll
-                    for (uint32_t t = 0; t < kNt; ++t)
+                    for (uint32_t t = 0; t < kNtHalf; ++t)
                         if (t < nt) bulk_copy(dst + t * 2048u, a.dig + ((size_t)vec[t] * nu + u) * 2048u, 2048u, full);
                     if (++p_slot == ring) {
                         p_slot = 0;
@@ -359,18 +371,21 @@ k_block_gemm(const __grid_constant__ GemmArgs a, uint32_t *status) {
                 }
             }
         } else if (is_issuer) {
-            // ---- MMA issue: thread m takes units m, m + 2, ... of every item (a ring slot always belongs
-            // to the same thread: items have an even number of units and the ring an even number of slots)
-            // and accumulates into an accumulator of its own; items alternate between two buffers ----
+            // ---- MMA issue.  One row tile per item: thread m takes units m, m + 2, ... of every item (a ring slot
+            // always belongs to the same thread: items have an even number of units and the ring an even number
+            // of slots).  Two row tiles: thread m takes EVERY stage for its half of the chunk's tokens. ----
             const uint32_t m = warp - kGMmaWarp0;
+            constexpr uint32_t kStep = kWide ? 1u : 2u;
             const uint64_t a_desc0 = smem_desc(smem_u32(sRing), 1, 64, 2);
             const uint64_t sf_desc0 = smem_desc(smem_u32(sRing) + kUnitBytes, 0, 8, 0);
-            const uint64_t b_desc0 = smem_desc(smem_u32(sRing) + kMt * kStageA, 1, 64, 2);
+            const uint64_t b_desc0 = smem_desc(smem_u32(sRing) + kMt * kStageA + (kWide ? m * kNtHalf * 2048u : 0u), 1, 64, 2);
             const uint32_t sfa_t = tmem + kGColSfa + m * 16u, sfb_t = tmem + kGColSfb + m * 16u;
 #pragma unroll 1
             for (uint32_t i = 0; i < nb && ok; ++i, ++gi) {
-                const uint32_t buf = gi & 1u;
-                const uint32_t idesc = umma_idesc_mxf4(16u * (s_rec[i].nt & 0xFFu));
+                const uint32_t buf = gi & 1u, nt_all = s_rec[i].nt & 0xFFu;
+                const uint32_t nt_m = !kWide ? nt_all
+                                             : (m == 0u ? (nt_all < kNtHalf ? nt_all : kNtHalf) : (nt_all > kNtHalf ? nt_all - kNtHalf : 0u));
+                const uint32_t idesc = umma_idesc_mxf4(16u * (nt_m ? nt_m : 1u));
                 // one row tile per item: the accumulators of item gi - 2 have been read; two: those of item gi - 1
                 if (kMt == 1u) {
                     if (gi >= 2u) ok = mbar_wait(bar(kGBarAccFree + buf), ((gi - 2u) >> 1) & 1u, abortp);
@@ -380,37 +395,40 @@ k_block_gemm(const __grid_constant__ GemmArgs a, uint32_t *status) {
                 ok = ok && mbar_wait(bar(kGBarSfb + buf), (gi >> 1) & 1u, abortp);
                 if (!ok) break;
                 fence_after();
-                const uint32_t acc = tmem + kGColAcc + ((kMt == 1u ? buf : 0u) * 2u + m) * (16u * kNt);   // row tile mt: + 2 * mt accumulators
-                const uint64_t sfb_desc0 = smem_desc(smem_u32(sSfb) + buf * kSfbBytes, 0, 8, 0);
+                const uint32_t acc = tmem + kGColAcc + ((kMt == 1u ? buf : 0u) * 2u + m) * kAccCols;   // row tile mt: + 2 * mt accumulators
+                // the scale atoms of the item's digit rows: one buffer per item parity, or (wide chunks) per half
+                const uint64_t sfb_desc0 = smem_desc(smem_u32(sSfb) + (kWide ? m : buf) * kSfbBytes, 0, 8, 0);
 #pragma unroll 1
-                for (uint32_t ku = m; ku < nu; ku += 2u) {
+                for (uint32_t ku = kWide ? 0u : m; ku < nu; ku += kStep) {
                     const uint32_t s = m_slot;
                     ok = mbar_wait(bar(kGBarFull + s), m_round & 1u, abortp);
                     if (!ok) break;
-                    m_slot += 2u;
+                    m_slot += kStep;
                     if (m_slot >= ring) {
                         m_slot -= ring;
                         ++m_round;
                     }
-                    fence_async_smem();  // the token tiles came by the threads' own copies: the tensor cores read them
-                    fence_after();
-                    const uint64_t sfd = sf_desc0 + s * (a.stage >> 4), sbd = sfb_desc0 + ku * (1024u >> 4);
+                    if (nt_m) {
+                        fence_async_smem();  // the token tiles came by the threads' own copies: the tensor cores read them
+                        fence_after();
+                        const uint64_t sfd = sf_desc0 + s * (a.stage >> 4), sbd = sfb_desc0 + ku * (1024u >> 4);
 #pragma unroll
-                    for (uint32_t mt = 0; mt < kMt; ++mt) {
-                        tmem_copy_scales(sfa_t + mt * 8u, sfd + mt * (kStageA >> 4));
-                        tmem_copy_scales(sfa_t + mt * 8u + 4u, sfd + mt * (kStageA >> 4) + (kAtomBytes >> 4));
-                    }
-                    tmem_copy_scales(sfb_t, sbd);
-                    tmem_copy_scales(sfb_t + 4u, sbd + (kAtomBytes >> 4));
-                    const uint64_t ad = a_desc0 + s * (a.stage >> 4), bd = b_desc0 + s * (a.stage >> 4);
+                        for (uint32_t mt = 0; mt < kMt; ++mt) {
+                            tmem_copy_scales(sfa_t + mt * 8u, sfd + mt * (kStageA >> 4));
+                            tmem_copy_scales(sfa_t + mt * 8u + 4u, sfd + mt * (kStageA >> 4) + (kAtomBytes >> 4));
+                        }
+                        tmem_copy_scales(sfb_t, sbd);
+                        tmem_copy_scales(sfb_t + 4u, sbd + (kAtomBytes >> 4));
+                        const uint64_t ad = a_desc0 + s * (a.stage >> 4), bd = b_desc0 + s * (a.stage >> 4);
 #pragma unroll
-                    for (uint32_t mt = 0; mt < kMt; ++mt) {
+                        for (uint32_t mt = 0; mt < kMt; ++mt) {
 #pragma unroll
-                        for (uint32_t kk = 0; kk < 4; ++kk) {
-                            const uint32_t atom = kk >> 1, sfid = (kk & 1u) * 2u;
-                            umma_mxf4(acc + mt * 2u * (16u * kNt), ad + mt * (kStageA >> 4) + kk * 2u, bd + kk * 2u,
-                                      idesc | (sfid << 29) | (sfid << 4), (sfa_t + mt * 8u + atom * 4u) | (sfid << 30),
-                                      (sfb_t + atom * 4u) | (sfid << 30), (ku >= 2u || kk) ? 1u : 0u);
+                            for (uint32_t kk = 0; kk < 4; ++kk) {
+                                const uint32_t atom = kk >> 1, sfid = (kk & 1u) * 2u;
+                                umma_mxf4(acc + mt * 2u * kAccCols, ad + mt * (kStageA >> 4) + kk * 2u, bd + kk * 2u,
+                                          idesc | (sfid << 29) | (sfid << 4), (sfa_t + mt * 8u + atom * 4u) | (sfid << 30),
+                                          (sfb_t + atom * 4u) | (sfid << 30), (ku >= kStep || kk) ? 1u : 0u);
+                            }
                         }
                     }
                     umma_commit(bar(kGBarDone + s));
@@ -426,34 +444,41 @@ k_block_gemm(const __grid_constant__ GemmArgs a, uint32_t *status) {
 #pragma unroll 1
             for (uint32_t i = 0; i < nb && ok; ++i, ++gi) {
                 const uint32_t idx0 = s_rec[i].r, buf = gi & 1u, nt = s_rec[i].nt & 0xFFu;
-                uint32_t pair[kNt];
-#pragma unroll
-                for (uint32_t t = 0; t < kNt; ++t) pair[t] = s_rec[i].pair[t];
+                const uint32_t *pair = s_rec[i].pair;
                 ok = epi_all(mbar_wait(bar(kGBarAccDone + buf), (gi >> 1) & 1u, abortp));
                 if (!ok) break;
                 fence_after();
-                float v[kMt][kNt];
+                float v[kMt][kTok];
+                // two loads of sixteen columns in flight per wait: the two issuing threads' accumulators of one token
+                // (even and odd stages), or, in wide chunks, two neighbouring tokens of the half that holds them
 #pragma unroll
                 for (uint32_t mt = 0; mt < kMt; ++mt) {
 #pragma unroll
-                    for (uint32_t t = 0; t < kNt; ++t) {
+                    for (uint32_t t = 0; t < kTok; t += (kWide ? 2u : 1u)) {
                         v[mt][t] = 0.0f;
+                        if (kWide) v[mt][t + (kWide ? 1u : 0u)] = 0.0f;
                         if (t < nt) {  // uniform in the CTA
-                            double sum = 0.0;
+                            uint32_t r0[16], r1[16];
+                            const uint32_t col0 = kWide ? (mt * 2u + t / kNtHalf) * kAccCols + 16u * (t % kNtHalf)
+                                                        : ((kMt == 1u ? buf : mt) * 2u) * kAccCols + 16u * t;
+                            const uint32_t col1 = kWide ? col0 + 16u : col0 + kAccCols;
+                            tmem_ld16(lane_base + kGColAcc + col0, r0);
+                            tmem_ld16(lane_base + kGColAcc + col1, r1);
+                            tmem_ld_wait();
+                            double lo0 = 0.0, hi0 = 0.0, lo1 = 0.0, hi1 = 0.0;
 #pragma unroll
-                            for (uint32_t half = 0; half < 2; ++half) {
-                                uint32_t r[16];
-                                tmem_ld16(lane_base + kGColAcc + ((kMt == 1u ? buf : mt) * 2u + half) * (16u * kNt) + 16u * t, r);
-                                tmem_ld_wait();
-                                double lo = 0.0, hi = 0.0;
-#pragma unroll
-                                for (int c = 0; c < 8; ++c) {
-                                    lo += (double)__uint_as_float(r[8 + c]);
-                                    hi += (double)__uint_as_float(r[c]);
-                                }
-                                sum += lo + hi;
+                            for (int c = 0; c < 8; ++c) {
+                                lo0 += (double)__uint_as_float(r0[8 + c]);
+                                hi0 += (double)__uint_as_float(r0[c]);
+                                lo1 += (double)__uint_as_float(r1[8 + c]);
+                                hi1 += (double)__uint_as_float(r1[c]);
                             }
-                            v[mt][t] = (float)sum;
+                            if (kWide) {
+                                v[mt][t] = (float)(lo0 + hi0);
+                                v[mt][t + (kWide ? 1u : 0u)] = (float)(lo1 + hi1);  // unused beyond nt
+                            } else {
+                                v[mt][t] = (float)((lo0 + hi0) + (lo1 + hi1));
+                            }
                         }
                     }
                 }
@@ -465,7 +490,7 @@ k_block_gemm(const __grid_constant__ GemmArgs a, uint32_t *status) {
                     if constexpr (kDown) {
                         // row idx * 128 + `row` of the pairs' expert outputs
 #pragma unroll
-                        for (uint32_t t = 0; t < kNt; ++t) {
+                        for (uint32_t t = 0; t < kTok; ++t) {
                             if (t < nt) {
                                 const size_t at = (size_t)pair[t] * a.hidden + idx * 128u + row;
                                 if (a.ep_world > 1u) {
@@ -480,11 +505,11 @@ k_block_gemm(const __grid_constant__ GemmArgs a, uint32_t *status) {
                         // lanes 0-63: gate of the slice's element `row`; lanes 64-127: its up projection
                         if (mt) epi_sync();  // the row tile before has been written out
 #pragma unroll
-                        for (uint32_t t = 0; t < kNt; ++t)
+                        for (uint32_t t = 0; t < kTok; ++t)
                             if (t < nt && row >= 64u) s_up[t][row - 64u] = v[mt][t];
                         epi_sync();
 #pragma unroll
-                        for (uint32_t t = 0; t < kNt; ++t) {
+                        for (uint32_t t = 0; t < kTok; ++t) {
                             if (t < nt && row < 64u) {
                                 // hidden value `row` of the slice -> sixteen digit nibbles; scale block = warp
                                 const float hv = swiglu_limit_f32(v[mt][t], s_up[t][row]);
@@ -518,7 +543,7 @@ k_block_gemm(const __grid_constant__ GemmArgs a, uint32_t *status) {
                         const uint32_t cc = (idx & 3u) * 2u + blk;
                         const uint32_t o = (idx >> 2) * 2048u + dj * 128u + ((cc ^ (dj & 7u)) << 4) + half * 8u;
 #pragma unroll
-                        for (uint32_t t = 0; t < kNt; ++t) {
+                        for (uint32_t t = 0; t < kTok; ++t) {
                             if (t < nt && (t & 1u) == (tid >> 6)) {
                                 const uint2 c8 = *reinterpret_cast<const uint2 *>(&s_hst[t][(dj * 2u + blk) * 16u + half * 8u]);
                                 *reinterpret_cast<uint2 *>(a.hdig + (size_t)pair[t] * KD * 2048u + o) = c8;
@@ -535,40 +560,20 @@ k_block_gemm(const __grid_constant__ GemmArgs a, uint32_t *status) {
             // A thread fetches its words of the item before it waits for the buffer. ----
             const uint32_t lt = tid - kGLayWarp0 * 32u;
             const uint32_t atom = lt >> 7, r32 = (lt >> 2) & 31u, col = lt & 3u;
-            const uint32_t t = 2u * col + (r32 >> 4), j = r32 & 15u;
+            const uint32_t tl = 2u * col + (r32 >> 4), j = r32 & 15u;   // the row's token inside a half, its digit row
             const int shift = j < 8u ? 4 + 3 * (int)j : 3 * (int)(j & 7u) - 20;
             const uint32_t bias = 0x01010101u * (uint32_t)shift;
 #pragma unroll 1
             for (uint32_t i = 0; i < nb && ok; ++i, ++gi) {
                 const uint32_t buf = gi & 1u, nt = s_rec[i].nt & 0xFFu;
-                uint32_t ew[16];
-                const bool mine = t < nt && t < kNt;
-                const uint32_t vec = mine ? (kDown ? s_rec[i].pair[t] : s_rec[i].tok[t]) : 0u;
-                const uint32_t *e4 = reinterpret_cast<const uint32_t *>(a.exps + (size_t)vec * (K >> 5)) + atom;
-#pragma unroll
-                for (uint32_t u = 0; u < 16; ++u) ew[u] = (mine && u < nu) ? __ldcg(e4 + u * 2u) + bias : 0x7F7F7F7Fu;
-                // the buffer's last readers were the copies of item gi - 2
-                if (gi >= 2u) ok = mbar_wait(bar(kGBarAccDone + buf), ((gi - 2u) >> 1) & 1u, abortp);
-                if (!ok) break;
-                uint8_t *dst = sSfb + buf * kSfbBytes + atom * kAtomBytes + r32 * 16u + col * 4u;
-#pragma unroll
-                for (uint32_t u = 0; u < 16; ++u)
-                    if (u < nu) *reinterpret_cast<uint32_t *>(dst + u * 1024u) = ew[u];
-                fence_async_smem();  // tcgen05.cp reads the atoms
-                mbar_arrive(bar(kGBarSfb + buf));
-                // ---- large blocks: the chunk's token tiles of every unit of the item, behind the unit in its
-                // ring stage: sixteen bytes per copy and thread (cp.async: these bytes do not pass through the
+                const uint32_t *vecs = kDown ? s_rec[i].pair : s_rec[i].tok;
+                // ---- large blocks: the chunk's token tiles of one unit of the item, behind the unit in its ring
+                // stage: sixteen bytes per copy and thread (cp.async: these bytes do not pass through the
                 // bulk-copy unit that brings the pages; measured 1.83 -> 1.65 ms for 370 tokens, but 151 -> 165 us
                 // for 8), the copies' completion counted on the stage's barrier ----
-                if (!a.by_threads) continue;   // (small blocks: the second copying thread brings them)
                 const uint32_t n16 = nt * 128u;   // sixteen-byte pieces of the chunk's tiles of one unit
-                const uint32_t *vecs = kDown ? s_rec[i].pair : s_rec[i].tok;
-#pragma unroll 1
-                for (uint32_t u = 0; u < nu; ++u) {
-                    if (p_round && !mbar_wait(bar(kGBarDone + p_slot), (p_round - 1u) & 1u, abortp)) {
-                        ok = false;
-                        break;
-                    }
+                auto copy_tiles = [&](uint32_t u) -> bool {
+                    if (p_round && !mbar_wait(bar(kGBarDone + p_slot), (p_round - 1u) & 1u, abortp)) return false;
                     const uint32_t dst0 = smem_u32(sRing) + p_slot * a.stage + kMt * kStageA;
 #pragma unroll 1
                     for (uint32_t c = lt; c < n16; c += kGLayThreads) {
@@ -581,7 +586,49 @@ k_block_gemm(const __grid_constant__ GemmArgs a, uint32_t *status) {
                         p_slot = 0;
                         ++p_round;
                     }
+                    return true;
+                };
+                // one set of atoms per item (rows of up to six tokens), in the buffer of the item's parity; wide
+                // chunks: one set per half of the chunk, a buffer each, rewritten when the item before is done
+                uint32_t ew[kWide ? 2 : 1][16];
+#pragma unroll
+                for (uint32_t h = 0; h < (kWide ? 2u : 1u); ++h) {
+                    const uint32_t t = h * kNtHalf + tl;
+                    const bool mine = tl < kNtHalf && t < nt;
+                    const uint32_t vec = mine ? vecs[t] : 0u;
+                    const uint32_t *e4 = reinterpret_cast<const uint32_t *>(a.exps + (size_t)vec * (K >> 5)) + atom;
+#pragma unroll
+                    for (uint32_t u = 0; u < 16; ++u) ew[h][u] = (mine && u < nu) ? __ldcg(e4 + u * 2u) + bias : 0x7F7F7F7Fu;
                 }
+                // wide chunks: the atoms wait for the item before, the token tiles of the item's first units do not
+                // (the stages they wait for belong to the item before: an item has at least as many units as the
+                // ring has stages)
+                uint32_t u0 = 0;
+                if (kWide && a.by_threads) {
+                    const uint32_t ahead = (ring - 1u) < nu ? ring - 1u : nu;
+#pragma unroll 1
+                    for (; u0 < ahead && ok; ++u0) ok = copy_tiles(u0);
+                    if (!ok) break;
+                }
+                // the buffers' last readers were the copies of item gi - 2, or (wide chunks) gi - 1
+                if (!kWide) {
+                    if (gi >= 2u) ok = mbar_wait(bar(kGBarAccDone + buf), ((gi - 2u) >> 1) & 1u, abortp);
+                } else if (gi >= 1u) {
+                    ok = mbar_wait(bar(kGBarAccDone + ((gi - 1u) & 1u)), ((gi - 1u) >> 1) & 1u, abortp);
+                }
+                if (!ok) break;
+#pragma unroll
+                for (uint32_t h = 0; h < (kWide ? 2u : 1u); ++h) {
+                    uint8_t *dst = sSfb + (kWide ? h : buf) * kSfbBytes + atom * kAtomBytes + r32 * 16u + col * 4u;
+#pragma unroll
+                    for (uint32_t u = 0; u < 16; ++u)
+                        if (u < nu) *reinterpret_cast<uint32_t *>(dst + u * 1024u) = ew[h][u];
+                }
+                fence_async_smem();  // tcgen05.cp reads the atoms
+                mbar_arrive(bar(kGBarSfb + buf));
+                if (!a.by_threads) continue;   // (small blocks: the second copying thread brings them)
+#pragma unroll 1
+                for (uint32_t u = u0; u < nu && ok; ++u) ok = copy_tiles(u);
             }
             asm volatile("cp.async.wait_all;" ::: "memory");
         }
@@ -682,14 +729,14 @@ k_block_mix(const float *__restrict__ d, const int32_t *__restrict__ ids, const 
 }
 
 constexpr int kMaxDevices = 64;
-size_t g_block_limit[kMaxDevices][2] = {};
+size_t g_block_limit[kMaxDevices][3] = {};
 
-// The dynamic shared memory the contraction kernels with `mt` row tiles per item may ask for on the
-// current device (set once per device; the variants with two row tiles hold fewer item records).
-size_t block_dynamic_limit(uint32_t mt) {
+// The dynamic shared memory the contraction kernels of a shape (0: one row tile per item, 1: two, 2: two with
+// wide chunks) may ask for on the current device (set once per device and shape).
+size_t block_dynamic_limit(uint32_t shape) {
     int dev = -1;
-    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= kMaxDevices || mt < 1u || mt > 2u) return 0;
-    if (g_block_limit[dev][mt - 1u]) return g_block_limit[dev][mt - 1u];
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= kMaxDevices || shape > 2u) return 0;
+    if (g_block_limit[dev][shape]) return g_block_limit[dev][shape];
     int optin = 0;
     if (cudaDeviceGetAttribute(&optin, cudaDevAttrMaxSharedMemoryPerBlockOptin, dev) != cudaSuccess) return 0;
     auto set_up = [&](auto up, auto down) -> size_t {
@@ -702,17 +749,19 @@ size_t block_dynamic_limit(uint32_t mt) {
         if (cudaFuncSetAttribute(down, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)most) != cudaSuccess) return 0;
         return most;
     };
-    const size_t most = mt == 1u ? set_up(k_block_gemm<false, 1>, k_block_gemm<true, 1>)
-                                 : set_up(k_block_gemm<false, 2>, k_block_gemm<true, 2>);
-    g_block_limit[dev][mt - 1u] = most;
+    const size_t most = shape == 0u   ? set_up(k_block_gemm<false, 1, false>, k_block_gemm<true, 1, false>)
+                        : shape == 1u ? set_up(k_block_gemm<false, 2, false>, k_block_gemm<true, 2, false>)
+                                      : set_up(k_block_gemm<false, 2, true>, k_block_gemm<true, 2, true>);
+    g_block_limit[dev][shape] = most;
     return most;
 }
 
-uint32_t block_ring(size_t limit, uint32_t stage) {
+// Ring stages that fit beside the scale atoms; with one row tile per item an even number (a slot belongs to one issuing thread).
+uint32_t block_ring(size_t limit, uint32_t stage, bool even) {
     if (limit < 2u * kSfbBytes + 2u * stage) return 0;
     uint32_t r = (uint32_t)((limit - 2u * kSfbBytes) / stage);
     if (r > kGRingMax) r = kGRingMax;
-    return r & ~1u;
+    return even ? (r & ~1u) : r;
 }
 
 }  // namespace
@@ -721,7 +770,9 @@ bool moe_block_ok(int sm_count, uint32_t hidden, uint32_t inter, uint32_t n_expe
     if (sm_count <= 0 || n_experts == 0u || n_experts > S14_N_ROUTED_EXPERTS || top_k == 0u || top_k > S14_EXPERTS_PER_TOKEN)
         return false;
     if ((hidden & 511u) || (inter & 511u) || hidden < 512u || inter < 512u || hidden > 4096u || inter > 4096u) return false;
-    return block_ring(block_dynamic_limit(1), kStageA + kNt * 2048u) >= 2u && block_ring(block_dynamic_limit(2), 2u * kStageA + kNt * 2048u) >= 2u;
+    return block_ring(block_dynamic_limit(0), kStageA + 2u * 2048u, true) >= 2u &&
+           block_ring(block_dynamic_limit(1), 2u * kStageA + kNtHalf * 2048u, true) >= 2u &&
+           block_ring(block_dynamic_limit(2), 2u * kStageA + kNt * 2048u, false) >= 2u;
 }
 
 size_t moe_block_max_chunks(uint32_t max_tokens) {
@@ -734,16 +785,18 @@ int launch_moe_block(cudaStream_t st, int sm_count, const BlockWork &w, const fl
                      const uint8_t *shared_page, uint32_t n_tokens, uint32_t top_k, uint32_t n_experts, uint32_t hidden,
                      uint32_t inter, uint32_t *status, cudaError_t *err, uint32_t nt_cap, bool residual, uint32_t ep_rank,
                      uint32_t ep_world, float *pairs_out, const BlockEp *ep, bool shared_by_token) {
-    // Tokens per chunk.  A small block is bound by the memory's latency: most experts have one token,
-    // and short stages make the ring deeper (more page bytes in flight); the shared expert's extra
-    // chunks come from the L2.  A large block wants few passes over every expert.
-    if (nt_cap == 0u) nt_cap = n_tokens <= 12u ? 2u : kNt;
-    if (nt_cap > kNt) nt_cap = kNt;
-    // Row tiles per item: a large block fetches a K range's token tiles once for two units (half the tile
-    // bytes); a small block has too few items for that (its items would not level out over the SMs).
-    const uint32_t mt = nt_cap > 2u ? 2u : 1u;
+    // Three shapes.  A small block (up to 12 tokens) is bound by the memory's latency: most experts have one
+    // token, chunks of two and short stages make the ring deeper (more page bytes in flight), the shared expert's
+    // extra chunks come from the L2, and one row tile per item keeps enough items to level out over the SMs.
+    // Larger blocks take two row tiles per item (half the tile bytes); with three or more pairs per expert on
+    // average they take wide chunks of twelve tokens (fewer passes over every page), else chunks of six.
+    uint32_t shape;
+    if (nt_cap == 0u) shape = n_tokens <= 12u ? 0u : ((uint64_t)n_tokens * top_k >= 3ull * n_experts ? 2u : 1u);
+    else shape = nt_cap <= 2u ? 0u : (nt_cap <= kNtHalf ? 1u : 2u);
+    nt_cap = shape == 0u ? (nt_cap ? nt_cap : 2u) : (shape == 1u ? kNtHalf : kNt);
+    const uint32_t mt = shape == 0u ? 1u : 2u;
     const uint32_t stage = mt * kStageA + nt_cap * 2048u;
-    const uint32_t ring = block_ring(block_dynamic_limit(mt), stage);
+    const uint32_t ring = block_ring(block_dynamic_limit(shape), stage, shape != 2u);
     *err = cudaErrorInvalidConfiguration;
     if (ring < 2u || n_tokens == 0u) return 0;
     const uint32_t S = inter >> 6, RT = hidden >> 7;
@@ -771,12 +824,15 @@ int launch_moe_block(cudaStream_t st, int sm_count, const BlockWork &w, const fl
         down.ep_rank = ep->rank;
         down.ep_call = ep->call;
     }
-    if (mt == 1u) {
-        k_block_gemm<false, 1><<<sm_count, kGThreads, smem, st>>>(up, status);
-        k_block_gemm<true, 1><<<sm_count, kGThreads, smem, st>>>(down, status);
+    if (shape == 0u) {
+        k_block_gemm<false, 1, false><<<sm_count, kGThreads, smem, st>>>(up, status);
+        k_block_gemm<true, 1, false><<<sm_count, kGThreads, smem, st>>>(down, status);
+    } else if (shape == 1u) {
+        k_block_gemm<false, 2, false><<<sm_count, kGThreads, smem, st>>>(up, status);
+        k_block_gemm<true, 2, false><<<sm_count, kGThreads, smem, st>>>(down, status);
     } else {
-        k_block_gemm<false, 2><<<sm_count, kGThreads, smem, st>>>(up, status);
-        k_block_gemm<true, 2><<<sm_count, kGThreads, smem, st>>>(down, status);
+        k_block_gemm<false, 2, true><<<sm_count, kGThreads, smem, st>>>(up, status);
+        k_block_gemm<true, 2, true><<<sm_count, kGThreads, smem, st>>>(down, status);
     }
     if (pairs_out) {
         *err = cudaGetLastError();

@@ -64,7 +64,7 @@ def test_block_equals_every_tokens_own_layer(ctx, oracle, n_tokens):
         for ids, _ in routes:
             for e in ids:
                 members[e] = members.get(e, 0) + 1
-        cap = 2 if n_tokens <= 12 else 6   # tokens per chunk: a small block takes short chunks
+        cap = 2 if n_tokens <= 12 else 6   # tokens per chunk: a small block takes short chunks (routes from the host: never wide chunks)
         assert chunks == sum(-(-m // cap) for m in members.values()) + -(-n_tokens // cap)
         ctx.set_accumulation(L.ACCUM_PAIRWISE)
         for t in range(n_tokens):
@@ -149,7 +149,7 @@ def test_block_of_the_largest_size(ctx):
         torch.cuda.synchronize()
         assert ctx.device_status() == 0
         chunks, n_up, n_down, bad = blk.last_counts()
-        assert bad == 0 and chunks >= (7 * n_tokens) // 6 and n_up == chunks * (inter // 64) // 2
+        assert bad == 0 and chunks >= (7 * n_tokens) // 12 and n_up == chunks * (inter // 64) // 2
         assert not torch.isnan(dy).any()
         y = dy.cpu().numpy()
         ids_np, w_np = ids.cpu().numpy(), wts.cpu().numpy()
