@@ -230,7 +230,7 @@ k_block_gemm(const __grid_constant__ GemmArgs a, uint32_t *status) {
     constexpr uint32_t kTok = kWide ? kNt : kNtHalf;   // most tokens of a chunk in this shape
     constexpr uint32_t kBatch = kWide ? 96u : 48u;     // items decoded at a time (the records share the static shared memory with the ring)
     __shared__ __align__(16) ItemRec s_rec[kBatch];
-    __shared__ float s_up[kTok][64];                          // an item's up projections, handed to the gate threads
+    __shared__ float s_up[kTok][64];                          // an item's up projections (even tokens) and gates (odd tokens), handed across
     __shared__ __align__(16) uint8_t s_hst[kTok][16 * 2 * 16]; // an up item's digit chunks per token: [row][block][16 bytes]
     __shared__ uint32_t tmem_slot, s_units;
     __shared__ int abort_flag;
@@ -502,17 +502,21 @@ k_block_gemm(const __grid_constant__ GemmArgs a, uint32_t *status) {
                             }
                         }
                     } else {
-                        // lanes 0-63: gate of the slice's element `row`; lanes 64-127: its up projection
+                        // threads 0-63: gate of the slice's element `row`; threads 64-127: the up projection of
+                        // element row - 64.  The first half works out the even tokens, the second the odd ones:
+                        // each hands the other the values it lacks
+                        const uint32_t el = row & 63u, par = row >> 6, blk2 = warp & 1u;
                         if (mt) epi_sync();  // the row tile before has been written out
 #pragma unroll
                         for (uint32_t t = 0; t < kTok; ++t)
-                            if (t < nt && row >= 64u) s_up[t][row - 64u] = v[mt][t];
+                            if (t < nt && (t & 1u) != par) s_up[t][el] = v[mt][t];
                         epi_sync();
 #pragma unroll
                         for (uint32_t t = 0; t < kTok; ++t) {
-                            if (t < nt && row < 64u) {
-                                // hidden value `row` of the slice -> sixteen digit nibbles; scale block = warp
-                                const float hv = swiglu_limit_f32(v[mt][t], s_up[t][row]);
+                            if (t < nt && (t & 1u) == par) {
+                                // hidden value `el` of the slice -> sixteen digit nibbles; scale block = warp % 2
+                                const float other = s_up[t][el];
+                                const float hv = par ? swiglu_limit_f32(other, v[mt][t]) : swiglu_limit_f32(v[mt][t], other);
                                 float bm = fabsf(hv);
 #pragma unroll
                                 for (int o = 16; o > 0; o >>= 1) bm = fmaxf(bm, __shfl_xor_sync(0xffffffffu, bm, o));
@@ -527,12 +531,12 @@ k_block_gemm(const __grid_constant__ GemmArgs a, uint32_t *status) {
 #pragma unroll
                                 for (uint32_t jj = 0; jj < 4; ++jj) {
                                     const uint32_t dj = (lane & 1u) * 4u + jj;
-                                    s_hst[t][(dj * 2u + warp) * 16u + (lane >> 1)] =
+                                    s_hst[t][(dj * 2u + blk2) * 16u + (lane >> 1)] =
                                         (uint8_t)(((e_hw >> (4u * dj)) & 0xFu) | (((o_hw >> (4u * dj)) & 0xFu) << 4));
-                                    s_hst[t][((8u + dj) * 2u + warp) * 16u + (lane >> 1)] =
+                                    s_hst[t][((8u + dj) * 2u + blk2) * 16u + (lane >> 1)] =
                                         (uint8_t)(((e_lw >> (4u * dj)) & 0xFu) | (((o_lw >> (4u * dj)) & 0xFu) << 4));
                                 }
-                                if (lane == 0) a.hexp[(size_t)pair[t] * (a.inter >> 5) + idx * 2u + warp] = (uint8_t)(E + 100);
+                                if (lane == 0) a.hexp[(size_t)pair[t] * (a.inter >> 5) + idx * 2u + blk2] = (uint8_t)(E + 100);
                             }
                         }
                         epi_sync();
