@@ -468,7 +468,8 @@ S14_API int32_t s14_routed_moe_layer_host(s14_ctx *ctx, const s14_routed_layer_d
  * its tokens one by one through the same layer loop, ssd_inference/src/forward.rs:544-549; the
  * semantics are that loop, examples/s14_vulkan_numeric.rs:929-947, applied to every token).  Every
  * distinct expert's page is streamed once from memory for all the tokens routed to it (in chunks of
- * six tokens, of two for blocks of up to 12 tokens; an expert's later chunks find the page in the
+ * two tokens for blocks of up to 12 tokens, of twelve for blocks with at least three (token, route)
+ * pairs per expert, else of six; an expert's later chunks find the page in the
  * L2): per layer five launches - digit rows of the tokens, grouping of the (token, route) pairs by
  * expert, the w1 | w3 contraction with SwiGLU, the w2 contraction, the ordered mix - the two
  * contractions on tcgen05 kind::mxf4.block_scale with N = 16 digit rows per token of a chunk; the
