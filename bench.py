@@ -160,12 +160,12 @@ class HostPages:
         return self.cache[key]
 
 
-def cpu_layer(oracle, pages: HostPages, layer: int, x: np.ndarray, acc64: bool = False):
+def cpu_layer(oracle, pages: HostPages, layer: int, x: np.ndarray, acc64: bool = False, official: bool = False):
     """Router + layer of one token on the CPU oracle; returns (y, ids, weights)."""
     wr, bias = router_of_layer(layer)
     ids, w, _, _ = oracle.router(x, wr, bias, 0, TOP_K, 1.0)
     sel = [pages.get(layer, e) for e in ids]
-    fn = oracle.moe_layer_acc64 if acc64 else oracle.moe_layer
+    fn = oracle.official_moe_layer if official else (oracle.moe_layer_acc64 if acc64 else oracle.moe_layer)
     return fn(x, sel, w, pages.get(layer, N_EXPERTS), 0, HIDDEN, INTER), ids, w
 
 
@@ -1300,6 +1300,7 @@ def run_small_workload(args, workload, torch, L, synth, S14Context, TokenRoute) 
         ids_dev = torch.empty((n_tok, TOP_K), dtype=torch.int32, device="cuda")
         w_dev = torch.empty((n_tok, TOP_K), dtype=torch.float32, device="cuda")
         blk = MoeBlock(ctx, HIDDEN, INTER, n_tok)
+        blk.set_semantics(args.official)
         distinct = []
         for l in range(2):
             wr, bias = router_of_layer(l)
@@ -1312,7 +1313,9 @@ def run_small_workload(args, workload, torch, L, synth, S14Context, TokenRoute) 
         unit_bytes = int((d_avg + 1) * PAGE_BYTES + ROUTER_BYTES + n_tok * 2 * HIDDEN * 4)
         what = (f"{n_tok}-token {'verify block' if workload == 'verify8' else 'prefill'} through one layer, routes picked on the "
                 f"device, tokens grouped by expert: {d_avg:.0f} distinct routed experts + the shared one (every distinct page "
-                "counted once), router weights, x and y")
+                "counted once), router weights, x and y"
+                + ("; the official expert arithmetic (E4M3FN activation quantisation per 128 elements, BF16 results, "
+                   "route weight before w2)" if args.official else ""))
 
         def block_call(l, st):
             lay = layers[l]
@@ -1331,6 +1334,12 @@ def run_small_workload(args, workload, torch, L, synth, S14Context, TokenRoute) 
             assert ctx.last_layer_path == L.LAYER_PATH_TENSOR_BLOCK
             hp = HostPages()
             b64, b32 = [], []
+            if args.official:
+                for t in sample:
+                    yo, ido, _ = cpu_layer(oracle, hp, 0, x_np[t], official=True)
+                    assert np.array_equal(ids_dev[t].cpu().numpy(), ido), "the device's routes differ from the oracle's"
+                    b64.append(error_block(oracle, y.cpu().numpy()[t], yo))
+                return {"vs_official_oracle": worst(b64), "tokens_checked": list(sample)}
             for t in sample:
                 y64, ids64, _ = cpu_layer(oracle, hp, 0, x_np[t], acc64=True)
                 y32, _, _ = cpu_layer(oracle, hp, 0, x_np[t], acc64=False)
@@ -1345,10 +1354,10 @@ def run_small_workload(args, workload, torch, L, synth, S14Context, TokenRoute) 
             # the reference's way through a block: token after token (forward.rs:544-549); a bounded sample of
             # n_cpu tokens, scaled to the block
             hp = HostPages()
-            cpu_layer(oracle, hp, 0, x_np[0])
+            cpu_layer(oracle, hp, 0, x_np[0], official=args.official)
             t0 = time.perf_counter()
             for t in range(n_cpu):
-                cpu_layer(oracle, hp, 0, x_np[t % n_tok])
+                cpu_layer(oracle, hp, 0, x_np[t % n_tok], official=args.official)
             return (time.perf_counter() - t0) * n_tok / n_cpu
 
     with torch.cuda.stream(stream):
@@ -1399,6 +1408,7 @@ def run_small_workload(args, workload, torch, L, synth, S14Context, TokenRoute) 
             "ms_per_step": ms / args.steps, "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "f32",
             "data": "synthetic",
             "config": {"workload": what, "bench_workload": workload, "accumulation": args.accum,
+                       "semantics": "official" if args.official else "f32",
                        "l2": "inputs larger than L2: distinct weights of more than 126 MB walked round-robin",
                        "launch": f"cuda graph of the {args.steps} calls of a region"},
             "repeats": {"count": len(ms_all), "region_ms_median": ms, "region_ms_min": float(np.min(ms_all)),
@@ -1430,6 +1440,8 @@ def main() -> None:
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--workload", default=None, choices=["stack", "layer", "expert_chain", "wq_a", "verify8", "prefill", "glue", "decode"])
     ap.add_argument("--tokens", type=int, default=1, help="tokens of the wq_a workload (1, 4 or 8); of the prefill workload (default 370)")
+    ap.add_argument("--official", action="store_true",
+                    help="verify8 / prefill on one GPU: the official expert arithmetic instead of the F32 one")
     ap.add_argument("--accum", default="pairwise", choices=["pairwise", "reference"])
     ap.add_argument("--exchange", default="peer", choices=["peer", "nccl"],
                     help="several GPUs: down vectors exchanged inside the layer kernel over peer memory, or by NCCL all-reduce")
@@ -1456,6 +1468,8 @@ def main() -> None:
         ROUTER_BYTES = N_EXPERTS * HIDDEN * 2 + N_EXPERTS * 4
         STEP_BYTES = 7 * PAGE_BYTES + ROUTER_BYTES + HIDDEN * 4 + HIDDEN * 4
         WORKLOAD = WORKLOAD.replace("top-6 of 256", f"top-6 of {N_EXPERTS} (reduced pool, not the benchmark)")
+    if args.official and (args.gpus != 1 or args.impl != "ours" or args.workload not in ("verify8", "prefill")):
+        raise SystemExit("--official: the verify8 and prefill workloads on one GPU")
     if args.impl == "reference":
         args.steps = args.steps if args.steps is not None else 40
         args.warmup = args.warmup if args.warmup is not None else 3

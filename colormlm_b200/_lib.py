@@ -165,6 +165,7 @@ SIGNATURES = {
     "s14_block_create": (_I32, [_VP, _U32, _U32, _U32, _P(_VP)]),
     "s14_block_destroy": (_I32, [_VP]),
     "s14_block_set_residual": (_I32, [_VP, _I32]),
+    "s14_block_set_semantics": (_I32, [_VP, _U32]),
     "s14_cmd_moe_block": (_I32, [_VP, _VP, _VP, _P(MoeLayerDesc)]),
     "s14_cmd_routed_moe_block": (_I32, [_VP, _VP, _VP, _P(RoutedLayerDesc)]),
     "s14_block_last_counts": (_I32, [_VP, _P(_U32)]),

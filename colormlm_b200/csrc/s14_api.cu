@@ -1792,6 +1792,7 @@ struct s14_block {
     cudaEvent_t staged = nullptr;                 // the staging buffer's last copy has left it
     bool stage_busy = false;
     bool residual = false;                        // y = x + moe(x)
+    bool official = false;                        // the official expert arithmetic (s14_block_set_semantics)
     // expert-parallel exchange inside the block kernels: this rank's buffer (two pair buffers, then two rows of
     // flag words) and the ranks' buffers as mapped here
     struct {
@@ -1822,6 +1823,7 @@ extern "C" int32_t s14_block_destroy(s14_block *blk) {
     cudaFree(blk->w.hdig);
     cudaFree(blk->w.hexp);
     cudaFree(blk->w.d);
+    cudaFree(blk->w.hval);
     cudaFree(blk->scores);
     cudaFree(blk->select);
     cudaFree(blk->counter);
@@ -1880,7 +1882,8 @@ static int32_t block_launch(s14_block *blk, cudaStream_t st, const float *x, flo
     s14_ctx *ctx = blk->ctx;
     cudaError_t err;
     ctx->launches += launch_moe_block(st, ctx->sm_count, blk->w, x, y, ids, weights, pages, page_table, shared_page, n_tokens,
-                                      top_k, n_experts, blk->hidden, blk->inter, ctx->status, &err, 0, blk->residual);
+                                      top_k, n_experts, blk->hidden, blk->inter, ctx->status, &err, 0, blk->residual, 0, 1, nullptr,
+                                      nullptr, false, blk->official);
     ctx->last_path = S14_LAYER_PATH_TENSOR_BLOCK;
     if (err != cudaSuccess) return cuda_fail(err, "S14 MoE block launch");
     return S14_OK;
@@ -1993,6 +1996,7 @@ extern "C" int32_t s14_cmd_routed_moe_block_experts_ep(s14_ctx *ctx, void *strea
                                                        const s14_routed_layer_desc *desc, uint32_t ep_rank, uint32_t ep_world,
                                                        uint32_t shared_owner, float *pairs_out) {
     if (!ctx || !blk || !desc || !pairs_out) return fail(S14_ERR_CONTRACT, "s14_cmd_routed_moe_block_experts_ep: NULL argument");
+    if (blk->official) return fail(S14_ERR_CONTRACT, "s14_cmd_routed_moe_block_experts_ep: the official arithmetic runs on one GPU");
     const bool by_token = shared_owner == S14_EP_SHARED_BY_TOKEN;
     if (ep_world == 0 || ep_world > kMaxEpWorld || ep_rank >= ep_world || (!by_token && shared_owner >= ep_world))
         return fail(S14_ERR_CONTRACT, "s14_cmd_routed_moe_block_experts_ep: rank or shared owner outside the world (1..8 ranks)");
@@ -2018,6 +2022,7 @@ extern "C" int32_t s14_block_ep_create(s14_block *blk, uint32_t rank, uint32_t w
     if (!blk) throw ContractError("s14_block_ep_create: blk is NULL");
     if (world < 2 || world > kMaxEpWorld || rank >= world) throw ContractError("s14_block_ep_create: 2..8 ranks, rank inside the world");
     if (blk->ep.buf) throw ContractError("s14_block_ep_create: already created for this block object");
+    if (blk->official) throw ContractError("s14_block_ep_create: the official arithmetic runs on one GPU");
     CUDA_OK(cudaSetDevice(blk->device));
     blk->ep.pair_bytes = ((size_t)blk->max_tokens * (S14_EXPERTS_PER_TOKEN + 1) * blk->hidden * sizeof(float) + 255u) & ~(size_t)255u;
     CUDA_OK(cudaMalloc(&blk->ep.buf, block_ep_bytes(blk)));
@@ -2155,6 +2160,26 @@ extern "C" int32_t s14_cmd_moe_block_mix(s14_ctx *ctx, void *stream, s14_block *
     ctx->launches += 1;
     if (err != cudaSuccess) return cuda_fail(err, "S14 MoE block mix launch");
     return S14_OK;
+}
+
+// The arithmetic of the block's experts: this library's (F32 values, exact sums, one rounding per matvec) or
+// the official one of s14_first_real_token/executor.py:712-743.  The official one needs one more buffer
+// (the pairs' weighted hidden values, 7 * max_tokens * intermediate floats), allocated on first use.
+extern "C" int32_t s14_block_set_semantics(s14_block *blk, uint32_t semantics) {
+    S14_TRY
+    if (!blk) return fail(S14_ERR_CONTRACT, "s14_block_set_semantics: blk is NULL");
+    if (semantics != S14_BLOCK_SEMANTICS_F32 && semantics != S14_BLOCK_SEMANTICS_OFFICIAL)
+        return fail(S14_ERR_CONTRACT, "s14_block_set_semantics: unknown semantics");
+    if (semantics == S14_BLOCK_SEMANTICS_OFFICIAL) {
+        if (blk->ep.buf) return fail(S14_ERR_CONTRACT, "s14_block_set_semantics: the official arithmetic runs on one GPU (the block has an exchange)");
+        if (!blk->w.hval) {
+            CUDA_OK(cudaSetDevice(blk->device));
+            CUDA_OK(cudaMalloc((void **)&blk->w.hval, (size_t)blk->max_tokens * 7u * blk->inter * sizeof(float)));
+        }
+    }
+    blk->official = semantics == S14_BLOCK_SEMANTICS_OFFICIAL;
+    return S14_OK;
+    S14_CATCH
 }
 
 extern "C" int32_t s14_block_set_residual(s14_block *blk, int32_t residual) {

@@ -182,6 +182,7 @@ struct BlockWork {
     uint8_t *xdig, *xexp;      // the tokens' digit tiles and block exponents
     uint8_t *hdig, *hexp;      // the pairs' hidden values likewise
     float *d;                  // the pairs' expert outputs [pair, hidden]
+    float *hval;               // official arithmetic: the pairs' weighted hidden values [pair, inter] (NULL until asked for)
 };
 // Expert-parallel exchange of the block kernels over peer memory: every rank holds two pair buffers
 // [pairs, hidden] F32 (calls alternate between them) and, per buffer, one 8-byte word per rank: the number
@@ -207,7 +208,7 @@ int launch_moe_block(cudaStream_t st, int sm_count, const BlockWork &w, const fl
                      const uint8_t *shared_page, uint32_t n_tokens, uint32_t top_k, uint32_t n_experts, uint32_t hidden,
                      uint32_t inter, uint32_t *status, cudaError_t *err, uint32_t nt_cap = 0, bool residual = false,
                      uint32_t ep_rank = 0, uint32_t ep_world = 1, float *pairs_out = nullptr, const BlockEp *ep = nullptr,
-                     bool shared_by_token = false);
+                     bool shared_by_token = false, bool official = false);
 // With pairs_out (expert parallel: rank ep_rank of ep_world computes the experts e with e mod world == rank) the
 // pairs' expert outputs [n_tokens * 7, hidden] go there, zero where another rank owns the expert, and no mix runs;
 // launch_block_mix mixes such a buffer once the ranks' buffers have been added up (x: the layer's input for a residual, or NULL).

@@ -85,16 +85,57 @@ struct GemmArgs {
     unsigned long long *flag_peer[kMaxEpWorld];
     unsigned int *ep_counter;   // this GPU's arrival counter, zero at rest
     uint32_t ep_world, ep_rank, ep_call;
+    // Official expert arithmetic (up kernel): the pairs' weighted hidden values, BF16-valued F32 [pair][inter],
+    // and the routes' weights [token][top_k]
+    float *hval;
+    const float *weights;
+    uint32_t top_k;
 };
 
-// The digit tiles and block exponents of n vectors of K elements (one CTA per vector).
+// torch's .to(torch.bfloat16).float()
+__device__ __forceinline__ float bf16_round(float v) { return __bfloat162float(__float2bfloat16_rn(v)); }
+
+// The nearest E4M3FN value (ties to even) of |v| <= 448: three mantissa bits; below 2^-6 multiples of 2^-9.
+__device__ __forceinline__ float e4m3fn_round(float v) {
+    const float a = fabsf(v);
+    float q;
+    if (a < 0.015625f) {
+        q = __fmul_rn(rintf(__fmul_rn(a, 512.0f)), 0.001953125f);
+    } else {
+        const int e = (int)(__float_as_uint(a) >> 23) - 127;   // floor(log2 a)
+        q = __fmul_rn(rintf(__fmul_rn(a, __uint_as_float((uint32_t)(130 - e) << 23))), __uint_as_float((uint32_t)(124 + e) << 23));
+    }
+    return copysignf(q, v);
+}
+
+// The digit tiles and block exponents of n vectors of K elements (one CTA per vector).  With `quant` the
+// vector is first quantised as the official linears quantise their input
+// (l42_real_reference/l42_reference.py:389-403): per 128 elements amax = max(|x|, 1e-4), scale =
+// 2^ceil(log2(amax / 448)) (F32 quotient, the logarithm taken in double and rounded to F32), x / scale
+// clipped to +-448, rounded to E4M3FN, times the scale.  The quantised values are F32 values with four
+// significant bits, which the digit rows hold exactly.
 __global__ void __launch_bounds__(512)
-k_block_digits(const float *__restrict__ x, uint32_t K, uint8_t *__restrict__ dig, uint8_t *__restrict__ exps) {
+k_block_digits(const float *__restrict__ x, uint32_t K, uint8_t *__restrict__ dig, uint8_t *__restrict__ exps, uint32_t quant) {
     const uint32_t v = blockIdx.x, g = threadIdx.x;
     if (g >= (K >> 3)) return;  // whole warps leave: K is a multiple of 256
     const float4 p0 = __ldg(reinterpret_cast<const float4 *>(x + (size_t)v * K) + 2u * g);
     const float4 p1 = __ldg(reinterpret_cast<const float4 *>(x + (size_t)v * K) + 2u * g + 1u);
-    const float xs[8] = {p0.x, p0.y, p0.z, p0.w, p1.x, p1.y, p1.z, p1.w};
+    float xs[8] = {p0.x, p0.y, p0.z, p0.w, p1.x, p1.y, p1.z, p1.w};
+    if (quant) {
+        // a group of 128 elements is sixteen neighbouring threads
+        float am = 0.0f;
+#pragma unroll
+        for (int i = 0; i < 8; ++i) am = fmaxf(am, fabsf(xs[i]));
+#pragma unroll
+        for (int o = 8; o > 0; o >>= 1) am = fmaxf(am, __shfl_xor_sync(0xffffffffu, am, o));
+        am = fmaxf(am, 1e-4f);
+        int e = (int)ceilf((float)log2((double)__fdiv_rn(am, 448.0f)));
+        e = e < -126 ? -126 : (e > 126 ? 126 : e);
+        const float scale = __uint_as_float((uint32_t)(127 + e) << 23), inv = __uint_as_float((uint32_t)(127 - e) << 23);
+#pragma unroll
+        for (int i = 0; i < 8; ++i)
+            xs[i] = __fmul_rn(e4m3fn_round(fminf(fmaxf(__fmul_rn(xs[i], inv), -448.0f), 448.0f)), scale);
+    }
     digits_of8(xs, g, dig + (size_t)v * (K >> 8) * 2048u, exps + (size_t)v * (K >> 5));
 }
 
@@ -222,7 +263,7 @@ struct ItemRec {
 //     kWide (many tokens per expert): a chunk holds up to TWELVE tokens; issuing thread m takes the tokens
 //     6 m .. 6 m + 5 (its own rows of the tile region, its own scale atoms, N = 96) for EVERY stage: fewer
 //     passes over an expert's page.  Otherwise chunks of six and even / odd stages as with one row tile.
-template <bool kDown, uint32_t kMt, bool kWide>
+template <bool kDown, uint32_t kMt, bool kWide, bool kOfficial>
 __global__ void __launch_bounds__(kGThreads, 1)
 k_block_gemm(const __grid_constant__ GemmArgs a, uint32_t *status) {
     extern __shared__ __align__(1024) uint8_t smem[];
@@ -493,11 +534,12 @@ k_block_gemm(const __grid_constant__ GemmArgs a, uint32_t *status) {
                         for (uint32_t t = 0; t < kTok; ++t) {
                             if (t < nt) {
                                 const size_t at = (size_t)pair[t] * a.hidden + idx * 128u + row;
+                                const float o = kOfficial ? bf16_round(v[mt][t]) : v[mt][t];   // official: a linear's result is BF16
                                 if (a.ep_world > 1u) {
 #pragma unroll 1
-                                    for (uint32_t p = 0; p < a.ep_world; ++p) a.out_peer[p][at] = v[mt][t];
+                                    for (uint32_t p = 0; p < a.ep_world; ++p) a.out_peer[p][at] = o;
                                 } else {
-                                    a.out[at] = v[mt][t];
+                                    a.out[at] = o;
                                 }
                             }
                         }
@@ -507,6 +549,27 @@ k_block_gemm(const __grid_constant__ GemmArgs a, uint32_t *status) {
                         // each hands the other the values it lacks
                         const uint32_t el = row & 63u, par = row >> 6, blk2 = warp & 1u;
                         if (mt) epi_sync();  // the row tile before has been written out
+                        if constexpr (kOfficial) {
+                            // official arithmetic (s14_first_real_token/executor.py:712-743): gate and up rounded to
+                            // BF16, the limited SwiGLU in F32, times the route's weight (not for the shared expert),
+                            // rounded to BF16; the values go out as they are - their quantisation per 128 elements
+                            // and their digit rows are the next launch's
+#pragma unroll
+                            for (uint32_t t = 0; t < kTok; ++t)
+                                if (t < nt && (t & 1u) != par) s_up[t][el] = bf16_round(v[mt][t]);
+                            epi_sync();
+#pragma unroll
+                            for (uint32_t t = 0; t < kTok; ++t) {
+                                if (t < nt && (t & 1u) == par) {
+                                    const float other = s_up[t][el], mine = bf16_round(v[mt][t]);
+                                    const float hv = par ? swiglu_limit_f32(other, mine) : swiglu_limit_f32(mine, other);
+                                    const uint32_t pr = pair[t], tok = pr / kPairsPerToken, pos = pr - tok * kPairsPerToken;
+                                    const float wh = pos < S14_EXPERTS_PER_TOKEN ? __fmul_rn(hv, __ldg(a.weights + tok * a.top_k + pos)) : hv;
+                                    a.hval[(size_t)pr * a.inter + idx * 64u + el] = bf16_round(wh);
+                                }
+                            }
+                        }
+                        if constexpr (!kOfficial) {
 #pragma unroll
                         for (uint32_t t = 0; t < kTok; ++t)
                             if (t < nt && (t & 1u) != par) s_up[t][el] = v[mt][t];
@@ -553,6 +616,7 @@ k_block_gemm(const __grid_constant__ GemmArgs a, uint32_t *status) {
                                 *reinterpret_cast<uint2 *>(a.hdig + (size_t)pair[t] * KD * 2048u + o) = c8;
                             }
                         }
+                        }  // (this library's arithmetic)
                     }
                 }
             }
@@ -695,7 +759,7 @@ __global__ void __launch_bounds__(256)
 k_block_mix(const float *__restrict__ d, const int32_t *__restrict__ ids, const float *__restrict__ weights,
             uint32_t top_k, int has_shared, float *y, uint32_t hidden, const uint32_t *__restrict__ counts,
             const float *x, uint32_t residual, const unsigned long long *flags, uint32_t ep_world, uint32_t ep_call,
-            uint32_t wait_limit, uint32_t *status) {
+            uint32_t wait_limit, uint32_t *status, uint32_t official) {
     const uint32_t n = blockIdx.x * blockDim.x + threadIdx.x, t = blockIdx.y;
     if (flags) {
         // expert parallel, exchange inside the kernels: every rank's rows of this call are in this rank's buffer
@@ -725,10 +789,14 @@ k_block_mix(const float *__restrict__ d, const int32_t *__restrict__ ids, const 
     if (n >= hidden || __ldcg(counts + 3)) return;
     const float *dt = d + (size_t)t * kPairsPerToken * hidden + n;
     float acc = 0.0f;
+    // official arithmetic: the route's weight went into the expert's hidden values; the BF16 outputs are added
+    // in F32 and the sum is rounded to BF16 (moe_branch, s14_first_real_token/executor.py:716-735)
     for (uint32_t m = 0; m < top_k; ++m)
         if (__ldg(ids + t * top_k + m) >= 0)
-            acc = __fadd_rn(acc, __fmul_rn(__ldg(weights + t * top_k + m), __ldcg(dt + (size_t)m * hidden)));
+            acc = __fadd_rn(acc, official ? __ldcg(dt + (size_t)m * hidden)
+                                          : __fmul_rn(__ldg(weights + t * top_k + m), __ldcg(dt + (size_t)m * hidden)));
     if (has_shared) acc = __fadd_rn(acc, __ldcg(dt + (size_t)S14_EXPERTS_PER_TOKEN * hidden));
+    if (official) acc = bf16_round(acc);
     y[(size_t)t * hidden + n] = residual ? __fadd_rn(x[(size_t)t * hidden + n], acc) : acc;
 }
 
@@ -743,19 +811,27 @@ size_t block_dynamic_limit(uint32_t shape) {
     if (g_block_limit[dev][shape]) return g_block_limit[dev][shape];
     int optin = 0;
     if (cudaDeviceGetAttribute(&optin, cudaDevAttrMaxSharedMemoryPerBlockOptin, dev) != cudaSuccess) return 0;
-    auto set_up = [&](auto up, auto down) -> size_t {
-        cudaFuncAttributes fa, fb;
-        if (cudaFuncGetAttributes(&fa, up) != cudaSuccess || cudaFuncGetAttributes(&fb, down) != cudaSuccess) return 0;
-        const size_t fixed = fa.sharedSizeBytes > fb.sharedSizeBytes ? fa.sharedSizeBytes : fb.sharedSizeBytes;
+    // the four kernels of a shape (up and down, this library's arithmetic and the official one) get the same limit
+    auto set_up = [&](auto up, auto down, auto up_official, auto down_official) -> size_t {
+        size_t fixed = 0;
+        cudaFuncAttributes fa;
+        const void *fns[4] = {(const void *)up, (const void *)down, (const void *)up_official, (const void *)down_official};
+        for (const void *fn : fns) {
+            if (cudaFuncGetAttributes(&fa, fn) != cudaSuccess) return 0;
+            if (fa.sharedSizeBytes > fixed) fixed = fa.sharedSizeBytes;
+        }
         if ((size_t)optin <= fixed) return 0;
         const size_t most = (size_t)optin - fixed;
-        if (cudaFuncSetAttribute(up, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)most) != cudaSuccess) return 0;
-        if (cudaFuncSetAttribute(down, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)most) != cudaSuccess) return 0;
+        for (const void *fn : fns)
+            if (cudaFuncSetAttribute(fn, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)most) != cudaSuccess) return 0;
         return most;
     };
-    const size_t most = shape == 0u   ? set_up(k_block_gemm<false, 1, false>, k_block_gemm<true, 1, false>)
-                        : shape == 1u ? set_up(k_block_gemm<false, 2, false>, k_block_gemm<true, 2, false>)
-                                      : set_up(k_block_gemm<false, 2, true>, k_block_gemm<true, 2, true>);
+    const size_t most = shape == 0u   ? set_up(k_block_gemm<false, 1, false, false>, k_block_gemm<true, 1, false, false>,
+                                               k_block_gemm<false, 1, false, true>, k_block_gemm<true, 1, false, true>)
+                        : shape == 1u ? set_up(k_block_gemm<false, 2, false, false>, k_block_gemm<true, 2, false, false>,
+                                               k_block_gemm<false, 2, false, true>, k_block_gemm<true, 2, false, true>)
+                                      : set_up(k_block_gemm<false, 2, true, false>, k_block_gemm<true, 2, true, false>,
+                                               k_block_gemm<false, 2, true, true>, k_block_gemm<true, 2, true, true>);
     g_block_limit[dev][shape] = most;
     return most;
 }
@@ -788,13 +864,15 @@ int launch_moe_block(cudaStream_t st, int sm_count, const BlockWork &w, const fl
                      const float *weights, const uint8_t *const *pages, const uint8_t *const *page_table,
                      const uint8_t *shared_page, uint32_t n_tokens, uint32_t top_k, uint32_t n_experts, uint32_t hidden,
                      uint32_t inter, uint32_t *status, cudaError_t *err, uint32_t nt_cap, bool residual, uint32_t ep_rank,
-                     uint32_t ep_world, float *pairs_out, const BlockEp *ep, bool shared_by_token) {
+                     uint32_t ep_world, float *pairs_out, const BlockEp *ep, bool shared_by_token, bool official) {
     // Three shapes.  A small block (up to 12 tokens) is bound by the memory's latency: most experts have one
     // token, chunks of two and short stages make the ring deeper (more page bytes in flight), the shared expert's
     // extra chunks come from the L2, and one row tile per item keeps enough items to level out over the SMs.
     // Larger blocks take two row tiles per item (half the tile bytes); with three or more pairs per expert on
     // average they take wide chunks of twelve tokens (fewer passes over every page), else chunks of six.
     uint32_t shape;
+    *err = cudaErrorInvalidConfiguration;
+    if (official && (ep || pairs_out || !w.hval)) return 0;   // the official arithmetic runs on one GPU
     if (nt_cap == 0u) shape = n_tokens <= 12u ? 0u : ((uint64_t)n_tokens * top_k >= 3ull * n_experts ? 2u : 1u);
     else shape = nt_cap <= 2u ? 0u : (nt_cap <= kNtHalf ? 1u : 2u);
     nt_cap = shape == 0u ? (nt_cap ? nt_cap : 2u) : (shape == 1u ? kNtHalf : kNt);
@@ -805,7 +883,7 @@ int launch_moe_block(cudaStream_t st, int sm_count, const BlockWork &w, const fl
     if (ring < 2u || n_tokens == 0u) return 0;
     const uint32_t S = inter >> 6, RT = hidden >> 7;
     const size_t smem = (size_t)ring * stage + 2u * kSfbBytes;
-    k_block_digits<<<n_tokens, 512, 0, st>>>(x, hidden, w.xdig, w.xexp);
+    k_block_digits<<<n_tokens, 512, 0, st>>>(x, hidden, w.xdig, w.xexp, official ? 1u : 0u);
     if (ep_world == 0u) ep_world = 1u;
     k_block_group<<<1, 1024, 0, st>>>(ids, pages, page_table, shared_page, n_tokens, top_k, n_experts, S / mt, RT / mt, nt_cap,
                                      w.chunks, w.counts, ep_rank, ep_world, (shared_by_token && ep_world > 1u) ? 1u : 0u);
@@ -828,22 +906,43 @@ int launch_moe_block(cudaStream_t st, int sm_count, const BlockWork &w, const fl
         down.ep_rank = ep->rank;
         down.ep_call = ep->call;
     }
+    if (official) {
+        // the up kernel leaves the pairs' weighted hidden values; a second digits launch quantises them per 128
+        // elements and lays out their digit rows (pairs without a route: zeros)
+        up.hval = w.hval;
+        up.weights = weights;
+        up.top_k = top_k;
+        const uint32_t n_pairs = n_tokens * kPairsPerToken;
+        *err = cudaMemsetAsync(w.hval, 0, (size_t)n_pairs * inter * sizeof(float), st);
+        if (*err != cudaSuccess) return 2;
+        if (shape == 0u) k_block_gemm<false, 1, false, true><<<sm_count, kGThreads, smem, st>>>(up, status);
+        else if (shape == 1u) k_block_gemm<false, 2, false, true><<<sm_count, kGThreads, smem, st>>>(up, status);
+        else k_block_gemm<false, 2, true, true><<<sm_count, kGThreads, smem, st>>>(up, status);
+        k_block_digits<<<n_pairs, 512, 0, st>>>(w.hval, inter, w.hdig, w.hexp, 1u);
+        if (shape == 0u) k_block_gemm<true, 1, false, true><<<sm_count, kGThreads, smem, st>>>(down, status);
+        else if (shape == 1u) k_block_gemm<true, 2, false, true><<<sm_count, kGThreads, smem, st>>>(down, status);
+        else k_block_gemm<true, 2, true, true><<<sm_count, kGThreads, smem, st>>>(down, status);
+        k_block_mix<<<dim3((hidden + 255u) / 256u, n_tokens), 256, 0, st>>>(w.d, ids, weights, top_k, shared_page != nullptr, y, hidden,
+                                                                           w.counts, x, residual ? 1u : 0u, nullptr, 1u, 0u, 0u, status, 1u);
+        *err = cudaGetLastError();
+        return 7;
+    }
     if (shape == 0u) {
-        k_block_gemm<false, 1, false><<<sm_count, kGThreads, smem, st>>>(up, status);
-        k_block_gemm<true, 1, false><<<sm_count, kGThreads, smem, st>>>(down, status);
+        k_block_gemm<false, 1, false, false><<<sm_count, kGThreads, smem, st>>>(up, status);
+        k_block_gemm<true, 1, false, false><<<sm_count, kGThreads, smem, st>>>(down, status);
     } else if (shape == 1u) {
-        k_block_gemm<false, 2, false><<<sm_count, kGThreads, smem, st>>>(up, status);
-        k_block_gemm<true, 2, false><<<sm_count, kGThreads, smem, st>>>(down, status);
+        k_block_gemm<false, 2, false, false><<<sm_count, kGThreads, smem, st>>>(up, status);
+        k_block_gemm<true, 2, false, false><<<sm_count, kGThreads, smem, st>>>(down, status);
     } else {
-        k_block_gemm<false, 2, true><<<sm_count, kGThreads, smem, st>>>(up, status);
-        k_block_gemm<true, 2, true><<<sm_count, kGThreads, smem, st>>>(down, status);
+        k_block_gemm<false, 2, true, false><<<sm_count, kGThreads, smem, st>>>(up, status);
+        k_block_gemm<true, 2, true, false><<<sm_count, kGThreads, smem, st>>>(down, status);
     }
     if (pairs_out) {
         *err = cudaGetLastError();
         return 4;
     }
     k_block_mix<<<dim3((hidden + 255u) / 256u, n_tokens), 256, 0, st>>>(w.d, ids, weights, top_k, shared_page != nullptr, y, hidden,
-                                                                       w.counts, x, residual ? 1u : 0u, nullptr, 1u, 0u, 0u, status);
+                                                                       w.counts, x, residual ? 1u : 0u, nullptr, 1u, 0u, 0u, status, 0u);
     *err = cudaGetLastError();
     return 5;
 }
@@ -853,7 +952,7 @@ cudaError_t launch_block_mix(cudaStream_t st, const float *pairs, const int32_t 
                              const BlockEp *ep, uint32_t *status) {
     k_block_mix<<<dim3((hidden + 255u) / 256u, n_tokens), 256, 0, st>>>(pairs, ids, weights, top_k, has_shared, y, hidden, counts, x,
                                                                        x ? 1u : 0u, ep ? ep->flags : nullptr, ep ? ep->world : 1u,
-                                                                       ep ? ep->call : 0u, ep ? ep->wait_limit : 0u, status);
+                                                                       ep ? ep->call : 0u, ep ? ep->wait_limit : 0u, status, 0u);
     return cudaGetLastError();
 }
 

@@ -599,6 +599,12 @@ class MoeBlock:
         """The calls that follow write y = x + moe(x); y may then be x."""
         check(L.lib().s14_block_set_residual(self._h, 1 if residual else 0))
 
+    def set_semantics(self, official: bool) -> None:
+        """The experts' arithmetic of the calls that follow: this library's F32 one, or the official one
+        (s14_first_real_token/executor.py:712-743: E4M3FN activation quantisation per 128 elements, BF16
+        results, the route weight before w2, y = moe_branch in BF16 values).  One GPU only."""
+        check(L.lib().s14_block_set_semantics(self._h, 1 if official else 0))
+
     def last_counts(self):
         """(chunks, up items, down items, bad id flag) of the last call; synchronise the stream first."""
         out = (C.c_uint32 * 4)()

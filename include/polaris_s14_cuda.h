@@ -492,6 +492,25 @@ S14_API int32_t s14_block_destroy(s14_block *blk);
 /* residual != 0: the calls that follow write y = x + moe(x), the step of a stack of layers
  * (h <- h + moe_l(h), as s14_stack_create's `residual`); y may then be the same buffer as x. */
 S14_API int32_t s14_block_set_residual(s14_block *blk, int32_t residual);
+/* The arithmetic of the block's experts.  S14_BLOCK_SEMANTICS_F32 (the default): F32 values, every matvec's
+ * exact sum rounded once, the route weight applied in the mix (examples/s14_vulkan_numeric.rs:929-947).
+ * S14_BLOCK_SEMANTICS_OFFICIAL: the official expert arithmetic of
+ * fast16/research/polaris_meridian_v1/s14_first_real_token/executor.py:712-743 (finish_layer) with
+ * l42_real_reference/l42_reference.py:389-419 (_activation_quant, _linear_fp4): every linear quantises its
+ * input per 128 elements to E4M3FN with a power-of-two scale and rounds its result to BF16; gate and up in
+ * BF16, the limited SwiGLU in F32; a routed expert's hidden values are multiplied by the route weight and
+ * rounded to BF16 BEFORE w2 (the shared expert's are rounded only); the experts' BF16 outputs are added in
+ * F32 in route order, the shared expert last, and y is that sum rounded to BF16 (moe_branch; with the
+ * residual switch y = x + moe_branch).  The dot products are exact sums rounded once to F32, where the
+ * reference's are a float32 BLAS call in the library's order.  x holds F32 values (the reference's are
+ * BF16-valued).  MXFP4 pages, the shared expert's included; s14_cmd_moe_block and s14_cmd_routed_moe_block
+ * only: the expert-parallel calls refuse an official block, and an official block takes no exchange.
+ * Seven launches per layer instead of five (the quantisation and digit rows of the hidden values are a
+ * launch of their own, after a clearing of their buffer of 7 * max_tokens * intermediate floats, which the
+ * first switch to the official arithmetic allocates). */
+#define S14_BLOCK_SEMANTICS_F32 0u
+#define S14_BLOCK_SEMANTICS_OFFICIAL 1u
+S14_API int32_t s14_block_set_semantics(s14_block *blk, uint32_t semantics);
 S14_API int32_t s14_cmd_moe_block(s14_ctx *ctx, void *stream, s14_block *blk, const s14_moe_layer_desc *desc);
 S14_API int32_t s14_cmd_routed_moe_block(s14_ctx *ctx, void *stream, s14_block *blk, const s14_routed_layer_desc *desc);
 /* Expert parallel (no counterpart in the reference; partition as s14_cmd_routed_moe_experts_ep: expert e

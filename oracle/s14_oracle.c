@@ -336,6 +336,97 @@ S14O_API void s14o_moe_layer_acc64(const float *x, const uint8_t *const *routed_
     }
 }
 
+/* torch's .to(torch.bfloat16).float(): nearest, ties to even (l42_reference.py:356-358). */
+static float bf16_round(float f) {
+    uint32_t u;
+    memcpy(&u, &f, 4);
+    if ((u & 0x7F800000u) == 0x7F800000u) return f;
+    u += 0x7FFFu + ((u >> 16) & 1u);
+    u &= 0xFFFF0000u;
+    memcpy(&f, &u, 4);
+    return f;
+}
+
+/* The nearest E4M3FN value (ties to even) of |v| <= 448: three mantissa bits, subnormals are
+ * multiples of 2^-9 below 2^-6 (torch's .to(torch.float8_e4m3fn).float()). */
+static float e4m3fn_round(float v) {
+    const float a = fabsf(v);
+    float q;
+    if (a < 0.015625f) {
+        q = rintf(a * 512.0f) / 512.0f;
+    } else {
+        int e;
+        (void)frexpf(a, &e); /* a = m * 2^e, m in [0.5, 1) */
+        const float step = ldexpf(1.0f, e - 4);
+        q = rintf(a / step) * step;
+    }
+    return copysignf(q, v);
+}
+
+/* l42_reference.py:389-403 (_activation_quant): per group of 128 elements amax = max(|x|, 1e-4),
+ * scale = 2^ceil(log2(amax / 448)) with the F32 quotient and the F32 logarithm, the elements divided
+ * by the scale, clipped to +-448, rounded to E4M3FN and multiplied by the scale again.  The F32
+ * logarithm is taken as the double one rounded to F32 (numpy's log2 of a float32 is within an ulp of
+ * that; the two can differ only where amax / 448 is within a few ulps of a power of two).  n must
+ * be a multiple of 128. */
+S14O_API void s14o_act_quant(const float *x, uint32_t n, float *out) {
+    for (uint32_t g = 0; g + 128 <= n; g += 128) {
+        float amax = 0.0f;
+        for (uint32_t i = 0; i < 128; ++i) amax = fmaxf(amax, fabsf(x[g + i]));
+        amax = fmaxf(amax, 1e-4f);
+        const float r = amax / 448.0f;
+        const float scale = ldexpf(1.0f, (int)ceilf((float)log2((double)r)));
+        for (uint32_t i = 0; i < 128; ++i) {
+            float v = x[g + i] / scale;
+            v = fminf(fmaxf(v, -448.0f), 448.0f);
+            out[g + i] = e4m3fn_round(v) * scale;
+        }
+    }
+}
+
+/* The official expert arithmetic of one token (s14_first_real_token/executor.py:712-743 finish_layer with
+ * l42_reference.py:405-419 _linear_fp8 / _linear_fp4): every linear quantises its input per 128
+ * elements (s14o_act_quant), multiplies with the dequantised weights and rounds the result to BF16;
+ * hidden = limited SwiGLU of the BF16 gate and up in F32; a routed expert's hidden values are
+ * multiplied by its route weight and rounded to BF16 BEFORE w2, the shared expert's are rounded
+ * only; the BF16 outputs are added in F32 in route order, the shared expert last, and the sum is
+ * rounded to BF16 (moe_branch).  The reference's product `activation @ weight.T` is a float32 BLAS
+ * call whose summation order is the library's; here every dot product is summed in double and
+ * rounded to F32 once (the quantised activations have four significant bits, the weights two: the
+ * double sums are exact at the magnitudes of this path), then to BF16.  shared_kind: 0 MXFP4 page,
+ * 1 FP8 page (the reference's), 2 none.  work: 2*hidden + 4*inter floats, work64: 2*max(hidden,
+ * inter) doubles. */
+S14O_API void s14o_official_moe_layer(const float *x, const uint8_t *const *routed_pages,
+                                      const float *route_weights, uint32_t n_routed,
+                                      const uint8_t *shared_page, int shared_kind, uint32_t hidden,
+                                      uint32_t inter, float *work, double *work64, float *branch) {
+    const uint32_t big = hidden > inter ? hidden : inter;
+    float *gate = work, *up = work + inter, *h = work + 2 * (size_t)inter, *hq = work + 3 * (size_t)inter;
+    float *xq = work + 4 * (size_t)inter, *down = xq + hidden;
+    double *xd = work64, *yd = work64 + big;
+    s14o_act_quant(x, hidden, xq);
+    for (uint32_t i = 0; i < hidden; ++i) branch[i] = 0.0f;
+    for (uint32_t e = 0; e <= n_routed; ++e) {
+        const int is_shared = (e == n_routed);
+        if (is_shared && shared_kind == 2) break;
+        const uint8_t *page = is_shared ? shared_page : routed_pages[e];
+        const int kind = (is_shared && shared_kind == 1) ? 1 : 0;
+        s14o_expert_view v = kind ? fp8_view(page, hidden, inter) : mxfp4_view(page, hidden, inter);
+        matvec_acc64(xq, v.w1, v.s1, kind, inter, hidden, xd, yd, gate);
+        matvec_acc64(xq, v.w3, v.s3, kind, inter, hidden, xd, yd, up);
+        for (uint32_t i = 0; i < inter; ++i) {
+            gate[i] = bf16_round(gate[i]);
+            up[i] = bf16_round(up[i]);
+        }
+        s14o_swiglu_limit(gate, up, inter, h);
+        for (uint32_t i = 0; i < inter; ++i) h[i] = bf16_round(is_shared ? h[i] : h[i] * route_weights[e]);
+        s14o_act_quant(h, inter, hq);
+        matvec_acc64(hq, v.w2, v.s2, kind, hidden, inter, xd, yd, down);
+        for (uint32_t i = 0; i < hidden; ++i) branch[i] += bf16_round(down[i]);
+    }
+    for (uint32_t i = 0; i < hidden; ++i) branch[i] = bf16_round(branch[i]);
+}
+
 static float bf16_to_f32(uint16_t bits) {
     uint32_t u = (uint32_t)bits << 16;
     float f;
@@ -453,15 +544,6 @@ S14O_API int s14o_error_stats(const float *actual, const float *expected, uint64
  * Python code itself are met within a few F32 ulps (tests/test_oracle_golden.py states the bound).
  * dtype 0: F32 streams; 1: BF16 streams (the reference's state is BF16 [1,1,4,4096]; results are
  * rounded to BF16 where the Python code casts back with .to(original_dtype) / type_as). */
-static inline float bf16_round(float v) {
-    uint32_t b;
-    memcpy(&b, &v, 4);
-    if ((b & 0x7F800000u) == 0x7F800000u) return v; /* inf / nan as they are */
-    b += 0x7FFFu + ((b >> 16) & 1u);
-    b &= 0xFFFF0000u;
-    memcpy(&v, &b, 4);
-    return v;
-}
 static inline float stream_get(const void *p, size_t i, int dtype) {
     return dtype ? bf16_to_f32(((const uint16_t *)p)[i]) : ((const float *)p)[i];
 }

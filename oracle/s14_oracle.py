@@ -190,6 +190,31 @@ def moe_layer_acc64(x, routed_pages, route_weights, shared_page, shared_kind: in
     return y
 
 
+def act_quant(x) -> np.ndarray:
+    """l42_reference.py:389-403: the E4M3FN quantisation of activations per 128 elements (last axis)."""
+    x = _f32(x)
+    assert x.shape[-1] % 128 == 0
+    out = np.empty_like(x)
+    lib().s14o_act_quant(_p(x), C.c_uint32(x.size), _p(out))
+    return out
+
+
+def official_moe_layer(x, routed_pages, route_weights, shared_page, shared_kind: int, hidden: int,
+                       inter: int) -> np.ndarray:
+    """executor.py:712-743: moe_branch of one token with the official roundings (exact dot products)."""
+    x = _f32(x)
+    pages, arr = _page_ptrs(routed_pages)
+    rw = _f32(route_weights)
+    shared = _u8(shared_page) if shared_page is not None else np.zeros(1, np.uint8)
+    work = np.empty(2 * hidden + 4 * inter, np.float32)
+    work64 = np.empty(2 * max(hidden, inter), np.float64)
+    y = np.empty(hidden, np.float32)
+    lib().s14o_official_moe_layer(_p(x), arr, _p(rw), C.c_uint32(len(pages)), _p(shared),
+                                  C.c_int(shared_kind), C.c_uint32(hidden), C.c_uint32(inter), _p(work),
+                                  _p(work64), _p(y))
+    return y
+
+
 def router(x, wr_bf16_bits, bias, score_fn: int = 0, top_k: int = 6, route_scale: float = 1.0):
     """Returns (ids int32[top_k], weights f32[top_k], scores f32[E], select f32[E])."""
     x = _f32(x)

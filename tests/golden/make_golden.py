@@ -29,7 +29,10 @@ stored here.  Cases:
   ``hc_pre``, ``hc_post``, ``hc_head_reduce``, ``official_rms_norm``) on the reference's own
   fixtures (tests/test_primitives.py:126-141, tests/test_final_head.py:22-46) and on seeded streams
   of the model's size in F32 and BF16; the hash-routed layers' weights from the torch expressions
-  of executor.py:638-668.
+  of executor.py:638-668;
+* the official expert arithmetic: ``_activation_quant`` (l42_reference.py:389-403) on seeded rows and
+  ``finish_layer`` (s14_first_real_token/executor.py:712-743) itself on synthetic pages of hidden 4096 x
+  intermediate 512, with an MXFP4 and with an FP8 shared expert.
 """
 from __future__ import annotations
 
@@ -273,6 +276,77 @@ def main(reference_root: str) -> None:
     out["nf_logits"] = logits.numpy().reshape(2, 768)
     out["nf_normalized"] = normalized.float().numpy().reshape(2, 1024)
     out["nf_pre"] = npre.numpy().reshape(2, 4)
+
+    # official expert semantics: the reference's own _activation_quant, _linear_fp4 / _linear_fp8 and
+    # finish_layer (l42_reference.py:389-419, s14_first_real_token/executor.py:712-743) run on synthetic
+    # pages; only the two weight loaders (which read checkpoint files) are replaced by the dequantisation
+    # of the synthetic tensors, written as l42_reference.py:360-387 does it
+    from fast16.research.polaris_meridian_v1.l42_real_reference import l42_reference as l42
+    from fast16.research.polaris_meridian_v1.s14_first_real_token import executor as ex
+
+    g = synth.rng(1011)
+    aq_x = synth.activations(g, 6, 512)
+    aq_x[1] *= np.float32(1e-5)          # below the 1e-4 floor of amax
+    aq_x[2] *= np.float32(300.0)
+    aq_x[3, :128] = 0.0                  # an all-zero group
+    aq_x[4, :128] = np.clip(aq_x[4, :128], -1.0, 1.0) * np.float32(100.0)
+    aq_x[4, 0] = np.float32(112.0)       # amax / 448 an exact power of two
+    aq_x[5] = synth.bf16_bits_to_f32(synth.f32_to_bf16_bits(aq_x[5]))
+    out["aq_x"] = aq_x
+    out["aq_y"] = ex.NativeLayerReference._activation_quant(aq_x)
+
+    hidden, inter = 4096, 512            # finish_layer fixes the hidden size
+    g = synth.rng(1012)
+    lay4 = ExpertPageLayout(hidden, inter, 0)
+    lay8 = ExpertPageLayout(hidden, inter, 1)
+    of_pages = [synth.mxfp4_expert_page(g, hidden, inter) for _ in range(7)]
+    of_page8 = synth.fp8_expert_page(g, hidden, inter)
+    of_x = synth.bf16_bits_to_f32(synth.f32_to_bf16_bits(synth.activations(g, 2, hidden)))
+    of_w = np.asarray([[0.52, 0.33, 0.27, 0.18, 0.12, 0.08], [0.29, 0.26, 0.25, 0.24, 0.23, 0.23]], dtype=np.float32)
+    out["of_inputs_sha256"] = np.frombuffer(_digest(*of_pages, of_page8, of_x), dtype=np.uint8)
+    out["of_w"] = of_w
+
+    def dense4(packed, scales):
+        weight = np.empty((packed.shape[0], packed.shape[1] * 2), dtype=np.float32)
+        weight[:, 0::2] = l42._FP4_LUT[packed & 15]
+        weight[:, 1::2] = l42._FP4_LUT[packed >> 4]
+        weight = weight.reshape(scales.shape[0], scales.shape[1], 32)
+        weight *= np.exp2(scales.astype(np.float32) - 127)[:, :, None]
+        return weight.reshape(packed.shape[0], packed.shape[1] * 2)
+
+    def dense8(packed, scales):
+        expanded = np.repeat(np.repeat(np.exp2(scales.astype(np.float32) - 127), 128, 0), 128, 1)
+        return l42._FP8_LUT[packed] * expanded[: packed.shape[0], : packed.shape[1]]
+
+    shapes = {"w1": (inter, hidden), "w3": (inter, hidden), "w2": (hidden, inter)}
+    table = {}
+    for e, page in enumerate(of_pages):
+        parts = lay4.split(page)
+        for name, (n, k) in shapes.items():
+            prefix = ("layers.5.ffn.experts.%d." % e if e < 6 else "mxfp4_shared.") + name
+            table[prefix] = dense4(np.ascontiguousarray(parts[name]).reshape(n, k // 2),
+                                   np.ascontiguousarray(parts["s" + name[1]]).reshape(n, k // 32))
+    parts = lay8.split(of_page8)
+    for name, (n, k) in shapes.items():
+        table["fp8_shared." + name] = dense8(np.ascontiguousarray(parts[name]).reshape(n, k),
+                                             np.ascontiguousarray(parts["s" + name[1]]).reshape((n + 127) // 128, (k + 127) // 128))
+
+    for shared_name in ("mxfp4_shared", "fp8_shared"):
+        ref = object.__new__(ex.NativeLayerReference)
+        ref.layer = 5
+        ref._weight_fp4 = lambda prefix: table[prefix]
+        ref._weight_fp8 = lambda prefix, _s=shared_name: table[prefix.replace("layers.5.ffn.shared_experts", _s)]
+        branches = []
+        for tok in range(2):
+            pending = ex.PendingLayer(
+                post_attention_state=torch.zeros(1, 1, 4, hidden, dtype=torch.bfloat16),
+                post_ffn=torch.ones(1, 1, 4), comb_ffn=torch.eye(4).reshape(1, 1, 4, 4),
+                ffn_input=torch.from_numpy(of_x[tok]).to(torch.bfloat16).reshape(1, 1, hidden),
+                route_ids=[0, 1, 2, 3, 4, 5], route_weights=[float(v) for v in of_w[tok]], route_source="golden",
+                attention_branch=None, runtime_state=None)
+            branch, _ = ref.finish_layer(pending)
+            branches.append(branch.float().numpy().reshape(hidden))
+        out["of_branch_" + shared_name] = np.stack(branches)
 
     path = os.path.join(HERE, "s14_golden.npz")
     np.savez_compressed(path, **out)
