@@ -1861,6 +1861,10 @@ extern "C" int32_t s14_block_create(s14_ctx *ctx, uint32_t hidden, uint32_t inte
     CUDA_OK(cudaMalloc((void **)&blk->w.hdig, P * (inter >> 8) * 2048u));
     CUDA_OK(cudaMalloc((void **)&blk->w.hexp, P * (inter >> 5)));
     CUDA_OK(cudaMalloc((void **)&blk->w.d, P * hidden * sizeof(float)));
+    // the pairs' hidden values as F32 (large blocks and the official arithmetic); zero, so that the slot of a
+    // pair without a route always holds a finite value
+    CUDA_OK(cudaMalloc((void **)&blk->w.hval, P * inter * sizeof(float)));
+    CUDA_OK(cudaMemset(blk->w.hval, 0, P * inter * sizeof(float)));
     CUDA_OK(cudaMalloc((void **)&blk->scores, T * S14_N_ROUTED_EXPERTS * sizeof(float)));
     CUDA_OK(cudaMalloc((void **)&blk->select, T * S14_N_ROUTED_EXPERTS * sizeof(float)));
     CUDA_OK(cudaMalloc((void **)&blk->counter, 64));
@@ -2163,8 +2167,7 @@ extern "C" int32_t s14_cmd_moe_block_mix(s14_ctx *ctx, void *stream, s14_block *
 }
 
 // The arithmetic of the block's experts: this library's (F32 values, exact sums, one rounding per matvec) or
-// the official one of s14_first_real_token/executor.py:712-743.  The official one needs one more buffer
-// (the pairs' weighted hidden values, 7 * max_tokens * intermediate floats), allocated on first use.
+// the official one of s14_first_real_token/executor.py:712-743.
 extern "C" int32_t s14_block_set_semantics(s14_block *blk, uint32_t semantics) {
     S14_TRY
     if (!blk) return fail(S14_ERR_CONTRACT, "s14_block_set_semantics: blk is NULL");
@@ -2172,10 +2175,6 @@ extern "C" int32_t s14_block_set_semantics(s14_block *blk, uint32_t semantics) {
         return fail(S14_ERR_CONTRACT, "s14_block_set_semantics: unknown semantics");
     if (semantics == S14_BLOCK_SEMANTICS_OFFICIAL) {
         if (blk->ep.buf) return fail(S14_ERR_CONTRACT, "s14_block_set_semantics: the official arithmetic runs on one GPU (the block has an exchange)");
-        if (!blk->w.hval) {
-            CUDA_OK(cudaSetDevice(blk->device));
-            CUDA_OK(cudaMalloc((void **)&blk->w.hval, (size_t)blk->max_tokens * 7u * blk->inter * sizeof(float)));
-        }
     }
     blk->official = semantics == S14_BLOCK_SEMANTICS_OFFICIAL;
     return S14_OK;

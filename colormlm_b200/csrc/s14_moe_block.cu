@@ -69,6 +69,11 @@ constexpr uint32_t kGBarFin = kGBarSfb + 2;
 constexpr uint32_t kGBars = kGBarFin + 1;
 constexpr uint32_t kPairsPerToken = S14_EXPERTS_PER_TOKEN + 1;   // pair = token * 7 + position in the mix (6: shared)
 
+// What the up kernel's epilogue leaves (the down kernel: kModeOfficial rounds its rows to BF16, the others do not)
+constexpr uint32_t kModeFused = 0u;      // the digit rows of the hidden values, laid out by the epilogue itself (small blocks)
+constexpr uint32_t kModeOfficial = 1u;   // the official arithmetic's BF16 hidden values, times the route weight
+constexpr uint32_t kModeValues = 2u;     // the F32 hidden values; a digits launch follows (large blocks)
+
 struct GemmArgs {
     const BlockChunk *chunks;
     const uint32_t *n_items;    // device memory: written by the grouping kernel (chunks x slices or row tiles)
@@ -85,8 +90,8 @@ struct GemmArgs {
     unsigned long long *flag_peer[kMaxEpWorld];
     unsigned int *ep_counter;   // this GPU's arrival counter, zero at rest
     uint32_t ep_world, ep_rank, ep_call;
-    // Official expert arithmetic (up kernel): the pairs' weighted hidden values, BF16-valued F32 [pair][inter],
-    // and the routes' weights [token][top_k]
+    // Up kernel, kModeOfficial / kModeValues: the pairs' hidden values [pair][inter] (official: weighted and
+    // BF16-valued) and, for the official arithmetic, the routes' weights [token][top_k]
     float *hval;
     const float *weights;
     uint32_t top_k;
@@ -263,7 +268,7 @@ struct ItemRec {
 //     kWide (many tokens per expert): a chunk holds up to TWELVE tokens; issuing thread m takes the tokens
 //     6 m .. 6 m + 5 (its own rows of the tile region, its own scale atoms, N = 96) for EVERY stage: fewer
 //     passes over an expert's page.  Otherwise chunks of six and even / odd stages as with one row tile.
-template <bool kDown, uint32_t kMt, bool kWide, bool kOfficial>
+template <bool kDown, uint32_t kMt, bool kWide, uint32_t kMode>
 __global__ void __launch_bounds__(kGThreads, 1)
 k_block_gemm(const __grid_constant__ GemmArgs a, uint32_t *status) {
     extern __shared__ __align__(1024) uint8_t smem[];
@@ -534,7 +539,7 @@ k_block_gemm(const __grid_constant__ GemmArgs a, uint32_t *status) {
                         for (uint32_t t = 0; t < kTok; ++t) {
                             if (t < nt) {
                                 const size_t at = (size_t)pair[t] * a.hidden + idx * 128u + row;
-                                const float o = kOfficial ? bf16_round(v[mt][t]) : v[mt][t];   // official: a linear's result is BF16
+                                const float o = kMode == kModeOfficial ? bf16_round(v[mt][t]) : v[mt][t];   // official: a linear's result is BF16
                                 if (a.ep_world > 1u) {
 #pragma unroll 1
                                     for (uint32_t p = 0; p < a.ep_world; ++p) a.out_peer[p][at] = o;
@@ -549,27 +554,35 @@ k_block_gemm(const __grid_constant__ GemmArgs a, uint32_t *status) {
                         // each hands the other the values it lacks
                         const uint32_t el = row & 63u, par = row >> 6, blk2 = warp & 1u;
                         if (mt) epi_sync();  // the row tile before has been written out
-                        if constexpr (kOfficial) {
-                            // official arithmetic (s14_first_real_token/executor.py:712-743): gate and up rounded to
-                            // BF16, the limited SwiGLU in F32, times the route's weight (not for the shared expert),
-                            // rounded to BF16; the values go out as they are - their quantisation per 128 elements
-                            // and their digit rows are the next launch's
+                        if constexpr (kMode != kModeFused) {
+                            // The hidden values go out as F32 values; their digit rows are the next launch's
+                            // (large blocks: this epilogue then costs a third of the one that lays out the digit
+                            // rows itself, and it is what the MMAs of the next item wait for).  Official
+                            // arithmetic (s14_first_real_token/executor.py:712-743): gate and up rounded to BF16,
+                            // the limited SwiGLU in F32, times the route's weight (not for the shared expert),
+                            // rounded to BF16; the next launch also quantises them per 128 elements.
+                            constexpr bool kOff = kMode == kModeOfficial;
 #pragma unroll
                             for (uint32_t t = 0; t < kTok; ++t)
-                                if (t < nt && (t & 1u) != par) s_up[t][el] = bf16_round(v[mt][t]);
+                                if (t < nt && (t & 1u) != par) s_up[t][el] = kOff ? bf16_round(v[mt][t]) : v[mt][t];
                             epi_sync();
 #pragma unroll
                             for (uint32_t t = 0; t < kTok; ++t) {
                                 if (t < nt && (t & 1u) == par) {
-                                    const float other = s_up[t][el], mine = bf16_round(v[mt][t]);
+                                    const float other = s_up[t][el], mine = kOff ? bf16_round(v[mt][t]) : v[mt][t];
                                     const float hv = par ? swiglu_limit_f32(other, mine) : swiglu_limit_f32(mine, other);
-                                    const uint32_t pr = pair[t], tok = pr / kPairsPerToken, pos = pr - tok * kPairsPerToken;
-                                    const float wh = pos < S14_EXPERTS_PER_TOKEN ? __fmul_rn(hv, __ldg(a.weights + tok * a.top_k + pos)) : hv;
-                                    a.hval[(size_t)pr * a.inter + idx * 64u + el] = bf16_round(wh);
+                                    const uint32_t pr = pair[t];
+                                    float wh = hv;
+                                    if constexpr (kOff) {
+                                        const uint32_t tok = pr / kPairsPerToken, pos = pr - tok * kPairsPerToken;
+                                        if (pos < S14_EXPERTS_PER_TOKEN) wh = __fmul_rn(hv, __ldg(a.weights + tok * a.top_k + pos));
+                                        wh = bf16_round(wh);
+                                    }
+                                    a.hval[(size_t)pr * a.inter + idx * 64u + el] = wh;
                                 }
                             }
                         }
-                        if constexpr (!kOfficial) {
+                        if constexpr (kMode == kModeFused) {
 #pragma unroll
                         for (uint32_t t = 0; t < kTok; ++t)
                             if (t < nt && (t & 1u) != par) s_up[t][el] = v[mt][t];
@@ -616,7 +629,7 @@ k_block_gemm(const __grid_constant__ GemmArgs a, uint32_t *status) {
                                 *reinterpret_cast<uint2 *>(a.hdig + (size_t)pair[t] * KD * 2048u + o) = c8;
                             }
                         }
-                        }  // (this library's arithmetic)
+                        }  // (digit rows laid out here)
                     }
                 }
             }
@@ -811,11 +824,10 @@ size_t block_dynamic_limit(uint32_t shape) {
     if (g_block_limit[dev][shape]) return g_block_limit[dev][shape];
     int optin = 0;
     if (cudaDeviceGetAttribute(&optin, cudaDevAttrMaxSharedMemoryPerBlockOptin, dev) != cudaSuccess) return 0;
-    // the four kernels of a shape (up and down, this library's arithmetic and the official one) get the same limit
-    auto set_up = [&](auto up, auto down, auto up_official, auto down_official) -> size_t {
+    // the kernels of a shape (up in its three modes, down in two) get the same limit
+    auto set_up = [&](std::initializer_list<const void *> fns) -> size_t {
         size_t fixed = 0;
         cudaFuncAttributes fa;
-        const void *fns[4] = {(const void *)up, (const void *)down, (const void *)up_official, (const void *)down_official};
         for (const void *fn : fns) {
             if (cudaFuncGetAttributes(&fa, fn) != cudaSuccess) return 0;
             if (fa.sharedSizeBytes > fixed) fixed = fa.sharedSizeBytes;
@@ -826,12 +838,12 @@ size_t block_dynamic_limit(uint32_t shape) {
             if (cudaFuncSetAttribute(fn, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)most) != cudaSuccess) return 0;
         return most;
     };
-    const size_t most = shape == 0u   ? set_up(k_block_gemm<false, 1, false, false>, k_block_gemm<true, 1, false, false>,
-                                               k_block_gemm<false, 1, false, true>, k_block_gemm<true, 1, false, true>)
-                        : shape == 1u ? set_up(k_block_gemm<false, 2, false, false>, k_block_gemm<true, 2, false, false>,
-                                               k_block_gemm<false, 2, false, true>, k_block_gemm<true, 2, false, true>)
-                                      : set_up(k_block_gemm<false, 2, true, false>, k_block_gemm<true, 2, true, false>,
-                                               k_block_gemm<false, 2, true, true>, k_block_gemm<true, 2, true, true>);
+#define S14_BLOCK_KERNELS(MT, WIDE)                                                                                              \
+    set_up({(const void *)k_block_gemm<false, MT, WIDE, kModeFused>, (const void *)k_block_gemm<false, MT, WIDE, kModeOfficial>, \
+            (const void *)k_block_gemm<false, MT, WIDE, kModeValues>, (const void *)k_block_gemm<true, MT, WIDE, kModeFused>,    \
+            (const void *)k_block_gemm<true, MT, WIDE, kModeOfficial>})
+    const size_t most = shape == 0u ? S14_BLOCK_KERNELS(1, false) : (shape == 1u ? S14_BLOCK_KERNELS(2, false) : S14_BLOCK_KERNELS(2, true));
+#undef S14_BLOCK_KERNELS
     g_block_limit[dev][shape] = most;
     return most;
 }
@@ -906,45 +918,40 @@ int launch_moe_block(cudaStream_t st, int sm_count, const BlockWork &w, const fl
         down.ep_rank = ep->rank;
         down.ep_call = ep->call;
     }
-    if (official) {
-        // the up kernel leaves the pairs' weighted hidden values; a second digits launch quantises them per 128
-        // elements and lays out their digit rows (pairs without a route: zeros)
+    // Small blocks: the up epilogue lays out the digit rows of the hidden values itself.  Large blocks and the
+    // official arithmetic: it leaves the values, and a second digits launch (which also quantises them per 128
+    // elements for the official arithmetic) lays out the rows of all pairs' slots (a slot without a route holds
+    // zeros or an earlier call's values: finite numbers nobody reads the rows of).
+    const bool values = official || (shape != 0u && w.hval != nullptr);
+    int launches = 4;
+    if (values) {
         up.hval = w.hval;
         up.weights = weights;
         up.top_k = top_k;
-        const uint32_t n_pairs = n_tokens * kPairsPerToken;
-        *err = cudaMemsetAsync(w.hval, 0, (size_t)n_pairs * inter * sizeof(float), st);
-        if (*err != cudaSuccess) return 2;
-        if (shape == 0u) k_block_gemm<false, 1, false, true><<<sm_count, kGThreads, smem, st>>>(up, status);
-        else if (shape == 1u) k_block_gemm<false, 2, false, true><<<sm_count, kGThreads, smem, st>>>(up, status);
-        else k_block_gemm<false, 2, true, true><<<sm_count, kGThreads, smem, st>>>(up, status);
-        k_block_digits<<<n_pairs, 512, 0, st>>>(w.hval, inter, w.hdig, w.hexp, 1u);
-        if (shape == 0u) k_block_gemm<true, 1, false, true><<<sm_count, kGThreads, smem, st>>>(down, status);
-        else if (shape == 1u) k_block_gemm<true, 2, false, true><<<sm_count, kGThreads, smem, st>>>(down, status);
-        else k_block_gemm<true, 2, true, true><<<sm_count, kGThreads, smem, st>>>(down, status);
-        k_block_mix<<<dim3((hidden + 255u) / 256u, n_tokens), 256, 0, st>>>(w.d, ids, weights, top_k, shared_page != nullptr, y, hidden,
-                                                                           w.counts, x, residual ? 1u : 0u, nullptr, 1u, 0u, 0u, status, 1u);
-        *err = cudaGetLastError();
-        return 7;
+        ++launches;
     }
-    if (shape == 0u) {
-        k_block_gemm<false, 1, false, false><<<sm_count, kGThreads, smem, st>>>(up, status);
-        k_block_gemm<true, 1, false, false><<<sm_count, kGThreads, smem, st>>>(down, status);
-    } else if (shape == 1u) {
-        k_block_gemm<false, 2, false, false><<<sm_count, kGThreads, smem, st>>>(up, status);
-        k_block_gemm<true, 2, false, false><<<sm_count, kGThreads, smem, st>>>(down, status);
-    } else {
-        k_block_gemm<false, 2, true, false><<<sm_count, kGThreads, smem, st>>>(up, status);
-        k_block_gemm<true, 2, true, false><<<sm_count, kGThreads, smem, st>>>(down, status);
-    }
+#define S14_BLOCK_UP(MT, WIDE)                                                                                  \
+    do {                                                                                                        \
+        if (official) k_block_gemm<false, MT, WIDE, kModeOfficial><<<sm_count, kGThreads, smem, st>>>(up, status);   \
+        else if (values) k_block_gemm<false, MT, WIDE, kModeValues><<<sm_count, kGThreads, smem, st>>>(up, status);  \
+        else k_block_gemm<false, MT, WIDE, kModeFused><<<sm_count, kGThreads, smem, st>>>(up, status);              \
+        if (values) k_block_digits<<<n_tokens * kPairsPerToken, 512, 0, st>>>(w.hval, inter, w.hdig, w.hexp, official ? 1u : 0u); \
+        if (official) k_block_gemm<true, MT, WIDE, kModeOfficial><<<sm_count, kGThreads, smem, st>>>(down, status);  \
+        else k_block_gemm<true, MT, WIDE, kModeFused><<<sm_count, kGThreads, smem, st>>>(down, status);             \
+    } while (0)
+    if (shape == 0u) S14_BLOCK_UP(1, false);
+    else if (shape == 1u) S14_BLOCK_UP(2, false);
+    else S14_BLOCK_UP(2, true);
+#undef S14_BLOCK_UP
     if (pairs_out) {
         *err = cudaGetLastError();
-        return 4;
+        return launches;
     }
     k_block_mix<<<dim3((hidden + 255u) / 256u, n_tokens), 256, 0, st>>>(w.d, ids, weights, top_k, shared_page != nullptr, y, hidden,
-                                                                       w.counts, x, residual ? 1u : 0u, nullptr, 1u, 0u, 0u, status, 0u);
+                                                                       w.counts, x, residual ? 1u : 0u, nullptr, 1u, 0u, 0u, status,
+                                                                       official ? 1u : 0u);
     *err = cudaGetLastError();
-    return 5;
+    return launches + 1;
 }
 
 cudaError_t launch_block_mix(cudaStream_t st, const float *pairs, const int32_t *ids, const float *weights, uint32_t n_tokens,

@@ -471,13 +471,14 @@ S14_API int32_t s14_routed_moe_layer_host(s14_ctx *ctx, const s14_routed_layer_d
  * two tokens for blocks of up to 12 tokens, of twelve for blocks with at least three (token, route)
  * pairs per expert, else of six; an expert's later chunks find the page in the
  * L2): per layer five launches - digit rows of the tokens, grouping of the (token, route) pairs by
- * expert, the w1 | w3 contraction with SwiGLU, the w2 contraction, the ordered mix - the two
+ * expert, the w1 | w3 contraction with SwiGLU, the w2 contraction, the ordered mix (blocks of more than 12
+ * tokens: six, the digit rows of the hidden values being a launch of their own) - the two
  * contractions on tcgen05 kind::mxf4.block_scale with N = 16 digit rows per token of a chunk; the
  * routed call runs two router launches first (scores of all tokens, one warp per token selects).  Every token's y is bit-identical to what
  * s14_cmd_moe_layer / s14_cmd_routed_moe_layer give for that token alone in pairwise order.
  * MXFP4 pages only (routed and shared); hidden and intermediate multiples of 512 up to 4096.
  *   create:  allocates the workspace for up to max_tokens (<= 1024) tokens:
- *            about max_tokens * (28 * hidden + 57 * intermediate + 8 * hidden) bytes.
+ *            about max_tokens * (28 * hidden + 85 * intermediate + 8 * hidden) bytes.
  *   s14_cmd_moe_block:        routes from the host (desc->n_tokens up to max_tokens; expert_ids < 256
  *            identify the groups, a group's page is the page of one of its members).  The routes are
  *            staged through one pinned buffer of the block object: not for stream capture.
@@ -505,9 +506,8 @@ S14_API int32_t s14_block_set_residual(s14_block *blk, int32_t residual);
  * reference's are a float32 BLAS call in the library's order.  x holds F32 values (the reference's are
  * BF16-valued).  MXFP4 pages, the shared expert's included; s14_cmd_moe_block and s14_cmd_routed_moe_block
  * only: the expert-parallel calls refuse an official block, and an official block takes no exchange.
- * Seven launches per layer instead of five (the quantisation and digit rows of the hidden values are a
- * launch of their own, after a clearing of their buffer of 7 * max_tokens * intermediate floats, which the
- * first switch to the official arithmetic allocates). */
+ * The quantisation and the digit rows of the hidden values are a launch of their own between the two
+ * contractions (as for large blocks in the F32 arithmetic): six launches per layer. */
 #define S14_BLOCK_SEMANTICS_F32 0u
 #define S14_BLOCK_SEMANTICS_OFFICIAL 1u
 S14_API int32_t s14_block_set_semantics(s14_block *blk, uint32_t semantics);
