@@ -279,9 +279,8 @@ def main(reference_root: str) -> None:
 
     # official expert semantics: the reference's own _activation_quant, _linear_fp4 / _linear_fp8 and
     # finish_layer (l42_reference.py:389-419, s14_first_real_token/executor.py:712-743) run on synthetic
-    # pages; only the two weight loaders (which read checkpoint files) are replaced by the dequantisation
-    # of the synthetic tensors, written as l42_reference.py:360-387 does it
-    from fast16.research.polaris_meridian_v1.l42_real_reference import l42_reference as l42
+    # pages; only the two weight loaders (which read checkpoint files and return the dequantised F32 matrix,
+    # l42_reference.py:360-387) are replaced by the dequantisation of the synthetic tensors
     from fast16.research.polaris_meridian_v1.s14_first_real_token import executor as ex
 
     g = synth.rng(1011)
@@ -306,17 +305,21 @@ def main(reference_root: str) -> None:
     out["of_inputs_sha256"] = np.frombuffer(_digest(*of_pages, of_page8, of_x), dtype=np.uint8)
     out["of_w"] = of_w
 
+    e2m1 = np.asarray(FP4_E2M1_VALUES, dtype=np.float32)
+    all_codes = np.arange(256, dtype=np.uint8)
+    finite = (all_codes & 0x7F) != 0x7F      # 0x7F and 0xFF are NaN and never occur in the synthetic pages
+    e4m3 = np.zeros(256, dtype=np.float32)
+    e4m3[finite] = decode_fp8_e4m3fn(torch.from_numpy(all_codes[finite])).numpy()
+
     def dense4(packed, scales):
-        weight = np.empty((packed.shape[0], packed.shape[1] * 2), dtype=np.float32)
-        weight[:, 0::2] = l42._FP4_LUT[packed & 15]
-        weight[:, 1::2] = l42._FP4_LUT[packed >> 4]
-        weight = weight.reshape(scales.shape[0], scales.shape[1], 32)
-        weight *= np.exp2(scales.astype(np.float32) - 127)[:, :, None]
-        return weight.reshape(packed.shape[0], packed.shape[1] * 2)
+        # [n, k/2] bytes (low nibble = even k) and [n, k/32] UE8M0 codes -> [n, k] F32 (exact: powers of two)
+        codes = np.stack([packed & 15, packed >> 4], axis=-1).reshape(packed.shape[0], -1)
+        return np.ldexp(e2m1[codes], np.repeat(scales.astype(np.int32) - 127, 32, axis=1)).astype(np.float32)
 
     def dense8(packed, scales):
-        expanded = np.repeat(np.repeat(np.exp2(scales.astype(np.float32) - 127), 128, 0), 128, 1)
-        return l42._FP8_LUT[packed] * expanded[: packed.shape[0], : packed.shape[1]]
+        # [n, k] E4M3FN codes and one UE8M0 code per 128 x 128 block -> [n, k] F32
+        expo = np.kron(scales.astype(np.int32) - 127, np.ones((128, 128), dtype=np.int32))
+        return np.ldexp(e4m3[packed], expo[: packed.shape[0], : packed.shape[1]]).astype(np.float32)
 
     shapes = {"w1": (inter, hidden), "w3": (inter, hidden), "w2": (hidden, inter)}
     table = {}
