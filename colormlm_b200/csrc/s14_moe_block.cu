@@ -12,13 +12,14 @@
 // dot product rounded to F32, so every token's result is bit-identical to what the one-token kernel
 // and the double-accumulating CPU restatement give for that token alone.
 //
-// Five launches per layer, all plain stream order (the routed calls run the router's two launches first):
+// Five or six launches per layer, all plain stream order (the routed calls run the router's two launches first):
 //   k_block_digits   x [T, hidden] -> digit tiles (2 KB per token and 256 elements) + block exponents
-//   k_block_group    routes [T, top_k] -> chunks (expert page, <= nt_cap tokens: 2 for small blocks, else 6);
-//                    an item index decodes to (chunk, slice or row tile) from the chunk records
+//   k_block_group    routes [T, top_k] -> chunks (expert page, <= nt_cap tokens: 2 for small blocks, else 6 or
+//                    12); an item index decodes to (chunk, slice or row tile) from the chunk records
 //   k_block_gemm<0>  up items (chunk, one or two slices of 64 intermediate elements): w1 | w3 units x the
-//                    chunk's token tiles; epilogue: limited SwiGLU, digit tiles of the hidden values per
-//                    (token, route) pair
+//                    chunk's token tiles; epilogue: limited SwiGLU, then either the digit tiles of the hidden
+//                    values per (token, route) pair (small blocks) or the hidden values themselves, whose
+//                    digit tiles a second k_block_digits launch over the pairs lays out (larger blocks)
 //   k_block_gemm<1>  down items (chunk, one or two tiles of 128 rows of w2) x the pairs' digit tiles -> the
 //                    pairs' expert outputs [pair, hidden] (expert parallel: into every rank's pair buffer)
 //   k_block_mix      per token the ordered mix: routes in order, shared expert last (expert parallel: after
@@ -34,7 +35,11 @@
 // tiles of every stage (cp.async, 16 bytes a thread; for small blocks a second copying thread brings them by
 // bulk copies).  What bounds the kernels is the number of bytes an SM takes in (45-50 GB/s per SM, whether
 // from memory or from the L2), so a large block takes TWO slices or row tiles per item: the token tiles of a
-// K range are fetched once for two units.  Every wait is bounded; a wait that runs out raises the CTA's abort
+// K range are fetched once for two units.  With the official expert arithmetic
+// (fast16/research/polaris_meridian_v1/s14_first_real_token/executor.py:712-743) the same contractions run on
+// quantised inputs: k_block_digits quantises per 128 elements to E4M3FN values (which the digit rows hold
+// exactly), the up epilogue works on BF16 gate and up and multiplies by the route weight, the down epilogue
+// and the mix round to BF16.  Every wait is bounded; a wait that runs out raises the CTA's abort
 // flag, the status word is set, and the CTA waits for its copies in flight, frees its tensor memory and returns.
 #include "s14_umma.cuh"
 
